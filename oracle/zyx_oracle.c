@@ -1,0 +1,498 @@
+/*
+ * zyx_oracle.c — TEST INFRASTRUCTURE ONLY.
+ *
+ * A CPU restatement, in plain C, of the arithmetic the reference zyx C/CPU backend
+ * performs for the row-reduce, matmul, elementwise and optimizer paths.  It is the
+ * checker that the parity tests, the smoke check and the bench's cpu_baseline leg compare
+ * the CUDA path against; nothing in the shipped library links or calls it.
+ *
+ * The reference is Rust and cannot be built here, but its CPU backend emits plain C
+ * (zyx/src/codegen/c.rs) compiled with
+ *   -O3 -ffast-math -fno-associative-math -fopenmp        (zyx/src/backend/c.rs:221-227)
+ * so this file restates the emitted arithmetic and is compiled with the same flags:
+ *   - bf16/f16 values live in `float` registers (codegen/c.rs:616-629), are widened on load
+ *     (138-140) and TRUNCATED on store: f32tobf16 = bits >> 16 (494-496), f32tof16
+ *     truncating with subnormals flushed (475-490);
+ *   - a reduce is a sequential accumulate over the reduced axis in index order
+ *     (zyx/src/kernel/linearize.rs:418-443, 920-950), accumulator f32 for floats and
+ *     i32/u32 for small integers (zyx/src/tensor/reduce_ops.rs:52-60);
+ *   - OpenMP parallelises the outermost index only (codegen/c.rs:89-91);
+ *   - rank-0 scalar operands are cast to the tensor's dtype (zyx/src/tensor/mod.rs:3033-3113),
+ *     for bf16 by truncation (zyx/src/scalar.rs:43-45).
+ * Where the reference's kernelizer is free to cut kernels in different places (a run-time
+ * cast to bf16 is a no-op until a store, codegen/c.rs:243-260), this oracle rounds exactly
+ * where the CUDA path writes a tensor to memory and nowhere else.
+ *
+ * Parity pins: tests/golden/reference_vectors.json holds the known-answer vectors of the
+ * reference's own tests for this path; tests/test_oracle_golden.py checks this file
+ * against every one of them.  Optimizer numerics, GELU values and the Linear::new stream
+ * have no reference test: for those the restatement is pinned by source citation only.
+ */
+#include <math.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+
+#define ZO_BF16 0
+#define ZO_F16 1
+#define ZO_F32 2
+#define ZO_I32 10
+
+/* ---------------------------------------------------------------------------------------
+ * Scalar conversions — zyx/src/codegen/c.rs:452-497, zyx/src/scalar.rs:13-235
+ * ------------------------------------------------------------------------------------- */
+static inline float zo_bf16tof32(uint16_t h) { uint32_t b = (uint32_t)h << 16; float r; memcpy(&r, &b, 4); return r; }
+static inline uint16_t zo_f32tobf16(float v) { uint32_t b; memcpy(&b, &v, 4); return (uint16_t)(b >> 16); }
+
+static inline float zo_f16tof32(uint16_t h) {
+  uint32_t sign = ((uint32_t)h & 0x8000u) << 16, exp = (h >> 10) & 0x1F, man = h & 0x3FF, f;
+  if (exp == 0) {
+    if (man == 0) f = sign;
+    else {
+      /* literal restatement of codegen/c.rs:461-466; for f16 SUBNORMAL inputs this yields a
+       * wrong exponent (the reference's own quirk).  Its f32tof16 flushes subnormals, so such
+       * values only arise from caller-supplied data; the parity tests do not feed them. */
+      int e = -1; uint32_t m = man;
+      while ((m & 0x400) == 0) { m <<= 1; e--; }
+      f = sign | ((uint32_t)(127 + e) << 23) | ((m & 0x3FF) << 13);
+    }
+  } else if (exp == 31) f = sign | 0x7F800000u | (man << 13);
+  else f = sign | ((exp + 112) << 23) | (man << 13);
+  float r; memcpy(&r, &f, 4); return r;
+}
+static inline uint16_t zo_f32tof16(float v) {
+  uint32_t f; memcpy(&f, &v, 4);
+  uint32_t sign = (f >> 16) & 0x8000, exp = (f >> 23) & 0xFF, man = f & 0x7FFFFF;
+  if (exp == 0) return (uint16_t)sign;
+  if (exp == 255) return (uint16_t)(sign | 0x7C00 | (man >> 13));
+  int ne = (int)exp - 127 + 15;
+  if (ne >= 31) return (uint16_t)(sign | 0x7C00);
+  if (ne <= 0) return (uint16_t)sign;
+  return (uint16_t)(sign | ((uint32_t)ne << 10) | (man >> 13));
+}
+
+static inline float zo_load(const void* p, int dtype, uint64_t i) {
+  switch (dtype) {
+    case ZO_BF16: return zo_bf16tof32(((const uint16_t*)p)[i]);
+    case ZO_F16: return zo_f16tof32(((const uint16_t*)p)[i]);
+    default: return ((const float*)p)[i];
+  }
+}
+static inline void zo_store(void* p, int dtype, uint64_t i, float v) {
+  switch (dtype) {
+    case ZO_BF16: ((uint16_t*)p)[i] = zo_f32tobf16(v); break;
+    case ZO_F16: ((uint16_t*)p)[i] = zo_f32tof16(v); break;
+    default: ((float*)p)[i] = v;
+  }
+}
+/* a rank-0 scalar cast to the tensor dtype */
+static inline float zo_const(int dtype, float v) {
+  switch (dtype) {
+    case ZO_BF16: return zo_bf16tof32(zo_f32tobf16(v));
+    case ZO_F16: return zo_f16tof32(zo_f32tof16(v));
+    default: return v;
+  }
+}
+float zo_const_cast(int dtype, float v) { return zo_const(dtype, v); }
+void zo_cast_from_f32(int dtype, const float* x, void* y, uint64_t n) { for (uint64_t i = 0; i < n; i++) zo_store(y, dtype, i, x[i]); }
+void zo_cast_to_f32(int dtype, const void* x, float* y, uint64_t n) { for (uint64_t i = 0; i < n; i++) y[i] = zo_load(x, dtype, i); }
+
+/* ---------------------------------------------------------------------------------------
+ * RNG — zyx/src/rng.rs:15-141 (xoshiro256++ seeded by splitmix64, LCG float),
+ *       Tensor::rand/randn/uniform — zyx/src/tensor/mod.rs:516-648.  Default seed 42069
+ *       (zyx/src/runtime.rs:178).
+ * ------------------------------------------------------------------------------------- */
+typedef struct { uint64_t s[4]; } zo_rng;
+
+void zo_rng_seed(zo_rng* r, uint64_t state) {
+  for (int i = 0; i < 4; i++) {
+    state += 0x9e3779b97f4a7c15ull;
+    uint64_t z = state;
+    z = (z ^ (z >> 30)) * 0xbf58476d1ce4e5b9ull;
+    z = (z ^ (z >> 27)) * 0x94d049bb133111ebull;
+    r->s[i] = z ^ (z >> 31);
+  }
+}
+static inline uint64_t zo_rotl(uint64_t x, int k) { return (x << k) | (x >> (64 - k)); }
+uint64_t zo_rng_next_u64(zo_rng* r) {
+  uint64_t res = zo_rotl(r->s[0] + r->s[3], 23) + r->s[0];
+  uint64_t t = r->s[1] << 17;
+  r->s[2] ^= r->s[0]; r->s[3] ^= r->s[1]; r->s[1] ^= r->s[2]; r->s[0] ^= r->s[3];
+  r->s[2] ^= t; r->s[3] = zo_rotl(r->s[3], 45);
+  return res;
+}
+float zo_rng_next_f32(zo_rng* r) {
+  uint32_t seed = (uint32_t)zo_rng_next_u64(r);                       /* low 4 bytes */
+  uint32_t next = (uint32_t)(1664525u * seed + 1013904223u) % 0xFFFFFFFFu;
+  return (float)next / (float)0xFFFFFFFFu;
+}
+void zo_rand_f32(zo_rng* r, float* out, uint64_t n) { for (uint64_t i = 0; i < n; i++) out[i] = zo_rng_next_f32(r); }
+/* (rand * (high - low) + low) — tensor/mod.rs:635-648 */
+void zo_uniform_f32(zo_rng* r, float* out, uint64_t n, float low, float high) {
+  float w = high - low;
+  for (uint64_t i = 0; i < n; i++) out[i] = zo_rng_next_f32(r) * w + low;
+}
+/* Box-Muller over rand([2, n]) — tensor/mod.rs:601-612 */
+void zo_randn_f32(zo_rng* r, float* out, uint64_t n) {
+  float* src = (float*)malloc(sizeof(float) * 2 * n);
+  zo_rand_f32(r, src, 2 * n);
+  const float two_pi = 2.0f * 3.14159265358979323846f;
+  for (uint64_t i = 0; i < n; i++) {
+    float x1 = cosf(src[i] * two_pi);
+    float x2 = sqrtf(logf(1.0f - src[n + i]) * -2.0f);
+    out[i] = x1 * x2;
+  }
+  free(src);
+}
+/* Linear::new — zyx-nn/src/linear.rs:19-36: weight [out,in] then bias [out], both
+ * U(-1/sqrt(in), 1/sqrt(in)), then cast to dtype (stored, hence truncated). */
+void zo_linear_init(zo_rng* r, int dtype, uint64_t in_f, uint64_t out_f, void* w, void* b) {
+  float l = -sqrtf(1.0f / (float)in_f), u = sqrtf(1.0f / (float)in_f);
+  float* tmp = (float*)malloc(sizeof(float) * in_f * out_f);
+  zo_uniform_f32(r, tmp, in_f * out_f, l, u);
+  zo_cast_from_f32(dtype, tmp, w, in_f * out_f);
+  if (b) { zo_uniform_f32(r, tmp, out_f, l, u); zo_cast_from_f32(dtype, tmp, b, out_f); }
+  free(tmp);
+}
+
+/* ---------------------------------------------------------------------------------------
+ * Elementwise formulas — zyx/src/tensor/elementwise.rs
+ * ------------------------------------------------------------------------------------- */
+/* tanh = (exp(x+x) - 1) / (exp(x+x) + 1)  — elementwise.rs:585-588 */
+static inline float zo_tanh_f(float x) { float e = expf(x + x); return (e - 1.0f) / (e + 1.0f); }
+/* relu = (x > 0) * x — elementwise.rs:289-293 */
+static inline float zo_relu_f(float x) { return (float)(x > 0.0f) * x; }
+/* gelu = x*0.5*(tanh((x + x*x*x*0.044715) * sqrt(2/pi)) + 1) — elementwise.rs:168-170;
+ * the three scalars are cast to the tensor dtype first. */
+static inline float zo_gelu_f(float x, float c_half, float c_a, float c_s) {
+  return x * c_half * (zo_tanh_f((x + x * x * x * c_a) * c_s) + 1.0f);
+}
+/* derivative of the formula above (product and chain rule, zyx/src/graph/autograd.rs:47-175) */
+static inline float zo_gelu_grad_f(float x, float c_half, float c_a, float c_s) {
+  float u = (x + x * x * x * c_a) * c_s;
+  float t = zo_tanh_f(u);
+  float du = (1.0f + 3.0f * c_a * x * x) * c_s;
+  return c_half * (t + 1.0f) + x * c_half * (1.0f - t * t) * du;
+}
+static inline float zo_sqrt_2_over_pi(void) { return sqrtf(2.0f / 3.14159265358979323846f); }
+
+enum { ZO_EW_RELU = 0, ZO_EW_GELU = 1, ZO_EW_ADD = 2, ZO_EW_SUB = 3, ZO_EW_MUL = 4, ZO_EW_SCALE = 5, ZO_EW_RELU_BWD = 6,
+       ZO_EW_GELU_BWD = 7, ZO_EW_MSE_BWD = 8, ZO_EW_CAST = 9, ZO_EW_TANH = 10, ZO_EW_SIGMOID = 11, ZO_EW_EXP = 12, ZO_EW_BIAS_ADD = 13 };
+
+void zo_eltwise(int op, int dtype, int dtype_out, const void* a, const void* b, void* y, uint64_t n, uint64_t cols, float p0) {
+  float ch = zo_const(dtype, 0.5f), ca = zo_const(dtype, 0.044715f), cs = zo_const(dtype, zo_sqrt_2_over_pi());
+  float cp = zo_const(dtype, p0);
+  int od = (op == ZO_EW_CAST) ? dtype_out : dtype;
+#pragma omp parallel for
+  for (uint64_t i = 0; i < n; i++) {
+    float x = zo_load(a, dtype, i), r;
+    switch (op) {
+      case ZO_EW_RELU: r = zo_relu_f(x); break;
+      case ZO_EW_GELU: r = zo_gelu_f(x, ch, ca, cs); break;
+      case ZO_EW_ADD: r = x + zo_load(b, dtype, i); break;
+      case ZO_EW_SUB: r = x - zo_load(b, dtype, i); break;
+      case ZO_EW_MUL: r = x * zo_load(b, dtype, i); break;
+      case ZO_EW_SCALE: r = x * cp; break;
+      case ZO_EW_RELU_BWD: r = x * (float)(zo_load(b, dtype, i) > 0.0f); break;
+      case ZO_EW_GELU_BWD: r = x * zo_gelu_grad_f(zo_load(b, dtype, i), ch, ca, cs); break;
+      case ZO_EW_MSE_BWD: r = (x - zo_load(b, dtype, i)) * 2.0f * p0; break;
+      case ZO_EW_TANH: r = zo_tanh_f(x); break;
+      case ZO_EW_SIGMOID: { float e = expf(x); r = e / (e + 1.0f); } break;   /* elementwise.rs:457-460 */
+      case ZO_EW_EXP: r = expf(x); break;
+      case ZO_EW_BIAS_ADD: r = x + zo_load(b, dtype, i % cols); break;
+      default: r = x;
+    }
+    zo_store(y, od, i, r);
+  }
+}
+
+/* ---------------------------------------------------------------------------------------
+ * Row reductions — Tensor::reduce_impl (zyx/src/tensor/reduce_ops.rs:45-157): Sum/Max in
+ * the accumulator dtype, Mean = sum / n, Var = sum((x-mean)^2) / (n - correction),
+ * Min = -max(-x); sequential accumulate (linearize.rs:920-950), accumulator initialised
+ * 0 / -inf.
+ * ------------------------------------------------------------------------------------- */
+enum { ZO_RR_SUM = 0, ZO_RR_MAX = 1, ZO_RR_MIN = 2, ZO_RR_MEAN = 3, ZO_RR_VAR = 4, ZO_RR_STD = 5 };
+
+static float zo_row_sum(const void* x, int dtype, uint64_t base, uint64_t cols) {
+  float acc = 0.0f;
+  for (uint64_t j = 0; j < cols; j++) acc = zo_load(x, dtype, base + j) + acc;
+  return acc;
+}
+static float zo_row_max(const void* x, int dtype, uint64_t base, uint64_t cols, float sign) {
+  float acc = -INFINITY;
+  for (uint64_t j = 0; j < cols; j++) acc = fmaxf(sign * zo_load(x, dtype, base + j), acc);
+  return acc;
+}
+
+void zo_row_reduce(int op, int dtype, const void* x, void* y, uint64_t rows, uint64_t cols, int correction) {
+#pragma omp parallel for
+  for (uint64_t r = 0; r < rows; r++) {
+    uint64_t base = r * cols; float out;
+    switch (op) {
+      case ZO_RR_SUM: out = zo_row_sum(x, dtype, base, cols); break;
+      case ZO_RR_MAX: out = zo_row_max(x, dtype, base, cols, 1.0f); break;
+      case ZO_RR_MIN: out = -zo_row_max(x, dtype, base, cols, -1.0f); break;
+      case ZO_RR_MEAN: out = zo_row_sum(x, dtype, base, cols) / zo_const(dtype, (float)cols); break;
+      default: {
+        float mean = zo_row_sum(x, dtype, base, cols) / zo_const(dtype, (float)cols);
+        float acc = 0.0f;
+        for (uint64_t j = 0; j < cols; j++) { float d = zo_load(x, dtype, base + j) - mean; acc = d * d + acc; }
+        out = acc / zo_const(dtype, (float)((int64_t)cols - correction));
+        if (op == ZO_RR_STD) out = sqrtf(out);
+      }
+    }
+    zo_store(y, dtype, r, out);
+  }
+}
+
+/* integer reductions are exact: i32 accumulator (reduce_ops.rs:52-60) */
+void zo_row_reduce_i32(int op, const int32_t* x, int32_t* y, uint64_t rows, uint64_t cols) {
+#pragma omp parallel for
+  for (uint64_t r = 0; r < rows; r++) {
+    const int32_t* p = x + r * cols;
+    if (op == ZO_RR_SUM) { int32_t a = 0; for (uint64_t j = 0; j < cols; j++) a = (int32_t)((uint32_t)p[j] + (uint32_t)a); y[r] = a; }
+    else if (op == ZO_RR_MAX) { int32_t a = INT32_MIN; for (uint64_t j = 0; j < cols; j++) a = p[j] > a ? p[j] : a; y[r] = a; }
+    else { int32_t a = INT32_MAX; for (uint64_t j = 0; j < cols; j++) a = p[j] < a ? p[j] : a; y[r] = a; }
+  }
+}
+
+/* softmax: e = exp(x - max_kd(x)); e / sum_kd(e) — zyx/src/tensor/mod.rs:1457-1461.
+ * `scale` multiplies x first and `causal` masks column j > r % period with -inf, which is
+ * what MultiheadAttention::forward intends (zyx-nn/src/multi_head_attention.rs:198-219). */
+void zo_softmax(int dtype, const void* x, void* y, uint64_t rows, uint64_t cols, float scale, int causal, uint64_t period) {
+  if (scale == 0.0f) scale = 1.0f;
+  float cscale = zo_const(dtype, scale);
+#pragma omp parallel for
+  for (uint64_t r = 0; r < rows; r++) {
+    uint64_t base = r * cols;
+    uint64_t lim = causal ? (r % period) + 1 : cols; if (lim > cols) lim = cols;
+    float m = -INFINITY;
+    for (uint64_t j = 0; j < lim; j++) { float v = zo_load(x, dtype, base + j); if (scale != 1.0f) v = v * cscale; m = fmaxf(v, m); }
+    float s = 0.0f;
+    for (uint64_t j = 0; j < lim; j++) { float v = zo_load(x, dtype, base + j); if (scale != 1.0f) v = v * cscale; s = expf(v - m) + s; }
+    for (uint64_t j = 0; j < cols; j++) {
+      float v = zo_load(x, dtype, base + j); if (scale != 1.0f) v = v * cscale;
+      zo_store(y, dtype, base + j, j < lim ? expf(v - m) / s : 0.0f);
+    }
+  }
+}
+
+/* ln_softmax: m = x - max_kd(x); m - ln(sum_kd(exp(m))) — tensor/mod.rs:1427-1431 */
+void zo_ln_softmax(int dtype, const void* x, void* y, uint64_t rows, uint64_t cols) {
+#pragma omp parallel for
+  for (uint64_t r = 0; r < rows; r++) {
+    uint64_t base = r * cols;
+    float mx = zo_row_max(x, dtype, base, cols, 1.0f), s = 0.0f;
+    for (uint64_t j = 0; j < cols; j++) s = expf(zo_load(x, dtype, base + j) - mx) + s;
+    float ls = logf(s);
+    for (uint64_t j = 0; j < cols; j++) zo_store(y, dtype, base + j, (zo_load(x, dtype, base + j) - mx) - ls);
+  }
+}
+
+/* LayerNorm::forward — zyx-nn/src/layer_norm.rs:95-135:
+ * (x - mean_kd) / sqrt(var_kd + eps) [* weight] [+ bias]; var is UNBIASED (correction 1,
+ * reduce_ops.rs:113-125, var_keepdim 803-805); eps is cast to x's dtype. */
+void zo_layernorm(int dtype, const void* x, const void* w, const void* b, void* y, uint64_t rows, uint64_t cols, float eps) {
+  float ceps = zo_const(dtype, eps), cn = zo_const(dtype, (float)cols), cd = zo_const(dtype, (float)((int64_t)cols - 1));
+#pragma omp parallel for
+  for (uint64_t r = 0; r < rows; r++) {
+    uint64_t base = r * cols;
+    float mean = zo_row_sum(x, dtype, base, cols) / cn, acc = 0.0f;
+    for (uint64_t j = 0; j < cols; j++) { float d = zo_load(x, dtype, base + j) - mean; acc = d * d + acc; }
+    float denom = sqrtf(acc / cd + ceps);
+    for (uint64_t j = 0; j < cols; j++) {
+      float v = (zo_load(x, dtype, base + j) - mean) / denom;
+      if (w) v = v * zo_load(w, dtype, j);
+      if (b) v = v + zo_load(b, dtype, j);
+      zo_store(y, dtype, base + j, v);
+    }
+  }
+}
+
+/* layernorm backward for dx (standard adjoint of the forward above, unbiased variance):
+ * xhat = (x-mean)/s, s = sqrt(var+eps), g = dy*w;
+ * dx = ( g - mean(g) - (x-mean) * sum(g*(x-mean)) / ((n-1) * s^2) ) / s */
+void zo_layernorm_bwd(int dtype, const void* x, const void* dy, const void* w, void* dx, uint64_t rows, uint64_t cols, float eps) {
+  float ceps = zo_const(dtype, eps);
+#pragma omp parallel for
+  for (uint64_t r = 0; r < rows; r++) {
+    uint64_t base = r * cols;
+    float n = (float)cols;
+    float mean = zo_row_sum(x, dtype, base, cols) / n, acc = 0.0f;
+    for (uint64_t j = 0; j < cols; j++) { float d = zo_load(x, dtype, base + j) - mean; acc = d * d + acc; }
+    float s2 = acc / (n - 1.0f) + ceps, s = sqrtf(s2);
+    float sg = 0.0f, sgd = 0.0f;
+    for (uint64_t j = 0; j < cols; j++) {
+      float g = zo_load(dy, dtype, base + j); if (w) g = g * zo_load(w, dtype, j);
+      float d = zo_load(x, dtype, base + j) - mean;
+      sg = g + sg; sgd = g * d + sgd;
+    }
+    for (uint64_t j = 0; j < cols; j++) {
+      float g = zo_load(dy, dtype, base + j); if (w) g = g * zo_load(w, dtype, j);
+      float d = zo_load(x, dtype, base + j) - mean;
+      zo_store(dx, dtype, base + j, (g - sg / n - d * sgd / ((n - 1.0f) * s2)) / s);
+    }
+  }
+}
+
+/* softmax backward: ds = p * (dp - sum(dp * p)) */
+void zo_softmax_bwd(int dtype, const void* p, const void* dp, void* ds, uint64_t rows, uint64_t cols) {
+#pragma omp parallel for
+  for (uint64_t r = 0; r < rows; r++) {
+    uint64_t base = r * cols; float acc = 0.0f;
+    for (uint64_t j = 0; j < cols; j++) acc = zo_load(p, dtype, base + j) * zo_load(dp, dtype, base + j) + acc;
+    for (uint64_t j = 0; j < cols; j++) zo_store(ds, dtype, base + j, zo_load(p, dtype, base + j) * (zo_load(dp, dtype, base + j) - acc));
+  }
+}
+
+/* cross_entropy with class-index targets — tensor/mod.rs:1639-1655: one-hot by
+ * equal(arange) (1920-1948), per_sample = sum(-ln_softmax * onehot, 1), Mean = mean_all. */
+void zo_cross_entropy(const float* logits, const int32_t* labels, float* per_sample, float* mean, uint64_t rows, uint64_t classes) {
+  for (uint64_t r = 0; r < rows; r++) {
+    const float* x = logits + r * classes;
+    float mx = -INFINITY, s = 0.0f, acc = 0.0f;
+    for (uint64_t j = 0; j < classes; j++) mx = fmaxf(x[j], mx);
+    for (uint64_t j = 0; j < classes; j++) s = expf(x[j] - mx) + s;
+    float ls = logf(s);
+    for (uint64_t j = 0; j < classes; j++) acc = (-((x[j] - mx) - ls)) * (float)(labels[r] == (int32_t)j) + acc;
+    per_sample[r] = acc;
+  }
+  float t = 0.0f;
+  for (uint64_t r = 0; r < rows; r++) t = per_sample[r] + t;
+  *mean = t / (float)rows;
+}
+/* d mean-CE / d logits = (softmax - onehot) / rows */
+void zo_cross_entropy_bwd(const float* logits, const int32_t* labels, float* dlogits, uint64_t rows, uint64_t classes) {
+  for (uint64_t r = 0; r < rows; r++) {
+    const float* x = logits + r * classes;
+    float mx = -INFINITY, s = 0.0f;
+    for (uint64_t j = 0; j < classes; j++) mx = fmaxf(x[j], mx);
+    for (uint64_t j = 0; j < classes; j++) s = expf(x[j] - mx) + s;
+    for (uint64_t j = 0; j < classes; j++) dlogits[r * classes + j] = (expf(x[j] - mx) / s - (float)(labels[r] == (int32_t)j)) / (float)rows;
+  }
+}
+/* column sums (sum over rows) — the bias gradient */
+void zo_colsum(int dtype, const void* x, void* y, uint64_t rows, uint64_t cols) {
+#pragma omp parallel for
+  for (uint64_t j = 0; j < cols; j++) {
+    float acc = 0.0f;
+    for (uint64_t r = 0; r < rows; r++) acc = zo_load(x, dtype, r * cols + j) + acc;
+    zo_store(y, dtype, j, acc);
+  }
+}
+/* mse = mean((y - t)^2) over all elements; accumulated in f32, returned as f32 */
+float zo_mse(int dtype, const void* y, const void* t, uint64_t n) {
+  double acc = 0.0;
+  for (uint64_t i = 0; i < n; i++) { float d = zo_load(y, dtype, i) - zo_load(t, dtype, i); acc += (double)(d * d); }
+  return (float)(acc / (double)n);
+}
+
+/* ---------------------------------------------------------------------------------------
+ * Matmul — Tensor::dot (zyx/src/tensor/mod.rs:1469-1490): elementwise product in the input
+ * dtype (exact in f32 registers for bf16/f16), then sum over k with an f32 accumulator
+ * (reduce_ops.rs:52-60) in index order, result stored in the input dtype.  Linear adds the
+ * bias afterwards (zyx-nn/src/linear.rs:39-45).
+ *   C[b] = epi(alpha * op(A[b]) . op(B[b]) + bias);   ta: A stored [k,m];  tb: B stored [n,k]
+ * ------------------------------------------------------------------------------------- */
+enum { ZO_EPI_NONE = 0, ZO_EPI_BIAS = 1, ZO_EPI_BIAS_RELU = 2, ZO_EPI_BIAS_GELU = 3 };
+
+void zo_gemm(int dtype, int ta, int tb, uint64_t m, uint64_t n, uint64_t k, uint64_t batch, const void* a, const void* b,
+             const void* bias, void* c, void* preact, int64_t sa, int64_t sb, int64_t sc, int epi, float alpha) {
+  if (alpha == 0.0f) alpha = 1.0f;
+  float ch = zo_const(dtype, 0.5f), ca = zo_const(dtype, 0.044715f), cs = zo_const(dtype, zo_sqrt_2_over_pi());
+  float calpha = zo_const(dtype, alpha);
+  for (uint64_t bb = 0; bb < batch; bb++) {
+    uint64_t oa = bb * (uint64_t)sa, ob = bb * (uint64_t)sb, oc = bb * (uint64_t)sc;
+#pragma omp parallel for
+    for (uint64_t i = 0; i < m; i++) {
+      float* arow = (float*)malloc(sizeof(float) * k);
+      for (uint64_t kk = 0; kk < k; kk++) arow[kk] = zo_load(a, dtype, oa + (ta ? kk * m + i : i * k + kk));
+      for (uint64_t j = 0; j < n; j++) {
+        float acc = 0.0f;
+        if (tb) for (uint64_t kk = 0; kk < k; kk++) acc = arow[kk] * zo_load(b, dtype, ob + j * k + kk) + acc;
+        else for (uint64_t kk = 0; kk < k; kk++) acc = arow[kk] * zo_load(b, dtype, ob + kk * n + j) + acc;
+        if (alpha != 1.0f) acc = acc * calpha;
+        if (epi != ZO_EPI_NONE) acc = acc + zo_load(bias, dtype, j);
+        if (preact) zo_store(preact, dtype, oc + i * n + j, acc);
+        if (epi == ZO_EPI_BIAS_RELU) acc = zo_relu_f(acc);
+        else if (epi == ZO_EPI_BIAS_GELU) acc = zo_gelu_f(acc, ch, ca, cs);
+        zo_store(c, dtype, oc + i * n + j, acc);
+      }
+      free(arow);
+    }
+  }
+}
+
+/* integer matmul is exact (zyx/tests/05_misc.rs:210-237): i32 accumulator, wrapping */
+void zo_gemm_i32(int ta, int tb, uint64_t m, uint64_t n, uint64_t k, uint64_t batch, const int32_t* a, const int32_t* b, int32_t* c) {
+  for (uint64_t bb = 0; bb < batch; bb++) {
+    const int32_t *A = a + bb * m * k, *B = b + bb * k * n; int32_t* C = c + bb * m * n;
+#pragma omp parallel for
+    for (uint64_t i = 0; i < m; i++)
+      for (uint64_t j = 0; j < n; j++) {
+        uint32_t acc = 0;
+        for (uint64_t kk = 0; kk < k; kk++) {
+          uint32_t x = (uint32_t)(ta ? A[kk * m + i] : A[i * k + kk]);
+          uint32_t y = (uint32_t)(tb ? B[j * k + kk] : B[kk * n + j]);
+          acc += x * y;
+        }
+        C[i * n + j] = (int32_t)acc;
+      }
+  }
+}
+
+/* ---------------------------------------------------------------------------------------
+ * Optimizers — zyx-optim/src/{sgd,adam,adamw}.rs.  Every hyper-parameter enters as a
+ * rank-0 scalar and is therefore cast to the tensor dtype (truncated for bf16).  State
+ * tensors (momentum buffer, m, v) are stored, hence truncated, and the stored value is what
+ * the rest of the step reads.
+ * ------------------------------------------------------------------------------------- */
+/* SGD::update — sgd.rs:45-84.  `first` = the momentum buffer does not exist yet. */
+void zo_sgd(int dtype, void* p, const void* g, void* buf, uint64_t n, float lr, float wd, float momentum, float dampening,
+            int nesterov, int maximize, int first, float grad_scale) {
+  float clr = zo_const(dtype, lr), cwd = zo_const(dtype, wd), cmu = zo_const(dtype, momentum), cd = zo_const(dtype, 1.0f - dampening);
+  if (grad_scale == 0.0f) grad_scale = 1.0f;
+#pragma omp parallel for
+  for (uint64_t i = 0; i < n; i++) {
+    float pv = zo_load(p, dtype, i), gv = zo_load(g, dtype, i);
+    if (grad_scale != 1.0f) gv = gv * grad_scale;
+    if (wd != 0.0f) gv = gv + pv * cwd;
+    if (momentum != 0.0f) {
+      float bv = first ? gv : zo_load(buf, dtype, i) * cmu + gv * cd;
+      zo_store(buf, dtype, i, bv); bv = zo_load(buf, dtype, i);
+      gv = nesterov ? gv + bv * cmu : bv;
+    }
+    zo_store(p, dtype, i, maximize ? pv + gv * clr : pv - gv * clr);
+  }
+}
+
+/* Adam::update (adam.rs:51-98) and AdamW::update (adamw.rs:51-97); t is the step number
+ * AFTER the increment (1 on the first call).  adamw: 0 = Adam (L2 into the gradient,
+ * p - lr*mh/(sqrt(vh)+eps)), 1 = AdamW as written (p - mh/((sqrt(vh)+eps)*lr), then
+ * p*(1-lr*wd)), 2 = textbook AdamW (p - lr*mh/(sqrt(vh)+eps), then p*(1-lr*wd)). */
+void zo_adam(int dtype, void* p, const void* g, void* m, void* v, uint64_t n, float lr, float wd, float beta1, float beta2,
+             float eps, uint64_t t, int adamw, float grad_scale) {
+  float cb1 = zo_const(dtype, beta1), cb2 = zo_const(dtype, beta2);
+  float c1mb1 = zo_const(dtype, 1.0f - beta1), c1mb2 = zo_const(dtype, 1.0f - beta2);
+  float cbc1 = zo_const(dtype, 1.0f - powf(beta1, (float)t)), cbc2 = zo_const(dtype, 1.0f - powf(beta2, (float)t));
+  float clr = zo_const(dtype, lr), ceps = zo_const(dtype, eps), cwd = zo_const(dtype, wd);
+  float cdecay = zo_const(dtype, 1.0f - lr * wd);
+  int first = (t == 1);
+  if (grad_scale == 0.0f) grad_scale = 1.0f;
+#pragma omp parallel for
+  for (uint64_t i = 0; i < n; i++) {
+    float pv = zo_load(p, dtype, i), gv = zo_load(g, dtype, i);
+    if (grad_scale != 1.0f) gv = gv * grad_scale;
+    if (adamw == 0 && wd != 0.0f) gv = gv + pv * cwd;
+    float mv = first ? gv * c1mb1 : zo_load(m, dtype, i) * cb1 + gv * c1mb1;
+    float vv = first ? gv * gv * c1mb2 : zo_load(v, dtype, i) * cb2 + gv * gv * c1mb2;
+    zo_store(m, dtype, i, mv); mv = zo_load(m, dtype, i);
+    zo_store(v, dtype, i, vv); vv = zo_load(v, dtype, i);
+    float mh = mv / cbc1, vh = vv / cbc2, np;
+    if (adamw == 1) np = pv - mh / ((sqrtf(vh) + ceps) * clr);
+    else np = pv - clr * mh / (sqrtf(vh) + ceps);
+    if (adamw != 0 && wd != 0.0f) np = np * cdecay;
+    zo_store(p, dtype, i, np);
+  }
+}

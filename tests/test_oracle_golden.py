@@ -1,0 +1,163 @@
+"""Pins the CPU oracle to the reference's own known-answer tests (tests/golden)."""
+import numpy as np
+
+from oracle import oracle as zo
+from tests.parity import ref_is_equal
+
+
+def f32(x):
+    return np.asarray(x, np.float32)
+
+
+def test_softmax(golden):
+    for case in golden["softmax"]:
+        y = zo.softmax(zo.F32, f32(case["x"]))
+        assert ref_is_equal(y, f32(case["y"])), case["src"]
+
+
+def test_layernorm(golden):
+    for case in golden["layernorm"]:
+        y = zo.layernorm(zo.F32, f32(case["x"]), w=f32(case["weight"]), eps=case["eps"])
+        assert ref_is_equal(y, f32(case["y"])), case["src"]
+
+
+def test_cross_entropy(golden):
+    for case in golden["cross_entropy"]:
+        logits, labels = f32(case["logits"]), np.asarray(case["labels"], np.int32)
+        want = f32(case["neg_ln_softmax_times_onehot"])
+        ls = zo.ln_softmax(zo.F32, logits)
+        onehot = (labels[:, None] == np.arange(logits.shape[1])[None, :]).astype(np.float32)
+        assert ref_is_equal(-ls * onehot, want), case["src"]
+        per, mean = zo.cross_entropy(logits, labels)
+        assert ref_is_equal(per, want.sum(1)), case["src"]
+        assert ref_is_equal(mean, [want.sum() / len(labels)])
+
+
+def test_reduce_f32(golden):
+    ops = {"sum": zo.RR_SUM, "max": zo.RR_MAX, "mean": zo.RR_MEAN, "var": zo.RR_VAR}
+    for case in golden["reduce_f32"]:
+        y = zo.row_reduce(ops[case["op"]], zo.F32, f32(case["x"]), correction=case["correction"])
+        assert ref_is_equal(y, f32(case["y"])), case["src"]
+
+
+def _int_input(case):
+    rows, cols = case["rows"], case["cols"]
+    if "x_fill" in case:
+        return np.full((rows, cols), case["x_fill"], np.int32)
+    return (np.arange(rows * cols, dtype=np.int32) + case["x_arange_from"]).reshape(rows, cols)
+
+
+def test_reduce_i32(golden):
+    ops = {"sum": zo.RR_SUM, "max": zo.RR_MAX}
+    for case in golden["reduce_i32"]:
+        y = zo.row_reduce(ops[case["op"]], zo.I32, _int_input(case))
+        assert y.tolist() == case["y"], case["src"]
+
+
+def test_matmul_small(golden):
+    for case in golden["matmul_i32"]:
+        c = zo.gemm(zo.I32, np.asarray(case["a"], np.int32), np.asarray(case["b"], np.int32))
+        assert c.tolist() == case["c"], case["src"]
+    for case in golden["matmul_f32"]:
+        c = zo.gemm(zo.F32, f32(case["a"]), f32(case["b"]))
+        assert ref_is_equal(c, f32(case["c"])), case["src"]
+
+
+def test_matmul_i32_procedural(golden):
+    g = golden["matmul_i32_procedural"]
+    for m in g["m"]:
+        for k in g["k"]:
+            for n in g["n"]:
+                x = (np.arange(m)[:, None] + np.arange(k)[None, :]).astype(np.int32)
+                y = (np.arange(k)[:, None] - np.arange(n)[None, :]).astype(np.int32)
+                want = (x.astype(np.int64) @ y.astype(np.int64)).astype(np.int32)
+                assert np.array_equal(zo.gemm(zo.I32, x, y), want), (m, k, n)
+
+
+def test_batched_matmul_i32_procedural(golden):
+    g = golden["batched_matmul_i32_procedural"]
+    for b in g["b"]:
+        for m in g["m"]:
+            for k in g["k"]:
+                for n in g["n"]:
+                    bb = np.arange(b)[:, None, None]
+                    x = (bb + np.arange(m)[None, :, None] + np.arange(k)[None, None, :]).astype(np.int32)
+                    y = (bb + np.arange(k)[None, :, None] - np.arange(n)[None, None, :]).astype(np.int32)
+                    want = np.einsum("bmk,bkn->bmn", x.astype(np.int64), y.astype(np.int64)).astype(np.int32)
+                    assert np.array_equal(zo.gemm(zo.I32, x, y), want), (b, m, k, n)
+
+
+def test_bf16_matmul_procedural(golden):
+    g = golden["bf16_matmul_procedural"]
+    m, k, n = g["m"], g["k"], g["n"]
+    xf = np.fmod(np.arange(m)[:, None] + np.arange(k)[None, :], 10).astype(np.float32)
+    yf = np.fmod((np.arange(k)[:, None] - np.arange(n)[None, :]).astype(np.float32), 10).astype(np.float32)
+    x, y = zo.to_bits(xf, zo.BF16), zo.to_bits(yf, zo.BF16)
+    # expected as the reference test builds it: running sum rounded to bf16 after every add
+    want = np.zeros((m, n), np.float32)
+    for kk in range(k):
+        want = zo.to_f32(zo.to_bits(want + xf[:, kk:kk + 1] * yf[kk:kk + 1, :], zo.BF16), zo.BF16)
+    got = zo.to_f32(zo.gemm(zo.BF16, x, y), zo.BF16)
+    assert ref_is_equal(got, want, rel=0.01, abs_tol=0.001)
+
+
+def test_relu(golden):
+    for case in golden["relu"]:
+        y = zo.eltwise(zo.EW_RELU, zo.F32, f32(case["x"]))
+        assert ref_is_equal(y, f32(case["y"])), case["src"]
+
+
+def test_mlp_fwd_bwd_known_answer(golden):
+    """2-layer ReLU MLP forward + backward built from oracle pieces, exact in f32 (small ints)."""
+    g = golden["mlp_fwd_bwd_i32"]
+    x, y = f32([g["x"]]), f32([g["y"]])
+    w1, b1, w2, b2 = f32(g["w1"]), f32(g["b1"]), f32(g["w2"]), f32(g["b2"])
+    h, z1 = zo.gemm(zo.F32, x, w1, bias=b1, epi=zo.EPI_BIAS_RELU, want_preact=True)
+    o = zo.gemm(zo.F32, h, w2, bias=b2, epi=zo.EPI_BIAS)
+    do = zo.eltwise(zo.EW_MSE_BWD, zo.F32, o, y, p0=1.0)          # d sum((o-y)^2) = 2 (o-y)
+    dw2 = zo.gemm(zo.F32, h, do, ta=True)
+    db2 = zo.colsum(zo.F32, do)
+    dh = zo.gemm(zo.F32, do, w2, tb=True)
+    dz1 = zo.eltwise(zo.EW_RELU_BWD, zo.F32, dh, z1)
+    dw1 = zo.gemm(zo.F32, x, dz1, ta=True)
+    db1 = zo.colsum(zo.F32, dz1)
+    assert dw1.astype(np.int64).tolist() == g["w1_grad"]
+    assert db1.astype(np.int64).tolist() == g["b1_grad"]
+    assert dw2.astype(np.int64).tolist() == g["w2_grad"]
+    assert db2.astype(np.int64).tolist() == g["b2_grad"]
+
+
+def test_self_attention_known_answer(golden):
+    g = golden["self_attention_f32"]
+    w = f32(g["c_attn_weight_before_t"])          # [4, 12]; the test multiplies x by this matrix
+    x = f32(g["x"])                                # [T=4, C=4]
+    qkv = zo.gemm(zo.F32, x, w)                    # [4, 12]
+    q, k, v = qkv[:, 0:4], qkv[:, 4:8], qkv[:, 8:12]
+    # 4 heads of width 1: per head h, q/k/v are [T,1]
+    out = np.zeros((4, 4), np.float32)
+    for h in range(4):
+        qh, kh, vh = (np.ascontiguousarray(t[:, h:h + 1]) for t in (q, k, v))
+        att = zo.gemm(zo.F32, qh, kh, tb=True, alpha=1.0)
+        att = zo.softmax(zo.F32, att)
+        out[:, h:h + 1] = zo.gemm(zo.F32, att, vh)
+    assert ref_is_equal(out, f32(g["y"]))
+
+
+def test_rng_is_deterministic_and_in_range():
+    r1, r2 = zo.Rng(42069), zo.Rng(42069)
+    a, b = r1.rand(1000), r2.rand(1000)
+    assert np.array_equal(a, b) and a.min() >= 0.0 and a.max() <= 1.0
+    # splitmix64 seeding of xoshiro256++ (zyx/src/rng.rs:15-57): published first outputs of
+    # splitmix64 for state 0 are the xoshiro state words for seed 0
+    r0 = zo.Rng(0)
+    assert [int(v) for v in r0.state] == [0xe220a8397b1dcdaf, 0x6e789e6aa1b965f4, 0x06c45d188009454f, 0xf88bb8a8724c81ec]
+    n = zo.Rng(1).randn(20000)
+    assert abs(float(n.mean())) < 0.05 and abs(float(n.std()) - 1.0) < 0.05
+
+
+def test_bf16_store_truncates():
+    x = f32([1.0, 1.00390625, 1.0078124, 0.9, 0.999, 1e-3, 0.99999])
+    got = zo.to_f32(zo.to_bits(x, zo.BF16), zo.BF16)
+    # bf16::from_f32 = bits >> 16 (zyx/src/scalar.rs:43-45): 0.9 -> 0.8984375, 0.999 -> 0.99609375
+    assert got.tolist()[:5] == [1.0, 1.0, 1.0, 0.8984375, 0.99609375]
+    assert got[6] == 0.99609375
