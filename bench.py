@@ -1,0 +1,314 @@
+#!/usr/bin/env python
+"""Benchmark of the zyx_b200 hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference]
+
+Prints ONE JSON line.  Workloads (synthetic, seeded, shapes of the reference's configurations):
+  rowreduce   row softmax + row layernorm on f32 [8192, 32768]         (fused-reduce GB/s)
+  gemm_bf16   C = A.B, M=N=K=8192 bf16, f32 accumulate                  (GEMM TFLOP/s)
+  gemm_f32    C = A.B, M=N=K=4096 f32                                   (GEMM TFLOP/s)
+Under torchrun every rank drives its own GPU through its own libzyxb context.
+`--impl reference` times the CPU oracle (the restatement of the reference's C backend; the
+reference itself is Rust and cannot be built here) on the host cores instead.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+
+def load_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            d = json.load(f)
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"], "bf16_tflops_sustained": d["bf16_tflops_sustained"],
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+# ---- clocks ----------------------------------------------------------------------------------------
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons of one GPU every 200 ms (read-only)."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.rows, self.proc, self.thread, self.gpu = [], None, None, gpu_index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.gpu), "--query-gpu=" + self.Q, "--format=csv,noheader,nounits",
+                                          "-lms", "200"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        time.sleep(0.25)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for r in self.rows:
+            if len(r) < 7:
+                continue
+            try:
+                sm.append(float(r[0])); mx.append(float(r[1]))
+            except ValueError:
+                continue
+            for name, v in zip(["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"], r[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# ---- workloads ---------------------------------------------------------------------------------------
+class RowReduce:
+    """Row softmax and row layernorm (gamma=1, beta=0, eps=1e-5, unbiased variance) on f32 [8192, 32768], N(0,1) seeded."""
+    name = "rowreduce_softmax_layernorm_f32_8192x32768"
+    metric, unit, dtype, bound = "fused-reduce GB/s (row softmax + row layernorm)", "GB/s", "f32", "hbm"
+    rows, cols = 8192, 32768
+
+    def __init__(self, rows=None):
+        if rows:
+            self.rows = rows
+        self.alg_bytes_softmax = self.rows * self.cols * 8                       # read once + write once
+        self.alg_bytes_layernorm = self.rows * self.cols * 8 + 2 * self.cols * 4
+        self.units_per_step = (self.alg_bytes_softmax + self.alg_bytes_layernorm) / 1e9   # GB of algorithmic traffic
+        self.h2d_bytes = self.rows * self.cols * 4
+        self.d2h_bytes = 2 * self.rows * self.cols * 4
+
+    def host_inputs(self, seed=1):
+        rng = np.random.default_rng(seed)
+        self.x = rng.standard_normal((self.rows, self.cols), dtype=np.float32)
+        self.gamma, self.beta = np.ones(self.cols, np.float32), np.zeros(self.cols, np.float32)
+
+    def setup(self, sess):
+        from zyx_b200 import _lib as L, backend as B
+        self.sess, self.L = sess, L
+        self.host_inputs()
+        p, d = sess.pool, sess.device
+        self.bx, self.bg, self.bb = p.upload(self.x), p.upload(self.gamma), p.upload(self.beta)
+        self.by1, _ = p.allocate(self.x.nbytes)
+        self.by2, _ = p.allocate(self.x.nbytes)
+        self.p_sm = d.create_program(B.rowreduce_desc(L.RR_SOFTMAX, L.F32, self.rows, self.cols))
+        self.p_ln = d.create_program(B.rowreduce_desc(L.RR_LAYERNORM, L.F32, self.rows, self.cols, eps=1e-5, has_weight=True, has_bias=True))
+        self.config = {"workload": self.name, "l2": "inputs (1 GiB) larger than L2 (126 MB)", "ops": "softmax, layernorm"}
+        self.kernel_events = []
+
+    def step(self, timed=False):
+        d = self.sess.device
+        if timed:
+            e0 = d.event_record()
+        d.launch(self.p_sm, [self.bx, self.by1])
+        if timed:
+            e1 = d.event_record()
+        d.launch(self.p_ln, [self.bx, self.bg, self.bb, self.by2])
+        if timed:
+            e2 = d.event_record()
+            self.kernel_events.append((e0, e1, e2))
+
+    def roofline(self, peaks):
+        d = self.sess.device
+        sm = [d.elapsed_ms(a, b) for a, b, _ in self.kernel_events]
+        ln = [d.elapsed_ms(b, c) for _, b, c in self.kernel_events]
+        t_sm, t_ln = float(np.mean(sm)), float(np.mean(ln))
+        ach = self.alg_bytes_softmax / (t_sm * 1e-3) / 1e9
+        ach_ln = self.alg_bytes_layernorm / (t_ln * 1e-3) / 1e9
+        return ({"bound": "hbm", "kernel": "row_kernel<f32, softmax>", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                 "frac": ach / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"], "ms_per_launch": t_sm},
+                {"softmax": {"ms": t_sm, "GB/s": ach, "frac": ach / peaks["hbm_gbs"]},
+                 "layernorm": {"ms": t_ln, "GB/s": ach_ln, "frac": ach_ln / peaks["hbm_gbs"]}})
+
+    def e2e_setup(self):
+        self.hy1, self.hy2 = np.empty_like(self.x), np.empty_like(self.x)
+        for a in (self.x, self.hy1, self.hy2):
+            self.sess.backend.host_register(a)
+
+    def e2e_step(self):
+        p, d = self.sess.pool, self.sess.device
+        ev = p.host_to_pool(self.x, self.bx)
+        d.launch(self.p_sm, [self.bx, self.by1], [ev])
+        d.launch(self.p_ln, [self.bx, self.bg, self.bb, self.by2])
+        p.pool_to_host(self.by1, self.hy1)
+        p.pool_to_host(self.by2, self.hy2)
+
+    def check(self):
+        """One small invocation against the oracle (sampled rows)."""
+        from oracle import oracle as zo
+        pick = np.array([0, 1, self.rows // 2, self.rows - 1])
+        y = np.empty((len(pick), self.cols), np.float32)
+        for i, r in enumerate(pick):
+            self.sess.pool.pool_to_host(self.by1, y[i], src_offset=int(r) * self.cols * 4)
+        want = zo.softmax(zo.F32, self.x[pick])
+        return float(np.max(np.abs(y - want) / np.maximum(np.abs(want), 1e-2 * want.max(1, keepdims=True))))
+
+    # CPU leg: the oracle on a bounded sample of the same rows
+    def cpu_run(self, rows):
+        from oracle import oracle as zo
+        x = self.x[:rows]
+        t0 = time.perf_counter()
+        zo.softmax(zo.F32, x)
+        zo.layernorm(zo.F32, x, self.gamma, self.beta, 1e-5)
+        dt = time.perf_counter() - t0
+        return rows * self.cols * 16 / 1e9 / dt, dt
+
+    def cpu_baseline(self, budget_s=12.0):
+        self.host_inputs() if not hasattr(self, "x") else None
+        v, dt = self.cpu_run(64)
+        rows = int(min(self.rows, max(64, 64 * budget_s / max(dt, 1e-6))))
+        v, dt = self.cpu_run(rows)
+        return v, "%d of %d rows of [%d, %d] f32, softmax + layernorm, %.1f s" % (rows, self.rows, self.rows, self.cols, dt)
+
+
+WORKLOADS = {"rowreduce": RowReduce}
+
+
+def host_threads():
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
+def run_reference(args, rank, world):
+    """The reference arm: the CPU oracle (port of the reference C backend) on all host threads."""
+    if rank != 0:
+        return
+    os.environ.setdefault("OMP_NUM_THREADS", str(host_threads()))
+    w = WORKLOADS[args.workload]()
+    w.host_inputs()
+    vals = []
+    sample = ""
+    budget = max(2.0, min(20.0, 120.0 / max(1, args.steps + args.warmup)))
+    for i in range(args.warmup + args.steps):
+        v, sample = w.cpu_baseline(budget_s=budget)
+        if i >= args.warmup:
+            vals.append(v)
+    value = float(np.mean(vals))
+    ms = 1e3 * w.units_per_step / value
+    line = {"impl": "reference", "metric": w.metric, "value": value, "unit": w.unit, "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": w.dtype, "data": "synthetic", "config": {"workload": w.name},
+            "cpu_baseline": {"value": value, "unit": w.unit, "cores": host_threads(), "kind": "port", "sample": sample},
+            "e2e": {"value": value, "unit": w.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--workload", default="rowreduce", choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="zyx_b200", choices=["zyx_b200", "reference"])
+    ap.add_argument("--e2e-steps", type=int, default=3)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        return run_reference(args, rank, world)
+
+    import torch
+    import torch.distributed as dist
+    if world > 1:
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", local_rank))
+
+    from zyx_b200 import build
+    from zyx_b200.ops import Session
+    if rank == 0 or not os.path.exists(os.path.join(ROOT, "zyx_b200", "libzyxb.so")):
+        build.build()
+    if world > 1:
+        dist.barrier()
+    sess = Session(device_ids=[local_rank])
+    dev = sess.device
+    peaks = load_peaks()
+    w = WORKLOADS[args.workload]()
+    w.setup(sess)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        dev.sync()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        w.step()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    launches0 = dev.launch_count()
+    barrier()
+    e_start = dev.event_record()
+    for _ in range(args.steps):
+        w.step(timed=True)
+    e_stop = dev.event_record()
+    barrier()
+    ms_total = dev.elapsed_ms(e_start, e_stop)
+    launches = dev.launch_count() - launches0
+    clocks = sampler.stop() if rank == 0 else None
+    if world > 1:
+        t = torch.tensor([ms_total], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total = float(t.item())
+    ms_step = ms_total / args.steps
+    value = world * w.units_per_step / (ms_step * 1e-3)
+    roofline, kernels = w.roofline(peaks)
+    err = w.check()
+
+    # end to end through the public API: host buffers in, host buffers out, copies inside the timed region
+    w.e2e_setup()
+    w.e2e_step()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.e2e_steps):
+        w.e2e_step()
+    dev.sync()
+    e2e_s = (time.perf_counter() - t0) / args.e2e_steps
+    if world > 1:
+        t = torch.tensor([e2e_s], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+    e2e = {"value": world * w.units_per_step / e2e_s, "unit": w.unit, "h2d_bytes_per_step": w.h2d_bytes, "d2h_bytes_per_step": w.d2h_bytes,
+           "steps": args.e2e_steps, "ms_per_step": e2e_s * 1e3}
+
+    if rank == 0:
+        line = {"metric": w.metric, "value": value, "unit": w.unit, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+                "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": w.dtype,
+                "data": "synthetic", "config": w.config, "roofline": roofline, "kernels": kernels, "e2e": e2e,
+                "gpu_launches": int(launches), "clocks": clocks, "max_rel_err_vs_oracle": err}
+        if world == 1 and not args.no_cpu_baseline:
+            os.environ.setdefault("OMP_NUM_THREADS", str(host_threads()))
+            v, sample = w.cpu_baseline()
+            line["cpu_baseline"] = {"value": v, "unit": w.unit, "cores": host_threads(), "kind": "port", "sample": sample}
+        print(json.dumps(line), flush=True)
+    sess.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -85,7 +85,7 @@ typedef struct {
   uint64_t total_mem_bytes;
   int32_t  cc_major, cc_minor;
   char     name[128];
-} zyxb_device_info;
+} zyxb_devinfo;
 
 /* ------------------------------------------------------------------------------------
  * Kernel descriptors: what `zyxb_program_create` consumes.  A descriptor is what the
@@ -220,7 +220,7 @@ const char* zyxb_last_error(zyxb_ctx* ctx);
 
 /* Device::info (mod.rs:839), Device::free_compute (mod.rs:875) */
 int32_t zyxb_device_count(zyxb_ctx* ctx, int32_t* out_count);
-int32_t zyxb_device_info(zyxb_ctx* ctx, int32_t dev, zyxb_device_info* out_info);
+int32_t zyxb_device_info(zyxb_ctx* ctx, int32_t dev, zyxb_devinfo* out_info);
 int32_t zyxb_free_compute(zyxb_ctx* ctx, int32_t dev, uint64_t* out_flops);
 
 /* ---- memory pool ---------------------------------------------------------------------

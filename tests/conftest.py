@@ -17,3 +17,14 @@ def golden():
     import json
     with open(os.path.join(ROOT, "tests", "golden", "reference_vectors.json")) as f:
         return json.load(f)
+
+
+@pytest.fixture(scope="session")
+def sess():
+    """One libzyxb context on cuda:0 for the whole GPU test session."""
+    from zyx_b200 import build
+    from zyx_b200.ops import Session
+    build.build()
+    s = Session(device_ids=[0])
+    yield s
+    s.close()

@@ -1,0 +1,188 @@
+"""Parity of the CUDA row kernels (through the C ABI) with the CPU oracle and the reference's
+golden vectors.  f32: max relative error <= 1e-5; bf16/f16: <= 2e-2; integers bit-exact."""
+import numpy as np
+import pytest
+
+from oracle import oracle as zo
+from tests.parity import TOL_BF16, TOL_F32, max_rel_err, ref_is_equal
+from zyx_b200 import _lib as L
+
+pytestmark = pytest.mark.gpu
+
+RNG = np.random.default_rng(7)
+TOL = {L.F32: TOL_F32, L.BF16: TOL_BF16, L.F16: TOL_BF16}
+# shapes that exercise every geometry: warp rows, CTA rows, register-resident long rows,
+# the streaming form, ragged (non multiple of the vector width) and single-column rows
+SHAPES = [(1, 1), (3, 2), (2, 3), (64, 10), (5, 37), (7, 255), (33, 256), (4, 1000), (9, 1024), (3, 4099), (5, 8192), (2, 16384),
+          (3, 32768), (2, 40000), (2, 70001)]
+
+
+def rand(shape, dtype, scale=1.0):
+    x = (RNG.standard_normal(shape) * scale).astype(np.float32)
+    return zo.to_bits(x, dtype) if dtype != L.F32 else x
+
+
+def f(x, dtype):
+    return zo.to_f32(x, dtype)
+
+
+def f32(x):
+    return np.asarray(x, np.float32)
+
+
+# ---- golden vectors of the reference's own tests, run on the GPU path ------------------------------
+def test_golden_softmax(sess, golden):
+    for case in golden["softmax"]:
+        assert ref_is_equal(sess.softmax(L.F32, f32(case["x"])), f32(case["y"])), case["src"]
+
+
+def test_golden_layernorm(sess, golden):
+    for case in golden["layernorm"]:
+        y = sess.layernorm(L.F32, f32(case["x"]), w=f32(case["weight"]), eps=case["eps"])
+        assert ref_is_equal(y, f32(case["y"])), case["src"]
+
+
+def test_golden_cross_entropy(sess, golden):
+    for case in golden["cross_entropy"]:
+        logits, labels = f32(case["logits"]), np.asarray(case["labels"], np.int32)
+        want = f32(case["neg_ln_softmax_times_onehot"])
+        per, mean = sess.cross_entropy(logits, labels)
+        assert ref_is_equal(per, want.sum(1)) and ref_is_equal(mean, [want.sum() / len(labels)])
+        onehot = (labels[:, None] == np.arange(logits.shape[1])[None, :]).astype(np.float32)
+        assert ref_is_equal(-sess.softmax(L.F32, logits, log=True) * onehot, want)
+
+
+def test_golden_reduce(sess, golden):
+    ops = {"sum": L.RR_SUM, "max": L.RR_MAX, "mean": L.RR_MEAN, "var": L.RR_VAR}
+    for case in golden["reduce_f32"]:
+        y = sess.row_reduce(ops[case["op"]], L.F32, f32(case["x"]), correction=case["correction"])
+        assert ref_is_equal(y, f32(case["y"])), case["src"]
+    for case in golden["reduce_i32"]:
+        rows, cols = case["rows"], case["cols"]
+        x = np.full((rows, cols), case["x_fill"], np.int32) if "x_fill" in case else \
+            (np.arange(rows * cols, dtype=np.int32) + case["x_arange_from"]).reshape(rows, cols)
+        assert sess.row_reduce(ops[case["op"]], L.I32, x).tolist() == case["y"], case["src"]
+
+
+# ---- randomised parity against the oracle -------------------------------------------------------------
+@pytest.mark.parametrize("dtype", [L.F32, L.BF16, L.F16])
+@pytest.mark.parametrize("shape", SHAPES)
+def test_softmax_and_ln_softmax(sess, dtype, shape):
+    x = rand(shape, dtype, 3.0)
+    assert max_rel_err(f(sess.softmax(dtype, x), dtype), f(zo.softmax(dtype, x), dtype)) <= TOL[dtype]
+    got, want = f(sess.softmax(dtype, x, log=True), dtype), f(zo.ln_softmax(dtype, x), dtype)
+    assert max_rel_err(got, want) <= TOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", [L.F32, L.BF16])
+def test_softmax_scaled_causal(sess, dtype):
+    T = 96
+    x = rand((4 * T, T), dtype, 4.0)
+    got = f(sess.softmax(dtype, x, scale=0.125, causal=True, period=T), dtype)
+    want = f(zo.softmax(dtype, x, scale=0.125, causal=True, period=T), dtype)
+    assert max_rel_err(got, want) <= TOL[dtype]
+    r = np.arange(4 * T) % T
+    assert np.all(got[np.arange(T)[None, :] > r[:, None]] == 0.0)     # masked columns are exactly zero
+
+
+@pytest.mark.parametrize("dtype", [L.F32, L.BF16, L.F16])
+@pytest.mark.parametrize("shape", [s for s in SHAPES if s[1] >= 2])
+@pytest.mark.parametrize("affine", [False, True])
+def test_layernorm(sess, dtype, shape, affine):
+    x = rand(shape, dtype, 2.0)
+    w = rand((shape[1],), dtype) if affine else None
+    b = rand((shape[1],), dtype) if affine else None
+    got, want = f(sess.layernorm(dtype, x, w, b, 1e-5), dtype), f(zo.layernorm(dtype, x, w, b, 1e-5), dtype)
+    assert max_rel_err(got, want) <= TOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", [L.F32, L.BF16])
+@pytest.mark.parametrize("shape", [(3, 2), (64, 10), (5, 37), (4, 1000), (3, 4099), (2, 16384), (2, 32768), (2, 70001)])
+def test_backward_rows(sess, dtype, shape):
+    x, dy, w = rand(shape, dtype, 2.0), rand(shape, dtype), rand((shape[1],), dtype)
+    got, want = f(sess.layernorm_bwd(dtype, x, dy, w, 1e-5), dtype), f(zo.layernorm_bwd(dtype, x, dy, w, 1e-5), dtype)
+    assert max_rel_err(got, want, floor=1e-2) <= TOL[dtype] * (20 if dtype == L.F32 else 1)   # three chained f32 sums
+    p = zo.softmax(dtype, rand(shape, dtype, 2.0))
+    got, want = f(sess.softmax_bwd(dtype, p, dy), dtype), f(zo.softmax_bwd(dtype, p, dy), dtype)
+    assert max_rel_err(got, want, floor=1e-2) <= TOL[dtype] * (20 if dtype == L.F32 else 1)
+
+
+@pytest.mark.parametrize("dtype", [L.F32, L.BF16, L.F16])
+@pytest.mark.parametrize("shape", SHAPES)
+def test_scalar_reductions(sess, dtype, shape):
+    x = rand(shape, dtype, 2.0)
+    ops = [(L.RR_SUM, zo.RR_SUM), (L.RR_MAX, zo.RR_MAX), (L.RR_MIN, zo.RR_MIN), (L.RR_MEAN, zo.RR_MEAN)]
+    if shape[1] >= 2:
+        ops += [(L.RR_VAR, zo.RR_VAR), (L.RR_STD, zo.RR_STD)]
+    for gop, oop in ops:
+        got, want = f(sess.row_reduce(gop, dtype, x), dtype), f(zo.row_reduce(oop, dtype, x), dtype)
+        if gop in (L.RR_MAX, L.RR_MIN):
+            assert np.array_equal(got, want)                       # order-independent: bit-exact
+        else:
+            # a sum is compared relative to the magnitude of what was summed
+            scale = np.abs(f(x, dtype)).sum(1) if gop in (L.RR_SUM, L.RR_MEAN) else np.abs(want)
+            denom = np.maximum(np.abs(want), 1e-3 * np.maximum(scale / (shape[1] if gop == L.RR_MEAN else 1), 1e-30))
+            assert float(np.max(np.abs(got - want) / denom)) <= TOL[dtype], (gop, shape)
+
+
+@pytest.mark.parametrize("shape", SHAPES)
+def test_integer_reductions_bit_exact(sess, shape):
+    x = RNG.integers(-2**31, 2**31 - 1, size=shape, dtype=np.int64).astype(np.int32)
+    for gop, oop in [(L.RR_SUM, zo.RR_SUM), (L.RR_MAX, zo.RR_MAX), (L.RR_MIN, zo.RR_MIN)]:
+        assert np.array_equal(sess.row_reduce(gop, L.I32, x), zo.row_reduce(oop, zo.I32, x)), (gop, shape)
+
+
+@pytest.mark.parametrize("shape", [(1, 2), (64, 10), (128, 1000), (3, 50257)])
+def test_cross_entropy_forward_backward(sess, shape):
+    logits = rand(shape, L.F32, 3.0)
+    labels = RNG.integers(0, shape[1], size=shape[0]).astype(np.int32)
+    per, mean = sess.cross_entropy(logits, labels)
+    wper, wmean = zo.cross_entropy(logits, labels)
+    assert max_rel_err(per, wper, row_axis=0) <= TOL_F32 and max_rel_err(mean, wmean, row_axis=0) <= TOL_F32
+    got, want = sess.cross_entropy_bwd(logits, labels), zo.cross_entropy_bwd(logits, labels)
+    assert max_rel_err(got, want) <= TOL_F32
+    # bit-exact indexing: the only negative entry of each row sits at the label
+    assert np.array_equal(np.argmin(got, axis=1), labels) or shape[1] == 1
+
+
+@pytest.mark.parametrize("dtype", [L.F32, L.BF16])
+@pytest.mark.parametrize("shape", [(1, 1), (5, 3), (1000, 10), (64, 128), (777, 130), (4096, 4096), (300, 16384)])
+def test_colsum_and_mse(sess, dtype, shape):
+    x, t = rand(shape, dtype), rand(shape, dtype)
+    got, want = f(sess.colsum(dtype, x), dtype), f(zo.colsum(dtype, x), dtype)
+    scale = np.abs(f(x, dtype)).sum(0)
+    assert float(np.max(np.abs(got - want) / np.maximum(np.abs(want), 1e-3 * np.maximum(scale, 1e-30)))) <= TOL[dtype]
+    assert abs(sess.mse(dtype, x, t) - zo.mse(dtype, x, t)) <= 1e-5 * abs(zo.mse(dtype, x, t))
+
+
+def test_baseline_shape_properties(sess):
+    """The [8192, 32768] f32 configuration: rows of a softmax sum to 1, a layernorm row has zero
+    mean and unit (unbiased) variance, and sampled rows match the oracle."""
+    rows, cols = 8192, 32768
+    x = np.random.default_rng(1).standard_normal((rows, cols), dtype=np.float32)
+    pick = np.array([0, 1, 17, 4095, 4096, 8190, 8191])
+    y = sess.softmax(L.F32, x)
+    assert np.max(np.abs(y.sum(1, dtype=np.float64) - 1.0)) < 1e-5
+    assert max_rel_err(y[pick], zo.softmax(zo.F32, x[pick])) <= TOL_F32
+    g, b = np.ones(cols, np.float32), np.zeros(cols, np.float32)
+    z = sess.layernorm(L.F32, x, g, b, 1e-5)
+    assert np.max(np.abs(z.mean(1, dtype=np.float64))) < 1e-5
+    assert np.max(np.abs(z.var(1, dtype=np.float64, ddof=1) - 1.0)) < 1e-4
+    assert max_rel_err(z[pick], zo.layernorm(zo.F32, x[pick], g, b, 1e-5)) <= TOL_F32
+
+
+def test_bad_arguments_are_reported_not_faulted(sess):
+    from zyx_b200 import BackendError
+    from zyx_b200 import backend as B
+    prog = sess.device.create_program(B.rowreduce_desc(L.RR_SOFTMAX, L.F32, 8, 8))
+    small, _ = sess.pool.allocate(16)
+    with pytest.raises(BackendError) as e:
+        sess.device.launch(prog, [small, small])
+    assert e.value.status_name == "IncorrectKernelArg"
+    with pytest.raises(BackendError):
+        sess.device.launch(prog, [small])
+    with pytest.raises(BackendError) as e:
+        sess.device.create_program(B.rowreduce_desc(L.RR_SOFTMAX, L.F32, 0, 8))
+    assert e.value.status_name == "KernelCompilation"
+    sess.pool.deallocate(small)
+    sess.device.release(prog)

@@ -1,0 +1,143 @@
+// Device-side helpers shared by every kernel file: storage <-> f32 conversions that follow
+// the reference C backend (zyx/src/codegen/c.rs:452-497), vector I/O, warp/block reductions.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace zyxb {
+
+struct bf16_t { uint16_t bits; };
+struct f16_t { uint16_t bits; };
+
+// ---- conversions -----------------------------------------------------------------------
+// Loads widen exactly.  Stores truncate by default, as f32tobf16 / f32tof16 in the reference
+// C backend do (bits >> 16; f16: mantissa cut, subnormals flushed to signed zero), or round
+// to nearest even when the context was created with round_nearest.
+__device__ __forceinline__ float bf16_to_f32(uint16_t h) { return __uint_as_float((uint32_t)h << 16); }
+__device__ __forceinline__ uint16_t f32_to_bf16(float v, bool rn) {
+  uint32_t b = __float_as_uint(v);
+  if (rn) {
+    if ((b & 0x7fffffffu) > 0x7f800000u) return (uint16_t)((b >> 16) | 0x40);  // quiet NaN
+    b += 0x7fffu + ((b >> 16) & 1u);
+  }
+  return (uint16_t)(b >> 16);
+}
+__device__ __forceinline__ float f16_to_f32(uint16_t h) {
+  uint32_t sign = ((uint32_t)h & 0x8000u) << 16, exp = (h >> 10) & 0x1f, man = h & 0x3ff;
+  if (exp == 0) {
+    if (man == 0) return __uint_as_float(sign);
+    // IEEE subnormal: man * 2^-24
+    float m = (float)man * 5.9604644775390625e-8f;
+    return __uint_as_float(__float_as_uint(m) | sign);
+  }
+  if (exp == 31) return __uint_as_float(sign | 0x7f800000u | (man << 13));
+  return __uint_as_float(sign | ((exp + 112) << 23) | (man << 13));
+}
+__device__ __forceinline__ uint16_t f32_to_f16(float v, bool rn) {
+  uint32_t f = __float_as_uint(v);
+  uint32_t sign = (f >> 16) & 0x8000u, exp = (f >> 23) & 0xff, man = f & 0x7fffffu;
+  if (exp == 0) return (uint16_t)sign;
+  if (exp == 255) return (uint16_t)(sign | 0x7c00u | (man >> 13));
+  int ne = (int)exp - 127 + 15;
+  if (ne >= 31) return (uint16_t)(sign | 0x7c00u);
+  if (ne <= 0) return (uint16_t)sign;
+  uint32_t h = sign | ((uint32_t)ne << 10) | (man >> 13);
+  if (rn) {
+    uint32_t rem = man & 0x1fffu;
+    if (rem > 0x1000u || (rem == 0x1000u && (h & 1u))) h += 1;  // may carry into the exponent: still correct
+  }
+  return (uint16_t)h;
+}
+
+template <typename T> struct Elem;
+template <> struct Elem<float> {
+  using store_t = float; using acc_t = float;
+  static __device__ __forceinline__ float load(float v) { return v; }
+  static __device__ __forceinline__ float store(float v, bool) { return v; }
+};
+template <> struct Elem<bf16_t> {
+  using store_t = uint16_t; using acc_t = float;
+  static __device__ __forceinline__ float load(uint16_t v) { return bf16_to_f32(v); }
+  static __device__ __forceinline__ uint16_t store(float v, bool rn) { return f32_to_bf16(v, rn); }
+};
+template <> struct Elem<f16_t> {
+  using store_t = uint16_t; using acc_t = float;
+  static __device__ __forceinline__ float load(uint16_t v) { return f16_to_f32(v); }
+  static __device__ __forceinline__ uint16_t store(float v, bool rn) { return f32_to_f16(v, rn); }
+};
+template <> struct Elem<int32_t> {
+  using store_t = int32_t; using acc_t = int32_t;
+  static __device__ __forceinline__ int32_t load(int32_t v) { return v; }
+  static __device__ __forceinline__ int32_t store(int32_t v, bool) { return v; }
+};
+
+// a rank-0 scalar operand is cast to the tensor dtype before use (zyx/src/tensor/mod.rs:3033-3113)
+template <typename T> __device__ __forceinline__ float const_cast_dtype(float v) {
+  return Elem<T>::load(Elem<T>::store(v, false));
+}
+template <> __device__ __forceinline__ float const_cast_dtype<float>(float v) { return v; }
+
+// ---- 128-bit vector I/O ------------------------------------------------------------------
+// VEC elements of storage type S moved as one aligned access when VEC * sizeof(S) == 16.
+template <typename S, int VEC> struct alignas(sizeof(S) * VEC) Pack { S v[VEC]; };
+
+template <typename S, int VEC>
+__device__ __forceinline__ Pack<S, VEC> load_pack(const S* p) {
+  return *reinterpret_cast<const Pack<S, VEC>*>(p);
+}
+// streaming variants: data touched once, keep it from displacing L2-resident operands
+template <typename S, int VEC>
+__device__ __forceinline__ Pack<S, VEC> load_pack_stream(const S* p) {
+  Pack<S, VEC> r;
+  if constexpr (sizeof(S) * VEC == 16) {
+    uint4 u = __ldcs(reinterpret_cast<const uint4*>(p));
+    r = *reinterpret_cast<Pack<S, VEC>*>(&u);
+  } else {
+    r = *reinterpret_cast<const Pack<S, VEC>*>(p);
+  }
+  return r;
+}
+template <typename S, int VEC>
+__device__ __forceinline__ void store_pack(S* p, const Pack<S, VEC>& v) {
+  *reinterpret_cast<Pack<S, VEC>*>(p) = v;
+}
+template <typename S, int VEC>
+__device__ __forceinline__ void store_pack_stream(S* p, const Pack<S, VEC>& v) {
+  if constexpr (sizeof(S) * VEC == 16) {
+    __stcs(reinterpret_cast<uint4*>(p), *reinterpret_cast<const uint4*>(&v));
+  } else {
+    *reinterpret_cast<Pack<S, VEC>*>(p) = v;
+  }
+}
+
+// ---- reductions ----------------------------------------------------------------------------
+struct OpSum { template <typename A> __device__ __forceinline__ A operator()(A a, A b) const { return a + b; } };
+struct OpMax { template <typename A> __device__ __forceinline__ A operator()(A a, A b) const { return a > b ? a : b; } };
+struct OpMin { template <typename A> __device__ __forceinline__ A operator()(A a, A b) const { return a < b ? a : b; } };
+struct OpMaxF { __device__ __forceinline__ float operator()(float a, float b) const { return fmaxf(a, b); } };
+
+template <typename A, typename Op>
+__device__ __forceinline__ A warp_reduce(A v, Op op) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = op(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Reduce across a group of GROUP threads (GROUP == 32: a warp; otherwise the whole CTA, whose
+// size must be GROUP).  `scratch` needs GROUP/32 elements of shared memory; every thread of the
+// group gets the result.  Two barriers per call make back-to-back calls on one scratch safe.
+template <int GROUP, typename A, typename Op>
+__device__ __forceinline__ A group_reduce(A v, Op op, A* scratch, A identity) {
+  v = warp_reduce(v, op);
+  if constexpr (GROUP > 32) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    A w = (lane < GROUP / 32) ? scratch[lane] : identity;
+    v = warp_reduce(w, op);
+    __syncthreads();
+  }
+  return v;
+}
+
+}  // namespace zyxb

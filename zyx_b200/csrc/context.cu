@@ -1,0 +1,652 @@
+// The C ABI of libzyxb: context, memory pool, events, programs.  Each entry point stands in
+// for one method of zyx's backend interface (zyx/src/backend/mod.rs); the header cites them.
+//
+// Threading model: zyx serialises backend calls under its global runtime mutex
+// (zyx/src/lib.rs:96), possibly from different OS threads.  Instead of the reference CUDA
+// backend's worker thread per device (zyx/src/backend/cuda.rs:475-519) every call here makes
+// its device current and enqueues on that device's streams:
+//   compute : every kernel, d2h, memset            (in-order: a launch sees all earlier launches)
+//   copy    : h2d, so uploads can overlap kernels  (ordered against compute by events)
+//   comm    : NCCL collectives                      (ordered against compute by events)
+#include <cuda_runtime.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <map>
+#include <mutex>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "comm.h"
+#include "internal.h"
+
+using namespace zyxb;
+
+namespace {
+
+struct Buffer {
+  void* ptr = nullptr;
+  uint64_t bytes = 0;      // bytes the caller asked for
+  uint64_t capacity = 0;   // bytes of the underlying block
+  bool live = false;
+  bool is_variable = false;
+  int32_t var_dtype = 0;
+  uint8_t var_bytes[8] = {0};
+};
+
+struct Program {
+  zyxb_kernel_desc desc{};
+  std::vector<uint64_t> numel;  // optimizer programs: copy of desc.u.optim.numel
+  uint64_t step = 0;            // optimizer programs: AdamW::t
+  bool live = false;
+};
+
+struct Device {
+  int cuda_id = 0;
+  cudaDeviceProp prop{};
+  cudaStream_t compute = nullptr, copy = nullptr, comm_stream = nullptr;
+  std::vector<Buffer> buffers;
+  std::vector<uint32_t> free_buffer_ids;
+  std::vector<Program> programs;
+  std::vector<uint32_t> free_program_ids;
+  std::unordered_map<uint64_t, cudaEvent_t> events;
+  uint64_t next_event = 1;
+  std::multimap<uint64_t, void*> cache;   // freed blocks by capacity
+  uint64_t cached_bytes = 0;
+  void* scratch = nullptr;
+  size_t scratch_bytes = 0;
+  uint32_t* status_word = nullptr;
+  void* flush_buf = nullptr;
+  size_t flush_bytes = 0;
+  uint64_t launch_count = 0;
+  void* tma_encode = nullptr;
+  Comm* comm = nullptr;
+};
+
+std::string g_init_error;
+
+}  // namespace
+
+struct zyxb_ctx {
+  std::vector<Device> devs;
+  std::string last_error;
+  bool round_nearest = false;
+  int debug = 0;
+  std::unordered_map<void*, int> registered;   // page-locked host ranges
+};
+
+namespace {
+
+int fail(zyxb_ctx* ctx, int status, const std::string& msg) {
+  if (ctx) ctx->last_error = msg; else g_init_error = msg;
+  return status;
+}
+int cuda_fail(zyxb_ctx* ctx, int status, const char* what, cudaError_t e) {
+  return fail(ctx, status, std::string(what) + ": " + cudaGetErrorString(e));
+}
+
+#define DEV_OR_FAIL(status)                                                              \
+  if (!ctx) return ZYXB_ERR_INITIALIZATION;                                              \
+  if (dev < 0 || dev >= (int)ctx->devs.size()) return fail(ctx, status, "no such device"); \
+  Device& D = ctx->devs[dev];                                                            \
+  { cudaError_t e_ = cudaSetDevice(D.cuda_id); if (e_ != cudaSuccess) return cuda_fail(ctx, status, "cudaSetDevice", e_); }
+
+Buffer* get_buffer(Device& D, uint32_t id) {
+  if (id >= D.buffers.size() || !D.buffers[id].live) return nullptr;
+  return &D.buffers[id];
+}
+
+uint64_t round_up(uint64_t v, uint64_t a) { return (v + a - 1) / a * a; }
+
+// Events named in a wait list are consumed: the stream waits for them and they are destroyed,
+// as zyx moves `Vec<Event>` into the backend call.
+int wait_and_consume(zyxb_ctx* ctx, Device& D, cudaStream_t stream, const zyxb_event* wait, int n, int status) {
+  for (int i = 0; i < n; ++i) {
+    if (wait[i].id == 0) continue;
+    auto it = D.events.find(wait[i].id);
+    if (it == D.events.end()) return fail(ctx, status, "unknown event in wait list");
+    cudaError_t e = cudaStreamWaitEvent(stream, it->second, 0);
+    cudaEventDestroy(it->second);
+    D.events.erase(it);
+    if (e != cudaSuccess) return cuda_fail(ctx, status, "cudaStreamWaitEvent", e);
+  }
+  return ZYXB_OK;
+}
+
+int record_event(zyxb_ctx* ctx, Device& D, cudaStream_t stream, zyxb_event* out, int status, bool timing = false) {
+  if (!out) return ZYXB_OK;
+  cudaEvent_t ev;
+  cudaError_t e = cudaEventCreateWithFlags(&ev, timing ? cudaEventDefault : cudaEventDisableTiming);
+  if (e != cudaSuccess) return cuda_fail(ctx, status, "cudaEventCreate", e);
+  e = cudaEventRecord(ev, stream);
+  if (e != cudaSuccess) { cudaEventDestroy(ev); return cuda_fail(ctx, status, "cudaEventRecord", e); }
+  out->id = D.next_event++;
+  D.events[out->id] = ev;
+  return ZYXB_OK;
+}
+
+// make `later` wait for everything enqueued on `earlier` so far
+int order_streams(zyxb_ctx* ctx, cudaStream_t earlier, cudaStream_t later, int status) {
+  cudaEvent_t ev;
+  cudaError_t e = cudaEventCreateWithFlags(&ev, cudaEventDisableTiming);
+  if (e != cudaSuccess) return cuda_fail(ctx, status, "cudaEventCreate", e);
+  cudaEventRecord(ev, earlier);
+  e = cudaStreamWaitEvent(later, ev, 0);
+  cudaEventDestroy(ev);
+  if (e != cudaSuccess) return cuda_fail(ctx, status, "cudaStreamWaitEvent", e);
+  return ZYXB_OK;
+}
+
+cudaError_t device_malloc(Device& D, uint64_t capacity, void** out) {
+  auto it = D.cache.lower_bound(capacity);
+  // reuse a cached block when it is not wastefully larger than the request
+  if (it != D.cache.end() && it->first <= capacity + capacity / 4 + (1u << 20)) {
+    *out = it->second;
+    D.cached_bytes -= it->first;
+    D.cache.erase(it);
+    return cudaSuccess;
+  }
+  cudaError_t e = cudaMalloc(out, capacity);
+  if (e == cudaErrorMemoryAllocation) {
+    cudaGetLastError();
+    for (auto& kv : D.cache) cudaFree(kv.second);   // give the cache back and retry once
+    D.cache.clear(); D.cached_bytes = 0;
+    e = cudaMalloc(out, capacity);
+  }
+  return e;
+}
+
+LaunchCtx make_launch_ctx(zyxb_ctx* ctx, Device& D) {
+  LaunchCtx lc{};
+  lc.stream = D.compute; lc.round_nearest = ctx->round_nearest; lc.sm_count = D.prop.multiProcessorCount;
+  lc.status_word = D.status_word; lc.scratch = D.scratch; lc.scratch_bytes = D.scratch_bytes;
+  lc.launch_counter = &D.launch_count; lc.tma_encode = D.tma_encode; lc.device = D.cuda_id;
+  return lc;
+}
+
+}  // namespace
+
+extern "C" {
+#pragma GCC visibility push(default)
+
+const char* zyxb_last_error(zyxb_ctx* ctx) { return ctx ? ctx->last_error.c_str() : g_init_error.c_str(); }
+
+int32_t zyxb_init(const zyxb_config* config, zyxb_ctx** out_ctx) {
+  if (!out_ctx) return fail(nullptr, ZYXB_ERR_INITIALIZATION, "out_ctx is null");
+  *out_ctx = nullptr;
+  int count = 0;
+  cudaError_t e = cudaGetDeviceCount(&count);
+  if (e != cudaSuccess || count == 0) {
+    cudaGetLastError();
+    return fail(nullptr, ZYXB_ERR_DEVICE_ENUMERATION,
+                std::string("no CUDA device: ") + (e != cudaSuccess ? cudaGetErrorString(e) : "device count is 0") +
+                    " (this backend has no CPU fallback)");
+  }
+  std::vector<int> ids;
+  if (config && config->n_device_ids > 0) {
+    for (int i = 0; i < config->n_device_ids && i < 16; ++i) {
+      if (config->device_ids[i] < 0 || config->device_ids[i] >= count) return fail(nullptr, ZYXB_ERR_DEVICE_ENUMERATION, "device id out of range");
+      ids.push_back(config->device_ids[i]);
+    }
+  } else {
+    for (int i = 0; i < count; ++i) ids.push_back(i);
+  }
+  zyxb_ctx* ctx = new zyxb_ctx();
+  ctx->round_nearest = config && config->round_nearest;
+  ctx->debug = config ? config->debug : 0;
+  for (int id : ids) {
+    Device D;
+    D.cuda_id = id;
+    if ((e = cudaSetDevice(id)) != cudaSuccess || (e = cudaGetDeviceProperties(&D.prop, id)) != cudaSuccess) {
+      delete ctx; return cuda_fail(nullptr, ZYXB_ERR_DEVICE_QUERY, "device query", e);
+    }
+    if (D.prop.major != 10) {   // kernels are built for sm_100a only
+      if (config && config->n_device_ids > 0) { delete ctx; return fail(nullptr, ZYXB_ERR_INITIALIZATION, "device is not compute capability 10.x (B200)"); }
+      continue;
+    }
+    if ((e = cudaStreamCreateWithFlags(&D.compute, cudaStreamNonBlocking)) != cudaSuccess ||
+        (e = cudaStreamCreateWithFlags(&D.copy, cudaStreamNonBlocking)) != cudaSuccess ||
+        (e = cudaStreamCreateWithFlags(&D.comm_stream, cudaStreamNonBlocking)) != cudaSuccess) {
+      delete ctx; return cuda_fail(nullptr, ZYXB_ERR_INITIALIZATION, "stream creation", e);
+    }
+    D.scratch_bytes = 64ull << 20;
+    if ((e = cudaMalloc(&D.scratch, D.scratch_bytes)) != cudaSuccess || (e = cudaMalloc((void**)&D.status_word, 256)) != cudaSuccess) {
+      delete ctx; return cuda_fail(nullptr, ZYXB_ERR_MEMORY_ALLOCATION, "scratch allocation", e);
+    }
+    cudaMemset(D.status_word, 0, 256);
+    cudaDriverEntryPointQueryResult qres;
+    void* fn = nullptr;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) == cudaSuccess && qres == cudaDriverEntryPointSuccess)
+      D.tma_encode = fn;
+    else cudaGetLastError();
+    D.buffers.emplace_back();   // id 0 is never handed out
+    D.programs.emplace_back();
+    if (ctx->debug & 1) fprintf(stderr, "[zyxb] device %d: %s, %d SMs, %.1f GB\n", id, D.prop.name, D.prop.multiProcessorCount, D.prop.totalGlobalMem / 1e9);
+    ctx->devs.push_back(std::move(D));
+  }
+  if (ctx->devs.empty()) { delete ctx; return fail(nullptr, ZYXB_ERR_DEVICE_ENUMERATION, "no compute capability 10.x (B200) device found"); }
+  *out_ctx = ctx;
+  return ZYXB_OK;
+}
+
+int32_t zyxb_shutdown(zyxb_ctx* ctx) {
+  if (!ctx) return ZYXB_OK;
+  for (auto& D : ctx->devs) {
+    cudaSetDevice(D.cuda_id);
+    cudaDeviceSynchronize();
+    if (D.comm) { comm_destroy(D.comm); D.comm = nullptr; }
+    for (auto& kv : D.events) cudaEventDestroy(kv.second);
+    for (auto& b : D.buffers) if (b.live && b.ptr) cudaFree(b.ptr);
+    for (auto& kv : D.cache) cudaFree(kv.second);
+    if (D.scratch) cudaFree(D.scratch);
+    if (D.status_word) cudaFree(D.status_word);
+    if (D.flush_buf) cudaFree(D.flush_buf);
+    cudaStreamDestroy(D.compute); cudaStreamDestroy(D.copy); cudaStreamDestroy(D.comm_stream);
+  }
+  for (auto& kv : ctx->registered) cudaHostUnregister(kv.first);
+  delete ctx;
+  return ZYXB_OK;
+}
+
+int32_t zyxb_device_count(zyxb_ctx* ctx, int32_t* out_count) {
+  if (!ctx || !out_count) return ZYXB_ERR_DEVICE_ENUMERATION;
+  *out_count = (int32_t)ctx->devs.size();
+  return ZYXB_OK;
+}
+
+int32_t zyxb_device_info(zyxb_ctx* ctx, int32_t dev, zyxb_devinfo* o) {
+  DEV_OR_FAIL(ZYXB_ERR_DEVICE_QUERY);
+  if (!o) return fail(ctx, ZYXB_ERR_DEVICE_QUERY, "out_info is null");
+  memset(o, 0, sizeof(*o));
+  o->compute_flops = 2250000000000000ull;   // dense bf16 tensor-core peak of a B200
+  for (int i = 0; i < 3; ++i) { o->max_global_work_dims[i] = (uint64_t)D.prop.maxGridSize[i]; o->max_local_work_dims[i] = (uint32_t)D.prop.maxThreadsDim[i]; }
+  o->max_local_threads = (uint32_t)D.prop.maxThreadsPerBlock;
+  o->preferred_vector_size = 16;
+  o->local_mem_size = D.prop.sharedMemPerBlockOptin;
+  o->max_register_bytes = (uint64_t)D.prop.regsPerBlock * 4;
+  o->tensor_cores = 1;
+  o->warp_size = (uint32_t)D.prop.warpSize;
+  // every elementwise/reduce capability bit for the dtypes the kernels accept
+  for (int dt : {ZYXB_BF16, ZYXB_F16, ZYXB_F32}) o->dtype_capability[dt] = 0x7fffffffu;
+  o->dtype_capability[ZYXB_I32] = 0x7fffffffu;
+  o->has_native_exp2 = 1;
+  o->sm_count = (uint32_t)D.prop.multiProcessorCount;
+  o->total_mem_bytes = D.prop.totalGlobalMem;
+  o->cc_major = D.prop.major; o->cc_minor = D.prop.minor;
+  strncpy(o->name, D.prop.name, sizeof(o->name) - 1);
+  return ZYXB_OK;
+}
+
+int32_t zyxb_free_compute(zyxb_ctx* ctx, int32_t dev, uint64_t* out_flops) {
+  DEV_OR_FAIL(ZYXB_ERR_DEVICE_QUERY);
+  if (out_flops) *out_flops = 2250000000000000ull;
+  return ZYXB_OK;
+}
+
+int32_t zyxb_free_bytes(zyxb_ctx* ctx, int32_t dev, uint64_t* out_bytes) {
+  DEV_OR_FAIL(ZYXB_ERR_DEVICE_QUERY);
+  size_t fr = 0, total = 0;
+  cudaError_t e = cudaMemGetInfo(&fr, &total);
+  if (e != cudaSuccess) return cuda_fail(ctx, ZYXB_ERR_DEVICE_QUERY, "cudaMemGetInfo", e);
+  if (out_bytes) *out_bytes = (uint64_t)fr + D.cached_bytes;
+  return ZYXB_OK;
+}
+
+int32_t zyxb_alloc(zyxb_ctx* ctx, int32_t dev, uint64_t bytes, uint32_t* out_buf, zyxb_event* out_event) {
+  DEV_OR_FAIL(ZYXB_ERR_MEMORY_ALLOCATION);
+  if (!out_buf) return fail(ctx, ZYXB_ERR_MEMORY_ALLOCATION, "out_buf is null");
+  const uint64_t capacity = round_up(bytes == 0 ? 1 : bytes, 512);
+  void* ptr = nullptr;
+  cudaError_t e = device_malloc(D, capacity, &ptr);
+  if (e != cudaSuccess) { cudaGetLastError(); return cuda_fail(ctx, ZYXB_ERR_MEMORY_ALLOCATION, "cudaMalloc", e); }
+  uint32_t id;
+  if (!D.free_buffer_ids.empty()) { id = D.free_buffer_ids.back(); D.free_buffer_ids.pop_back(); }
+  else { id = (uint32_t)D.buffers.size(); D.buffers.emplace_back(); }
+  Buffer& b = D.buffers[id];
+  b = Buffer();
+  b.ptr = ptr; b.bytes = bytes; b.capacity = capacity; b.live = true;
+  *out_buf = id;
+  if (out_event) out_event->id = 0;   // allocation is synchronous: nothing to wait for
+  return ZYXB_OK;
+}
+
+int32_t zyxb_free(zyxb_ctx* ctx, int32_t dev, uint32_t buf, const zyxb_event* wait, int32_t n_wait) {
+  DEV_OR_FAIL(ZYXB_ERR_MEMORY_DEALLOCATION);
+  Buffer* b = get_buffer(D, buf);
+  if (!b) return fail(ctx, ZYXB_ERR_MEMORY_DEALLOCATION, "free: unknown buffer");
+  // the block goes back to the cache and may be handed out again at once: order every stream
+  // that could still touch it before later work on the compute stream
+  int st = wait_and_consume(ctx, D, D.compute, wait, n_wait, ZYXB_ERR_MEMORY_DEALLOCATION);
+  if (st) return st;
+  if (!b->is_variable) {
+    if ((st = order_streams(ctx, D.copy, D.compute, ZYXB_ERR_MEMORY_DEALLOCATION))) return st;
+    if ((st = order_streams(ctx, D.comm_stream, D.compute, ZYXB_ERR_MEMORY_DEALLOCATION))) return st;
+    D.cache.emplace(b->capacity, b->ptr);
+    D.cached_bytes += b->capacity;
+  }
+  *b = Buffer();
+  D.free_buffer_ids.push_back(buf);
+  return ZYXB_OK;
+}
+
+int32_t zyxb_buffer_bytes(zyxb_ctx* ctx, int32_t dev, uint32_t buf, uint64_t* out_bytes) {
+  DEV_OR_FAIL(ZYXB_ERR_INCORRECT_KERNEL_ARG);
+  Buffer* b = get_buffer(D, buf);
+  if (!b) return fail(ctx, ZYXB_ERR_INCORRECT_KERNEL_ARG, "unknown buffer");
+  if (out_bytes) *out_bytes = b->bytes;
+  return ZYXB_OK;
+}
+
+int32_t zyxb_h2d(zyxb_ctx* ctx, int32_t dev, const void* src, uint64_t bytes, uint32_t dst, uint64_t dst_offset,
+                 const zyxb_event* wait, int32_t n_wait, zyxb_event* out_event) {
+  DEV_OR_FAIL(ZYXB_ERR_MEMORY_COPY_H2P);
+  Buffer* b = get_buffer(D, dst);
+  if (!b || b->is_variable) return fail(ctx, ZYXB_ERR_MEMORY_COPY_H2P, "h2d: unknown buffer");
+  if (dst_offset + bytes > b->bytes) return fail(ctx, ZYXB_ERR_MEMORY_COPY_H2P, "h2d: copy exceeds the buffer");
+  int st = wait_and_consume(ctx, D, D.copy, wait, n_wait, ZYXB_ERR_MEMORY_COPY_H2P);
+  if (st) return st;
+  // kernels already enqueued may still read or write dst: the upload goes after them
+  if ((st = order_streams(ctx, D.compute, D.copy, ZYXB_ERR_MEMORY_COPY_H2P))) return st;
+  if (bytes) {
+    cudaError_t e = cudaMemcpyAsync((char*)b->ptr + dst_offset, src, bytes, cudaMemcpyHostToDevice, D.copy);
+    if (e != cudaSuccess) return cuda_fail(ctx, ZYXB_ERR_MEMORY_COPY_H2P, "cudaMemcpyAsync h2d", e);
+  }
+  if (out_event) return record_event(ctx, D, D.copy, out_event, ZYXB_ERR_MEMORY_COPY_H2P);
+  // no event requested: later kernels must still see the data
+  return order_streams(ctx, D.copy, D.compute, ZYXB_ERR_MEMORY_COPY_H2P);
+}
+
+int32_t zyxb_d2h(zyxb_ctx* ctx, int32_t dev, uint32_t src, uint64_t src_offset, void* dst, uint64_t bytes,
+                 const zyxb_event* wait, int32_t n_wait) {
+  DEV_OR_FAIL(ZYXB_ERR_MEMORY_COPY_P2H);
+  Buffer* b = get_buffer(D, src);
+  if (!b || b->is_variable) return fail(ctx, ZYXB_ERR_MEMORY_COPY_P2H, "d2h: unknown buffer");
+  if (src_offset + bytes > b->bytes) return fail(ctx, ZYXB_ERR_MEMORY_COPY_P2H, "d2h: copy exceeds the buffer");
+  int st = wait_and_consume(ctx, D, D.compute, wait, n_wait, ZYXB_ERR_MEMORY_COPY_P2H);
+  if (st) return st;
+  cudaError_t e = cudaSuccess;
+  if (bytes) e = cudaMemcpyAsync(dst, (const char*)b->ptr + src_offset, bytes, cudaMemcpyDeviceToHost, D.compute);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(D.compute);
+  if (e != cudaSuccess) return cuda_fail(ctx, ZYXB_ERR_MEMORY_COPY_P2H, "d2h", e);
+  return ZYXB_OK;
+}
+
+int32_t zyxb_d2d(zyxb_ctx* ctx, int32_t src_dev, uint32_t src, uint64_t src_offset, int32_t dev, uint32_t dst, uint64_t dst_offset,
+                 uint64_t bytes, const zyxb_event* wait, int32_t n_wait, zyxb_event* out_event) {
+  DEV_OR_FAIL(ZYXB_ERR_MEMORY_COPY_H2P);
+  if (src_dev < 0 || src_dev >= (int)ctx->devs.size()) return fail(ctx, ZYXB_ERR_MEMORY_COPY_H2P, "d2d: no such source device");
+  Device& SD = ctx->devs[src_dev];
+  Buffer* sb = get_buffer(SD, src);
+  Buffer* db = get_buffer(D, dst);
+  if (!sb || !db || sb->is_variable || db->is_variable) return fail(ctx, ZYXB_ERR_MEMORY_COPY_H2P, "d2d: unknown buffer");
+  if (src_offset + bytes > sb->bytes || dst_offset + bytes > db->bytes) return fail(ctx, ZYXB_ERR_MEMORY_COPY_H2P, "d2d: copy exceeds a buffer");
+  int st = wait_and_consume(ctx, D, D.compute, wait, n_wait, ZYXB_ERR_MEMORY_COPY_H2P);
+  if (st) return st;
+  cudaError_t e = cudaSuccess;
+  if (src_dev == dev) e = cudaMemcpyAsync((char*)db->ptr + dst_offset, (const char*)sb->ptr + src_offset, bytes, cudaMemcpyDeviceToDevice, D.compute);
+  else {
+    if ((st = order_streams(ctx, SD.compute, D.compute, ZYXB_ERR_MEMORY_COPY_H2P))) return st;
+    e = cudaMemcpyPeerAsync((char*)db->ptr + dst_offset, D.cuda_id, (const char*)sb->ptr + src_offset, SD.cuda_id, bytes, D.compute);
+  }
+  if (e != cudaSuccess) return cuda_fail(ctx, ZYXB_ERR_MEMORY_COPY_H2P, "d2d", e);
+  return record_event(ctx, D, D.compute, out_event, ZYXB_ERR_MEMORY_COPY_H2P);
+}
+
+int32_t zyxb_memset(zyxb_ctx* ctx, int32_t dev, uint32_t buf, uint64_t offset, int32_t byte_value, uint64_t bytes) {
+  DEV_OR_FAIL(ZYXB_ERR_MEMORY_COPY_H2P);
+  Buffer* b = get_buffer(D, buf);
+  if (!b || b->is_variable) return fail(ctx, ZYXB_ERR_MEMORY_COPY_H2P, "memset: unknown buffer");
+  if (offset + bytes > b->bytes) return fail(ctx, ZYXB_ERR_MEMORY_COPY_H2P, "memset: range exceeds the buffer");
+  cudaError_t e = cudaMemsetAsync((char*)b->ptr + offset, byte_value, bytes, D.compute);
+  if (e != cudaSuccess) return cuda_fail(ctx, ZYXB_ERR_MEMORY_COPY_H2P, "cudaMemsetAsync", e);
+  return ZYXB_OK;
+}
+
+int32_t zyxb_sync(zyxb_ctx* ctx, int32_t dev, const zyxb_event* events, int32_t n) {
+  DEV_OR_FAIL(ZYXB_ERR_KERNEL_SYNC);
+  int status = ZYXB_OK;
+  for (int i = 0; i < n; ++i) {
+    if (events[i].id == 0) continue;
+    auto it = D.events.find(events[i].id);
+    if (it == D.events.end()) { status = fail(ctx, ZYXB_ERR_KERNEL_SYNC, "sync: unknown event"); continue; }
+    cudaError_t e = cudaEventSynchronize(it->second);
+    cudaEventDestroy(it->second);
+    D.events.erase(it);
+    if (e != cudaSuccess) status = cuda_fail(ctx, ZYXB_ERR_KERNEL_SYNC, "cudaEventSynchronize", e);
+  }
+  return status;
+}
+
+int32_t zyxb_release_events(zyxb_ctx* ctx, int32_t dev, const zyxb_event* events, int32_t n) {
+  DEV_OR_FAIL(ZYXB_ERR_KERNEL_SYNC);
+  for (int i = 0; i < n; ++i) {
+    auto it = D.events.find(events[i].id);
+    if (it == D.events.end()) continue;
+    cudaEventDestroy(it->second);
+    D.events.erase(it);
+  }
+  return ZYXB_OK;
+}
+
+int32_t zyxb_device_sync(zyxb_ctx* ctx, int32_t dev) {
+  DEV_OR_FAIL(ZYXB_ERR_KERNEL_SYNC);
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) return cuda_fail(ctx, ZYXB_ERR_KERNEL_SYNC, "cudaDeviceSynchronize", e);
+  return ZYXB_OK;
+}
+
+int32_t zyxb_store_variable(zyxb_ctx* ctx, int32_t dev, int32_t dtype, const void* le_bytes, uint32_t* out_buf) {
+  DEV_OR_FAIL(ZYXB_ERR_MEMORY_ALLOCATION);
+  if (!le_bytes || !out_buf || dtype < 0 || dtype > ZYXB_BOOL) return fail(ctx, ZYXB_ERR_MEMORY_ALLOCATION, "store_variable: bad argument");
+  uint32_t id;
+  if (!D.free_buffer_ids.empty()) { id = D.free_buffer_ids.back(); D.free_buffer_ids.pop_back(); }
+  else { id = (uint32_t)D.buffers.size(); D.buffers.emplace_back(); }
+  Buffer& b = D.buffers[id];
+  b = Buffer();
+  b.live = true; b.is_variable = true; b.var_dtype = dtype; b.bytes = dtype_size(dtype);
+  memcpy(b.var_bytes, le_bytes, b.bytes);
+  *out_buf = id;
+  return ZYXB_OK;
+}
+
+int32_t zyxb_get_variable(zyxb_ctx* ctx, int32_t dev, uint32_t buf, int32_t* out_dtype, void* out_le_bytes) {
+  DEV_OR_FAIL(ZYXB_ERR_INCORRECT_KERNEL_ARG);
+  Buffer* b = get_buffer(D, buf);
+  if (!b || !b->is_variable) return fail(ctx, ZYXB_ERR_INCORRECT_KERNEL_ARG, "get_variable: not a variable");
+  if (out_dtype) *out_dtype = b->var_dtype;
+  if (out_le_bytes) memcpy(out_le_bytes, b->var_bytes, b->bytes);
+  return ZYXB_OK;
+}
+
+int32_t zyxb_host_register(zyxb_ctx* ctx, void* ptr, uint64_t bytes) {
+  if (!ctx) return ZYXB_ERR_INITIALIZATION;
+  cudaSetDevice(ctx->devs[0].cuda_id);
+  cudaError_t e = cudaHostRegister(ptr, bytes, cudaHostRegisterPortable);
+  if (e != cudaSuccess) { cudaGetLastError(); return cuda_fail(ctx, ZYXB_ERR_MEMORY_ALLOCATION, "cudaHostRegister", e); }
+  ctx->registered[ptr] = 1;
+  return ZYXB_OK;
+}
+
+int32_t zyxb_host_unregister(zyxb_ctx* ctx, void* ptr) {
+  if (!ctx) return ZYXB_ERR_INITIALIZATION;
+  auto it = ctx->registered.find(ptr);
+  if (it == ctx->registered.end()) return fail(ctx, ZYXB_ERR_MEMORY_DEALLOCATION, "host_unregister: range was not registered");
+  cudaSetDevice(ctx->devs[0].cuda_id);
+  cudaDeviceSynchronize();
+  cudaHostUnregister(ptr);
+  ctx->registered.erase(it);
+  return ZYXB_OK;
+}
+
+// ---- programs --------------------------------------------------------------------------------
+int32_t zyxb_program_create(zyxb_ctx* ctx, int32_t dev, const zyxb_kernel_desc* desc, uint32_t* out_prog) {
+  DEV_OR_FAIL(ZYXB_ERR_KERNEL_COMPILATION);
+  if (!desc || !out_prog) return fail(ctx, ZYXB_ERR_KERNEL_COMPILATION, "program_create: null argument");
+  std::string err;
+  int st;
+  switch (desc->kind) {
+    case ZYXB_KIND_ROWREDUCE: st = validate_rowreduce(desc->u.rowreduce, err); break;
+    case ZYXB_KIND_GEMM: st = validate_gemm(desc->u.gemm, err); break;
+    case ZYXB_KIND_ELTWISE: st = validate_eltwise(desc->u.eltwise, err); break;
+    case ZYXB_KIND_OPTIM: st = validate_optim(desc->u.optim, err); break;
+    default: st = ZYXB_ERR_KERNEL_COMPILATION; err = "unknown kernel kind";
+  }
+  if (st) return fail(ctx, st, err);
+  uint32_t id;
+  if (!D.free_program_ids.empty()) { id = D.free_program_ids.back(); D.free_program_ids.pop_back(); }
+  else { id = (uint32_t)D.programs.size(); D.programs.emplace_back(); }
+  Program& P = D.programs[id];
+  P = Program();
+  P.desc = *desc; P.live = true;
+  if (desc->kind == ZYXB_KIND_OPTIM) {
+    P.numel.assign(desc->u.optim.numel, desc->u.optim.numel + desc->u.optim.n_tensors);
+    P.desc.u.optim.numel = nullptr;   // the caller's array need not outlive this call
+  }
+  *out_prog = id;
+  return ZYXB_OK;
+}
+
+int32_t zyxb_program_release(zyxb_ctx* ctx, int32_t dev, uint32_t prog) {
+  DEV_OR_FAIL(ZYXB_ERR_KERNEL_COMPILATION);
+  if (prog == 0 || prog >= D.programs.size() || !D.programs[prog].live) return fail(ctx, ZYXB_ERR_KERNEL_COMPILATION, "release: unknown program");
+  D.programs[prog] = Program();
+  D.free_program_ids.push_back(prog);
+  return ZYXB_OK;
+}
+
+int32_t zyxb_program_set_step(zyxb_ctx* ctx, int32_t dev, uint32_t prog, uint64_t t) {
+  DEV_OR_FAIL(ZYXB_ERR_INCORRECT_KERNEL_ARG);
+  if (prog == 0 || prog >= D.programs.size() || !D.programs[prog].live || D.programs[prog].desc.kind != ZYXB_KIND_OPTIM)
+    return fail(ctx, ZYXB_ERR_INCORRECT_KERNEL_ARG, "set_step: not an optimizer program");
+  D.programs[prog].step = t;
+  return ZYXB_OK;
+}
+
+int32_t zyxb_launch(zyxb_ctx* ctx, int32_t dev, uint32_t prog, const uint32_t* args, int32_t n_args, const zyxb_event* wait,
+                    int32_t n_wait, zyxb_event* out_event) {
+  DEV_OR_FAIL(ZYXB_ERR_KERNEL_LAUNCH);
+  if (prog == 0 || prog >= D.programs.size() || !D.programs[prog].live) return fail(ctx, ZYXB_ERR_KERNEL_LAUNCH, "launch: unknown program");
+  if (n_args < 0 || n_args > 4096 || (n_args > 0 && !args)) return fail(ctx, ZYXB_ERR_INCORRECT_KERNEL_ARG, "launch: bad argument list");
+  Program& P = D.programs[prog];
+  std::vector<void*> ptrs(n_args);
+  std::vector<uint64_t> sizes(n_args);
+  for (int i = 0; i < n_args; ++i) {
+    Buffer* b = get_buffer(D, args[i]);
+    if (!b || b->is_variable) return fail(ctx, ZYXB_ERR_INCORRECT_KERNEL_ARG, "launch: argument " + std::to_string(i) + " is not a pool buffer");
+    ptrs[i] = b->ptr; sizes[i] = b->bytes;
+  }
+  int st = wait_and_consume(ctx, D, D.compute, wait, n_wait, ZYXB_ERR_KERNEL_LAUNCH);
+  if (st) return st;
+  LaunchCtx lc = make_launch_ctx(ctx, D);
+  std::string err;
+  switch (P.desc.kind) {
+    case ZYXB_KIND_ROWREDUCE: st = launch_rowreduce(P.desc.u.rowreduce, ptrs.data(), sizes.data(), n_args, lc, err); break;
+    case ZYXB_KIND_GEMM: st = launch_gemm(P.desc.u.gemm, ptrs.data(), sizes.data(), n_args, lc, err); break;
+    case ZYXB_KIND_ELTWISE: st = launch_eltwise(P.desc.u.eltwise, ptrs.data(), sizes.data(), n_args, lc, err); break;
+    case ZYXB_KIND_OPTIM:
+      st = launch_optim(P.desc.u.optim, P.numel.data(), P.step + 1, ptrs.data(), sizes.data(), n_args, lc, err);
+      if (st == ZYXB_OK) P.step += 1;
+      break;
+    default: st = ZYXB_ERR_KERNEL_LAUNCH; err = "launch: unknown kernel kind";
+  }
+  if (st) return fail(ctx, st, err);
+  if (ctx->debug & 1) fprintf(stderr, "[zyxb] launch program %u kind %d\n", prog, P.desc.kind);
+  return record_event(ctx, D, D.compute, out_event, ZYXB_ERR_KERNEL_LAUNCH);
+}
+
+int32_t zyxb_launch_count(zyxb_ctx* ctx, int32_t dev, uint64_t* out_count) {
+  DEV_OR_FAIL(ZYXB_ERR_DEVICE_QUERY);
+  if (out_count) *out_count = D.launch_count;
+  return ZYXB_OK;
+}
+
+int32_t zyxb_device_status(zyxb_ctx* ctx, int32_t dev, uint32_t* out_status) {
+  DEV_OR_FAIL(ZYXB_ERR_KERNEL_SYNC);
+  uint32_t w = 0;
+  cudaError_t e = cudaStreamSynchronize(D.compute);
+  if (e == cudaSuccess) e = cudaMemcpy(&w, D.status_word, 4, cudaMemcpyDeviceToHost);
+  if (e == cudaSuccess && w != 0) e = cudaMemset(D.status_word, 0, 4);
+  if (e != cudaSuccess) return cuda_fail(ctx, ZYXB_ERR_KERNEL_SYNC, "device_status", e);
+  if (out_status) *out_status = w;
+  if (w != 0) return fail(ctx, ZYXB_ERR_KERNEL_SYNC, "a kernel gave up a bounded wait (status word " + std::to_string(w) + ")");
+  return ZYXB_OK;
+}
+
+// ---- timing -------------------------------------------------------------------------------------
+int32_t zyxb_event_record(zyxb_ctx* ctx, int32_t dev, zyxb_event* out_event) {
+  DEV_OR_FAIL(ZYXB_ERR_KERNEL_SYNC);
+  if (!out_event) return fail(ctx, ZYXB_ERR_KERNEL_SYNC, "event_record: null");
+  return record_event(ctx, D, D.compute, out_event, ZYXB_ERR_KERNEL_SYNC, true);
+}
+
+int32_t zyxb_event_elapsed_ms(zyxb_ctx* ctx, int32_t dev, zyxb_event start, zyxb_event stop, float* out_ms) {
+  DEV_OR_FAIL(ZYXB_ERR_KERNEL_SYNC);
+  auto a = D.events.find(start.id), b = D.events.find(stop.id);
+  if (a == D.events.end() || b == D.events.end()) return fail(ctx, ZYXB_ERR_KERNEL_SYNC, "event_elapsed: unknown event");
+  cudaError_t e = cudaEventSynchronize(b->second);
+  float ms = 0.0f;
+  if (e == cudaSuccess) e = cudaEventElapsedTime(&ms, a->second, b->second);
+  if (e != cudaSuccess) return cuda_fail(ctx, ZYXB_ERR_KERNEL_SYNC, "cudaEventElapsedTime", e);
+  if (out_ms) *out_ms = ms;
+  return ZYXB_OK;
+}
+
+int32_t zyxb_flush_l2(zyxb_ctx* ctx, int32_t dev) {
+  DEV_OR_FAIL(ZYXB_ERR_KERNEL_LAUNCH);
+  if (!D.flush_buf) {
+    D.flush_bytes = 256ull << 20;   // twice the 126 MB L2
+    cudaError_t e = cudaMalloc(&D.flush_buf, D.flush_bytes);
+    if (e != cudaSuccess) { cudaGetLastError(); D.flush_buf = nullptr; return cuda_fail(ctx, ZYXB_ERR_MEMORY_ALLOCATION, "flush buffer", e); }
+  }
+  cudaError_t e = cudaMemsetAsync(D.flush_buf, 0, D.flush_bytes, D.compute);
+  if (e != cudaSuccess) return cuda_fail(ctx, ZYXB_ERR_KERNEL_LAUNCH, "flush_l2", e);
+  return ZYXB_OK;
+}
+
+// ---- collectives ------------------------------------------------------------------------------------
+int32_t zyxb_comm_unique_id(zyxb_ctx* ctx, void* out_id_128_bytes) {
+  if (!ctx) return ZYXB_ERR_INITIALIZATION;
+  std::string err;
+  int st = comm_unique_id(out_id_128_bytes, err);
+  if (st) return fail(ctx, st, err);
+  return ZYXB_OK;
+}
+
+int32_t zyxb_comm_init(zyxb_ctx* ctx, int32_t dev, int32_t rank, int32_t world, const void* id_128_bytes) {
+  DEV_OR_FAIL(ZYXB_ERR_INITIALIZATION);
+  if (D.comm) return fail(ctx, ZYXB_ERR_INITIALIZATION, "comm_init: communicator already exists");
+  std::string err;
+  int st = comm_create(&D.comm, rank, world, id_128_bytes, err);
+  if (st) return fail(ctx, st, err);
+  return ZYXB_OK;
+}
+
+int32_t zyxb_allreduce_sum(zyxb_ctx* ctx, int32_t dev, uint32_t buf, uint64_t offset_elems, uint64_t count, int32_t dtype,
+                           const zyxb_event* wait, int32_t n_wait, zyxb_event* out_event) {
+  DEV_OR_FAIL(ZYXB_ERR_KERNEL_LAUNCH);
+  if (!D.comm) return fail(ctx, ZYXB_ERR_KERNEL_LAUNCH, "allreduce: no communicator (call zyxb_comm_init)");
+  Buffer* b = get_buffer(D, buf);
+  if (!b || b->is_variable) return fail(ctx, ZYXB_ERR_INCORRECT_KERNEL_ARG, "allreduce: unknown buffer");
+  const uint64_t es = dtype_size(dtype);
+  if ((offset_elems + count) * es > b->bytes) return fail(ctx, ZYXB_ERR_INCORRECT_KERNEL_ARG, "allreduce: range exceeds the buffer");
+  int st = wait_and_consume(ctx, D, D.comm_stream, wait, n_wait, ZYXB_ERR_KERNEL_LAUNCH);
+  if (st) return st;
+  // the producer kernels were enqueued on the compute stream before this call
+  if ((st = order_streams(ctx, D.compute, D.comm_stream, ZYXB_ERR_KERNEL_LAUNCH))) return st;
+  std::string err;
+  char* p = (char*)b->ptr + offset_elems * es;
+  st = comm_allreduce_sum(D.comm, p, p, count, dtype, D.comm_stream, err);
+  if (st) return fail(ctx, st, err);
+  if (out_event) return record_event(ctx, D, D.comm_stream, out_event, ZYXB_ERR_KERNEL_LAUNCH);
+  return order_streams(ctx, D.comm_stream, D.compute, ZYXB_ERR_KERNEL_LAUNCH);
+}
+
+int32_t zyxb_comm_destroy(zyxb_ctx* ctx, int32_t dev) {
+  DEV_OR_FAIL(ZYXB_ERR_DEINITIALIZATION);
+  if (D.comm) { cudaDeviceSynchronize(); comm_destroy(D.comm); D.comm = nullptr; }
+  return ZYXB_OK;
+}
+
+#pragma GCC visibility pop
+}  // extern "C"

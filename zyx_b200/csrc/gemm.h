@@ -1,0 +1,26 @@
+// Matmul launch parameters shared by the SIMT and tensor-core paths.
+#pragma once
+#include <type_traits>
+
+#include "internal.h"
+
+namespace zyxb {
+
+struct GemmParams {
+  const void* a; const void* b; const void* bias;
+  void* c; void* preact;
+  uint64_t m, n, k, batch;
+  int64_t stride_a, stride_b, stride_c;   // elements between consecutive batches
+  int trans_a, trans_b;                   // A stored [k,m] / B stored [n,k]
+  int epilogue;
+  float alpha;
+  int rn;
+  bool vec_a, vec_b;
+};
+
+int launch_gemm_simt(GemmParams p, int dtype, const LaunchCtx& lc, std::string& err);
+// Tensor-core path (tcgen05 + TMEM + TMA).  Returns true when the shape is one it takes.
+bool gemm_tc_supported(const GemmParams& p, int dtype, const LaunchCtx& lc);
+int launch_gemm_tc(const GemmParams& p, int dtype, const LaunchCtx& lc, std::string& err);
+
+}  // namespace zyxb

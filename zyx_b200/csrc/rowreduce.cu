@@ -1,0 +1,229 @@
+// Host-side dispatch of the row kernels, plus the reductions that cross rows:
+// column sums (bias gradients), the mean of per-sample losses and the MSE loss.
+#include <algorithm>
+
+#include "rowreduce_impl.cuh"
+
+namespace zyxb {
+
+void launch_row_i32(const RowParams& p, cudaStream_t s) { launch_row_family<int32_t, FAM_REDUCE>(p, s); }
+
+// ---- mean over rows of the per-sample losses (cross_entropy ReduceOp::Mean,
+//      zyx/src/tensor/mod.rs:1650) --------------------------------------------------------------
+__global__ void __launch_bounds__(256) mean_of_rows_kernel(const float* per, float* out, uint64_t rows) {
+  __shared__ float red[32];
+  float acc = 0.0f;
+  for (uint64_t r = threadIdx.x; r < rows; r += 256) acc += per[r];
+  acc = group_reduce<256>(acc, OpSum(), red, 0.0f);
+  if (threadIdx.x == 0) out[0] = acc / (float)rows;
+}
+
+// ---- column sums: y[j] = sum_r x[r, j] -----------------------------------------------------
+// Stage 1: each CTA owns 128*VEC columns and one slice of the rows; a warp reads consecutive
+// vectors of one row (coalesced).  Partials go to scratch as f32 [splits, cols].
+// Stage 2 folds the splits in order and stores in the tensor dtype.
+template <typename T, int VEC>
+__global__ void __launch_bounds__(128) colsum_partial_kernel(const typename Elem<T>::store_t* x, float* partial, uint64_t rows,
+                                                             uint64_t cols, uint64_t rows_per_split) {
+  using S = typename Elem<T>::store_t;
+  const uint64_t c = ((uint64_t)blockIdx.x * 128 + threadIdx.x) * VEC;
+  if (c >= cols) return;
+  const uint64_t r0 = (uint64_t)blockIdx.y * rows_per_split;
+  const uint64_t r1 = min(r0 + rows_per_split, rows);
+  float acc[VEC];
+#pragma unroll
+  for (int k = 0; k < VEC; ++k) acc[k] = 0.0f;
+  uint64_t r = r0;
+  for (; r + 4 <= r1; r += 4) {   // four independent loads in flight per thread
+    Pack<S, VEC> pk[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) pk[u] = load_pack_stream<S, VEC>(x + (r + u) * cols + c);
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) acc[k] += (float)Elem<T>::load(pk[u].v[k]);
+  }
+  for (; r < r1; ++r) {
+    Pack<S, VEC> pk = load_pack_stream<S, VEC>(x + r * cols + c);
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) acc[k] += (float)Elem<T>::load(pk.v[k]);
+  }
+#pragma unroll
+  for (int k = 0; k < VEC; ++k) partial[(uint64_t)blockIdx.y * cols + c + k] = acc[k];
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) colsum_final_kernel(const float* partial, typename Elem<T>::store_t* y, uint64_t cols,
+                                                           uint32_t splits, int rn) {
+  const uint64_t c = (uint64_t)blockIdx.x * 256 + threadIdx.x;
+  if (c >= cols) return;
+  float acc = 0.0f;
+  for (uint32_t s = 0; s < splits; ++s) acc += partial[(uint64_t)s * cols + c];
+  y[c] = Elem<T>::store(acc, rn != 0);
+}
+
+template <typename T>
+static int launch_colsum(const void* x, void* y, uint64_t rows, uint64_t cols, const LaunchCtx& lc, std::string& err) {
+  using S = typename Elem<T>::store_t;
+  constexpr int V = 16 / sizeof(S);
+  const bool vec_ok = cols % V == 0 && (uintptr_t)x % 16 == 0;
+  const uint64_t per_cta = 128ull * (vec_ok ? V : 1);
+  const uint64_t col_blocks = (cols + per_cta - 1) / per_cta;
+  uint64_t splits = (4ull * lc.sm_count + col_blocks - 1) / col_blocks;
+  splits = std::max<uint64_t>(1, std::min<uint64_t>({splits, rows, 1024ull, lc.scratch_bytes / (cols * sizeof(float))}));
+  ZYXB_CHECK_ARG(cols * sizeof(float) <= lc.scratch_bytes, "colsum: cols too large for the scratch buffer");
+  ZYXB_CHECK_ARG(col_blocks <= 0x7fffffffull, "colsum: too many columns");
+  const uint64_t rps = (rows + splits - 1) / splits;
+  splits = (rows + rps - 1) / rps;
+  dim3 grid((unsigned)col_blocks, (unsigned)splits);
+  float* partial = reinterpret_cast<float*>(lc.scratch);
+  if (vec_ok) colsum_partial_kernel<T, V><<<grid, 128, 0, lc.stream>>>((const S*)x, partial, rows, cols, rps);
+  else colsum_partial_kernel<T, 1><<<grid, 128, 0, lc.stream>>>((const S*)x, partial, rows, cols, rps);
+  colsum_final_kernel<T><<<(unsigned)((cols + 255) / 256), 256, 0, lc.stream>>>(partial, (S*)y, cols, (uint32_t)splits, lc.round_nearest);
+  return check_launch(lc, err, "colsum", 2);
+}
+
+// ---- MSE loss: mean((y - t)^2) over every element, f32 result ---------------------------------
+template <typename T, int VEC>
+__global__ void __launch_bounds__(256) mse_partial_kernel(const typename Elem<T>::store_t* y, const typename Elem<T>::store_t* t,
+                                                          float* partial, uint64_t n_vec) {
+  using S = typename Elem<T>::store_t;
+  __shared__ float red[32];
+  float acc = 0.0f;
+  for (uint64_t i = (uint64_t)blockIdx.x * 256 + threadIdx.x; i < n_vec; i += (uint64_t)gridDim.x * 256) {
+    Pack<S, VEC> a = load_pack_stream<S, VEC>(y + i * VEC), b = load_pack_stream<S, VEC>(t + i * VEC);
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) { const float d = (float)Elem<T>::load(a.v[k]) - (float)Elem<T>::load(b.v[k]); acc = fmaf(d, d, acc); }
+  }
+  acc = group_reduce<256>(acc, OpSum(), red, 0.0f);
+  if (threadIdx.x == 0) partial[blockIdx.x] = acc;
+}
+__global__ void __launch_bounds__(256) mse_final_kernel(const float* partial, float* out, uint32_t n_partial, double inv_n) {
+  __shared__ double red[32];
+  double acc = 0.0;
+  for (uint32_t i = threadIdx.x; i < n_partial; i += 256) acc += (double)partial[i];
+  acc = group_reduce<256>(acc, OpSum(), red, 0.0);
+  if (threadIdx.x == 0) out[0] = (float)(acc * inv_n);
+}
+template <typename T>
+static int launch_mse(const void* y, const void* t, void* out, uint64_t n, const LaunchCtx& lc, std::string& err) {
+  using S = typename Elem<T>::store_t;
+  constexpr int V = 16 / sizeof(S);
+  const bool vec_ok = n % V == 0 && (uintptr_t)y % 16 == 0 && (uintptr_t)t % 16 == 0;
+  const uint64_t n_vec = vec_ok ? n / V : n;
+  uint32_t grid = (uint32_t)std::min<uint64_t>((n_vec + 255) / 256, 8ull * lc.sm_count);
+  grid = std::max(grid, 1u);
+  ZYXB_CHECK_ARG(grid * sizeof(float) <= lc.scratch_bytes, "mse: scratch too small");
+  float* partial = reinterpret_cast<float*>(lc.scratch);
+  if (vec_ok) mse_partial_kernel<T, V><<<grid, 256, 0, lc.stream>>>((const S*)y, (const S*)t, partial, n_vec);
+  else mse_partial_kernel<T, 1><<<grid, 256, 0, lc.stream>>>((const S*)y, (const S*)t, partial, n_vec);
+  mse_final_kernel<<<1, 256, 0, lc.stream>>>(partial, (float*)out, grid, 1.0 / (double)n);
+  return check_launch(lc, err, "mse", 2);
+}
+
+// ---- validation and dispatch ---------------------------------------------------------------------
+static bool is_float_dtype(int d) { return d == ZYXB_F32 || d == ZYXB_BF16 || d == ZYXB_F16; }
+
+int validate_rowreduce(const zyxb_rowreduce_desc& d, std::string& err) {
+  if (d.op < ZYXB_RR_SUM || d.op > ZYXB_RR_MSE) { err = "rowreduce: unknown op"; return ZYXB_ERR_KERNEL_COMPILATION; }
+  if (d.rows == 0 || d.cols == 0) { err = "rowreduce: rows and cols must be positive"; return ZYXB_ERR_KERNEL_COMPILATION; }
+  if (d.rows > 0x7fffffffull) { err = "rowreduce: more than 2^31-1 rows"; return ZYXB_ERR_KERNEL_COMPILATION; }
+  const bool int_ok = d.dtype == ZYXB_I32 && (d.op == ZYXB_RR_SUM || d.op == ZYXB_RR_MAX || d.op == ZYXB_RR_MIN);
+  if (!is_float_dtype(d.dtype) && !int_ok) { err = "rowreduce: dtype not supported for this op"; return ZYXB_ERR_KERNEL_COMPILATION; }
+  if ((d.op == ZYXB_RR_CROSS_ENTROPY || d.op == ZYXB_RR_CROSS_ENTROPY_BWD) && d.dtype != ZYXB_F32) {
+    err = "cross_entropy: logits must be f32"; return ZYXB_ERR_KERNEL_COMPILATION;
+  }
+  if (d.causal && d.period == 0) { err = "softmax: causal mask needs period > 0"; return ZYXB_ERR_KERNEL_COMPILATION; }
+  if ((d.op == ZYXB_RR_VAR || d.op == ZYXB_RR_STD) && (int64_t)d.cols - d.correction <= 0) {
+    err = "var: cols - correction must be positive"; return ZYXB_ERR_KERNEL_COMPILATION;
+  }
+  if ((d.op == ZYXB_RR_LAYERNORM || d.op == ZYXB_RR_LAYERNORM_BWD) && d.cols < 2) {
+    err = "layernorm: unbiased variance needs at least 2 columns"; return ZYXB_ERR_KERNEL_COMPILATION;
+  }
+  return ZYXB_OK;
+}
+
+int launch_rowreduce(const zyxb_rowreduce_desc& d, void* const* args, const uint64_t* arg_bytes, int n_args, const LaunchCtx& lc,
+                     std::string& err) {
+  const uint64_t es = dtype_size(d.dtype);
+  const uint64_t full = d.rows * d.cols * es;
+  RowParams p{};
+  p.rows = d.rows; p.cols = d.cols; p.op = d.op; p.correction = d.correction; p.eps = d.eps;
+  p.scale = d.scale == 0.0f ? 1.0f : d.scale; p.causal = d.causal; p.period = d.period; p.rn = lc.round_nearest ? 1 : 0;
+  int fam = -1;
+  switch (d.op) {
+    case ZYXB_RR_SUM: case ZYXB_RR_MAX: case ZYXB_RR_MIN: case ZYXB_RR_MEAN: case ZYXB_RR_VAR: case ZYXB_RR_STD:
+      ZYXB_CHECK_ARG(n_args == 2, "reduce: expected args x -> y");
+      ZYXB_CHECK_ARG(arg_bytes[0] >= full && arg_bytes[1] >= d.rows * es, "reduce: buffer too small");
+      p.x = args[0]; p.y = args[1]; fam = FAM_REDUCE; break;
+    case ZYXB_RR_SOFTMAX: case ZYXB_RR_LN_SOFTMAX:
+      ZYXB_CHECK_ARG(n_args == 2, "softmax: expected args x -> y");
+      ZYXB_CHECK_ARG(arg_bytes[0] >= full && arg_bytes[1] >= full, "softmax: buffer too small");
+      p.x = args[0]; p.y = args[1]; fam = FAM_SOFTMAX; break;
+    case ZYXB_RR_LAYERNORM: {
+      const int want = 2 + (d.has_weight ? 1 : 0) + (d.has_bias ? 1 : 0);
+      ZYXB_CHECK_ARG(n_args == want, "layernorm: expected args x [,weight][,bias] -> y");
+      int i = 0; p.x = args[i++];
+      ZYXB_CHECK_ARG(arg_bytes[0] >= full, "layernorm: x too small");
+      if (d.has_weight) { ZYXB_CHECK_ARG(arg_bytes[i] >= d.cols * es, "layernorm: weight too small"); p.w = args[i++]; }
+      if (d.has_bias) { ZYXB_CHECK_ARG(arg_bytes[i] >= d.cols * es, "layernorm: bias too small"); p.b = args[i++]; }
+      ZYXB_CHECK_ARG(arg_bytes[i] >= full, "layernorm: y too small");
+      p.y = args[i]; fam = FAM_LAYERNORM; break;
+    }
+    case ZYXB_RR_SOFTMAX_BWD:
+      ZYXB_CHECK_ARG(n_args == 3, "softmax_bwd: expected args p, dp -> ds");
+      ZYXB_CHECK_ARG(arg_bytes[0] >= full && arg_bytes[1] >= full && arg_bytes[2] >= full, "softmax_bwd: buffer too small");
+      p.x = args[0]; p.x2 = args[1]; p.y = args[2]; fam = FAM_SOFTMAX_BWD; break;
+    case ZYXB_RR_LAYERNORM_BWD: {
+      const int want = 3 + (d.has_weight ? 1 : 0);
+      ZYXB_CHECK_ARG(n_args == want, "layernorm_bwd: expected args x, dy [,weight] -> dx");
+      ZYXB_CHECK_ARG(arg_bytes[0] >= full && arg_bytes[1] >= full && arg_bytes[want - 1] >= full, "layernorm_bwd: buffer too small");
+      p.x = args[0]; p.x2 = args[1];
+      if (d.has_weight) { ZYXB_CHECK_ARG(arg_bytes[2] >= d.cols * es, "layernorm_bwd: weight too small"); p.w = args[2]; }
+      p.y = args[want - 1]; fam = FAM_LAYERNORM_BWD; break;
+    }
+    case ZYXB_RR_CROSS_ENTROPY: {
+      ZYXB_CHECK_ARG(n_args == 4, "cross_entropy: expected args logits, labels -> per_sample, mean");
+      ZYXB_CHECK_ARG(arg_bytes[0] >= full && arg_bytes[1] >= d.rows * 4 && arg_bytes[2] >= d.rows * 4 && arg_bytes[3] >= 4,
+                     "cross_entropy: buffer too small");
+      p.x = args[0]; p.x2 = args[1]; p.y = args[2];
+      launch_row_f32(FAM_CE, p, lc.stream);
+      mean_of_rows_kernel<<<1, 256, 0, lc.stream>>>((const float*)args[2], (float*)args[3], d.rows);
+      return check_launch(lc, err, "cross_entropy", 2);
+    }
+    case ZYXB_RR_CROSS_ENTROPY_BWD:
+      ZYXB_CHECK_ARG(n_args == 3, "cross_entropy_bwd: expected args logits, labels -> dlogits");
+      ZYXB_CHECK_ARG(arg_bytes[0] >= full && arg_bytes[1] >= d.rows * 4 && arg_bytes[2] >= full, "cross_entropy_bwd: buffer too small");
+      p.x = args[0]; p.x2 = args[1]; p.y = args[2];
+      launch_row_f32(FAM_CE, p, lc.stream);
+      return check_launch(lc, err, "cross_entropy_bwd");
+    case ZYXB_RR_COLSUM:
+      ZYXB_CHECK_ARG(n_args == 2, "colsum: expected args x -> y");
+      ZYXB_CHECK_ARG(arg_bytes[0] >= full && arg_bytes[1] >= d.cols * es, "colsum: buffer too small");
+      switch (d.dtype) {
+        case ZYXB_F32: return launch_colsum<float>(args[0], args[1], d.rows, d.cols, lc, err);
+        case ZYXB_BF16: return launch_colsum<bf16_t>(args[0], args[1], d.rows, d.cols, lc, err);
+        default: return launch_colsum<f16_t>(args[0], args[1], d.rows, d.cols, lc, err);
+      }
+    case ZYXB_RR_MSE:
+      ZYXB_CHECK_ARG(n_args == 3, "mse: expected args y, t -> loss");
+      ZYXB_CHECK_ARG(arg_bytes[0] >= full && arg_bytes[1] >= full && arg_bytes[2] >= 4, "mse: buffer too small");
+      switch (d.dtype) {
+        case ZYXB_F32: return launch_mse<float>(args[0], args[1], args[2], d.rows * d.cols, lc, err);
+        case ZYXB_BF16: return launch_mse<bf16_t>(args[0], args[1], args[2], d.rows * d.cols, lc, err);
+        default: return launch_mse<f16_t>(args[0], args[1], args[2], d.rows * d.cols, lc, err);
+      }
+    default:
+      err = "rowreduce: unknown op"; return ZYXB_ERR_INCORRECT_KERNEL_ARG;
+  }
+  switch (d.dtype) {
+    case ZYXB_F32: launch_row_f32(fam, p, lc.stream); break;
+    case ZYXB_BF16: launch_row_bf16(fam, p, lc.stream); break;
+    case ZYXB_F16: launch_row_f16(fam, p, lc.stream); break;
+    case ZYXB_I32: launch_row_i32(p, lc.stream); break;
+    default: err = "rowreduce: dtype"; return ZYXB_ERR_INCORRECT_KERNEL_ARG;
+  }
+  return check_launch(lc, err, "rowreduce");
+}
+
+}  // namespace zyxb

@@ -1,0 +1,389 @@
+// Row kernels: an elementwise chain with a trailing reduce over the last axis, one pass over HBM.
+//
+// A row is owned by a GROUP of threads (a warp, or a whole CTA).  When the row fits in
+// ITEMS 128-bit vectors per thread it is read from HBM exactly once into registers, reduced
+// with warp shuffles (+ one shared-memory hop across warps) and written exactly once.
+// ITEMS == 0 selects the streaming form for rows too long for registers: every pass re-reads
+// the row (the second and third reads hit L2 for rows up to a few MB).
+//
+// Arithmetic follows the reference decompositions: softmax / ln_softmax
+// (zyx/src/tensor/mod.rs:1427-1461), LayerNorm::forward with unbiased variance
+// (zyx-nn/src/layer_norm.rs:95-135, zyx/src/tensor/reduce_ops.rs:113-125), reduce_impl
+// (reduce_ops.rs:45-157), cross_entropy (tensor/mod.rs:1639-1655).
+#pragma once
+#include <math_constants.h>
+
+#include <type_traits>
+
+#include "common.cuh"
+#include "eltwise_math.cuh"
+#include "internal.h"
+
+namespace zyxb {
+
+enum RowFamily { FAM_REDUCE = 0, FAM_SOFTMAX = 1, FAM_LAYERNORM = 2, FAM_SOFTMAX_BWD = 3, FAM_LAYERNORM_BWD = 4, FAM_CE = 5 };
+
+struct RowParams {
+  const void* x;    // first input
+  const void* x2;   // second input (dp / dy / labels)
+  const void* w;    // layernorm weight
+  const void* b;    // layernorm bias
+  void* y;          // output
+  uint64_t rows, cols;
+  int op;           // ZYXB_RR_*
+  int correction;
+  float eps;
+  float scale;      // softmax pre-scale (1 = none)
+  int causal;
+  uint64_t period;
+  int rn;           // round-to-nearest stores
+};
+
+template <typename T, int VEC, int ITEMS, int GROUP, int FAM>
+__global__ void __launch_bounds__(GROUP == 32 ? 128 : GROUP) row_kernel(RowParams p) {
+  using S = typename Elem<T>::store_t;
+  using A = typename Elem<T>::acc_t;
+  constexpr bool CACHED = ITEMS > 0;
+  constexpr int NI = CACHED ? ITEMS : 1;
+  constexpr bool TWO_IN = (FAM == FAM_SOFTMAX_BWD || FAM == FAM_LAYERNORM_BWD);
+  __shared__ A red[32];
+
+  const int gl = (GROUP == 32) ? (threadIdx.x & 31) : threadIdx.x;
+  const uint64_t row = (GROUP == 32) ? (uint64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5) : (uint64_t)blockIdx.x;
+  if (row >= p.rows) return;  // GROUP == 32: whole warps leave, nobody waits on a CTA barrier
+  const uint64_t cols = p.cols;
+  const S* xr = reinterpret_cast<const S*>(p.x) + row * cols;
+  const S* x2r = TWO_IN ? reinterpret_cast<const S*>(p.x2) + row * cols : nullptr;
+  const bool rn = p.rn != 0;
+  const uint64_t step = (uint64_t)GROUP * VEC;
+  const int n_iter = CACHED ? ITEMS : (int)((cols + step - 1) / step);
+
+  A v[NI][VEC];
+  A v2[TWO_IN ? NI : 1][VEC];
+  (void)v2;
+
+  auto fetch = [&](const S* base, uint64_t c, A (&out)[VEC]) {
+    Pack<S, VEC> pk = load_pack_stream<S, VEC>(base + c);
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) out[k] = Elem<T>::load(pk.v[k]);
+  };
+  if constexpr (CACHED) {
+#pragma unroll
+    for (int it = 0; it < ITEMS; ++it) {
+      const uint64_t c = ((uint64_t)it * GROUP + gl) * VEC;
+      if (c < cols) {
+        fetch(xr, c, v[it]);
+        if constexpr (TWO_IN) fetch(x2r, c, v2[it]);
+      }
+    }
+  }
+  // visit every vector of the row that this thread owns: f(it, column, values[, values2])
+  auto for_each = [&](auto&& f) {
+    if constexpr (CACHED) {
+#pragma unroll
+      for (int it = 0; it < ITEMS; ++it) {
+        const uint64_t c = ((uint64_t)it * GROUP + gl) * VEC;
+        if (c < cols) {
+          if constexpr (TWO_IN) f(c, v[it], v2[it]); else f(c, v[it], v[it]);
+        }
+      }
+    } else {
+      for (int it = 0; it < n_iter; ++it) {
+        const uint64_t c = ((uint64_t)it * GROUP + gl) * VEC;
+        if (c < cols) {
+          A a[VEC], a2[VEC];
+          fetch(xr, c, a);
+          if constexpr (TWO_IN) { fetch(x2r, c, a2); f(c, a, a2); } else f(c, a, a);
+        }
+      }
+    }
+  };
+  auto write = [&](S* base, uint64_t c, const A (&val)[VEC]) {
+    Pack<S, VEC> pk;
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) pk.v[k] = Elem<T>::store(val[k], rn);
+    store_pack_stream<S, VEC>(base + c, pk);
+  };
+
+  // ---------------------------------------------------------------------------------------
+  if constexpr (FAM == FAM_REDUCE) {
+    S* out = reinterpret_cast<S*>(p.y);
+    if constexpr (std::is_same_v<A, int32_t>) {
+      // integers: exact, wrapping i32 accumulator
+      A acc = (p.op == ZYXB_RR_SUM) ? 0 : (p.op == ZYXB_RR_MAX ? INT32_MIN : INT32_MAX);
+      for_each([&](uint64_t, const A (&a)[VEC], const A (&)[VEC]) {
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) {
+          if (p.op == ZYXB_RR_SUM) acc = (A)((uint32_t)acc + (uint32_t)a[k]);
+          else if (p.op == ZYXB_RR_MAX) acc = a[k] > acc ? a[k] : acc;
+          else acc = a[k] < acc ? a[k] : acc;
+        }
+      });
+      if (p.op == ZYXB_RR_SUM) acc = group_reduce<GROUP>(acc, OpSum(), red, (A)0);
+      else if (p.op == ZYXB_RR_MAX) acc = group_reduce<GROUP>(acc, OpMax(), red, (A)INT32_MIN);
+      else acc = group_reduce<GROUP>(acc, OpMin(), red, (A)INT32_MAX);
+      if (gl == 0) out[row] = acc;
+    } else {
+      float res;
+      if (p.op == ZYXB_RR_MAX || p.op == ZYXB_RR_MIN) {
+        const float sgn = p.op == ZYXB_RR_MAX ? 1.0f : -1.0f;   // min = -max(-x)
+        float acc = -CUDART_INF_F;
+        for_each([&](uint64_t, const A (&a)[VEC], const A (&)[VEC]) {
+#pragma unroll
+          for (int k = 0; k < VEC; ++k) acc = fmaxf(sgn * (float)a[k], acc);
+        });
+        res = sgn * group_reduce<GROUP>(acc, OpMaxF(), (float*)red, -CUDART_INF_F);
+      } else {
+        float acc = 0.0f;
+        for_each([&](uint64_t, const A (&a)[VEC], const A (&)[VEC]) {
+#pragma unroll
+          for (int k = 0; k < VEC; ++k) acc += (float)a[k];
+        });
+        res = group_reduce<GROUP>(acc, OpSum(), (float*)red, 0.0f);
+        if (p.op != ZYXB_RR_SUM) {
+          const float mean = res / const_cast_dtype<T>((float)cols);
+          res = mean;
+          if (p.op == ZYXB_RR_VAR || p.op == ZYXB_RR_STD) {
+            float sq = 0.0f;
+            for_each([&](uint64_t, const A (&a)[VEC], const A (&)[VEC]) {
+#pragma unroll
+              for (int k = 0; k < VEC; ++k) { const float d = (float)a[k] - mean; sq = fmaf(d, d, sq); }
+            });
+            sq = group_reduce<GROUP>(sq, OpSum(), (float*)red, 0.0f);
+            res = sq / const_cast_dtype<T>((float)((int64_t)cols - p.correction));
+            if (p.op == ZYXB_RR_STD) res = sqrtf(res);
+          }
+        }
+      }
+      if (gl == 0) out[row] = Elem<T>::store((A)res, rn);
+    }
+  }
+  // ---------------------------------------------------------------------------------------
+  else if constexpr (FAM == FAM_SOFTMAX || FAM == FAM_CE) {
+    // softmax, ln_softmax, cross-entropy forward/backward all start from max and sum(exp(x-max))
+    const bool scaled = p.scale != 1.0f;
+    const float cscale = const_cast_dtype<T>(p.scale);
+    const uint64_t lim = p.causal ? min((uint64_t)(row % p.period) + 1, cols) : cols;
+    auto val = [&](float a, uint64_t c) -> float {
+      if (scaled) a *= cscale;
+      return c < lim ? a : -CUDART_INF_F;
+    };
+    float mx = -CUDART_INF_F;
+    for_each([&](uint64_t c, const A (&a)[VEC], const A (&)[VEC]) {
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) mx = fmaxf(val((float)a[k], c + k), mx);
+    });
+    mx = group_reduce<GROUP>(mx, OpMaxF(), (float*)red, -CUDART_INF_F);
+    float s = 0.0f;
+    for_each([&](uint64_t c, const A (&a)[VEC], const A (&)[VEC]) {
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) s += fast_exp(val((float)a[k], c + k) - mx);
+    });
+    s = group_reduce<GROUP>(s, OpSum(), (float*)red, 0.0f);
+    if constexpr (FAM == FAM_SOFTMAX) {
+      S* yr = reinterpret_cast<S*>(p.y) + row * cols;
+      if (p.op == ZYXB_RR_SOFTMAX) {
+        const float inv = 1.0f / s;
+        for_each([&](uint64_t c, const A (&a)[VEC], const A (&)[VEC]) {
+          A o[VEC];
+#pragma unroll
+          for (int k = 0; k < VEC; ++k) o[k] = (A)(fast_exp(val((float)a[k], c + k) - mx) * inv);
+          write(yr, c, o);
+        });
+      } else {  // ln_softmax: (x - max) - ln(sum)
+        const float ls = logf(s);
+        for_each([&](uint64_t c, const A (&a)[VEC], const A (&)[VEC]) {
+          A o[VEC];
+#pragma unroll
+          for (int k = 0; k < VEC; ++k) o[k] = (A)((val((float)a[k], c + k) - mx) - ls);
+          write(yr, c, o);
+        });
+      }
+    } else {
+      const int32_t label = reinterpret_cast<const int32_t*>(p.x2)[row];
+      if (p.op == ZYXB_RR_CROSS_ENTROPY) {
+        // per_sample = sum_j -((x_j - max) - ln s) * onehot_j: only j == label contributes
+        const float ls = logf(s);
+        float acc = 0.0f;
+        for_each([&](uint64_t c, const A (&a)[VEC], const A (&)[VEC]) {
+#pragma unroll
+          for (int k = 0; k < VEC; ++k)
+            if ((int64_t)(c + k) == (int64_t)label) acc += -(((float)a[k] - mx) - ls);
+        });
+        acc = group_reduce<GROUP>(acc, OpSum(), (float*)red, 0.0f);
+        if (gl == 0) reinterpret_cast<float*>(p.y)[row] = acc;
+      } else {  // d mean-CE / d logits = (softmax - onehot) / rows
+        S* yr = reinterpret_cast<S*>(p.y) + row * cols;
+        const float inv = 1.0f / s, invr = 1.0f / (float)p.rows;
+        for_each([&](uint64_t c, const A (&a)[VEC], const A (&)[VEC]) {
+          A o[VEC];
+#pragma unroll
+          for (int k = 0; k < VEC; ++k) {
+            const float sm = fast_exp((float)a[k] - mx) * inv;
+            o[k] = (A)((sm - ((int64_t)(c + k) == (int64_t)label ? 1.0f : 0.0f)) * invr);
+          }
+          write(yr, c, o);
+        });
+      }
+    }
+  }
+  // ---------------------------------------------------------------------------------------
+  else if constexpr (FAM == FAM_LAYERNORM) {
+    float acc = 0.0f;
+    for_each([&](uint64_t, const A (&a)[VEC], const A (&)[VEC]) {
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) acc += (float)a[k];
+    });
+    const float mean = group_reduce<GROUP>(acc, OpSum(), (float*)red, 0.0f) / const_cast_dtype<T>((float)cols);
+    float sq = 0.0f;
+    for_each([&](uint64_t, const A (&a)[VEC], const A (&)[VEC]) {
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) { const float d = (float)a[k] - mean; sq = fmaf(d, d, sq); }
+    });
+    sq = group_reduce<GROUP>(sq, OpSum(), (float*)red, 0.0f);
+    const float var = sq / const_cast_dtype<T>((float)((int64_t)cols - 1));   // unbiased
+    const float rstd = 1.0f / sqrtf(var + const_cast_dtype<T>(p.eps));
+    S* yr = reinterpret_cast<S*>(p.y) + row * cols;
+    const S* wp = reinterpret_cast<const S*>(p.w);
+    const S* bp = reinterpret_cast<const S*>(p.b);
+    for_each([&](uint64_t c, const A (&a)[VEC], const A (&)[VEC]) {
+      A o[VEC];
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) o[k] = (A)(((float)a[k] - mean) * rstd);
+      if (wp) {
+        Pack<S, VEC> pk = load_pack<S, VEC>(wp + c);
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) o[k] = (A)((float)o[k] * (float)Elem<T>::load(pk.v[k]));
+      }
+      if (bp) {
+        Pack<S, VEC> pk = load_pack<S, VEC>(bp + c);
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) o[k] = (A)((float)o[k] + (float)Elem<T>::load(pk.v[k]));
+      }
+      write(yr, c, o);
+    });
+  }
+  // ---------------------------------------------------------------------------------------
+  else if constexpr (FAM == FAM_SOFTMAX_BWD) {
+    // ds = p * (dp - sum(dp * p))
+    float acc = 0.0f;
+    for_each([&](uint64_t, const A (&a)[VEC], const A (&d)[VEC]) {
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) acc = fmaf((float)a[k], (float)d[k], acc);
+    });
+    acc = group_reduce<GROUP>(acc, OpSum(), (float*)red, 0.0f);
+    S* yr = reinterpret_cast<S*>(p.y) + row * cols;
+    for_each([&](uint64_t c, const A (&a)[VEC], const A (&d)[VEC]) {
+      A o[VEC];
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) o[k] = (A)((float)a[k] * ((float)d[k] - acc));
+      write(yr, c, o);
+    });
+  }
+  // ---------------------------------------------------------------------------------------
+  else if constexpr (FAM == FAM_LAYERNORM_BWD) {
+    // dx = (g - mean(g) - (x-mean) * sum(g*(x-mean)) / ((n-1) * (var+eps))) / sqrt(var+eps), g = dy*w
+    const S* wp = reinterpret_cast<const S*>(p.w);
+    const float n = (float)cols;
+    float acc = 0.0f;
+    for_each([&](uint64_t, const A (&a)[VEC], const A (&)[VEC]) {
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) acc += (float)a[k];
+    });
+    const float mean = group_reduce<GROUP>(acc, OpSum(), (float*)red, 0.0f) / n;
+    float sq = 0.0f, sg = 0.0f, sgd = 0.0f;
+    for_each([&](uint64_t c, const A (&a)[VEC], const A (&d)[VEC]) {
+      float wv[VEC];
+      if (wp) {
+        Pack<S, VEC> pk = load_pack<S, VEC>(wp + c);
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) wv[k] = (float)Elem<T>::load(pk.v[k]);
+      }
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) {
+        const float dx = (float)a[k] - mean;
+        const float g = wp ? (float)d[k] * wv[k] : (float)d[k];
+        sq = fmaf(dx, dx, sq); sg += g; sgd = fmaf(g, dx, sgd);
+      }
+    });
+    sq = group_reduce<GROUP>(sq, OpSum(), (float*)red, 0.0f);
+    sg = group_reduce<GROUP>(sg, OpSum(), (float*)red, 0.0f);
+    sgd = group_reduce<GROUP>(sgd, OpSum(), (float*)red, 0.0f);
+    const float s2 = sq / (n - 1.0f) + const_cast_dtype<T>(p.eps);
+    const float rs = 1.0f / sqrtf(s2);
+    const float k1 = sg / n, k2 = sgd / ((n - 1.0f) * s2);
+    S* yr = reinterpret_cast<S*>(p.y) + row * cols;
+    for_each([&](uint64_t c, const A (&a)[VEC], const A (&d)[VEC]) {
+      float wv[VEC];
+      if (wp) {
+        Pack<S, VEC> pk = load_pack<S, VEC>(wp + c);
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) wv[k] = (float)Elem<T>::load(pk.v[k]);
+      }
+      A o[VEC];
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) {
+        const float dx = (float)a[k] - mean;
+        const float g = wp ? (float)d[k] * wv[k] : (float)d[k];
+        o[k] = (A)((g - k1 - dx * k2) * rs);
+      }
+      write(yr, c, o);
+    });
+  }
+}
+
+// ---- host-side geometry selection -----------------------------------------------------------
+template <typename T, int VEC, int ITEMS, int GROUP, int FAM>
+static void launch_row_geom(const RowParams& p, cudaStream_t s) {
+  if constexpr (GROUP == 32) {
+    const unsigned rows_per_cta = 4;
+    row_kernel<T, VEC, ITEMS, GROUP, FAM><<<(unsigned)((p.rows + rows_per_cta - 1) / rows_per_cta), 128, 0, s>>>(p);
+  } else {
+    row_kernel<T, VEC, ITEMS, GROUP, FAM><<<(unsigned)p.rows, GROUP, 0, s>>>(p);
+  }
+}
+
+// Pick the smallest geometry whose register budget holds the row; fall back to streaming.
+template <typename T, int VEC, int FAM>
+static void launch_row_vec(const RowParams& p, cudaStream_t s) {
+  constexpr bool TWO_IN = (FAM == FAM_SOFTMAX_BWD || FAM == FAM_LAYERNORM_BWD);
+  const uint64_t c = p.cols;
+  if (c <= 32ull * 2 * VEC) launch_row_geom<T, VEC, 2, 32, FAM>(p, s);
+  else if (c <= 32ull * 8 * VEC) launch_row_geom<T, VEC, 8, 32, FAM>(p, s);
+  else if (c <= 256ull * 4 * VEC) launch_row_geom<T, VEC, 4, 256, FAM>(p, s);
+  else if (c <= 1024ull * 4 * VEC) launch_row_geom<T, VEC, 4, 1024, FAM>(p, s);
+  else if (!TWO_IN && VEC > 1 && c <= 1024ull * 8 * VEC) launch_row_geom<T, VEC, (TWO_IN || VEC == 1) ? 4 : 8, 1024, FAM>(p, s);
+  else launch_row_geom<T, VEC, 0, 1024, FAM>(p, s);
+}
+
+template <typename T, int FAM>
+static void launch_row_family(const RowParams& p, cudaStream_t s) {
+  using S = typename Elem<T>::store_t;
+  constexpr int V = 16 / sizeof(S);
+  // 128-bit accesses need every row to start on a 16-byte boundary
+  const bool vec_ok = (p.cols % V == 0) && ((uintptr_t)p.x % 16 == 0) && ((uintptr_t)p.y % 16 == 0) &&
+                      (p.x2 == nullptr || FAM == FAM_CE || (uintptr_t)p.x2 % 16 == 0) &&
+                      (p.w == nullptr || (uintptr_t)p.w % 16 == 0) && (p.b == nullptr || (uintptr_t)p.b % 16 == 0);
+  if (vec_ok) launch_row_vec<T, V, FAM>(p, s);
+  else launch_row_vec<T, 1, FAM>(p, s);
+}
+
+// One translation unit per dtype instantiates this.
+template <typename T>
+static void launch_row_dtype(int fam, const RowParams& p, cudaStream_t s) {
+  switch (fam) {
+    case FAM_REDUCE: launch_row_family<T, FAM_REDUCE>(p, s); break;
+    case FAM_SOFTMAX: launch_row_family<T, FAM_SOFTMAX>(p, s); break;
+    case FAM_LAYERNORM: launch_row_family<T, FAM_LAYERNORM>(p, s); break;
+    case FAM_SOFTMAX_BWD: launch_row_family<T, FAM_SOFTMAX_BWD>(p, s); break;
+    case FAM_LAYERNORM_BWD: launch_row_family<T, FAM_LAYERNORM_BWD>(p, s); break;
+    default: break;
+  }
+}
+
+void launch_row_f32(int fam, const RowParams& p, cudaStream_t s);
+void launch_row_bf16(int fam, const RowParams& p, cudaStream_t s);
+void launch_row_f16(int fam, const RowParams& p, cudaStream_t s);
+void launch_row_i32(const RowParams& p, cudaStream_t s);
+
+}  // namespace zyxb

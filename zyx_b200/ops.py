@@ -1,0 +1,123 @@
+"""Host-array convenience layer: numpy in, numpy out, every call through the C ABI
+(allocate -> host_to_pool -> launch -> pool_to_host -> deallocate), the call sequence
+Runtime::materialize_kernel makes (zyx/src/runtime.rs:2075-2308).
+
+bf16 / f16 tensors are carried as numpy uint16 bit patterns.
+"""
+import numpy as np
+
+from . import _lib as L
+from . import backend as B
+
+NP_DTYPE = {L.BF16: np.uint16, L.F16: np.uint16, L.F32: np.float32, L.I32: np.int32}
+
+
+class Session:
+    """A device plus its pool; programs are cached per descriptor like the reference's kernel cache."""
+
+    def __init__(self, backend=None, dev=0, **kw):
+        self.backend = backend or B.Backend(**kw)
+        self.device = self.backend.devices[dev]
+        self.pool = self.backend.pools[dev]
+
+    def close(self):
+        self.backend.deinitialize()
+
+    def run(self, desc, inputs, out_specs):
+        """inputs: host arrays; out_specs: [(shape, np dtype)] -> list of host arrays."""
+        prog = self.device.create_program(desc)
+        in_bufs = [self.pool.upload(a) for a in inputs]
+        out_bufs = [self.pool.allocate(max(int(np.prod(s)) * np.dtype(t).itemsize, 1))[0] for s, t in out_specs]
+        try:
+            self.device.launch(prog, in_bufs + out_bufs)
+            return [self.pool.download(b, s, t) for b, (s, t) in zip(out_bufs, out_specs)]
+        finally:
+            for b in in_bufs + out_bufs:
+                self.pool.deallocate(b)
+            self.device.release(prog)
+
+    # ---- row kernels ---------------------------------------------------------------------------
+    def row_reduce(self, op, dtype, x, correction=1):
+        rows, cols = x.shape
+        return self.run(B.rowreduce_desc(op, dtype, rows, cols, correction=correction), [x], [((rows,), NP_DTYPE[dtype])])[0]
+
+    def softmax(self, dtype, x, scale=0.0, causal=False, period=0, log=False):
+        rows, cols = x.shape
+        op = L.RR_LN_SOFTMAX if log else L.RR_SOFTMAX
+        return self.run(B.rowreduce_desc(op, dtype, rows, cols, scale=scale, causal=causal, period=period), [x], [(x.shape, x.dtype)])[0]
+
+    def layernorm(self, dtype, x, w=None, b=None, eps=1e-5):
+        rows, cols = x.shape
+        ins = [x] + ([w] if w is not None else []) + ([b] if b is not None else [])
+        d = B.rowreduce_desc(L.RR_LAYERNORM, dtype, rows, cols, eps=eps, has_weight=w is not None, has_bias=b is not None)
+        return self.run(d, ins, [(x.shape, x.dtype)])[0]
+
+    def layernorm_bwd(self, dtype, x, dy, w=None, eps=1e-5):
+        rows, cols = x.shape
+        ins = [x, dy] + ([w] if w is not None else [])
+        d = B.rowreduce_desc(L.RR_LAYERNORM_BWD, dtype, rows, cols, eps=eps, has_weight=w is not None)
+        return self.run(d, ins, [(x.shape, x.dtype)])[0]
+
+    def softmax_bwd(self, dtype, p, dp):
+        rows, cols = p.shape
+        return self.run(B.rowreduce_desc(L.RR_SOFTMAX_BWD, dtype, rows, cols), [p, dp], [(p.shape, p.dtype)])[0]
+
+    def cross_entropy(self, logits, labels):
+        rows, cols = logits.shape
+        per, mean = self.run(B.rowreduce_desc(L.RR_CROSS_ENTROPY, L.F32, rows, cols), [logits, labels],
+                             [((rows,), np.float32), ((1,), np.float32)])
+        return per, mean
+
+    def cross_entropy_bwd(self, logits, labels):
+        rows, cols = logits.shape
+        return self.run(B.rowreduce_desc(L.RR_CROSS_ENTROPY_BWD, L.F32, rows, cols), [logits, labels], [(logits.shape, np.float32)])[0]
+
+    def colsum(self, dtype, x):
+        rows, cols = x.shape
+        return self.run(B.rowreduce_desc(L.RR_COLSUM, dtype, rows, cols), [x], [((cols,), x.dtype)])[0]
+
+    def mse(self, dtype, y, t):
+        rows, cols = y.shape
+        return float(self.run(B.rowreduce_desc(L.RR_MSE, dtype, rows, cols), [y, t], [((1,), np.float32)])[0][0])
+
+    # ---- elementwise ---------------------------------------------------------------------------
+    def eltwise(self, op, dtype, a, b=None, p0=0.0, dtype_out=None, cols=0):
+        od = NP_DTYPE[dtype_out] if (op == L.EW_CAST and dtype_out is not None) else a.dtype
+        ins = [a] + ([b] if b is not None else [])
+        return self.run(B.eltwise_desc(op, dtype, a.size, p0=p0, dtype_out=dtype_out, cols=cols), ins, [(a.shape, od)])[0]
+
+    # ---- matmul --------------------------------------------------------------------------------
+    def gemm(self, dtype, a, b, ta=False, tb=False, bias=None, epi=L.EPI_NONE, alpha=0.0, want_preact=False):
+        batch = a.shape[0] if a.ndim == 3 else 1
+        m, k = (a.shape[-1], a.shape[-2]) if ta else (a.shape[-2], a.shape[-1])
+        n = b.shape[-2] if tb else b.shape[-1]
+        shape = (batch, m, n) if a.ndim == 3 else (m, n)
+        d = B.gemm_desc(dtype, m, n, k, batch=batch, trans_a=ta, trans_b=tb, stride_b=(0 if b.ndim == 2 else k * n),
+                        epilogue=epi, store_preact=want_preact, alpha=alpha)
+        ins = [a, b] + ([bias] if bias is not None else [])
+        outs = [(shape, a.dtype)] * (2 if want_preact else 1)
+        r = self.run(d, ins, outs)
+        return (r[0], r[1]) if want_preact else r[0]
+
+    # ---- optimizers (in place on the host arrays, like the oracle's) ------------------------------
+    def optim_step(self, desc_kw, dtype, algo, tensors, t=None):
+        """tensors: list of groups [p, g (, m, v | , buf)] of host arrays per parameter; updated in place."""
+        n = len(tensors)
+        groups = len(tensors[0])
+        numels = [int(tt[0].size) for tt in tensors]
+        prog = self.device.create_program(B.optim_desc(algo, dtype, numels, **desc_kw))
+        if t is not None:
+            self.device.set_step(prog, t - 1)
+        bufs = [[self.pool.upload(tt[g]) for tt in tensors] for g in range(groups)]
+        try:
+            self.device.launch(prog, [b for grp in bufs for b in grp])
+            for g in range(groups):
+                if g == 1:
+                    continue
+                for i in range(n):
+                    tensors[i][g][...] = self.pool.download(bufs[g][i], tensors[i][g].shape, tensors[i][g].dtype)
+        finally:
+            for grp in bufs:
+                for b in grp:
+                    self.pool.deallocate(b)
+            self.device.release(prog)
