@@ -85,15 +85,18 @@ static inline void zo_store(void* p, int dtype, uint64_t i, float v) {
     default: ((float*)p)[i] = v;
   }
 }
-/* a rank-0 scalar cast to the tensor dtype */
-static inline float zo_const(int dtype, float v) {
+/* a rank-0 scalar cast to the tensor dtype.  Deliberately out of line: gcc 13.3 at -O3 was
+ * seen to drop the truncation of some of several scalars converted in one declaration when
+ * this was inlined (tests/test_oracle_golden.py::test_scalar_operands_are_cast pins it). */
+__attribute__((noinline)) float zo_const_cast(int dtype, float v) {
+  volatile uint16_t h;
   switch (dtype) {
-    case ZO_BF16: return zo_bf16tof32(zo_f32tobf16(v));
-    case ZO_F16: return zo_f16tof32(zo_f32tof16(v));
+    case ZO_BF16: h = zo_f32tobf16(v); return zo_bf16tof32(h);
+    case ZO_F16: h = zo_f32tof16(v); return zo_f16tof32(h);
     default: return v;
   }
 }
-float zo_const_cast(int dtype, float v) { return zo_const(dtype, v); }
+#define zo_const zo_const_cast
 void zo_cast_from_f32(int dtype, const float* x, void* y, uint64_t n) { for (uint64_t i = 0; i < n; i++) zo_store(y, dtype, i, x[i]); }
 void zo_cast_to_f32(int dtype, const void* x, float* y, uint64_t n) { for (uint64_t i = 0; i < n; i++) y[i] = zo_load(x, dtype, i); }
 

@@ -3,7 +3,7 @@ import numpy as np
 import pytest
 
 from oracle import oracle as zo
-from tests.parity import TOL_BF16, TOL_F32, max_rel_err, ref_is_equal
+from tests.parity import TOL_BF16, TOL_F32, assert_parity, max_rel_err, ref_is_equal
 from zyx_b200 import _lib as L
 
 pytestmark = pytest.mark.gpu
@@ -35,22 +35,42 @@ BINARY = [(L.EW_ADD, zo.EW_ADD), (L.EW_SUB, zo.EW_SUB), (L.EW_MUL, zo.EW_MUL), (
 @pytest.mark.parametrize("dtype", [L.F32, L.BF16, L.F16])
 @pytest.mark.parametrize("n", [1, 7, 1024, 4099, 1 << 20])
 def test_eltwise(sess, dtype, n):
+    # |x| <= 6: the tanh-by-exp GELU overflows to inf/inf = NaN near |x| = 10 in f32, in the reference as here
+    # (and the reference C code is compiled with -ffast-math, which leaves inf/NaN results unspecified)
     a, b = rand((n,), dtype, 2.0), rand((n,), dtype, 2.0)
+    if dtype == L.F32:
+        a, b = np.clip(a, -6, 6), np.clip(b, -6, 6)
+    else:
+        a, b = zo.to_bits(np.clip(f(a, dtype), -6, 6), dtype), zo.to_bits(np.clip(f(b, dtype), -6, 6), dtype)
     # the tanh-by-exp formulas cancel near zero (the reference notes the instability,
     # zyx/tests/11_autograd.rs:476): compare against the scale of the whole tensor
+    # The oracle is built with the reference's -ffast-math, whose vectorised expf is good to a few
+    # ulp only; where it and the GPU differ by more than the tolerance the float64 value of the
+    # same formula arbitrates (tests/parity.py::assert_parity).
+    af64, bf64 = f(a, dtype).astype(np.float64), f(b, dtype).astype(np.float64)
+    cc = lambda v: zo.const_cast(dtype, v)
+    tanh = lambda u: (np.exp(u + u) - 1) / (np.exp(u + u) + 1)
+    u_of = lambda x: (x + x * x * x * cc(0.044715)) * cc(0.7978845608028654)
+    gelu = lambda x: x * cc(0.5) * (tanh(u_of(x)) + 1)
+    dgelu = lambda x: cc(0.5) * (tanh(u_of(x)) + 1) + x * cc(0.5) * (1 - tanh(u_of(x)) ** 2) * (1 + 3 * cc(0.044715) * x * x) * cc(0.7978845608028654)
+    exact_unary = {L.EW_RELU: (af64 > 0) * af64, L.EW_GELU: gelu(af64), L.EW_TANH: tanh(af64), L.EW_SIGMOID: np.exp(af64) / (np.exp(af64) + 1),
+                   L.EW_EXP: np.exp(af64), L.EW_SCALE: af64 * cc(0.37)}
+    exact_binary = {L.EW_ADD: af64 + bf64, L.EW_SUB: af64 - bf64, L.EW_MUL: af64 * bf64, L.EW_RELU_BWD: af64 * (bf64 > 0),
+                    L.EW_GELU_BWD: af64 * dgelu(bf64), L.EW_MSE_BWD: (af64 - bf64) * 2.0 * np.float32(0.01)}
     for gop, oop in UNARY:
         got, want = f(sess.eltwise(gop, dtype, a, p0=0.37), dtype), f(zo.eltwise(oop, dtype, a, p0=0.37), dtype)
-        assert max_rel_err(got, want, floor=3e-2) <= TOL[dtype], gop
+        assert_parity(got, want, exact_unary[gop], TOL[dtype], floor=3e-2, what="unary %d" % gop)
     for gop, oop in BINARY:
         got, want = f(sess.eltwise(gop, dtype, a, b, p0=0.01), dtype), f(zo.eltwise(oop, dtype, a, b, p0=0.01), dtype)
-        assert max_rel_err(got, want, floor=3e-2) <= TOL[dtype], gop
+        assert_parity(got, want, exact_binary[gop], TOL[dtype], floor=3e-2, what="binary %d" % gop)
 
 
 def test_relu_is_bit_exact_and_follows_the_formula(sess):
-    x = np.array([-0.0, 0.0, -1.5, 2.5, np.inf, -np.inf, 1e-38, -1e-38], np.float32)
+    x = np.array([-0.0, 0.0, -1.5, 2.5, 3e38, -3e38, 1e-38, -1e-38], np.float32)
     got, want = sess.eltwise(L.EW_RELU, L.F32, x), zo.eltwise(zo.EW_RELU, zo.F32, x)
-    assert np.array_equal(got.view(np.uint32)[2:], want.view(np.uint32)[2:])
-    assert np.all(got[:2] == 0)
+    # equal as numbers: the sign of a zero product is left open by the reference's -ffast-math build
+    assert np.array_equal(got, want) and np.all(got[[0, 1, 2, 5, 7]] == 0)
+    assert np.array_equal(got.view(np.uint32)[[3, 4, 6]], x.view(np.uint32)[[3, 4, 6]])   # positive inputs pass through bit for bit
 
 
 @pytest.mark.parametrize("src,dst", [(L.F32, L.BF16), (L.F32, L.F16), (L.BF16, L.F32), (L.F16, L.F32), (L.BF16, L.F16)])

@@ -161,3 +161,54 @@ def test_bf16_store_truncates():
     # bf16::from_f32 = bits >> 16 (zyx/src/scalar.rs:43-45): 0.9 -> 0.8984375, 0.999 -> 0.99609375
     assert got.tolist()[:5] == [1.0, 1.0, 1.0, 0.8984375, 0.99609375]
     assert got[6] == 0.99609375
+
+
+def _tr(x, dtype=zo.BF16):
+    """store-then-load in `dtype`: what the reference does to a value that passes through a bf16 buffer"""
+    return zo.to_f32(zo.to_bits(np.asarray(x, np.float32), dtype), dtype)
+
+
+def test_scalar_operands_are_cast():
+    """The compiled oracle honours its own source: rank-0 scalars are truncated to the tensor dtype
+    (an independent float32 numpy restatement of SGD / AdamW / layernorm agrees bit for bit)."""
+    F = np.float32
+    assert zo.const_cast(zo.BF16, 0.05) == 0.0498046875 and zo.const_cast(zo.BF16, 0.9) == 0.8984375
+    p, g = zo.to_bits(F([-0.1240234375]), zo.BF16), zo.to_bits(F([0.2734375]), zo.BF16)
+    zo.sgd(zo.BF16, p, g, None, lr=0.05)
+    assert zo.to_f32(p, zo.BF16)[0] == F(-0.13671875)        # trunc(p - g * bf16(0.05)), not bf16(p - g * 0.05)
+
+    rng = np.random.default_rng(3)
+    n = 2000
+    c = lambda v: F(zo.const_cast(zo.BF16, float(F(v))))
+    # SGD with momentum and dampening, two steps
+    p0, buf = _tr(rng.standard_normal(n)), np.zeros(n, F)
+    pb, bb = zo.to_bits(p0, zo.BF16), np.zeros(n, np.uint16)
+    pe = p0.copy()
+    for step in (1, 2):
+        g = _tr(rng.standard_normal(n) * 0.1)
+        zo.sgd(zo.BF16, pb, zo.to_bits(g, zo.BF16), bb, lr=0.05, momentum=0.9, dampening=0.1, first=(step == 1))
+        buf = _tr(g if step == 1 else (buf * c(0.9) + g * c(F(1.0) - F(0.1))).astype(F))
+        pe = _tr((pe - buf * c(0.05)).astype(F))
+        assert np.array_equal(zo.to_f32(pb, zo.BF16), pe) and np.array_equal(zo.to_f32(bb, zo.BF16), buf)
+    # AdamW as the reference writes it, two steps
+    pe, m, v = p0.copy(), np.zeros(n, F), np.zeros(n, F)
+    pb, mb, vb = zo.to_bits(p0, zo.BF16), np.zeros(n, np.uint16), np.zeros(n, np.uint16)
+    lr, wd, b1, b2, eps = F(1e-3), F(0.01), F(0.9), F(0.999), F(1e-8)
+    for t in (1, 2):
+        g = _tr(rng.standard_normal(n) * 0.1)
+        zo.adam(zo.BF16, pb, zo.to_bits(g, zo.BF16), mb, vb, t, lr=1e-3, wd=0.01, mode=1)
+        m = _tr(g * c(F(1) - b1) if t == 1 else (m * c(b1) + g * c(F(1) - b1)).astype(F))
+        v = _tr(g * g * c(F(1) - b2) if t == 1 else (v * c(b2) + g * g * c(F(1) - b2)).astype(F))
+        mh, vh = m / c(F(1) - F(b1 ** F(t))), v / c(F(1) - F(b2 ** F(t)))
+        pe = _tr(((pe - mh / ((np.sqrt(vh) + c(eps)) * c(lr))) * c(F(1) - lr * wd)).astype(F))
+        assert np.array_equal(zo.to_f32(mb, zo.BF16), m) and np.array_equal(zo.to_f32(vb, zo.BF16), v)
+        got = zo.to_f32(pb, zo.BF16)
+        assert np.max(np.abs(got - pe) / np.maximum(np.abs(pe), 1e-6)) <= 2 ** -7     # at most one bf16 ulp (FMA contraction)
+    # layernorm with a column count that bf16 cannot hold: n -> bf16(1000) = 1000, n-1 = 999 -> 996
+    x = _tr(rng.standard_normal((4, 1000)) * 2)
+    mean = (x.sum(1, dtype=np.float64) / float(c(1000.0)))[:, None]
+    var = (((x - mean) ** 2).sum(1) / float(c(999.0)))[:, None]
+    want = (x - mean) / np.sqrt(var + float(c(1e-5)))
+    got = zo.to_f32(zo.layernorm(zo.BF16, zo.to_bits(x, zo.BF16)), zo.BF16)
+    assert float(c(999.0)) == 996.0
+    assert np.max(np.abs(got - want) / np.maximum(np.abs(want), 1e-2)) <= 2 ** -7
