@@ -1,0 +1,92 @@
+"""Parity of the tensor-core (tcgen05 / TMEM / TMA) matmul with the CPU oracle: every operand
+layout, both 16-bit dtypes, ragged edges, epilogues, batches; and the 8192^3 bf16 configuration
+checked on sampled rows against float64."""
+import numpy as np
+import pytest
+
+from oracle import oracle as zo
+from tests.parity import TOL_BF16, max_rel_err
+from zyx_b200 import _lib as L
+
+pytestmark = pytest.mark.gpu
+RNG = np.random.default_rng(17)
+
+
+def rand(shape, dtype):
+    return zo.to_bits(RNG.uniform(-1, 1, size=shape).astype(np.float32), dtype)
+
+
+def f(x, dtype):
+    return zo.to_f32(x, dtype)
+
+
+def err(got, want, dtype):
+    return max_rel_err(f(got, dtype), f(want, dtype), floor=0.1)
+
+
+def test_status_word_is_clear(sess):
+    assert sess.device.status() == 0
+
+
+# m, n, k: multiples of the tile, ragged in every dimension, n <= 128 (the 128-wide tile), k below one k-block
+SHAPES = [(128, 256, 64), (256, 512, 320), (130, 264, 72), (384, 128, 256), (200, 96, 136), (1024, 1024, 1024), (64, 2048, 40), (4096, 16, 512)]
+
+
+@pytest.mark.parametrize("dtype", [L.BF16, L.F16])
+@pytest.mark.parametrize("m,n,k", SHAPES)
+@pytest.mark.parametrize("ta,tb", [(False, True), (False, False), (True, False), (True, True)])
+def test_tc_layouts(sess, dtype, m, n, k, ta, tb):
+    if (ta and m % 8) or ((not ta) and k % 8) or (tb and k % 8) or ((not tb) and n % 8):
+        pytest.skip("row pitch not a multiple of 16 bytes: served by the SIMT kernel")
+    a = rand((k, m) if ta else (m, k), dtype)
+    b = rand((n, k) if tb else (k, n), dtype)
+    got = sess.gemm(dtype, a, b, ta=ta, tb=tb)
+    assert sess.device.status() == 0
+    assert err(got, zo.gemm(dtype, a, b, ta=ta, tb=tb), dtype) <= TOL_BF16
+
+
+@pytest.mark.parametrize("dtype", [L.BF16, L.F16])
+@pytest.mark.parametrize("epi", [L.EPI_NONE, L.EPI_BIAS, L.EPI_BIAS_RELU, L.EPI_BIAS_GELU])
+def test_tc_epilogues(sess, dtype, epi):
+    m, n, k = 192, 328, 264
+    a, w = rand((m, k), dtype), rand((n, k), dtype)
+    bias = rand((n,), dtype) if epi != L.EPI_NONE else None
+    got, gpre = sess.gemm(dtype, a, w, tb=True, bias=bias, epi=epi, alpha=0.25, want_preact=True)
+    want, wpre = zo.gemm(dtype, a, w, tb=True, bias=bias, epi=epi, alpha=0.25, want_preact=True)
+    assert err(got, want, dtype) <= TOL_BF16 and err(gpre, wpre, dtype) <= TOL_BF16
+
+
+def test_tc_mostly_bit_identical_with_truncating_stores(sess):
+    """Both sides accumulate exact products in f32 and truncate to bf16: apart from sums that land
+    on opposite sides of a bf16 boundary because of the summation order, results are identical."""
+    a, b = rand((256, 512), L.BF16), rand((384, 512), L.BF16)
+    got, want = sess.gemm(L.BF16, a, b, tb=True), zo.gemm(L.BF16, a, b, tb=True)
+    assert np.mean(got == want) > 0.97
+    assert np.max(np.abs(got.astype(np.int32) - want.astype(np.int32))[np.sign(f(got, L.BF16)) == np.sign(f(want, L.BF16))]) <= 1
+
+
+@pytest.mark.parametrize("dtype", [L.BF16])
+def test_tc_batched(sess, dtype):
+    bsz, m, n, k = 6, 256, 136, 128
+    a, b = rand((bsz, m, k), dtype), rand((bsz, n, k), dtype)
+    assert err(sess.gemm(dtype, a, b, tb=True, alpha=0.088), zo.gemm(dtype, a, b, tb=True, alpha=0.088), dtype) <= TOL_BF16
+    b2 = rand((bsz, k, n), dtype)
+    assert err(sess.gemm(dtype, a, b2), zo.gemm(dtype, a, b2), dtype) <= TOL_BF16
+    shared = rand((k, n), dtype)
+    assert err(sess.gemm(dtype, a, shared), zo.gemm(dtype, a, shared), dtype) <= TOL_BF16
+
+
+def test_tc_8192_cubed_sampled_rows(sess):
+    """The M=N=K=8192 bf16 configuration: 24 sampled rows against a float64 product of the same bf16 inputs,
+    and linearity C(A, B) + C(A, -B) == 0 exactly (a size-independent property of truncating stores)."""
+    n = 8192
+    rng = np.random.default_rng(2)
+    a = zo.to_bits(rng.uniform(-1, 1, (n, n)).astype(np.float32), zo.BF16)
+    b = zo.to_bits(rng.uniform(-1, 1, (n, n)).astype(np.float32), zo.BF16)
+    got = sess.gemm(L.BF16, a, b)
+    assert sess.device.status() == 0
+    rows = np.array([0, 1, 127, 128, 129, 255, 256, 1000, 2047, 2048, 4095, 4096, 4097, 5000, 6143, 6144, 7000, 8000, 8063, 8064, 8190, 8191, 3, 777])
+    want = f(a[rows], zo.BF16).astype(np.float64) @ f(b, zo.BF16).astype(np.float64)
+    assert max_rel_err(f(got[rows], zo.BF16), want, floor=0.1) <= TOL_BF16
+    neg = sess.gemm(L.BF16, a, b ^ np.uint16(0x8000))
+    assert np.array_equal(neg, got ^ np.uint16(0x8000)) or np.array_equal(f(neg, zo.BF16), -f(got, zo.BF16))

@@ -1,0 +1,463 @@
+// bf16 / f16 matmul on the 5th-generation tensor cores: tcgen05.mma accumulating f32 in TMEM,
+// operands staged by TMA into 128-byte-swizzled shared memory, mbarrier pipeline.
+//   C[b] = epi(alpha * op(A[b]) . op(B[b]) + bias)        Tensor::dot, zyx/src/tensor/mod.rs:1469-1490
+// Products of bf16/f16 inputs are exact in f32 and the accumulator is f32, which is what the
+// reference C backend computes (zyx/src/codegen/c.rs:616-629, reduce_ops.rs:52-60); only the
+// summation order differs.
+//
+// One persistent CTA per SM, 192 threads:
+//   warp 0      TMA producer   (one lane): fills a ring of STAGES {A tile, B tile} slots
+//   warp 1      MMA issuer     (one lane): tcgen05.mma 128 x BN x 16 per instruction, 4 per k-block;
+//                               tcgen05.commit releases the slot, and the accumulator when a tile is done
+//   warps 2..5  epilogue       : tcgen05.ld the 128 x BN f32 accumulator (lane = row), apply
+//                               alpha / bias / ReLU / GELU, convert and store 64 bytes per thread per chunk
+// The accumulator is double-buffered in TMEM (2 x BN columns) so the epilogue of tile i overlaps
+// the MMAs of tile i+1.  Operands may be K-major (rows of K) or MN-major (rows of M or N) in
+// memory: all four transposition cases of the descriptor are served without a transpose pass.
+// No multicast and no clusters: every CTA loads its own tiles.
+//
+// Every wait on an mbarrier is bounded by wall-clock time; a wait that runs out sets a bit in
+// the device status word, raises the CTA's abort flag and the kernel drains and returns.
+#include <cuda.h>
+
+#include <algorithm>
+
+#include "common.cuh"
+#include "eltwise_math.cuh"
+#include "gemm.h"
+
+namespace zyxb {
+
+constexpr int TC_BM = 128;          // UMMA M (cta_group::1): TMEM lane = row of the tile
+constexpr int TC_BK = 64;           // 64 x 2 bytes = one 128-byte swizzle atom along K
+constexpr int TC_UMMA_K = 16;
+constexpr int TC_THREADS = 192;
+constexpr uint64_t TC_WAIT_NS = 2000000000ull;   // 2 s bound on any single wait
+
+struct TcParams {
+  const void* bias; void* c; void* preact;
+  uint32_t m, n, k, batch;
+  uint32_t tiles_m, tiles_n;
+  int64_t stride_c;       // elements between batches of C
+  float alpha;
+  int epilogue;
+  int rn;
+  int is_bf16;
+  int a_batched, b_batched;   // 0: one matrix shared by every batch (its map has batch extent 1)
+  uint32_t* status;
+};
+
+// ---- PTX wrappers ------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ uint64_t global_timer_ns() { uint64_t t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok;
+}
+// Bounded wait.  Returns false when the wait was abandoned (time limit or another role aborted).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, uint32_t* status, uint32_t code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = global_timer_ns();
+  uint32_t spins = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    if ((++spins & 0xff) == 0) {
+      if (*abort_flag) return false;
+      if (global_timer_ns() - t0 > TC_WAIT_NS) {
+        *abort_flag = 1;
+        atomicOr(status, code);
+        return false;
+      }
+    }
+  }
+  return true;
+}
+__device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y, int z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "r"(z) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// mbarrier arrives once every tcgen05.mma issued so far by this thread has completed
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+        "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+        "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor for a 128-byte-swizzled tile (tcgen05 "SmemDescriptor"):
+//   bits [0,14) start address >> 4, [16,30) leading byte offset >> 4, [32,46) stride byte offset >> 4,
+//   [46,48) version = 1, [61,64) layout = 2 (SWIZZLE_128B).
+// K-major tile  (rows of 64 K-elements = 128 B):   SBO = 1024 B between groups of 8 rows, LBO unused (1).
+// MN-major tile (rows of 64 M/N-elements, one row per k): SBO = 1024 B between groups of 8 k,
+//   LBO = bytes between consecutive 64-element chunks along M/N (one TMA box each).
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  return (uint64_t)((addr & 0x3ffff) >> 4) | ((uint64_t)((lbo_bytes >> 4) & 0x3fff) << 16) |
+         ((uint64_t)((sbo_bytes >> 4) & 0x3fff) << 32) | (1ull << 46) | (2ull << 61);
+}
+
+// Instruction descriptor for kind::f16: f32 accumulate, A/B format f16 (0) or bf16 (1),
+// bit 15 / 16 = A / B is MN-major, N >> 3 at [17,23), M >> 4 at [24,29).
+__host__ __device__ constexpr uint32_t make_idesc(bool bf16, bool a_mn, bool b_mn, int M, int N) {
+  return (1u << 4) | ((bf16 ? 1u : 0u) << 7) | ((bf16 ? 1u : 0u) << 10) | ((a_mn ? 1u : 0u) << 15) | ((b_mn ? 1u : 0u) << 16) |
+         ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+
+template <int BN, int STAGES>
+struct TcSmem {
+  static constexpr int A_BYTES = TC_BM * TC_BK * 2;
+  static constexpr int B_BYTES = BN * TC_BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
+  static constexpr int TOTAL = BAR_OFFSET + 256 + 1024;   // + barriers + slack to align the base to 1024 B
+};
+
+enum { TC_ERR_PRODUCER = 1u, TC_ERR_MMA = 2u, TC_ERR_EPILOGUE = 4u };
+
+template <bool A_MN, bool B_MN, int BN, int STAGES>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, TcParams p) {
+  using SM = TcSmem<BN, STAGES>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;          // swizzle atoms repeat every 1024 B
+  uint8_t* base_ptr = smem_raw + (base - raw);
+  const uint32_t bar_base = base + SM::BAR_OFFSET;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+  auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
+  auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + SM::BAR_OFFSET + 8 * (2 * STAGES + 4));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  constexpr uint32_t TMEM_COLS = 2 * BN;                  // two accumulator buffers (power of two >= 32)
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), 128); }
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const uint32_t tiles_per_batch = p.tiles_m * p.tiles_n;
+  const uint32_t total_tiles = tiles_per_batch * p.batch;
+  const uint32_t k_blocks = (p.k + TC_BK - 1) / TC_BK;
+  constexpr uint32_t GROUP_M = 16;   // tiles that run together share A and B panels in L2
+  auto tile_coords = [&](uint32_t t, uint32_t& bz, uint32_t& tm, uint32_t& tn) {
+    bz = t / tiles_per_batch;
+    const uint32_t r = t % tiles_per_batch;
+    const uint32_t group_size = GROUP_M * p.tiles_n;
+    const uint32_t g = r / group_size, first_m = g * GROUP_M;
+    const uint32_t rows_in_group = min(GROUP_M, p.tiles_m - first_m);
+    const uint32_t in_group = r % group_size;
+    tm = first_m + in_group % rows_in_group;
+    tn = in_group / rows_in_group;
+  };
+
+  if (warp == 0) {
+    // ---------------------------------- TMA producer ----------------------------------
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      uint32_t issued = 0;
+      bool ok = true;
+      for (uint32_t t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        uint32_t bz, tm, tn;
+        tile_coords(t, bz, tm, tn);
+        const int za = p.a_batched ? (int)bz : 0, zb = p.b_batched ? (int)bz : 0;
+        for (uint32_t kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1, abort_flag, p.status, TC_ERR_PRODUCER)) { ok = false; break; }
+          const uint32_t a_dst = base + stage * SM::STAGE_BYTES, b_dst = a_dst + SM::A_BYTES;
+          mbar_expect_tx(full_bar(stage), SM::STAGE_BYTES);
+          const int k0 = (int)(kb * TC_BK);
+          if constexpr (A_MN) {   // A stored [k, m]: boxes of 64 m x 64 k
+#pragma unroll
+            for (int j = 0; j < TC_BM / 64; ++j)
+              tma_load_3d(a_dst + j * (64 * TC_BK * 2), &tma_a, full_bar(stage), (int)(tm * TC_BM) + j * 64, k0, za);
+          } else {                // A stored [m, k]: one box of 64 k x 128 m
+            tma_load_3d(a_dst, &tma_a, full_bar(stage), k0, (int)(tm * TC_BM), za);
+          }
+          if constexpr (B_MN) {   // B stored [k, n]: boxes of 64 n x 64 k
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)
+              tma_load_3d(b_dst + j * (64 * TC_BK * 2), &tma_b, full_bar(stage), (int)(tn * BN) + j * 64, k0, zb);
+          } else {                // B stored [n, k]: one box of 64 k x BN n
+            tma_load_3d(b_dst, &tma_b, full_bar(stage), k0, (int)(tn * BN), zb);
+          }
+          ++issued;
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (!ok) {
+        // drain: wait (bounded) for the copies still in flight so none lands after the CTA has gone
+        uint32_t s = stage, ph = phase;
+        const uint32_t n_back = issued < (uint32_t)STAGES ? issued : (uint32_t)STAGES;
+        for (uint32_t i = 0; i < n_back; ++i) {
+          if (s == 0) { s = STAGES - 1; ph ^= 1; } else --s;
+          const uint64_t t0 = global_timer_ns();
+          while (!mbar_try_wait(full_bar(s), ph) && global_timer_ns() - t0 < TC_WAIT_NS) {}
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------- MMA issuer ----------------------------------
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc(p.is_bf16 != 0, A_MN, B_MN, TC_BM, BN);
+      uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
+      bool ok = true;
+      for (uint32_t t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1, abort_flag, p.status, TC_ERR_MMA)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (uint32_t kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(full_bar(stage), phase, abort_flag, p.status, TC_ERR_MMA)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_addr = base + stage * SM::STAGE_BYTES, b_addr = a_addr + SM::A_BYTES;
+#pragma unroll
+          for (int kk = 0; kk < TC_BK / TC_UMMA_K; ++kk) {
+            // K-major: 16 K-elements = 32 B inside the swizzle atom; MN-major: 16 k-rows of 128 B = 2048 B
+            const uint64_t adesc = A_MN ? make_smem_desc(a_addr + kk * (TC_UMMA_K * 128), 64 * TC_BK * 2, 1024)
+                                        : make_smem_desc(a_addr + kk * (TC_UMMA_K * 2), 16, 1024);
+            const uint64_t bdesc = B_MN ? make_smem_desc(b_addr + kk * (TC_UMMA_K * 128), 64 * TC_BK * 2, 1024)
+                                        : make_smem_desc(b_addr + kk * (TC_UMMA_K * 2), 16, 1024);
+            umma_f16(d_tmem, adesc, bdesc, idesc, (kb | (uint32_t)kk) != 0 ? 1u : 0u);
+          }
+          umma_commit(empty_bar(stage));                 // slot is free once these MMAs have read it
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        umma_commit(tfull_bar(acc));                     // accumulator complete
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      }
+    }
+  } else {
+    // ---------------------------------- epilogue (warps 2..5) ----------------------------------
+    const uint32_t quarter = (uint32_t)(warp & 3);       // TMEM lanes this warp may read: 32*quarter .. +31
+    const uint32_t row_in_tile = quarter * 32 + lane;
+    uint32_t acc = 0, acc_phase = 0;
+    const bool rn = p.rn != 0, is_bf16 = p.is_bf16 != 0;
+    const uint16_t* bias = reinterpret_cast<const uint16_t*>(p.bias);
+    auto ld16 = [&](uint16_t h) { return is_bf16 ? bf16_to_f32(h) : f16_to_f32(h); };
+    auto st16 = [&](float v) { return is_bf16 ? f32_to_bf16(v, rn) : f32_to_f16(v, rn); };
+    auto cdt = [&](float v) { return ld16(is_bf16 ? f32_to_bf16(v, false) : f32_to_f16(v, false)); };
+    const float calpha = cdt(p.alpha);
+    const GeluConsts gc{cdt(0.5f), cdt(0.044715f), cdt(0.7978845608028654f)};
+    bool ok = true;
+    for (uint32_t t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      uint32_t bz, tm, tn;
+      tile_coords(t, bz, tm, tn);
+      if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.status, TC_ERR_EPILOGUE)) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t row = tm * TC_BM + row_in_tile;
+      const uint32_t col0 = tn * BN;
+      uint16_t* crow = reinterpret_cast<uint16_t*>(p.c) + (int64_t)bz * p.stride_c + (int64_t)row * p.n;
+      uint16_t* zrow = p.preact ? reinterpret_cast<uint16_t*>(p.preact) + (int64_t)bz * p.stride_c + (int64_t)row * p.n : nullptr;
+#pragma unroll 1
+      for (int ch = 0; ch < BN / 32; ++ch) {
+        uint32_t r[32];
+        tmem_ld32(tmem_base + ((quarter * 32u) << 16) + acc * BN + ch * 32, r);
+        tmem_ld_wait();
+        const uint32_t c = col0 + ch * 32;
+        if (row < p.m && c < p.n) {
+          const bool full = c + 32 <= p.n;               // n % 8 == 0 is guaranteed by the host
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+          if (p.alpha != 1.0f) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] *= calpha;
+          }
+          if (p.epilogue != ZYXB_EPI_NONE) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              if (full || c + q * 8 < p.n) {
+                const Pack<uint16_t, 8> pk = load_pack<uint16_t, 8>(bias + c + q * 8);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[q * 8 + j] += ld16(pk.v[j]);
+              }
+            }
+          }
+          if (zrow) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              if (full || c + q * 8 < p.n) {
+                Pack<uint16_t, 8> pk;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) pk.v[j] = st16(v[q * 8 + j]);
+                store_pack<uint16_t, 8>(zrow + c + q * 8, pk);
+              }
+            }
+          }
+          if (p.epilogue == ZYXB_EPI_BIAS_RELU) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = relu_ref(v[j]);
+          } else if (p.epilogue == ZYXB_EPI_BIAS_GELU) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              // gelu_ref with the SFU exponential and a fast divide: within 2^-20 of the formula
+              const float x = v[j];
+              const float u = (x + x * x * x * gc.a) * gc.s;
+              const float e = fast_exp(u + u);
+              const float th = __fdividef(e - 1.0f, e + 1.0f);
+              v[j] = x * gc.half * (th + 1.0f);
+            }
+          }
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            if (full || c + q * 8 < p.n) {
+              Pack<uint16_t, 8> pk;
+#pragma unroll
+              for (int j = 0; j < 8; ++j) pk.v[j] = st16(v[q * 8 + j]);
+              store_pack<uint16_t, 8>(crow + c + q * 8, pk);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(tempty_bar(acc));                      // 128 arrivals hand the accumulator back
+      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ---- host side ---------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// A rank-3 map {inner, outer, batch} over a row-major matrix with `inner` contiguous; box {64, box_outer, 1}.
+static bool encode_map(void* fn, CUtensorMap* map, bool bf16, const void* ptr, uint64_t inner, uint64_t outer, uint64_t batch,
+                       uint64_t batch_stride_elems, uint32_t box_outer) {
+  // a shared operand (batch stride 0) is described as one matrix; every batch reads z = 0
+  if (batch_stride_elems == 0) batch = 1;
+  cuuint64_t dims[3] = {inner, outer, batch};
+  cuuint64_t strides[2] = {inner * 2, (batch_stride_elems ? batch_stride_elems : inner * outer) * 2};
+  cuuint32_t box[3] = {64, box_outer, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = reinterpret_cast<EncodeTiledFn>(fn)(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
+                                                   const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+bool gemm_tc_supported(const GemmParams& p, int dtype, const LaunchCtx& lc) {
+  if (dtype != ZYXB_BF16 && dtype != ZYXB_F16) return false;
+  if (!lc.tma_encode) return false;
+  // TMA: 16-byte aligned bases and row pitches; the epilogue stores 8 elements at a time
+  const uint64_t a_inner = p.trans_a ? p.m : p.k, b_inner = p.trans_b ? p.k : p.n;
+  if (a_inner % 8 || b_inner % 8 || p.n % 8) return false;
+  if ((uintptr_t)p.a % 16 || (uintptr_t)p.b % 16 || (uintptr_t)p.c % 16) return false;
+  if (p.preact && (uintptr_t)p.preact % 16) return false;
+  if (p.bias && (uintptr_t)p.bias % 16) return false;
+  if (p.batch > 1 && ((p.stride_a % 8) || (p.stride_b % 8) || (p.stride_c % 8))) return false;
+  if (p.m > 0x7fffff00ull || p.n > 0x7fffff00ull || p.k > 0x7fffff00ull || p.batch > 65535) return false;
+  if (p.batch > 1 && p.stride_a == 0 && p.stride_b == 0) return false;
+  // tiny problems are latency-bound: the SIMT kernel has no descriptor set-up cost
+  if (p.m * p.n * p.k < (1ull << 21) || p.m < 32) return false;
+  return true;
+}
+
+template <bool A_MN, bool B_MN, int BN, int STAGES>
+static cudaError_t launch_tc_variant(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& tp, unsigned grid, cudaStream_t s) {
+  using SM = TcSmem<BN, STAGES>;
+  static bool configured = false;
+  auto kern = gemm_tc_kernel<A_MN, B_MN, BN, STAGES>;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SM::TOTAL);
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  kern<<<grid, TC_THREADS, SM::TOTAL, s>>>(ma, mb, tp);
+  return cudaGetLastError();
+}
+
+template <int BN, int STAGES>
+static cudaError_t launch_tc_bn(bool a_mn, bool b_mn, const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& tp, unsigned grid,
+                                cudaStream_t s) {
+  if (a_mn) return b_mn ? launch_tc_variant<true, true, BN, STAGES>(ma, mb, tp, grid, s) : launch_tc_variant<true, false, BN, STAGES>(ma, mb, tp, grid, s);
+  return b_mn ? launch_tc_variant<false, true, BN, STAGES>(ma, mb, tp, grid, s) : launch_tc_variant<false, false, BN, STAGES>(ma, mb, tp, grid, s);
+}
+
+int launch_gemm_tc(const GemmParams& p, int dtype, const LaunchCtx& lc, std::string& err) {
+  const bool bf16 = dtype == ZYXB_BF16;
+  const bool a_mn = p.trans_a != 0;      // A stored [k, m]: M is the contiguous axis
+  const bool b_mn = p.trans_b == 0;      // B stored [k, n]: N is the contiguous axis
+  const int bn = p.n <= 128 ? 128 : 256;
+  CUtensorMap ma, mb;
+  const bool oka = a_mn ? encode_map(lc.tma_encode, &ma, bf16, p.a, p.m, p.k, p.batch, (uint64_t)p.stride_a, 64)
+                        : encode_map(lc.tma_encode, &ma, bf16, p.a, p.k, p.m, p.batch, (uint64_t)p.stride_a, TC_BM);
+  const bool okb = b_mn ? encode_map(lc.tma_encode, &mb, bf16, p.b, p.n, p.k, p.batch, (uint64_t)p.stride_b, 64)
+                        : encode_map(lc.tma_encode, &mb, bf16, p.b, p.k, p.n, p.batch, (uint64_t)p.stride_b, (uint32_t)bn);
+  if (!oka || !okb) { err = "gemm: cuTensorMapEncodeTiled rejected an operand"; return ZYXB_ERR_KERNEL_LAUNCH; }
+  TcParams tp{};
+  tp.bias = p.bias; tp.c = p.c; tp.preact = p.preact;
+  tp.m = (uint32_t)p.m; tp.n = (uint32_t)p.n; tp.k = (uint32_t)p.k; tp.batch = (uint32_t)p.batch;
+  tp.tiles_m = (uint32_t)((p.m + TC_BM - 1) / TC_BM); tp.tiles_n = (uint32_t)((p.n + bn - 1) / bn);
+  tp.stride_c = p.stride_c; tp.alpha = p.alpha; tp.epilogue = p.epilogue; tp.rn = p.rn; tp.is_bf16 = bf16 ? 1 : 0;
+  tp.status = lc.status_word;
+  tp.a_batched = (p.batch > 1 && p.stride_a != 0) ? 1 : 0;
+  tp.b_batched = (p.batch > 1 && p.stride_b != 0) ? 1 : 0;
+  const uint64_t total = (uint64_t)tp.tiles_m * tp.tiles_n * tp.batch;
+  ZYXB_CHECK_ARG(total < 0x7fffffffull, "gemm: too many tiles");
+  const unsigned grid = (unsigned)std::min<uint64_t>(total, (uint64_t)lc.sm_count);
+  cudaError_t e = bn == 256 ? launch_tc_bn<256, 4>(a_mn, b_mn, ma, mb, tp, grid, lc.stream)
+                            : launch_tc_bn<128, 6>(a_mn, b_mn, ma, mb, tp, grid, lc.stream);
+  if (e != cudaSuccess) { err = std::string("gemm_tcgen05: ") + cudaGetErrorString(e); return ZYXB_ERR_KERNEL_LAUNCH; }
+  *lc.launch_counter += 1;
+  return ZYXB_OK;
+}
+
+}  // namespace zyxb
