@@ -91,6 +91,7 @@ class RowReduce:
     def __init__(self, rows=None):
         if rows:
             self.rows = rows
+            self.name = "rowreduce_softmax_layernorm_f32_%dx%d" % (rows, self.cols)
         self.alg_bytes_softmax = self.rows * self.cols * 8                       # read once + write once
         self.alg_bytes_layernorm = self.rows * self.cols * 8 + 2 * self.cols * 4
         self.units_per_step = (self.alg_bytes_softmax + self.alg_bytes_layernorm) / 1e9   # GB of algorithmic traffic
@@ -127,7 +128,7 @@ class RowReduce:
             e2 = d.event_record()
             self.kernel_events.append((e0, e1, e2))
 
-    def roofline(self, peaks):
+    def roofline(self, peaks, clocks=None):
         d = self.sess.device
         sm = [d.elapsed_ms(a, b) for a, b, _ in self.kernel_events]
         ln = [d.elapsed_ms(b, c) for _, b, c in self.kernel_events]
@@ -180,7 +181,116 @@ class RowReduce:
         return v, "%d of %d rows of [%d, %d] f32, softmax + layernorm, %.1f s" % (rows, self.rows, self.rows, self.cols, dt)
 
 
-WORKLOADS = {"rowreduce": RowReduce}
+class Gemm:
+    """C = A.B, row-major, A and B uniform(-1, 1) seeded; bf16 inputs are rounded the way bf16::from_f32 does (truncation)."""
+    bound = "tensor"
+
+    def __init__(self, dtype_name="bf16", n=None):
+        from zyx_b200 import _lib as L
+        self.dtype = dtype_name
+        self.dt = {"bf16": L.BF16, "f32": L.F32}[dtype_name]
+        self.n = n or (8192 if dtype_name == "bf16" else 4096)
+        self.es = 2 if dtype_name == "bf16" else 4
+        self.name = "gemm_%s_%d^3" % (dtype_name, self.n)
+        self.metric, self.unit = "GEMM TFLOP/s (%s, M=N=K=%d, f32 accumulate)" % (dtype_name, self.n), "TFLOP/s"
+        self.flops = 2.0 * self.n ** 3
+        self.units_per_step = self.flops / 1e12
+        self.h2d_bytes = 2 * self.n * self.n * self.es
+        self.d2h_bytes = self.n * self.n * self.es
+
+    def host_inputs(self):
+        from oracle import oracle as zo
+        rng = np.random.default_rng(2)
+        a = rng.uniform(-1, 1, (self.n, self.n)).astype(np.float32)
+        rng = np.random.default_rng(3)
+        b = rng.uniform(-1, 1, (self.n, self.n)).astype(np.float32)
+        if self.dtype == "bf16":
+            a, b = zo.to_bits(a, zo.BF16), zo.to_bits(b, zo.BF16)
+        self.a, self.b = a, b
+
+    def setup(self, sess):
+        from zyx_b200 import backend as B
+        self.sess = sess
+        self.host_inputs()
+        p, d = sess.pool, sess.device
+        self.ba, self.bb = p.upload(self.a), p.upload(self.b)
+        self.bc, _ = p.allocate(self.a.nbytes)
+        self.prog = d.create_program(B.gemm_desc(self.dt, self.n, self.n, self.n))
+        self.config = {"workload": self.name, "l2": "L2 flushed between timed iterations (256 MB memset)", "layout": "NN row-major"}
+        self.kernel_events = []
+
+    def step(self, timed=False):
+        d = self.sess.device
+        d.flush_l2()
+        if timed:
+            e0 = d.event_record()
+        d.launch(self.prog, [self.ba, self.bb, self.bc])
+        if timed:
+            self.kernel_events.append((e0, d.event_record()))
+
+    def roofline(self, peaks, clocks=None):
+        d = self.sess.device
+        ms = [d.elapsed_ms(a, b) for a, b in self.kernel_events]
+        t = float(np.mean(ms))
+        ach = self.flops / (t * 1e-3) / 1e12
+        if self.dtype == "bf16":
+            peak, kern, src = peaks["bf16_tflops"], "gemm_tc_kernel (tcgen05)", peaks["source"]
+        else:
+            mhz = (clocks or {}).get("sm_mhz") or 1965.0
+            peak, kern, src = 148 * 128 * 2 * mhz * 1e6 / 1e12, "gemm_simt_kernel<f32>", "computed: 148 SM x 128 FMA x 2 x %.0f MHz (median sampled SM clock)" % mhz
+        self.t_kernel_ms = t
+        return ({"bound": "tensor" if self.dtype == "bf16" else "fp32-fma", "kernel": kern, "achieved": ach, "peak": peak, "unit": "TFLOP/s",
+                 "frac": ach / peak, "traffic": None, "peak_source": src, "ms_per_launch": t, "ms_best": float(np.min(ms))},
+                {"gemm": {"ms": t, "TFLOP/s": ach}})
+
+    def e2e_setup(self):
+        self.hc = np.empty_like(self.a)
+        for a in (self.a, self.b, self.hc):
+            self.sess.backend.host_register(a)
+
+    def e2e_step(self):
+        p, d = self.sess.pool, self.sess.device
+        e1, e2 = p.host_to_pool(self.a, self.ba), p.host_to_pool(self.b, self.bb)
+        d.launch(self.prog, [self.ba, self.bb, self.bc], [e1, e2])
+        p.pool_to_host(self.bc, self.hc)
+
+    def check(self):
+        from oracle import oracle as zo
+        rows = np.array([0, 129, self.n // 2 + 1, self.n - 1])
+        got = np.empty((len(rows), self.n), self.a.dtype)
+        for i, r in enumerate(rows):
+            self.sess.pool.pool_to_host(self.bc, got[i], src_offset=int(r) * self.n * self.es)
+        af = zo.to_f32(self.a[rows], zo.BF16) if self.dtype == "bf16" else self.a[rows]
+        bf = zo.to_f32(self.b, zo.BF16) if self.dtype == "bf16" else self.b
+        want = af.astype(np.float64) @ bf.astype(np.float64)
+        gf = zo.to_f32(got, zo.BF16) if self.dtype == "bf16" else got
+        return float(np.max(np.abs(gf - want) / np.maximum(np.abs(want), 0.1 * np.abs(want).max(1, keepdims=True))))
+
+    def cpu_run(self, n):
+        from oracle import oracle as zo
+        a, b = np.ascontiguousarray(self.a[:n, :n]), np.ascontiguousarray(self.b[:n, :n])
+        t0 = time.perf_counter()
+        zo.gemm(zo.BF16 if self.dtype == "bf16" else zo.F32, a, b)
+        dt = time.perf_counter() - t0
+        return 2.0 * n ** 3 / 1e12 / dt, dt
+
+    def cpu_baseline(self, budget_s=12.0):
+        if not hasattr(self, "a"):
+            self.host_inputs()
+        v, dt = self.cpu_run(512)
+        n = int(min(self.n, max(512, 512 * (budget_s / max(dt, 1e-6)) ** (1.0 / 3.0)))) // 64 * 64
+        v, dt = self.cpu_run(n)
+        return v, "%d^3 corner of the %d^3 problem (%s), %.1f s" % (n, self.n, self.dtype, dt)
+
+
+WORKLOADS = {"rowreduce": RowReduce, "gemm_bf16": lambda: Gemm("bf16"), "gemm_f32": lambda: Gemm("f32")}
+
+
+def make_workload(args):
+    if args.size:
+        return {"rowreduce": lambda: RowReduce(rows=args.size), "gemm_bf16": lambda: Gemm("bf16", args.size),
+                "gemm_f32": lambda: Gemm("f32", args.size)}[args.workload]()
+    return WORKLOADS[args.workload]()
 
 
 def host_threads():
@@ -195,7 +305,7 @@ def run_reference(args, rank, world):
     if rank != 0:
         return
     os.environ.setdefault("OMP_NUM_THREADS", str(host_threads()))
-    w = WORKLOADS[args.workload]()
+    w = make_workload(args)
     w.host_inputs()
     vals = []
     sample = ""
@@ -223,6 +333,8 @@ def main():
     ap.add_argument("--impl", default="zyx_b200", choices=["zyx_b200", "reference"])
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end leg (profiling runs)")
+    ap.add_argument("--size", type=int, default=0, help="reduced problem size for profiler captures: rows (rowreduce) or N (gemm)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
@@ -245,7 +357,7 @@ def main():
     sess = Session(device_ids=[local_rank])
     dev = sess.device
     peaks = load_peaks()
-    w = WORKLOADS[args.workload]()
+    w = make_workload(args)
     w.setup(sess)
 
     def barrier():
@@ -276,30 +388,32 @@ def main():
         ms_total = float(t.item())
     ms_step = ms_total / args.steps
     value = world * w.units_per_step / (ms_step * 1e-3)
-    roofline, kernels = w.roofline(peaks)
+    roofline, kernels = w.roofline(peaks, clocks)
     err = w.check()
 
     # end to end through the public API: host buffers in, host buffers out, copies inside the timed region
-    w.e2e_setup()
-    w.e2e_step()
-    barrier()
-    t0 = time.perf_counter()
-    for _ in range(args.e2e_steps):
+    e2e = None
+    if not args.no_e2e:
+        w.e2e_setup()
         w.e2e_step()
-    dev.sync()
-    e2e_s = (time.perf_counter() - t0) / args.e2e_steps
-    if world > 1:
-        t = torch.tensor([e2e_s], device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_s = float(t.item())
-    e2e = {"value": world * w.units_per_step / e2e_s, "unit": w.unit, "h2d_bytes_per_step": w.h2d_bytes, "d2h_bytes_per_step": w.d2h_bytes,
-           "steps": args.e2e_steps, "ms_per_step": e2e_s * 1e3}
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(args.e2e_steps):
+            w.e2e_step()
+        dev.sync()
+        e2e_s = (time.perf_counter() - t0) / args.e2e_steps
+        if world > 1:
+            t = torch.tensor([e2e_s], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            e2e_s = float(t.item())
+        e2e = {"value": world * w.units_per_step / e2e_s, "unit": w.unit, "h2d_bytes_per_step": w.h2d_bytes, "d2h_bytes_per_step": w.d2h_bytes,
+               "steps": args.e2e_steps, "ms_per_step": e2e_s * 1e3}
 
     if rank == 0:
         line = {"metric": w.metric, "value": value, "unit": w.unit, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
                 "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": w.dtype,
                 "data": "synthetic", "config": w.config, "roofline": roofline, "kernels": kernels, "e2e": e2e,
-                "gpu_launches": int(launches), "clocks": clocks, "max_rel_err_vs_oracle": err}
+                "gpu_launches": int(launches), "clocks": clocks, "max_rel_err_sampled": err}
         if world == 1 and not args.no_cpu_baseline:
             os.environ.setdefault("OMP_NUM_THREADS", str(host_threads()))
             v, sample = w.cpu_baseline()

@@ -62,7 +62,8 @@ def test_tc_mostly_bit_identical_with_truncating_stores(sess):
     a, b = rand((256, 512), L.BF16), rand((384, 512), L.BF16)
     got, want = sess.gemm(L.BF16, a, b, tb=True), zo.gemm(L.BF16, a, b, tb=True)
     assert np.mean(got == want) > 0.97
-    assert np.max(np.abs(got.astype(np.int32) - want.astype(np.int32))[np.sign(f(got, L.BF16)) == np.sign(f(want, L.BF16))]) <= 1
+    big = np.abs(f(want, L.BF16)) >= 0.1 * np.abs(f(want, L.BF16)).max(1, keepdims=True)   # sums that did not cancel
+    assert np.max(np.abs(got.astype(np.int32) - want.astype(np.int32))[big]) <= 1          # differ by at most one bf16 ulp
 
 
 @pytest.mark.parametrize("dtype", [L.BF16])
