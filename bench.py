@@ -4,6 +4,7 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference]
 
 Prints ONE JSON line.  Workloads (synthetic, seeded, shapes of the reference's configurations):
+  mlp         4 x Linear 4096<->16384, GELU, bf16, batch 8192 per GPU, MSE, AdamW; data parallel   (samples/s)  [default]
   rowreduce   row softmax + row layernorm on f32 [8192, 32768]         (fused-reduce GB/s)
   gemm_bf16   C = A.B, M=N=K=8192 bf16, f32 accumulate                  (GEMM TFLOP/s)
   gemm_f32    C = A.B, M=N=K=4096 f32                                   (GEMM TFLOP/s)
@@ -283,10 +284,151 @@ class Gemm:
         return v, "%d^3 corner of the %d^3 problem (%s), %.1f s" % (n, self.n, self.dtype, dt)
 
 
-WORKLOADS = {"rowreduce": RowReduce, "gemm_bf16": lambda: Gemm("bf16"), "gemm_f32": lambda: Gemm("f32")}
+def f32_to_bf16_bits(x):
+    """bf16 storage of an f32 array, truncating like the reference's bf16::from_f32."""
+    return (np.ascontiguousarray(x, np.float32).view(np.uint32) >> 16).astype(np.uint16)
 
 
-def make_workload(args):
+class MlpTrain:
+    """Config 4: 4 x Linear 4096 -> 16384 -> 4096 -> 16384 -> 4096, GELU between, bf16, batch 8192 per GPU, MSE against
+    N(0,1) targets, AdamW lr 1e-3 wd 0.01; data parallel over the ranks with an NCCL gradient allreduce."""
+    dims = [4096, 16384, 4096, 16384, 4096]
+    batch = 8192
+    unit, dtype, bound = "samples/s", "bf16", "tensor"
+
+    def __init__(self, size=0, standard=False, rank=0, world=1):
+        if size:
+            self.batch = size
+        self.standard, self.rank, self.world = standard, rank, world
+        self.name = "mlp_4xlinear_4096_16384_gelu_bf16_adamw_batch%d_per_gpu" % self.batch
+        self.metric = "MLP train samples/s (4x Linear 4096<->16384, GELU, bf16, AdamW, batch %d per GPU)" % self.batch
+        self.units_per_step = float(self.batch)
+        self.h2d_bytes = self.batch * (self.dims[0] + self.dims[-1]) * 2
+        self.d2h_bytes = 4
+        n = len(self.dims) - 1
+        # matmul FLOPs of one step: forward, weight gradient and (all but the first layer) input gradient
+        self.gemm_flops = sum(2.0 * self.batch * self.dims[i] * self.dims[i + 1] * (3 if i > 0 else 2) for i in range(n))
+        self.n_params = sum(self.dims[i] * self.dims[i + 1] + self.dims[i + 1] for i in range(n))
+
+    def host_inputs(self):
+        rng = np.random.default_rng(100 + self.rank)
+        self.hx = f32_to_bf16_bits(rng.standard_normal((self.batch, self.dims[0]), dtype=np.float32))
+        self.ht = f32_to_bf16_bits(rng.standard_normal((self.batch, self.dims[-1]), dtype=np.float32))
+
+    def setup(self, sess):
+        from zyx_b200 import _lib as L, host as H
+        self.sess, self.H = sess, H
+        self.host_inputs()
+        self.mlp = H.Mlp(sess, L.BF16, self.batch, self.dims, activation=H.ACT_GELU, loss=H.LOSS_MSE, algo=L.OPT_ADAMW, world=self.world,
+                         bucket_per_layer=True, lr=1e-3, weight_decay=0.01, standard=self.standard)
+        rng = np.random.default_rng(0)            # the same random-init weights on every rank (Linear::new's distribution)
+        for i in range(self.mlp.n_params()):
+            layer = i // 2
+            bound = 1.0 / np.sqrt(self.dims[layer])
+            self.mlp.set_tensor(H.PARAM, i, f32_to_bf16_bits(rng.uniform(-bound, bound, self.mlp.shape(i)).astype(np.float32)))
+        sess.pool.sync_events(self.mlp.set_batch(self.hx, self.ht))
+        # Pristine copies of the parameters.  Every step starts by copying them back (device to device, inside the
+        # timed step): the reference's AdamW divides its update by lr, so after one step every weight is about
+        # -+1/lr and from the second step on all values are NaN; timing GEMMs on NaNs draws less power and
+        # flatters the clock.  With the reset every timed step is the configuration's step on finite N(0,1)-scale data.
+        self.params = [self.mlp.tensor(H.PARAM, i) for i in range(self.mlp.n_params())]
+        self.pristine = []
+        for buf, numel in self.params:
+            copy, _ = sess.pool.allocate(numel * 2)
+            sess.pool.release_events([sess.pool.pool_to_pool(sess.pool, buf, copy, numel * 2)])
+            self.pristine.append(copy)
+        self.reset_bytes = sum(n for _, n in self.params) * 2
+        launches, colls = self.mlp.plan_size()
+        self.config = {"workload": self.name, "global_batch": self.batch * self.world, "parallelism": "dp%d" % self.world,
+                       "optimizer": "AdamW lr=1e-3 wd=0.01, " + ("textbook update" if self.standard else
+                                    "update as the reference writes it (step divided by lr)"),
+                       "l2": "working set (params 0.5 GB, activations 2.7 GB) larger than L2", "launches_per_step": launches,
+                       "collectives_per_step": colls,
+                       "param_reset": "parameters copied back from a pristine device copy at the start of every step "
+                                      "(%d bytes d2d inside the timed step) so all values stay finite" % self.reset_bytes}
+        self.mlp.profile(True)
+        self.losses = []
+
+    def reset_params(self):
+        p = self.sess.pool
+        for (buf, numel), copy in zip(self.params, self.pristine):
+            p.release_events([p.pool_to_pool(p, copy, buf, numel * 2)])
+
+    def step(self, timed=False):
+        self.reset_params()
+        self.mlp.step()
+
+    def warm_reset(self):
+        self.mlp.profile_read()    # drop what the warm-up steps recorded
+
+    def roofline(self, peaks, clocks=None):
+        ms, kind, steps = self.mlp.profile_read()
+        gemm_ms = sum(m for m, k in zip(ms, kind) if k // 100 == 2) / max(steps, 1)
+        groups = {}
+        names = {2: "matmul", 1: "row", 3: "eltwise", 4: "optimizer"}
+        for m, k in zip(ms, kind):
+            key = "allreduce(+wait)" if k < 0 else names.get(k // 100, "?") + (":" + ["NN", "NT", "TN", "TT"][k % 100] if k // 100 == 2 else "")
+            groups[key] = groups.get(key, 0.0) + m / max(steps, 1)
+        ach = self.gemm_flops / (gemm_ms * 1e-3) / 1e12
+        n_gemm = sum(1 for k in kind if k // 100 == 2)
+        return ({"bound": "tensor", "kernel": "gemm_tc_kernel (tcgen05), %d launches per step" % n_gemm, "achieved": ach,
+                 "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s", "frac": ach / peaks["bf16_tflops_sustained"], "traffic": None,
+                 "peak_source": peaks["source"] + " (sustained: the kernel runs inside a long step)", "ms_per_launch": gemm_ms / n_gemm,
+                 "flops_per_step": self.gemm_flops},
+                {"ms_per_step_by_kind": {k: round(v, 4) for k, v in groups.items()}})
+
+    def e2e_setup(self):
+        """Two device input sets: the upload of the next batch (pinned host memory, copy stream) overlaps this step."""
+        self.mlp.profile(False)
+        p = self.sess.pool
+        for a in (self.hx, self.ht):
+            self.sess.backend.host_register(a)
+        self.sets = [(self.mlp.x, self.mlp.target), (p.allocate(self.hx.nbytes)[0], p.allocate(self.ht.nbytes)[0])]
+        self.cur = 0
+        self.ready = [p.host_to_pool(self.hx, self.sets[0][0]), p.host_to_pool(self.ht, self.sets[0][1])]
+        self.done = [None, None]      # event of the last step that read each set
+
+    def e2e_step(self):
+        p, cur, nxt = self.sess.pool, self.cur, 1 - self.cur
+        # upload the next batch into the other set as soon as the step that last read it has finished
+        dep = [self.done[nxt]] if self.done[nxt] is not None else []
+        nx = p.host_to_pool(self.hx, self.sets[nxt][0], dep)
+        nt = p.host_to_pool(self.ht, self.sets[nxt][1])          # no wait list: ordered after everything queued, hence after dep too
+        self.mlp.bind_inputs(*self.sets[cur])
+        self.reset_params()
+        self.done[cur] = self.mlp.step(self.ready, want_event=True)
+        self.losses.append(self.mlp.read_loss())                 # 4-byte device-to-host read; blocks until the step is done
+        self.ready, self.cur = [nx, nt], nxt
+
+    def check(self):
+        return None
+
+    def cpu_baseline(self, budget_s=12.0):
+        from oracle import models as om, oracle as zo
+        rng = np.random.default_rng(0)
+        layers = []
+        for i in range(len(self.dims) - 1):
+            b = 1.0 / np.sqrt(self.dims[i])
+            layers.append((f32_to_bf16_bits(rng.uniform(-b, b, (self.dims[i + 1], self.dims[i])).astype(np.float32)),
+                           f32_to_bf16_bits(rng.uniform(-b, b, (self.dims[i + 1],)).astype(np.float32))))
+        if not hasattr(self, "hx"):
+            self.host_inputs()
+        bs = 32
+        opt = om.Optim("adamw", zo.BF16, om.flat(layers), lr=1e-3, weight_decay=0.01, standard=self.standard)
+        t0 = time.perf_counter()
+        _, grads, _ = om.forward_backward(zo.BF16, layers, self.hx[:bs], self.ht[:bs], om.ACT_GELU, om.LOSS_MSE)
+        opt.update(om.flat(layers), om.flat(grads))
+        dt = time.perf_counter() - t0
+        return bs / dt, "one full training step (forward, MSE, backward, AdamW over all %d parameters) at batch %d instead of %d, %.1f s" % (
+            self.n_params, bs, self.batch, dt)
+
+
+WORKLOADS = {"mlp": MlpTrain, "rowreduce": RowReduce, "gemm_bf16": lambda: Gemm("bf16"), "gemm_f32": lambda: Gemm("f32")}
+
+
+def make_workload(args, rank=0, world=1):
+    if args.workload == "mlp":
+        return MlpTrain(size=args.size, standard=args.standard_adamw, rank=rank, world=world)
     if args.size:
         return {"rowreduce": lambda: RowReduce(rows=args.size), "gemm_bf16": lambda: Gemm("bf16", args.size),
                 "gemm_f32": lambda: Gemm("f32", args.size)}[args.workload]()
@@ -306,7 +448,8 @@ def run_reference(args, rank, world):
         return
     os.environ.setdefault("OMP_NUM_THREADS", str(host_threads()))
     w = make_workload(args)
-    w.host_inputs()
+    if hasattr(w, "host_inputs"):
+        w.host_inputs()
     vals = []
     sample = ""
     budget = max(2.0, min(20.0, 120.0 / max(1, args.steps + args.warmup)))
@@ -329,7 +472,8 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--workload", default="rowreduce", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="mlp", choices=sorted(WORKLOADS))
+    ap.add_argument("--standard-adamw", action="store_true", help="mlp: textbook AdamW instead of the reference's literal update")
     ap.add_argument("--impl", default="zyx_b200", choices=["zyx_b200", "reference"])
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -357,7 +501,14 @@ def main():
     sess = Session(device_ids=[local_rank])
     dev = sess.device
     peaks = load_peaks()
-    w = make_workload(args)
+    w = make_workload(args, rank, world)
+    if world > 1:
+        # one NCCL communicator for the library: rank 0 creates the id, torch.distributed carries it
+        uid = torch.zeros(128, dtype=torch.uint8, device="cuda")
+        if rank == 0:
+            uid = torch.tensor(list(dev.comm_unique_id()), dtype=torch.uint8, device="cuda")
+        dist.broadcast(uid, 0)
+        dev.comm_init(rank, world, bytes(uid.cpu().tolist()))
     w.setup(sess)
 
     def barrier():
@@ -369,6 +520,8 @@ def main():
     for _ in range(args.warmup):
         w.step()
     barrier()
+    if hasattr(w, "warm_reset"):
+        w.warm_reset()
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
@@ -414,6 +567,8 @@ def main():
                 "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": w.dtype,
                 "data": "synthetic", "config": w.config, "roofline": roofline, "kernels": kernels, "e2e": e2e,
                 "gpu_launches": int(launches), "clocks": clocks, "max_rel_err_sampled": err}
+        if getattr(w, "losses", None):
+            line["loss_e2e_steps"] = w.losses[:8]
         if world == 1 and not args.no_cpu_baseline:
             os.environ.setdefault("OMP_NUM_THREADS", str(host_threads()))
             v, sample = w.cpu_baseline()

@@ -135,7 +135,10 @@ typedef struct {
  * (zyx-nn/src/linear.rs:39-45), matched the way Graph::match_matmul does
  * (zyx/src/vendor/matmul.rs:43-71), launched like cblas_sgemm in backend/cblas.rs:241-271.
  * C[b] = epilogue(alpha * op(A[b]) . op(B[b]) [+ bias]) */
-enum { ZYXB_EPI_NONE = 0, ZYXB_EPI_BIAS = 1, ZYXB_EPI_BIAS_RELU = 2, ZYXB_EPI_BIAS_GELU = 3 };
+enum { ZYXB_EPI_NONE = 0, ZYXB_EPI_BIAS = 1, ZYXB_EPI_BIAS_RELU = 2, ZYXB_EPI_BIAS_GELU = 3,
+       /* backward through an activation fused into the input-gradient matmul: C = (alpha * A.B) * act'(z),
+        * z [m,n] being the activation's stored input (GELU) or output (ReLU: relu'(z) = z > 0 either way) */
+       ZYXB_EPI_MUL_RELU_GRAD = 4, ZYXB_EPI_MUL_GELU_GRAD = 5 };
 
 typedef struct {
   int32_t  dtype;        /* element type of A, B, C: bf16 / f16 / f32 / i32; accumulation is
@@ -149,7 +152,7 @@ typedef struct {
   int32_t  store_preact; /* 1: second output receives alpha*A.B+bias before the activation */
   float    alpha;        /* 0 means 1 */
 } zyxb_gemm_desc;
-/* args: a, b [,bias] -> c [,preact] */
+/* args: a, b [,bias | ,z] -> c [,preact] */
 
 /* Elementwise kernels (zyx/src/tensor/elementwise.rs:157-170,289-293,585-588 and the
  * adjoints of zyx/src/graph/autograd.rs:47-175). */
@@ -231,7 +234,9 @@ int32_t zyxb_free_bytes(zyxb_ctx* ctx, int32_t dev, uint64_t* out_bytes);
 int32_t zyxb_alloc(zyxb_ctx* ctx, int32_t dev, uint64_t bytes, uint32_t* out_buf, zyxb_event* out_event);
 /* waits for the events (consumed), then frees */
 int32_t zyxb_free(zyxb_ctx* ctx, int32_t dev, uint32_t buf, const zyxb_event* wait, int32_t n_wait);
-/* asynchronous: src must stay valid until out_event has been synced (runtime.rs:1-16) */
+/* asynchronous: src must stay valid until out_event has been synced (runtime.rs:1-16).  The copy runs on its own
+ * stream: with a non-empty wait list it depends on those events only (so it can overlap kernels already queued);
+ * with an empty one it is ordered after everything queued so far. */
 int32_t zyxb_h2d(zyxb_ctx* ctx, int32_t dev, const void* src, uint64_t bytes, uint32_t dst, uint64_t dst_offset,
                  const zyxb_event* wait, int32_t n_wait, zyxb_event* out_event);
 /* blocking */
@@ -242,6 +247,11 @@ int32_t zyxb_d2d(zyxb_ctx* ctx, int32_t src_dev, uint32_t src, uint64_t src_offs
                  uint64_t dst_offset, uint64_t bytes, const zyxb_event* wait, int32_t n_wait, zyxb_event* out_event);
 int32_t zyxb_memset(zyxb_ctx* ctx, int32_t dev, uint32_t buf, uint64_t offset, int32_t byte_value, uint64_t bytes);
 int32_t zyxb_buffer_bytes(zyxb_ctx* ctx, int32_t dev, uint32_t buf, uint64_t* out_bytes);
+/* A second id for the byte range [offset, offset+bytes) of `parent` (offset a multiple of 256).  Lets
+ * every gradient live inside one contiguous bucket that a single collective can cover, the way the
+ * plan's `Alias` instruction shares storage (zyx/src/graph/plan.rs:47-54).  Freeing a view releases
+ * only the id; the parent must outlive its views. */
+int32_t zyxb_buffer_view(zyxb_ctx* ctx, int32_t dev, uint32_t parent, uint64_t offset, uint64_t bytes, uint32_t* out_buf);
 /* blocking; destroys the events */
 int32_t zyxb_sync(zyxb_ctx* ctx, int32_t dev, const zyxb_event* events, int32_t n);
 /* non-blocking destroy */

@@ -1,0 +1,77 @@
+/*
+ * zyxb_host.h — host-side runtime above the C ABI of zyxb.h (libzyxb_host.so).
+ *
+ * The reference's host side is Rust: `Tape::gradient` builds the backward graph, `optim.update`
+ * appends the optimizer expressions, `Tape::realize` compiles an `ExecPlan` once and replays its
+ * `Launch` nodes every iteration (zyx/src/tape.rs:117-202, zyx/src/graph/plan.rs:271-361).  With no
+ * Rust toolchain available the same plan is built here in C++ for the one model family the
+ * configurations use — a stack of zyx_nn::Linear layers with an activation between them — and
+ * replayed through nothing but zyxb.h calls, so what the library sees is the call sequence zyx
+ * would produce.  Parameter, gradient and optimizer-state order is `Module::iter()` order: per
+ * Linear `weight` then `bias` (zyx-nn/src/linear.rs:11-16, zyx-derive/src/lib.rs:75-106).
+ */
+#ifndef ZYXB_HOST_H
+#define ZYXB_HOST_H
+
+#include "zyxb.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum { ZYXB_ACT_NONE = 0, ZYXB_ACT_RELU = 1, ZYXB_ACT_GELU = 2 };
+enum { ZYXB_LOSS_MSE = 0,            /* mean((y - target)^2), target [batch, dims[n]] of `dtype` (README loop, README.md:144-150) */
+       ZYXB_LOSS_CROSS_ENTROPY = 1   /* Tensor::cross_entropy(.., ReduceOp::Mean), target [batch] i32 class indices, f32 only */ };
+
+typedef struct {
+  int32_t  dtype;            /* ZYXB_F32 / ZYXB_BF16 / ZYXB_F16: parameters, activations, gradients, optimizer state */
+  uint64_t batch;            /* rows per step on this rank */
+  int32_t  n_layers;         /* 1..8 Linear layers */
+  uint64_t dims[9];          /* dims[0] = input features, dims[i+1] = out_features of layer i */
+  int32_t  activation;       /* between layers (not after the last) */
+  int32_t  loss;
+  zyxb_optim_desc optim;     /* algo and hyper-parameters; dtype, n_tensors and numel are filled in */
+  int32_t  world;            /* data-parallel ranks; > 1: gradients are all-reduced (needs zyxb_comm_init) and
+                                optim.grad_scale is set to 1/world */
+  int32_t  bucket_per_layer; /* 1: one allreduce per layer as soon as its gradients are queued (overlaps the rest of
+                                the backward pass); 0: one allreduce over the whole gradient bucket */
+} zyxb_mlp_config;
+
+typedef struct zyxb_mlp zyxb_mlp;
+
+/* Allocates parameters, gradients (one contiguous bucket), optimizer state and activations, and creates
+ * every program of the step once — the analogue of compile_graph + ExecPlan::new (graph/mod.rs:1508-1581). */
+int32_t zyxb_mlp_create(zyxb_ctx* ctx, int32_t dev, const zyxb_mlp_config* config, zyxb_mlp** out);
+int32_t zyxb_mlp_destroy(zyxb_mlp* mlp);
+const char* zyxb_mlp_last_error(zyxb_mlp* mlp);
+
+/* Buffers, in Module::iter() order (index i = 2*layer + {0: weight [out,in], 1: bias [out]}).
+ * which: 0 parameter, 1 gradient, 2 first optimizer state (SGD momentum buffer / Adam m), 3 second (Adam v). */
+int32_t zyxb_mlp_tensor(zyxb_mlp* mlp, int32_t which, int32_t i, uint32_t* out_buf, uint64_t* out_numel);
+/* Input [batch, dims[0]], target, loss [1] f32, output of the last layer [batch, dims[n]]. */
+int32_t zyxb_mlp_io(zyxb_mlp* mlp, uint32_t* out_x, uint32_t* out_target, uint32_t* out_loss, uint32_t* out_y);
+
+/* forward + loss + backward (+ gradient allreduce): the Launch nodes up to the gradients */
+int32_t zyxb_mlp_forward_backward(zyxb_mlp* mlp);
+/* the optimizer update (SGD::update / AdamW::update) */
+int32_t zyxb_mlp_update(zyxb_mlp* mlp);
+/* one training step = forward_backward + update; `wait` are consumed (e.g. the h2d events of this step's batch) */
+int32_t zyxb_mlp_step(zyxb_mlp* mlp, const zyxb_event* wait, int32_t n_wait);
+/* the same, and an event that completes when the step's last launch has finished */
+int32_t zyxb_mlp_step_event(zyxb_mlp* mlp, const zyxb_event* wait, int32_t n_wait, zyxb_event* out_event);
+/* Rebind the plan to caller-owned input / target buffers (e.g. to alternate two sets so that the upload of the
+ * next batch overlaps this step); the buffers the plan allocated stay owned by it. */
+int32_t zyxb_mlp_bind_inputs(zyxb_mlp* mlp, uint32_t x, uint32_t target);
+/* Per-instruction timing: while enabled, zyxb_mlp_step records an event after every instruction of the plan.
+ * profile_read sums, over the steps recorded since the last read, the time between consecutive events (ms) per
+ * instruction, and reports what each instruction is: -1 for a collective, else 100*ZYXB_KIND_* + sub, where sub is
+ * 2*trans_a + trans_b for a matmul, the op for row / elementwise programs and the algorithm for the optimizer. */
+int32_t zyxb_mlp_profile(zyxb_mlp* mlp, int32_t enable);
+int32_t zyxb_mlp_profile_read(zyxb_mlp* mlp, float* out_ms, int32_t* out_kind, int32_t capacity, int32_t* out_n, int32_t* out_steps);
+/* number of zyxb_launch / zyxb_allreduce_sum calls one step makes */
+int32_t zyxb_mlp_plan_size(zyxb_mlp* mlp, int32_t* out_launches, int32_t* out_collectives);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ZYXB_HOST_H */

@@ -207,11 +207,12 @@ def eltwise(op, dtype, a, b=None, p0=0.0, dtype_out=None, cols=1):
 
 
 # ---- matmul ------------------------------------------------------------------------------
-EPI_NONE, EPI_BIAS, EPI_BIAS_RELU, EPI_BIAS_GELU = range(4)
+EPI_NONE, EPI_BIAS, EPI_BIAS_RELU, EPI_BIAS_GELU, EPI_MUL_RELU_GRAD, EPI_MUL_GELU_GRAD = range(6)
 
 
 def gemm(dtype, a, b, ta=False, tb=False, bias=None, epi=EPI_NONE, alpha=0.0, want_preact=False):
-    """a: [batch?, m, k] (or [.., k, m] when ta); b: [batch?, k, n] (or [.., n, k] when tb)."""
+    """a: [batch?, m, k] (or [.., k, m] when ta); b: [batch?, k, n] (or [.., n, k] when tb).
+    For the MUL_*_GRAD epilogues `bias` is z, shaped like the result."""
     a, b = np.ascontiguousarray(a), np.ascontiguousarray(b)
     batch = a.shape[0] if a.ndim == 3 else 1
     am, ak = (a.shape[-1], a.shape[-2]) if ta else (a.shape[-2], a.shape[-1])

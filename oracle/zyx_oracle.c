@@ -398,7 +398,10 @@ float zo_mse(int dtype, const void* y, const void* t, uint64_t n) {
  * bias afterwards (zyx-nn/src/linear.rs:39-45).
  *   C[b] = epi(alpha * op(A[b]) . op(B[b]) + bias);   ta: A stored [k,m];  tb: B stored [n,k]
  * ------------------------------------------------------------------------------------- */
-enum { ZO_EPI_NONE = 0, ZO_EPI_BIAS = 1, ZO_EPI_BIAS_RELU = 2, ZO_EPI_BIAS_GELU = 3 };
+enum { ZO_EPI_NONE = 0, ZO_EPI_BIAS = 1, ZO_EPI_BIAS_RELU = 2, ZO_EPI_BIAS_GELU = 3,
+       /* (alpha * A.B) * act'(z): the input-gradient matmul followed by the activation's adjoint; `bias` then points at
+        * z [m,n].  The product is not rounded in between because the GPU path does not write it to memory. */
+       ZO_EPI_MUL_RELU_GRAD = 4, ZO_EPI_MUL_GELU_GRAD = 5 };
 
 void zo_gemm(int dtype, int ta, int tb, uint64_t m, uint64_t n, uint64_t k, uint64_t batch, const void* a, const void* b,
              const void* bias, void* c, void* preact, int64_t sa, int64_t sb, int64_t sc, int epi, float alpha) {
@@ -416,10 +419,12 @@ void zo_gemm(int dtype, int ta, int tb, uint64_t m, uint64_t n, uint64_t k, uint
         if (tb) for (uint64_t kk = 0; kk < k; kk++) acc = arow[kk] * zo_load(b, dtype, ob + j * k + kk) + acc;
         else for (uint64_t kk = 0; kk < k; kk++) acc = arow[kk] * zo_load(b, dtype, ob + kk * n + j) + acc;
         if (alpha != 1.0f) acc = acc * calpha;
-        if (epi != ZO_EPI_NONE) acc = acc + zo_load(bias, dtype, j);
+        if (epi >= ZO_EPI_BIAS && epi <= ZO_EPI_BIAS_GELU) acc = acc + zo_load(bias, dtype, j);
         if (preact) zo_store(preact, dtype, oc + i * n + j, acc);
         if (epi == ZO_EPI_BIAS_RELU) acc = zo_relu_f(acc);
         else if (epi == ZO_EPI_BIAS_GELU) acc = zo_gelu_f(acc, ch, ca, cs);
+        else if (epi == ZO_EPI_MUL_RELU_GRAD) acc = acc * (float)(zo_load(bias, dtype, oc + i * n + j) > 0.0f);
+        else if (epi == ZO_EPI_MUL_GELU_GRAD) acc = acc * zo_gelu_grad_f(zo_load(bias, dtype, oc + i * n + j), ch, ca, cs);
         zo_store(c, dtype, oc + i * n + j, acc);
       }
       free(arow);

@@ -126,3 +126,11 @@ def test_f32_gemm_1024_against_float64(sess):
     got = sess.gemm(L.F32, a, b)
     want = a.astype(np.float64) @ b.astype(np.float64)
     assert max_rel_err(got, want, floor=0.1) <= TOL_F32
+
+
+@pytest.mark.parametrize("epi", [L.EPI_MUL_RELU_GRAD, L.EPI_MUL_GELU_GRAD])
+def test_activation_gradient_epilogue_f32(sess, epi):
+    m, n, k = 70, 50, 33
+    dz, w = rand((m, k), L.F32), rand((k, n), L.F32)
+    z = RNG.normal(0, 1.5, size=(m, n)).astype(np.float32)
+    assert gemm_err(sess.gemm(L.F32, dz, w, bias=z, epi=epi), zo.gemm(L.F32, dz, w, bias=z, epi=epi), L.F32) <= TOL[L.F32] * 3

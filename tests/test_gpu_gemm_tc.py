@@ -91,3 +91,15 @@ def test_tc_8192_cubed_sampled_rows(sess):
     assert max_rel_err(f(got[rows], zo.BF16), want, floor=0.1) <= TOL_BF16
     neg = sess.gemm(L.BF16, a, b ^ np.uint16(0x8000))
     assert np.array_equal(neg, got ^ np.uint16(0x8000)) or np.array_equal(f(neg, zo.BF16), -f(got, zo.BF16))
+
+
+@pytest.mark.parametrize("dtype", [L.BF16, L.F16])
+@pytest.mark.parametrize("epi", [L.EPI_MUL_RELU_GRAD, L.EPI_MUL_GELU_GRAD])
+def test_tc_activation_gradient_epilogue(sess, dtype, epi):
+    """dZ_prev = (dZ . W) * act'(z): the input-gradient matmul with the activation's adjoint in its epilogue."""
+    m, n, k = 192, 264, 136
+    dz, w = rand((m, k), dtype), rand((k, n), dtype)
+    z = zo.to_bits(RNG.normal(0, 1.5, size=(m, n)).astype(np.float32), dtype)
+    got = sess.gemm(dtype, dz, w, bias=z, epi=epi)
+    want = zo.gemm(dtype, dz, w, bias=z, epi=epi)
+    assert err(got, want, dtype) <= TOL_BF16

@@ -20,7 +20,7 @@ DTYPE_SIZE = {BF16: 2, F16: 2, F32: 4, F64: 8, U8: 1, U16: 2, U32: 4, U64: 8, I8
 KIND_ROWREDUCE, KIND_GEMM, KIND_ELTWISE, KIND_OPTIM = 1, 2, 3, 4
 (RR_SUM, RR_MAX, RR_MIN, RR_MEAN, RR_VAR, RR_STD, RR_SOFTMAX, RR_LN_SOFTMAX, RR_LAYERNORM, RR_CROSS_ENTROPY,
  RR_CROSS_ENTROPY_BWD, RR_SOFTMAX_BWD, RR_LAYERNORM_BWD, RR_COLSUM, RR_MSE) = range(15)
-EPI_NONE, EPI_BIAS, EPI_BIAS_RELU, EPI_BIAS_GELU = range(4)
+EPI_NONE, EPI_BIAS, EPI_BIAS_RELU, EPI_BIAS_GELU, EPI_MUL_RELU_GRAD, EPI_MUL_GELU_GRAD = range(6)
 (EW_RELU, EW_GELU, EW_ADD, EW_SUB, EW_MUL, EW_SCALE, EW_RELU_BWD, EW_GELU_BWD, EW_MSE_BWD, EW_CAST, EW_TANH, EW_SIGMOID,
  EW_EXP, EW_BIAS_ADD) = range(14)
 OPT_SGD, OPT_ADAM, OPT_ADAMW = range(3)
@@ -96,6 +96,7 @@ SIGNATURES = {
                              C.c_int32, _EV_P]),
     "zyxb_memset": (C.c_int32, [_CTX, C.c_int32, C.c_uint32, C.c_uint64, C.c_int32, C.c_uint64]),
     "zyxb_buffer_bytes": (C.c_int32, [_CTX, C.c_int32, C.c_uint32, C.POINTER(C.c_uint64)]),
+    "zyxb_buffer_view": (C.c_int32, [_CTX, C.c_int32, C.c_uint32, C.c_uint64, C.c_uint64, _U32_P]),
     "zyxb_sync": (C.c_int32, [_CTX, C.c_int32, _EV_P, C.c_int32]),
     "zyxb_release_events": (C.c_int32, [_CTX, C.c_int32, _EV_P, C.c_int32]),
     "zyxb_device_sync": (C.c_int32, [_CTX, C.c_int32]),

@@ -142,6 +142,11 @@ class MemoryPool:
             return None
         return dt.value, bytes(raw)[:L.DTYPE_SIZE[dt.value]]
 
+    def view(self, parent, offset, nbytes):
+        buf = C.c_uint32()
+        self.be._check(self.be.lib.zyxb_buffer_view(self.be.ctx, self.dev, parent, int(offset), int(nbytes), C.byref(buf)))
+        return buf.value
+
     def buffer_bytes(self, buffer_id):
         v = C.c_uint64()
         self.be._check(self.be.lib.zyxb_buffer_bytes(self.be.ctx, self.dev, buffer_id, C.byref(v)))

@@ -15,6 +15,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "_build")
 LIB = os.path.join(HERE, "libzyxb.so")
+HOST_LIB = os.path.join(HERE, "libzyxb_host.so")
 ROOT = os.path.dirname(HERE)
 
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
@@ -60,7 +61,20 @@ def build(force=False, verbose=False):
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError("link failed:\n%s\n%s" % (r.stdout, r.stderr))
+    build_host(force or bool(jobs))
     return LIB
+
+
+def build_host(force=False):
+    """libzyxb_host.so: the C++ host runtime (include/zyxb_host.h); it uses libzyxb.so only through its C ABI."""
+    srcs = sorted(glob.glob(os.path.join(CSRC, "host", "*.cpp")))
+    newest = max([os.path.getmtime(s) for s in srcs] + [_newest_header()])
+    if force or not os.path.exists(HOST_LIB) or os.path.getmtime(HOST_LIB) < newest:
+        cmd = ["g++", "-shared", "-o", HOST_LIB] + CXX_FLAGS + srcs + ["-L", HERE, "-lzyxb", "-Wl,-rpath,$ORIGIN"]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError("host link failed: %s\n%s\n%s" % (" ".join(cmd), r.stdout, r.stderr))
+    return HOST_LIB
 
 
 if __name__ == "__main__":

@@ -31,6 +31,7 @@ struct Buffer {
   uint64_t capacity = 0;   // bytes of the underlying block
   bool live = false;
   bool is_variable = false;
+  bool is_view = false;    // aliases a range of another buffer; freeing it releases only the id
   int32_t var_dtype = 0;
   uint8_t var_bytes[8] = {0};
 };
@@ -237,7 +238,7 @@ int32_t zyxb_shutdown(zyxb_ctx* ctx) {
     cudaDeviceSynchronize();
     if (D.comm) { comm_destroy(D.comm); D.comm = nullptr; }
     for (auto& kv : D.events) cudaEventDestroy(kv.second);
-    for (auto& b : D.buffers) if (b.live && b.ptr) cudaFree(b.ptr);
+    for (auto& b : D.buffers) if (b.live && b.ptr && !b.is_view && !b.is_variable) cudaFree(b.ptr);
     for (auto& kv : D.cache) cudaFree(kv.second);
     if (D.scratch) cudaFree(D.scratch);
     if (D.status_word) cudaFree(D.status_word);
@@ -319,7 +320,7 @@ int32_t zyxb_free(zyxb_ctx* ctx, int32_t dev, uint32_t buf, const zyxb_event* wa
   // that could still touch it before later work on the compute stream
   int st = wait_and_consume(ctx, D, D.compute, wait, n_wait, ZYXB_ERR_MEMORY_DEALLOCATION);
   if (st) return st;
-  if (!b->is_variable) {
+  if (!b->is_variable && !b->is_view) {
     if ((st = order_streams(ctx, D.copy, D.compute, ZYXB_ERR_MEMORY_DEALLOCATION))) return st;
     if ((st = order_streams(ctx, D.comm_stream, D.compute, ZYXB_ERR_MEMORY_DEALLOCATION))) return st;
     D.cache.emplace(b->capacity, b->ptr);
@@ -327,6 +328,23 @@ int32_t zyxb_free(zyxb_ctx* ctx, int32_t dev, uint32_t buf, const zyxb_event* wa
   }
   *b = Buffer();
   D.free_buffer_ids.push_back(buf);
+  return ZYXB_OK;
+}
+
+int32_t zyxb_buffer_view(zyxb_ctx* ctx, int32_t dev, uint32_t parent, uint64_t offset, uint64_t bytes, uint32_t* out_buf) {
+  DEV_OR_FAIL(ZYXB_ERR_MEMORY_ALLOCATION);
+  Buffer* pb = get_buffer(D, parent);
+  if (!pb || pb->is_variable || !out_buf) return fail(ctx, ZYXB_ERR_MEMORY_ALLOCATION, "buffer_view: unknown parent buffer");
+  if (offset % 256 != 0) return fail(ctx, ZYXB_ERR_MEMORY_ALLOCATION, "buffer_view: offset must be a multiple of 256 bytes");
+  if (offset + bytes > pb->bytes) return fail(ctx, ZYXB_ERR_MEMORY_ALLOCATION, "buffer_view: range exceeds the parent");
+  void* ptr = (char*)pb->ptr + offset;
+  uint32_t id;
+  if (!D.free_buffer_ids.empty()) { id = D.free_buffer_ids.back(); D.free_buffer_ids.pop_back(); }
+  else { id = (uint32_t)D.buffers.size(); D.buffers.emplace_back(); }
+  Buffer& b = D.buffers[id];
+  b = Buffer();
+  b.ptr = ptr; b.bytes = bytes; b.capacity = bytes; b.live = true; b.is_view = true;
+  *out_buf = id;
   return ZYXB_OK;
 }
 
@@ -346,8 +364,10 @@ int32_t zyxb_h2d(zyxb_ctx* ctx, int32_t dev, const void* src, uint64_t bytes, ui
   if (dst_offset + bytes > b->bytes) return fail(ctx, ZYXB_ERR_MEMORY_COPY_H2P, "h2d: copy exceeds the buffer");
   int st = wait_and_consume(ctx, D, D.copy, wait, n_wait, ZYXB_ERR_MEMORY_COPY_H2P);
   if (st) return st;
-  // kernels already enqueued may still read or write dst: the upload goes after them
-  if ((st = order_streams(ctx, D.compute, D.copy, ZYXB_ERR_MEMORY_COPY_H2P))) return st;
+  // With a wait list the caller has named what the upload depends on, as zyx does (it passes the events of
+  // every pending use of dst), and the copy may overlap kernels already queued.  Without one, kernels
+  // already enqueued may still read or write dst: the upload goes after them.
+  if (n_wait == 0 && (st = order_streams(ctx, D.compute, D.copy, ZYXB_ERR_MEMORY_COPY_H2P))) return st;
   if (bytes) {
     cudaError_t e = cudaMemcpyAsync((char*)b->ptr + dst_offset, src, bytes, cudaMemcpyHostToDevice, D.copy);
     if (e != cudaSuccess) return cuda_fail(ctx, ZYXB_ERR_MEMORY_COPY_H2P, "cudaMemcpyAsync h2d", e);

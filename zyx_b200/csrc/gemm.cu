@@ -13,7 +13,7 @@ int validate_gemm(const zyxb_gemm_desc& d, std::string& err) {
   }
   if (d.m == 0 || d.n == 0 || d.k == 0 || d.batch == 0) { err = "gemm: m, n, k and batch must be positive"; return ZYXB_ERR_KERNEL_COMPILATION; }
   if (d.m > 0x7fffffffull || d.n > 0x7fffffffull || d.k > 0x7fffffffull) { err = "gemm: dimension too large"; return ZYXB_ERR_KERNEL_COMPILATION; }
-  if (d.epilogue < ZYXB_EPI_NONE || d.epilogue > ZYXB_EPI_BIAS_GELU) { err = "gemm: unknown epilogue"; return ZYXB_ERR_KERNEL_COMPILATION; }
+  if (d.epilogue < ZYXB_EPI_NONE || d.epilogue > ZYXB_EPI_MUL_GELU_GRAD) { err = "gemm: unknown epilogue"; return ZYXB_ERR_KERNEL_COMPILATION; }
   if (d.dtype == ZYXB_I32 && (d.epilogue != ZYXB_EPI_NONE || d.store_preact || (d.alpha != 0.0f && d.alpha != 1.0f))) {
     err = "gemm: integer matmul takes no epilogue"; return ZYXB_ERR_KERNEL_COMPILATION;
   }
@@ -24,9 +24,10 @@ int validate_gemm(const zyxb_gemm_desc& d, std::string& err) {
 
 int launch_gemm(const zyxb_gemm_desc& d, void* const* args, const uint64_t* arg_bytes, int n_args, const LaunchCtx& lc,
                 std::string& err) {
-  const bool has_bias = d.epilogue != ZYXB_EPI_NONE;
-  const int want = 2 + (has_bias ? 1 : 0) + 1 + (d.store_preact ? 1 : 0);
-  ZYXB_CHECK_ARG(n_args == want, "gemm: expected args a, b [,bias] -> c [,preact]");
+  const bool has_bias = d.epilogue >= ZYXB_EPI_BIAS && d.epilogue <= ZYXB_EPI_BIAS_GELU;
+  const bool has_z = d.epilogue == ZYXB_EPI_MUL_RELU_GRAD || d.epilogue == ZYXB_EPI_MUL_GELU_GRAD;
+  const int want = 2 + (has_bias || has_z ? 1 : 0) + 1 + (d.store_preact ? 1 : 0);
+  ZYXB_CHECK_ARG(n_args == want, "gemm: expected args a, b [,bias | ,z] -> c [,preact]");
   const uint64_t es = dtype_size(d.dtype);
   const uint64_t need_a = ((d.batch - 1) * (uint64_t)d.stride_a + d.m * d.k) * es;
   const uint64_t need_b = ((d.batch - 1) * (uint64_t)d.stride_b + d.k * d.n) * es;
@@ -36,6 +37,7 @@ int launch_gemm(const zyxb_gemm_desc& d, void* const* args, const uint64_t* arg_
   ZYXB_CHECK_ARG(arg_bytes[i] >= need_a, "gemm: A too small"); p.a = args[i++];
   ZYXB_CHECK_ARG(arg_bytes[i] >= need_b, "gemm: B too small"); p.b = args[i++];
   if (has_bias) { ZYXB_CHECK_ARG(arg_bytes[i] >= d.n * es, "gemm: bias too small"); p.bias = args[i++]; }
+  if (has_z) { ZYXB_CHECK_ARG(arg_bytes[i] >= need_c, "gemm: z too small"); p.z = args[i++]; }
   ZYXB_CHECK_ARG(arg_bytes[i] >= need_c, "gemm: C too small"); p.c = args[i++];
   if (d.store_preact) { ZYXB_CHECK_ARG(arg_bytes[i] >= need_c, "gemm: preact too small"); p.preact = args[i++]; }
   p.m = d.m; p.n = d.n; p.k = d.k; p.batch = d.batch;

@@ -8,6 +8,7 @@ namespace zyxb {
 
 struct GemmParams {
   const void* a; const void* b; const void* bias;
+  const void* z;   // MUL_*_GRAD epilogues: [m, n] (per batch, C's stride)
   void* c; void* preact;
   uint64_t m, n, k, batch;
   int64_t stride_a, stride_b, stride_c;   // elements between consecutive batches

@@ -141,6 +141,7 @@ __global__ void __launch_bounds__(STHREADS) gemm_simt_kernel(GemmParams p) {
   S* C = reinterpret_cast<S*>(p.c) + (int64_t)blockIdx.z * p.stride_c;
   S* Z = p.preact ? reinterpret_cast<S*>(p.preact) + (int64_t)blockIdx.z * p.stride_c : nullptr;
   const S* bias = reinterpret_cast<const S*>(p.bias);
+  const S* zin = p.z ? reinterpret_cast<const S*>(p.z) + (int64_t)blockIdx.z * p.stride_c : nullptr;
   const bool rn = p.rn != 0;
   if constexpr (std::is_same_v<ACC, float>) {
     const GeluConsts gc = gelu_consts<T>();
@@ -155,10 +156,12 @@ __global__ void __launch_bounds__(STHREADS) gemm_simt_kernel(GemmParams p) {
         if (c >= n) continue;
         float v = acc[i][j];
         if (p.alpha != 1.0f) v *= calpha;
-        if (p.epilogue != ZYXB_EPI_NONE) v += (float)Elem<T>::load(bias[c]);
+        if (p.epilogue >= ZYXB_EPI_BIAS && p.epilogue <= ZYXB_EPI_BIAS_GELU) v += (float)Elem<T>::load(bias[c]);
         if (Z) Z[r * n + c] = Elem<T>::store(v, rn);
         if (p.epilogue == ZYXB_EPI_BIAS_RELU) v = relu_ref(v);
         else if (p.epilogue == ZYXB_EPI_BIAS_GELU) v = gelu_ref<T>(v, gc);
+        else if (p.epilogue == ZYXB_EPI_MUL_RELU_GRAD) v *= ((float)Elem<T>::load(zin[r * n + c]) > 0.0f ? 1.0f : 0.0f);
+        else if (p.epilogue == ZYXB_EPI_MUL_GELU_GRAD) v *= gelu_grad_ref<T>((float)Elem<T>::load(zin[r * n + c]), gc);
         C[r * n + c] = Elem<T>::store(v, rn);
       }
     }

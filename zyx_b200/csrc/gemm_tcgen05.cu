@@ -35,7 +35,7 @@ constexpr int TC_THREADS = 192;
 constexpr uint64_t TC_WAIT_NS = 2000000000ull;   // 2 s bound on any single wait
 
 struct TcParams {
-  const void* bias; void* c; void* preact;
+  const void* bias; const void* z; void* c; void* preact;
   uint32_t m, n, k, batch;
   uint32_t tiles_m, tiles_n;
   int64_t stride_c;       // elements between batches of C
@@ -312,7 +312,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
 #pragma unroll
             for (int j = 0; j < 32; ++j) v[j] *= calpha;
           }
-          if (p.epilogue != ZYXB_EPI_NONE) {
+          if (p.epilogue >= ZYXB_EPI_BIAS && p.epilogue <= ZYXB_EPI_BIAS_GELU) {
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
               if (full || c + q * 8 < p.n) {
@@ -333,7 +333,29 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
               }
             }
           }
-          if (p.epilogue == ZYXB_EPI_BIAS_RELU) {
+          if (p.epilogue == ZYXB_EPI_MUL_RELU_GRAD || p.epilogue == ZYXB_EPI_MUL_GELU_GRAD) {
+            // backward through the activation: multiply the input gradient by act'(z), z read once from HBM
+            const uint16_t* zr = reinterpret_cast<const uint16_t*>(p.z) + (int64_t)bz * p.stride_c + (int64_t)row * p.n;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              if (full || c + q * 8 < p.n) {
+                const Pack<uint16_t, 8> pk = load_pack_stream<uint16_t, 8>(zr + c + q * 8);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                  const float x = ld16(pk.v[j]);
+                  float g;
+                  if (p.epilogue == ZYXB_EPI_MUL_RELU_GRAD) g = x > 0.0f ? 1.0f : 0.0f;
+                  else {
+                    const float u = (x + x * x * x * gc.a) * gc.s;
+                    const float e = fast_exp(u + u);
+                    const float th = __fdividef(e - 1.0f, e + 1.0f);
+                    g = gc.half * (th + 1.0f) + x * gc.half * (1.0f - th * th) * ((1.0f + 3.0f * gc.a * x * x) * gc.s);
+                  }
+                  v[q * 8 + j] *= g;
+                }
+              }
+            }
+          } else if (p.epilogue == ZYXB_EPI_BIAS_RELU) {
 #pragma unroll
             for (int j = 0; j < 32; ++j) v[j] = relu_ref(v[j]);
           } else if (p.epilogue == ZYXB_EPI_BIAS_GELU) {
@@ -402,6 +424,7 @@ bool gemm_tc_supported(const GemmParams& p, int dtype, const LaunchCtx& lc) {
   if ((uintptr_t)p.a % 16 || (uintptr_t)p.b % 16 || (uintptr_t)p.c % 16) return false;
   if (p.preact && (uintptr_t)p.preact % 16) return false;
   if (p.bias && (uintptr_t)p.bias % 16) return false;
+  if (p.z && (uintptr_t)p.z % 16) return false;
   if (p.batch > 1 && ((p.stride_a % 8) || (p.stride_b % 8) || (p.stride_c % 8))) return false;
   if (p.m > 0x7fffff00ull || p.n > 0x7fffff00ull || p.k > 0x7fffff00ull || p.batch > 65535) return false;
   if (p.batch > 1 && p.stride_a == 0 && p.stride_b == 0) return false;
@@ -443,7 +466,7 @@ int launch_gemm_tc(const GemmParams& p, int dtype, const LaunchCtx& lc, std::str
                         : encode_map(lc.tma_encode, &mb, bf16, p.b, p.k, p.n, p.batch, (uint64_t)p.stride_b, (uint32_t)bn);
   if (!oka || !okb) { err = "gemm: cuTensorMapEncodeTiled rejected an operand"; return ZYXB_ERR_KERNEL_LAUNCH; }
   TcParams tp{};
-  tp.bias = p.bias; tp.c = p.c; tp.preact = p.preact;
+  tp.bias = p.bias; tp.z = p.z; tp.c = p.c; tp.preact = p.preact;
   tp.m = (uint32_t)p.m; tp.n = (uint32_t)p.n; tp.k = (uint32_t)p.k; tp.batch = (uint32_t)p.batch;
   tp.tiles_m = (uint32_t)((p.m + TC_BM - 1) / TC_BM); tp.tiles_n = (uint32_t)((p.n + bn - 1) / bn);
   tp.stride_c = p.stride_c; tp.alpha = p.alpha; tp.epilogue = p.epilogue; tp.rn = p.rn; tp.is_bf16 = bf16 ? 1 : 0;

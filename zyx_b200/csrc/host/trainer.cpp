@@ -1,0 +1,419 @@
+// Host-side training plan for a stack of Linear layers, built once and replayed every step
+// through the C ABI of zyxb.h only (see include/zyxb_host.h).
+//
+// What each part mirrors in the reference:
+//   Linear          zyx-nn/src/linear.rs:8-45        weight [out, in], bias [out]; forward x.dot(W.t()) + b
+//   Plan / Instr    zyx/src/graph/plan.rs:47-54      ExecPlan: Launch instructions replayed by execute_plan (271-361)
+//   backward        zyx/src/graph/autograd.rs:47-175 adjoints of mul/add/relu/exp...; for dot, reshape, expand and sum the
+//                                                    standard adjoints spelled out in autograd.rs:195-242, 269-379
+//   SGD / AdamW     zyx-optim/src/sgd.rs:45-84, adamw.rs:51-97   one fused program over all parameters
+// Gradients live in one contiguous bucket, last layer first, so that each layer's slice can be
+// all-reduced as soon as its two gradient launches are queued.
+#include <stdio.h>
+#include <string.h>
+
+#include <string>
+#include <vector>
+
+#include "../../../include/zyxb_host.h"
+
+namespace {
+
+struct Linear {
+  uint64_t in_features = 0, out_features = 0;
+  uint32_t weight = 0, bias = 0;          // parameters
+  uint32_t weight_grad = 0, bias_grad = 0; // views into the gradient bucket
+  uint32_t state[2][2] = {{0, 0}, {0, 0}}; // [m|v][weight|bias]
+  uint64_t bucket_offset = 0, bucket_count = 0;  // this layer's slice of the bucket, in elements
+};
+
+struct Instr {
+  enum Kind { LAUNCH, ALLREDUCE } kind = LAUNCH;
+  uint32_t program = 0;
+  std::vector<uint32_t> args;
+  uint64_t offset = 0, count = 0;          // ALLREDUCE: slice of the gradient bucket
+  bool wait_collectives = false;           // LAUNCH: wait for every pending allreduce event first
+  int desc_kind = 0, desc_sub = 0;         // ZYXB_KIND_* and the op / layout, for profile reports
+};
+
+uint64_t dsize(int32_t dtype) { return dtype == ZYXB_F32 ? 4 : 2; }
+uint64_t align_up(uint64_t v, uint64_t a) { return (v + a - 1) / a * a; }
+
+}  // namespace
+
+struct zyxb_mlp {
+  zyxb_ctx* ctx = nullptr;
+  int32_t dev = 0;
+  zyxb_mlp_config cfg{};
+  std::vector<Linear> layers;
+  uint32_t grad_bucket = 0;
+  uint64_t bucket_elems = 0;
+  uint32_t x = 0, target = 0, loss = 0, per_sample = 0, y = 0;
+  std::vector<uint32_t> act, preact, dact;     // per hidden layer output: A_i, Z_i (GELU only), dA_i
+  uint32_t dy = 0;
+  std::vector<uint32_t> owned_buffers, owned_programs;
+  std::vector<Instr> forward_backward, update;
+  int n_launches = 0, n_collectives = 0;
+  std::vector<zyxb_event> pending;
+  // profiling: one event before the first instruction and one after every instruction of a profiled step
+  bool profiling = false;
+  std::vector<std::vector<zyxb_event>> prof_steps;
+  std::string err;
+};
+
+namespace {
+
+#define TRY(call)                                                              \
+  do {                                                                         \
+    int32_t st_ = (call);                                                      \
+    if (st_ != ZYXB_OK) {                                                      \
+      M->err = std::string(#call) + ": " + zyxb_last_error(M->ctx);            \
+      return st_;                                                              \
+    }                                                                          \
+  } while (0)
+
+int32_t alloc(zyxb_mlp* M, uint64_t bytes, uint32_t* out, bool zero = false) {
+  zyxb_event ev{};
+  TRY(zyxb_alloc(M->ctx, M->dev, bytes, out, &ev));
+  M->owned_buffers.push_back(*out);
+  if (zero) TRY(zyxb_memset(M->ctx, M->dev, *out, 0, 0, bytes));
+  return ZYXB_OK;
+}
+
+int32_t program(zyxb_mlp* M, const zyxb_kernel_desc& d, uint32_t* out) {
+  TRY(zyxb_program_create(M->ctx, M->dev, &d, out));
+  M->owned_programs.push_back(*out);
+  return ZYXB_OK;
+}
+
+zyxb_kernel_desc gemm_desc(int32_t dtype, uint64_t m, uint64_t n, uint64_t k, bool ta, bool tb, int32_t epi, bool preact) {
+  zyxb_kernel_desc d{};
+  d.kind = ZYXB_KIND_GEMM;
+  d.u.gemm.dtype = dtype; d.u.gemm.m = m; d.u.gemm.n = n; d.u.gemm.k = k; d.u.gemm.batch = 1;
+  d.u.gemm.trans_a = ta; d.u.gemm.trans_b = tb; d.u.gemm.stride_a = (int64_t)(m * k); d.u.gemm.stride_b = (int64_t)(k * n);
+  d.u.gemm.stride_c = (int64_t)(m * n); d.u.gemm.epilogue = epi; d.u.gemm.store_preact = preact; d.u.gemm.alpha = 1.0f;
+  return d;
+}
+zyxb_kernel_desc row_desc(int32_t op, int32_t dtype, uint64_t rows, uint64_t cols) {
+  zyxb_kernel_desc d{};
+  d.kind = ZYXB_KIND_ROWREDUCE;
+  d.u.rowreduce.op = op; d.u.rowreduce.dtype = dtype; d.u.rowreduce.rows = rows; d.u.rowreduce.cols = cols; d.u.rowreduce.correction = 1;
+  return d;
+}
+zyxb_kernel_desc ew_desc(int32_t op, int32_t dtype, uint64_t numel, float p0) {
+  zyxb_kernel_desc d{};
+  d.kind = ZYXB_KIND_ELTWISE;
+  d.u.eltwise.op = op; d.u.eltwise.dtype = dtype; d.u.eltwise.dtype_out = dtype; d.u.eltwise.numel = numel; d.u.eltwise.p0 = p0;
+  return d;
+}
+
+int32_t push_launch(zyxb_mlp* M, std::vector<Instr>& plan, const zyxb_kernel_desc& d, std::vector<uint32_t> args, bool wait_coll = false) {
+  Instr in;
+  in.kind = Instr::LAUNCH; in.args = std::move(args); in.wait_collectives = wait_coll;
+  in.desc_kind = d.kind;
+  in.desc_sub = d.kind == ZYXB_KIND_GEMM ? (d.u.gemm.trans_a * 2 + d.u.gemm.trans_b)
+              : d.kind == ZYXB_KIND_ROWREDUCE ? d.u.rowreduce.op : d.kind == ZYXB_KIND_ELTWISE ? d.u.eltwise.op : d.u.optim.algo;
+  int32_t st = program(M, d, &in.program);
+  if (st) return st;
+  plan.push_back(std::move(in));
+  M->n_launches++;
+  return ZYXB_OK;
+}
+
+int32_t build(zyxb_mlp* M) {
+  const zyxb_mlp_config& c = M->cfg;
+  const int n = c.n_layers;
+  const int32_t dt = c.dtype;
+  const uint64_t es = dsize(dt), B = c.batch;
+
+  // ---- parameters, gradient bucket (last layer first), optimizer state ----
+  M->layers.resize(n);
+  const uint64_t align_elems = 256 / es;
+  uint64_t off = 0;
+  for (int i = n - 1; i >= 0; --i) {
+    Linear& L = M->layers[i];
+    L.in_features = c.dims[i]; L.out_features = c.dims[i + 1];
+    L.bucket_offset = off;
+    off += align_up(L.in_features * L.out_features, align_elems) + align_up(L.out_features, align_elems);
+    L.bucket_count = off - L.bucket_offset;
+  }
+  M->bucket_elems = off;
+  int32_t st;
+  if ((st = alloc(M, M->bucket_elems * es, &M->grad_bucket, true))) return st;
+  const bool adam = c.optim.algo != ZYXB_OPT_SGD;
+  const bool sgd_momentum = c.optim.algo == ZYXB_OPT_SGD && c.optim.momentum != 0.0f;
+  const int n_state = adam ? 2 : (sgd_momentum ? 1 : 0);
+  for (int i = 0; i < n; ++i) {
+    Linear& L = M->layers[i];
+    const uint64_t wn = L.in_features * L.out_features, bn = L.out_features;
+    if ((st = alloc(M, wn * es, &L.weight, true)) || (st = alloc(M, bn * es, &L.bias, true))) return st;
+    TRY(zyxb_buffer_view(M->ctx, M->dev, M->grad_bucket, L.bucket_offset * es, wn * es, &L.weight_grad));
+    TRY(zyxb_buffer_view(M->ctx, M->dev, M->grad_bucket, (L.bucket_offset + align_up(wn, align_elems)) * es, bn * es, &L.bias_grad));
+    M->owned_buffers.push_back(L.weight_grad); M->owned_buffers.push_back(L.bias_grad);
+    for (int s = 0; s < n_state; ++s)
+      if ((st = alloc(M, wn * es, &L.state[s][0], true)) || (st = alloc(M, bn * es, &L.state[s][1], true))) return st;
+  }
+
+  // ---- activations ----
+  if ((st = alloc(M, B * c.dims[0] * es, &M->x))) return st;
+  const bool ce = c.loss == ZYXB_LOSS_CROSS_ENTROPY;
+  if ((st = alloc(M, ce ? B * 4 : B * c.dims[n] * es, &M->target))) return st;
+  if ((st = alloc(M, 4, &M->loss, true))) return st;
+  if (ce && (st = alloc(M, B * 4, &M->per_sample))) return st;
+  if ((st = alloc(M, B * c.dims[n] * es, &M->y)) || (st = alloc(M, B * c.dims[n] * es, &M->dy))) return st;
+  M->act.assign(n, 0); M->preact.assign(n, 0); M->dact.assign(n, 0);
+  for (int i = 0; i + 1 < n; ++i) {
+    const uint64_t bytes = B * c.dims[i + 1] * es;
+    if ((st = alloc(M, bytes, &M->act[i])) || (st = alloc(M, bytes, &M->dact[i]))) return st;
+    if (c.activation == ZYXB_ACT_GELU && (st = alloc(M, bytes, &M->preact[i]))) return st;
+  }
+
+  // ---- forward: Linear::forward per layer, activation fused into the matmul epilogue ----
+  std::vector<Instr>& P = M->forward_backward;
+  for (int i = 0; i < n; ++i) {
+    const Linear& L = M->layers[i];
+    const bool last = i == n - 1;
+    const uint32_t in = i == 0 ? M->x : M->act[i - 1];
+    int32_t epi = ZYXB_EPI_BIAS;
+    if (!last && c.activation == ZYXB_ACT_RELU) epi = ZYXB_EPI_BIAS_RELU;
+    if (!last && c.activation == ZYXB_ACT_GELU) epi = ZYXB_EPI_BIAS_GELU;
+    const bool keep_z = !last && c.activation == ZYXB_ACT_GELU;   // gelu' needs the pre-activation; relu' reads the output
+    std::vector<uint32_t> args = {in, L.weight, L.bias, last ? M->y : M->act[i]};
+    if (keep_z) args.push_back(M->preact[i]);
+    if ((st = push_launch(M, P, gemm_desc(dt, B, L.out_features, L.in_features, false, true, epi, keep_z), args))) return st;
+  }
+  // ---- loss and its gradient ----
+  const uint64_t out_f = c.dims[n];
+  if (ce) {
+    if ((st = push_launch(M, P, row_desc(ZYXB_RR_CROSS_ENTROPY, ZYXB_F32, B, out_f), {M->y, M->target, M->per_sample, M->loss}))) return st;
+    if ((st = push_launch(M, P, row_desc(ZYXB_RR_CROSS_ENTROPY_BWD, ZYXB_F32, B, out_f), {M->y, M->target, M->dy}))) return st;
+  } else {
+    if ((st = push_launch(M, P, row_desc(ZYXB_RR_MSE, dt, B, out_f), {M->y, M->target, M->loss}))) return st;
+    if ((st = push_launch(M, P, ew_desc(ZYXB_EW_MSE_BWD, dt, B * out_f, 1.0f / (float)(B * out_f)), {M->y, M->target, M->dy}))) return st;
+  }
+  // ---- backward, last layer first ----
+  for (int i = n - 1; i >= 0; --i) {
+    const Linear& L = M->layers[i];
+    const uint32_t dz = i == n - 1 ? M->dy : M->dact[i];
+    const uint32_t in = i == 0 ? M->x : M->act[i - 1];
+    // dW = dZ^T . input   ([out, B] x [B, in]); db = column sums of dZ
+    if ((st = push_launch(M, P, gemm_desc(dt, L.out_features, L.in_features, B, true, false, ZYXB_EPI_NONE, false), {dz, in, L.weight_grad}))) return st;
+    if ((st = push_launch(M, P, row_desc(ZYXB_RR_COLSUM, dt, B, L.out_features), {dz, L.bias_grad}))) return st;
+    if (c.world > 1 && c.bucket_per_layer) {
+      Instr ar; ar.kind = Instr::ALLREDUCE; ar.offset = L.bucket_offset; ar.count = L.bucket_count;
+      P.push_back(ar); M->n_collectives++;
+    }
+    if (i > 0) {
+      // dZ_prev = (dZ . W) * act'(z_prev)   ([B, out] x [out, in]); the activation's adjoint rides in the matmul epilogue
+      if (c.activation == ZYXB_ACT_RELU) {
+        if ((st = push_launch(M, P, gemm_desc(dt, B, L.in_features, L.out_features, false, false, ZYXB_EPI_MUL_RELU_GRAD, false),
+                              {dz, L.weight, M->act[i - 1], M->dact[i - 1]}))) return st;
+      } else if (c.activation == ZYXB_ACT_GELU) {
+        if ((st = push_launch(M, P, gemm_desc(dt, B, L.in_features, L.out_features, false, false, ZYXB_EPI_MUL_GELU_GRAD, false),
+                              {dz, L.weight, M->preact[i - 1], M->dact[i - 1]}))) return st;
+      } else {
+        if ((st = push_launch(M, P, gemm_desc(dt, B, L.in_features, L.out_features, false, false, ZYXB_EPI_NONE, false),
+                              {dz, L.weight, M->dact[i - 1]}))) return st;
+      }
+    }
+  }
+  if (c.world > 1 && !c.bucket_per_layer) {
+    Instr ar; ar.kind = Instr::ALLREDUCE; ar.offset = 0; ar.count = M->bucket_elems;
+    P.push_back(ar); M->n_collectives++;
+  }
+
+  // ---- optimizer: one program over every parameter, Module::iter() order ----
+  std::vector<uint64_t> numel;
+  std::vector<uint32_t> p, g, s0, s1;
+  for (int i = 0; i < n; ++i) {
+    const Linear& L = M->layers[i];
+    numel.push_back(L.in_features * L.out_features); numel.push_back(L.out_features);
+    p.push_back(L.weight); p.push_back(L.bias);
+    g.push_back(L.weight_grad); g.push_back(L.bias_grad);
+    s0.push_back(L.state[0][0]); s0.push_back(L.state[0][1]);
+    s1.push_back(L.state[1][0]); s1.push_back(L.state[1][1]);
+  }
+  zyxb_kernel_desc od{};
+  od.kind = ZYXB_KIND_OPTIM;
+  od.u.optim = c.optim;
+  od.u.optim.dtype = dt; od.u.optim.n_tensors = 2 * n; od.u.optim.numel = numel.data();
+  if (c.world > 1) od.u.optim.grad_scale = 1.0f / (float)c.world;
+  std::vector<uint32_t> args = p;
+  args.insert(args.end(), g.begin(), g.end());
+  if (n_state >= 1) args.insert(args.end(), s0.begin(), s0.end());
+  if (n_state >= 2) args.insert(args.end(), s1.begin(), s1.end());
+  return push_launch(M, M->update, od, args, /*wait_coll=*/true);
+}
+
+int32_t mark(zyxb_mlp* M) {
+  if (!M->profiling) return ZYXB_OK;
+  zyxb_event ev{};
+  TRY(zyxb_event_record(M->ctx, M->dev, &ev));
+  M->prof_steps.back().push_back(ev);
+  return ZYXB_OK;
+}
+
+int32_t run(zyxb_mlp* M, const std::vector<Instr>& plan, const zyxb_event* wait, int32_t n_wait) {
+  bool first = true;
+  for (const Instr& in : plan) {
+    if (in.kind == Instr::ALLREDUCE) {
+      zyxb_event ev{};
+      TRY(zyxb_allreduce_sum(M->ctx, M->dev, M->grad_bucket, in.offset, in.count, M->cfg.dtype, nullptr, 0, &ev));
+      M->pending.push_back(ev);
+      int32_t stm = mark(M);   // keeps one mark per instruction; a collective runs on its own stream
+      if (stm) return stm;
+      continue;
+    }
+    std::vector<zyxb_event> w;
+    if (first && n_wait > 0) w.assign(wait, wait + n_wait);
+    if (in.wait_collectives) { w.insert(w.end(), M->pending.begin(), M->pending.end()); M->pending.clear(); }
+    TRY(zyxb_launch(M->ctx, M->dev, in.program, in.args.data(), (int32_t)in.args.size(), w.empty() ? nullptr : w.data(), (int32_t)w.size(), nullptr));
+    first = false;
+    int32_t stm = mark(M);
+    if (stm) return stm;
+  }
+  return ZYXB_OK;
+}
+
+}  // namespace
+
+extern "C" {
+#pragma GCC visibility push(default)
+
+int32_t zyxb_mlp_create(zyxb_ctx* ctx, int32_t dev, const zyxb_mlp_config* config, zyxb_mlp** out) {
+  if (!ctx || !config || !out) return ZYXB_ERR_INITIALIZATION;
+  *out = nullptr;
+  zyxb_mlp* M = new zyxb_mlp();
+  M->ctx = ctx; M->dev = dev; M->cfg = *config;
+  const zyxb_mlp_config& c = M->cfg;
+  bool ok = c.n_layers >= 1 && c.n_layers <= 8 && c.batch > 0 && (c.dtype == ZYXB_F32 || c.dtype == ZYXB_BF16 || c.dtype == ZYXB_F16);
+  for (int i = 0; ok && i <= c.n_layers; ++i) ok = c.dims[i] > 0;
+  if (ok && c.loss == ZYXB_LOSS_CROSS_ENTROPY && c.dtype != ZYXB_F32) ok = false;
+  if (c.world < 1) M->cfg.world = 1;
+  if (!ok) { delete M; return ZYXB_ERR_INCORRECT_KERNEL_ARG; }
+  int32_t st = build(M);
+  if (st != ZYXB_OK) {
+    fprintf(stderr, "zyxb_mlp_create: %s\n", M->err.c_str());
+    zyxb_mlp_destroy(M);
+    return st;
+  }
+  *out = M;
+  return ZYXB_OK;
+}
+
+int32_t zyxb_mlp_destroy(zyxb_mlp* M) {
+  if (!M) return ZYXB_OK;
+  zyxb_device_sync(M->ctx, M->dev);
+  if (!M->pending.empty()) zyxb_release_events(M->ctx, M->dev, M->pending.data(), (int32_t)M->pending.size());
+  for (uint32_t p : M->owned_programs) zyxb_program_release(M->ctx, M->dev, p);
+  // views were pushed after their parent: free in reverse so a parent outlives its views
+  for (auto it = M->owned_buffers.rbegin(); it != M->owned_buffers.rend(); ++it) zyxb_free(M->ctx, M->dev, *it, nullptr, 0);
+  delete M;
+  return ZYXB_OK;
+}
+
+const char* zyxb_mlp_last_error(zyxb_mlp* M) { return M ? M->err.c_str() : ""; }
+
+int32_t zyxb_mlp_tensor(zyxb_mlp* M, int32_t which, int32_t i, uint32_t* out_buf, uint64_t* out_numel) {
+  if (!M || i < 0 || i >= 2 * M->cfg.n_layers || which < 0 || which > 3) return ZYXB_ERR_INCORRECT_KERNEL_ARG;
+  const Linear& L = M->layers[i / 2];
+  const int wb = i % 2;
+  uint32_t b = 0;
+  switch (which) {
+    case 0: b = wb ? L.bias : L.weight; break;
+    case 1: b = wb ? L.bias_grad : L.weight_grad; break;
+    default: b = L.state[which - 2][wb];
+  }
+  if (b == 0) return ZYXB_ERR_INCORRECT_KERNEL_ARG;
+  if (out_buf) *out_buf = b;
+  if (out_numel) *out_numel = wb ? L.out_features : L.in_features * L.out_features;
+  return ZYXB_OK;
+}
+
+int32_t zyxb_mlp_io(zyxb_mlp* M, uint32_t* out_x, uint32_t* out_target, uint32_t* out_loss, uint32_t* out_y) {
+  if (!M) return ZYXB_ERR_INCORRECT_KERNEL_ARG;
+  if (out_x) *out_x = M->x;
+  if (out_target) *out_target = M->target;
+  if (out_loss) *out_loss = M->loss;
+  if (out_y) *out_y = M->y;
+  return ZYXB_OK;
+}
+
+int32_t zyxb_mlp_forward_backward(zyxb_mlp* M) { return M ? run(M, M->forward_backward, nullptr, 0) : ZYXB_ERR_INCORRECT_KERNEL_ARG; }
+int32_t zyxb_mlp_update(zyxb_mlp* M) { return M ? run(M, M->update, nullptr, 0) : ZYXB_ERR_INCORRECT_KERNEL_ARG; }
+
+int32_t zyxb_mlp_bind_inputs(zyxb_mlp* M, uint32_t x, uint32_t target) {
+  if (!M) return ZYXB_ERR_INCORRECT_KERNEL_ARG;
+  const uint64_t es = dsize(M->cfg.dtype);
+  uint64_t bx = 0, bt = 0;
+  TRY(zyxb_buffer_bytes(M->ctx, M->dev, x, &bx));
+  TRY(zyxb_buffer_bytes(M->ctx, M->dev, target, &bt));
+  const uint64_t need_t = M->cfg.loss == ZYXB_LOSS_CROSS_ENTROPY ? M->cfg.batch * 4 : M->cfg.batch * M->cfg.dims[M->cfg.n_layers] * es;
+  if (bx < M->cfg.batch * M->cfg.dims[0] * es || bt < need_t) { M->err = "bind_inputs: buffer too small"; return ZYXB_ERR_INCORRECT_KERNEL_ARG; }
+  for (Instr& in : M->forward_backward)
+    for (uint32_t& a : in.args) { if (a == M->x) a = x; else if (a == M->target) a = target; }
+  M->x = x; M->target = target;
+  return ZYXB_OK;
+}
+
+int32_t zyxb_mlp_step_event(zyxb_mlp* M, const zyxb_event* wait, int32_t n_wait, zyxb_event* out_event) {
+  int32_t st = zyxb_mlp_step(M, wait, n_wait);
+  if (st || !out_event) return st;
+  // a non-timing marker after the last launch of the step
+  TRY(zyxb_event_record(M->ctx, M->dev, out_event));
+  return ZYXB_OK;
+}
+
+int32_t zyxb_mlp_step(zyxb_mlp* M, const zyxb_event* wait, int32_t n_wait) {
+  if (!M) return ZYXB_ERR_INCORRECT_KERNEL_ARG;
+  if (M->profiling) {
+    M->prof_steps.emplace_back();
+    zyxb_event ev{};
+    TRY(zyxb_event_record(M->ctx, M->dev, &ev));
+    M->prof_steps.back().push_back(ev);
+  }
+  int32_t st = run(M, M->forward_backward, wait, n_wait);
+  if (st) return st;
+  return run(M, M->update, nullptr, 0);
+}
+
+int32_t zyxb_mlp_profile(zyxb_mlp* M, int32_t enable) {
+  if (!M) return ZYXB_ERR_INCORRECT_KERNEL_ARG;
+  M->profiling = enable != 0;
+  return ZYXB_OK;
+}
+
+int32_t zyxb_mlp_profile_read(zyxb_mlp* M, float* out_ms, int32_t* out_kind, int32_t capacity, int32_t* out_n, int32_t* out_steps) {
+  if (!M) return ZYXB_ERR_INCORRECT_KERNEL_ARG;
+  const int n = (int)(M->forward_backward.size() + M->update.size());
+  if (out_n) *out_n = n;
+  if (out_steps) *out_steps = (int32_t)M->prof_steps.size();
+  if (capacity < n) return out_ms ? ZYXB_ERR_INCORRECT_KERNEL_ARG : ZYXB_OK;
+  for (int i = 0; i < n; ++i) out_ms[i] = 0.0f;
+  for (auto& evs : M->prof_steps) {
+    if ((int)evs.size() != n + 1) continue;
+    for (int i = 0; i < n; ++i) {
+      float ms = 0.0f;
+      TRY(zyxb_event_elapsed_ms(M->ctx, M->dev, evs[i], evs[i + 1], &ms));
+      out_ms[i] += ms;
+    }
+    TRY(zyxb_release_events(M->ctx, M->dev, evs.data(), (int32_t)evs.size()));
+  }
+  if (out_kind) {
+    int i = 0;
+    for (const auto* plan : {&M->forward_backward, &M->update})
+      for (const Instr& in : *plan) out_kind[i++] = in.kind == Instr::ALLREDUCE ? -1 : in.desc_kind * 100 + in.desc_sub;
+  }
+  M->prof_steps.clear();
+  return ZYXB_OK;
+}
+
+int32_t zyxb_mlp_plan_size(zyxb_mlp* M, int32_t* out_launches, int32_t* out_collectives) {
+  if (!M) return ZYXB_ERR_INCORRECT_KERNEL_ARG;
+  if (out_launches) *out_launches = M->n_launches;
+  if (out_collectives) *out_collectives = M->n_collectives;
+  return ZYXB_OK;
+}
+
+#pragma GCC visibility pop
+}  // extern "C"

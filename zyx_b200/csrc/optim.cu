@@ -35,6 +35,14 @@ struct OptHyper {
   int rn;
 };
 
+// f32 tensors use IEEE division and square root (1e-5 parity); 16-bit tensors, whose results are
+// cut to 8 or 11 significant bits anyway, use the SFU forms (a few ulp of f32) so that the kernel
+// stays memory-bound.
+template <typename T> __device__ __forceinline__ float opt_div(float a, float b) { return __fdividef(a, b); }
+template <> __device__ __forceinline__ float opt_div<float>(float a, float b) { return a / b; }
+template <typename T> __device__ __forceinline__ float opt_sqrt(float a) { float r; asm("sqrt.approx.f32 %0, %1;" : "=f"(r) : "f"(a)); return r; }
+template <> __device__ __forceinline__ float opt_sqrt<float>(float a) { return sqrtf(a); }
+
 template <typename T, int ALGO>
 __device__ __forceinline__ void opt_update(float& pv, float gv, float& mv, float& vv, const OptHyper& h, bool rn) {
   auto round_state = [&](float x) { return (float)Elem<T>::load(Elem<T>::store(x, rn)); };
@@ -53,10 +61,10 @@ __device__ __forceinline__ void opt_update(float& pv, float gv, float& mv, float
     float nv = h.first ? gv * gv * h.one_minus_b2 : vv * h.beta2 + gv * gv * h.one_minus_b2;
     nm = round_state(nm); nv = round_state(nv);
     mv = nm; vv = nv;
-    const float mh = nm / h.bc1, vh = nv / h.bc2;
+    const float mh = opt_div<T>(nm, h.bc1), vh = opt_div<T>(nv, h.bc2);
     float np;
-    if (h.mode == 1) np = pv - mh / ((sqrtf(vh) + h.eps) * h.lr);
-    else np = pv - h.lr * mh / (sqrtf(vh) + h.eps);
+    if (h.mode == 1) np = pv - opt_div<T>(mh, (opt_sqrt<T>(vh) + h.eps) * h.lr);
+    else np = pv - opt_div<T>(h.lr * mh, opt_sqrt<T>(vh) + h.eps);
     if (h.mode != 0 && h.wd != 0.0f) np = np * h.decay;
     pv = np;
   }
@@ -75,7 +83,6 @@ __global__ void __launch_bounds__(OPT_THREADS) optim_kernel(OptTable tab, OptHyp
   S* m = reinterpret_cast<S*>(tab.m[t]);
   S* v = reinterpret_cast<S*>(tab.v[t]);
   const bool rn = hy.rn != 0;
-  constexpr bool HAS_M = true;
   const bool use_m = (ALGO != ZYXB_OPT_SGD) || (hy.momentum != 0.0f);
   // hyper-parameters as scalars of the tensor dtype
   OptHyper h = hy;
@@ -87,31 +94,44 @@ __global__ void __launch_bounds__(OPT_THREADS) optim_kernel(OptTable tab, OptHyp
   // keep the "is it zero" tests on the caller's values, as the reference tests its f32 fields
   if (hy.wd == 0.0f) h.wd = 0.0f;
   if (hy.momentum == 0.0f) h.momentum = 0.0f;
-  (void)HAS_M;
 
   const uint64_t base = chunk * (uint64_t)(OPT_THREADS * OPT_UNROLL * VEC);
+  const bool read_state = use_m && !hy.first;
+  // all loads of the chunk are issued before any store: p, m and v are read and written through
+  // pointers the compiler must assume may alias, so a load placed after a store would wait for it
+  Pack<S, VEC> pp[OPT_UNROLL], pg[OPT_UNROLL], pm[OPT_UNROLL], pv[OPT_UNROLL];
+  bool whole[OPT_UNROLL];
 #pragma unroll
   for (int u = 0; u < OPT_UNROLL; ++u) {
     const uint64_t i = base + ((uint64_t)u * OPT_THREADS + threadIdx.x) * VEC;
-    if (i + VEC <= numel) {
-      Pack<S, VEC> pp = load_pack<S, VEC>(p + i), pg = load_pack_stream<S, VEC>(g + i), pm, pv;
-      const bool read_state = use_m && !hy.first;
-      if (read_state) { pm = load_pack<S, VEC>(m + i); if constexpr (ALGO != ZYXB_OPT_SGD) pv = load_pack<S, VEC>(v + i); }
+    whole[u] = i + VEC <= numel;
+    if (whole[u]) {
+      pp[u] = load_pack<S, VEC>(p + i);
+      pg[u] = load_pack_stream<S, VEC>(g + i);
+      if (read_state) {
+        pm[u] = load_pack<S, VEC>(m + i);
+        if constexpr (ALGO != ZYXB_OPT_SGD) pv[u] = load_pack<S, VEC>(v + i);
+      }
+    }
+  }
+#pragma unroll
+  for (int u = 0; u < OPT_UNROLL; ++u) {
+    const uint64_t i = base + ((uint64_t)u * OPT_THREADS + threadIdx.x) * VEC;
+    if (whole[u]) {
 #pragma unroll
       for (int k = 0; k < VEC; ++k) {
-        float fp = (float)Elem<T>::load(pp.v[k]), fg = (float)Elem<T>::load(pg.v[k]);
-        float fm = read_state ? (float)Elem<T>::load(pm.v[k]) : 0.0f;
-        float fv = (read_state && ALGO != ZYXB_OPT_SGD) ? (float)Elem<T>::load(pv.v[k]) : 0.0f;
+        float fp = (float)Elem<T>::load(pp[u].v[k]), fg = (float)Elem<T>::load(pg[u].v[k]);
+        float fm = read_state ? (float)Elem<T>::load(pm[u].v[k]) : 0.0f;
+        float fv = (read_state && ALGO != ZYXB_OPT_SGD) ? (float)Elem<T>::load(pv[u].v[k]) : 0.0f;
         opt_update<T, ALGO>(fp, fg, fm, fv, h, rn);
-        pp.v[k] = Elem<T>::store(fp, rn); pm.v[k] = Elem<T>::store(fm, rn);
-        if constexpr (ALGO != ZYXB_OPT_SGD) pv.v[k] = Elem<T>::store(fv, rn);
+        pp[u].v[k] = Elem<T>::store(fp, rn); pm[u].v[k] = Elem<T>::store(fm, rn);
+        if constexpr (ALGO != ZYXB_OPT_SGD) pv[u].v[k] = Elem<T>::store(fv, rn);
       }
-      store_pack<S, VEC>(p + i, pp);
-      if (use_m) { store_pack<S, VEC>(m + i, pm); if constexpr (ALGO != ZYXB_OPT_SGD) store_pack<S, VEC>(v + i, pv); }
+      store_pack<S, VEC>(p + i, pp[u]);
+      if (use_m) { store_pack<S, VEC>(m + i, pm[u]); if constexpr (ALGO != ZYXB_OPT_SGD) store_pack<S, VEC>(v + i, pv[u]); }
     } else {
       // ragged tail of a tensor whose length is not a multiple of VEC
       for (uint64_t j = i; j < numel && j < i + VEC; ++j) {
-        const bool read_state = use_m && !hy.first;
         float fp = (float)Elem<T>::load(p[j]), fg = (float)Elem<T>::load(g[j]);
         float fm = read_state ? (float)Elem<T>::load(m[j]) : 0.0f;
         float fv = (read_state && ALGO != ZYXB_OPT_SGD) ? (float)Elem<T>::load(v[j]) : 0.0f;

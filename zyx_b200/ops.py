@@ -94,7 +94,7 @@ class Session:
         shape = (batch, m, n) if a.ndim == 3 else (m, n)
         d = B.gemm_desc(dtype, m, n, k, batch=batch, trans_a=ta, trans_b=tb, stride_b=(0 if b.ndim == 2 else k * n),
                         epilogue=epi, store_preact=want_preact, alpha=alpha)
-        ins = [a, b] + ([bias] if bias is not None else [])
+        ins = [a, b] + ([bias] if bias is not None else [])      # bias [n], or z shaped like the result for MUL_*_GRAD
         outs = [(shape, a.dtype)] * (2 if want_preact else 1)
         r = self.run(d, ins, outs)
         return (r[0], r[1]) if want_preact else r[0]
