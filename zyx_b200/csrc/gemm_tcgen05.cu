@@ -5,12 +5,13 @@
 // reference C backend computes (zyx/src/codegen/c.rs:616-629, reduce_ops.rs:52-60); only the
 // summation order differs.
 //
-// One persistent CTA per SM, 192 threads:
+// One persistent CTA per SM, 320 threads:
 //   warp 0      TMA producer   (one lane): fills a ring of STAGES {A tile, B tile} slots
 //   warp 1      MMA issuer     (one lane): tcgen05.mma 128 x BN x 16 per instruction, 4 per k-block;
 //                               tcgen05.commit releases the slot, and the accumulator when a tile is done
-//   warps 2..5  epilogue       : tcgen05.ld the 128 x BN f32 accumulator (lane = row), apply
-//                               alpha / bias / ReLU / GELU, convert and store 64 bytes per thread per chunk
+//   warps 2..9  epilogue       : tcgen05.ld the 128 x BN f32 accumulator (lane = row; two warps per TMEM
+//                               lane quarter, each taking half of the columns), apply alpha / bias / ReLU /
+//                               GELU / activation gradient, convert and store 64 bytes per thread per chunk
 // The accumulator is double-buffered in TMEM (2 x BN columns) so the epilogue of tile i overlaps
 // the MMAs of tile i+1.  Operands may be K-major (rows of K) or MN-major (rows of M or N) in
 // memory: all four transposition cases of the descriptor are served without a transpose pass.
@@ -31,7 +32,8 @@ namespace zyxb {
 constexpr int TC_BM = 128;          // UMMA M (cta_group::1): TMEM lane = row of the tile
 constexpr int TC_BK = 64;           // 64 x 2 bytes = one 128-byte swizzle atom along K
 constexpr int TC_UMMA_K = 16;
-constexpr int TC_THREADS = 192;
+constexpr int TC_THREADS = 320;
+constexpr int TC_EPI_THREADS = 256;
 constexpr uint64_t TC_WAIT_NS = 2000000000ull;   // 2 s bound on any single wait
 
 struct TcParams {
@@ -175,7 +177,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-    for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), 128); }
+    for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), TC_EPI_THREADS); }
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -276,7 +278,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
       }
     }
   } else {
-    // ---------------------------------- epilogue (warps 2..5) ----------------------------------
+    // ---------------------------------- epilogue (warps 2..9) ----------------------------------
+    const int col_half = (warp - 2) >> 2;                // warps 2..5 take the left half of the columns, 6..9 the right
     const uint32_t quarter = (uint32_t)(warp & 3);       // TMEM lanes this warp may read: 32*quarter .. +31
     const uint32_t row_in_tile = quarter * 32 + lane;
     uint32_t acc = 0, acc_phase = 0;
@@ -298,7 +301,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
       uint16_t* crow = reinterpret_cast<uint16_t*>(p.c) + (int64_t)bz * p.stride_c + (int64_t)row * p.n;
       uint16_t* zrow = p.preact ? reinterpret_cast<uint16_t*>(p.preact) + (int64_t)bz * p.stride_c + (int64_t)row * p.n : nullptr;
 #pragma unroll 1
-      for (int ch = 0; ch < BN / 32; ++ch) {
+      for (int ch = col_half * (BN / 64); ch < (col_half + 1) * (BN / 64); ++ch) {
         uint32_t r[32];
         tmem_ld32(tmem_base + ((quarter * 32u) << 16) + acc * BN + ch * 32, r);
         tmem_ld_wait();
@@ -381,7 +384,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
         }
       }
       tc_fence_before();
-      mbar_arrive(tempty_bar(acc));                      // 128 arrivals hand the accumulator back
+      mbar_arrive(tempty_bar(acc));                      // all epilogue threads arrive: the accumulator goes back to the MMA issuer
       if (++acc == 2) { acc = 0; acc_phase ^= 1; }
     }
   }
