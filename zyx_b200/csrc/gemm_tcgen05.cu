@@ -15,7 +15,7 @@
 // The accumulator is double-buffered in TMEM (2 x BN columns) so the epilogue of tile i overlaps
 // the MMAs of tile i+1.  Operands may be K-major (rows of K) or MN-major (rows of M or N) in
 // memory: all four transposition cases of the descriptor are served without a transpose pass.
-// No multicast and no clusters: every CTA loads its own tiles.
+// Every CTA loads its own tiles with plain per-CTA TMA loads; no thread-block clusters are used.
 //
 // Every wait on an mbarrier is bounded by wall-clock time; a wait that runs out sets a bit in
 // the device status word, raises the CTA's abort flag and the kernel drains and returns.
