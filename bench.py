@@ -445,8 +445,8 @@ def host_threads():
 def run_reference(args, rank, world):
     """The reference arm: the CPU oracle (port of the reference C backend) on all host threads."""
     if rank != 0:
-        return
-    os.environ.setdefault("OMP_NUM_THREADS", str(host_threads()))
+        return None
+    os.environ["OMP_NUM_THREADS"] = str(host_threads())     # torchrun sets it to 1
     w = make_workload(args)
     if hasattr(w, "host_inputs"):
         w.host_inputs()
@@ -464,10 +464,23 @@ def run_reference(args, rank, world):
             "dtype": w.dtype, "data": "synthetic", "config": {"workload": w.name},
             "cpu_baseline": {"value": value, "unit": w.unit, "cores": host_threads(), "kind": "port", "sample": sample},
             "e2e": {"value": value, "unit": w.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
-    print(json.dumps(line), flush=True)
+    return json.dumps(line)
 
 
 def main():
+    # stdout carries exactly one JSON line: anything a library prints there (NCCL's version banner) goes to stderr
+    real_stdout = os.dup(1)
+    os.dup2(2, 1)
+    try:
+        line = run()
+    finally:
+        sys.stdout.flush()
+        os.dup2(real_stdout, 1)
+    if line is not None:
+        print(line, flush=True)
+
+
+def run():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
@@ -485,6 +498,7 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         return run_reference(args, rank, world)
+    out_line = None
 
     import torch
     import torch.distributed as dist
@@ -573,10 +587,11 @@ def main():
             os.environ.setdefault("OMP_NUM_THREADS", str(host_threads()))
             v, sample = w.cpu_baseline()
             line["cpu_baseline"] = {"value": v, "unit": w.unit, "cores": host_threads(), "kind": "port", "sample": sample}
-        print(json.dumps(line), flush=True)
+        out_line = json.dumps(line)
     sess.close()
     if world > 1:
         dist.destroy_process_group()
+    return out_line
 
 
 if __name__ == "__main__":

@@ -21,6 +21,8 @@
 // the device status word, raises the CTA's abort flag and the kernel drains and returns.
 #include <cuda.h>
 
+#include <stdlib.h>
+
 #include <algorithm>
 
 #include "common.cuh"
@@ -47,6 +49,8 @@ struct TcParams {
   int is_bf16;
   int a_batched, b_batched;   // 0: one matrix shared by every batch (its map has batch extent 1)
   uint32_t* status;
+  uint32_t* tile_counter;     // zeroed before the launch; CTAs draw tile indices from it
+  int dynamic_tiles;          // 1: draw tiles from the counter; 0: CTA i takes tiles i, i + grid, ...
 };
 
 // ---- PTX wrappers ------------------------------------------------------------------------------
@@ -169,8 +173,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
   auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
   auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
   auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + SM::BAR_OFFSET + 8 * (2 * STAGES + 4));
+  // tile queue: the producer draws tile indices from a global counter and hands them to the MMA issuer
+  // and the epilogue warps, so a CTA that starts late (SMs busy with a collective) simply takes fewer tiles
+  constexpr int TQ = 4;
+  constexpr uint32_t TILE_NONE = 0xffffffffu;
+  auto tq_full = [&](int i) { return bar_base + 8u * (2 * STAGES + 4 + i); };
+  auto tq_empty = [&](int i) { return bar_base + 8u * (2 * STAGES + 4 + TQ + i); };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + SM::BAR_OFFSET + 8 * (2 * STAGES + 4 + 2 * TQ));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile uint32_t* tile_q = reinterpret_cast<volatile uint32_t*>(tmem_slot + 2);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   constexpr uint32_t TMEM_COLS = 2 * BN;                  // two accumulator buffers (power of two >= 32)
@@ -178,6 +189,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
     for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), TC_EPI_THREADS); }
+    for (int i = 0; i < TQ; ++i) { mbar_init(tq_full(i), 1); mbar_init(tq_empty(i), 1 + TC_EPI_THREADS); }
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -201,6 +213,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
     tm = first_m + in_group % rows_in_group;
     tn = in_group / rows_in_group;
   };
+  // consumer side of the tile queue (MMA issuer and every epilogue thread keep their own cursor)
+  uint32_t tq_slot = 0, tq_phase = 0;
+  auto next_tile = [&](uint32_t code) -> uint32_t {
+    if (!mbar_wait(tq_full(tq_slot), tq_phase, abort_flag, p.status, code)) return TILE_NONE;
+    const uint32_t t = tile_q[tq_slot];
+    mbar_arrive(tq_empty(tq_slot));
+    if (++tq_slot == TQ) { tq_slot = 0; tq_phase ^= 1; }
+    return t;
+  };
 
   if (warp == 0) {
     // ---------------------------------- TMA producer ----------------------------------
@@ -208,7 +229,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
       uint32_t stage = 0, phase = 0;
       uint32_t issued = 0;
       bool ok = true;
-      for (uint32_t t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      // the index of the tile after this one is drawn while this one's loads are issued, so the round trip of
+      // the atomic never stalls the ring
+      uint32_t t_next = p.dynamic_tiles ? atomicAdd(p.tile_counter, 1u) : blockIdx.x;
+      while (ok) {
+        // publish the tile (a slot is free once the MMA issuer and all epilogue threads have read it)
+        if (!mbar_wait(tq_empty(tq_slot), tq_phase ^ 1, abort_flag, p.status, TC_ERR_PRODUCER)) { ok = false; break; }
+        uint32_t t = t_next;
+        if (t >= total_tiles) t = TILE_NONE;
+        else t_next = p.dynamic_tiles ? atomicAdd(p.tile_counter, 1u) : t + gridDim.x;
+        tile_q[tq_slot] = t;
+        mbar_arrive(tq_full(tq_slot));
+        if (++tq_slot == TQ) { tq_slot = 0; tq_phase ^= 1; }
+        if (t == TILE_NONE) break;
         uint32_t bz, tm, tn;
         tile_coords(t, bz, tm, tn);
         const int za = p.a_batched ? (int)bz : 0, zb = p.b_batched ? (int)bz : 0;
@@ -252,7 +285,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
       const uint32_t idesc = make_idesc(p.is_bf16 != 0, A_MN, B_MN, TC_BM, BN);
       uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
       bool ok = true;
-      for (uint32_t t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      while (ok) {
+        if (next_tile(TC_ERR_MMA) == TILE_NONE) break;
         if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1, abort_flag, p.status, TC_ERR_MMA)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
@@ -291,7 +325,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
     const float calpha = cdt(p.alpha);
     const GeluConsts gc{cdt(0.5f), cdt(0.044715f), cdt(0.7978845608028654f)};
     bool ok = true;
-    for (uint32_t t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+    while (ok) {
+      const uint32_t t = next_tile(TC_ERR_EPILOGUE);
+      if (t == TILE_NONE) break;
       uint32_t bz, tm, tn;
       tile_coords(t, bz, tm, tn);
       if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.status, TC_ERR_EPILOGUE)) { ok = false; break; }
@@ -474,6 +510,16 @@ int launch_gemm_tc(const GemmParams& p, int dtype, const LaunchCtx& lc, std::str
   tp.tiles_m = (uint32_t)((p.m + TC_BM - 1) / TC_BM); tp.tiles_n = (uint32_t)((p.n + bn - 1) / bn);
   tp.stride_c = p.stride_c; tp.alpha = p.alpha; tp.epilogue = p.epilogue; tp.rn = p.rn; tp.is_bf16 = bf16 ? 1 : 0;
   tp.status = lc.status_word;
+  // tile counters live in the words after the status word, used in rotation and zeroed in stream order
+  // While a collective may be running beside the matmul (a communicator exists) some SMs are not available to
+  // the persistent grid; drawing tiles from a counter lets the CTAs that do run share the work evenly.  Alone on
+  // the GPU the fixed assignment is marginally faster (no atomic per tile).
+  static const char* dyn_env = getenv("ZYXB_DYNAMIC_TILES");
+  tp.dynamic_tiles = dyn_env ? (dyn_env[0] == '1') : (lc.overlap_hint ? 1 : 0);
+  tp.tile_counter = lc.status_word + 8 + (*lc.launch_counter % 48);
+  if (tp.dynamic_tiles && cudaMemsetAsync(tp.tile_counter, 0, sizeof(uint32_t), lc.stream) != cudaSuccess) {
+    err = "gemm: tile counter reset failed"; return ZYXB_ERR_KERNEL_LAUNCH;
+  }
   tp.a_batched = (p.batch > 1 && p.stride_a != 0) ? 1 : 0;
   tp.b_batched = (p.batch > 1 && p.stride_b != 0) ? 1 : 0;
   const uint64_t total = (uint64_t)tp.tiles_m * tp.tiles_n * tp.batch;

@@ -12,6 +12,7 @@
 #include <stdio.h>
 #include <string.h>
 
+#include <algorithm>
 #include <string>
 #include <vector>
 
@@ -32,7 +33,7 @@ struct Instr {
   uint32_t program = 0;
   std::vector<uint32_t> args;
   uint64_t offset = 0, count = 0;          // ALLREDUCE: slice of the gradient bucket
-  bool wait_collectives = false;           // LAUNCH: wait for every pending allreduce event first
+  int wait_collectives = 0;                // LAUNCH: wait first for this many of the oldest pending allreduce events (-1: all)
   int desc_kind = 0, desc_sub = 0;         // ZYXB_KIND_* and the op / layout, for profile reports
 };
 
@@ -107,7 +108,7 @@ zyxb_kernel_desc ew_desc(int32_t op, int32_t dtype, uint64_t numel, float p0) {
   return d;
 }
 
-int32_t push_launch(zyxb_mlp* M, std::vector<Instr>& plan, const zyxb_kernel_desc& d, std::vector<uint32_t> args, bool wait_coll = false) {
+int32_t push_launch(zyxb_mlp* M, std::vector<Instr>& plan, const zyxb_kernel_desc& d, std::vector<uint32_t> args, int wait_coll = 0) {
   Instr in;
   in.kind = Instr::LAUNCH; in.args = std::move(args); in.wait_collectives = wait_coll;
   in.desc_kind = d.kind;
@@ -222,27 +223,36 @@ int32_t build(zyxb_mlp* M) {
     P.push_back(ar); M->n_collectives++;
   }
 
-  // ---- optimizer: one program over every parameter, Module::iter() order ----
-  std::vector<uint64_t> numel;
-  std::vector<uint32_t> p, g, s0, s1;
-  for (int i = 0; i < n; ++i) {
-    const Linear& L = M->layers[i];
-    numel.push_back(L.in_features * L.out_features); numel.push_back(L.out_features);
-    p.push_back(L.weight); p.push_back(L.bias);
-    g.push_back(L.weight_grad); g.push_back(L.bias_grad);
-    s0.push_back(L.state[0][0]); s0.push_back(L.state[0][1]);
-    s1.push_back(L.state[1][0]); s1.push_back(L.state[1][1]);
+  // ---- optimizer ----
+  // One rank: one program over every parameter, Module::iter() order.  Data parallel with a collective per layer:
+  // one program per layer, last layer first, each waiting only for its own layer's allreduce, so the update of the
+  // layers whose gradients have arrived overlaps the allreduce of the first layer's (the last to be produced).
+  const bool per_layer = c.world > 1 && c.bucket_per_layer;
+  const int groups = per_layer ? n : 1;
+  for (int gi = 0; gi < groups; ++gi) {
+    const int lo = per_layer ? n - 1 - gi : 0, hi = per_layer ? n - 1 - gi : n - 1;
+    std::vector<uint64_t> numel;
+    std::vector<uint32_t> p, g, s0, s1;
+    for (int i = lo; i <= hi; ++i) {
+      const Linear& L = M->layers[i];
+      numel.push_back(L.in_features * L.out_features); numel.push_back(L.out_features);
+      p.push_back(L.weight); p.push_back(L.bias);
+      g.push_back(L.weight_grad); g.push_back(L.bias_grad);
+      s0.push_back(L.state[0][0]); s0.push_back(L.state[0][1]);
+      s1.push_back(L.state[1][0]); s1.push_back(L.state[1][1]);
+    }
+    zyxb_kernel_desc od{};
+    od.kind = ZYXB_KIND_OPTIM;
+    od.u.optim = c.optim;
+    od.u.optim.dtype = dt; od.u.optim.n_tensors = (int32_t)p.size(); od.u.optim.numel = numel.data();
+    if (c.world > 1) od.u.optim.grad_scale = 1.0f / (float)c.world;
+    std::vector<uint32_t> args = p;
+    args.insert(args.end(), g.begin(), g.end());
+    if (n_state >= 1) args.insert(args.end(), s0.begin(), s0.end());
+    if (n_state >= 2) args.insert(args.end(), s1.begin(), s1.end());
+    if ((st = push_launch(M, M->update, od, args, per_layer ? 1 : -1))) return st;
   }
-  zyxb_kernel_desc od{};
-  od.kind = ZYXB_KIND_OPTIM;
-  od.u.optim = c.optim;
-  od.u.optim.dtype = dt; od.u.optim.n_tensors = 2 * n; od.u.optim.numel = numel.data();
-  if (c.world > 1) od.u.optim.grad_scale = 1.0f / (float)c.world;
-  std::vector<uint32_t> args = p;
-  args.insert(args.end(), g.begin(), g.end());
-  if (n_state >= 1) args.insert(args.end(), s0.begin(), s0.end());
-  if (n_state >= 2) args.insert(args.end(), s1.begin(), s1.end());
-  return push_launch(M, M->update, od, args, /*wait_coll=*/true);
+  return ZYXB_OK;
 }
 
 int32_t mark(zyxb_mlp* M) {
@@ -266,7 +276,11 @@ int32_t run(zyxb_mlp* M, const std::vector<Instr>& plan, const zyxb_event* wait,
     }
     std::vector<zyxb_event> w;
     if (first && n_wait > 0) w.assign(wait, wait + n_wait);
-    if (in.wait_collectives) { w.insert(w.end(), M->pending.begin(), M->pending.end()); M->pending.clear(); }
+    if (in.wait_collectives != 0) {
+      const size_t take = in.wait_collectives < 0 ? M->pending.size() : std::min(M->pending.size(), (size_t)in.wait_collectives);
+      w.insert(w.end(), M->pending.begin(), M->pending.begin() + take);
+      M->pending.erase(M->pending.begin(), M->pending.begin() + take);
+    }
     TRY(zyxb_launch(M->ctx, M->dev, in.program, in.args.data(), (int32_t)in.args.size(), w.empty() ? nullptr : w.data(), (int32_t)w.size(), nullptr));
     first = false;
     int32_t stm = mark(M);

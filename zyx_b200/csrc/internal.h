@@ -20,6 +20,7 @@ struct LaunchCtx {
   uint64_t* launch_counter; // host counter of kernels launched
   void* tma_encode;         // cuTensorMapEncodeTiled entry point (driver), or nullptr
   int device;
+  bool overlap_hint;        // a communicator exists: collectives may run beside the kernels
 };
 
 // Every launcher validates the argument count and the byte size of each buffer before it
