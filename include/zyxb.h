@@ -280,6 +280,26 @@ int32_t zyxb_launch_count(zyxb_ctx* ctx, int32_t dev, uint64_t* out_count);
  * reading it synchronises the device and clears it */
 int32_t zyxb_device_status(zyxb_ctx* ctx, int32_t dev, uint32_t* out_status);
 
+/* ---- column sums for callers that cannot allocate -------------------------------------------------------
+ * No counterpart in the reference.  y[cols] = sum over rows of x[rows, cols] (what a ZYXB_RR_COLSUM program
+ * computes: the bias gradient of a Linear layer), for callers that must not reach an allocator while they
+ * run: a zyx plan being replayed inside a latency-critical serving loop, a host that has handed all device
+ * memory to its own pool so that cudaMalloc would fail, or code running where cudaMalloc's implicit device
+ * synchronisation is not acceptable.  The partial sums go to a fixed array inside the loaded library
+ * (1 Mi floats = 4 MiB per GPU, resident from the moment the library is loaded on that GPU until the process
+ * exits) instead of the context's scratch buffer, and the call itself performs no cudaMalloc / cudaFree and
+ * calls no allocating library routine; x and y are existing pool buffers.
+ *   - limit: cols <= 1 048 576 (zyxb_colsum_static_capacity); larger shapes are refused with
+ *     IncorrectKernelArg and a message naming the limit — use a ZYXB_RR_COLSUM program for those;
+ *   - the first call on a device looks up the array's device address (cudaGetSymbolAddress) and caches it:
+ *     make that first call during set-up, before any stream capture begins;
+ *   - every call on a device shares the one array, which keeps the previous call's partials; each call
+ *     overwrites all the partials it reads, so nothing needs clearing, but calls that overlap on the GPU
+ *     race — issue them one after another (they are queued in order on the device's compute stream);
+ *   - dtype f32 / bf16 / f16; runs in order on the compute stream like zyxb_launch, no wait list, no event. */
+int32_t zyxb_colsum_static(zyxb_ctx* ctx, int32_t dev, int32_t dtype, uint32_t x, uint32_t y, uint64_t rows, uint64_t cols);
+int32_t zyxb_colsum_static_capacity(uint64_t* out_floats);
+
 /* ---- timing (the ZYX_DEBUG perf print, zyx/src/runtime.rs:1798-1838) ---- */
 int32_t zyxb_event_record(zyxb_ctx* ctx, int32_t dev, zyxb_event* out_event);
 int32_t zyxb_event_elapsed_ms(zyxb_ctx* ctx, int32_t dev, zyxb_event start, zyxb_event stop, float* out_ms);

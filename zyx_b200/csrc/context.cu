@@ -575,6 +575,26 @@ int32_t zyxb_launch(zyxb_ctx* ctx, int32_t dev, uint32_t prog, const uint32_t* a
   return record_event(ctx, D, D.compute, out_event, ZYXB_ERR_KERNEL_LAUNCH);
 }
 
+int32_t zyxb_colsum_static(zyxb_ctx* ctx, int32_t dev, int32_t dtype, uint32_t x, uint32_t y, uint64_t rows, uint64_t cols) {
+  DEV_OR_FAIL(ZYXB_ERR_KERNEL_LAUNCH);
+  Buffer* bx = get_buffer(D, x);
+  Buffer* by = get_buffer(D, y);
+  if (!bx || !by || bx->is_variable || by->is_variable) return fail(ctx, ZYXB_ERR_INCORRECT_KERNEL_ARG, "colsum_static: unknown buffer");
+  const uint64_t es = dtype_size(dtype);
+  if (rows != 0 && cols > UINT64_MAX / rows / 8) return fail(ctx, ZYXB_ERR_INCORRECT_KERNEL_ARG, "colsum_static: shape overflows");
+  if (bx->bytes < rows * cols * es || by->bytes < cols * es) return fail(ctx, ZYXB_ERR_INCORRECT_KERNEL_ARG, "colsum_static: buffer too small");
+  LaunchCtx lc = make_launch_ctx(ctx, D);
+  std::string err;
+  int st = launch_colsum_static(dtype, bx->ptr, by->ptr, rows, cols, lc, err);
+  if (st) return fail(ctx, st, err);
+  return ZYXB_OK;
+}
+
+int32_t zyxb_colsum_static_capacity(uint64_t* out_floats) {
+  if (out_floats) *out_floats = colsum_static_capacity();
+  return ZYXB_OK;
+}
+
 int32_t zyxb_launch_count(zyxb_ctx* ctx, int32_t dev, uint64_t* out_count) {
   DEV_OR_FAIL(ZYXB_ERR_DEVICE_QUERY);
   if (out_count) *out_count = D.launch_count;

@@ -83,6 +83,74 @@ static int launch_colsum(const void* x, void* y, uint64_t rows, uint64_t cols, c
   return check_launch(lc, err, "colsum", 2);
 }
 
+// ---- column sums without any allocation ------------------------------------------------------------
+// Same two-stage kernels as launch_colsum, but the f32 partials live in a fixed array that is part of the
+// loaded module, so the call path never reaches an allocator.  The array is shared by every call on the
+// device and keeps whatever the previous call left in it; stage 1 overwrites every partial that stage 2
+// reads, so nothing needs clearing, but two calls that overlap on the GPU (different streams or threads)
+// would write the same partials and race.
+constexpr uint64_t COLSUM_STATIC_FLOATS = 1ull << 20;      // 4 MiB of device memory per GPU, held until the process exits
+static __device__ __align__(256) float g_colsum_static[COLSUM_STATIC_FLOATS];
+constexpr int COLSUM_STATIC_MAX_DEVICES = 64;
+static float* g_colsum_static_ptr[COLSUM_STATIC_MAX_DEVICES];   // device address of the array, per CUDA device
+
+uint64_t colsum_static_capacity() { return COLSUM_STATIC_FLOATS; }
+
+// In host code the array's name is only a handle for the runtime, not a device address: the address is
+// looked up once per device (with that device current) and cached.
+static int colsum_static_address(int cuda_device, float** out, std::string& err) {
+  if (cuda_device < 0 || cuda_device >= COLSUM_STATIC_MAX_DEVICES) { err = "colsum_static: device index out of range"; return ZYXB_ERR_KERNEL_LAUNCH; }
+  if (!g_colsum_static_ptr[cuda_device]) {
+    float* ptr = nullptr;
+    cudaError_t e = cudaGetSymbolAddress((void**)&ptr, g_colsum_static);
+    if (e != cudaSuccess || !ptr) {
+      err = std::string("colsum_static: cudaGetSymbolAddress: ") + cudaGetErrorString(e);
+      return ZYXB_ERR_KERNEL_LAUNCH;
+    }
+    g_colsum_static_ptr[cuda_device] = ptr;
+  }
+  *out = g_colsum_static_ptr[cuda_device];
+  return ZYXB_OK;
+}
+
+template <typename T>
+static int launch_colsum_static_t(const void* x, void* y, uint64_t rows, uint64_t cols, float* partial, const LaunchCtx& lc,
+                                  std::string& err) {
+  using S = typename Elem<T>::store_t;
+  constexpr int V = 16 / sizeof(S);
+  const bool vec_ok = cols % V == 0 && (uintptr_t)x % 16 == 0;
+  const uint64_t per_cta = 128ull * (vec_ok ? V : 1);
+  const uint64_t col_blocks = (cols + per_cta - 1) / per_cta;
+  uint64_t splits = (4ull * lc.sm_count + col_blocks - 1) / col_blocks;
+  splits = std::max<uint64_t>(1, std::min<uint64_t>({splits, rows, 1024ull, COLSUM_STATIC_FLOATS / cols}));
+  const uint64_t rps = (rows + splits - 1) / splits;
+  splits = (rows + rps - 1) / rps;
+  dim3 grid((unsigned)col_blocks, (unsigned)splits);
+  if (vec_ok) colsum_partial_kernel<T, V><<<grid, 128, 0, lc.stream>>>((const S*)x, partial, rows, cols, rps);
+  else colsum_partial_kernel<T, 1><<<grid, 128, 0, lc.stream>>>((const S*)x, partial, rows, cols, rps);
+  colsum_final_kernel<T><<<(unsigned)((cols + 255) / 256), 256, 0, lc.stream>>>(partial, (S*)y, cols, (uint32_t)splits, lc.round_nearest);
+  return check_launch(lc, err, "colsum_static", 2);
+}
+
+int launch_colsum_static(int dtype, const void* x, void* y, uint64_t rows, uint64_t cols, const LaunchCtx& lc, std::string& err) {
+  if (rows == 0 || cols == 0) { err = "colsum_static: rows and cols must be positive"; return ZYXB_ERR_INCORRECT_KERNEL_ARG; }
+  if (cols > COLSUM_STATIC_FLOATS) {
+    err = "colsum_static: " + std::to_string(cols) + " columns exceed the fixed scratch of " + std::to_string(COLSUM_STATIC_FLOATS) +
+          " floats; use a ZYXB_RR_COLSUM program instead";
+    return ZYXB_ERR_INCORRECT_KERNEL_ARG;
+  }
+  if ((cols + 127) / 128 > 0x7fffffffull) { err = "colsum_static: too many columns"; return ZYXB_ERR_INCORRECT_KERNEL_ARG; }
+  float* partial = nullptr;
+  int st = colsum_static_address(lc.device, &partial, err);
+  if (st) return st;
+  switch (dtype) {
+    case ZYXB_F32: return launch_colsum_static_t<float>(x, y, rows, cols, partial, lc, err);
+    case ZYXB_BF16: return launch_colsum_static_t<bf16_t>(x, y, rows, cols, partial, lc, err);
+    case ZYXB_F16: return launch_colsum_static_t<f16_t>(x, y, rows, cols, partial, lc, err);
+    default: err = "colsum_static: dtype must be f32, bf16 or f16"; return ZYXB_ERR_INCORRECT_KERNEL_ARG;
+  }
+}
+
 // ---- MSE loss: mean((y - t)^2) over every element, f32 result ---------------------------------
 template <typename T, int VEC>
 __global__ void __launch_bounds__(256) mse_partial_kernel(const typename Elem<T>::store_t* y, const typename Elem<T>::store_t* t,
