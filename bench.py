@@ -5,6 +5,7 @@
 
 Prints ONE JSON line.  Workloads (synthetic, seeded, shapes of the reference's configurations):
   mlp         4 x Linear 4096<->16384, GELU, bf16, batch 8192 per GPU, MSE, AdamW; data parallel   (samples/s)  [default]
+  simplenet   README SimpleNet 784->128->10, f32, batch 64, CE, SGD; step replayed from a captured graph   (samples/s)
   rowreduce   row softmax + row layernorm on f32 [8192, 32768]         (fused-reduce GB/s)
   gemm_bf16   C = A.B, M=N=K=8192 bf16, f32 accumulate                  (GEMM TFLOP/s)
   gemm_f32    C = A.B, M=N=K=4096 f32                                   (GEMM TFLOP/s)
@@ -423,12 +424,101 @@ class MlpTrain:
             self.n_params, bs, self.batch, dt)
 
 
-WORKLOADS = {"mlp": MlpTrain, "rowreduce": RowReduce, "gemm_bf16": lambda: Gemm("bf16"), "gemm_f32": lambda: Gemm("f32")}
+class SimpleNet:
+    """Config 1: README SimpleNet 784 -> 128 (ReLU) -> 10, f32, batch 64, cross-entropy, SGD lr 0.01 (the MNIST shapes of the
+    reference's own benchmark; inputs N(0,1), labels uniform in [0,10)).  Launch-latency bound: the step is replayed from a
+    captured graph (FrozenTape::replay's analogue); the eager figure is reported beside it."""
+    dims, batch = [784, 128, 10], 64
+    unit, dtype, bound = "samples/s", "f32", "launch"
+
+    def __init__(self, size=0, rank=0, world=1):
+        if size:
+            self.batch = size
+        self.rank, self.world = rank, world
+        self.name = "simplenet_784_128_10_f32_batch%d_ce_sgd" % self.batch
+        self.metric = "SimpleNet train samples/s (784->128->10, f32, batch %d, CE, SGD)" % self.batch
+        self.units_per_step = float(self.batch)
+        self.h2d_bytes, self.d2h_bytes = self.batch * 784 * 4 + self.batch * 4, 4
+
+    def host_inputs(self):
+        rng = np.random.default_rng(200 + self.rank)
+        self.hx = rng.standard_normal((self.batch, 784), dtype=np.float32)
+        self.ht = rng.integers(0, 10, size=self.batch).astype(np.int32)
+
+    def setup(self, sess):
+        from zyx_b200 import _lib as L, host as H
+        self.sess, self.H = sess, H
+        self.host_inputs()
+        self.mlp = H.Mlp(sess, L.F32, self.batch, self.dims, activation=H.ACT_RELU, loss=H.LOSS_CROSS_ENTROPY, algo=L.OPT_SGD, lr=0.01)
+        rng = np.random.default_rng(0)
+        for i in range(self.mlp.n_params()):
+            bound = 1.0 / np.sqrt(self.dims[i // 2])
+            self.mlp.set_tensor(H.PARAM, i, rng.uniform(-bound, bound, self.mlp.shape(i)).astype(np.float32))
+        sess.pool.sync_events(self.mlp.set_batch(self.hx, self.ht))
+        d = sess.device
+        d.sync()
+        t0 = time.perf_counter()
+        for _ in range(200):
+            self.mlp.step()
+        d.sync()
+        self.eager_us = (time.perf_counter() - t0) / 200 * 1e6
+        d.capture_begin()
+        self.mlp.step()
+        self.graph = d.capture_end()
+        self.inner = 100       # replays per timed "step" so that a step is long enough for event timing
+        self.units_per_step = float(self.batch * self.inner)
+        self.config = {"workload": self.name, "l2": "working set (0.8 MB) is L2-resident by nature: the step is launch-latency bound",
+                       "replay": "captured graph, %d replays per timed step" % self.inner, "launches_per_train_step": self.mlp.plan_size()[0]}
+        self.losses = []
+
+    def step(self, timed=False):
+        for _ in range(self.inner):
+            self.sess.device.graph_launch(self.graph)
+
+    def roofline(self, peaks, clocks=None):
+        return ({"bound": "launch-latency", "kernel": "13 kernels per training step (39 MFLOP)", "achieved": None, "peak": None, "unit": "us/step",
+                 "frac": None, "traffic": None}, {"eager_us_per_train_step": self.eager_us})
+
+    def e2e_setup(self):
+        for a in (self.hx, self.ht):
+            self.sess.backend.host_register(a)
+
+    def e2e_step(self):
+        p = self.sess.pool
+        for _ in range(self.inner):
+            evs = self.mlp.set_batch(self.hx, self.ht)        # upload this step's batch, replay the step, read the loss
+            self.sess.device.graph_launch(self.graph, evs)
+            loss = self.mlp.read_loss()
+        self.losses.append(loss)
+
+    def check(self):
+        return None
+
+    def cpu_baseline(self, budget_s=12.0):
+        from oracle import models as om, oracle as zo
+        rng = np.random.default_rng(0)
+        layers = [(rng.uniform(-1, 1, (self.dims[i + 1], self.dims[i])).astype(np.float32) / np.float32(np.sqrt(self.dims[i])),
+                   rng.uniform(-1, 1, (self.dims[i + 1],)).astype(np.float32) / np.float32(np.sqrt(self.dims[i]))) for i in range(2)]
+        if not hasattr(self, "hx"):
+            self.host_inputs()
+        opt = om.Optim("sgd", zo.F32, om.flat(layers), lr=0.01)
+        n, t0 = 0, time.perf_counter()
+        while time.perf_counter() - t0 < min(budget_s, 5.0):
+            _, grads, _ = om.forward_backward(zo.F32, layers, self.hx, self.ht, om.ACT_RELU, om.LOSS_CE)
+            opt.update(om.flat(layers), om.flat(grads))
+            n += 1
+        dt = time.perf_counter() - t0
+        return n * self.batch / dt, "%d full training steps at batch %d, %.1f s" % (n, self.batch, dt)
+
+
+WORKLOADS = {"simplenet": SimpleNet, "mlp": MlpTrain, "rowreduce": RowReduce, "gemm_bf16": lambda: Gemm("bf16"), "gemm_f32": lambda: Gemm("f32")}
 
 
 def make_workload(args, rank=0, world=1):
     if args.workload == "mlp":
         return MlpTrain(size=args.size, standard=args.standard_adamw, rank=rank, world=world)
+    if args.workload == "simplenet":
+        return SimpleNet(size=args.size, rank=rank, world=world)
     if args.size:
         return {"rowreduce": lambda: RowReduce(rows=args.size), "gemm_bf16": lambda: Gemm("bf16", args.size),
                 "gemm_f32": lambda: Gemm("f32", args.size)}[args.workload]()

@@ -280,6 +280,18 @@ int32_t zyxb_launch_count(zyxb_ctx* ctx, int32_t dev, uint64_t* out_count);
  * reading it synchronises the device and clears it */
 int32_t zyxb_device_status(zyxb_ctx* ctx, int32_t dev, uint32_t* out_status);
 
+/* ---- captured launch sequences ---------------------------------------------------------------------------
+ * FrozenTape::replay (zyx/src/tape.rs:204-288) re-runs a realised plan without rebuilding it; here the launches
+ * issued between capture_begin and capture_end are recorded into a CUDA graph instead of being run, and
+ * zyxb_graph_launch replays them with one submission (what makes a 10-launch, 40-microsecond training step
+ * launch-latency free).  Inside a capture only zyxb_launch (without wait lists), zyxb_memset and the
+ * host-runtime steps built from them are allowed; buffers must stay allocated while the graph lives; the step
+ * counter of an optimizer program is frozen at its value at capture time (SGD does not use it). */
+int32_t zyxb_capture_begin(zyxb_ctx* ctx, int32_t dev);
+int32_t zyxb_capture_end(zyxb_ctx* ctx, int32_t dev, uint32_t* out_graph);
+int32_t zyxb_graph_launch(zyxb_ctx* ctx, int32_t dev, uint32_t graph, const zyxb_event* wait, int32_t n_wait, zyxb_event* out_event);
+int32_t zyxb_graph_release(zyxb_ctx* ctx, int32_t dev, uint32_t graph);
+
 /* ---- column sums for callers that cannot allocate -------------------------------------------------------
  * No counterpart in the reference.  y[cols] = sum over rows of x[rows, cols] (what a ZYXB_RR_COLSUM program
  * computes: the bias gradient of a Linear layer), for callers that must not reach an allocator while they

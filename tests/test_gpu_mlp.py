@@ -124,3 +124,37 @@ def test_config4_layer_shapes_one_step_gradients(sess):
             assert e_g <= TOL_BF16, ("grad", i, e_g)
     finally:
         mlp.close()
+
+
+def test_simplenet_step_replayed_from_a_captured_graph(sess):
+    """The same SimpleNet step recorded once (capture_begin / capture_end) and replayed, the way FrozenTape::replay re-runs a
+    realised plan: three replays on three batches give the oracle's parameters."""
+    dims, batch = [784, 128, 10], 64
+    rng = zo.Rng(42069)
+    layers = om.init_linears(rng, zo.F32, dims)
+    mlp = H.Mlp(sess, L.F32, batch, dims, activation=H.ACT_RELU, loss=H.LOSS_CROSS_ENTROPY, algo=L.OPT_SGD, lr=0.01)
+    graph = None
+    try:
+        load_params(mlp, layers)
+        opt = om.Optim("sgd", zo.F32, om.flat(layers), lr=0.01)
+        nprng = np.random.default_rng(9)
+        sess.device.sync()
+        sess.device.capture_begin()
+        mlp.step()
+        graph = sess.device.capture_end()
+        before = sess.device.launch_count()
+        for step in range(3):
+            x = rng.randn(batch * dims[0]).reshape(batch, dims[0])
+            labels = nprng.integers(0, 10, size=batch).astype(np.int32)
+            sess.pool.sync_events(mlp.set_batch(x, labels))
+            sess.device.graph_launch(graph)
+            want_loss, grads, _ = om.forward_backward(zo.F32, layers, x, labels, om.ACT_RELU, om.LOSS_CE)
+            opt.update(om.flat(layers), om.flat(grads))
+            assert abs(mlp.read_loss() - want_loss) <= TOL_F32 * abs(want_loss)
+            for i, p in enumerate(om.flat(layers)):
+                assert max_rel_err(mlp.get_tensor(H.PARAM, i), p, floor=0.1) <= TOL_F32, ("param", step, i)
+        assert sess.device.launch_count() - before == 3 * 13      # 10 programs, three of them two kernels each
+    finally:
+        if graph:
+            sess.device.graph_release(graph)
+        mlp.close()

@@ -240,6 +240,24 @@ class Device:
     def flush_l2(self):
         self.be._check(self.be.lib.zyxb_flush_l2(self.be.ctx, self.dev))
 
+    # ---- captured launch sequences (FrozenTape::replay) ---------------------------------------------
+    def capture_begin(self):
+        self.be._check(self.be.lib.zyxb_capture_begin(self.be.ctx, self.dev))
+
+    def capture_end(self):
+        g = C.c_uint32()
+        self.be._check(self.be.lib.zyxb_capture_end(self.be.ctx, self.dev, C.byref(g)))
+        return g.value
+
+    def graph_launch(self, graph, event_wait_list=None, want_event=False):
+        arr, n = _evs(event_wait_list)
+        ev = L.Event()
+        self.be._check(self.be.lib.zyxb_graph_launch(self.be.ctx, self.dev, graph, arr, n, C.byref(ev) if want_event else None))
+        return ev
+
+    def graph_release(self, graph):
+        self.be._check(self.be.lib.zyxb_graph_release(self.be.ctx, self.dev, graph))
+
     # ---- data-parallel exchange -------------------------------------------------------------
     def comm_unique_id(self):
         raw = (C.c_uint8 * 128)()

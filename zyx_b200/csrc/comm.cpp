@@ -74,8 +74,6 @@ int comm_create(Comm** out, int rank, int world, const void* id_bytes, std::stri
   if (world < 1 || rank < 0 || rank >= world) { err = "comm_init: bad rank/world"; return ZYXB_ERR_INITIALIZATION; }
   ncclUniqueId id;
   memcpy(&id, id_bytes, sizeof(id));
-  // The collectives run beside matmuls that want every SM: keep NCCL's footprint small unless the user chose one.
-  setenv("NCCL_MAX_CTAS", "16", 0);
   Comm* c = new Comm();
   c->rank = rank; c->world = world;
   int r = a.CommInitRank(&c->comm, world, id, rank);

@@ -63,6 +63,10 @@ struct Device {
   uint64_t launch_count = 0;
   void* tma_encode = nullptr;
   Comm* comm = nullptr;
+  // captured launch sequences (the analogue of a FrozenTape): executable graph + kernels per replay
+  std::vector<std::pair<cudaGraphExec_t, uint64_t>> graphs;
+  bool capturing = false;
+  uint64_t capture_launch_base = 0;
 };
 
 std::string g_init_error;
@@ -237,6 +241,7 @@ int32_t zyxb_shutdown(zyxb_ctx* ctx) {
     cudaSetDevice(D.cuda_id);
     cudaDeviceSynchronize();
     if (D.comm) { comm_destroy(D.comm); D.comm = nullptr; }
+    for (auto& g : D.graphs) if (g.first) cudaGraphExecDestroy(g.first);
     for (auto& kv : D.events) cudaEventDestroy(kv.second);
     for (auto& b : D.buffers) if (b.live && b.ptr && !b.is_view && !b.is_variable) cudaFree(b.ptr);
     for (auto& kv : D.cache) cudaFree(kv.second);
@@ -592,6 +597,55 @@ int32_t zyxb_colsum_static(zyxb_ctx* ctx, int32_t dev, int32_t dtype, uint32_t x
 
 int32_t zyxb_colsum_static_capacity(uint64_t* out_floats) {
   if (out_floats) *out_floats = colsum_static_capacity();
+  return ZYXB_OK;
+}
+
+// ---- captured launch sequences ---------------------------------------------------------------------
+int32_t zyxb_capture_begin(zyxb_ctx* ctx, int32_t dev) {
+  DEV_OR_FAIL(ZYXB_ERR_KERNEL_LAUNCH);
+  if (D.capturing) return fail(ctx, ZYXB_ERR_KERNEL_LAUNCH, "capture_begin: a capture is already open");
+  cudaError_t e = cudaStreamBeginCapture(D.compute, cudaStreamCaptureModeThreadLocal);
+  if (e != cudaSuccess) return cuda_fail(ctx, ZYXB_ERR_KERNEL_LAUNCH, "cudaStreamBeginCapture", e);
+  D.capturing = true;
+  D.capture_launch_base = D.launch_count;
+  return ZYXB_OK;
+}
+
+int32_t zyxb_capture_end(zyxb_ctx* ctx, int32_t dev, uint32_t* out_graph) {
+  DEV_OR_FAIL(ZYXB_ERR_KERNEL_LAUNCH);
+  if (!D.capturing || !out_graph) return fail(ctx, ZYXB_ERR_KERNEL_LAUNCH, "capture_end: no capture is open");
+  D.capturing = false;
+  cudaGraph_t graph = nullptr;
+  cudaError_t e = cudaStreamEndCapture(D.compute, &graph);
+  if (e != cudaSuccess || !graph) { cudaGetLastError(); return cuda_fail(ctx, ZYXB_ERR_KERNEL_LAUNCH, "cudaStreamEndCapture", e); }
+  cudaGraphExec_t exec = nullptr;
+  e = cudaGraphInstantiate(&exec, graph, 0);
+  cudaGraphDestroy(graph);
+  if (e != cudaSuccess) return cuda_fail(ctx, ZYXB_ERR_KERNEL_COMPILATION, "cudaGraphInstantiate", e);
+  const uint64_t kernels = D.launch_count - D.capture_launch_base;
+  D.launch_count = D.capture_launch_base;      // captured launches have not run yet; replays are counted
+  D.graphs.emplace_back(exec, kernels);
+  *out_graph = (uint32_t)D.graphs.size();      // ids start at 1
+  return ZYXB_OK;
+}
+
+int32_t zyxb_graph_launch(zyxb_ctx* ctx, int32_t dev, uint32_t graph, const zyxb_event* wait, int32_t n_wait, zyxb_event* out_event) {
+  DEV_OR_FAIL(ZYXB_ERR_KERNEL_LAUNCH);
+  if (graph == 0 || graph > D.graphs.size() || !D.graphs[graph - 1].first) return fail(ctx, ZYXB_ERR_KERNEL_LAUNCH, "graph_launch: unknown graph");
+  int st = wait_and_consume(ctx, D, D.compute, wait, n_wait, ZYXB_ERR_KERNEL_LAUNCH);
+  if (st) return st;
+  cudaError_t e = cudaGraphLaunch(D.graphs[graph - 1].first, D.compute);
+  if (e != cudaSuccess) return cuda_fail(ctx, ZYXB_ERR_KERNEL_LAUNCH, "cudaGraphLaunch", e);
+  D.launch_count += D.graphs[graph - 1].second;
+  return record_event(ctx, D, D.compute, out_event, ZYXB_ERR_KERNEL_LAUNCH);
+}
+
+int32_t zyxb_graph_release(zyxb_ctx* ctx, int32_t dev, uint32_t graph) {
+  DEV_OR_FAIL(ZYXB_ERR_KERNEL_LAUNCH);
+  if (graph == 0 || graph > D.graphs.size() || !D.graphs[graph - 1].first) return fail(ctx, ZYXB_ERR_KERNEL_LAUNCH, "graph_release: unknown graph");
+  cudaStreamSynchronize(D.compute);
+  cudaGraphExecDestroy(D.graphs[graph - 1].first);
+  D.graphs[graph - 1].first = nullptr;
   return ZYXB_OK;
 }
 
