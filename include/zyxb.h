@@ -138,7 +138,9 @@ typedef struct {
 enum { ZYXB_EPI_NONE = 0, ZYXB_EPI_BIAS = 1, ZYXB_EPI_BIAS_RELU = 2, ZYXB_EPI_BIAS_GELU = 3,
        /* backward through an activation fused into the input-gradient matmul: C = (alpha * A.B) * act'(z),
         * z [m,n] being the activation's stored input (GELU) or output (ReLU: relu'(z) = z > 0 either way) */
-       ZYXB_EPI_MUL_RELU_GRAD = 4, ZYXB_EPI_MUL_GELU_GRAD = 5 };
+       ZYXB_EPI_MUL_RELU_GRAD = 4, ZYXB_EPI_MUL_GELU_GRAD = 5,
+       /* C = alpha * A.B + z, z shaped and strided like C (a residual / gradient accumulation) */
+       ZYXB_EPI_ADD = 6 };
 
 typedef struct {
   int32_t  dtype;        /* element type of A, B, C: bf16 / f16 / f32 / i32; accumulation is
@@ -151,6 +153,12 @@ typedef struct {
   int32_t  epilogue;     /* ZYXB_EPI_*; bias is [n] */
   int32_t  store_preact; /* 1: second output receives alpha*A.B+bias before the activation */
   float    alpha;        /* 0 means 1 */
+  /* Strided views, so that the [B, T, H, D] <-> [B, H, T, D] reshapes and transposes of attention
+   * (zyx-nn/src/multi_head_attention.rs:160-226) need no copy: */
+  uint64_t lda, ldb, ldc;   /* row pitch of the stored A / B / C in elements; 0 = packed (the contiguous extent) */
+  uint64_t batch_inner;     /* 0 or 1: none.  Otherwise the launch runs batch * batch_inner matrices; matrix
+                               z uses offset (z / batch_inner) * stride_x + (z % batch_inner) * stride_x_inner */
+  int64_t  stride_a_inner, stride_b_inner, stride_c_inner;
 } zyxb_gemm_desc;
 /* args: a, b [,bias | ,z] -> c [,preact] */
 

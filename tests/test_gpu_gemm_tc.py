@@ -103,3 +103,48 @@ def test_tc_activation_gradient_epilogue(sess, dtype, epi):
     got = sess.gemm(dtype, dz, w, bias=z, epi=epi)
     want = zo.gemm(dtype, dz, w, bias=z, epi=epi)
     assert err(got, want, dtype) <= TOL_BF16
+
+
+@pytest.mark.parametrize("dtype,T,D", [(L.BF16, 256, 64), (L.BF16, 200, 128), (L.F32, 48, 16)])
+def test_attention_shaped_strided_batches(sess, dtype, T, D):
+    """q, k, v live as [B, T, H*D] (what the q/k/v projections write); the per-head matmuls read them in place through
+    row pitches and a two-level batch (B, H), and the P.V product writes straight back into [B, T, H*D]:
+    the reshapes and transposes of MultiheadAttention::forward (zyx-nn/src/multi_head_attention.rs:160-226) without a copy."""
+    from zyx_b200 import backend as Bk
+    Bsz, H = 2, 4
+    E = H * D
+    mk = (lambda shape: rand(shape, dtype)) if dtype != L.F32 else (lambda shape: RNG.uniform(-1, 1, size=shape).astype(np.float32))
+    tof = (lambda x: f(x, dtype)) if dtype != L.F32 else (lambda x: x)
+    tol = TOL_BF16 if dtype != L.F32 else 1e-5
+    q, k, v = mk((Bsz, T, E)), mk((Bsz, T, E)), mk((Bsz, T, E))
+    heads = lambda x: np.ascontiguousarray(x.reshape(Bsz, T, H, D).transpose(0, 2, 1, 3)).reshape(Bsz * H, T, D)
+    scale = 1.0 / np.sqrt(D)
+    # scores[b, h] = q[b, :, h, :] . k[b, :, h, :]^T * scale  -> [B*H, T, T] packed
+    d = Bk.gemm_desc(dtype, T, T, D, batch=Bsz, trans_b=True, stride_a=T * E, stride_b=T * E, stride_c=H * T * T, alpha=scale,
+                     lda=E, ldb=E, batch_inner=H, stride_a_inner=D, stride_b_inner=D, stride_c_inner=T * T)
+    s_got = sess.run(d, [q, k], [((Bsz * H, T, T), q.dtype)])[0]
+    s_want = zo.gemm(dtype, heads(q), heads(k), tb=True, alpha=scale)
+    assert max_rel_err(tof(s_got), tof(s_want), floor=0.1) <= tol
+    # out[b, :, h, :] = p[b, h] . v[b, :, h, :]   -> written into [B, T, H*D]
+    p = zo.softmax(dtype, s_want.reshape(-1, T)).reshape(Bsz * H, T, T)
+    d = Bk.gemm_desc(dtype, T, D, T, batch=Bsz, stride_a=H * T * T, stride_b=T * E, stride_c=T * E, ldb=E, ldc=E, batch_inner=H,
+                     stride_a_inner=T * T, stride_b_inner=D, stride_c_inner=D)
+    o_got = sess.run(d, [p, v], [((Bsz, T, E), q.dtype)])[0]
+    o_want = zo.gemm(dtype, p, heads(v)).reshape(Bsz, H, T, D).transpose(0, 2, 1, 3).reshape(Bsz, T, E)
+    assert max_rel_err(tof(o_got), tof(o_want), floor=0.1) <= tol
+    # dV[b, :, h, :] = p[b, h]^T . dO[b, :, h, :]: transposed A, strided B and C
+    do = mk((Bsz, T, E))
+    d = Bk.gemm_desc(dtype, T, D, T, batch=Bsz, trans_a=True, stride_a=H * T * T, stride_b=T * E, stride_c=T * E, ldb=E, ldc=E,
+                     batch_inner=H, stride_a_inner=T * T, stride_b_inner=D, stride_c_inner=D)
+    dv_got = sess.run(d, [p, do], [((Bsz, T, E), q.dtype)])[0]
+    dv_want = zo.gemm(dtype, p, heads(do), ta=True).reshape(Bsz, H, T, D).transpose(0, 2, 1, 3).reshape(Bsz, T, E)
+    assert max_rel_err(tof(dv_got), tof(dv_want), floor=0.1) <= tol
+    assert sess.device.status() == 0
+
+
+def test_residual_add_epilogue(sess):
+    m, n, k = 256, 264, 128
+    a, w, r = rand((m, k), L.BF16), rand((n, k), L.BF16), rand((m, n), L.BF16)
+    got = sess.gemm(L.BF16, a, w, tb=True, bias=r, epi=L.EPI_ADD)
+    acc = f(a, L.BF16).astype(np.float64) @ f(w, L.BF16).astype(np.float64).T + f(r, L.BF16)
+    assert max_rel_err(f(got, L.BF16), acc, floor=0.1) <= TOL_BF16

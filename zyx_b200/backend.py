@@ -291,7 +291,8 @@ def rowreduce_desc(op, dtype, rows, cols, eps=0.0, correction=1, has_weight=Fals
 
 
 def gemm_desc(dtype, m, n, k, batch=1, trans_a=False, trans_b=False, stride_a=None, stride_b=None, stride_c=None,
-              epilogue=L.EPI_NONE, store_preact=False, alpha=0.0):
+              epilogue=L.EPI_NONE, store_preact=False, alpha=0.0, lda=0, ldb=0, ldc=0, batch_inner=0, stride_a_inner=0,
+              stride_b_inner=0, stride_c_inner=0):
     d = L.KernelDesc()
     d.kind = L.KIND_GEMM
     g = d.u.gemm
@@ -301,6 +302,8 @@ def gemm_desc(dtype, m, n, k, batch=1, trans_a=False, trans_b=False, stride_a=No
     g.stride_b = k * n if stride_b is None else stride_b
     g.stride_c = m * n if stride_c is None else stride_c
     g.epilogue, g.store_preact, g.alpha = epilogue, int(store_preact), alpha
+    g.lda, g.ldb, g.ldc, g.batch_inner = lda, ldb, ldc, batch_inner
+    g.stride_a_inner, g.stride_b_inner, g.stride_c_inner = stride_a_inner, stride_b_inner, stride_c_inner
     return d
 
 

@@ -11,7 +11,10 @@ struct GemmParams {
   const void* z;   // MUL_*_GRAD epilogues: [m, n] (per batch, C's stride)
   void* c; void* preact;
   uint64_t m, n, k, batch;
-  int64_t stride_a, stride_b, stride_c;   // elements between consecutive batches
+  int64_t stride_a, stride_b, stride_c;   // elements between consecutive (outer) batches
+  uint64_t lda, ldb, ldc;                 // row pitch of the stored operands, elements
+  uint64_t batch_inner;                   // >= 1; matrix z: (z / batch_inner) * stride + (z % batch_inner) * stride_inner
+  int64_t stride_a_inner, stride_b_inner, stride_c_inner;
   int trans_a, trans_b;                   // A stored [k,m] / B stored [n,k]
   int epilogue;
   float alpha;

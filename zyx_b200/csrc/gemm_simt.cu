@@ -47,9 +47,11 @@ __global__ void __launch_bounds__(STHREADS) gemm_simt_kernel(GemmParams p) {
   const int tid = threadIdx.x;
   const int64_t m = p.m, n = p.n, k = p.k;
   const int64_t m0 = (int64_t)blockIdx.y * SBM, n0 = (int64_t)blockIdx.x * SBN;
-  const S* A = reinterpret_cast<const S*>(p.a) + (int64_t)blockIdx.z * p.stride_a;
-  const S* B = reinterpret_cast<const S*>(p.b) + (int64_t)blockIdx.z * p.stride_b;
-  const int64_t lda = TA ? m : k, ldb = TB ? k : n;
+  const int64_t zo = blockIdx.z / p.batch_inner, zi = blockIdx.z % p.batch_inner;
+  const S* A = reinterpret_cast<const S*>(p.a) + zo * p.stride_a + zi * p.stride_a_inner;
+  const S* B = reinterpret_cast<const S*>(p.b) + zo * p.stride_b + zi * p.stride_b_inner;
+  const int64_t lda = (int64_t)p.lda, ldb = (int64_t)p.ldb, ldc = (int64_t)p.ldc;
+  const int64_t c_off = zo * p.stride_c + zi * p.stride_c_inner;
   const bool va = p.vec_a, vb = p.vec_b;
 
   // per-thread fetch coordinates: two 4-element groups of A and of B per k-tile
@@ -138,10 +140,10 @@ __global__ void __launch_bounds__(STHREADS) gemm_simt_kernel(GemmParams p) {
   }
 
   // epilogue: alpha, bias, activation; optional second output with the pre-activation
-  S* C = reinterpret_cast<S*>(p.c) + (int64_t)blockIdx.z * p.stride_c;
-  S* Z = p.preact ? reinterpret_cast<S*>(p.preact) + (int64_t)blockIdx.z * p.stride_c : nullptr;
+  S* C = reinterpret_cast<S*>(p.c) + c_off;
+  S* Z = p.preact ? reinterpret_cast<S*>(p.preact) + c_off : nullptr;
   const S* bias = reinterpret_cast<const S*>(p.bias);
-  const S* zin = p.z ? reinterpret_cast<const S*>(p.z) + (int64_t)blockIdx.z * p.stride_c : nullptr;
+  const S* zin = p.z ? reinterpret_cast<const S*>(p.z) + c_off : nullptr;
   const bool rn = p.rn != 0;
   if constexpr (std::is_same_v<ACC, float>) {
     const GeluConsts gc = gelu_consts<T>();
@@ -157,12 +159,13 @@ __global__ void __launch_bounds__(STHREADS) gemm_simt_kernel(GemmParams p) {
         float v = acc[i][j];
         if (p.alpha != 1.0f) v *= calpha;
         if (p.epilogue >= ZYXB_EPI_BIAS && p.epilogue <= ZYXB_EPI_BIAS_GELU) v += (float)Elem<T>::load(bias[c]);
-        if (Z) Z[r * n + c] = Elem<T>::store(v, rn);
+        if (Z) Z[r * ldc + c] = Elem<T>::store(v, rn);
         if (p.epilogue == ZYXB_EPI_BIAS_RELU) v = relu_ref(v);
         else if (p.epilogue == ZYXB_EPI_BIAS_GELU) v = gelu_ref<T>(v, gc);
-        else if (p.epilogue == ZYXB_EPI_MUL_RELU_GRAD) v *= ((float)Elem<T>::load(zin[r * n + c]) > 0.0f ? 1.0f : 0.0f);
-        else if (p.epilogue == ZYXB_EPI_MUL_GELU_GRAD) v *= gelu_grad_ref<T>((float)Elem<T>::load(zin[r * n + c]), gc);
-        C[r * n + c] = Elem<T>::store(v, rn);
+        else if (p.epilogue == ZYXB_EPI_MUL_RELU_GRAD) v *= ((float)Elem<T>::load(zin[r * ldc + c]) > 0.0f ? 1.0f : 0.0f);
+        else if (p.epilogue == ZYXB_EPI_MUL_GELU_GRAD) v *= gelu_grad_ref<T>((float)Elem<T>::load(zin[r * ldc + c]), gc);
+        else if (p.epilogue == ZYXB_EPI_ADD) v += (float)Elem<T>::load(zin[r * ldc + c]);
+        C[r * ldc + c] = Elem<T>::store(v, rn);
       }
     }
   } else {
@@ -173,7 +176,7 @@ __global__ void __launch_bounds__(STHREADS) gemm_simt_kernel(GemmParams p) {
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         const int64_t c = n0 + (j / 4) * 64 + tx * 4 + (j % 4);
-        if (c < n) C[r * n + c] = acc[i][j];
+        if (c < n) C[r * ldc + c] = acc[i][j];
       }
     }
   }
@@ -192,14 +195,15 @@ static void launch_simt_t(const GemmParams& p, dim3 grid, cudaStream_t s) {
 
 int launch_gemm_simt(GemmParams p, int dtype, const LaunchCtx& lc, std::string& err) {
   const uint64_t gx = (p.n + SBN - 1) / SBN, gy = (p.m + SBM - 1) / SBM;
-  ZYXB_CHECK_ARG(gy <= 65535 && p.batch <= 65535, "gemm: m or batch too large for the SIMT path");
-  dim3 grid((unsigned)gx, (unsigned)gy, (unsigned)p.batch);
+  ZYXB_CHECK_ARG(gy <= 65535 && p.batch * p.batch_inner <= 65535, "gemm: m or batch too large for the SIMT path");
+  dim3 grid((unsigned)gx, (unsigned)gy, (unsigned)(p.batch * p.batch_inner));
   // one aligned access per 4 elements needs the contiguous extent, the batch stride and the base aligned
   const uint64_t es = dtype_size(dtype);
-  const uint64_t lda = p.trans_a ? p.m : p.k, ldb = p.trans_b ? p.k : p.n;
-  const uint64_t align_elems = dtype == ZYXB_F32 || dtype == ZYXB_I32 ? 4 : 4;   // 16 B for 4-byte, 8 B for 2-byte types
-  p.vec_a = (lda % align_elems == 0) && ((uintptr_t)p.a % (4 * es) == 0) && ((uint64_t)p.stride_a % align_elems == 0);
-  p.vec_b = (ldb % align_elems == 0) && ((uintptr_t)p.b % (4 * es) == 0) && ((uint64_t)p.stride_b % align_elems == 0);
+  const uint64_t align_elems = 4;   // one access of 4 elements: 16 B for 4-byte, 8 B for 2-byte types
+  p.vec_a = (p.lda % align_elems == 0) && ((uintptr_t)p.a % (4 * es) == 0) && ((uint64_t)p.stride_a % align_elems == 0) &&
+            ((uint64_t)p.stride_a_inner % align_elems == 0);
+  p.vec_b = (p.ldb % align_elems == 0) && ((uintptr_t)p.b % (4 * es) == 0) && ((uint64_t)p.stride_b % align_elems == 0) &&
+            ((uint64_t)p.stride_b_inner % align_elems == 0);
   switch (dtype) {
     case ZYXB_F32: launch_simt_t<float, float>(p, grid, lc.stream); break;
     case ZYXB_BF16: launch_simt_t<bf16_t, float>(p, grid, lc.stream); break;

@@ -42,12 +42,14 @@ struct TcParams {
   const void* bias; const void* z; void* c; void* preact;
   uint32_t m, n, k, batch;
   uint32_t tiles_m, tiles_n;
-  int64_t stride_c;       // elements between batches of C
+  int64_t stride_c, stride_c_inner;   // elements between outer / inner batches of C
+  uint32_t ldc;           // row pitch of C (and of z / preact), elements
+  uint32_t batch_inner;   // matrix z = (z / batch_inner, z % batch_inner)
   float alpha;
   int epilogue;
   int rn;
   int is_bf16;
-  int a_batched, b_batched;   // 0: one matrix shared by every batch (its map has batch extent 1)
+  int a_batched, b_batched;   // bit 0: the operand has an outer batch stride, bit 1: an inner one (else that map extent is 1)
   uint32_t* status;
   uint32_t* tile_counter;     // zeroed before the launch; CTAs draw tile indices from it
   int dynamic_tiles;          // 1: draw tiles from the counter; 0: CTA i takes tiles i, i + grid, ...
@@ -96,10 +98,11 @@ __device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarr
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
-__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y, int z) {
+// rank-4 map {contiguous, rows, inner batch, outer batch}
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y, int zi, int zo) {
   asm volatile(
-      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-      ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "r"(z) : "memory");
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "r"(zi), "r"(zo) : "memory");
 }
 __device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
@@ -244,7 +247,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
         if (t == TILE_NONE) break;
         uint32_t bz, tm, tn;
         tile_coords(t, bz, tm, tn);
-        const int za = p.a_batched ? (int)bz : 0, zb = p.b_batched ? (int)bz : 0;
+        const int zo = (int)(bz / p.batch_inner), zi = (int)(bz % p.batch_inner);
+        const int zao = p.a_batched & 1 ? zo : 0, zai = p.a_batched & 2 ? zi : 0;
+        const int zbo = p.b_batched & 1 ? zo : 0, zbi = p.b_batched & 2 ? zi : 0;
         for (uint32_t kb = 0; kb < k_blocks; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1, abort_flag, p.status, TC_ERR_PRODUCER)) { ok = false; break; }
           const uint32_t a_dst = base + stage * SM::STAGE_BYTES, b_dst = a_dst + SM::A_BYTES;
@@ -253,16 +258,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
           if constexpr (A_MN) {   // A stored [k, m]: boxes of 64 m x 64 k
 #pragma unroll
             for (int j = 0; j < TC_BM / 64; ++j)
-              tma_load_3d(a_dst + j * (64 * TC_BK * 2), &tma_a, full_bar(stage), (int)(tm * TC_BM) + j * 64, k0, za);
+              tma_load_4d(a_dst + j * (64 * TC_BK * 2), &tma_a, full_bar(stage), (int)(tm * TC_BM) + j * 64, k0, zai, zao);
           } else {                // A stored [m, k]: one box of 64 k x 128 m
-            tma_load_3d(a_dst, &tma_a, full_bar(stage), k0, (int)(tm * TC_BM), za);
+            tma_load_4d(a_dst, &tma_a, full_bar(stage), k0, (int)(tm * TC_BM), zai, zao);
           }
           if constexpr (B_MN) {   // B stored [k, n]: boxes of 64 n x 64 k
 #pragma unroll
             for (int j = 0; j < BN / 64; ++j)
-              tma_load_3d(b_dst + j * (64 * TC_BK * 2), &tma_b, full_bar(stage), (int)(tn * BN) + j * 64, k0, zb);
+              tma_load_4d(b_dst + j * (64 * TC_BK * 2), &tma_b, full_bar(stage), (int)(tn * BN) + j * 64, k0, zbi, zbo);
           } else {                // B stored [n, k]: one box of 64 k x BN n
-            tma_load_3d(b_dst, &tma_b, full_bar(stage), k0, (int)(tn * BN), zb);
+            tma_load_4d(b_dst, &tma_b, full_bar(stage), k0, (int)(tn * BN), zbi, zbo);
           }
           ++issued;
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -334,8 +339,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
       tc_fence_after();
       const uint32_t row = tm * TC_BM + row_in_tile;
       const uint32_t col0 = tn * BN;
-      uint16_t* crow = reinterpret_cast<uint16_t*>(p.c) + (int64_t)bz * p.stride_c + (int64_t)row * p.n;
-      uint16_t* zrow = p.preact ? reinterpret_cast<uint16_t*>(p.preact) + (int64_t)bz * p.stride_c + (int64_t)row * p.n : nullptr;
+      const int64_t c_off = (int64_t)(bz / p.batch_inner) * p.stride_c + (int64_t)(bz % p.batch_inner) * p.stride_c_inner + (int64_t)row * p.ldc;
+      uint16_t* crow = reinterpret_cast<uint16_t*>(p.c) + c_off;
+      uint16_t* zrow = p.preact ? reinterpret_cast<uint16_t*>(p.preact) + c_off : nullptr;
 #pragma unroll 1
       for (int ch = col_half * (BN / 64); ch < (col_half + 1) * (BN / 64); ++ch) {
         uint32_t r[32];
@@ -372,9 +378,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
               }
             }
           }
-          if (p.epilogue == ZYXB_EPI_MUL_RELU_GRAD || p.epilogue == ZYXB_EPI_MUL_GELU_GRAD) {
+          if (p.epilogue == ZYXB_EPI_ADD) {
+            const uint16_t* zr = reinterpret_cast<const uint16_t*>(p.z) + c_off;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              if (full || c + q * 8 < p.n) {
+                const Pack<uint16_t, 8> pk = load_pack_stream<uint16_t, 8>(zr + c + q * 8);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[q * 8 + j] += ld16(pk.v[j]);
+              }
+            }
+          } else if (p.epilogue == ZYXB_EPI_MUL_RELU_GRAD || p.epilogue == ZYXB_EPI_MUL_GELU_GRAD) {
             // backward through the activation: multiply the input gradient by act'(z), z read once from HBM
-            const uint16_t* zr = reinterpret_cast<const uint16_t*>(p.z) + (int64_t)bz * p.stride_c + (int64_t)row * p.n;
+            const uint16_t* zr = reinterpret_cast<const uint16_t*>(p.z) + c_off;
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
               if (full || c + q * 8 < p.n) {
@@ -438,16 +454,18 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
-// A rank-3 map {inner, outer, batch} over a row-major matrix with `inner` contiguous; box {64, box_outer, 1}.
-static bool encode_map(void* fn, CUtensorMap* map, bool bf16, const void* ptr, uint64_t inner, uint64_t outer, uint64_t batch,
-                       uint64_t batch_stride_elems, uint32_t box_outer) {
-  // a shared operand (batch stride 0) is described as one matrix; every batch reads z = 0
-  if (batch_stride_elems == 0) batch = 1;
-  cuuint64_t dims[3] = {inner, outer, batch};
-  cuuint64_t strides[2] = {inner * 2, (batch_stride_elems ? batch_stride_elems : inner * outer) * 2};
-  cuuint32_t box[3] = {64, box_outer, 1};
-  cuuint32_t estr[3] = {1, 1, 1};
-  CUresult r = reinterpret_cast<EncodeTiledFn>(fn)(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
+// A rank-4 map {inner, outer, inner batch, outer batch} over a row-major matrix with `inner` contiguous and row pitch
+// `ld`; box {64, box_outer, 1, 1}.  A batch level the operand does not have (stride 0: shared) gets extent 1.
+static bool encode_map(void* fn, CUtensorMap* map, bool bf16, const void* ptr, uint64_t inner, uint64_t outer, uint64_t ld,
+                       uint64_t batch_inner, uint64_t stride_inner, uint64_t batch, uint64_t stride, uint32_t box_outer) {
+  if (stride_inner == 0) batch_inner = 1;
+  if (stride == 0) batch = 1;
+  const uint64_t one = ld * outer;
+  cuuint64_t dims[4] = {inner, outer, batch_inner, batch};
+  cuuint64_t strides[3] = {ld * 2, (stride_inner ? stride_inner : one) * 2, (stride ? stride : one * batch_inner) * 2};
+  cuuint32_t box[4] = {64, box_outer, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = reinterpret_cast<EncodeTiledFn>(fn)(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
                                                    const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                                                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                                                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -460,13 +478,15 @@ bool gemm_tc_supported(const GemmParams& p, int dtype, const LaunchCtx& lc) {
   // TMA: 16-byte aligned bases and row pitches; the epilogue stores 8 elements at a time
   const uint64_t a_inner = p.trans_a ? p.m : p.k, b_inner = p.trans_b ? p.k : p.n;
   if (a_inner % 8 || b_inner % 8 || p.n % 8) return false;
+  if (p.lda % 8 || p.ldb % 8 || p.ldc % 8) return false;
+  if (p.stride_a_inner % 8 || p.stride_b_inner % 8 || p.stride_c_inner % 8) return false;
+  if (p.ldc > 0xffffffffull) return false;
   if ((uintptr_t)p.a % 16 || (uintptr_t)p.b % 16 || (uintptr_t)p.c % 16) return false;
   if (p.preact && (uintptr_t)p.preact % 16) return false;
   if (p.bias && (uintptr_t)p.bias % 16) return false;
   if (p.z && (uintptr_t)p.z % 16) return false;
-  if (p.batch > 1 && ((p.stride_a % 8) || (p.stride_b % 8) || (p.stride_c % 8))) return false;
-  if (p.m > 0x7fffff00ull || p.n > 0x7fffff00ull || p.k > 0x7fffff00ull || p.batch > 65535) return false;
-  if (p.batch > 1 && p.stride_a == 0 && p.stride_b == 0) return false;
+  if ((p.stride_a % 8) || (p.stride_b % 8) || (p.stride_c % 8)) return false;
+  if (p.m > 0x7fffff00ull || p.n > 0x7fffff00ull || p.k > 0x7fffff00ull || p.batch * p.batch_inner > 65535) return false;
   // tiny problems are latency-bound: the SIMT kernel has no descriptor set-up cost
   if (p.m * p.n * p.k < (1ull << 21) || p.m < 32) return false;
   return true;
@@ -499,14 +519,17 @@ int launch_gemm_tc(const GemmParams& p, int dtype, const LaunchCtx& lc, std::str
   const bool b_mn = p.trans_b == 0;      // B stored [k, n]: N is the contiguous axis
   const int bn = p.n <= 128 ? 128 : 256;
   CUtensorMap ma, mb;
-  const bool oka = a_mn ? encode_map(lc.tma_encode, &ma, bf16, p.a, p.m, p.k, p.batch, (uint64_t)p.stride_a, 64)
-                        : encode_map(lc.tma_encode, &ma, bf16, p.a, p.k, p.m, p.batch, (uint64_t)p.stride_a, TC_BM);
-  const bool okb = b_mn ? encode_map(lc.tma_encode, &mb, bf16, p.b, p.n, p.k, p.batch, (uint64_t)p.stride_b, 64)
-                        : encode_map(lc.tma_encode, &mb, bf16, p.b, p.k, p.n, p.batch, (uint64_t)p.stride_b, (uint32_t)bn);
+  const uint64_t sa = p.batch > 1 ? (uint64_t)p.stride_a : 0, sb = p.batch > 1 ? (uint64_t)p.stride_b : 0;
+  const uint64_t sai = p.batch_inner > 1 ? (uint64_t)p.stride_a_inner : 0, sbi = p.batch_inner > 1 ? (uint64_t)p.stride_b_inner : 0;
+  const bool oka = a_mn ? encode_map(lc.tma_encode, &ma, bf16, p.a, p.m, p.k, p.lda, p.batch_inner, sai, p.batch, sa, 64)
+                        : encode_map(lc.tma_encode, &ma, bf16, p.a, p.k, p.m, p.lda, p.batch_inner, sai, p.batch, sa, TC_BM);
+  const bool okb = b_mn ? encode_map(lc.tma_encode, &mb, bf16, p.b, p.n, p.k, p.ldb, p.batch_inner, sbi, p.batch, sb, 64)
+                        : encode_map(lc.tma_encode, &mb, bf16, p.b, p.k, p.n, p.ldb, p.batch_inner, sbi, p.batch, sb, (uint32_t)bn);
   if (!oka || !okb) { err = "gemm: cuTensorMapEncodeTiled rejected an operand"; return ZYXB_ERR_KERNEL_LAUNCH; }
   TcParams tp{};
   tp.bias = p.bias; tp.z = p.z; tp.c = p.c; tp.preact = p.preact;
-  tp.m = (uint32_t)p.m; tp.n = (uint32_t)p.n; tp.k = (uint32_t)p.k; tp.batch = (uint32_t)p.batch;
+  tp.m = (uint32_t)p.m; tp.n = (uint32_t)p.n; tp.k = (uint32_t)p.k; tp.batch = (uint32_t)(p.batch * p.batch_inner);
+  tp.batch_inner = (uint32_t)p.batch_inner; tp.ldc = (uint32_t)p.ldc; tp.stride_c_inner = p.stride_c_inner;
   tp.tiles_m = (uint32_t)((p.m + TC_BM - 1) / TC_BM); tp.tiles_n = (uint32_t)((p.n + bn - 1) / bn);
   tp.stride_c = p.stride_c; tp.alpha = p.alpha; tp.epilogue = p.epilogue; tp.rn = p.rn; tp.is_bf16 = bf16 ? 1 : 0;
   tp.status = lc.status_word;
@@ -520,8 +543,8 @@ int launch_gemm_tc(const GemmParams& p, int dtype, const LaunchCtx& lc, std::str
   if (tp.dynamic_tiles && cudaMemsetAsync(tp.tile_counter, 0, sizeof(uint32_t), lc.stream) != cudaSuccess) {
     err = "gemm: tile counter reset failed"; return ZYXB_ERR_KERNEL_LAUNCH;
   }
-  tp.a_batched = (p.batch > 1 && p.stride_a != 0) ? 1 : 0;
-  tp.b_batched = (p.batch > 1 && p.stride_b != 0) ? 1 : 0;
+  tp.a_batched = (sa ? 1 : 0) | (sai ? 2 : 0);
+  tp.b_batched = (sb ? 1 : 0) | (sbi ? 2 : 0);
   const uint64_t total = (uint64_t)tp.tiles_m * tp.tiles_n * tp.batch;
   ZYXB_CHECK_ARG(total < 0x7fffffffull, "gemm: too many tiles");
   const unsigned grid = (unsigned)std::min<uint64_t>(total, (uint64_t)lc.sm_count);
