@@ -116,7 +116,8 @@ enum {
   ZYXB_RR_SOFTMAX_BWD = 11,       /* args: p, dp -> ds = p*(dp - sum(dp*p)) */
   ZYXB_RR_LAYERNORM_BWD = 12,     /* args: x, dy [,weight] -> dx */
   ZYXB_RR_COLSUM = 13,            /* args: x[rows,cols] -> y[cols]  (sum over rows; bias gradient) */
-  ZYXB_RR_MSE = 14                /* args: y, t -> loss[1] = mean((y-t)^2) over rows*cols */
+  ZYXB_RR_MSE = 14,               /* args: y, t -> loss[1] = mean((y-t)^2) over rows*cols */
+  ZYXB_RR_LAYERNORM_DYXHAT = 15   /* args: x, dy -> dy * (x-mean)/sqrt(var+eps); its column sums are the layernorm weight gradient */
 };
 
 typedef struct {

@@ -71,6 +71,39 @@ int32_t zyxb_mlp_profile_read(zyxb_mlp* mlp, float* out_ms, int32_t* out_kind, i
 /* number of zyxb_launch / zyxb_allreduce_sum calls one step makes */
 int32_t zyxb_mlp_plan_size(zyxb_mlp* mlp, int32_t* out_launches, int32_t* out_collectives);
 
+/* ------------------------------------------------------------------------------------------------------------
+ * One transformer block, forward + backward + optimizer, as the reference's README example composes it
+ * (zyx-examples/examples/readme_test.rs:9-40): y = norm2(x1 + mlp2(gelu(mlp(x1)))), x1 = norm1(x + attn(x, x, x)),
+ * attn = zyx_nn::MultiheadAttention (zyx-nn/src/multi_head_attention.rs:134-245: q/k/v/out projections with bias,
+ * scores = q.k^T / sqrt(head_dim), optional causal mask, softmax, .v), LayerNorm with weight and bias and unbiased
+ * variance (zyx-nn/src/layer_norm.rs:95-135).  Loss: mean((y - target)^2).
+ * Parameters in Module::iter() order (16 tensors): attn.q_proj.{weight,bias}, k_proj, v_proj, out_proj,
+ * mlp.{weight,bias}, mlp2.{weight,bias}, norm1.{weight,bias}, norm2.{weight,bias}. */
+typedef struct {
+  int32_t  dtype;        /* ZYXB_BF16 / ZYXB_F16 / ZYXB_F32 */
+  uint64_t batch, seq;   /* this rank's input is [batch, seq, dim] */
+  uint64_t dim, heads, ffn;
+  int32_t  causal;       /* 1: key j is masked for query i when j > i */
+  float    eps;          /* LayerNorm epsilon (1e-5 in the example) */
+  zyxb_optim_desc optim; /* algo and hyper-parameters; dtype, n_tensors, numel are filled in */
+  int32_t  world;        /* > 1: gradients are all-reduced in three groups (ffn, attention output side, q/k/v) */
+} zyxb_block_config;
+
+typedef struct zyxb_block zyxb_block;
+int32_t zyxb_block_create(zyxb_ctx* ctx, int32_t dev, const zyxb_block_config* config, zyxb_block** out);
+int32_t zyxb_block_destroy(zyxb_block* blk);
+const char* zyxb_block_last_error(zyxb_block* blk);
+/* which: 0 parameter, 1 gradient, 2 / 3 optimizer state; i in Module::iter() order */
+int32_t zyxb_block_tensor(zyxb_block* blk, int32_t which, int32_t i, uint32_t* out_buf, uint64_t* out_numel);
+int32_t zyxb_block_io(zyxb_block* blk, uint32_t* out_x, uint32_t* out_target, uint32_t* out_loss, uint32_t* out_y);
+int32_t zyxb_block_forward_backward(zyxb_block* blk);
+int32_t zyxb_block_update(zyxb_block* blk);
+int32_t zyxb_block_step(zyxb_block* blk, const zyxb_event* wait, int32_t n_wait);
+int32_t zyxb_block_plan_size(zyxb_block* blk, int32_t* out_launches, int32_t* out_collectives);
+/* intermediate activations for tests: 0 attention probabilities [batch*heads, seq, seq], 1 attention output [rows, dim],
+ * 2 x1 (after norm1) [rows, dim] */
+int32_t zyxb_block_activation(zyxb_block* blk, int32_t which, uint32_t* out_buf);
+
 #ifdef __cplusplus
 }
 #endif

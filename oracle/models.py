@@ -77,3 +77,85 @@ class Optim:
 
 def flat(pairs):
     return [t for pair in pairs for t in pair]
+
+
+# ---- one transformer block (zyx-examples/examples/readme_test.rs:9-40) ---------------------------------
+BLOCK_PARAMS = ["wq", "bq", "wk", "bk", "wv", "bv", "wo", "bo", "w1", "b1", "w2", "b2", "g1", "be1", "g2", "be2"]
+
+
+def block_init(nprng, dtype, dim, ffn, std=0.02):
+    """Random-init weights N(0, std) (the configuration's choice), biases N(0, std); LayerNorm weight 1, bias 0
+    (zyx-nn/src/layer_norm.rs:23-45).  Returned in Module::iter() order as a dict."""
+    shapes = {"wq": (dim, dim), "bq": (dim,), "wk": (dim, dim), "bk": (dim,), "wv": (dim, dim), "bv": (dim,), "wo": (dim, dim),
+              "bo": (dim,), "w1": (ffn, dim), "b1": (ffn,), "w2": (dim, ffn), "b2": (dim,)}
+    p = {k: zo.to_bits((nprng.standard_normal(s) * std).astype(np.float32), dtype) for k, s in shapes.items()}
+    for k in ("g1", "g2"):
+        p[k] = zo.to_bits(np.ones(dim, np.float32), dtype)
+    for k in ("be1", "be2"):
+        p[k] = zo.to_bits(np.zeros(dim, np.float32), dtype)
+    return p
+
+
+def block_forward_backward(dtype, p, x, target, heads, causal, eps=1e-5):
+    """x, target: [B, T, E].  -> (loss, grads dict, y, intermediates).  Rounds to `dtype` wherever the GPU plan stores a tensor."""
+    B, T, E = x.shape
+    H, D, R = heads, E // heads, B * T
+    scale = 1.0 / np.sqrt(np.float32(D))
+    x2 = np.ascontiguousarray(x.reshape(R, E))
+    t2 = np.ascontiguousarray(target.reshape(R, E))
+    lin = lambda a, w, b, epi=zo.EPI_BIAS, pre=False: zo.gemm(dtype, a, p[w], tb=True, bias=p[b], epi=epi, want_preact=pre)
+    heads_of = lambda a: np.ascontiguousarray(a.reshape(B, T, H, D).transpose(0, 2, 1, 3)).reshape(B * H, T, D)
+    merge = lambda a: np.ascontiguousarray(a.reshape(B, H, T, D).transpose(0, 2, 1, 3)).reshape(R, E)
+    q, k, v = lin(x2, "wq", "bq"), lin(x2, "wk", "bk"), lin(x2, "wv", "bv")
+    qh, kh, vh = heads_of(q), heads_of(k), heads_of(v)
+    s = zo.gemm(dtype, qh, kh, tb=True, alpha=float(scale))
+    pr = zo.softmax(dtype, s.reshape(B * H * T, T), causal=causal, period=T).reshape(B * H, T, T)
+    attn = merge(zo.gemm(dtype, pr, vh))
+    o = lin(attn, "wo", "bo")
+    s1 = zo.eltwise(zo.EW_ADD, dtype, x2, o)
+    x1 = zo.layernorm(dtype, s1, p["g1"], p["be1"], eps)
+    h, z1 = lin(x1, "w1", "b1", zo.EPI_BIAS_GELU, True)
+    m = lin(h, "w2", "b2")
+    s2 = zo.eltwise(zo.EW_ADD, dtype, x1, m)
+    y = zo.layernorm(dtype, s2, p["g2"], p["be2"], eps)
+    loss = zo.mse(dtype, y, t2)
+    # ---- backward ----
+    g = {}
+    dy = zo.eltwise(zo.EW_MSE_BWD, dtype, y, t2, p0=1.0 / y.size)
+
+    def ln_bwd(xin, dout, w, gw, gb):
+        g[gw] = zo.colsum(dtype, zo.layernorm_dyxhat(dtype, xin, dout, eps))
+        g[gb] = zo.colsum(dtype, dout)
+        return zo.layernorm_bwd(dtype, xin, dout, p[w], eps)
+
+    def lin_grads(dout, xin, gw, gb):
+        g[gw] = zo.gemm(dtype, dout, xin, ta=True)
+        g[gb] = zo.colsum(dtype, dout)
+
+    ds2 = ln_bwd(s2, dy, "g2", "g2", "be2")
+    lin_grads(ds2, h, "w2", "b2")
+    dz1 = zo.gemm(dtype, ds2, p["w2"], bias=z1, epi=zo.EPI_MUL_GELU_GRAD)
+    lin_grads(dz1, x1, "w1", "b1")
+    # (dz1 . W1) + ds2 with a single rounding, like the fused residual epilogue
+    acc = _gemm_f32(dtype, dz1, p["w1"]) + zo.to_f32(ds2, dtype)
+    dx1 = zo.to_bits(acc, dtype)
+    ds1 = ln_bwd(s1, dx1, "g1", "g1", "be1")
+    lin_grads(ds1, attn, "wo", "bo")
+    dattn = zo.gemm(dtype, ds1, p["wo"])
+    dah = heads_of(dattn)
+    dp = zo.gemm(dtype, dah, vh, tb=True)
+    dv = merge(zo.gemm(dtype, pr, dah, ta=True))
+    dsc = zo.softmax_bwd(dtype, pr.reshape(B * H * T, T), dp.reshape(B * H * T, T)).reshape(B * H, T, T)
+    dq = merge(zo.gemm(dtype, dsc, kh, alpha=float(scale)))
+    dk = merge(zo.gemm(dtype, dsc, qh, ta=True, alpha=float(scale)))
+    lin_grads(dv, x2, "wv", "bv")
+    lin_grads(dk, x2, "wk", "bk")
+    lin_grads(dq, x2, "wq", "bq")
+    return loss, g, y.reshape(B, T, E), {"p": pr, "attn": attn, "x1": x1}
+
+
+def _gemm_f32(dtype, a, b):
+    """a . b with the oracle's sequential f32 accumulation, returned unrounded (f32)."""
+    if dtype == zo.F32:
+        return zo.gemm(zo.F32, a, b)
+    return zo.gemm(zo.F32, zo.to_f32(a, dtype), zo.to_f32(b, dtype))

@@ -157,6 +157,13 @@ def layernorm_bwd(dtype, x, dy, w=None, eps=1e-5):
     return dx
 
 
+def layernorm_dyxhat(dtype, x, dy, eps=1e-5):
+    x, dy = _c(x, dtype), _c(dy, dtype)
+    out = np.empty_like(x)
+    lib().zo_layernorm_dyxhat(dtype, _p(x), _p(dy), _p(out), _u64(x.shape[0]), _u64(x.shape[1]), C.c_float(eps))
+    return out
+
+
 def softmax_bwd(dtype, p, dp):
     p, dp = _c(p, dtype), _c(dp, dtype)
     ds = np.empty_like(p)

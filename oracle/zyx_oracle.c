@@ -339,6 +339,21 @@ void zo_layernorm_bwd(int dtype, const void* x, const void* dy, const void* w, v
   }
 }
 
+/* dy * xhat with xhat = (x - mean)/sqrt(var + eps): its column sums are the gradient of the layernorm weight */
+void zo_layernorm_dyxhat(int dtype, const void* x, const void* dy, void* out, uint64_t rows, uint64_t cols, float eps) {
+  float ceps = zo_const(dtype, eps);
+#pragma omp parallel for
+  for (uint64_t r = 0; r < rows; r++) {
+    uint64_t base = r * cols;
+    float n = (float)cols;
+    float mean = zo_row_sum(x, dtype, base, cols) / n, acc = 0.0f;
+    for (uint64_t j = 0; j < cols; j++) { float d = zo_load(x, dtype, base + j) - mean; acc = d * d + acc; }
+    float s = sqrtf(acc / (n - 1.0f) + ceps);
+    for (uint64_t j = 0; j < cols; j++)
+      zo_store(out, dtype, base + j, zo_load(dy, dtype, base + j) * ((zo_load(x, dtype, base + j) - mean) / s));
+  }
+}
+
 /* softmax backward: ds = p * (dp - sum(dp * p)) */
 void zo_softmax_bwd(int dtype, const void* p, const void* dp, void* ds, uint64_t rows, uint64_t cols) {
 #pragma omp parallel for

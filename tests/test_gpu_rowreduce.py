@@ -111,6 +111,8 @@ def test_backward_rows(sess, dtype, shape):
     x, dy, w = rand(shape, dtype, 2.0), rand(shape, dtype), rand((shape[1],), dtype)
     got, want = f(sess.layernorm_bwd(dtype, x, dy, w, 1e-5), dtype), f(zo.layernorm_bwd(dtype, x, dy, w, 1e-5), dtype)
     assert max_rel_err(got, want, floor=1e-2) <= TOL[dtype] * (20 if dtype == L.F32 else 1)   # three chained f32 sums
+    got, want = f(sess.layernorm_dyxhat(dtype, x, dy, 1e-5), dtype), f(zo.layernorm_dyxhat(dtype, x, dy, 1e-5), dtype)
+    assert max_rel_err(got, want, floor=1e-2) <= TOL[dtype] * (20 if dtype == L.F32 else 1)
     p = zo.softmax(dtype, rand(shape, dtype, 2.0))
     got, want = f(sess.softmax_bwd(dtype, p, dy), dtype), f(zo.softmax_bwd(dtype, p, dy), dtype)
     assert max_rel_err(got, want, floor=1e-2) <= TOL[dtype] * (20 if dtype == L.F32 else 1)

@@ -193,7 +193,7 @@ static int launch_mse(const void* y, const void* t, void* out, uint64_t n, const
 static bool is_float_dtype(int d) { return d == ZYXB_F32 || d == ZYXB_BF16 || d == ZYXB_F16; }
 
 int validate_rowreduce(const zyxb_rowreduce_desc& d, std::string& err) {
-  if (d.op < ZYXB_RR_SUM || d.op > ZYXB_RR_MSE) { err = "rowreduce: unknown op"; return ZYXB_ERR_KERNEL_COMPILATION; }
+  if (d.op < ZYXB_RR_SUM || d.op > ZYXB_RR_LAYERNORM_DYXHAT) { err = "rowreduce: unknown op"; return ZYXB_ERR_KERNEL_COMPILATION; }
   if (d.rows == 0 || d.cols == 0) { err = "rowreduce: rows and cols must be positive"; return ZYXB_ERR_KERNEL_COMPILATION; }
   if (d.rows > 0x7fffffffull) { err = "rowreduce: more than 2^31-1 rows"; return ZYXB_ERR_KERNEL_COMPILATION; }
   const bool int_ok = d.dtype == ZYXB_I32 && (d.op == ZYXB_RR_SUM || d.op == ZYXB_RR_MAX || d.op == ZYXB_RR_MIN);
@@ -205,7 +205,7 @@ int validate_rowreduce(const zyxb_rowreduce_desc& d, std::string& err) {
   if ((d.op == ZYXB_RR_VAR || d.op == ZYXB_RR_STD) && (int64_t)d.cols - d.correction <= 0) {
     err = "var: cols - correction must be positive"; return ZYXB_ERR_KERNEL_COMPILATION;
   }
-  if ((d.op == ZYXB_RR_LAYERNORM || d.op == ZYXB_RR_LAYERNORM_BWD) && d.cols < 2) {
+  if ((d.op == ZYXB_RR_LAYERNORM || d.op == ZYXB_RR_LAYERNORM_BWD || d.op == ZYXB_RR_LAYERNORM_DYXHAT) && d.cols < 2) {
     err = "layernorm: unbiased variance needs at least 2 columns"; return ZYXB_ERR_KERNEL_COMPILATION;
   }
   return ZYXB_OK;
@@ -250,6 +250,10 @@ int launch_rowreduce(const zyxb_rowreduce_desc& d, void* const* args, const uint
       if (d.has_weight) { ZYXB_CHECK_ARG(arg_bytes[2] >= d.cols * es, "layernorm_bwd: weight too small"); p.w = args[2]; }
       p.y = args[want - 1]; fam = FAM_LAYERNORM_BWD; break;
     }
+    case ZYXB_RR_LAYERNORM_DYXHAT:
+      ZYXB_CHECK_ARG(n_args == 3, "layernorm_dyxhat: expected args x, dy -> out");
+      ZYXB_CHECK_ARG(arg_bytes[0] >= full && arg_bytes[1] >= full && arg_bytes[2] >= full, "layernorm_dyxhat: buffer too small");
+      p.x = args[0]; p.x2 = args[1]; p.y = args[2]; fam = FAM_LAYERNORM_BWD; break;
     case ZYXB_RR_CROSS_ENTROPY: {
       ZYXB_CHECK_ARG(n_args == 4, "cross_entropy: expected args logits, labels -> per_sample, mean");
       ZYXB_CHECK_ARG(arg_bytes[0] >= full && arg_bytes[1] >= d.rows * 4 && arg_bytes[2] >= d.rows * 4 && arg_bytes[3] >= 4,

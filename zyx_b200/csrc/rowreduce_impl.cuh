@@ -325,7 +325,8 @@ __global__ void __launch_bounds__(GROUP == 32 ? 128 : GROUP) row_kernel(RowParam
       for (int k = 0; k < VEC; ++k) {
         const float dx = (float)a[k] - mean;
         const float g = wp ? (float)d[k] * wv[k] : (float)d[k];
-        o[k] = (A)((g - k1 - dx * k2) * rs);
+        if (p.op == ZYXB_RR_LAYERNORM_DYXHAT) o[k] = (A)((float)d[k] * (dx * rs));   // dy * xhat: summed over rows it is d(weight)
+        else o[k] = (A)((g - k1 - dx * k2) * rs);
       }
       write(yr, c, o);
     });

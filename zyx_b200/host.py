@@ -161,3 +161,106 @@ class Mlp:
         if self.h:
             self.lib.zyxb_mlp_destroy(self.h)
             self.h = None
+
+
+# ---- transformer block ---------------------------------------------------------------------------------
+class BlockConfig(C.Structure):
+    _fields_ = [("dtype", C.c_int32), ("batch", C.c_uint64), ("seq", C.c_uint64), ("dim", C.c_uint64), ("heads", C.c_uint64),
+                ("ffn", C.c_uint64), ("causal", C.c_int32), ("eps", C.c_float), ("optim", L.OptimDesc), ("world", C.c_int32)]
+
+
+BLOCK_SIGNATURES = {
+    "zyxb_block_create": (C.c_int32, [_P, C.c_int32, C.POINTER(BlockConfig), C.POINTER(_P)]),
+    "zyxb_block_destroy": (C.c_int32, [_P]),
+    "zyxb_block_last_error": (C.c_char_p, [_P]),
+    "zyxb_block_tensor": (C.c_int32, [_P, C.c_int32, C.c_int32, C.POINTER(C.c_uint32), C.POINTER(C.c_uint64)]),
+    "zyxb_block_io": (C.c_int32, [_P] + [C.POINTER(C.c_uint32)] * 4),
+    "zyxb_block_forward_backward": (C.c_int32, [_P]),
+    "zyxb_block_update": (C.c_int32, [_P]),
+    "zyxb_block_step": (C.c_int32, [_P, C.POINTER(L.Event), C.c_int32]),
+    "zyxb_block_plan_size": (C.c_int32, [_P, C.POINTER(C.c_int32), C.POINTER(C.c_int32)]),
+    "zyxb_block_activation": (C.c_int32, [_P, C.c_int32, C.POINTER(C.c_uint32)]),
+}
+HOST_SIGNATURES.update(BLOCK_SIGNATURES)
+BLOCK_PARAM_NAMES = ["wq", "bq", "wk", "bk", "wv", "bv", "wo", "bo", "w1", "b1", "w2", "b2", "g1", "be1", "g2", "be2"]
+
+
+class Block:
+    """One transformer block (attention + feed-forward, post-norm) with its training plan."""
+
+    def __init__(self, session, dtype, batch, seq, dim, heads, ffn, causal=True, eps=1e-5, algo=L.OPT_ADAMW, world=1, **optim_kw):
+        self.lib, self.sess = load(), session
+        cfg = BlockConfig()
+        cfg.dtype, cfg.batch, cfg.seq, cfg.dim, cfg.heads, cfg.ffn, cfg.causal, cfg.eps, cfg.world = dtype, batch, seq, dim, heads, ffn, int(causal), eps, world
+        o = cfg.optim
+        o.algo = algo
+        o.lr, o.weight_decay = optim_kw.get("lr", 1e-3), optim_kw.get("weight_decay", 0.0)
+        o.momentum, o.beta1, o.beta2, o.eps = optim_kw.get("momentum", 0.0), optim_kw.get("beta1", 0.9), optim_kw.get("beta2", 0.999), optim_kw.get("eps", 1e-8)
+        o.standard = int(optim_kw.get("standard", False))
+        self.cfg, self.dtype = cfg, dtype
+        self.shape_in = (batch, seq, dim)
+        self.h = _P()
+        st = self.lib.zyxb_block_create(session.backend.ctx, session.device.dev, C.byref(cfg), C.byref(self.h))
+        if st != L.OK:
+            raise BackendError(st, session.backend.lib.zyxb_last_error(session.backend.ctx).decode())
+        bufs = [C.c_uint32() for _ in range(4)]
+        self._check(self.lib.zyxb_block_io(self.h, *[C.byref(b) for b in bufs]))
+        self.x, self.target, self.loss, self.y = (b.value for b in bufs)
+        self.np_dtype = np.float32 if dtype == L.F32 else np.uint16
+        E, F = dim, ffn
+        self.shapes = [(E, E), (E,)] * 4 + [(F, E), (F,), (E, F), (E,)] + [(E,)] * 4
+
+    def _check(self, st):
+        if st != L.OK:
+            raise BackendError(st, self.lib.zyxb_block_last_error(self.h).decode())
+
+    def tensor(self, which, i):
+        buf, n = C.c_uint32(), C.c_uint64()
+        self._check(self.lib.zyxb_block_tensor(self.h, which, i, C.byref(buf), C.byref(n)))
+        return buf.value, n.value
+
+    def set_tensor(self, which, i, arr):
+        buf, n = self.tensor(which, i)
+        arr = np.ascontiguousarray(arr)
+        assert arr.size == n and arr.dtype == self.np_dtype
+        self.sess.pool.sync_events([self.sess.pool.host_to_pool(arr, buf)])
+
+    def get_tensor(self, which, i):
+        buf, _ = self.tensor(which, i)
+        return self.sess.pool.download(buf, self.shapes[i], self.np_dtype)
+
+    def set_batch(self, x, target):
+        p = self.sess.pool
+        return [p.host_to_pool(np.ascontiguousarray(x), self.x), p.host_to_pool(np.ascontiguousarray(target), self.target)]
+
+    def activation(self, which, shape):
+        buf = C.c_uint32()
+        self._check(self.lib.zyxb_block_activation(self.h, which, C.byref(buf)))
+        return self.sess.pool.download(buf.value, shape, self.np_dtype)
+
+    def forward_backward(self):
+        self._check(self.lib.zyxb_block_forward_backward(self.h))
+
+    def update(self):
+        self._check(self.lib.zyxb_block_update(self.h))
+
+    def step(self, events=None):
+        events = [e for e in (events or []) if e.id != 0]
+        arr = (L.Event * len(events))(*events) if events else None
+        self._check(self.lib.zyxb_block_step(self.h, arr, len(events)))
+
+    def read_loss(self):
+        return float(self.sess.pool.download(self.loss, (1,), np.float32)[0])
+
+    def read_output(self):
+        return self.sess.pool.download(self.y, self.shape_in, self.np_dtype)
+
+    def plan_size(self):
+        a, b = C.c_int32(), C.c_int32()
+        self._check(self.lib.zyxb_block_plan_size(self.h, C.byref(a), C.byref(b)))
+        return a.value, b.value
+
+    def close(self):
+        if self.h:
+            self.lib.zyxb_block_destroy(self.h)
+            self.h = None

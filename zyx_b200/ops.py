@@ -58,6 +58,10 @@ class Session:
         d = B.rowreduce_desc(L.RR_LAYERNORM_BWD, dtype, rows, cols, eps=eps, has_weight=w is not None)
         return self.run(d, ins, [(x.shape, x.dtype)])[0]
 
+    def layernorm_dyxhat(self, dtype, x, dy, eps=1e-5):
+        rows, cols = x.shape
+        return self.run(B.rowreduce_desc(L.RR_LAYERNORM_DYXHAT, dtype, rows, cols, eps=eps), [x, dy], [(x.shape, x.dtype)])[0]
+
     def softmax_bwd(self, dtype, p, dp):
         rows, cols = p.shape
         return self.run(B.rowreduce_desc(L.RR_SOFTMAX_BWD, dtype, rows, cols), [p, dp], [(p.shape, p.dtype)])[0]
