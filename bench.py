@@ -5,6 +5,7 @@
 
 Prints ONE JSON line.  Workloads (synthetic, seeded, shapes of the reference's configurations):
   mlp         4 x Linear 4096<->16384, GELU, bf16, batch 8192 per GPU, MSE, AdamW; data parallel   (samples/s)  [default]
+  block       transformer block d=2048, 16 heads, FFN 8192, seq 2048, batch 8 over the GPUs, bf16, causal; fwd+bwd+AdamW   (samples/s)
   simplenet   README SimpleNet 784->128->10, f32, batch 64, CE, SGD; step replayed from a captured graph   (samples/s)
   rowreduce   row softmax + row layernorm on f32 [8192, 32768]         (fused-reduce GB/s)
   gemm_bf16   C = A.B, M=N=K=8192 bf16, f32 accumulate                  (GEMM TFLOP/s)
@@ -511,7 +512,91 @@ class SimpleNet:
         return n * self.batch / dt, "%d full training steps at batch %d, %.1f s" % (n, self.batch, dt)
 
 
-WORKLOADS = {"simplenet": SimpleNet, "mlp": MlpTrain, "rowreduce": RowReduce, "gemm_bf16": lambda: Gemm("bf16"), "gemm_f32": lambda: Gemm("f32")}
+class BlockTrain:
+    """Config 5: one transformer block (MultiheadAttention + MLP, post-norm), d_model 2048, 16 heads x 128, FFN 8192, seq 2048,
+    batch 8 split across the GPUs, bf16, causal, weights N(0, 0.02), inputs and targets N(0,1): forward + backward (+ AdamW)."""
+    E, H, F, T, GLOBAL_B = 2048, 16, 8192, 2048, 8
+    unit, dtype, bound = "samples/s", "bf16", "tensor"
+
+    def __init__(self, size=0, rank=0, world=1):
+        self.rank, self.world = rank, world
+        self.B = size if size else max(1, self.GLOBAL_B // world)
+        self.name = "transformer_block_d2048_h16_ffn8192_seq2048_bf16_causal_batch%d_per_gpu" % self.B
+        self.metric = "transformer block train samples/s (d=2048, 16x128 heads, FFN 8192, seq 2048, bf16, causal, fwd+bwd+AdamW)"
+        self.units_per_step = float(self.B)
+        R, E, F, T, H, D = self.B * self.T, self.E, self.F, self.T, self.H, self.E // self.H
+        proj = 4 * 2.0 * R * E * E            # q, k, v, out
+        attn = 2 * 2.0 * self.B * H * T * T * D
+        ffn = 2 * 2.0 * R * E * F
+        self.gemm_flops = 3.0 * (proj + attn + ffn) - 3 * 2.0 * R * E * E      # no input gradient for the q/k/v projections
+        self.h2d_bytes, self.d2h_bytes = 2 * R * E * 2, 4
+
+    def host_inputs(self):
+        rng = np.random.default_rng(300 + self.rank)
+        self.hx = f32_to_bf16_bits(rng.standard_normal((self.B, self.T, self.E), dtype=np.float32))
+        self.ht = f32_to_bf16_bits(rng.standard_normal((self.B, self.T, self.E), dtype=np.float32))
+
+    def setup(self, sess):
+        from zyx_b200 import _lib as L, host as H
+        self.sess, self.Hm = sess, H
+        self.host_inputs()
+        self.blk = H.Block(sess, L.BF16, self.B, self.T, self.E, self.H, self.F, causal=True, algo=L.OPT_ADAMW, world=self.world,
+                           lr=1e-3, weight_decay=0.01, standard=True)
+        rng = np.random.default_rng(0)
+        for i, shape in enumerate(self.blk.shapes):
+            if i >= 12:
+                w = np.ones(shape, np.float32) if i % 2 == 0 else np.zeros(shape, np.float32)     # LayerNorm weight 1, bias 0
+            else:
+                w = (rng.standard_normal(shape) * 0.02).astype(np.float32)
+            self.blk.set_tensor(H.PARAM, i, f32_to_bf16_bits(w))
+        sess.pool.sync_events(self.blk.set_batch(self.hx, self.ht))
+        launches, colls = self.blk.plan_size()
+        self.config = {"workload": self.name, "global_batch": self.B * self.world, "parallelism": "dp%d" % self.world,
+                       "optimizer": "AdamW lr=1e-3 wd=0.01 (textbook update: the reference's literal form overflows after one step)",
+                       "attention": "scores materialised ([B*H, T, T] bf16) as in the reference; causal mask as a select",
+                       "l2": "working set (scores alone %d MiB) larger than L2" % (self.B * self.H * self.T * self.T * 2 >> 20),
+                       "launches_per_step": launches, "collectives_per_step": colls}
+        self.losses = []
+        self.step_events = []
+
+    def step(self, timed=False):
+        self.blk.step()
+
+    def roofline(self, peaks, clocks=None):
+        # the whole step against the matmul FLOPs it contains (the step is one plan; per-kernel shares are in profiles/)
+        t = self.ms_per_step_hint
+        ach = self.gemm_flops / (t * 1e-3) / 1e12
+        return ({"bound": "tensor", "kernel": "whole step (gemm_tc_kernel dominant)", "achieved": ach, "peak": peaks["bf16_tflops_sustained"],
+                 "unit": "TFLOP/s", "frac": ach / peaks["bf16_tflops_sustained"], "traffic": None, "peak_source": peaks["source"] + " (sustained)",
+                 "ms_per_launch": t, "flops_per_step": self.gemm_flops}, {})
+
+    def e2e_setup(self):
+        for a in (self.hx, self.ht):
+            self.sess.backend.host_register(a)
+
+    def e2e_step(self):
+        self.blk.step(self.blk.set_batch(self.hx, self.ht))
+        self.losses.append(self.blk.read_loss())
+
+    def check(self):
+        return None
+
+    def cpu_baseline(self, budget_s=12.0):
+        from oracle import models as om, oracle as zo
+        E, F, H, T = 256, 1024, 2, 256        # one sample of a 1/8-width block: the full-size scalar step would take hours
+        rng = np.random.default_rng(0)
+        p = om.block_init(rng, zo.BF16, E, F, std=0.02)
+        x = zo.to_bits(rng.standard_normal((1, T, E)).astype(np.float32), zo.BF16)
+        t0 = time.perf_counter()
+        om.block_forward_backward(zo.BF16, p, x, x, H, True)
+        dt = time.perf_counter() - t0
+        flops = 3.0 * (4 * 2.0 * T * E * E + 2 * 2.0 * H * T * T * (E // H) + 2 * 2.0 * T * E * F)
+        full = self.gemm_flops / self.B
+        return (flops / dt) / full, ("forward + backward of a reduced block (d=%d, ffn=%d, %d heads, seq %d, 1 sample: %.2f GFLOP in %.1f s); "
+                                      "samples/s extrapolated to the full block by matmul FLOPs (%.1f GFLOP per sample)") % (E, F, H, T, flops / 1e9, dt, full / 1e9)
+
+
+WORKLOADS = {"block": BlockTrain, "simplenet": SimpleNet, "mlp": MlpTrain, "rowreduce": RowReduce, "gemm_bf16": lambda: Gemm("bf16"), "gemm_f32": lambda: Gemm("f32")}
 
 
 def make_workload(args, rank=0, world=1):
@@ -519,6 +604,8 @@ def make_workload(args, rank=0, world=1):
         return MlpTrain(size=args.size, standard=args.standard_adamw, rank=rank, world=world)
     if args.workload == "simplenet":
         return SimpleNet(size=args.size, rank=rank, world=world)
+    if args.workload == "block":
+        return BlockTrain(size=args.size, rank=rank, world=world)
     if args.size:
         return {"rowreduce": lambda: RowReduce(rows=args.size), "gemm_bf16": lambda: Gemm("bf16", args.size),
                 "gemm_f32": lambda: Gemm("f32", args.size)}[args.workload]()
@@ -645,6 +732,7 @@ def run():
         ms_total = float(t.item())
     ms_step = ms_total / args.steps
     value = world * w.units_per_step / (ms_step * 1e-3)
+    w.ms_per_step_hint = ms_step
     roofline, kernels = w.roofline(peaks, clocks)
     err = w.check()
 
