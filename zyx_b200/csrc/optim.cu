@@ -9,6 +9,7 @@
 // stored (rounded) value is what the rest of the step uses.
 #include <algorithm>
 #include <cmath>
+#include <type_traits>
 
 #include "common.cuh"
 #include "internal.h"
@@ -17,7 +18,7 @@ namespace zyxb {
 
 constexpr int OPT_MAX_TENSORS = 32;   // tensors per launch; larger models take several launches
 constexpr int OPT_THREADS = 256;
-constexpr int OPT_UNROLL = 4;         // packs per thread per chunk
+constexpr int OPT_UNROLL = 2;         // packs per thread per chunk
 
 struct OptTable {
   void* p[OPT_MAX_TENSORS];
@@ -31,6 +32,7 @@ struct OptTable {
 
 struct OptHyper {
   float lr, wd, momentum, one_minus_damp, beta1, beta2, one_minus_b1, one_minus_b2, bc1, bc2, eps, decay, grad_scale;
+  float rbc1, rbc2;   // 1 / bc1, 1 / bc2 of the dtype-cast bias corrections (filled in on the device)
   int nesterov, maximize, first, mode;   // mode: 0 Adam, 1 AdamW as the reference writes it, 2 textbook AdamW
   int rn;
 };
@@ -40,6 +42,7 @@ struct OptHyper {
 // stays memory-bound.
 template <typename T> __device__ __forceinline__ float opt_div(float a, float b) { return __fdividef(a, b); }
 template <> __device__ __forceinline__ float opt_div<float>(float a, float b) { return a / b; }
+__device__ __forceinline__ float opt_rcp(float a) { float r; asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(a)); return r; }
 template <typename T> __device__ __forceinline__ float opt_sqrt(float a) { float r; asm("sqrt.approx.f32 %0, %1;" : "=f"(r) : "f"(a)); return r; }
 template <> __device__ __forceinline__ float opt_sqrt<float>(float a) { return sqrtf(a); }
 
@@ -61,10 +64,18 @@ __device__ __forceinline__ void opt_update(float& pv, float gv, float& mv, float
     float nv = h.first ? gv * gv * h.one_minus_b2 : vv * h.beta2 + gv * gv * h.one_minus_b2;
     nm = round_state(nm); nv = round_state(nv);
     mv = nm; vv = nv;
-    const float mh = opt_div<T>(nm, h.bc1), vh = opt_div<T>(nv, h.bc2);
-    float np;
-    if (h.mode == 1) np = pv - opt_div<T>(mh, (opt_sqrt<T>(vh) + h.eps) * h.lr);
-    else np = pv - opt_div<T>(h.lr * mh, opt_sqrt<T>(vh) + h.eps);
+    float mh, vh, np;
+    if constexpr (std::is_same_v<T, float>) {
+      mh = nm / h.bc1; vh = nv / h.bc2;
+      if (h.mode == 1) np = pv - mh / ((sqrtf(vh) + h.eps) * h.lr);
+      else np = pv - h.lr * mh / (sqrtf(vh) + h.eps);
+    } else {
+      // 16-bit tensors: reciprocals of the bias corrections are formed once per thread, the remaining division is
+      // one SFU reciprocal; a few ulp of f32, far inside the 8 / 11 significant bits the result keeps
+      mh = nm * h.rbc1; vh = nv * h.rbc2;
+      if (h.mode == 1) np = pv - mh * opt_rcp((opt_sqrt<T>(vh) + h.eps) * h.lr);
+      else np = pv - h.lr * mh * opt_rcp(opt_sqrt<T>(vh) + h.eps);
+    }
     if (h.mode != 0 && h.wd != 0.0f) np = np * h.decay;
     pv = np;
   }
@@ -91,6 +102,7 @@ __global__ void __launch_bounds__(OPT_THREADS) optim_kernel(OptTable tab, OptHyp
   h.beta2 = const_cast_dtype<T>(hy.beta2); h.one_minus_b1 = const_cast_dtype<T>(hy.one_minus_b1);
   h.one_minus_b2 = const_cast_dtype<T>(hy.one_minus_b2); h.bc1 = const_cast_dtype<T>(hy.bc1); h.bc2 = const_cast_dtype<T>(hy.bc2);
   h.eps = const_cast_dtype<T>(hy.eps); h.decay = const_cast_dtype<T>(hy.decay);
+  h.rbc1 = 1.0f / h.bc1; h.rbc2 = 1.0f / h.bc2;
   // keep the "is it zero" tests on the caller's values, as the reference tests its f32 fields
   if (hy.wd == 0.0f) h.wd = 0.0f;
   if (hy.momentum == 0.0f) h.momentum = 0.0f;

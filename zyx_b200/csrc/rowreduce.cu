@@ -19,37 +19,53 @@ __global__ void __launch_bounds__(256) mean_of_rows_kernel(const float* per, flo
 }
 
 // ---- column sums: y[j] = sum_r x[r, j] -----------------------------------------------------
-// Stage 1: each CTA owns 128*VEC columns and one slice of the rows; a warp reads consecutive
-// vectors of one row (coalesced).  Partials go to scratch as f32 [splits, cols].
-// Stage 2 folds the splits in order and stores in the tensor dtype.
+// Stage 1: a CTA of 8 warps owns a strip of 32*VEC columns and one slice of the rows; each warp reads whole
+// 32*VEC-column segments of its rows (one coalesced 512-byte access per row per warp, four rows in flight),
+// the eight warps fold through shared memory.  Partials go to scratch as f32 [splits, cols].
+// Stage 2 folds the (few) splits in order and stores in the tensor dtype.
+constexpr int COLSUM_WARPS = 8;
 template <typename T, int VEC>
-__global__ void __launch_bounds__(128) colsum_partial_kernel(const typename Elem<T>::store_t* x, float* partial, uint64_t rows,
-                                                             uint64_t cols, uint64_t rows_per_split) {
+__global__ void __launch_bounds__(32 * COLSUM_WARPS) colsum_partial_kernel(const typename Elem<T>::store_t* x, float* partial, uint64_t rows,
+                                                                           uint64_t cols, uint64_t rows_per_split) {
   using S = typename Elem<T>::store_t;
-  const uint64_t c = ((uint64_t)blockIdx.x * 128 + threadIdx.x) * VEC;
-  if (c >= cols) return;
+  __shared__ float fold[COLSUM_WARPS][32 * VEC + 1];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const uint64_t c = ((uint64_t)blockIdx.x * 32 + lane) * VEC;
+  const bool live = c < cols;
   const uint64_t r0 = (uint64_t)blockIdx.y * rows_per_split;
   const uint64_t r1 = min(r0 + rows_per_split, rows);
   float acc[VEC];
 #pragma unroll
   for (int k = 0; k < VEC; ++k) acc[k] = 0.0f;
-  uint64_t r = r0;
-  for (; r + 4 <= r1; r += 4) {   // four independent loads in flight per thread
-    Pack<S, VEC> pk[4];
+  if (live) {
+    uint64_t r = r0 + warp;
+    for (; r + 3 * COLSUM_WARPS < r1; r += 4 * COLSUM_WARPS) {   // four independent loads in flight per thread
+      Pack<S, VEC> pk[4];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) pk[u] = load_pack_stream<S, VEC>(x + (r + u) * cols + c);
+      for (int u = 0; u < 4; ++u) pk[u] = load_pack_stream<S, VEC>(x + (r + u * COLSUM_WARPS) * cols + c);
 #pragma unroll
-    for (int u = 0; u < 4; ++u)
+      for (int u = 0; u < 4; ++u)
 #pragma unroll
-      for (int k = 0; k < VEC; ++k) acc[k] += (float)Elem<T>::load(pk[u].v[k]);
+        for (int k = 0; k < VEC; ++k) acc[k] += (float)Elem<T>::load(pk[u].v[k]);
+    }
+    for (; r < r1; r += COLSUM_WARPS) {
+      Pack<S, VEC> pk = load_pack_stream<S, VEC>(x + r * cols + c);
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) acc[k] += (float)Elem<T>::load(pk.v[k]);
+    }
   }
-  for (; r < r1; ++r) {
-    Pack<S, VEC> pk = load_pack_stream<S, VEC>(x + r * cols + c);
 #pragma unroll
-    for (int k = 0; k < VEC; ++k) acc[k] += (float)Elem<T>::load(pk.v[k]);
+  for (int k = 0; k < VEC; ++k) fold[warp][lane * VEC + k] = acc[k];
+  __syncthreads();
+  for (int i = threadIdx.x; i < 32 * VEC; i += 32 * COLSUM_WARPS) {
+    const uint64_t cc = (uint64_t)blockIdx.x * 32 * VEC + i;
+    if (cc < cols) {
+      float t = 0.0f;
+#pragma unroll
+      for (int w = 0; w < COLSUM_WARPS; ++w) t += fold[w][i];
+      partial[(uint64_t)blockIdx.y * cols + cc] = t;
+    }
   }
-#pragma unroll
-  for (int k = 0; k < VEC; ++k) partial[(uint64_t)blockIdx.y * cols + c + k] = acc[k];
 }
 
 template <typename T>
@@ -67,18 +83,18 @@ static int launch_colsum(const void* x, void* y, uint64_t rows, uint64_t cols, c
   using S = typename Elem<T>::store_t;
   constexpr int V = 16 / sizeof(S);
   const bool vec_ok = cols % V == 0 && (uintptr_t)x % 16 == 0;
-  const uint64_t per_cta = 128ull * (vec_ok ? V : 1);
+  const uint64_t per_cta = 32ull * (vec_ok ? V : 1);
   const uint64_t col_blocks = (cols + per_cta - 1) / per_cta;
   uint64_t splits = (4ull * lc.sm_count + col_blocks - 1) / col_blocks;
-  splits = std::max<uint64_t>(1, std::min<uint64_t>({splits, rows, 1024ull, lc.scratch_bytes / (cols * sizeof(float))}));
+  splits = std::max<uint64_t>(1, std::min<uint64_t>({splits, (rows + 31) / 32, 64ull, lc.scratch_bytes / (cols * sizeof(float))}));
   ZYXB_CHECK_ARG(cols * sizeof(float) <= lc.scratch_bytes, "colsum: cols too large for the scratch buffer");
   ZYXB_CHECK_ARG(col_blocks <= 0x7fffffffull, "colsum: too many columns");
   const uint64_t rps = (rows + splits - 1) / splits;
   splits = (rows + rps - 1) / rps;
   dim3 grid((unsigned)col_blocks, (unsigned)splits);
   float* partial = reinterpret_cast<float*>(lc.scratch);
-  if (vec_ok) colsum_partial_kernel<T, V><<<grid, 128, 0, lc.stream>>>((const S*)x, partial, rows, cols, rps);
-  else colsum_partial_kernel<T, 1><<<grid, 128, 0, lc.stream>>>((const S*)x, partial, rows, cols, rps);
+  if (vec_ok) colsum_partial_kernel<T, V><<<grid, 32 * COLSUM_WARPS, 0, lc.stream>>>((const S*)x, partial, rows, cols, rps);
+  else colsum_partial_kernel<T, 1><<<grid, 32 * COLSUM_WARPS, 0, lc.stream>>>((const S*)x, partial, rows, cols, rps);
   colsum_final_kernel<T><<<(unsigned)((cols + 255) / 256), 256, 0, lc.stream>>>(partial, (S*)y, cols, (uint32_t)splits, lc.round_nearest);
   return check_launch(lc, err, "colsum", 2);
 }
@@ -119,15 +135,15 @@ static int launch_colsum_static_t(const void* x, void* y, uint64_t rows, uint64_
   using S = typename Elem<T>::store_t;
   constexpr int V = 16 / sizeof(S);
   const bool vec_ok = cols % V == 0 && (uintptr_t)x % 16 == 0;
-  const uint64_t per_cta = 128ull * (vec_ok ? V : 1);
+  const uint64_t per_cta = 32ull * (vec_ok ? V : 1);
   const uint64_t col_blocks = (cols + per_cta - 1) / per_cta;
   uint64_t splits = (4ull * lc.sm_count + col_blocks - 1) / col_blocks;
-  splits = std::max<uint64_t>(1, std::min<uint64_t>({splits, rows, 1024ull, COLSUM_STATIC_FLOATS / cols}));
+  splits = std::max<uint64_t>(1, std::min<uint64_t>({splits, (rows + 31) / 32, 64ull, COLSUM_STATIC_FLOATS / cols}));
   const uint64_t rps = (rows + splits - 1) / splits;
   splits = (rows + rps - 1) / rps;
   dim3 grid((unsigned)col_blocks, (unsigned)splits);
-  if (vec_ok) colsum_partial_kernel<T, V><<<grid, 128, 0, lc.stream>>>((const S*)x, partial, rows, cols, rps);
-  else colsum_partial_kernel<T, 1><<<grid, 128, 0, lc.stream>>>((const S*)x, partial, rows, cols, rps);
+  if (vec_ok) colsum_partial_kernel<T, V><<<grid, 32 * COLSUM_WARPS, 0, lc.stream>>>((const S*)x, partial, rows, cols, rps);
+  else colsum_partial_kernel<T, 1><<<grid, 32 * COLSUM_WARPS, 0, lc.stream>>>((const S*)x, partial, rows, cols, rps);
   colsum_final_kernel<T><<<(unsigned)((cols + 255) / 256), 256, 0, lc.stream>>>(partial, (S*)y, cols, (uint32_t)splits, lc.round_nearest);
   return check_launch(lc, err, "colsum_static", 2);
 }
@@ -139,7 +155,7 @@ int launch_colsum_static(int dtype, const void* x, void* y, uint64_t rows, uint6
           " floats; use a ZYXB_RR_COLSUM program instead";
     return ZYXB_ERR_INCORRECT_KERNEL_ARG;
   }
-  if ((cols + 127) / 128 > 0x7fffffffull) { err = "colsum_static: too many columns"; return ZYXB_ERR_INCORRECT_KERNEL_ARG; }
+  if ((cols + 31) / 32 > 0x7fffffffull) { err = "colsum_static: too many columns"; return ZYXB_ERR_INCORRECT_KERNEL_ARG; }
   float* partial = nullptr;
   int st = colsum_static_address(lc.device, &partial, err);
   if (st) return st;
