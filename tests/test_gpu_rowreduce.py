@@ -222,3 +222,25 @@ def test_bad_arguments_are_reported_not_faulted(sess):
     assert e.value.status_name == "KernelCompilation"
     sess.pool.deallocate(small)
     sess.device.release(prog)
+
+
+@pytest.mark.parametrize("dtype,cols", [(L.F32, 4096), (L.F32, 20000), (L.F32, 32768), (L.BF16, 8192), (L.BF16, 32768), (L.F16, 16384)])
+def test_long_rows_staged_through_shared_memory(sess, dtype, cols):
+    """Enough rows (>= 2 per SM) of 16..128 KB each select the persistent kernel that stages rows with bulk copies:
+    softmax, ln_softmax, scaled + causal softmax and layernorm without affine parameters, against the oracle."""
+    rows = 333
+    x = rand((rows, cols), dtype, 3.0)
+    xf = f(x, dtype)
+    af = F16_MIN_NORMAL / TOL_BF16 if dtype == L.F16 else 0.0
+    assert_parity(f(sess.softmax(dtype, x), dtype), f(zo.softmax(dtype, x), dtype), exact_softmax(xf), TOL[dtype], what="softmax", abs_floor=af)
+    assert_parity(f(sess.softmax(dtype, x, log=True), dtype), f(zo.ln_softmax(dtype, x), dtype), exact_softmax(xf, log=True), TOL[dtype],
+                  what="ln_softmax")
+    period = 111
+    got = f(sess.softmax(dtype, x, scale=0.25, causal=True, period=period), dtype)
+    want = f(zo.softmax(dtype, x, scale=0.25, causal=True, period=period), dtype)
+    assert max_rel_err(got, want, abs_floor=af) <= TOL[dtype]
+    assert np.all(got[np.arange(cols)[None, :] > (np.arange(rows) % period)[:, None]] == 0.0)
+    cc = lambda v: zo.const_cast(dtype, float(v))
+    assert_parity(f(sess.layernorm(dtype, x), dtype), f(zo.layernorm(dtype, x), dtype),
+                  exact_layernorm(xf, None, None, cc(1e-5), cc(cols), cc(cols - 1)), TOL[dtype], what="layernorm")
+    assert sess.device.status() == 0

@@ -1,5 +1,7 @@
 // Host-side dispatch of the row kernels, plus the reductions that cross rows:
 // column sums (bias gradients), the mean of per-sample losses and the MSE loss.
+#include <stdlib.h>
+
 #include <algorithm>
 
 #include "rowreduce_impl.cuh"
@@ -234,6 +236,8 @@ int launch_rowreduce(const zyxb_rowreduce_desc& d, void* const* args, const uint
   RowParams p{};
   p.rows = d.rows; p.cols = d.cols; p.op = d.op; p.correction = d.correction; p.eps = d.eps;
   p.scale = d.scale == 0.0f ? 1.0f : d.scale; p.causal = d.causal; p.period = d.period; p.rn = lc.round_nearest ? 1 : 0;
+  static const bool no_staged = getenv("ZYXB_NO_STAGED_ROWS") != nullptr;
+  p.sm_count = no_staged ? 0 : lc.sm_count; p.status = lc.status_word;
   int fam = -1;
   switch (d.op) {
     case ZYXB_RR_SUM: case ZYXB_RR_MAX: case ZYXB_RR_MIN: case ZYXB_RR_MEAN: case ZYXB_RR_VAR: case ZYXB_RR_STD:

@@ -13,6 +13,7 @@
 #pragma once
 #include <math_constants.h>
 
+#include <algorithm>
 #include <type_traits>
 
 #include "common.cuh"
@@ -37,6 +38,8 @@ struct RowParams {
   int causal;
   uint64_t period;
   int rn;           // round-to-nearest stores
+  int sm_count;     // host side only: size of the persistent grid of the staged kernel
+  uint32_t* status; // device status word (bounded waits report here)
 };
 
 template <typename T, int VEC, int ITEMS, int GROUP, int FAM>
@@ -333,6 +336,184 @@ __global__ void __launch_bounds__(GROUP == 32 ? 128 : GROUP) row_kernel(RowParam
   }
 }
 
+// ---- long rows staged through shared memory with bulk (TMA) copies -------------------------------------
+// For rows of 16 KB .. 128 KB (softmax, ln_softmax, layernorm): a persistent CTA of 512 threads per SM walks its
+// rows; while it reduces and stores row i from registers, one bulk copy (cp.async.bulk, completion on an mbarrier)
+// is already bringing row i+1 into shared memory, so every SM keeps loads and stores in flight at the same time
+// instead of alternating between them.  The row is read from HBM once and written once.
+constexpr int STG_THREADS = 512;
+constexpr uint64_t STG_WAIT_NS = 2000000000ull;
+
+__device__ __forceinline__ uint32_t stg_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ uint64_t stg_timer_ns() { uint64_t t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
+__device__ __forceinline__ uint32_t stg_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+               : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok;
+}
+// thread 0: arm the barrier with the row's byte count and start the bulk copy (in chunks of at most 32 KB)
+__device__ __forceinline__ void stg_fetch_row(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy reads of the buffer are done; the async proxy may overwrite it
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+  for (uint32_t off = 0; off < bytes; off += 32768u) {
+    const uint32_t n = min(32768u, bytes - off);
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst + off), "l"((const char*)src + off), "r"(n), "r"(bar) : "memory");
+  }
+}
+
+template <typename T, int ITEMS, int FAM>
+__global__ void __launch_bounds__(STG_THREADS, 1) row_staged_kernel(RowParams p, uint32_t* status) {
+  using S = typename Elem<T>::store_t;
+  constexpr int VEC = 16 / sizeof(S);
+  extern __shared__ __align__(128) uint8_t stg_smem[];
+  __shared__ float red[32];
+  __shared__ __align__(8) uint64_t bar_storage;
+  __shared__ int abort_flag;
+  const uint32_t buf = stg_smem_u32(stg_smem), bar = stg_smem_u32(&bar_storage);
+  const uint64_t cols = p.cols;
+  const uint32_t row_bytes = (uint32_t)(cols * sizeof(S));
+  const S* X = reinterpret_cast<const S*>(p.x);
+  S* Y = reinterpret_cast<S*>(p.y);
+  const bool rn = p.rn != 0;
+  const int tid = threadIdx.x;
+  if (tid == 0) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(1) : "memory");
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    abort_flag = 0;
+  }
+  __syncthreads();
+  uint64_t row = blockIdx.x;
+  if (tid == 0 && row < p.rows) stg_fetch_row(buf, X + row * cols, row_bytes, bar);
+  uint32_t parity = 0;
+  const bool scaled = p.scale != 1.0f;
+  const float cscale = const_cast_dtype<T>(p.scale);
+  for (; row < p.rows; row += gridDim.x) {
+    // wait (bounded) for this row to land in shared memory
+    if (!stg_try_wait(bar, parity)) {
+      const uint64_t t0 = stg_timer_ns();
+      while (!stg_try_wait(bar, parity)) {
+        if (stg_timer_ns() - t0 > STG_WAIT_NS) { abort_flag = 1; atomicOr(status, 8u); break; }
+      }
+    }
+    __syncthreads();
+    if (abort_flag) return;
+    parity ^= 1;
+    float v[ITEMS][VEC];
+#pragma unroll
+    for (int it = 0; it < ITEMS; ++it) {
+      const uint64_t c = ((uint64_t)it * STG_THREADS + tid) * VEC;
+      if (c < cols) {
+        const Pack<S, VEC> pk = *reinterpret_cast<const Pack<S, VEC>*>(stg_smem + c * sizeof(S));
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) v[it][k] = (float)Elem<T>::load(pk.v[k]);
+      }
+    }
+    __syncthreads();                                   // every thread has its part of the row in registers
+    const uint64_t next = row + gridDim.x;
+    if (tid == 0 && next < p.rows) stg_fetch_row(buf, X + next * cols, row_bytes, bar);
+    S* yr = Y + row * cols;
+    auto for_each = [&](auto&& f) {
+#pragma unroll
+      for (int it = 0; it < ITEMS; ++it) {
+        const uint64_t c = ((uint64_t)it * STG_THREADS + tid) * VEC;
+        if (c < cols) f(c, v[it]);
+      }
+    };
+    auto write = [&](uint64_t c, const float (&o)[VEC]) {
+      Pack<S, VEC> pk;
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) pk.v[k] = Elem<T>::store(o[k], rn);
+      store_pack_stream<S, VEC>(yr + c, pk);
+    };
+    if constexpr (FAM == FAM_SOFTMAX) {
+      const uint64_t lim = p.causal ? min((uint64_t)(row % p.period) + 1, cols) : cols;
+      auto val = [&](float a, uint64_t c) -> float { if (scaled) a *= cscale; return c < lim ? a : -CUDART_INF_F; };
+      float mx = -CUDART_INF_F;
+      for_each([&](uint64_t c, const float (&a)[VEC]) {
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) mx = fmaxf(val(a[k], c + k), mx);
+      });
+      mx = group_reduce<STG_THREADS>(mx, OpMaxF(), red, -CUDART_INF_F);
+      float sum = 0.0f;
+      for_each([&](uint64_t c, const float (&a)[VEC]) {
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) sum += fast_exp(val(a[k], c + k) - mx);
+      });
+      sum = group_reduce<STG_THREADS>(sum, OpSum(), red, 0.0f);
+      if (p.op == ZYXB_RR_SOFTMAX) {
+        const float inv = 1.0f / sum;
+        for_each([&](uint64_t c, const float (&a)[VEC]) {
+          float o[VEC];
+#pragma unroll
+          for (int k = 0; k < VEC; ++k) o[k] = fast_exp(val(a[k], c + k) - mx) * inv;
+          write(c, o);
+        });
+      } else {
+        const float ls = logf(sum);
+        for_each([&](uint64_t c, const float (&a)[VEC]) {
+          float o[VEC];
+#pragma unroll
+          for (int k = 0; k < VEC; ++k) o[k] = (val(a[k], c + k) - mx) - ls;
+          write(c, o);
+        });
+      }
+    } else {   // layernorm, unbiased variance
+      float acc = 0.0f;
+      for_each([&](uint64_t, const float (&a)[VEC]) {
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) acc += a[k];
+      });
+      const float mean = group_reduce<STG_THREADS>(acc, OpSum(), red, 0.0f) / const_cast_dtype<T>((float)cols);
+      float sq = 0.0f;
+      for_each([&](uint64_t, const float (&a)[VEC]) {
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) { const float d = a[k] - mean; sq = fmaf(d, d, sq); }
+      });
+      sq = group_reduce<STG_THREADS>(sq, OpSum(), red, 0.0f);
+      const float rstd = 1.0f / sqrtf(sq / const_cast_dtype<T>((float)((int64_t)cols - 1)) + const_cast_dtype<T>(p.eps));
+      const S* wp = reinterpret_cast<const S*>(p.w);
+      const S* bp = reinterpret_cast<const S*>(p.b);
+      for_each([&](uint64_t c, const float (&a)[VEC]) {
+        float o[VEC];
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) o[k] = (a[k] - mean) * rstd;
+        if (wp) {
+          const Pack<S, VEC> pk = load_pack<S, VEC>(wp + c);
+#pragma unroll
+          for (int k = 0; k < VEC; ++k) o[k] *= (float)Elem<T>::load(pk.v[k]);
+        }
+        if (bp) {
+          const Pack<S, VEC> pk = load_pack<S, VEC>(bp + c);
+#pragma unroll
+          for (int k = 0; k < VEC; ++k) o[k] += (float)Elem<T>::load(pk.v[k]);
+        }
+        write(c, o);
+      });
+    }
+  }
+}
+
+// Takes the launch when the shape suits it; returns false otherwise.
+template <typename T, int FAM>
+static bool launch_row_staged(const RowParams& p, cudaStream_t s, int sm_count, uint32_t* status) {
+  using S = typename Elem<T>::store_t;
+  constexpr int V = 16 / sizeof(S);
+  constexpr int ITEMS = 64 / V;                                   // 64 values per thread in registers
+  const uint64_t row_bytes = p.cols * sizeof(S);
+  if (row_bytes < 16384 || p.cols > (uint64_t)STG_THREADS * ITEMS * V || p.cols % V || p.rows < 2ull * sm_count) return false;
+  if ((uintptr_t)p.x % 16 || (uintptr_t)p.y % 16 || (p.w && (uintptr_t)p.w % 16) || (p.b && (uintptr_t)p.b % 16)) return false;
+  auto kern = row_staged_kernel<T, ITEMS, FAM>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 1024) != cudaSuccess) { cudaGetLastError(); return false; }
+    configured = true;
+  }
+  kern<<<(unsigned)std::min<uint64_t>(p.rows, (uint64_t)sm_count), STG_THREADS, (size_t)row_bytes, s>>>(p, status);
+  return true;
+}
+
 // ---- host-side geometry selection -----------------------------------------------------------
 template <typename T, int VEC, int ITEMS, int GROUP, int FAM>
 static void launch_row_geom(const RowParams& p, cudaStream_t s) {
@@ -367,6 +548,12 @@ static void launch_row_family(const RowParams& p, cudaStream_t s) {
   const bool vec_ok = (p.cols % V == 0) && ((uintptr_t)p.x % 16 == 0) && ((uintptr_t)p.y % 16 == 0) &&
                       (p.x2 == nullptr || FAM == FAM_CE || (uintptr_t)p.x2 % 16 == 0) &&
                       (p.w == nullptr || (uintptr_t)p.w % 16 == 0) && (p.b == nullptr || (uintptr_t)p.b % 16 == 0);
+  if constexpr ((FAM == FAM_SOFTMAX || FAM == FAM_LAYERNORM) && !std::is_same_v<T, int32_t>) {
+    // layernorm with weight / bias stays on the register kernel: its per-element weight and bias loads (L2 latency,
+    // 16 dependent iterations per thread at 512 threads) cost more than the staging gains (measured 0.70 vs 0.79 of peak)
+    const bool affine = FAM == FAM_LAYERNORM && (p.w || p.b);
+    if (vec_ok && !affine && p.sm_count > 0 && p.status && launch_row_staged<T, FAM>(p, s, p.sm_count, p.status)) return;
+  }
   if (vec_ok) launch_row_vec<T, V, FAM>(p, s);
   else launch_row_vec<T, 1, FAM>(p, s);
 }
