@@ -291,6 +291,106 @@ def f32_to_bf16_bits(x):
     return (np.ascontiguousarray(x, np.float32).view(np.uint32) >> 16).astype(np.uint16)
 
 
+class AttnRows(RowReduce):
+    """The two row kernels of the transformer block's attention on its score matrix: causal softmax over keys and the
+    softmax backward, bf16 [batch*heads*T, T] with T = 2048 (rows restart their causal position every T rows)."""
+    name = "attn_rows_causal_softmax_fwd_bwd_bf16_262144x2048"
+    metric, unit, dtype, bound = "fused-reduce GB/s (causal softmax + softmax backward)", "GB/s", "bf16", "hbm"
+    rows, cols = 8 * 16 * 2048, 2048
+
+    def __init__(self, rows=None):
+        if rows:
+            self.rows = rows
+            self.name = "attn_rows_causal_softmax_fwd_bwd_bf16_%dx%d" % (rows, self.cols)
+        self.alg_bytes_softmax = self.rows * (self.cols + 1) + self.rows * self.cols * 2     # bf16: lower triangle read, all written
+        self.alg_bytes_layernorm = self.rows * (self.cols + 1) * 2 + self.rows * self.cols * 2  # backward: triangles of p and dp read
+        self.units_per_step = (self.alg_bytes_softmax + self.alg_bytes_layernorm) / 1e9
+        self.h2d_bytes = self.rows * self.cols * 2
+        self.d2h_bytes = 2 * self.rows * self.cols * 2
+
+    def host_inputs(self, seed=1):
+        rng = np.random.default_rng(seed)
+        self.x = f32_to_bf16_bits(rng.standard_normal((self.rows, self.cols), dtype=np.float32))
+
+    def setup(self, sess):
+        from zyx_b200 import _lib as L, backend as B
+        self.sess, self.L = sess, L
+        self.host_inputs()
+        p, d = sess.pool, sess.device
+        self.bx = p.upload(self.x)
+        self.by1, _ = p.allocate(self.x.nbytes)
+        self.by2, _ = p.allocate(self.x.nbytes)
+        self.p_sm = d.create_program(B.rowreduce_desc(L.RR_SOFTMAX, L.BF16, self.rows, self.cols, causal=True, period=self.cols))
+        self.p_bw = d.create_program(B.rowreduce_desc(L.RR_SOFTMAX_BWD, L.BF16, self.rows, self.cols, causal=True, period=self.cols))
+        self.config = {"workload": self.name, "l2": "inputs (%d MiB) larger than L2 (126 MB)" % (self.x.nbytes >> 20),
+                       "ops": "causal softmax, softmax backward (upstream gradient = the scores)"}
+        self.kernel_events = []
+
+    def step(self, timed=False):
+        d = self.sess.device
+        if timed:
+            e0 = d.event_record()
+        d.launch(self.p_sm, [self.bx, self.by1])
+        if timed:
+            e1 = d.event_record()
+        d.launch(self.p_bw, [self.by1, self.bx, self.by2])
+        if timed:
+            e2 = d.event_record()
+            self.kernel_events.append((e0, e1, e2))
+
+    def roofline(self, peaks, clocks=None):
+        main, both = RowReduce.roofline(self, peaks, clocks)
+        main["kernel"] = "row kernel <bf16, causal softmax>"
+        both["softmax_bwd"] = both.pop("layernorm")
+        return main, both
+
+    def e2e_setup(self):
+        self.hy1, self.hy2 = np.empty_like(self.x), np.empty_like(self.x)
+        for a in (self.x, self.hy1, self.hy2):
+            self.sess.backend.host_register(a)
+
+    def e2e_step(self):
+        p, d = self.sess.pool, self.sess.device
+        ev = p.host_to_pool(self.x, self.bx)
+        d.launch(self.p_sm, [self.bx, self.by1], [ev])
+        d.launch(self.p_bw, [self.by1, self.bx, self.by2])
+        p.pool_to_host(self.by1, self.hy1)
+        p.pool_to_host(self.by2, self.hy2)
+
+    def check(self):
+        from oracle import oracle as zo
+        T = self.cols
+        first = min(self.rows - T, (self.rows // T // 2) * T)                    # one whole causal period
+        pick = first + np.array([0, 1, T // 2, T - 1])
+        y = np.empty((len(pick), self.cols), np.uint16)
+        g = np.empty((len(pick), self.cols), np.uint16)
+        for i, r in enumerate(pick):
+            self.sess.pool.pool_to_host(self.by1, y[i], src_offset=int(r) * self.cols * 2)
+            self.sess.pool.pool_to_host(self.by2, g[i], src_offset=int(r) * self.cols * 2)
+        want = zo.softmax(zo.BF16, self.x[first:first + T], causal=True, period=T)[pick - first]
+        want_g = zo.softmax_bwd(zo.BF16, want, self.x[pick])
+        f = lambda b: (b.astype(np.uint32) << 16).view(np.float32)
+        e1 = np.max(np.abs(f(y) - f(want)) / np.maximum(np.abs(f(want)), 1e-2 * f(want).max(1, keepdims=True)))
+        e2 = np.max(np.abs(f(g) - f(want_g)) / np.maximum(np.maximum(np.abs(f(want_g)), 1e-2 * np.abs(f(want_g)).max(1, keepdims=True)), 1e-30))
+        return float(max(e1, e2))
+
+    def cpu_run(self, rows):
+        from oracle import oracle as zo
+        x = self.x[:rows]
+        t0 = time.perf_counter()
+        p = zo.softmax(zo.BF16, x, causal=True, period=self.cols)
+        zo.softmax_bwd(zo.BF16, p, x)
+        dt = time.perf_counter() - t0
+        return rows * self.cols * 10 / 1e9 / dt, dt
+
+    def cpu_baseline(self, budget_s=12.0):
+        self.host_inputs() if not hasattr(self, "x") else None
+        v, dt = self.cpu_run(2048)
+        rows = int(min(self.rows, max(2048, 2048 * int(budget_s / max(dt, 1e-6)))))
+        v, dt = self.cpu_run(rows)
+        return v, "%d of %d rows of [%d, %d] bf16, causal softmax + backward, %.1f s" % (rows, self.rows, self.rows, self.cols, dt)
+
+
 class MlpTrain:
     """Config 4: 4 x Linear 4096 -> 16384 -> 4096 -> 16384 -> 4096, GELU between, bf16, batch 8192 per GPU, MSE against
     N(0,1) targets, AdamW lr 1e-3 wd 0.01; data parallel over the ranks with an NCCL gradient allreduce."""
@@ -596,7 +696,7 @@ class BlockTrain:
                                       "samples/s extrapolated to the full block by matmul FLOPs (%.1f GFLOP per sample)") % (E, F, H, T, flops / 1e9, dt, full / 1e9)
 
 
-WORKLOADS = {"block": BlockTrain, "simplenet": SimpleNet, "mlp": MlpTrain, "rowreduce": RowReduce, "gemm_bf16": lambda: Gemm("bf16"), "gemm_f32": lambda: Gemm("f32")}
+WORKLOADS = {"block": BlockTrain, "simplenet": SimpleNet, "mlp": MlpTrain, "rowreduce": RowReduce, "attn_rows": AttnRows, "gemm_bf16": lambda: Gemm("bf16"), "gemm_f32": lambda: Gemm("f32")}
 
 
 def make_workload(args, rank=0, world=1):
@@ -607,7 +707,7 @@ def make_workload(args, rank=0, world=1):
     if args.workload == "block":
         return BlockTrain(size=args.size, rank=rank, world=world)
     if args.size:
-        return {"rowreduce": lambda: RowReduce(rows=args.size), "gemm_bf16": lambda: Gemm("bf16", args.size),
+        return {"rowreduce": lambda: RowReduce(rows=args.size), "attn_rows": lambda: AttnRows(rows=args.size), "gemm_bf16": lambda: Gemm("bf16", args.size),
                 "gemm_f32": lambda: Gemm("f32", args.size)}[args.workload]()
     return WORKLOADS[args.workload]()
 

@@ -113,7 +113,8 @@ enum {
   ZYXB_RR_LAYERNORM = 8,  /* args: x [,weight][,bias] -> y[rows,cols] */
   ZYXB_RR_CROSS_ENTROPY = 9,      /* args: logits, labels(i32) -> per_sample[rows], mean[1] */
   ZYXB_RR_CROSS_ENTROPY_BWD = 10, /* args: logits, labels(i32) -> dlogits  ((softmax-onehot)/rows) */
-  ZYXB_RR_SOFTMAX_BWD = 11,       /* args: p, dp -> ds = p*(dp - sum(dp*p)) */
+  ZYXB_RR_SOFTMAX_BWD = 11,       /* args: p, dp -> ds = p*(dp - sum(dp*p)); with causal set, p is zero past the diagonal by
+                                     construction, so those columns of p and dp are not read and ds is written as 0 there */
   ZYXB_RR_LAYERNORM_BWD = 12,     /* args: x, dy [,weight] -> dx */
   ZYXB_RR_COLSUM = 13,            /* args: x[rows,cols] -> y[cols]  (sum over rows; bias gradient) */
   ZYXB_RR_MSE = 14,               /* args: y, t -> loss[1] = mean((y-t)^2) over rows*cols */
@@ -128,7 +129,7 @@ typedef struct {
   int32_t  correction;  /* var/std: divisor = cols - correction (zyx default 1) */
   int32_t  has_weight, has_bias;  /* layernorm affine */
   float    scale;       /* softmax: x is multiplied by scale first; 0 means 1 */
-  int32_t  causal;      /* softmax: column j of row r is masked (-inf) when j > r % period */
+  int32_t  causal;      /* softmax, softmax backward: column j of row r is masked (-inf; never read) when j > r % period */
   uint64_t period;      /* sequence length T for the causal mask */
 } zyxb_rowreduce_desc;
 

@@ -89,6 +89,29 @@ def test_softmax_scaled_causal(sess, dtype):
     assert np.all(got[np.arange(T)[None, :] > r[:, None]] == 0.0)     # masked columns are exactly zero
 
 
+@pytest.mark.parametrize("dtype", [L.F32, L.BF16])
+@pytest.mark.parametrize("T", [40, 96, 2048, 4100])
+def test_causal_softmax_forward_backward_skip_masked_columns(sess, dtype, T):
+    """Columns past the diagonal are never read: poison them with NaN bit patterns and the results must not change."""
+    rows = 2 * T
+    x, dp = rand((rows, T), dtype, 4.0), rand((rows, T), dtype)
+    masked = np.arange(T)[None, :] > (np.arange(rows) % T)[:, None]
+    p_want = zo.softmax(dtype, x, causal=True, period=T)
+    ds_want = f(zo.softmax_bwd(dtype, p_want, dp), dtype)
+    nan = np.float32(np.nan) if dtype == L.F32 else np.uint16(0x7fc0)
+    xp, dpp = x.copy(), dp.copy()
+    xp[masked], dpp[masked] = nan, nan
+    p_got = sess.softmax(dtype, xp, causal=True, period=T)
+    exact = exact_softmax(np.where(masked, -np.inf, f(x, dtype).astype(np.float64)))
+    assert_parity(f(p_got, dtype), f(p_want, dtype), exact, TOL[dtype], what="causal softmax")
+    assert np.all(f(p_got, dtype)[masked] == 0.0)
+    ds_got = f(sess.softmax_bwd(dtype, p_want, dpp, causal=True, period=T), dtype)
+    assert np.all(ds_got[masked] == 0.0)
+    # rows just under the diagonal hold one dominant probability, so dp - sum(p*dp) cancels down to the rounding noise of
+    # the f32 sum: the error is bounded relative to |dp| (order 1), not to the result, hence the absolute floor
+    assert max_rel_err(ds_got, ds_want, floor=1e-2, abs_floor=5e-3) <= TOL[dtype] * (20 if dtype == L.F32 else 1)
+
+
 @pytest.mark.parametrize("dtype", [L.F32, L.BF16, L.F16])
 @pytest.mark.parametrize("shape", [s for s in SHAPES if s[1] >= 2])
 @pytest.mark.parametrize("affine", [False, True])

@@ -4,6 +4,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <type_traits>
+
 namespace zyxb {
 
 struct bf16_t { uint16_t bits; };
@@ -108,6 +110,25 @@ __device__ __forceinline__ void store_pack_stream(S* p, const Pack<S, VEC>& v) {
   } else {
     *reinterpret_cast<Pack<S, VEC>*>(p) = v;
   }
+}
+
+// VEC accumulator values -> one pack of storage values.  bf16 truncation of a pair is a single byte permute
+// (the high halves of two f32 words); every other case converts element by element.
+template <typename T, int VEC, typename A>
+__device__ __forceinline__ Pack<typename Elem<T>::store_t, VEC> encode_pack(const A (&val)[VEC], bool rn) {
+  using S = typename Elem<T>::store_t;
+  Pack<S, VEC> pk;
+  if constexpr (std::is_same_v<T, bf16_t> && VEC % 2 == 0) {
+    if (!rn) {
+      uint32_t* w = reinterpret_cast<uint32_t*>(pk.v);
+#pragma unroll
+      for (int j = 0; j < VEC / 2; ++j) w[j] = __byte_perm(__float_as_uint(val[2 * j]), __float_as_uint(val[2 * j + 1]), 0x7632);
+      return pk;
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < VEC; ++k) pk.v[k] = Elem<T>::store(val[k], rn);
+  return pk;
 }
 
 // ---- reductions ----------------------------------------------------------------------------

@@ -163,7 +163,11 @@ int32_t build(zyxb_block* K) {
     score_view_a(d.u.gemm, H, T); head_view_b(d.u.gemm, T, E, D); head_view_c(d.u.gemm, T, E, D);
     CHK(P.launch(d, {K->p, K->dattn, K->dv}));
   }
-  CHK(P.launch(row(ZYXB_RR_SOFTMAX_BWD, dt, B * H * T, T), {K->p, K->dp, K->dp}));   // dS in place of dP; masked entries have p = 0
+  {  // dS in place of dP; masked entries have p = 0 and are skipped
+    zyxb_kernel_desc d = row(ZYXB_RR_SOFTMAX_BWD, dt, B * H * T, T);
+    d.u.rowreduce.causal = c.causal; d.u.rowreduce.period = T;
+    CHK(P.launch(d, {K->p, K->dp, K->dp}));
+  }
   {  // dQ[b,:,h,:] = dS[b,h] . k[b,:,h,:] * scale
     zyxb_kernel_desc d = gemm(dt, T, D, T, false, false, ZYXB_EPI_NONE, false, scale);
     d.u.gemm.batch = B; d.u.gemm.batch_inner = H;

@@ -42,8 +42,14 @@ struct RowParams {
   uint32_t* status; // device status word (bounded waits report here)
 };
 
+// A warp-per-row kernel with two cached inputs holds 2 x ITEMS 128-bit vectors per thread: ask for five CTAs of 128 threads
+// per SM (about 100 registers) so the packed rows are decoded per pass instead of being kept as floats at a third of the occupancy.
+constexpr int row_min_ctas(int group, int items, int fam) {
+  return (group == 32 && items == 8 && (fam == FAM_SOFTMAX_BWD || fam == FAM_LAYERNORM_BWD)) ? 5 : 1;
+}
+
 template <typename T, int VEC, int ITEMS, int GROUP, int FAM>
-__global__ void __launch_bounds__(GROUP == 32 ? 128 : GROUP) row_kernel(RowParams p) {
+__global__ void __launch_bounds__(GROUP == 32 ? 128 : GROUP, row_min_ctas(GROUP, ITEMS, FAM)) row_kernel(RowParams p) {
   using S = typename Elem<T>::store_t;
   using A = typename Elem<T>::acc_t;
   constexpr bool CACHED = ITEMS > 0;
@@ -61,33 +67,61 @@ __global__ void __launch_bounds__(GROUP == 32 ? 128 : GROUP) row_kernel(RowParam
   const uint64_t step = (uint64_t)GROUP * VEC;
   const int n_iter = CACHED ? ITEMS : (int)((cols + step - 1) / step);
 
-  A v[NI][VEC];
-  A v2[TWO_IN ? NI : 1][VEC];
+  // causal softmax (and its backward): columns past the diagonal are masked, so they are never read
+  uint64_t lim = cols;
+  if constexpr (FAM == FAM_SOFTMAX || FAM == FAM_SOFTMAX_BWD) {
+    if (p.causal) lim = min((uint64_t)(row % p.period) + 1, cols);
+  }
+
+  // the cached row stays in its storage type (16-bit rows: 8 elements per 128-bit register quad) and is decoded per pass
+  Pack<S, VEC> v[NI];
+  Pack<S, VEC> v2[TWO_IN ? NI : 1];
   (void)v2;
 
-  auto fetch = [&](const S* base, uint64_t c, A (&out)[VEC]) {
-    Pack<S, VEC> pk = load_pack_stream<S, VEC>(base + c);
+  auto fetch_raw = [&](const S* base, uint64_t c) -> Pack<S, VEC> {
+    if (c < lim) return load_pack_stream<S, VEC>(base + c);
+    Pack<S, VEC> z;
 #pragma unroll
-    for (int k = 0; k < VEC; ++k) out[k] = Elem<T>::load(pk.v[k]);
+    for (int k = 0; k < VEC; ++k) z.v[k] = S(0);
+    return z;
+  };
+  auto decode = [&](const Pack<S, VEC>& pk, A (&out)[VEC]) {
+    if constexpr (std::is_same_v<T, bf16_t> && CACHED && TWO_IN && VEC % 2 == 0) {
+      // two cached bf16 rows: the widening is volatile so that every pass repeats it (two ALU operations per pair) instead
+      // of the compiler keeping 2 x 64 widened values live across the passes and spilling them
+      const uint32_t* w = reinterpret_cast<const uint32_t*>(pk.v);
+#pragma unroll
+      for (int j = 0; j < VEC / 2; ++j) {
+        uint32_t lo, hi;
+        asm volatile("shl.b32 %0, %2, 16;\n\tand.b32 %1, %2, 0xffff0000;" : "=r"(lo), "=r"(hi) : "r"(w[j]));
+        out[2 * j] = __uint_as_float(lo);
+        out[2 * j + 1] = __uint_as_float(hi);
+      }
+    } else {
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) out[k] = Elem<T>::load(pk.v[k]);
+    }
   };
   if constexpr (CACHED) {
 #pragma unroll
     for (int it = 0; it < ITEMS; ++it) {
       const uint64_t c = ((uint64_t)it * GROUP + gl) * VEC;
       if (c < cols) {
-        fetch(xr, c, v[it]);
-        if constexpr (TWO_IN) fetch(x2r, c, v2[it]);
+        v[it] = fetch_raw(xr, c);
+        if constexpr (TWO_IN) v2[it] = fetch_raw(x2r, c);
       }
     }
   }
-  // visit every vector of the row that this thread owns: f(it, column, values[, values2])
+  // visit every vector of the row that this thread owns: f(column, values, values2)
   auto for_each = [&](auto&& f) {
     if constexpr (CACHED) {
 #pragma unroll
       for (int it = 0; it < ITEMS; ++it) {
         const uint64_t c = ((uint64_t)it * GROUP + gl) * VEC;
         if (c < cols) {
-          if constexpr (TWO_IN) f(c, v[it], v2[it]); else f(c, v[it], v[it]);
+          A a[VEC];
+          decode(v[it], a);
+          if constexpr (TWO_IN) { A a2[VEC]; decode(v2[it], a2); f(c, a, a2); } else f(c, a, a);
         }
       }
     } else {
@@ -95,18 +129,13 @@ __global__ void __launch_bounds__(GROUP == 32 ? 128 : GROUP) row_kernel(RowParam
         const uint64_t c = ((uint64_t)it * GROUP + gl) * VEC;
         if (c < cols) {
           A a[VEC], a2[VEC];
-          fetch(xr, c, a);
-          if constexpr (TWO_IN) { fetch(x2r, c, a2); f(c, a, a2); } else f(c, a, a);
+          decode(fetch_raw(xr, c), a);
+          if constexpr (TWO_IN) { decode(fetch_raw(x2r, c), a2); f(c, a, a2); } else f(c, a, a);
         }
       }
     }
   };
-  auto write = [&](S* base, uint64_t c, const A (&val)[VEC]) {
-    Pack<S, VEC> pk;
-#pragma unroll
-    for (int k = 0; k < VEC; ++k) pk.v[k] = Elem<T>::store(val[k], rn);
-    store_pack_stream<S, VEC>(base + c, pk);
-  };
+  auto write = [&](S* base, uint64_t c, const A (&val)[VEC]) { store_pack_stream<S, VEC>(base + c, encode_pack<T, VEC>(val, rn)); };
 
   // ---------------------------------------------------------------------------------------
   if constexpr (FAM == FAM_REDUCE) {
@@ -162,11 +191,99 @@ __global__ void __launch_bounds__(GROUP == 32 ? 128 : GROUP) row_kernel(RowParam
     }
   }
   // ---------------------------------------------------------------------------------------
+  else if constexpr (FAM == FAM_SOFTMAX && CACHED && !std::is_same_v<A, int32_t>) {
+    // Cached softmax / ln_softmax.  Work is decided per 128-bit vector: vectors wholly left of the causal limit take the
+    // unmasked loops, the one vector that straddles it masks per element, vectors right of it cost nothing but the store of
+    // zeros.  16-bit rows keep the exponentials of the sum pass in registers (the packed row is dead by then), so each
+    // element costs one SFU operation instead of two.
+    constexpr bool KEEP_E = sizeof(S) == 2 && GROUP <= 256;
+    constexpr float LOG2E = 1.4426950408889634f;
+    const uint32_t cols32 = (uint32_t)cols, lim32 = (uint32_t)lim;
+    const float mul = const_cast_dtype<T>(p.scale);      // 1 when unscaled: x * 1 is exact
+    float mx = -CUDART_INF_F;
+#pragma unroll
+    for (int it = 0; it < ITEMS; ++it) {
+      const uint32_t c = ((uint32_t)it * GROUP + gl) * VEC;
+      if (c < lim32) {
+        A a[VEC];
+        decode(v[it], a);
+        if (c + VEC <= lim32) {
+#pragma unroll
+          for (int k = 0; k < VEC; ++k) mx = fmaxf((float)a[k] * mul, mx);
+        } else {
+#pragma unroll
+          for (int k = 0; k < VEC; ++k) mx = (c + k < lim32) ? fmaxf((float)a[k] * mul, mx) : mx;
+        }
+      }
+    }
+    mx = group_reduce<GROUP>(mx, OpMaxF(), (float*)red, -CUDART_INF_F);
+    const float nmx = -mx * LOG2E;
+    auto ex = [&](float a) -> float {                     // exp(a*mul - mx)
+      float r;
+      asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(fmaf(a * mul, LOG2E, nmx)));
+      return r;
+    };
+    S* yr = reinterpret_cast<S*>(p.y) + row * cols;
+    // sum pass and output pass; `keep` holds the exponentials between the two (softmax only), so that the packed row is
+    // dead after the sum pass; ln_softmax re-reads the packed row and keeps nothing
+    auto finish = [&](auto keep_tag, auto log_tag) {
+      constexpr bool KEEP = decltype(keep_tag)::value, LOGF = decltype(log_tag)::value;
+      float e[KEEP ? NI : 1][VEC];
+      (void)e;
+      float s = 0.0f;
+#pragma unroll
+      for (int it = 0; it < ITEMS; ++it) {
+        const uint32_t c = ((uint32_t)it * GROUP + gl) * VEC;
+        if (c < lim32) {
+          A a[VEC];
+          decode(v[it], a);
+          const bool whole = c + VEC <= lim32;
+#pragma unroll
+          for (int k = 0; k < VEC; ++k) {
+            float t = ex((float)a[k]);
+            if (!whole) t = (c + k < lim32) ? t : 0.0f;
+            s += t;
+            if constexpr (KEEP) e[it][k] = t;
+          }
+        }
+      }
+      s = group_reduce<GROUP>(s, OpSum(), (float*)red, 0.0f);
+      const float inv = 1.0f / s, ls = LOGF ? logf(s) : 0.0f;
+      const float MASKED = LOGF ? -CUDART_INF_F : 0.0f;
+#pragma unroll
+      for (int it = 0; it < ITEMS; ++it) {
+        const uint32_t c = ((uint32_t)it * GROUP + gl) * VEC;
+        if (c < cols32) {
+          A o[VEC];
+          if (c < lim32) {
+            A a[VEC];
+            if constexpr (!KEEP) decode(v[it], a);
+            const bool whole = c + VEC <= lim32;
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) {
+              float r;
+              if constexpr (LOGF) r = ((float)a[k] * mul - mx) - ls;
+              else if constexpr (KEEP) r = e[it][k] * inv;
+              else r = ex((float)a[k]) * inv;
+              if (!whole && !(c + k < lim32)) r = MASKED;
+              o[k] = (A)r;
+            }
+          } else {
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) o[k] = (A)MASKED;
+          }
+          write(yr, c, o);
+        }
+      }
+    };
+    if (p.op == ZYXB_RR_SOFTMAX) finish(std::bool_constant<KEEP_E>(), std::false_type());
+    else finish(std::false_type(), std::true_type());
+  }
+  // ---------------------------------------------------------------------------------------
   else if constexpr (FAM == FAM_SOFTMAX || FAM == FAM_CE) {
-    // softmax, ln_softmax, cross-entropy forward/backward all start from max and sum(exp(x-max))
+    // streamed softmax / ln_softmax and cross-entropy forward/backward all start from max and sum(exp(x-max))
     const bool scaled = p.scale != 1.0f;
     const float cscale = const_cast_dtype<T>(p.scale);
-    const uint64_t lim = p.causal ? min((uint64_t)(row % p.period) + 1, cols) : cols;
     auto val = [&](float a, uint64_t c) -> float {
       if (scaled) a *= cscale;
       return c < lim ? a : -CUDART_INF_F;
@@ -267,19 +384,65 @@ __global__ void __launch_bounds__(GROUP == 32 ? 128 : GROUP) row_kernel(RowParam
     });
   }
   // ---------------------------------------------------------------------------------------
-  else if constexpr (FAM == FAM_SOFTMAX_BWD) {
-    // ds = p * (dp - sum(dp * p))
+  else if constexpr (FAM == FAM_SOFTMAX_BWD && CACHED) {
+    // ds = p * (dp - sum(dp * p)), decided per vector like the forward: past a causal diagonal p counts as 0
+    const uint32_t cols32 = (uint32_t)cols, lim32 = (uint32_t)lim;
     float acc = 0.0f;
-    for_each([&](uint64_t, const A (&a)[VEC], const A (&d)[VEC]) {
 #pragma unroll
-      for (int k = 0; k < VEC; ++k) acc = fmaf((float)a[k], (float)d[k], acc);
+    for (int it = 0; it < ITEMS; ++it) {
+      const uint32_t c = ((uint32_t)it * GROUP + gl) * VEC;
+      if (c < lim32) {
+        A a[VEC], d[VEC];
+        decode(v[it], a);
+        decode(v2[it], d);
+        if (c + VEC <= lim32) {
+#pragma unroll
+          for (int k = 0; k < VEC; ++k) acc = fmaf((float)a[k], (float)d[k], acc);
+        } else {
+#pragma unroll
+          for (int k = 0; k < VEC; ++k) acc = (c + k < lim32) ? fmaf((float)a[k], (float)d[k], acc) : acc;
+        }
+      }
+    }
+    acc = group_reduce<GROUP>(acc, OpSum(), (float*)red, 0.0f);
+    S* yr = reinterpret_cast<S*>(p.y) + row * cols;
+#pragma unroll
+    for (int it = 0; it < ITEMS; ++it) {
+      const uint32_t c = ((uint32_t)it * GROUP + gl) * VEC;
+      if (c < cols32) {
+        A o[VEC];
+        if (c < lim32) {
+          A a[VEC], d[VEC];
+          decode(v[it], a);
+          decode(v2[it], d);
+          const bool whole = c + VEC <= lim32;
+#pragma unroll
+          for (int k = 0; k < VEC; ++k) {
+            const float r = (float)a[k] * ((float)d[k] - acc);
+            o[k] = (A)((whole || c + k < lim32) ? r : 0.0f);
+          }
+        } else {
+#pragma unroll
+          for (int k = 0; k < VEC; ++k) o[k] = (A)0;
+        }
+        write(yr, c, o);
+      }
+    }
+  }
+  // ---------------------------------------------------------------------------------------
+  else if constexpr (FAM == FAM_SOFTMAX_BWD) {
+    // streamed form.  ds = p * (dp - sum(dp * p)); elements past a causal diagonal count as p = 0
+    float acc = 0.0f;
+    for_each([&](uint64_t c, const A (&a)[VEC], const A (&d)[VEC]) {
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) acc = (c + k < lim) ? fmaf((float)a[k], (float)d[k], acc) : acc;
     });
     acc = group_reduce<GROUP>(acc, OpSum(), (float*)red, 0.0f);
     S* yr = reinterpret_cast<S*>(p.y) + row * cols;
     for_each([&](uint64_t c, const A (&a)[VEC], const A (&d)[VEC]) {
       A o[VEC];
 #pragma unroll
-      for (int k = 0; k < VEC; ++k) o[k] = (A)((float)a[k] * ((float)d[k] - acc));
+      for (int k = 0; k < VEC; ++k) o[k] = (c + k < lim) ? (A)((float)a[k] * ((float)d[k] - acc)) : (A)0;
       write(yr, c, o);
     });
   }

@@ -62,9 +62,10 @@ class Session:
         rows, cols = x.shape
         return self.run(B.rowreduce_desc(L.RR_LAYERNORM_DYXHAT, dtype, rows, cols, eps=eps), [x, dy], [(x.shape, x.dtype)])[0]
 
-    def softmax_bwd(self, dtype, p, dp):
+    def softmax_bwd(self, dtype, p, dp, causal=False, period=0):
         rows, cols = p.shape
-        return self.run(B.rowreduce_desc(L.RR_SOFTMAX_BWD, dtype, rows, cols), [p, dp], [(p.shape, p.dtype)])[0]
+        return self.run(B.rowreduce_desc(L.RR_SOFTMAX_BWD, dtype, rows, cols, causal=causal, period=period), [p, dp],
+                        [(p.shape, p.dtype)])[0]
 
     def cross_entropy(self, logits, labels):
         rows, cols = logits.shape
