@@ -1,6 +1,7 @@
 // Device-side helpers shared by every kernel file: storage <-> f32 conversions that follow
 // the reference C backend (zyx/src/codegen/c.rs:452-497), vector I/O, warp/block reductions.
 #pragma once
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -24,17 +25,7 @@ __device__ __forceinline__ uint16_t f32_to_bf16(float v, bool rn) {
   }
   return (uint16_t)(b >> 16);
 }
-__device__ __forceinline__ float f16_to_f32(uint16_t h) {
-  uint32_t sign = ((uint32_t)h & 0x8000u) << 16, exp = (h >> 10) & 0x1f, man = h & 0x3ff;
-  if (exp == 0) {
-    if (man == 0) return __uint_as_float(sign);
-    // IEEE subnormal: man * 2^-24
-    float m = (float)man * 5.9604644775390625e-8f;
-    return __uint_as_float(__float_as_uint(m) | sign);
-  }
-  if (exp == 31) return __uint_as_float(sign | 0x7f800000u | (man << 13));
-  return __uint_as_float(sign | ((exp + 112) << 23) | (man << 13));
-}
+__device__ __forceinline__ float f16_to_f32(uint16_t h) { return __half2float(__ushort_as_half(h)); }   // exact, IEEE subnormals
 __device__ __forceinline__ uint16_t f32_to_f16(float v, bool rn) {
   uint32_t f = __float_as_uint(v);
   uint32_t sign = (f >> 16) & 0x8000u, exp = (f >> 23) & 0xff, man = f & 0x7fffffu;
@@ -112,24 +103,85 @@ __device__ __forceinline__ void store_pack_stream(S* p, const Pack<S, VEC>& v) {
   }
 }
 
-// VEC accumulator values -> one pack of storage values.  bf16 truncation of a pair is a single byte permute
-// (the high halves of two f32 words); every other case converts element by element.
-template <typename T, int VEC, typename A>
-__device__ __forceinline__ Pack<typename Elem<T>::store_t, VEC> encode_pack(const A (&val)[VEC], bool rn) {
+// The register image of VEC storage elements, held as 32-bit words whenever the byte count allows, so that a 128-bit
+// load of eight 16-bit values stays four registers until a pass widens it (two ALU operations per bf16 pair) and a store
+// packs a truncated bf16 pair with one byte permute (the high halves of two f32 words).
+template <typename T, int VEC> struct RawVec {
   using S = typename Elem<T>::store_t;
-  Pack<S, VEC> pk;
-  if constexpr (std::is_same_v<T, bf16_t> && VEC % 2 == 0) {
-    if (!rn) {
-      uint32_t* w = reinterpret_cast<uint32_t*>(pk.v);
+  using A = typename Elem<T>::acc_t;
+  static constexpr int BYTES = VEC * (int)sizeof(S);
+  static constexpr bool WORDS = BYTES % 4 == 0;
+  static constexpr int NW = WORDS ? BYTES / 4 : 1;
+  uint32_t w[NW];
+
+  __device__ __forceinline__ void zero() {
 #pragma unroll
-      for (int j = 0; j < VEC / 2; ++j) w[j] = __byte_perm(__float_as_uint(val[2 * j]), __float_as_uint(val[2 * j + 1]), 0x7632);
-      return pk;
+    for (int i = 0; i < NW; ++i) w[i] = 0u;
+  }
+  __device__ __forceinline__ void load_stream(const S* p) {
+    if constexpr (BYTES == 16) {
+      const uint4 u = __ldcs(reinterpret_cast<const uint4*>(p));
+      w[0] = u.x; w[1] = u.y; w[2] = u.z; w[3] = u.w;
+    } else if constexpr (WORDS) {
+#pragma unroll
+      for (int i = 0; i < NW; ++i) w[i] = reinterpret_cast<const uint32_t*>(p)[i];
+    } else {
+      w[0] = (uint32_t)*reinterpret_cast<const uint16_t*>(p);
     }
   }
+  __device__ __forceinline__ void store_stream(S* p) const {
+    if constexpr (BYTES == 16) {
+      __stcs(reinterpret_cast<uint4*>(p), make_uint4(w[0], w[1], w[2], w[3]));
+    } else if constexpr (WORDS) {
 #pragma unroll
-  for (int k = 0; k < VEC; ++k) pk.v[k] = Elem<T>::store(val[k], rn);
-  return pk;
-}
+      for (int i = 0; i < NW; ++i) reinterpret_cast<uint32_t*>(p)[i] = w[i];
+    } else {
+      *reinterpret_cast<uint16_t*>(p) = (uint16_t)w[0];
+    }
+  }
+  __device__ __forceinline__ void decode(A (&out)[VEC]) const {
+    if constexpr (sizeof(S) == 4) {
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) {
+        if constexpr (std::is_same_v<A, float>) out[k] = __uint_as_float(w[k]); else out[k] = (A)w[k];
+      }
+    } else if constexpr (WORDS) {
+#pragma unroll
+      for (int j = 0; j < NW; ++j) {
+        if constexpr (std::is_same_v<T, bf16_t>) {
+          out[2 * j] = __uint_as_float(w[j] << 16);
+          out[2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
+        } else {
+          out[2 * j] = Elem<T>::load((uint16_t)(w[j] & 0xffffu));
+          out[2 * j + 1] = Elem<T>::load((uint16_t)(w[j] >> 16));
+        }
+      }
+    } else {
+      out[0] = Elem<T>::load((uint16_t)w[0]);
+    }
+  }
+  __device__ __forceinline__ void encode(const A (&val)[VEC], bool rn) {
+    if constexpr (sizeof(S) == 4) {
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) {
+        if constexpr (std::is_same_v<A, float>) w[k] = __float_as_uint(val[k]); else w[k] = (uint32_t)val[k];
+      }
+    } else if constexpr (WORDS) {
+      if constexpr (std::is_same_v<T, bf16_t>) {
+        if (!rn) {
+#pragma unroll
+          for (int j = 0; j < NW; ++j) w[j] = __byte_perm(__float_as_uint(val[2 * j]), __float_as_uint(val[2 * j + 1]), 0x7632);
+          return;
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < NW; ++j)
+        w[j] = (uint32_t)Elem<T>::store(val[2 * j], rn) | ((uint32_t)Elem<T>::store(val[2 * j + 1], rn) << 16);
+    } else {
+      w[0] = (uint32_t)Elem<T>::store(val[0], rn);
+    }
+  }
+};
 
 // ---- reductions ----------------------------------------------------------------------------
 struct OpSum { template <typename A> __device__ __forceinline__ A operator()(A a, A b) const { return a + b; } };

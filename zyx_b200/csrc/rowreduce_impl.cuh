@@ -73,35 +73,18 @@ __global__ void __launch_bounds__(GROUP == 32 ? 128 : GROUP, row_min_ctas(GROUP,
     if (p.causal) lim = min((uint64_t)(row % p.period) + 1, cols);
   }
 
-  // the cached row stays in its storage type (16-bit rows: 8 elements per 128-bit register quad) and is decoded per pass
-  Pack<S, VEC> v[NI];
-  Pack<S, VEC> v2[TWO_IN ? NI : 1];
+  // the cached row stays in its storage form (16-bit rows: eight elements per four registers) and is widened per pass
+  using Raw = RawVec<T, VEC>;
+  Raw v[NI];
+  Raw v2[TWO_IN ? NI : 1];
   (void)v2;
 
-  auto fetch_raw = [&](const S* base, uint64_t c) -> Pack<S, VEC> {
-    if (c < lim) return load_pack_stream<S, VEC>(base + c);
-    Pack<S, VEC> z;
-#pragma unroll
-    for (int k = 0; k < VEC; ++k) z.v[k] = S(0);
-    return z;
+  auto fetch_raw = [&](const S* base, uint64_t c) -> Raw {
+    Raw r;
+    if (c < lim) r.load_stream(base + c); else r.zero();
+    return r;
   };
-  auto decode = [&](const Pack<S, VEC>& pk, A (&out)[VEC]) {
-    if constexpr (std::is_same_v<T, bf16_t> && CACHED && TWO_IN && VEC % 2 == 0) {
-      // two cached bf16 rows: the widening is volatile so that every pass repeats it (two ALU operations per pair) instead
-      // of the compiler keeping 2 x 64 widened values live across the passes and spilling them
-      const uint32_t* w = reinterpret_cast<const uint32_t*>(pk.v);
-#pragma unroll
-      for (int j = 0; j < VEC / 2; ++j) {
-        uint32_t lo, hi;
-        asm volatile("shl.b32 %0, %2, 16;\n\tand.b32 %1, %2, 0xffff0000;" : "=r"(lo), "=r"(hi) : "r"(w[j]));
-        out[2 * j] = __uint_as_float(lo);
-        out[2 * j + 1] = __uint_as_float(hi);
-      }
-    } else {
-#pragma unroll
-      for (int k = 0; k < VEC; ++k) out[k] = Elem<T>::load(pk.v[k]);
-    }
-  };
+  auto decode = [&](const Raw& r, A (&out)[VEC]) { r.decode(out); };
   if constexpr (CACHED) {
 #pragma unroll
     for (int it = 0; it < ITEMS; ++it) {
@@ -135,7 +118,11 @@ __global__ void __launch_bounds__(GROUP == 32 ? 128 : GROUP, row_min_ctas(GROUP,
       }
     }
   };
-  auto write = [&](S* base, uint64_t c, const A (&val)[VEC]) { store_pack_stream<S, VEC>(base + c, encode_pack<T, VEC>(val, rn)); };
+  auto write = [&](S* base, uint64_t c, const A (&val)[VEC]) {
+    Raw r;
+    r.encode(val, rn);
+    r.store_stream(base + c);
+  };
 
   // ---------------------------------------------------------------------------------------
   if constexpr (FAM == FAM_REDUCE) {
@@ -194,42 +181,75 @@ __global__ void __launch_bounds__(GROUP == 32 ? 128 : GROUP, row_min_ctas(GROUP,
   else if constexpr (FAM == FAM_SOFTMAX && CACHED && !std::is_same_v<A, int32_t>) {
     // Cached softmax / ln_softmax.  Work is decided per 128-bit vector: vectors wholly left of the causal limit take the
     // unmasked loops, the one vector that straddles it masks per element, vectors right of it cost nothing but the store of
-    // zeros.  16-bit rows keep the exponentials of the sum pass in registers (the packed row is dead by then), so each
-    // element costs one SFU operation instead of two.
-    constexpr bool KEEP_E = sizeof(S) == 2 && GROUP <= 256;
+    // zeros.  The exponentials are computed twice (sum pass, output pass) rather than kept: 64 more live registers per
+    // thread cost more in occupancy than the second SFU operation does.
     constexpr float LOG2E = 1.4426950408889634f;
+    constexpr bool HALF2 = sizeof(S) == 2 && VEC % 2 == 0;
     const uint32_t cols32 = (uint32_t)cols, lim32 = (uint32_t)lim;
-    const float mul = const_cast_dtype<T>(p.scale);      // 1 when unscaled: x * 1 is exact
+    const float mul = const_cast_dtype<T>(p.scale);      // 1 when unscaled
     float mx = -CUDART_INF_F;
+    if (mul > 0.0f) {
+      // x -> fl(x * mul) is monotone for mul > 0, so max(x * mul) = max(x) * mul exactly; 16-bit rows take the maximum of
+      // whole vectors on the packed pairs
+      uint32_t pm = std::is_same_v<T, bf16_t> ? 0xff80ff80u : 0xfc00fc00u;   // (-inf, -inf)
+      (void)pm;
 #pragma unroll
-    for (int it = 0; it < ITEMS; ++it) {
-      const uint32_t c = ((uint32_t)it * GROUP + gl) * VEC;
-      if (c < lim32) {
-        A a[VEC];
-        decode(v[it], a);
-        if (c + VEC <= lim32) {
+      for (int it = 0; it < ITEMS; ++it) {
+        const uint32_t c = ((uint32_t)it * GROUP + gl) * VEC;
+        if (c < lim32) {
+          if (c + VEC <= lim32) {
+            if constexpr (HALF2) {
 #pragma unroll
-          for (int k = 0; k < VEC; ++k) mx = fmaxf((float)a[k] * mul, mx);
-        } else {
+              for (int j = 0; j < Raw::NW; ++j) {
+                if constexpr (std::is_same_v<T, bf16_t>) asm("max.bf16x2 %0, %0, %1;" : "+r"(pm) : "r"(v[it].w[j]));
+                else asm("max.f16x2 %0, %0, %1;" : "+r"(pm) : "r"(v[it].w[j]));
+              }
+            } else {
+              A a[VEC];
+              decode(v[it], a);
+#pragma unroll
+              for (int k = 0; k < VEC; ++k) mx = fmaxf((float)a[k], mx);
+            }
+          } else {
+            A a[VEC];
+            decode(v[it], a);
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) mx = (c + k < lim32) ? fmaxf((float)a[k], mx) : mx;
+          }
+        }
+      }
+      if constexpr (HALF2) {
+        mx = fmaxf(mx, fmaxf((float)Elem<T>::load((uint16_t)(pm & 0xffffu)), (float)Elem<T>::load((uint16_t)(pm >> 16))));
+      }
+      mx *= mul;
+    } else {
+#pragma unroll
+      for (int it = 0; it < ITEMS; ++it) {
+        const uint32_t c = ((uint32_t)it * GROUP + gl) * VEC;
+        if (c < lim32) {
+          A a[VEC];
+          decode(v[it], a);
 #pragma unroll
           for (int k = 0; k < VEC; ++k) mx = (c + k < lim32) ? fmaxf((float)a[k] * mul, mx) : mx;
         }
       }
     }
     mx = group_reduce<GROUP>(mx, OpMaxF(), (float*)red, -CUDART_INF_F);
-    const float nmx = -mx * LOG2E;
-    auto ex = [&](float a) -> float {                     // exp(a*mul - mx)
-      float r;
-      asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(fmaf(a * mul, LOG2E, nmx)));
-      return r;
-    };
+    const float nmx = -mx * LOG2E, m2 = mul * LOG2E;
     S* yr = reinterpret_cast<S*>(p.y) + row * cols;
-    // sum pass and output pass; `keep` holds the exponentials between the two (softmax only), so that the packed row is
-    // dead after the sum pass; ln_softmax re-reads the packed row and keeps nothing
-    auto finish = [&](auto keep_tag, auto log_tag) {
-      constexpr bool KEEP = decltype(keep_tag)::value, LOGF = decltype(log_tag)::value;
-      float e[KEEP ? NI : 1][VEC];
-      (void)e;
+    // sum pass and output pass.  UNIT: mul == 1, the product is skipped.  16-bit rows fold mul into the exponent's scale
+    // (one FMA per element; the argument moves by an ulp, far inside their tolerance), f32 rows round x*mul first as the
+    // reference does.
+    auto finish = [&](auto log_tag, auto unit_tag) {
+      constexpr bool LOGF = decltype(log_tag)::value, UNIT = decltype(unit_tag)::value;
+      auto ex = [&](float a) -> float {                     // exp(a*mul - mx)
+        float arg, r;
+        if constexpr (sizeof(S) == 2) arg = fmaf(a, m2, nmx);
+        else if constexpr (UNIT) arg = fmaf(a, LOG2E, nmx);
+        else arg = fmaf(a * mul, LOG2E, nmx);
+        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(arg));
+        return r;
+      };
       float s = 0.0f;
 #pragma unroll
       for (int it = 0; it < ITEMS; ++it) {
@@ -237,13 +257,12 @@ __global__ void __launch_bounds__(GROUP == 32 ? 128 : GROUP, row_min_ctas(GROUP,
         if (c < lim32) {
           A a[VEC];
           decode(v[it], a);
-          const bool whole = c + VEC <= lim32;
+          if (c + VEC <= lim32) {
 #pragma unroll
-          for (int k = 0; k < VEC; ++k) {
-            float t = ex((float)a[k]);
-            if (!whole) t = (c + k < lim32) ? t : 0.0f;
-            s += t;
-            if constexpr (KEEP) e[it][k] = t;
+            for (int k = 0; k < VEC; ++k) s += ex((float)a[k]);
+          } else {
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) s += (c + k < lim32) ? ex((float)a[k]) : 0.0f;
           }
         }
       }
@@ -257,13 +276,12 @@ __global__ void __launch_bounds__(GROUP == 32 ? 128 : GROUP, row_min_ctas(GROUP,
           A o[VEC];
           if (c < lim32) {
             A a[VEC];
-            if constexpr (!KEEP) decode(v[it], a);
+            decode(v[it], a);
             const bool whole = c + VEC <= lim32;
 #pragma unroll
             for (int k = 0; k < VEC; ++k) {
               float r;
-              if constexpr (LOGF) r = ((float)a[k] * mul - mx) - ls;
-              else if constexpr (KEEP) r = e[it][k] * inv;
+              if constexpr (LOGF) r = ((UNIT ? (float)a[k] : (float)a[k] * mul) - mx) - ls;
               else r = ex((float)a[k]) * inv;
               if (!whole && !(c + k < lim32)) r = MASKED;
               o[k] = (A)r;
@@ -276,8 +294,9 @@ __global__ void __launch_bounds__(GROUP == 32 ? 128 : GROUP, row_min_ctas(GROUP,
         }
       }
     };
-    if (p.op == ZYXB_RR_SOFTMAX) finish(std::bool_constant<KEEP_E>(), std::false_type());
-    else finish(std::false_type(), std::true_type());
+    const bool unit = mul == 1.0f && sizeof(S) == 4;       // 16-bit rows have one variant
+    if (p.op == ZYXB_RR_SOFTMAX) { if (unit) finish(std::false_type(), std::true_type()); else finish(std::false_type(), std::false_type()); }
+    else { if (unit) finish(std::true_type(), std::true_type()); else finish(std::true_type(), std::false_type()); }
   }
   // ---------------------------------------------------------------------------------------
   else if constexpr (FAM == FAM_SOFTMAX || FAM == FAM_CE) {
