@@ -122,6 +122,9 @@ template <typename T, int VEC> struct RawVec {
     if constexpr (BYTES == 16) {
       const uint4 u = __ldcs(reinterpret_cast<const uint4*>(p));
       w[0] = u.x; w[1] = u.y; w[2] = u.z; w[3] = u.w;
+    } else if constexpr (BYTES == 8) {
+      const uint2 u = __ldcs(reinterpret_cast<const uint2*>(p));
+      w[0] = u.x; w[1] = u.y;
     } else if constexpr (WORDS) {
 #pragma unroll
       for (int i = 0; i < NW; ++i) w[i] = reinterpret_cast<const uint32_t*>(p)[i];
@@ -129,9 +132,23 @@ template <typename T, int VEC> struct RawVec {
       w[0] = (uint32_t)*reinterpret_cast<const uint16_t*>(p);
     }
   }
+  __device__ __forceinline__ void load(const S* p) {
+    if constexpr (BYTES == 16) {
+      const uint4 u = *reinterpret_cast<const uint4*>(p);
+      w[0] = u.x; w[1] = u.y; w[2] = u.z; w[3] = u.w;
+    } else {
+      load_stream(p);
+    }
+  }
+  __device__ __forceinline__ void store(S* p) const {
+    if constexpr (BYTES == 16) *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+    else store_stream(p);
+  }
   __device__ __forceinline__ void store_stream(S* p) const {
     if constexpr (BYTES == 16) {
       __stcs(reinterpret_cast<uint4*>(p), make_uint4(w[0], w[1], w[2], w[3]));
+    } else if constexpr (BYTES == 8) {
+      __stcs(reinterpret_cast<uint2*>(p), make_uint2(w[0], w[1]));
     } else if constexpr (WORDS) {
 #pragma unroll
       for (int i = 0; i < NW; ++i) reinterpret_cast<uint32_t*>(p)[i] = w[i];

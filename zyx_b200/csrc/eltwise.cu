@@ -34,18 +34,22 @@ __global__ void __launch_bounds__(256) eltwise_kernel(EwParams p) {
   constexpr bool BINARY = (OP == ZYXB_EW_ADD || OP == ZYXB_EW_SUB || OP == ZYXB_EW_MUL || OP == ZYXB_EW_RELU_BWD ||
                            OP == ZYXB_EW_GELU_BWD || OP == ZYXB_EW_MSE_BWD);
   for (uint64_t i = (uint64_t)blockIdx.x * 256 + threadIdx.x; i < p.n_vec; i += (uint64_t)gridDim.x * 256) {
-    Pack<S, VEC> pa = load_pack_stream<S, VEC>(a + i * VEC), pb;
-    if constexpr (BINARY) pb = load_pack_stream<S, VEC>(b + i * VEC);
+    RawVec<T, VEC> pa, pb;
+    pa.load_stream(a + i * VEC);
+    if constexpr (BINARY) pb.load_stream(b + i * VEC);
     if constexpr (OP == ZYXB_EW_BIAS_ADD) {
-      if constexpr (VEC > 1) pb = load_pack<S, VEC>(b + (i * VEC) % p.cols);   // cols % VEC == 0 checked by the host
-      else pb.v[0] = b[i % p.cols];
+      if constexpr (VEC > 1) pb.load(b + (i * VEC) % p.cols);   // cols % VEC == 0 checked by the host
+      else pb.load(b + i % p.cols);
     }
-    Pack<SO, VEC> out;
+    typename Elem<T>::acc_t xa[VEC], za[VEC];
+    pa.decode(xa);
+    if constexpr (BINARY || OP == ZYXB_EW_BIAS_ADD) pb.decode(za);
+    typename Elem<TO>::acc_t ro[VEC];
 #pragma unroll
     for (int k = 0; k < VEC; ++k) {
-      const float x = (float)Elem<T>::load(pa.v[k]);
+      const float x = (float)xa[k];
       float z = 0.0f, r;
-      if constexpr (BINARY || OP == ZYXB_EW_BIAS_ADD) z = (float)Elem<T>::load(pb.v[k]);
+      if constexpr (BINARY || OP == ZYXB_EW_BIAS_ADD) z = (float)za[k];
       if constexpr (OP == ZYXB_EW_RELU) r = relu_ref(x);
       else if constexpr (OP == ZYXB_EW_GELU) r = gelu_ref<T>(x, gc);
       else if constexpr (OP == ZYXB_EW_ADD || OP == ZYXB_EW_BIAS_ADD) r = x + z;
@@ -59,9 +63,11 @@ __global__ void __launch_bounds__(256) eltwise_kernel(EwParams p) {
       else if constexpr (OP == ZYXB_EW_SIGMOID) { const float e = exp_for<T>(x); r = e / (e + 1.0f); }
       else if constexpr (OP == ZYXB_EW_EXP) r = exp_for<T>(x);
       else r = x;  // CAST
-      out.v[k] = Elem<TO>::store((typename Elem<TO>::acc_t)r, rn);
+      ro[k] = (typename Elem<TO>::acc_t)r;
     }
-    store_pack_stream<SO, VEC>(y + i * VEC, out);
+    RawVec<TO, VEC> out;
+    out.encode(ro, rn);
+    out.store_stream(y + i * VEC);
   }
 }
 

@@ -111,18 +111,18 @@ __global__ void __launch_bounds__(OPT_THREADS) optim_kernel(OptTable tab, OptHyp
   const bool read_state = use_m && !hy.first;
   // all loads of the chunk are issued before any store: p, m and v are read and written through
   // pointers the compiler must assume may alias, so a load placed after a store would wait for it
-  Pack<S, VEC> pp[OPT_UNROLL], pg[OPT_UNROLL], pm[OPT_UNROLL], pv[OPT_UNROLL];
+  RawVec<T, VEC> pp[OPT_UNROLL], pg[OPT_UNROLL], pm[OPT_UNROLL], pv[OPT_UNROLL];
   bool whole[OPT_UNROLL];
 #pragma unroll
   for (int u = 0; u < OPT_UNROLL; ++u) {
     const uint64_t i = base + ((uint64_t)u * OPT_THREADS + threadIdx.x) * VEC;
     whole[u] = i + VEC <= numel;
     if (whole[u]) {
-      pp[u] = load_pack<S, VEC>(p + i);
-      pg[u] = load_pack_stream<S, VEC>(g + i);
+      pp[u].load(p + i);
+      pg[u].load_stream(g + i);
       if (read_state) {
-        pm[u] = load_pack<S, VEC>(m + i);
-        if constexpr (ALGO != ZYXB_OPT_SGD) pv[u] = load_pack<S, VEC>(v + i);
+        pm[u].load(m + i);
+        if constexpr (ALGO != ZYXB_OPT_SGD) pv[u].load(v + i);
       }
     }
   }
@@ -130,17 +130,24 @@ __global__ void __launch_bounds__(OPT_THREADS) optim_kernel(OptTable tab, OptHyp
   for (int u = 0; u < OPT_UNROLL; ++u) {
     const uint64_t i = base + ((uint64_t)u * OPT_THREADS + threadIdx.x) * VEC;
     if (whole[u]) {
+      float fp[VEC], fg[VEC], fm[VEC], fv[VEC];
+      pp[u].decode(fp);
+      pg[u].decode(fg);
 #pragma unroll
-      for (int k = 0; k < VEC; ++k) {
-        float fp = (float)Elem<T>::load(pp[u].v[k]), fg = (float)Elem<T>::load(pg[u].v[k]);
-        float fm = read_state ? (float)Elem<T>::load(pm[u].v[k]) : 0.0f;
-        float fv = (read_state && ALGO != ZYXB_OPT_SGD) ? (float)Elem<T>::load(pv[u].v[k]) : 0.0f;
-        opt_update<T, ALGO>(fp, fg, fm, fv, h, rn);
-        pp[u].v[k] = Elem<T>::store(fp, rn); pm[u].v[k] = Elem<T>::store(fm, rn);
-        if constexpr (ALGO != ZYXB_OPT_SGD) pv[u].v[k] = Elem<T>::store(fv, rn);
+      for (int k = 0; k < VEC; ++k) { fm[k] = 0.0f; fv[k] = 0.0f; }
+      if (read_state) {
+        pm[u].decode(fm);
+        if constexpr (ALGO != ZYXB_OPT_SGD) pv[u].decode(fv);
       }
-      store_pack<S, VEC>(p + i, pp[u]);
-      if (use_m) { store_pack<S, VEC>(m + i, pm[u]); if constexpr (ALGO != ZYXB_OPT_SGD) store_pack<S, VEC>(v + i, pv[u]); }
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) opt_update<T, ALGO>(fp[k], fg[k], fm[k], fv[k], h, rn);
+      pp[u].encode(fp, rn);
+      pp[u].store(p + i);
+      if (use_m) {
+        pm[u].encode(fm, rn);
+        pm[u].store(m + i);
+        if constexpr (ALGO != ZYXB_OPT_SGD) { pv[u].encode(fv, rn); pv[u].store(v + i); }
+      }
     } else {
       // ragged tail of a tensor whose length is not a multiple of VEC
       for (uint64_t j = i; j < numel && j < i + VEC; ++j) {

@@ -42,18 +42,24 @@ __global__ void __launch_bounds__(32 * COLSUM_WARPS) colsum_partial_kernel(const
   if (live) {
     uint64_t r = r0 + warp;
     for (; r + 3 * COLSUM_WARPS < r1; r += 4 * COLSUM_WARPS) {   // four independent loads in flight per thread
-      Pack<S, VEC> pk[4];
+      RawVec<T, VEC> pk[4];
 #pragma unroll
-      for (int u = 0; u < 4; ++u) pk[u] = load_pack_stream<S, VEC>(x + (r + u * COLSUM_WARPS) * cols + c);
+      for (int u = 0; u < 4; ++u) pk[u].load_stream(x + (r + u * COLSUM_WARPS) * cols + c);
 #pragma unroll
-      for (int u = 0; u < 4; ++u)
+      for (int u = 0; u < 4; ++u) {
+        typename Elem<T>::acc_t a[VEC];
+        pk[u].decode(a);
 #pragma unroll
-        for (int k = 0; k < VEC; ++k) acc[k] += (float)Elem<T>::load(pk[u].v[k]);
+        for (int k = 0; k < VEC; ++k) acc[k] += (float)a[k];
+      }
     }
     for (; r < r1; r += COLSUM_WARPS) {
-      Pack<S, VEC> pk = load_pack_stream<S, VEC>(x + r * cols + c);
+      RawVec<T, VEC> pk;
+      pk.load_stream(x + r * cols + c);
+      typename Elem<T>::acc_t a[VEC];
+      pk.decode(a);
 #pragma unroll
-      for (int k = 0; k < VEC; ++k) acc[k] += (float)Elem<T>::load(pk.v[k]);
+      for (int k = 0; k < VEC; ++k) acc[k] += (float)a[k];
     }
   }
 #pragma unroll
@@ -177,9 +183,14 @@ __global__ void __launch_bounds__(256) mse_partial_kernel(const typename Elem<T>
   __shared__ float red[32];
   float acc = 0.0f;
   for (uint64_t i = (uint64_t)blockIdx.x * 256 + threadIdx.x; i < n_vec; i += (uint64_t)gridDim.x * 256) {
-    Pack<S, VEC> a = load_pack_stream<S, VEC>(y + i * VEC), b = load_pack_stream<S, VEC>(t + i * VEC);
+    RawVec<T, VEC> a, b;
+    a.load_stream(y + i * VEC);
+    b.load_stream(t + i * VEC);
+    typename Elem<T>::acc_t fa[VEC], fb[VEC];
+    a.decode(fa);
+    b.decode(fb);
 #pragma unroll
-    for (int k = 0; k < VEC; ++k) { const float d = (float)Elem<T>::load(a.v[k]) - (float)Elem<T>::load(b.v[k]); acc = fmaf(d, d, acc); }
+    for (int k = 0; k < VEC; ++k) { const float d = (float)fa[k] - (float)fb[k]; acc = fmaf(d, d, acc); }
   }
   acc = group_reduce<256>(acc, OpSum(), red, 0.0f);
   if (threadIdx.x == 0) partial[blockIdx.x] = acc;

@@ -390,14 +390,16 @@ __global__ void __launch_bounds__(GROUP == 32 ? 128 : GROUP, row_min_ctas(GROUP,
 #pragma unroll
       for (int k = 0; k < VEC; ++k) o[k] = (A)(((float)a[k] - mean) * rstd);
       if (wp) {
-        Pack<S, VEC> pk = load_pack<S, VEC>(wp + c);
+        Raw pk; A wv[VEC];
+        pk.load(wp + c); pk.decode(wv);
 #pragma unroll
-        for (int k = 0; k < VEC; ++k) o[k] = (A)((float)o[k] * (float)Elem<T>::load(pk.v[k]));
+        for (int k = 0; k < VEC; ++k) o[k] = (A)((float)o[k] * (float)wv[k]);
       }
       if (bp) {
-        Pack<S, VEC> pk = load_pack<S, VEC>(bp + c);
+        Raw pk; A bv[VEC];
+        pk.load(bp + c); pk.decode(bv);
 #pragma unroll
-        for (int k = 0; k < VEC; ++k) o[k] = (A)((float)o[k] + (float)Elem<T>::load(pk.v[k]));
+        for (int k = 0; k < VEC; ++k) o[k] = (A)((float)o[k] + (float)bv[k]);
       }
       write(yr, c, o);
     });
@@ -478,11 +480,10 @@ __global__ void __launch_bounds__(GROUP == 32 ? 128 : GROUP, row_min_ctas(GROUP,
     const float mean = group_reduce<GROUP>(acc, OpSum(), (float*)red, 0.0f) / n;
     float sq = 0.0f, sg = 0.0f, sgd = 0.0f;
     for_each([&](uint64_t c, const A (&a)[VEC], const A (&d)[VEC]) {
-      float wv[VEC];
+      A wv[VEC];
       if (wp) {
-        Pack<S, VEC> pk = load_pack<S, VEC>(wp + c);
-#pragma unroll
-        for (int k = 0; k < VEC; ++k) wv[k] = (float)Elem<T>::load(pk.v[k]);
+        Raw pk;
+        pk.load(wp + c); pk.decode(wv);
       }
 #pragma unroll
       for (int k = 0; k < VEC; ++k) {
@@ -499,11 +500,10 @@ __global__ void __launch_bounds__(GROUP == 32 ? 128 : GROUP, row_min_ctas(GROUP,
     const float k1 = sg / n, k2 = sgd / ((n - 1.0f) * s2);
     S* yr = reinterpret_cast<S*>(p.y) + row * cols;
     for_each([&](uint64_t c, const A (&a)[VEC], const A (&d)[VEC]) {
-      float wv[VEC];
+      A wv[VEC];
       if (wp) {
-        Pack<S, VEC> pk = load_pack<S, VEC>(wp + c);
-#pragma unroll
-        for (int k = 0; k < VEC; ++k) wv[k] = (float)Elem<T>::load(pk.v[k]);
+        Raw pk;
+        pk.load(wp + c); pk.decode(wv);
       }
       A o[VEC];
 #pragma unroll
@@ -587,9 +587,9 @@ __global__ void __launch_bounds__(STG_THREADS, 1) row_staged_kernel(RowParams p,
     for (int it = 0; it < ITEMS; ++it) {
       const uint64_t c = ((uint64_t)it * STG_THREADS + tid) * VEC;
       if (c < cols) {
-        const Pack<S, VEC> pk = *reinterpret_cast<const Pack<S, VEC>*>(stg_smem + c * sizeof(S));
-#pragma unroll
-        for (int k = 0; k < VEC; ++k) v[it][k] = (float)Elem<T>::load(pk.v[k]);
+        RawVec<T, VEC> pk;
+        pk.load(reinterpret_cast<const S*>(stg_smem + c * sizeof(S)));
+        pk.decode(v[it]);
       }
     }
     __syncthreads();                                   // every thread has its part of the row in registers
@@ -604,10 +604,9 @@ __global__ void __launch_bounds__(STG_THREADS, 1) row_staged_kernel(RowParams p,
       }
     };
     auto write = [&](uint64_t c, const float (&o)[VEC]) {
-      Pack<S, VEC> pk;
-#pragma unroll
-      for (int k = 0; k < VEC; ++k) pk.v[k] = Elem<T>::store(o[k], rn);
-      store_pack_stream<S, VEC>(yr + c, pk);
+      RawVec<T, VEC> pk;
+      pk.encode(o, rn);
+      pk.store_stream(yr + c);
     };
     if constexpr (FAM == FAM_SOFTMAX) {
       const uint64_t lim = p.causal ? min((uint64_t)(row % p.period) + 1, cols) : cols;
@@ -662,14 +661,16 @@ __global__ void __launch_bounds__(STG_THREADS, 1) row_staged_kernel(RowParams p,
 #pragma unroll
         for (int k = 0; k < VEC; ++k) o[k] = (a[k] - mean) * rstd;
         if (wp) {
-          const Pack<S, VEC> pk = load_pack<S, VEC>(wp + c);
+          RawVec<T, VEC> pk; float wv[VEC];
+          pk.load(wp + c); pk.decode(wv);
 #pragma unroll
-          for (int k = 0; k < VEC; ++k) o[k] *= (float)Elem<T>::load(pk.v[k]);
+          for (int k = 0; k < VEC; ++k) o[k] *= wv[k];
         }
         if (bp) {
-          const Pack<S, VEC> pk = load_pack<S, VEC>(bp + c);
+          RawVec<T, VEC> pk; float bv[VEC];
+          pk.load(bp + c); pk.decode(bv);
 #pragma unroll
-          for (int k = 0; k < VEC; ++k) o[k] += (float)Elem<T>::load(pk.v[k]);
+          for (int k = 0; k < VEC; ++k) o[k] += bv[k];
         }
         write(c, o);
       });
