@@ -90,6 +90,7 @@ class RowReduce:
     name = "rowreduce_softmax_layernorm_f32_8192x32768"
     metric, unit, dtype, bound = "fused-reduce GB/s (row softmax + row layernorm)", "GB/s", "f32", "hbm"
     rows, cols = 8192, 32768
+    traffic_rows, traffic_bytes = 2048, 268.50e6 + 209.61e6       # softmax launch at [2048, 32768]: read + written
 
     def __init__(self, rows=None):
         if rows:
@@ -138,8 +139,13 @@ class RowReduce:
         t_sm, t_ln = float(np.mean(sm)), float(np.mean(ln))
         ach = self.alg_bytes_softmax / (t_sm * 1e-3) / 1e9
         ach_ln = self.alg_bytes_layernorm / (t_ln * 1e-3) / 1e9
-        return ({"bound": "hbm", "kernel": "row_kernel<f32, softmax>", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                 "frac": ach / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"], "ms_per_launch": t_sm},
+        # DRAM bytes of one softmax launch: dram__bytes_read + write of an ncu capture of a smaller case of the same kernel,
+        # scaled by rows (traffic grows in proportion to the rows processed)
+        traffic = self.rows / self.traffic_rows * self.traffic_bytes
+        return ({"bound": "hbm", "kernel": "row_staged_kernel<f32, softmax>", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                 "frac": ach / peaks["hbm_gbs"], "traffic": traffic,
+                 "traffic_source": "ncu capture at %d rows scaled by rows" % self.traffic_rows,
+                 "peak_source": peaks["source"], "ms_per_launch": t_sm},
                 {"softmax": {"ms": t_sm, "GB/s": ach, "frac": ach / peaks["hbm_gbs"]},
                  "layernorm": {"ms": t_ln, "GB/s": ach_ln, "frac": ach_ln / peaks["hbm_gbs"]}})
 
@@ -297,6 +303,7 @@ class AttnRows(RowReduce):
     name = "attn_rows_causal_softmax_fwd_bwd_bf16_262144x2048"
     metric, unit, dtype, bound = "fused-reduce GB/s (causal softmax + softmax backward)", "GB/s", "bf16", "hbm"
     rows, cols = 8 * 16 * 2048, 2048
+    traffic_rows, traffic_bytes = 65536, 138.48e6 + 210.46e6      # causal softmax launch at [65536, 2048]: read + written
 
     def __init__(self, rows=None):
         if rows:
@@ -399,6 +406,7 @@ class MlpTrain:
     unit, dtype, bound = "samples/s", "bf16", "tensor"
 
     def __init__(self, size=0, standard=False, rank=0, world=1):
+        self.full_size = not size
         if size:
             self.batch = size
         self.standard, self.rank, self.world = standard, rank, world
@@ -474,7 +482,9 @@ class MlpTrain:
         ach = self.gemm_flops / (gemm_ms * 1e-3) / 1e12
         n_gemm = sum(1 for k in kind if k // 100 == 2)
         return ({"bound": "tensor", "kernel": "gemm_tc_kernel (tcgen05), %d launches per step" % n_gemm, "achieved": ach,
-                 "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s", "frac": ach / peaks["bf16_tflops_sustained"], "traffic": None,
+                 "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s", "frac": ach / peaks["bf16_tflops_sustained"],
+                 # dram__bytes_read + write of the step's eleven matmul launches (one-pass ncu capture at full size), mean per launch
+                 "traffic": 1.2508e9 if self.full_size else None,
                  "peak_source": peaks["source"] + " (sustained: the kernel runs inside a long step)", "ms_per_launch": gemm_ms / n_gemm,
                  "flops_per_step": self.gemm_flops},
                 {"ms_per_step_by_kind": {k: round(v, 4) for k, v in groups.items()}})
