@@ -144,6 +144,16 @@ enum { ZYXB_EPI_NONE = 0, ZYXB_EPI_BIAS = 1, ZYXB_EPI_BIAS_RELU = 2, ZYXB_EPI_BI
        /* C = alpha * A.B + z, z shaped and strided like C (a residual / gradient accumulation) */
        ZYXB_EPI_ADD = 6 };
 
+/* Causal (lower-triangular) structure a matcher may declare when an operand or the result is known to be
+ * masked_fill(tril(..) == 0, ..) (zyx-nn/src/multi_head_attention.rs:208-211).  Declaring it never changes a value that
+ * is defined; it lets the kernel skip work:
+ *   OUT_LOWER  m == n; entries of C above the diagonal (col > row) are not needed: tiles wholly above it are neither
+ *              computed nor written, their memory keeps whatever it held (scores = q.k^T, dP = dO.v^T)
+ *   A_LOWER    m == k; the stored A [m,k] is zero above its diagonal: the sum over k stops at the row (P.v, dS.k)
+ *   AT_LOWER   m == k, trans_a; the stored A [k,m] is zero above its diagonal, so column m of it starts at row m: the sum
+ *              over k starts there (dV = P^T.dO, dK = dS^T.q) */
+enum { ZYXB_TRI_NONE = 0, ZYXB_TRI_OUT_LOWER = 1, ZYXB_TRI_A_LOWER = 2, ZYXB_TRI_AT_LOWER = 3 };
+
 typedef struct {
   int32_t  dtype;        /* element type of A, B, C: bf16 / f16 / f32 / i32; accumulation is
                             f32 (i32 for integers), as reduce_acc_dtype (reduce_ops.rs:52-60) */
@@ -161,6 +171,7 @@ typedef struct {
   uint64_t batch_inner;     /* 0 or 1: none.  Otherwise the launch runs batch * batch_inner matrices; matrix
                                z uses offset (z / batch_inner) * stride_x + (z % batch_inner) * stride_x_inner */
   int64_t  stride_a_inner, stride_b_inner, stride_c_inner;
+  int32_t  tri;             /* ZYXB_TRI_*: causal structure of square attention operands, per matrix of the batch */
 } zyxb_gemm_desc;
 /* args: a, b [,bias | ,z] -> c [,preact] */
 

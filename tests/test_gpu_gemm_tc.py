@@ -148,3 +148,43 @@ def test_residual_add_epilogue(sess):
     got = sess.gemm(L.BF16, a, w, tb=True, bias=r, epi=L.EPI_ADD)
     acc = f(a, L.BF16).astype(np.float64) @ f(w, L.BF16).astype(np.float64).T + f(r, L.BF16)
     assert max_rel_err(f(got, L.BF16), acc, floor=0.1) <= TOL_BF16
+
+
+# ---- causal (lower-triangular) structure ---------------------------------------------------------------
+@pytest.mark.parametrize("dtype", [L.BF16, L.F16])
+@pytest.mark.parametrize("T,d", [(128, 64), (384, 128), (1024, 128), (520, 72)])
+def test_tc_triangular_modes(sess, dtype, T, d):
+    """The three declarations a causal attention makes: results equal the plain matmul wherever they are defined."""
+    batch = 3
+    q, k = rand((batch, T, d), dtype), rand((batch, T, d), dtype)
+    # OUT_LOWER: scores = q.k^T; entries on and below the diagonal are defined, tiles wholly above it keep the buffer's content
+    sentinel = np.full((batch, T, T), 0x4321, np.uint16)
+    got = sess.gemm(dtype, q, k, tb=True, alpha=0.125, tri=L.TRI_OUT_LOWER, out_init=sentinel)
+    want = zo.gemm(dtype, q, k, tb=True, alpha=0.125)
+    lower = np.tril(np.ones((T, T), bool))
+    assert max_rel_err(np.where(lower, f(got, dtype), 0.0), np.where(lower, f(want, dtype), 0.0), floor=0.1) <= TOL_BF16
+    if T >= 384:   # a 128 x 256 tile wholly above the diagonal exists and was left alone
+        assert np.all(got[:, :128, 256:] == 0x4321)
+    # A_LOWER: p.v with p zero above the diagonal (k range cut per row tile)
+    p = np.where(lower, rand((batch, T, T), dtype), np.uint16(0)).astype(np.uint16)
+    nan = np.uint16(0x7fc0 if dtype == L.BF16 else 0x7e00)
+    v = rand((batch, T, d), dtype)
+    want = zo.gemm(dtype, p, v)
+    assert err(sess.gemm(dtype, p, v, tri=L.TRI_A_LOWER), want, dtype) <= TOL_BF16
+    if T % 128 == 0 and T > 128:   # whole k-blocks right of the diagonal tile are not even read: NaN there changes nothing
+        poisoned = p.copy()
+        for r0 in range(0, T, 128):
+            poisoned[:, r0:r0 + 128, r0 + 128:] = nan
+        assert err(sess.gemm(dtype, poisoned, v, tri=L.TRI_A_LOWER), want, dtype) <= TOL_BF16
+    # AT_LOWER: p^T.dO (k range starts at the row tile)
+    want = zo.gemm(dtype, p, v, ta=True)
+    assert err(sess.gemm(dtype, p, v, ta=True, tri=L.TRI_AT_LOWER), want, dtype) <= TOL_BF16
+    assert sess.device.status() == 0
+
+
+def test_triangular_declarations_are_validated(sess):
+    from zyx_b200 import backend as B
+    for kw in (dict(m=128, n=256, k=64, tri=L.TRI_OUT_LOWER), dict(m=128, n=64, k=256, tri=L.TRI_A_LOWER),
+               dict(m=128, n=64, k=128, tri=L.TRI_AT_LOWER), dict(m=128, n=64, k=128, tri=L.TRI_A_LOWER, trans_a=True), dict(m=8, n=8, k=8, tri=7)):
+        with pytest.raises(B.BackendError):
+            sess.device.create_program(B.gemm_desc(L.BF16, **kw))

@@ -21,6 +21,7 @@ KIND_ROWREDUCE, KIND_GEMM, KIND_ELTWISE, KIND_OPTIM = 1, 2, 3, 4
 (RR_SUM, RR_MAX, RR_MIN, RR_MEAN, RR_VAR, RR_STD, RR_SOFTMAX, RR_LN_SOFTMAX, RR_LAYERNORM, RR_CROSS_ENTROPY,
  RR_CROSS_ENTROPY_BWD, RR_SOFTMAX_BWD, RR_LAYERNORM_BWD, RR_COLSUM, RR_MSE, RR_LAYERNORM_DYXHAT) = range(16)
 EPI_NONE, EPI_BIAS, EPI_BIAS_RELU, EPI_BIAS_GELU, EPI_MUL_RELU_GRAD, EPI_MUL_GELU_GRAD, EPI_ADD = range(7)
+TRI_NONE, TRI_OUT_LOWER, TRI_A_LOWER, TRI_AT_LOWER = range(4)
 (EW_RELU, EW_GELU, EW_ADD, EW_SUB, EW_MUL, EW_SCALE, EW_RELU_BWD, EW_GELU_BWD, EW_MSE_BWD, EW_CAST, EW_TANH, EW_SIGMOID,
  EW_EXP, EW_BIAS_ADD) = range(14)
 OPT_SGD, OPT_ADAM, OPT_ADAMW = range(3)
@@ -54,7 +55,7 @@ class GemmDesc(C.Structure):
                 ("trans_a", C.c_int32), ("trans_b", C.c_int32), ("stride_a", C.c_int64), ("stride_b", C.c_int64),
                 ("stride_c", C.c_int64), ("epilogue", C.c_int32), ("store_preact", C.c_int32), ("alpha", C.c_float),
                 ("lda", C.c_uint64), ("ldb", C.c_uint64), ("ldc", C.c_uint64), ("batch_inner", C.c_uint64),
-                ("stride_a_inner", C.c_int64), ("stride_b_inner", C.c_int64), ("stride_c_inner", C.c_int64)]
+                ("stride_a_inner", C.c_int64), ("stride_b_inner", C.c_int64), ("stride_c_inner", C.c_int64), ("tri", C.c_int32)]
 
 
 class EltwiseDesc(C.Structure):

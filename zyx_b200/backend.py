@@ -292,7 +292,7 @@ def rowreduce_desc(op, dtype, rows, cols, eps=0.0, correction=1, has_weight=Fals
 
 def gemm_desc(dtype, m, n, k, batch=1, trans_a=False, trans_b=False, stride_a=None, stride_b=None, stride_c=None,
               epilogue=L.EPI_NONE, store_preact=False, alpha=0.0, lda=0, ldb=0, ldc=0, batch_inner=0, stride_a_inner=0,
-              stride_b_inner=0, stride_c_inner=0):
+              stride_b_inner=0, stride_c_inner=0, tri=0):
     d = L.KernelDesc()
     d.kind = L.KIND_GEMM
     g = d.u.gemm
@@ -304,6 +304,7 @@ def gemm_desc(dtype, m, n, k, batch=1, trans_a=False, trans_b=False, stride_a=No
     g.epilogue, g.store_preact, g.alpha = epilogue, int(store_preact), alpha
     g.lda, g.ldb, g.ldc, g.batch_inner = lda, ldb, ldc, batch_inner
     g.stride_a_inner, g.stride_b_inner, g.stride_c_inner = stride_a_inner, stride_b_inner, stride_c_inner
+    g.tri = tri
     return d
 
 

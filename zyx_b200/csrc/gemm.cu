@@ -20,6 +20,12 @@ int validate_gemm(const zyxb_gemm_desc& d, std::string& err) {
   if (d.stride_a < 0 || d.stride_b < 0 || d.stride_c < 0 || d.stride_a_inner < 0 || d.stride_b_inner < 0 || d.stride_c_inner < 0) {
     err = "gemm: negative batch stride"; return ZYXB_ERR_KERNEL_COMPILATION;
   }
+  if (d.tri < ZYXB_TRI_NONE || d.tri > ZYXB_TRI_AT_LOWER) { err = "gemm: unknown triangular mode"; return ZYXB_ERR_KERNEL_COMPILATION; }
+  if (d.tri == ZYXB_TRI_OUT_LOWER && d.m != d.n) { err = "gemm: a lower-triangular result needs m == n"; return ZYXB_ERR_KERNEL_COMPILATION; }
+  if ((d.tri == ZYXB_TRI_A_LOWER || d.tri == ZYXB_TRI_AT_LOWER) && d.m != d.k) { err = "gemm: a lower-triangular A needs m == k"; return ZYXB_ERR_KERNEL_COMPILATION; }
+  if ((d.tri == ZYXB_TRI_A_LOWER && d.trans_a) || (d.tri == ZYXB_TRI_AT_LOWER && !d.trans_a)) {
+    err = "gemm: A_LOWER takes A stored [m,k], AT_LOWER takes A stored [k,m]"; return ZYXB_ERR_KERNEL_COMPILATION;
+  }
   if (d.batch > 1 && d.stride_c == 0) { err = "gemm: batches of C must not overlap (stride_c is 0)"; return ZYXB_ERR_KERNEL_COMPILATION; }
   if (d.batch_inner > 1 && d.stride_c_inner == 0) { err = "gemm: inner batches of C must not overlap"; return ZYXB_ERR_KERNEL_COMPILATION; }
   if (d.batch * (d.batch_inner ? d.batch_inner : 1) > 65535) { err = "gemm: more than 65535 matrices in one launch"; return ZYXB_ERR_KERNEL_COMPILATION; }
@@ -41,7 +47,7 @@ int launch_gemm(const zyxb_gemm_desc& d, void* const* args, const uint64_t* arg_
   GemmParams p{};
   p.m = d.m; p.n = d.n; p.k = d.k; p.batch = d.batch;
   p.batch_inner = d.batch_inner ? d.batch_inner : 1;
-  p.trans_a = d.trans_a ? 1 : 0; p.trans_b = d.trans_b ? 1 : 0; p.epilogue = d.epilogue;
+  p.trans_a = d.trans_a ? 1 : 0; p.trans_b = d.trans_b ? 1 : 0; p.epilogue = d.epilogue; p.tri = d.tri;
   const uint64_t a_rows = p.trans_a ? d.k : d.m, a_cols = p.trans_a ? d.m : d.k;
   const uint64_t b_rows = p.trans_b ? d.n : d.k, b_cols = p.trans_b ? d.k : d.n;
   p.lda = d.lda ? d.lda : a_cols; p.ldb = d.ldb ? d.ldb : b_cols; p.ldc = d.ldc ? d.ldc : d.n;

@@ -17,6 +17,7 @@ struct GemmParams {
   int64_t stride_a_inner, stride_b_inner, stride_c_inner;
   int trans_a, trans_b;                   // A stored [k,m] / B stored [n,k]
   int epilogue;
+  int tri;                                // ZYXB_TRI_*
   float alpha;
   int rn;
   bool vec_a, vec_b;

@@ -53,6 +53,7 @@ struct TcParams {
   uint32_t* status;
   uint32_t* tile_counter;     // zeroed before the launch; CTAs draw tile indices from it
   int dynamic_tiles;          // 1: draw tiles from the counter; 0: CTA i takes tiles i, i + grid, ...
+  int tri;                    // ZYXB_TRI_*: tiles above the diagonal are skipped / the k range of a tile is cut at it
 };
 
 // ---- PTX wrappers ------------------------------------------------------------------------------
@@ -216,6 +217,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
     tm = first_m + in_group % rows_in_group;
     tn = in_group / rows_in_group;
   };
+  // causal structure: is the tile wholly above the diagonal of a lower-triangular result, and which k-blocks of a
+  // lower-triangular A (or of its transpose) can be non-zero for the rows of this tile
+  auto tile_skipped = [&](uint32_t tm, uint32_t tn) { return p.tri == ZYXB_TRI_OUT_LOWER && tn * BN > tm * TC_BM + (TC_BM - 1); };
+  auto k_range = [&](uint32_t tm, uint32_t& kb0, uint32_t& kb1) {
+    kb0 = 0; kb1 = k_blocks;
+    if (p.tri == ZYXB_TRI_A_LOWER) kb1 = min(k_blocks, ((tm + 1) * TC_BM + TC_BK - 1) / TC_BK);
+    else if (p.tri == ZYXB_TRI_AT_LOWER) kb0 = min(k_blocks - 1, (tm * TC_BM) / TC_BK);
+  };
   // consumer side of the tile queue (MMA issuer and every epilogue thread keep their own cursor)
   uint32_t tq_slot = 0, tq_phase = 0;
   auto next_tile = [&](uint32_t code) -> uint32_t {
@@ -238,19 +247,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
       while (ok) {
         // publish the tile (a slot is free once the MMA issuer and all epilogue threads have read it)
         if (!mbar_wait(tq_empty(tq_slot), tq_phase ^ 1, abort_flag, p.status, TC_ERR_PRODUCER)) { ok = false; break; }
-        uint32_t t = t_next;
-        if (t >= total_tiles) t = TILE_NONE;
-        else t_next = p.dynamic_tiles ? atomicAdd(p.tile_counter, 1u) : t + gridDim.x;
+        uint32_t t, bz = 0, tm = 0, tn = 0;
+        for (;;) {   // draw until a tile that has work (tiles above a causal diagonal are never published)
+          t = t_next;
+          if (t >= total_tiles) { t = TILE_NONE; break; }
+          t_next = p.dynamic_tiles ? atomicAdd(p.tile_counter, 1u) : t + gridDim.x;
+          tile_coords(t, bz, tm, tn);
+          if (!tile_skipped(tm, tn)) break;
+        }
         tile_q[tq_slot] = t;
         mbar_arrive(tq_full(tq_slot));
         if (++tq_slot == TQ) { tq_slot = 0; tq_phase ^= 1; }
         if (t == TILE_NONE) break;
-        uint32_t bz, tm, tn;
-        tile_coords(t, bz, tm, tn);
+        uint32_t kb0, kb1;
+        k_range(tm, kb0, kb1);
         const int zo = (int)(bz / p.batch_inner), zi = (int)(bz % p.batch_inner);
         const int zao = p.a_batched & 1 ? zo : 0, zai = p.a_batched & 2 ? zi : 0;
         const int zbo = p.b_batched & 1 ? zo : 0, zbi = p.b_batched & 2 ? zi : 0;
-        for (uint32_t kb = 0; kb < k_blocks; ++kb) {
+        for (uint32_t kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1, abort_flag, p.status, TC_ERR_PRODUCER)) { ok = false; break; }
           const uint32_t a_dst = base + stage * SM::STAGE_BYTES, b_dst = a_dst + SM::A_BYTES;
           mbar_expect_tx(full_bar(stage), SM::STAGE_BYTES);
@@ -291,11 +305,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
       uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
       bool ok = true;
       while (ok) {
-        if (next_tile(TC_ERR_MMA) == TILE_NONE) break;
+        const uint32_t t = next_tile(TC_ERR_MMA);
+        if (t == TILE_NONE) break;
+        uint32_t bz, tm, tn, kb0, kb1;
+        tile_coords(t, bz, tm, tn);
+        k_range(tm, kb0, kb1);
         if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1, abort_flag, p.status, TC_ERR_MMA)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (uint32_t kb = 0; kb < k_blocks; ++kb) {
+        for (uint32_t kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(full_bar(stage), phase, abort_flag, p.status, TC_ERR_MMA)) { ok = false; break; }
           tc_fence_after();
           const uint32_t a_addr = base + stage * SM::STAGE_BYTES, b_addr = a_addr + SM::A_BYTES;
@@ -306,7 +324,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
                                         : make_smem_desc(a_addr + kk * (TC_UMMA_K * 2), 16, 1024);
             const uint64_t bdesc = B_MN ? make_smem_desc(b_addr + kk * (TC_UMMA_K * 128), 64 * TC_BK * 2, 1024)
                                         : make_smem_desc(b_addr + kk * (TC_UMMA_K * 2), 16, 1024);
-            umma_f16(d_tmem, adesc, bdesc, idesc, (kb | (uint32_t)kk) != 0 ? 1u : 0u);
+            umma_f16(d_tmem, adesc, bdesc, idesc, (kb != kb0 || kk != 0) ? 1u : 0u);
           }
           umma_commit(empty_bar(stage));                 // slot is free once these MMAs have read it
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -532,13 +550,13 @@ int launch_gemm_tc(const GemmParams& p, int dtype, const LaunchCtx& lc, std::str
   tp.batch_inner = (uint32_t)p.batch_inner; tp.ldc = (uint32_t)p.ldc; tp.stride_c_inner = p.stride_c_inner;
   tp.tiles_m = (uint32_t)((p.m + TC_BM - 1) / TC_BM); tp.tiles_n = (uint32_t)((p.n + bn - 1) / bn);
   tp.stride_c = p.stride_c; tp.alpha = p.alpha; tp.epilogue = p.epilogue; tp.rn = p.rn; tp.is_bf16 = bf16 ? 1 : 0;
-  tp.status = lc.status_word;
+  tp.status = lc.status_word; tp.tri = p.tri;
   // tile counters live in the words after the status word, used in rotation and zeroed in stream order
   // While a collective may be running beside the matmul (a communicator exists) some SMs are not available to
   // the persistent grid; drawing tiles from a counter lets the CTAs that do run share the work evenly.  Alone on
   // the GPU the fixed assignment is marginally faster (no atomic per tile).
   static const char* dyn_env = getenv("ZYXB_DYNAMIC_TILES");
-  tp.dynamic_tiles = dyn_env ? (dyn_env[0] == '1') : (lc.overlap_hint ? 1 : 0);
+  tp.dynamic_tiles = dyn_env ? (dyn_env[0] == '1') : ((lc.overlap_hint || p.tri != ZYXB_TRI_NONE) ? 1 : 0);   // causal tiles differ in cost
   tp.tile_counter = lc.status_word + 8 + (*lc.launch_counter % 48);
   if (tp.dynamic_tiles && cudaMemsetAsync(tp.tile_counter, 0, sizeof(uint32_t), lc.stream) != cudaSuccess) {
     err = "gemm: tile counter reset failed"; return ZYXB_ERR_KERNEL_LAUNCH;

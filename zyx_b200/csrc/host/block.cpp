@@ -96,6 +96,7 @@ int32_t build(zyxb_block* K) {
     zyxb_kernel_desc d = gemm(dt, T, T, D, false, true, ZYXB_EPI_NONE, false, scale);
     d.u.gemm.batch = B; d.u.gemm.batch_inner = H;
     head_view_a(d.u.gemm, T, E, D); head_view_b(d.u.gemm, T, E, D); score_view_c(d.u.gemm, H, T);
+    if (c.causal) d.u.gemm.tri = ZYXB_TRI_OUT_LOWER;   // the softmax never reads above the diagonal
     CHK(P.launch(d, {K->q, K->k, K->s}));
   }
   {  // softmax over keys, masked above the diagonal when causal
@@ -107,6 +108,7 @@ int32_t build(zyxb_block* K) {
     zyxb_kernel_desc d = gemm(dt, T, D, T, false, false);
     d.u.gemm.batch = B; d.u.gemm.batch_inner = H;
     score_view_a(d.u.gemm, H, T); head_view_b(d.u.gemm, T, E, D); head_view_c(d.u.gemm, T, E, D);
+    if (c.causal) d.u.gemm.tri = ZYXB_TRI_A_LOWER;     // p is zero above the diagonal
     CHK(P.launch(d, {K->p, K->v, K->attn}));
   }
   CHK(linear(K->attn, P_WO, P_BO, K->o, E, E, ZYXB_EPI_BIAS, 0));
@@ -155,12 +157,14 @@ int32_t build(zyxb_block* K) {
     zyxb_kernel_desc d = gemm(dt, T, T, D, false, true);
     d.u.gemm.batch = B; d.u.gemm.batch_inner = H;
     head_view_a(d.u.gemm, T, E, D); head_view_b(d.u.gemm, T, E, D); score_view_c(d.u.gemm, H, T);
+    if (c.causal) d.u.gemm.tri = ZYXB_TRI_OUT_LOWER;
     CHK(P.launch(d, {K->dattn, K->v, K->dp}));
   }
   {  // dV[b,:,h,:] = p[b,h]^T . dattn[b,:,h,:]
     zyxb_kernel_desc d = gemm(dt, T, D, T, true, false);
     d.u.gemm.batch = B; d.u.gemm.batch_inner = H;
     score_view_a(d.u.gemm, H, T); head_view_b(d.u.gemm, T, E, D); head_view_c(d.u.gemm, T, E, D);
+    if (c.causal) d.u.gemm.tri = ZYXB_TRI_AT_LOWER;
     CHK(P.launch(d, {K->p, K->dattn, K->dv}));
   }
   {  // dS in place of dP; masked entries have p = 0 and are skipped
@@ -172,8 +176,10 @@ int32_t build(zyxb_block* K) {
     zyxb_kernel_desc d = gemm(dt, T, D, T, false, false, ZYXB_EPI_NONE, false, scale);
     d.u.gemm.batch = B; d.u.gemm.batch_inner = H;
     score_view_a(d.u.gemm, H, T); head_view_b(d.u.gemm, T, E, D); head_view_c(d.u.gemm, T, E, D);
+    if (c.causal) d.u.gemm.tri = ZYXB_TRI_A_LOWER;     // dS is zero above the diagonal
     CHK(P.launch(d, {K->dp, K->k, K->dq}));
     d.u.gemm.trans_a = 1;   // dK[b,:,h,:] = dS[b,h]^T . q[b,:,h,:] * scale
+    if (c.causal) d.u.gemm.tri = ZYXB_TRI_AT_LOWER;
     CHK(P.launch(d, {K->dp, K->q, K->dk}));
   }
   CHK(linear_param_grads(K->dv, K->x, P_WV, P_BV, E, E));

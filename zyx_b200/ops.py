@@ -23,12 +23,15 @@ class Session:
     def close(self):
         self.backend.deinitialize()
 
-    def run(self, desc, inputs, out_specs):
-        """inputs: host arrays; out_specs: [(shape, np dtype)] -> list of host arrays."""
+    def run(self, desc, inputs, out_specs, out_init=None):
+        """inputs: host arrays; out_specs: [(shape, np dtype)] -> list of host arrays.  out_init: host array the first
+        output buffer holds before the launch (for kernels that leave part of their output untouched)."""
         prog = self.device.create_program(desc)
         in_bufs = [self.pool.upload(a) for a in inputs]
         out_bufs = [self.pool.allocate(max(int(np.prod(s)) * np.dtype(t).itemsize, 1))[0] for s, t in out_specs]
         try:
+            if out_init is not None:
+                self.pool.sync_events([self.pool.host_to_pool(np.ascontiguousarray(out_init), out_bufs[0])])
             self.device.launch(prog, in_bufs + out_bufs)
             return [self.pool.download(b, s, t) for b, (s, t) in zip(out_bufs, out_specs)]
         finally:
@@ -92,16 +95,16 @@ class Session:
         return self.run(B.eltwise_desc(op, dtype, a.size, p0=p0, dtype_out=dtype_out, cols=cols), ins, [(a.shape, od)])[0]
 
     # ---- matmul --------------------------------------------------------------------------------
-    def gemm(self, dtype, a, b, ta=False, tb=False, bias=None, epi=L.EPI_NONE, alpha=0.0, want_preact=False):
+    def gemm(self, dtype, a, b, ta=False, tb=False, bias=None, epi=L.EPI_NONE, alpha=0.0, want_preact=False, tri=0, out_init=None):
         batch = a.shape[0] if a.ndim == 3 else 1
         m, k = (a.shape[-1], a.shape[-2]) if ta else (a.shape[-2], a.shape[-1])
         n = b.shape[-2] if tb else b.shape[-1]
         shape = (batch, m, n) if a.ndim == 3 else (m, n)
         d = B.gemm_desc(dtype, m, n, k, batch=batch, trans_a=ta, trans_b=tb, stride_b=(0 if b.ndim == 2 else k * n),
-                        epilogue=epi, store_preact=want_preact, alpha=alpha)
+                        epilogue=epi, store_preact=want_preact, alpha=alpha, tri=tri)
         ins = [a, b] + ([bias] if bias is not None else [])      # bias [n], or z shaped like the result for MUL_*_GRAD
         outs = [(shape, a.dtype)] * (2 if want_preact else 1)
-        r = self.run(d, ins, outs)
+        r = self.run(d, ins, outs, out_init=out_init)
         return (r[0], r[1]) if want_preact else r[0]
 
     # ---- optimizers (in place on the host arrays, like the oracle's) ------------------------------
