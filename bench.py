@@ -398,6 +398,93 @@ class AttnRows(RowReduce):
         return v, "%d of %d rows of [%d, %d] bf16, causal softmax + backward, %.1f s" % (rows, self.rows, self.rows, self.cols, dt)
 
 
+class AttentionFwd:
+    """Fused causal self-attention forward at config 5's shape: q, k, v bf16 [8, 2048, 16*128], N(0,1) seeded."""
+    metric, unit, dtype, bound = "fused attention forward TFLOP/s (causal, executed FLOPs)", "TFLOP/s", "bf16", "tensor"
+    B, T, H, D = 8, 2048, 16, 128
+
+    def __init__(self, size=0):
+        if size:
+            self.B = size
+        self.name = "attention_fwd_causal_bf16_b%d_h%d_t%d_d%d" % (self.B, self.H, self.T, self.D)
+        n_t = self.T // 128
+        self.flops = 4.0 * 128 * 128 * self.D * (n_t * (n_t + 1) // 2) * self.B * self.H     # the tiles on and below the diagonal
+        self.flops_dense = 4.0 * self.T * self.T * self.D * self.B * self.H
+        self.units_per_step = self.flops / 1e12
+        self.h2d_bytes = 3 * self.B * self.T * self.H * self.D * 2
+        self.d2h_bytes = self.B * self.T * self.H * self.D * 2
+
+    def host_inputs(self):
+        rng = np.random.default_rng(5)
+        shape = (self.B, self.T, self.H * self.D)
+        self.q, self.k, self.v = (f32_to_bf16_bits(rng.standard_normal(shape, dtype=np.float32)) for _ in range(3))
+
+    def setup(self, sess):
+        from zyx_b200 import _lib as L, backend as B
+        self.sess = sess
+        self.host_inputs()
+        p, d = sess.pool, sess.device
+        self.bq, self.bk, self.bv = p.upload(self.q), p.upload(self.k), p.upload(self.v)
+        self.bo, _ = p.allocate(self.q.nbytes)
+        self.blse, _ = p.allocate(self.B * self.H * self.T * 4)
+        self.prog = d.create_program(B.attention_desc(L.BF16, self.B, self.H, self.T, self.D, causal=True))
+        self.config = {"workload": self.name, "l2": "L2 flushed (256 MB memset) before every timed launch",
+                       "flops": "executed: 128 x 128 tiles on and below the diagonal; dense equivalent %.0f GFLOP" % (self.flops_dense / 1e9)}
+        self.kernel_events = []
+
+    def step(self, timed=False):
+        d = self.sess.device
+        d.flush_l2()
+        e0 = d.event_record() if timed else None
+        d.launch(self.prog, [self.bq, self.bk, self.bv, self.bo, self.blse])
+        if timed:
+            self.kernel_events.append((e0, d.event_record()))
+
+    def roofline(self, peaks, clocks=None):
+        d = self.sess.device
+        ms = [d.elapsed_ms(a, b) for a, b in self.kernel_events]
+        t = float(np.mean(ms))
+        ach = self.flops / (t * 1e-3) / 1e12
+        return ({"bound": "tensor", "kernel": "attn_fwd_kernel (tcgen05)", "achieved": ach, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                 "frac": ach / peaks["bf16_tflops"], "traffic": None, "peak_source": peaks["source"], "ms_per_launch": t,
+                 "tflops_dense_equivalent": self.flops_dense / (t * 1e-3) / 1e12}, {"attention": {"ms": t, "TFLOP/s": ach}})
+
+    def e2e_setup(self):
+        self.ho = np.empty_like(self.q)
+        for a in (self.q, self.k, self.v, self.ho):
+            self.sess.backend.host_register(a)
+
+    def e2e_step(self):
+        p, d = self.sess.pool, self.sess.device
+        evs = [p.host_to_pool(a, b) for a, b in ((self.q, self.bq), (self.k, self.bk), (self.v, self.bv))]
+        d.launch(self.prog, [self.bq, self.bk, self.bv, self.bo, self.blse], evs)
+        p.pool_to_host(self.bo, self.ho)
+
+    def check(self):
+        from oracle import models as zm, oracle as zo
+        rows = 256                                            # the first 256 queries of one head of one batch: causal, so self-contained
+        o = np.empty((rows, self.D), np.uint16)
+        for r in range(rows):
+            self.sess.pool.pool_to_host(self.bo, o[r], src_offset=(r * self.H * self.D) * 2)
+        sl = lambda a: np.ascontiguousarray(a[:1, :rows, :self.D])
+        want, _, _ = zm.attention(zo.BF16, sl(self.q), sl(self.k), sl(self.v), 1, True)
+        f = lambda b: (b.astype(np.uint32) << 16).view(np.float32)
+        w = f(want.reshape(rows, self.D))
+        return float(np.max(np.abs(f(o) - w) / np.maximum(np.abs(w), np.abs(w).max(1, keepdims=True))))
+
+    def cpu_baseline(self, budget_s=12.0):
+        from oracle import models as zm, oracle as zo
+        self.host_inputs() if not hasattr(self, "q") else None
+        heads = 2
+        sl = lambda a: np.ascontiguousarray(a[:1, :, :heads * self.D])
+        t0 = time.perf_counter()
+        zm.attention(zo.BF16, sl(self.q), sl(self.k), sl(self.v), heads, True)
+        dt = time.perf_counter() - t0
+        n_t = self.T // 128
+        fl = 4.0 * 128 * 128 * self.D * (n_t * (n_t + 1) // 2) * heads
+        return fl / dt / 1e12, "%d of %d (batch, head) pairs, composed scores -> softmax -> P.V (plus a float64 check), %.1f s" % (heads, self.B * self.H, dt)
+
+
 class MlpTrain:
     """Config 4: 4 x Linear 4096 -> 16384 -> 4096 -> 16384 -> 4096, GELU between, bf16, batch 8192 per GPU, MSE against
     N(0,1) targets, AdamW lr 1e-3 wd 0.01; data parallel over the ranks with an NCCL gradient allreduce."""
@@ -714,7 +801,7 @@ class BlockTrain:
                                       "samples/s extrapolated to the full block by matmul FLOPs (%.1f GFLOP per sample)") % (E, F, H, T, flops / 1e9, dt, full / 1e9)
 
 
-WORKLOADS = {"block": BlockTrain, "simplenet": SimpleNet, "mlp": MlpTrain, "rowreduce": RowReduce, "attn_rows": AttnRows, "gemm_bf16": lambda: Gemm("bf16"), "gemm_f32": lambda: Gemm("f32")}
+WORKLOADS = {"block": BlockTrain, "simplenet": SimpleNet, "mlp": MlpTrain, "rowreduce": RowReduce, "attn_rows": AttnRows, "attention": AttentionFwd, "gemm_bf16": lambda: Gemm("bf16"), "gemm_f32": lambda: Gemm("f32")}
 
 
 def make_workload(args, rank=0, world=1):
@@ -725,7 +812,7 @@ def make_workload(args, rank=0, world=1):
     if args.workload == "block":
         return BlockTrain(size=args.size, rank=rank, world=world)
     if args.size:
-        return {"rowreduce": lambda: RowReduce(rows=args.size), "attn_rows": lambda: AttnRows(rows=args.size), "gemm_bf16": lambda: Gemm("bf16", args.size),
+        return {"rowreduce": lambda: RowReduce(rows=args.size), "attn_rows": lambda: AttnRows(rows=args.size), "attention": lambda: AttentionFwd(args.size), "gemm_bf16": lambda: Gemm("bf16", args.size),
                 "gemm_f32": lambda: Gemm("f32", args.size)}[args.workload]()
     return WORKLOADS[args.workload]()
 

@@ -95,7 +95,7 @@ typedef struct {
  * Launch arguments are always inputs first, then outputs, as `Device::launch` receives
  * them (zyx/src/backend/mod.rs:974, zyx/src/runtime.rs:2285-2291).
  * ---------------------------------------------------------------------------------- */
-enum { ZYXB_KIND_ROWREDUCE = 1, ZYXB_KIND_GEMM = 2, ZYXB_KIND_ELTWISE = 3, ZYXB_KIND_OPTIM = 4 };
+enum { ZYXB_KIND_ROWREDUCE = 1, ZYXB_KIND_GEMM = 2, ZYXB_KIND_ELTWISE = 3, ZYXB_KIND_OPTIM = 4, ZYXB_KIND_ATTENTION = 5 };
 
 /* Row kernels: an elementwise chain with a trailing reduce over the last axis.
  * Semantics: Tensor::reduce_impl (zyx/src/tensor/reduce_ops.rs:45-157), softmax /
@@ -223,6 +223,22 @@ typedef struct {
  *                              Adam p[0..n), g[0..n), m[0..n), v[0..n)
  * The step counter t starts at 0 and is incremented by every launch (AdamW::t). */
 
+/* Fused scaled-dot-product self-attention (forward), the subgraph of MultiheadAttention::forward between the
+ * projections (zyx-nn/src/multi_head_attention.rs:197-226): o = softmax(scale * q.k^T [masked above the diagonal]) . v
+ * per (batch, head), computed tile by tile without materialising the [seq, seq] scores.  q, k, v, o are [batch, seq,
+ * heads*head_dim] activations read and written in place (head h of row t starts at t*ld + h*head_dim).  The second output
+ * lse [batch*heads, seq] f32 is ln(sum_j exp(scale * s_ij)) per query, which a backward pass needs.
+ * Scores and probabilities are never rounded to the tensor dtype (the reference rounds both where it stores them). */
+typedef struct {
+  int32_t  dtype;        /* bf16 / f16 */
+  uint64_t batch, heads, seq;
+  uint64_t head_dim;     /* 128 */
+  uint64_t ld;           /* row pitch of q, k, v, o in elements; 0 = heads*head_dim */
+  float    scale;        /* 0 means 1/sqrt(head_dim) */
+  int32_t  causal;
+} zyxb_attention_desc;
+/* args: q, k, v -> o, lse */
+
 typedef struct {
   int32_t kind;  /* ZYXB_KIND_* */
   union {
@@ -230,6 +246,7 @@ typedef struct {
     zyxb_gemm_desc      gemm;
     zyxb_eltwise_desc   eltwise;
     zyxb_optim_desc     optim;
+    zyxb_attention_desc attention;
   } u;
 } zyxb_kernel_desc;
 

@@ -96,6 +96,31 @@ def block_init(nprng, dtype, dim, ffn, std=0.02):
     return p
 
 
+def attention(dtype, q, k, v, heads, causal, scale=None):
+    """Self-attention as MultiheadAttention::forward composes it (zyx-nn/src/multi_head_attention.rs:197-226): per head
+    scores = q.k^T * scale, masked softmax, probabilities . v, each tensor stored in `dtype` as the reference's kernels
+    store them.  q, k, v: [B, T, H*D] -> (o [B, T, H*D], lse [B*H, T] float64 = ln sum exp(scale * q.k^T) of the stored q, k,
+    exact [B, T, H*D] float64 = the same attention of the stored q, k, v without any intermediate rounding)."""
+    B, T, E = q.shape
+    H, D = heads, E // heads
+    scale = float(1.0 / np.sqrt(np.float32(D))) if scale is None else float(scale)
+    heads_of = lambda a: np.ascontiguousarray(a.reshape(B, T, H, D).transpose(0, 2, 1, 3)).reshape(B * H, T, D)
+    qh, kh, vh = heads_of(q), heads_of(k), heads_of(v)
+    s = zo.gemm(dtype, qh, kh, tb=True, alpha=scale)
+    pr = zo.softmax(dtype, s.reshape(B * H * T, T), causal=causal, period=T).reshape(B * H, T, T)
+    o = zo.gemm(dtype, pr, vh)
+    o = np.ascontiguousarray(o.reshape(B, H, T, D).transpose(0, 2, 1, 3)).reshape(B, T, E)
+    sx = np.einsum("btd,bsd->bts", zo.to_f32(qh, dtype).astype(np.float64), zo.to_f32(kh, dtype).astype(np.float64)) * scale
+    if causal:
+        sx = np.where(np.arange(T)[None, None, :] > np.arange(T)[None, :, None], -np.inf, sx)
+    mx = sx.max(-1, keepdims=True)
+    ex = np.exp(sx - mx)
+    lse = (mx + np.log(ex.sum(-1, keepdims=True)))[..., 0]
+    exact = np.einsum("bts,bsd->btd", ex / ex.sum(-1, keepdims=True), zo.to_f32(vh, dtype).astype(np.float64))
+    exact = np.ascontiguousarray(exact.reshape(B, H, T, D).transpose(0, 2, 1, 3)).reshape(B, T, E)
+    return o, lse, exact
+
+
 def block_forward_backward(dtype, p, x, target, heads, causal, eps=1e-5):
     """x, target: [B, T, E].  -> (loss, grads dict, y, intermediates).  Rounds to `dtype` wherever the GPU plan stores a tensor."""
     B, T, E = x.shape

@@ -1,0 +1,59 @@
+"""Parity of the fused attention kernel (tcgen05) with the oracle's composition of the reference's attention:
+scores matmul -> masked softmax -> probabilities matmul, each stored in the tensor dtype."""
+import numpy as np
+import pytest
+
+from oracle import models as zm
+from oracle import oracle as zo
+from tests.parity import TOL_BF16, assert_parity
+from zyx_b200 import _lib as L
+from zyx_b200 import backend as B
+
+pytestmark = pytest.mark.gpu
+RNG = np.random.default_rng(23)
+
+
+def rand(shape, dtype, scale=1.0):
+    return zo.to_bits((RNG.standard_normal(size=shape) * scale).astype(np.float32), dtype)
+
+
+def check(o, want, exact, dtype):
+    """An attention output is a weighted mean of value rows, so errors scale with the row's largest magnitude, not with
+    the entry: tolerance 2e-2 relative to max(|want|, the row's largest |want|).  The reference composition truncates
+    the scores and the probabilities to the 16-bit type, which moves its own result by 1e-2 .. 6e-2 on that scale away
+    from the unrounded attention of the same inputs (probabilities that no longer sum to one); the fused kernel keeps
+    both in f32.  So: within tolerance of the oracle, or within tolerance of the unrounded (float64) attention with the
+    remaining gap to the oracle no larger than the tolerance plus the oracle's own distance from it."""
+    got, ref = zo.to_f32(o, dtype).astype(np.float64), zo.to_f32(want, dtype).astype(np.float64)
+    assert_parity(got, ref, exact, TOL_BF16, floor=1.0, what="attention")
+
+
+@pytest.mark.parametrize("dtype", [L.BF16, L.F16])
+@pytest.mark.parametrize("causal", [True, False])
+@pytest.mark.parametrize("batch,heads,seq", [(1, 1, 128), (2, 3, 256), (1, 2, 640)])
+def test_fused_attention_matches_the_composed_reference(sess, dtype, causal, batch, heads, seq):
+    D = 128
+    q, k, v = (rand((batch, seq, heads * D), dtype) for _ in range(3))
+    o, lse = sess.attention(dtype, q, k, v, heads, causal=causal)
+    assert sess.device.status() == 0
+    want, want_lse, exact = zm.attention(dtype, q, k, v, heads, causal)
+    check(o, want, exact, dtype)
+    assert np.max(np.abs(lse - want_lse)) <= 1e-3 * max(1.0, float(np.max(np.abs(want_lse))))
+
+
+def test_fused_attention_large_scores_and_custom_scale(sess):
+    """Peaked softmax rows (scores of order 30) exercise the running-maximum rescale of the output tile."""
+    dtype, batch, heads, seq, D = L.BF16, 1, 2, 512, 128
+    q, k, v = rand((batch, seq, heads * D), dtype, 1.5), rand((batch, seq, heads * D), dtype, 1.5), rand((batch, seq, heads * D), dtype)
+    o, _ = sess.attention(dtype, q, k, v, heads, scale=0.25, causal=True)
+    want, _, exact = zm.attention(dtype, q, k, v, heads, True, scale=0.25)
+    assert sess.device.status() == 0
+    check(o, want, exact, dtype)
+
+
+def test_attention_descriptor_is_validated(sess):
+    for kw in (dict(head_dim=64, seq=128), dict(head_dim=128, seq=100), dict(head_dim=128, seq=128, dtype=L.F32)):
+        args = dict(dtype=L.BF16, batch=1, heads=1)
+        args.update(kw)
+        with pytest.raises(B.BackendError):
+            sess.device.create_program(B.attention_desc(args["dtype"], args["batch"], args["heads"], args["seq"], args["head_dim"]))

@@ -290,6 +290,14 @@ def rowreduce_desc(op, dtype, rows, cols, eps=0.0, correction=1, has_weight=Fals
     return d
 
 
+def attention_desc(dtype, batch, heads, seq, head_dim, ld=0, scale=0.0, causal=False):
+    d = L.KernelDesc()
+    d.kind = L.KIND_ATTENTION
+    a = d.u.attention
+    a.dtype, a.batch, a.heads, a.seq, a.head_dim, a.ld, a.scale, a.causal = dtype, batch, heads, seq, head_dim, ld, scale, int(causal)
+    return d
+
+
 def gemm_desc(dtype, m, n, k, batch=1, trans_a=False, trans_b=False, stride_a=None, stride_b=None, stride_c=None,
               epilogue=L.EPI_NONE, store_preact=False, alpha=0.0, lda=0, ldb=0, ldc=0, batch_inner=0, stride_a_inner=0,
               stride_b_inner=0, stride_c_inner=0, tri=0):

@@ -36,6 +36,10 @@ int launch_optim(const zyxb_optim_desc& d, const uint64_t* numel, uint64_t step,
 int launch_gemm(const zyxb_gemm_desc& d, void* const* args, const uint64_t* arg_bytes, int n_args, const LaunchCtx& lc,
                 std::string& err);
 
+int launch_attention(const zyxb_attention_desc& d, void* const* args, const uint64_t* arg_bytes, int n_args, const LaunchCtx& lc,
+                     std::string& err);
+int validate_attention(const zyxb_attention_desc& d, std::string& err);
+
 // column sums with the partials in a fixed device array (no allocation anywhere on the path)
 int launch_colsum_static(int dtype, const void* x, void* y, uint64_t rows, uint64_t cols, const LaunchCtx& lc, std::string& err);
 uint64_t colsum_static_capacity();

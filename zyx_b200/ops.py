@@ -107,6 +107,13 @@ class Session:
         r = self.run(d, ins, outs, out_init=out_init)
         return (r[0], r[1]) if want_preact else r[0]
 
+    def attention(self, dtype, q, k, v, heads, scale=0.0, causal=False):
+        """q, k, v: [batch, seq, heads*head_dim] -> (o like q, lse [batch*heads, seq] f32)."""
+        batch, seq, e = q.shape
+        d = B.attention_desc(dtype, batch, heads, seq, e // heads, scale=scale, causal=causal)
+        o, lse = self.run(d, [q, k, v], [(q.shape, q.dtype), ((batch * heads, seq), np.float32)])
+        return o, lse
+
     # ---- optimizers (in place on the host arrays, like the oracle's) ------------------------------
     def optim_step(self, desc_kw, dtype, algo, tensors, t=None):
         """tensors: list of groups [p, g (, m, v | , buf)] of host arrays per parameter; updated in place."""
