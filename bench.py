@@ -428,6 +428,10 @@ class AttentionFwd:
         self.bo, _ = p.allocate(self.q.nbytes)
         self.blse, _ = p.allocate(self.B * self.H * self.T * 4)
         self.prog = d.create_program(B.attention_desc(L.BF16, self.B, self.H, self.T, self.D, causal=True))
+        self.prog_bwd = d.create_program(B.attention_desc(L.BF16, self.B, self.H, self.T, self.D, causal=True, backward=True))
+        self.bdo = p.upload(self.q[::-1].copy())              # any N(0,1) tensor serves as the upstream gradient
+        self.bdq, self.bdk, self.bdv = (p.allocate(self.q.nbytes)[0] for _ in range(3))
+        self.bwd_events = []
         self.config = {"workload": self.name, "l2": "L2 flushed (256 MB memset) before every timed launch",
                        "flops": "executed: 128 x 128 tiles on and below the diagonal; dense equivalent %.0f GFLOP" % (self.flops_dense / 1e9)}
         self.kernel_events = []
@@ -439,6 +443,11 @@ class AttentionFwd:
         d.launch(self.prog, [self.bq, self.bk, self.bv, self.bo, self.blse])
         if timed:
             self.kernel_events.append((e0, d.event_record()))
+        d.flush_l2()
+        e1 = d.event_record() if timed else None
+        d.launch(self.prog_bwd, [self.bq, self.bk, self.bv, self.bo, self.bdo, self.blse, self.bdq, self.bdk, self.bdv])
+        if timed:
+            self.bwd_events.append((e1, d.event_record()))
 
     def roofline(self, peaks, clocks=None):
         d = self.sess.device
@@ -447,7 +456,11 @@ class AttentionFwd:
         ach = self.flops / (t * 1e-3) / 1e12
         return ({"bound": "tensor", "kernel": "attn_fwd_kernel (tcgen05)", "achieved": ach, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
                  "frac": ach / peaks["bf16_tflops"], "traffic": None, "peak_source": peaks["source"], "ms_per_launch": t,
-                 "tflops_dense_equivalent": self.flops_dense / (t * 1e-3) / 1e12}, {"attention": {"ms": t, "TFLOP/s": ach}})
+                 "tflops_dense_equivalent": self.flops_dense / (t * 1e-3) / 1e12},
+                {"attention": {"ms": t, "TFLOP/s": ach},
+                 "attention_backward": (lambda tb: {"ms": tb, "TFLOP/s": 3.5 * self.flops / (tb * 1e-3) / 1e12,
+                                                    "note": "7 tensor-core products per tile pair (S and dP are computed by both backward kernels)"})(
+                     float(np.mean([d.elapsed_ms(a, b) for a, b in self.bwd_events])))})
 
     def e2e_setup(self):
         self.ho = np.empty_like(self.q)

@@ -95,7 +95,7 @@ typedef struct {
  * Launch arguments are always inputs first, then outputs, as `Device::launch` receives
  * them (zyx/src/backend/mod.rs:974, zyx/src/runtime.rs:2285-2291).
  * ---------------------------------------------------------------------------------- */
-enum { ZYXB_KIND_ROWREDUCE = 1, ZYXB_KIND_GEMM = 2, ZYXB_KIND_ELTWISE = 3, ZYXB_KIND_OPTIM = 4, ZYXB_KIND_ATTENTION = 5 };
+enum { ZYXB_KIND_ROWREDUCE = 1, ZYXB_KIND_GEMM = 2, ZYXB_KIND_ELTWISE = 3, ZYXB_KIND_OPTIM = 4, ZYXB_KIND_ATTENTION = 5, ZYXB_KIND_ATTENTION_BWD = 6 };
 
 /* Row kernels: an elementwise chain with a trailing reduce over the last axis.
  * Semantics: Tensor::reduce_impl (zyx/src/tensor/reduce_ops.rs:45-157), softmax /
@@ -237,7 +237,9 @@ typedef struct {
   float    scale;        /* 0 means 1/sqrt(head_dim) */
   int32_t  causal;
 } zyxb_attention_desc;
-/* args: q, k, v -> o, lse */
+/* ZYXB_KIND_ATTENTION      args: q, k, v -> o, lse
+ * ZYXB_KIND_ATTENTION_BWD  args: q, k, v, o, do, lse -> dq, dk, dv   (the adjoint; the same descriptor as the forward;
+ *                          probabilities are recomputed from lse tile by tile, nothing of size [seq, seq] is stored) */
 
 typedef struct {
   int32_t kind;  /* ZYXB_KIND_* */
@@ -246,7 +248,7 @@ typedef struct {
     zyxb_gemm_desc      gemm;
     zyxb_eltwise_desc   eltwise;
     zyxb_optim_desc     optim;
-    zyxb_attention_desc attention;
+    zyxb_attention_desc attention;   /* both attention kinds */
   } u;
 } zyxb_kernel_desc;
 

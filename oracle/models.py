@@ -121,6 +121,36 @@ def attention(dtype, q, k, v, heads, causal, scale=None):
     return o, lse, exact
 
 
+def attention_bwd(dtype, q, k, v, do, heads, causal, scale=None):
+    """The adjoint of `attention` as the reference's autograd composes it from stored tensors: dP = dO.V^T,
+    dV = P^T.dO, dS = P*(dP - sum(dP*P)), dQ = dS.K*scale, dK = dS^T.Q*scale, every tensor stored in `dtype`.
+    -> (dq, dk, dv, exact) with exact = (dq, dk, dv) in float64 from the stored q, k, v, do without intermediate rounding."""
+    B, T, E = q.shape
+    H, D = heads, E // heads
+    scale = float(1.0 / np.sqrt(np.float32(D))) if scale is None else float(scale)
+    heads_of = lambda a: np.ascontiguousarray(a.reshape(B, T, H, D).transpose(0, 2, 1, 3)).reshape(B * H, T, D)
+    merge = lambda a: np.ascontiguousarray(a.reshape(B, H, T, D).transpose(0, 2, 1, 3)).reshape(B, T, E)
+    qh, kh, vh, doh = heads_of(q), heads_of(k), heads_of(v), heads_of(do)
+    s = zo.gemm(dtype, qh, kh, tb=True, alpha=scale)
+    pr = zo.softmax(dtype, s.reshape(B * H * T, T), causal=causal, period=T).reshape(B * H, T, T)
+    dp = zo.gemm(dtype, doh, vh, tb=True)
+    dv = zo.gemm(dtype, pr, doh, ta=True)
+    ds = zo.softmax_bwd(dtype, pr.reshape(B * H * T, T), dp.reshape(B * H * T, T)).reshape(B * H, T, T)
+    dq = zo.gemm(dtype, ds, kh, alpha=scale)
+    dk = zo.gemm(dtype, ds, qh, ta=True, alpha=scale)
+    f = lambda a: zo.to_f32(a, dtype).astype(np.float64)
+    sx = np.einsum("btd,bsd->bts", f(qh), f(kh)) * scale
+    if causal:
+        sx = np.where(np.arange(T)[None, None, :] > np.arange(T)[None, :, None], -np.inf, sx)
+    px = np.exp(sx - sx.max(-1, keepdims=True))
+    px /= px.sum(-1, keepdims=True)
+    dpx = np.einsum("btd,bsd->bts", f(doh), f(vh))
+    dsx = px * (dpx - (dpx * px).sum(-1, keepdims=True))
+    exact = (merge(np.einsum("bts,bsd->btd", dsx, f(kh)) * scale), merge(np.einsum("bts,btd->bsd", dsx, f(qh)) * scale),
+             merge(np.einsum("bts,btd->bsd", px, f(doh))))
+    return merge(dq), merge(dk), merge(dv), exact
+
+
 def block_forward_backward(dtype, p, x, target, heads, causal, eps=1e-5):
     """x, target: [B, T, E].  -> (loss, grads dict, y, intermediates).  Rounds to `dtype` wherever the GPU plan stores a tensor."""
     B, T, E = x.shape

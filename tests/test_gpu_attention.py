@@ -5,7 +5,7 @@ import pytest
 
 from oracle import models as zm
 from oracle import oracle as zo
-from tests.parity import TOL_BF16, assert_parity
+from tests.parity import TOL_BF16, assert_parity, max_rel_err
 from zyx_b200 import _lib as L
 from zyx_b200 import backend as B
 
@@ -49,6 +49,29 @@ def test_fused_attention_large_scores_and_custom_scale(sess):
     want, _, exact = zm.attention(dtype, q, k, v, heads, True, scale=0.25)
     assert sess.device.status() == 0
     check(o, want, exact, dtype)
+
+
+@pytest.mark.parametrize("dtype", [L.BF16, L.F16])
+@pytest.mark.parametrize("causal", [True, False])
+@pytest.mark.parametrize("batch,heads,seq", [(1, 1, 128), (2, 2, 256), (1, 2, 640)])
+def test_fused_attention_backward(sess, dtype, causal, batch, heads, seq):
+    D = 128
+    q, k, v, do = (rand((batch, seq, heads * D), dtype) for _ in range(4))
+    o, lse = sess.attention(dtype, q, k, v, heads, causal=causal)
+    dq, dk, dv = sess.attention_bwd(dtype, q, k, v, o, do, lse, heads, causal=causal)
+    assert sess.device.status() == 0
+    wq, wk, wv, exact = zm.attention_bwd(dtype, q, k, v, do, heads, causal)
+    for name, got, want, ex in (("dq", dq, wq, exact[0]), ("dk", dk, wk, exact[1]), ("dv", dv, wv, exact[2])):
+        g, w = zo.to_f32(got, dtype).astype(np.float64), zo.to_f32(want, dtype).astype(np.float64)
+        # The adjoint is ill-conditioned in 16-bit storage on both sides: dS = P*(dP - delta) subtracts numbers of size
+        # sqrt(head_dim) to get one of size 1, the reference from a dP stored in the 16-bit type, the fused kernel from a
+        # delta computed from the stored o.  Both land a few percent (of the row scale) from the unrounded adjoint, and
+        # the first rows of a causal dq are exactly zero mathematically (one key), so the scale is also bounded below by
+        # 5 % of the tensor's largest magnitude.  Required: as close to the unrounded adjoint as the reference
+        # composition is (within a quarter), and no farther from the reference than tolerance plus its own distance.
+        kw = dict(floor=1.0, abs_floor=0.05 * float(np.abs(ex).max()))
+        e_go, e_ge, e_oe = max_rel_err(g, w, **kw), max_rel_err(g, ex, **kw), max_rel_err(w, ex, **kw)
+        assert e_go <= TOL_BF16 or (e_ge <= max(TOL_BF16, 1.25 * e_oe) and e_go <= TOL_BF16 + e_oe), (name, e_go, e_ge, e_oe)
 
 
 def test_attention_descriptor_is_validated(sess):

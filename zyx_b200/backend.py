@@ -290,9 +290,9 @@ def rowreduce_desc(op, dtype, rows, cols, eps=0.0, correction=1, has_weight=Fals
     return d
 
 
-def attention_desc(dtype, batch, heads, seq, head_dim, ld=0, scale=0.0, causal=False):
+def attention_desc(dtype, batch, heads, seq, head_dim, ld=0, scale=0.0, causal=False, backward=False):
     d = L.KernelDesc()
-    d.kind = L.KIND_ATTENTION
+    d.kind = L.KIND_ATTENTION_BWD if backward else L.KIND_ATTENTION
     a = d.u.attention
     a.dtype, a.batch, a.heads, a.seq, a.head_dim, a.ld, a.scale, a.causal = dtype, batch, heads, seq, head_dim, ld, scale, int(causal)
     return d

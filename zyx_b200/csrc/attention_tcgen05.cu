@@ -5,8 +5,8 @@
 // q, k, v and o are [B, T, H*D] activations addressed in place as strided per-head views (row pitch ld, head stride D).
 // The row-wise log-sum-exp is stored for a backward pass.
 //
-// Two CTAs of 192 threads per SM (96 KB of shared memory and 256 TMEM columns each), key tiles of 64:
-//   warp 0      TMA producer (one lane): Q once, then K_j into a 2-stage ring and V_j into a single stage
+// Two CTAs of 192 threads per SM (112 KB of shared memory and 256 TMEM columns each), key tiles of 64:
+//   warp 0      TMA producer (one lane): Q once, then K_j and V_j into 2-stage rings
 //   warp 1      MMA issuer   (one lane): S_{j+1} = Q.K_{j+1}^T is issued before P_j.V_j, so the tensor core works on the
 //               next scores while the softmax warps work on the current ones (S is double-buffered in TMEM)
 //   warps 2..5  softmax      : thread = query row = TMEM lane; row maximum and sum stay in registers
@@ -26,15 +26,17 @@ namespace zyxb {
 
 constexpr int AT_BM = 128, AT_BN = 64, AT_D = 128;
 constexpr int AT_THREADS = 192;
-constexpr int AT_SOFTMAX_THREADS = 128;
+constexpr int AT_SOFTMAX_WARPS = 4;        // barriers the softmax warps signal count warps: one lane arrives per warp
 constexpr int AT_Q_BYTES = AT_BM * AT_D * 2;                 // 32 KB: two boxes of [128 rows x 64 d]
 constexpr int AT_KV_BYTES = AT_BN * AT_D * 2;                // 16 KB: two boxes of [64 keys x 64 d]
 constexpr int AT_P_BYTES = AT_BM * AT_BN * 2;                // 16 KB: [128 rows x 64 keys]
 constexpr int AT_Q_OFF = 0, AT_K_OFF = AT_Q_BYTES, AT_V_OFF = AT_K_OFF + 2 * AT_KV_BYTES;
-constexpr int AT_P_OFF = AT_V_OFF + AT_KV_BYTES;
+constexpr int AT_P_OFF = AT_V_OFF + 2 * AT_KV_BYTES;
 constexpr int AT_BAR_OFF = AT_P_OFF + AT_P_BYTES;
-constexpr int AT_SMEM_TOTAL = AT_BAR_OFF + 256 + 1024;       // 96 KB + barriers + alignment slack: two CTAs per SM
-enum { AT_ERR_PRODUCER = 16u, AT_ERR_MMA = 32u, AT_ERR_SOFTMAX = 64u };
+// 112 KB + barriers: two CTAs per SM fit only without alignment slack, so the kernel requires the dynamic shared memory
+// window to start on a 1024-byte boundary (it does when the kernel has no static shared memory) and reports otherwise
+constexpr int AT_SMEM_TOTAL = AT_BAR_OFF + 256;
+enum { AT_ERR_PRODUCER = 16u, AT_ERR_MMA = 32u, AT_ERR_SOFTMAX = 64u, AT_ERR_ALIGN = 1024u };
 
 struct AttnParams {
   void* o; float* lse;
@@ -46,34 +48,26 @@ struct AttnParams {
   uint32_t* status;
 };
 
-__device__ __forceinline__ uint32_t pack2(float lo, float hi, bool bf16) {
-  uint32_t d;
-  if (bf16) asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
-  else asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
-  return d;
-}
-__device__ __forceinline__ float ex2f(float x) {
-  float r;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
-  return r;
-}
-
 __global__ void __launch_bounds__(AT_THREADS, 2)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                 const __grid_constant__ CUtensorMap map_v, AttnParams p) {
-  extern __shared__ uint8_t smem_raw[];
-  const uint32_t raw = smem_u32(smem_raw);
-  const uint32_t base = (raw + 1023u) & ~1023u;
-  uint8_t* base_ptr = smem_raw + (base - raw);
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const uint32_t base = smem_u32(smem_raw);
+  if (base & 1023u) {                                        // swizzle atoms repeat every 1024 B: refuse rather than compute garbage
+    if (threadIdx.x == 0) atomicOr(p.status, AT_ERR_ALIGN);
+    return;
+  }
+  uint8_t* base_ptr = smem_raw;
   const uint32_t bar = base + AT_BAR_OFF;
   const uint32_t q_full = bar;
   auto k_full = [&](int s) { return bar + 8u * (1 + s); };
   auto k_empty = [&](int s) { return bar + 8u * (3 + s); };
-  const uint32_t v_full = bar + 8u * 5, v_empty = bar + 8u * 6;
-  auto s_full = [&](int b) { return bar + 8u * (7 + b); };
-  auto s_empty = [&](int b) { return bar + 8u * (9 + b); };
-  const uint32_t p_full = bar + 8u * 11, pv_done = bar + 8u * 12;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + AT_BAR_OFF + 8 * 13);
+  auto v_full = [&](int s) { return bar + 8u * (5 + s); };
+  auto v_empty = [&](int s) { return bar + 8u * (7 + s); };
+  auto s_full = [&](int b) { return bar + 8u * (9 + b); };
+  auto s_empty = [&](int b) { return bar + 8u * (11 + b); };
+  const uint32_t p_full = bar + 8u * 13, pv_done = bar + 8u * 14;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + AT_BAR_OFF + 8 * 15);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -85,10 +79,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    for (int s = 0; s < 2; ++s) { mbar_init(k_full(s), 1); mbar_init(k_empty(s), 1); }
-    mbar_init(v_full, 1); mbar_init(v_empty, 1);
-    for (int i = 0; i < 2; ++i) { mbar_init(s_full(i), 1); mbar_init(s_empty(i), AT_SOFTMAX_THREADS); }
-    mbar_init(p_full, AT_SOFTMAX_THREADS);
+    for (int s = 0; s < 2; ++s) { mbar_init(k_full(s), 1); mbar_init(k_empty(s), 1); mbar_init(v_full(s), 1); mbar_init(v_empty(s), 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(s_full(i), 1); mbar_init(s_empty(i), AT_SOFTMAX_WARPS); }
+    mbar_init(p_full, AT_SOFTMAX_WARPS);
     mbar_init(pv_done, 1);
     *abort_flag = 0;
     fence_barrier_init();
@@ -114,9 +107,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         const uint32_t k_dst = base + AT_K_OFF + s * AT_KV_BYTES;
         mbar_expect_tx(k_full(s), AT_KV_BYTES);
         for (int c = 0; c < 2; ++c) tma_load_4d(k_dst + c * (AT_KV_BYTES / 2), &map_k, k_full(s), c * 64, (int)(j * AT_BN), (int)h, (int)b);
-        if (!mbar_wait(v_empty, (j & 1) ^ 1, abort_flag, p.status, AT_ERR_PRODUCER)) { ok = false; ++issued; break; }
-        mbar_expect_tx(v_full, AT_KV_BYTES);
-        for (int c = 0; c < 2; ++c) tma_load_4d(base + AT_V_OFF + c * (AT_KV_BYTES / 2), &map_v, v_full, c * 64, (int)(j * AT_BN), (int)h, (int)b);
+        if (!mbar_wait(v_empty(s), ((j >> 1) & 1) ^ 1, abort_flag, p.status, AT_ERR_PRODUCER)) { ok = false; ++issued; break; }
+        mbar_expect_tx(v_full(s), AT_KV_BYTES);
+        for (int c = 0; c < 2; ++c)
+          tma_load_4d(base + AT_V_OFF + s * AT_KV_BYTES + c * (AT_KV_BYTES / 2), &map_v, v_full(s), c * 64, (int)(j * AT_BN), (int)h, (int)b);
         ++issued; ++v_issued;
       }
       if (!ok) {   // drain: wait (bounded) for copies still in flight so none lands after the CTA has gone
@@ -125,7 +119,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           const uint32_t j = issued - 1 - i;
           while (!mbar_try_wait(k_full(j & 1), (j >> 1) & 1) && global_timer_ns() - t0 < TC_WAIT_NS) {}
         }
-        if (v_issued) while (!mbar_try_wait(v_full, (v_issued - 1) & 1) && global_timer_ns() - t0 < TC_WAIT_NS) {}
+        for (uint32_t i = 0; i < 2 && i < v_issued; ++i) {
+          const uint32_t j = v_issued - 1 - i;
+          while (!mbar_try_wait(v_full(j & 1), (j >> 1) & 1) && global_timer_ns() - t0 < TC_WAIT_NS) {}
+        }
         while (!mbar_try_wait(q_full, 0) && global_timer_ns() - t0 < TC_WAIT_NS) {}
       }
     }
@@ -157,13 +154,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           issue_s(jn);
         }
         if (!mbar_wait(p_full, j & 1, abort_flag, p.status, AT_ERR_MMA)) { ok = false; break; }
-        if (!mbar_wait(v_full, j & 1, abort_flag, p.status, AT_ERR_MMA)) { ok = false; break; }
+        if (!mbar_wait(v_full(j & 1), (j >> 1) & 1, abort_flag, p.status, AT_ERR_MMA)) { ok = false; break; }
         tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < AT_BN / 16; ++kk)   // 16 keys per instruction; V rows are 128 B of one 64-wide d chunk, chunks 8 KB apart
           umma_f16(tmem_o, make_smem_desc(base + AT_P_OFF + kk * 32, 16, 1024),
-                   make_smem_desc(base + AT_V_OFF + kk * (16 * 128), AT_KV_BYTES / 2, 1024), idesc_pv, (j != 0 || kk != 0) ? 1u : 0u);
-        umma_commit(v_empty);              // V_j has been read
+                   make_smem_desc(base + AT_V_OFF + (j & 1) * AT_KV_BYTES + kk * (16 * 128), AT_KV_BYTES / 2, 1024), idesc_pv,
+                   (j != 0 || kk != 0) ? 1u : 0u);
+        umma_commit(v_empty(j & 1));       // V_j has been read
         umma_commit(pv_done);              // O holds tiles 0..j; P may be overwritten
       }
     }
@@ -242,9 +240,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         }
       }
       tc_fence_before();
-      mbar_arrive(s_empty(sb));            // this S buffer may be overwritten by S_{j+2}
       fence_proxy_async_smem();
-      mbar_arrive(p_full);
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(s_empty(sb));          // this S buffer may be overwritten by S_{j+2}
+        mbar_arrive(p_full);
+      }
       l = l * alpha + sum;
       m = m_new;
     }

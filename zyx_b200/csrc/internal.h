@@ -38,6 +38,8 @@ int launch_gemm(const zyxb_gemm_desc& d, void* const* args, const uint64_t* arg_
 
 int launch_attention(const zyxb_attention_desc& d, void* const* args, const uint64_t* arg_bytes, int n_args, const LaunchCtx& lc,
                      std::string& err);
+int launch_attention_bwd(const zyxb_attention_desc& d, void* const* args, const uint64_t* arg_bytes, int n_args, const LaunchCtx& lc,
+                         std::string& err);
 int validate_attention(const zyxb_attention_desc& d, std::string& err);
 
 // column sums with the partials in a fixed device array (no allocation anywhere on the path)

@@ -33,14 +33,18 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
   return ok;
 }
 // Bounded wait.  Returns false when the wait was abandoned (time limit or another role aborted).
+// The wall clock (%globaltimer, a slow read) is consulted only every 1024 failed polls, so that a wait that is satisfied
+// after a few polls - the common case on the critical path of a pipeline - never pays for it.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, uint32_t* status, uint32_t code) {
   if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t t0 = global_timer_ns();
+  uint64_t t0 = 0;
   uint32_t spins = 0;
   while (!mbar_try_wait(bar, parity)) {
-    if ((++spins & 0xff) == 0) {
+    if ((++spins & 0x3ff) == 0) {
       if (*abort_flag) return false;
-      if (global_timer_ns() - t0 > TC_WAIT_NS) {
+      const uint64_t now = global_timer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > TC_WAIT_NS) {
         *abort_flag = 1;
         atomicOr(status, code);
         return false;
@@ -119,6 +123,19 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, uint32_t lbo_b
 __host__ __device__ constexpr uint32_t make_idesc(bool bf16, bool a_mn, bool b_mn, int M, int N) {
   return (1u << 4) | ((bf16 ? 1u : 0u) << 7) | ((bf16 ? 1u : 0u) << 10) | ((a_mn ? 1u : 0u) << 15) | ((b_mn ? 1u : 0u) << 16) |
          ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+
+// two f32 -> one packed pair of the 16-bit storage type, round to nearest (lo in the low half)
+__device__ __forceinline__ uint32_t pack2(float lo, float hi, bool bf16) {
+  uint32_t d;
+  if (bf16) asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+  else asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+  return d;
+}
+__device__ __forceinline__ float ex2f(float x) {
+  float r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+  return r;
 }
 
 // ---- host side ---------------------------------------------------------------------------------------

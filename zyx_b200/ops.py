@@ -114,6 +114,12 @@ class Session:
         o, lse = self.run(d, [q, k, v], [(q.shape, q.dtype), ((batch * heads, seq), np.float32)])
         return o, lse
 
+    def attention_bwd(self, dtype, q, k, v, o, do, lse, heads, scale=0.0, causal=False):
+        """-> (dq, dk, dv), each like q."""
+        batch, seq, e = q.shape
+        d = B.attention_desc(dtype, batch, heads, seq, e // heads, scale=scale, causal=causal, backward=True)
+        return tuple(self.run(d, [q, k, v, o, do, np.ascontiguousarray(lse, np.float32)], [(q.shape, q.dtype)] * 3))
+
     # ---- optimizers (in place on the host arrays, like the oracle's) ------------------------------
     def optim_step(self, desc_kw, dtype, algo, tensors, t=None):
         """tensors: list of groups [p, g (, m, v | , buf)] of host arrays per parameter; updated in place."""
