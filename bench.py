@@ -728,8 +728,8 @@ class BlockTrain:
     E, H, F, T, GLOBAL_B = 2048, 16, 8192, 2048, 8
     unit, dtype, bound = "samples/s", "bf16", "tensor"
 
-    def __init__(self, size=0, rank=0, world=1):
-        self.rank, self.world = rank, world
+    def __init__(self, size=0, rank=0, world=1, fused=False):
+        self.rank, self.world, self.fused = rank, world, fused
         self.B = size if size else max(1, self.GLOBAL_B // world)
         self.name = "transformer_block_d2048_h16_ffn8192_seq2048_bf16_causal_batch%d_per_gpu" % self.B
         self.metric = "transformer block train samples/s (d=2048, 16x128 heads, FFN 8192, seq 2048, bf16, causal, fwd+bwd+AdamW)"
@@ -758,7 +758,7 @@ class BlockTrain:
         self.sess, self.Hm = sess, H
         self.host_inputs()
         self.blk = H.Block(sess, L.BF16, self.B, self.T, self.E, self.H, self.F, causal=True, algo=L.OPT_ADAMW, world=self.world,
-                           lr=1e-3, weight_decay=0.01, standard=True)
+                           fused_attention=self.fused, lr=1e-3, weight_decay=0.01, standard=True)
         rng = np.random.default_rng(0)
         for i, shape in enumerate(self.blk.shapes):
             if i >= 12:
@@ -770,8 +770,9 @@ class BlockTrain:
         launches, colls = self.blk.plan_size()
         self.config = {"workload": self.name, "global_batch": self.B * self.world, "parallelism": "dp%d" % self.world,
                        "optimizer": "AdamW lr=1e-3 wd=0.01 (textbook update: the reference's literal form overflows after one step)",
-                       "attention": "scores materialised ([B*H, T, T] bf16) as in the reference; causal mask as a select",
-                       "l2": "working set (scores alone %d MiB) larger than L2" % (self.B * self.H * self.T * self.T * 2 >> 20),
+                       "attention": ("fused (scores and probabilities stay on chip, recomputed in the backward)" if self.fused else
+                                     "scores materialised ([B*H, T, T] bf16) as in the reference; causal mask as a select"),
+                       "l2": "working set (activations %d MiB) larger than L2" % (30 * self.B * self.T * self.E * 2 >> 20),
                        "launches_per_step": launches, "collectives_per_step": colls}
         self.losses = []
         self.step_events = []
@@ -823,7 +824,7 @@ def make_workload(args, rank=0, world=1):
     if args.workload == "simplenet":
         return SimpleNet(size=args.size, rank=rank, world=world)
     if args.workload == "block":
-        return BlockTrain(size=args.size, rank=rank, world=world)
+        return BlockTrain(size=args.size, rank=rank, world=world, fused=args.fused_attention)
     if args.size:
         return {"rowreduce": lambda: RowReduce(rows=args.size), "attn_rows": lambda: AttnRows(rows=args.size), "attention": lambda: AttentionFwd(args.size), "gemm_bf16": lambda: Gemm("bf16", args.size),
                 "gemm_f32": lambda: Gemm("f32", args.size)}[args.workload]()
@@ -881,6 +882,7 @@ def run():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--workload", default="mlp", choices=sorted(WORKLOADS))
+    ap.add_argument("--fused-attention", action="store_true", help="block: run attention as the fused forward / backward programs")
     ap.add_argument("--standard-adamw", action="store_true", help="mlp: textbook AdamW instead of the reference's literal update")
     ap.add_argument("--impl", default="zyx_b200", choices=["zyx_b200", "reference"])
     ap.add_argument("--e2e-steps", type=int, default=3)

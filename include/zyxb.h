@@ -314,6 +314,7 @@ int32_t zyxb_launch(zyxb_ctx* ctx, int32_t dev, uint32_t prog, const uint32_t* a
 int32_t zyxb_program_release(zyxb_ctx* ctx, int32_t dev, uint32_t prog);
 /* optimizer programs: read / set the step counter t (AdamW::t, adamw.rs:57) */
 int32_t zyxb_program_set_step(zyxb_ctx* ctx, int32_t dev, uint32_t prog, uint64_t t);
+int32_t zyxb_program_get_step(zyxb_ctx* ctx, int32_t dev, uint32_t prog, uint64_t* out_t);
 /* number of CUDA kernels this library has launched on the device since init */
 int32_t zyxb_launch_count(zyxb_ctx* ctx, int32_t dev, uint64_t* out_count);
 /* device-side status word written by kernels whose bounded waits ran out (0 = none);

@@ -87,6 +87,9 @@ typedef struct {
   float    eps;          /* LayerNorm epsilon (1e-5 in the example) */
   zyxb_optim_desc optim; /* algo and hyper-parameters; dtype, n_tensors, numel are filled in */
   int32_t  world;        /* > 1: gradients are all-reduced in three groups (ffn, attention output side, q/k/v) */
+  int32_t  fused_attention; /* 1: scores, softmax and probabilities.v (and their adjoints) run as the fused attention
+                               programs where the shape allows (16-bit dtype, head_dim 128, seq a multiple of 128); the
+                               [batch*heads, seq, seq] tensors are then not allocated and activation 0 does not exist */
 } zyxb_block_config;
 
 typedef struct zyxb_block zyxb_block;
@@ -103,6 +106,42 @@ int32_t zyxb_block_plan_size(zyxb_block* blk, int32_t* out_launches, int32_t* ou
 /* intermediate activations for tests: 0 attention probabilities [batch*heads, seq, seq], 1 attention output [rows, dim],
  * 2 x1 (after norm1) [rows, dim] */
 int32_t zyxb_block_activation(zyxb_block* blk, int32_t which, uint32_t* out_buf);
+
+/* ---- safetensors files: parameters, optimizer state and parity fixtures on disk -------------------------
+ * The writer restates Module::save (zyx/src/module.rs:36-63): an 8-byte little-endian header length, a JSON header
+ * {"name":{"dtype":"BF16","shape":[..],"data_offsets":[begin,end]},...} without whitespace, keys in exactly that order,
+ * then the tensors' little-endian bytes back to back in header order - the layout Tensor::load_safetensors
+ * (module.rs:436-529) relies on (it scans the header's strings positionally and reads the data at a running offset).
+ * The reader accepts that layout and any other valid safetensors file (a leading "__metadata__" object, keys in any
+ * order, data in any order): it honours data_offsets and checks them against shape and dtype as the reference does.
+ * dtype names are DType::safetensors (zyx/src/dtype.rs:227-243). */
+typedef struct {
+  const char* name;
+  int32_t dtype;             /* ZYXB_* element type */
+  int32_t rank;
+  const uint64_t* shape;     /* [rank] */
+  const void* data;          /* numel * element size bytes, host memory */
+} zyxb_st_tensor;
+typedef struct zyxb_st_file zyxb_st_file;
+int32_t zyxb_st_save(const char* path, const zyxb_st_tensor* tensors, int32_t n);
+int32_t zyxb_st_open(const char* path, zyxb_st_file** out);
+int32_t zyxb_st_count(const zyxb_st_file* f);
+/* the pointers stay valid until zyxb_st_close */
+int32_t zyxb_st_info(const zyxb_st_file* f, int32_t i, const char** out_name, int32_t* out_dtype, int32_t* out_rank,
+                     const uint64_t** out_shape, uint64_t* out_bytes);
+int32_t zyxb_st_find(const zyxb_st_file* f, const char* name);   /* index, or -1 */
+int32_t zyxb_st_read(zyxb_st_file* f, int32_t i, void* dst, uint64_t dst_bytes);
+int32_t zyxb_st_close(zyxb_st_file* f);
+const char* zyxb_st_last_error(void);   /* of the calling thread's last failed zyxb_st_* call */
+
+/* Checkpoints of the plans: parameters ("<name>"), optimizer state ("optim.m.<name>", "optim.v.<name>" or
+ * "optim.buf.<name>") and the step counter ("optim.t", one U32) in one safetensors file, names in Module::iter_tensors
+ * order (e.g. "attn.q_proj.weight"; "layers.0.weight" for the Linear stack).  Loading a file written by zyx itself
+ * works when its labels match; tensors absent from the file are left untouched and counted in *out_missing. */
+int32_t zyxb_mlp_save(zyxb_mlp* mlp, const char* path);
+int32_t zyxb_mlp_load(zyxb_mlp* mlp, const char* path, int32_t* out_missing);
+int32_t zyxb_block_save(zyxb_block* blk, const char* path);
+int32_t zyxb_block_load(zyxb_block* blk, const char* path, int32_t* out_missing);
 
 #ifdef __cplusplus
 }

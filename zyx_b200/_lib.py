@@ -117,6 +117,7 @@ SIGNATURES = {
     "zyxb_launch": (C.c_int32, [_CTX, C.c_int32, C.c_uint32, _U32_P, C.c_int32, _EV_P, C.c_int32, _EV_P]),
     "zyxb_program_release": (C.c_int32, [_CTX, C.c_int32, C.c_uint32]),
     "zyxb_program_set_step": (C.c_int32, [_CTX, C.c_int32, C.c_uint32, C.c_uint64]),
+    "zyxb_program_get_step": (C.c_int32, [_CTX, C.c_int32, C.c_uint32, C.POINTER(C.c_uint64)]),
     "zyxb_capture_begin": (C.c_int32, [_CTX, C.c_int32]),
     "zyxb_capture_end": (C.c_int32, [_CTX, C.c_int32, _U32_P]),
     "zyxb_graph_launch": (C.c_int32, [_CTX, C.c_int32, C.c_uint32, _EV_P, C.c_int32, _EV_P]),

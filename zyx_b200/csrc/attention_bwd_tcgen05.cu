@@ -88,7 +88,7 @@ __device__ __forceinline__ void write_tile_row(uint8_t* tile, uint32_t row, int 
 namespace dqk {
 constexpr int NS = 4;                      // K_j / V_j stages: a tile is requested three iterations before its first use
 constexpr int Q_OFF = 0, DO_OFF = AB_BIG, KV_OFF = 2 * AB_BIG, STAGE = 2 * AB_SMALL, DS_OFF = KV_OFF + NS * STAGE;
-constexpr int BAR_OFF = DS_OFF + AB_PT, SMEM_TOTAL = BAR_OFF + 256 + 1024;
+constexpr int BAR_OFF = DS_OFF + 2 * AB_PT, SMEM_TOTAL = BAR_OFF + 256 + 1024;   // dS is double-buffered
 }  // namespace dqk
 
 __global__ void __launch_bounds__(AB_THREADS, 1)
@@ -105,8 +105,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   auto kv_empty = [&](int s) { return bar + 8u * (1 + NS + s); };
   auto sdp_full = [&](int b) { return bar + 8u * (1 + 2 * NS + b); };
   auto sdp_empty = [&](int b) { return bar + 8u * (3 + 2 * NS + b); };
-  const uint32_t ds_full = bar + 8u * (5 + 2 * NS), ds_empty = bar + 8u * (6 + 2 * NS);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + BAR_OFF + 8 * (7 + 2 * NS));
+  const uint32_t ds_full = bar + 8u * (5 + 2 * NS);
+  auto ds_empty = [&](int b) { return bar + 8u * (6 + 2 * NS + b); };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + BAR_OFF + 8 * (8 + 2 * NS));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -120,7 +121,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     for (int s = 0; s < NS; ++s) { mbar_init(kv_full(s), 1); mbar_init(kv_empty(s), 1); }
     for (int s = 0; s < 2; ++s) { mbar_init(sdp_full(s), 1); mbar_init(sdp_empty(s), AB_EW_WARPS); }
     mbar_init(ds_full, AB_EW_WARPS);
-    mbar_init(ds_empty, 1);
+    mbar_init(ds_empty(0), 1); mbar_init(ds_empty(1), 1);
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -198,10 +199,10 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         const uint32_t k_addr = base + KV_OFF + (j % NS) * STAGE;
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)     // 16 keys per instruction; K_j read MN-major: rows of 128 B, the two d chunks 8 KB apart
-          umma_f16(tmem_dq, make_smem_desc(base + DS_OFF + kk * 32, 16, 1024),
+          umma_f16(tmem_dq, make_smem_desc(base + DS_OFF + (j & 1) * AB_PT + kk * 32, 16, 1024),
                    make_smem_desc(k_addr + kk * (16 * 128), AB_SMALL / 2, 1024), idesc_dq, (j != 0 || kk != 0) ? 1u : 0u);
         umma_commit(kv_empty(j % NS));
-        umma_commit(ds_empty);
+        umma_commit(ds_empty(j & 1));
       }
     }
   } else {
@@ -239,13 +240,13 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         const float g0 = p0 * (__uint_as_float(d[2 * i]) - dl) * p.scale, g1 = p1 * (__uint_as_float(d[2 * i + 1]) - dl) * p.scale;
         pk[i] = pack2(g0, g1, bf16);
       }
-      if (!mbar_wait(ds_empty, (j & 1) ^ 1, abort_flag, p.status, AB_ERR_EW)) { ok = false; break; }
-      write_tile_row(base_ptr + DS_OFF, row, half, pk);
+      if (!mbar_wait(ds_empty(sb), ((j >> 1) & 1) ^ 1, abort_flag, p.status, AB_ERR_EW)) { ok = false; break; }   // read two tiles ago
+      write_tile_row(base_ptr + DS_OFF + sb * AB_PT, row, half, pk);
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(ds_full);
     }
-    if (ok && mbar_wait(ds_empty, (n_kv - 1) & 1, abort_flag, p.status, AB_ERR_EW)) {
+    if (ok && mbar_wait(ds_empty((n_kv - 1) & 1), ((n_kv - 1) >> 1) & 1, abort_flag, p.status, AB_ERR_EW)) {
       tc_fence_after();
       uint16_t* out = reinterpret_cast<uint16_t*>(p.dq) + (int64_t)b * p.stride_batch + (int64_t)grow * p.ld + (int64_t)h * 128 + half * 64;
 #pragma unroll 1
@@ -268,8 +269,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 // ---- dK, dV ------------------------------------------------------------------------------------------------
 namespace dkv {
 constexpr int NS = 3;                      // Q_i / dO_i stages
-constexpr int K_OFF = 0, V_OFF = AB_BIG, QDO_OFF = 2 * AB_BIG, STAGE = 2 * AB_SMALL, PT_OFF = QDO_OFF + NS * STAGE, DST_OFF = PT_OFF + AB_PT;
-constexpr int BAR_OFF = DST_OFF + AB_PT, SMEM_TOTAL = BAR_OFF + 256 + 1024;
+constexpr int K_OFF = 0, V_OFF = AB_BIG, QDO_OFF = 2 * AB_BIG, STAGE = 2 * AB_SMALL, PT_OFF = QDO_OFF + NS * STAGE, DST_OFF = PT_OFF + 2 * AB_PT;
+constexpr int BAR_OFF = DST_OFF + 2 * AB_PT, SMEM_TOTAL = BAR_OFF + 256 + 1024;   // P^T and dS^T are double-buffered
 }  // namespace dkv
 
 __global__ void __launch_bounds__(AB_THREADS, 1)
@@ -286,9 +287,10 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
   auto qdo_empty = [&](int s) { return bar + 8u * (1 + NS + s); };
   auto sdp_full = [&](int b) { return bar + 8u * (1 + 2 * NS + b); };
   auto sdp_empty = [&](int b) { return bar + 8u * (3 + 2 * NS + b); };
-  const uint32_t pt_full = bar + 8u * (5 + 2 * NS), pt_empty = bar + 8u * (6 + 2 * NS), dst_full = bar + 8u * (7 + 2 * NS),
-                 dst_empty = bar + 8u * (8 + 2 * NS);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + BAR_OFF + 8 * (9 + 2 * NS));
+  const uint32_t pt_full = bar + 8u * (5 + 2 * NS), dst_full = bar + 8u * (6 + 2 * NS);
+  auto pt_empty = [&](int b) { return bar + 8u * (7 + 2 * NS + b); };
+  auto dst_empty = [&](int b) { return bar + 8u * (9 + 2 * NS + b); };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + BAR_OFF + 8 * (11 + 2 * NS));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -301,8 +303,8 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     mbar_init(kv_full, 1);
     for (int s = 0; s < NS; ++s) { mbar_init(qdo_full(s), 1); mbar_init(qdo_empty(s), 1); }
     for (int s = 0; s < 2; ++s) { mbar_init(sdp_full(s), 1); mbar_init(sdp_empty(s), AB_EW_WARPS); }
-    mbar_init(pt_full, AB_EW_WARPS); mbar_init(pt_empty, 1);
-    mbar_init(dst_full, AB_EW_WARPS); mbar_init(dst_empty, 1);
+    mbar_init(pt_full, AB_EW_WARPS); mbar_init(dst_full, AB_EW_WARPS);
+    for (int s = 0; s < 2; ++s) { mbar_init(pt_empty(s), 1); mbar_init(dst_empty(s), 1); }
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -380,17 +382,17 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)     // dV += P^T . dO_i, 16 queries per instruction, dO_i read MN-major
-          umma_f16(tmem_dv, make_smem_desc(base + PT_OFF + kk * 32, 16, 1024),
+          umma_f16(tmem_dv, make_smem_desc(base + PT_OFF + (i & 1) * AB_PT + kk * 32, 16, 1024),
                    make_smem_desc(do_addr + kk * (16 * 128), AB_SMALL / 2, 1024), idesc_acc, (i != 0 || kk != 0) ? 1u : 0u);
-        umma_commit(pt_empty);
+        umma_commit(pt_empty(i & 1));
         if (!mbar_wait(dst_full, i & 1, abort_flag, p.status, AB_ERR_MMA)) { ok = false; break; }
         tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)     // dK += dS^T . Q_i
-          umma_f16(tmem_dk, make_smem_desc(base + DST_OFF + kk * 32, 16, 1024),
+          umma_f16(tmem_dk, make_smem_desc(base + DST_OFF + (i & 1) * AB_PT + kk * 32, 16, 1024),
                    make_smem_desc(q_addr + kk * (16 * 128), AB_SMALL / 2, 1024), idesc_acc, (i != 0 || kk != 0) ? 1u : 0u);
         umma_commit(qdo_empty(i % NS));
-        umma_commit(dst_empty);
+        umma_commit(dst_empty(i & 1));
       }
     }
   } else {
@@ -432,8 +434,8 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       }
 #pragma unroll
       for (int i2 = 0; i2 < 16; ++i2) pk[i2] = pack2(pr[2 * i2], pr[2 * i2 + 1], bf16);
-      if (!mbar_wait(pt_empty, (i & 1) ^ 1, abort_flag, p.status, AB_ERR_EW)) { ok = false; break; }
-      write_tile_row(base_ptr + PT_OFF, row, half, pk);
+      if (!mbar_wait(pt_empty(sb), ((i >> 1) & 1) ^ 1, abort_flag, p.status, AB_ERR_EW)) { ok = false; break; }   // read two tiles ago
+      write_tile_row(base_ptr + PT_OFF + sb * AB_PT, row, half, pk);
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(pt_full);
@@ -449,13 +451,13 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       }
 #pragma unroll
       for (int i2 = 0; i2 < 16; ++i2) pk[i2] = pack2(pr[2 * i2], pr[2 * i2 + 1], bf16);
-      if (!mbar_wait(dst_empty, (i & 1) ^ 1, abort_flag, p.status, AB_ERR_EW)) { ok = false; break; }
-      write_tile_row(base_ptr + DST_OFF, row, half, pk);
+      if (!mbar_wait(dst_empty(sb), ((i >> 1) & 1) ^ 1, abort_flag, p.status, AB_ERR_EW)) { ok = false; break; }
+      write_tile_row(base_ptr + DST_OFF + sb * AB_PT, row, half, pk);
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(dst_full);
     }
-    if (ok && mbar_wait(dst_empty, (n_q - 1) & 1, abort_flag, p.status, AB_ERR_EW)) {
+    if (ok && mbar_wait(dst_empty((n_q - 1) & 1), ((n_q - 1) >> 1) & 1, abort_flag, p.status, AB_ERR_EW)) {
       tc_fence_after();
       const int64_t off = (int64_t)b * p.stride_batch + (int64_t)gkey * p.ld + (int64_t)h * 128 + half * 64;
       uint16_t* out_v = reinterpret_cast<uint16_t*>(p.dv) + off;

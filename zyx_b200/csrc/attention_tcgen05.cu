@@ -6,7 +6,7 @@
 // The row-wise log-sum-exp is stored for a backward pass.
 //
 // Two CTAs of 192 threads per SM (112 KB of shared memory and 256 TMEM columns each), key tiles of 64:
-//   warp 0      TMA producer (one lane): Q once, then K_j and V_j into 2-stage rings
+//   warp 0      TMA producer (one lane): Q once, then K_j into a 2-stage ring and V_j into a single stage
 //   warp 1      MMA issuer   (one lane): S_{j+1} = Q.K_{j+1}^T is issued before P_j.V_j, so the tensor core works on the
 //               next scores while the softmax warps work on the current ones (S is double-buffered in TMEM)
 //   warps 2..5  softmax      : thread = query row = TMEM lane; row maximum and sum stay in registers
@@ -31,10 +31,10 @@ constexpr int AT_Q_BYTES = AT_BM * AT_D * 2;                 // 32 KB: two boxes
 constexpr int AT_KV_BYTES = AT_BN * AT_D * 2;                // 16 KB: two boxes of [64 keys x 64 d]
 constexpr int AT_P_BYTES = AT_BM * AT_BN * 2;                // 16 KB: [128 rows x 64 keys]
 constexpr int AT_Q_OFF = 0, AT_K_OFF = AT_Q_BYTES, AT_V_OFF = AT_K_OFF + 2 * AT_KV_BYTES;
-constexpr int AT_P_OFF = AT_V_OFF + 2 * AT_KV_BYTES;
-constexpr int AT_BAR_OFF = AT_P_OFF + AT_P_BYTES;
-// 112 KB + barriers: two CTAs per SM fit only without alignment slack, so the kernel requires the dynamic shared memory
-// window to start on a 1024-byte boundary (it does when the kernel has no static shared memory) and reports otherwise
+constexpr int AT_P_OFF = AT_V_OFF + AT_KV_BYTES;            // V is single-buffered (measured: a second stage changes nothing)
+constexpr int AT_BAR_OFF = AT_P_OFF + 2 * AT_P_BYTES;        // P is double-buffered: the softmax of tile j+1 does not wait for P_j.V_j
+// no alignment slack: the kernel requires the dynamic shared memory window to start on a 1024-byte boundary (it does
+// when the kernel has no static shared memory) and reports through the status word otherwise
 constexpr int AT_SMEM_TOTAL = AT_BAR_OFF + 256;
 enum { AT_ERR_PRODUCER = 16u, AT_ERR_MMA = 32u, AT_ERR_SOFTMAX = 64u, AT_ERR_ALIGN = 1024u };
 
@@ -67,7 +67,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   auto s_full = [&](int b) { return bar + 8u * (9 + b); };
   auto s_empty = [&](int b) { return bar + 8u * (11 + b); };
   const uint32_t p_full = bar + 8u * 13, pv_done = bar + 8u * 14;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + AT_BAR_OFF + 8 * 15);
+  auto p_empty = [&](int b) { return bar + 8u * (15 + b); };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + AT_BAR_OFF + 8 * 17);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -83,6 +84,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     for (int i = 0; i < 2; ++i) { mbar_init(s_full(i), 1); mbar_init(s_empty(i), AT_SOFTMAX_WARPS); }
     mbar_init(p_full, AT_SOFTMAX_WARPS);
     mbar_init(pv_done, 1);
+    mbar_init(p_empty(0), 1); mbar_init(p_empty(1), 1);
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -107,10 +109,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         const uint32_t k_dst = base + AT_K_OFF + s * AT_KV_BYTES;
         mbar_expect_tx(k_full(s), AT_KV_BYTES);
         for (int c = 0; c < 2; ++c) tma_load_4d(k_dst + c * (AT_KV_BYTES / 2), &map_k, k_full(s), c * 64, (int)(j * AT_BN), (int)h, (int)b);
-        if (!mbar_wait(v_empty(s), ((j >> 1) & 1) ^ 1, abort_flag, p.status, AT_ERR_PRODUCER)) { ok = false; ++issued; break; }
-        mbar_expect_tx(v_full(s), AT_KV_BYTES);
+        if (!mbar_wait(v_empty(0), (j & 1) ^ 1, abort_flag, p.status, AT_ERR_PRODUCER)) { ok = false; ++issued; break; }
+        mbar_expect_tx(v_full(0), AT_KV_BYTES);
         for (int c = 0; c < 2; ++c)
-          tma_load_4d(base + AT_V_OFF + s * AT_KV_BYTES + c * (AT_KV_BYTES / 2), &map_v, v_full(s), c * 64, (int)(j * AT_BN), (int)h, (int)b);
+          tma_load_4d(base + AT_V_OFF + c * (AT_KV_BYTES / 2), &map_v, v_full(0), c * 64, (int)(j * AT_BN), (int)h, (int)b);
         ++issued; ++v_issued;
       }
       if (!ok) {   // drain: wait (bounded) for copies still in flight so none lands after the CTA has gone
@@ -119,10 +121,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           const uint32_t j = issued - 1 - i;
           while (!mbar_try_wait(k_full(j & 1), (j >> 1) & 1) && global_timer_ns() - t0 < TC_WAIT_NS) {}
         }
-        for (uint32_t i = 0; i < 2 && i < v_issued; ++i) {
-          const uint32_t j = v_issued - 1 - i;
-          while (!mbar_try_wait(v_full(j & 1), (j >> 1) & 1) && global_timer_ns() - t0 < TC_WAIT_NS) {}
-        }
+        if (v_issued) while (!mbar_try_wait(v_full(0), (v_issued - 1) & 1) && global_timer_ns() - t0 < TC_WAIT_NS) {}
         while (!mbar_try_wait(q_full, 0) && global_timer_ns() - t0 < TC_WAIT_NS) {}
       }
     }
@@ -154,15 +153,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           issue_s(jn);
         }
         if (!mbar_wait(p_full, j & 1, abort_flag, p.status, AT_ERR_MMA)) { ok = false; break; }
-        if (!mbar_wait(v_full(j & 1), (j >> 1) & 1, abort_flag, p.status, AT_ERR_MMA)) { ok = false; break; }
+        if (!mbar_wait(v_full(0), j & 1, abort_flag, p.status, AT_ERR_MMA)) { ok = false; break; }
         tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < AT_BN / 16; ++kk)   // 16 keys per instruction; V rows are 128 B of one 64-wide d chunk, chunks 8 KB apart
-          umma_f16(tmem_o, make_smem_desc(base + AT_P_OFF + kk * 32, 16, 1024),
-                   make_smem_desc(base + AT_V_OFF + (j & 1) * AT_KV_BYTES + kk * (16 * 128), AT_KV_BYTES / 2, 1024), idesc_pv,
-                   (j != 0 || kk != 0) ? 1u : 0u);
-        umma_commit(v_empty(j & 1));       // V_j has been read
-        umma_commit(pv_done);              // O holds tiles 0..j; P may be overwritten
+          umma_f16(tmem_o, make_smem_desc(base + AT_P_OFF + (j & 1) * AT_P_BYTES + kk * 32, 16, 1024),
+                   make_smem_desc(base + AT_V_OFF + kk * (16 * 128), AT_KV_BYTES / 2, 1024), idesc_pv, (j != 0 || kk != 0) ? 1u : 0u);
+        umma_commit(v_empty(0));           // V_j has been read
+        umma_commit(pv_done);              // O holds tiles 0..j
+        umma_commit(p_empty(j & 1));       // this P buffer may be overwritten (signalled after pv_done: a warp that has seen
+                                           // P_{j}'s buffer free may rely on pv_done having reached phase j as well)
       }
     }
   } else {
@@ -195,26 +195,27 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       const float m_new = fmaxf(m, mx * p.scale_log2);
       const bool same = m_new == m;
       const float alpha = same ? 1.0f : ex2f(m - m_new);     // first tile: exp2(-inf) = 0
-      // P may be overwritten and O rescaled once the previous P.V has completed
-      if (j > 0) {
+      // this tile's P buffer was last read by P.V two tiles ago (this also bounds how far the softmax runs ahead:
+      // P.V of tile j-2 is complete from here on)
+      if (!mbar_wait(p_empty(sb), ((j >> 1) & 1) ^ 1, abort_flag, p.status, AT_ERR_SOFTMAX)) { ok = false; break; }
+      // O is rescaled only when some row's maximum moved, and only then does the warp wait for the previous P.V
+      if (j > 0 && !__all_sync(0xffffffffu, same)) {
         if (!mbar_wait(pv_done, (j - 1) & 1, abort_flag, p.status, AT_ERR_SOFTMAX)) { ok = false; break; }
         tc_fence_after();
-        if (!__all_sync(0xffffffffu, same)) {
 #pragma unroll 1
-          for (int ch = 0; ch < 4; ++ch) {
-            uint32_t r[32];
-            tmem_ld32(tmem_o + lane_addr + ch * 32, r);
-            tmem_ld_wait();
+        for (int ch = 0; ch < 4; ++ch) {
+          uint32_t r[32];
+          tmem_ld32(tmem_o + lane_addr + ch * 32, r);
+          tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-            tmem_st32(tmem_o + lane_addr + ch * 32, r);
-          }
-          tmem_st_wait();
+          for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+          tmem_st32(tmem_o + lane_addr + ch * 32, r);
         }
+        tmem_st_wait();
       }
       // pass B: exponentials, running sum, P tile into shared memory in the swizzled K-major layout the MMA reads
       float sum = 0.0f;
-      uint8_t* p_row = base_ptr + AT_P_OFF + row * 128;
+      uint8_t* p_row = base_ptr + AT_P_OFF + sb * AT_P_BYTES + row * 128;
 #pragma unroll 1
       for (int ch = 0; ch < AT_BN / 32; ++ch) {
         uint32_t r[32];

@@ -549,6 +549,14 @@ int32_t zyxb_program_set_step(zyxb_ctx* ctx, int32_t dev, uint32_t prog, uint64_
   return ZYXB_OK;
 }
 
+int32_t zyxb_program_get_step(zyxb_ctx* ctx, int32_t dev, uint32_t prog, uint64_t* out_t) {
+  DEV_OR_FAIL(ZYXB_ERR_INCORRECT_KERNEL_ARG);
+  if (!out_t || prog == 0 || prog >= D.programs.size() || !D.programs[prog].live || D.programs[prog].desc.kind != ZYXB_KIND_OPTIM)
+    return fail(ctx, ZYXB_ERR_INCORRECT_KERNEL_ARG, "get_step: not an optimizer program");
+  *out_t = D.programs[prog].step;
+  return ZYXB_OK;
+}
+
 int32_t zyxb_launch(zyxb_ctx* ctx, int32_t dev, uint32_t prog, const uint32_t* args, int32_t n_args, const zyxb_event* wait,
                     int32_t n_wait, zyxb_event* out_event) {
   DEV_OR_FAIL(ZYXB_ERR_KERNEL_LAUNCH);

@@ -12,6 +12,7 @@
 #include <stdio.h>
 
 #include "../../../include/zyxb_host.h"
+#include "checkpoint.hpp"
 #include "plan.hpp"
 
 using namespace zyxb_host;
@@ -30,6 +31,8 @@ struct zyxb_block {
   uint32_t x = 0, target = 0, loss = 0, y = 0;
   uint32_t q = 0, k = 0, v = 0, s = 0, p = 0, attn = 0, o = 0, s1 = 0, x1 = 0, z1 = 0, h = 0, m = 0, s2 = 0;
   uint32_t dy = 0, ds2 = 0, tmp = 0, dz1 = 0, dx1 = 0, ds1 = 0, dattn = 0, dp = 0, dq = 0, dk = 0, dv = 0;
+  uint32_t lse = 0;                // fused attention: log-sum-exp per (batch, head, query), f32
+  bool fused = false;
   size_t n_forward_backward = 0;   // instructions before the optimizer launches
 };
 
@@ -80,7 +83,17 @@ int32_t build(zyxb_block* K) {
                       &K->tmp, &K->dx1, &K->ds1, &K->dattn, &K->dq, &K->dk, &K->dv})
     CHK(P.alloc(RE, b));
   for (uint32_t* b : {&K->z1, &K->h, &K->dz1}) CHK(P.alloc(RF, b));
-  for (uint32_t* b : {&K->s, &K->p, &K->dp}) CHK(P.alloc(SS, b));
+  const bool fused = c.fused_attention && dt != ZYXB_F32 && D == 128 && T % 128 == 0;
+  K->fused = fused;
+  if (fused) CHK(P.alloc(B * H * T * 4, &K->lse));
+  else for (uint32_t* b : {&K->s, &K->p, &K->dp}) CHK(P.alloc(SS, b));
+  auto attention = [&](bool backward) {
+    zyxb_kernel_desc d{};
+    d.kind = backward ? ZYXB_KIND_ATTENTION_BWD : ZYXB_KIND_ATTENTION;
+    d.u.attention.dtype = dt; d.u.attention.batch = B; d.u.attention.heads = H; d.u.attention.seq = T; d.u.attention.head_dim = D;
+    d.u.attention.scale = scale; d.u.attention.causal = c.causal;
+    return d;
+  };
   CHK(P.alloc(4, &K->loss, true));
 
   // ================================== forward ==================================
@@ -92,6 +105,9 @@ int32_t build(zyxb_block* K) {
   CHK(linear(K->x, P_WQ, P_BQ, K->q, E, E, ZYXB_EPI_BIAS, 0));
   CHK(linear(K->x, P_WK, P_BK, K->k, E, E, ZYXB_EPI_BIAS, 0));
   CHK(linear(K->x, P_WV, P_BV, K->v, E, E, ZYXB_EPI_BIAS, 0));
+  if (fused) {
+    CHK(P.launch(attention(false), {K->q, K->k, K->v, K->attn, K->lse}));
+  } else {
   {  // scores[b,h] = q[b,:,h,:] . k[b,:,h,:]^T * (1/sqrt(D))
     zyxb_kernel_desc d = gemm(dt, T, T, D, false, true, ZYXB_EPI_NONE, false, scale);
     d.u.gemm.batch = B; d.u.gemm.batch_inner = H;
@@ -110,6 +126,7 @@ int32_t build(zyxb_block* K) {
     score_view_a(d.u.gemm, H, T); head_view_b(d.u.gemm, T, E, D); head_view_c(d.u.gemm, T, E, D);
     if (c.causal) d.u.gemm.tri = ZYXB_TRI_A_LOWER;     // p is zero above the diagonal
     CHK(P.launch(d, {K->p, K->v, K->attn}));
+  }
   }
   CHK(linear(K->attn, P_WO, P_BO, K->o, E, E, ZYXB_EPI_BIAS, 0));
   CHK(P.launch(eltwise(ZYXB_EW_ADD, dt, R * E), {K->x, K->o, K->s1}));
@@ -153,6 +170,9 @@ int32_t build(zyxb_block* K) {
   CHK(linear_param_grads(K->ds1, K->attn, P_WO, P_BO, E, E));
   if (c.world > 1) P.allreduce(K->grad_bucket, group_off[1], group_off[2] - group_off[1]);
   CHK(P.launch(gemm(dt, R, E, E, false, false), {K->ds1, K->param[P_WO], K->dattn}));
+  if (fused) {
+    CHK(P.launch(attention(true), {K->q, K->k, K->v, K->attn, K->dattn, K->lse, K->dq, K->dk, K->dv}));
+  } else {
   {  // dP[b,h] = dattn[b,:,h,:] . v[b,:,h,:]^T
     zyxb_kernel_desc d = gemm(dt, T, T, D, false, true);
     d.u.gemm.batch = B; d.u.gemm.batch_inner = H;
@@ -181,6 +201,7 @@ int32_t build(zyxb_block* K) {
     d.u.gemm.trans_a = 1;   // dK[b,:,h,:] = dS[b,h]^T . q[b,:,h,:] * scale
     if (c.causal) d.u.gemm.tri = ZYXB_TRI_AT_LOWER;
     CHK(P.launch(d, {K->dp, K->q, K->dk}));
+  }
   }
   CHK(linear_param_grads(K->dv, K->x, P_WV, P_BV, E, E));
   CHK(linear_param_grads(K->dk, K->x, P_WK, P_BK, E, E));
@@ -267,6 +288,7 @@ int32_t zyxb_block_io(zyxb_block* K, uint32_t* out_x, uint32_t* out_target, uint
 
 int32_t zyxb_block_activation(zyxb_block* K, int32_t which, uint32_t* out_buf) {
   if (!K || !out_buf || which < 0 || which > 2) return ZYXB_ERR_INCORRECT_KERNEL_ARG;
+  if (which == 0 && K->fused) return ZYXB_ERR_INCORRECT_KERNEL_ARG;   // the probabilities are never materialised
   *out_buf = which == 0 ? K->p : which == 1 ? K->attn : K->x1;
   return ZYXB_OK;
 }
@@ -285,3 +307,59 @@ int32_t zyxb_block_plan_size(zyxb_block* K, int32_t* out_launches, int32_t* out_
 
 #pragma GCC visibility pop
 }  // extern "C"
+
+// ---- checkpoints (Module::save / Tensor::load of the block's tensors, zyx/src/module.rs:36-63, 436-529) ----------
+namespace {
+// labels in Module::iter_tensors order of the block (derive(Module) field paths)
+const char* const BLOCK_LABELS[N_PARAMS] = {
+    "attn.q_proj.weight", "attn.q_proj.bias", "attn.k_proj.weight", "attn.k_proj.bias", "attn.v_proj.weight", "attn.v_proj.bias",
+    "attn.out_proj.weight", "attn.out_proj.bias", "mlp.weight", "mlp.bias", "mlp2.weight", "mlp2.bias",
+    "norm1.weight", "norm1.bias", "norm2.weight", "norm2.bias"};
+
+std::vector<zyxb_host::CkptTensor> block_ckpt_tensors(zyxb_block* K) {
+  const zyxb_block_config& c = K->cfg;
+  const uint64_t E = c.dim, F = c.ffn;
+  std::vector<zyxb_host::CkptTensor> out;
+  const int n_state = c.optim.algo == ZYXB_OPT_SGD ? (c.optim.momentum != 0.0f ? 1 : 0) : 2;
+  const char* state_prefix[2] = {c.optim.algo == ZYXB_OPT_SGD ? "optim.buf." : "optim.m.", "optim.v."};
+  for (int s = -1; s < n_state; ++s)
+    for (int i = 0; i < N_PARAMS; ++i) {
+      zyxb_host::CkptTensor t;
+      t.name = std::string(s < 0 ? "" : state_prefix[s]) + BLOCK_LABELS[i];
+      t.buffer = s < 0 ? K->param[i] : K->state[s][i];
+      if (i == P_W1) t.shape = {F, E};
+      else if (i == P_W2) t.shape = {E, F};
+      else if (i == P_B1) t.shape = {F};
+      else if (i < P_W1 && i % 2 == 0) t.shape = {E, E};
+      else t.shape = {E};
+      out.push_back(std::move(t));
+    }
+  return out;
+}
+}  // namespace
+
+#pragma GCC visibility push(default)
+int32_t zyxb_block_save(zyxb_block* K, const char* path) {
+  if (!K || !path) return ZYXB_ERR_INCORRECT_KERNEL_ARG;
+  uint64_t t = 0;
+  if (K->n_forward_backward < K->plan.instrs.size()) {
+    int32_t st = zyxb_program_get_step(K->plan.ctx, K->plan.dev, K->plan.instrs[K->n_forward_backward].program, &t);
+    if (st) return K->plan.fail(st, "zyxb_program_get_step");
+  }
+  return zyxb_host::checkpoint_save(K->plan.ctx, K->plan.dev, K->cfg.dtype, block_ckpt_tensors(K), t, path, K->plan.err);
+}
+
+int32_t zyxb_block_load(zyxb_block* K, const char* path, int32_t* out_missing) {
+  if (!K || !path) return ZYXB_ERR_INCORRECT_KERNEL_ARG;
+  uint64_t t = 0;
+  bool have_t = false;
+  int32_t st = zyxb_host::checkpoint_load(K->plan.ctx, K->plan.dev, K->cfg.dtype, block_ckpt_tensors(K), &t, &have_t, out_missing, path, K->plan.err);
+  if (st || !have_t) return st;
+  for (size_t i = K->n_forward_backward; i < K->plan.instrs.size(); ++i)
+    if (K->plan.instrs[i].kind == Instr::LAUNCH) {
+      st = zyxb_program_set_step(K->plan.ctx, K->plan.dev, K->plan.instrs[i].program, t);
+      if (st) return K->plan.fail(st, "zyxb_program_set_step");
+    }
+  return ZYXB_OK;
+}
+#pragma GCC visibility pop

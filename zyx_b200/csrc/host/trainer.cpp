@@ -17,6 +17,7 @@
 #include <vector>
 
 #include "../../../include/zyxb_host.h"
+#include "checkpoint.hpp"
 
 namespace {
 
@@ -431,3 +432,45 @@ int32_t zyxb_mlp_plan_size(zyxb_mlp* M, int32_t* out_launches, int32_t* out_coll
 
 #pragma GCC visibility pop
 }  // extern "C"
+
+// ---- checkpoints (Module::save / Tensor::load of the stack's tensors, zyx/src/module.rs:36-63, 436-529) ----------
+namespace {
+std::vector<zyxb_host::CkptTensor> mlp_ckpt_tensors(zyxb_mlp* M) {
+  std::vector<zyxb_host::CkptTensor> out;
+  const int n_state = M->cfg.optim.algo == ZYXB_OPT_SGD ? (M->cfg.optim.momentum != 0.0f ? 1 : 0) : 2;
+  const char* state_prefix[2] = {M->cfg.optim.algo == ZYXB_OPT_SGD ? "optim.buf." : "optim.m.", "optim.v."};
+  for (int s = -1; s < n_state; ++s)
+    for (size_t i = 0; i < M->layers.size(); ++i) {
+      const Linear& L = M->layers[i];
+      for (int wb = 0; wb < 2; ++wb) {
+        zyxb_host::CkptTensor t;
+        t.name = std::string(s < 0 ? "" : state_prefix[s]) + "layers." + std::to_string(i) + (wb ? ".bias" : ".weight");
+        t.buffer = s < 0 ? (wb ? L.bias : L.weight) : L.state[s][wb];
+        if (wb) t.shape = {L.out_features}; else t.shape = {L.out_features, L.in_features};
+        out.push_back(std::move(t));
+      }
+    }
+  return out;
+}
+}  // namespace
+
+#pragma GCC visibility push(default)
+int32_t zyxb_mlp_save(zyxb_mlp* M, const char* path) {
+  if (!M || !path) return ZYXB_ERR_INCORRECT_KERNEL_ARG;
+  uint64_t t = 0;
+  for (const Instr& in : M->update)
+    if (in.kind == Instr::LAUNCH) { TRY(zyxb_program_get_step(M->ctx, M->dev, in.program, &t)); break; }
+  return zyxb_host::checkpoint_save(M->ctx, M->dev, M->cfg.dtype, mlp_ckpt_tensors(M), t, path, M->err);
+}
+
+int32_t zyxb_mlp_load(zyxb_mlp* M, const char* path, int32_t* out_missing) {
+  if (!M || !path) return ZYXB_ERR_INCORRECT_KERNEL_ARG;
+  uint64_t t = 0;
+  bool have_t = false;
+  int32_t st = zyxb_host::checkpoint_load(M->ctx, M->dev, M->cfg.dtype, mlp_ckpt_tensors(M), &t, &have_t, out_missing, path, M->err);
+  if (st || !have_t) return st;
+  for (const Instr& in : M->update)
+    if (in.kind == Instr::LAUNCH) TRY(zyxb_program_set_step(M->ctx, M->dev, in.program, t));
+  return ZYXB_OK;
+}
+#pragma GCC visibility pop

@@ -121,6 +121,16 @@ class Mlp:
     def update(self):
         self._check(self.lib.zyxb_mlp_update(self.h))
 
+    def save(self, path):
+        """Parameters, optimizer state and step counter into a safetensors file (Module::save)."""
+        self._check(self.lib.zyxb_mlp_save(self.h, os.fsencode(path)))
+
+    def load(self, path):
+        """-> number of the plan's tensors the file did not hold."""
+        missing = C.c_int32()
+        self._check(self.lib.zyxb_mlp_load(self.h, os.fsencode(path), C.byref(missing)))
+        return missing.value
+
     def step(self, events=None, want_event=False):
         events = [e for e in (events or []) if e.id != 0]
         arr = (L.Event * len(events))(*events) if events else None
@@ -166,7 +176,8 @@ class Mlp:
 # ---- transformer block ---------------------------------------------------------------------------------
 class BlockConfig(C.Structure):
     _fields_ = [("dtype", C.c_int32), ("batch", C.c_uint64), ("seq", C.c_uint64), ("dim", C.c_uint64), ("heads", C.c_uint64),
-                ("ffn", C.c_uint64), ("causal", C.c_int32), ("eps", C.c_float), ("optim", L.OptimDesc), ("world", C.c_int32)]
+                ("ffn", C.c_uint64), ("causal", C.c_int32), ("eps", C.c_float), ("optim", L.OptimDesc), ("world", C.c_int32),
+                ("fused_attention", C.c_int32)]
 
 
 BLOCK_SIGNATURES = {
@@ -182,16 +193,40 @@ BLOCK_SIGNATURES = {
     "zyxb_block_activation": (C.c_int32, [_P, C.c_int32, C.POINTER(C.c_uint32)]),
 }
 HOST_SIGNATURES.update(BLOCK_SIGNATURES)
+
+
+class StTensor(C.Structure):
+    _fields_ = [("name", C.c_char_p), ("dtype", C.c_int32), ("rank", C.c_int32), ("shape", C.POINTER(C.c_uint64)), ("data", C.c_void_p)]
+
+
+ST_SIGNATURES = {
+    "zyxb_st_save": (C.c_int32, [C.c_char_p, C.POINTER(StTensor), C.c_int32]),
+    "zyxb_st_open": (C.c_int32, [C.c_char_p, C.POINTER(_P)]),
+    "zyxb_st_count": (C.c_int32, [_P]),
+    "zyxb_st_info": (C.c_int32, [_P, C.c_int32, C.POINTER(C.c_char_p), C.POINTER(C.c_int32), C.POINTER(C.c_int32),
+                                 C.POINTER(C.POINTER(C.c_uint64)), C.POINTER(C.c_uint64)]),
+    "zyxb_st_find": (C.c_int32, [_P, C.c_char_p]),
+    "zyxb_st_read": (C.c_int32, [_P, C.c_int32, C.c_void_p, C.c_uint64]),
+    "zyxb_st_close": (C.c_int32, [_P]),
+    "zyxb_st_last_error": (C.c_char_p, []),
+    "zyxb_mlp_save": (C.c_int32, [_P, C.c_char_p]),
+    "zyxb_mlp_load": (C.c_int32, [_P, C.c_char_p, C.POINTER(C.c_int32)]),
+    "zyxb_block_save": (C.c_int32, [_P, C.c_char_p]),
+    "zyxb_block_load": (C.c_int32, [_P, C.c_char_p, C.POINTER(C.c_int32)]),
+}
+HOST_SIGNATURES.update(ST_SIGNATURES)
 BLOCK_PARAM_NAMES = ["wq", "bq", "wk", "bk", "wv", "bv", "wo", "bo", "w1", "b1", "w2", "b2", "g1", "be1", "g2", "be2"]
 
 
 class Block:
     """One transformer block (attention + feed-forward, post-norm) with its training plan."""
 
-    def __init__(self, session, dtype, batch, seq, dim, heads, ffn, causal=True, eps=1e-5, algo=L.OPT_ADAMW, world=1, **optim_kw):
+    def __init__(self, session, dtype, batch, seq, dim, heads, ffn, causal=True, eps=1e-5, algo=L.OPT_ADAMW, world=1, fused_attention=False,
+                 **optim_kw):
         self.lib, self.sess = load(), session
         cfg = BlockConfig()
         cfg.dtype, cfg.batch, cfg.seq, cfg.dim, cfg.heads, cfg.ffn, cfg.causal, cfg.eps, cfg.world = dtype, batch, seq, dim, heads, ffn, int(causal), eps, world
+        cfg.fused_attention = int(fused_attention)
         o = cfg.optim
         o.algo = algo
         o.lr, o.weight_decay = optim_kw.get("lr", 1e-3), optim_kw.get("weight_decay", 0.0)
@@ -243,6 +278,14 @@ class Block:
 
     def update(self):
         self._check(self.lib.zyxb_block_update(self.h))
+
+    def save(self, path):
+        self._check(self.lib.zyxb_block_save(self.h, os.fsencode(path)))
+
+    def load(self, path):
+        missing = C.c_int32()
+        self._check(self.lib.zyxb_block_load(self.h, os.fsencode(path), C.byref(missing)))
+        return missing.value
 
     def step(self, events=None):
         events = [e for e in (events or []) if e.id != 0]
