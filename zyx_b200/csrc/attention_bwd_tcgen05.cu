@@ -15,8 +15,9 @@
 // between CTAs: no atomics, no reduction pass, bit-reproducible results.
 // One shared-memory image of a [rows, 128] tile (two 128-byte-swizzled boxes of 64 columns) serves both as a K-major
 // operand (contraction over the 128 columns) and as an MN-major B operand (contraction over the rows): only the
-// descriptor differs.  320 threads: warp 0 TMA producer, warp 1 MMA issuer, warps 2..9 elementwise (two warps per TMEM
-// lane quarter, each taking half of the columns).  Every mbarrier wait is time-bounded and reports through the status word.
+// descriptor differs.  352 threads: warp 0 TMA producer, warps 1 and 10 MMA issuers (the recomputed scores / the gradient
+// accumulations: issuing an instruction occupies its thread about as long as the tensor core executes it, so two threads
+// issue side by side), warps 2..9 elementwise (two warps per TMEM lane quarter, each taking half of the columns).  Every mbarrier wait is time-bounded and reports through the status word.
 #include <cuda.h>
 #include <math_constants.h>
 
@@ -28,7 +29,7 @@
 
 namespace zyxb {
 
-constexpr int AB_THREADS = 320, AB_EW_WARPS = 8;   // barriers the elementwise warps signal count warps: one lane arrives per warp
+constexpr int AB_THREADS = 352, AB_EW_WARPS = 8;   // barriers the elementwise warps signal count warps: one lane arrives per warp
 constexpr int AB_BIG = 128 * 128 * 2;        // [128 rows x 128 d] tile, 32 KB
 constexpr int AB_SMALL = 64 * 128 * 2;       // [64 rows x 128 d] tile, 16 KB
 constexpr int AB_PT = 128 * 64 * 2;          // [128 rows x 64] probability / dS tile, 16 KB
@@ -105,9 +106,11 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   auto kv_empty = [&](int s) { return bar + 8u * (1 + NS + s); };
   auto sdp_full = [&](int b) { return bar + 8u * (1 + 2 * NS + b); };
   auto sdp_empty = [&](int b) { return bar + 8u * (3 + 2 * NS + b); };
-  const uint32_t ds_full = bar + 8u * (5 + 2 * NS);
-  auto ds_empty = [&](int b) { return bar + 8u * (6 + 2 * NS + b); };
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + BAR_OFF + 8 * (8 + 2 * NS));
+  // barriers of double-buffered tiles exist once per buffer: a role that runs a tile ahead can then never complete two
+  // phases of one barrier before its waiter has seen the first
+  auto ds_full = [&](int b) { return bar + 8u * (5 + 2 * NS + b); };
+  auto ds_empty = [&](int b) { return bar + 8u * (7 + 2 * NS + b); };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + BAR_OFF + 8 * (9 + 2 * NS));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -120,8 +123,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     mbar_init(qdo_full, 1);
     for (int s = 0; s < NS; ++s) { mbar_init(kv_full(s), 1); mbar_init(kv_empty(s), 1); }
     for (int s = 0; s < 2; ++s) { mbar_init(sdp_full(s), 1); mbar_init(sdp_empty(s), AB_EW_WARPS); }
-    mbar_init(ds_full, AB_EW_WARPS);
-    mbar_init(ds_empty(0), 1); mbar_init(ds_empty(1), 1);
+    for (int s = 0; s < 2; ++s) { mbar_init(ds_full(s), AB_EW_WARPS); mbar_init(ds_empty(s), 1); }
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -166,7 +168,6 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     if (lane == 0) {
       const bool bf16 = p.is_bf16 != 0;
       const uint32_t idesc_s = make_idesc(bf16, false, false, 128, 64);      // [128 q x d] x [64 keys x d]^T
-      const uint32_t idesc_dq = make_idesc(bf16, false, true, 128, 128);     // dS [128 q x 64 keys] x K_j [64 keys x d]
       auto issue_sdp = [&](uint32_t j) {
         const uint32_t k_addr = base + KV_OFF + (j % NS) * STAGE, v_addr = k_addr + AB_SMALL;
         const uint32_t t_s = tmem_base + (j & 1) * 64, t_dp = tmem_base + 128 + (j & 1) * 64;
@@ -184,17 +185,22 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                      make_smem_desc(v_addr + c * (AB_SMALL / 2) + kk * 32, 16, 1024), idesc_s, (c | kk) != 0 ? 1u : 0u);
         umma_commit(sdp_full(j & 1));
       };
-      bool ok = mbar_wait(qdo_full, 0, abort_flag, p.status, AB_ERR_MMA) && mbar_wait(kv_full(0), 0, abort_flag, p.status, AB_ERR_MMA);
-      if (ok) { tc_fence_after(); issue_sdp(0); }
+      bool ok = mbar_wait(qdo_full, 0, abort_flag, p.status, AB_ERR_MMA);
       for (uint32_t j = 0; j < n_kv && ok; ++j) {
-        if (j + 1 < n_kv) {
-          const uint32_t jn = j + 1;
-          if (!mbar_wait(kv_full(jn % NS), (jn / NS) & 1, abort_flag, p.status, AB_ERR_MMA)) { ok = false; break; }
-          if (!mbar_wait(sdp_empty(jn & 1), ((jn >> 1) & 1) ^ 1, abort_flag, p.status, AB_ERR_MMA)) { ok = false; break; }
-          tc_fence_after();
-          issue_sdp(jn);
-        }
-        if (!mbar_wait(ds_full, j & 1, abort_flag, p.status, AB_ERR_MMA)) { ok = false; break; }
+        if (!mbar_wait(kv_full(j % NS), (j / NS) & 1, abort_flag, p.status, AB_ERR_MMA)) { ok = false; break; }
+        if (!mbar_wait(sdp_empty(j & 1), ((j >> 1) & 1) ^ 1, abort_flag, p.status, AB_ERR_MMA)) { ok = false; break; }
+        tc_fence_after();
+        issue_sdp(j);
+      }
+    }
+  } else if (warp == 10) {
+    // second MMA issuer (issuing an instruction costs its thread about as long as the tensor core needs to execute it):
+    // dQ += dS_j . K_j, while warp 1 issues the scores of the next tiles
+    if (lane == 0) {
+      const uint32_t idesc_dq = make_idesc(p.is_bf16 != 0, false, true, 128, 128);     // dS [128 q x 64 keys] x K_j [64 keys x d]
+      bool ok = true;
+      for (uint32_t j = 0; j < n_kv && ok; ++j) {
+        if (!mbar_wait(ds_full(j & 1), (j >> 1) & 1, abort_flag, p.status, AB_ERR_MMA)) { ok = false; break; }
         tc_fence_after();
         const uint32_t k_addr = base + KV_OFF + (j % NS) * STAGE;
 #pragma unroll
@@ -244,7 +250,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       write_tile_row(base_ptr + DS_OFF + sb * AB_PT, row, half, pk);
       fence_proxy_async_smem();
       __syncwarp();
-      if (lane == 0) mbar_arrive(ds_full);
+      if (lane == 0) mbar_arrive(ds_full(sb));
     }
     if (ok && mbar_wait(ds_empty((n_kv - 1) & 1), ((n_kv - 1) >> 1) & 1, abort_flag, p.status, AB_ERR_EW)) {
       tc_fence_after();
@@ -287,10 +293,11 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
   auto qdo_empty = [&](int s) { return bar + 8u * (1 + NS + s); };
   auto sdp_full = [&](int b) { return bar + 8u * (1 + 2 * NS + b); };
   auto sdp_empty = [&](int b) { return bar + 8u * (3 + 2 * NS + b); };
-  const uint32_t pt_full = bar + 8u * (5 + 2 * NS), dst_full = bar + 8u * (6 + 2 * NS);
-  auto pt_empty = [&](int b) { return bar + 8u * (7 + 2 * NS + b); };
-  auto dst_empty = [&](int b) { return bar + 8u * (9 + 2 * NS + b); };
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + BAR_OFF + 8 * (11 + 2 * NS));
+  auto pt_full = [&](int b) { return bar + 8u * (5 + 2 * NS + b); };
+  auto dst_full = [&](int b) { return bar + 8u * (7 + 2 * NS + b); };
+  auto pt_empty = [&](int b) { return bar + 8u * (9 + 2 * NS + b); };
+  auto dst_empty = [&](int b) { return bar + 8u * (11 + 2 * NS + b); };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + BAR_OFF + 8 * (13 + 2 * NS));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -303,8 +310,9 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     mbar_init(kv_full, 1);
     for (int s = 0; s < NS; ++s) { mbar_init(qdo_full(s), 1); mbar_init(qdo_empty(s), 1); }
     for (int s = 0; s < 2; ++s) { mbar_init(sdp_full(s), 1); mbar_init(sdp_empty(s), AB_EW_WARPS); }
-    mbar_init(pt_full, AB_EW_WARPS); mbar_init(dst_full, AB_EW_WARPS);
-    for (int s = 0; s < 2; ++s) { mbar_init(pt_empty(s), 1); mbar_init(dst_empty(s), 1); }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(pt_full(s), AB_EW_WARPS); mbar_init(dst_full(s), AB_EW_WARPS); mbar_init(pt_empty(s), 1); mbar_init(dst_empty(s), 1);
+    }
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -349,7 +357,6 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     if (lane == 0) {
       const bool bf16 = p.is_bf16 != 0;
       const uint32_t idesc_st = make_idesc(bf16, false, false, 128, 64);     // [128 keys x d] x [64 q x d]^T
-      const uint32_t idesc_acc = make_idesc(bf16, false, true, 128, 128);    // [128 keys x 64 q] x [64 q x d]
       auto issue_sdp = [&](uint32_t i) {
         const uint32_t q_addr = base + QDO_OFF + (i % NS) * STAGE, do_addr = q_addr + AB_SMALL;
         const uint32_t t_s = tmem_base + (i & 1) * 64, t_dp = tmem_base + 128 + (i & 1) * 64;
@@ -367,25 +374,29 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                      make_smem_desc(do_addr + c * (AB_SMALL / 2) + kk * 32, 16, 1024), idesc_st, (c | kk) != 0 ? 1u : 0u);
         umma_commit(sdp_full(i & 1));
       };
-      bool ok = mbar_wait(kv_full, 0, abort_flag, p.status, AB_ERR_MMA) && mbar_wait(qdo_full(0), 0, abort_flag, p.status, AB_ERR_MMA);
-      if (ok) { tc_fence_after(); issue_sdp(0); }
+      bool ok = mbar_wait(kv_full, 0, abort_flag, p.status, AB_ERR_MMA);
       for (uint32_t i = 0; i < n_q && ok; ++i) {
-        if (i + 1 < n_q) {
-          const uint32_t in = i + 1;
-          if (!mbar_wait(qdo_full(in % NS), (in / NS) & 1, abort_flag, p.status, AB_ERR_MMA)) { ok = false; break; }
-          if (!mbar_wait(sdp_empty(in & 1), ((in >> 1) & 1) ^ 1, abort_flag, p.status, AB_ERR_MMA)) { ok = false; break; }
-          tc_fence_after();
-          issue_sdp(in);
-        }
+        if (!mbar_wait(qdo_full(i % NS), (i / NS) & 1, abort_flag, p.status, AB_ERR_MMA)) { ok = false; break; }
+        if (!mbar_wait(sdp_empty(i & 1), ((i >> 1) & 1) ^ 1, abort_flag, p.status, AB_ERR_MMA)) { ok = false; break; }
+        tc_fence_after();
+        issue_sdp(i);
+      }
+    }
+  } else if (warp == 10) {
+    // second MMA issuer: dV += P^T . dO_i and dK += dS^T . Q_i, while warp 1 issues the scores of the next tiles
+    if (lane == 0) {
+      const uint32_t idesc_acc = make_idesc(p.is_bf16 != 0, false, true, 128, 128);    // [128 keys x 64 q] x [64 q x d]
+      bool ok = true;
+      for (uint32_t i = 0; i < n_q && ok; ++i) {
         const uint32_t q_addr = base + QDO_OFF + (i % NS) * STAGE, do_addr = q_addr + AB_SMALL;
-        if (!mbar_wait(pt_full, i & 1, abort_flag, p.status, AB_ERR_MMA)) { ok = false; break; }
+        if (!mbar_wait(pt_full(i & 1), (i >> 1) & 1, abort_flag, p.status, AB_ERR_MMA)) { ok = false; break; }
         tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)     // dV += P^T . dO_i, 16 queries per instruction, dO_i read MN-major
           umma_f16(tmem_dv, make_smem_desc(base + PT_OFF + (i & 1) * AB_PT + kk * 32, 16, 1024),
                    make_smem_desc(do_addr + kk * (16 * 128), AB_SMALL / 2, 1024), idesc_acc, (i != 0 || kk != 0) ? 1u : 0u);
         umma_commit(pt_empty(i & 1));
-        if (!mbar_wait(dst_full, i & 1, abort_flag, p.status, AB_ERR_MMA)) { ok = false; break; }
+        if (!mbar_wait(dst_full(i & 1), (i >> 1) & 1, abort_flag, p.status, AB_ERR_MMA)) { ok = false; break; }
         tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)     // dK += dS^T . Q_i
@@ -438,7 +449,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       write_tile_row(base_ptr + PT_OFF + sb * AB_PT, row, half, pk);
       fence_proxy_async_smem();
       __syncwarp();
-      if (lane == 0) mbar_arrive(pt_full);
+      if (lane == 0) mbar_arrive(pt_full(sb));
 #pragma unroll
       for (int c4 = 0; c4 < 8; ++c4) {
         const float4 d4 = __ldg(reinterpret_cast<const float4*>(delta_bh + q0) + c4);
@@ -455,7 +466,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       write_tile_row(base_ptr + DST_OFF + sb * AB_PT, row, half, pk);
       fence_proxy_async_smem();
       __syncwarp();
-      if (lane == 0) mbar_arrive(dst_full);
+      if (lane == 0) mbar_arrive(dst_full(sb));
     }
     if (ok && mbar_wait(dst_empty((n_q - 1) & 1), ((n_q - 1) >> 1) & 1, abort_flag, p.status, AB_ERR_EW)) {
       tc_fence_after();
