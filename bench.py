@@ -745,6 +745,8 @@ class BlockTrain:
         out_frac = sum(min(T // 256, t // 2 + 1) for t in range(n_t)) / float(n_t * (T // 256)) if T % 256 == 0 else 1.0
         k_frac = sum((t + 1) * 2 for t in range(n_t)) / float(n_t * (T // 64)) if T % 128 == 0 else 1.0
         attn_exec = (attn / 2) * (2 * out_frac + 4 * k_frac)
+        if self.fused:   # 128 x 128 tiles on and below the diagonal; 2 products forward, 7 backward (both backward kernels recompute S and dP)
+            attn_exec = (attn / 2) * 9 * (n_t * (n_t + 1) / 2.0) / float(n_t * n_t) if T % 128 == 0 else 9 * attn / 2
         self.gemm_flops = self.gemm_flops_dense - 3.0 * attn + attn_exec             # FLOPs the kernels execute
         self.h2d_bytes, self.d2h_bytes = 2 * R * E * 2, 4
 
@@ -824,7 +826,7 @@ def make_workload(args, rank=0, world=1):
     if args.workload == "simplenet":
         return SimpleNet(size=args.size, rank=rank, world=world)
     if args.workload == "block":
-        return BlockTrain(size=args.size, rank=rank, world=world, fused=args.fused_attention)
+        return BlockTrain(size=args.size, rank=rank, world=world, fused=not args.unfused_attention)
     if args.size:
         return {"rowreduce": lambda: RowReduce(rows=args.size), "attn_rows": lambda: AttnRows(rows=args.size), "attention": lambda: AttentionFwd(args.size), "gemm_bf16": lambda: Gemm("bf16", args.size),
                 "gemm_f32": lambda: Gemm("f32", args.size)}[args.workload]()
@@ -882,7 +884,8 @@ def run():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--workload", default="mlp", choices=sorted(WORKLOADS))
-    ap.add_argument("--fused-attention", action="store_true", help="block: run attention as the fused forward / backward programs")
+    ap.add_argument("--unfused-attention", action="store_true",
+                    help="block: materialise scores and probabilities as the reference does instead of the fused attention programs")
     ap.add_argument("--standard-adamw", action="store_true", help="mlp: textbook AdamW instead of the reference's literal update")
     ap.add_argument("--impl", default="zyx_b200", choices=["zyx_b200", "reference"])
     ap.add_argument("--e2e-steps", type=int, default=3)
