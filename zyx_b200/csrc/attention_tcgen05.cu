@@ -219,8 +219,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       xm[half * 128 + row] = mx;
       pair_sync();
       mx = fmaxf(mx, xm[(half ^ 1) * 128 + row]);
-      const float m_new = fmaxf(m, mx * p.scale_log2);       // a half that is wholly masked contributes -inf; the row is not
-      const bool same = m_new == m;
+      // The reference point m of the exponentials follows the running maximum lazily: it moves only when the maximum has
+      // grown by more than 2^8 beyond it, so exponentials stay below 256 (exact enough in the 16-bit operand, far from
+      // overflow in the f32 sums) and the output tile is rescaled a few times per row instead of at almost every tile.
+      // Normalising by the sum at the end makes the result independent of the reference point.
+      const float m_seen = fmaxf(m, mx * p.scale_log2);      // a half that is wholly masked contributes -inf; the row is not
+      const bool same = !(m_seen - m > 8.0f);                // first tile: m = -inf, the difference is +inf
+      const float m_new = same ? m : m_seen;
       const float alpha = same ? 1.0f : ex2f(m - m_new);     // first tile: exp2(-inf) = 0
       // exponentials of this thread's 64 keys, rounded to the storage type as the tensor-core operand
       float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
