@@ -726,6 +726,7 @@ class BlockTrain:
     """Config 5: one transformer block (MultiheadAttention + MLP, post-norm), d_model 2048, 16 heads x 128, FFN 8192, seq 2048,
     batch 8 split across the GPUs, bf16, causal, weights N(0, 0.02), inputs and targets N(0,1): forward + backward (+ AdamW)."""
     E, H, F, T, GLOBAL_B = 2048, 16, 8192, 2048, 8
+    scaling = "strong"      # the global batch of 8 is divided over the ranks (one sample per GPU at 8 GPUs)
     unit, dtype, bound = "samples/s", "bf16", "tensor"
 
     def __init__(self, size=0, rank=0, world=1, fused=False):
@@ -979,7 +980,7 @@ def run():
 
     if rank == 0:
         line = {"metric": w.metric, "value": value, "unit": w.unit, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-                "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": w.dtype,
+                "ms_per_step": ms_step, "higher_is_better": True, "scaling": getattr(w, "scaling", "weak"), "vs_baseline": None, "dtype": w.dtype,
                 "data": "synthetic", "config": w.config, "roofline": roofline, "kernels": kernels, "e2e": e2e,
                 "gpu_launches": int(launches), "clocks": clocks, "max_rel_err_sampled": err}
         if getattr(w, "losses", None):
