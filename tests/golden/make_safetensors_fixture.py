@@ -43,4 +43,6 @@ def main(root):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        sys.exit("usage: make_safetensors_fixture.py /path/to/zyx-checkout")
+    main(sys.argv[1])

@@ -39,9 +39,12 @@ def test_writer_emits_the_reference_header_byte_for_byte(tmp_path):
     assert len(raw) == REF["file_bytes"]
 
 
-@pytest.mark.skipif(not os.path.exists("/root/reference/zyx/tests/xyz2.safetensors"), reason="the reference checkout is not on this machine")
+REF_CHECKOUT = os.environ.get("ZYX_REFERENCE", "")       # path of a zyx checkout, when one is at hand
+
+
+@pytest.mark.skipif(not os.path.exists(os.path.join(REF_CHECKOUT, "zyx/tests/xyz2.safetensors")), reason="ZYX_REFERENCE does not point at a zyx checkout")
 def test_reads_the_reference_file_itself():
-    t = st.load("/root/reference/zyx/tests/xyz2.safetensors")
+    t = st.load(os.path.join(REF_CHECKOUT, "zyx/tests/xyz2.safetensors"))
     for k, a in t.items():
         assert hashlib.sha256(a.tobytes()).hexdigest() == REF["sha256"][k]
 
