@@ -21,6 +21,8 @@ struct GemmParams {
   float alpha;
   int rn;
   bool vec_a, vec_b;
+  int splits;        // SIMT path: > 1 = the k range is divided over this many CTAs per tile, partial sums go to `partial`
+  void* partial;     // [batch][splits][m][n] accumulators (f32 / i32) in the context's scratch
 };
 
 int launch_gemm_simt(GemmParams p, int dtype, const LaunchCtx& lc, std::string& err);

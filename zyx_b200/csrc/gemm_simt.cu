@@ -9,6 +9,8 @@
 // staged through shared memory as [k][m] / [k][n] so that the inner product reads two
 // conflict-free float4 per operand per k; the next k-tile is fetched into registers while
 // the current one is multiplied (one barrier per k-tile).
+#include <algorithm>
+
 #include "common.cuh"
 #include "eltwise_math.cuh"
 #include "gemm.h"
@@ -47,7 +49,8 @@ __global__ void __launch_bounds__(STHREADS) gemm_simt_kernel(GemmParams p) {
   const int tid = threadIdx.x;
   const int64_t m = p.m, n = p.n, k = p.k;
   const int64_t m0 = (int64_t)blockIdx.y * SBM, n0 = (int64_t)blockIdx.x * SBN;
-  const int64_t zo = blockIdx.z / p.batch_inner, zi = blockIdx.z % p.batch_inner;
+  const int64_t bz = blockIdx.z / p.splits, split = blockIdx.z % p.splits;
+  const int64_t zo = bz / p.batch_inner, zi = bz % p.batch_inner;
   const S* A = reinterpret_cast<const S*>(p.a) + zo * p.stride_a + zi * p.stride_a_inner;
   const S* B = reinterpret_cast<const S*>(p.b) + zo * p.stride_b + zi * p.stride_b_inner;
   const int64_t lda = (int64_t)p.lda, ldb = (int64_t)p.ldb, ldc = (int64_t)p.ldc;
@@ -108,11 +111,15 @@ __global__ void __launch_bounds__(STHREADS) gemm_simt_kernel(GemmParams p) {
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[i][j] = (ACC)0;
 
-  const int64_t n_tiles = (k + SBK - 1) / SBK;
-  fetch_tile(0);
-  stage_tile(0);
+  const int64_t all_tiles = (k + SBK - 1) / SBK;
+  const int64_t per_split = (all_tiles + p.splits - 1) / p.splits;
+  const int64_t t_first = split * per_split, n_tiles = min(all_tiles, t_first + per_split);   // this CTA's k-tiles: [t_first, n_tiles)
+  if (t_first < n_tiles) {
+    fetch_tile(t_first * SBK);
+    stage_tile((int)(t_first & 1));
+  }
   __syncthreads();
-  for (int64_t t = 0; t < n_tiles; ++t) {
+  for (int64_t t = t_first; t < n_tiles; ++t) {
     const int buf = (int)(t & 1);
     if (t + 1 < n_tiles) fetch_tile((t + 1) * SBK);
 #pragma unroll
@@ -139,6 +146,20 @@ __global__ void __launch_bounds__(STHREADS) gemm_simt_kernel(GemmParams p) {
     }
   }
 
+  if (p.splits > 1) {   // partial sums of this k range; gemm_splitk_finish_kernel adds them in order and applies the epilogue
+    ACC* part = reinterpret_cast<ACC*>(p.partial) + ((bz * p.splits + split) * m) * n;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int64_t r = m0 + (i / 4) * 64 + ty * 4 + (i % 4);
+      if (r >= m) continue;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int64_t c = n0 + (j / 4) * 64 + tx * 4 + (j % 4);
+        if (c < n) part[r * n + c] = acc[i][j];
+      }
+    }
+    return;
+  }
   // epilogue: alpha, bias, activation; optional second output with the pre-activation
   S* C = reinterpret_cast<S*>(p.c) + c_off;
   S* Z = p.preact ? reinterpret_cast<S*>(p.preact) + c_off : nullptr;
@@ -182,6 +203,45 @@ __global__ void __launch_bounds__(STHREADS) gemm_simt_kernel(GemmParams p) {
   }
 }
 
+// Second pass of a split-k matmul: the partial sums of each output element are added in split order (so the result does
+// not depend on which CTA finished first) and the epilogue is applied.
+template <typename T, typename ACC>
+__global__ void __launch_bounds__(256) gemm_splitk_finish_kernel(GemmParams p) {
+  using S = typename Elem<T>::store_t;
+  const int64_t m = p.m, n = p.n, ldc = (int64_t)p.ldc;
+  const int64_t per = m * n, total = per * (int64_t)(p.batch * p.batch_inner);
+  const ACC* part = reinterpret_cast<const ACC*>(p.partial);
+  const S* bias = reinterpret_cast<const S*>(p.bias);
+  const bool rn = p.rn != 0;
+  for (int64_t idx = (int64_t)blockIdx.x * 256 + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * 256) {
+    const int64_t bz = idx / per, e = idx % per, r = e / n, c = e % n;
+    const int64_t zo = bz / p.batch_inner, zi = bz % p.batch_inner;
+    const int64_t off = zo * p.stride_c + zi * p.stride_c_inner + r * ldc + c;
+    ACC sum = (ACC)0;
+    for (int s = 0; s < p.splits; ++s) {
+      const ACC v = part[(bz * p.splits + s) * per + e];
+      if constexpr (std::is_same_v<ACC, float>) sum += v; else sum = (ACC)((uint32_t)sum + (uint32_t)v);
+    }
+    S* C = reinterpret_cast<S*>(p.c);
+    if constexpr (std::is_same_v<ACC, float>) {
+      const GeluConsts gc = gelu_consts<T>();
+      const S* zin = reinterpret_cast<const S*>(p.z);
+      float v = sum;
+      if (p.alpha != 1.0f) v *= const_cast_dtype<T>(p.alpha);
+      if (p.epilogue >= ZYXB_EPI_BIAS && p.epilogue <= ZYXB_EPI_BIAS_GELU) v += (float)Elem<T>::load(bias[c]);
+      if (p.preact) reinterpret_cast<S*>(p.preact)[off] = Elem<T>::store(v, rn);
+      if (p.epilogue == ZYXB_EPI_BIAS_RELU) v = relu_ref(v);
+      else if (p.epilogue == ZYXB_EPI_BIAS_GELU) v = gelu_ref<T>(v, gc);
+      else if (p.epilogue == ZYXB_EPI_MUL_RELU_GRAD) v *= ((float)Elem<T>::load(zin[off]) > 0.0f ? 1.0f : 0.0f);
+      else if (p.epilogue == ZYXB_EPI_MUL_GELU_GRAD) v *= gelu_grad_ref<T>((float)Elem<T>::load(zin[off]), gc);
+      else if (p.epilogue == ZYXB_EPI_ADD) v += (float)Elem<T>::load(zin[off]);
+      C[off] = Elem<T>::store(v, rn);
+    } else {
+      C[off] = sum;
+    }
+  }
+}
+
 template <typename T, typename ACC>
 static void launch_simt_t(const GemmParams& p, dim3 grid, cudaStream_t s) {
   if (p.trans_a) {
@@ -196,7 +256,17 @@ static void launch_simt_t(const GemmParams& p, dim3 grid, cudaStream_t s) {
 int launch_gemm_simt(GemmParams p, int dtype, const LaunchCtx& lc, std::string& err) {
   const uint64_t gx = (p.n + SBN - 1) / SBN, gy = (p.m + SBM - 1) / SBM;
   ZYXB_CHECK_ARG(gy <= 65535 && p.batch * p.batch_inner <= 65535, "gemm: m or batch too large for the SIMT path");
-  dim3 grid((unsigned)gx, (unsigned)gy, (unsigned)(p.batch * p.batch_inner));
+  // Few output tiles and a long k: divide k over several CTAs per tile (a [64, 784] x [784, 128] Linear is one tile and
+  // would occupy one SM for 49 k-steps), partial sums in the context's scratch, a second launch adds them in order.
+  const uint64_t n_mat = p.batch * p.batch_inner, tiles = gx * gy * n_mat, k_tiles = (p.k + SBK - 1) / SBK;
+  p.splits = 1;
+  p.partial = lc.scratch;
+  if (tiles * 2 <= (uint64_t)lc.sm_count && k_tiles >= 16) {   // k >= 256: shorter sums are not worth a second launch
+    uint64_t s = std::min<uint64_t>({k_tiles / 2, ((uint64_t)lc.sm_count + tiles - 1) / tiles, (uint64_t)32});
+    while (s > 1 && n_mat * s * p.m * p.n * 4 > lc.scratch_bytes) --s;
+    if (s > 1 && n_mat * s <= 65535) p.splits = (int)s;
+  }
+  dim3 grid((unsigned)gx, (unsigned)gy, (unsigned)(n_mat * p.splits));
   // one aligned access per 4 elements needs the contiguous extent, the batch stride and the base aligned
   const uint64_t es = dtype_size(dtype);
   const uint64_t align_elems = 4;   // one access of 4 elements: 16 B for 4-byte, 8 B for 2-byte types
@@ -210,6 +280,16 @@ int launch_gemm_simt(GemmParams p, int dtype, const LaunchCtx& lc, std::string& 
     case ZYXB_F16: launch_simt_t<f16_t, float>(p, grid, lc.stream); break;
     case ZYXB_I32: launch_simt_t<int32_t, int32_t>(p, grid, lc.stream); break;
     default: err = "gemm: dtype"; return ZYXB_ERR_INCORRECT_KERNEL_ARG;
+  }
+  if (p.splits > 1) {
+    const unsigned fgrid = (unsigned)std::min<uint64_t>((n_mat * p.m * p.n + 255) / 256, (uint64_t)lc.sm_count * 8);
+    switch (dtype) {
+      case ZYXB_F32: gemm_splitk_finish_kernel<float, float><<<fgrid, 256, 0, lc.stream>>>(p); break;
+      case ZYXB_BF16: gemm_splitk_finish_kernel<bf16_t, float><<<fgrid, 256, 0, lc.stream>>>(p); break;
+      case ZYXB_F16: gemm_splitk_finish_kernel<f16_t, float><<<fgrid, 256, 0, lc.stream>>>(p); break;
+      default: gemm_splitk_finish_kernel<int32_t, int32_t><<<fgrid, 256, 0, lc.stream>>>(p); break;
+    }
+    return check_launch(lc, err, "gemm_simt (split k)", 2);
   }
   return check_launch(lc, err, "gemm_simt");
 }
