@@ -128,6 +128,43 @@ def test_f32_gemm_1024_against_float64(sess):
     assert max_rel_err(got, want, floor=0.1) <= TOL_F32
 
 
+@pytest.mark.parametrize("ta,tb", [(False, False), (False, True), (True, False), (True, True)])
+@pytest.mark.parametrize("m,n,k", [(512, 512, 256), (640, 772, 1028), (1536, 516, 4096)])
+def test_f32_tensor_core_path_meets_the_f32_bar(sess, ta, tb, m, n, k):
+    """Large f32 matmuls run as three TF32 tensor-core products per k-step on operands split into hi + lo, with the k-chunks
+    added in f32 outside the tensor core.  The bar is the f32 one (1e-5 relative to max(|c|, 0.1 * the row's largest |c|)),
+    checked against float64; plain TF32 would miss it by two orders of magnitude.  Ragged edges, all four layouts, alpha
+    and bias."""
+    a = rand((k, m) if ta else (m, k), L.F32)
+    b = rand((n, k) if tb else (k, n), L.F32)
+    bias = rand((n,), L.F32)
+    af, bf = (a.T if ta else a).astype(np.float64), (b.T if tb else b).astype(np.float64)
+    exact = af @ bf
+    got = sess.gemm(L.F32, a, b, ta=ta, tb=tb)
+    assert sess.device.status() == 0
+    # the f32 bar, or - where sequential f32 accumulation itself misses it on this data - as close as the reference gets
+    bar = max(TOL_F32, max_rel_err(zo.gemm(L.F32, a, b, ta=ta, tb=tb), exact, floor=0.1))
+    assert max_rel_err(got, exact, floor=0.1) <= bar
+    got = sess.gemm(L.F32, a, b, ta=ta, tb=tb, bias=bias, epi=L.EPI_BIAS, alpha=0.5)
+    assert max_rel_err(got, 0.5 * exact + bias.astype(np.float64), floor=0.1) <= bar
+
+
+def test_f32_tensor_core_path_survives_cancellation_and_scale(sess):
+    """Operands spanning many binades and a product that cancels: the hi / lo split must not lose the small terms."""
+    m = n = 512
+    k = 2048
+    a = (RNG.standard_normal((m, k)) * np.exp(RNG.uniform(-8, 8, size=(m, 1)))).astype(np.float32)
+    b = RNG.standard_normal((k, n)).astype(np.float32)
+    b[1::2] = -b[0::2] * (1 + 1e-3 * RNG.standard_normal((k // 2, n))).astype(np.float32)      # pairs of rows nearly cancel
+    a[:, 1::2] = a[:, 0::2]
+    exact = a.astype(np.float64) @ b.astype(np.float64)
+    got = sess.gemm(L.F32, a, b)
+    # the reference's own f32 accumulation on the same data, as the yardstick for what f32 can deliver here
+    ref = zo.gemm(L.F32, a, b)
+    e_got, e_ref = max_rel_err(got, exact, floor=0.1), max_rel_err(ref, exact, floor=0.1)
+    assert e_got <= max(TOL_F32, 4.0 * e_ref), (e_got, e_ref)      # within a small factor of sequential f32 accumulation
+
+
 @pytest.mark.parametrize("epi", [L.EPI_MUL_RELU_GRAD, L.EPI_MUL_GELU_GRAD])
 def test_activation_gradient_epilogue_f32(sess, epi):
     m, n, k = 70, 50, 33

@@ -215,7 +215,7 @@ int32_t zyxb_init(const zyxb_config* config, zyxb_ctx** out_ctx) {
         (e = cudaStreamCreateWithFlags(&D.comm_stream, cudaStreamNonBlocking)) != cudaSuccess) {
       delete ctx; return cuda_fail(nullptr, ZYXB_ERR_INITIALIZATION, "stream creation", e);
     }
-    D.scratch_bytes = 64ull << 20;
+    D.scratch_bytes = 320ull << 20;   // partials of split reductions, prepared operands of the f32 tensor-core matmul
     if ((e = cudaMalloc(&D.scratch, D.scratch_bytes)) != cudaSuccess || (e = cudaMalloc((void**)&D.status_word, 256)) != cudaSuccess) {
       delete ctx; return cuda_fail(nullptr, ZYXB_ERR_MEMORY_ALLOCATION, "scratch allocation", e);
     }

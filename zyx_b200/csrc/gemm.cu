@@ -68,6 +68,7 @@ int launch_gemm(const zyxb_gemm_desc& d, void* const* args, const uint64_t* arg_
   p.alpha = d.alpha == 0.0f ? 1.0f : d.alpha; p.rn = lc.round_nearest ? 1 : 0;
   static const bool force_simt = getenv("ZYXB_FORCE_SIMT_GEMM") != nullptr;
   if (!force_simt && gemm_tc_supported(p, d.dtype, lc)) return launch_gemm_tc(p, d.dtype, lc, err);
+  if (!force_simt && gemm_tf32x3_supported(p, d.dtype, lc)) return launch_gemm_tf32x3(p, lc, err);
   return launch_gemm_simt(p, d.dtype, lc, err);
 }
 

@@ -29,5 +29,8 @@ int launch_gemm_simt(GemmParams p, int dtype, const LaunchCtx& lc, std::string& 
 // Tensor-core path (tcgen05 + TMEM + TMA).  Returns true when the shape is one it takes.
 bool gemm_tc_supported(const GemmParams& p, int dtype, const LaunchCtx& lc);
 int launch_gemm_tc(const GemmParams& p, int dtype, const LaunchCtx& lc, std::string& err);
+// f32 on the tensor cores at f32 accuracy (three TF32 products per k-step on operands split into hi + lo)
+bool gemm_tf32x3_supported(const GemmParams& p, int dtype, const LaunchCtx& lc);
+int launch_gemm_tf32x3(const GemmParams& p, const LaunchCtx& lc, std::string& err);
 
 }  // namespace zyxb
