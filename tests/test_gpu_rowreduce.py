@@ -267,3 +267,19 @@ def test_long_rows_staged_through_shared_memory(sess, dtype, cols):
     assert_parity(f(sess.layernorm(dtype, x), dtype), f(zo.layernorm(dtype, x), dtype),
                   exact_layernorm(xf, None, None, cc(1e-5), cc(cols), cc(cols - 1)), TOL[dtype], what="layernorm")
     assert sess.device.status() == 0
+
+
+@pytest.mark.parametrize("dtype,shape", [(L.F32, (300, 32768)), (L.F32, (150, 8192)), (L.F32, (149, 32760)), (L.BF16, (200, 16384)),
+                                         (L.F16, (160, 65536 - 16))])
+def test_affine_layernorm_of_long_rows_on_cluster_pairs(sess, dtype, shape):
+    """Rows of 16 .. 128 KB with weight and bias: two CTAs of a cluster share each row and combine their halves' statistics."""
+    if dtype == L.F16 and shape[1] > 65504:
+        pytest.skip("the column count itself overflows f16")
+    x = rand(shape, dtype, 2.0)
+    x[::7] = zo.to_bits(f(x[::7], dtype) + 3.0, dtype)             # rows with a mean far from zero: the halves' means differ from the row's
+    w, b = rand((shape[1],), dtype), rand((shape[1],), dtype)
+    got, want = f(sess.layernorm(dtype, x, w, b, 1e-5), dtype), f(zo.layernorm(dtype, x, w, b, 1e-5), dtype)
+    assert sess.device.status() == 0
+    cc = lambda v: zo.const_cast(dtype, float(v))
+    exact = exact_layernorm(f(x, dtype), f(w, dtype), f(b, dtype), cc(1e-5), cc(shape[1]), cc(shape[1] - 1))
+    assert_parity(got, want, exact, TOL[dtype], what="layernorm on cluster pairs")

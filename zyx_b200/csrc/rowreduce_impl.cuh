@@ -11,6 +11,7 @@
 // (zyx-nn/src/layer_norm.rs:95-135, zyx/src/tensor/reduce_ops.rs:113-125), reduce_impl
 // (reduce_ops.rs:45-157), cross_entropy (tensor/mod.rs:1639-1655).
 #pragma once
+#include <stdlib.h>
 #include <math_constants.h>
 
 #include <algorithm>
@@ -697,6 +698,186 @@ static bool launch_row_staged(const RowParams& p, cudaStream_t s, int sm_count, 
   return true;
 }
 
+// ---- affine layernorm of long rows: a cluster of two CTAs per row ----------------------------------------
+// With weight and bias the staged kernel above would read 2 x row bytes of parameters from L2 for every row.  Here two
+// CTAs (one thread-block cluster, two SMs) share each row: each keeps its half of weight and bias in shared memory for
+// the whole launch (2 x 64 KB) next to a 64 KB stage for its half-rows, so parameters are read from L2 once per CTA.
+// The halves combine their statistics through distributed shared memory once per row: each CTA computes the sum and
+// the centred second moment of its half exactly (two passes over registers), writes the pair into its partner's
+// shared memory, and after one cluster barrier both hold
+//   mean = (s0 + s1) / n,    sum (x - mean)^2 = M0 + M1 + n/2 * ((mean0 - mean)^2 + (mean1 - mean)^2),
+// which is algebraically the reference's two-pass variance (zyx-nn/src/layer_norm.rs:117-131).
+constexpr int LNC_ITEMS = 8;   // vectors per thread: 512 threads x 8 x 16 bytes = 64 KB per half-row
+
+__device__ __forceinline__ uint32_t cluster_ctarank() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+template <typename T>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(STG_THREADS, 1) ln_cluster_kernel(RowParams p, uint32_t* status) {
+  using S = typename Elem<T>::store_t;
+  constexpr int VEC = 16 / sizeof(S);
+  extern __shared__ __align__(128) uint8_t stg_smem[];          // [stage | weight half | bias half]
+  __shared__ float red[32];
+  __shared__ float xchg[2][2];                                  // [row parity][sum, second moment] written by the partner
+  __shared__ __align__(8) uint64_t bar_storage[4];              // stage, parameters, exchange slot 0 / 1
+  __shared__ int abort_flag;
+  const int tid = threadIdx.x;
+  const uint32_t half = cluster_ctarank();
+  const uint64_t cols = p.cols, hc = cols / 2;                  // this CTA's columns: [half * hc, half * hc + hc)
+  const uint32_t half_bytes = (uint32_t)(hc * sizeof(S));
+  const uint32_t buf = stg_smem_u32(stg_smem), bar = stg_smem_u32(&bar_storage[0]), wbar = stg_smem_u32(&bar_storage[1]);
+  const S* X = reinterpret_cast<const S*>(p.x) + half * hc;
+  S* Y = reinterpret_cast<S*>(p.y) + half * hc;
+  const S* w_s = reinterpret_cast<const S*>(stg_smem + half_bytes);
+  const S* b_s = reinterpret_cast<const S*>(stg_smem + 2 * (size_t)half_bytes);
+  const bool rn = p.rn != 0;
+  if (tid == 0) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(1) : "memory");
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(wbar), "r"(1) : "memory");
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(stg_smem_u32(&bar_storage[2])), "r"(1) : "memory");
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(stg_smem_u32(&bar_storage[3])), "r"(1) : "memory");
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    abort_flag = 0;
+  }
+  __syncthreads();
+  cluster_sync_all();                                  // the partner's barriers exist before anything is sent to them
+  const uint64_t n_clusters = gridDim.x / 2;
+  uint64_t row = blockIdx.x / 2;
+  if (tid == 0) {
+    // weight and bias halves: one expected byte count, two sets of copies
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(wbar), "r"(2 * half_bytes) : "memory");
+    for (int which = 0; which < 2; ++which) {
+      const char* src = reinterpret_cast<const char*>((which ? reinterpret_cast<const S*>(p.b) : reinterpret_cast<const S*>(p.w)) + half * hc);
+      for (uint32_t off = 0; off < half_bytes; off += 32768u) {
+        const uint32_t nb = min(32768u, half_bytes - off);
+        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                     ::"r"(buf + (1 + which) * half_bytes + off), "l"(src + off), "r"(nb), "r"(wbar) : "memory");
+      }
+    }
+    if (row < p.rows) stg_fetch_row(buf, X + row * cols, half_bytes, bar);
+  }
+  // the partner's exchange slots and their barriers, as addresses in the cluster's shared window
+  uint32_t peer_xchg, peer_xbar;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(peer_xchg) : "r"(stg_smem_u32(&xchg[0][0])), "r"(half ^ 1u));
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(peer_xbar) : "r"(stg_smem_u32(&bar_storage[2])), "r"(half ^ 1u));
+  auto bounded_wait = [&](uint32_t b, uint32_t parity) {
+    if (!stg_try_wait(b, parity)) {
+      const uint64_t t0 = stg_timer_ns();
+      while (!stg_try_wait(b, parity)) {
+        if (stg_timer_ns() - t0 > STG_WAIT_NS) { abort_flag = 1; atomicOr(status, 8u); break; }
+      }
+    }
+  };
+  // weight and bias arrive once
+  bounded_wait(wbar, 0);
+  uint32_t parity = 0, it_row = 0;
+  const float n = const_cast_dtype<T>((float)cols), nm1 = const_cast_dtype<T>((float)((int64_t)cols - 1));
+  const float n_half = (float)hc;
+  // Both CTAs of a cluster walk the same rows; a CTA whose copy timed out keeps sending its (meaningless) pair with its
+  // work skipped, so that its partner is never left waiting, and every wait is bounded anyway.
+  for (; row < p.rows; row += n_clusters, ++it_row) {
+    bounded_wait(bar, parity);
+    __syncthreads();
+    const bool dead = abort_flag != 0;
+    parity ^= 1;
+    float v[LNC_ITEMS][VEC];
+#pragma unroll
+    for (int it = 0; it < LNC_ITEMS; ++it) {
+      const uint64_t c = ((uint64_t)it * STG_THREADS + tid) * VEC;
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) v[it][k] = 0.0f;
+      if (c < hc && !dead) {
+        RawVec<T, VEC> pk;
+        pk.load(reinterpret_cast<const S*>(stg_smem + c * sizeof(S)));
+        pk.decode(v[it]);
+      }
+    }
+    __syncthreads();                                   // the half-row is in registers: the stage may be refilled
+    const uint64_t next = row + n_clusters;
+    if (tid == 0 && next < p.rows && !dead) stg_fetch_row(buf, X + next * cols, half_bytes, bar);
+    float acc = 0.0f;
+#pragma unroll
+    for (int it = 0; it < LNC_ITEMS; ++it)
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) acc += v[it][k];   // columns past hc hold zeros
+    const float sum_h = group_reduce<STG_THREADS>(acc, OpSum(), red, 0.0f);
+    const float mean_h = sum_h / n_half;
+    float sq = 0.0f;
+#pragma unroll
+    for (int it = 0; it < LNC_ITEMS; ++it) {
+      const uint64_t c = ((uint64_t)it * STG_THREADS + tid) * VEC;
+      if (c < hc) {
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) { const float d = v[it][k] - mean_h; sq = fmaf(d, d, sq); }
+      }
+    }
+    const float m2_h = group_reduce<STG_THREADS>(sq, OpSum(), red, 0.0f);
+    // The pair travels as two asynchronous 4-byte stores that complete a barrier in the partner's shared memory: no
+    // cluster-wide barrier or fence per row (a release fence here would wait for the previous row's output stores).
+    // Slots alternate by row; a CTA can be at most one row ahead of its partner, because it needs the partner's pair
+    // of row i to finish row i.
+    const uint32_t slot = it_row & 1u, xbar = stg_smem_u32(&bar_storage[2 + slot]);
+    if (tid == 0) {
+      asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(xbar), "r"(8) : "memory");
+      asm volatile("st.async.shared::cluster.mbarrier::complete_tx::bytes.b32 [%0], %1, [%2];"
+                   ::"r"(peer_xchg + slot * 8u), "r"(__float_as_uint(sum_h)), "r"(peer_xbar + slot * 8u) : "memory");
+      asm volatile("st.async.shared::cluster.mbarrier::complete_tx::bytes.b32 [%0], %1, [%2];"
+                   ::"r"(peer_xchg + slot * 8u + 4u), "r"(__float_as_uint(m2_h)), "r"(peer_xbar + slot * 8u) : "memory");
+    }
+    bounded_wait(xbar, (it_row >> 1) & 1u);            // the partner's pair has landed in xchg[slot]
+    const float sum_o = reinterpret_cast<volatile float*>(&xchg[slot][0])[0], m2_o = reinterpret_cast<volatile float*>(&xchg[slot][0])[1];
+    // identical arithmetic in both CTAs: operands ordered by half, not by "mine / theirs"
+    const float s0 = half == 0 ? sum_h : sum_o, s1 = half == 0 ? sum_o : sum_h;
+    const float q0 = half == 0 ? m2_h : m2_o, q1 = half == 0 ? m2_o : m2_h;
+    const float mean = (s0 + s1) / n;
+    const float d0 = s0 / n_half - mean, d1 = s1 / n_half - mean;
+    const float m2 = (q0 + q1) + n_half * (d0 * d0 + d1 * d1);
+    const float rstd = 1.0f / sqrtf(m2 / nm1 + const_cast_dtype<T>(p.eps));
+    if (!dead) {
+      S* yr = Y + row * cols;
+#pragma unroll
+      for (int it = 0; it < LNC_ITEMS; ++it) {
+        const uint64_t c = ((uint64_t)it * STG_THREADS + tid) * VEC;
+        if (c < hc) {
+          RawVec<T, VEC> pw, pb, po;
+          float wv[VEC], bv[VEC], o[VEC];
+          pw.load(w_s + c); pw.decode(wv);
+          pb.load(b_s + c); pb.decode(bv);
+#pragma unroll
+          for (int k = 0; k < VEC; ++k) o[k] = (v[it][k] - mean) * rstd * wv[k] + bv[k];
+          po.encode(o, rn);
+          po.store_stream(yr + c);
+        }
+      }
+    }
+  }
+  cluster_sync_all();                                  // no CTA leaves while its partner might still address its shared memory
+}
+
+// Takes affine layernorm launches whose rows split into two halves of 8 .. 64 KB; returns false otherwise.
+template <typename T>
+static bool launch_ln_cluster(const RowParams& p, cudaStream_t s, int sm_count, uint32_t* status) {
+  using S = typename Elem<T>::store_t;
+  constexpr int V = 16 / sizeof(S);
+  static const bool off = getenv("ZYXB_NO_LN_CLUSTER") != nullptr;
+  if (off || !p.w || !p.b || sm_count < 2) return false;
+  const uint64_t hc = p.cols / 2, half_bytes = hc * sizeof(S);
+  if (p.cols % (2 * V) || half_bytes < 8192 || half_bytes > 65536 || hc > (uint64_t)STG_THREADS * LNC_ITEMS * V) return false;
+  if (p.rows < (uint64_t)sm_count) return false;      // at least two rows per cluster
+  if ((uintptr_t)p.x % 16 || (uintptr_t)p.y % 16 || (uintptr_t)p.w % 16 || (uintptr_t)p.b % 16) return false;
+  auto kern = ln_cluster_kernel<T>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 3 * 65536) != cudaSuccess) { cudaGetLastError(); return false; }
+    configured = true;
+  }
+  const unsigned clusters = (unsigned)std::min<uint64_t>(p.rows, (uint64_t)(sm_count / 2));
+  kern<<<2 * clusters, STG_THREADS, (size_t)(3 * half_bytes), s>>>(p, status);
+  return true;
+}
+
 // ---- host-side geometry selection -----------------------------------------------------------
 template <typename T, int VEC, int ITEMS, int GROUP, int FAM>
 static void launch_row_geom(const RowParams& p, cudaStream_t s) {
@@ -735,6 +916,9 @@ static void launch_row_family(const RowParams& p, cudaStream_t s) {
     // layernorm with weight / bias stays on the register kernel: its per-element weight and bias loads (L2 latency,
     // 16 dependent iterations per thread at 512 threads) cost more than the staging gains (measured 0.70 vs 0.79 of peak)
     const bool affine = FAM == FAM_LAYERNORM && (p.w || p.b);
+    if constexpr (FAM == FAM_LAYERNORM) {
+      if (vec_ok && p.w && p.b && p.sm_count > 0 && p.status && launch_ln_cluster<T>(p, s, p.sm_count, p.status)) return;
+    }
     if (vec_ok && !affine && p.sm_count > 0 && p.status && launch_row_staged<T, FAM>(p, s, p.sm_count, p.status)) return;
   }
   if (vec_ok) launch_row_vec<T, V, FAM>(p, s);
