@@ -610,34 +610,64 @@ __global__ void __launch_bounds__(STG_THREADS, 1) row_staged_kernel(RowParams p,
       pk.store_stream(yr + c);
     };
     if constexpr (FAM == FAM_SOFTMAX) {
-      const uint64_t lim = p.causal ? min((uint64_t)(row % p.period) + 1, cols) : cols;
-      auto val = [&](float a, uint64_t c) -> float { if (scaled) a *= cscale; return c < lim ? a : -CUDART_INF_F; };
+      // Scale and causal mask are applied once, in place (masked entries become -inf, whose exponential is 0); the three
+      // passes that follow are free of compares.  Plain softmax then replaces each entry by its exponential (one SFU
+      // operation per element); the log form keeps x.
+      constexpr float LOG2E = 1.4426950408889634f;
+      const uint32_t cols32 = (uint32_t)cols, lim32 = p.causal ? (uint32_t)min((uint64_t)(row % p.period) + 1, cols) : cols32;
       float mx = -CUDART_INF_F;
-      for_each([&](uint64_t c, const float (&a)[VEC]) {
 #pragma unroll
-        for (int k = 0; k < VEC; ++k) mx = fmaxf(val(a[k], c + k), mx);
-      });
+      for (int it = 0; it < ITEMS; ++it) {
+        const uint32_t c = ((uint32_t)it * STG_THREADS + tid) * VEC;
+        if (c < cols32) {
+          if (scaled) {
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) v[it][k] *= cscale;
+          }
+          if (c + VEC > lim32) {
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) v[it][k] = c + k < lim32 ? v[it][k] : -CUDART_INF_F;
+          }
+#pragma unroll
+          for (int k = 0; k < VEC; ++k) mx = fmaxf(v[it][k], mx);
+        }
+      }
       mx = group_reduce<STG_THREADS>(mx, OpMaxF(), red, -CUDART_INF_F);
+      const float nmx = -mx * LOG2E;
+      auto ex = [&](float a) -> float {                   // exp(a - mx)
+        float r;
+        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(fmaf(a, LOG2E, nmx)));
+        return r;
+      };
       float sum = 0.0f;
-      for_each([&](uint64_t c, const float (&a)[VEC]) {
-#pragma unroll
-        for (int k = 0; k < VEC; ++k) sum += fast_exp(val(a[k], c + k) - mx);
-      });
-      sum = group_reduce<STG_THREADS>(sum, OpSum(), red, 0.0f);
       if (p.op == ZYXB_RR_SOFTMAX) {
+#pragma unroll
+        for (int it = 0; it < ITEMS; ++it) {
+          const uint32_t c = ((uint32_t)it * STG_THREADS + tid) * VEC;
+          if (c < cols32) {
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) { v[it][k] = ex(v[it][k]); sum += v[it][k]; }
+          }
+        }
+        sum = group_reduce<STG_THREADS>(sum, OpSum(), red, 0.0f);
         const float inv = 1.0f / sum;
-        for_each([&](uint64_t c, const float (&a)[VEC]) {
+        for_each([&](uint64_t c, const float (&e)[VEC]) {
           float o[VEC];
 #pragma unroll
-          for (int k = 0; k < VEC; ++k) o[k] = fast_exp(val(a[k], c + k) - mx) * inv;
+          for (int k = 0; k < VEC; ++k) o[k] = e[k] * inv;
           write(c, o);
         });
       } else {
+        for_each([&](uint64_t, const float (&a)[VEC]) {
+#pragma unroll
+          for (int k = 0; k < VEC; ++k) sum += ex(a[k]);
+        });
+        sum = group_reduce<STG_THREADS>(sum, OpSum(), red, 0.0f);
         const float ls = logf(sum);
         for_each([&](uint64_t c, const float (&a)[VEC]) {
           float o[VEC];
 #pragma unroll
-          for (int k = 0; k < VEC; ++k) o[k] = (val(a[k], c + k) - mx) - ls;
+          for (int k = 0; k < VEC; ++k) o[k] = (a[k] - mx) - ls;
           write(c, o);
         });
       }
@@ -698,15 +728,17 @@ static bool launch_row_staged(const RowParams& p, cudaStream_t s, int sm_count, 
   return true;
 }
 
-// ---- affine layernorm of long rows: a cluster of two CTAs per row ----------------------------------------
+// ---- long rows on thread-block cluster pairs: a cluster of two CTAs per row ---------------------------------
+// (layernorm with or without weight and bias; rows of 16 .. 128 KB.)
 // With weight and bias the staged kernel above would read 2 x row bytes of parameters from L2 for every row.  Here two
 // CTAs (one thread-block cluster, two SMs) share each row: each keeps its half of weight and bias in shared memory for
 // the whole launch (2 x 64 KB) next to a 64 KB stage for its half-rows, so parameters are read from L2 once per CTA.
 // The halves combine their statistics through distributed shared memory once per row: each CTA computes the sum and
 // the centred second moment of its half exactly (two passes over registers), writes the pair into its partner's
-// shared memory, and after one cluster barrier both hold
+// shared memory (asynchronous stores that complete a barrier there), and both hold
 //   mean = (s0 + s1) / n,    sum (x - mean)^2 = M0 + M1 + n/2 * ((mean0 - mean)^2 + (mean1 - mean)^2),
 // which is algebraically the reference's two-pass variance (zyx-nn/src/layer_norm.rs:117-131).
+// Softmax stays on the single-CTA staged kernel above: it has no parameters to keep resident and reaches the HBM peak there.
 constexpr int LNC_ITEMS = 8;   // vectors per thread: 512 threads x 8 x 16 bytes = 64 KB per half-row
 
 __device__ __forceinline__ uint32_t cluster_ctarank() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
@@ -714,8 +746,8 @@ __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
-template <typename T>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(STG_THREADS, 1) ln_cluster_kernel(RowParams p, uint32_t* status) {
+template <typename T, int FAM>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(STG_THREADS, 1) row_cluster_kernel(RowParams p, uint32_t* status) {
   using S = typename Elem<T>::store_t;
   constexpr int VEC = 16 / sizeof(S);
   extern __shared__ __align__(128) uint8_t stg_smem[];          // [stage | weight half | bias half]
@@ -730,6 +762,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(STG_THREADS, 1) ln_c
   const uint32_t buf = stg_smem_u32(stg_smem), bar = stg_smem_u32(&bar_storage[0]), wbar = stg_smem_u32(&bar_storage[1]);
   const S* X = reinterpret_cast<const S*>(p.x) + half * hc;
   S* Y = reinterpret_cast<S*>(p.y) + half * hc;
+  static_assert(FAM == FAM_LAYERNORM, "cluster pairs serve layernorm only");
+  const bool affine = p.w != nullptr;                  // weight and bias come together (the launcher checks)
   const S* w_s = reinterpret_cast<const S*>(stg_smem + half_bytes);
   const S* b_s = reinterpret_cast<const S*>(stg_smem + 2 * (size_t)half_bytes);
   const bool rn = p.rn != 0;
@@ -745,7 +779,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(STG_THREADS, 1) ln_c
   cluster_sync_all();                                  // the partner's barriers exist before anything is sent to them
   const uint64_t n_clusters = gridDim.x / 2;
   uint64_t row = blockIdx.x / 2;
-  if (tid == 0) {
+  if (tid == 0 && affine) {
     // weight and bias halves: one expected byte count, two sets of copies
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(wbar), "r"(2 * half_bytes) : "memory");
     for (int which = 0; which < 2; ++which) {
@@ -756,8 +790,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(STG_THREADS, 1) ln_c
                      ::"r"(buf + (1 + which) * half_bytes + off), "l"(src + off), "r"(nb), "r"(wbar) : "memory");
       }
     }
-    if (row < p.rows) stg_fetch_row(buf, X + row * cols, half_bytes, bar);
   }
+  if (tid == 0 && row < p.rows) stg_fetch_row(buf, X + row * cols, half_bytes, bar);
   // the partner's exchange slots and their barriers, as addresses in the cluster's shared window
   uint32_t peer_xchg, peer_xbar;
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(peer_xchg) : "r"(stg_smem_u32(&xchg[0][0])), "r"(half ^ 1u));
@@ -770,8 +804,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(STG_THREADS, 1) ln_c
       }
     }
   };
-  // weight and bias arrive once
-  bounded_wait(wbar, 0);
+  if (affine) bounded_wait(wbar, 0);                  // weight and bias arrive once
   uint32_t parity = 0, it_row = 0;
   const float n = const_cast_dtype<T>((float)cols), nm1 = const_cast_dtype<T>((float)((int64_t)cols - 1));
   const float n_half = (float)hc;
@@ -797,23 +830,27 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(STG_THREADS, 1) ln_c
     __syncthreads();                                   // the half-row is in registers: the stage may be refilled
     const uint64_t next = row + n_clusters;
     if (tid == 0 && next < p.rows && !dead) stg_fetch_row(buf, X + next * cols, half_bytes, bar);
-    float acc = 0.0f;
+    // this half's pair of statistics: (sum, centred second moment)
+    float st0, st1;
+    {
+      float acc = 0.0f;
 #pragma unroll
-    for (int it = 0; it < LNC_ITEMS; ++it)
+      for (int it = 0; it < LNC_ITEMS; ++it)
 #pragma unroll
-      for (int k = 0; k < VEC; ++k) acc += v[it][k];   // columns past hc hold zeros
-    const float sum_h = group_reduce<STG_THREADS>(acc, OpSum(), red, 0.0f);
-    const float mean_h = sum_h / n_half;
-    float sq = 0.0f;
+        for (int k = 0; k < VEC; ++k) acc += v[it][k];   // columns past hc hold zeros
+      st0 = group_reduce<STG_THREADS>(acc, OpSum(), red, 0.0f);
+      const float mean_h = st0 / n_half;
+      float sq = 0.0f;
 #pragma unroll
-    for (int it = 0; it < LNC_ITEMS; ++it) {
-      const uint64_t c = ((uint64_t)it * STG_THREADS + tid) * VEC;
-      if (c < hc) {
+      for (int it = 0; it < LNC_ITEMS; ++it) {
+        const uint64_t c = ((uint64_t)it * STG_THREADS + tid) * VEC;
+        if (c < hc) {
 #pragma unroll
-        for (int k = 0; k < VEC; ++k) { const float d = v[it][k] - mean_h; sq = fmaf(d, d, sq); }
+          for (int k = 0; k < VEC; ++k) { const float d = v[it][k] - mean_h; sq = fmaf(d, d, sq); }
+        }
       }
+      st1 = group_reduce<STG_THREADS>(sq, OpSum(), red, 0.0f);
     }
-    const float m2_h = group_reduce<STG_THREADS>(sq, OpSum(), red, 0.0f);
     // The pair travels as two asynchronous 4-byte stores that complete a barrier in the partner's shared memory: no
     // cluster-wide barrier or fence per row (a release fence here would wait for the previous row's output stores).
     // Slots alternate by row; a CTA can be at most one row ahead of its partner, because it needs the partner's pair
@@ -822,33 +859,41 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(STG_THREADS, 1) ln_c
     if (tid == 0) {
       asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(xbar), "r"(8) : "memory");
       asm volatile("st.async.shared::cluster.mbarrier::complete_tx::bytes.b32 [%0], %1, [%2];"
-                   ::"r"(peer_xchg + slot * 8u), "r"(__float_as_uint(sum_h)), "r"(peer_xbar + slot * 8u) : "memory");
+                   ::"r"(peer_xchg + slot * 8u), "r"(__float_as_uint(st0)), "r"(peer_xbar + slot * 8u) : "memory");
       asm volatile("st.async.shared::cluster.mbarrier::complete_tx::bytes.b32 [%0], %1, [%2];"
-                   ::"r"(peer_xchg + slot * 8u + 4u), "r"(__float_as_uint(m2_h)), "r"(peer_xbar + slot * 8u) : "memory");
+                   ::"r"(peer_xchg + slot * 8u + 4u), "r"(__float_as_uint(st1)), "r"(peer_xbar + slot * 8u) : "memory");
     }
     bounded_wait(xbar, (it_row >> 1) & 1u);            // the partner's pair has landed in xchg[slot]
-    const float sum_o = reinterpret_cast<volatile float*>(&xchg[slot][0])[0], m2_o = reinterpret_cast<volatile float*>(&xchg[slot][0])[1];
+    const float o0 = reinterpret_cast<volatile float*>(&xchg[slot][0])[0], o1 = reinterpret_cast<volatile float*>(&xchg[slot][0])[1];
     // identical arithmetic in both CTAs: operands ordered by half, not by "mine / theirs"
-    const float s0 = half == 0 ? sum_h : sum_o, s1 = half == 0 ? sum_o : sum_h;
-    const float q0 = half == 0 ? m2_h : m2_o, q1 = half == 0 ? m2_o : m2_h;
-    const float mean = (s0 + s1) / n;
-    const float d0 = s0 / n_half - mean, d1 = s1 / n_half - mean;
-    const float m2 = (q0 + q1) + n_half * (d0 * d0 + d1 * d1);
-    const float rstd = 1.0f / sqrtf(m2 / nm1 + const_cast_dtype<T>(p.eps));
-    if (!dead) {
-      S* yr = Y + row * cols;
+    const float a0 = half == 0 ? st0 : o0, a1 = half == 0 ? o0 : st0;
+    const float b0 = half == 0 ? st1 : o1, b1 = half == 0 ? o1 : st1;
+    S* yr = Y + row * cols;
+    {
+      const float mean = (a0 + a1) / n;
+      const float d0 = a0 / n_half - mean, d1 = a1 / n_half - mean;
+      const float m2 = (b0 + b1) + n_half * (d0 * d0 + d1 * d1);
+      const float rstd = 1.0f / sqrtf(m2 / nm1 + const_cast_dtype<T>(p.eps));
+      if (!dead) {
 #pragma unroll
-      for (int it = 0; it < LNC_ITEMS; ++it) {
-        const uint64_t c = ((uint64_t)it * STG_THREADS + tid) * VEC;
-        if (c < hc) {
-          RawVec<T, VEC> pw, pb, po;
-          float wv[VEC], bv[VEC], o[VEC];
-          pw.load(w_s + c); pw.decode(wv);
-          pb.load(b_s + c); pb.decode(bv);
+        for (int it = 0; it < LNC_ITEMS; ++it) {
+          const uint64_t c = ((uint64_t)it * STG_THREADS + tid) * VEC;
+          if (c < hc) {
+            RawVec<T, VEC> po;
+            float o[VEC];
 #pragma unroll
-          for (int k = 0; k < VEC; ++k) o[k] = (v[it][k] - mean) * rstd * wv[k] + bv[k];
-          po.encode(o, rn);
-          po.store_stream(yr + c);
+            for (int k = 0; k < VEC; ++k) o[k] = (v[it][k] - mean) * rstd;
+            if (affine) {
+              RawVec<T, VEC> pw, pb;
+              float wv[VEC], bv[VEC];
+              pw.load(w_s + c); pw.decode(wv);
+              pb.load(b_s + c); pb.decode(bv);
+#pragma unroll
+              for (int k = 0; k < VEC; ++k) o[k] = o[k] * wv[k] + bv[k];
+            }
+            po.encode(o, rn);
+            po.store_stream(yr + c);
+          }
         }
       }
     }
@@ -856,25 +901,25 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(STG_THREADS, 1) ln_c
   cluster_sync_all();                                  // no CTA leaves while its partner might still address its shared memory
 }
 
-// Takes affine layernorm launches whose rows split into two halves of 8 .. 64 KB; returns false otherwise.
-template <typename T>
-static bool launch_ln_cluster(const RowParams& p, cudaStream_t s, int sm_count, uint32_t* status) {
+// Takes layernorm launches whose rows split into two halves of 8 .. 64 KB; returns false otherwise.
+template <typename T, int FAM>
+static bool launch_row_cluster(const RowParams& p, cudaStream_t s, int sm_count, uint32_t* status) {
   using S = typename Elem<T>::store_t;
   constexpr int V = 16 / sizeof(S);
-  static const bool off = getenv("ZYXB_NO_LN_CLUSTER") != nullptr;
-  if (off || !p.w || !p.b || sm_count < 2) return false;
+  static const bool off = getenv("ZYXB_NO_ROW_CLUSTER") != nullptr;
+  if (off || sm_count < 2 || (p.w == nullptr) != (p.b == nullptr)) return false;
   const uint64_t hc = p.cols / 2, half_bytes = hc * sizeof(S);
   if (p.cols % (2 * V) || half_bytes < 8192 || half_bytes > 65536 || hc > (uint64_t)STG_THREADS * LNC_ITEMS * V) return false;
   if (p.rows < (uint64_t)sm_count) return false;      // at least two rows per cluster
-  if ((uintptr_t)p.x % 16 || (uintptr_t)p.y % 16 || (uintptr_t)p.w % 16 || (uintptr_t)p.b % 16) return false;
-  auto kern = ln_cluster_kernel<T>;
+  if ((uintptr_t)p.x % 16 || (uintptr_t)p.y % 16 || (p.w && ((uintptr_t)p.w % 16 || (uintptr_t)p.b % 16))) return false;
+  auto kern = row_cluster_kernel<T, FAM>;
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 3 * 65536) != cudaSuccess) { cudaGetLastError(); return false; }
     configured = true;
   }
   const unsigned clusters = (unsigned)std::min<uint64_t>(p.rows, (uint64_t)(sm_count / 2));
-  kern<<<2 * clusters, STG_THREADS, (size_t)(3 * half_bytes), s>>>(p, status);
+  kern<<<2 * clusters, STG_THREADS, (size_t)((p.w ? 3 : 1) * half_bytes), s>>>(p, status);
   return true;
 }
 
@@ -916,8 +961,10 @@ static void launch_row_family(const RowParams& p, cudaStream_t s) {
     // layernorm with weight / bias stays on the register kernel: its per-element weight and bias loads (L2 latency,
     // 16 dependent iterations per thread at 512 threads) cost more than the staging gains (measured 0.70 vs 0.79 of peak)
     const bool affine = FAM == FAM_LAYERNORM && (p.w || p.b);
+    // Measured at f32 [8192, 32768]: layernorm 0.99 of the HBM peak on cluster pairs (0.76-0.79 without them); softmax
+    // 0.996 on the single-CTA stage below against 0.90 on pairs (twice the row iterations per CTA, nothing to keep resident).
     if constexpr (FAM == FAM_LAYERNORM) {
-      if (vec_ok && p.w && p.b && p.sm_count > 0 && p.status && launch_ln_cluster<T>(p, s, p.sm_count, p.status)) return;
+      if (vec_ok && p.sm_count > 0 && p.status && launch_row_cluster<T, FAM>(p, s, p.sm_count, p.status)) return;
     }
     if (vec_ok && !affine && p.sm_count > 0 && p.status && launch_row_staged<T, FAM>(p, s, p.sm_count, p.status)) return;
   }
