@@ -506,6 +506,88 @@ class AttentionFwd:
         return fl / dt / 1e12, "%d of %d (batch, head) pairs, composed scores -> softmax -> P.V (plus a float64 check), %.1f s" % (heads, self.B * self.H, dt)
 
 
+class Conv:
+    """A ResNet-style 3x3 convolution layer, bf16: x [32, 256, 56, 56] N(0,1), w [256, 256, 3, 3] U(+-1/sqrt(c*9)) as
+    Conv2d::new draws it (zyx-nn/src/conv2d.rs:38-47), bias, stride 1, padding 1; channels-first in and out."""
+    metric, unit, dtype, bound = "convolution forward TFLOP/s (implicit GEMM, 3x3, 256 -> 256 channels)", "TFLOP/s", "bf16", "tensor"
+    N, C, H, W, O, K = 32, 256, 56, 56, 256, 3
+
+    def __init__(self, size=0):
+        if size:
+            self.N = size
+        self.name = "conv3x3_bf16_n%d_c%d_%dx%d_o%d" % (self.N, self.C, self.H, self.W, self.O)
+        self.flops = 2.0 * self.N * self.H * self.W * self.O * self.C * self.K * self.K
+        self.units_per_step = self.flops / 1e12
+        self.h2d_bytes = self.N * self.C * self.H * self.W * 2
+        self.d2h_bytes = self.N * self.O * self.H * self.W * 2
+
+    def host_inputs(self):
+        rng = np.random.default_rng(6)
+        bound = 1.0 / np.sqrt(self.C * self.K * self.K)
+        self.x = f32_to_bf16_bits(rng.standard_normal((self.N, self.C, self.H, self.W), dtype=np.float32))
+        self.w = f32_to_bf16_bits(rng.uniform(-bound, bound, (self.O, self.C, self.K, self.K)).astype(np.float32))
+        self.b = f32_to_bf16_bits(rng.uniform(-bound, bound, self.O).astype(np.float32))
+
+    def setup(self, sess):
+        from zyx_b200 import _lib as L, backend as B
+        self.sess = sess
+        self.host_inputs()
+        p, d = sess.pool, sess.device
+        self.bx, self.bw, self.bb = p.upload(self.x), p.upload(self.w), p.upload(self.b)
+        self.by, _ = p.allocate(self.d2h_bytes)
+        self.prog = d.create_program(B.conv_desc(L.BF16, self.x.shape, self.w.shape, 1, 1, 1, has_bias=True))
+        self.config = {"workload": self.name, "l2": "L2 flushed (256 MB memset) before every timed launch",
+                       "launch": "three kernels: activations to channels-last, filters to [o, tap, c], implicit GEMM"}
+        self.kernel_events = []
+
+    def step(self, timed=False):
+        d = self.sess.device
+        d.flush_l2()
+        e0 = d.event_record() if timed else None
+        d.launch(self.prog, [self.bx, self.bw, self.bb, self.by])
+        if timed:
+            self.kernel_events.append((e0, d.event_record()))
+
+    def roofline(self, peaks, clocks=None):
+        d = self.sess.device
+        t = float(np.mean([d.elapsed_ms(a, b) for a, b in self.kernel_events]))
+        ach = self.flops / (t * 1e-3) / 1e12
+        return ({"bound": "tensor", "kernel": "conv_tc_kernel (tcgen05) with its two layout kernels", "achieved": ach, "peak": peaks["bf16_tflops"],
+                 "unit": "TFLOP/s", "frac": ach / peaks["bf16_tflops"], "traffic": None, "peak_source": peaks["source"], "ms_per_launch": t},
+                {"conv": {"ms": t, "TFLOP/s": ach}})
+
+    def e2e_setup(self):
+        self.hy = np.empty((self.N, self.O, self.H, self.W), np.uint16)
+        for a in (self.x, self.hy):
+            self.sess.backend.host_register(a)
+
+    def e2e_step(self):
+        p, d = self.sess.pool, self.sess.device
+        ev = p.host_to_pool(self.x, self.bx)
+        d.launch(self.prog, [self.bx, self.bw, self.bb, self.by], [ev])
+        p.pool_to_host(self.by, self.hy)
+
+    def check(self):
+        from oracle import oracle as zo
+        y = np.empty((1, self.O, self.H, self.W), np.uint16)               # the first image, every filter
+        self.sess.pool.pool_to_host(self.by, y)
+        o = 8
+        want = zo.conv(zo.BF16, self.x[:1], self.w[:o], self.b[:o], 1, 1, 1)
+        f = lambda b: (b.astype(np.uint32) << 16).view(np.float32)
+        g, w = f(y[:, :o]), f(want)
+        return float(np.max(np.abs(g - w) / np.maximum(np.abs(w), 0.1 * np.abs(w).max())))
+
+    def cpu_baseline(self, budget_s=12.0):
+        from oracle import oracle as zo
+        self.host_inputs() if not hasattr(self, "x") else None
+        n, o = 1, 32
+        t0 = time.perf_counter()
+        zo.conv(zo.BF16, self.x[:n], self.w[:o], self.b[:o], 1, 1, 1)
+        dt = time.perf_counter() - t0
+        fl = 2.0 * n * self.H * self.W * o * self.C * self.K * self.K
+        return fl / dt / 1e12, "%d image(s) x %d of %d filters, %.1f s" % (n, o, self.O, dt)
+
+
 class MlpTrain:
     """Config 4: 4 x Linear 4096 -> 16384 -> 4096 -> 16384 -> 4096, GELU between, bf16, batch 8192 per GPU, MSE against
     N(0,1) targets, AdamW lr 1e-3 wd 0.01; data parallel over the ranks with an NCCL gradient allreduce."""
@@ -826,7 +908,7 @@ class BlockTrain:
                                       "samples/s extrapolated to the full block by matmul FLOPs (%.1f GFLOP per sample)") % (E, F, H, T, flops / 1e9, dt, full / 1e9)
 
 
-WORKLOADS = {"block": BlockTrain, "simplenet": SimpleNet, "mlp": MlpTrain, "rowreduce": RowReduce, "attn_rows": AttnRows, "attention": AttentionFwd, "gemm_bf16": lambda: Gemm("bf16"), "gemm_f32": lambda: Gemm("f32")}
+WORKLOADS = {"block": BlockTrain, "simplenet": SimpleNet, "mlp": MlpTrain, "rowreduce": RowReduce, "attn_rows": AttnRows, "attention": AttentionFwd, "conv": Conv, "gemm_bf16": lambda: Gemm("bf16"), "gemm_f32": lambda: Gemm("f32")}
 
 
 def make_workload(args, rank=0, world=1):
@@ -837,7 +919,7 @@ def make_workload(args, rank=0, world=1):
     if args.workload == "block":
         return BlockTrain(size=args.size, rank=rank, world=world, fused=not args.unfused_attention)
     if args.size:
-        return {"rowreduce": lambda: RowReduce(rows=args.size), "attn_rows": lambda: AttnRows(rows=args.size), "attention": lambda: AttentionFwd(args.size), "gemm_bf16": lambda: Gemm("bf16", args.size),
+        return {"rowreduce": lambda: RowReduce(rows=args.size), "attn_rows": lambda: AttnRows(rows=args.size), "attention": lambda: AttentionFwd(args.size), "conv": lambda: Conv(args.size), "gemm_bf16": lambda: Gemm("bf16", args.size),
                 "gemm_f32": lambda: Gemm("f32", args.size)}[args.workload]()
     return WORKLOADS[args.workload]()
 

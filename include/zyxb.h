@@ -95,7 +95,8 @@ typedef struct {
  * Launch arguments are always inputs first, then outputs, as `Device::launch` receives
  * them (zyx/src/backend/mod.rs:974, zyx/src/runtime.rs:2285-2291).
  * ---------------------------------------------------------------------------------- */
-enum { ZYXB_KIND_ROWREDUCE = 1, ZYXB_KIND_GEMM = 2, ZYXB_KIND_ELTWISE = 3, ZYXB_KIND_OPTIM = 4, ZYXB_KIND_ATTENTION = 5, ZYXB_KIND_ATTENTION_BWD = 6 };
+enum { ZYXB_KIND_ROWREDUCE = 1, ZYXB_KIND_GEMM = 2, ZYXB_KIND_ELTWISE = 3, ZYXB_KIND_OPTIM = 4, ZYXB_KIND_ATTENTION = 5, ZYXB_KIND_ATTENTION_BWD = 6,
+       ZYXB_KIND_CONV = 7 };
 
 /* Row kernels: an elementwise chain with a trailing reduce over the last axis.
  * Semantics: Tensor::reduce_impl (zyx/src/tensor/reduce_ops.rs:45-157), softmax /
@@ -241,6 +242,26 @@ typedef struct {
  * ZYXB_KIND_ATTENTION_BWD  args: q, k, v, o, do, lse -> dq, dk, dv   (the adjoint; the same descriptor as the forward;
  *                          probabilities are recomputed from lse tile by tile, nothing of size [seq, seq] is stored) */
 
+/* 2-D convolution (forward) with groups = 1, Tensor::conv (zyx/src/tensor/mod.rs:2583-2680) as Conv2d::forward calls it
+ * (zyx-nn/src/conv2d.rs:58-68):
+ *   y[n,o,i,j] = bias[o] + sum over (c, r, s) of  x[n, c, i*stride_h + r*dil_h - pad_top, j*stride_w + s*dil_w - pad_left] * w[o,c,r,s]
+ * x [n,c,h,w], w [o,c,kh,kw], bias [o], y [n,o,oh,ow], dense, in the reference's own (channels-first) layout; positions
+ * outside x read 0 (rpad_zeros, mod.rs:2647); oh = (h + pad_top + pad_bottom - dil_h*(kh-1) - 1) / stride_h + 1, ow alike.
+ * The sum runs over c, then r, then s (the order of the reference's sum_keepdim axes); products of bf16 / f16 inputs are
+ * exact in f32 and accumulate in f32 (i32 for integers); sum + bias is rounded to the tensor dtype once, when stored.
+ * bf16 / f16 launches with enough work run as an implicit GEMM on the tensor cores: TMA reads, per filter tap, a box
+ * of [output rows x output columns x 64 channels] at the tap's offset (the element strides of the tensor map carry the
+ * convolution stride, out-of-range coordinates read the zero padding), so no im2col matrix exists anywhere. */
+typedef struct {
+  int32_t  dtype;        /* bf16 / f16 / f32 / i32 */
+  uint64_t n, c, h, w;
+  uint64_t o, kh, kw;
+  uint32_t stride_h, stride_w, dil_h, dil_w;                 /* 0 means 1 */
+  uint32_t pad_top, pad_bottom, pad_left, pad_right;
+  int32_t  has_bias;
+} zyxb_conv_desc;
+/* args: x, w [,bias] -> y */
+
 typedef struct {
   int32_t kind;  /* ZYXB_KIND_* */
   union {
@@ -249,6 +270,7 @@ typedef struct {
     zyxb_eltwise_desc   eltwise;
     zyxb_optim_desc     optim;
     zyxb_attention_desc attention;   /* both attention kinds */
+    zyxb_conv_desc      conv;
   } u;
 } zyxb_kernel_desc;
 

@@ -240,6 +240,25 @@ def gemm(dtype, a, b, ta=False, tb=False, bias=None, epi=EPI_NONE, alpha=0.0, wa
     return (c, pre) if want_preact else c
 
 
+# ---- convolution -------------------------------------------------------------------------
+def conv(dtype, x, w, bias=None, stride=1, dilation=1, padding=0):
+    """Tensor::conv with groups = 1: x [n,c,h,w], w [o,c,kh,kw], bias [o] -> y [n,o,oh,ow].
+    padding: int, (pad_h, pad_w) or (top, bottom, left, right)."""
+    sh, sw = (stride, stride) if isinstance(stride, int) else stride
+    dh, dw = (dilation, dilation) if isinstance(dilation, int) else dilation
+    pad = (padding,) * 4 if isinstance(padding, int) else ((padding[0], padding[0], padding[1], padding[1]) if len(padding) == 2 else tuple(padding))
+    n, c, h, wd = x.shape
+    o, c2, kh, kw = w.shape
+    assert c == c2, (x.shape, w.shape)
+    oh = (h + pad[0] + pad[1] - dh * (kh - 1) - 1) // sh + 1
+    ow = (wd + pad[2] + pad[3] - dw * (kw - 1) - 1) // sw + 1
+    y = np.empty((n, o, oh, ow), _NP[dtype])
+    pads = (C.c_int64 * 4)(*pad)
+    lib().zo_conv(dtype, _p(_c(x, dtype)), _p(_c(w, dtype)), _p(None if bias is None else _c(bias, dtype)), _p(y), _u64(n), _u64(c), _u64(h),
+                  _u64(wd), _u64(o), _u64(kh), _u64(kw), _u64(sh), _u64(sw), _u64(dh), _u64(dw), pads)
+    return y
+
+
 # ---- optimizers --------------------------------------------------------------------------
 def sgd(dtype, p, g, buf=None, lr=0.01, wd=0.0, momentum=0.0, dampening=0.0, nesterov=False, maximize=False, first=True,
         grad_scale=1.0):

@@ -465,6 +465,37 @@ void zo_gemm_i32(int ta, int tb, uint64_t m, uint64_t n, uint64_t k, uint64_t ba
   }
 }
 
+/* Tensor::conv with groups = 1 — zyx/src/tensor/mod.rs:2583-2680.  The reference pads with zeros (rpad_zeros, 2647), takes
+ * the pooled view (pool, 2442: window element (r, s) of output (i, j) is padded input (i*stride + r*dilation,
+ * j*stride + s*dilation)), multiplies by the weights and sums over (c, r, s) in that order (sum_keepdim over the last
+ * axes, 2665), then adds the bias (2667-2671).  Products of bf16 / f16 inputs are exact in f32, the accumulator is f32
+ * (i32, wrapping, for integers); sum + bias is rounded once, by the store.  pad = {top, bottom, left, right}. */
+void zo_conv(int dtype, const void* x, const void* w, const void* bias, void* y, uint64_t n, uint64_t c, uint64_t h, uint64_t wd,
+             uint64_t o, uint64_t kh, uint64_t kw, uint64_t sh, uint64_t sw, uint64_t dh, uint64_t dw, const int64_t* pad) {
+  int64_t oh = ((int64_t)h + pad[0] + pad[1] - (int64_t)dh * ((int64_t)kh - 1) - 1) / (int64_t)sh + 1;
+  int64_t ow = ((int64_t)wd + pad[2] + pad[3] - (int64_t)dw * ((int64_t)kw - 1) - 1) / (int64_t)sw + 1;
+#pragma omp parallel for collapse(2)
+  for (uint64_t in = 0; in < n; in++)
+    for (uint64_t io = 0; io < o; io++)
+      for (int64_t i = 0; i < oh; i++)
+        for (int64_t j = 0; j < ow; j++) {
+          float acc = 0.0f; uint32_t iacc = 0;
+          for (uint64_t ic = 0; ic < c; ic++)
+            for (uint64_t r = 0; r < kh; r++)
+              for (uint64_t s = 0; s < kw; s++) {
+                int64_t iy = i * (int64_t)sh + (int64_t)(r * dh) - pad[0], ix = j * (int64_t)sw + (int64_t)(s * dw) - pad[2];
+                int inside = iy >= 0 && iy < (int64_t)h && ix >= 0 && ix < (int64_t)wd;
+                uint64_t xi = ((in * c + ic) * h + (uint64_t)(inside ? iy : 0)) * wd + (uint64_t)(inside ? ix : 0);
+                uint64_t wi = ((io * c + ic) * kh + r) * kw + s;
+                if (dtype == ZO_I32) iacc += (inside ? (uint32_t)((const int32_t*)x)[xi] : 0u) * (uint32_t)((const int32_t*)w)[wi];
+                else acc = (inside ? zo_load(x, dtype, xi) : 0.0f) * zo_load(w, dtype, wi) + acc;
+              }
+          uint64_t yi = ((in * o + io) * (uint64_t)oh + (uint64_t)i) * (uint64_t)ow + (uint64_t)j;
+          if (dtype == ZO_I32) ((int32_t*)y)[yi] = (int32_t)(iacc + (bias ? (uint32_t)((const int32_t*)bias)[io] : 0u));
+          else zo_store(y, dtype, yi, bias ? acc + zo_load(bias, dtype, io) : acc);
+        }
+}
+
 /* ---------------------------------------------------------------------------------------
  * Optimizers — zyx-optim/src/{sgd,adam,adamw}.rs.  Every hyper-parameter enters as a
  * rank-0 scalar and is therefore cast to the tensor dtype (truncated for bf16).  State

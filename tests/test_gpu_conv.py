@@ -1,0 +1,97 @@
+"""Parity of the convolution program (Tensor::conv, groups = 1) with the oracle: the direct kernel (f32, i32, small
+problems) and the implicit GEMM on the tensor cores (bf16 / f16), over strides, dilations, paddings and channel counts."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle as zo
+from tests.parity import TOL_BF16, TOL_F32, assert_parity
+from zyx_b200 import _lib as L
+
+pytestmark = pytest.mark.gpu
+RNG = np.random.default_rng(41)
+
+
+def exact_conv(x, w, b, stride, dilation, padding):
+    """float64 convolution of the same stored values: the third party for error attribution."""
+    pad = (padding,) * 4 if isinstance(padding, int) else ((padding[0], padding[0], padding[1], padding[1]) if len(padding) == 2 else padding)
+    xt = torch.nn.functional.pad(torch.from_numpy(np.asarray(x, np.float64)), (pad[2], pad[3], pad[0], pad[1]))
+    bt = None if b is None else torch.from_numpy(np.asarray(b, np.float64))
+    return torch.nn.functional.conv2d(xt, torch.from_numpy(np.asarray(w, np.float64)), bt, stride=stride, dilation=dilation).numpy()
+
+
+def test_reference_golden_vector(sess):
+    """zyx/tests/05_misc.rs:880-888 (conv1): arange(9) as [1,1,3,3] with a 2x2 filter of ones."""
+    t = np.arange(9, dtype=np.float32).reshape(1, 1, 3, 3)
+    y = sess.conv(L.F32, t, np.ones((1, 1, 2, 2), np.float32))
+    assert y.tolist() == [[[[8.0, 12.0], [20.0, 24.0]]]]
+
+
+@pytest.mark.parametrize("stride,dilation,padding", [(1, 1, 0), (2, 1, 1), ((2, 1), (1, 2), (1, 2)), (1, 2, (0, 2, 1, 3)), (3, 1, 2)])
+def test_f32_direct_kernel(sess, stride, dilation, padding):
+    x = RNG.standard_normal((2, 5, 19, 23)).astype(np.float32)
+    w = RNG.standard_normal((7, 5, 3, 2)).astype(np.float32)
+    b = RNG.standard_normal(7).astype(np.float32)
+    got = sess.conv(L.F32, x, w, b, stride, dilation, padding)
+    want = zo.conv(zo.F32, x, w, b, stride, dilation, padding)
+    assert got.shape == want.shape
+    assert_parity(got, want, exact_conv(x, w, b, stride, dilation, padding), TOL_F32, floor=0.1, what="conv f32")
+
+
+def test_i32_is_bit_exact(sess):
+    x = RNG.integers(-50, 50, (2, 3, 9, 8)).astype(np.int32)
+    w = RNG.integers(-9, 9, (4, 3, 3, 3)).astype(np.int32)
+    b = RNG.integers(-100, 100, 4).astype(np.int32)
+    got = sess.conv(L.I32, x, w, b, 2, 1, 1)
+    assert np.array_equal(got, zo.conv(zo.I32, x, w, b, 2, 1, 1))
+    assert np.array_equal(got, exact_conv(x, w, b, 2, 1, 1).astype(np.int64))
+
+
+# (n, c, h, w, o, kh, kw, stride, dilation, padding): every case has enough work for the tensor-core path
+TC_CASES = [
+    (2, 64, 56, 56, 64, 3, 3, 1, 1, 1),               # a ResNet 3x3 layer: 64-wide patches, two rows each
+    (1, 32, 57, 57, 96, 3, 3, 2, 1, 1),               # stride 2 through the tensor map's element strides
+    (2, 3, 64, 64, 64, 7, 7, 2, 1, 3),                # 3 channels (padded to 8), 7x7 stride 2
+    (3, 128, 14, 14, 256, 3, 3, 1, 1, 1),             # 256 filters per tile, 16 x 8 patches
+    (1, 72, 20, 300, 40, 1, 3, 1, 2, (0, 0, 2, 2)),   # rows wider than a patch, dilation 2, channels not a multiple of 64
+    (2, 40, 31, 29, 24, 3, 3, (2, 1), (1, 2), (0, 2, 1, 3)),   # mixed strides / dilations, asymmetric padding
+    (1, 256, 28, 28, 128, 1, 1, 1, 1, 0),             # 1x1: a plain matmul over channels
+    (4, 16, 9, 7, 512, 5, 5, 1, 1, 2),                # images smaller than a patch
+]
+
+
+@pytest.mark.parametrize("dtype", [L.BF16, L.F16])
+@pytest.mark.parametrize("case", TC_CASES)
+def test_implicit_gemm_on_tensor_cores(sess, dtype, case):
+    n, c, h, w_, o, kh, kw, stride, dilation, padding = case
+    x = zo.to_bits(RNG.standard_normal((n, c, h, w_)).astype(np.float32), dtype)
+    w = zo.to_bits((RNG.standard_normal((o, c, kh, kw)) / np.sqrt(c * kh * kw)).astype(np.float32), dtype)
+    b = zo.to_bits(RNG.standard_normal(o).astype(np.float32), dtype)
+    before = sess.device.launch_count()
+    got = sess.conv(dtype, x, w, b, stride, dilation, padding)
+    assert sess.device.launch_count() - before == 3, "expected the two layout kernels and the tensor-core kernel"
+    assert sess.device.status() == 0
+    want = zo.conv(dtype, x, w, b, stride, dilation, padding)
+    assert got.shape == want.shape
+    exact = exact_conv(zo.to_f32(x, dtype), zo.to_f32(w, dtype), zo.to_f32(b, dtype), stride, dilation, padding)
+    # tolerance 2e-2 relative to max(|want|, a tenth of the largest |want| along the row): sums of hundreds of products
+    assert_parity(zo.to_f32(got, dtype), zo.to_f32(want, dtype), exact, TOL_BF16, floor=0.1, what="conv %s" % (case,))
+
+
+def test_without_bias_and_small_problem_takes_the_direct_kernel(sess):
+    x = zo.to_bits(RNG.standard_normal((1, 4, 8, 8)).astype(np.float32), L.BF16)
+    w = zo.to_bits(RNG.standard_normal((4, 4, 3, 3)).astype(np.float32), L.BF16)
+    before = sess.device.launch_count()
+    got = sess.conv(L.BF16, x, w, None, 1, 1, 1)
+    assert sess.device.launch_count() - before == 1
+    want = zo.conv(zo.BF16, x, w, None, 1, 1, 1)
+    exact = exact_conv(zo.to_f32(x, L.BF16), zo.to_f32(w, L.BF16), None, 1, 1, 1)
+    assert_parity(zo.to_f32(got, L.BF16), zo.to_f32(want, L.BF16), exact, TOL_BF16, floor=0.1, what="conv direct bf16")
+
+
+def test_bad_arguments_are_errors(sess):
+    from zyx_b200 import backend as B
+    with pytest.raises(B.BackendError):
+        sess.device.create_program(B.conv_desc(L.F32, (1, 1, 2, 2), (1, 1, 3, 3)))      # filter larger than the input
+    with pytest.raises(B.BackendError):
+        sess.device.create_program(B.conv_desc(L.F64, (1, 1, 4, 4), (1, 1, 3, 3)))

@@ -212,3 +212,32 @@ def test_scalar_operands_are_cast():
     got = zo.to_f32(zo.layernorm(zo.BF16, zo.to_bits(x, zo.BF16)), zo.BF16)
     assert float(c(999.0)) == 996.0
     assert np.max(np.abs(got - want) / np.maximum(np.abs(want), 1e-2)) <= 2 ** -7
+
+
+def test_conv_golden_and_float64():
+    """zyx/tests/05_misc.rs:880-888 (conv1) is the reference's conv vector; strides, dilations and paddings are then held
+    against a float64 convolution of the same values (f32 sums of 30 products: 1e-5 relative to the largest output)."""
+    import torch
+    t = np.arange(9, dtype=np.float32).reshape(1, 1, 3, 3)
+    assert zo.conv(zo.F32, t, np.ones((1, 1, 2, 2), np.float32)).tolist() == [[[[8.0, 12.0], [20.0, 24.0]]]]
+    rng = np.random.default_rng(0)
+    x = rng.standard_normal((2, 5, 9, 11)).astype(np.float32)
+    w = rng.standard_normal((7, 5, 3, 2)).astype(np.float32)
+    b = rng.standard_normal(7).astype(np.float32)
+    for stride, dilation, pad in [(1, 1, (0, 0, 0, 0)), (2, 1, (1, 1, 1, 1)), ((2, 1), (1, 2), (1, 1, 2, 2)), (1, 2, (0, 2, 1, 3))]:
+        y = zo.conv(zo.F32, x, w, b, stride, dilation, pad)
+        xt = torch.nn.functional.pad(torch.from_numpy(x).double(), (pad[2], pad[3], pad[0], pad[1]))
+        want = torch.nn.functional.conv2d(xt, torch.from_numpy(w).double(), torch.from_numpy(b).double(), stride=stride, dilation=dilation).numpy()
+        assert y.shape == want.shape
+        assert np.abs(y - want).max() <= 1e-5 * np.abs(want).max()
+    xi = rng.integers(-50, 50, (1, 3, 6, 7)).astype(np.int32)
+    wi = rng.integers(-9, 9, (2, 3, 3, 3)).astype(np.int32)
+    yi = zo.conv(zo.I32, xi, wi, None, 1, 1, 1)
+    want = torch.nn.functional.conv2d(torch.from_numpy(xi).double(), torch.from_numpy(wi).double(), padding=1).numpy()
+    assert np.array_equal(yi, want.astype(np.int64))
+    # bf16: products exact in f32, one truncating store
+    xb, wb = zo.to_bits(x, zo.BF16), zo.to_bits(w, zo.BF16)
+    yb = zo.conv(zo.BF16, xb, wb, None, 1, 1, 1)
+    exact = torch.nn.functional.conv2d(torch.from_numpy(zo.to_f32(xb, zo.BF16)).double(), torch.from_numpy(zo.to_f32(wb, zo.BF16)).double(), padding=1).numpy()
+    got = zo.to_f32(yb, zo.BF16).astype(np.float64)
+    assert np.all(np.abs(got) <= np.abs(exact) + 1e-4) and np.abs(got - exact).max() <= 2.0 ** -7 * np.abs(exact).max()

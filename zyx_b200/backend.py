@@ -298,6 +298,39 @@ def attention_desc(dtype, batch, heads, seq, head_dim, ld=0, scale=0.0, causal=F
     return d
 
 
+def _pads(padding):
+    """(top, bottom, left, right) from an int, (pad_h, pad_w) or the four values."""
+    if isinstance(padding, int):
+        return (padding,) * 4
+    if len(padding) == 2:
+        return (padding[0], padding[0], padding[1], padding[1])
+    return tuple(padding)
+
+
+def conv_out_shape(x_shape, w_shape, stride=1, dilation=1, padding=0):
+    """[n, o, oh, ow] of Tensor::conv (zyx/src/tensor/mod.rs:2583-2680) for x [n,c,h,w], w [o,c,kh,kw]."""
+    sh, sw = (stride, stride) if isinstance(stride, int) else stride
+    dh, dw = (dilation, dilation) if isinstance(dilation, int) else dilation
+    pt, pb, pl, pr = _pads(padding)
+    n, _, h, w = x_shape
+    o, _, kh, kw = w_shape
+    return (n, o, (h + pt + pb - dh * (kh - 1) - 1) // sh + 1, (w + pl + pr - dw * (kw - 1) - 1) // sw + 1)
+
+
+def conv_desc(dtype, x_shape, w_shape, stride=1, dilation=1, padding=0, has_bias=False):
+    d = L.KernelDesc()
+    d.kind = L.KIND_CONV
+    c = d.u.conv
+    c.dtype = dtype
+    c.n, c.c, c.h, c.w = x_shape
+    c.o, _, c.kh, c.kw = w_shape
+    c.stride_h, c.stride_w = (stride, stride) if isinstance(stride, int) else stride
+    c.dil_h, c.dil_w = (dilation, dilation) if isinstance(dilation, int) else dilation
+    c.pad_top, c.pad_bottom, c.pad_left, c.pad_right = _pads(padding)
+    c.has_bias = int(has_bias)
+    return d
+
+
 def gemm_desc(dtype, m, n, k, batch=1, trans_a=False, trans_b=False, stride_a=None, stride_b=None, stride_c=None,
               epilogue=L.EPI_NONE, store_preact=False, alpha=0.0, lda=0, ldb=0, ldc=0, batch_inner=0, stride_a_inner=0,
               stride_b_inner=0, stride_c_inner=0, tri=0):

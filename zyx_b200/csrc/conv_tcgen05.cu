@@ -1,0 +1,413 @@
+// 2-D convolution forward (Tensor::conv with groups = 1, zyx/src/tensor/mod.rs:2583-2680).
+//   y[n,o,i,j] = bias[o] + sum_{c,r,s} x[n, c, i*stride_h + r*dil_h - pad_top, j*stride_w + s*dil_w - pad_left] * w[o,c,r,s]
+//
+// bf16 / f16 with enough work: implicit GEMM on the 5th-generation tensor cores.  The reference builds the im2col view
+// by reshape / expand / permute (pool, mod.rs:2442) and multiplies it with the weights; here no such matrix exists:
+//   prep   x [n,c,h,w] -> xt [n,h,w,cp] and w [o,c,kh,kw] -> wt [o, kh*kw, cp]  (channels innermost, cp = c rounded up
+//          to 8 so that every TMA row pitch is a multiple of 16 bytes; the added channels are zeros)
+//   GEMM   M = 128 output positions (a TH x TW patch of one image), N = BN output channels, K = kh*kw*cp walked as
+//          (tap, 64-channel block).  For every k-block one TMA box {64 channels, TW columns, TH rows} of xt at the tap's
+//          offset is the A tile - the tensor map's element strides carry the convolution stride, coordinates outside the
+//          image read the zero padding - and one box {64 channels, 1 tap, BN filters} of wt is the B tile.  Both land
+//          K-major in 128-byte-swizzled shared memory, exactly the layout of the matmul kernel's NT case.
+//   store  TMEM lane = output position, so for one output channel the 32 lanes of a warp hold 32 neighbouring positions:
+//          each warp store writes a run of the channels-first output directly, no transposition pass.
+// One persistent CTA per SM, 320 threads: warp 0 TMA producer, warp 1 MMA issuer, warps 2..9 epilogue; the accumulator is
+// double-buffered in TMEM.  Every mbarrier wait is bounded by wall-clock time and reports through the status word.
+//
+// Everything else (f32, i32, tiny problems, shapes the boxes cannot express): a direct kernel, one thread per output
+// element, summing in the reference's order (c, then r, then s), so integer results are bit-exact.
+#include <cuda.h>
+
+#include <algorithm>
+
+#include "common.cuh"
+#include "internal.h"
+#include "tc_ptx.cuh"
+
+namespace zyxb {
+
+namespace {
+
+constexpr int CV_BM = 128, CV_BK = 64, CV_UMMA_K = 16, CV_THREADS = 320, CV_EPI_THREADS = 256;
+
+struct ConvGeom {
+  uint32_t n, c, h, w, o, kh, kw, oh, ow;
+  uint32_t sh, sw, dh, dw;
+  int pt, pl;
+};
+
+struct ConvTcParams {
+  const void* bias; void* y;
+  ConvGeom g;
+  uint32_t cp, cblocks;              // padded channels; 64-channel blocks per tap
+  uint32_t tw, th, tw_shift;         // patch of output positions per tile: th * tw = 128
+  uint32_t tiles_w, tiles_h, tiles_n;
+  int rn, is_bf16;
+  uint32_t* status;
+};
+
+template <int BN, int STAGES>
+struct ConvSmem {
+  static constexpr int A_BYTES = CV_BM * CV_BK * 2;
+  static constexpr int B_BYTES = BN * CV_BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
+  static constexpr int TOTAL = BAR_OFFSET + 256 + 1024;   // + barriers + slack to align the base to 1024 B
+};
+
+enum { CV_ERR_PRODUCER = 16384u, CV_ERR_MMA = 32768u, CV_ERR_EPILOGUE = 65536u };
+
+// ---- prep: channels innermost ----------------------------------------------------------------------
+// x [n][c][hw] -> xt [n][hw][cp], 32 x 32 tiles through shared memory; channels c..cp-1 are written as zeros
+__global__ void conv_nhwc_kernel(const uint16_t* __restrict__ x, uint16_t* __restrict__ xt, uint32_t c, uint32_t cp, uint32_t hw) {
+  __shared__ uint16_t tile[32][33];
+  const uint32_t n = blockIdx.z, p0 = blockIdx.x * 32, c0 = blockIdx.y * 32;
+  const uint16_t* xs = x + (size_t)n * c * hw;
+  uint16_t* xd = xt + (size_t)n * hw * cp;
+  for (uint32_t j = threadIdx.y; j < 32; j += blockDim.y) {
+    const uint32_t ci = c0 + j, p = p0 + threadIdx.x;
+    tile[j][threadIdx.x] = (ci < c && p < hw) ? xs[(size_t)ci * hw + p] : (uint16_t)0;
+  }
+  __syncthreads();
+  for (uint32_t j = threadIdx.y; j < 32; j += blockDim.y) {
+    const uint32_t p = p0 + j, ci = c0 + threadIdx.x;
+    if (p < hw && ci < cp) xd[(size_t)p * cp + ci] = tile[threadIdx.x][j];
+  }
+}
+
+// w [o][c][taps] -> wt [o][taps][cp]
+__global__ void conv_weight_kernel(const uint16_t* __restrict__ w, uint16_t* __restrict__ wt, uint32_t c, uint32_t cp, uint32_t taps, uint64_t total) {
+  const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const uint32_t ci = (uint32_t)(i % cp);
+  const uint64_t ot = i / cp;
+  const uint32_t tap = (uint32_t)(ot % taps);
+  const uint64_t o = ot / taps;
+  wt[i] = ci < c ? w[(o * c + ci) * taps + tap] : (uint16_t)0;
+}
+
+// ---- implicit GEMM ---------------------------------------------------------------------------------
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(CV_THREADS, 1)
+conv_tc_kernel(const __grid_constant__ CUtensorMap tma_x, const __grid_constant__ CUtensorMap tma_w, ConvTcParams p) {
+  using SM = ConvSmem<BN, STAGES>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;          // swizzle atoms repeat every 1024 B
+  uint8_t* base_ptr = smem_raw + (base - raw);
+  const uint32_t bar_base = base + SM::BAR_OFFSET;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+  auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
+  auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + SM::BAR_OFFSET + 8 * (2 * STAGES + 4));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  constexpr uint32_t TMEM_COLS = 2 * BN;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), CV_EPI_THREADS); }
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const ConvGeom& g = p.g;
+  const uint32_t taps = g.kh * g.kw, k_blocks = taps * p.cblocks;
+  const uint32_t total_tiles = g.n * p.tiles_h * p.tiles_w * p.tiles_n;
+  // filter blocks vary fastest: the CTAs that share a patch of the image run at the same time and meet in L2
+  auto tile_coords = [&](uint32_t t, uint32_t& tn, uint32_t& img, uint32_t& oh0, uint32_t& ow0) {
+    tn = t % p.tiles_n; t /= p.tiles_n;
+    ow0 = (t % p.tiles_w) * p.tw; t /= p.tiles_w;
+    oh0 = (t % p.tiles_h) * p.th;
+    img = t / p.tiles_h;
+  };
+
+  if (warp == 0) {
+    // ---------------------------------- TMA producer ----------------------------------
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0, issued = 0;
+      bool ok = true;
+      for (uint32_t t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
+        uint32_t tn, img, oh0, ow0;
+        tile_coords(t, tn, img, oh0, ow0);
+        const int x0 = (int)(ow0 * g.sw) - g.pl, y0 = (int)(oh0 * g.sh) - g.pt;
+        for (uint32_t tap = 0; ok && tap < taps; ++tap) {
+          const int r = (int)(tap / g.kw), s = (int)(tap % g.kw);
+          for (uint32_t cb = 0; cb < p.cblocks; ++cb) {
+            if (!mbar_wait(empty_bar(stage), phase ^ 1, abort_flag, p.status, CV_ERR_PRODUCER)) { ok = false; break; }
+            const uint32_t a_dst = base + stage * SM::STAGE_BYTES, b_dst = a_dst + SM::A_BYTES;
+            mbar_expect_tx(full_bar(stage), SM::STAGE_BYTES);
+            // the channel coordinate (innermost) is a multiple of 64 elements: always on a 16-byte boundary
+            tma_load_4d(a_dst, &tma_x, full_bar(stage), (int)(cb * CV_BK), x0 + s * (int)g.dw, y0 + r * (int)g.dh, (int)img);
+            tma_load_4d(b_dst, &tma_w, full_bar(stage), (int)(cb * CV_BK), (int)tap, (int)(tn * BN), 0);
+            ++issued;
+            if (++stage == STAGES) { stage = 0; phase ^= 1; }
+          }
+        }
+      }
+      if (!ok) {
+        // drain: wait (bounded) for the copies still in flight so none lands after the CTA has gone
+        uint32_t s = stage, ph = phase;
+        const uint32_t n_back = issued < (uint32_t)STAGES ? issued : (uint32_t)STAGES;
+        for (uint32_t i = 0; i < n_back; ++i) {
+          if (s == 0) { s = STAGES - 1; ph ^= 1; } else --s;
+          const uint64_t t0 = global_timer_ns();
+          while (!mbar_try_wait(full_bar(s), ph) && global_timer_ns() - t0 < TC_WAIT_NS) {}
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------- MMA issuer ----------------------------------
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc(p.is_bf16 != 0, false, false, CV_BM, BN);
+      uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
+      bool ok = true;
+      for (uint32_t t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
+        if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1, abort_flag, p.status, CV_ERR_MMA)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (uint32_t kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(full_bar(stage), phase, abort_flag, p.status, CV_ERR_MMA)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_addr = base + stage * SM::STAGE_BYTES, b_addr = a_addr + SM::A_BYTES;
+#pragma unroll
+          for (int kk = 0; kk < CV_BK / CV_UMMA_K; ++kk) {
+            const uint64_t adesc = make_smem_desc(a_addr + kk * (CV_UMMA_K * 2), 16, 1024);
+            const uint64_t bdesc = make_smem_desc(b_addr + kk * (CV_UMMA_K * 2), 16, 1024);
+            umma_f16(d_tmem, adesc, bdesc, idesc, (kb != 0 || kk != 0) ? 1u : 0u);
+          }
+          umma_commit(empty_bar(stage));
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        umma_commit(tfull_bar(acc));
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      }
+    }
+  } else {
+    // ---------------------------------- epilogue (warps 2..9) ----------------------------------
+    const int col_half = (warp - 2) >> 2;
+    const uint32_t quarter = (uint32_t)(warp & 3);
+    const uint32_t row_in_tile = quarter * 32 + lane;
+    const uint32_t ty = row_in_tile >> p.tw_shift, tx = row_in_tile & (p.tw - 1);
+    uint32_t acc = 0, acc_phase = 0;
+    const bool rn = p.rn != 0, is_bf16 = p.is_bf16 != 0;
+    const uint16_t* bias = reinterpret_cast<const uint16_t*>(p.bias);
+    uint16_t* y = reinterpret_cast<uint16_t*>(p.y);
+    const size_t plane = (size_t)g.oh * g.ow;
+    for (uint32_t t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+      uint32_t tn, img, oh0, ow0;
+      tile_coords(t, tn, img, oh0, ow0);
+      if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.status, CV_ERR_EPILOGUE)) break;
+      tc_fence_after();
+      const uint32_t oy = oh0 + ty, ox = ow0 + tx;
+      const bool inside = oy < g.oh && ox < g.ow;
+      uint16_t* ypos = y + (size_t)img * g.o * plane + (size_t)oy * g.ow + ox;
+#pragma unroll 1
+      for (int ch = col_half * (BN / 64); ch < (col_half + 1) * (BN / 64); ++ch) {
+        uint32_t r[32];
+        tmem_ld32(tmem_base + ((quarter * 32u) << 16) + acc * BN + ch * 32, r);
+        tmem_ld_wait();
+        const uint32_t o0 = tn * BN + ch * 32;
+        if (inside && o0 < g.o) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const uint32_t o = o0 + j;
+            if (o < g.o) {
+              float v = __uint_as_float(r[j]);
+              if (bias) v += is_bf16 ? bf16_to_f32(bias[o]) : f16_to_f32(bias[o]);
+              ypos[(size_t)o * plane] = is_bf16 ? f32_to_bf16(v, rn) : f32_to_f16(v, rn);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(tempty_bar(acc));
+      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ---- direct kernel -----------------------------------------------------------------------------------
+template <typename T>
+__global__ void conv_direct_kernel(const typename Elem<T>::store_t* __restrict__ x, const typename Elem<T>::store_t* __restrict__ w,
+                                   const typename Elem<T>::store_t* __restrict__ bias, typename Elem<T>::store_t* __restrict__ y,
+                                   ConvGeom g, uint64_t total, int rn) {
+  using A = typename Elem<T>::acc_t;
+  for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
+    const uint32_t ox = (uint32_t)(i % g.ow);
+    uint64_t q = i / g.ow;
+    const uint32_t oy = (uint32_t)(q % g.oh); q /= g.oh;
+    const uint32_t o = (uint32_t)(q % g.o);
+    const uint64_t n = q / g.o;
+    A acc = 0;
+    for (uint32_t c = 0; c < g.c; ++c) {
+      const auto* xp = x + (n * g.c + c) * (uint64_t)g.h * g.w;
+      const auto* wp = w + ((uint64_t)o * g.c + c) * g.kh * g.kw;
+      for (uint32_t r = 0; r < g.kh; ++r) {
+        const int iy = (int)(oy * g.sh + r * g.dh) - g.pt;
+        if (iy < 0 || iy >= (int)g.h) continue;           // zero padding contributes nothing
+        for (uint32_t s = 0; s < g.kw; ++s) {
+          const int ix = (int)(ox * g.sw + s * g.dw) - g.pl;
+          if (ix < 0 || ix >= (int)g.w) continue;
+          acc += (A)Elem<T>::load(xp[(uint64_t)iy * g.w + ix]) * (A)Elem<T>::load(wp[r * g.kw + s]);
+        }
+      }
+    }
+    if (bias) acc += (A)Elem<T>::load(bias[o]);
+    y[i] = Elem<T>::store(acc, rn != 0);
+  }
+}
+
+bool geometry(const zyxb_conv_desc& d, ConvGeom& g, std::string& err) {
+  auto one = [](uint32_t v) { return v ? v : 1u; };
+  const uint64_t lim = 1u << 24;
+  if (!d.n || !d.c || !d.h || !d.w || !d.o || !d.kh || !d.kw) { err = "conv: every extent must be positive"; return false; }
+  if (d.n > lim || d.c > lim || d.h > lim || d.w > lim || d.o > lim || d.kh > 4096 || d.kw > 4096 || d.pad_top > lim || d.pad_left > lim ||
+      d.pad_bottom > lim || d.pad_right > lim || d.stride_h > lim || d.stride_w > lim || d.dil_h > lim || d.dil_w > lim) {
+    err = "conv: extent too large"; return false;
+  }
+  g.n = (uint32_t)d.n; g.c = (uint32_t)d.c; g.h = (uint32_t)d.h; g.w = (uint32_t)d.w; g.o = (uint32_t)d.o; g.kh = (uint32_t)d.kh; g.kw = (uint32_t)d.kw;
+  g.sh = one(d.stride_h); g.sw = one(d.stride_w); g.dh = one(d.dil_h); g.dw = one(d.dil_w);
+  g.pt = (int)d.pad_top; g.pl = (int)d.pad_left;
+  const int64_t eh = (int64_t)d.h + d.pad_top + d.pad_bottom - (int64_t)g.dh * (g.kh - 1) - 1;
+  const int64_t ew = (int64_t)d.w + d.pad_left + d.pad_right - (int64_t)g.dw * (g.kw - 1) - 1;
+  if (eh < 0 || ew < 0) { err = "conv: the dilated filter is larger than the padded input"; return false; }
+  g.oh = (uint32_t)(eh / g.sh + 1); g.ow = (uint32_t)(ew / g.sw + 1);
+  return true;
+}
+
+template <int BN, int STAGES>
+cudaError_t launch_conv_tc(const CUtensorMap& mx, const CUtensorMap& mw, const ConvTcParams& tp, unsigned grid, cudaStream_t s) {
+  using SM = ConvSmem<BN, STAGES>;
+  static bool configured = false;
+  auto kern = conv_tc_kernel<BN, STAGES>;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SM::TOTAL);
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  kern<<<grid, CV_THREADS, SM::TOTAL, s>>>(mx, mw, tp);
+  return cudaGetLastError();
+}
+
+// The tensor-core path: returns 1 when it took the launch, 0 when the shape is not for it, < 0 on an error (err set).
+int try_conv_tc(const zyxb_conv_desc& d, const ConvGeom& g, const void* x, const void* w, const void* bias, void* y, const LaunchCtx& lc,
+                std::string& err) {
+  static const bool off = getenv("ZYXB_NO_CONV_TC") != nullptr;
+  if (off || !lc.tma_encode || (d.dtype != ZYXB_BF16 && d.dtype != ZYXB_F16)) return 0;
+  // latency-bound problems and single-filter outputs stay on the direct kernel
+  const uint64_t positions = (uint64_t)g.n * g.oh * g.ow, kdim = (uint64_t)g.c * g.kh * g.kw;
+  if (positions * g.o * kdim < (1ull << 22) || g.o < 8 || positions < 128) return 0;
+  // patch of 128 output positions: tw = the power of two that covers a row (at most 128), th = 128 / tw
+  uint32_t tw = 8;
+  while (tw < 128 && tw < g.ow) tw <<= 1;
+  while (tw > 8 && tw * g.sw > 256) tw >>= 1;             // a TMA box spans at most 256 elements per dimension
+  const uint32_t th = 128 / tw;
+  if (tw * g.sw > 256 || th * g.sh > 256 || g.sw > 8 || g.sh > 8) return 0;   // element strides go up to 8
+  const uint32_t cp = (g.c + 7) / 8 * 8, taps = g.kh * g.kw;
+  const size_t xt_bytes = (size_t)g.n * g.h * g.w * cp * 2, wt_bytes = (size_t)g.o * taps * cp * 2;
+  const size_t wt_off = (xt_bytes + 1023) / 1024 * 1024;
+  if (wt_off + wt_bytes > lc.scratch_bytes) return 0;
+  if ((uintptr_t)lc.scratch % 1024) return 0;
+  uint16_t* xt = reinterpret_cast<uint16_t*>(lc.scratch);
+  uint16_t* wt = reinterpret_cast<uint16_t*>(reinterpret_cast<char*>(lc.scratch) + wt_off);
+  const bool bf16 = d.dtype == ZYXB_BF16;
+  const CUtensorMapDataType dt = bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  const int bn = g.o > 128 ? 256 : 128;
+  CUtensorMap mx, mw;
+  {
+    cuuint64_t dims[4] = {cp, g.w, g.h, g.n};
+    cuuint64_t strides[3] = {(cuuint64_t)cp * 2, (cuuint64_t)g.w * cp * 2, (cuuint64_t)g.h * g.w * cp * 2};
+    cuuint32_t box[4] = {64, tw * g.sw, th * g.sh, 1};    // loads ceil(box / element stride) = tw x th positions
+    cuuint32_t estr[4] = {1, g.sw, g.sh, 1};
+    if (reinterpret_cast<EncodeTiledFn>(lc.tma_encode)(&mx, dt, 4, xt, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                                       CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) return 0;
+    cuuint64_t wdims[4] = {cp, taps, g.o, 1};
+    cuuint64_t wstrides[3] = {(cuuint64_t)cp * 2, (cuuint64_t)taps * cp * 2, (cuuint64_t)g.o * taps * cp * 2};
+    cuuint32_t wbox[4] = {64, 1, (cuuint32_t)bn, 1};
+    cuuint32_t one[4] = {1, 1, 1, 1};
+    if (reinterpret_cast<EncodeTiledFn>(lc.tma_encode)(&mw, dt, 4, wt, wdims, wstrides, wbox, one, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                                       CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) return 0;
+  }
+  const uint32_t hw = g.h * g.w;
+  conv_nhwc_kernel<<<dim3((hw + 31) / 32, (cp + 31) / 32, g.n), dim3(32, 8), 0, lc.stream>>>(reinterpret_cast<const uint16_t*>(x), xt, g.c, cp, hw);
+  const uint64_t wtotal = (uint64_t)g.o * taps * cp;
+  conv_weight_kernel<<<(unsigned)((wtotal + 255) / 256), 256, 0, lc.stream>>>(reinterpret_cast<const uint16_t*>(w), wt, g.c, cp, taps, wtotal);
+  ConvTcParams tp{};
+  tp.bias = bias; tp.y = y; tp.g = g; tp.cp = cp; tp.cblocks = (cp + CV_BK - 1) / CV_BK;
+  tp.tw = tw; tp.th = th; tp.tw_shift = 0;
+  while ((1u << tp.tw_shift) < tw) ++tp.tw_shift;
+  tp.tiles_w = (g.ow + tw - 1) / tw; tp.tiles_h = (g.oh + th - 1) / th; tp.tiles_n = (g.o + bn - 1) / bn;
+  tp.rn = lc.round_nearest ? 1 : 0; tp.is_bf16 = bf16 ? 1 : 0; tp.status = lc.status_word;
+  const uint64_t total = (uint64_t)g.n * tp.tiles_h * tp.tiles_w * tp.tiles_n;
+  if (total >= 0x7fffffffull) { err = "conv: too many tiles"; return -ZYXB_ERR_INCORRECT_KERNEL_ARG; }
+  const unsigned grid = (unsigned)std::min<uint64_t>(total, (uint64_t)lc.sm_count);
+  cudaError_t e = bn == 256 ? launch_conv_tc<256, 4>(mx, mw, tp, grid, lc.stream) : launch_conv_tc<128, 6>(mx, mw, tp, grid, lc.stream);
+  if (e != cudaSuccess) { err = std::string("conv_tcgen05: ") + cudaGetErrorString(e); return -ZYXB_ERR_KERNEL_LAUNCH; }
+  *lc.launch_counter += 3;
+  return 1;
+}
+
+template <typename T>
+int launch_conv_direct(const ConvGeom& g, const void* x, const void* w, const void* bias, void* y, const LaunchCtx& lc, std::string& err) {
+  using S = typename Elem<T>::store_t;
+  const uint64_t total = (uint64_t)g.n * g.o * g.oh * g.ow;
+  const unsigned grid = (unsigned)std::min<uint64_t>((total + 255) / 256, (uint64_t)lc.sm_count * 16);
+  conv_direct_kernel<T><<<grid, 256, 0, lc.stream>>>(reinterpret_cast<const S*>(x), reinterpret_cast<const S*>(w), reinterpret_cast<const S*>(bias),
+                                                     reinterpret_cast<S*>(y), g, total, lc.round_nearest ? 1 : 0);
+  return check_launch(lc, err, "conv_direct");
+}
+
+}  // namespace
+
+int validate_conv(const zyxb_conv_desc& d, std::string& err) {
+  ZYXB_CHECK_ARG(d.dtype == ZYXB_BF16 || d.dtype == ZYXB_F16 || d.dtype == ZYXB_F32 || d.dtype == ZYXB_I32, "conv: dtype must be bf16, f16, f32 or i32");
+  ConvGeom g;
+  if (!geometry(d, g, err)) return ZYXB_ERR_INCORRECT_KERNEL_ARG;
+  return ZYXB_OK;
+}
+
+int launch_conv(const zyxb_conv_desc& d, void* const* args, const uint64_t* arg_bytes, int n_args, const LaunchCtx& lc, std::string& err) {
+  ConvGeom g;
+  if (!geometry(d, g, err)) return ZYXB_ERR_INCORRECT_KERNEL_ARG;
+  const int want = d.has_bias ? 4 : 3;
+  ZYXB_CHECK_ARG(n_args == want, "conv: expects x, w [,bias] -> y");
+  const uint64_t es = dtype_size(d.dtype);
+  ZYXB_CHECK_ARG(arg_bytes[0] >= (uint64_t)g.n * g.c * g.h * g.w * es, "conv: x is smaller than [n, c, h, w]");
+  ZYXB_CHECK_ARG(arg_bytes[1] >= (uint64_t)g.o * g.c * g.kh * g.kw * es, "conv: w is smaller than [o, c, kh, kw]");
+  if (d.has_bias) ZYXB_CHECK_ARG(arg_bytes[2] >= (uint64_t)g.o * es, "conv: bias is smaller than [o]");
+  ZYXB_CHECK_ARG(arg_bytes[want - 1] >= (uint64_t)g.n * g.o * g.oh * g.ow * es, "conv: y is smaller than [n, o, oh, ow]");
+  const void* x = args[0];
+  const void* w = args[1];
+  const void* bias = d.has_bias ? args[2] : nullptr;
+  void* y = args[want - 1];
+  const int took = try_conv_tc(d, g, x, w, bias, y, lc, err);
+  if (took < 0) return -took;
+  if (took) return ZYXB_OK;
+  switch (d.dtype) {
+    case ZYXB_F32: return launch_conv_direct<float>(g, x, w, bias, y, lc, err);
+    case ZYXB_BF16: return launch_conv_direct<bf16_t>(g, x, w, bias, y, lc, err);
+    case ZYXB_F16: return launch_conv_direct<f16_t>(g, x, w, bias, y, lc, err);
+    default: return launch_conv_direct<int32_t>(g, x, w, bias, y, lc, err);
+  }
+}
+
+}  // namespace zyxb

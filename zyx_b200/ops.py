@@ -120,6 +120,13 @@ class Session:
         d = B.attention_desc(dtype, batch, heads, seq, e // heads, scale=scale, causal=causal, backward=True)
         return tuple(self.run(d, [q, k, v, o, do, np.ascontiguousarray(lse, np.float32)], [(q.shape, q.dtype)] * 3))
 
+    def conv(self, dtype, x, w, bias=None, stride=1, dilation=1, padding=0):
+        """x [n,c,h,w], w [o,c,kh,kw], bias [o] -> y [n,o,oh,ow]  (Tensor::conv, groups = 1)."""
+        assert x.shape[1] == w.shape[1], "conv: channel counts differ"
+        d = B.conv_desc(dtype, x.shape, w.shape, stride, dilation, padding, has_bias=bias is not None)
+        shape = B.conv_out_shape(x.shape, w.shape, stride, dilation, padding)
+        return self.run(d, [x, w] + ([bias] if bias is not None else []), [(shape, x.dtype)])[0]
+
     # ---- optimizers (in place on the host arrays, like the oracle's) ------------------------------
     def optim_step(self, desc_kw, dtype, algo, tensors, t=None):
         """tensors: list of groups [p, g (, m, v | , buf)] of host arrays per parameter; updated in place."""
