@@ -56,7 +56,8 @@ TC_CASES = [
     (1, 72, 20, 300, 40, 1, 3, 1, 2, (0, 0, 2, 2)),   # rows wider than a patch, dilation 2, channels not a multiple of 64
     (2, 40, 31, 29, 24, 3, 3, (2, 1), (1, 2), (0, 2, 1, 3)),   # mixed strides / dilations, asymmetric padding
     (1, 256, 28, 28, 128, 1, 1, 1, 1, 0),             # 1x1: a plain matmul over channels
-    (4, 16, 9, 7, 512, 5, 5, 1, 1, 2),                # images smaller than a patch
+    (4, 16, 9, 7, 512, 5, 5, 1, 1, 2),                # images smaller than a tile: a tile spans several images
+    (1, 16, 12, 20, 32, 3, 3, 1, 1, (1, 1, 130, 2)),  # padding beyond the 8-bit corners of an im2col-mode map: patch mode
 ]
 
 

@@ -62,6 +62,7 @@ struct Device {
   size_t flush_bytes = 0;
   uint64_t launch_count = 0;
   void* tma_encode = nullptr;
+  void* tma_encode_im2col = nullptr;
   Comm* comm = nullptr;
   // captured launch sequences (the analogue of a FrozenTape): executable graph + kernels per replay
   std::vector<std::pair<cudaGraphExec_t, uint64_t>> graphs;
@@ -166,7 +167,7 @@ LaunchCtx make_launch_ctx(zyxb_ctx* ctx, Device& D) {
   LaunchCtx lc{};
   lc.stream = D.compute; lc.round_nearest = ctx->round_nearest; lc.sm_count = D.prop.multiProcessorCount;
   lc.status_word = D.status_word; lc.scratch = D.scratch; lc.scratch_bytes = D.scratch_bytes;
-  lc.launch_counter = &D.launch_count; lc.tma_encode = D.tma_encode; lc.device = D.cuda_id; lc.overlap_hint = D.comm != nullptr;
+  lc.launch_counter = &D.launch_count; lc.tma_encode = D.tma_encode; lc.tma_encode_im2col = D.tma_encode_im2col; lc.device = D.cuda_id; lc.overlap_hint = D.comm != nullptr;
   return lc;
 }
 
@@ -224,6 +225,10 @@ int32_t zyxb_init(const zyxb_config* config, zyxb_ctx** out_ctx) {
     void* fn = nullptr;
     if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) == cudaSuccess && qres == cudaDriverEntryPointSuccess)
       D.tma_encode = fn;
+    else cudaGetLastError();
+    fn = nullptr;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeIm2col", &fn, cudaEnableDefault, &qres) == cudaSuccess && qres == cudaDriverEntryPointSuccess)
+      D.tma_encode_im2col = fn;
     else cudaGetLastError();
     D.buffers.emplace_back();   // id 0 is never handed out
     D.programs.emplace_back();

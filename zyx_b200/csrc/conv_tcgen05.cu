@@ -43,6 +43,7 @@ struct ConvTcParams {
   uint32_t cp, cblocks;              // padded channels; 64-channel blocks per tap
   uint32_t tw, th, tw_shift;         // patch of output positions per tile: th * tw = 128
   uint32_t tiles_w, tiles_h, tiles_n;
+  uint32_t positions, tiles_m;        // im2col mode: n*oh*ow output positions in tiles of 128 consecutive ones
   int rn, is_bf16;
   uint32_t* status;
 };
@@ -76,6 +77,33 @@ __global__ void conv_nhwc_kernel(const uint16_t* __restrict__ x, uint16_t* __res
   }
 }
 
+// The same for an even hw: 64 x 64 tiles moved as 32-bit words on both sides (two positions per word when read, two
+// channels per word when written), so every warp access covers whole 128-byte lines.
+__global__ void __launch_bounds__(256) conv_nhwc_pairs_kernel(const uint16_t* __restrict__ x, uint16_t* __restrict__ xt, uint32_t c, uint32_t cp, uint32_t hw) {
+  __shared__ __align__(4) uint16_t tile[64][66];
+  const uint32_t n = blockIdx.z, p0 = blockIdx.x * 64, c0 = blockIdx.y * 64;
+  const uint16_t* xs = x + (size_t)n * c * hw;
+  uint16_t* xd = xt + (size_t)n * hw * cp;
+#pragma unroll
+  for (uint32_t i = 0; i < 8; ++i) {
+    const uint32_t idx = i * 256 + threadIdx.x, cj = idx >> 5, pp = (idx & 31) * 2;
+    const uint32_t ci = c0 + cj, p = p0 + pp;
+    uint32_t v = 0;
+    if (ci < c && p < hw) v = __ldcs(reinterpret_cast<const uint32_t*>(xs + (size_t)ci * hw + p));   // hw even: p + 1 < hw too
+    *reinterpret_cast<uint32_t*>(&tile[cj][pp]) = v;
+  }
+  __syncthreads();
+#pragma unroll
+  for (uint32_t i = 0; i < 8; ++i) {
+    const uint32_t idx = i * 256 + threadIdx.x, pj = idx >> 5, cc = (idx & 31) * 2;
+    const uint32_t p = p0 + pj, ci = c0 + cc;
+    if (p < hw && ci < cp) {                              // cp even: ci + 1 < cp too
+      const uint32_t v = (uint32_t)tile[cc][pj] | ((uint32_t)tile[cc + 1][pj] << 16);
+      *reinterpret_cast<uint32_t*>(xd + (size_t)p * cp + ci) = v;
+    }
+  }
+}
+
 // w [o][c][taps] -> wt [o][taps][cp]
 __global__ void conv_weight_kernel(const uint16_t* __restrict__ w, uint16_t* __restrict__ wt, uint32_t c, uint32_t cp, uint32_t taps, uint64_t total) {
   const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -88,7 +116,7 @@ __global__ void conv_weight_kernel(const uint16_t* __restrict__ w, uint16_t* __r
 }
 
 // ---- implicit GEMM ---------------------------------------------------------------------------------
-template <int BN, int STAGES>
+template <int BN, int STAGES, bool IM2COL>
 __global__ void __launch_bounds__(CV_THREADS, 1)
 conv_tc_kernel(const __grid_constant__ CUtensorMap tma_x, const __grid_constant__ CUtensorMap tma_w, ConvTcParams p) {
   using SM = ConvSmem<BN, STAGES>;
@@ -121,13 +149,24 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tma_x, const __grid_constant_
 
   const ConvGeom& g = p.g;
   const uint32_t taps = g.kh * g.kw, k_blocks = taps * p.cblocks;
-  const uint32_t total_tiles = g.n * p.tiles_h * p.tiles_w * p.tiles_n;
-  // filter blocks vary fastest: the CTAs that share a patch of the image run at the same time and meet in L2
-  auto tile_coords = [&](uint32_t t, uint32_t& tn, uint32_t& img, uint32_t& oh0, uint32_t& ow0) {
+  const uint32_t total_tiles = (IM2COL ? p.tiles_m : g.n * p.tiles_h * p.tiles_w) * p.tiles_n;
+  const uint32_t plane = g.oh * g.ow;
+  // Filter blocks vary fastest: the CTAs that share a patch of the image run at the same time and meet in L2.
+  // Tiled mode: the tile is a th x tw patch of image img at (oh0, ow0).  im2col mode: the tile is the 128 positions that
+  // follow (img, oh0, ow0) in row-major order, across rows and images; m0 is the first one's flat index.
+  auto tile_coords = [&](uint32_t t, uint32_t& tn, uint32_t& img, uint32_t& oh0, uint32_t& ow0, uint32_t& m0) {
     tn = t % p.tiles_n; t /= p.tiles_n;
-    ow0 = (t % p.tiles_w) * p.tw; t /= p.tiles_w;
-    oh0 = (t % p.tiles_h) * p.th;
-    img = t / p.tiles_h;
+    if constexpr (IM2COL) {
+      m0 = t * CV_BM;
+      img = m0 / plane;
+      const uint32_t rem = m0 - img * plane;
+      oh0 = rem / g.ow; ow0 = rem - oh0 * g.ow;
+    } else {
+      m0 = 0;
+      ow0 = (t % p.tiles_w) * p.tw; t /= p.tiles_w;
+      oh0 = (t % p.tiles_h) * p.th;
+      img = t / p.tiles_h;
+    }
   };
 
   if (warp == 0) {
@@ -136,8 +175,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tma_x, const __grid_constant_
       uint32_t stage = 0, phase = 0, issued = 0;
       bool ok = true;
       for (uint32_t t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
-        uint32_t tn, img, oh0, ow0;
-        tile_coords(t, tn, img, oh0, ow0);
+        uint32_t tn, img, oh0, ow0, m0;
+        tile_coords(t, tn, img, oh0, ow0, m0);
         const int x0 = (int)(ow0 * g.sw) - g.pl, y0 = (int)(oh0 * g.sh) - g.pt;
         for (uint32_t tap = 0; ok && tap < taps; ++tap) {
           const int r = (int)(tap / g.kw), s = (int)(tap % g.kw);
@@ -146,7 +185,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tma_x, const __grid_constant_
             const uint32_t a_dst = base + stage * SM::STAGE_BYTES, b_dst = a_dst + SM::A_BYTES;
             mbar_expect_tx(full_bar(stage), SM::STAGE_BYTES);
             // the channel coordinate (innermost) is a multiple of 64 elements: always on a 16-byte boundary
-            tma_load_4d(a_dst, &tma_x, full_bar(stage), (int)(cb * CV_BK), x0 + s * (int)g.dw, y0 + r * (int)g.dh, (int)img);
+            if constexpr (IM2COL) tma_load_im2col_4d(a_dst, &tma_x, full_bar(stage), (int)(cb * CV_BK), x0, y0, (int)img, (uint16_t)(s * g.dw), (uint16_t)(r * g.dh));
+            else tma_load_4d(a_dst, &tma_x, full_bar(stage), (int)(cb * CV_BK), x0 + s * (int)g.dw, y0 + r * (int)g.dh, (int)img);
             tma_load_4d(b_dst, &tma_w, full_bar(stage), (int)(cb * CV_BK), (int)tap, (int)(tn * BN), 0);
             ++issued;
             if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -202,15 +242,22 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tma_x, const __grid_constant_
     const bool rn = p.rn != 0, is_bf16 = p.is_bf16 != 0;
     const uint16_t* bias = reinterpret_cast<const uint16_t*>(p.bias);
     uint16_t* y = reinterpret_cast<uint16_t*>(p.y);
-    const size_t plane = (size_t)g.oh * g.ow;
     for (uint32_t t = blockIdx.x; t < total_tiles; t += gridDim.x) {
-      uint32_t tn, img, oh0, ow0;
-      tile_coords(t, tn, img, oh0, ow0);
+      uint32_t tn, img, oh0, ow0, m0;
+      tile_coords(t, tn, img, oh0, ow0, m0);
       if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.status, CV_ERR_EPILOGUE)) break;
       tc_fence_after();
-      const uint32_t oy = oh0 + ty, ox = ow0 + tx;
-      const bool inside = oy < g.oh && ox < g.ow;
-      uint16_t* ypos = y + (size_t)img * g.o * plane + (size_t)oy * g.ow + ox;
+      bool inside;
+      uint16_t* ypos;
+      if constexpr (IM2COL) {
+        const uint32_t m = m0 + row_in_tile, im = m / plane;      // this lane's position: image im, offset m - im * plane in its plane
+        inside = m < p.positions;
+        ypos = y + (size_t)im * g.o * plane + (m - im * plane);
+      } else {
+        const uint32_t oy = oh0 + ty, ox = ow0 + tx;
+        inside = oy < g.oh && ox < g.ow;
+        ypos = y + (size_t)img * g.o * plane + (size_t)oy * g.ow + ox;
+      }
 #pragma unroll 1
       for (int ch = col_half * (BN / 64); ch < (col_half + 1) * (BN / 64); ++ch) {
         uint32_t r[32];
@@ -292,11 +339,11 @@ bool geometry(const zyxb_conv_desc& d, ConvGeom& g, std::string& err) {
   return true;
 }
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, bool IM2COL>
 cudaError_t launch_conv_tc(const CUtensorMap& mx, const CUtensorMap& mw, const ConvTcParams& tp, unsigned grid, cudaStream_t s) {
   using SM = ConvSmem<BN, STAGES>;
   static bool configured = false;
-  auto kern = conv_tc_kernel<BN, STAGES>;
+  auto kern = conv_tc_kernel<BN, STAGES, IM2COL>;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SM::TOTAL);
     if (e != cudaSuccess) return e;
@@ -314,12 +361,20 @@ int try_conv_tc(const zyxb_conv_desc& d, const ConvGeom& g, const void* x, const
   // latency-bound problems and single-filter outputs stay on the direct kernel
   const uint64_t positions = (uint64_t)g.n * g.oh * g.ow, kdim = (uint64_t)g.c * g.kh * g.kw;
   if (positions * g.o * kdim < (1ull << 22) || g.o < 8 || positions < 128) return 0;
-  // patch of 128 output positions: tw = the power of two that covers a row (at most 128), th = 128 / tw
+  if (g.sw > 8 || g.sh > 8) return 0;                     // element strides of a tensor map go up to 8
+  // im2col-mode tensor map: 128 consecutive output positions per tile, whatever the image's width.  Its corners and tap
+  // offsets are 8-bit fields for a rank-4 map.
+  static const bool tiled_only = getenv("ZYXB_CONV_TILED") != nullptr;
+  const int lo_w = -g.pl, lo_h = -g.pt;
+  const int up_w = (int)d.pad_right - (int)((g.kw - 1) * g.dw), up_h = (int)d.pad_bottom - (int)((g.kh - 1) * g.dh);
+  const bool im2col = !tiled_only && lc.tma_encode_im2col && lo_w >= -128 && lo_h >= -128 && up_w >= -128 && up_w <= 127 && up_h >= -128 &&
+                      up_h <= 127 && (g.kw - 1) * g.dw <= 255 && (g.kh - 1) * g.dh <= 255 && positions < 0x7fffff00ull;
+  // tiled-mode fallback: a th x tw patch of one image per tile, tw = the power of two that covers a row (at most 128)
   uint32_t tw = 8;
   while (tw < 128 && tw < g.ow) tw <<= 1;
   while (tw > 8 && tw * g.sw > 256) tw >>= 1;             // a TMA box spans at most 256 elements per dimension
   const uint32_t th = 128 / tw;
-  if (tw * g.sw > 256 || th * g.sh > 256 || g.sw > 8 || g.sh > 8) return 0;   // element strides go up to 8
+  if (!im2col && (tw * g.sw > 256 || th * g.sh > 256)) return 0;
   const uint32_t cp = (g.c + 7) / 8 * 8, taps = g.kh * g.kw;
   const size_t xt_bytes = (size_t)g.n * g.h * g.w * cp * 2, wt_bytes = (size_t)g.o * taps * cp * 2;
   const size_t wt_off = (xt_bytes + 1023) / 1024 * 1024;
@@ -334,11 +389,19 @@ int try_conv_tc(const zyxb_conv_desc& d, const ConvGeom& g, const void* x, const
   {
     cuuint64_t dims[4] = {cp, g.w, g.h, g.n};
     cuuint64_t strides[3] = {(cuuint64_t)cp * 2, (cuuint64_t)g.w * cp * 2, (cuuint64_t)g.h * g.w * cp * 2};
-    cuuint32_t box[4] = {64, tw * g.sw, th * g.sh, 1};    // loads ceil(box / element stride) = tw x th positions
     cuuint32_t estr[4] = {1, g.sw, g.sh, 1};
-    if (reinterpret_cast<EncodeTiledFn>(lc.tma_encode)(&mx, dt, 4, xt, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                                                       CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                                                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) return 0;
+    if (im2col) {
+      // bounding box of the filter windows' first elements: [-pad, extent + pad - dilated filter extent] per dimension
+      const int lower[2] = {lo_w, lo_h}, upper[2] = {up_w, up_h};
+      if (reinterpret_cast<EncodeIm2colFn>(lc.tma_encode_im2col)(&mx, dt, 4, xt, dims, strides, lower, upper, 64, CV_BM, estr,
+                                                                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                                                 CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) return 0;
+    } else {
+      cuuint32_t box[4] = {64, tw * g.sw, th * g.sh, 1};  // loads ceil(box / element stride) = tw x th positions
+      if (reinterpret_cast<EncodeTiledFn>(lc.tma_encode)(&mx, dt, 4, xt, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) return 0;
+    }
     cuuint64_t wdims[4] = {cp, taps, g.o, 1};
     cuuint64_t wstrides[3] = {(cuuint64_t)cp * 2, (cuuint64_t)taps * cp * 2, (cuuint64_t)g.o * taps * cp * 2};
     cuuint32_t wbox[4] = {64, 1, (cuuint32_t)bn, 1};
@@ -348,7 +411,10 @@ int try_conv_tc(const zyxb_conv_desc& d, const ConvGeom& g, const void* x, const
                                                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) return 0;
   }
   const uint32_t hw = g.h * g.w;
-  conv_nhwc_kernel<<<dim3((hw + 31) / 32, (cp + 31) / 32, g.n), dim3(32, 8), 0, lc.stream>>>(reinterpret_cast<const uint16_t*>(x), xt, g.c, cp, hw);
+  if (hw % 2 == 0 && (uintptr_t)x % 4 == 0)
+    conv_nhwc_pairs_kernel<<<dim3((hw + 63) / 64, (cp + 63) / 64, g.n), 256, 0, lc.stream>>>(reinterpret_cast<const uint16_t*>(x), xt, g.c, cp, hw);
+  else
+    conv_nhwc_kernel<<<dim3((hw + 31) / 32, (cp + 31) / 32, g.n), dim3(32, 8), 0, lc.stream>>>(reinterpret_cast<const uint16_t*>(x), xt, g.c, cp, hw);
   const uint64_t wtotal = (uint64_t)g.o * taps * cp;
   conv_weight_kernel<<<(unsigned)((wtotal + 255) / 256), 256, 0, lc.stream>>>(reinterpret_cast<const uint16_t*>(w), wt, g.c, cp, taps, wtotal);
   ConvTcParams tp{};
@@ -357,10 +423,13 @@ int try_conv_tc(const zyxb_conv_desc& d, const ConvGeom& g, const void* x, const
   while ((1u << tp.tw_shift) < tw) ++tp.tw_shift;
   tp.tiles_w = (g.ow + tw - 1) / tw; tp.tiles_h = (g.oh + th - 1) / th; tp.tiles_n = (g.o + bn - 1) / bn;
   tp.rn = lc.round_nearest ? 1 : 0; tp.is_bf16 = bf16 ? 1 : 0; tp.status = lc.status_word;
-  const uint64_t total = (uint64_t)g.n * tp.tiles_h * tp.tiles_w * tp.tiles_n;
+  tp.positions = (uint32_t)positions; tp.tiles_m = (uint32_t)((positions + CV_BM - 1) / CV_BM);
+  const uint64_t total = (im2col ? (uint64_t)tp.tiles_m : (uint64_t)g.n * tp.tiles_h * tp.tiles_w) * tp.tiles_n;
   if (total >= 0x7fffffffull) { err = "conv: too many tiles"; return -ZYXB_ERR_INCORRECT_KERNEL_ARG; }
   const unsigned grid = (unsigned)std::min<uint64_t>(total, (uint64_t)lc.sm_count);
-  cudaError_t e = bn == 256 ? launch_conv_tc<256, 4>(mx, mw, tp, grid, lc.stream) : launch_conv_tc<128, 6>(mx, mw, tp, grid, lc.stream);
+  cudaError_t e;
+  if (im2col) e = bn == 256 ? launch_conv_tc<256, 4, true>(mx, mw, tp, grid, lc.stream) : launch_conv_tc<128, 6, true>(mx, mw, tp, grid, lc.stream);
+  else e = bn == 256 ? launch_conv_tc<256, 4, false>(mx, mw, tp, grid, lc.stream) : launch_conv_tc<128, 6, false>(mx, mw, tp, grid, lc.stream);
   if (e != cudaSuccess) { err = std::string("conv_tcgen05: ") + cudaGetErrorString(e); return -ZYXB_ERR_KERNEL_LAUNCH; }
   *lc.launch_counter += 3;
   return 1;

@@ -19,6 +19,7 @@ struct LaunchCtx {
   size_t scratch_bytes;
   uint64_t* launch_counter; // host counter of kernels launched
   void* tma_encode;         // cuTensorMapEncodeTiled entry point (driver), or nullptr
+  void* tma_encode_im2col;  // cuTensorMapEncodeIm2col entry point (driver), or nullptr
   int device;
   bool overlap_hint;        // a communicator exists: collectives may run beside the kernels
 };
