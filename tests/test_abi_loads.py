@@ -43,16 +43,16 @@ def test_struct_sizes_match_the_header():
 #include <stdio.h>
 #include "zyxb.h"
 int main(void) {
-  printf("%zu %zu %zu %zu %zu %zu %zu %zu\n", sizeof(zyxb_event), sizeof(zyxb_config), sizeof(zyxb_devinfo),
+  printf("%zu %zu %zu %zu %zu %zu %zu %zu %zu %zu\n", sizeof(zyxb_event), sizeof(zyxb_config), sizeof(zyxb_devinfo),
          sizeof(zyxb_rowreduce_desc), sizeof(zyxb_gemm_desc), sizeof(zyxb_eltwise_desc), sizeof(zyxb_optim_desc),
-         sizeof(zyxb_kernel_desc));
+         sizeof(zyxb_attention_desc), sizeof(zyxb_conv_desc), sizeof(zyxb_kernel_desc));
   return 0;
 }'''
     with tempfile.TemporaryDirectory() as d:
         open(os.path.join(d, "t.c"), "w").write(src)
         subprocess.check_call(["gcc", "-std=c11", "-I", os.path.join(ROOT, "include"), os.path.join(d, "t.c"), "-o", os.path.join(d, "t")])
         out = subprocess.check_output([os.path.join(d, "t")]).split()
-    want = [C.sizeof(t) for t in (L.Event, L.Config, L.DevInfo, L.RowReduceDesc, L.GemmDesc, L.EltwiseDesc, L.OptimDesc, L.KernelDesc)]
+    want = [C.sizeof(t) for t in (L.Event, L.Config, L.DevInfo, L.RowReduceDesc, L.GemmDesc, L.EltwiseDesc, L.OptimDesc, L.AttentionDesc, L.ConvDesc, L.KernelDesc)]
     assert [int(v) for v in out] == want
 
 
