@@ -595,11 +595,11 @@ class MlpTrain:
     batch = 8192
     unit, dtype, bound = "samples/s", "bf16", "tensor"
 
-    def __init__(self, size=0, standard=False, rank=0, world=1):
+    def __init__(self, size=0, standard=False, rank=0, world=1, shard_optimizer=False):
         self.full_size = not size
         if size:
             self.batch = size
-        self.standard, self.rank, self.world = standard, rank, world
+        self.standard, self.rank, self.world, self.shard = standard, rank, world, shard_optimizer
         self.name = "mlp_4xlinear_4096_16384_gelu_bf16_adamw_batch%d_per_gpu" % self.batch
         self.metric = "MLP train samples/s (4x Linear 4096<->16384, GELU, bf16, AdamW, batch %d per GPU)" % self.batch
         self.units_per_step = float(self.batch)
@@ -620,7 +620,7 @@ class MlpTrain:
         self.sess, self.H = sess, H
         self.host_inputs()
         self.mlp = H.Mlp(sess, L.BF16, self.batch, self.dims, activation=H.ACT_GELU, loss=H.LOSS_MSE, algo=L.OPT_ADAMW, world=self.world,
-                         bucket_per_layer=True, lr=1e-3, weight_decay=0.01, standard=self.standard)
+                         bucket_per_layer=True, shard_optimizer=self.shard, lr=1e-3, weight_decay=0.01, standard=self.standard)
         rng = np.random.default_rng(0)            # the same random-init weights on every rank (Linear::new's distribution)
         for i in range(self.mlp.n_params()):
             layer = i // 2
@@ -643,7 +643,7 @@ class MlpTrain:
                        "optimizer": "AdamW lr=1e-3 wd=0.01, " + ("textbook update" if self.standard else
                                     "update as the reference writes it (step divided by lr)"),
                        "l2": "working set (params 0.5 GB, activations 2.7 GB) larger than L2", "launches_per_step": launches,
-                       "collectives_per_step": colls,
+                       "collectives_per_step": colls, "optimizer_state": "sharded over the ranks (reduce-scatter, shard update, all-gather)" if self.shard else "replicated",
                        "param_reset": "parameters copied back from a pristine device copy at the start of every step "
                                       "(%d bytes d2d inside the timed step) so all values stay finite" % self.reset_bytes}
         self.mlp.profile(True)
@@ -651,6 +651,8 @@ class MlpTrain:
 
     def reset_params(self):
         p = self.sess.pool
+        if self.shard:
+            self.mlp.tensor(self.H.PARAM, 0)      # blocks until the previous step's parameter all-gathers have landed: the reset must not race them
         for (buf, numel), copy in zip(self.params, self.pristine):
             p.release_events([p.pool_to_pool(p, copy, buf, numel * 2)])
 
@@ -913,7 +915,7 @@ WORKLOADS = {"block": BlockTrain, "simplenet": SimpleNet, "mlp": MlpTrain, "rowr
 
 def make_workload(args, rank=0, world=1):
     if args.workload == "mlp":
-        return MlpTrain(size=args.size, standard=args.standard_adamw, rank=rank, world=world)
+        return MlpTrain(size=args.size, standard=args.standard_adamw, rank=rank, world=world, shard_optimizer=args.shard_optimizer)
     if args.workload == "simplenet":
         return SimpleNet(size=args.size, rank=rank, world=world)
     if args.workload == "block":
@@ -982,6 +984,7 @@ def run():
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end leg (profiling runs)")
+    ap.add_argument("--shard-optimizer", action="store_true", help="mlp workload: ZeRO stage 1 (reduce-scatter, sharded AdamW, all-gather) instead of allreduce + replicated AdamW")
     ap.add_argument("--size", type=int, default=0, help="reduced problem size for profiler captures: rows (rowreduce) or N (gemm)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)

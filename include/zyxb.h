@@ -387,6 +387,15 @@ int32_t zyxb_comm_unique_id(zyxb_ctx* ctx, void* out_id_128_bytes);
 int32_t zyxb_comm_init(zyxb_ctx* ctx, int32_t dev, int32_t rank, int32_t world, const void* id_128_bytes);
 int32_t zyxb_allreduce_sum(zyxb_ctx* ctx, int32_t dev, uint32_t buf, uint64_t offset_elems, uint64_t count, int32_t dtype,
                            const zyxb_event* wait, int32_t n_wait, zyxb_event* out_event);
+/* The two halves of an allreduce, for an optimizer whose state is sharded over the ranks (ZeRO stage 1).  Both work in
+ * place on `world` consecutive slices of count_per_rank elements starting at offset_elems: after reduce_scatter_sum
+ * slice `rank` holds the sum over ranks (the other slices are unspecified); allgather sends this rank's slice and
+ * leaves all `world` slices filled.  Same stream and event rules as zyxb_allreduce_sum. */
+int32_t zyxb_reduce_scatter_sum(zyxb_ctx* ctx, int32_t dev, uint32_t buf, uint64_t offset_elems, uint64_t count_per_rank, int32_t dtype,
+                                const zyxb_event* wait, int32_t n_wait, zyxb_event* out_event);
+int32_t zyxb_allgather(zyxb_ctx* ctx, int32_t dev, uint32_t buf, uint64_t offset_elems, uint64_t count_per_rank, int32_t dtype,
+                       const zyxb_event* wait, int32_t n_wait, zyxb_event* out_event);
+int32_t zyxb_comm_rank(zyxb_ctx* ctx, int32_t dev, int32_t* out_rank, int32_t* out_world);
 int32_t zyxb_comm_destroy(zyxb_ctx* ctx, int32_t dev);
 
 #ifdef __cplusplus

@@ -35,6 +35,12 @@ typedef struct {
                                 optim.grad_scale is set to 1/world */
   int32_t  bucket_per_layer; /* 1: one allreduce per layer as soon as its gradients are queued (overlaps the rest of
                                 the backward pass); 0: one allreduce over the whole gradient bucket */
+  int32_t  shard_optimizer;  /* 1 (needs a communicator, any world >= 1, and bucket_per_layer): ZeRO stage 1.  Parameters live in
+                                one bucket laid out like the gradients'; each layer's slice is cut into `world` shards;
+                                gradients are reduce-scattered, this rank updates its shard (optimizer state of shard size
+                                only: 1/world of the memory and of the update's HBM traffic), and the parameters are
+                                all-gathered, first layer first, behind the next step's forward pass.  zyxb_mlp_tensor then
+                                has no optimizer-state buffers, and a checkpoint holds this rank's state shards. */
 } zyxb_mlp_config;
 
 typedef struct zyxb_mlp zyxb_mlp;

@@ -176,3 +176,43 @@ def test_simplenet_step_replayed_from_a_captured_graph(sess):
         if graph:
             sess.device.graph_release(graph)
         mlp.close()
+
+
+def test_sharded_optimizer_plan_equals_the_replicated_plan(sess):
+    """ZeRO stage 1 on a one-rank communicator: parameters in one bucket, reduce-scatter / shard update / all-gather.  The
+    kernels and their arithmetic are those of the replicated plan (an elementwise update does not care where tensors begin),
+    so after three steps parameters and loss are bit-identical."""
+    dims, batch, dt = [64, 128, 64, 128, 64], 96, L.BF16
+    rng = zo.Rng(7)
+    layers = om.init_linears(rng, zo.BF16, dims)
+    kw = dict(lr=1e-3, weight_decay=0.01, standard=True)
+    batches = [(zo.to_bits(rng.randn(batch * dims[0]).reshape(batch, dims[0]), zo.BF16),
+                zo.to_bits(rng.randn(batch * dims[-1]).reshape(batch, dims[-1]), zo.BF16)) for _ in range(3)]
+
+    def train(shard):
+        mlp = H.Mlp(sess, dt, batch, dims, activation=H.ACT_GELU, loss=H.LOSS_MSE, algo=L.OPT_ADAMW, world=1, shard_optimizer=shard, **kw)
+        try:
+            load_params(mlp, layers)
+            losses = []
+            for x, t in batches:
+                mlp.step(mlp.set_batch(x, t))
+                losses.append(mlp.read_loss())
+            assert sess.device.status() == 0
+            if shard:
+                assert mlp.plan_size()[1] == 8                      # four reduce-scatters, four all-gathers
+                with pytest.raises(Exception):
+                    mlp.tensor(H.STATE0, 0)                         # the state has no per-tensor buffers
+            return losses, [mlp.get_tensor(H.PARAM, i) for i in range(mlp.n_params())]
+        finally:
+            mlp.close()
+
+    want_losses, want = train(False)
+    sess.device.comm_init(0, 1, sess.device.comm_unique_id())
+    try:
+        assert sess.device.comm_rank() == (0, 1)
+        got_losses, got = train(True)
+    finally:
+        sess.device.comm_destroy()
+    assert got_losses == want_losses
+    for g, w in zip(got, want):
+        assert np.array_equal(g, w)

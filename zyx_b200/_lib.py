@@ -139,6 +139,9 @@ SIGNATURES = {
     "zyxb_comm_unique_id": (C.c_int32, [_CTX, C.c_void_p]),
     "zyxb_comm_init": (C.c_int32, [_CTX, C.c_int32, C.c_int32, C.c_int32, C.c_void_p]),
     "zyxb_allreduce_sum": (C.c_int32, [_CTX, C.c_int32, C.c_uint32, C.c_uint64, C.c_uint64, C.c_int32, _EV_P, C.c_int32, _EV_P]),
+    "zyxb_reduce_scatter_sum": (C.c_int32, [_CTX, C.c_int32, C.c_uint32, C.c_uint64, C.c_uint64, C.c_int32, _EV_P, C.c_int32, _EV_P]),
+    "zyxb_allgather": (C.c_int32, [_CTX, C.c_int32, C.c_uint32, C.c_uint64, C.c_uint64, C.c_int32, _EV_P, C.c_int32, _EV_P]),
+    "zyxb_comm_rank": (C.c_int32, [_CTX, C.c_int32, C.POINTER(C.c_int32), C.POINTER(C.c_int32)]),
     "zyxb_comm_destroy": (C.c_int32, [_CTX, C.c_int32]),
 }
 

@@ -275,6 +275,25 @@ class Device:
                                                       C.byref(ev) if want_event else None))
         return ev
 
+    def reduce_scatter_sum(self, buf, count_per_rank, dtype, offset_elems=0, event_wait_list=None, want_event=False):
+        arr, n = _evs(event_wait_list)
+        ev = L.Event()
+        self.be._check(self.be.lib.zyxb_reduce_scatter_sum(self.be.ctx, self.dev, buf, offset_elems, count_per_rank, dtype, arr, n,
+                                                           C.byref(ev) if want_event else None))
+        return ev
+
+    def allgather(self, buf, count_per_rank, dtype, offset_elems=0, event_wait_list=None, want_event=False):
+        arr, n = _evs(event_wait_list)
+        ev = L.Event()
+        self.be._check(self.be.lib.zyxb_allgather(self.be.ctx, self.dev, buf, offset_elems, count_per_rank, dtype, arr, n,
+                                                  C.byref(ev) if want_event else None))
+        return ev
+
+    def comm_rank(self):
+        r, w = C.c_int32(), C.c_int32()
+        self.be._check(self.be.lib.zyxb_comm_rank(self.be.ctx, self.dev, C.byref(r), C.byref(w)))
+        return r.value, w.value
+
     def comm_destroy(self):
         self.be._check(self.be.lib.zyxb_comm_destroy(self.be.ctx, self.dev))
 

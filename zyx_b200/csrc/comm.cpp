@@ -23,6 +23,8 @@ struct Api {
   int (*GetUniqueId)(ncclUniqueId*) = nullptr;
   int (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int) = nullptr;
   int (*AllReduce)(const void*, void*, size_t, int, int, ncclComm_t, cudaStream_t) = nullptr;
+  int (*ReduceScatter)(const void*, void*, size_t, int, int, ncclComm_t, cudaStream_t) = nullptr;
+  int (*AllGather)(const void*, void*, size_t, int, ncclComm_t, cudaStream_t) = nullptr;
   int (*CommDestroy)(ncclComm_t) = nullptr;
   const char* (*GetErrorString)(int) = nullptr;
   std::string load_error;
@@ -44,9 +46,11 @@ Api& api() {
   a.GetUniqueId = (decltype(a.GetUniqueId))dlsym(a.handle, "ncclGetUniqueId");
   a.CommInitRank = (decltype(a.CommInitRank))dlsym(a.handle, "ncclCommInitRank");
   a.AllReduce = (decltype(a.AllReduce))dlsym(a.handle, "ncclAllReduce");
+  a.ReduceScatter = (decltype(a.ReduceScatter))dlsym(a.handle, "ncclReduceScatter");
+  a.AllGather = (decltype(a.AllGather))dlsym(a.handle, "ncclAllGather");
   a.CommDestroy = (decltype(a.CommDestroy))dlsym(a.handle, "ncclCommDestroy");
   a.GetErrorString = (decltype(a.GetErrorString))dlsym(a.handle, "ncclGetErrorString");
-  if (!a.GetUniqueId || !a.CommInitRank || !a.AllReduce || !a.CommDestroy) { a.load_error = "libnccl is missing a required symbol"; a.handle = nullptr; }
+  if (!a.GetUniqueId || !a.CommInitRank || !a.AllReduce || !a.ReduceScatter || !a.AllGather || !a.CommDestroy) { a.load_error = "libnccl is missing a required symbol"; a.handle = nullptr; }
   return a;
 }
 
@@ -82,20 +86,49 @@ int comm_create(Comm** out, int rank, int world, const void* id_bytes, std::stri
   return ZYXB_OK;
 }
 
+static int nccl_type(int dtype, std::string& err) {
+  switch (dtype) {
+    case ZYXB_F32: return ncclFloat32;
+    case ZYXB_BF16: return ncclBfloat16;
+    case ZYXB_F16: return ncclFloat16;
+    case ZYXB_I32: return ncclInt32;
+    default: err = "collective: dtype must be f32, bf16, f16 or i32"; return -1;
+  }
+}
+
 int comm_allreduce_sum(Comm* c, const void* send, void* recv, uint64_t count, int dtype, cudaStream_t stream, std::string& err) {
   Api& a = api();
-  int nt;
-  switch (dtype) {
-    case ZYXB_F32: nt = ncclFloat32; break;
-    case ZYXB_BF16: nt = ncclBfloat16; break;
-    case ZYXB_F16: nt = ncclFloat16; break;
-    case ZYXB_I32: nt = ncclInt32; break;
-    default: err = "allreduce: dtype must be f32, bf16, f16 or i32"; return ZYXB_ERR_INCORRECT_KERNEL_ARG;
-  }
+  const int nt = nccl_type(dtype, err);
+  if (nt < 0) return ZYXB_ERR_INCORRECT_KERNEL_ARG;
   int r = a.AllReduce(send, recv, (size_t)count, nt, ncclSum, c->comm, stream);
   if (r != ncclSuccess) { err = nccl_err("ncclAllReduce", r); return ZYXB_ERR_KERNEL_LAUNCH; }
   return ZYXB_OK;
 }
+
+// In place over `world` consecutive slices of count_per_rank elements starting at base: afterwards this rank's slice
+// holds the sum over ranks (NCCL's in-place form: the receive buffer is the rank's own slice of the send buffer).
+int comm_reduce_scatter_sum(Comm* c, void* base, uint64_t count_per_rank, uint64_t elem_bytes, int dtype, cudaStream_t stream, std::string& err) {
+  Api& a = api();
+  const int nt = nccl_type(dtype, err);
+  if (nt < 0) return ZYXB_ERR_INCORRECT_KERNEL_ARG;
+  char* mine = (char*)base + (uint64_t)c->rank * count_per_rank * elem_bytes;
+  int r = a.ReduceScatter(base, mine, (size_t)count_per_rank, nt, ncclSum, c->comm, stream);
+  if (r != ncclSuccess) { err = nccl_err("ncclReduceScatter", r); return ZYXB_ERR_KERNEL_LAUNCH; }
+  return ZYXB_OK;
+}
+
+// In place: every rank contributes its own slice, afterwards all hold the `world` slices.
+int comm_allgather(Comm* c, void* base, uint64_t count_per_rank, uint64_t elem_bytes, int dtype, cudaStream_t stream, std::string& err) {
+  Api& a = api();
+  const int nt = nccl_type(dtype, err);
+  if (nt < 0) return ZYXB_ERR_INCORRECT_KERNEL_ARG;
+  const char* mine = (const char*)base + (uint64_t)c->rank * count_per_rank * elem_bytes;
+  int r = a.AllGather(mine, base, (size_t)count_per_rank, nt, c->comm, stream);
+  if (r != ncclSuccess) { err = nccl_err("ncclAllGather", r); return ZYXB_ERR_KERNEL_LAUNCH; }
+  return ZYXB_OK;
+}
+
+void comm_rank(const Comm* c, int* rank, int* world) { *rank = c->rank; *world = c->world; }
 
 void comm_destroy(Comm* c) {
   if (!c) return;

@@ -754,6 +754,50 @@ int32_t zyxb_allreduce_sum(zyxb_ctx* ctx, int32_t dev, uint32_t buf, uint64_t of
   return order_streams(ctx, D.comm_stream, D.compute, ZYXB_ERR_KERNEL_LAUNCH);
 }
 
+// reduce-scatter (gather == false) or all-gather over `world` consecutive slices of count_per_rank elements, in place
+static int32_t sliced_collective(zyxb_ctx* ctx, int32_t dev, bool gather, uint32_t buf, uint64_t offset_elems, uint64_t count_per_rank,
+                                 int32_t dtype, const zyxb_event* wait, int32_t n_wait, zyxb_event* out_event) {
+  const char* what = gather ? "allgather" : "reduce_scatter";
+  DEV_OR_FAIL(ZYXB_ERR_KERNEL_LAUNCH);
+  if (!D.comm) return fail(ctx, ZYXB_ERR_KERNEL_LAUNCH, std::string(what) + ": no communicator (call zyxb_comm_init)");
+  Buffer* b = get_buffer(D, buf);
+  if (!b || b->is_variable) return fail(ctx, ZYXB_ERR_INCORRECT_KERNEL_ARG, std::string(what) + ": unknown buffer");
+  int rank = 0, world = 1;
+  comm_rank(D.comm, &rank, &world);
+  const uint64_t es = dtype_size(dtype);
+  if ((offset_elems + count_per_rank * (uint64_t)world) * es > b->bytes) return fail(ctx, ZYXB_ERR_INCORRECT_KERNEL_ARG, std::string(what) + ": range exceeds the buffer");
+  int st = wait_and_consume(ctx, D, D.comm_stream, wait, n_wait, ZYXB_ERR_KERNEL_LAUNCH);
+  if (st) return st;
+  if ((st = order_streams(ctx, D.compute, D.comm_stream, ZYXB_ERR_KERNEL_LAUNCH))) return st;   // producers were queued on the compute stream
+  std::string err;
+  char* p = (char*)b->ptr + offset_elems * es;
+  st = gather ? comm_allgather(D.comm, p, count_per_rank, es, dtype, D.comm_stream, err)
+              : comm_reduce_scatter_sum(D.comm, p, count_per_rank, es, dtype, D.comm_stream, err);
+  if (st) return fail(ctx, st, err);
+  if (out_event) return record_event(ctx, D, D.comm_stream, out_event, ZYXB_ERR_KERNEL_LAUNCH);
+  return order_streams(ctx, D.comm_stream, D.compute, ZYXB_ERR_KERNEL_LAUNCH);
+}
+
+int32_t zyxb_reduce_scatter_sum(zyxb_ctx* ctx, int32_t dev, uint32_t buf, uint64_t offset_elems, uint64_t count_per_rank, int32_t dtype,
+                                const zyxb_event* wait, int32_t n_wait, zyxb_event* out_event) {
+  return sliced_collective(ctx, dev, false, buf, offset_elems, count_per_rank, dtype, wait, n_wait, out_event);
+}
+
+int32_t zyxb_allgather(zyxb_ctx* ctx, int32_t dev, uint32_t buf, uint64_t offset_elems, uint64_t count_per_rank, int32_t dtype,
+                       const zyxb_event* wait, int32_t n_wait, zyxb_event* out_event) {
+  return sliced_collective(ctx, dev, true, buf, offset_elems, count_per_rank, dtype, wait, n_wait, out_event);
+}
+
+int32_t zyxb_comm_rank(zyxb_ctx* ctx, int32_t dev, int32_t* out_rank, int32_t* out_world) {
+  DEV_OR_FAIL(ZYXB_ERR_INITIALIZATION);
+  if (!D.comm) return fail(ctx, ZYXB_ERR_INITIALIZATION, "comm_rank: no communicator (call zyxb_comm_init)");
+  int rank = 0, world = 1;
+  comm_rank(D.comm, &rank, &world);
+  if (out_rank) *out_rank = rank;
+  if (out_world) *out_world = world;
+  return ZYXB_OK;
+}
+
 int32_t zyxb_comm_destroy(zyxb_ctx* ctx, int32_t dev) {
   DEV_OR_FAIL(ZYXB_ERR_DEINITIALIZATION);
   if (D.comm) { cudaDeviceSynchronize(); comm_destroy(D.comm); D.comm = nullptr; }

@@ -9,6 +9,10 @@
 //   SGD / AdamW     zyx-optim/src/sgd.rs:45-84, adamw.rs:51-97   one fused program over all parameters
 // Gradients live in one contiguous bucket, last layer first, so that each layer's slice can be
 // all-reduced as soon as its two gradient launches are queued.
+// With shard_optimizer (ZeRO stage 1) the parameters live in a second bucket of the same layout; each layer's slice is
+// cut into `world` shards: the gradients are reduce-scattered, every rank updates its shard with optimizer state of
+// shard size only, and the updated parameters are all-gathered - layer 0 first, so that the next forward pass starts
+// as soon as its first weight has arrived while the later layers' gathers run behind it.
 #include <stdio.h>
 #include <string.h>
 
@@ -27,14 +31,17 @@ struct Linear {
   uint32_t weight_grad = 0, bias_grad = 0; // views into the gradient bucket
   uint32_t state[2][2] = {{0, 0}, {0, 0}}; // [m|v][weight|bias]
   uint64_t bucket_offset = 0, bucket_count = 0;  // this layer's slice of the bucket, in elements
+  uint64_t shard = 0;                      // sharded optimizer: elements of the slice this rank updates
+  uint32_t param_shard = 0, grad_shard = 0; // views of this rank's shard in the parameter / gradient bucket
 };
 
 struct Instr {
-  enum Kind { LAUNCH, ALLREDUCE } kind = LAUNCH;
+  enum Kind { LAUNCH, ALLREDUCE, REDUCE_SCATTER, ALLGATHER } kind = LAUNCH;
   uint32_t program = 0;
   std::vector<uint32_t> args;
-  uint64_t offset = 0, count = 0;          // ALLREDUCE: slice of the gradient bucket
-  int wait_collectives = 0;                // LAUNCH: wait first for this many of the oldest pending allreduce events (-1: all)
+  uint64_t offset = 0, count = 0;          // collectives: slice of the bucket (count per rank for the sliced ones)
+  int layer = -1;                          // ALLGATHER: the layer whose parameters it completes; LAUNCH: wait for that layer's gather
+  int wait_collectives = 0;                // LAUNCH: wait first for this many of the oldest pending gradient-collective events (-1: all)
   int desc_kind = 0, desc_sub = 0;         // ZYXB_KIND_* and the op / layout, for profile reports
 };
 
@@ -48,8 +55,12 @@ struct zyxb_mlp {
   int32_t dev = 0;
   zyxb_mlp_config cfg{};
   std::vector<Linear> layers;
-  uint32_t grad_bucket = 0;
+  uint32_t grad_bucket = 0, param_bucket = 0;
   uint64_t bucket_elems = 0;
+  bool sharded = false;                    // optimizer state sharded over the ranks
+  int rank = 0;
+  std::vector<zyxb_event> param_ready;     // per layer: the event of its last parameter all-gather, if not yet waited for
+  std::vector<char> param_ready_set;
   uint32_t x = 0, target = 0, loss = 0, per_sample = 0, y = 0;
   std::vector<uint32_t> act, preact, dact;     // per hidden layer output: A_i, Z_i (GELU only), dA_i
   uint32_t dy = 0;
@@ -130,30 +141,53 @@ int32_t build(zyxb_mlp* M) {
 
   // ---- parameters, gradient bucket (last layer first), optimizer state ----
   M->layers.resize(n);
+  M->sharded = c.shard_optimizer != 0;
+  int world = c.world;
+  if (M->sharded) {
+    if (!c.bucket_per_layer) { M->err = "shard_optimizer needs bucket_per_layer"; return ZYXB_ERR_INCORRECT_KERNEL_ARG; }
+    int32_t r = 0, w = 1;
+    TRY(zyxb_comm_rank(M->ctx, M->dev, &r, &w));
+    if (w != c.world) { M->err = "shard_optimizer: config.world differs from the communicator's"; return ZYXB_ERR_INCORRECT_KERNEL_ARG; }
+    M->rank = r;
+  }
   const uint64_t align_elems = 256 / es;
+  const uint64_t slice_align = M->sharded ? align_elems * (uint64_t)world : align_elems;   // a sharded slice divides into aligned shards
   uint64_t off = 0;
   for (int i = n - 1; i >= 0; --i) {
     Linear& L = M->layers[i];
     L.in_features = c.dims[i]; L.out_features = c.dims[i + 1];
     L.bucket_offset = off;
-    off += align_up(L.in_features * L.out_features, align_elems) + align_up(L.out_features, align_elems);
+    off += align_up(align_up(L.in_features * L.out_features, align_elems) + align_up(L.out_features, align_elems), slice_align);
     L.bucket_count = off - L.bucket_offset;
+    if (M->sharded) L.shard = L.bucket_count / (uint64_t)world;
   }
   M->bucket_elems = off;
+  M->param_ready.assign(n, zyxb_event{}); M->param_ready_set.assign(n, 0);
   int32_t st;
   if ((st = alloc(M, M->bucket_elems * es, &M->grad_bucket, true))) return st;
+  if (M->sharded && (st = alloc(M, M->bucket_elems * es, &M->param_bucket, true))) return st;
   const bool adam = c.optim.algo != ZYXB_OPT_SGD;
   const bool sgd_momentum = c.optim.algo == ZYXB_OPT_SGD && c.optim.momentum != 0.0f;
   const int n_state = adam ? 2 : (sgd_momentum ? 1 : 0);
   for (int i = 0; i < n; ++i) {
     Linear& L = M->layers[i];
     const uint64_t wn = L.in_features * L.out_features, bn = L.out_features;
-    if ((st = alloc(M, wn * es, &L.weight, true)) || (st = alloc(M, bn * es, &L.bias, true))) return st;
+    if (M->sharded) {
+      // parameters are views into the parameter bucket (the same layout as the gradients'), state covers this rank's shard
+      TRY(zyxb_buffer_view(M->ctx, M->dev, M->param_bucket, L.bucket_offset * es, wn * es, &L.weight));
+      TRY(zyxb_buffer_view(M->ctx, M->dev, M->param_bucket, (L.bucket_offset + align_up(wn, align_elems)) * es, bn * es, &L.bias));
+      const uint64_t shard_off = (L.bucket_offset + (uint64_t)M->rank * L.shard) * es;
+      TRY(zyxb_buffer_view(M->ctx, M->dev, M->param_bucket, shard_off, L.shard * es, &L.param_shard));
+      TRY(zyxb_buffer_view(M->ctx, M->dev, M->grad_bucket, shard_off, L.shard * es, &L.grad_shard));
+      for (uint32_t v : {L.weight, L.bias, L.param_shard, L.grad_shard}) M->owned_buffers.push_back(v);
+    } else if ((st = alloc(M, wn * es, &L.weight, true)) || (st = alloc(M, bn * es, &L.bias, true))) return st;
     TRY(zyxb_buffer_view(M->ctx, M->dev, M->grad_bucket, L.bucket_offset * es, wn * es, &L.weight_grad));
     TRY(zyxb_buffer_view(M->ctx, M->dev, M->grad_bucket, (L.bucket_offset + align_up(wn, align_elems)) * es, bn * es, &L.bias_grad));
     M->owned_buffers.push_back(L.weight_grad); M->owned_buffers.push_back(L.bias_grad);
-    for (int s = 0; s < n_state; ++s)
-      if ((st = alloc(M, wn * es, &L.state[s][0], true)) || (st = alloc(M, bn * es, &L.state[s][1], true))) return st;
+    for (int s = 0; s < n_state; ++s) {
+      if (M->sharded) { if ((st = alloc(M, L.shard * es, &L.state[s][0], true))) return st; }
+      else if ((st = alloc(M, wn * es, &L.state[s][0], true)) || (st = alloc(M, bn * es, &L.state[s][1], true))) return st;
+    }
   }
 
   // ---- activations ----
@@ -183,6 +217,7 @@ int32_t build(zyxb_mlp* M) {
     std::vector<uint32_t> args = {in, L.weight, L.bias, last ? M->y : M->act[i]};
     if (keep_z) args.push_back(M->preact[i]);
     if ((st = push_launch(M, P, gemm_desc(dt, B, L.out_features, L.in_features, false, true, epi, keep_z), args))) return st;
+    if (M->sharded) P.back().layer = i;     // the first reader of this layer's gathered parameters
   }
   // ---- loss and its gradient ----
   const uint64_t out_f = c.dims[n];
@@ -201,7 +236,10 @@ int32_t build(zyxb_mlp* M) {
     // dW = dZ^T . input   ([out, B] x [B, in]); db = column sums of dZ
     if ((st = push_launch(M, P, gemm_desc(dt, L.out_features, L.in_features, B, true, false, ZYXB_EPI_NONE, false), {dz, in, L.weight_grad}))) return st;
     if ((st = push_launch(M, P, row_desc(ZYXB_RR_COLSUM, dt, B, L.out_features), {dz, L.bias_grad}))) return st;
-    if (c.world > 1 && c.bucket_per_layer) {
+    if (M->sharded) {
+      Instr rs; rs.kind = Instr::REDUCE_SCATTER; rs.offset = L.bucket_offset; rs.count = L.shard;
+      P.push_back(rs); M->n_collectives++;
+    } else if (c.world > 1 && c.bucket_per_layer) {
       Instr ar; ar.kind = Instr::ALLREDUCE; ar.offset = L.bucket_offset; ar.count = L.bucket_count;
       P.push_back(ar); M->n_collectives++;
     }
@@ -228,6 +266,26 @@ int32_t build(zyxb_mlp* M) {
   // One rank: one program over every parameter, Module::iter() order.  Data parallel with a collective per layer:
   // one program per layer, last layer first, each waiting only for its own layer's allreduce, so the update of the
   // layers whose gradients have arrived overlaps the allreduce of the first layer's (the last to be produced).
+  if (M->sharded) {
+    // Sharded: one program per layer over this rank's shard of the slice (an elementwise update does not care where
+    // tensors begin; the padding holds zero parameters and zero gradients and stays zero), first layer first, each
+    // followed by the all-gather of that layer's parameters.  The first waits for every reduce-scatter.
+    for (int i = 0; i < n; ++i) {
+      const Linear& L = M->layers[i];
+      zyxb_kernel_desc od{};
+      od.kind = ZYXB_KIND_OPTIM;
+      od.u.optim = c.optim;
+      uint64_t numel = L.shard;
+      od.u.optim.dtype = dt; od.u.optim.n_tensors = 1; od.u.optim.numel = &numel;
+      od.u.optim.grad_scale = 1.0f / (float)c.world;
+      std::vector<uint32_t> args = {L.param_shard, L.grad_shard};
+      for (int s = 0; s < n_state; ++s) args.push_back(L.state[s][0]);
+      if ((st = push_launch(M, M->update, od, args, i == 0 ? -1 : 0))) return st;
+      Instr ag; ag.kind = Instr::ALLGATHER; ag.offset = L.bucket_offset; ag.count = L.shard; ag.layer = i;
+      M->update.push_back(ag); M->n_collectives++;
+    }
+    return ZYXB_OK;
+  }
   const bool per_layer = c.world > 1 && c.bucket_per_layer;
   const int groups = per_layer ? n : 1;
   for (int gi = 0; gi < groups; ++gi) {
@@ -267,16 +325,25 @@ int32_t mark(zyxb_mlp* M) {
 int32_t run(zyxb_mlp* M, const std::vector<Instr>& plan, const zyxb_event* wait, int32_t n_wait) {
   bool first = true;
   for (const Instr& in : plan) {
-    if (in.kind == Instr::ALLREDUCE) {
+    if (in.kind != Instr::LAUNCH) {
       zyxb_event ev{};
-      TRY(zyxb_allreduce_sum(M->ctx, M->dev, M->grad_bucket, in.offset, in.count, M->cfg.dtype, nullptr, 0, &ev));
-      M->pending.push_back(ev);
+      if (in.kind == Instr::ALLREDUCE) TRY(zyxb_allreduce_sum(M->ctx, M->dev, M->grad_bucket, in.offset, in.count, M->cfg.dtype, nullptr, 0, &ev));
+      else if (in.kind == Instr::REDUCE_SCATTER) TRY(zyxb_reduce_scatter_sum(M->ctx, M->dev, M->grad_bucket, in.offset, in.count, M->cfg.dtype, nullptr, 0, &ev));
+      else TRY(zyxb_allgather(M->ctx, M->dev, M->param_bucket, in.offset, in.count, M->cfg.dtype, nullptr, 0, &ev));
+      if (in.kind == Instr::ALLGATHER) {
+        if (M->param_ready_set[in.layer]) TRY(zyxb_release_events(M->ctx, M->dev, &M->param_ready[in.layer], 1));
+        M->param_ready[in.layer] = ev; M->param_ready_set[in.layer] = 1;
+      } else M->pending.push_back(ev);
       int32_t stm = mark(M);   // keeps one mark per instruction; a collective runs on its own stream
       if (stm) return stm;
       continue;
     }
     std::vector<zyxb_event> w;
     if (first && n_wait > 0) w.assign(wait, wait + n_wait);
+    if (in.layer >= 0 && M->param_ready_set[in.layer]) {   // this layer's parameters are still being gathered
+      w.push_back(M->param_ready[in.layer]);
+      M->param_ready_set[in.layer] = 0;
+    }
     if (in.wait_collectives != 0) {
       const size_t take = in.wait_collectives < 0 ? M->pending.size() : std::min(M->pending.size(), (size_t)in.wait_collectives);
       w.insert(w.end(), M->pending.begin(), M->pending.begin() + take);
@@ -287,6 +354,16 @@ int32_t run(zyxb_mlp* M, const std::vector<Instr>& plan, const zyxb_event* wait,
     int32_t stm = mark(M);
     if (stm) return stm;
   }
+  return ZYXB_OK;
+}
+
+// Blocks until every outstanding parameter all-gather has finished (a no-op unless the optimizer is sharded).
+int32_t join_params(zyxb_mlp* M) {
+  for (size_t i = 0; i < M->param_ready.size(); ++i)
+    if (M->param_ready_set[i]) {
+      TRY(zyxb_sync(M->ctx, M->dev, &M->param_ready[i], 1));
+      M->param_ready_set[i] = 0;
+    }
   return ZYXB_OK;
 }
 
@@ -320,6 +397,8 @@ int32_t zyxb_mlp_destroy(zyxb_mlp* M) {
   if (!M) return ZYXB_OK;
   zyxb_device_sync(M->ctx, M->dev);
   if (!M->pending.empty()) zyxb_release_events(M->ctx, M->dev, M->pending.data(), (int32_t)M->pending.size());
+  for (size_t i = 0; i < M->param_ready.size(); ++i)
+    if (M->param_ready_set[i]) zyxb_release_events(M->ctx, M->dev, &M->param_ready[i], 1);
   for (uint32_t p : M->owned_programs) zyxb_program_release(M->ctx, M->dev, p);
   // views were pushed after their parent: free in reverse so a parent outlives its views
   for (auto it = M->owned_buffers.rbegin(); it != M->owned_buffers.rend(); ++it) zyxb_free(M->ctx, M->dev, *it, nullptr, 0);
@@ -333,6 +412,11 @@ int32_t zyxb_mlp_tensor(zyxb_mlp* M, int32_t which, int32_t i, uint32_t* out_buf
   if (!M || i < 0 || i >= 2 * M->cfg.n_layers || which < 0 || which > 3) return ZYXB_ERR_INCORRECT_KERNEL_ARG;
   const Linear& L = M->layers[i / 2];
   const int wb = i % 2;
+  if (M->sharded) {
+    if (which >= 2) { M->err = "mlp_tensor: the optimizer state is sharded over the ranks; it has no per-tensor buffers"; return ZYXB_ERR_INCORRECT_KERNEL_ARG; }
+    int32_t stj = join_params(M);          // whoever asks for a buffer may read it: the gathers must have landed
+    if (stj) return stj;
+  }
   uint32_t b = 0;
   switch (which) {
     case 0: b = wb ? L.bias : L.weight; break;
@@ -355,7 +439,11 @@ int32_t zyxb_mlp_io(zyxb_mlp* M, uint32_t* out_x, uint32_t* out_target, uint32_t
 }
 
 int32_t zyxb_mlp_forward_backward(zyxb_mlp* M) { return M ? run(M, M->forward_backward, nullptr, 0) : ZYXB_ERR_INCORRECT_KERNEL_ARG; }
-int32_t zyxb_mlp_update(zyxb_mlp* M) { return M ? run(M, M->update, nullptr, 0) : ZYXB_ERR_INCORRECT_KERNEL_ARG; }
+int32_t zyxb_mlp_update(zyxb_mlp* M) {
+  if (!M) return ZYXB_ERR_INCORRECT_KERNEL_ARG;
+  int32_t st = run(M, M->update, nullptr, 0);
+  return st ? st : join_params(M);         // the stand-alone update returns with complete parameters; zyxb_mlp_step does not wait
+}
 
 int32_t zyxb_mlp_bind_inputs(zyxb_mlp* M, uint32_t x, uint32_t target) {
   if (!M) return ZYXB_ERR_INCORRECT_KERNEL_ARG;
@@ -417,7 +505,7 @@ int32_t zyxb_mlp_profile_read(zyxb_mlp* M, float* out_ms, int32_t* out_kind, int
   if (out_kind) {
     int i = 0;
     for (const auto* plan : {&M->forward_backward, &M->update})
-      for (const Instr& in : *plan) out_kind[i++] = in.kind == Instr::ALLREDUCE ? -1 : in.desc_kind * 100 + in.desc_sub;
+      for (const Instr& in : *plan) out_kind[i++] = in.kind != Instr::LAUNCH ? -1 : in.desc_kind * 100 + in.desc_sub;
   }
   M->prof_steps.clear();
   return ZYXB_OK;
@@ -442,6 +530,15 @@ std::vector<zyxb_host::CkptTensor> mlp_ckpt_tensors(zyxb_mlp* M) {
   for (int s = -1; s < n_state; ++s)
     for (size_t i = 0; i < M->layers.size(); ++i) {
       const Linear& L = M->layers[i];
+      if (M->sharded && s >= 0) {
+        // a rank's file holds its own shard of the state, named for the rank: every rank saves to its own path
+        zyxb_host::CkptTensor t;
+        t.name = std::string(state_prefix[s]) + "shard" + std::to_string(M->rank) + "of" + std::to_string(M->cfg.world) + ".layers." + std::to_string(i);
+        t.buffer = L.state[s][0];
+        t.shape = {L.shard};
+        out.push_back(std::move(t));
+        continue;
+      }
       for (int wb = 0; wb < 2; ++wb) {
         zyxb_host::CkptTensor t;
         t.name = std::string(s < 0 ? "" : state_prefix[s]) + "layers." + std::to_string(i) + (wb ? ".bias" : ".weight");
@@ -457,6 +554,8 @@ std::vector<zyxb_host::CkptTensor> mlp_ckpt_tensors(zyxb_mlp* M) {
 #pragma GCC visibility push(default)
 int32_t zyxb_mlp_save(zyxb_mlp* M, const char* path) {
   if (!M || !path) return ZYXB_ERR_INCORRECT_KERNEL_ARG;
+  int32_t stj = join_params(M);
+  if (stj) return stj;
   uint64_t t = 0;
   for (const Instr& in : M->update)
     if (in.kind == Instr::LAUNCH) { TRY(zyxb_program_get_step(M->ctx, M->dev, in.program, &t)); break; }

@@ -17,7 +17,7 @@ LOSS_MSE, LOSS_CROSS_ENTROPY = range(2)
 
 class MlpConfig(C.Structure):
     _fields_ = [("dtype", C.c_int32), ("batch", C.c_uint64), ("n_layers", C.c_int32), ("dims", C.c_uint64 * 9), ("activation", C.c_int32),
-                ("loss", C.c_int32), ("optim", L.OptimDesc), ("world", C.c_int32), ("bucket_per_layer", C.c_int32)]
+                ("loss", C.c_int32), ("optim", L.OptimDesc), ("world", C.c_int32), ("bucket_per_layer", C.c_int32), ("shard_optimizer", C.c_int32)]
 
 
 _P = C.c_void_p
@@ -61,7 +61,7 @@ class Mlp:
     """A stack of Linear layers with its training plan (forward, loss, backward, optimizer)."""
 
     def __init__(self, session, dtype, batch, dims, activation=ACT_GELU, loss=LOSS_MSE, algo=L.OPT_ADAMW, world=1,
-                 bucket_per_layer=True, **optim_kw):
+                 bucket_per_layer=True, shard_optimizer=False, **optim_kw):
         self.lib, self.sess = load(), session
         cfg = MlpConfig()
         cfg.dtype, cfg.batch, cfg.n_layers, cfg.activation, cfg.loss = dtype, batch, len(dims) - 1, activation, loss
@@ -74,7 +74,7 @@ class Mlp:
         o.nesterov, o.maximize = int(optim_kw.get("nesterov", False)), int(optim_kw.get("maximize", False))
         o.beta1, o.beta2, o.eps = optim_kw.get("beta1", 0.9), optim_kw.get("beta2", 0.999), optim_kw.get("eps", 1e-8)
         o.standard = int(optim_kw.get("standard", False))
-        cfg.world, cfg.bucket_per_layer = world, int(bucket_per_layer)
+        cfg.world, cfg.bucket_per_layer, cfg.shard_optimizer = world, int(bucket_per_layer), int(shard_optimizer)
         self.cfg, self.dims, self.dtype, self.batch = cfg, list(dims), dtype, batch
         self.h = _P()
         st = self.lib.zyxb_mlp_create(session.backend.ctx, session.device.dev, C.byref(cfg), C.byref(self.h))
