@@ -5,10 +5,13 @@
 // by reshape / expand / permute (pool, mod.rs:2442) and multiplies it with the weights; here no such matrix exists:
 //   prep   x [n,c,h,w] -> xt [n,h,w,cp] and w [o,c,kh,kw] -> wt [o, kh*kw, cp]  (channels innermost, cp = c rounded up
 //          to 8 so that every TMA row pitch is a multiple of 16 bytes; the added channels are zeros)
-//   GEMM   M = 128 output positions (a TH x TW patch of one image), N = BN output channels, K = kh*kw*cp walked as
-//          (tap, 64-channel block).  For every k-block one TMA box {64 channels, TW columns, TH rows} of xt at the tap's
-//          offset is the A tile - the tensor map's element strides carry the convolution stride, coordinates outside the
-//          image read the zero padding - and one box {64 channels, 1 tap, BN filters} of wt is the B tile.  Both land
+//   GEMM   M = 128 output positions, N = BN output channels, K = kh*kw*cp walked as (tap, 64-channel block).  The A tile
+//          of a k-block is one TMA load through an im2col-mode tensor map: its bounding box is the set of window origins
+//          ([-pad, extent + pad - dilated filter extent]), its element strides are the convolution's strides, the load's
+//          coordinates name the tile's first output position and its two offsets the filter tap; the hardware walks the
+//          128 positions that follow in row-major order, across rows and images, and zero-fills the padding.  (Paddings
+//          beyond the 8-bit corner fields of a rank-4 map use a tiled map instead: a TH x TW patch of one image per tile,
+//          box {64, TW*stride, TH*stride}.)  One box {64 channels, 1 tap, BN filters} of wt is the B tile.  Both land
 //          K-major in 128-byte-swizzled shared memory, exactly the layout of the matmul kernel's NT case.
 //   store  TMEM lane = output position, so for one output channel the 32 lanes of a warp hold 32 neighbouring positions:
 //          each warp store writes a run of the channels-first output directly, no transposition pass.
