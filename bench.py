@@ -512,10 +512,11 @@ class Conv:
     metric, unit, dtype, bound = "convolution forward TFLOP/s (implicit GEMM, 3x3, 256 -> 256 channels)", "TFLOP/s", "bf16", "tensor"
     N, C, H, W, O, K = 32, 256, 56, 56, 256, 3
 
-    def __init__(self, size=0):
+    def __init__(self, size=0, channels_last=False):
         if size:
             self.N = size
-        self.name = "conv3x3_bf16_n%d_c%d_%dx%d_o%d" % (self.N, self.C, self.H, self.W, self.O)
+        self.channels_last = channels_last
+        self.name = "conv3x3_bf16_n%d_c%d_%dx%d_o%d%s" % (self.N, self.C, self.H, self.W, self.O, "_channels_last" if channels_last else "")
         self.flops = 2.0 * self.N * self.H * self.W * self.O * self.C * self.K * self.K
         self.units_per_step = self.flops / 1e12
         self.h2d_bytes = self.N * self.C * self.H * self.W * 2
@@ -533,11 +534,13 @@ class Conv:
         self.sess = sess
         self.host_inputs()
         p, d = sess.pool, sess.device
-        self.bx, self.bw, self.bb = p.upload(self.x), p.upload(self.w), p.upload(self.b)
+        self.xdev = np.ascontiguousarray(self.x.transpose(0, 2, 3, 1)) if self.channels_last else self.x
+        self.bx, self.bw, self.bb = p.upload(self.xdev), p.upload(self.w), p.upload(self.b)
         self.by, _ = p.allocate(self.d2h_bytes)
-        self.prog = d.create_program(B.conv_desc(L.BF16, self.x.shape, self.w.shape, 1, 1, 1, has_bias=True))
+        self.prog = d.create_program(B.conv_desc(L.BF16, self.x.shape, self.w.shape, 1, 1, 1, has_bias=True, channels_last=self.channels_last))
         self.config = {"workload": self.name, "l2": "L2 flushed (256 MB memset) before every timed launch",
-                       "launch": "three kernels: activations to channels-last, filters to [o, tap, c], implicit GEMM"}
+                       "launch": "two kernels: filters to [o, tap, c], implicit GEMM reading x in place" if self.channels_last else
+                                 "three kernels: activations to channels-last, filters to [o, tap, c], implicit GEMM"}
         self.kernel_events = []
 
     def step(self, timed=False):
@@ -558,19 +561,21 @@ class Conv:
 
     def e2e_setup(self):
         self.hy = np.empty((self.N, self.O, self.H, self.W), np.uint16)
-        for a in (self.x, self.hy):
+        for a in (self.xdev, self.hy):
             self.sess.backend.host_register(a)
 
     def e2e_step(self):
         p, d = self.sess.pool, self.sess.device
-        ev = p.host_to_pool(self.x, self.bx)
+        ev = p.host_to_pool(self.xdev, self.bx)
         d.launch(self.prog, [self.bx, self.bw, self.bb, self.by], [ev])
         p.pool_to_host(self.by, self.hy)
 
     def check(self):
         from oracle import oracle as zo
-        y = np.empty((1, self.O, self.H, self.W), np.uint16)               # the first image, every filter
+        y = np.empty((1, self.H, self.W, self.O) if self.channels_last else (1, self.O, self.H, self.W), np.uint16)   # the first image, every filter
         self.sess.pool.pool_to_host(self.by, y)
+        if self.channels_last:
+            y = y.transpose(0, 3, 1, 2)
         o = 8
         want = zo.conv(zo.BF16, self.x[:1], self.w[:o], self.b[:o], 1, 1, 1)
         f = lambda b: (b.astype(np.uint32) << 16).view(np.float32)
@@ -910,7 +915,7 @@ class BlockTrain:
                                       "samples/s extrapolated to the full block by matmul FLOPs (%.1f GFLOP per sample)") % (E, F, H, T, flops / 1e9, dt, full / 1e9)
 
 
-WORKLOADS = {"block": BlockTrain, "simplenet": SimpleNet, "mlp": MlpTrain, "rowreduce": RowReduce, "attn_rows": AttnRows, "attention": AttentionFwd, "conv": Conv, "gemm_bf16": lambda: Gemm("bf16"), "gemm_f32": lambda: Gemm("f32")}
+WORKLOADS = {"block": BlockTrain, "simplenet": SimpleNet, "mlp": MlpTrain, "rowreduce": RowReduce, "attn_rows": AttnRows, "attention": AttentionFwd, "conv": Conv, "conv_nhwc": lambda: Conv(channels_last=True), "gemm_bf16": lambda: Gemm("bf16"), "gemm_f32": lambda: Gemm("f32")}
 
 
 def make_workload(args, rank=0, world=1):
@@ -921,7 +926,7 @@ def make_workload(args, rank=0, world=1):
     if args.workload == "block":
         return BlockTrain(size=args.size, rank=rank, world=world, fused=not args.unfused_attention)
     if args.size:
-        return {"rowreduce": lambda: RowReduce(rows=args.size), "attn_rows": lambda: AttnRows(rows=args.size), "attention": lambda: AttentionFwd(args.size), "conv": lambda: Conv(args.size), "gemm_bf16": lambda: Gemm("bf16", args.size),
+        return {"rowreduce": lambda: RowReduce(rows=args.size), "attn_rows": lambda: AttnRows(rows=args.size), "attention": lambda: AttentionFwd(args.size), "conv": lambda: Conv(args.size), "conv_nhwc": lambda: Conv(args.size, True), "gemm_bf16": lambda: Gemm("bf16", args.size),
                 "gemm_f32": lambda: Gemm("f32", args.size)}[args.workload]()
     return WORKLOADS[args.workload]()
 

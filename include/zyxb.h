@@ -259,6 +259,8 @@ typedef struct {
   uint32_t stride_h, stride_w, dil_h, dil_w;                 /* 0 means 1 */
   uint32_t pad_top, pad_bottom, pad_left, pad_right;
   int32_t  has_bias;
+  int32_t  channels_last;  /* 1: x is [n,h,w,c] and y is [n,oh,ow,o] (w stays [o,c,kh,kw]): chained convolutions skip the
+                              layout pass, TMA reads x in place (needs c % 8 == 0 for the tensor-core path) */
 } zyxb_conv_desc;
 /* args: x, w [,bias] -> y */
 

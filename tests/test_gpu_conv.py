@@ -79,6 +79,36 @@ def test_implicit_gemm_on_tensor_cores(sess, dtype, case):
     assert_parity(zo.to_f32(got, dtype), zo.to_f32(want, dtype), exact, TOL_BF16, floor=0.1, what="conv %s" % (case,))
 
 
+@pytest.mark.parametrize("dtype", [L.BF16, L.F16])
+@pytest.mark.parametrize("case", [TC_CASES[0], TC_CASES[1], TC_CASES[4], TC_CASES[8], (2, 36, 20, 20, 20, 3, 3, 1, 1, 1)])
+def test_channels_last_reads_and_writes_in_place(sess, dtype, case):
+    """x [n,h,w,c] -> y [n,oh,ow,o]: no layout kernel when c is a multiple of 8 (two launches), and the same values as the
+    channels-first oracle on the transposed tensors.  The last case (c = 36, o = 20) takes the direct kernel."""
+    n, c, h, w_, o, kh, kw, stride, dilation, padding = case
+    x = zo.to_bits(RNG.standard_normal((n, c, h, w_)).astype(np.float32), dtype)
+    w = zo.to_bits((RNG.standard_normal((o, c, kh, kw)) / np.sqrt(c * kh * kw)).astype(np.float32), dtype)
+    b = zo.to_bits(RNG.standard_normal(o).astype(np.float32), dtype)
+    before = sess.device.launch_count()
+    got = sess.conv(dtype, np.ascontiguousarray(x.transpose(0, 2, 3, 1)), w, b, stride, dilation, padding, channels_last=True)
+    assert sess.device.launch_count() - before == (2 if c % 8 == 0 else 1)
+    assert sess.device.status() == 0
+    want = zo.conv(dtype, x, w, b, stride, dilation, padding)
+    assert got.shape == tuple(np.array(want.shape)[[0, 2, 3, 1]])
+    exact = exact_conv(zo.to_f32(x, dtype), zo.to_f32(w, dtype), zo.to_f32(b, dtype), stride, dilation, padding)
+    assert_parity(zo.to_f32(got, dtype).transpose(0, 3, 1, 2), zo.to_f32(want, dtype), exact, TOL_BF16, floor=0.1, what="conv nhwc %s" % (case,))
+
+
+def test_channels_last_f32_and_i32(sess):
+    x = RNG.integers(-50, 50, (2, 3, 9, 8)).astype(np.int32)
+    w = RNG.integers(-9, 9, (4, 3, 3, 3)).astype(np.int32)
+    got = sess.conv(L.I32, np.ascontiguousarray(x.transpose(0, 2, 3, 1)), w, None, 2, 1, 1, channels_last=True)
+    assert np.array_equal(got.transpose(0, 3, 1, 2), zo.conv(zo.I32, x, w, None, 2, 1, 1))
+    xf = RNG.standard_normal((2, 5, 11, 7)).astype(np.float32)
+    wf = RNG.standard_normal((6, 5, 3, 3)).astype(np.float32)
+    got = sess.conv(L.F32, np.ascontiguousarray(xf.transpose(0, 2, 3, 1)), wf, None, 1, 1, 1, channels_last=True)
+    assert_parity(got.transpose(0, 3, 1, 2), zo.conv(zo.F32, xf, wf, None, 1, 1, 1), exact_conv(xf, wf, None, 1, 1, 1), TOL_F32, floor=0.1, what="conv nhwc f32")
+
+
 def test_without_bias_and_small_problem_takes_the_direct_kernel(sess):
     x = zo.to_bits(RNG.standard_normal((1, 4, 8, 8)).astype(np.float32), L.BF16)
     w = zo.to_bits(RNG.standard_normal((4, 4, 3, 3)).astype(np.float32), L.BF16)

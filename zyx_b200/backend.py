@@ -336,7 +336,8 @@ def conv_out_shape(x_shape, w_shape, stride=1, dilation=1, padding=0):
     return (n, o, (h + pt + pb - dh * (kh - 1) - 1) // sh + 1, (w + pl + pr - dw * (kw - 1) - 1) // sw + 1)
 
 
-def conv_desc(dtype, x_shape, w_shape, stride=1, dilation=1, padding=0, has_bias=False):
+def conv_desc(dtype, x_shape, w_shape, stride=1, dilation=1, padding=0, has_bias=False, channels_last=False):
+    """x_shape is always given as (n, c, h, w), whatever the memory layout."""
     d = L.KernelDesc()
     d.kind = L.KIND_CONV
     c = d.u.conv
@@ -346,7 +347,7 @@ def conv_desc(dtype, x_shape, w_shape, stride=1, dilation=1, padding=0, has_bias
     c.stride_h, c.stride_w = (stride, stride) if isinstance(stride, int) else stride
     c.dil_h, c.dil_w = (dilation, dilation) if isinstance(dilation, int) else dilation
     c.pad_top, c.pad_bottom, c.pad_left, c.pad_right = _pads(padding)
-    c.has_bias = int(has_bias)
+    c.has_bias, c.channels_last = int(has_bias), int(channels_last)
     return d
 
 

@@ -48,6 +48,7 @@ struct ConvTcParams {
   uint32_t tiles_w, tiles_h, tiles_n;
   uint32_t positions, tiles_m;        // im2col mode: n*oh*ow output positions in tiles of 128 consecutive ones
   int rn, is_bf16;
+  int channels_last;                  // y is [positions, o]: a lane's 32 filters are contiguous
   uint32_t* status;
 };
 
@@ -251,15 +252,18 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tma_x, const __grid_constant_
       if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.status, CV_ERR_EPILOGUE)) break;
       tc_fence_after();
       bool inside;
-      uint16_t* ypos;
+      uint16_t* ypos;          // channels-first: this lane's position in filter 0's plane
+      size_t pos;              // flat index of the position over (image, row, column)
       if constexpr (IM2COL) {
         const uint32_t m = m0 + row_in_tile, im = m / plane;      // this lane's position: image im, offset m - im * plane in its plane
         inside = m < p.positions;
         ypos = y + (size_t)im * g.o * plane + (m - im * plane);
+        pos = m;
       } else {
         const uint32_t oy = oh0 + ty, ox = ow0 + tx;
         inside = oy < g.oh && ox < g.ow;
         ypos = y + (size_t)img * g.o * plane + (size_t)oy * g.ow + ox;
+        pos = ((size_t)img * g.oh + oy) * g.ow + ox;
       }
 #pragma unroll 1
       for (int ch = col_half * (BN / 64); ch < (col_half + 1) * (BN / 64); ++ch) {
@@ -267,7 +271,27 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tma_x, const __grid_constant_
         tmem_ld32(tmem_base + ((quarter * 32u) << 16) + acc * BN + ch * 32, r);
         tmem_ld_wait();
         const uint32_t o0 = tn * BN + ch * 32;
-        if (inside && o0 < g.o) {
+        if (inside && o0 < g.o && p.channels_last) {
+          // channels-last output: this lane's position is a row of g.o filters, 32 of them here
+          uint16_t* yrow = y + pos * g.o + o0;
+          const bool vec = (g.o % 8 == 0) && o0 + 32 <= g.o;
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            Pack<uint16_t, 8> pk;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const uint32_t o = o0 + q * 8 + j;
+              float v = __uint_as_float(r[q * 8 + j]);
+              if (bias && o < g.o) v += is_bf16 ? bf16_to_f32(bias[o]) : f16_to_f32(bias[o]);
+              pk.v[j] = is_bf16 ? f32_to_bf16(v, rn) : f32_to_f16(v, rn);
+            }
+            if (vec) store_pack<uint16_t, 8>(yrow + q * 8, pk);
+            else {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) if (o0 + q * 8 + j < g.o) yrow[q * 8 + j] = pk.v[j];
+            }
+          }
+        } else if (inside && o0 < g.o) {
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
             const uint32_t o = o0 + j;
@@ -297,17 +321,18 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tma_x, const __grid_constant_
 template <typename T>
 __global__ void conv_direct_kernel(const typename Elem<T>::store_t* __restrict__ x, const typename Elem<T>::store_t* __restrict__ w,
                                    const typename Elem<T>::store_t* __restrict__ bias, typename Elem<T>::store_t* __restrict__ y,
-                                   ConvGeom g, uint64_t total, int rn) {
+                                   ConvGeom g, uint64_t total, int rn, int channels_last) {
   using A = typename Elem<T>::acc_t;
+  // element strides of x: channels-first [n,c,h,w] or channels-last [n,h,w,c]
+  const uint64_t xs_c = channels_last ? 1 : (uint64_t)g.h * g.w, xs_p = channels_last ? g.c : 1;
   for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
-    const uint32_t ox = (uint32_t)(i % g.ow);
-    uint64_t q = i / g.ow;
-    const uint32_t oy = (uint32_t)(q % g.oh); q /= g.oh;
-    const uint32_t o = (uint32_t)(q % g.o);
-    const uint64_t n = q / g.o;
+    uint32_t ox, oy, o;
+    uint64_t n, q = i;
+    if (channels_last) { o = (uint32_t)(q % g.o); q /= g.o; ox = (uint32_t)(q % g.ow); q /= g.ow; oy = (uint32_t)(q % g.oh); n = q / g.oh; }
+    else { ox = (uint32_t)(q % g.ow); q /= g.ow; oy = (uint32_t)(q % g.oh); q /= g.oh; o = (uint32_t)(q % g.o); n = q / g.o; }
     A acc = 0;
     for (uint32_t c = 0; c < g.c; ++c) {
-      const auto* xp = x + (n * g.c + c) * (uint64_t)g.h * g.w;
+      const auto* xp = x + n * g.c * (uint64_t)g.h * g.w + c * xs_c;
       const auto* wp = w + ((uint64_t)o * g.c + c) * g.kh * g.kw;
       for (uint32_t r = 0; r < g.kh; ++r) {
         const int iy = (int)(oy * g.sh + r * g.dh) - g.pt;
@@ -315,7 +340,7 @@ __global__ void conv_direct_kernel(const typename Elem<T>::store_t* __restrict__
         for (uint32_t s = 0; s < g.kw; ++s) {
           const int ix = (int)(ox * g.sw + s * g.dw) - g.pl;
           if (ix < 0 || ix >= (int)g.w) continue;
-          acc += (A)Elem<T>::load(xp[(uint64_t)iy * g.w + ix]) * (A)Elem<T>::load(wp[r * g.kw + s]);
+          acc += (A)Elem<T>::load(xp[((uint64_t)iy * g.w + ix) * xs_p]) * (A)Elem<T>::load(wp[r * g.kw + s]);
         }
       }
     }
@@ -379,11 +404,14 @@ int try_conv_tc(const zyxb_conv_desc& d, const ConvGeom& g, const void* x, const
   const uint32_t th = 128 / tw;
   if (!im2col && (tw * g.sw > 256 || th * g.sh > 256)) return 0;
   const uint32_t cp = (g.c + 7) / 8 * 8, taps = g.kh * g.kw;
-  const size_t xt_bytes = (size_t)g.n * g.h * g.w * cp * 2, wt_bytes = (size_t)g.o * taps * cp * 2;
+  // channels-last input is read by TMA where it lies: its pitch (c elements) must already be a multiple of 16 bytes
+  const bool in_place = d.channels_last != 0;
+  if (in_place && (g.c % 8 || (uintptr_t)x % 16 || (uintptr_t)y % 16)) return 0;
+  const size_t xt_bytes = in_place ? 0 : (size_t)g.n * g.h * g.w * cp * 2, wt_bytes = (size_t)g.o * taps * cp * 2;
   const size_t wt_off = (xt_bytes + 1023) / 1024 * 1024;
   if (wt_off + wt_bytes > lc.scratch_bytes) return 0;
   if ((uintptr_t)lc.scratch % 1024) return 0;
-  uint16_t* xt = reinterpret_cast<uint16_t*>(lc.scratch);
+  uint16_t* xt = in_place ? reinterpret_cast<uint16_t*>(const_cast<void*>(x)) : reinterpret_cast<uint16_t*>(lc.scratch);
   uint16_t* wt = reinterpret_cast<uint16_t*>(reinterpret_cast<char*>(lc.scratch) + wt_off);
   const bool bf16 = d.dtype == ZYXB_BF16;
   const CUtensorMapDataType dt = bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
@@ -414,7 +442,8 @@ int try_conv_tc(const zyxb_conv_desc& d, const ConvGeom& g, const void* x, const
                                                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) return 0;
   }
   const uint32_t hw = g.h * g.w;
-  if (hw % 2 == 0 && (uintptr_t)x % 4 == 0)
+  if (in_place) {}
+  else if (hw % 2 == 0 && (uintptr_t)x % 4 == 0)
     conv_nhwc_pairs_kernel<<<dim3((hw + 63) / 64, (cp + 63) / 64, g.n), 256, 0, lc.stream>>>(reinterpret_cast<const uint16_t*>(x), xt, g.c, cp, hw);
   else
     conv_nhwc_kernel<<<dim3((hw + 31) / 32, (cp + 31) / 32, g.n), dim3(32, 8), 0, lc.stream>>>(reinterpret_cast<const uint16_t*>(x), xt, g.c, cp, hw);
@@ -425,7 +454,7 @@ int try_conv_tc(const zyxb_conv_desc& d, const ConvGeom& g, const void* x, const
   tp.tw = tw; tp.th = th; tp.tw_shift = 0;
   while ((1u << tp.tw_shift) < tw) ++tp.tw_shift;
   tp.tiles_w = (g.ow + tw - 1) / tw; tp.tiles_h = (g.oh + th - 1) / th; tp.tiles_n = (g.o + bn - 1) / bn;
-  tp.rn = lc.round_nearest ? 1 : 0; tp.is_bf16 = bf16 ? 1 : 0; tp.status = lc.status_word;
+  tp.rn = lc.round_nearest ? 1 : 0; tp.is_bf16 = bf16 ? 1 : 0; tp.status = lc.status_word; tp.channels_last = in_place ? 1 : 0;
   tp.positions = (uint32_t)positions; tp.tiles_m = (uint32_t)((positions + CV_BM - 1) / CV_BM);
   const uint64_t total = (im2col ? (uint64_t)tp.tiles_m : (uint64_t)g.n * tp.tiles_h * tp.tiles_w) * tp.tiles_n;
   if (total >= 0x7fffffffull) { err = "conv: too many tiles"; return -ZYXB_ERR_INCORRECT_KERNEL_ARG; }
@@ -434,17 +463,17 @@ int try_conv_tc(const zyxb_conv_desc& d, const ConvGeom& g, const void* x, const
   if (im2col) e = bn == 256 ? launch_conv_tc<256, 4, true>(mx, mw, tp, grid, lc.stream) : launch_conv_tc<128, 6, true>(mx, mw, tp, grid, lc.stream);
   else e = bn == 256 ? launch_conv_tc<256, 4, false>(mx, mw, tp, grid, lc.stream) : launch_conv_tc<128, 6, false>(mx, mw, tp, grid, lc.stream);
   if (e != cudaSuccess) { err = std::string("conv_tcgen05: ") + cudaGetErrorString(e); return -ZYXB_ERR_KERNEL_LAUNCH; }
-  *lc.launch_counter += 3;
+  *lc.launch_counter += in_place ? 2 : 3;
   return 1;
 }
 
 template <typename T>
-int launch_conv_direct(const ConvGeom& g, const void* x, const void* w, const void* bias, void* y, const LaunchCtx& lc, std::string& err) {
+int launch_conv_direct(const ConvGeom& g, int channels_last, const void* x, const void* w, const void* bias, void* y, const LaunchCtx& lc, std::string& err) {
   using S = typename Elem<T>::store_t;
   const uint64_t total = (uint64_t)g.n * g.o * g.oh * g.ow;
   const unsigned grid = (unsigned)std::min<uint64_t>((total + 255) / 256, (uint64_t)lc.sm_count * 16);
   conv_direct_kernel<T><<<grid, 256, 0, lc.stream>>>(reinterpret_cast<const S*>(x), reinterpret_cast<const S*>(w), reinterpret_cast<const S*>(bias),
-                                                     reinterpret_cast<S*>(y), g, total, lc.round_nearest ? 1 : 0);
+                                                     reinterpret_cast<S*>(y), g, total, lc.round_nearest ? 1 : 0, channels_last);
   return check_launch(lc, err, "conv_direct");
 }
 
@@ -475,10 +504,10 @@ int launch_conv(const zyxb_conv_desc& d, void* const* args, const uint64_t* arg_
   if (took < 0) return -took;
   if (took) return ZYXB_OK;
   switch (d.dtype) {
-    case ZYXB_F32: return launch_conv_direct<float>(g, x, w, bias, y, lc, err);
-    case ZYXB_BF16: return launch_conv_direct<bf16_t>(g, x, w, bias, y, lc, err);
-    case ZYXB_F16: return launch_conv_direct<f16_t>(g, x, w, bias, y, lc, err);
-    default: return launch_conv_direct<int32_t>(g, x, w, bias, y, lc, err);
+    case ZYXB_F32: return launch_conv_direct<float>(g, d.channels_last != 0, x, w, bias, y, lc, err);
+    case ZYXB_BF16: return launch_conv_direct<bf16_t>(g, d.channels_last != 0, x, w, bias, y, lc, err);
+    case ZYXB_F16: return launch_conv_direct<f16_t>(g, d.channels_last != 0, x, w, bias, y, lc, err);
+    default: return launch_conv_direct<int32_t>(g, d.channels_last != 0, x, w, bias, y, lc, err);
   }
 }
 

@@ -120,11 +120,15 @@ class Session:
         d = B.attention_desc(dtype, batch, heads, seq, e // heads, scale=scale, causal=causal, backward=True)
         return tuple(self.run(d, [q, k, v, o, do, np.ascontiguousarray(lse, np.float32)], [(q.shape, q.dtype)] * 3))
 
-    def conv(self, dtype, x, w, bias=None, stride=1, dilation=1, padding=0):
-        """x [n,c,h,w], w [o,c,kh,kw], bias [o] -> y [n,o,oh,ow]  (Tensor::conv, groups = 1)."""
-        assert x.shape[1] == w.shape[1], "conv: channel counts differ"
-        d = B.conv_desc(dtype, x.shape, w.shape, stride, dilation, padding, has_bias=bias is not None)
-        shape = B.conv_out_shape(x.shape, w.shape, stride, dilation, padding)
+    def conv(self, dtype, x, w, bias=None, stride=1, dilation=1, padding=0, channels_last=False):
+        """x [n,c,h,w], w [o,c,kh,kw], bias [o] -> y [n,o,oh,ow]  (Tensor::conv, groups = 1);
+        channels_last: x [n,h,w,c] -> y [n,oh,ow,o]."""
+        xs = (x.shape[0], x.shape[3], x.shape[1], x.shape[2]) if channels_last else x.shape
+        assert xs[1] == w.shape[1], "conv: channel counts differ"
+        d = B.conv_desc(dtype, xs, w.shape, stride, dilation, padding, has_bias=bias is not None, channels_last=channels_last)
+        shape = B.conv_out_shape(xs, w.shape, stride, dilation, padding)
+        if channels_last:
+            shape = (shape[0], shape[2], shape[3], shape[1])
         return self.run(d, [x, w] + ([bias] if bias is not None else []), [(shape, x.dtype)])[0]
 
     # ---- optimizers (in place on the host arrays, like the oracle's) ------------------------------
