@@ -261,6 +261,10 @@ typedef struct {
   int32_t  has_bias;
   int32_t  channels_last;  /* 1: x is [n,h,w,c] and y is [n,oh,ow,o] (w stays [o,c,kh,kw]): chained convolutions skip the
                               layout pass, TMA reads x in place (needs c % 8 == 0 for the tensor-core path) */
+  int32_t  flip_filter;    /* 1: the input gradient of a stride-1 convolution F (filter [O,C,kh,kw], padding p, dilation d).  x is
+                              dy of F (so this descriptor's c = O), this descriptor's o = C, w is F's filter buffer unchanged,
+                              read as w'[o][c][r][s] = w[c][o][kh-1-r][kw-1-s]; the caller sets padding to d*(k-1) - p per
+                              side (bottom / right: d*(k-1) - p_bottom / p_right) and dilation to d.  dx = this convolution. */
 } zyxb_conv_desc;
 /* args: x, w [,bias] -> y */
 

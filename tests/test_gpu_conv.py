@@ -126,3 +126,28 @@ def test_bad_arguments_are_errors(sess):
         sess.device.create_program(B.conv_desc(L.F32, (1, 1, 2, 2), (1, 1, 3, 3)))      # filter larger than the input
     with pytest.raises(B.BackendError):
         sess.device.create_program(B.conv_desc(L.F64, (1, 1, 4, 4), (1, 1, 3, 3)))
+
+
+@pytest.mark.parametrize("dtype", [L.BF16, L.F32])
+@pytest.mark.parametrize("case", [(2, 64, 28, 28, 96, 3, 3, 1, 1), (1, 32, 20, 24, 48, 3, 2, 2, (2, 1, 0, 2)), (1, 4, 9, 9, 6, 2, 3, 1, (0, 1, 2, 0))])
+def test_input_gradient_of_a_stride_one_convolution(sess, dtype, case):
+    """flip_filter: dx = conv(dy, filter transposed in (o, c) and reversed in (r, s), padding d*(k-1) - p), read from the
+    forward filter's buffer as it is.  Held against the oracle's convolution with an explicitly flipped filter, and
+    against autograd in float64."""
+    n, c, h, w_, o, kh, kw, dil, padding = case
+    pads = (padding,) * 4 if isinstance(padding, int) else padding
+    oh, ow = h + pads[0] + pads[1] - dil * (kh - 1), w_ + pads[2] + pads[3] - dil * (kw - 1)
+    wt = zo.to_bits((RNG.standard_normal((o, c, kh, kw)) / np.sqrt(o * kh * kw)).astype(np.float32), dtype)
+    dy = zo.to_bits(RNG.standard_normal((n, o, oh, ow)).astype(np.float32), dtype)
+    got = sess.conv_input_grad(dtype, dy, wt, (h, w_), dil, padding)
+    assert got.shape == (n, c, h, w_)
+    flipped = np.ascontiguousarray(wt.transpose(1, 0, 2, 3)[:, :, ::-1, ::-1])
+    back = (dil * (kh - 1) - pads[0], dil * (kh - 1) - pads[1], dil * (kw - 1) - pads[2], dil * (kw - 1) - pads[3])
+    want = zo.conv(dtype, dy, flipped, None, 1, dil, back)
+    x = torch.zeros((n, c, h, w_), dtype=torch.float64, requires_grad=True)
+    y = torch.nn.functional.conv2d(torch.nn.functional.pad(x, (pads[2], pads[3], pads[0], pads[1])),
+                                   torch.from_numpy(zo.to_f32(wt, dtype).astype(np.float64)), dilation=dil)
+    y.backward(torch.from_numpy(zo.to_f32(dy, dtype).astype(np.float64)))
+    exact = x.grad.numpy()
+    tol = TOL_F32 if dtype == L.F32 else TOL_BF16
+    assert_parity(zo.to_f32(got, dtype), zo.to_f32(want, dtype), exact, tol, floor=0.1, what="conv dgrad %s" % (case,))

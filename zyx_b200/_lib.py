@@ -79,7 +79,7 @@ class ConvDesc(C.Structure):
     _fields_ = [("dtype", C.c_int32), ("n", C.c_uint64), ("c", C.c_uint64), ("h", C.c_uint64), ("w", C.c_uint64), ("o", C.c_uint64),
                 ("kh", C.c_uint64), ("kw", C.c_uint64), ("stride_h", C.c_uint32), ("stride_w", C.c_uint32), ("dil_h", C.c_uint32),
                 ("dil_w", C.c_uint32), ("pad_top", C.c_uint32), ("pad_bottom", C.c_uint32), ("pad_left", C.c_uint32),
-                ("pad_right", C.c_uint32), ("has_bias", C.c_int32), ("channels_last", C.c_int32)]
+                ("pad_right", C.c_uint32), ("has_bias", C.c_int32), ("channels_last", C.c_int32), ("flip_filter", C.c_int32)]
 
 
 class _DescUnion(C.Union):

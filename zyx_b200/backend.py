@@ -336,8 +336,9 @@ def conv_out_shape(x_shape, w_shape, stride=1, dilation=1, padding=0):
     return (n, o, (h + pt + pb - dh * (kh - 1) - 1) // sh + 1, (w + pl + pr - dw * (kw - 1) - 1) // sw + 1)
 
 
-def conv_desc(dtype, x_shape, w_shape, stride=1, dilation=1, padding=0, has_bias=False, channels_last=False):
-    """x_shape is always given as (n, c, h, w), whatever the memory layout."""
+def conv_desc(dtype, x_shape, w_shape, stride=1, dilation=1, padding=0, has_bias=False, channels_last=False, flip_filter=False):
+    """x_shape is always given as (n, c, h, w), whatever the memory layout; w_shape as (o, c, kh, kw) of THIS convolution
+    (with flip_filter the buffer itself is laid out [c, o, kh, kw]: the forward convolution's filter)."""
     d = L.KernelDesc()
     d.kind = L.KIND_CONV
     c = d.u.conv
@@ -347,7 +348,7 @@ def conv_desc(dtype, x_shape, w_shape, stride=1, dilation=1, padding=0, has_bias
     c.stride_h, c.stride_w = (stride, stride) if isinstance(stride, int) else stride
     c.dil_h, c.dil_w = (dilation, dilation) if isinstance(dilation, int) else dilation
     c.pad_top, c.pad_bottom, c.pad_left, c.pad_right = _pads(padding)
-    c.has_bias, c.channels_last = int(has_bias), int(channels_last)
+    c.has_bias, c.channels_last, c.flip_filter = int(has_bias), int(channels_last), int(flip_filter)
     return d
 
 

@@ -108,15 +108,19 @@ __global__ void __launch_bounds__(256) conv_nhwc_pairs_kernel(const uint16_t* __
   }
 }
 
-// w [o][c][taps] -> wt [o][taps][cp]
-__global__ void conv_weight_kernel(const uint16_t* __restrict__ w, uint16_t* __restrict__ wt, uint32_t c, uint32_t cp, uint32_t taps, uint64_t total) {
+// w [o][c][taps] -> wt [o][taps][cp].  flipped: the buffer holds the filter of the convolution whose input gradient this
+// one computes, [c][o][taps], and is read transposed in (o, c) with the taps reversed.
+__global__ void conv_weight_kernel(const uint16_t* __restrict__ w, uint16_t* __restrict__ wt, uint32_t c, uint32_t cp, uint32_t o_count,
+                                   uint32_t taps, uint64_t total, int flipped) {
   const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= total) return;
   const uint32_t ci = (uint32_t)(i % cp);
   const uint64_t ot = i / cp;
   const uint32_t tap = (uint32_t)(ot % taps);
   const uint64_t o = ot / taps;
-  wt[i] = ci < c ? w[(o * c + ci) * taps + tap] : (uint16_t)0;
+  uint16_t v = 0;
+  if (ci < c) v = flipped ? w[((uint64_t)ci * o_count + o) * taps + (taps - 1 - tap)] : w[(o * c + ci) * taps + tap];
+  wt[i] = v;
 }
 
 // ---- implicit GEMM ---------------------------------------------------------------------------------
@@ -321,7 +325,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tma_x, const __grid_constant_
 template <typename T>
 __global__ void conv_direct_kernel(const typename Elem<T>::store_t* __restrict__ x, const typename Elem<T>::store_t* __restrict__ w,
                                    const typename Elem<T>::store_t* __restrict__ bias, typename Elem<T>::store_t* __restrict__ y,
-                                   ConvGeom g, uint64_t total, int rn, int channels_last) {
+                                   ConvGeom g, uint64_t total, int rn, int channels_last, int flipped) {
   using A = typename Elem<T>::acc_t;
   // element strides of x: channels-first [n,c,h,w] or channels-last [n,h,w,c]
   const uint64_t xs_c = channels_last ? 1 : (uint64_t)g.h * g.w, xs_p = channels_last ? g.c : 1;
@@ -333,14 +337,15 @@ __global__ void conv_direct_kernel(const typename Elem<T>::store_t* __restrict__
     A acc = 0;
     for (uint32_t c = 0; c < g.c; ++c) {
       const auto* xp = x + n * g.c * (uint64_t)g.h * g.w + c * xs_c;
-      const auto* wp = w + ((uint64_t)o * g.c + c) * g.kh * g.kw;
+      // flipped: the stored filter is [c][o][kh][kw] and tap (r, s) reads its (kh-1-r, kw-1-s)
+      const auto* wp = w + (flipped ? ((uint64_t)c * g.o + o) : ((uint64_t)o * g.c + c)) * g.kh * g.kw;
       for (uint32_t r = 0; r < g.kh; ++r) {
         const int iy = (int)(oy * g.sh + r * g.dh) - g.pt;
         if (iy < 0 || iy >= (int)g.h) continue;           // zero padding contributes nothing
         for (uint32_t s = 0; s < g.kw; ++s) {
           const int ix = (int)(ox * g.sw + s * g.dw) - g.pl;
           if (ix < 0 || ix >= (int)g.w) continue;
-          acc += (A)Elem<T>::load(xp[((uint64_t)iy * g.w + ix) * xs_p]) * (A)Elem<T>::load(wp[r * g.kw + s]);
+          acc += (A)Elem<T>::load(xp[((uint64_t)iy * g.w + ix) * xs_p]) * (A)Elem<T>::load(wp[flipped ? (g.kh - 1 - r) * g.kw + (g.kw - 1 - s) : r * g.kw + s]);
         }
       }
     }
@@ -448,7 +453,7 @@ int try_conv_tc(const zyxb_conv_desc& d, const ConvGeom& g, const void* x, const
   else
     conv_nhwc_kernel<<<dim3((hw + 31) / 32, (cp + 31) / 32, g.n), dim3(32, 8), 0, lc.stream>>>(reinterpret_cast<const uint16_t*>(x), xt, g.c, cp, hw);
   const uint64_t wtotal = (uint64_t)g.o * taps * cp;
-  conv_weight_kernel<<<(unsigned)((wtotal + 255) / 256), 256, 0, lc.stream>>>(reinterpret_cast<const uint16_t*>(w), wt, g.c, cp, taps, wtotal);
+  conv_weight_kernel<<<(unsigned)((wtotal + 255) / 256), 256, 0, lc.stream>>>(reinterpret_cast<const uint16_t*>(w), wt, g.c, cp, g.o, taps, wtotal, d.flip_filter != 0);
   ConvTcParams tp{};
   tp.bias = bias; tp.y = y; tp.g = g; tp.cp = cp; tp.cblocks = (cp + CV_BK - 1) / CV_BK;
   tp.tw = tw; tp.th = th; tp.tw_shift = 0;
@@ -468,12 +473,12 @@ int try_conv_tc(const zyxb_conv_desc& d, const ConvGeom& g, const void* x, const
 }
 
 template <typename T>
-int launch_conv_direct(const ConvGeom& g, int channels_last, const void* x, const void* w, const void* bias, void* y, const LaunchCtx& lc, std::string& err) {
+int launch_conv_direct(const ConvGeom& g, int channels_last, int flipped, const void* x, const void* w, const void* bias, void* y, const LaunchCtx& lc, std::string& err) {
   using S = typename Elem<T>::store_t;
   const uint64_t total = (uint64_t)g.n * g.o * g.oh * g.ow;
   const unsigned grid = (unsigned)std::min<uint64_t>((total + 255) / 256, (uint64_t)lc.sm_count * 16);
   conv_direct_kernel<T><<<grid, 256, 0, lc.stream>>>(reinterpret_cast<const S*>(x), reinterpret_cast<const S*>(w), reinterpret_cast<const S*>(bias),
-                                                     reinterpret_cast<S*>(y), g, total, lc.round_nearest ? 1 : 0, channels_last);
+                                                     reinterpret_cast<S*>(y), g, total, lc.round_nearest ? 1 : 0, channels_last, flipped);
   return check_launch(lc, err, "conv_direct");
 }
 
@@ -504,10 +509,10 @@ int launch_conv(const zyxb_conv_desc& d, void* const* args, const uint64_t* arg_
   if (took < 0) return -took;
   if (took) return ZYXB_OK;
   switch (d.dtype) {
-    case ZYXB_F32: return launch_conv_direct<float>(g, d.channels_last != 0, x, w, bias, y, lc, err);
-    case ZYXB_BF16: return launch_conv_direct<bf16_t>(g, d.channels_last != 0, x, w, bias, y, lc, err);
-    case ZYXB_F16: return launch_conv_direct<f16_t>(g, d.channels_last != 0, x, w, bias, y, lc, err);
-    default: return launch_conv_direct<int32_t>(g, d.channels_last != 0, x, w, bias, y, lc, err);
+    case ZYXB_F32: return launch_conv_direct<float>(g, d.channels_last != 0, d.flip_filter != 0, x, w, bias, y, lc, err);
+    case ZYXB_BF16: return launch_conv_direct<bf16_t>(g, d.channels_last != 0, d.flip_filter != 0, x, w, bias, y, lc, err);
+    case ZYXB_F16: return launch_conv_direct<f16_t>(g, d.channels_last != 0, d.flip_filter != 0, x, w, bias, y, lc, err);
+    default: return launch_conv_direct<int32_t>(g, d.channels_last != 0, d.flip_filter != 0, x, w, bias, y, lc, err);
   }
 }
 

@@ -131,6 +131,20 @@ class Session:
             shape = (shape[0], shape[2], shape[3], shape[1])
         return self.run(d, [x, w] + ([bias] if bias is not None else []), [(shape, x.dtype)])[0]
 
+    def conv_input_grad(self, dtype, dy, w, x_hw, dilation=1, padding=0):
+        """dx of y = conv(x, w, stride 1, dilation, padding): dy [n,o,oh,ow], w [o,c,kh,kw] (the forward filter, unchanged)
+        -> dx [n,c,h,w].  The adjoint of a stride-1 convolution is a convolution of dy with the filter transposed in
+        (o, c) and reversed in (r, s), padded by dilation*(k-1) - padding."""
+        o, c, kh, kw = w.shape
+        dh, dw = (dilation, dilation) if isinstance(dilation, int) else dilation
+        pt, pb, pl, pr = B._pads(padding)
+        pads = (dh * (kh - 1) - pt, dh * (kh - 1) - pb, dw * (kw - 1) - pl, dw * (kw - 1) - pr)
+        assert min(pads) >= 0, "conv_input_grad: padding larger than the dilated filter extent"
+        d = B.conv_desc(dtype, dy.shape, (c, o, kh, kw), 1, (dh, dw), pads, flip_filter=True)
+        shape = B.conv_out_shape(dy.shape, (c, o, kh, kw), 1, (dh, dw), pads)
+        assert shape[2:] == tuple(x_hw), (shape, x_hw)
+        return self.run(d, [dy, w], [(shape, dy.dtype)])[0]
+
     # ---- optimizers (in place on the host arrays, like the oracle's) ------------------------------
     def optim_step(self, desc_kw, dtype, algo, tensors, t=None):
         """tensors: list of groups [p, g (, m, v | , buf)] of host arrays per parameter; updated in place."""
