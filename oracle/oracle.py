@@ -259,6 +259,21 @@ def conv(dtype, x, w, bias=None, stride=1, dilation=1, padding=0):
     return y
 
 
+def conv_weight_grad(dtype, x, dy, w_shape, stride=1, dilation=1, padding=0):
+    """Filter gradient of conv: x [n,c,h,w], dy [n,o,oh,ow] -> dw [o,c,kh,kw]."""
+    sh, sw = (stride, stride) if isinstance(stride, int) else stride
+    dh, dw = (dilation, dilation) if isinstance(dilation, int) else dilation
+    pad = (padding,) * 4 if isinstance(padding, int) else ((padding[0], padding[0], padding[1], padding[1]) if len(padding) == 2 else tuple(padding))
+    n, c, h, wd = x.shape
+    o, c2, kh, kw = w_shape
+    assert c == c2 and dy.shape[:2] == (n, o), (x.shape, dy.shape, w_shape)
+    out = np.empty(tuple(w_shape), _NP[dtype])
+    pads = (C.c_int64 * 4)(*pad)
+    lib().zo_conv_wgrad(dtype, _p(_c(x, dtype)), _p(_c(dy, dtype)), _p(out), _u64(n), _u64(c), _u64(h), _u64(wd), _u64(o), _u64(kh), _u64(kw),
+                        _u64(sh), _u64(sw), _u64(dh), _u64(dw), pads)
+    return out
+
+
 # ---- optimizers --------------------------------------------------------------------------
 def sgd(dtype, p, g, buf=None, lr=0.01, wd=0.0, momentum=0.0, dampening=0.0, nesterov=False, maximize=False, first=True,
         grad_scale=1.0):

@@ -496,6 +496,35 @@ void zo_conv(int dtype, const void* x, const void* w, const void* bias, void* y,
         }
 }
 
+/* Gradient of zo_conv with respect to the filter: the filter enters the product expanded over (n, i, j), so its adjoint
+ * (zyx/src/graph/autograd.rs: Expand -> sum over the expanded axes) is the sum over them, taken in that order, of
+ * dy * (padded, pooled x); f32 accumulator, one rounding at the store. */
+void zo_conv_wgrad(int dtype, const void* x, const void* dy, void* dwt, uint64_t n, uint64_t c, uint64_t h, uint64_t wd, uint64_t o, uint64_t kh,
+                   uint64_t kw, uint64_t sh, uint64_t sw, uint64_t dh, uint64_t dw, const int64_t* pad) {
+  int64_t oh = ((int64_t)h + pad[0] + pad[1] - (int64_t)dh * ((int64_t)kh - 1) - 1) / (int64_t)sh + 1;
+  int64_t ow = ((int64_t)wd + pad[2] + pad[3] - (int64_t)dw * ((int64_t)kw - 1) - 1) / (int64_t)sw + 1;
+#pragma omp parallel for collapse(2)
+  for (uint64_t io = 0; io < o; io++)
+    for (uint64_t ic = 0; ic < c; ic++)
+      for (uint64_t r = 0; r < kh; r++)
+        for (uint64_t s = 0; s < kw; s++) {
+          float acc = 0.0f; uint32_t iacc = 0;
+          for (uint64_t in = 0; in < n; in++)
+            for (int64_t i = 0; i < oh; i++)
+              for (int64_t j = 0; j < ow; j++) {
+                int64_t iy = i * (int64_t)sh + (int64_t)(r * dh) - pad[0], ix = j * (int64_t)sw + (int64_t)(s * dw) - pad[2];
+                if (iy < 0 || iy >= (int64_t)h || ix < 0 || ix >= (int64_t)wd) continue;
+                uint64_t xi = ((in * c + ic) * h + (uint64_t)iy) * wd + (uint64_t)ix;
+                uint64_t yi = ((in * o + io) * (uint64_t)oh + (uint64_t)i) * (uint64_t)ow + (uint64_t)j;
+                if (dtype == ZO_I32) iacc += (uint32_t)((const int32_t*)dy)[yi] * (uint32_t)((const int32_t*)x)[xi];
+                else acc = zo_load(dy, dtype, yi) * zo_load(x, dtype, xi) + acc;
+              }
+          uint64_t wi = ((io * c + ic) * kh + r) * kw + s;
+          if (dtype == ZO_I32) ((int32_t*)dwt)[wi] = (int32_t)iacc;
+          else zo_store(dwt, dtype, wi, acc);
+        }
+}
+
 /* ---------------------------------------------------------------------------------------
  * Optimizers — zyx-optim/src/{sgd,adam,adamw}.rs.  Every hyper-parameter enters as a
  * rank-0 scalar and is therefore cast to the tensor dtype (truncated for bf16).  State

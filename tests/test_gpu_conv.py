@@ -151,3 +151,59 @@ def test_input_gradient_of_a_stride_one_convolution(sess, dtype, case):
     exact = x.grad.numpy()
     tol = TOL_F32 if dtype == L.F32 else TOL_BF16
     assert_parity(zo.to_f32(got, dtype), zo.to_f32(want, dtype), exact, tol, floor=0.1, what="conv dgrad %s" % (case,))
+
+
+def exact_weight_grad(x, dy, w_shape, stride, dilation, padding):
+    pad = (padding,) * 4 if isinstance(padding, int) else ((padding[0], padding[0], padding[1], padding[1]) if len(padding) == 2 else padding)
+    w = torch.zeros(tuple(w_shape), dtype=torch.float64, requires_grad=True)
+    xt = torch.nn.functional.pad(torch.from_numpy(np.asarray(x, np.float64)), (pad[2], pad[3], pad[0], pad[1]))
+    torch.nn.functional.conv2d(xt, w, stride=stride, dilation=dilation).backward(torch.from_numpy(np.asarray(dy, np.float64)))
+    return w.grad.numpy()
+
+
+WG_CASES = [
+    (2, 64, 28, 28, 64, 3, 3, 1, 1, 1),                # 1568 positions, one 128 x 128 tile per tap
+    (2, 160, 20, 20, 200, 3, 3, 1, 1, 1),              # two filter blocks, 256-wide channel block with a ragged tail
+    (3, 24, 33, 31, 40, 3, 2, (2, 1), (1, 2), (1, 0, 2, 1)),   # strides, dilations, asymmetric padding, odd plane
+    (16, 8, 32, 32, 8, 5, 5, 2, 1, 2),                 # one chunk of 64 in each operand mostly empty
+    (4, 128, 14, 14, 128, 1, 1, 1, 1, 0),              # 1x1
+]
+
+
+@pytest.mark.parametrize("dtype", [L.BF16, L.F16])
+@pytest.mark.parametrize("case", WG_CASES)
+def test_weight_gradient_on_tensor_cores(sess, dtype, case):
+    n, c, h, w_, o, kh, kw, stride, dilation, padding = case
+    from zyx_b200 import backend as B
+    shape = B.conv_out_shape((n, c, h, w_), (o, c, kh, kw), stride, dilation, padding)
+    x = zo.to_bits(RNG.standard_normal((n, c, h, w_)).astype(np.float32), dtype)
+    dy = zo.to_bits((RNG.standard_normal(shape) / np.sqrt(shape[0] * shape[2] * shape[3])).astype(np.float32), dtype)
+    before = sess.device.launch_count()
+    got = sess.conv_weight_grad(dtype, x, dy, (o, c, kh, kw), stride, dilation, padding)
+    assert sess.device.launch_count() - before == 4, "expected two layout kernels, the tensor-core kernel and the split sum"
+    assert sess.device.status() == 0
+    want = zo.conv_weight_grad(dtype, x, dy, (o, c, kh, kw), stride, dilation, padding)
+    exact = exact_weight_grad(zo.to_f32(x, dtype), zo.to_f32(dy, dtype), (o, c, kh, kw), stride, dilation, padding)
+    # sums over thousands of positions: measured per filter [c*kh*kw] against a tenth of its largest entry
+    g, w, e = (a.reshape(o, -1) for a in (zo.to_f32(got, dtype), zo.to_f32(want, dtype), exact))
+    assert_parity(g, w, e, TOL_BF16, floor=0.1, what="conv wgrad %s" % (case,))
+    if c % 8 == 0 and o % 8 == 0:
+        got_cl = sess.conv_weight_grad(dtype, np.ascontiguousarray(x.transpose(0, 2, 3, 1)), np.ascontiguousarray(dy.transpose(0, 2, 3, 1)),
+                                       (o, c, kh, kw), stride, dilation, padding, channels_last=True)
+        assert np.array_equal(got_cl, got)                 # the same tiles, the same order of sums
+
+
+def test_weight_gradient_direct_kernel(sess):
+    x = RNG.integers(-20, 20, (2, 3, 9, 8)).astype(np.int32)
+    dy = RNG.integers(-9, 9, (2, 4, 5, 4)).astype(np.int32)
+    got = sess.conv_weight_grad(L.I32, x, dy, (4, 3, 3, 3), 2, 1, 1)
+    assert np.array_equal(got, zo.conv_weight_grad(zo.I32, x, dy, (4, 3, 3, 3), 2, 1, 1))
+    assert np.array_equal(got, exact_weight_grad(x, dy, (4, 3, 3, 3), 2, 1, 1).astype(np.int64))
+    xf = RNG.standard_normal((2, 5, 11, 7)).astype(np.float32)
+    dyf = RNG.standard_normal((2, 6, 11, 7)).astype(np.float32)
+    got = sess.conv_weight_grad(L.F32, xf, dyf, (6, 5, 3, 3), 1, 1, 1)
+    want = zo.conv_weight_grad(zo.F32, xf, dyf, (6, 5, 3, 3), 1, 1, 1)
+    assert_parity(got.reshape(6, -1), want.reshape(6, -1), exact_weight_grad(xf, dyf, (6, 5, 3, 3), 1, 1, 1).reshape(6, -1), TOL_F32, floor=0.1, what="wgrad f32")
+    got_cl = sess.conv_weight_grad(L.F32, np.ascontiguousarray(xf.transpose(0, 2, 3, 1)), np.ascontiguousarray(dyf.transpose(0, 2, 3, 1)), (6, 5, 3, 3), 1, 1, 1,
+                                   channels_last=True)
+    assert np.array_equal(got_cl, got)

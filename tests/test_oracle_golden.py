@@ -241,3 +241,15 @@ def test_conv_golden_and_float64():
     exact = torch.nn.functional.conv2d(torch.from_numpy(zo.to_f32(xb, zo.BF16)).double(), torch.from_numpy(zo.to_f32(wb, zo.BF16)).double(), padding=1).numpy()
     got = zo.to_f32(yb, zo.BF16).astype(np.float64)
     assert np.all(np.abs(got) <= np.abs(exact) + 1e-4) and np.abs(got - exact).max() <= 2.0 ** -7 * np.abs(exact).max()
+
+
+def test_conv_weight_gradient_against_float64_autograd():
+    import torch
+    rng = np.random.default_rng(3)
+    x = rng.standard_normal((2, 5, 11, 7)).astype(np.float32)
+    dy = rng.standard_normal((2, 6, 5, 8)).astype(np.float32)
+    got = zo.conv_weight_grad(zo.F32, x, dy, (6, 5, 3, 2), (2, 1), (1, 2), (1, 0, 2, 1))
+    w = torch.zeros((6, 5, 3, 2), dtype=torch.float64, requires_grad=True)
+    xt = torch.nn.functional.pad(torch.from_numpy(x).double(), (2, 1, 1, 0))
+    torch.nn.functional.conv2d(xt, w, stride=(2, 1), dilation=(1, 2)).backward(torch.from_numpy(dy).double())
+    assert np.abs(got - w.grad.numpy()).max() <= 1e-5 * np.abs(w.grad.numpy()).max()

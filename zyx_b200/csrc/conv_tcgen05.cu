@@ -482,6 +482,8 @@ int launch_conv_direct(const ConvGeom& g, int channels_last, int flipped, const 
   return check_launch(lc, err, "conv_direct");
 }
 
+#include "conv_wgrad_impl.cuh"
+
 }  // namespace
 
 int validate_conv(const zyxb_conv_desc& d, std::string& err) {
@@ -513,6 +515,26 @@ int launch_conv(const zyxb_conv_desc& d, void* const* args, const uint64_t* arg_
     case ZYXB_BF16: return launch_conv_direct<bf16_t>(g, d.channels_last != 0, d.flip_filter != 0, x, w, bias, y, lc, err);
     case ZYXB_F16: return launch_conv_direct<f16_t>(g, d.channels_last != 0, d.flip_filter != 0, x, w, bias, y, lc, err);
     default: return launch_conv_direct<int32_t>(g, d.channels_last != 0, d.flip_filter != 0, x, w, bias, y, lc, err);
+  }
+}
+
+int launch_conv_wgrad(const zyxb_conv_desc& d, void* const* args, const uint64_t* arg_bytes, int n_args, const LaunchCtx& lc, std::string& err) {
+  ConvGeom g;
+  if (!geometry(d, g, err)) return ZYXB_ERR_INCORRECT_KERNEL_ARG;
+  ZYXB_CHECK_ARG(n_args == 3, "conv weight gradient: expects x, dy -> dw");
+  const uint64_t es = dtype_size(d.dtype);
+  ZYXB_CHECK_ARG(arg_bytes[0] >= (uint64_t)g.n * g.c * g.h * g.w * es, "conv weight gradient: x is smaller than [n, c, h, w]");
+  ZYXB_CHECK_ARG(arg_bytes[1] >= (uint64_t)g.n * g.o * g.oh * g.ow * es, "conv weight gradient: dy is smaller than [n, o, oh, ow]");
+  ZYXB_CHECK_ARG(arg_bytes[2] >= (uint64_t)g.o * g.c * g.kh * g.kw * es, "conv weight gradient: dw is smaller than [o, c, kh, kw]");
+  const int took = try_conv_wgrad_tc(d, g, args[0], args[1], args[2], lc, err);
+  if (took < 0) return -took;
+  if (took) return ZYXB_OK;
+  const int cl = d.channels_last != 0;
+  switch (d.dtype) {
+    case ZYXB_F32: return launch_conv_wgrad_direct<float>(g, cl, args[0], args[1], args[2], lc, err);
+    case ZYXB_BF16: return launch_conv_wgrad_direct<bf16_t>(g, cl, args[0], args[1], args[2], lc, err);
+    case ZYXB_F16: return launch_conv_wgrad_direct<f16_t>(g, cl, args[0], args[1], args[2], lc, err);
+    default: return launch_conv_wgrad_direct<int32_t>(g, cl, args[0], args[1], args[2], lc, err);
   }
 }
 

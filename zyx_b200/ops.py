@@ -131,6 +131,13 @@ class Session:
             shape = (shape[0], shape[2], shape[3], shape[1])
         return self.run(d, [x, w] + ([bias] if bias is not None else []), [(shape, x.dtype)])[0]
 
+    def conv_weight_grad(self, dtype, x, dy, w_shape, stride=1, dilation=1, padding=0, channels_last=False):
+        """dw of y = conv(x, w, ...): x [n,c,h,w], dy [n,o,oh,ow] -> dw [o,c,kh,kw] (channels_last: x [n,h,w,c], dy [n,oh,ow,o])."""
+        xs = (x.shape[0], x.shape[3], x.shape[1], x.shape[2]) if channels_last else x.shape
+        d = B.conv_desc(dtype, xs, w_shape, stride, dilation, padding, channels_last=channels_last)
+        d.kind = L.KIND_CONV_WGRAD
+        return self.run(d, [x, dy], [(tuple(w_shape), x.dtype)])[0]
+
     def conv_input_grad(self, dtype, dy, w, x_hw, dilation=1, padding=0):
         """dx of y = conv(x, w, stride 1, dilation, padding): dy [n,o,oh,ow], w [o,c,kh,kw] (the forward filter, unchanged)
         -> dx [n,c,h,w].  The adjoint of a stride-1 convolution is a convolution of dy with the filter transposed in
