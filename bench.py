@@ -509,7 +509,7 @@ class AttentionFwd:
 class Conv:
     """A ResNet-style 3x3 convolution layer, bf16: x [32, 256, 56, 56] N(0,1), w [256, 256, 3, 3] U(+-1/sqrt(c*9)) as
     Conv2d::new draws it (zyx-nn/src/conv2d.rs:38-47), bias, stride 1, padding 1; channels-first in and out."""
-    metric, unit, dtype, bound = "convolution forward TFLOP/s (implicit GEMM, 3x3, 256 -> 256 channels)", "TFLOP/s", "bf16", "tensor"
+    metric, unit, dtype, bound = "convolution forward + input gradient + weight gradient TFLOP/s (implicit GEMM, 3x3, 256 -> 256 channels; L2 flushes inside the step)", "TFLOP/s", "bf16", "tensor"
     N, C, H, W, O, K = 32, 256, 56, 56, 256, 3
 
     def __init__(self, size=0, channels_last=False):
@@ -518,7 +518,7 @@ class Conv:
         self.channels_last = channels_last
         self.name = "conv3x3_bf16_n%d_c%d_%dx%d_o%d%s" % (self.N, self.C, self.H, self.W, self.O, "_channels_last" if channels_last else "")
         self.flops = 2.0 * self.N * self.H * self.W * self.O * self.C * self.K * self.K
-        self.units_per_step = self.flops / 1e12
+        self.units_per_step = 3 * self.flops / 1e12            # forward and the two gradients: the same product count each
         self.h2d_bytes = self.N * self.C * self.H * self.W * 2
         self.d2h_bytes = self.N * self.O * self.H * self.W * 2
 
@@ -538,6 +538,17 @@ class Conv:
         self.bx, self.bw, self.bb = p.upload(self.xdev), p.upload(self.w), p.upload(self.b)
         self.by, _ = p.allocate(self.d2h_bytes)
         self.prog = d.create_program(B.conv_desc(L.BF16, self.x.shape, self.w.shape, 1, 1, 1, has_bias=True, channels_last=self.channels_last))
+        # the two gradients of the same layer (timed beside the forward, reported under "kernels"): dy stands in as an
+        # N(0,1) tensor of y's shape; the input gradient is the flipped-filter convolution of dy (3x3, padding 1: same shape)
+        dgrad = B.conv_desc(L.BF16, (self.N, self.O, self.H, self.W), (self.C, self.O, self.K, self.K), 1, 1, 1, channels_last=self.channels_last, flip_filter=True)
+        wgrad = B.conv_desc(L.BF16, self.x.shape, self.w.shape, 1, 1, 1, channels_last=self.channels_last)
+        wgrad.kind = L.KIND_CONV_WGRAD
+        self.prog_dgrad, self.prog_wgrad = d.create_program(dgrad), d.create_program(wgrad)
+        rng = np.random.default_rng(7)
+        self.bdy = p.upload(f32_to_bf16_bits(rng.standard_normal((self.N * self.O * self.H * self.W,), dtype=np.float32)))
+        self.bdx, _ = p.allocate(self.h2d_bytes)
+        self.bdw, _ = p.allocate(self.w.nbytes)
+        self.grad_events = {"input_gradient": [], "weight_gradient": []}
         self.config = {"workload": self.name, "l2": "L2 flushed (256 MB memset) before every timed launch",
                        "launch": "two kernels: filters to [o, tap, c], implicit GEMM reading x in place" if self.channels_last else
                                  "three kernels: activations to channels-last, filters to [o, tap, c], implicit GEMM"}
@@ -550,14 +561,25 @@ class Conv:
         d.launch(self.prog, [self.bx, self.bw, self.bb, self.by])
         if timed:
             self.kernel_events.append((e0, d.event_record()))
+        for name, prog, args in (("input_gradient", self.prog_dgrad, [self.bdy, self.bw, self.bdx]),
+                                 ("weight_gradient", self.prog_wgrad, [self.bx, self.bdy, self.bdw])):
+            d.flush_l2()
+            e1 = d.event_record() if timed else None
+            d.launch(prog, args)
+            if timed:
+                self.grad_events[name].append((e1, d.event_record()))
 
     def roofline(self, peaks, clocks=None):
         d = self.sess.device
         t = float(np.mean([d.elapsed_ms(a, b) for a, b in self.kernel_events]))
         ach = self.flops / (t * 1e-3) / 1e12
+        grads = {}
+        for name, evs in self.grad_events.items():
+            tg = float(np.mean([d.elapsed_ms(a, b) for a, b in evs]))
+            grads[name] = {"ms": tg, "TFLOP/s": self.flops / (tg * 1e-3) / 1e12}
         return ({"bound": "tensor", "kernel": "conv_tc_kernel (tcgen05) with its two layout kernels", "achieved": ach, "peak": peaks["bf16_tflops"],
                  "unit": "TFLOP/s", "frac": ach / peaks["bf16_tflops"], "traffic": None, "peak_source": peaks["source"], "ms_per_launch": t},
-                {"conv": {"ms": t, "TFLOP/s": ach}})
+                dict({"conv": {"ms": t, "TFLOP/s": ach}}, **grads))
 
     def e2e_setup(self):
         self.hy = np.empty((self.N, self.O, self.H, self.W), np.uint16)
