@@ -608,11 +608,15 @@ class Conv:
         from oracle import oracle as zo
         self.host_inputs() if not hasattr(self, "x") else None
         n, o = 1, 32
+        dy = np.ascontiguousarray(self.x[:n, :o])                      # any tensor of y's shape [n, o, 56, 56] serves as dy
+        flipped = np.ascontiguousarray(self.w[:o].transpose(1, 0, 2, 3)[:, :, ::-1, ::-1])
         t0 = time.perf_counter()
         zo.conv(zo.BF16, self.x[:n], self.w[:o], self.b[:o], 1, 1, 1)
+        zo.conv(zo.BF16, dy, flipped, None, 1, 1, 1)                   # input gradient: dy with the transposed, reversed filter
+        zo.conv_weight_grad(zo.BF16, self.x[:n], dy, (o, self.C, self.K, self.K), 1, 1, 1)
         dt = time.perf_counter() - t0
-        fl = 2.0 * n * self.H * self.W * o * self.C * self.K * self.K
-        return fl / dt / 1e12, "%d image(s) x %d of %d filters, %.1f s" % (n, o, self.O, dt)
+        fl = 3 * 2.0 * n * self.H * self.W * o * self.C * self.K * self.K
+        return fl / dt / 1e12, "forward, input gradient and filter gradient of %d image(s) x %d of %d filters, %.1f s" % (n, o, self.O, dt)
 
 
 class MlpTrain:
