@@ -96,7 +96,7 @@ typedef struct {
  * them (zyx/src/backend/mod.rs:974, zyx/src/runtime.rs:2285-2291).
  * ---------------------------------------------------------------------------------- */
 enum { ZYXB_KIND_ROWREDUCE = 1, ZYXB_KIND_GEMM = 2, ZYXB_KIND_ELTWISE = 3, ZYXB_KIND_OPTIM = 4, ZYXB_KIND_ATTENTION = 5, ZYXB_KIND_ATTENTION_BWD = 6,
-       ZYXB_KIND_CONV = 7, ZYXB_KIND_CONV_WGRAD = 8 };
+       ZYXB_KIND_CONV = 7, ZYXB_KIND_CONV_WGRAD = 8, ZYXB_KIND_CONV_DGRAD = 9 };
 
 /* Row kernels: an elementwise chain with a trailing reduce over the last axis.
  * Semantics: Tensor::reduce_impl (zyx/src/tensor/reduce_ops.rs:45-157), softmax /
@@ -267,6 +267,9 @@ typedef struct {
                               side (bottom / right: d*(k-1) - p_bottom / p_right) and dilation to d.  dx = this convolution. */
 } zyxb_conv_desc;
 /* ZYXB_KIND_CONV        args: x, w [,bias] -> y
+ * ZYXB_KIND_CONV_DGRAD  args: dy, w -> dx   the input gradient of the convolution the descriptor names (has_bias and flip_filter
+ *                       ignored).  Stride 1 with padding <= dil*(k-1): runs as the flip_filter convolution of dy, tensor cores
+ *                       included; other strides: a direct kernel.
  * ZYXB_KIND_CONV_WGRAD  args: x, dy -> dw   the filter gradient of the convolution the descriptor names (has_bias and
  *                       flip_filter ignored): dw[o,c,r,s] = sum over (n,i,j) of dy[n,o,i,j] * x[n,c,i*stride_h+r*dil_h-pad_top, ...];
  *                       bf16 / f16 with enough work run per tap as a matmul over the output positions on the tensor cores

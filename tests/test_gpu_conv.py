@@ -139,7 +139,7 @@ def test_input_gradient_of_a_stride_one_convolution(sess, dtype, case):
     oh, ow = h + pads[0] + pads[1] - dil * (kh - 1), w_ + pads[2] + pads[3] - dil * (kw - 1)
     wt = zo.to_bits((RNG.standard_normal((o, c, kh, kw)) / np.sqrt(o * kh * kw)).astype(np.float32), dtype)
     dy = zo.to_bits(RNG.standard_normal((n, o, oh, ow)).astype(np.float32), dtype)
-    got = sess.conv_input_grad(dtype, dy, wt, (h, w_), dil, padding)
+    got = sess.conv_input_grad(dtype, dy, wt, (h, w_), 1, dil, padding)
     assert got.shape == (n, c, h, w_)
     flipped = np.ascontiguousarray(wt.transpose(1, 0, 2, 3)[:, :, ::-1, ::-1])
     back = (dil * (kh - 1) - pads[0], dil * (kh - 1) - pads[1], dil * (kw - 1) - pads[2], dil * (kw - 1) - pads[3])
@@ -207,3 +207,34 @@ def test_weight_gradient_direct_kernel(sess):
     got_cl = sess.conv_weight_grad(L.F32, np.ascontiguousarray(xf.transpose(0, 2, 3, 1)), np.ascontiguousarray(dyf.transpose(0, 2, 3, 1)), (6, 5, 3, 3), 1, 1, 1,
                                    channels_last=True)
     assert np.array_equal(got_cl, got)
+
+
+@pytest.mark.parametrize("dtype", [L.BF16, L.F32, L.I32])
+@pytest.mark.parametrize("channels_last", [False, True])
+def test_input_gradient_with_strides_takes_the_direct_kernel(sess, dtype, channels_last):
+    """Stride 2 x 3 with dilation and asymmetric padding: dx against float64 autograd (integers exactly)."""
+    n, c, h, w_, o, kh, kw, stride, dil, pads = 2, 5, 13, 17, 6, 3, 2, (2, 3), (1, 2), (1, 0, 2, 1)
+    from zyx_b200 import backend as B
+    shape = B.conv_out_shape((n, c, h, w_), (o, c, kh, kw), stride, dil, pads)
+    if dtype == L.I32:
+        wt, dy = RNG.integers(-9, 9, (o, c, kh, kw)).astype(np.int32), RNG.integers(-20, 20, shape).astype(np.int32)
+        f = lambda a: a
+    else:
+        wt = zo.to_bits(RNG.standard_normal((o, c, kh, kw)).astype(np.float32), dtype)
+        dy = zo.to_bits(RNG.standard_normal(shape).astype(np.float32), dtype)
+        f = lambda a: zo.to_f32(a, dtype)
+    dy_in = np.ascontiguousarray(dy.transpose(0, 2, 3, 1)) if channels_last else dy
+    got = sess.conv_input_grad(dtype, dy_in, wt, (h, w_), stride, dil, pads, channels_last=channels_last)
+    if channels_last:
+        got = got.transpose(0, 3, 1, 2)
+    x = torch.zeros((n, c, h, w_), dtype=torch.float64, requires_grad=True)
+    y = torch.nn.functional.conv2d(torch.nn.functional.pad(x, (pads[2], pads[3], pads[0], pads[1])), torch.from_numpy(np.asarray(f(wt), np.float64)),
+                                   stride=stride, dilation=dil)
+    y.backward(torch.from_numpy(np.asarray(f(dy), np.float64)))
+    exact = x.grad.numpy()
+    if dtype == L.I32:
+        assert np.array_equal(got, exact.astype(np.int64))
+    else:
+        tol = TOL_F32 if dtype == L.F32 else TOL_BF16
+        from tests.parity import max_rel_err
+        assert max_rel_err(f(got), exact, floor=0.1) <= tol

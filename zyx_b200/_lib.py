@@ -17,7 +17,7 @@ ERR_NAMES = {1: "DyLibNotFound", 2: "Initialization", 3: "Deinitialization", 4: 
              11: "KernelCompilation", 12: "KernelLaunch", 13: "KernelSync"}
 BF16, F16, F32, F64, U8, U16, U32, U64, I8, I16, I32, I64, BOOL = range(13)
 DTYPE_SIZE = {BF16: 2, F16: 2, F32: 4, F64: 8, U8: 1, U16: 2, U32: 4, U64: 8, I8: 1, I16: 2, I32: 4, I64: 8, BOOL: 1}
-KIND_ROWREDUCE, KIND_GEMM, KIND_ELTWISE, KIND_OPTIM, KIND_ATTENTION, KIND_ATTENTION_BWD, KIND_CONV, KIND_CONV_WGRAD = 1, 2, 3, 4, 5, 6, 7, 8
+KIND_ROWREDUCE, KIND_GEMM, KIND_ELTWISE, KIND_OPTIM, KIND_ATTENTION, KIND_ATTENTION_BWD, KIND_CONV, KIND_CONV_WGRAD, KIND_CONV_DGRAD = 1, 2, 3, 4, 5, 6, 7, 8, 9
 (RR_SUM, RR_MAX, RR_MIN, RR_MEAN, RR_VAR, RR_STD, RR_SOFTMAX, RR_LN_SOFTMAX, RR_LAYERNORM, RR_CROSS_ENTROPY,
  RR_CROSS_ENTROPY_BWD, RR_SOFTMAX_BWD, RR_LAYERNORM_BWD, RR_COLSUM, RR_MSE, RR_LAYERNORM_DYXHAT) = range(16)
 EPI_NONE, EPI_BIAS, EPI_BIAS_RELU, EPI_BIAS_GELU, EPI_MUL_RELU_GRAD, EPI_MUL_GELU_GRAD, EPI_ADD = range(7)

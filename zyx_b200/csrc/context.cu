@@ -521,7 +521,7 @@ int32_t zyxb_program_create(zyxb_ctx* ctx, int32_t dev, const zyxb_kernel_desc* 
     case ZYXB_KIND_ELTWISE: st = validate_eltwise(desc->u.eltwise, err); break;
     case ZYXB_KIND_OPTIM: st = validate_optim(desc->u.optim, err); break;
     case ZYXB_KIND_ATTENTION: case ZYXB_KIND_ATTENTION_BWD: st = validate_attention(desc->u.attention, err); break;
-    case ZYXB_KIND_CONV: case ZYXB_KIND_CONV_WGRAD: st = validate_conv(desc->u.conv, err); break;
+    case ZYXB_KIND_CONV: case ZYXB_KIND_CONV_WGRAD: case ZYXB_KIND_CONV_DGRAD: st = validate_conv(desc->u.conv, err); break;
     default: st = ZYXB_ERR_KERNEL_COMPILATION; err = "unknown kernel kind";
   }
   if (st) return fail(ctx, st, err);
@@ -587,6 +587,7 @@ int32_t zyxb_launch(zyxb_ctx* ctx, int32_t dev, uint32_t prog, const uint32_t* a
     case ZYXB_KIND_ATTENTION: st = launch_attention(P.desc.u.attention, ptrs.data(), sizes.data(), n_args, lc, err); break;
     case ZYXB_KIND_ATTENTION_BWD: st = launch_attention_bwd(P.desc.u.attention, ptrs.data(), sizes.data(), n_args, lc, err); break;
     case ZYXB_KIND_CONV: st = launch_conv(P.desc.u.conv, ptrs.data(), sizes.data(), n_args, lc, err); break;
+    case ZYXB_KIND_CONV_DGRAD: st = launch_conv_dgrad(P.desc.u.conv, ptrs.data(), sizes.data(), n_args, lc, err); break;
     case ZYXB_KIND_CONV_WGRAD: st = launch_conv_wgrad(P.desc.u.conv, ptrs.data(), sizes.data(), n_args, lc, err); break;
     case ZYXB_KIND_OPTIM:
       st = launch_optim(P.desc.u.optim, P.numel.data(), P.step + 1, ptrs.data(), sizes.data(), n_args, lc, err);

@@ -482,6 +482,46 @@ int launch_conv_direct(const ConvGeom& g, int channels_last, int flipped, const 
   return check_launch(lc, err, "conv_direct");
 }
 
+// input gradient, direct form (any stride): dx[n,c,y,x] = sum over (o, r, s) of dy[n,o,i,j] * w[o,c,r,s] for the output
+// positions (i, j) whose window element (r, s) is input position (y, x): i*stride_h + r*dil_h - pad_top = y, j alike
+template <typename T>
+__global__ void conv_dgrad_direct_kernel(const typename Elem<T>::store_t* __restrict__ dy, const typename Elem<T>::store_t* __restrict__ w,
+                                         typename Elem<T>::store_t* __restrict__ dx, ConvGeom g, uint64_t total, int rn, int channels_last) {
+  using A = typename Elem<T>::acc_t;
+  const uint64_t ys_o = channels_last ? 1 : (uint64_t)g.oh * g.ow, ys_p = channels_last ? g.o : 1;
+  for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
+    uint32_t ix, iy, c;
+    uint64_t n, q = i;
+    if (channels_last) { c = (uint32_t)(q % g.c); q /= g.c; ix = (uint32_t)(q % g.w); q /= g.w; iy = (uint32_t)(q % g.h); n = q / g.h; }
+    else { ix = (uint32_t)(q % g.w); q /= g.w; iy = (uint32_t)(q % g.h); q /= g.h; c = (uint32_t)(q % g.c); n = q / g.c; }
+    A acc = 0;
+    for (uint32_t o = 0; o < g.o; ++o) {
+      const auto* yp = dy + n * g.o * (uint64_t)g.oh * g.ow + o * ys_o;
+      const auto* wp = w + ((uint64_t)o * g.c + c) * g.kh * g.kw;
+      for (uint32_t r = 0; r < g.kh; ++r) {
+        const int ty = (int)iy + g.pt - (int)(r * g.dh);
+        if (ty < 0 || ty % (int)g.sh || ty / (int)g.sh >= (int)g.oh) continue;
+        for (uint32_t s = 0; s < g.kw; ++s) {
+          const int tx = (int)ix + g.pl - (int)(s * g.dw);
+          if (tx < 0 || tx % (int)g.sw || tx / (int)g.sw >= (int)g.ow) continue;
+          acc += (A)Elem<T>::load(yp[((uint64_t)(ty / (int)g.sh) * g.ow + (uint64_t)(tx / (int)g.sw)) * ys_p]) * (A)Elem<T>::load(wp[r * g.kw + s]);
+        }
+      }
+    }
+    dx[i] = Elem<T>::store(acc, rn != 0);
+  }
+}
+
+template <typename T>
+int launch_conv_dgrad_direct(const ConvGeom& g, int channels_last, const void* dy, const void* w, void* dx, const LaunchCtx& lc, std::string& err) {
+  using S = typename Elem<T>::store_t;
+  const uint64_t total = (uint64_t)g.n * g.c * g.h * g.w;
+  const unsigned grid = (unsigned)std::min<uint64_t>((total + 255) / 256, (uint64_t)lc.sm_count * 16);
+  conv_dgrad_direct_kernel<T><<<grid, 256, 0, lc.stream>>>(reinterpret_cast<const S*>(dy), reinterpret_cast<const S*>(w), reinterpret_cast<S*>(dx), g, total,
+                                                           lc.round_nearest ? 1 : 0, channels_last);
+  return check_launch(lc, err, "conv_dgrad_direct");
+}
+
 #include "conv_wgrad_impl.cuh"
 
 }  // namespace
@@ -515,6 +555,37 @@ int launch_conv(const zyxb_conv_desc& d, void* const* args, const uint64_t* arg_
     case ZYXB_BF16: return launch_conv_direct<bf16_t>(g, d.channels_last != 0, d.flip_filter != 0, x, w, bias, y, lc, err);
     case ZYXB_F16: return launch_conv_direct<f16_t>(g, d.channels_last != 0, d.flip_filter != 0, x, w, bias, y, lc, err);
     default: return launch_conv_direct<int32_t>(g, d.channels_last != 0, d.flip_filter != 0, x, w, bias, y, lc, err);
+  }
+}
+
+// Input gradient of the convolution the descriptor names: args dy, w -> dx.  With stride 1 it is itself a convolution
+// (of dy, with the filter transposed in (o, c) and reversed in (r, s), padding dil*(k-1) - pad): the forward program with
+// flip_filter, tensor cores included.  Other strides take the direct kernel.
+int launch_conv_dgrad(const zyxb_conv_desc& d, void* const* args, const uint64_t* arg_bytes, int n_args, const LaunchCtx& lc, std::string& err) {
+  ConvGeom g;
+  if (!geometry(d, g, err)) return ZYXB_ERR_INCORRECT_KERNEL_ARG;
+  ZYXB_CHECK_ARG(n_args == 3, "conv input gradient: expects dy, w -> dx");
+  const uint64_t es = dtype_size(d.dtype);
+  ZYXB_CHECK_ARG(arg_bytes[0] >= (uint64_t)g.n * g.o * g.oh * g.ow * es, "conv input gradient: dy is smaller than [n, o, oh, ow]");
+  ZYXB_CHECK_ARG(arg_bytes[1] >= (uint64_t)g.o * g.c * g.kh * g.kw * es, "conv input gradient: w is smaller than [o, c, kh, kw]");
+  ZYXB_CHECK_ARG(arg_bytes[2] >= (uint64_t)g.n * g.c * g.h * g.w * es, "conv input gradient: dx is smaller than [n, c, h, w]");
+  const int64_t eh = (int64_t)g.dh * (g.kh - 1), ew = (int64_t)g.dw * (g.kw - 1);
+  const bool as_conv = g.sh == 1 && g.sw == 1 && d.pad_top <= eh && d.pad_bottom <= eh && d.pad_left <= ew && d.pad_right <= ew;
+  if (as_conv) {
+    zyxb_conv_desc f = d;
+    f.c = g.o; f.h = g.oh; f.w = g.ow; f.o = g.c;
+    f.pad_top = (uint32_t)(eh - d.pad_top); f.pad_bottom = (uint32_t)(eh - d.pad_bottom);
+    f.pad_left = (uint32_t)(ew - d.pad_left); f.pad_right = (uint32_t)(ew - d.pad_right);
+    f.has_bias = 0; f.flip_filter = 1;
+    void* fargs[3] = {args[0], args[1], args[2]};
+    return launch_conv(f, fargs, arg_bytes, 3, lc, err);
+  }
+  const int cl = d.channels_last != 0;
+  switch (d.dtype) {
+    case ZYXB_F32: return launch_conv_dgrad_direct<float>(g, cl, args[0], args[1], args[2], lc, err);
+    case ZYXB_BF16: return launch_conv_dgrad_direct<bf16_t>(g, cl, args[0], args[1], args[2], lc, err);
+    case ZYXB_F16: return launch_conv_dgrad_direct<f16_t>(g, cl, args[0], args[1], args[2], lc, err);
+    default: return launch_conv_dgrad_direct<int32_t>(g, cl, args[0], args[1], args[2], lc, err);
   }
 }
 

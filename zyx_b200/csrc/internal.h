@@ -44,6 +44,7 @@ int launch_attention_bwd(const zyxb_attention_desc& d, void* const* args, const 
 int validate_attention(const zyxb_attention_desc& d, std::string& err);
 int launch_conv(const zyxb_conv_desc& d, void* const* args, const uint64_t* arg_bytes, int n_args, const LaunchCtx& lc, std::string& err);
 int validate_conv(const zyxb_conv_desc& d, std::string& err);
+int launch_conv_dgrad(const zyxb_conv_desc& d, void* const* args, const uint64_t* arg_bytes, int n_args, const LaunchCtx& lc, std::string& err);
 int launch_conv_wgrad(const zyxb_conv_desc& d, void* const* args, const uint64_t* arg_bytes, int n_args, const LaunchCtx& lc, std::string& err);
 
 // column sums with the partials in a fixed device array (no allocation anywhere on the path)

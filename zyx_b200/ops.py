@@ -138,19 +138,19 @@ class Session:
         d.kind = L.KIND_CONV_WGRAD
         return self.run(d, [x, dy], [(tuple(w_shape), x.dtype)])[0]
 
-    def conv_input_grad(self, dtype, dy, w, x_hw, dilation=1, padding=0):
-        """dx of y = conv(x, w, stride 1, dilation, padding): dy [n,o,oh,ow], w [o,c,kh,kw] (the forward filter, unchanged)
-        -> dx [n,c,h,w].  The adjoint of a stride-1 convolution is a convolution of dy with the filter transposed in
-        (o, c) and reversed in (r, s), padded by dilation*(k-1) - padding."""
+    def conv_input_grad(self, dtype, dy, w, x_hw, stride=1, dilation=1, padding=0, channels_last=False):
+        """dx of y = conv(x, w, stride, dilation, padding): dy [n,o,oh,ow], w [o,c,kh,kw] (the forward filter, unchanged)
+        -> dx [n,c,h,w] (channels_last: dy [n,oh,ow,o] -> dx [n,h,w,c]).  The descriptor is the forward convolution's."""
         o, c, kh, kw = w.shape
-        dh, dw = (dilation, dilation) if isinstance(dilation, int) else dilation
-        pt, pb, pl, pr = B._pads(padding)
-        pads = (dh * (kh - 1) - pt, dh * (kh - 1) - pb, dw * (kw - 1) - pl, dw * (kw - 1) - pr)
-        assert min(pads) >= 0, "conv_input_grad: padding larger than the dilated filter extent"
-        d = B.conv_desc(dtype, dy.shape, (c, o, kh, kw), 1, (dh, dw), pads, flip_filter=True)
-        shape = B.conv_out_shape(dy.shape, (c, o, kh, kw), 1, (dh, dw), pads)
-        assert shape[2:] == tuple(x_hw), (shape, x_hw)
-        return self.run(d, [dy, w], [(shape, dy.dtype)])[0]
+        n = dy.shape[0]
+        xs = (n, c, x_hw[0], x_hw[1])
+        d = B.conv_desc(dtype, xs, w.shape, stride, dilation, padding, channels_last=channels_last)
+        d.kind = L.KIND_CONV_DGRAD
+        want = B.conv_out_shape(xs, w.shape, stride, dilation, padding)
+        got = (n, dy.shape[3], dy.shape[1], dy.shape[2]) if channels_last else dy.shape
+        assert tuple(got) == tuple(want), (got, want)
+        out = (n, x_hw[0], x_hw[1], c) if channels_last else xs
+        return self.run(d, [dy, w], [(out, dy.dtype)])[0]
 
     # ---- optimizers (in place on the host arrays, like the oracle's) ------------------------------
     def optim_step(self, desc_kw, dtype, algo, tensors, t=None):
