@@ -57,6 +57,11 @@ int32_t zyxb_mlp_tensor(zyxb_mlp* mlp, int32_t which, int32_t i, uint32_t* out_b
 /* Input [batch, dims[0]], target, loss [1] f32, output of the last layer [batch, dims[n]]. */
 int32_t zyxb_mlp_io(zyxb_mlp* mlp, uint32_t* out_x, uint32_t* out_target, uint32_t* out_loss, uint32_t* out_y);
 
+/* Tensors the plan stores between forward and backward, all [batch, dims[layer+1]], for parity checks at full size:
+ * which 0 = the layer's output (after the activation; the network output for the last layer), 1 = its pre-activation
+ * (stored only under GELU, and not for the last layer), 2 = the gradient of the loss w.r.t. its pre-activation. */
+int32_t zyxb_mlp_activation(zyxb_mlp* mlp, int32_t which, int32_t layer, uint32_t* out_buf, uint64_t* out_numel);
+
 /* forward + loss + backward (+ gradient allreduce): the Launch nodes up to the gradients */
 int32_t zyxb_mlp_forward_backward(zyxb_mlp* mlp);
 /* the optimizer update (SGD::update / AdamW::update) */
@@ -109,8 +114,10 @@ int32_t zyxb_block_forward_backward(zyxb_block* blk);
 int32_t zyxb_block_update(zyxb_block* blk);
 int32_t zyxb_block_step(zyxb_block* blk, const zyxb_event* wait, int32_t n_wait);
 int32_t zyxb_block_plan_size(zyxb_block* blk, int32_t* out_launches, int32_t* out_collectives);
-/* intermediate activations for tests: 0 attention probabilities [batch*heads, seq, seq], 1 attention output [rows, dim],
- * 2 x1 (after norm1) [rows, dim] */
+/* intermediate tensors for tests (rows = batch*seq): 0 attention probabilities [batch*heads, seq, seq] (absent when fused),
+ * 1 attention output [rows, dim], 2 x1 (after norm1), 3 q, 4 k, 5 v, 6 o (output projection), 7 s1 = x + o,
+ * 8 z1 (feed-forward pre-activation) [rows, ffn], 9 h = gelu(z1) [rows, ffn], 10 m (second feed-forward output), 11 s2 = x1 + m;
+ * gradients: 12 dy, 13 ds2, 14 dz1 [rows, ffn], 15 dx1, 16 ds1, 17 dattn, 18 dq, 19 dk, 20 dv */
 int32_t zyxb_block_activation(zyxb_block* blk, int32_t which, uint32_t* out_buf);
 
 /* ---- safetensors files: parameters, optimizer state and parity fixtures on disk -------------------------

@@ -18,8 +18,8 @@ def init_linears(rng, dtype, dims):
     return [rng.linear_init(dtype, dims[i], dims[i + 1]) for i in range(len(dims) - 1)]
 
 
-def forward_backward(dtype, layers, x, target, activation, loss):
-    """-> (loss, [(dW, db)], y)."""
+def forward_backward(dtype, layers, x, target, activation, loss, keep=None):
+    """-> (loss, [(dW, db)], y).  `keep` (a dict) receives the stored intermediates: "act" / "pre" / "dz" lists per layer."""
     n = len(layers)
     acts, zs = [x], []
     for i, (w, b) in enumerate(layers):
@@ -37,8 +37,10 @@ def forward_backward(dtype, layers, x, target, activation, loss):
         lval = zo.mse(dtype, y, target)
         dz = zo.eltwise(zo.EW_MSE_BWD, dtype, y, target, p0=1.0 / y.size)
     grads = [None] * n
+    dzs = [None] * n
     for i in range(n - 1, -1, -1):
         w, _ = layers[i]
+        dzs[i] = dz
         dw = zo.gemm(dtype, dz, acts[i], ta=True)           # dZ^T . input
         db = zo.colsum(dtype, dz)
         grads[i] = (dw, db)
@@ -50,6 +52,8 @@ def forward_backward(dtype, layers, x, target, activation, loss):
                 dz = zo.gemm(dtype, dz, w, bias=zs[i - 1], epi=zo.EPI_MUL_GELU_GRAD)
             else:
                 dz = zo.gemm(dtype, dz, w)
+    if keep is not None:
+        keep.update(act=acts[1:], pre=zs, dz=dzs)
     return lval, grads, y
 
 
@@ -206,7 +210,9 @@ def block_forward_backward(dtype, p, x, target, heads, causal, eps=1e-5):
     lin_grads(dv, x2, "wv", "bv")
     lin_grads(dk, x2, "wk", "bk")
     lin_grads(dq, x2, "wq", "bq")
-    return loss, g, y.reshape(B, T, E), {"p": pr, "attn": attn, "x1": x1}
+    mid = {"p": pr, "attn": attn, "x1": x1, "q": q, "k": k, "v": v, "o": o, "s1": s1, "z1": z1, "h": h, "m": m, "s2": s2, "dy": dy, "ds2": ds2,
+           "dz1": dz1, "dx1": dx1, "ds1": ds1, "dattn": dattn, "dq": dq, "dk": dk, "dv": dv}
+    return loss, g, y.reshape(B, T, E), mid
 
 
 def _gemm_f32(dtype, a, b):

@@ -171,3 +171,23 @@ def test_activation_gradient_epilogue_f32(sess, epi):
     dz, w = rand((m, k), L.F32), rand((k, n), L.F32)
     z = RNG.normal(0, 1.5, size=(m, n)).astype(np.float32)
     assert gemm_err(sess.gemm(L.F32, dz, w, bias=z, epi=epi), zo.gemm(L.F32, dz, w, bias=z, epi=epi), L.F32) <= TOL[L.F32] * 3
+
+
+def test_f32_4096_cubed_sampled_rows(sess):
+    """The M=N=K=4096 f32 configuration at its stated size (A, B uniform(-1, 1), seeds 2 and 3, row-major): 24 sampled rows
+    against the oracle's product of the same rows (rows of A.B are independent, so the oracle on A[rows] is the oracle's
+    own answer for those rows) and against float64, at the f32 bar; and C(A, -B) == -C(A, B) over the whole matrix (a
+    size-independent property; the tensor core's accumulator rounding need not be symmetric, so it is held to the bar, not to bits)."""
+    n = 4096
+    a = np.random.default_rng(2).uniform(-1, 1, (n, n)).astype(np.float32)
+    b = np.random.default_rng(3).uniform(-1, 1, (n, n)).astype(np.float32)
+    got = sess.gemm(L.F32, a, b)
+    assert sess.device.status() == 0
+    rows = np.array([0, 1, 127, 128, 129, 255, 256, 1000, 2047, 2048, 2049, 3000, 3071, 3072, 3967, 3968, 4000, 4094, 4095, 3, 777, 1535, 1536, 2500])
+    exact = a[rows].astype(np.float64) @ b.astype(np.float64)
+    want = zo.gemm(L.F32, np.ascontiguousarray(a[rows]), b)
+    e_ge, e_go, e_oe = (max_rel_err(got[rows], exact, floor=0.1), max_rel_err(got[rows], want, floor=0.1), max_rel_err(want, exact, floor=0.1))
+    assert e_ge <= TOL_F32, (e_ge, e_go, e_oe)
+    assert e_go <= TOL_F32 + e_oe, (e_ge, e_go, e_oe)        # the oracle's sequential f32 sum of 4096 terms is itself about 1e-5 from exact
+    neg = sess.gemm(L.F32, a, -b)
+    assert max_rel_err(neg, -got.astype(np.float64), floor=0.1) <= TOL_F32

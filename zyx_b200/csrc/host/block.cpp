@@ -287,9 +287,11 @@ int32_t zyxb_block_io(zyxb_block* K, uint32_t* out_x, uint32_t* out_target, uint
 }
 
 int32_t zyxb_block_activation(zyxb_block* K, int32_t which, uint32_t* out_buf) {
-  if (!K || !out_buf || which < 0 || which > 2) return ZYXB_ERR_INCORRECT_KERNEL_ARG;
+  if (!K || !out_buf || which < 0 || which > 20) return ZYXB_ERR_INCORRECT_KERNEL_ARG;
   if (which == 0 && K->fused) return ZYXB_ERR_INCORRECT_KERNEL_ARG;   // the probabilities are never materialised
-  *out_buf = which == 0 ? K->p : which == 1 ? K->attn : K->x1;
+  const uint32_t table[21] = {K->p, K->attn, K->x1, K->q, K->k, K->v, K->o, K->s1, K->z1, K->h, K->m, K->s2,
+                              K->dy, K->ds2, K->dz1, K->dx1, K->ds1, K->dattn, K->dq, K->dk, K->dv};
+  *out_buf = table[which];
   return ZYXB_OK;
 }
 

@@ -438,6 +438,21 @@ int32_t zyxb_mlp_io(zyxb_mlp* M, uint32_t* out_x, uint32_t* out_target, uint32_t
   return ZYXB_OK;
 }
 
+int32_t zyxb_mlp_activation(zyxb_mlp* M, int32_t which, int32_t layer, uint32_t* out_buf, uint64_t* out_numel) {
+  if (!M || !out_buf || layer < 0 || layer >= M->cfg.n_layers || which < 0 || which > 2) return ZYXB_ERR_INCORRECT_KERNEL_ARG;
+  const bool last = layer == M->cfg.n_layers - 1;
+  uint32_t b = 0;
+  switch (which) {
+    case 0: b = last ? M->y : M->act[layer]; break;
+    case 1: b = last ? 0 : M->preact[layer]; break;
+    default: b = last ? M->dy : M->dact[layer];
+  }
+  if (b == 0) { M->err = "mlp_activation: this plan does not store that tensor"; return ZYXB_ERR_INCORRECT_KERNEL_ARG; }
+  *out_buf = b;
+  if (out_numel) *out_numel = M->cfg.batch * M->cfg.dims[layer + 1];
+  return ZYXB_OK;
+}
+
 int32_t zyxb_mlp_forward_backward(zyxb_mlp* M) { return M ? run(M, M->forward_backward, nullptr, 0) : ZYXB_ERR_INCORRECT_KERNEL_ARG; }
 int32_t zyxb_mlp_update(zyxb_mlp* M) {
   if (!M) return ZYXB_ERR_INCORRECT_KERNEL_ARG;

@@ -27,6 +27,7 @@ HOST_SIGNATURES = {
     "zyxb_mlp_last_error": (C.c_char_p, [_P]),
     "zyxb_mlp_tensor": (C.c_int32, [_P, C.c_int32, C.c_int32, C.POINTER(C.c_uint32), C.POINTER(C.c_uint64)]),
     "zyxb_mlp_io": (C.c_int32, [_P] + [C.POINTER(C.c_uint32)] * 4),
+    "zyxb_mlp_activation": (C.c_int32, [_P, C.c_int32, C.c_int32, C.POINTER(C.c_uint32), C.POINTER(C.c_uint64)]),
     "zyxb_mlp_forward_backward": (C.c_int32, [_P]),
     "zyxb_mlp_update": (C.c_int32, [_P]),
     "zyxb_mlp_step": (C.c_int32, [_P, C.POINTER(L.Event), C.c_int32]),
@@ -55,6 +56,7 @@ def load():
 
 
 PARAM, GRAD, STATE0, STATE1 = range(4)
+ACT_OUT, ACT_PRE, ACT_GRAD = range(3)
 
 
 class Mlp:
@@ -114,6 +116,19 @@ class Mlp:
     def set_batch(self, x, target):
         p = self.sess.pool
         return [p.host_to_pool(np.ascontiguousarray(x), self.x), p.host_to_pool(np.ascontiguousarray(target), self.target)]
+
+    def activation(self, which, layer, rows=None):
+        """A tensor the plan keeps between forward and backward: which = ACT_OUT (the layer's output), ACT_PRE (its
+        pre-activation) or ACT_GRAD (the loss gradient w.r.t. the pre-activation), [batch, dims[layer+1]]; `rows` selects rows."""
+        buf, n = C.c_uint32(), C.c_uint64()
+        self._check(self.lib.zyxb_mlp_activation(self.h, which, layer, C.byref(buf), C.byref(n)))
+        cols = self.dims[layer + 1]
+        if rows is None:
+            return self.sess.pool.download(buf.value, (self.batch, cols), self.np_dtype)
+        out = np.empty((len(rows), cols), self.np_dtype)
+        for i, r in enumerate(rows):
+            self.sess.pool.pool_to_host(buf.value, out[i], src_offset=int(r) * cols * out.itemsize)
+        return out
 
     def forward_backward(self):
         self._check(self.lib.zyxb_mlp_forward_backward(self.h))
@@ -215,6 +230,8 @@ ST_SIGNATURES = {
     "zyxb_block_load": (C.c_int32, [_P, C.c_char_p, C.POINTER(C.c_int32)]),
 }
 HOST_SIGNATURES.update(ST_SIGNATURES)
+BLOCK_ACTIVATIONS = {name: i for i, name in enumerate(["p", "attn", "x1", "q", "k", "v", "o", "s1", "z1", "h", "m", "s2", "dy", "ds2", "dz1", "dx1",
+                                                        "ds1", "dattn", "dq", "dk", "dv"])}
 BLOCK_PARAM_NAMES = ["wq", "bq", "wk", "bk", "wv", "bv", "wo", "bo", "w1", "b1", "w2", "b2", "g1", "be1", "g2", "be2"]
 
 
@@ -269,8 +286,9 @@ class Block:
         return [p.host_to_pool(np.ascontiguousarray(x), self.x), p.host_to_pool(np.ascontiguousarray(target), self.target)]
 
     def activation(self, which, shape):
+        """which: an index or a name of BLOCK_ACTIVATIONS."""
         buf = C.c_uint32()
-        self._check(self.lib.zyxb_block_activation(self.h, which, C.byref(buf)))
+        self._check(self.lib.zyxb_block_activation(self.h, BLOCK_ACTIVATIONS.get(which, which), C.byref(buf)))
         return self.sess.pool.download(buf.value, shape, self.np_dtype)
 
     def forward_backward(self):
