@@ -156,6 +156,46 @@ int32_t zyxb_mlp_load(zyxb_mlp* mlp, const char* path, int32_t* out_missing);
 int32_t zyxb_block_save(zyxb_block* blk, const char* path);
 int32_t zyxb_block_load(zyxb_block* blk, const char* path, int32_t* out_missing);
 
+/* ---- e-graph matcher: subgraph -> kernel descriptor ---------------------------------------------------------------
+ * The device's `match_graph` hook (zyx/src/backend/mod.rs:952-961; the reference's model is CblasDevice::match_graph,
+ * backend/cblas.rs:213-238, over Graph::match_matmul, vendor/matmul.rs:43-71) written over a mirror of zyx's graph, so that
+ * it can be built and tested without a Rust toolchain.  A node constructor returns the id of the class that holds the node
+ * (identical nodes share a class, as in the e-graph); 0xffffffff reports a bad argument.  Shapes are constants (symbolic
+ * dimensions never match in the reference either).  dtype / uop / bop values are zyx's enum orders (dtype.rs:18-32,
+ * kernel/ops.rs:187-214, 222-262: uop Neg 0, BitNot 1, Exp 2, Exp2 3, Ln 4, Log2 5, Reciprocal 6, Sqrt 7, ...; bop Add 0, Sub 1,
+ * Mul 2, Div 3, Pow 4, Mod 5, Cmplt 6, Cmpgt 7, Cmpge 8, Max 9, ..., NotEq 17, Eq 18). */
+typedef struct zyxb_mgraph zyxb_mgraph;
+int32_t  zyxb_mgraph_create(zyxb_mgraph** out);
+int32_t  zyxb_mgraph_destroy(zyxb_mgraph* g);
+uint32_t zyxb_mgraph_const(zyxb_mgraph* g, int32_t dtype, double value);                                  /* Node::Const */
+uint32_t zyxb_mgraph_leaf(zyxb_mgraph* g, int32_t dtype, uint32_t leaf_id, const uint64_t* shape, int32_t rank);   /* Node::Leaf */
+uint32_t zyxb_mgraph_expand(zyxb_mgraph* g, uint32_t x, const uint64_t* shape, int32_t rank);             /* Node::Expand */
+uint32_t zyxb_mgraph_reshape(zyxb_mgraph* g, uint32_t x, const uint64_t* shape, int32_t rank);            /* Node::Reshape */
+uint32_t zyxb_mgraph_permute(zyxb_mgraph* g, uint32_t x, const int32_t* axes, int32_t rank);              /* Node::Permute */
+uint32_t zyxb_mgraph_reduce(zyxb_mgraph* g, uint32_t x, int32_t rop, const int32_t* axes, int32_t n_axes); /* Node::Reduce */
+uint32_t zyxb_mgraph_cast(zyxb_mgraph* g, uint32_t x, int32_t dtype);                                     /* Node::Cast */
+uint32_t zyxb_mgraph_unary(zyxb_mgraph* g, uint32_t x, int32_t uop);                                      /* Node::Unary */
+uint32_t zyxb_mgraph_binary(zyxb_mgraph* g, uint32_t x, uint32_t y, int32_t bop);                         /* Node::Binary */
+/* dtype, rank, shape (up to 8 extents) of a class and how many Node::Kernel alternatives match_graph has pushed into it */
+int32_t  zyxb_mgraph_class_info(zyxb_mgraph* g, uint32_t cls, int32_t* out_dtype, int32_t* out_rank, uint64_t* out_shape8, int32_t* out_kernel_nodes);
+
+/* One recognised subgraph: what to hand to zyxb_program_create, and the classes whose buffers are the launch arguments
+ * (inputs then outputs, the order Device::launch receives, backend/mod.rs:974).  Patterns: matmul_nn / matmul_nt
+ * [_batched][_bias[_relu|_gelu]], softmax, ln_softmax, layernorm, sum, max, mean, sgd, adamw, adamw_first_step.  An optimizer
+ * match covers every parameter of the update (inputs p.., g.. [, m.., v..]; outputs p', m', v' per tensor - the kernel updates
+ * in place, so the shim binds each output to its input's buffer); its desc.u.optim.numel points into the graph mirror. */
+typedef struct {
+  char     pattern[32];
+  int32_t  n_inputs, n_outputs;
+  uint32_t inputs[128], outputs[96];
+  zyxb_kernel_desc desc;
+} zyxb_match;
+/* match_graph over every class the `outputs` depend on.  Classes in `outputs` are the ones other consumers read: a new
+ * parameter value is only matched as an optimizer update when it is one of them, and a GELU layer's pre-activation listed
+ * there becomes the matmul program's second output.  Each match is also pushed into its output classes as a Node::Kernel
+ * alternative (graph/mod.rs:177-182).  Returns the number of matches in *out_n (may exceed capacity). */
+int32_t  zyxb_mgraph_match(zyxb_mgraph* g, const uint32_t* outputs, int32_t n_outputs, zyxb_match* out, int32_t capacity, int32_t* out_n);
+
 #ifdef __cplusplus
 }
 #endif

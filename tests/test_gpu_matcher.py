@@ -1,0 +1,91 @@
+"""From a traced graph to a launch: the matcher's descriptor goes to zyxb_program_create as it is, the matched input and
+output classes name the buffers (loads first, then stores, as Device::launch receives them), and the result is the oracle's.
+This is the path a `Node::Kernel` pushed by match_graph takes when the plan is executed (zyx/src/backend/cblas.rs:213-271)."""
+import numpy as np
+import pytest
+
+from oracle import oracle as zo
+from tests.parity import TOL_BF16, TOL_F32, max_rel_err
+from tests.zyx_trace import LayerNorm, Linear, T, sgd_update
+from zyx_b200 import _lib as L
+from zyx_b200.matcher import MGraph
+
+pytestmark = pytest.mark.gpu
+NP = {L.F32: np.float32, L.BF16: np.uint16, L.F16: np.uint16}
+
+
+def run_match(sess, g, match, values):
+    """values: class id -> host array for every input class.  -> {output class: host array}"""
+    prog = sess.device.create_program(match.desc)
+    ins = [sess.pool.upload(values[c]) for c in match.inputs[:match.n_inputs]]
+    outs, specs = [], []
+    for c in match.outputs[:match.n_outputs]:
+        dt, shape, _ = g.info(c)
+        specs.append((shape, NP[dt]))
+        outs.append(sess.pool.allocate(int(np.prod(shape)) * np.dtype(NP[dt]).itemsize)[0])
+    try:
+        sess.device.launch(prog, ins + outs)
+        return {c: sess.pool.download(b, s, t) for c, b, (s, t) in zip(match.outputs[:match.n_outputs], outs, specs)}
+    finally:
+        for b in ins + outs:
+            sess.pool.deallocate(b)
+        sess.device.release(prog)
+
+
+def pick(matches, pattern, out_cls):
+    return next(m for m in matches if m.pattern == pattern and m.outputs[0] == out_cls)
+
+
+@pytest.mark.parametrize("dtype,tol", [(L.F32, TOL_F32), (L.BF16, TOL_BF16)])
+def test_linear_gelu_layer_from_graph_to_launch(sess, dtype, tol):
+    rng = np.random.default_rng(31)
+    g = MGraph()
+    try:
+        lin = Linear(g, dtype, 320, 264)
+        x = T.leaf(g, dtype, (200, 320))
+        z = lin.forward(x)
+        h = z.gelu()
+        m = pick(g.match([h.cls, z.cls]), b"matmul_nt_bias_gelu", h.cls)
+        bits = lambda a: zo.to_bits(a.astype(np.float32), dtype)
+        vals = {x.cls: bits(rng.standard_normal((200, 320))), lin.weight.cls: bits(rng.uniform(-0.05, 0.05, (264, 320))),
+                lin.bias.cls: bits(rng.uniform(-0.05, 0.05, 264))}
+        got = run_match(sess, g, m, vals)
+        want_h, want_z = zo.gemm(dtype, vals[x.cls], vals[lin.weight.cls], tb=True, bias=vals[lin.bias.cls], epi=zo.EPI_BIAS_GELU, want_preact=True)
+        f = lambda a: zo.to_f32(a, dtype)
+        assert max_rel_err(f(got[h.cls]), f(want_h), floor=0.1) <= tol
+        assert max_rel_err(f(got[z.cls]), f(want_z), floor=0.1) <= tol
+    finally:
+        g.close()
+
+
+def test_softmax_layernorm_and_sgd_from_graph_to_launch(sess):
+    rng = np.random.default_rng(32)
+    g = MGraph()
+    try:
+        x = T.leaf(g, L.F32, (96, 4096))
+        ln = LayerNorm(g, L.F32, 4096, eps=1e-5)
+        y_sm, y_ln = x.softmax(), ln.forward(x)
+        p, gr = T.leaf(g, L.F32, (50, 30)), T.leaf(g, L.F32, (50, 30))
+        new_p = sgd_update([p], [gr], 0.01)[0]
+        ms = g.match([y_sm.cls, y_ln.cls, new_p.cls])
+        xv = rng.standard_normal((96, 4096)).astype(np.float32)
+        wv, bv = (1 + 0.1 * rng.standard_normal(4096)).astype(np.float32), (0.1 * rng.standard_normal(4096)).astype(np.float32)
+        got = run_match(sess, g, pick(ms, b"softmax", y_sm.cls), {x.cls: xv})[y_sm.cls]
+        assert max_rel_err(got, zo.softmax(zo.F32, xv)) <= TOL_F32
+        got = run_match(sess, g, pick(ms, b"layernorm", y_ln.cls), {x.cls: xv, ln.weight.cls: wv, ln.bias.cls: bv})[y_ln.cls]
+        assert max_rel_err(got, zo.layernorm(zo.F32, xv, wv, bv, 1e-5)) <= TOL_F32
+        # the optimizer kernel updates in place: the shim binds the output class to the parameter's buffer
+        m = pick(ms, b"sgd", new_p.cls)
+        pv, gv = rng.standard_normal((50, 30)).astype(np.float32), rng.standard_normal((50, 30)).astype(np.float32)
+        prog = sess.device.create_program(m.desc)
+        bp, bg = sess.pool.upload(pv), sess.pool.upload(gv)
+        try:
+            sess.device.launch(prog, [bp, bg])
+            got = sess.pool.download(bp, pv.shape, np.float32)
+        finally:
+            sess.pool.deallocate(bp); sess.pool.deallocate(bg); sess.device.release(prog)
+        want = pv.copy()
+        zo.sgd(zo.F32, want, gv, None, lr=0.01)
+        assert max_rel_err(got, want) <= TOL_F32
+    finally:
+        g.close()

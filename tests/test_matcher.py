@@ -1,0 +1,232 @@
+"""The e-graph matcher (zyx_b200/csrc/host/matcher.hpp through the C ABI of include/zyxb_host.h) on node lists transcribed from
+the reference's Tensor::dot, Linear::forward, softmax, ln_softmax, LayerNorm::forward, SGD::update and AdamW::update
+(tests/zyx_trace.py): the emitted descriptor must equal the hand-written one the training plans create for the same layer, and
+the launch arguments must be the stored tensors (loads first, then stores).  CPU only; the GPU run of a matched descriptor is in
+tests/test_gpu_matcher.py."""
+import math
+
+import pytest
+
+from tests.zyx_trace import LayerNorm, Linear, T, adamw_update, sgd_update
+from zyx_b200 import _lib as L
+from zyx_b200 import backend as B
+from zyx_b200.matcher import MGraph
+
+
+def fields(struct):
+    out = {}
+    for name, _ in struct._fields_:
+        v = getattr(struct, name)
+        out[name] = v if isinstance(v, (int, float)) else None
+    return out
+
+
+def assert_same_gemm(got, want):
+    a, b = fields(got.u.gemm), fields(want.u.gemm)
+    for d in (a, b):
+        d["alpha"] = d["alpha"] or 1.0
+    assert got.kind == want.kind == L.KIND_GEMM and a == b, (a, b)
+
+
+def assert_same_row(got, want):
+    a, b = fields(got.u.rowreduce), fields(want.u.rowreduce)
+    assert abs(a.pop("eps") - b.pop("eps")) <= 1e-12
+    assert got.kind == want.kind == L.KIND_ROWREDUCE and a == b, (a, b)
+
+
+@pytest.fixture()
+def g():
+    graph = MGraph()
+    yield graph
+    graph.close()
+
+
+def by_pattern(matches):
+    """pattern -> the last match of that pattern in topological order.  Tensor::dot closes with a reshape to the shape the
+    reduce already has, so a matmul is matched at two classes (the Reduce's, as the reference does, and the reshape's, which
+    is what the users of the result read); the later one is the reshape's."""
+    return {m.pattern.decode(): m for m in matches}
+
+
+@pytest.mark.parametrize("dtype", [L.F32, L.BF16, L.F16, L.I32])
+def test_plain_matmul_is_the_reference_pattern(g, dtype):
+    """Tensor::dot of two stored matrices: the NN form Graph::match_matmul recognises (vendor/matmul.rs:43-71)."""
+    a, b = T.leaf(g, dtype, (96, 40)), T.leaf(g, dtype, (40, 72))
+    out = a.dot(b)
+    ms = g.match([out.cls])
+    assert [m.pattern for m in ms] == [b"matmul_nn", b"matmul_nn"]      # at the Reduce's class and at the closing reshape's
+    m = ms[1]
+    assert_same_gemm(m.desc, B.gemm_desc(dtype, 96, 72, 40))
+    assert list(m.inputs[:m.n_inputs]) == [a.cls, b.cls] and list(m.outputs[:m.n_outputs]) == [out.cls]
+    assert g.info(out.cls)[2] == 1                      # a Node::Kernel alternative now sits in the output class
+
+
+def test_linear_forward_is_nt_on_the_stored_weight(g):
+    """x.dot(W.t()) + b (zyx-nn/src/linear.rs:39-45): b of the matmul is the leaf W with trans_b, not the class W.t();
+    the descriptor equals the one the Linear-stack plan creates for a last layer (bias epilogue)."""
+    lin = Linear(g, L.BF16, 4096, 16384)
+    x = T.leaf(g, L.BF16, (8192, 4096))
+    y = lin.forward(x)
+    m = by_pattern(g.match([y.cls]))
+    assert set(m) == {"matmul_nt", "matmul_nt_bias"}   # the product alone is an alternative too; extraction picks
+    mt = m["matmul_nt_bias"]
+    assert_same_gemm(mt.desc, B.gemm_desc(L.BF16, 8192, 16384, 4096, trans_b=True, epilogue=L.EPI_BIAS))
+    assert list(mt.inputs[:mt.n_inputs]) == [x.cls, lin.weight.cls, lin.bias.cls]
+    assert list(mt.outputs[:mt.n_outputs]) == [y.cls]
+
+
+@pytest.mark.parametrize("dtype,act", [(L.F32, "relu"), (L.BF16, "gelu"), (L.F16, "gelu")])
+def test_linear_with_activation_and_the_stored_preactivation(g, dtype, act):
+    """Hidden layers of the configurations: bias + ReLU (SimpleNet) and bias + GELU storing the pre-activation the backward
+    pass reads (config 4) - exactly the forward descriptors of host/trainer.cpp."""
+    lin = Linear(g, dtype, 784, 128)
+    x = T.leaf(g, dtype, (64, 784))
+    z = lin.forward(x)
+    h = z.relu() if act == "relu" else z.gelu()
+    m = by_pattern(g.match([h.cls, z.cls]))            # z is wanted too (the backward reads it)
+    key = "matmul_nt_bias_" + act
+    assert key in m, sorted(m)
+    mt = m[key]
+    epi = L.EPI_BIAS_RELU if act == "relu" else L.EPI_BIAS_GELU
+    assert_same_gemm(mt.desc, B.gemm_desc(dtype, 64, 128, 784, trans_b=True, epilogue=epi, store_preact=act == "gelu"))
+    assert list(mt.inputs[:mt.n_inputs]) == [x.cls, lin.weight.cls, lin.bias.cls]
+    assert list(mt.outputs[:mt.n_outputs]) == ([h.cls, z.cls] if act == "gelu" else [h.cls])
+    # without z among the outputs nothing else reads the pre-activation: one output
+    g2 = MGraph()
+    try:
+        lin2, x2 = Linear(g2, dtype, 784, 128), T.leaf(g2, dtype, (64, 784))
+        h2 = lin2.forward(x2).gelu()
+        mt2 = by_pattern(g2.match([h2.cls]))["matmul_nt_bias_gelu"]
+        assert mt2.desc.u.gemm.store_preact == 0 and mt2.n_outputs == 1
+    finally:
+        g2.close()
+
+
+def test_batched_matmul_shared_and_per_batch_operands_and_scale(g):
+    """Rank > 2 (attention's per-head products as [B*H, T, D] tensors): batch strides; a shared right operand has stride 0;
+    `* 1/sqrt(d)` after the product (multi_head_attention.rs:198-199) becomes alpha."""
+    q, k = T.leaf(g, L.BF16, (12, 256, 64)), T.leaf(g, L.BF16, (12, 256, 64))
+    s = q.dot(k.t()) * (1.0 / math.sqrt(64.0))
+    m = by_pattern(g.match([s.cls]))
+    mt = m["matmul_nt_batched"]
+    assert mt.outputs[0] == s.cls
+    assert g.match([s.cls]) == []                         # a second pass: the classes already hold kernels, nothing new
+    want = B.gemm_desc(L.BF16, 256, 256, 64, batch=12, trans_b=True, alpha=1.0 / math.sqrt(64.0))
+    a, b = fields(mt.desc.u.gemm), fields(want.u.gemm)
+    assert abs(a.pop("alpha") - b.pop("alpha")) <= 1e-3 * b.get("alpha", 1) + 1e-3 and a == b
+    assert list(mt.inputs[:2]) == [q.cls, k.cls]
+    g3 = MGraph()
+    try:
+        a3, w3 = T.leaf(g3, L.F32, (6, 40, 24)), T.leaf(g3, L.F32, (24, 56))
+        o3 = a3.dot(w3)
+        m3 = g3.match([o3.cls])[-1]
+        assert m3.pattern == b"matmul_nn_batched" and m3.outputs[0] == o3.cls
+        assert_same_gemm(m3.desc, B.gemm_desc(L.F32, 40, 56, 24, batch=6, stride_b=0))
+    finally:
+        g3.close()
+
+
+@pytest.mark.parametrize("dtype", [L.F32, L.BF16])
+def test_softmax_and_ln_softmax(g, dtype):
+    x = T.leaf(g, dtype, (8192, 32768))
+    y, z = x.softmax(), x.ln_softmax()
+    m = by_pattern(g.match([y.cls, z.cls]))
+    assert_same_row(m["softmax"].desc, B.rowreduce_desc(L.RR_SOFTMAX, dtype, 8192, 32768))
+    assert_same_row(m["ln_softmax"].desc, B.rowreduce_desc(L.RR_LN_SOFTMAX, dtype, 8192, 32768))
+    for key, out in (("softmax", y), ("ln_softmax", z)):
+        assert list(m[key].inputs[:m[key].n_inputs]) == [x.cls] and m[key].outputs[0] == out.cls
+    # a rank-3 input: rows are every leading extent
+    x3 = T.leaf(g, dtype, (4, 16, 128))
+    m3 = by_pattern(g.match([x3.softmax().cls]))
+    assert_same_row(m3["softmax"].desc, B.rowreduce_desc(L.RR_SOFTMAX, dtype, 64, 128))
+
+
+@pytest.mark.parametrize("dtype", [L.F32, L.BF16])
+@pytest.mark.parametrize("weight,bias", [(True, True), (True, False), (False, False)])
+def test_layernorm(g, dtype, weight, bias):
+    """LayerNorm::forward (zyx-nn/src/layer_norm.rs:95-135): two means, the unbiased variance (divisor n - 1), eps, affine."""
+    ln = LayerNorm(g, dtype, 32768, eps=1e-5, weight=weight, bias=bias)
+    x = T.leaf(g, dtype, (8192, 32768))
+    y = ln.forward(x)
+    m = by_pattern(g.match([y.cls]))
+    assert "layernorm" in m, sorted(m)
+    mt = m["layernorm"]
+    assert_same_row(mt.desc, B.rowreduce_desc(L.RR_LAYERNORM, dtype, 8192, 32768, eps=1e-5, has_weight=weight, has_bias=bias))
+    want_in = [x.cls] + ([ln.weight.cls] if weight else []) + ([ln.bias.cls] if bias else [])
+    assert list(mt.inputs[:mt.n_inputs]) == want_in and mt.outputs[0] == y.cls
+
+
+def test_plain_reductions(g):
+    x = T.leaf(g, L.F32, (100, 333))
+    s, mx, mean = x.sum([-1]), x.max([-1]), x.mean([-1])
+    m = by_pattern(g.match([s.cls, mx.cls, mean.cls]))
+    assert_same_row(m["sum"].desc, B.rowreduce_desc(L.RR_SUM, L.F32, 100, 333))
+    assert_same_row(m["max"].desc, B.rowreduce_desc(L.RR_MAX, L.F32, 100, 333))
+    assert_same_row(m["mean"].desc, B.rowreduce_desc(L.RR_MEAN, L.F32, 100, 333))
+
+
+def test_sgd_update_of_simplenet_is_one_multi_tensor_program(g):
+    shapes = [(128, 784), (128,), (10, 128), (10,)]
+    params = [T.leaf(g, L.F32, s) for s in shapes]
+    grads = [T.leaf(g, L.F32, s) for s in shapes]
+    new = sgd_update(params, grads, 0.01)
+    ms = g.match([t.cls for t in new])
+    assert [m.pattern for m in ms] == [b"sgd"]
+    o = ms[0].desc.u.optim
+    assert (ms[0].desc.kind, o.algo, o.dtype, o.n_tensors) == (L.KIND_OPTIM, L.OPT_SGD, L.F32, 4)
+    assert [o.numel[i] for i in range(4)] == [100352, 128, 1280, 10] and abs(o.lr - 0.01) < 1e-9 and o.momentum == 0 and o.weight_decay == 0
+    assert list(ms[0].inputs[:8]) == [t.cls for t in params] + [t.cls for t in grads]
+    assert list(ms[0].outputs[:4]) == [t.cls for t in new]
+
+
+@pytest.mark.parametrize("dtype", [L.F32, L.BF16])
+@pytest.mark.parametrize("step", [1, 7])
+def test_adamw_update_is_one_multi_tensor_program(g, dtype, step):
+    """AdamW::update (zyx-optim/src/adamw.rs:51-97): hyper-parameters are read back from the graph's constants; on the first
+    step the moment buffers do not exist yet (adamw.rs:60-71), so they are outputs only."""
+    shapes = [(16384, 4096), (16384,), (4096, 16384), (4096,)]
+    params = [T.leaf(g, dtype, s) for s in shapes]
+    grads = [T.leaf(g, dtype, s) for s in shapes]
+    m = [T.leaf(g, dtype, s) for s in shapes] if step > 1 else None
+    v = [T.leaf(g, dtype, s) for s in shapes] if step > 1 else None
+    new_p, new_m, new_v = adamw_update(params, grads, m, v, step, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01)
+    ms = g.match([t.cls for t in new_p + new_m + new_v])
+    assert [x.pattern for x in ms] == [b"adamw" if step > 1 else b"adamw_first_step"]
+    mt = ms[0]
+    o = mt.desc.u.optim
+    assert (o.algo, o.dtype, o.n_tensors) == (L.OPT_ADAMW, dtype, 4)
+    assert [o.numel[i] for i in range(4)] == [16384 * 4096, 16384, 4096 * 16384, 4096]
+    assert abs(o.lr - 1e-3) < 1e-9 and abs(o.weight_decay - 0.01) < 1e-6 and abs(o.beta1 - 0.9) < 1e-6 and abs(o.beta2 - 0.999) < 1e-6
+    assert abs(o.eps - 1e-8) < 1e-12 and o.standard == 0
+    want_in = [t.cls for t in params] + [t.cls for t in grads] + ([t.cls for t in m] + [t.cls for t in v] if step > 1 else [])
+    assert list(mt.inputs[:mt.n_inputs]) == want_in
+    want_out = [c for trio in zip(new_p, new_m, new_v) for c in (trio[0].cls, trio[1].cls, trio[2].cls)]
+    assert list(mt.outputs[:mt.n_outputs]) == want_out
+
+
+def test_what_is_not_a_pattern_is_left_alone(g):
+    a, b = T.leaf(g, L.F32, (32, 16)), T.leaf(g, L.F32, (32, 16))
+    c = (a * b + a).exp()                       # an elementwise chain: no descriptor covers it
+    wrong_k = T.leaf(g, L.F32, (8, 5)).reshape((8, 1, 5)).expand((8, 3, 5)) * T.leaf(g, L.F32, (3, 5)).reshape((1, 3, 5)).expand((8, 3, 5))
+    d = wrong_k.sum([-1])                       # product and sum, but the right operand is not a transposed [k, n] tensor
+    assert g.match([c.cls, d.cls]) == []
+    # a bf16 tensor cast to f32 by the user and summed: the f32 row sum reads the *cast* class (somebody else has to produce
+    # it), never the bf16 leaf - the 16-bit kernel would round the result
+    leaf = T.leaf(g, L.BF16, (8, 4))
+    wide = leaf.cast(L.F32)
+    ms = g.match([wide.sum([-1]).cls])
+    assert [m.pattern for m in ms] == [b"sum"] and ms[0].desc.u.rowreduce.dtype == L.F32 and ms[0].inputs[0] == wide.cls != leaf.cls
+
+
+def test_constructor_arguments_are_validated(g):
+    x = g.leaf(L.F32, (4, 5))
+    with pytest.raises(ValueError):
+        g.reshape(x, (3, 7))
+    with pytest.raises(ValueError):
+        g.expand(x, (4, 6))
+    with pytest.raises(ValueError):
+        g.permute(x, (0, 0))
+    with pytest.raises(ValueError):
+        g.binary(x, g.leaf(L.F32, (5, 4)), 0)
+    with pytest.raises(ValueError):
+        g.reduce(x, 0, (2,))

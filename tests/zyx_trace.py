@@ -1,0 +1,218 @@
+"""A tracer that records, into the matcher's mirror graph, the nodes the reference's Tensor methods push in graph mode.
+TEST INFRASTRUCTURE: each method restates the decomposition of the reference method it is named after.
+
+    binary ops     Tensor::broadcast (zyx/src/tensor/mod.rs:3033-3113): a rank-0 operand is cast to the other's dtype, both are
+                   expanded to the common shape, then one Binary node
+    reductions     Tensor::reduce_impl (tensor/reduce_ops.rs:45-157): cast to the accumulator dtype (f32 for floats), Reduce,
+                   cast back when the dtype changed, reshape for keepdim; Mean = sum / const(n).cast(dtype); Var with correction 1
+    dot            tensor/mod.rs:1469-1490;  softmax / ln_softmax 1427-1461;  relu / gelu / tanh / exp / sqrt elementwise.rs
+    Linear         zyx-nn/src/linear.rs:39-45;  LayerNorm zyx-nn/src/layer_norm.rs:95-135
+    SGD / AdamW    zyx-optim/src/sgd.rs:45-84, adamw.rs:51-97
+Every `.cast(dtype)` pushes a Cast node, also when the dtype does not change (zyx/src/runtime.rs:696-700)."""
+import math
+
+from zyx_b200 import _lib as L
+from zyx_b200 import matcher as M
+
+
+class T:
+    def __init__(self, g, cls):
+        self.g, self.cls = g, cls
+
+    # ---- introspection
+    @property
+    def dtype(self):
+        return self.g.info(self.cls)[0]
+
+    @property
+    def shape(self):
+        return self.g.info(self.cls)[1]
+
+    # ---- constructors
+    @staticmethod
+    def leaf(g, dtype, shape):
+        return T(g, g.leaf(dtype, shape))
+
+    @staticmethod
+    def scalar(g, value, dtype=L.F32):
+        return T(g, g.const(dtype, value))
+
+    # ---- movement / dtype
+    def cast(self, dtype):
+        return T(self.g, self.g.cast(self.cls, dtype))
+
+    def reshape(self, shape):
+        return T(self.g, self.g.reshape(self.cls, list(shape)))
+
+    def expand(self, shape):
+        return T(self.g, self.g.expand(self.cls, list(shape)))
+
+    def permute(self, axes):
+        if list(axes) == list(range(len(axes))):
+            return self                                   # runtime.rs:1134-1137: the identity permutation returns the tensor itself
+        return T(self.g, self.g.permute(self.cls, list(axes)))
+
+    def t(self):
+        r = len(self.shape)
+        axes = list(range(r))
+        axes[-1], axes[-2] = axes[-2], axes[-1]
+        return self.permute(axes)
+
+    # ---- binary with broadcasting
+    def _lift(self, other):
+        return other if isinstance(other, T) else T.scalar(self.g, other)
+
+    def _binary(self, other, bop):
+        x, y = self, self._lift(other)
+        xd, yd, xs, ys = x.dtype, y.dtype, x.shape, y.shape
+        if xd != yd:
+            if len(xs) == 0 and len(ys) != 0:
+                x = x.cast(yd)
+            elif len(ys) == 0 and len(xs) != 0:
+                y = y.cast(xd)
+            else:
+                common = L.F32 if L.F32 in (xd, yd) else xd          # least_upper_dtype for the cases the tests use
+                if xd == L.BOOL:
+                    common = yd
+                if yd == L.BOOL:
+                    common = xd
+                x = x.cast(common) if xd != common else x
+                y = y.cast(common) if yd != common else y
+        rx, ry = len(xs), len(ys)
+        nx, ny = (1,) * max(ry - rx, 0) + tuple(xs), (1,) * max(rx - ry, 0) + tuple(ys)
+        eshape = tuple(max(a, b) for a, b in zip(nx, ny))
+        if tuple(xs) != eshape:
+            x = x.expand(eshape)
+        if tuple(ys) != eshape:
+            y = y.expand(eshape)
+        return T(self.g, self.g.binary(x.cls, y.cls, bop))
+
+    def __add__(self, o): return self._binary(o, M.B_ADD)
+    def __sub__(self, o): return self._binary(o, M.B_SUB)
+    def __mul__(self, o): return self._binary(o, M.B_MUL)
+    def __truediv__(self, o): return self._binary(o, M.B_DIV)
+    def cmpgt(self, o): return self._binary(o, M.B_CMPGT)
+
+    # ---- unary
+    def _unary(self, uop):
+        return T(self.g, self.g.unary(self.cls, uop))
+
+    def exp(self): return self._unary(M.U_EXP)
+    def ln(self): return self._unary(M.U_LN)
+    def sqrt(self): return self._unary(M.U_SQRT)
+
+    def relu(self):
+        return self.cmpgt(0.0) * self
+
+    def tanh(self):
+        e = (self + self).exp()
+        return (e - 1) / (e + 1)
+
+    def gelu(self):
+        return self * 0.5 * (((self + self * self * self * 0.044715) * math.sqrt(2.0 / math.pi)).tanh() + 1.0)
+
+    # ---- reductions (reduce_impl)
+    def _reduce(self, rop, axes, keepdim):
+        shape = list(self.shape)
+        axes = [a % len(shape) for a in axes]
+        xd = self.dtype
+        acc = L.F32 if xd in (L.F32, L.BF16, L.F16) else L.I32
+        t = T(self.g, self.g.reduce(self.cast(acc).cls, rop, axes))
+        if t.dtype != xd:
+            t = t.cast(xd)
+        if keepdim:
+            for a in axes:
+                shape[a] = 1
+            t = t.reshape(shape)
+        return t
+
+    def sum(self, axes, keepdim=False): return self._reduce(M.B_ADD, axes, keepdim)
+    def max(self, axes, keepdim=False): return self._reduce(M.B_MAX, axes, keepdim)
+
+    def mean(self, axes, keepdim=False):
+        shape = list(self.shape)
+        n = 1
+        for a in axes:
+            n *= shape[a % len(shape)]
+        t = self.sum(axes) / T.scalar(self.g, n, L.I64).cast(self.dtype)
+        if keepdim:
+            for a in axes:
+                shape[a % len(shape)] = 1
+            t = t.reshape(shape)
+        return t
+
+    def var(self, axes, keepdim=False, correction=1):
+        shape = list(self.shape)
+        n = 1
+        for a in axes:
+            n *= shape[a % len(shape)]
+        x = self - self.mean(axes, keepdim=True)
+        t = (x * x).sum(axes) / T.scalar(self.g, n - correction, L.I64).cast(self.dtype)
+        if keepdim:
+            for a in axes:
+                shape[a % len(shape)] = 1
+            t = t.reshape(shape)
+        return t
+
+    def softmax(self, axes=(-1,)):
+        e = (self - self.max(list(axes), keepdim=True)).exp()
+        return e / e.sum(list(axes), keepdim=True)
+
+    def ln_softmax(self, axes=(-1,)):
+        m = self - self.max(list(axes), keepdim=True)
+        return m - m.exp().sum(list(axes), keepdim=True).ln()
+
+    def dot(self, rhs):
+        y = rhs.t()
+        xs, ys = self.shape, y.shape
+        assert xs[-1] == ys[-1]
+        x_shape = list(xs[:-1]) + [1, xs[-1]]
+        y_shape = list(ys[:-2]) + [1] + list(ys[-2:])
+        out_shape = list(xs[:-1]) + [ys[-2]]
+        return (self.reshape(x_shape) * y.reshape(y_shape)).sum([-1]).reshape(out_shape)
+
+
+class Linear:
+    def __init__(self, g, dtype, in_f, out_f, bias=True):
+        self.weight = T.leaf(g, dtype, (out_f, in_f))
+        self.bias = T.leaf(g, dtype, (out_f,)) if bias else None
+
+    def forward(self, x):
+        y = x.dot(self.weight.t())
+        return y + self.bias if self.bias is not None else y
+
+
+class LayerNorm:
+    def __init__(self, g, dtype, n, eps=1e-5, weight=True, bias=True):
+        self.eps = eps
+        self.weight = T.leaf(g, dtype, (n,)) if weight else None
+        self.bias = T.leaf(g, dtype, (n,)) if bias else None
+
+    def forward(self, x):
+        mean = x.mean([-1], keepdim=True)
+        var = x.var([-1], keepdim=True)
+        out = (x - mean) / (var + T.scalar(x.g, self.eps, L.F64)).sqrt()
+        if self.weight is not None:
+            out = out * self.weight
+        if self.bias is not None:
+            out = out + self.bias
+        return out
+
+
+def sgd_update(params, grads, lr):
+    return [(p - g * lr).cast(p.dtype) for p, g in zip(params, grads)]
+
+
+def adamw_update(params, grads, m, v, t, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01):
+    """-> (new params, new m, new v); m / v are None on the first step."""
+    new_p, new_m, new_v = [], [], []
+    for i, (p, g) in enumerate(zip(params, grads)):
+        mi = m[i] * betas[0] + g * (1.0 - betas[0]) if m is not None else g * (1.0 - betas[0])
+        vi = v[i] * betas[1] + g * g * (1.0 - betas[1]) if v is not None else g * g * (1.0 - betas[1])
+        mh = mi / (1.0 - betas[0] ** t)
+        vh = vi / (1.0 - betas[1] ** t)
+        q = (p - mh / ((vh.sqrt() + eps) * lr)).cast(p.dtype)
+        if weight_decay != 0.0:
+            q = q * (1.0 - lr * weight_decay)
+        new_p.append(q); new_m.append(mi); new_v.append(vi)
+    return new_p, new_m, new_v

@@ -68,7 +68,7 @@ def build(force=False, verbose=False):
 def build_host(force=False):
     """libzyxb_host.so: the C++ host runtime (include/zyxb_host.h); it uses libzyxb.so only through its C ABI."""
     srcs = sorted(glob.glob(os.path.join(CSRC, "host", "*.cpp")))
-    newest = max([os.path.getmtime(s) for s in srcs] + [_newest_header()])
+    newest = max([os.path.getmtime(s) for s in srcs + glob.glob(os.path.join(CSRC, "host", "*.hpp"))] + [_newest_header()])
     if force or not os.path.exists(HOST_LIB) or os.path.getmtime(HOST_LIB) < newest:
         cmd = ["g++", "-shared", "-o", HOST_LIB] + CXX_FLAGS + srcs + ["-L", HERE, "-lzyxb", "-Wl,-rpath,$ORIGIN"]
         r = subprocess.run(cmd, capture_output=True, text=True)

@@ -1,0 +1,662 @@
+// Pattern matcher: zyx e-graph subgraphs -> kernel descriptors (the `match_graph` half of the backend boundary).
+//
+// zyx's graph op set is tiny (zyx/src/graph/mod.rs:100-182: Const, Leaf, Expand, Permute, Reshape, Reduce, Cast, Unary,
+// Binary, ..., Kernel), so whatever the user wrote collapses into a few canonical subgraphs (zyx/src/vendor/mod.rs:4-13).
+// The reference recognises one of them, the 2-D NN matmul (Graph::match_matmul, zyx/src/vendor/matmul.rs:43-71, helpers
+// vendor/mod.rs:28-95), and its consumer pushes a Node::Kernel into the matched class (backend/cblas.rs:213-238).  This file
+// is the same machinery over a mirror of that graph, extended to what an aot_only device must cover:
+//   matmul          NN as the reference; NT on a stored weight (`x.dot(W.t())` of Linear::forward, zyx-nn/src/linear.rs:39-45,
+//                   where the reference would hand the kernel the *class* W.t()); rank > 2 with batch strides; the accumulator
+//                   Casts that `sum` puts around the Reduce for 16-bit inputs (tensor/reduce_ops.rs:52-60,143-145); a
+//                   trailing `* const` (attention's 1/sqrt(d)) as alpha; `+ bias`, relu and gelu as epilogues
+//   row kernels     softmax, ln_softmax (tensor/mod.rs:1427-1461), LayerNorm::forward (zyx-nn/src/layer_norm.rs:95-135),
+//                   sum / max / mean over the last axis (tensor/reduce_ops.rs:45-157)
+//   optimizer       SGD::update (zyx-optim/src/sgd.rs:45-84, without momentum), AdamW::update (zyx-optim/src/adamw.rs:51-97,
+//                   first and later steps), all matched tensors of one update grouped into one multi-tensor program
+// A Rust port of this file is what `backend/b200.rs` carries; the mirror exists because the image has no Rust toolchain
+// and the matcher has to be testable on the CPU.  Symbolic (non-constant) shapes never match, as in the reference
+// (Graph::const_shape returns None).
+#pragma once
+#include <math.h>
+#include <stdint.h>
+#include <string.h>
+
+#include <algorithm>
+#include <map>
+#include <optional>
+#include <set>
+#include <string>
+#include <utility>
+#include <vector>
+
+#include "../../../include/zyxb.h"
+
+namespace zyxb_matcher {
+
+using ClassId = uint32_t;
+constexpr ClassId NONE = 0xffffffffu;
+
+enum Kind : int { K_CONST = 0, K_LEAF, K_EXPAND, K_PERMUTE, K_RESHAPE, K_REDUCE, K_CAST, K_UNARY, K_BINARY, K_KERNEL };
+// the order of zyx's enums (zyx/src/kernel/ops.rs:187-214 and 222-262)
+enum UOp : int { U_NEG = 0, U_BITNOT, U_EXP, U_EXP2, U_LN, U_LOG2, U_RECIPROCAL, U_SQRT, U_SIN, U_COS, U_FLOOR, U_TRUNC, U_ABS };
+enum BOp : int { B_ADD = 0, B_SUB, B_MUL, B_DIV, B_POW, B_MOD, B_CMPLT, B_CMPGT, B_CMPGE, B_MAX, B_OR, B_AND, B_BITXOR, B_BITOR, B_BITAND,
+                 B_SHL, B_SHR, B_NOTEQ, B_EQ };
+
+struct Node {
+  int kind = K_CONST;
+  ClassId x = NONE, y = NONE;
+  int op = 0;                    // UOp / BOp / reduce BOp
+  int dtype = ZYXB_F32;          // Const, Leaf, Cast
+  double value = 0.0;            // Const
+  uint32_t leaf_id = 0;
+  std::vector<uint64_t> shape;   // Leaf, Expand, Reshape
+  std::vector<int> axes;         // Permute, Reduce
+  std::vector<ClassId> inputs, outputs;   // Kernel
+  uint32_t program = 0;          // Kernel: index of the match (ProgramId once a device created the program)
+  uint64_t time = 0;
+};
+
+struct Class {
+  std::vector<uint32_t> nodes;   // node ids; nodes[0] defines shape and dtype, as Graph::shape / Graph::dtype read it
+  std::vector<uint64_t> shape;
+  int dtype = ZYXB_F32;
+};
+
+struct Match {
+  std::string pattern;
+  std::vector<ClassId> inputs, outputs;   // launch arguments: loads, then stores (Device::launch, backend/mod.rs:974)
+  zyxb_kernel_desc desc{};
+  std::vector<uint64_t> numel;            // optimizer: desc.u.optim.numel points here
+};
+
+inline bool is_float(int dt) { return dt == ZYXB_F32 || dt == ZYXB_BF16 || dt == ZYXB_F16 || dt == ZYXB_F64; }
+
+class Graph {
+ public:
+  std::vector<Node> nodes;
+  std::vector<Class> classes;
+
+  // ---- construction: one class per distinct node (the e-graph's hash-consing) --------------------------------------
+  ClassId add(const Node& n) {
+    const std::string key = key_of(n);
+    auto it = memo_.find(key);
+    if (it != memo_.end()) return it->second;
+    Class c;
+    switch (n.kind) {
+      case K_CONST: c.dtype = n.dtype; break;
+      case K_LEAF: c.dtype = n.dtype; c.shape = n.shape; break;
+      case K_EXPAND: case K_RESHAPE: c.dtype = classes[n.x].dtype; c.shape = n.shape; break;
+      case K_PERMUTE: c.dtype = classes[n.x].dtype; for (int a : n.axes) c.shape.push_back(classes[n.x].shape[a]); break;
+      case K_REDUCE: {
+        c.dtype = classes[n.x].dtype;
+        const auto& s = classes[n.x].shape;
+        for (size_t i = 0; i < s.size(); ++i) if (std::find(n.axes.begin(), n.axes.end(), (int)i) == n.axes.end()) c.shape.push_back(s[i]);
+        break;
+      }
+      case K_CAST: c.dtype = n.dtype; c.shape = classes[n.x].shape; break;
+      case K_UNARY: c.dtype = classes[n.x].dtype; c.shape = classes[n.x].shape; break;
+      case K_BINARY:
+        c.dtype = (n.op == B_CMPLT || n.op == B_CMPGT || n.op == B_CMPGE || n.op == B_NOTEQ || n.op == B_EQ) ? ZYXB_BOOL : classes[n.x].dtype;
+        c.shape = classes[n.x].shape;
+        break;
+      default: break;
+    }
+    nodes.push_back(n);
+    c.nodes.push_back((uint32_t)nodes.size() - 1);
+    classes.push_back(std::move(c));
+    const ClassId id = (ClassId)classes.size() - 1;
+    memo_[key] = id;
+    return id;
+  }
+  bool valid(ClassId c) const { return c < classes.size(); }
+
+  // ---- helpers, in the style of vendor/mod.rs:28-95 ---------------------------------------------------------------------
+  const std::vector<uint64_t>& shape(ClassId c) const { return classes[c].shape; }
+  int dtype(ClassId c) const { return classes[c].dtype; }
+  static uint64_t numel(const std::vector<uint64_t>& s) { uint64_t n = 1; for (uint64_t d : s) n *= d; return n; }
+
+  // A node of class c that satisfies pred.  In graph mode every `.cast(dtype)` pushes a Cast node, also when the dtype does
+  // not change (zyx/src/runtime.rs:696-700), so a class may be a no-op Cast of the class that holds the node looked for:
+  // those are looked through.
+  template <class F> const Node* find(ClassId c, F pred) const {
+    for (int depth = 0; depth < 8; ++depth) {
+      for (uint32_t nid : classes[c].nodes) if (pred(nodes[nid])) return &nodes[nid];
+      const Node* k = noop_cast(c);
+      if (!k) return nullptr;
+      c = k->x;
+    }
+    return nullptr;
+  }
+  const Node* noop_cast(ClassId c) const {
+    for (uint32_t nid : classes[c].nodes) if (nodes[nid].kind == K_CAST && classes[nodes[nid].x].dtype == classes[c].dtype) return &nodes[nid];
+    return nullptr;
+  }
+  ClassId canon(ClassId c) const { while (const Node* k = noop_cast(c)) c = k->x; return c; }
+  bool same(ClassId a, ClassId b) const { return canon(a) == canon(b); }
+  std::optional<std::pair<ClassId, ClassId>> binary(ClassId c, int bop) const {
+    const Node* n = find(c, [&](const Node& n) { return n.kind == K_BINARY && n.op == bop; });
+    if (!n) return std::nullopt;
+    return std::make_pair(n->x, n->y);
+  }
+  std::optional<ClassId> unary(ClassId c, int uop) const {
+    const Node* n = find(c, [&](const Node& n) { return n.kind == K_UNARY && n.op == uop; });
+    return n ? std::optional<ClassId>(n->x) : std::nullopt;
+  }
+  std::optional<ClassId> cast_src(ClassId c) const {
+    // the source of a dtype-changing Cast (no-op casts are looked through by find)
+    const Node* n = find(c, [&](const Node& n) { return n.kind == K_CAST && classes[n.x].dtype != n.dtype; });
+    return n ? std::optional<ClassId>(n->x) : std::nullopt;
+  }
+  std::optional<ClassId> expand_src(ClassId c) const {
+    const Node* n = find(c, [](const Node& n) { return n.kind == K_EXPAND; });
+    return n ? std::optional<ClassId>(n->x) : std::nullopt;
+  }
+  std::optional<ClassId> reshape_src(ClassId c) const {
+    const Node* n = find(c, [](const Node& n) { return n.kind == K_RESHAPE; });
+    return n ? std::optional<ClassId>(n->x) : std::nullopt;
+  }
+  // the class under any number of Expand / Reshape wrappers (a broadcast operand's source)
+  ClassId unbroadcast(ClassId c) const {
+    for (;;) {
+      if (auto e = expand_src(c)) { c = *e; continue; }
+      if (auto r = reshape_src(c)) { c = *r; continue; }
+      return c;
+    }
+  }
+  // a scalar constant under Expand / Reshape / Cast wrappers (rank-0 operands are cast to the tensor dtype and expanded,
+  // tensor/mod.rs:3033-3113)
+  std::optional<double> const_value(ClassId c) const {
+    for (;;) {
+      if (const Node* n = find(c, [](const Node& n) { return n.kind == K_CONST; })) return n->value;
+      if (auto e = expand_src(c)) { c = *e; continue; }
+      if (auto r = reshape_src(c)) { c = *r; continue; }
+      if (auto k = cast_src(c)) { c = *k; continue; }
+      return std::nullopt;
+    }
+  }
+  bool is_const(ClassId c, double v, double rel = 1e-2) const {
+    auto k = const_value(c);
+    return k && fabs(*k - v) <= rel * fabs(v) + 1e-30;
+  }
+  // x op const, in either operand order for commutative ops -> (x, const)
+  std::optional<std::pair<ClassId, double>> binary_const(ClassId c, int bop) const {
+    for (uint32_t nid : classes[c].nodes) {
+      const Node& n = nodes[nid];
+      if (n.kind != K_BINARY || n.op != bop) continue;
+      if (auto k = const_value(n.y)) return std::make_pair(n.x, *k);
+      if (bop == B_ADD || bop == B_MUL) if (auto k = const_value(n.x)) return std::make_pair(n.y, *k);
+    }
+    return std::nullopt;
+  }
+  // `x.<reduce>_keepdim / <reduce>([-1])` of reduce_impl: [Reshape]{[Cast back]{Reduce{[Cast to acc]{x}, rop, [last]}}} -> x
+  std::optional<ClassId> reduce_last(ClassId c, int rop) const {
+    if (auto r = reshape_src(c)) if (numel(shape(*r)) == numel(shape(c))) { if (auto x = reduce_last(*r, rop)) return x; }
+    ClassId r = c;
+    const Node* red = find(r, [&](const Node& n) { return n.kind == K_REDUCE && n.op == rop; });
+    if (!red) {
+      auto k = cast_src(c);
+      if (!k) return std::nullopt;
+      r = *k;
+      red = find(r, [&](const Node& n) { return n.kind == K_REDUCE && n.op == rop; });
+      if (!red) return std::nullopt;
+    }
+    const size_t rank = shape(red->x).size();
+    if (rank < 1 || red->axes.size() != 1 || red->axes[0] != (int)rank - 1) return std::nullopt;
+    ClassId x = red->x;
+    if (auto k = cast_src(x)) if (dtype(*k) == dtype(c)) x = *k;          // the accumulator cast (undone by the cast back) or a no-op cast
+    return canon(x);
+  }
+
+  // ---- matmul ------------------------------------------------------------------------------------------------------------
+  struct MatMul { ClassId a, b, out; uint64_t m, n, k, batch; bool trans_b, b_shared; int dtype; };
+
+  // The canonical broadcast-reduce form of Tensor::dot (tensor/mod.rs:1469-1490), ending at class `cid`:
+  //   a [.., m, k] -Reshape [.., m, 1, k]-> Expand -+
+  //   b [.., k, n] -Permute-> [.., n, k] -Reshape [.., 1, n, k]-> Expand -> Mul -[Cast acc]-> Reduce(Add, last) -[Cast back]-> [.., m, n]
+  std::optional<MatMul> match_matmul(ClassId cid) const {
+    const auto out_shape = shape(cid);
+    if (out_shape.size() < 2) return std::nullopt;
+    if (auto r = reshape_src(cid)) if (shape(*r) == out_shape) if (auto mm = match_matmul(*r)) { mm->out = cid; return mm; }  // dot's closing reshape
+    const uint64_t m = out_shape[out_shape.size() - 2], n = out_shape.back();
+    const Node* red = nullptr;
+    ClassId r = cid;
+    auto is_red = [](const Node& n) { return n.kind == K_REDUCE && n.op == B_ADD; };
+    if (!(red = find(r, is_red))) {
+      auto k = cast_src(cid);                                  // sum() casts the f32 accumulator back to the 16-bit input dtype
+      if (!k || !(red = find(r = *k, is_red))) return std::nullopt;
+    }
+    const auto prod_shape = shape(red->x);
+    const size_t pr = prod_shape.size();
+    if (pr != out_shape.size() + 1 || red->axes.size() != 1 || red->axes[0] != (int)pr - 1) return std::nullopt;
+    const uint64_t k = prod_shape.back();
+    ClassId prod = red->x;
+    auto mul = binary(prod, B_MUL);
+    if (!mul) { auto c = cast_src(prod); if (!c || !(mul = binary(*c, B_MUL))) return std::nullopt; }   // the accumulator cast
+    auto ea = expand_src(mul->first), eb = expand_src(mul->second);
+    if (!ea || !eb) return std::nullopt;
+    const auto a3 = shape(*ea), b3 = shape(*eb);
+    std::vector<uint64_t> batch_dims(out_shape.begin(), out_shape.end() - 2);
+    std::vector<uint64_t> want_a = batch_dims; want_a.insert(want_a.end(), {m, 1, k});
+    std::vector<uint64_t> want_b = batch_dims; want_b.insert(want_b.end(), {1, n, k});
+    const std::vector<uint64_t> shared_b = {1, n, k};
+    bool b_shared = false;
+    if (a3 != want_a) return std::nullopt;
+    if (b3 != want_b) {
+      // one B for every matrix of the batch: [1, n, k], or batch dims of extent 1
+      if (numel(b3) == n * k && b3.size() >= 3 && b3[b3.size() - 1] == k && b3[b3.size() - 2] == n && !batch_dims.empty()) b_shared = true;
+      else return std::nullopt;
+    }
+    // a: [.., m, 1, k] has the layout of [.., m, k]; prefer the tensor under the reshape
+    ClassId a = *ea;
+    if (auto s = reshape_src(a)) if (numel(shape(*s)) == numel(a3)) a = *s;
+    // b: through the reshape to the Permute that swaps the last two axes
+    ClassId bt = *eb;
+    const Node* perm = nullptr;
+    for (;;) {
+      perm = find(bt, [](const Node& n) {
+        if (n.kind != K_PERMUTE || n.axes.size() < 2) return false;
+        const size_t r = n.axes.size();
+        for (size_t i = 0; i + 2 < r; ++i) if (n.axes[i] != (int)i) return false;
+        return n.axes[r - 2] == (int)r - 1 && n.axes[r - 1] == (int)r - 2;
+      });
+      if (perm) break;
+      auto s = reshape_src(bt);
+      if (!s) return std::nullopt;
+      bt = *s;
+    }
+    ClassId b = perm->x;                                      // [.., k, n]
+    const auto bs = shape(b);
+    if (bs.size() < 2 || bs[bs.size() - 2] != k || bs.back() != n) return std::nullopt;
+    bool trans_b = false;
+    // NT on a stored tensor: b is itself `w.t()` of a [.., n, k] tensor (Linear passes W.t() to dot, which transposes again)
+    if (const Node* p2 = find(b, [&](const Node& n) { return n.kind == K_PERMUTE && n.axes == perm->axes; })) { b = p2->x; trans_b = true; }
+    const int dt = dtype(b);
+    if (dtype(a) != dt || dtype(cid) != dt) return std::nullopt;      // C is stored in the operands' dtype; accumulation is f32 / i32
+    if (!(dt == ZYXB_F32 || dt == ZYXB_BF16 || dt == ZYXB_F16 || dt == ZYXB_I32)) return std::nullopt;
+    return MatMul{a, b, cid, m, n, k, numel(batch_dims), trans_b, b_shared, dt};
+  }
+
+  static zyxb_kernel_desc gemm_desc(const MatMul& mm, int epi, bool preact, float alpha) {
+    zyxb_kernel_desc d{};
+    d.kind = ZYXB_KIND_GEMM;
+    auto& g = d.u.gemm;
+    g.dtype = mm.dtype; g.m = mm.m; g.n = mm.n; g.k = mm.k; g.batch = mm.batch;
+    g.trans_a = 0; g.trans_b = mm.trans_b;
+    g.stride_a = (int64_t)(mm.m * mm.k); g.stride_b = mm.b_shared ? 0 : (int64_t)(mm.k * mm.n); g.stride_c = (int64_t)(mm.m * mm.n);
+    g.epilogue = epi; g.store_preact = preact; g.alpha = alpha;
+    return d;
+  }
+
+  // relu(e) = e.cmpgt(0) * e (tensor/elementwise.rs:289-293): Mul{Cast{Cmpgt{e, 0}}, e} -> e
+  std::optional<ClassId> relu_of(ClassId c) const {
+    for (uint32_t nid : classes[c].nodes) {
+      const Node& n = nodes[nid];
+      if (n.kind != K_BINARY || n.op != B_MUL) continue;
+      for (int swap = 0; swap < 2; ++swap) {
+        ClassId mask = swap ? n.y : n.x, e = swap ? n.x : n.y;
+        if (auto k = cast_src(mask)) mask = *k;
+        auto cmp = binary(mask, B_CMPGT);
+        if (cmp && same(cmp->first, e) && is_const(cmp->second, 0.0, 0.0)) return e;
+      }
+    }
+    return std::nullopt;
+  }
+  // tanh(u) = ((u+u).exp() - 1) / ((u+u).exp() + 1) (elementwise.rs:585-588) -> u
+  std::optional<ClassId> tanh_of(ClassId c) const {
+    auto div = binary(c, B_DIV);
+    if (!div) return std::nullopt;
+    auto num = binary_const(div->first, B_SUB), den = binary_const(div->second, B_ADD);
+    if (!num || !den || !same(num->first, den->first) || fabs(num->second - 1.0) > 1e-6 || fabs(den->second - 1.0) > 1e-6) return std::nullopt;
+    auto arg = unary(num->first, U_EXP);
+    if (!arg) return std::nullopt;
+    auto two = binary(*arg, B_ADD);
+    if (!two || !same(two->first, two->second)) return std::nullopt;
+    return two->first;
+  }
+  // gelu(z) = z * 0.5 * (tanh((z + z*z*z*0.044715) * sqrt(2/pi)) + 1) (elementwise.rs:168-170) -> z
+  std::optional<ClassId> gelu_of(ClassId c) const {
+    auto top = binary(c, B_MUL);
+    if (!top) return std::nullopt;
+    auto half = binary_const(top->first, B_MUL);
+    auto plus1 = binary_const(top->second, B_ADD);
+    if (!half || !plus1 || !near(half->second, 0.5) || !near(plus1->second, 1.0)) return std::nullopt;
+    const ClassId z = half->first;
+    auto u = tanh_of(plus1->first);
+    if (!u) return std::nullopt;
+    auto scaled = binary_const(*u, B_MUL);
+    if (!scaled || !near(scaled->second, 0.7978845608028654)) return std::nullopt;
+    auto sum = binary(scaled->first, B_ADD);
+    if (!sum || !same(sum->first, z)) return std::nullopt;
+    auto cube = binary_const(sum->second, B_MUL);
+    if (!cube || !near(cube->second, 0.044715)) return std::nullopt;
+    auto zz_z = binary(cube->first, B_MUL);
+    if (!zz_z || !same(zz_z->second, z)) return std::nullopt;
+    auto zz = binary(zz_z->first, B_MUL);
+    if (!zz || !same(zz->first, z) || !same(zz->second, z)) return std::nullopt;
+    return z;
+  }
+  static bool near(double a, double b) { return fabs(a - b) <= 1e-2 * fabs(b); }     // constants arrive rounded to the tensor dtype
+
+  // matmul [* const] [+ bias [relu | gelu]] ending at cid.  `wanted` are classes somebody else reads (the outputs of the
+  // graph being matched): a pre-activation among them becomes the program's second output.
+  std::optional<Match> match_linear(ClassId cid, const std::set<ClassId>& wanted) const {
+    ClassId e = cid;
+    int act = 0;
+    if (auto z = gelu_of(cid)) { e = *z; act = 2; }
+    else if (auto z = relu_of(cid)) { e = *z; act = 1; }
+    // + bias: Add{mm, Expand{bias [n]}}
+    ClassId core = e, bias = NONE;
+    if (auto add = binary(e, B_ADD)) {
+      for (int swap = 0; swap < 2 && bias == NONE; ++swap) {
+        const ClassId lhs = swap ? add->second : add->first, rhs = swap ? add->first : add->second;
+        auto src = expand_src(rhs);
+        if (!src) continue;
+        const ClassId bsrc = unbroadcast(rhs);
+        if (shape(bsrc).size() == 1 && shape(bsrc)[0] == shape(e).back() && match_matmul_scaled(lhs)) { core = lhs; bias = bsrc; }
+      }
+    }
+    if (act && bias == NONE) return std::nullopt;            // the fused activations exist as bias epilogues only
+    auto sc = match_matmul_scaled(core);
+    if (!sc) return std::nullopt;
+    const MatMul& mm = sc->first;
+    if (bias != NONE && dtype(bias) != mm.dtype) return std::nullopt;
+    const int epi = bias == NONE ? ZYXB_EPI_NONE : act == 2 ? ZYXB_EPI_BIAS_GELU : act == 1 ? ZYXB_EPI_BIAS_RELU : ZYXB_EPI_BIAS;
+    const bool preact = act == 2 && wanted.count(e) != 0;
+    Match mt;
+    mt.pattern = std::string(mm.trans_b ? "matmul_nt" : "matmul_nn") + (mm.batch > 1 ? "_batched" : "") + (bias != NONE ? "_bias" : "") +
+                 (act == 2 ? "_gelu" : act == 1 ? "_relu" : "");
+    mt.desc = gemm_desc(mm, epi, preact, sc->second);
+    mt.inputs = {mm.a, mm.b};
+    if (bias != NONE) mt.inputs.push_back(bias);
+    mt.outputs = {cid};
+    if (preact) mt.outputs.push_back(e);
+    return mt;
+  }
+  // matmul, or matmul * const (the scale of attention scores, multi_head_attention.rs:198-199) -> (matmul, alpha)
+  std::optional<std::pair<MatMul, float>> match_matmul_scaled(ClassId cid) const {
+    if (auto mm = match_matmul(cid)) return std::make_pair(*mm, 1.0f);
+    if (auto sc = binary_const(cid, B_MUL)) if (auto mm = match_matmul(sc->first)) { mm->out = cid; return std::make_pair(*mm, (float)sc->second); }
+    return std::nullopt;
+  }
+
+  // ---- row kernels ---------------------------------------------------------------------------------------------------------
+  static zyxb_kernel_desc row_desc(int op, int dt, const std::vector<uint64_t>& s) {
+    zyxb_kernel_desc d{};
+    d.kind = ZYXB_KIND_ROWREDUCE;
+    d.u.rowreduce.op = op; d.u.rowreduce.dtype = dt; d.u.rowreduce.cols = s.back(); d.u.rowreduce.rows = numel(s) / s.back();
+    d.u.rowreduce.correction = 1;
+    return d;
+  }
+  bool row_dtype(int dt) const { return dt == ZYXB_F32 || dt == ZYXB_BF16 || dt == ZYXB_F16; }
+
+  // softmax(x, [-1]) = e / e.sum_keepdim, e = (x - x.max_keepdim).exp()   (tensor/mod.rs:1457-1461)
+  std::optional<Match> match_softmax(ClassId cid) const {
+    auto div = binary(cid, B_DIV);
+    if (!div || !expand_src(div->second)) return std::nullopt;
+    const ClassId e = div->first;
+    auto sum_of = reduce_last(unbroadcast_keepdim(div->second), B_ADD);
+    if (!sum_of || !same(*sum_of, e)) return std::nullopt;
+    auto x = shifted(e, U_EXP);
+    if (!x || !row_dtype(dtype(*x)) || shape(*x).empty()) return std::nullopt;
+    Match m; m.pattern = "softmax"; m.desc = row_desc(ZYXB_RR_SOFTMAX, dtype(*x), shape(*x)); m.inputs = {*x}; m.outputs = {cid};
+    return m;
+  }
+  // ln_softmax(x, [-1]) = m - m.exp().sum_keepdim().ln(), m = x - x.max_keepdim   (tensor/mod.rs:1427-1431)
+  std::optional<Match> match_ln_softmax(ClassId cid) const {
+    auto sub = binary(cid, B_SUB);
+    if (!sub || !expand_src(sub->second)) return std::nullopt;
+    const ClassId m = sub->first;
+    auto lnarg = unary(unbroadcast_keepdim(sub->second), U_LN);
+    if (!lnarg) return std::nullopt;
+    auto e = reduce_last(*lnarg, B_ADD);
+    if (!e) return std::nullopt;
+    auto earg = unary(*e, U_EXP);
+    if (!earg || !same(*earg, m)) return std::nullopt;
+    auto x = shifted(m, -1);
+    if (!x || !row_dtype(dtype(*x))) return std::nullopt;
+    Match mt; mt.pattern = "ln_softmax"; mt.desc = row_desc(ZYXB_RR_LN_SOFTMAX, dtype(*x), shape(*x)); mt.inputs = {*x}; mt.outputs = {cid};
+    return mt;
+  }
+  // a keepdim operand is expanded back over the row: strip exactly that Expand (its source keeps rank, last extent 1)
+  ClassId unbroadcast_keepdim(ClassId c) const { auto e = expand_src(c); return e ? *e : c; }
+  // c = uop(x - Expand{max_keepdim(x)}) (uop < 0: no unary) -> x
+  std::optional<ClassId> shifted(ClassId c, int uop) const {
+    ClassId d = c;
+    if (uop >= 0) { auto a = unary(c, uop); if (!a) return std::nullopt; d = *a; }
+    auto sub = binary(d, B_SUB);
+    if (!sub) return std::nullopt;
+    auto mx = reduce_last(unbroadcast_keepdim(sub->second), B_MAX);
+    if (!mx || !same(*mx, sub->first)) return std::nullopt;
+    return canon(sub->first);
+  }
+  // mean over the last axis, keepdim: sum / const(n)   (reduce_ops.rs:104-112) -> x
+  std::optional<ClassId> mean_last(ClassId c, double* n_out = nullptr) const {
+    ClassId d = c;
+    if (auto r = reshape_src(c)) if (numel(shape(*r)) == numel(shape(c))) d = *r;
+    auto div = binary_const(d, B_DIV);
+    if (!div) return std::nullopt;
+    auto x = reduce_last(div->first, B_ADD);
+    if (!x) return std::nullopt;
+    if (n_out) *n_out = div->second;
+    return x;
+  }
+  // LayerNorm::forward over the last axis (zyx-nn/src/layer_norm.rs:117-131):
+  //   ((x - mean) / sqrt(var + eps)) [* weight] [+ bias],  var = ((x - mean)^2).sum / (n - 1)
+  std::optional<Match> match_layernorm(ClassId cid) const {
+    ClassId c = cid, weight = NONE, bias = NONE;
+    auto affine = [&](int bop, ClassId& param) {
+      auto b = binary(c, bop);
+      if (!b || !expand_src(b->second)) return;
+      const ClassId src = unbroadcast(b->second);
+      if (shape(src).size() == 1 && shape(src)[0] == shape(cid).back() && !const_value(src)) { param = src; c = b->first; }
+    };
+    affine(B_ADD, bias);
+    affine(B_MUL, weight);
+    auto div = binary(c, B_DIV);
+    if (!div) return std::nullopt;
+    auto centred = binary(div->first, B_SUB);
+    if (!centred) return std::nullopt;
+    const ClassId x = canon(centred->first);
+    auto mx = mean_last(unbroadcast_keepdim(centred->second));
+    if (!mx || !same(*mx, x)) return std::nullopt;
+    auto root = unary(unbroadcast_keepdim(div->second), U_SQRT);
+    if (!root) return std::nullopt;
+    auto var_eps = binary_const(*root, B_ADD);
+    if (!var_eps) return std::nullopt;
+    double d = 0;
+    auto sq = mean_last(var_eps->first, &d);           // sum((x - mean)^2) / (n - correction)
+    if (!sq) return std::nullopt;
+    auto xx = binary(*sq, B_MUL);
+    if (!xx || !same(xx->first, xx->second) || !same(xx->first, div->first)) return std::nullopt;
+    if (!row_dtype(dtype(x))) return std::nullopt;
+    const double n = (double)shape(x).back();
+    const int correction = (int)llround(n - d);
+    Match m; m.pattern = "layernorm";
+    m.desc = row_desc(ZYXB_RR_LAYERNORM, dtype(x), shape(x));
+    m.desc.u.rowreduce.eps = (float)var_eps->second; m.desc.u.rowreduce.correction = near(d, n - 1) ? 1 : correction;
+    m.desc.u.rowreduce.has_weight = weight != NONE; m.desc.u.rowreduce.has_bias = bias != NONE;
+    m.inputs = {x};
+    if (weight != NONE) m.inputs.push_back(weight);
+    if (bias != NONE) m.inputs.push_back(bias);
+    m.outputs = {cid};
+    return m;
+  }
+  // sum / max / mean over the last axis of a tensor nobody computes as a matmul product
+  std::optional<Match> match_reduce(ClassId cid) const {
+    const std::pair<int, int> ops[] = {{B_ADD, ZYXB_RR_SUM}, {B_MAX, ZYXB_RR_MAX}};
+    if (auto x = mean_last(cid)) if (row_dtype(dtype(*x)) && shape(*x).size() >= 1) {
+      Match m; m.pattern = "mean"; m.desc = row_desc(ZYXB_RR_MEAN, dtype(*x), shape(*x)); m.inputs = {*x}; m.outputs = {cid};
+      return m;
+    }
+    for (auto [rop, rr] : ops)
+      if (auto x = reduce_last(cid, rop)) {
+        if (!(row_dtype(dtype(*x)) || dtype(*x) == ZYXB_I32) || dtype(cid) != dtype(*x) || shape(*x).empty()) continue;
+        if (is_broadcast_product(*x)) continue;       // the [.., m, n, k] product of a dot: never materialised, the matmul patterns own it
+        Match m; m.pattern = rop == B_ADD ? "sum" : "max"; m.desc = row_desc(rr, dtype(*x), shape(*x)); m.inputs = {*x}; m.outputs = {cid};
+        return m;
+      }
+    return std::nullopt;
+  }
+
+  bool is_broadcast_product(ClassId c) const {
+    if (auto k = cast_src(c)) c = *k;
+    auto mul = binary(c, B_MUL);
+    return mul && expand_src(mul->first) && expand_src(mul->second);
+  }
+
+  // ---- optimizer updates -------------------------------------------------------------------------------------------------
+  struct Update { int algo; ClassId p, g, m = NONE, v = NONE, p_new, m_new = NONE, v_new = NONE; double lr, wd = 0, b1 = 0, b2 = 0, eps = 0, bc1 = 0, bc2 = 0; bool first = false; };
+
+  // p' = (p - g * lr).cast(p.dtype)   (sgd.rs:79-82, no weight decay, no momentum)
+  std::optional<Update> match_sgd(ClassId cid) const {
+    const ClassId c = canon(cid);
+    auto sub = binary(c, B_SUB);
+    if (!sub) return std::nullopt;
+    auto step = binary_const(sub->second, B_MUL);
+    if (!step || !is_leaf(sub->first) || shape(step->first) != shape(sub->first)) return std::nullopt;
+    Update u{}; u.algo = ZYXB_OPT_SGD; u.p = sub->first; u.g = step->first; u.p_new = cid; u.lr = step->second;
+    return u;
+  }
+  bool is_leaf(ClassId c) const { return find(c, [](const Node& n) { return n.kind == K_LEAF; }) != nullptr; }
+
+  // AdamW::update for one parameter (adamw.rs:58-95), ending at the new parameter's class
+  std::optional<Update> match_adamw(ClassId cid) const {
+    Update u{}; u.algo = ZYXB_OPT_ADAMW; u.p_new = cid;
+    ClassId c = cid;
+    if (auto decay = binary_const(c, B_MUL)) if (!is_leaf(decay->first)) { u.wd = 1.0 - decay->second; c = decay->first; }   // p * (1 - lr*wd)
+    c = canon(c);
+    auto sub = binary(c, B_SUB);
+    if (!sub || !is_leaf(sub->first)) return std::nullopt;
+    u.p = sub->first;
+    auto step = binary(sub->second, B_DIV);                    // mh / ((sqrt(vh) + eps) * lr)
+    if (!step) return std::nullopt;
+    auto den = binary_const(step->second, B_MUL);
+    if (!den) return std::nullopt;
+    u.lr = den->second;
+    auto root_eps = binary_const(den->first, B_ADD);
+    if (!root_eps) return std::nullopt;
+    u.eps = root_eps->second;
+    auto vh = unary(root_eps->first, U_SQRT);
+    if (!vh) return std::nullopt;
+    auto mh = binary_const(step->first, B_DIV), vhd = binary_const(*vh, B_DIV);
+    if (!mh || !vhd) return std::nullopt;
+    u.bc1 = mh->second; u.bc2 = vhd->second; u.m_new = mh->first; u.v_new = vhd->first;
+    // m' = m*b1 + g*(1-b1)  |  g*(1-b1) on the first step
+    auto moment = [&](ClassId mc, bool squared, ClassId& state, double& beta, ClassId& g) -> bool {
+      auto grad_term = [&](ClassId t, double& one_minus) -> std::optional<ClassId> {
+        auto k = binary_const(t, B_MUL);
+        if (!k) return std::nullopt;
+        one_minus = k->second;
+        if (!squared) return k->first;
+        auto gg = binary(k->first, B_MUL);
+        if (!gg || !same(gg->first, gg->second)) return std::nullopt;
+        return gg->first;
+      };
+      double om = 0;
+      if (auto add = binary(mc, B_ADD)) {
+        auto decay = binary_const(add->first, B_MUL);
+        auto gt = grad_term(add->second, om);
+        if (decay && gt && is_leaf(decay->first)) { state = decay->first; beta = 1.0 - om; g = *gt; return true; }
+      }
+      if (auto gt = grad_term(mc, om)) { state = NONE; beta = 1.0 - om; g = *gt; return true; }
+      return false;
+    };
+    ClassId g1 = NONE, g2 = NONE;
+    if (!moment(u.m_new, false, u.m, u.b1, g1) || !moment(u.v_new, true, u.v, u.b2, g2) || !same(g1, g2)) return std::nullopt;
+    u.g = g1;
+    u.first = u.m == NONE;
+    if ((u.m == NONE) != (u.v == NONE)) return std::nullopt;
+    if (u.wd != 0) u.wd /= u.lr;
+    return u;
+  }
+
+  // ---- the device's match_graph (backend/mod.rs:952-961; model backend/cblas.rs:213-238) --------------------------------
+  // Visits `order` (Graph::topo_sort_classes_without_kernels of the outputs), and for every class some pattern ends at pushes a
+  // Node::Kernel{inputs, outputs, program_id, time: 1} into that class.  Optimizer updates of one dtype and one set of
+  // hyper-parameters become one multi-tensor program whose Kernel node is pushed into every class it writes.
+  std::vector<Match> match_graph(const std::vector<ClassId>& order, const std::set<ClassId>& wanted) {
+    std::vector<Match> out;
+    std::vector<Update> updates;
+    for (ClassId cid : order) {
+      if (!valid(cid) || find(cid, [](const Node& n) { return n.kind == K_KERNEL; })) continue;
+      std::optional<Match> m;
+      if (wanted.count(cid)) {      // new parameter values are outputs of the graph; their sub-expressions are not matched as updates
+        if (auto u = match_adamw(cid)) { updates.push_back(*u); continue; }
+        if (auto u = match_sgd(cid)) { updates.push_back(*u); continue; }
+      }
+      if (!(m = match_linear(cid, wanted)) && !(m = match_softmax(cid)) && !(m = match_ln_softmax(cid)) && !(m = match_layernorm(cid)) &&
+          !(m = match_reduce(cid)))
+        continue;
+      out.push_back(std::move(*m));
+    }
+    // group the per-parameter updates: one program per (algorithm, dtype, hyper-parameters, first step or not)
+    std::vector<char> used(updates.size(), 0);
+    for (size_t i = 0; i < updates.size(); ++i) {
+      if (used[i]) continue;
+      const Update& h = updates[i];
+      Match mt; mt.pattern = h.algo == ZYXB_OPT_SGD ? "sgd" : (h.first ? "adamw_first_step" : "adamw");
+      std::vector<ClassId> p, g, mm, vv, outs;
+      for (size_t j = i; j < updates.size(); ++j) {
+        const Update& u = updates[j];
+        if (used[j] || u.algo != h.algo || dtype(u.p) != dtype(h.p) || u.first != h.first || u.lr != h.lr || u.wd != h.wd || u.b1 != h.b1 ||
+            u.b2 != h.b2 || u.eps != h.eps || u.bc1 != h.bc1 || u.bc2 != h.bc2) continue;
+        used[j] = 1;
+        p.push_back(u.p); g.push_back(u.g); mt.numel.push_back(numel(shape(u.p)));
+        outs.push_back(u.p_new);
+        if (u.algo != ZYXB_OPT_SGD) { mm.push_back(u.m); vv.push_back(u.v); outs.push_back(u.m_new); outs.push_back(u.v_new); }
+      }
+      mt.desc.kind = ZYXB_KIND_OPTIM;
+      auto& o = mt.desc.u.optim;
+      o.algo = h.algo; o.dtype = dtype(h.p); o.n_tensors = (int32_t)p.size(); o.lr = (float)h.lr; o.weight_decay = (float)h.wd;
+      o.beta1 = (float)h.b1; o.beta2 = (float)h.b2; o.eps = (float)h.eps;
+      mt.inputs = p; mt.inputs.insert(mt.inputs.end(), g.begin(), g.end());
+      if (h.algo != ZYXB_OPT_SGD && !h.first) { mt.inputs.insert(mt.inputs.end(), mm.begin(), mm.end()); mt.inputs.insert(mt.inputs.end(), vv.begin(), vv.end()); }
+      mt.outputs = outs;
+      out.push_back(std::move(mt));
+    }
+    for (size_t i = 0; i < out.size(); ++i) {
+      if (out[i].desc.kind == ZYXB_KIND_OPTIM) out[i].desc.u.optim.numel = out[i].numel.data();
+      Node k; k.kind = K_KERNEL; k.inputs = out[i].inputs; k.outputs = out[i].outputs; k.program = (uint32_t)i; k.time = 1;
+      nodes.push_back(k);
+      for (ClassId o : out[i].outputs) classes[o].nodes.push_back((uint32_t)nodes.size() - 1);
+    }
+    return out;
+  }
+
+  // every class reachable from `outputs`, operands before users (the order match_graph walks)
+  std::vector<ClassId> topo_order(const std::vector<ClassId>& outputs) const {
+    std::vector<ClassId> order;
+    std::vector<char> seen(classes.size(), 0);
+    std::vector<std::pair<ClassId, bool>> stack;
+    for (auto it = outputs.rbegin(); it != outputs.rend(); ++it) stack.push_back({*it, false});   // the first output is visited first
+    while (!stack.empty()) {
+      auto [c, done] = stack.back();
+      stack.pop_back();
+      if (!valid(c)) continue;
+      if (done) { order.push_back(c); continue; }
+      if (seen[c]) continue;
+      seen[c] = 1;
+      stack.push_back({c, true});
+      const Node& n = nodes[classes[c].nodes[0]];
+      if (n.x != NONE) stack.push_back({n.x, false});
+      if (n.y != NONE) stack.push_back({n.y, false});
+    }
+    return order;
+  }
+
+ private:
+  std::map<std::string, ClassId> memo_;
+  static std::string key_of(const Node& n) {
+    std::string k = std::to_string(n.kind) + ":" + std::to_string(n.x) + ":" + std::to_string(n.y) + ":" + std::to_string(n.op) + ":" +
+                    std::to_string(n.dtype) + ":" + std::to_string(n.leaf_id) + ":";
+    char buf[32];
+    snprintf(buf, sizeof buf, "%.17g", n.value);
+    k += buf;
+    for (uint64_t d : n.shape) k += "," + std::to_string(d);
+    k += "|";
+    for (int a : n.axes) k += "," + std::to_string(a);
+    return k;
+  }
+};
+
+}  // namespace zyxb_matcher
