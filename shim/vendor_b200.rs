@@ -1,0 +1,387 @@
+// zyx/src/vendor/b200.rs — subgraph -> kernel-descriptor matching for the B200 backend (`mod b200;` in vendor/mod.rs).
+//
+// NOT COMPILED (no Rust toolchain in the build image).  It is a line-by-line port of zyx_b200/csrc/host/matcher.hpp, the C++
+// matcher that tests/test_matcher.py exercises through the C ABI on node lists transcribed from Tensor::dot, Linear::forward,
+// softmax, ln_softmax, LayerNorm::forward, SGD::update and AdamW::update; function names and order are kept the same so the two
+// can be read side by side.  It extends Graph::match_matmul (vendor/matmul.rs:43-71) and reuses the helpers of
+// vendor/mod.rs:28-95 (`const_shape`).
+
+#![allow(unused)]
+
+use std::collections::BTreeSet;
+
+use crate::{
+    DType,
+    backend::b200::{ZyxbDescUnion, ZyxbGemmDesc, ZyxbKernelDesc, ZyxbOptimDesc, ZyxbRowreduceDesc, ZYXB_KIND_GEMM, ZYXB_KIND_OPTIM, ZYXB_KIND_ROWREDUCE},
+    graph::{ClassId, Graph, Node},
+    kernel::{BOp, UOp},
+    shape::Dim,
+};
+
+/// One recognised subgraph: the descriptor for zyxb_program_create and the launch arguments (loads, then stores).
+pub(crate) struct B200Match {
+    pub(crate) pattern: &'static str,
+    pub(crate) inputs: Vec<ClassId>,
+    pub(crate) outputs: Vec<ClassId>,
+    pub(crate) desc: ZyxbKernelDesc,
+    /// optimizer programs: element counts per tensor (desc.u.optim.numel is pointed here by the caller)
+    pub(crate) numel: Vec<u64>,
+}
+
+#[derive(Clone, Copy)]
+struct MatMulX { a: ClassId, b: ClassId, m: Dim, n: Dim, k: Dim, batch: Dim, trans_b: bool, b_shared: bool, dtype: DType }
+
+#[derive(Clone, Copy)]
+struct Update { algo: i32, p: ClassId, g: ClassId, m: Option<ClassId>, v: Option<ClassId>, p_new: ClassId, m_new: Option<ClassId>,
+                v_new: Option<ClassId>, lr: f64, wd: f64, b1: f64, b2: f64, eps: f64, bc1: f64, bc2: f64, first: bool }
+
+const RR_SUM: i32 = 0; const RR_MAX: i32 = 1; const RR_MEAN: i32 = 3; const RR_SOFTMAX: i32 = 6; const RR_LN_SOFTMAX: i32 = 7; const RR_LAYERNORM: i32 = 8;
+const EPI_NONE: i32 = 0; const EPI_BIAS: i32 = 1; const EPI_BIAS_RELU: i32 = 2; const EPI_BIAS_GELU: i32 = 3;
+const OPT_SGD: i32 = 0; const OPT_ADAMW: i32 = 2;
+
+fn near(a: f64, b: f64) -> bool { (a - b).abs() <= 1e-2 * b.abs() }       // constants arrive rounded to the tensor dtype
+
+impl Graph {
+    // ---- node finders; a class may be a no-op Cast of the class holding the node (runtime.rs:696-700 pushes a Cast for every
+    // `.cast`, also when the dtype does not change), so those are looked through ------------------------------------------------
+    fn noop_cast(&self, c: ClassId) -> Option<ClassId> {
+        self.classes[c].nodes.iter().find_map(|&nid| match &self.nodes[nid].node {
+            Node::Cast { x, dtype } if self.dtype(*x) == *dtype => Some(*x),
+            _ => None,
+        })
+    }
+    fn canon(&self, mut c: ClassId) -> ClassId { while let Some(x) = self.noop_cast(c) { c = x; } c }
+    fn same(&self, a: ClassId, b: ClassId) -> bool { self.canon(a) == self.canon(b) }
+    fn find_in<T>(&self, mut c: ClassId, f: impl Fn(&Node) -> Option<T>) -> Option<T> {
+        for _ in 0..8 {
+            if let Some(t) = self.classes[c].nodes.iter().find_map(|&nid| f(&self.nodes[nid].node)) { return Some(t); }
+            c = self.noop_cast(c)?;
+        }
+        None
+    }
+    fn binary_of(&self, c: ClassId, op: BOp) -> Option<(ClassId, ClassId)> {
+        self.find_in(c, |n| match n { Node::Binary { x, y, bop } if *bop == op => Some((*x, *y)), _ => None })
+    }
+    fn unary_of(&self, c: ClassId, op: UOp) -> Option<ClassId> {
+        self.find_in(c, |n| match n { Node::Unary { x, uop } if *uop == op => Some(*x), _ => None })
+    }
+    /// the source of a dtype-changing Cast
+    fn cast_src(&self, c: ClassId) -> Option<ClassId> {
+        self.find_in(c, |n| match n { Node::Cast { x, dtype } if self.dtype(*x) != *dtype => Some(*x), _ => None })
+    }
+    fn expand_of(&self, c: ClassId) -> Option<ClassId> { self.find_in(c, |n| match n { Node::Expand { x, .. } => Some(*x), _ => None }) }
+    fn reshape_of(&self, c: ClassId) -> Option<ClassId> { self.find_in(c, |n| match n { Node::Reshape { x, .. } => Some(*x), _ => None }) }
+    fn is_leaf(&self, c: ClassId) -> bool { self.find_in(c, |n| matches!(n, Node::Leaf { .. }).then_some(())).is_some() }
+    fn unbroadcast(&self, mut c: ClassId) -> ClassId {
+        loop {
+            if let Some(x) = self.expand_of(c) { c = x; continue; }
+            if let Some(x) = self.reshape_of(c) { c = x; continue; }
+            return c;
+        }
+    }
+    /// a scalar constant under Expand / Reshape / Cast wrappers (tensor/mod.rs:3033-3113: rank-0 operands are cast and expanded)
+    fn const_value(&self, mut c: ClassId) -> Option<f64> {
+        loop {
+            if let Some(v) = self.find_in(c, |n| match n { Node::Const(k) => Some(k.as_f64()), _ => None }) { return Some(v); }
+            if let Some(x) = self.expand_of(c) { c = x; continue; }
+            if let Some(x) = self.reshape_of(c) { c = x; continue; }
+            if let Some(x) = self.cast_src(c) { c = x; continue; }
+            return None;
+        }
+    }
+    fn binary_const(&self, c: ClassId, op: BOp) -> Option<(ClassId, f64)> {
+        let (x, y) = self.binary_of(c, op)?;
+        if let Some(k) = self.const_value(y) { return Some((x, k)); }
+        if op.is_commutative() { if let Some(k) = self.const_value(x) { return Some((y, k)); } }
+        None
+    }
+    fn numel_of(&self, c: ClassId) -> Option<Dim> { Some(self.const_shape(c)?.iter().product()) }
+
+    /// `x.<reduce>([-1])` / `_keepdim` of reduce_impl (tensor/reduce_ops.rs:45-157):
+    /// [Reshape]{[Cast back]{Reduce{[Cast to acc]{x}, rop, [last]}}} -> x
+    fn reduce_last(&self, c: ClassId, rop: BOp) -> Option<ClassId> {
+        if let Some(r) = self.reshape_of(c) {
+            if self.numel_of(r) == self.numel_of(c) { if let Some(x) = self.reduce_last(r, rop) { return Some(x); } }
+        }
+        let red = |cls: ClassId| self.find_in(cls, |n| match n { Node::Reduce { x, rop: r, axes } if *r == rop => Some((*x, axes.clone())), _ => None });
+        let (x, axes) = red(c).or_else(|| red(self.cast_src(c)?))?;
+        let rank = self.const_shape(x)?.len();
+        if rank < 1 || axes.len() != 1 || axes[0] != rank - 1 { return None; }
+        let mut src = x;
+        if let Some(k) = self.cast_src(src) { if self.dtype(k) == self.dtype(c) { src = k; } }     // the accumulator cast, undone by the cast back
+        Some(self.canon(src))
+    }
+
+    // ---- matmul: Graph::match_matmul extended to NT on a stored tensor, rank > 2 and the accumulator casts of 16-bit inputs -------
+    fn match_matmul_x(&self, cid: ClassId) -> Option<MatMulX> {
+        let out_shape = self.const_shape(cid)?;
+        if out_shape.len() < 2 { return None; }
+        if let Some(r) = self.reshape_of(cid) {                      // dot's closing reshape to the shape the reduce already has
+            if self.const_shape(r).as_ref() == Some(&out_shape) { if let Some(mm) = self.match_matmul_x(r) { return Some(mm); } }
+        }
+        let (m, n) = (out_shape[out_shape.len() - 2], out_shape[out_shape.len() - 1]);
+        let red = |cls: ClassId| self.find_in(cls, |nd| match nd { Node::Reduce { x, rop: BOp::Add, axes } => Some((*x, axes.clone())), _ => None });
+        let (prod, axes) = red(cid).or_else(|| red(self.cast_src(cid)?))?;
+        let prod_shape = self.const_shape(prod)?;
+        let pr = prod_shape.len();
+        if pr != out_shape.len() + 1 || axes.len() != 1 || axes[0] != pr - 1 { return None; }
+        let k = prod_shape[pr - 1];
+        let (ea, eb) = self.binary_of(prod, BOp::Mul).or_else(|| self.binary_of(self.cast_src(prod)?, BOp::Mul))?;
+        let (ea, eb) = (self.expand_of(ea)?, self.expand_of(eb)?);
+        let (a3, b3) = (self.const_shape(ea)?, self.const_shape(eb)?);
+        let batch_dims = &out_shape[..out_shape.len() - 2];
+        let want_a: Vec<Dim> = batch_dims.iter().copied().chain([m, 1, k]).collect();
+        let want_b: Vec<Dim> = batch_dims.iter().copied().chain([1, n, k]).collect();
+        if a3 != want_a { return None; }
+        let mut b_shared = false;
+        if b3 != want_b {
+            let nb = b3.len();
+            if nb >= 3 && b3.iter().product::<Dim>() == n * k && b3[nb - 1] == k && b3[nb - 2] == n && !batch_dims.is_empty() { b_shared = true; } else { return None; }
+        }
+        let mut a = ea;
+        if let Some(s) = self.reshape_of(a) { if self.numel_of(s) == Some(a3.iter().product()) { a = s; } }
+        // b: through the reshape to the Permute that swaps the last two axes
+        let swaps_last_two = |axes: &[usize]| {
+            let r = axes.len();
+            r >= 2 && axes[..r - 2].iter().enumerate().all(|(i, &ax)| ax == i) && axes[r - 2] == r - 1 && axes[r - 1] == r - 2
+        };
+        let mut bt = eb;
+        let b = loop {
+            if let Some(x) = self.find_in(bt, |nd| match nd { Node::Permute { x, axes } if swaps_last_two(axes) => Some(*x), _ => None }) { break x; }
+            bt = self.reshape_of(bt)?;
+        };
+        let bs = self.const_shape(b)?;
+        if bs.len() < 2 || bs[bs.len() - 2] != k || bs[bs.len() - 1] != n { return None; }
+        // NT on a stored tensor: b is itself `w.t()` (Linear::forward hands W.t() to dot, which transposes it again)
+        let (b, trans_b) = match self.find_in(b, |nd| match nd { Node::Permute { x, axes } if swaps_last_two(axes) => Some(*x), _ => None }) {
+            Some(w) => (w, true),
+            None => (b, false),
+        };
+        let dt = self.dtype(b);
+        if self.dtype(a) != dt || self.dtype(cid) != dt || !matches!(dt, DType::F32 | DType::BF16 | DType::F16 | DType::I32) { return None; }
+        Some(MatMulX { a, b, m, n, k, batch: batch_dims.iter().product(), trans_b, b_shared, dtype: dt })
+    }
+    fn match_matmul_scaled(&self, cid: ClassId) -> Option<(MatMulX, f32)> {
+        if let Some(mm) = self.match_matmul_x(cid) { return Some((mm, 1.0)); }
+        let (x, k) = self.binary_const(cid, BOp::Mul)?;
+        Some((self.match_matmul_x(x)?, k as f32))
+    }
+    /// relu(e) = e.cmpgt(0) * e (tensor/elementwise.rs:289-293)
+    fn relu_of(&self, c: ClassId) -> Option<ClassId> {
+        let (x, y) = self.binary_of(c, BOp::Mul)?;
+        for (mask, e) in [(x, y), (y, x)] {
+            let mask = self.cast_src(mask).unwrap_or(mask);
+            if let Some((l, r)) = self.binary_of(mask, BOp::Cmpgt) { if self.same(l, e) && self.const_value(r) == Some(0.0) { return Some(e); } }
+        }
+        None
+    }
+    /// tanh(u) = ((u+u).exp() - 1) / ((u+u).exp() + 1) (elementwise.rs:585-588)
+    fn tanh_of(&self, c: ClassId) -> Option<ClassId> {
+        let (num, den) = self.binary_of(c, BOp::Div)?;
+        let (e1, one1) = self.binary_const(num, BOp::Sub)?;
+        let (e2, one2) = self.binary_const(den, BOp::Add)?;
+        if !self.same(e1, e2) || (one1 - 1.0).abs() > 1e-6 || (one2 - 1.0).abs() > 1e-6 { return None; }
+        let (u1, u2) = self.binary_of(self.unary_of(e1, UOp::Exp)?, BOp::Add)?;
+        self.same(u1, u2).then_some(u1)
+    }
+    /// gelu(z) = z * 0.5 * (tanh((z + z*z*z*0.044715) * sqrt(2/pi)) + 1) (elementwise.rs:168-170)
+    fn gelu_of(&self, c: ClassId) -> Option<ClassId> {
+        let (l, r) = self.binary_of(c, BOp::Mul)?;
+        let (z, half) = self.binary_const(l, BOp::Mul)?;
+        let (t, one) = self.binary_const(r, BOp::Add)?;
+        if !near(half, 0.5) || !near(one, 1.0) { return None; }
+        let (inner, c0) = self.binary_const(self.tanh_of(t)?, BOp::Mul)?;
+        if !near(c0, 0.797_884_560_802_865_4) { return None; }
+        let (z1, cube_term) = self.binary_of(inner, BOp::Add)?;
+        let (cube, c1) = self.binary_const(cube_term, BOp::Mul)?;
+        let (zz, z3) = self.binary_of(cube, BOp::Mul)?;
+        let (za, zb) = self.binary_of(zz, BOp::Mul)?;
+        (near(c1, 0.044_715) && [z1, z3, za, zb].iter().all(|&q| self.same(q, z))).then_some(z)
+    }
+    fn match_linear(&self, cid: ClassId, wanted: &BTreeSet<ClassId>) -> Option<B200Match> {
+        let (e, act) = if let Some(z) = self.gelu_of(cid) { (z, 2) } else if let Some(z) = self.relu_of(cid) { (z, 1) } else { (cid, 0) };
+        let (mut core, mut bias) = (e, None);
+        if let Some((x, y)) = self.binary_of(e, BOp::Add) {
+            for (lhs, rhs) in [(x, y), (y, x)] {
+                if bias.is_some() || self.expand_of(rhs).is_none() { continue; }
+                let src = self.unbroadcast(rhs);
+                let n = *self.const_shape(e)?.last()?;
+                if self.const_shape(src).as_deref() == Some(&[n][..]) && self.match_matmul_scaled(lhs).is_some() { core = lhs; bias = Some(src); }
+            }
+        }
+        if act != 0 && bias.is_none() { return None; }
+        let (mm, alpha) = self.match_matmul_scaled(core)?;
+        if let Some(b) = bias { if self.dtype(b) != mm.dtype { return None; } }
+        let epi = match (bias.is_some(), act) { (false, _) => EPI_NONE, (true, 2) => EPI_BIAS_GELU, (true, 1) => EPI_BIAS_RELU, _ => EPI_BIAS };
+        let preact = act == 2 && wanted.contains(&e);
+        let gemm = ZyxbGemmDesc {
+            dtype: mm.dtype as i32, m: mm.m, n: mm.n, k: mm.k, batch: mm.batch, trans_a: 0, trans_b: mm.trans_b as i32,
+            stride_a: (mm.m * mm.k) as i64, stride_b: if mm.b_shared { 0 } else { (mm.k * mm.n) as i64 }, stride_c: (mm.m * mm.n) as i64,
+            epilogue: epi, store_preact: preact as i32, alpha, ..Default::default()
+        };
+        let mut inputs = vec![mm.a, mm.b];
+        inputs.extend(bias);
+        let mut outputs = vec![cid];
+        if preact { outputs.push(e); }
+        Some(B200Match { pattern: "matmul", inputs, outputs, desc: ZyxbKernelDesc { kind: ZYXB_KIND_GEMM, u: ZyxbDescUnion { gemm } }, numel: Vec::new() })
+    }
+
+    // ---- row kernels ---------------------------------------------------------------------------------------------------------
+    fn row_desc(&self, op: i32, x: ClassId) -> Option<ZyxbRowreduceDesc> {
+        let s = self.const_shape(x)?;
+        let cols = *s.last()?;
+        matches!(self.dtype(x), DType::F32 | DType::BF16 | DType::F16)
+            .then(|| ZyxbRowreduceDesc { op, dtype: self.dtype(x) as i32, rows: s.iter().product::<Dim>() / cols, cols, correction: 1, ..Default::default() })
+    }
+    fn row_match(&self, pattern: &'static str, rowreduce: ZyxbRowreduceDesc, inputs: Vec<ClassId>, out: ClassId) -> B200Match {
+        B200Match { pattern, inputs, outputs: vec![out], desc: ZyxbKernelDesc { kind: ZYXB_KIND_ROWREDUCE, u: ZyxbDescUnion { rowreduce } }, numel: Vec::new() }
+    }
+    fn keepdim_src(&self, c: ClassId) -> ClassId { self.expand_of(c).unwrap_or(c) }
+    /// c = uop(x - Expand{max_keepdim(x)}) -> x
+    fn shifted(&self, c: ClassId, uop: Option<UOp>) -> Option<ClassId> {
+        let d = match uop { Some(u) => self.unary_of(c, u)?, None => c };
+        let (x, mx) = self.binary_of(d, BOp::Sub)?;
+        let src = self.reduce_last(self.keepdim_src(mx), BOp::Max)?;
+        self.same(src, x).then(|| self.canon(x))
+    }
+    /// softmax (tensor/mod.rs:1457-1461)
+    fn match_softmax(&self, cid: ClassId) -> Option<B200Match> {
+        let (e, s) = self.binary_of(cid, BOp::Div)?;
+        self.expand_of(s)?;
+        if !self.same(self.reduce_last(self.keepdim_src(s), BOp::Add)?, e) { return None; }
+        let x = self.shifted(e, Some(UOp::Exp))?;
+        Some(self.row_match("softmax", self.row_desc(RR_SOFTMAX, x)?, vec![x], cid))
+    }
+    /// ln_softmax (tensor/mod.rs:1427-1431)
+    fn match_ln_softmax(&self, cid: ClassId) -> Option<B200Match> {
+        let (m, l) = self.binary_of(cid, BOp::Sub)?;
+        self.expand_of(l)?;
+        let e = self.reduce_last(self.unary_of(self.keepdim_src(l), UOp::Ln)?, BOp::Add)?;
+        if !self.same(self.unary_of(e, UOp::Exp)?, m) { return None; }
+        let x = self.shifted(m, None)?;
+        Some(self.row_match("ln_softmax", self.row_desc(RR_LN_SOFTMAX, x)?, vec![x], cid))
+    }
+    /// mean over the last axis: sum / const(n) (reduce_ops.rs:104-112) -> (x, n)
+    fn mean_last(&self, c: ClassId) -> Option<(ClassId, f64)> {
+        let d = match self.reshape_of(c) { Some(r) if self.numel_of(r) == self.numel_of(c) => r, _ => c };
+        let (s, n) = self.binary_const(d, BOp::Div)?;
+        Some((self.reduce_last(s, BOp::Add)?, n))
+    }
+    /// LayerNorm::forward (zyx-nn/src/layer_norm.rs:117-131)
+    fn match_layernorm(&self, cid: ClassId) -> Option<B200Match> {
+        let cols = *self.const_shape(cid)?.last()?;
+        let (mut c, mut weight, mut bias) = (cid, None, None);
+        for (op, slot) in [(BOp::Add, &mut bias), (BOp::Mul, &mut weight)] {
+            if let Some((x, p)) = self.binary_of(c, op) {
+                let src = self.unbroadcast(p);
+                if self.expand_of(p).is_some() && self.const_shape(src).as_deref() == Some(&[cols][..]) && self.const_value(src).is_none() { *slot = Some(src); c = x; }
+            }
+        }
+        let (centred, denom) = self.binary_of(c, BOp::Div)?;
+        let (x, mean) = self.binary_of(centred, BOp::Sub)?;
+        let x = self.canon(x);
+        if !self.same(self.mean_last(self.keepdim_src(mean))?.0, x) { return None; }
+        let (var, eps) = self.binary_const(self.unary_of(self.keepdim_src(denom), UOp::Sqrt)?, BOp::Add)?;
+        let (sq, d) = self.mean_last(var)?;
+        let (l, r) = self.binary_of(sq, BOp::Mul)?;
+        if !self.same(l, r) || !self.same(l, centred) { return None; }
+        let mut desc = self.row_desc(RR_LAYERNORM, x)?;
+        desc.eps = eps as f32;
+        desc.correction = if near(d, cols as f64 - 1.0) { 1 } else { (cols as f64 - d).round() as i32 };
+        desc.has_weight = weight.is_some() as i32;
+        desc.has_bias = bias.is_some() as i32;
+        Some(self.row_match("layernorm", desc, [Some(x), weight, bias].into_iter().flatten().collect(), cid))
+    }
+    fn is_broadcast_product(&self, c: ClassId) -> bool {
+        let c = self.cast_src(c).unwrap_or(c);
+        matches!(self.binary_of(c, BOp::Mul), Some((x, y)) if self.expand_of(x).is_some() && self.expand_of(y).is_some())
+    }
+    fn match_reduce(&self, cid: ClassId) -> Option<B200Match> {
+        if let Some((x, _)) = self.mean_last(cid) { if let Some(d) = self.row_desc(RR_MEAN, x) { return Some(self.row_match("mean", d, vec![x], cid)); } }
+        for (rop, rr, name) in [(BOp::Add, RR_SUM, "sum"), (BOp::Max, RR_MAX, "max")] {
+            if let Some(x) = self.reduce_last(cid, rop) {
+                if self.dtype(cid) != self.dtype(x) || self.is_broadcast_product(x) { continue; }
+                if let Some(d) = self.row_desc(rr, x) { return Some(self.row_match(name, d, vec![x], cid)); }
+            }
+        }
+        None
+    }
+
+    // ---- optimizer updates -------------------------------------------------------------------------------------------------
+    /// p' = (p - g * lr).cast(p.dtype) (zyx-optim/src/sgd.rs:79-82)
+    fn match_sgd(&self, cid: ClassId) -> Option<Update> {
+        let (p, step) = self.binary_of(self.canon(cid), BOp::Sub)?;
+        let (g, lr) = self.binary_const(step, BOp::Mul)?;
+        (self.is_leaf(p) && self.const_shape(g) == self.const_shape(p)).then_some(Update {
+            algo: OPT_SGD, p, g, m: None, v: None, p_new: cid, m_new: None, v_new: None, lr, wd: 0.0, b1: 0.0, b2: 0.0, eps: 0.0, bc1: 0.0, bc2: 0.0, first: false })
+    }
+    /// AdamW::update for one parameter (zyx-optim/src/adamw.rs:58-95)
+    fn match_adamw(&self, cid: ClassId) -> Option<Update> {
+        let (mut c, mut wd) = (cid, 0.0);
+        if let Some((x, k)) = self.binary_const(c, BOp::Mul) { if !self.is_leaf(x) { wd = 1.0 - k; c = x; } }      // p * (1 - lr*wd)
+        let (p, step) = self.binary_of(self.canon(c), BOp::Sub)?;
+        if !self.is_leaf(p) { return None; }
+        let (mh, den) = self.binary_of(step, BOp::Div)?;                     // mh / ((sqrt(vh) + eps) * lr)
+        let (root_eps, lr) = self.binary_const(den, BOp::Mul)?;
+        let (root, eps) = self.binary_const(root_eps, BOp::Add)?;
+        let vh = self.unary_of(root, UOp::Sqrt)?;
+        let ((m_new, bc1), (v_new, bc2)) = (self.binary_const(mh, BOp::Div)?, self.binary_const(vh, BOp::Div)?);
+        // m' = m*b1 + g*(1-b1), or g*(1-b1) alone on the first step (adamw.rs:60-71); v' alike with g*g
+        let moment = |mc: ClassId, squared: bool| -> Option<(Option<ClassId>, f64, ClassId)> {
+            let grad_term = |t: ClassId| -> Option<(ClassId, f64)> {
+                let (x, om) = self.binary_const(t, BOp::Mul)?;
+                if !squared { return Some((x, om)); }
+                let (a, b) = self.binary_of(x, BOp::Mul)?;
+                self.same(a, b).then_some((a, om))
+            };
+            if let Some((l, r)) = self.binary_of(mc, BOp::Add) {
+                if let (Some((state, _)), Some((g, om))) = (self.binary_const(l, BOp::Mul), grad_term(r)) { if self.is_leaf(state) { return Some((Some(state), 1.0 - om, g)); } }
+            }
+            grad_term(mc).map(|(g, om)| (None, 1.0 - om, g))
+        };
+        let ((m, b1, g1), (v, b2, g2)) = (moment(m_new, false)?, moment(v_new, true)?);
+        if !self.same(g1, g2) || m.is_some() != v.is_some() { return None; }
+        Some(Update { algo: OPT_ADAMW, p, g: g1, m, v, p_new: cid, m_new: Some(m_new), v_new: Some(v_new), lr, wd: if wd != 0.0 { wd / lr } else { 0.0 },
+                      b1, b2, eps, bc1, bc2, first: m.is_none() })
+    }
+
+    /// Everything the device's match_graph needs: `order` is topo_sort_classes_without_kernels of the outputs, `wanted` the
+    /// outputs themselves (classes other consumers read).  Optimizer updates of one dtype and one set of hyper-parameters become
+    /// one multi-tensor program.
+    pub(crate) fn match_b200(&self, order: &[ClassId], wanted: &BTreeSet<ClassId>) -> Vec<B200Match> {
+        let mut out = Vec::new();
+        let mut updates: Vec<Update> = Vec::new();
+        for &cid in order {
+            if wanted.contains(&cid) {
+                if let Some(u) = self.match_adamw(cid).or_else(|| self.match_sgd(cid)) { updates.push(u); continue; }
+            }
+            let m = self.match_linear(cid, wanted).or_else(|| self.match_softmax(cid)).or_else(|| self.match_ln_softmax(cid))
+                .or_else(|| self.match_layernorm(cid)).or_else(|| self.match_reduce(cid));
+            out.extend(m);
+        }
+        let mut used = vec![false; updates.len()];
+        for i in 0..updates.len() {
+            if used[i] { continue; }
+            let h = updates[i];
+            let same_group = |u: &Update| u.algo == h.algo && self.dtype(u.p) == self.dtype(h.p) && u.first == h.first
+                && (u.lr, u.wd, u.b1, u.b2, u.eps, u.bc1, u.bc2) == (h.lr, h.wd, h.b1, h.b2, h.eps, h.bc1, h.bc2);
+            let (mut p, mut g, mut ms, mut vs, mut outs, mut numel) = (vec![], vec![], vec![], vec![], vec![], vec![]);
+            for j in i..updates.len() {
+                let u = updates[j];
+                if used[j] || !same_group(&u) { continue; }
+                used[j] = true;
+                p.push(u.p); g.push(u.g); numel.push(self.numel_of(u.p).unwrap_or(0));
+                outs.push(u.p_new);
+                if u.algo != OPT_SGD { ms.extend(u.m); vs.extend(u.v); outs.extend(u.m_new); outs.extend(u.v_new); }
+            }
+            let optim = ZyxbOptimDesc { algo: h.algo, dtype: self.dtype(h.p) as i32, n_tensors: p.len() as i32, numel: std::ptr::null(), lr: h.lr as f32,
+                                        weight_decay: h.wd as f32, momentum: 0.0, dampening: 0.0, nesterov: 0, maximize: 0, beta1: h.b1 as f32,
+                                        beta2: h.b2 as f32, eps: h.eps as f32, grad_scale: 0.0, standard: 0 };
+            let mut inputs = p;
+            inputs.extend(g); inputs.extend(ms); inputs.extend(vs);
+            out.push(B200Match { pattern: if h.algo == OPT_SGD { "sgd" } else { "adamw" }, inputs, outputs: outs,
+                                 desc: ZyxbKernelDesc { kind: ZYXB_KIND_OPTIM, u: ZyxbDescUnion { optim } }, numel });
+        }
+        out
+    }
+}
