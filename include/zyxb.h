@@ -361,8 +361,11 @@ int32_t zyxb_device_status(zyxb_ctx* ctx, int32_t dev, uint32_t* out_status);
  * issued between capture_begin and capture_end are recorded into a CUDA graph instead of being run, and
  * zyxb_graph_launch replays them with one submission (what makes a 10-launch, 40-microsecond training step
  * launch-latency free).  Inside a capture only zyxb_launch (without wait lists), zyxb_memset and the
- * host-runtime steps built from them are allowed; buffers must stay allocated while the graph lives; the step
- * counter of an optimizer program is frozen at its value at capture time (SGD does not use it). */
+ * host-runtime steps built from them are allowed: zyxb_alloc / free / h2d / d2h / d2d / sync / device_sync and a launch with a
+ * wait list are refused with a message while a capture is open.  Buffers must stay allocated while the graph lives.  A
+ * captured launch freezes its kernel parameters, so an optimizer program whose update depends on its step counter - SGD with
+ * momentum (the first step initialises the buffer, sgd.rs:66-72), Adam and AdamW (bias corrections) - is refused inside a
+ * capture: launch it after zyxb_graph_launch.  Plain SGD is captured; a captured launch does not advance the step counter. */
 int32_t zyxb_capture_begin(zyxb_ctx* ctx, int32_t dev);
 int32_t zyxb_capture_end(zyxb_ctx* ctx, int32_t dev, uint32_t* out_graph);
 int32_t zyxb_graph_launch(zyxb_ctx* ctx, int32_t dev, uint32_t graph, const zyxb_event* wait, int32_t n_wait, zyxb_event* out_event);
@@ -374,8 +377,9 @@ int32_t zyxb_graph_release(zyxb_ctx* ctx, int32_t dev, uint32_t graph);
  * run: a zyx plan being replayed inside a latency-critical serving loop, a host that has handed all device
  * memory to its own pool so that cudaMalloc would fail, or code running where cudaMalloc's implicit device
  * synchronisation is not acceptable.  The partial sums go to a fixed array inside the loaded library
- * (1 Mi floats = 4 MiB per GPU, resident from the moment the library is loaded on that GPU until the process
- * exits) instead of the context's scratch buffer, and the call itself performs no cudaMalloc / cudaFree and
+ * (1 Mi floats = 4 MiB per GPU, resident once the CUDA module that holds it has been loaded on that GPU - with
+ * CUDA's lazy module loading that can be as late as the first call, so make the first call during set-up - until
+ * the process exits) instead of the context's scratch buffer, and the call itself performs no cudaMalloc / cudaFree and
  * calls no allocating library routine; x and y are existing pool buffers.
  *   - limit: cols <= 1 048 576 (zyxb_colsum_static_capacity); larger shapes are refused with
  *     IncorrectKernelArg and a message naming the limit — use a ZYXB_RR_COLSUM program for those;

@@ -148,7 +148,7 @@ int32_t zyxb_st_close(zyxb_st_file* f);
 const char* zyxb_st_last_error(void);   /* of the calling thread's last failed zyxb_st_* call */
 
 /* Checkpoints of the plans: parameters ("<name>"), optimizer state ("optim.m.<name>", "optim.v.<name>" or
- * "optim.buf.<name>") and the step counter ("optim.t", one U32) in one safetensors file, names in Module::iter_tensors
+ * "optim.buf.<name>") and the step counter ("optim.t", one U64; a U32 is accepted when reading) in one safetensors file, names in Module::iter_tensors
  * order (e.g. "attn.q_proj.weight"; "layers.0.weight" for the Linear stack).  Loading a file written by zyx itself
  * works when its labels match; tensors absent from the file are left untouched and counted in *out_missing. */
 int32_t zyxb_mlp_save(zyxb_mlp* mlp, const char* path);

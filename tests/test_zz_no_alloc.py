@@ -3,8 +3,10 @@
 Some callers of this library may not allocate while they run — a plan replayed in a serving loop with a
 fixed memory budget, or a host whose own pool already owns all device memory — so this entry point keeps
 its partial sums in a fixed array inside the library instead of the context's scratch buffer.  The test
-checks it against the ordinary ZYXB_RR_COLSUM program on two calls in a row (the second call finds the
-first call's partials still in the array), and that a shape beyond the fixed capacity is refused.
+checks it against the ordinary ZYXB_RR_COLSUM program and against the CPU oracle on two calls in a row (the
+second call finds the first call's partials still in the array), that the pool's free bytes do not move
+across a call once the array's address has been looked up, and that a shape beyond the fixed capacity is
+refused.
 It is collected last so that a run which stops at the first failure has already run everything else.
 """
 import ctypes as C
@@ -12,6 +14,7 @@ import ctypes as C
 import numpy as np
 import pytest
 
+from oracle import oracle as zo
 from tests.parity import TOL_BF16, TOL_F32
 from zyx_b200 import _lib as L
 from zyx_b200 import backend as B
@@ -34,13 +37,16 @@ def _colsum_static(sess, dtype, x_buf, y_buf, rows, cols):
         raise B.BackendError(st, lib.zyxb_last_error(be.ctx).decode())
 
 
-@pytest.mark.parametrize("dtype,tol", [(L.F32, TOL_F32), (L.BF16, TOL_BF16)])
-def test_two_calls_match_the_colsum_program(sess, dtype, tol):
+@pytest.mark.parametrize("dtype,tol", [(L.F32, TOL_F32), (L.BF16, TOL_BF16), (L.F16, TOL_BF16)])
+@pytest.mark.parametrize("shapes", [[(777, 1032), (300, 4096)],      # vector path; the second call reuses dirty scratch
+                                    [(129, 1031), (64, 1031)],       # a width no 128-bit vector divides: the scalar path
+                                    [(3, 1 << 20), (2, 1 << 20)]])   # the widest shape the array takes: one partial row per column
+def test_two_calls_match_the_colsum_program(sess, dtype, tol, shapes):
     rng = np.random.default_rng(21)
     pool, dev = sess.pool, sess.device
-    for call, (rows, cols) in enumerate([(777, 1032), (300, 4096)]):       # different shapes: the second reuses dirty scratch
+    for call, (rows, cols) in enumerate(shapes):
         xf = rng.standard_normal((rows, cols)).astype(np.float32)
-        x = xf if dtype == L.F32 else _bf16(xf)
+        x = xf if dtype == L.F32 else zo.to_bits(xf, dtype)
         es = x.dtype.itemsize
         bx = pool.upload(x)
         by_ref, _ = pool.allocate(cols * es)
@@ -48,13 +54,21 @@ def test_two_calls_match_the_colsum_program(sess, dtype, tol):
         prog = dev.create_program(B.rowreduce_desc(L.RR_COLSUM, dtype, rows, cols))
         try:
             dev.launch(prog, [bx, by_ref])
+            if call == 1:
+                dev.sync()
+                free_before = pool.free_bytes()
             _colsum_static(sess, dtype, bx, by_new, rows, cols)
+            if call == 1:                                                    # the array's address is known by now: nothing is allocated
+                dev.sync()
+                assert pool.free_bytes() == free_before
             ref, new = pool.download(by_ref, (cols,), x.dtype), pool.download(by_new, (cols,), x.dtype)
-            if dtype != L.F32:
-                ref, new = _f32(ref), _f32(new)
-            scale = np.sqrt((xf.astype(np.float64) ** 2).sum(0))             # a sum that cancels is measured against |x|_2 / 10
+            want = zo.to_f32(zo.colsum(dtype, x), dtype).astype(np.float64)
+            ref, new = zo.to_f32(ref, dtype), zo.to_f32(new, dtype)
+            scale = np.sqrt((zo.to_f32(x, dtype).astype(np.float64) ** 2).sum(0))    # a sum that cancels is measured against |x|_2 / 10
             err = np.abs(new.astype(np.float64) - ref) / np.maximum(np.abs(ref), 0.1 * scale)
             assert float(err.max()) <= tol, (call, float(err.max()))
+            err = np.abs(new.astype(np.float64) - want) / np.maximum(np.abs(want), 0.1 * scale)
+            assert float(err.max()) <= tol, ("oracle", call, float(err.max()))
         finally:
             dev.release(prog)
             for b in (bx, by_ref, by_new):

@@ -214,6 +214,11 @@ class Device:
     def set_step(self, program_id, t):
         self.be._check(self.be.lib.zyxb_program_set_step(self.be.ctx, self.dev, program_id, int(t)))
 
+    def get_step(self, program_id):
+        t = C.c_uint64()
+        self.be._check(self.be.lib.zyxb_program_get_step(self.be.ctx, self.dev, program_id, C.byref(t)))
+        return t.value
+
     def sync(self):
         self.be._check(self.be.lib.zyxb_device_sync(self.be.ctx, self.dev))
 

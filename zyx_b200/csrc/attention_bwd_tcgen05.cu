@@ -526,12 +526,11 @@ int launch_attention_bwd(const zyxb_attention_desc& d, void* const* args, const 
   p.scale = d.scale > 0.0f ? d.scale : 1.0f / sqrtf((float)d.head_dim);
   p.scale_log2 = p.scale * 1.4426950408889634f;
   p.causal = d.causal ? 1 : 0; p.rn = lc.round_nearest ? 1 : 0; p.is_bf16 = bf16 ? 1 : 0; p.status = lc.status_word;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attn_bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dqk::SMEM_TOTAL);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_bwd_dkdv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dkv::SMEM_TOTAL);
+  static uint64_t configured_dq = 0, configured_dkdv = 0;
+  {
+    cudaError_t e = ensure_dynamic_smem(attn_bwd_dq_kernel, dqk::SMEM_TOTAL, &configured_dq);
+    if (e == cudaSuccess) e = ensure_dynamic_smem(attn_bwd_dkdv_kernel, dkv::SMEM_TOTAL, &configured_dkdv);
     if (e != cudaSuccess) { err = std::string("attention backward: ") + cudaGetErrorString(e); return ZYXB_ERR_KERNEL_LAUNCH; }
-    configured = true;
   }
   const dim3 grid((unsigned)(d.seq / 128), (unsigned)(d.batch * d.heads));
   attn_bwd_dq_kernel<<<grid, AB_THREADS, dqk::SMEM_TOTAL, lc.stream>>>(q128, do128, k64, v64, p);

@@ -354,11 +354,10 @@ int launch_attention(const zyxb_attention_desc& d, void* const* args, const uint
   const float scale = d.scale > 0.0f ? d.scale : 1.0f / sqrtf((float)d.head_dim);
   p.scale_log2 = scale * 1.4426950408889634f;
   p.causal = d.causal ? 1 : 0; p.rn = lc.round_nearest ? 1 : 0; p.is_bf16 = bf16 ? 1 : 0; p.status = lc.status_word;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_SMEM_TOTAL);
+  static uint64_t configured = 0;
+  {
+    cudaError_t e = ensure_dynamic_smem(attn_fwd_kernel, AT_SMEM_TOTAL, &configured);
     if (e != cudaSuccess) { err = std::string("attention: ") + cudaGetErrorString(e); return ZYXB_ERR_KERNEL_LAUNCH; }
-    configured = true;
   }
   const dim3 grid((unsigned)(d.seq / AT_BM), (unsigned)(d.batch * d.heads));
   attn_fwd_kernel<<<grid, AT_THREADS, AT_SMEM_TOTAL, lc.stream>>>(mq, mk, mv, p);

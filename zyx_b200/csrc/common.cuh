@@ -231,3 +231,17 @@ __device__ __forceinline__ A group_reduce(A v, Op op, A* scratch, A identity) {
 }
 
 }  // namespace zyxb
+
+// cudaFuncAttributeMaxDynamicSharedMemorySize is a per-device setting of a kernel: a context that drives several GPUs must raise
+// it on each of them.  `mask` (one static word per kernel instantiation) remembers the CUDA devices already configured.
+template <class Kernel>
+inline cudaError_t ensure_dynamic_smem(Kernel kern, int bytes, uint64_t* mask) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  const uint64_t bit = 1ull << (dev & 63);
+  if (*mask & bit) return cudaSuccess;
+  e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e == cudaSuccess) *mask |= bit;
+  return e;
+}

@@ -53,7 +53,10 @@ struct Device {
   std::vector<uint32_t> free_program_ids;
   std::unordered_map<uint64_t, cudaEvent_t> events;
   uint64_t next_event = 1;
-  std::multimap<uint64_t, void*> cache;   // freed blocks by capacity
+  // freed blocks by capacity; `ready` was recorded on the compute stream when the block was freed (after the copy and comm
+  // streams had been ordered before it): whoever reuses the block on another stream waits for it first
+  struct CachedBlock { void* ptr; cudaEvent_t ready; };
+  std::multimap<uint64_t, CachedBlock> cache;
   uint64_t cached_bytes = 0;
   void* scratch = nullptr;
   size_t scratch_bytes = 0;
@@ -92,6 +95,11 @@ int cuda_fail(zyxb_ctx* ctx, int status, const char* what, cudaError_t e) {
   return fail(ctx, status, std::string(what) + ": " + cudaGetErrorString(e));
 }
 
+// Inside a capture (zyxb_capture_begin .. zyxb_capture_end) only launches without wait lists and memsets are recorded; calls
+// that allocate, copy to or from the host, or block would invalidate the capture with an opaque CUDA error, so they are refused.
+#define NOT_WHILE_CAPTURING(name, status) \
+  if (D.capturing) return fail(ctx, status, std::string(name) + ": not allowed between zyxb_capture_begin and zyxb_capture_end")
+
 #define DEV_OR_FAIL(status)                                                              \
   if (!ctx) return ZYXB_ERR_INITIALIZATION;                                              \
   if (dev < 0 || dev >= (int)ctx->devs.size()) return fail(ctx, status, "no such device"); \
@@ -104,6 +112,14 @@ Buffer* get_buffer(Device& D, uint32_t id) {
 }
 
 uint64_t round_up(uint64_t v, uint64_t a) { return (v + a - 1) / a * a; }
+
+// [offset, offset + bytes) lies inside [0, limit), without letting offset + bytes wrap around
+bool range_ok(uint64_t offset, uint64_t bytes, uint64_t limit) { return offset <= limit && bytes <= limit - offset; }
+// (offset + count) * es <= limit for element counts supplied by the caller
+bool elems_ok(uint64_t offset, uint64_t count, uint64_t es, uint64_t limit) {
+  uint64_t sum = 0, bytes = 0;
+  return !__builtin_add_overflow(offset, count, &sum) && !__builtin_mul_overflow(sum, es, &bytes) && bytes <= limit;
+}
 
 // Events named in a wait list are consumed: the stream waits for them and they are destroyed,
 // as zyx moves `Vec<Event>` into the backend call.
@@ -148,7 +164,14 @@ cudaError_t device_malloc(Device& D, uint64_t capacity, void** out) {
   auto it = D.cache.lower_bound(capacity);
   // reuse a cached block when it is not wastefully larger than the request
   if (it != D.cache.end() && it->first <= capacity + capacity / 4 + (1u << 20)) {
-    *out = it->second;
+    *out = it->second.ptr;
+    if (it->second.ready) {
+      // kernels queued before the free may still use the block: uploads (copy stream) and collectives (comm stream) into
+      // its new owner go behind them; the compute stream is in order by itself
+      cudaStreamWaitEvent(D.copy, it->second.ready, 0);
+      cudaStreamWaitEvent(D.comm_stream, it->second.ready, 0);
+      cudaEventDestroy(it->second.ready);
+    }
     D.cached_bytes -= it->first;
     D.cache.erase(it);
     return cudaSuccess;
@@ -156,7 +179,7 @@ cudaError_t device_malloc(Device& D, uint64_t capacity, void** out) {
   cudaError_t e = cudaMalloc(out, capacity);
   if (e == cudaErrorMemoryAllocation) {
     cudaGetLastError();
-    for (auto& kv : D.cache) cudaFree(kv.second);   // give the cache back and retry once
+    for (auto& kv : D.cache) { if (kv.second.ready) cudaEventDestroy(kv.second.ready); cudaFree(kv.second.ptr); }   // give the cache back and retry once
     D.cache.clear(); D.cached_bytes = 0;
     e = cudaMalloc(out, capacity);
   }
@@ -249,7 +272,7 @@ int32_t zyxb_shutdown(zyxb_ctx* ctx) {
     for (auto& g : D.graphs) if (g.first) cudaGraphExecDestroy(g.first);
     for (auto& kv : D.events) cudaEventDestroy(kv.second);
     for (auto& b : D.buffers) if (b.live && b.ptr && !b.is_view && !b.is_variable) cudaFree(b.ptr);
-    for (auto& kv : D.cache) cudaFree(kv.second);
+    for (auto& kv : D.cache) { if (kv.second.ready) cudaEventDestroy(kv.second.ready); cudaFree(kv.second.ptr); }
     if (D.scratch) cudaFree(D.scratch);
     if (D.status_word) cudaFree(D.status_word);
     if (D.flush_buf) cudaFree(D.flush_buf);
@@ -307,6 +330,7 @@ int32_t zyxb_free_bytes(zyxb_ctx* ctx, int32_t dev, uint64_t* out_bytes) {
 int32_t zyxb_alloc(zyxb_ctx* ctx, int32_t dev, uint64_t bytes, uint32_t* out_buf, zyxb_event* out_event) {
   DEV_OR_FAIL(ZYXB_ERR_MEMORY_ALLOCATION);
   if (!out_buf) return fail(ctx, ZYXB_ERR_MEMORY_ALLOCATION, "out_buf is null");
+  NOT_WHILE_CAPTURING("zyxb_alloc", ZYXB_ERR_MEMORY_ALLOCATION);
   const uint64_t capacity = round_up(bytes == 0 ? 1 : bytes, 512);
   void* ptr = nullptr;
   cudaError_t e = device_malloc(D, capacity, &ptr);
@@ -326,6 +350,7 @@ int32_t zyxb_free(zyxb_ctx* ctx, int32_t dev, uint32_t buf, const zyxb_event* wa
   DEV_OR_FAIL(ZYXB_ERR_MEMORY_DEALLOCATION);
   Buffer* b = get_buffer(D, buf);
   if (!b) return fail(ctx, ZYXB_ERR_MEMORY_DEALLOCATION, "free: unknown buffer");
+  NOT_WHILE_CAPTURING("zyxb_free", ZYXB_ERR_MEMORY_DEALLOCATION);
   // the block goes back to the cache and may be handed out again at once: order every stream
   // that could still touch it before later work on the compute stream
   int st = wait_and_consume(ctx, D, D.compute, wait, n_wait, ZYXB_ERR_MEMORY_DEALLOCATION);
@@ -333,7 +358,13 @@ int32_t zyxb_free(zyxb_ctx* ctx, int32_t dev, uint32_t buf, const zyxb_event* wa
   if (!b->is_variable && !b->is_view) {
     if ((st = order_streams(ctx, D.copy, D.compute, ZYXB_ERR_MEMORY_DEALLOCATION))) return st;
     if ((st = order_streams(ctx, D.comm_stream, D.compute, ZYXB_ERR_MEMORY_DEALLOCATION))) return st;
-    D.cache.emplace(b->capacity, b->ptr);
+    cudaEvent_t ready = nullptr;
+    if (cudaEventCreateWithFlags(&ready, cudaEventDisableTiming) != cudaSuccess || cudaEventRecord(ready, D.compute) != cudaSuccess) {
+      cudaGetLastError();
+      if (ready) { cudaEventDestroy(ready); ready = nullptr; }
+      cudaStreamSynchronize(D.compute);      // no event to hand on: the block is idle before it enters the cache
+    }
+    D.cache.emplace(b->capacity, Device::CachedBlock{b->ptr, ready});
     D.cached_bytes += b->capacity;
   }
   *b = Buffer();
@@ -346,7 +377,7 @@ int32_t zyxb_buffer_view(zyxb_ctx* ctx, int32_t dev, uint32_t parent, uint64_t o
   Buffer* pb = get_buffer(D, parent);
   if (!pb || pb->is_variable || !out_buf) return fail(ctx, ZYXB_ERR_MEMORY_ALLOCATION, "buffer_view: unknown parent buffer");
   if (offset % 256 != 0) return fail(ctx, ZYXB_ERR_MEMORY_ALLOCATION, "buffer_view: offset must be a multiple of 256 bytes");
-  if (offset + bytes > pb->bytes) return fail(ctx, ZYXB_ERR_MEMORY_ALLOCATION, "buffer_view: range exceeds the parent");
+  if (!range_ok(offset, bytes, pb->bytes)) return fail(ctx, ZYXB_ERR_MEMORY_ALLOCATION, "buffer_view: range exceeds the parent");
   void* ptr = (char*)pb->ptr + offset;
   uint32_t id;
   if (!D.free_buffer_ids.empty()) { id = D.free_buffer_ids.back(); D.free_buffer_ids.pop_back(); }
@@ -371,13 +402,16 @@ int32_t zyxb_h2d(zyxb_ctx* ctx, int32_t dev, const void* src, uint64_t bytes, ui
   DEV_OR_FAIL(ZYXB_ERR_MEMORY_COPY_H2P);
   Buffer* b = get_buffer(D, dst);
   if (!b || b->is_variable) return fail(ctx, ZYXB_ERR_MEMORY_COPY_H2P, "h2d: unknown buffer");
-  if (dst_offset + bytes > b->bytes) return fail(ctx, ZYXB_ERR_MEMORY_COPY_H2P, "h2d: copy exceeds the buffer");
+  if (!range_ok(dst_offset, bytes, b->bytes)) return fail(ctx, ZYXB_ERR_MEMORY_COPY_H2P, "h2d: copy exceeds the buffer");
+  NOT_WHILE_CAPTURING("zyxb_h2d", ZYXB_ERR_MEMORY_COPY_H2P);
   int st = wait_and_consume(ctx, D, D.copy, wait, n_wait, ZYXB_ERR_MEMORY_COPY_H2P);
   if (st) return st;
   // With a wait list the caller has named what the upload depends on, as zyx does (it passes the events of
   // every pending use of dst), and the copy may overlap kernels already queued.  Without one, kernels
   // already enqueued may still read or write dst: the upload goes after them.
-  if (n_wait == 0 && (st = order_streams(ctx, D.compute, D.copy, ZYXB_ERR_MEMORY_COPY_H2P))) return st;
+  int named = 0;
+  for (int i = 0; i < n_wait; ++i) named += wait[i].id != 0;      // null events (e.g. the one zyxb_alloc returns) name nothing
+  if (named == 0 && (st = order_streams(ctx, D.compute, D.copy, ZYXB_ERR_MEMORY_COPY_H2P))) return st;
   if (bytes) {
     cudaError_t e = cudaMemcpyAsync((char*)b->ptr + dst_offset, src, bytes, cudaMemcpyHostToDevice, D.copy);
     if (e != cudaSuccess) return cuda_fail(ctx, ZYXB_ERR_MEMORY_COPY_H2P, "cudaMemcpyAsync h2d", e);
@@ -392,7 +426,8 @@ int32_t zyxb_d2h(zyxb_ctx* ctx, int32_t dev, uint32_t src, uint64_t src_offset, 
   DEV_OR_FAIL(ZYXB_ERR_MEMORY_COPY_P2H);
   Buffer* b = get_buffer(D, src);
   if (!b || b->is_variable) return fail(ctx, ZYXB_ERR_MEMORY_COPY_P2H, "d2h: unknown buffer");
-  if (src_offset + bytes > b->bytes) return fail(ctx, ZYXB_ERR_MEMORY_COPY_P2H, "d2h: copy exceeds the buffer");
+  if (!range_ok(src_offset, bytes, b->bytes)) return fail(ctx, ZYXB_ERR_MEMORY_COPY_P2H, "d2h: copy exceeds the buffer");
+  NOT_WHILE_CAPTURING("zyxb_d2h", ZYXB_ERR_MEMORY_COPY_P2H);
   int st = wait_and_consume(ctx, D, D.compute, wait, n_wait, ZYXB_ERR_MEMORY_COPY_P2H);
   if (st) return st;
   cudaError_t e = cudaSuccess;
@@ -406,11 +441,12 @@ int32_t zyxb_d2d(zyxb_ctx* ctx, int32_t src_dev, uint32_t src, uint64_t src_offs
                  uint64_t bytes, const zyxb_event* wait, int32_t n_wait, zyxb_event* out_event) {
   DEV_OR_FAIL(ZYXB_ERR_MEMORY_COPY_H2P);
   if (src_dev < 0 || src_dev >= (int)ctx->devs.size()) return fail(ctx, ZYXB_ERR_MEMORY_COPY_H2P, "d2d: no such source device");
+  NOT_WHILE_CAPTURING("zyxb_d2d", ZYXB_ERR_MEMORY_COPY_H2P);
   Device& SD = ctx->devs[src_dev];
   Buffer* sb = get_buffer(SD, src);
   Buffer* db = get_buffer(D, dst);
   if (!sb || !db || sb->is_variable || db->is_variable) return fail(ctx, ZYXB_ERR_MEMORY_COPY_H2P, "d2d: unknown buffer");
-  if (src_offset + bytes > sb->bytes || dst_offset + bytes > db->bytes) return fail(ctx, ZYXB_ERR_MEMORY_COPY_H2P, "d2d: copy exceeds a buffer");
+  if (!range_ok(src_offset, bytes, sb->bytes) || !range_ok(dst_offset, bytes, db->bytes)) return fail(ctx, ZYXB_ERR_MEMORY_COPY_H2P, "d2d: copy exceeds a buffer");
   int st = wait_and_consume(ctx, D, D.compute, wait, n_wait, ZYXB_ERR_MEMORY_COPY_H2P);
   if (st) return st;
   cudaError_t e = cudaSuccess;
@@ -427,7 +463,7 @@ int32_t zyxb_memset(zyxb_ctx* ctx, int32_t dev, uint32_t buf, uint64_t offset, i
   DEV_OR_FAIL(ZYXB_ERR_MEMORY_COPY_H2P);
   Buffer* b = get_buffer(D, buf);
   if (!b || b->is_variable) return fail(ctx, ZYXB_ERR_MEMORY_COPY_H2P, "memset: unknown buffer");
-  if (offset + bytes > b->bytes) return fail(ctx, ZYXB_ERR_MEMORY_COPY_H2P, "memset: range exceeds the buffer");
+  if (!range_ok(offset, bytes, b->bytes)) return fail(ctx, ZYXB_ERR_MEMORY_COPY_H2P, "memset: range exceeds the buffer");
   cudaError_t e = cudaMemsetAsync((char*)b->ptr + offset, byte_value, bytes, D.compute);
   if (e != cudaSuccess) return cuda_fail(ctx, ZYXB_ERR_MEMORY_COPY_H2P, "cudaMemsetAsync", e);
   return ZYXB_OK;
@@ -435,6 +471,7 @@ int32_t zyxb_memset(zyxb_ctx* ctx, int32_t dev, uint32_t buf, uint64_t offset, i
 
 int32_t zyxb_sync(zyxb_ctx* ctx, int32_t dev, const zyxb_event* events, int32_t n) {
   DEV_OR_FAIL(ZYXB_ERR_KERNEL_SYNC);
+  NOT_WHILE_CAPTURING("zyxb_sync", ZYXB_ERR_KERNEL_SYNC);
   int status = ZYXB_OK;
   for (int i = 0; i < n; ++i) {
     if (events[i].id == 0) continue;
@@ -461,6 +498,7 @@ int32_t zyxb_release_events(zyxb_ctx* ctx, int32_t dev, const zyxb_event* events
 
 int32_t zyxb_device_sync(zyxb_ctx* ctx, int32_t dev) {
   DEV_OR_FAIL(ZYXB_ERR_KERNEL_SYNC);
+  NOT_WHILE_CAPTURING("zyxb_device_sync", ZYXB_ERR_KERNEL_SYNC);
   cudaError_t e = cudaDeviceSynchronize();
   if (e != cudaSuccess) return cuda_fail(ctx, ZYXB_ERR_KERNEL_SYNC, "cudaDeviceSynchronize", e);
   return ZYXB_OK;
@@ -569,6 +607,16 @@ int32_t zyxb_launch(zyxb_ctx* ctx, int32_t dev, uint32_t prog, const uint32_t* a
   if (prog == 0 || prog >= D.programs.size() || !D.programs[prog].live) return fail(ctx, ZYXB_ERR_KERNEL_LAUNCH, "launch: unknown program");
   if (n_args < 0 || n_args > 4096 || (n_args > 0 && !args)) return fail(ctx, ZYXB_ERR_INCORRECT_KERNEL_ARG, "launch: bad argument list");
   Program& P = D.programs[prog];
+  if (D.capturing) {
+    int named = 0;
+    for (int i = 0; i < n_wait; ++i) named += wait[i].id != 0;
+    if (named) return fail(ctx, ZYXB_ERR_KERNEL_LAUNCH, "launch: a wait list cannot be recorded into a capture");
+    // A captured launch freezes its kernel parameters.  An update that depends on the step (the first-step test of a
+    // momentum buffer, Adam's bias corrections) would replay the captured step for ever.
+    if (P.desc.kind == ZYXB_KIND_OPTIM && (P.desc.u.optim.algo != ZYXB_OPT_SGD || P.desc.u.optim.momentum != 0.0f))
+      return fail(ctx, ZYXB_ERR_KERNEL_LAUNCH, "launch: an optimizer whose update depends on the step counter (SGD with momentum, Adam, AdamW) "
+                                               "cannot be captured; launch it after zyxb_graph_launch instead");
+  }
   std::vector<void*> ptrs(n_args);
   std::vector<uint64_t> sizes(n_args);
   for (int i = 0; i < n_args; ++i) {
@@ -591,7 +639,7 @@ int32_t zyxb_launch(zyxb_ctx* ctx, int32_t dev, uint32_t prog, const uint32_t* a
     case ZYXB_KIND_CONV_WGRAD: st = launch_conv_wgrad(P.desc.u.conv, ptrs.data(), sizes.data(), n_args, lc, err); break;
     case ZYXB_KIND_OPTIM:
       st = launch_optim(P.desc.u.optim, P.numel.data(), P.step + 1, ptrs.data(), sizes.data(), n_args, lc, err);
-      if (st == ZYXB_OK) P.step += 1;
+      if (st == ZYXB_OK && !D.capturing) P.step += 1;     // a captured launch has not run
       break;
     default: st = ZYXB_ERR_KERNEL_LAUNCH; err = "launch: unknown kernel kind";
   }
@@ -607,6 +655,8 @@ int32_t zyxb_colsum_static(zyxb_ctx* ctx, int32_t dev, int32_t dtype, uint32_t x
   if (!bx || !by || bx->is_variable || by->is_variable) return fail(ctx, ZYXB_ERR_INCORRECT_KERNEL_ARG, "colsum_static: unknown buffer");
   const uint64_t es = dtype_size(dtype);
   if (rows != 0 && cols > UINT64_MAX / rows / 8) return fail(ctx, ZYXB_ERR_INCORRECT_KERNEL_ARG, "colsum_static: shape overflows");
+  if (D.capturing && !colsum_static_ready(D.cuda_id))
+    return fail(ctx, ZYXB_ERR_KERNEL_LAUNCH, "colsum_static: the first call on a device looks up the array's address and cannot be captured; call it once during set-up");
   if (bx->bytes < rows * cols * es || by->bytes < cols * es) return fail(ctx, ZYXB_ERR_INCORRECT_KERNEL_ARG, "colsum_static: buffer too small");
   LaunchCtx lc = make_launch_ctx(ctx, D);
   std::string err;
@@ -743,7 +793,7 @@ int32_t zyxb_allreduce_sum(zyxb_ctx* ctx, int32_t dev, uint32_t buf, uint64_t of
   Buffer* b = get_buffer(D, buf);
   if (!b || b->is_variable) return fail(ctx, ZYXB_ERR_INCORRECT_KERNEL_ARG, "allreduce: unknown buffer");
   const uint64_t es = dtype_size(dtype);
-  if ((offset_elems + count) * es > b->bytes) return fail(ctx, ZYXB_ERR_INCORRECT_KERNEL_ARG, "allreduce: range exceeds the buffer");
+  if (!elems_ok(offset_elems, count, es, b->bytes)) return fail(ctx, ZYXB_ERR_INCORRECT_KERNEL_ARG, "allreduce: range exceeds the buffer");
   int st = wait_and_consume(ctx, D, D.comm_stream, wait, n_wait, ZYXB_ERR_KERNEL_LAUNCH);
   if (st) return st;
   // the producer kernels were enqueued on the compute stream before this call
@@ -767,7 +817,8 @@ static int32_t sliced_collective(zyxb_ctx* ctx, int32_t dev, bool gather, uint32
   int rank = 0, world = 1;
   comm_rank(D.comm, &rank, &world);
   const uint64_t es = dtype_size(dtype);
-  if ((offset_elems + count_per_rank * (uint64_t)world) * es > b->bytes) return fail(ctx, ZYXB_ERR_INCORRECT_KERNEL_ARG, std::string(what) + ": range exceeds the buffer");
+  uint64_t all_ranks = 0;
+  if (__builtin_mul_overflow(count_per_rank, (uint64_t)world, &all_ranks) || !elems_ok(offset_elems, all_ranks, es, b->bytes)) return fail(ctx, ZYXB_ERR_INCORRECT_KERNEL_ARG, std::string(what) + ": range exceeds the buffer");
   int st = wait_and_consume(ctx, D, D.comm_stream, wait, n_wait, ZYXB_ERR_KERNEL_LAUNCH);
   if (st) return st;
   if ((st = order_streams(ctx, D.compute, D.comm_stream, ZYXB_ERR_KERNEL_LAUNCH))) return st;   // producers were queued on the compute stream

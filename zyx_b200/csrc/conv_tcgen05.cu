@@ -375,12 +375,11 @@ bool geometry(const zyxb_conv_desc& d, ConvGeom& g, std::string& err) {
 template <int BN, int STAGES, bool IM2COL>
 cudaError_t launch_conv_tc(const CUtensorMap& mx, const CUtensorMap& mw, const ConvTcParams& tp, unsigned grid, cudaStream_t s) {
   using SM = ConvSmem<BN, STAGES>;
-  static bool configured = false;
+  static uint64_t configured = 0;
   auto kern = conv_tc_kernel<BN, STAGES, IM2COL>;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SM::TOTAL);
+  {
+    cudaError_t e = ensure_dynamic_smem(kern, SM::TOTAL, &configured);
     if (e != cudaSuccess) return e;
-    configured = true;
   }
   kern<<<grid, CV_THREADS, SM::TOTAL, s>>>(mx, mw, tp);
   return cudaGetLastError();

@@ -243,12 +243,11 @@ __global__ void conv_wgrad_direct_kernel(const typename Elem<T>::store_t* __rest
 template <int BN, int STAGES>
 cudaError_t launch_conv_wgrad_tc(const CUtensorMap& mdy, const CUtensorMap& mx, const ConvWgParams& wp, unsigned grid, cudaStream_t s) {
   using SM = ConvSmem<BN, STAGES>;
-  static bool configured = false;
+  static uint64_t configured = 0;
   auto kern = conv_wgrad_tc_kernel<BN, STAGES>;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SM::TOTAL);
+  {
+    cudaError_t e = ensure_dynamic_smem(kern, SM::TOTAL, &configured);
     if (e != cudaSuccess) return e;
-    configured = true;
   }
   kern<<<grid, CV_THREADS, SM::TOTAL, s>>>(mdy, mx, wp);
   return cudaGetLastError();

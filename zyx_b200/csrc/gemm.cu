@@ -33,8 +33,13 @@ int validate_gemm(const zyxb_gemm_desc& d, std::string& err) {
 }
 
 // Elements a strided operand spans: the last matrix's offset plus its last row.
+// Computed in 128 bits and saturated, so that huge caller-supplied strides or pitches cannot wrap around into a small value
+// that passes the buffer-size checks below.
 static uint64_t span(uint64_t batch, int64_t stride, uint64_t inner, int64_t stride_inner, uint64_t rows, uint64_t ld, uint64_t cols) {
-  return (batch - 1) * (uint64_t)stride + (inner - 1) * (uint64_t)stride_inner + (rows - 1) * ld + cols;
+  if (stride < 0 || stride_inner < 0) return UINT64_MAX;
+  const unsigned __int128 v = (unsigned __int128)(batch - 1) * (uint64_t)stride + (unsigned __int128)(inner - 1) * (uint64_t)stride_inner +
+                              (unsigned __int128)(rows - 1) * ld + cols;
+  return v > ((unsigned __int128)1 << 60) ? UINT64_MAX : (uint64_t)v;
 }
 
 int launch_gemm(const zyxb_gemm_desc& d, void* const* args, const uint64_t* arg_bytes, int n_args, const LaunchCtx& lc,
@@ -55,9 +60,10 @@ int launch_gemm(const zyxb_gemm_desc& d, void* const* args, const uint64_t* arg_
   p.stride_a = d.stride_a; p.stride_b = d.stride_b;
   p.stride_c = (d.batch > 1 || d.stride_c) ? d.stride_c : (int64_t)(d.m * p.ldc);
   p.stride_a_inner = d.stride_a_inner; p.stride_b_inner = d.stride_b_inner; p.stride_c_inner = d.stride_c_inner;
-  const uint64_t need_a = span(d.batch, p.stride_a, p.batch_inner, p.stride_a_inner, a_rows, p.lda, a_cols) * es;
-  const uint64_t need_b = span(d.batch, p.stride_b, p.batch_inner, p.stride_b_inner, b_rows, p.ldb, b_cols) * es;
-  const uint64_t need_c = span(d.batch, p.stride_c, p.batch_inner, p.stride_c_inner, d.m, p.ldc, d.n) * es;
+  auto bytes_of = [es](uint64_t elems) { return elems == UINT64_MAX ? UINT64_MAX : elems * es; };     // elems <= 2^60, es <= 8
+  const uint64_t need_a = bytes_of(span(d.batch, p.stride_a, p.batch_inner, p.stride_a_inner, a_rows, p.lda, a_cols));
+  const uint64_t need_b = bytes_of(span(d.batch, p.stride_b, p.batch_inner, p.stride_b_inner, b_rows, p.ldb, b_cols));
+  const uint64_t need_c = bytes_of(span(d.batch, p.stride_c, p.batch_inner, p.stride_c_inner, d.m, p.ldc, d.n));
   int i = 0;
   ZYXB_CHECK_ARG(arg_bytes[i] >= need_a, "gemm: A too small"); p.a = args[i++];
   ZYXB_CHECK_ARG(arg_bytes[i] >= need_b, "gemm: B too small"); p.b = args[i++];

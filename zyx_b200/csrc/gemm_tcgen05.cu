@@ -394,12 +394,11 @@ bool gemm_tc_supported(const GemmParams& p, int dtype, const LaunchCtx& lc) {
 template <bool A_MN, bool B_MN, int BN, int STAGES>
 static cudaError_t launch_tc_variant(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& tp, unsigned grid, cudaStream_t s) {
   using SM = TcSmem<BN, STAGES>;
-  static bool configured = false;
+  static uint64_t configured = 0;
   auto kern = gemm_tc_kernel<A_MN, B_MN, BN, STAGES>;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SM::TOTAL);
+  {
+    cudaError_t e = ensure_dynamic_smem(kern, SM::TOTAL, &configured);
     if (e != cudaSuccess) return e;
-    configured = true;
   }
   kern<<<grid, TC_THREADS, SM::TOTAL, s>>>(ma, mb, tp);
   return cudaGetLastError();

@@ -309,11 +309,10 @@ int launch_gemm_tf32x3(const GemmParams& p, const LaunchCtx& lc, std::string& er
   xp.m = (uint32_t)p.m; xp.n = (uint32_t)p.n; xp.k = (uint32_t)p.k; xp.ldc = (uint32_t)p.ldc;
   xp.tiles_m = (uint32_t)((p.m + X3_BM - 1) / X3_BM); xp.tiles_n = (uint32_t)((p.n + X3_BN - 1) / X3_BN);
   xp.alpha = p.alpha; xp.has_bias = p.epilogue == ZYXB_EPI_BIAS ? 1 : 0; xp.status = lc.status_word;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tf32x3_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, X3_SMEM_TOTAL);
+  static uint64_t configured = 0;
+  {
+    cudaError_t e = ensure_dynamic_smem(gemm_tf32x3_kernel, X3_SMEM_TOTAL, &configured);
     if (e != cudaSuccess) { err = std::string("gemm (tf32x3): ") + cudaGetErrorString(e); return ZYXB_ERR_KERNEL_LAUNCH; }
-    configured = true;
   }
   const unsigned grid = (unsigned)std::min<uint64_t>((uint64_t)xp.tiles_m * xp.tiles_n, (uint64_t)lc.sm_count);
   gemm_tf32x3_kernel<<<grid, X3_THREADS, X3_SMEM_TOTAL, lc.stream>>>(ma, mal, mb, mbl, xp);

@@ -28,9 +28,9 @@ inline int32_t checkpoint_save(zyxb_ctx* ctx, int32_t dev, int32_t dtype, const 
     r.name = tensors[i].name; r.dtype = dtype; r.shape = tensors[i].shape; r.data = host[i].data();
     refs.push_back(std::move(r));
   }
-  const uint32_t t32 = (uint32_t)step;
+  const uint64_t t64 = step;
   st::TensorRef t;
-  t.name = "optim.t"; t.dtype = ZYXB_U32; t.shape = {1}; t.data = &t32;
+  t.name = "optim.t"; t.dtype = ZYXB_U64; t.shape = {1}; t.data = &t64;
   refs.push_back(t);
   if (!st::write(path, refs, err)) return ZYXB_ERR_MEMORY_COPY_P2H;
   return ZYXB_OK;
@@ -40,16 +40,23 @@ inline int32_t checkpoint_load(zyxb_ctx* ctx, int32_t dev, int32_t dtype, const 
                                bool* have_step, int32_t* missing, const std::string& path, std::string& err) {
   st::File f;
   if (!st::open(path, f, err)) return ZYXB_ERR_MEMORY_COPY_H2P;
-  int32_t n_missing = 0, rc = ZYXB_OK;
-  std::vector<uint8_t> host;
+  int32_t n_missing = 0, n_state_missing = 0, rc = ZYXB_OK;
+  // first pass: every tensor the file holds must fit the plan's, so that a bad file is refused before anything is overwritten
   for (const CkptTensor& t : tensors) {
     const int i = st::find(f, t.name);
-    if (i < 0) { ++n_missing; continue; }
+    if (i < 0) { ++n_missing; n_state_missing += t.name.compare(0, 6, "optim.") == 0; continue; }
     const st::Entry& e = f.entries[i];
     if (e.dtype != dtype || st::numel(e.shape) != st::numel(t.shape)) {
       err = "checkpoint: '" + t.name + "' in " + path + " has another dtype or element count than the plan's tensor";
       rc = ZYXB_ERR_INCORRECT_KERNEL_ARG; break;
     }
+  }
+  std::vector<uint8_t> host;
+  for (size_t k = 0; !rc && k < tensors.size(); ++k) {
+    const CkptTensor& t = tensors[k];
+    const int i = st::find(f, t.name);
+    if (i < 0) continue;
+    const st::Entry& e = f.entries[i];
     host.resize(e.end - e.begin);
     if (!st::read(f, i, host.data(), host.size(), err)) { rc = ZYXB_ERR_MEMORY_COPY_H2P; break; }
     zyxb_event ev{};
@@ -57,12 +64,14 @@ inline int32_t checkpoint_load(zyxb_ctx* ctx, int32_t dev, int32_t dtype, const 
     if (!rc) rc = zyxb_sync(ctx, dev, &ev, 1);       // `host` is reused for the next tensor
     if (rc) { err = std::string("checkpoint: zyxb_h2d of '") + t.name + "': " + zyxb_last_error(ctx); break; }
   }
-  if (!rc) {
+  *have_step = false;
+  if (!rc && n_state_missing == 0) {       // a step counter without its moment buffers (e.g. another rank's shard file) would mis-scale Adam
     const int i = st::find(f, "optim.t");
-    *have_step = false;
-    if (i >= 0 && f.entries[i].dtype == ZYXB_U32 && st::numel(f.entries[i].shape) == 1) {
+    if (i >= 0 && st::numel(f.entries[i].shape) == 1) {
+      uint64_t t64 = 0;
       uint32_t t32 = 0;
-      if (st::read(f, i, &t32, 4, err)) { *step = t32; *have_step = true; }
+      if (f.entries[i].dtype == ZYXB_U64 && st::read(f, i, &t64, 8, err)) { *step = t64; *have_step = true; }
+      else if (f.entries[i].dtype == ZYXB_U32 && st::read(f, i, &t32, 4, err)) { *step = t32; *have_step = true; }
     }
   }
   st::close(f);

@@ -52,9 +52,11 @@ inline uint64_t dtype_bytes(int32_t d) {
     default: return 1;
   }
 }
+// Saturating: a crafted header (shape [2^63, 2]) must not wrap around into a small element count that passes the
+// shape / data_offsets check.
 inline uint64_t numel(const std::vector<uint64_t>& shape) {
   uint64_t n = 1;
-  for (uint64_t d : shape) n *= d;
+  for (uint64_t d : shape) if (__builtin_mul_overflow(n, d, &n)) return UINT64_MAX / 16;
   return n;
 }
 

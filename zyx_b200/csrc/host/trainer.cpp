@@ -579,6 +579,8 @@ int32_t zyxb_mlp_save(zyxb_mlp* M, const char* path) {
 
 int32_t zyxb_mlp_load(zyxb_mlp* M, const char* path, int32_t* out_missing) {
   if (!M || !path) return ZYXB_ERR_INCORRECT_KERNEL_ARG;
+  int32_t stj = join_params(M);          // parameter all-gathers still in flight would overwrite what is loaded
+  if (stj) return stj;
   uint64_t t = 0;
   bool have_t = false;
   int32_t st = zyxb_host::checkpoint_load(M->ctx, M->dev, M->cfg.dtype, mlp_ckpt_tensors(M), &t, &have_t, out_missing, path, M->err);

@@ -119,6 +119,10 @@ constexpr int COLSUM_STATIC_MAX_DEVICES = 64;
 static float* g_colsum_static_ptr[COLSUM_STATIC_MAX_DEVICES];   // device address of the array, per CUDA device
 
 uint64_t colsum_static_capacity() { return COLSUM_STATIC_FLOATS; }
+// whether the array's address on this CUDA device has been looked up already (the look-up cannot be part of a stream capture)
+bool colsum_static_ready(int cuda_device) {
+  return cuda_device >= 0 && cuda_device < COLSUM_STATIC_MAX_DEVICES && g_colsum_static_ptr[cuda_device] != nullptr;
+}
 
 // In host code the array's name is only a handle for the runtime, not a device address: the address is
 // looked up once per device (with that device current) and cached.

@@ -719,11 +719,8 @@ static bool launch_row_staged(const RowParams& p, cudaStream_t s, int sm_count, 
   if (row_bytes < 16384 || p.cols > (uint64_t)STG_THREADS * ITEMS * V || p.cols % V || p.rows < 2ull * sm_count) return false;
   if ((uintptr_t)p.x % 16 || (uintptr_t)p.y % 16 || (p.w && (uintptr_t)p.w % 16) || (p.b && (uintptr_t)p.b % 16)) return false;
   auto kern = row_staged_kernel<T, ITEMS, FAM>;
-  static bool configured = false;
-  if (!configured) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 1024) != cudaSuccess) { cudaGetLastError(); return false; }
-    configured = true;
-  }
+  static uint64_t configured = 0;
+  if (ensure_dynamic_smem(kern, 128 * 1024, &configured) != cudaSuccess) { cudaGetLastError(); return false; }
   kern<<<(unsigned)std::min<uint64_t>(p.rows, (uint64_t)sm_count), STG_THREADS, (size_t)row_bytes, s>>>(p, status);
   return true;
 }
@@ -913,11 +910,8 @@ static bool launch_row_cluster(const RowParams& p, cudaStream_t s, int sm_count,
   if (p.rows < (uint64_t)sm_count) return false;      // at least two rows per cluster
   if ((uintptr_t)p.x % 16 || (uintptr_t)p.y % 16 || (p.w && ((uintptr_t)p.w % 16 || (uintptr_t)p.b % 16))) return false;
   auto kern = row_cluster_kernel<T, FAM>;
-  static bool configured = false;
-  if (!configured) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 3 * 65536) != cudaSuccess) { cudaGetLastError(); return false; }
-    configured = true;
-  }
+  static uint64_t configured = 0;
+  if (ensure_dynamic_smem(kern, 3 * 65536, &configured) != cudaSuccess) { cudaGetLastError(); return false; }
   const unsigned clusters = (unsigned)std::min<uint64_t>(p.rows, (uint64_t)(sm_count / 2));
   kern<<<2 * clusters, STG_THREADS, (size_t)((p.w ? 3 : 1) * half_bytes), s>>>(p, status);
   return true;

@@ -23,6 +23,10 @@ class Session:
     def close(self):
         self.backend.deinitialize()
 
+    def on_device(self, dev):
+        """The same context's device `dev` (a context opened with several device ids drives them all)."""
+        return Session(backend=self.backend, dev=dev)
+
     def run(self, desc, inputs, out_specs, out_init=None):
         """inputs: host arrays; out_specs: [(shape, np dtype)] -> list of host arrays.  out_init: host array the first
         output buffer holds before the launch (for kernels that leave part of their output untouched)."""
