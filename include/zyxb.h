@@ -356,6 +356,13 @@ int32_t zyxb_launch_count(zyxb_ctx* ctx, int32_t dev, uint64_t* out_count);
  * reading it synchronises the device and clears it */
 int32_t zyxb_device_status(zyxb_ctx* ctx, int32_t dev, uint32_t* out_status);
 
+/* Failure detection without a failure: launches one CTA that waits, through the kernels' own bounded wait, on a barrier
+ * nothing will ever arrive on, with a limit of `limit_ns` (at most 100 ms) instead of the kernels' two seconds.  The wait gives
+ * up, the kernel returns normally, *out_gave_up is 1 and the device status word carries bit 0x8000, so the next
+ * zyxb_device_status reports ZYXB_ERR_KERNEL_SYNC (ErrorStatus::KernelSync, zyx/src/error.rs:151-152) and clears the word; the
+ * context stays usable.  Blocks until the kernel has finished. */
+int32_t zyxb_selftest_bounded_wait(zyxb_ctx* ctx, int32_t dev, uint64_t limit_ns, uint32_t* out_gave_up);
+
 /* ---- captured launch sequences ---------------------------------------------------------------------------
  * FrozenTape::replay (zyx/src/tape.rs:204-288) re-runs a realised plan without rebuilding it; here the launches
  * issued between capture_begin and capture_end are recorded into a CUDA graph instead of being run, and

@@ -154,3 +154,29 @@ def test_one_context_drives_two_gpus():
             assert sd.device.status() == 0
     finally:
         s.close()
+
+
+def test_a_wait_that_runs_out_is_reported_and_the_context_stays_usable(sess):
+    """The bounded wait every tensor-core kernel spins in, made to run out on purpose: a barrier nothing arrives on, a limit of
+    one millisecond.  The kernel returns by itself, the status word carries the code, zyxb_device_status turns it into
+    KernelSync once and clears it, and an ordinary tensor-core matmul afterwards is clean.  Nothing faults or hangs."""
+    import time
+    lib, be, d = sess.backend.lib, sess.backend, sess.device
+    assert d.status() == 0
+    gave_up = C.c_uint32(7)
+    t0 = time.perf_counter()
+    assert lib.zyxb_selftest_bounded_wait(be.ctx, d.dev, 1_000_000, C.byref(gave_up)) == L.OK
+    assert time.perf_counter() - t0 < 1.0                # a millisecond plus launch overhead, nowhere near the 2 s production bound
+    assert gave_up.value == 1
+    with pytest.raises(B.BackendError) as e:
+        d.status()
+    assert e.value.status_name == "KernelSync" and "bounded wait" in e.value.context
+    assert d.status() == 0                               # reading cleared it
+    rng = np.random.default_rng(2)
+    a = zo.to_bits(rng.uniform(-1, 1, (256, 512)).astype(np.float32), zo.BF16)
+    b = zo.to_bits(rng.uniform(-1, 1, (512, 384)).astype(np.float32), zo.BF16)
+    got = zo.to_f32(sess.gemm(L.BF16, a, b), zo.BF16)
+    assert max_rel_err(got, zo.to_f32(zo.gemm(zo.BF16, a, b), zo.BF16), floor=0.1) <= TOL_BF16
+    assert d.status() == 0
+    with pytest.raises(B.BackendError):                  # the limit is itself bounded
+        be._check(lib.zyxb_selftest_bounded_wait(be.ctx, d.dev, 10_000_000_000, C.byref(gave_up)))

@@ -15,6 +15,7 @@ OK = 0
 ERR_NAMES = {1: "DyLibNotFound", 2: "Initialization", 3: "Deinitialization", 4: "DeviceEnumeration", 5: "DeviceQuery",
              6: "MemoryAllocation", 7: "MemoryDeallocation", 8: "MemoryCopyH2P", 9: "MemoryCopyP2H", 10: "IncorrectKernelArg",
              11: "KernelCompilation", 12: "KernelLaunch", 13: "KernelSync"}
+ERR_NAMES_INV = {name: code for code, name in ERR_NAMES.items()}
 BF16, F16, F32, F64, U8, U16, U32, U64, I8, I16, I32, I64, BOOL = range(13)
 DTYPE_SIZE = {BF16: 2, F16: 2, F32: 4, F64: 8, U8: 1, U16: 2, U32: 4, U64: 8, I8: 1, I16: 2, I32: 4, I64: 8, BOOL: 1}
 KIND_ROWREDUCE, KIND_GEMM, KIND_ELTWISE, KIND_OPTIM, KIND_ATTENTION, KIND_ATTENTION_BWD, KIND_CONV, KIND_CONV_WGRAD, KIND_CONV_DGRAD = 1, 2, 3, 4, 5, 6, 7, 8, 9
@@ -133,6 +134,7 @@ SIGNATURES = {
     "zyxb_colsum_static_capacity": (C.c_int32, [C.POINTER(C.c_uint64)]),
     "zyxb_launch_count": (C.c_int32, [_CTX, C.c_int32, C.POINTER(C.c_uint64)]),
     "zyxb_device_status": (C.c_int32, [_CTX, C.c_int32, _U32_P]),
+    "zyxb_selftest_bounded_wait": (C.c_int32, [_CTX, C.c_int32, C.c_uint64, _U32_P]),
     "zyxb_event_record": (C.c_int32, [_CTX, C.c_int32, _EV_P]),
     "zyxb_event_elapsed_ms": (C.c_int32, [_CTX, C.c_int32, Event, Event, C.POINTER(C.c_float)]),
     "zyxb_flush_l2": (C.c_int32, [_CTX, C.c_int32]),

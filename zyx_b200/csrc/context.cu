@@ -737,6 +737,26 @@ int32_t zyxb_device_status(zyxb_ctx* ctx, int32_t dev, uint32_t* out_status) {
   return ZYXB_OK;
 }
 
+// A wait that nothing will ever satisfy, bounded by `limit_ns`: see selftest.cu.  The kernel's verdict goes to the second
+// word of the status allocation, the timeout code to the status word itself (read and cleared by zyxb_device_status).
+int32_t zyxb_selftest_bounded_wait(zyxb_ctx* ctx, int32_t dev, uint64_t limit_ns, uint32_t* out_gave_up) {
+  DEV_OR_FAIL(ZYXB_ERR_KERNEL_LAUNCH);
+  NOT_WHILE_CAPTURING("zyxb_selftest_bounded_wait", ZYXB_ERR_KERNEL_LAUNCH);
+  LaunchCtx lc = make_launch_ctx(ctx, D);
+  std::string err;
+  uint32_t* verdict = D.status_word + 1;
+  cudaError_t e = cudaMemsetAsync(verdict, 0xff, 4, D.compute);
+  if (e != cudaSuccess) return cuda_fail(ctx, ZYXB_ERR_KERNEL_LAUNCH, "selftest", e);
+  int st = launch_bounded_wait_selftest(limit_ns, verdict, lc, err);
+  if (st) return fail(ctx, st, err);
+  uint32_t w = 0;
+  e = cudaMemcpyAsync(&w, verdict, 4, cudaMemcpyDeviceToHost, D.compute);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(D.compute);
+  if (e != cudaSuccess) return cuda_fail(ctx, ZYXB_ERR_KERNEL_SYNC, "selftest", e);
+  if (out_gave_up) *out_gave_up = w;
+  return ZYXB_OK;
+}
+
 // ---- timing -------------------------------------------------------------------------------------
 int32_t zyxb_event_record(zyxb_ctx* ctx, int32_t dev, zyxb_event* out_event) {
   DEV_OR_FAIL(ZYXB_ERR_KERNEL_SYNC);

@@ -35,7 +35,9 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
 // Bounded wait.  Returns false when the wait was abandoned (time limit or another role aborted).
 // The wall clock (%globaltimer, a slow read) is consulted only every 1024 failed polls, so that a wait that is satisfied
 // after a few polls - the common case on the critical path of a pipeline - never pays for it.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, uint32_t* status, uint32_t code) {
+// `limit_ns` is the production constant everywhere except in the wait self-test, which passes a millisecond.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, uint32_t* status, uint32_t code,
+                                          uint64_t limit_ns = TC_WAIT_NS) {
   if (mbar_try_wait(bar, parity)) return true;
   uint64_t t0 = 0;
   uint32_t spins = 0;
@@ -44,7 +46,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
       if (*abort_flag) return false;
       const uint64_t now = global_timer_ns();
       if (t0 == 0) t0 = now;
-      else if (now - t0 > TC_WAIT_NS) {
+      else if (now - t0 > limit_ns) {
         *abort_flag = 1;
         atomicOr(status, code);
         return false;
