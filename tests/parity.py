@@ -41,6 +41,18 @@ def max_rel_err(got, want, row_axis=-1, floor=1e-2, abs_floor=0.0):
     return float(np.max(err))
 
 
+# Every comparison that did not meet the tolerance against the oracle directly and was decided by the float64 attribution
+# instead: (test id, what, tolerance, floor, gpu-vs-oracle, gpu-vs-float64, oracle-vs-float64).  tests/conftest.py writes the
+# table out at the end of a session so that it can be read beside the results.
+FALLBACKS = []
+
+
+def record_fallback(what, tol, floor, e_go, e_ge, e_oe):
+    import os
+    test = os.environ.get("PYTEST_CURRENT_TEST", "?").split(" ")[0]
+    FALLBACKS.append((test, what, tol, floor, e_go, e_ge, e_oe))
+
+
 def assert_parity(got, oracle, exact, tol, floor=1e-2, row_axis=-1, what="", abs_floor=0.0):
     """The parity bar for reductions whose order differs between the reference and the GPU.
 
@@ -56,6 +68,7 @@ def assert_parity(got, oracle, exact, tol, floor=1e-2, row_axis=-1, what="", abs
         return
     e_ge = max_rel_err(got, exact, row_axis, floor, abs_floor)
     e_oe = max_rel_err(oracle, exact, row_axis, floor, abs_floor)
+    record_fallback(what, tol, floor, e_go, e_ge, e_oe)
     assert (e_ge <= tol or e_ge <= 1.05 * e_oe) and e_go <= tol + e_oe, "%s: gpu-vs-oracle %.3g, gpu-vs-exact %.3g, oracle-vs-exact %.3g, tol %.3g" % (
         what, e_go, e_ge, e_oe, tol)
 

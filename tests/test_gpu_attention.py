@@ -5,7 +5,7 @@ import pytest
 
 from oracle import models as zm
 from oracle import oracle as zo
-from tests.parity import TOL_BF16, assert_parity, max_rel_err
+from tests.parity import TOL_BF16, assert_parity, max_rel_err, record_fallback
 from zyx_b200 import _lib as L
 from zyx_b200 import backend as B
 
@@ -71,6 +71,8 @@ def test_fused_attention_backward(sess, dtype, causal, batch, heads, seq):
         # composition is (within a quarter), and no farther from the reference than tolerance plus its own distance.
         kw = dict(floor=1.0, abs_floor=0.05 * float(np.abs(ex).max()))
         e_go, e_ge, e_oe = max_rel_err(g, w, **kw), max_rel_err(g, ex, **kw), max_rel_err(w, ex, **kw)
+        if e_go > TOL_BF16:
+            record_fallback("attention backward " + name, TOL_BF16, 1.0, e_go, e_ge, e_oe)
         assert e_go <= TOL_BF16 or (e_ge <= max(TOL_BF16, 1.25 * e_oe) and e_go <= TOL_BF16 + e_oe), (name, e_go, e_ge, e_oe)
 
 

@@ -9,7 +9,7 @@ import pytest
 from oracle import models as om
 from oracle import oracle as zo
 from oracle import sampled_checks as sc
-from tests.parity import TOL_BF16
+from tests.parity import TOL_BF16, record_fallback
 from zyx_b200 import _lib as L
 from zyx_b200 import host as H
 
@@ -66,6 +66,8 @@ def test_config5_seq_2048_every_stage_against_the_oracle(sess, record_property, 
         record_property(k, v)
     for k, v in att.items():
         record_property(k, "%.3g / %.3g / %.3g" % (v["gpu_vs_oracle"], v["gpu_vs_float64"], v["oracle_vs_float64"]))
+        if v["gpu_vs_oracle"] > TOL_BF16:
+            record_fallback("config 5 " + k, TOL_BF16, 1.0, v["gpu_vs_oracle"], v["gpu_vs_float64"], v["oracle_vs_float64"])
     bad = {k: v for k, v in errs.items() if not k.endswith("float64") and not (v <= TOL_BF16)}
     assert not bad, (bad, errs, att)
     assert errs["loss_vs_float64"] <= 1e-4, errs

@@ -49,7 +49,7 @@ def test_a_capture_refuses_what_it_cannot_record(sess):
         want = pv.copy()
         for _ in range(3):
             zo.sgd(zo.F32, want, gv, None, lr=0.1)
-        assert max_rel_err(p.download(bp, (n,), np.float32), want) <= 1e-6
+        assert max_rel_err(p.download(bp, (n,), np.float32), want) <= 1e-5       # FMA contraction differs by an ulp of the larger operand
         # outside a capture the step-dependent programs run and count
         d.launch(momentum, [bp, bg, bm])
         d.launch(momentum, [bp, bg, bm])

@@ -253,3 +253,58 @@ def test_conv_weight_gradient_against_float64_autograd():
     xt = torch.nn.functional.pad(torch.from_numpy(x).double(), (2, 1, 1, 0))
     torch.nn.functional.conv2d(xt, w, stride=(2, 1), dilation=(1, 2)).backward(torch.from_numpy(dy).double())
     assert np.abs(got - w.grad.numpy()).max() <= 1e-5 * np.abs(w.grad.numpy()).max()
+
+
+def causal_self_attention(x, w_attn, w_proj, n_head, gemm, softmax):
+    """CausalSelfAttention::forward (zyx-nn/src/causal_self_attention.rs:36-71) on one sequence x [T, C], composed from a
+    matmul and a row softmax (the oracle's or the GPU's): c_attn, split into q, k, v, per head q.k^T * (1/sqrt(d)) -> softmax
+    (no mask: lines 60-61) -> . v, heads merged, c_proj."""
+    t, c = x.shape
+    d = c // n_head
+    qkv = gemm(x, w_attn, tb=True)
+    q, k, v = qkv[:, :c], qkv[:, c:2 * c], qkv[:, 2 * c:]
+    scale = float(np.float32(1.0 / np.sqrt(float(d))))
+    y = np.zeros((t, c), np.float32)
+    for h in range(n_head):
+        qh, kh, vh = (np.ascontiguousarray(a[:, h * d:(h + 1) * d]) for a in (q, k, v))
+        att = softmax(gemm(qh, kh, tb=True, alpha=scale))
+        y[:, h * d:(h + 1) * d] = gemm(att, vh)
+    return gemm(y, w_proj, tb=True)
+
+
+def test_causal_self_attention_five_iterations_known_answer(golden):
+    """The only reference vector that pins projection -> attention -> projection end to end."""
+    g = golden["causal_self_attention_5_iterations_f32"]
+    x = f32(g["x"])
+    for _ in range(g["iterations"]):
+        x = causal_self_attention(x, f32(g["c_attn_weight"]), f32(g["c_proj_weight"]), g["n_head"],
+                                  lambda a, b, **kw: zo.gemm(zo.F32, a, b, **kw), lambda s: zo.softmax(zo.F32, s))
+    assert ref_is_equal(x, f32(g["y"]))
+
+
+def test_grad_dot_and_grad_sum_known_answers(golden):
+    """The adjoints the plans use for a matmul (dX = dZ . Y^T, dY = X^T . dZ) and a full sum (ones), on the reference's vectors."""
+    g = golden["grad_dot_i32"]
+    x, y = np.asarray(g["x"], np.int32).reshape(1, 3), np.asarray(g["y"], np.int32)
+    dz = np.ones((1, 1), np.int32)
+    assert zo.gemm(zo.I32, dz, y, tb=True).ravel().tolist() == g["x_grad"]
+    assert zo.gemm(zo.I32, x, dz, ta=True).tolist() == g["y_grad"]
+    s = golden["grad_sum_f32"]
+    xs = f32(s["x"]).reshape(1, -1)
+    base = float(zo.row_reduce(0, zo.F32, xs)[0])
+    fd = [float(zo.row_reduce(0, zo.F32, xs + np.eye(1, xs.size, i, dtype=np.float32))[0]) - base for i in range(xs.size)]
+    assert fd == s["x_grad"]
+
+
+def scalar_loop_softmax(x):
+    """The loop of zyx/tests/07_realize.rs:277-293 in f32: row maximum, exp, a running sum in index order, divide."""
+    m = x.max(1, keepdims=True)
+    e = np.exp((x - m).astype(np.float32)).astype(np.float32)
+    s = np.cumsum(e, axis=1, dtype=np.float32)[:, -1:]
+    return (e / s).astype(np.float32)
+
+
+def test_softmax_against_the_scalar_loop(golden):
+    g = golden["softmax_scalar_loop_procedural"]
+    x = zo.Rng().rand(g["rows"] * g["cols"]).reshape(g["rows"], g["cols"])
+    assert ref_is_equal(zo.softmax(zo.F32, x), scalar_loop_softmax(x))
