@@ -88,3 +88,77 @@ def test_sharded_and_replicated_plans_agree_on_two_ranks(tmp_path):
         got, w = zo.to_f32(r0["arr_%d" % (n + i)], zo.BF16), zo.to_f32(want, zo.BF16)
         err = np.abs(got - w) / np.maximum(np.abs(w), 0.1 * np.abs(w).max())
         assert np.quantile(err, 0.999) <= 2 * TOL_BF16, (i, float(err.max()))
+
+
+def _rank_allreduce(rank, world, tmp, mode):
+    """Every rank allreduces the same sequence of ranges (several dtypes, sizes that do not divide into shards, offsets into a
+    larger buffer, a view, repeated calls on one buffer) and checks the sum it can compute by itself from the seeds."""
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    os.environ["ZYXB_ALLREDUCE"] = mode
+    os.environ["ZYXB_PEER_WAIT_MS"] = "10000"
+    from oracle import oracle as zo
+    from zyx_b200 import _lib as L
+    from zyx_b200.ops import Session
+    sess = Session(device_ids=[rank])
+    try:
+        uid_path = os.path.join(tmp, "uid_" + mode)
+        if rank == 0:
+            with open(uid_path + ".tmp", "wb") as f:
+                f.write(sess.device.comm_unique_id())
+            os.rename(uid_path + ".tmp", uid_path)
+        t0 = time.time()
+        while not os.path.exists(uid_path):
+            assert time.time() - t0 < 60, "no unique id from rank 0"
+            time.sleep(0.05)
+        sess.device.comm_init(rank, world, open(uid_path, "rb").read())
+        p, d = sess.pool, sess.device
+        data = lambda r, n, seed: np.random.default_rng(1000 * seed + r).standard_normal(n).astype(np.float32)
+        cases = [(L.F32, 1 << 20, 0, 1 << 20), (L.F32, 100003, 256, 99000), (L.BF16, 5_000_000, 128, 4_999_000), (L.F16, 777, 0, 777),
+                 (L.BF16, 64, 0, 7), (L.I32, 4099, 3, 4000), (L.BF16, 1 << 24, 0, 1 << 24)]
+        for seed, (dt, n, off, count) in enumerate(cases):
+            conv = (lambda a: a) if dt == L.F32 else (lambda a: (a * 100).astype(np.int32)) if dt == L.I32 else (lambda a: zo.to_bits(a, dt))
+            back = (lambda a: a.astype(np.float64)) if dt in (L.F32, L.I32) else (lambda a: zo.to_f32(a, dt).astype(np.float64))
+            parts = [conv(data(r, n, seed)) for r in range(world)]
+            buf = p.upload(parts[rank])
+            for rep in range(2):                       # the second call sums the first call's sums: W * W * x
+                ev = d.allreduce_sum(buf, count, dt, offset_elems=off, want_event=True)
+                p.sync_events([ev])
+            got = p.download(buf, (n,), parts[rank].dtype)
+            want = sum(back(a) for a in parts)
+            lo, hi = off, off + count
+            assert np.array_equal(got[:lo], parts[rank][:lo]) and np.array_equal(got[hi:], parts[rank][hi:]), (mode, seed, "outside the range")
+            w2 = want[lo:hi] * world
+            err = np.abs(back(got[lo:hi]) - w2) / np.maximum(np.abs(w2), 0.05 * np.abs(w2).max())
+            tol = 0 if dt == L.I32 else 1e-6 if dt == L.F32 else 2e-2
+            assert err.max() <= tol, (mode, seed, float(err.max()))
+            p.deallocate(buf)
+        # a view of a bucket, as the plans use it
+        bucket, _ = p.allocate(4 << 20)
+        sess.backend._check(sess.backend.lib.zyxb_memset(sess.backend.ctx, d.dev, bucket, 0, 0, 4 << 20))
+        import ctypes as C
+        view = C.c_uint32()
+        sess.backend._check(sess.backend.lib.zyxb_buffer_view(sess.backend.ctx, d.dev, bucket, 1 << 20, 1 << 20, C.byref(view)))
+        x = data(rank, 1 << 18, 99)
+        p.sync_events([p.host_to_pool(x, view.value)])
+        d.allreduce_sum(view.value, 1 << 18, L.F32)
+        d.sync()
+        want = sum(data(r, 1 << 18, 99).astype(np.float64) for r in range(world))
+        got = p.download(view.value, (1 << 18,), np.float32)
+        assert np.max(np.abs(got - want)) <= 1e-5, mode
+        assert d.status() == 0
+        p.deallocate(view.value)
+        p.deallocate(bucket)
+        open(os.path.join(tmp, "ok_%s_%d" % (mode, rank)), "w").close()
+        sess.device.comm_destroy()
+    finally:
+        sess.close()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+@pytest.mark.parametrize("mode", ["peer", "nccl"])
+def test_allreduce_over_peer_memory_and_over_nccl(tmp_path, mode):
+    """zyxb_allreduce_sum on two ranks: the copy-engine path over IPC-mapped peer memory (the default) and the NCCL path
+    (ZYXB_ALLREDUCE=nccl) give the sum of the ranks' data, leave everything outside the range alone, and keep working call
+    after call (the sequence numbers of the peer path only grow)."""
+    mp.spawn(_rank_allreduce, args=(2, str(tmp_path), mode), nprocs=2, join=True)
+    assert all(os.path.exists(str(tmp_path / ("ok_%s_%d" % (mode, r)))) for r in range(2))

@@ -128,6 +128,13 @@ int comm_allgather(Comm* c, void* base, uint64_t count_per_rank, uint64_t elem_b
   return ZYXB_OK;
 }
 
+int comm_allgather_raw(Comm* c, const void* send, void* recv, uint64_t bytes, cudaStream_t stream, std::string& err) {
+  Api& a = api();
+  int r = a.AllGather(send, recv, (size_t)bytes, /* ncclInt8 */ 0, c->comm, stream);
+  if (r != ncclSuccess) { err = nccl_err("ncclAllGather", r); return ZYXB_ERR_KERNEL_LAUNCH; }
+  return ZYXB_OK;
+}
+
 void comm_rank(const Comm* c, int* rank, int* world) { *rank = c->rank; *world = c->world; }
 
 void comm_destroy(Comm* c) {

@@ -32,6 +32,7 @@ struct Buffer {
   bool live = false;
   bool is_variable = false;
   bool is_view = false;    // aliases a range of another buffer; freeing it releases only the id
+  uint32_t parent = 0;     // views: the id of the buffer that owns the block (views of views name the owner)
   int32_t var_dtype = 0;
   uint8_t var_bytes[8] = {0};
 };
@@ -67,6 +68,7 @@ struct Device {
   void* tma_encode = nullptr;
   void* tma_encode_im2col = nullptr;
   Comm* comm = nullptr;
+  PeerComm* peer = nullptr;               // allreduce over peer memory (peer_allreduce.cu); created with the communicator
   // captured launch sequences (the analogue of a FrozenTape): executable graph + kernels per replay
   std::vector<std::pair<cudaGraphExec_t, uint64_t>> graphs;
   bool capturing = false;
@@ -268,6 +270,7 @@ int32_t zyxb_shutdown(zyxb_ctx* ctx) {
   for (auto& D : ctx->devs) {
     cudaSetDevice(D.cuda_id);
     cudaDeviceSynchronize();
+    if (D.peer) { peer_destroy(D.peer); D.peer = nullptr; }
     if (D.comm) { comm_destroy(D.comm); D.comm = nullptr; }
     for (auto& g : D.graphs) if (g.first) cudaGraphExecDestroy(g.first);
     for (auto& kv : D.events) cudaEventDestroy(kv.second);
@@ -355,7 +358,13 @@ int32_t zyxb_free(zyxb_ctx* ctx, int32_t dev, uint32_t buf, const zyxb_event* wa
   // that could still touch it before later work on the compute stream
   int st = wait_and_consume(ctx, D, D.compute, wait, n_wait, ZYXB_ERR_MEMORY_DEALLOCATION);
   if (st) return st;
-  if (!b->is_variable && !b->is_view) {
+  if (!b->is_variable && !b->is_view && peer_has_exported(D.peer, b->ptr)) {
+    // other processes have this block mapped: it is not recycled (a new owner would inherit their mappings); everything that
+    // may still touch it finishes first, then the mappings held here are closed and the block goes back to the driver
+    cudaDeviceSynchronize();
+    peer_forget_buffer(D.peer, b->ptr);
+    cudaFree(b->ptr);
+  } else if (!b->is_variable && !b->is_view) {
     if ((st = order_streams(ctx, D.copy, D.compute, ZYXB_ERR_MEMORY_DEALLOCATION))) return st;
     if ((st = order_streams(ctx, D.comm_stream, D.compute, ZYXB_ERR_MEMORY_DEALLOCATION))) return st;
     cudaEvent_t ready = nullptr;
@@ -385,6 +394,7 @@ int32_t zyxb_buffer_view(zyxb_ctx* ctx, int32_t dev, uint32_t parent, uint64_t o
   Buffer& b = D.buffers[id];
   b = Buffer();
   b.ptr = ptr; b.bytes = bytes; b.capacity = bytes; b.live = true; b.is_view = true;
+  b.parent = D.buffers[parent].is_view ? D.buffers[parent].parent : parent;
   *out_buf = id;
   return ZYXB_OK;
 }
@@ -803,6 +813,9 @@ int32_t zyxb_comm_init(zyxb_ctx* ctx, int32_t dev, int32_t rank, int32_t world, 
   std::string err;
   int st = comm_create(&D.comm, rank, world, id_128_bytes, err);
   if (st) return fail(ctx, st, err);
+  // set-up of the peer-memory allreduce is collective too (flag blocks are exchanged through the communicator)
+  if ((st = peer_create(&D.peer, D.comm, D.status_word, D.comm_stream, err))) return fail(ctx, st, err);
+  if (ctx->debug & 1) fprintf(stderr, "[zyxb] rank %d/%d: allreduce over %s\n", rank, world, peer_usable(D.peer) ? "peer memory (copy engines)" : "NCCL");
   return ZYXB_OK;
 }
 
@@ -820,7 +833,14 @@ int32_t zyxb_allreduce_sum(zyxb_ctx* ctx, int32_t dev, uint32_t buf, uint64_t of
   if ((st = order_streams(ctx, D.compute, D.comm_stream, ZYXB_ERR_KERNEL_LAUNCH))) return st;
   std::string err;
   char* p = (char*)b->ptr + offset_elems * es;
-  st = comm_allreduce_sum(D.comm, p, p, count, dtype, D.comm_stream, err);
+  Buffer* root = b->is_view ? get_buffer(D, b->parent) : b;
+  if (peer_usable(D.peer) && root && !root->is_view && !D.capturing) {
+    // the whole cudaMalloc block is mapped by the peers; the range is an offset into it
+    const uint64_t byte_offset = (uint64_t)(p - (char*)root->ptr);
+    st = peer_allreduce_sum(D.peer, D.comm, root->ptr, root->capacity, byte_offset, count, dtype, D.comm_stream, &D.launch_count, err);
+  } else {
+    st = comm_allreduce_sum(D.comm, p, p, count, dtype, D.comm_stream, err);
+  }
   if (st) return fail(ctx, st, err);
   if (out_event) return record_event(ctx, D, D.comm_stream, out_event, ZYXB_ERR_KERNEL_LAUNCH);
   return order_streams(ctx, D.comm_stream, D.compute, ZYXB_ERR_KERNEL_LAUNCH);
@@ -873,7 +893,11 @@ int32_t zyxb_comm_rank(zyxb_ctx* ctx, int32_t dev, int32_t* out_rank, int32_t* o
 
 int32_t zyxb_comm_destroy(zyxb_ctx* ctx, int32_t dev) {
   DEV_OR_FAIL(ZYXB_ERR_DEINITIALIZATION);
-  if (D.comm) { cudaDeviceSynchronize(); comm_destroy(D.comm); D.comm = nullptr; }
+  if (D.comm) {
+    cudaDeviceSynchronize();
+    if (D.peer) { peer_destroy(D.peer); D.peer = nullptr; }
+    comm_destroy(D.comm); D.comm = nullptr;
+  }
   return ZYXB_OK;
 }
 
