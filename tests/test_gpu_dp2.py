@@ -11,10 +11,13 @@ import torch.multiprocessing as mp
 
 pytestmark = pytest.mark.gpu
 
-DIMS, BATCH, STEPS = [64, 128, 64, 128, 64], 48, 3
+CONFIGS = {"small": ([64, 128, 64, 128, 64], 48, 3),
+           # a first layer large enough for the plan to produce its weight gradient in two halves, each with its own allreduce
+           "split_first_layer": ([4096, 4096, 64], 32, 2)}
 
 
-def _data(rank):
+def _data(config):
+    DIMS, BATCH, STEPS = CONFIGS[config]
     from oracle import models as om
     from oracle import oracle as zo
     rng = zo.Rng(7)
@@ -27,7 +30,8 @@ def _data(rank):
     return layers, batches
 
 
-def _rank(rank, world, tmp):
+def _rank(rank, world, tmp, config):
+    DIMS, BATCH, STEPS = CONFIGS[config]
     os.environ["NCCL_NVLS_ENABLE"] = "0"
     from oracle import models as om
     from zyx_b200 import _lib as L
@@ -45,7 +49,7 @@ def _rank(rank, world, tmp):
             assert time.time() - t0 < 60, "no unique id from rank 0"
             time.sleep(0.05)
         sess.device.comm_init(rank, world, open(uid_path, "rb").read())
-        layers, batches = _data(rank)
+        layers, batches = _data(config)
         out = {}
         for shard in (False, True):
             mlp = H.Mlp(sess, L.BF16, BATCH, DIMS, activation=H.ACT_GELU, loss=H.LOSS_MSE, algo=L.OPT_ADAMW, world=world,
@@ -67,11 +71,13 @@ def _rank(rank, world, tmp):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_sharded_and_replicated_plans_agree_on_two_ranks(tmp_path):
+@pytest.mark.parametrize("config", sorted(CONFIGS))
+def test_sharded_and_replicated_plans_agree_on_two_ranks(tmp_path, config):
     from oracle import models as om
     from oracle import oracle as zo
     from tests.parity import TOL_BF16
-    mp.spawn(_rank, args=(2, str(tmp_path)), nprocs=2, join=True)
+    DIMS, BATCH, STEPS = CONFIGS[config]
+    mp.spawn(_rank, args=(2, str(tmp_path), config), nprocs=2, join=True)
     r0, r1 = (np.load(str(tmp_path / ("rank%d.npz" % r))) for r in range(2))
     n = 2 * (len(DIMS) - 1)
     for i in range(n):
@@ -79,7 +85,7 @@ def test_sharded_and_replicated_plans_agree_on_two_ranks(tmp_path):
         assert np.array_equal(rep0, r1["arr_%d" % i]) and np.array_equal(shd0, r1["arr_%d" % (n + i)])    # ranks hold the same parameters
         assert np.array_equal(rep0, shd0)                                                                # and the two plans the same bits
     # one oracle step sequence on the concatenated batch (mean over 2 x BATCH rows = mean of the two ranks' means)
-    layers, batches = _data(0)
+    layers, batches = _data(config)
     opt = om.Optim("adamw", zo.BF16, om.flat(layers), lr=1e-3, weight_decay=0.01, standard=True)
     for x, t in batches:
         _, grads, _ = om.forward_backward(zo.BF16, layers, x, t, om.ACT_GELU, om.LOSS_MSE)
@@ -87,7 +93,10 @@ def test_sharded_and_replicated_plans_agree_on_two_ranks(tmp_path):
     for i, want in enumerate(om.flat(layers)):
         got, w = zo.to_f32(r0["arr_%d" % (n + i)], zo.BF16), zo.to_f32(want, zo.BF16)
         err = np.abs(got - w) / np.maximum(np.abs(w), 0.1 * np.abs(w).max())
-        assert np.quantile(err, 0.999) <= 2 * TOL_BF16, (i, float(err.max()))
+        # Adam moves every element by about lr per step whatever the size of its gradient, so an element whose (tiny) gradient
+        # rounds to the other sign on the two sides ends 2 * lr apart: with weights of 1/64 (the large layer) that is a few
+        # percent of an element for a fraction of a percent of them
+        assert np.quantile(err, 0.999 if config == "small" else 0.99) <= 2 * TOL_BF16, (i, float(err.max()))
 
 
 def _rank_allreduce(rank, world, tmp, mode):

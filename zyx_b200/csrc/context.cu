@@ -192,7 +192,7 @@ LaunchCtx make_launch_ctx(zyxb_ctx* ctx, Device& D) {
   LaunchCtx lc{};
   lc.stream = D.compute; lc.round_nearest = ctx->round_nearest; lc.sm_count = D.prop.multiProcessorCount;
   lc.status_word = D.status_word; lc.scratch = D.scratch; lc.scratch_bytes = D.scratch_bytes;
-  lc.launch_counter = &D.launch_count; lc.tma_encode = D.tma_encode; lc.tma_encode_im2col = D.tma_encode_im2col; lc.device = D.cuda_id; lc.overlap_hint = D.comm != nullptr;
+  lc.launch_counter = &D.launch_count; lc.tma_encode = D.tma_encode; lc.tma_encode_im2col = D.tma_encode_im2col; lc.device = D.cuda_id; lc.overlap_hint = D.comm != nullptr && !peer_usable(D.peer);   // NCCL's kernels take SMs away; the copy-engine allreduce does not
   return lc;
 }
 

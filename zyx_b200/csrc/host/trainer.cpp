@@ -229,11 +229,38 @@ int32_t build(zyxb_mlp* M) {
     if ((st = push_launch(M, P, ew_desc(ZYXB_EW_MSE_BWD, dt, B * out_f, 1.0f / (float)(B * out_f)), {M->y, M->target, M->dy}))) return st;
   }
   // ---- backward, last layer first ----
+  std::vector<int> collectives_of_layer(n, 1);
   for (int i = n - 1; i >= 0; --i) {
     const Linear& L = M->layers[i];
     const uint32_t dz = i == n - 1 ? M->dy : M->dact[i];
     const uint32_t in = i == 0 ? M->x : M->act[i - 1];
     // dW = dZ^T . input   ([out, B] x [B, in]); db = column sums of dZ
+    // The first layer's gradients are the last ones the backward pass produces, so their allreduce has nothing left to hide
+    // behind but the optimizer launches of the other layers.  Its weight gradient is therefore produced in two halves (rows
+    // [0, out/2) and [out/2, out) of dW: two column ranges of dZ, read in place through the row pitch), each followed by the
+    // allreduce of its part of the bucket: the first half travels while the second is being multiplied.
+    const bool data_parallel = !M->sharded && c.world > 1 && c.bucket_per_layer;
+    const uint64_t wn = L.in_features * L.out_features, half_rows = L.out_features / 2;
+    const bool split = data_parallel && i == 0 && n > 1 && wn >= (1ull << 24) && L.out_features % 256 == 0 && (half_rows * es) % 256 == 0 &&
+                       (half_rows * L.in_features * es) % 256 == 0;
+    if (split) {
+      uint32_t dz_hi = 0, dw_lo = 0, dw_hi = 0;
+      const uint64_t dz_bytes = B * L.out_features * es;
+      TRY(zyxb_buffer_view(M->ctx, M->dev, dz, half_rows * es, dz_bytes - half_rows * es, &dz_hi));
+      TRY(zyxb_buffer_view(M->ctx, M->dev, L.weight_grad, 0, half_rows * L.in_features * es, &dw_lo));
+      TRY(zyxb_buffer_view(M->ctx, M->dev, L.weight_grad, half_rows * L.in_features * es, half_rows * L.in_features * es, &dw_hi));
+      for (uint32_t v : {dz_hi, dw_lo, dw_hi}) M->owned_buffers.push_back(v);
+      zyxb_kernel_desc hd = gemm_desc(dt, half_rows, L.in_features, B, true, false, ZYXB_EPI_NONE, false);
+      hd.u.gemm.lda = L.out_features;                       // dZ is [B, out]: a half is a column range of every row
+      if ((st = push_launch(M, P, hd, {dz, in, dw_lo}))) return st;
+      Instr ar; ar.kind = Instr::ALLREDUCE; ar.offset = L.bucket_offset; ar.count = half_rows * L.in_features;
+      P.push_back(ar); M->n_collectives++;
+      if ((st = push_launch(M, P, hd, {dz_hi, in, dw_hi}))) return st;
+      if ((st = push_launch(M, P, row_desc(ZYXB_RR_COLSUM, dt, B, L.out_features), {dz, L.bias_grad}))) return st;
+      ar.offset = L.bucket_offset + half_rows * L.in_features; ar.count = L.bucket_count - half_rows * L.in_features;
+      P.push_back(ar); M->n_collectives++;
+      collectives_of_layer[i] = 2;
+    } else {
     if ((st = push_launch(M, P, gemm_desc(dt, L.out_features, L.in_features, B, true, false, ZYXB_EPI_NONE, false), {dz, in, L.weight_grad}))) return st;
     if ((st = push_launch(M, P, row_desc(ZYXB_RR_COLSUM, dt, B, L.out_features), {dz, L.bias_grad}))) return st;
     if (M->sharded) {
@@ -242,6 +269,7 @@ int32_t build(zyxb_mlp* M) {
     } else if (c.world > 1 && c.bucket_per_layer) {
       Instr ar; ar.kind = Instr::ALLREDUCE; ar.offset = L.bucket_offset; ar.count = L.bucket_count;
       P.push_back(ar); M->n_collectives++;
+    }
     }
     if (i > 0) {
       // dZ_prev = (dZ . W) * act'(z_prev)   ([B, out] x [out, in]); the activation's adjoint rides in the matmul epilogue
@@ -309,7 +337,7 @@ int32_t build(zyxb_mlp* M) {
     args.insert(args.end(), g.begin(), g.end());
     if (n_state >= 1) args.insert(args.end(), s0.begin(), s0.end());
     if (n_state >= 2) args.insert(args.end(), s1.begin(), s1.end());
-    if ((st = push_launch(M, M->update, od, args, per_layer ? 1 : -1))) return st;
+    if ((st = push_launch(M, M->update, od, args, per_layer ? collectives_of_layer[lo] : -1))) return st;
   }
   return ZYXB_OK;
 }

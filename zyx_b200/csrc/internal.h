@@ -21,7 +21,7 @@ struct LaunchCtx {
   void* tma_encode;         // cuTensorMapEncodeTiled entry point (driver), or nullptr
   void* tma_encode_im2col;  // cuTensorMapEncodeIm2col entry point (driver), or nullptr
   int device;
-  bool overlap_hint;        // a communicator exists: collectives may run beside the kernels
+  bool overlap_hint;        // collectives that occupy SMs (NCCL) may run beside the kernels: draw matmul tiles from a queue
 };
 
 // Every launcher validates the argument count and the byte size of each buffer before it

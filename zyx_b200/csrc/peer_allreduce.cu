@@ -109,24 +109,38 @@ __global__ void peer_reduce_kernel(ReduceSrc src, void* out, uint64_t n, int wor
     bool aligned = ((uintptr_t)out % 16) == 0;
     for (int r = 0; r < world; ++r) aligned = aligned && ((uintptr_t)src.ptr[r] % 16) == 0;
     const uint64_t nv = aligned ? n / 8 : 0;
-    for (uint64_t i = tid; i < nv; i += nthreads) {
-      float acc[8];
-      {
-        const uint4 v = ((const uint4*)src.ptr[0])[i];
-        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    // four 128-bit vectors per thread and pass, every source's loads issued before the first add: the kernel is a pure
+    // stream over HBM and has to keep enough bytes in flight with few, short-lived CTAs
+    constexpr int U = 4;
+    for (uint64_t i0 = tid; i0 < nv; i0 += nthreads * U) {
+      float acc[U][8];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) { acc[2 * j] = widen((uint16_t)(w[j] & 0xffff)); acc[2 * j + 1] = widen((uint16_t)(w[j] >> 16)); }
+      for (int u = 0; u < U; ++u)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[u][j] = 0.0f;
+      for (int r = 0; r < world; ++r) {
+        uint4 v[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const uint64_t i = i0 + (uint64_t)u * nthreads;
+          v[u] = i < nv ? __ldcs(((const uint4*)src.ptr[r]) + i) : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const uint32_t w[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) { acc[u][2 * j] += widen((uint16_t)(w[j] & 0xffff)); acc[u][2 * j + 1] += widen((uint16_t)(w[j] >> 16)); }
+        }
       }
-      for (int r = 1; r < world; ++r) {
-        const uint4 v = ((const uint4*)src.ptr[r])[i];
-        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-        for (int j = 0; j < 4; ++j) { acc[2 * j] += widen((uint16_t)(w[j] & 0xffff)); acc[2 * j + 1] += widen((uint16_t)(w[j] >> 16)); }
+      for (int u = 0; u < U; ++u) {
+        const uint64_t i = i0 + (uint64_t)u * nthreads;
+        if (i >= nv) continue;
+        uint32_t o[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) o[j] = (uint32_t)narrow(acc[u][2 * j]) | ((uint32_t)narrow(acc[u][2 * j + 1]) << 16);
+        ((uint4*)out)[i] = make_uint4(o[0], o[1], o[2], o[3]);
       }
-      uint32_t o[4];
-#pragma unroll
-      for (int j = 0; j < 4; ++j) o[j] = (uint32_t)narrow(acc[2 * j]) | ((uint32_t)narrow(acc[2 * j + 1]) << 16);
-      ((uint4*)out)[i] = make_uint4(o[0], o[1], o[2], o[3]);
     }
     for (uint64_t i = nv * 8 + tid; i < n; i += nthreads) {
       float a = widen(((const uint16_t*)src.ptr[0])[i]);
@@ -310,7 +324,8 @@ int peer_allreduce_sum(PeerComm* p, Comm* c, void* base, uint64_t buffer_bytes, 
   if (e != cudaSuccess) { err = std::string("peer allreduce pull: ") + cudaGetErrorString(e); return ZYXB_ERR_KERNEL_LAUNCH; }
   // 3. add, in rank order
   if (mine_n) {
-    const unsigned grid = (unsigned)std::max<uint64_t>(1, std::min<uint64_t>(32, mine_n / 8192 + 1));
+    // short-lived CTAs without shared memory: they slot in beside the matmul's CTAs; enough of them to stream at HBM speed
+    const unsigned grid = (unsigned)std::max<uint64_t>(1, std::min<uint64_t>(296, mine_n / 8192 + 1));
     void* out = at(base, lo(me));
     switch (dtype) {
       case ZYXB_F32: peer_reduce_kernel<0><<<grid, 256, 0, stream>>>(src, out, mine_n, W); break;
