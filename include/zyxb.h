@@ -63,7 +63,8 @@ typedef struct { uint64_t id; } zyxb_event;
 typedef struct {
   int32_t n_device_ids;    /* 0 = use every visible device */
   int32_t device_ids[16];
-  int32_t debug;           /* ZYX_DEBUG-style bitmask; 1 prints devices and launches */
+  int32_t debug;           /* ZYX_DEBUG-style bitmask; 1 prints devices and launches; 2 puts guard words behind every
+                              allocation (see zyxb_check_guards) */
   int32_t round_nearest;   /* 0 (default): bf16/f16 stores truncate like the reference C
                               backend (zyx/src/codegen/c.rs:475-496); 1: round to nearest */
 } zyxb_config;
@@ -355,6 +356,13 @@ int32_t zyxb_launch_count(zyxb_ctx* ctx, int32_t dev, uint64_t* out_count);
 /* device-side status word written by kernels whose bounded waits ran out (0 = none);
  * reading it synchronises the device and clears it */
 int32_t zyxb_device_status(zyxb_ctx* ctx, int32_t dev, uint32_t* out_status);
+
+/* With zyxb_config.debug bit 2 every pool allocation is followed by at least 256 bytes of a fixed pattern (the reference
+ * gives every buffer one spare trailing element, zyx/src/runtime.rs:622-625, backend/mod.rs:627).  This call waits for the
+ * device and verifies the pattern of every live buffer: a kernel that wrote past the end of one is reported as
+ * IncorrectKernelArg with the buffer's id in *out_bad_buffer and the distance in the error text.  It is the library's own
+ * out-of-bounds check for machines on which no memory checker may run. */
+int32_t zyxb_check_guards(zyxb_ctx* ctx, int32_t dev, uint32_t* out_bad_buffer);
 
 /* Failure detection without a failure: launches one CTA that waits, through the kernels' own bounded wait, on a barrier
  * nothing will ever arrive on, with a limit of `limit_ns` (at most 100 ms) instead of the kernels' two seconds.  The wait gives

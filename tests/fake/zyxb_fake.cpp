@@ -250,6 +250,7 @@ int32_t zyxb_launch(zyxb_ctx* c, int32_t, uint32_t prog, const uint32_t* args, i
 }
 int32_t zyxb_launch_count(zyxb_ctx* c, int32_t, uint64_t* o) { *o = c->launches; return ZYXB_OK; }
 int32_t zyxb_device_status(zyxb_ctx*, int32_t, uint32_t* o) { if (o) *o = 0; return ZYXB_OK; }
+int32_t zyxb_check_guards(zyxb_ctx*, int32_t, uint32_t* o) { if (o) *o = 0; return ZYXB_OK; }
 int32_t zyxb_selftest_bounded_wait(zyxb_ctx* c, int32_t, uint64_t, uint32_t*) { return fail(c, ZYXB_ERR_KERNEL_LAUNCH, "fake: no kernels"); }
 int32_t zyxb_capture_begin(zyxb_ctx* c, int32_t) { return fail(c, ZYXB_ERR_KERNEL_LAUNCH, "fake: no captures"); }
 int32_t zyxb_capture_end(zyxb_ctx* c, int32_t, uint32_t*) { return fail(c, ZYXB_ERR_KERNEL_LAUNCH, "fake: no captures"); }

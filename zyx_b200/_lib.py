@@ -134,6 +134,7 @@ SIGNATURES = {
     "zyxb_colsum_static_capacity": (C.c_int32, [C.POINTER(C.c_uint64)]),
     "zyxb_launch_count": (C.c_int32, [_CTX, C.c_int32, C.POINTER(C.c_uint64)]),
     "zyxb_device_status": (C.c_int32, [_CTX, C.c_int32, _U32_P]),
+    "zyxb_check_guards": (C.c_int32, [_CTX, C.c_int32, _U32_P]),
     "zyxb_selftest_bounded_wait": (C.c_int32, [_CTX, C.c_int32, C.c_uint64, _U32_P]),
     "zyxb_event_record": (C.c_int32, [_CTX, C.c_int32, _EV_P]),
     "zyxb_event_elapsed_ms": (C.c_int32, [_CTX, C.c_int32, Event, Event, C.POINTER(C.c_float)]),

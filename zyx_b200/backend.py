@@ -214,6 +214,11 @@ class Device:
     def set_step(self, program_id, t):
         self.be._check(self.be.lib.zyxb_program_set_step(self.be.ctx, self.dev, program_id, int(t)))
 
+    def check_guards(self):
+        """With Backend(debug=2): raises BackendError naming the buffer a kernel wrote past the end of; returns None when all are intact."""
+        bad = C.c_uint32()
+        self.be._check(self.be.lib.zyxb_check_guards(self.be.ctx, self.dev, C.byref(bad)))
+
     def get_step(self, program_id):
         t = C.c_uint64()
         self.be._check(self.be.lib.zyxb_program_get_step(self.be.ctx, self.dev, program_id, C.byref(t)))

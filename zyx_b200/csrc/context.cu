@@ -84,6 +84,7 @@ struct zyxb_ctx {
   std::string last_error;
   bool round_nearest = false;
   int debug = 0;
+  bool guards = false;     // debug bit 2: every allocation carries guard words behind its last byte (zyxb_check_guards)
   std::unordered_map<void*, int> registered;   // page-locked host ranges
 };
 
@@ -114,6 +115,13 @@ Buffer* get_buffer(Device& D, uint32_t id) {
 }
 
 uint64_t round_up(uint64_t v, uint64_t a) { return (v + a - 1) / a * a; }
+
+// Guard words (zyxb_config.debug bit 2): the stand-in for a memory checker on machines where none may run.  Every pool
+// allocation is followed by at least GUARD_BYTES of a fixed pattern; a kernel that writes past the end of an output (the
+// reference gives every buffer a spare trailing element for the same reason, zyx/src/runtime.rs:622-625) destroys it, and
+// zyxb_check_guards finds the buffer.
+constexpr uint64_t GUARD_BYTES = 256;
+constexpr int GUARD_PATTERN = 0xC5;
 
 // [offset, offset + bytes) lies inside [0, limit), without letting offset + bytes wrap around
 bool range_ok(uint64_t offset, uint64_t bytes, uint64_t limit) { return offset <= limit && bytes <= limit - offset; }
@@ -226,6 +234,7 @@ int32_t zyxb_init(const zyxb_config* config, zyxb_ctx** out_ctx) {
   zyxb_ctx* ctx = new zyxb_ctx();
   ctx->round_nearest = config && config->round_nearest;
   ctx->debug = config ? config->debug : 0;
+  ctx->guards = (ctx->debug & 2) != 0;
   for (int id : ids) {
     Device D;
     D.cuda_id = id;
@@ -334,10 +343,12 @@ int32_t zyxb_alloc(zyxb_ctx* ctx, int32_t dev, uint64_t bytes, uint32_t* out_buf
   DEV_OR_FAIL(ZYXB_ERR_MEMORY_ALLOCATION);
   if (!out_buf) return fail(ctx, ZYXB_ERR_MEMORY_ALLOCATION, "out_buf is null");
   NOT_WHILE_CAPTURING("zyxb_alloc", ZYXB_ERR_MEMORY_ALLOCATION);
-  const uint64_t capacity = round_up(bytes == 0 ? 1 : bytes, 512);
+  const uint64_t capacity = round_up((bytes == 0 ? 1 : bytes) + (ctx->guards ? GUARD_BYTES : 0), 512);
   void* ptr = nullptr;
   cudaError_t e = device_malloc(D, capacity, &ptr);
   if (e != cudaSuccess) { cudaGetLastError(); return cuda_fail(ctx, ZYXB_ERR_MEMORY_ALLOCATION, "cudaMalloc", e); }
+  if (ctx->guards && (e = cudaMemsetAsync((char*)ptr + bytes, GUARD_PATTERN, capacity - bytes, D.compute)) != cudaSuccess)
+    return cuda_fail(ctx, ZYXB_ERR_MEMORY_ALLOCATION, "guard words", e);
   uint32_t id;
   if (!D.free_buffer_ids.empty()) { id = D.free_buffer_ids.back(); D.free_buffer_ids.pop_back(); }
   else { id = (uint32_t)D.buffers.size(); D.buffers.emplace_back(); }
@@ -764,6 +775,30 @@ int32_t zyxb_selftest_bounded_wait(zyxb_ctx* ctx, int32_t dev, uint64_t limit_ns
   if (e == cudaSuccess) e = cudaStreamSynchronize(D.compute);
   if (e != cudaSuccess) return cuda_fail(ctx, ZYXB_ERR_KERNEL_SYNC, "selftest", e);
   if (out_gave_up) *out_gave_up = w;
+  return ZYXB_OK;
+}
+
+int32_t zyxb_check_guards(zyxb_ctx* ctx, int32_t dev, uint32_t* out_bad_buffer) {
+  DEV_OR_FAIL(ZYXB_ERR_KERNEL_SYNC);
+  NOT_WHILE_CAPTURING("zyxb_check_guards", ZYXB_ERR_KERNEL_SYNC);
+  if (out_bad_buffer) *out_bad_buffer = 0;
+  if (!ctx->guards) return fail(ctx, ZYXB_ERR_INCORRECT_KERNEL_ARG, "check_guards: the context was not opened with debug bit 2");
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) return cuda_fail(ctx, ZYXB_ERR_KERNEL_SYNC, "check_guards", e);
+  std::vector<uint8_t> host;
+  for (uint32_t id = 1; id < D.buffers.size(); ++id) {
+    const Buffer& b = D.buffers[id];
+    if (!b.live || b.is_view || b.is_variable || b.capacity <= b.bytes) continue;
+    host.resize(b.capacity - b.bytes);
+    if ((e = cudaMemcpy(host.data(), (const char*)b.ptr + b.bytes, host.size(), cudaMemcpyDeviceToHost)) != cudaSuccess)
+      return cuda_fail(ctx, ZYXB_ERR_KERNEL_SYNC, "check_guards", e);
+    for (size_t i = 0; i < host.size(); ++i)
+      if (host[i] != (uint8_t)GUARD_PATTERN) {
+        if (out_bad_buffer) *out_bad_buffer = id;
+        return fail(ctx, ZYXB_ERR_INCORRECT_KERNEL_ARG, "check_guards: buffer " + std::to_string(id) + " (" + std::to_string(b.bytes) +
+                                                         " bytes) was written " + std::to_string(i) + " bytes past its end");
+      }
+  }
   return ZYXB_OK;
 }
 

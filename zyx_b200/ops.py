@@ -19,6 +19,7 @@ class Session:
         self.backend = backend or B.Backend(**kw)
         self.device = self.backend.devices[dev]
         self.pool = self.backend.pools[dev]
+        self.check_guards = bool(kw.get("debug", 0) & 2)
 
     def close(self):
         self.backend.deinitialize()
@@ -37,6 +38,8 @@ class Session:
             if out_init is not None:
                 self.pool.sync_events([self.pool.host_to_pool(np.ascontiguousarray(out_init), out_bufs[0])])
             self.device.launch(prog, in_bufs + out_bufs)
+            if self.check_guards:          # a context opened with debug=2: no kernel may have written past the end of a buffer
+                self.device.check_guards()
             return [self.pool.download(b, s, t) for b, (s, t) in zip(out_bufs, out_specs)]
         finally:
             for b in in_bufs + out_bufs:
