@@ -7,7 +7,7 @@ import pytest
 
 from oracle import models as zm
 from oracle import oracle as zo
-from tests.parity import TOL_BF16, max_rel_err
+from tests.parity import TOL_BF16, assert_parity, exact_layernorm, exact_softmax, max_rel_err
 from zyx_b200 import _lib as L
 
 pytestmark = pytest.mark.gpu
@@ -50,9 +50,9 @@ def test_row_eltwise_and_optimizer_kernels_stay_inside_their_buffers(guarded):
     rng = np.random.default_rng(42)
     for rows, cols in [(3, 1031), (129, 4096), (300, 32768), (5, 7), (64, 40000)]:
         x = rng.standard_normal((rows, cols)).astype(np.float32)
-        assert max_rel_err(guarded.softmax(L.F32, x), zo.softmax(zo.F32, x)) <= 1e-5
+        assert_parity(guarded.softmax(L.F32, x), zo.softmax(zo.F32, x), exact_softmax(x), 1e-5, what="guarded softmax")
         w, b = np.ones(cols, np.float32), np.zeros(cols, np.float32)
-        assert max_rel_err(guarded.layernorm(L.F32, x, w, b, 1e-5), zo.layernorm(zo.F32, x, w, b, 1e-5)) <= 3e-5
+        assert_parity(guarded.layernorm(L.F32, x, w, b, 1e-5), zo.layernorm(zo.F32, x, w, b, 1e-5), exact_layernorm(x, w, b, 1e-5), 1e-5, what="guarded layernorm")
         xb = zo.to_bits(x, zo.BF16)
         guarded.softmax(L.BF16, xb)
         guarded.colsum(L.BF16, xb)

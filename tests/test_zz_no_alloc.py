@@ -67,8 +67,12 @@ def test_two_calls_match_the_colsum_program(sess, dtype, tol, shapes):
             scale = np.sqrt((zo.to_f32(x, dtype).astype(np.float64) ** 2).sum(0))    # a sum that cancels is measured against |x|_2 / 10
             err = np.abs(new.astype(np.float64) - ref) / np.maximum(np.abs(ref), 0.1 * scale)
             assert float(err.max()) <= tol, (call, float(err.max()))
+            # the oracle adds the rows one after the other in f32, the kernel adds partial sums: within the tolerance of the oracle,
+            # or of the float64 column sums where the two f32 orders themselves are farther apart than that
+            exact = zo.to_f32(x, dtype).astype(np.float64).sum(0)
             err = np.abs(new.astype(np.float64) - want) / np.maximum(np.abs(want), 0.1 * scale)
-            assert float(err.max()) <= tol, ("oracle", call, float(err.max()))
+            err64 = np.abs(new.astype(np.float64) - exact) / np.maximum(np.abs(exact), 0.1 * scale)
+            assert float(err.max()) <= tol or float(err64.max()) <= tol, ("oracle", call, float(err.max()), float(err64.max()))
         finally:
             dev.release(prog)
             for b in (bx, by_ref, by_new):

@@ -171,6 +171,8 @@ class Session:
         bufs = [[self.pool.upload(tt[g]) for tt in tensors] for g in range(groups)]
         try:
             self.device.launch(prog, [b for grp in bufs for b in grp])
+            if self.check_guards:
+                self.device.check_guards()
             for g in range(groups):
                 if g == 1:
                     continue
