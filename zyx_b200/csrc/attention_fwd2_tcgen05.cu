@@ -1,0 +1,353 @@
+// Fused self-attention forward, two query tiles per CTA (used when seq is a multiple of 256; attention_tcgen05.cu otherwise).
+//   O = softmax(scale * Q.K^T [causal mask]) . V            MultiheadAttention::forward, zyx-nn/src/multi_head_attention.rs:197-226
+//
+// What bounded the one-tile kernel was not arithmetic: with Q, two K, two V and two P tiles the shared memory was full, so the
+// K/V rings were two deep against a load latency of thousands of clocks, every K/V tile was fetched from L2 once per 128 query
+// rows, and P went through shared memory (a 32 KB write and a 32 KB operand read per tile on top of the products' own 128 KB).
+// Here one CTA owns 256 query rows (tiles a and b) of one (batch, head):
+//   - every K_j / V_j tile is loaded once and used by both query tiles: half the L2 traffic and twice the work per ring slot;
+//   - P never touches shared memory: the softmax writes it as packed 16-bit pairs over the first 64 columns of its own S tile
+//     in TMEM, and P.V takes its A operand from TMEM (tcgen05.mma with a tensor-memory A);
+//   - the two tiles ping-pong: while the softmax warps of one tile work on S_a, the tensor core computes S_b or P_b.V.
+// TMEM (512 columns): S_a | S_b | O_a | O_b, 128 f32 columns each.  Shared memory: Q_a, Q_b, K x 2, V x 2 (192 KB).
+// Roles (640 threads): warp 0 TMA producer, warp 1 issues S = Q.K^T, warp 2 issues O += P.V, warps 4..11 softmax of tile a,
+// warps 12..19 softmax of tile b (two threads per query row, 64 keys each, as in the one-tile kernel).
+// Per tile the chain S_g(j) -> softmax_g(j) -> P_g.V(j) -> S_g(j+1) is sequential (P overwrites S); the other tile fills the gaps.
+// Every mbarrier wait is time-bounded and reports through the device status word.
+#include <cuda.h>
+#include <math_constants.h>
+#include <stdlib.h>
+
+#include <algorithm>
+
+#include "common.cuh"
+#include "internal.h"
+#include "tc_ptx.cuh"
+
+namespace zyxb {
+
+namespace {
+
+constexpr int A2_BM = 128, A2_BN = 128, A2_D = 128;
+constexpr int A2_THREADS = 640;
+constexpr int A2_TILE = 128 * 128 * 2;                      // one 128 x 128 16-bit tile, 32 KB
+constexpr int A2_Q_OFF = 0, A2_K_OFF = 2 * A2_TILE, A2_V_OFF = 4 * A2_TILE;
+constexpr int A2_XCHG_OFF = 6 * A2_TILE;                    // [2 tiles][2 parities][2 halves][128 rows] f32 = 4 KB
+constexpr int A2_BAR_OFF = A2_XCHG_OFF + 4096;
+constexpr int A2_SMEM_TOTAL = A2_BAR_OFF + 256;
+enum { A2_ERR_PRODUCER = 16u, A2_ERR_MMA = 32u, A2_ERR_SOFTMAX = 64u, A2_ERR_ALIGN = 1024u };
+
+struct Attn2Params {
+  void* o; float* lse;
+  uint32_t T, heads;
+  uint32_t ldo;
+  int64_t stride_o_batch;
+  float scale_log2;
+  int causal, rn, is_bf16;
+  uint32_t* status;
+};
+
+// D[tmem] (+)= A[tmem] . B[smem]: the A operand is read from tensor memory (128 lanes = rows, two 16-bit k-elements per column)
+__device__ __forceinline__ void umma_f16_tmem_a(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+__global__ void __launch_bounds__(A2_THREADS, 1)
+attn_fwd2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                 const __grid_constant__ CUtensorMap map_v, Attn2Params p) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const uint32_t base = smem_u32(smem_raw);
+  if (base & 1023u) {
+    if (threadIdx.x == 0) atomicOr(p.status, A2_ERR_ALIGN);
+    return;
+  }
+  uint8_t* base_ptr = smem_raw;
+  const uint32_t bar = base + A2_BAR_OFF;
+  const uint32_t q_full = bar;
+  auto k_full = [&](int s) { return bar + 8u * (1 + s); };
+  auto v_full = [&](int s) { return bar + 8u * (3 + s); };
+  auto k_empty = [&](int s) { return bar + 8u * (5 + s); };    // both tiles' S products of the K tile in stage s have finished
+  auto v_empty = [&](int s) { return bar + 8u * (7 + s); };    // both tiles' P.V products of the V tile in stage s have finished
+  auto s_full = [&](int g) { return bar + 8u * (9 + g); };     // S_g(j) is in TMEM
+  auto p_full = [&](int g) { return bar + 8u * (11 + g); };    // P_g(j) is in TMEM (and O_g rescaled if it had to be)
+  auto pv_done = [&](int g) { return bar + 8u * (13 + g); };   // P_g.V(j) has finished: S_g / P_g may be overwritten, O_g is current
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + A2_BAR_OFF + 8 * 15);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t n_super = p.T / (2 * A2_BM);
+  const uint32_t qs = p.causal ? n_super - 1 - blockIdx.x : blockIdx.x;    // heavy (late) query rows first under a causal mask
+  const uint32_t bh = blockIdx.y, b = bh / p.heads, h = bh % p.heads;
+  // key tiles each query tile visits: tile a = 2*qs sees 0 .. 2*qs, tile b = 2*qs + 1 sees one more
+  const uint32_t n_kv_g[2] = {p.causal ? 2 * qs + 1 : p.T / A2_BN, p.causal ? 2 * qs + 2 : p.T / A2_BN};
+  const uint32_t n_kv = n_kv_g[1];
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(k_full(s), 1); mbar_init(v_full(s), 1); mbar_init(k_empty(s), 1); mbar_init(v_empty(s), 1);
+      mbar_init(s_full(s), 1); mbar_init(p_full(s), 8); mbar_init(pv_done(s), 1);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  constexpr uint32_t TMEM_COLS = 512;
+  if (warp == 1) tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  auto tmem_s = [&](int g) { return tmem_base + (uint32_t)g * A2_BN; };
+  auto tmem_o = [&](int g) { return tmem_base + 2 * A2_BN + (uint32_t)g * A2_D; };
+
+  if (warp == 0) {
+    // ---------------------------------- TMA producer ----------------------------------
+    if (lane == 0) {
+      mbar_expect_tx(q_full, 2 * A2_TILE);
+      for (int g = 0; g < 2; ++g)
+        for (int c = 0; c < 2; ++c)
+          tma_load_4d(base + A2_Q_OFF + g * A2_TILE + c * (A2_TILE / 2), &map_q, q_full, c * 64, (int)((2 * qs + g) * A2_BM), (int)h, (int)b);
+      uint32_t k_issued = 0, v_issued = 0;
+      bool ok = true;
+      for (uint32_t j = 0; j < n_kv; ++j) {
+        const int s = (int)(j & 1);
+        const uint32_t free_parity = ((j >> 1) & 1) ^ 1;
+        if (!mbar_wait(k_empty(s), free_parity, abort_flag, p.status, A2_ERR_PRODUCER)) { ok = false; break; }
+        mbar_expect_tx(k_full(s), A2_TILE);
+        for (int c = 0; c < 2; ++c)
+          tma_load_4d(base + A2_K_OFF + s * A2_TILE + c * (A2_TILE / 2), &map_k, k_full(s), c * 64, (int)(j * A2_BN), (int)h, (int)b);
+        ++k_issued;
+        if (!mbar_wait(v_empty(s), free_parity, abort_flag, p.status, A2_ERR_PRODUCER)) { ok = false; break; }
+        mbar_expect_tx(v_full(s), A2_TILE);
+        for (int kb = 0; kb < 2; ++kb)
+          for (int c = 0; c < 2; ++c)
+            tma_load_4d(base + A2_V_OFF + s * A2_TILE + kb * (A2_TILE / 2) + c * (A2_TILE / 4), &map_v, v_full(s), c * 64,
+                        (int)(j * A2_BN) + kb * 64, (int)h, (int)b);
+        ++v_issued;
+      }
+      if (!ok) {   // drain: wait (bounded) for copies still in flight so none lands after the CTA has gone
+        const uint64_t t0 = global_timer_ns();
+        for (uint32_t i = 0; i < 2; ++i) {
+          if (i < k_issued) { const uint32_t j = k_issued - 1 - i; while (!mbar_try_wait(k_full(j & 1), (j >> 1) & 1) && global_timer_ns() - t0 < TC_WAIT_NS) {} }
+          if (i < v_issued) { const uint32_t j = v_issued - 1 - i; while (!mbar_try_wait(v_full(j & 1), (j >> 1) & 1) && global_timer_ns() - t0 < TC_WAIT_NS) {} }
+        }
+        while (!mbar_try_wait(q_full, 0) && global_timer_ns() - t0 < TC_WAIT_NS) {}
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------- S = Q_g . K_j^T ----------------------------------
+    if (lane == 0) {
+      const bool bf16 = p.is_bf16 != 0;
+      const uint32_t idesc_s = make_idesc(bf16, false, false, A2_BM, A2_BN);
+      bool ok = mbar_wait(q_full, 0, abort_flag, p.status, A2_ERR_MMA);
+      for (uint32_t j = 0; j < n_kv && ok; ++j) {
+        const int s = (int)(j & 1);
+        if (!mbar_wait(k_full(s), (j >> 1) & 1, abort_flag, p.status, A2_ERR_MMA)) { ok = false; break; }
+        for (int g = 0; g < 2 && ok; ++g) {
+          if (j >= n_kv_g[g]) continue;
+          // S_g aliases P_g: the previous tile's P_g.V must have consumed it
+          if (j > 0 && !mbar_wait(pv_done(g), (j - 1) & 1, abort_flag, p.status, A2_ERR_MMA)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t q_addr = base + A2_Q_OFF + g * A2_TILE, k_addr = base + A2_K_OFF + s * A2_TILE;
+#pragma unroll
+          for (int c = 0; c < 2; ++c)
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk)
+              umma_f16(tmem_s(g), make_smem_desc(q_addr + c * (A2_TILE / 2) + kk * 32, 16, 1024),
+                       make_smem_desc(k_addr + c * (A2_TILE / 2) + kk * 32, 16, 1024), idesc_s, (c | kk) != 0 ? 1u : 0u);
+          umma_commit(s_full(g));
+        }
+        if (ok) umma_commit(k_empty(s));
+      }
+    }
+  } else if (warp == 2) {
+    // ---------------------------------- O_g += P_g . V_j ----------------------------------
+    if (lane == 0) {
+      const bool bf16 = p.is_bf16 != 0;
+      const uint32_t idesc_pv = make_idesc(bf16, false, true, A2_BM, A2_D);     // P (from TMEM, K-major) x V (N-major)
+      bool ok = true;
+      for (uint32_t j = 0; j < n_kv && ok; ++j) {
+        const int s = (int)(j & 1);
+        if (!mbar_wait(v_full(s), (j >> 1) & 1, abort_flag, p.status, A2_ERR_MMA)) { ok = false; break; }
+        for (int g = 0; g < 2 && ok; ++g) {
+          if (j >= n_kv_g[g]) continue;
+          if (!mbar_wait(p_full(g), j & 1, abort_flag, p.status, A2_ERR_MMA)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t v_addr = base + A2_V_OFF + s * A2_TILE;
+#pragma unroll
+          for (int kb = 0; kb < 2; ++kb)       // 64 keys per k-block of V
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk)     // 16 keys per instruction = 8 columns of packed P
+              umma_f16_tmem_a(tmem_o(g), tmem_s(g) + (uint32_t)(kb * 32 + kk * 8),
+                              make_smem_desc(v_addr + kb * (A2_TILE / 2) + kk * (16 * 128), A2_TILE / 4, 1024), idesc_pv,
+                              (j != 0 || (kb | kk) != 0) ? 1u : 0u);
+          umma_commit(pv_done(g));
+        }
+        if (ok) umma_commit(v_empty(s));
+      }
+    }
+  } else if (warp >= 4) {
+    // ---------------------------------- softmax warps ----------------------------------
+    const int g = (warp - 4) >> 3;                           // which query tile
+    const uint32_t quarter = (uint32_t)(warp & 3);           // TMEM lanes this warp may access
+    const int half = ((warp - 4) >> 2) & 1;                  // keys 0..63 or 64..127 of a tile
+    const uint32_t row = quarter * 32 + lane;
+    const uint32_t lane_addr = (quarter * 32u) << 16;
+    const bool bf16 = p.is_bf16 != 0;
+    const uint32_t qt = 2 * qs + (uint32_t)g;                // this group's query tile
+    const uint32_t my_kv = n_kv_g[g];
+    float* xchg = reinterpret_cast<float*>(base_ptr + A2_XCHG_OFF) + g * 512;       // [2 parities][2 halves][128 rows]
+    auto pair_sync = [&]() { asm volatile("bar.sync %0, 64;" ::"r"(1 + g * 4 + (int)quarter) : "memory"); };
+    float m = -CUDART_INF_F, l = 0.0f;
+    bool ok = true;
+    for (uint32_t j = 0; j < my_kv && ok; ++j) {
+      if (!mbar_wait(s_full(g), j & 1, abort_flag, p.status, A2_ERR_SOFTMAX)) { ok = false; break; }
+      tc_fence_after();
+      uint32_t r[64];
+      {
+        uint32_t (&r0)[32] = *reinterpret_cast<uint32_t (*)[32]>(&r[0]);
+        uint32_t (&r1)[32] = *reinterpret_cast<uint32_t (*)[32]>(&r[32]);
+        tmem_ld32(tmem_s(g) + lane_addr + half * 64, r0);
+        tmem_ld32(tmem_s(g) + lane_addr + half * 64 + 32, r1);
+      }
+      tmem_ld_wait();
+      tc_fence_before();                                     // the partner's P store below overwrites columns this thread has just read
+      const bool diag = p.causal && j == qt;
+      const int32_t lim = (int32_t)row - half * 64;
+      float mx4[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
+      if (!diag) {
+#pragma unroll
+        for (int i = 0; i < 64; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(r[i]));
+      } else {
+#pragma unroll
+        for (int i = 0; i < 64; ++i) mx4[i & 3] = i > lim ? mx4[i & 3] : fmaxf(mx4[i & 3], __uint_as_float(r[i]));
+      }
+      float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+      float* xm = xchg + (j & 1) * 256;
+      xm[half * 128 + row] = mx;
+      pair_sync();                                           // also: both halves hold their scores in registers, P may overwrite S
+      tc_fence_after();
+      mx = fmaxf(mx, xm[(half ^ 1) * 128 + row]);
+      // lazy reference point (see attention_tcgen05.cu): it moves only when the maximum grew by more than 2^8 beyond it
+      const float m_seen = fmaxf(m, mx * p.scale_log2);
+      const bool same = !(m_seen - m > 8.0f);
+      const float m_new = same ? m : m_seen;
+      const float alpha = same ? 1.0f : ex2f(m - m_new);
+      float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+      uint32_t pk[32];
+      if (!diag) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const float e0 = ex2f(fmaf(__uint_as_float(r[2 * i]), p.scale_log2, -m_new));
+          const float e1 = ex2f(fmaf(__uint_as_float(r[2 * i + 1]), p.scale_log2, -m_new));
+          sum4[i & 3] += e0 + e1;
+          pk[i] = pack2(e0, e1, bf16);
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float e0 = ex2f(fmaf(__uint_as_float(r[2 * i]), p.scale_log2, -m_new));
+          float e1 = ex2f(fmaf(__uint_as_float(r[2 * i + 1]), p.scale_log2, -m_new));
+          e0 = 2 * i > lim ? 0.0f : e0;
+          e1 = 2 * i + 1 > lim ? 0.0f : e1;
+          sum4[i & 3] += e0 + e1;
+          pk[i] = pack2(e0, e1, bf16);
+        }
+      }
+      // O_g is rescaled only when some row's reference point moved; the previous P_g.V has finished by then (S_g(j) was
+      // issued after it), the wait only makes that visible to this thread
+      if (j > 0 && !__all_sync(0xffffffffu, same)) {
+        if (!mbar_wait(pv_done(g), (j - 1) & 1, abort_flag, p.status, A2_ERR_SOFTMAX)) { ok = false; break; }
+        tc_fence_after();
+#pragma unroll 1
+        for (int ch = 0; ch < 2; ++ch) {
+          uint32_t o[32];
+          tmem_ld32(tmem_o(g) + lane_addr + half * 64 + ch * 32, o);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+          tmem_st32(tmem_o(g) + lane_addr + half * 64 + ch * 32, o);
+        }
+      }
+      // P_g: 64 keys = 32 packed columns, over the first 64 columns of S_g (keys 64*half ..)
+      tmem_st32(tmem_s(g) + lane_addr + half * 32, pk);
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_full(g));
+      l = l * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
+      m = m_new;
+    }
+    if (ok && mbar_wait(pv_done(g), (my_kv - 1) & 1, abort_flag, p.status, A2_ERR_SOFTMAX)) {
+      tc_fence_after();
+      float* xl = xchg + (my_kv & 1) * 256;                  // the parity the last tile did not use
+      xl[half * 128 + row] = l;
+      pair_sync();
+      l += xl[(half ^ 1) * 128 + row];
+      const float inv = 1.0f / l;
+      const bool rn = p.rn != 0;
+      const uint64_t grow = (uint64_t)qt * A2_BM + row;
+      uint16_t* orow = reinterpret_cast<uint16_t*>(p.o) + (int64_t)b * p.stride_o_batch + (int64_t)grow * p.ldo + (int64_t)h * A2_D + half * 64;
+#pragma unroll 1
+      for (int ch = 0; ch < 2; ++ch) {
+        uint32_t o[32];
+        tmem_ld32(tmem_o(g) + lane_addr + half * 64 + ch * 32, o);
+        tmem_ld_wait();
+        uint32_t w[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const float a = __uint_as_float(o[2 * i]) * inv, c = __uint_as_float(o[2 * i + 1]) * inv;
+          const uint16_t lo = bf16 ? f32_to_bf16(a, rn) : f32_to_f16(a, rn), hi = bf16 ? f32_to_bf16(c, rn) : f32_to_f16(c, rn);
+          w[i] = (uint32_t)lo | ((uint32_t)hi << 16);
+        }
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+          *reinterpret_cast<uint4*>(orow + ch * 32 + q * 8) = make_uint4(w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
+      }
+      if (p.lse && half == 0) p.lse[(uint64_t)bh * p.T + grow] = (m + log2f(l)) * 0.6931471805599453f;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+}  // namespace
+
+bool attention_fwd2_supported(const zyxb_attention_desc& d) {
+  static const bool off = getenv("ZYXB_ATTENTION_ONE_TILE") != nullptr;
+  return !off && d.seq % (2 * A2_BM) == 0;
+}
+
+int launch_attention_fwd2(const zyxb_attention_desc& d, void* const* args, const LaunchCtx& lc, std::string& err) {
+  const uint64_t E = d.heads * d.head_dim, ld = d.ld ? d.ld : E;
+  const bool bf16 = d.dtype == ZYXB_BF16;
+  CUtensorMap mq, mk, mv;
+  const bool okm = encode_map(lc.tma_encode, &mq, bf16, args[0], d.head_dim, d.seq, ld, d.heads, d.head_dim, d.batch, d.seq * ld, A2_BM) &&
+                   encode_map(lc.tma_encode, &mk, bf16, args[1], d.head_dim, d.seq, ld, d.heads, d.head_dim, d.batch, d.seq * ld, A2_BN) &&
+                   encode_map(lc.tma_encode, &mv, bf16, args[2], d.head_dim, d.seq, ld, d.heads, d.head_dim, d.batch, d.seq * ld, 64);
+  if (!okm) { err = "attention: cuTensorMapEncodeTiled rejected an operand"; return ZYXB_ERR_KERNEL_LAUNCH; }
+  Attn2Params p{};
+  p.o = args[3]; p.lse = reinterpret_cast<float*>(args[4]);
+  p.T = (uint32_t)d.seq; p.heads = (uint32_t)d.heads; p.ldo = (uint32_t)ld; p.stride_o_batch = (int64_t)(d.seq * ld);
+  const float scale = d.scale > 0.0f ? d.scale : 1.0f / sqrtf((float)d.head_dim);
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.causal = d.causal ? 1 : 0; p.rn = lc.round_nearest ? 1 : 0; p.is_bf16 = bf16 ? 1 : 0; p.status = lc.status_word;
+  static uint64_t configured = 0;
+  {
+    cudaError_t e = ensure_dynamic_smem(attn_fwd2_kernel, A2_SMEM_TOTAL, &configured);
+    if (e != cudaSuccess) { err = std::string("attention: ") + cudaGetErrorString(e); return ZYXB_ERR_KERNEL_LAUNCH; }
+  }
+  const dim3 grid((unsigned)(d.seq / (2 * A2_BM)), (unsigned)(d.batch * d.heads));
+  attn_fwd2_kernel<<<grid, A2_THREADS, A2_SMEM_TOTAL, lc.stream>>>(mq, mk, mv, p);
+  return check_launch(lc, err, "attention");
+}
+
+}  // namespace zyxb

@@ -342,6 +342,7 @@ int launch_attention(const zyxb_attention_desc& d, void* const* args, const uint
     ZYXB_CHECK_ARG((uintptr_t)args[i] % 16 == 0, "attention: operands must be 16-byte aligned");
   }
   ZYXB_CHECK_ARG(arg_bytes[4] >= d.batch * d.heads * d.seq * 4, "attention: lse too small");
+  if (attention_fwd2_supported(d)) return launch_attention_fwd2(d, args, lc, err);     // two query tiles per CTA
   const bool bf16 = d.dtype == ZYXB_BF16;
   CUtensorMap mq, mk, mv;
   const bool okm = encode_map(lc.tma_encode, &mq, bf16, args[0], d.head_dim, d.seq, ld, d.heads, d.head_dim, d.batch, d.seq * ld, AT_BM) &&

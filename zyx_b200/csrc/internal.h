@@ -51,6 +51,8 @@ int launch_conv_wgrad(const zyxb_conv_desc& d, void* const* args, const uint64_t
 int launch_colsum_static(int dtype, const void* x, void* y, uint64_t rows, uint64_t cols, const LaunchCtx& lc, std::string& err);
 uint64_t colsum_static_capacity();
 bool colsum_static_ready(int cuda_device);
+bool attention_fwd2_supported(const zyxb_attention_desc& d);
+int launch_attention_fwd2(const zyxb_attention_desc& d, void* const* args, const LaunchCtx& lc, std::string& err);
 int launch_bounded_wait_selftest(uint64_t limit_ns, uint32_t* out_gave_up_dev, const LaunchCtx& lc, std::string& err);
 
 int validate_rowreduce(const zyxb_rowreduce_desc& d, std::string& err);

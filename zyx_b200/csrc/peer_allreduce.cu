@@ -169,6 +169,9 @@ struct PeerComm {
   void* staging = nullptr;              // (world - 1) shards pulled from the peers
   uint64_t staging_bytes = 0;
   void* xchg = nullptr;                 // device scratch for handle exchange: world + 1 slots of 128 bytes
+  // the world-1 peer copies of a phase run side by side, one copy engine each: one extra stream and one event per peer
+  cudaStream_t side[PEER_MAX_WORLD] = {nullptr};
+  cudaEvent_t fork = nullptr, join[PEER_MAX_WORLD] = {nullptr};
   std::map<const void*, PeerBuffer> buffers;
 };
 
@@ -242,6 +245,11 @@ int peer_create(PeerComm** out, Comm* c, uint32_t* status_word, cudaStream_t str
   if (e == cudaSuccess) e = cudaMalloc((void**)&p->flags, FLAG_KINDS * PEER_MAX_WORLD * sizeof(uint32_t));
   if (e == cudaSuccess) e = cudaMemset(p->flags, 0, FLAG_KINDS * PEER_MAX_WORLD * sizeof(uint32_t));
   if (e == cudaSuccess) e = cudaDeviceSynchronize();
+  if (e == cudaSuccess) e = cudaEventCreateWithFlags(&p->fork, cudaEventDisableTiming);
+  for (int i = 0; i + 2 < p->world && e == cudaSuccess; ++i) {
+    e = cudaStreamCreateWithFlags(&p->side[i], cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&p->join[i], cudaEventDisableTiming);
+  }
   if (e != cudaSuccess) { err = std::string("peer allreduce set-up: ") + cudaGetErrorString(e); return ZYXB_ERR_MEMORY_ALLOCATION; }
   void* mapped[PEER_MAX_WORLD];
   bool ok = false;
@@ -265,6 +273,8 @@ void peer_destroy(PeerComm* p) {
   cudaDeviceSynchronize();
   while (!p->buffers.empty()) peer_forget_buffer(p, p->buffers.begin()->first);
   for (int r = 0; r < p->world; ++r) if (r != p->rank && p->table.peer[r]) cudaIpcCloseMemHandle(p->table.peer[r]);
+  for (int i = 0; i < PEER_MAX_WORLD; ++i) { if (p->side[i]) cudaStreamDestroy(p->side[i]); if (p->join[i]) cudaEventDestroy(p->join[i]); }
+  if (p->fork) cudaEventDestroy(p->fork);
   if (p->staging) cudaFree(p->staging);
   if (p->flags) cudaFree(p->flags);
   if (p->xchg) cudaFree(p->xchg);
@@ -312,14 +322,26 @@ int peer_allreduce_sum(PeerComm* p, Comm* c, void* base, uint64_t buffer_bytes, 
   // 1. my gradients are complete / theirs are
   signal_wait(FLAG_READY);
   // 2. pull my shard of every peer's buffer (nearest rank first, so that the W pulls of one moment spread over the peers)
+  // copy number d of a phase goes to the main stream (d == 1) or to side stream d - 2, forked from and joined to the main one
+  auto fork = [&]() { if (W > 2 && e == cudaSuccess) e = cudaEventRecord(p->fork, stream); };
+  auto copy_on = [&](int d, void* dst, const void* srcp, uint64_t bytes) {
+    if (e != cudaSuccess) return;
+    cudaStream_t st = d == 1 ? stream : p->side[d - 2];
+    if (d > 1) e = cudaStreamWaitEvent(st, p->fork, 0);
+    if (e == cudaSuccess && bytes) e = cudaMemcpyAsync(dst, srcp, bytes, cudaMemcpyDeviceToDevice, st);
+    if (d > 1 && e == cudaSuccess) e = cudaEventRecord(p->join[d - 2], st);
+  };
+  auto join = [&]() { for (int d = 2; d < W && e == cudaSuccess; ++d) e = cudaStreamWaitEvent(stream, p->join[d - 2], 0); };
   ReduceSrc src{};
   int slot = 0;
+  fork();
   for (int d = 1; d < W; ++d) {
     const int r = (me + d) % W;
     char* dst = (char*)p->staging + (uint64_t)slot++ * cs * es;
     src.ptr[r] = dst;
-    if (mine_n && e == cudaSuccess) e = cudaMemcpyAsync(dst, at(B.peer_base[r], lo(me)), mine_n * es, cudaMemcpyDeviceToDevice, stream);
+    copy_on(d, dst, at(B.peer_base[r], lo(me)), mine_n * es);
   }
+  join();
   src.ptr[me] = at(base, lo(me));
   if (e != cudaSuccess) { err = std::string("peer allreduce pull: ") + cudaGetErrorString(e); return ZYXB_ERR_KERNEL_LAUNCH; }
   // 3. add, in rank order
@@ -339,11 +361,12 @@ int peer_allreduce_sum(PeerComm* p, Comm* c, void* base, uint64_t buffer_bytes, 
   // 4. my shard is reduced / theirs are
   signal_wait(FLAG_REDUCED);
   // 5. pull every peer's reduced shard
-  for (int d = 1; d < W && e == cudaSuccess; ++d) {
+  fork();
+  for (int d = 1; d < W; ++d) {
     const int r = (me + d) % W;
-    const uint64_t n = hi(r) - lo(r);
-    if (n) e = cudaMemcpyAsync(at(base, lo(r)), at(B.peer_base[r], lo(r)), n * es, cudaMemcpyDeviceToDevice, stream);
+    copy_on(d, at(base, lo(r)), at(B.peer_base[r], lo(r)), (hi(r) - lo(r)) * es);
   }
+  join();
   if (e != cudaSuccess) { err = std::string("peer allreduce gather: ") + cudaGetErrorString(e); return ZYXB_ERR_KERNEL_LAUNCH; }
   // 6. I have read every peer's shard / every peer has read mine: from here on the buffer may be written again
   signal_wait(FLAG_GATHERED);
