@@ -1,5 +1,9 @@
 """Parity of the fused attention kernel (tcgen05) with the oracle's composition of the reference's attention:
 scores matmul -> masked softmax -> probabilities matmul, each stored in the tensor dtype."""
+import os
+import subprocess
+import sys
+
 import numpy as np
 import pytest
 
@@ -39,6 +43,41 @@ def test_fused_attention_matches_the_composed_reference(sess, dtype, causal, bat
     want, want_lse, exact = zm.attention(dtype, q, k, v, heads, causal)
     check(o, want, exact, dtype)
     assert np.max(np.abs(lse - want_lse)) <= 1e-3 * max(1.0, float(np.max(np.abs(want_lse))))
+
+
+_CHILD = """
+import sys, numpy as np
+from zyx_b200 import ops
+d = np.load(sys.argv[1])
+s = ops.Session(device_ids=[0])
+o, lse = s.attention(int(d['dtype']), d['q'], d['k'], d['v'], int(d['heads']), causal=bool(d['causal']))
+assert s.device.status() == 0
+np.savez(sys.argv[2], o=o, lse=lse)
+s.close()
+"""
+
+
+@pytest.mark.parametrize("causal", [True, False])
+def test_two_tile_and_one_tile_forward_agree(sess, tmp_path, causal):
+    """Lengths that are multiples of 256 take the kernel with two query tiles per CTA (P as a TMEM operand); a child
+    process with ZYXB_ATTENTION_ONE_TILE set runs the same inputs through the one-tile kernel.  Both keep scores and sums
+    in f32 and round P to the 16-bit type once, so outputs differ by at most one rounding step of the output type."""
+    dtype, batch, heads, seq, D = L.BF16, 2, 2, 1024, 128
+    q, k, v = (rand((batch, seq, heads * D), dtype) for _ in range(3))
+    o2, lse2 = sess.attention(dtype, q, k, v, heads, causal=causal)
+    assert sess.device.status() == 0
+    want, want_lse, exact = zm.attention(dtype, q, k, v, heads, causal)
+    check(o2, want, exact, dtype)
+    src, dst = tmp_path / "in.npz", tmp_path / "out.npz"
+    np.savez(src, q=q, k=k, v=v, dtype=dtype, heads=heads, causal=causal)
+    env = dict(os.environ, ZYXB_ATTENTION_ONE_TILE="1")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    subprocess.run([sys.executable, "-c", _CHILD, str(src), str(dst)], check=True, env=env, cwd=root, timeout=600)
+    one = np.load(dst)
+    a, b = zo.to_f32(o2, dtype).astype(np.float64), zo.to_f32(one["o"], dtype).astype(np.float64)
+    scale = np.maximum(np.abs(b), np.max(np.abs(b), axis=-1, keepdims=True))
+    assert np.max(np.abs(a - b) / scale) <= 2.0 ** -7          # two bf16 roundings of nearly equal f32 values
+    assert np.max(np.abs(lse2 - one["lse"])) <= 1e-4 * max(1.0, float(np.max(np.abs(want_lse))))
 
 
 def test_fused_attention_large_scores_and_custom_scale(sess):
