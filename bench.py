@@ -907,8 +907,8 @@ class BlockTrain:
     scaling = "strong"      # the global batch of 8 is divided over the ranks (one sample per GPU at 8 GPUs)
     unit, dtype, bound = "samples/s", "bf16", "tensor"
 
-    def __init__(self, size=0, rank=0, world=1, fused=False):
-        self.rank, self.world, self.fused = rank, world, fused
+    def __init__(self, size=0, rank=0, world=1, fused=False, shard_optimizer=False):
+        self.rank, self.world, self.fused, self.shard = rank, world, fused, shard_optimizer
         self.B = size if size else max(1, self.GLOBAL_B // world)
         self.name = "transformer_block_d2048_h16_ffn8192_seq2048_bf16_causal_batch%d_per_gpu" % self.B
         self.metric = "transformer block train samples/s (d=2048, 16x128 heads, FFN 8192, seq 2048, bf16, causal, fwd+bwd+AdamW)"
@@ -939,7 +939,7 @@ class BlockTrain:
         self.sess, self.Hm = sess, H
         self.host_inputs()
         self.blk = H.Block(sess, L.BF16, self.B, self.T, self.E, self.H, self.F, causal=True, algo=L.OPT_ADAMW, world=self.world,
-                           fused_attention=self.fused, lr=1e-3, weight_decay=0.01, standard=True)
+                           fused_attention=self.fused, shard_optimizer=self.shard, lr=1e-3, weight_decay=0.01, standard=True)
         rng = np.random.default_rng(0)
         for i, shape in enumerate(self.blk.shapes):
             if i >= 12:
@@ -954,7 +954,8 @@ class BlockTrain:
                        "attention": ("fused (scores and probabilities stay on chip, recomputed in the backward)" if self.fused else
                                      "scores materialised ([B*H, T, T] bf16) as in the reference; causal mask as a select"),
                        "l2": "working set (activations %d MiB) larger than L2" % (30 * self.B * self.T * self.E * 2 >> 20),
-                       "launches_per_step": launches, "collectives_per_step": colls}
+                       "launches_per_step": launches, "collectives_per_step": colls,
+                       "optimizer_state": "sharded over the ranks (reduce-scatter, shard update, all-gather)" if self.shard else "replicated"}
         self.losses = []
         self.step_events = []
 
@@ -1018,7 +1019,7 @@ def make_workload(args, rank=0, world=1):
     if args.workload == "simplenet":
         return SimpleNet(size=args.size, rank=rank, world=world)
     if args.workload == "block":
-        return BlockTrain(size=args.size, rank=rank, world=world, fused=not args.unfused_attention)
+        return BlockTrain(size=args.size, rank=rank, world=world, fused=not args.unfused_attention, shard_optimizer=args.shard_optimizer)
     if args.size:
         return {"rowreduce": lambda: RowReduce(rows=args.size), "attn_rows": lambda: AttnRows(rows=args.size), "attention": lambda: AttentionFwd(args.size), "conv": lambda: Conv(args.size), "conv_nhwc": lambda: Conv(args.size, True), "gemm_bf16": lambda: Gemm("bf16", args.size),
                 "gemm_f32": lambda: Gemm("f32", args.size)}[args.workload]()
@@ -1128,7 +1129,7 @@ def run():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end leg (profiling runs)")
     ap.add_argument("--no-check", action="store_true", help="skip the sampled parity check against the oracle (quick comparisons)")
-    ap.add_argument("--shard-optimizer", action="store_true", help="mlp workload: ZeRO stage 1 (reduce-scatter, sharded AdamW, all-gather) instead of allreduce + replicated AdamW")
+    ap.add_argument("--shard-optimizer", action="store_true", help="mlp and block workloads: ZeRO stage 1 (reduce-scatter, sharded AdamW, all-gather) instead of allreduce + replicated AdamW")
     ap.add_argument("--size", type=int, default=0, help="reduced problem size for profiler captures: rows (rowreduce) or N (gemm)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)

@@ -101,6 +101,9 @@ typedef struct {
   int32_t  fused_attention; /* 1: scores, softmax and probabilities.v (and their adjoints) run as the fused attention
                                programs where the shape allows (16-bit dtype, head_dim 128, seq a multiple of 128); the
                                [batch*heads, seq, seq] tensors are then not allocated and activation 0 does not exist */
+  int32_t  shard_optimizer; /* 1 (needs a communicator of `world` ranks): ZeRO stage 1 as in zyxb_mlp_config - parameters in
+                               one bucket laid out like the gradients', each of the three groups reduce-scattered, updated by
+                               shard with optimizer state of shard size only, and all-gathered, the q/k/v group first */
 } zyxb_block_config;
 
 typedef struct zyxb_block zyxb_block;

@@ -79,3 +79,63 @@ def test_block_forward_backward_and_update(sess, dtype, B, T, E, heads, F, causa
             assert e <= max(tol * 5, 2e-3 if dtype == L.F32 else tol), (name, e)
     finally:
         blk.close()
+
+
+def block_case(seed, dtype, B, T, E, F, steps):
+    """Seeded parameters and batches of a block (also used by the two-rank test)."""
+    rng = np.random.default_rng(seed)
+    p = om.block_init(rng, dtype, E, F, std=0.05)
+    for k in ("g1", "g2"):
+        p[k] = zo.to_bits((1 + 0.1 * rng.standard_normal(E)).astype(np.float32), dtype)
+    batches = [(zo.to_bits(rng.standard_normal((B, T, E)).astype(np.float32), dtype),
+                zo.to_bits(rng.standard_normal((B, T, E)).astype(np.float32), dtype)) for _ in range(steps)]
+    return p, batches
+
+
+@pytest.mark.parametrize("fused", [False, True])
+def test_sharded_optimizer_block_plan_equals_the_replicated_plan(sess, tmp_path, fused):
+    """ZeRO stage 1 of the block plan on a one-rank communicator: parameters in one bucket, three reduce-scatters, three
+    shard updates, three all-gathers.  Kernels and arithmetic are the replicated plan's, so after three steps losses and
+    parameters are bit-identical; the optimizer state has no per-tensor buffers; a checkpoint of the sharded plan restores
+    into a fresh sharded plan and continues with the same bits."""
+    dtype, B, T, E, heads, F = L.BF16, 2, 256, 512, 4, 1024
+    p, batches = block_case(11, dtype, B, T, E, F, 4)
+    kw = dict(lr=1e-3, weight_decay=0.01, standard=True)
+
+    def train(shard, steps, resume=None, save_at=None):
+        blk = H.Block(sess, dtype, B, T, E, heads, F, causal=True, algo=L.OPT_ADAMW, world=1, fused_attention=fused, shard_optimizer=shard, **kw)
+        try:
+            if resume:
+                assert blk.load(resume) == 0
+            else:
+                for i, name in enumerate(om.BLOCK_PARAMS):
+                    blk.set_tensor(H.PARAM, i, p[name])
+            losses = []
+            for n, (x, t) in enumerate(steps):
+                blk.step(blk.set_batch(x, t))
+                losses.append(blk.read_loss())
+                if save_at == n:
+                    blk.save(save_at_path)
+            assert sess.device.status() == 0
+            if shard:
+                assert blk.plan_size()[1] == 6
+                with pytest.raises(Exception):
+                    blk.tensor(H.STATE0, 0)
+            return losses, [blk.get_tensor(H.PARAM, i) for i in range(len(om.BLOCK_PARAMS))]
+        finally:
+            blk.close()
+
+    save_at_path = str(tmp_path / "blk.safetensors")
+    want_losses, want = train(False, batches)
+    sess.device.comm_init(0, 1, sess.device.comm_unique_id())
+    try:
+        got_losses, got = train(True, batches, save_at=1)
+        tail_losses, tail = train(True, batches[2:], resume=save_at_path)
+    finally:
+        sess.device.comm_destroy()
+    assert got_losses == want_losses
+    for g, w in zip(got, want):
+        assert np.array_equal(g, w)
+    assert tail_losses == want_losses[2:]
+    for g, w in zip(tail, want):
+        assert np.array_equal(g, w)

@@ -238,3 +238,55 @@ def test_input_gradient_with_strides_takes_the_direct_kernel(sess, dtype, channe
         tol = TOL_F32 if dtype == L.F32 else TOL_BF16
         from tests.parity import max_rel_err
         assert max_rel_err(f(got), exact, floor=0.1) <= tol
+
+
+STRIDED_DGRAD_CASES = [
+    (2, 64, 56, 56, 128, 3, 3, 2, 1, 1),                          # the down-sampling 3x3 of a residual network: four phases of 1, 2, 2, 4 taps
+    (4, 64, 57, 55, 128, 1, 1, 2, 1, 0),                          # 1x1 stride 2: three of the four phases have no tap (zero gradient)
+    (1, 24, 64, 64, 64, 7, 7, 2, 1, 3),                           # 7x7 stride 2, 24 channels
+    (6, 40, 31, 29, 24, 3, 3, (2, 1), (1, 2), (0, 2, 1, 3)),      # stride only in h, dilation only in w, asymmetric padding
+    (8, 48, 30, 30, 64, 3, 3, 3, 1, 0),                           # stride = filter size: nine one-tap phases
+    (4, 32, 40, 40, 64, 3, 3, 2, 2, 2),                           # stride 2 with dilation 2: only the even input positions are ever read
+]
+
+
+@pytest.mark.parametrize("dtype,channels_last", [(L.BF16, False), (L.BF16, True), (L.F16, False)])
+@pytest.mark.parametrize("case", STRIDED_DGRAD_CASES)
+def test_strided_input_gradient_on_tensor_cores(sess, dtype, channels_last, case):
+    """Stride > 1: one stride-1 convolution per residue class of the input positions, each with the sub-filter of the taps
+    that reach the class, written to the class's positions of dx.  Oracle: the transposed-convolution identity through the
+    oracle's own convolution - dy with stride-1 zeros inserted between its elements, convolved with the filter transposed in
+    (o, c) and reversed in (r, s) - and float64 autograd as the third party."""
+    from zyx_b200 import backend as B
+    n, c, h, w_, o, kh, kw, stride, dil, padding = case
+    sh, sw = (stride, stride) if isinstance(stride, int) else stride
+    dh, dw = (dil, dil) if isinstance(dil, int) else dil
+    pads = (padding,) * 4 if isinstance(padding, int) else padding
+    shape = B.conv_out_shape((n, c, h, w_), (o, c, kh, kw), stride, dil, pads)
+    wt = zo.to_bits((RNG.standard_normal((o, c, kh, kw)) / np.sqrt(o * kh * kw)).astype(np.float32), dtype)
+    dy = zo.to_bits(RNG.standard_normal(shape).astype(np.float32), dtype)
+    dy_in = np.ascontiguousarray(dy.transpose(0, 2, 3, 1)) if channels_last else dy
+    before = sess.device.launch_count()
+    got = sess.conv_input_grad(dtype, dy_in, wt, (h, w_), stride, dil, pads, channels_last=channels_last)
+    launches = sess.device.launch_count() - before
+    assert sess.device.status() == 0
+    if channels_last:
+        got = np.ascontiguousarray(got.transpose(0, 3, 1, 2))
+    assert got.shape == (n, c, h, w_)
+    assert launches >= 2, "the phases launch a filter layout kernel and a matmul kernel each; the direct kernel is one launch"
+    oh, ow = shape[2], shape[3]
+    up = np.zeros((n, o, (oh - 1) * sh + 1, (ow - 1) * sw + 1), dy.dtype)
+    up[:, :, ::sh, ::sw] = dy
+    flipped = np.ascontiguousarray(wt.transpose(1, 0, 2, 3)[:, :, ::-1, ::-1])
+    top, left = dh * (kh - 1) - pads[0], dw * (kw - 1) - pads[2]
+    back = (top, h + pads[0] - up.shape[2], left, w_ + pads[2] - up.shape[3])
+    assert min(back) >= 0
+    want = zo.conv(dtype, up, flipped, None, 1, dil, back)
+    x = torch.zeros((n, c, h, w_), dtype=torch.float64, requires_grad=True)
+    y = torch.nn.functional.conv2d(torch.nn.functional.pad(x, (pads[2], pads[3], pads[0], pads[1])),
+                                   torch.from_numpy(zo.to_f32(wt, dtype).astype(np.float64)), stride=stride, dilation=dil)
+    y.backward(torch.from_numpy(zo.to_f32(dy, dtype).astype(np.float64)))
+    exact = x.grad.numpy()
+    assert_parity(zo.to_f32(got, dtype), zo.to_f32(want, dtype), exact, TOL_BF16, floor=0.1, what="strided conv dgrad %s" % (case,))
+    never_read = exact == 0.0            # positions no window element covers
+    assert np.all(zo.to_f32(got, dtype)[never_read] == 0.0)

@@ -171,3 +171,71 @@ def test_allreduce_over_peer_memory_and_over_nccl(tmp_path, mode):
     after call (the sequence numbers of the peer path only grow)."""
     mp.spawn(_rank_allreduce, args=(2, str(tmp_path), mode), nprocs=2, join=True)
     assert all(os.path.exists(str(tmp_path / ("ok_%s_%d" % (mode, r)))) for r in range(2))
+
+
+def _rank_block(rank, world, tmp):
+    """The transformer-block plan on two ranks, replicated (three allreduces) and with the sharded optimizer (three
+    reduce-scatters, shard updates, all-gathers), each rank on its half of the batch."""
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    from oracle import models as om
+    from tests.test_gpu_block import block_case
+    from zyx_b200 import _lib as L
+    from zyx_b200 import host as H
+    from zyx_b200.ops import Session
+    B, T, E, heads, F, STEPS = 1, 256, 512, 4, 1024, 3
+    sess = Session(device_ids=[rank])
+    try:
+        uid_path = os.path.join(tmp, "uid")
+        if rank == 0:
+            with open(uid_path + ".tmp", "wb") as f:
+                f.write(sess.device.comm_unique_id())
+            os.rename(uid_path + ".tmp", uid_path)
+        t0 = time.time()
+        while not os.path.exists(uid_path):
+            assert time.time() - t0 < 60, "no unique id from rank 0"
+            time.sleep(0.05)
+        sess.device.comm_init(rank, world, open(uid_path, "rb").read())
+        p, batches = block_case(5, L.BF16, world * B, T, E, F, STEPS)
+        out, losses = {}, {}
+        for shard in (False, True):
+            blk = H.Block(sess, L.BF16, B, T, E, heads, F, causal=True, algo=L.OPT_ADAMW, world=world, fused_attention=True,
+                          shard_optimizer=shard, lr=1e-3, weight_decay=0.01, standard=True)
+            try:
+                for i, name in enumerate(om.BLOCK_PARAMS):
+                    blk.set_tensor(H.PARAM, i, p[name])
+                losses[shard] = []
+                for x, t in batches:
+                    blk.step(blk.set_batch(x[rank * B:(rank + 1) * B], t[rank * B:(rank + 1) * B]))
+                    losses[shard].append(blk.read_loss())
+                out[shard] = [blk.get_tensor(H.PARAM, i) for i in range(len(om.BLOCK_PARAMS))]
+                assert blk.plan_size()[1] == (6 if shard else 3)
+                assert sess.device.status() == 0
+            finally:
+                blk.close()
+        assert losses[False] == losses[True]
+        np.savez(os.path.join(tmp, "rank%d.npz" % rank), *(out[False] + out[True]), losses=np.array(losses[True]))
+        sess.device.comm_destroy()
+    finally:
+        sess.close()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_block_plans_agree_on_two_ranks(tmp_path):
+    """Both ranks end with the same parameter bits, the sharded plan with the replicated plan's bits, and the first step's
+    loss (taken with identical parameters) is the oracle's on the concatenated batch: the mean over 2 x B samples equals the
+    mean of the two ranks' means."""
+    from oracle import models as om
+    from oracle import oracle as zo
+    from tests.test_gpu_block import block_case
+    mp.spawn(_rank_block, args=(2, str(tmp_path)), nprocs=2, join=True)
+    r0, r1 = (np.load(str(tmp_path / ("rank%d.npz" % r))) for r in range(2))
+    n = len(om.BLOCK_PARAMS)
+    for i in range(n):
+        rep0, shd0 = r0["arr_%d" % i], r0["arr_%d" % (n + i)]
+        assert np.array_equal(rep0, r1["arr_%d" % i]) and np.array_equal(shd0, r1["arr_%d" % (n + i)]), om.BLOCK_PARAMS[i]
+        assert np.array_equal(rep0, shd0), om.BLOCK_PARAMS[i]
+    p, batches = block_case(5, zo.BF16, 2, 256, 512, 1024, 3)
+    assert any(not np.array_equal(r0["arr_%d" % i], p[name]) for i, name in enumerate(om.BLOCK_PARAMS))     # the steps did move them
+    want_loss, _, _, _ = om.block_forward_backward(zo.BF16, p, batches[0][0], batches[0][1], 4, True)
+    got = 0.5 * (float(r0["losses"][0]) + float(r1["losses"][0]))
+    assert abs(got - want_loss) <= 0.02 * abs(want_loss)

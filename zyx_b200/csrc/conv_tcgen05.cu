@@ -23,6 +23,7 @@
 #include <cuda.h>
 
 #include <algorithm>
+#include <vector>
 
 #include "common.cuh"
 #include "internal.h"
@@ -49,7 +50,21 @@ struct ConvTcParams {
   uint32_t positions, tiles_m;        // im2col mode: n*oh*ow output positions in tiles of 128 consecutive ones
   int rn, is_bf16;
   int channels_last;                  // y is [positions, o]: a lane's 32 filters are contiguous
+  // Output placement: position (oy, ox) of the g.oh x g.ow result lands at (off_h + step_h*oy, off_w + step_w*ox) of a
+  // full_h x full_w plane.  The identity (steps 1, offsets 0, full = oh x ow) for a convolution; one residue class of the
+  // input positions for a phase of a strided convolution's input gradient.
+  uint32_t full_h, full_w, step_h, step_w, off_h, off_w;
+  int out_mapped;
   uint32_t* status;
+};
+
+// What a phase of a strided convolution's input gradient changes in the tensor-core launch (see launch_conv_dgrad).
+struct ConvPhase {
+  uint32_t r0, step_r, s0, step_s;    // the forward filter's taps this phase uses: r0 + t*step_r (t < kh of the phase), columns alike
+  uint32_t fkh, fkw;                  // the forward filter's extents
+  uint32_t full_h, full_w, step_h, step_w, off_h, off_w;
+  int pad_bottom, pad_right;          // signed: a phase may ignore the last rows / columns of dy (and its first: negative pt / pl)
+  bool x_ready;                       // the channels-innermost copy of the input already sits in scratch (an earlier phase wrote it)
 };
 
 template <int BN, int STAGES>
@@ -121,6 +136,21 @@ __global__ void conv_weight_kernel(const uint16_t* __restrict__ w, uint16_t* __r
   uint16_t v = 0;
   if (ci < c) v = flipped ? w[((uint64_t)ci * o_count + o) * taps + (taps - 1 - tap)] : w[(o * c + ci) * taps + tap];
   wt[i] = v;
+}
+
+// A phase of a strided input gradient: wt [o][nr*ns][cp] from the forward filter [c][o][fkh][fkw], transposed in (o, c),
+// restricted to the taps (r0 + t*step_r, s0 + u*step_s) and reversed in (t, u).
+__global__ void conv_weight_phase_kernel(const uint16_t* __restrict__ w, uint16_t* __restrict__ wt, uint32_t c, uint32_t cp, uint32_t o_count,
+                                         uint32_t nr, uint32_t ns, uint32_t r0, uint32_t step_r, uint32_t s0, uint32_t step_s, uint32_t fkh, uint32_t fkw,
+                                         uint64_t total) {
+  const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const uint32_t ci = (uint32_t)(i % cp);
+  const uint64_t ot = i / cp;
+  const uint32_t tap = (uint32_t)(ot % (nr * ns));
+  const uint64_t o = ot / (nr * ns);
+  const uint32_t r = r0 + (nr - 1 - tap / ns) * step_r, sx = s0 + (ns - 1 - tap % ns) * step_s;
+  wt[i] = ci < c ? w[((uint64_t)ci * o_count + o) * fkh * fkw + r * fkw + sx] : (uint16_t)0;
 }
 
 // ---- implicit GEMM ---------------------------------------------------------------------------------
@@ -258,16 +288,28 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tma_x, const __grid_constant_
       bool inside;
       uint16_t* ypos;          // channels-first: this lane's position in filter 0's plane
       size_t pos;              // flat index of the position over (image, row, column)
+      size_t oplane = plane;   // elements between two filters' planes of the channels-first output
       if constexpr (IM2COL) {
         const uint32_t m = m0 + row_in_tile, im = m / plane;      // this lane's position: image im, offset m - im * plane in its plane
         inside = m < p.positions;
         ypos = y + (size_t)im * g.o * plane + (m - im * plane);
         pos = m;
+        if (p.out_mapped) {
+          const uint32_t rem = m - im * plane, oy = rem / g.ow, ox = rem - oy * g.ow;
+          oplane = (size_t)p.full_h * p.full_w;
+          pos = ((size_t)im * p.full_h + p.off_h + (size_t)p.step_h * oy) * p.full_w + p.off_w + (size_t)p.step_w * ox;
+          ypos = y + (size_t)im * g.o * oplane + (pos - (size_t)im * oplane);
+        }
       } else {
         const uint32_t oy = oh0 + ty, ox = ow0 + tx;
         inside = oy < g.oh && ox < g.ow;
         ypos = y + (size_t)img * g.o * plane + (size_t)oy * g.ow + ox;
         pos = ((size_t)img * g.oh + oy) * g.ow + ox;
+        if (p.out_mapped) {
+          oplane = (size_t)p.full_h * p.full_w;
+          pos = ((size_t)img * p.full_h + p.off_h + (size_t)p.step_h * oy) * p.full_w + p.off_w + (size_t)p.step_w * ox;
+          ypos = y + (size_t)img * g.o * oplane + (pos - (size_t)img * oplane);
+        }
       }
 #pragma unroll 1
       for (int ch = col_half * (BN / 64); ch < (col_half + 1) * (BN / 64); ++ch) {
@@ -302,7 +344,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tma_x, const __grid_constant_
             if (o < g.o) {
               float v = __uint_as_float(r[j]);
               if (bias) v += is_bf16 ? bf16_to_f32(bias[o]) : f16_to_f32(bias[o]);
-              ypos[(size_t)o * plane] = is_bf16 ? f32_to_bf16(v, rn) : f32_to_f16(v, rn);
+              ypos[(size_t)o * oplane] = is_bf16 ? f32_to_bf16(v, rn) : f32_to_f16(v, rn);
             }
           }
         }
@@ -387,19 +429,20 @@ cudaError_t launch_conv_tc(const CUtensorMap& mx, const CUtensorMap& mw, const C
 
 // The tensor-core path: returns 1 when it took the launch, 0 when the shape is not for it, < 0 on an error (err set).
 int try_conv_tc(const zyxb_conv_desc& d, const ConvGeom& g, const void* x, const void* w, const void* bias, void* y, const LaunchCtx& lc,
-                std::string& err) {
+                std::string& err, const ConvPhase* phase = nullptr) {
   static const bool off = getenv("ZYXB_NO_CONV_TC") != nullptr;
   if (off || !lc.tma_encode || (d.dtype != ZYXB_BF16 && d.dtype != ZYXB_F16)) return 0;
   // latency-bound problems and single-filter outputs stay on the direct kernel
   const uint64_t positions = (uint64_t)g.n * g.oh * g.ow, kdim = (uint64_t)g.c * g.kh * g.kw;
-  if (positions * g.o * kdim < (1ull << 22) || g.o < 8 || positions < 128) return 0;
+  if ((!phase && positions * g.o * kdim < (1ull << 22)) || g.o < 8 || positions < 128) return 0;
   if (g.sw > 8 || g.sh > 8) return 0;                     // element strides of a tensor map go up to 8
   // im2col-mode tensor map: 128 consecutive output positions per tile, whatever the image's width.  Its corners and tap
   // offsets are 8-bit fields for a rank-4 map.
   static const bool tiled_only = getenv("ZYXB_CONV_TILED") != nullptr;
   const int lo_w = -g.pl, lo_h = -g.pt;
-  const int up_w = (int)d.pad_right - (int)((g.kw - 1) * g.dw), up_h = (int)d.pad_bottom - (int)((g.kh - 1) * g.dh);
-  const bool im2col = !tiled_only && lc.tma_encode_im2col && lo_w >= -128 && lo_h >= -128 && up_w >= -128 && up_w <= 127 && up_h >= -128 &&
+  const int pad_r = phase ? phase->pad_right : (int)d.pad_right, pad_b = phase ? phase->pad_bottom : (int)d.pad_bottom;
+  const int up_w = pad_r - (int)((g.kw - 1) * g.dw), up_h = pad_b - (int)((g.kh - 1) * g.dh);
+  const bool im2col = !tiled_only && lc.tma_encode_im2col && lo_w >= -128 && lo_h >= -128 && lo_w <= 127 && lo_h <= 127 && up_w >= -128 && up_w <= 127 && up_h >= -128 &&
                       up_h <= 127 && (g.kw - 1) * g.dw <= 255 && (g.kh - 1) * g.dh <= 255 && positions < 0x7fffff00ull;
   // tiled-mode fallback: a th x tw patch of one image per tile, tw = the power of two that covers a row (at most 128)
   uint32_t tw = 8;
@@ -446,14 +489,23 @@ int try_conv_tc(const zyxb_conv_desc& d, const ConvGeom& g, const void* x, const
                                                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) return 0;
   }
   const uint32_t hw = g.h * g.w;
-  if (in_place) {}
+  if (in_place || (phase && phase->x_ready)) {}
   else if (hw % 2 == 0 && (uintptr_t)x % 4 == 0)
     conv_nhwc_pairs_kernel<<<dim3((hw + 63) / 64, (cp + 63) / 64, g.n), 256, 0, lc.stream>>>(reinterpret_cast<const uint16_t*>(x), xt, g.c, cp, hw);
   else
     conv_nhwc_kernel<<<dim3((hw + 31) / 32, (cp + 31) / 32, g.n), dim3(32, 8), 0, lc.stream>>>(reinterpret_cast<const uint16_t*>(x), xt, g.c, cp, hw);
   const uint64_t wtotal = (uint64_t)g.o * taps * cp;
-  conv_weight_kernel<<<(unsigned)((wtotal + 255) / 256), 256, 0, lc.stream>>>(reinterpret_cast<const uint16_t*>(w), wt, g.c, cp, g.o, taps, wtotal, d.flip_filter != 0);
+  if (phase)
+    conv_weight_phase_kernel<<<(unsigned)((wtotal + 255) / 256), 256, 0, lc.stream>>>(reinterpret_cast<const uint16_t*>(w), wt, g.c, cp, g.o, g.kh, g.kw, phase->r0,
+                                                                                     phase->step_r, phase->s0, phase->step_s, phase->fkh, phase->fkw, wtotal);
+  else
+    conv_weight_kernel<<<(unsigned)((wtotal + 255) / 256), 256, 0, lc.stream>>>(reinterpret_cast<const uint16_t*>(w), wt, g.c, cp, g.o, taps, wtotal, d.flip_filter != 0);
   ConvTcParams tp{};
+  tp.full_h = g.oh; tp.full_w = g.ow; tp.step_h = tp.step_w = 1;
+  if (phase) {
+    tp.full_h = phase->full_h; tp.full_w = phase->full_w; tp.step_h = phase->step_h; tp.step_w = phase->step_w;
+    tp.off_h = phase->off_h; tp.off_w = phase->off_w; tp.out_mapped = 1;
+  }
   tp.bias = bias; tp.y = y; tp.g = g; tp.cp = cp; tp.cblocks = (cp + CV_BK - 1) / CV_BK;
   tp.tw = tw; tp.th = th; tp.tw_shift = 0;
   while ((1u << tp.tw_shift) < tw) ++tp.tw_shift;
@@ -467,7 +519,7 @@ int try_conv_tc(const zyxb_conv_desc& d, const ConvGeom& g, const void* x, const
   if (im2col) e = bn == 256 ? launch_conv_tc<256, 4, true>(mx, mw, tp, grid, lc.stream) : launch_conv_tc<128, 6, true>(mx, mw, tp, grid, lc.stream);
   else e = bn == 256 ? launch_conv_tc<256, 4, false>(mx, mw, tp, grid, lc.stream) : launch_conv_tc<128, 6, false>(mx, mw, tp, grid, lc.stream);
   if (e != cudaSuccess) { err = std::string("conv_tcgen05: ") + cudaGetErrorString(e); return -ZYXB_ERR_KERNEL_LAUNCH; }
-  *lc.launch_counter += in_place ? 2 : 3;
+  *lc.launch_counter += (in_place || (phase && phase->x_ready)) ? 2 : 3;
   return 1;
 }
 
@@ -557,9 +609,83 @@ int launch_conv(const zyxb_conv_desc& d, void* const* args, const uint64_t* arg_
   }
 }
 
+// One dimension of a phase of a strided input gradient.  Input positions y = a + stride*i (i < count) receive
+//   dx[y] = sum over the taps r with (a + pad - r*dil) divisible by stride of dy[i + (a + pad - r*dil)/stride] * w[r].
+// Those taps are r0 + t*step (t < taps) and their dy offsets q0 - t*dq, which makes the phase a stride-1 convolution of dy
+// with the reversed sub-filter, dilation dq and padding (taps-1)*dq - q0 before / `after` behind.
+struct PhaseDim {
+  uint32_t count = 0, taps = 0, r0 = 0, step = 1, dq = 1;
+  int64_t before = 0, after = 0;
+};
+PhaseDim phase_dim(uint32_t a, uint32_t extent, uint32_t out_extent, uint32_t k, uint32_t stride, uint32_t dil, int pad) {
+  PhaseDim ph;
+  if (a >= extent) return ph;
+  ph.count = (extent - a + stride - 1) / stride;
+  uint32_t gc = stride, t = dil % stride;                 // gcd(dil, stride)
+  while (t) { const uint32_t u = gc % t; gc = t; t = u; }
+  ph.step = stride / gc; ph.dq = dil / gc;
+  int64_t q0 = 0;
+  for (uint32_t r = 0; r < k; ++r) {
+    const int64_t v = (int64_t)a + pad - (int64_t)r * dil;
+    if (((v % (int64_t)stride) + stride) % stride) continue;
+    ph.r0 = r; q0 = (v - (((v % (int64_t)stride) + stride) % stride)) / (int64_t)stride;
+    ph.taps = (k - 1 - r) / ph.step + 1;
+    break;
+  }
+  if (!ph.taps) return ph;
+  ph.before = (int64_t)(ph.taps - 1) * ph.dq - q0;
+  ph.after = (int64_t)ph.count + (int64_t)(ph.taps - 1) * ph.dq - ph.before - (int64_t)out_extent;
+  return ph;
+}
+
+// Strided input gradient on the tensor cores: the input positions fall into stride_h * stride_w residue classes, and each
+// class is a stride-1 convolution of dy with the sub-filter of the taps that reach it, its result written to that class's
+// positions of dx (ConvPhase).  No zeros are multiplied: the phases together execute exactly the gradient's FLOPs.
+// Returns 1 when every phase ran there, 0 when the shape is not for it (nothing useful written), < 0 on an error.
+int try_conv_dgrad_phases(const zyxb_conv_desc& d, const ConvGeom& g, const void* dy, const void* w, void* dx, const LaunchCtx& lc, std::string& err) {
+  if (d.dtype != ZYXB_BF16 && d.dtype != ZYXB_F16) return 0;
+  if (g.sh > 8 || g.sw > 8 || (uint64_t)g.n * g.o * g.oh * g.ow * g.c * g.kh * g.kw < (1ull << 24)) return 0;
+  std::vector<PhaseDim> ph_h, ph_w;
+  bool empty = false;
+  for (uint32_t a = 0; a < g.sh; ++a) ph_h.push_back(phase_dim(a, g.h, g.oh, g.kh, g.sh, g.dh, g.pt));
+  for (uint32_t b = 0; b < g.sw; ++b) ph_w.push_back(phase_dim(b, g.w, g.ow, g.kw, g.sw, g.dw, g.pl));
+  for (const std::vector<PhaseDim>* v : {&ph_h, &ph_w})
+    for (const PhaseDim& q : *v) {
+      if (q.count && !q.taps) empty = true;               // positions no window element ever covers: their gradient is zero
+      // negative values crop dy instead of padding it: window origins then start later / end earlier, nothing else changes
+      if (q.taps && (q.before < -(1 << 20) || q.after < -(1 << 20) || q.before > (1 << 20) || q.after > (1 << 20))) return 0;
+    }
+  if (empty) {
+    const cudaError_t e = cudaMemsetAsync(dx, 0, (size_t)g.n * g.c * g.h * g.w * 2, lc.stream);
+    if (e != cudaSuccess) { err = std::string("conv input gradient: ") + cudaGetErrorString(e); return -ZYXB_ERR_KERNEL_LAUNCH; }
+  }
+  bool x_ready = false;
+  for (uint32_t a = 0; a < g.sh; ++a)
+    for (uint32_t b = 0; b < g.sw; ++b) {
+      const PhaseDim &H = ph_h[a], &W = ph_w[b];
+      if (!H.count || !W.count || !H.taps || !W.taps) continue;
+      zyxb_conv_desc f = d;                               // dtype and channels_last; the extents travel in the geometry
+      f.has_bias = 0; f.flip_filter = 0;
+      ConvGeom pg{};
+      pg.n = g.n; pg.c = g.o; pg.h = g.oh; pg.w = g.ow; pg.o = g.c; pg.kh = H.taps; pg.kw = W.taps; pg.oh = H.count; pg.ow = W.count;
+      pg.sh = pg.sw = 1; pg.dh = H.dq; pg.dw = W.dq; pg.pt = (int)H.before; pg.pl = (int)W.before;
+      ConvPhase cp{};
+      cp.pad_bottom = (int)H.after; cp.pad_right = (int)W.after;
+      cp.r0 = H.r0; cp.step_r = H.step; cp.s0 = W.r0; cp.step_s = W.step; cp.fkh = g.kh; cp.fkw = g.kw;
+      cp.full_h = g.h; cp.full_w = g.w; cp.step_h = g.sh; cp.step_w = g.sw; cp.off_h = a; cp.off_w = b;
+      cp.x_ready = x_ready;
+      const int took = try_conv_tc(f, pg, dy, w, nullptr, dx, lc, err, &cp);
+      if (took < 0) return took;
+      if (!took) return 0;                                // the caller's direct kernel rewrites every element
+      x_ready = true;
+    }
+  return 1;
+}
+
 // Input gradient of the convolution the descriptor names: args dy, w -> dx.  With stride 1 it is itself a convolution
 // (of dy, with the filter transposed in (o, c) and reversed in (r, s), padding dil*(k-1) - pad): the forward program with
-// flip_filter, tensor cores included.  Other strides take the direct kernel.
+// flip_filter, tensor cores included.  Other strides split into one such convolution per residue class of the input
+// positions (try_conv_dgrad_phases); what neither takes runs the direct kernel.
 int launch_conv_dgrad(const zyxb_conv_desc& d, void* const* args, const uint64_t* arg_bytes, int n_args, const LaunchCtx& lc, std::string& err) {
   ConvGeom g;
   if (!geometry(d, g, err)) return ZYXB_ERR_INCORRECT_KERNEL_ARG;
@@ -578,6 +704,12 @@ int launch_conv_dgrad(const zyxb_conv_desc& d, void* const* args, const uint64_t
     f.has_bias = 0; f.flip_filter = 1;
     void* fargs[3] = {args[0], args[1], args[2]};
     return launch_conv(f, fargs, arg_bytes, 3, lc, err);
+  }
+  if (!as_conv) {
+    static const bool no_phases = getenv("ZYXB_NO_CONV_DGRAD_TC") != nullptr;
+    const int took = no_phases ? 0 : try_conv_dgrad_phases(d, g, args[0], args[1], args[2], lc, err);
+    if (took < 0) return -took;
+    if (took) return ZYXB_OK;
   }
   const int cl = d.channels_last != 0;
   switch (d.dtype) {

@@ -26,8 +26,14 @@ struct zyxb_block {
   zyxb_block_config cfg{};
   uint64_t numel[N_PARAMS] = {0};
   uint32_t param[N_PARAMS] = {0}, grad[N_PARAMS] = {0}, state[2][N_PARAMS] = {{0}, {0}};
-  uint32_t grad_bucket = 0;
+  uint32_t grad_bucket = 0, param_bucket = 0;
   uint64_t bucket_off[N_PARAMS] = {0};
+  // sharded optimizer (ZeRO stage 1): each of the three gradient groups is cut into `world` shards; this rank updates
+  // one shard per group with state of shard size and the updated parameters are all-gathered
+  bool sharded = false;
+  int rank = 0;
+  uint64_t shard[3] = {0, 0, 0};
+  uint32_t param_shard[3] = {0, 0, 0}, grad_shard[3] = {0, 0, 0}, shard_state[2][3] = {{0, 0, 0}, {0, 0, 0}};
   uint32_t x = 0, target = 0, loss = 0, y = 0;
   uint32_t q = 0, k = 0, v = 0, s = 0, p = 0, attn = 0, o = 0, s1 = 0, x1 = 0, z1 = 0, h = 0, m = 0, s2 = 0;
   uint32_t dy = 0, ds2 = 0, tmp = 0, dz1 = 0, dx1 = 0, ds1 = 0, dattn = 0, dp = 0, dq = 0, dk = 0, dv = 0;
@@ -62,21 +68,41 @@ int32_t build(zyxb_block* K) {
                                P_G1, P_BE1, P_WO, P_BO,                      // group 1: norm1 + output projection
                                P_WV, P_BV, P_WK, P_BK, P_WQ, P_BQ};          // group 2: value / key / query projections
   const int group_end[3] = {6, 10, 16};
+  K->sharded = c.shard_optimizer != 0;
+  if (K->sharded) {
+    int32_t r = 0, w = 1;
+    int32_t st = zyxb_comm_rank(P.ctx, P.dev, &r, &w);
+    if (st) return P.fail(st, "zyxb_comm_rank");
+    if (w != c.world) { P.err = "shard_optimizer: config.world differs from the communicator's"; return ZYXB_ERR_INCORRECT_KERNEL_ARG; }
+    K->rank = r;
+  }
   const uint64_t align_elems = 256 / es;
+  const uint64_t group_align = K->sharded ? align_elems * (uint64_t)c.world : align_elems;   // a sharded group divides into aligned shards
   uint64_t off = 0, group_off[4] = {0, 0, 0, 0};
   for (int j = 0, g = 0; j < N_PARAMS; ++j) {
     K->bucket_off[order[j]] = off;
     off += align_up(sizes[order[j]], align_elems);
-    if (j + 1 == group_end[g]) group_off[++g] = off;
+    if (j + 1 == group_end[g]) { off = align_up(off, group_align); group_off[++g] = off; }
   }
   CHK(P.alloc(off * es, &K->grad_bucket, true));
+  if (K->sharded) CHK(P.alloc(off * es, &K->param_bucket, true));   // the same layout; the padding stays zero
   const bool adam = c.optim.algo != ZYXB_OPT_SGD;
   const int n_state = adam ? 2 : (c.optim.momentum != 0.0f ? 1 : 0);
   for (int i = 0; i < N_PARAMS; ++i) {
-    CHK(P.alloc(sizes[i] * es, &K->param[i], true));
+    if (K->sharded) CHK(P.view(K->param_bucket, K->bucket_off[i] * es, sizes[i] * es, &K->param[i]));
+    else CHK(P.alloc(sizes[i] * es, &K->param[i], true));
     CHK(P.view(K->grad_bucket, K->bucket_off[i] * es, sizes[i] * es, &K->grad[i]));
-    for (int s = 0; s < n_state; ++s) CHK(P.alloc(sizes[i] * es, &K->state[s][i], true));
+    if (!K->sharded)
+      for (int s = 0; s < n_state; ++s) CHK(P.alloc(sizes[i] * es, &K->state[s][i], true));
   }
+  if (K->sharded)
+    for (int g = 0; g < 3; ++g) {
+      K->shard[g] = (group_off[g + 1] - group_off[g]) / (uint64_t)c.world;
+      const uint64_t at = (group_off[g] + (uint64_t)K->rank * K->shard[g]) * es;
+      CHK(P.view(K->param_bucket, at, K->shard[g] * es, &K->param_shard[g]));
+      CHK(P.view(K->grad_bucket, at, K->shard[g] * es, &K->grad_shard[g]));
+      for (int s = 0; s < n_state; ++s) CHK(P.alloc(K->shard[g] * es, &K->shard_state[s][g], true));
+    }
   // ---- activations ----
   const uint64_t RE = R * E * es, RF = R * F * es, SS = B * H * T * T * es;
   for (uint32_t* b : {&K->x, &K->target, &K->y, &K->q, &K->k, &K->v, &K->attn, &K->o, &K->s1, &K->x1, &K->m, &K->s2, &K->dy, &K->ds2,
@@ -97,12 +123,13 @@ int32_t build(zyxb_block* K) {
   CHK(P.alloc(4, &K->loss, true));
 
   // ================================== forward ==================================
-  auto linear = [&](uint32_t in, int w, int b, uint32_t out, uint64_t in_f, uint64_t out_f, int32_t epi, uint32_t pre) {
+  // `group`: this launch is the first reader of that parameter group in a step and waits for its all-gather (sharded optimizer)
+  auto linear = [&](uint32_t in, int w, int b, uint32_t out, uint64_t in_f, uint64_t out_f, int32_t epi, uint32_t pre, int group = -1) {
     std::vector<uint32_t> args = {in, K->param[w], K->param[b], out};
     if (pre) args.push_back(pre);
-    return P.launch(gemm(dt, R, out_f, in_f, false, true, epi, pre != 0), args);   // x.dot(W.t()) + b
+    return P.launch(gemm(dt, R, out_f, in_f, false, true, epi, pre != 0), args, 0, K->sharded ? group : -1);   // x.dot(W.t()) + b
   };
-  CHK(linear(K->x, P_WQ, P_BQ, K->q, E, E, ZYXB_EPI_BIAS, 0));
+  CHK(linear(K->x, P_WQ, P_BQ, K->q, E, E, ZYXB_EPI_BIAS, 0, 2));
   CHK(linear(K->x, P_WK, P_BK, K->k, E, E, ZYXB_EPI_BIAS, 0));
   CHK(linear(K->x, P_WV, P_BV, K->v, E, E, ZYXB_EPI_BIAS, 0));
   if (fused) {
@@ -128,7 +155,7 @@ int32_t build(zyxb_block* K) {
     CHK(P.launch(d, {K->p, K->v, K->attn}));
   }
   }
-  CHK(linear(K->attn, P_WO, P_BO, K->o, E, E, ZYXB_EPI_BIAS, 0));
+  CHK(linear(K->attn, P_WO, P_BO, K->o, E, E, ZYXB_EPI_BIAS, 0, 1));
   CHK(P.launch(eltwise(ZYXB_EW_ADD, dt, R * E), {K->x, K->o, K->s1}));
   auto layernorm = [&](uint32_t in, int w, int b, uint32_t out) {
     zyxb_kernel_desc d = row(ZYXB_RR_LAYERNORM, dt, R, E);
@@ -136,7 +163,7 @@ int32_t build(zyxb_block* K) {
     return P.launch(d, {in, K->param[w], K->param[b], out});
   };
   CHK(layernorm(K->s1, P_G1, P_BE1, K->x1));
-  CHK(linear(K->x1, P_W1, P_B1, K->h, E, F, ZYXB_EPI_BIAS_GELU, K->z1));
+  CHK(linear(K->x1, P_W1, P_B1, K->h, E, F, ZYXB_EPI_BIAS_GELU, K->z1, 0));
   CHK(linear(K->h, P_W2, P_B2, K->m, F, E, ZYXB_EPI_BIAS, 0));
   CHK(P.launch(eltwise(ZYXB_EW_ADD, dt, R * E), {K->x1, K->m, K->s2}));
   CHK(layernorm(K->s2, P_G2, P_BE2, K->y));
@@ -160,15 +187,20 @@ int32_t build(zyxb_block* K) {
     CHK(P.launch(gemm(dt, out_f, in_f, R, true, false), {dout, in, K->grad[w]}));
     return P.launch(row(ZYXB_RR_COLSUM, dt, R, out_f), {dout, K->grad[b]});
   };
+  auto reduce_group = [&](int g) {
+    if (K->sharded) P.reduce_scatter(K->grad_bucket, group_off[g], K->shard[g]);
+    else if (c.world > 1) P.allreduce(K->grad_bucket, group_off[g], group_off[g + 1] - group_off[g]);
+    return (int32_t)ZYXB_OK;
+  };
   CHK(layernorm_bwd(K->s2, K->dy, P_G2, P_BE2, K->ds2));       // ds2 flows to both x1 (residual) and mlp2's output
   CHK(linear_param_grads(K->ds2, K->h, P_W2, P_B2, F, E));
   CHK(P.launch(gemm(dt, R, F, E, false, false, ZYXB_EPI_MUL_GELU_GRAD), {K->ds2, K->param[P_W2], K->z1, K->dz1}));
   CHK(linear_param_grads(K->dz1, K->x1, P_W1, P_B1, E, F));
-  if (c.world > 1) P.allreduce(K->grad_bucket, group_off[0], group_off[1] - group_off[0]);
+  CHK(reduce_group(0));
   CHK(P.launch(gemm(dt, R, E, F, false, false, ZYXB_EPI_ADD), {K->dz1, K->param[P_W1], K->ds2, K->dx1}));   // + residual
   CHK(layernorm_bwd(K->s1, K->dx1, P_G1, P_BE1, K->ds1));      // ds1 = d(x + o): gradient of the attention output projection
   CHK(linear_param_grads(K->ds1, K->attn, P_WO, P_BO, E, E));
-  if (c.world > 1) P.allreduce(K->grad_bucket, group_off[1], group_off[2] - group_off[1]);
+  CHK(reduce_group(1));
   CHK(P.launch(gemm(dt, R, E, E, false, false), {K->ds1, K->param[P_WO], K->dattn}));
   if (fused) {
     CHK(P.launch(attention(true), {K->q, K->k, K->v, K->attn, K->dattn, K->lse, K->dq, K->dk, K->dv}));
@@ -206,10 +238,28 @@ int32_t build(zyxb_block* K) {
   CHK(linear_param_grads(K->dv, K->x, P_WV, P_BV, E, E));
   CHK(linear_param_grads(K->dk, K->x, P_WK, P_BK, E, E));
   CHK(linear_param_grads(K->dq, K->x, P_WQ, P_BQ, E, E));
-  if (c.world > 1) P.allreduce(K->grad_bucket, group_off[2], group_off[3] - group_off[2]);
+  CHK(reduce_group(2));
   K->n_forward_backward = P.instrs.size();
 
   // ================================== optimizer ==================================
+  // Sharded: one program per group over this rank's shard of the group's slice (an elementwise update does not care where
+  // tensors begin; the padding holds zero parameters and zero gradients and stays zero), the group the forward pass reads
+  // first (q/k/v) first, each followed by the all-gather of that group's parameters.  The first waits for every reduce-scatter.
+  if (K->sharded) {
+    for (int g = 2; g >= 0; --g) {
+      zyxb_kernel_desc od{};
+      od.kind = ZYXB_KIND_OPTIM;
+      od.u.optim = c.optim;
+      uint64_t numel = K->shard[g];
+      od.u.optim.dtype = dt; od.u.optim.n_tensors = 1; od.u.optim.numel = &numel;
+      od.u.optim.grad_scale = 1.0f / (float)c.world;
+      std::vector<uint32_t> args = {K->param_shard[g], K->grad_shard[g]};
+      for (int s = 0; s < n_state; ++s) args.push_back(K->shard_state[s][g]);
+      CHK(P.launch(od, args, g == 2 ? -1 : 0));
+      P.allgather(K->param_bucket, group_off[g], K->shard[g], g);
+    }
+    return ZYXB_OK;
+  }
   // one program per gradient group, each waiting only for its own group's allreduce
   for (int g = 0; g < 3; ++g) {
     std::vector<uint64_t> numel;
@@ -270,6 +320,11 @@ const char* zyxb_block_last_error(zyxb_block* K) { return K ? K->plan.err.c_str(
 
 int32_t zyxb_block_tensor(zyxb_block* K, int32_t which, int32_t i, uint32_t* out_buf, uint64_t* out_numel) {
   if (!K || i < 0 || i >= N_PARAMS || which < 0 || which > 3) return ZYXB_ERR_INCORRECT_KERNEL_ARG;
+  if (K->sharded && which >= 2) {
+    K->plan.err = "block_tensor: the optimizer state is sharded over the ranks; it has no per-tensor buffers";
+    return ZYXB_ERR_INCORRECT_KERNEL_ARG;
+  }
+  CHK(K->plan.join_gathers());          // whoever asks for a buffer may read or write it: the gathers must have landed
   const uint32_t b = which == 0 ? K->param[i] : which == 1 ? K->grad[i] : K->state[which - 2][i];
   if (b == 0) return ZYXB_ERR_INCORRECT_KERNEL_ARG;
   if (out_buf) *out_buf = b;
@@ -296,7 +351,11 @@ int32_t zyxb_block_activation(zyxb_block* K, int32_t which, uint32_t* out_buf) {
 }
 
 int32_t zyxb_block_forward_backward(zyxb_block* K) { return K ? K->plan.run(0, K->n_forward_backward, nullptr, 0) : ZYXB_ERR_INCORRECT_KERNEL_ARG; }
-int32_t zyxb_block_update(zyxb_block* K) { return K ? K->plan.run(K->n_forward_backward, K->plan.instrs.size(), nullptr, 0) : ZYXB_ERR_INCORRECT_KERNEL_ARG; }
+int32_t zyxb_block_update(zyxb_block* K) {
+  if (!K) return ZYXB_ERR_INCORRECT_KERNEL_ARG;
+  int32_t st = K->plan.run(K->n_forward_backward, K->plan.instrs.size(), nullptr, 0);
+  return st ? st : K->plan.join_gathers();   // the stand-alone update returns with complete parameters; zyxb_block_step does not wait
+}
 int32_t zyxb_block_step(zyxb_block* K, const zyxb_event* wait, int32_t n_wait) {
   return K ? K->plan.run(0, K->plan.instrs.size(), wait, n_wait) : ZYXB_ERR_INCORRECT_KERNEL_ARG;
 }
@@ -324,7 +383,17 @@ std::vector<zyxb_host::CkptTensor> block_ckpt_tensors(zyxb_block* K) {
   std::vector<zyxb_host::CkptTensor> out;
   const int n_state = c.optim.algo == ZYXB_OPT_SGD ? (c.optim.momentum != 0.0f ? 1 : 0) : 2;
   const char* state_prefix[2] = {c.optim.algo == ZYXB_OPT_SGD ? "optim.buf." : "optim.m.", "optim.v."};
-  for (int s = -1; s < n_state; ++s)
+  static const char* const GROUP_LABELS[3] = {"ffn", "attn_out", "qkv"};
+  for (int s = 0; K->sharded && s < n_state; ++s)
+    for (int g = 0; g < 3; ++g) {
+      // a rank's file holds its own shard of the state, named for the rank: every rank saves to its own path
+      zyxb_host::CkptTensor t;
+      t.name = std::string(state_prefix[s]) + "shard" + std::to_string(K->rank) + "of" + std::to_string(c.world) + "." + GROUP_LABELS[g];
+      t.buffer = K->shard_state[s][g];
+      t.shape = {K->shard[g]};
+      out.push_back(std::move(t));
+    }
+  for (int s = -1; s < (K->sharded ? 0 : n_state); ++s)
     for (int i = 0; i < N_PARAMS; ++i) {
       zyxb_host::CkptTensor t;
       t.name = std::string(s < 0 ? "" : state_prefix[s]) + BLOCK_LABELS[i];
@@ -343,6 +412,7 @@ std::vector<zyxb_host::CkptTensor> block_ckpt_tensors(zyxb_block* K) {
 #pragma GCC visibility push(default)
 int32_t zyxb_block_save(zyxb_block* K, const char* path) {
   if (!K || !path) return ZYXB_ERR_INCORRECT_KERNEL_ARG;
+  CHK(K->plan.join_gathers());
   uint64_t t = 0;
   if (K->n_forward_backward < K->plan.instrs.size()) {
     int32_t st = zyxb_program_get_step(K->plan.ctx, K->plan.dev, K->plan.instrs[K->n_forward_backward].program, &t);
@@ -353,6 +423,7 @@ int32_t zyxb_block_save(zyxb_block* K, const char* path) {
 
 int32_t zyxb_block_load(zyxb_block* K, const char* path, int32_t* out_missing) {
   if (!K || !path) return ZYXB_ERR_INCORRECT_KERNEL_ARG;
+  CHK(K->plan.join_gathers());          // parameter all-gathers still in flight would overwrite what is loaded
   uint64_t t = 0;
   bool have_t = false;
   int32_t st = zyxb_host::checkpoint_load(K->plan.ctx, K->plan.dev, K->cfg.dtype, block_ckpt_tensors(K), &t, &have_t, out_missing, path, K->plan.err);

@@ -11,12 +11,13 @@
 namespace zyxb_host {
 
 struct Instr {
-  enum Kind { LAUNCH, ALLREDUCE } kind = LAUNCH;
+  enum Kind { LAUNCH, ALLREDUCE, REDUCE_SCATTER, ALLGATHER } kind = LAUNCH;
   uint32_t program = 0;
   std::vector<uint32_t> args;
-  uint32_t buffer = 0;            // ALLREDUCE: buffer, first element and element count
+  uint32_t buffer = 0;            // collectives: buffer, first element and element count (per rank for the sliced two)
   uint64_t offset = 0, count = 0;
-  int wait_collectives = 0;       // LAUNCH: wait first for this many of the oldest pending allreduce events (-1: all)
+  int wait_collectives = 0;       // LAUNCH: wait first for this many of the oldest pending gradient-collective events (-1: all)
+  int group = -1;                 // ALLGATHER: the parameter group it completes; LAUNCH: the first reader of that group's parameters
 };
 
 inline uint64_t dsize(int32_t dtype) { return dtype == ZYXB_F32 ? 4 : 2; }
@@ -30,6 +31,8 @@ class Plan {
   std::vector<Instr> instrs;
   std::vector<uint32_t> owned_buffers, owned_programs;
   std::vector<zyxb_event> pending;
+  std::vector<zyxb_event> gathered;        // per parameter group: the event of its last all-gather, if nobody has waited for it yet
+  std::vector<char> gathered_set;
   int n_launches = 0, n_collectives = 0;
   std::string err;
 
@@ -51,10 +54,11 @@ class Plan {
     owned_buffers.push_back(*out);
     return ZYXB_OK;
   }
-  int32_t launch(const zyxb_kernel_desc& d, std::vector<uint32_t> args, int wait_coll = 0) {
+  int32_t launch(const zyxb_kernel_desc& d, std::vector<uint32_t> args, int wait_coll = 0, int group = -1) {
     Instr in;
     in.args = std::move(args);
     in.wait_collectives = wait_coll;
+    in.group = group;
     int32_t st = zyxb_program_create(ctx, dev, &d, &in.program);
     if (st) return fail(st, "zyxb_program_create");
     owned_programs.push_back(in.program);
@@ -68,20 +72,56 @@ class Plan {
     instrs.push_back(in);
     ++n_collectives;
   }
+  void reduce_scatter(uint32_t buffer, uint64_t offset, uint64_t count_per_rank) {
+    Instr in;
+    in.kind = Instr::REDUCE_SCATTER; in.buffer = buffer; in.offset = offset; in.count = count_per_rank;
+    instrs.push_back(in);
+    ++n_collectives;
+  }
+  void allgather(uint32_t buffer, uint64_t offset, uint64_t count_per_rank, int group) {
+    Instr in;
+    in.kind = Instr::ALLGATHER; in.buffer = buffer; in.offset = offset; in.count = count_per_rank; in.group = group;
+    instrs.push_back(in);
+    ++n_collectives;
+    if ((size_t)group >= gathered.size()) { gathered.resize(group + 1, zyxb_event{}); gathered_set.resize(group + 1, 0); }
+  }
+  // Blocks until every outstanding parameter all-gather has landed (whoever reads or writes a parameter from the host).
+  int32_t join_gathers() {
+    for (size_t g = 0; g < gathered.size(); ++g)
+      if (gathered_set[g]) {
+        int32_t st = zyxb_sync(ctx, dev, &gathered[g], 1);
+        if (st) return fail(st, "zyxb_sync");
+        gathered_set[g] = 0;
+      }
+    return ZYXB_OK;
+  }
   // replay instructions [first, last)
   int32_t run(size_t first, size_t last, const zyxb_event* wait, int32_t n_wait) {
     bool head = true;
     for (size_t i = first; i < last && i < instrs.size(); ++i) {
       const Instr& in = instrs[i];
-      if (in.kind == Instr::ALLREDUCE) {
+      if (in.kind != Instr::LAUNCH) {
         zyxb_event ev{};
-        int32_t st = zyxb_allreduce_sum(ctx, dev, in.buffer, in.offset, in.count, dtype, nullptr, 0, &ev);
-        if (st) return fail(st, "zyxb_allreduce_sum");
-        pending.push_back(ev);
+        int32_t st;
+        if (in.kind == Instr::ALLREDUCE) {
+          if ((st = zyxb_allreduce_sum(ctx, dev, in.buffer, in.offset, in.count, dtype, nullptr, 0, &ev))) return fail(st, "zyxb_allreduce_sum");
+        } else if (in.kind == Instr::REDUCE_SCATTER) {
+          if ((st = zyxb_reduce_scatter_sum(ctx, dev, in.buffer, in.offset, in.count, dtype, nullptr, 0, &ev))) return fail(st, "zyxb_reduce_scatter_sum");
+        } else {
+          if ((st = zyxb_allgather(ctx, dev, in.buffer, in.offset, in.count, dtype, nullptr, 0, &ev))) return fail(st, "zyxb_allgather");
+        }
+        if (in.kind == Instr::ALLGATHER) {
+          if (gathered_set[in.group]) zyxb_release_events(ctx, dev, &gathered[in.group], 1);
+          gathered[in.group] = ev; gathered_set[in.group] = 1;
+        } else pending.push_back(ev);
         continue;
       }
       std::vector<zyxb_event> w;
       if (head && n_wait > 0) w.assign(wait, wait + n_wait);
+      if (in.group >= 0 && (size_t)in.group < gathered.size() && gathered_set[in.group]) {   // these parameters are still being gathered
+        w.push_back(gathered[in.group]);
+        gathered_set[in.group] = 0;
+      }
       if (in.wait_collectives != 0) {
         const size_t take = in.wait_collectives < 0 ? pending.size() : std::min(pending.size(), (size_t)in.wait_collectives);
         w.insert(w.end(), pending.begin(), pending.begin() + take);
@@ -97,6 +137,9 @@ class Plan {
   void destroy() {
     zyxb_device_sync(ctx, dev);
     if (!pending.empty()) zyxb_release_events(ctx, dev, pending.data(), (int32_t)pending.size());
+    for (size_t g = 0; g < gathered.size(); ++g)
+      if (gathered_set[g]) zyxb_release_events(ctx, dev, &gathered[g], 1);
+    gathered.clear(); gathered_set.clear();
     for (uint32_t p : owned_programs) zyxb_program_release(ctx, dev, p);
     for (auto it = owned_buffers.rbegin(); it != owned_buffers.rend(); ++it) zyxb_free(ctx, dev, *it, nullptr, 0);   // views before parents
     owned_programs.clear(); owned_buffers.clear(); pending.clear();

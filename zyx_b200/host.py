@@ -192,7 +192,7 @@ class Mlp:
 class BlockConfig(C.Structure):
     _fields_ = [("dtype", C.c_int32), ("batch", C.c_uint64), ("seq", C.c_uint64), ("dim", C.c_uint64), ("heads", C.c_uint64),
                 ("ffn", C.c_uint64), ("causal", C.c_int32), ("eps", C.c_float), ("optim", L.OptimDesc), ("world", C.c_int32),
-                ("fused_attention", C.c_int32)]
+                ("fused_attention", C.c_int32), ("shard_optimizer", C.c_int32)]
 
 
 BLOCK_SIGNATURES = {
@@ -238,12 +238,12 @@ BLOCK_PARAM_NAMES = ["wq", "bq", "wk", "bk", "wv", "bv", "wo", "bo", "w1", "b1",
 class Block:
     """One transformer block (attention + feed-forward, post-norm) with its training plan."""
 
-    def __init__(self, session, dtype, batch, seq, dim, heads, ffn, causal=True, eps=1e-5, algo=L.OPT_ADAMW, world=1, fused_attention=False,
+    def __init__(self, session, dtype, batch, seq, dim, heads, ffn, causal=True, eps=1e-5, algo=L.OPT_ADAMW, world=1, fused_attention=False, shard_optimizer=False,
                  **optim_kw):
         self.lib, self.sess = load(), session
         cfg = BlockConfig()
         cfg.dtype, cfg.batch, cfg.seq, cfg.dim, cfg.heads, cfg.ffn, cfg.causal, cfg.eps, cfg.world = dtype, batch, seq, dim, heads, ffn, int(causal), eps, world
-        cfg.fused_attention = int(fused_attention)
+        cfg.fused_attention, cfg.shard_optimizer = int(fused_attention), int(shard_optimizer)
         o = cfg.optim
         o.algo = algo
         o.lr, o.weight_decay = optim_kw.get("lr", 1e-3), optim_kw.get("weight_decay", 0.0)
