@@ -270,7 +270,9 @@ typedef struct {
 /* ZYXB_KIND_CONV        args: x, w [,bias] -> y
  * ZYXB_KIND_CONV_DGRAD  args: dy, w -> dx   the input gradient of the convolution the descriptor names (has_bias and flip_filter
  *                       ignored).  Stride 1 with padding <= dil*(k-1): runs as the flip_filter convolution of dy, tensor cores
- *                       included; other strides: a direct kernel.
+ *                       included; other strides (bf16 / f16 with enough work): one stride-1 convolution of dy per residue
+ *                       class of the input positions, each with the sub-filter of the taps that reach the class, on the
+ *                       tensor cores as well; everything else: a direct kernel.
  * ZYXB_KIND_CONV_WGRAD  args: x, dy -> dw   the filter gradient of the convolution the descriptor names (has_bias and
  *                       flip_filter ignored): dw[o,c,r,s] = sum over (n,i,j) of dy[n,o,i,j] * x[n,c,i*stride_h+r*dil_h-pad_top, ...];
  *                       bf16 / f16 with enough work run per tap as a matmul over the output positions on the tensor cores
