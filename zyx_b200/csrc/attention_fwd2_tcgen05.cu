@@ -55,6 +55,30 @@ __device__ __forceinline__ void umma_f16_tmem_a(uint32_t tmem_d, uint32_t tmem_a
       ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
 
+// One thread's 64 scores of a tile -> P = 2^(s*scale - m) as 32 packed pairs of the 16-bit type, and their sum.  The
+// multiply-subtract and the sum run two lanes per instruction (fma.rn.f32x2 / add.rn.f32x2); the exponentials are one SFU
+// operation each.  DIAG: keys beyond `lim` (above the diagonal) give exactly zero.
+template <bool BF16, bool DIAG>
+__device__ __forceinline__ float exp_tile(const uint32_t (&r)[64], float scale, float neg_m, int32_t lim, uint32_t (&pk)[32]) {
+  const uint64_t sc = f2_pack(scale, scale), nm = f2_pack(neg_m, neg_m);
+  uint64_t acc[2] = {f2_pack(0.0f, 0.0f), f2_pack(0.0f, 0.0f)};
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    float a, b;
+    f2_unpack(f2_fma(f2_pack_bits(r[2 * i], r[2 * i + 1]), sc, nm), a, b);
+    float e0 = ex2f(a), e1 = ex2f(b);
+    if (DIAG) {
+      e0 = 2 * i > lim ? 0.0f : e0;
+      e1 = 2 * i + 1 > lim ? 0.0f : e1;
+    }
+    acc[i & 1] = f2_add(acc[i & 1], f2_pack(e0, e1));
+    pk[i] = pack2_t<BF16>(e0, e1);
+  }
+  float s0, s1;
+  f2_unpack(f2_add(acc[0], acc[1]), s0, s1);
+  return s0 + s1;
+}
+
 __global__ void __launch_bounds__(A2_THREADS, 1)
 attn_fwd2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                  const __grid_constant__ CUtensorMap map_v, Attn2Params p) {
@@ -220,7 +244,7 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       float mx4[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
       if (!diag) {
 #pragma unroll
-        for (int i = 0; i < 64; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(r[i]));
+        for (int i = 0; i < 64; i += 2) mx4[(i >> 1) & 3] = fmax3(mx4[(i >> 1) & 3], __uint_as_float(r[i]), __uint_as_float(r[i + 1]));
       } else {
 #pragma unroll
         for (int i = 0; i < 64; ++i) mx4[i & 3] = i > lim ? mx4[i & 3] : fmaxf(mx4[i & 3], __uint_as_float(r[i]));
@@ -236,27 +260,9 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       const bool same = !(m_seen - m > 8.0f);
       const float m_new = same ? m : m_seen;
       const float alpha = same ? 1.0f : ex2f(m - m_new);
-      float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
       uint32_t pk[32];
-      if (!diag) {
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float e0 = ex2f(fmaf(__uint_as_float(r[2 * i]), p.scale_log2, -m_new));
-          const float e1 = ex2f(fmaf(__uint_as_float(r[2 * i + 1]), p.scale_log2, -m_new));
-          sum4[i & 3] += e0 + e1;
-          pk[i] = pack2(e0, e1, bf16);
-        }
-      } else {
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float e0 = ex2f(fmaf(__uint_as_float(r[2 * i]), p.scale_log2, -m_new));
-          float e1 = ex2f(fmaf(__uint_as_float(r[2 * i + 1]), p.scale_log2, -m_new));
-          e0 = 2 * i > lim ? 0.0f : e0;
-          e1 = 2 * i + 1 > lim ? 0.0f : e1;
-          sum4[i & 3] += e0 + e1;
-          pk[i] = pack2(e0, e1, bf16);
-        }
-      }
+      const float tile_sum = bf16 ? (diag ? exp_tile<true, true>(r, p.scale_log2, -m_new, lim, pk) : exp_tile<true, false>(r, p.scale_log2, -m_new, lim, pk))
+                                  : (diag ? exp_tile<false, true>(r, p.scale_log2, -m_new, lim, pk) : exp_tile<false, false>(r, p.scale_log2, -m_new, lim, pk));
       // O_g is rescaled only when some row's reference point moved; the previous P_g.V has finished by then (S_g(j) was
       // issued after it), the wait only makes that visible to this thread
       if (j > 0 && !__all_sync(0xffffffffu, same)) {
@@ -278,7 +284,7 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(p_full(g));
-      l = l * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
+      l = l * alpha + tile_sum;
       m = m_new;
     }
     if (ok && mbar_wait(pv_done(g), (my_kv - 1) & 1, abort_flag, p.status, A2_ERR_SOFTMAX)) {

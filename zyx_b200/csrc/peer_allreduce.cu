@@ -24,6 +24,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
+#include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
 
@@ -257,6 +258,46 @@ int peer_create(PeerComm** out, Comm* c, uint32_t* status_word, cudaStream_t str
   if (st) return st;
   if (ok) for (int r = 0; r < p->world; ++r) p->table.peer[r] = (uint32_t*)mapped[r];
   p->usable = ok;
+  if (!ok) return ZYXB_OK;
+  // One small allreduce of known values before anyone relies on the path: every rank must read the exact sum and see no
+  // wait give up, and the ranks must agree on that; otherwise all of them stay on the communicator's own allreduce.
+  const uint64_t n = 4096;
+  float* probe = nullptr;
+  std::vector<float> host(n);
+  for (uint64_t i = 0; i < n; ++i) host[i] = (float)((p->rank + 1) * (int)(i % 7 + 1));
+  bool good = cudaMalloc((void**)&probe, n * 4) == cudaSuccess &&
+              cudaMemcpyAsync(probe, host.data(), n * 4, cudaMemcpyHostToDevice, stream) == cudaSuccess;
+  const uint64_t limit = p->wait_limit_ns;
+  p->wait_limit_ns = std::min<uint64_t>(limit, 5000000000ull);
+  std::string probe_err;
+  // the call is collective (it maps the probe everywhere), so every rank makes it whatever its own state
+  if (probe && peer_allreduce_sum(p, c, probe, n * 4, 0, n, ZYXB_F32, stream, nullptr, probe_err) != ZYXB_OK) good = false;
+  p->wait_limit_ns = limit;
+  uint32_t word = 0;
+  if (probe && (cudaMemcpyAsync(host.data(), probe, n * 4, cudaMemcpyDeviceToHost, stream) != cudaSuccess ||
+                cudaMemcpyAsync(&word, status_word, 4, cudaMemcpyDeviceToHost, stream) != cudaSuccess ||
+                cudaStreamSynchronize(stream) != cudaSuccess)) good = false;
+  const int tri = p->world * (p->world + 1) / 2;
+  for (uint64_t i = 0; good && i < n; ++i) good = host[i] == (float)(tri * (int)(i % 7 + 1));
+  if (word & PEER_STATUS_TIMEOUT) {
+    good = false;
+    word &= ~PEER_STATUS_TIMEOUT;             // the probe's own expiry is reported by falling back, not through the status word
+    cudaMemcpyAsync(status_word, &word, 4, cudaMemcpyHostToDevice, stream);
+    cudaStreamSynchronize(stream);
+  }
+  cudaGetLastError();
+  HandleMsg verdict{};
+  verdict.ok = good ? 1 : 0;
+  std::vector<HandleMsg> all;
+  st = exchange(p, c, verdict, all, stream, err);
+  if (st) return st;
+  for (int r = 0; r < p->world; ++r) good = good && all[r].ok;
+  if (probe) { peer_forget_buffer(p, probe); cudaFree(probe); }
+  if (!good) {
+    fprintf(stderr, "[zyxb] rank %d: the peer-memory allreduce failed its set-up probe (%s); using the communicator's allreduce\n", p->rank,
+            probe_err.empty() ? "wrong sum or a wait that gave up" : probe_err.c_str());
+    p->usable = false;
+  }
   return ZYXB_OK;
 }
 
