@@ -21,6 +21,7 @@ ROOT = os.path.dirname(HERE)
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC",
               "-Xcompiler", "-fvisibility=hidden", "--expt-relaxed-constexpr", "-diag-suppress", "177"]
+NVCC_FLAGS += os.environ.get("ZYXB_NVCC_EXTRA", "").split()      # e.g. -DZYXB_ATTN_TRACE for the attention kernel's clock trace
 CXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-fvisibility=hidden", "-I/usr/local/cuda/include"]
 
 

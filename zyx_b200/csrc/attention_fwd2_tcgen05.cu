@@ -162,40 +162,35 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       }
     }
   } else if (warp == 1) {
-    // ---------------------------------- S = Q_g . K_j^T ----------------------------------
+    // ---------------------------------- every tensor-core product of the CTA ----------------------------------
+    // One thread issues S_a(0), S_b(0) and then, per key tile, P_a.V, S_a(next), P_b.V, S_b(next).  The tensor core executes
+    // one thread's products in issue order, so S_g(j+1), which overwrites P_g(j), needs no barrier between it and P_g(j).V:
+    // it is queued right behind it.  The fixed alternation also keeps the two tiles half a period apart.
     if (lane == 0) {
       const bool bf16 = p.is_bf16 != 0;
       const uint32_t idesc_s = make_idesc(bf16, false, false, A2_BM, A2_BN);
-      bool ok = mbar_wait(q_full, 0, abort_flag, p.status, A2_ERR_MMA);
-      for (uint32_t j = 0; j < n_kv && ok; ++j) {
-        const int s = (int)(j & 1);
-        if (!mbar_wait(k_full(s), (j >> 1) & 1, abort_flag, p.status, A2_ERR_MMA)) { ok = false; break; }
-        for (int g = 0; g < 2 && ok; ++g) {
-          if (j >= n_kv_g[g]) continue;
-          // S_g aliases P_g: the previous tile's P_g.V must have consumed it
-          if (j > 0 && !mbar_wait(pv_done(g), (j - 1) & 1, abort_flag, p.status, A2_ERR_MMA)) { ok = false; break; }
-          tc_fence_after();
-          const uint32_t q_addr = base + A2_Q_OFF + g * A2_TILE, k_addr = base + A2_K_OFF + s * A2_TILE;
-#pragma unroll
-          for (int c = 0; c < 2; ++c)
-#pragma unroll
-            for (int kk = 0; kk < 4; ++kk)
-              umma_f16(tmem_s(g), make_smem_desc(q_addr + c * (A2_TILE / 2) + kk * 32, 16, 1024),
-                       make_smem_desc(k_addr + c * (A2_TILE / 2) + kk * 32, 16, 1024), idesc_s, (c | kk) != 0 ? 1u : 0u);
-          umma_commit(s_full(g));
-        }
-        if (ok) umma_commit(k_empty(s));
-      }
-    }
-  } else if (warp == 2) {
-    // ---------------------------------- O_g += P_g . V_j ----------------------------------
-    if (lane == 0) {
-      const bool bf16 = p.is_bf16 != 0;
       const uint32_t idesc_pv = make_idesc(bf16, false, true, A2_BM, A2_D);     // P (from TMEM, K-major) x V (N-major)
-      bool ok = true;
+      auto issue_s = [&](int g, int s) {
+        const uint32_t q_addr = base + A2_Q_OFF + g * A2_TILE, k_addr = base + A2_K_OFF + s * A2_TILE;
+#pragma unroll
+        for (int c = 0; c < 2; ++c)
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk)
+            umma_f16(tmem_s(g), make_smem_desc(q_addr + c * (A2_TILE / 2) + kk * 32, 16, 1024),
+                     make_smem_desc(k_addr + c * (A2_TILE / 2) + kk * 32, 16, 1024), idesc_s, (c | kk) != 0 ? 1u : 0u);
+        umma_commit(s_full(g));
+      };
+      bool ok = mbar_wait(q_full, 0, abort_flag, p.status, A2_ERR_MMA) && mbar_wait(k_full(0), 0, abort_flag, p.status, A2_ERR_MMA);
+      if (ok) {
+        tc_fence_after();
+        issue_s(0, 0);
+        issue_s(1, 0);
+        umma_commit(k_empty(0));
+      }
       for (uint32_t j = 0; j < n_kv && ok; ++j) {
-        const int s = (int)(j & 1);
+        const int s = (int)(j & 1), sn = s ^ 1;
         if (!mbar_wait(v_full(s), (j >> 1) & 1, abort_flag, p.status, A2_ERR_MMA)) { ok = false; break; }
+        bool k_ready = false, s_issued = false;
         for (int g = 0; g < 2 && ok; ++g) {
           if (j >= n_kv_g[g]) continue;
           if (!mbar_wait(p_full(g), j & 1, abort_flag, p.status, A2_ERR_MMA)) { ok = false; break; }
@@ -209,8 +204,17 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                               make_smem_desc(v_addr + kb * (A2_TILE / 2) + kk * (16 * 128), A2_TILE / 4, 1024), idesc_pv,
                               (j != 0 || (kb | kk) != 0) ? 1u : 0u);
           umma_commit(pv_done(g));
+          if (j + 1 < n_kv_g[g]) {
+            if (!k_ready && !mbar_wait(k_full(sn), ((j + 1) >> 1) & 1, abort_flag, p.status, A2_ERR_MMA)) { ok = false; break; }
+            k_ready = true;
+            tc_fence_after();
+            issue_s(g, sn);
+            s_issued = true;
+          }
         }
-        if (ok) umma_commit(v_empty(s));
+        if (!ok) break;
+        umma_commit(v_empty(s));
+        if (s_issued) umma_commit(k_empty(sn));
       }
     }
   } else if (warp >= 4) {
