@@ -488,7 +488,7 @@ class AttentionFwd:
         ms = [d.elapsed_ms(a, b) for a, b in self.kernel_events]
         t = float(np.mean(ms))
         ach = self.flops / (t * 1e-3) / 1e12
-        return ({"bound": "tensor", "kernel": "attn_fwd_kernel (tcgen05)", "achieved": ach, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+        return ({"bound": "tensor", "kernel": "attn_fwd2_kernel (tcgen05; two query tiles per CTA, P as a TMEM operand)", "achieved": ach, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
                  "frac": ach / peaks["bf16_tflops"], "traffic": None, "peak_source": peaks["source"], "ms_per_launch": t,
                  "tflops_dense_equivalent": self.flops_dense / (t * 1e-3) / 1e12},
                 {"attention": {"ms": t, "TFLOP/s": ach},

@@ -86,6 +86,7 @@ pub const ZYXB_KIND_ROWREDUCE: i32 = 1;
 pub const ZYXB_KIND_GEMM: i32 = 2;
 pub const ZYXB_KIND_ELTWISE: i32 = 3;
 pub const ZYXB_KIND_OPTIM: i32 = 4;
+pub const ZYXB_KIND_ATTENTION: i32 = 5;
 
 // ------------------------------------------------------------------------------------------------------------------
 // The entry points, resolved once (as CUDAMemoryPool / CblasDevice resolve theirs with libloading)

@@ -244,6 +244,44 @@ impl Graph {
         let src = self.reduce_last(self.keepdim_src(mx), BOp::Max)?;
         self.same(src, x).then(|| self.canon(x))
     }
+    // ---- fused attention ----------------------------------------------------------------------------------------------------
+    fn permute_of(&self, c: ClassId, want: &[usize]) -> Option<ClassId> {
+        self.find_in(c, |n| match n { Node::Permute { x, axes } if axes.as_ref() == want => Some(*x), _ => None })
+    }
+    /// c [b, h, t, d] = x.reshape([b, t, h, d]).transpose(1, 2) of a stored x [b, t, h*d] (multi_head_attention.rs:160-172) -> x
+    fn head_split_src(&self, c: ClassId) -> Option<ClassId> {
+        let s4 = self.const_shape(c)?;
+        if s4.len() != 4 { return None; }
+        let x = self.reshape_of(self.permute_of(c, &[0, 2, 1, 3])?)?;
+        let s3 = self.const_shape(x)?;
+        (s3.len() == 3 && s3[0] == s4[0] && s3[1] == s4[2] && s3[2] == s4[1] * s4[3]).then(|| self.canon(x))
+    }
+    /// The mask-free core of MultiheadAttention::forward (multi_head_attention.rs:197-226) ending at the class of
+    /// `attn_weights.matmul(v).transpose(1, 2).reshape([b, t, h*d])`: one fused program on the three stored [b, t, h*d] tensors.
+    /// The kernel's shapes only (16-bit dtype, head dimension 128, equal lengths that are a multiple of 128).  A causal mask is
+    /// built from pad nodes (Tensor::tri), which fall back to the separate matmul and softmax programs.
+    fn match_attention(&self, cid: ClassId) -> Option<B200Match> {
+        let s3 = self.const_shape(cid)?;
+        if s3.len() != 3 { return None; }
+        let pv_cls = self.permute_of(self.reshape_of(cid)?, &[0, 2, 1, 3])?;
+        let pv = self.match_matmul_x(pv_cls)?;
+        if pv.trans_b || pv.b_shared { return None; }
+        let sm = self.match_softmax(pv.a)?;
+        let (qk, scale) = self.match_matmul_scaled(sm.inputs[0])?;
+        if !qk.trans_b || qk.b_shared { return None; }
+        let (xq, xk, xv) = (self.head_split_src(qk.a)?, self.head_split_src(qk.b)?, self.head_split_src(pv.b)?);
+        let hs = self.const_shape(pv_cls)?;
+        let (b, h, t, d) = (hs[0], hs[1], hs[2], hs[3]);
+        let shapes_ok = qk.m == t && qk.n == t && qk.k == d && pv.m == t && pv.k == t && pv.n == d && qk.batch == b * h && pv.batch == b * h
+            && s3[0] == b && s3[1] == t && s3[2] == h * d;
+        let dt = qk.dtype;
+        if !shapes_ok || !matches!(dt, DType::BF16 | DType::F16) || pv.dtype != dt || d != 128 || t % 128 != 0 { return None; }
+        let attention = ZyxbAttentionDesc { dtype: dt as i32, batch: b as u64, heads: h as u64, seq: t as u64, head_dim: d as u64, ld: 0, scale, causal: 0 };
+        // the launch takes one more buffer behind the output: the log-sum-exp [b*h, t] f32 the backward program reads
+        Some(B200Match { pattern: "attention", inputs: vec![xq, xk, xv], outputs: vec![cid],
+                         desc: ZyxbKernelDesc { kind: ZYXB_KIND_ATTENTION, u: ZyxbDescUnion { attention } }, numel: Vec::new() })
+    }
+
     /// softmax (tensor/mod.rs:1457-1461)
     fn match_softmax(&self, cid: ClassId) -> Option<B200Match> {
         let (e, s) = self.binary_of(cid, BOp::Div)?;
@@ -355,7 +393,7 @@ impl Graph {
             if wanted.contains(&cid) {
                 if let Some(u) = self.match_adamw(cid).or_else(|| self.match_sgd(cid)) { updates.push(u); continue; }
             }
-            let m = self.match_linear(cid, wanted).or_else(|| self.match_softmax(cid)).or_else(|| self.match_ln_softmax(cid))
+            let m = self.match_attention(cid).or_else(|| self.match_linear(cid, wanted)).or_else(|| self.match_softmax(cid)).or_else(|| self.match_ln_softmax(cid))
                 .or_else(|| self.match_layernorm(cid)).or_else(|| self.match_reduce(cid));
             out.extend(m);
         }

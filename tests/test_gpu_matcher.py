@@ -90,3 +90,35 @@ def test_softmax_layernorm_and_sgd_from_graph_to_launch(sess):
         assert max_rel_err(got, want) <= TOL_F32
     finally:
         g.close()
+
+
+def test_attention_core_from_graph_to_launch(sess):
+    """The mask-free core of MultiheadAttention::forward, traced, matched as one fused program and launched on the three stored
+    [b, t, e] tensors (plus the log-sum-exp buffer the program takes behind its output): the oracle's composed attention."""
+    from oracle import models as zm
+    from tests.zyx_trace import attention_core
+    rng = np.random.default_rng(33)
+    dtype, b, t, heads, d = L.BF16, 2, 256, 3, 128
+    g = MGraph()
+    try:
+        q, k, v = (T.leaf(g, dtype, (b, t, heads * d)) for _ in range(3))
+        out = attention_core(q, k, v, heads)
+        m = pick(g.match([out.cls]), b"attention", out.cls)
+        vals = {c.cls: zo.to_bits(rng.standard_normal((b, t, heads * d)).astype(np.float32), dtype) for c in (q, k, v)}
+        prog = sess.device.create_program(m.desc)
+        bufs = [sess.pool.upload(vals[c]) for c in m.inputs[:m.n_inputs]]
+        o_buf = sess.pool.allocate(b * t * heads * d * 2)[0]
+        lse_buf = sess.pool.allocate(b * heads * t * 4)[0]
+        try:
+            sess.device.launch(prog, bufs + [o_buf, lse_buf])
+            got = sess.pool.download(o_buf, (b, t, heads * d), np.uint16)
+            assert sess.device.status() == 0
+        finally:
+            for x in bufs + [o_buf, lse_buf]:
+                sess.pool.deallocate(x)
+            sess.device.release(prog)
+        want, _, exact = zm.attention(dtype, vals[q.cls], vals[k.cls], vals[v.cls], heads, False)
+        assert_parity(zo.to_f32(got, dtype).astype(np.float64), zo.to_f32(want, dtype).astype(np.float64), exact, TOL_BF16, floor=1.0,
+                      what="matched attention")
+    finally:
+        g.close()

@@ -230,3 +230,28 @@ def test_constructor_arguments_are_validated(g):
         g.binary(x, g.leaf(L.F32, (5, 4)), 0)
     with pytest.raises(ValueError):
         g.reduce(x, 0, (2,))
+
+
+def test_mask_free_attention_core_is_one_fused_program(g):
+    """q, k, v [b, t, h*128] -> head split, scores * scale, softmax, .matmul(v), heads merged: the fused attention program on
+    the three stored tensors.  Outside the kernel's shapes (f32, head dimension 64) the same graph yields its separate
+    batched matmuls and the softmax instead."""
+    from tests.zyx_trace import attention_core
+    q, k, v = (T.leaf(g, L.BF16, (2, 256, 512)) for _ in range(3))
+    out = attention_core(q, k, v, heads=4)
+    ms = g.match([out.cls])
+    att = [m for m in ms if m.pattern == b"attention"]
+    # the inner classes keep their own alternatives (the scores' matmul, the softmax, ...), as in an e-graph; the class of
+    # the merged result holds the fused program, and extraction takes the cheaper cover
+    assert len(att) == 1 and att[0].outputs[0] == out.cls and not any(m.outputs[0] == out.cls for m in ms if m.pattern != b"attention")
+    m = att[0]
+    assert m.desc.kind == L.KIND_ATTENTION
+    a = m.desc.u.attention
+    assert (a.dtype, a.batch, a.heads, a.seq, a.head_dim, a.causal) == (L.BF16, 2, 4, 256, 128, 0)
+    assert abs(a.scale - 1.0 / math.sqrt(128)) < 1e-3
+    assert list(m.inputs[:m.n_inputs]) == [q.cls, k.cls, v.cls] and list(m.outputs[:m.n_outputs]) == [out.cls]
+    # head dimension 64: not the fused kernel's shape
+    q2, k2, v2 = (T.leaf(g, L.BF16, (2, 256, 256)) for _ in range(3))
+    out2 = attention_core(q2, k2, v2, heads=4)
+    pats = sorted(m.pattern for m in g.match([out2.cls]))
+    assert b"attention" not in pats and b"softmax" in pats and sum(p.startswith(b"matmul") for p in pats) >= 2

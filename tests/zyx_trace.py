@@ -216,3 +216,16 @@ def adamw_update(params, grads, m, v, t, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, 
             q = q * (1.0 - lr * weight_decay)
         new_p.append(q); new_m.append(mi); new_v.append(vi)
     return new_p, new_m, new_v
+
+
+def attention_core(q, k, v, heads):
+    """The mask-free core of MultiheadAttention::forward between the projections (zyx-nn/src/multi_head_attention.rs:160-172,
+    197-199, 219-226): q, k, v [b, t, e] -> head split, scores * 1/sqrt(d), softmax, .matmul(v), heads merged -> [b, t, e].
+    `matmul` is `dot` (tensor/mod.rs:1464-1467); transpose(1, 2) and transpose(-2, -1) are permutes."""
+    b, t, e = q.shape
+    d = e // heads
+    split = lambda x: x.reshape([x.shape[0], x.shape[1], heads, d]).permute([0, 2, 1, 3])
+    qh, kh, vh = split(q), split(k), split(v)
+    scores = qh.dot(kh.t()) * (1.0 / math.sqrt(d))
+    out = scores.softmax().dot(vh)
+    return out.permute([0, 2, 1, 3]).reshape([b, t, e])

@@ -57,11 +57,13 @@ def build(force=False, verbose=False):
                 if verbose:
                     print("compiled", os.path.basename(done))
     if jobs or not os.path.exists(LIB):
-        cmd = [NVCC, "-shared", "-o", LIB] + objs + ["-cudart", "static", "-ldl", "-lpthread",
+        tmp = LIB + ".tmp%d" % os.getpid()           # linked beside the target and renamed: a reader never sees half a library
+        cmd = [NVCC, "-shared", "-o", tmp] + objs + ["-cudart", "static", "-ldl", "-lpthread",
                                                       "-gencode", "arch=compute_100a,code=sm_100a"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError("link failed:\n%s\n%s" % (r.stdout, r.stderr))
+        os.replace(tmp, LIB)
     build_host(force or bool(jobs))
     return LIB
 
@@ -71,10 +73,12 @@ def build_host(force=False):
     srcs = sorted(glob.glob(os.path.join(CSRC, "host", "*.cpp")))
     newest = max([os.path.getmtime(s) for s in srcs + glob.glob(os.path.join(CSRC, "host", "*.hpp"))] + [_newest_header()])
     if force or not os.path.exists(HOST_LIB) or os.path.getmtime(HOST_LIB) < newest:
-        cmd = ["g++", "-shared", "-o", HOST_LIB] + CXX_FLAGS + srcs + ["-L", HERE, "-lzyxb", "-Wl,-rpath,$ORIGIN"]
+        tmp = HOST_LIB + ".tmp%d" % os.getpid()
+        cmd = ["g++", "-shared", "-o", tmp] + CXX_FLAGS + srcs + ["-L", HERE, "-lzyxb", "-Wl,-rpath,$ORIGIN"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError("host link failed: %s\n%s\n%s" % (" ".join(cmd), r.stdout, r.stderr))
+        os.replace(tmp, HOST_LIB)
     return HOST_LIB
 
 

@@ -379,6 +379,62 @@ class Graph {
     return std::nullopt;
   }
 
+  // ---- fused attention ---------------------------------------------------------------------------------------------------
+  std::optional<ClassId> permute_src(ClassId c, const std::vector<int>& axes) const {
+    const Node* n = find(c, [&](const Node& n) { return n.kind == K_PERMUTE && n.axes == axes; });
+    return n ? std::optional<ClassId>(n->x) : std::nullopt;
+  }
+  // c [b, h, t, d] = x.reshape([b, t, h, d]).transpose(1, 2) of a stored x [b, t, h*d] (multi_head_attention.rs:160-172) -> x
+  std::optional<ClassId> head_split_src(ClassId c) const {
+    const auto s4 = shape(c);
+    if (s4.size() != 4) return std::nullopt;
+    auto r = permute_src(c, {0, 2, 1, 3});
+    if (!r) return std::nullopt;
+    auto x = reshape_src(*r);
+    if (!x) return std::nullopt;
+    const auto s3 = shape(*x);
+    if (s3.size() != 3 || s3[0] != s4[0] || s3[1] != s4[2] || s3[2] != s4[1] * s4[3]) return std::nullopt;
+    return canon(*x);
+  }
+  // The core of MultiheadAttention::forward without masks (multi_head_attention.rs:197-226), ending at the class of
+  //   attn_weights.matmul(v).transpose(1, 2).reshape([b, t, h*d]),  attn_weights = (q.matmul(k.transpose(-2, -1)) * scale).softmax([-1]),
+  // with q, k, v the head-split views of three stored [b, t, h*d] tensors: one fused program that reads those three where they
+  // lie and writes the [b, t, h*d] result; scores and probabilities never exist.  The kernel's shapes only: 16-bit dtype, head
+  // dimension 128, equal query and key lengths that are a multiple of 128.  A causal mask is built from pad nodes
+  // (Tensor::tri, tensor/mod.rs:2396-2418), which this mirror does not carry: such graphs fall back to the separate
+  // matmul and softmax programs.
+  std::optional<Match> match_attention(ClassId cid) const {
+    const auto s3 = shape(cid);
+    if (s3.size() != 3) return std::nullopt;
+    auto r = reshape_src(cid);
+    if (!r || shape(*r).size() != 4) return std::nullopt;
+    auto pv_cls = permute_src(*r, {0, 2, 1, 3});
+    if (!pv_cls) return std::nullopt;
+    auto pv = match_matmul(*pv_cls);
+    if (!pv || pv->trans_b || pv->b_shared) return std::nullopt;
+    auto sm = match_softmax(pv->a);
+    if (!sm) return std::nullopt;
+    auto sc = match_matmul_scaled(sm->inputs[0]);
+    if (!sc || !sc->first.trans_b || sc->first.b_shared) return std::nullopt;
+    const MatMul& qk = sc->first;
+    auto xq = head_split_src(qk.a), xk = head_split_src(qk.b), xv = head_split_src(pv->b);
+    if (!xq || !xk || !xv) return std::nullopt;
+    const auto hs = shape(*pv_cls);                          // [b, h, t, d]
+    const uint64_t B = hs[0], H = hs[1], T = hs[2], D = hs[3];
+    if (qk.m != T || qk.n != T || qk.k != D || pv->m != T || pv->k != T || pv->n != D || qk.batch != B * H || pv->batch != B * H) return std::nullopt;
+    const int dt = qk.dtype;
+    if ((dt != ZYXB_BF16 && dt != ZYXB_F16) || pv->dtype != dt || D != 128 || T % 128 != 0) return std::nullopt;
+    if (s3[0] != B || s3[1] != T || s3[2] != H * D) return std::nullopt;
+    Match m;
+    m.pattern = "attention";
+    m.desc.kind = ZYXB_KIND_ATTENTION;
+    auto& a = m.desc.u.attention;
+    a.dtype = dt; a.batch = B; a.heads = H; a.seq = T; a.head_dim = D; a.scale = sc->second; a.causal = 0;
+    m.inputs = {*xq, *xk, *xv};
+    m.outputs = {cid};      // the launch takes one more buffer behind it: the log-sum-exp [b*h, t] f32 the backward program reads
+    return m;
+  }
+
   // ---- row kernels ---------------------------------------------------------------------------------------------------------
   static zyxb_kernel_desc row_desc(int op, int dt, const std::vector<uint64_t>& s) {
     zyxb_kernel_desc d{};
@@ -584,7 +640,7 @@ class Graph {
         if (auto u = match_adamw(cid)) { updates.push_back(*u); continue; }
         if (auto u = match_sgd(cid)) { updates.push_back(*u); continue; }
       }
-      if (!(m = match_linear(cid, wanted)) && !(m = match_softmax(cid)) && !(m = match_ln_softmax(cid)) && !(m = match_layernorm(cid)) &&
+      if (!(m = match_attention(cid)) && !(m = match_linear(cid, wanted)) && !(m = match_softmax(cid)) && !(m = match_ln_softmax(cid)) && !(m = match_layernorm(cid)) &&
           !(m = match_reduce(cid)))
         continue;
       out.push_back(std::move(*m));
