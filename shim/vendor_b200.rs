@@ -35,7 +35,7 @@ struct MatMulX { a: ClassId, b: ClassId, m: Dim, n: Dim, k: Dim, batch: Dim, tra
 struct Update { algo: i32, p: ClassId, g: ClassId, m: Option<ClassId>, v: Option<ClassId>, p_new: ClassId, m_new: Option<ClassId>,
                 v_new: Option<ClassId>, lr: f64, wd: f64, b1: f64, b2: f64, eps: f64, bc1: f64, bc2: f64, first: bool }
 
-const RR_SUM: i32 = 0; const RR_MAX: i32 = 1; const RR_MEAN: i32 = 3; const RR_SOFTMAX: i32 = 6; const RR_LN_SOFTMAX: i32 = 7; const RR_LAYERNORM: i32 = 8;
+const RR_SUM: i32 = 0; const RR_MAX: i32 = 1; const RR_MEAN: i32 = 3; const RR_SOFTMAX: i32 = 6; const RR_LN_SOFTMAX: i32 = 7; const RR_LAYERNORM: i32 = 8; const RR_MSE: i32 = 14;
 const EPI_NONE: i32 = 0; const EPI_BIAS: i32 = 1; const EPI_BIAS_RELU: i32 = 2; const EPI_BIAS_GELU: i32 = 3;
 const OPT_SGD: i32 = 0; const OPT_ADAMW: i32 = 2;
 
@@ -334,6 +334,20 @@ impl Graph {
         let c = self.cast_src(c).unwrap_or(c);
         matches!(self.binary_of(c, BOp::Mul), Some((x, y)) if self.expand_of(x).is_some() && self.expand_of(y).is_some())
     }
+    /// mse_loss(y, t) = ((y - t) * (y - t)).mean_all() (tensor/mod.rs:1999-2003); f32 only: the program leaves an f32 scalar
+    fn match_mse(&self, cid: ClassId) -> Option<B200Match> {
+        let (sum, n) = self.binary_const(cid, BOp::Div)?;
+        let (x, axes) = self.find_in(sum, |nd| match nd { Node::Reduce { x, rop: BOp::Add, axes } => Some((*x, axes.clone())), _ => None })?;
+        let xs = self.const_shape(x)?;
+        if xs.is_empty() || axes.len() != xs.len() || (n - xs.iter().product::<Dim>() as f64).abs() > 0.5 { return None; }
+        let (d0, d1) = self.binary_of(x, BOp::Mul)?;
+        if !self.same(d0, d1) { return None; }
+        let (y, t) = self.binary_of(d0, BOp::Sub)?;
+        let (y, t) = (self.canon(y), self.canon(t));
+        let f32s = [y, t, cid].iter().all(|&c| self.dtype(c) == DType::F32);
+        if !f32s || self.const_shape(y)? != xs || self.const_shape(t)? != xs { return None; }
+        Some(self.row_match("mse_loss", self.row_desc(RR_MSE, y)?, vec![y, t], cid))
+    }
     fn match_reduce(&self, cid: ClassId) -> Option<B200Match> {
         if let Some((x, _)) = self.mean_last(cid) { if let Some(d) = self.row_desc(RR_MEAN, x) { return Some(self.row_match("mean", d, vec![x], cid)); } }
         for (rop, rr, name) in [(BOp::Add, RR_SUM, "sum"), (BOp::Max, RR_MAX, "max")] {
@@ -394,7 +408,7 @@ impl Graph {
                 if let Some(u) = self.match_adamw(cid).or_else(|| self.match_sgd(cid)) { updates.push(u); continue; }
             }
             let m = self.match_attention(cid).or_else(|| self.match_linear(cid, wanted)).or_else(|| self.match_softmax(cid)).or_else(|| self.match_ln_softmax(cid))
-                .or_else(|| self.match_layernorm(cid)).or_else(|| self.match_reduce(cid));
+                .or_else(|| self.match_layernorm(cid)).or_else(|| self.match_mse(cid)).or_else(|| self.match_reduce(cid));
             out.extend(m);
         }
         let mut used = vec![false; updates.len()];

@@ -255,3 +255,14 @@ def test_mask_free_attention_core_is_one_fused_program(g):
     out2 = attention_core(q2, k2, v2, heads=4)
     pats = sorted(m.pattern for m in g.match([out2.cls]))
     assert b"attention" not in pats and b"softmax" in pats and sum(p.startswith(b"matmul") for p in pats) >= 2
+
+
+def test_mse_loss_is_the_two_stage_loss_program(g):
+    y, t = T.leaf(g, L.F32, (96, 40)), T.leaf(g, L.F32, (96, 40))
+    loss = y.mse_loss(t)
+    m = by_pattern(g.match([loss.cls]))["mse_loss"]
+    assert_same_row(m.desc, B.rowreduce_desc(L.RR_MSE, L.F32, 96, 40))
+    assert list(m.inputs[:m.n_inputs]) == [y.cls, t.cls] and list(m.outputs[:m.n_outputs]) == [loss.cls]
+    # 16-bit tensors: the reference's loss is a scalar of the tensor's dtype, the program's an f32 one - left to the generic path
+    yb, tb = T.leaf(g, L.BF16, (96, 40)), T.leaf(g, L.BF16, (96, 40))
+    assert "mse_loss" not in by_pattern(g.match([yb.mse_loss(tb).cls]))

@@ -141,6 +141,13 @@ class T:
             t = t.reshape(shape)
         return t
 
+    def mean_all(self):
+        return self.mean(list(range(len(self.shape))))          # reduce_impl with no axes: every axis (reduce_ops.rs:286-288)
+
+    def mse_loss(self, target):
+        d = self - target                                       # tensor/mod.rs:1999-2003
+        return (d * d).mean_all()
+
     def var(self, axes, keepdim=False, correction=1):
         shape = list(self.shape)
         n = 1

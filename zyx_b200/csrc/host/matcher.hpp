@@ -554,6 +554,25 @@ class Graph {
     return std::nullopt;
   }
 
+  // mse_loss(y, t) = ((y - t) * (y - t)).mean_all()   (tensor/mod.rs:1999-2003): Div{Reduce{Mul{d, d}, Add, every axis}, n}.
+  // f32 only: the program leaves an f32 scalar, the reference a scalar of the tensor's dtype.
+  std::optional<Match> match_mse(ClassId cid) const {
+    auto div = binary_const(cid, B_DIV);
+    if (!div) return std::nullopt;
+    const Node* red = find(div->first, [](const Node& n) { return n.kind == K_REDUCE && n.op == B_ADD; });
+    if (!red) return std::nullopt;
+    const auto xs = shape(red->x);
+    if (xs.empty() || red->axes.size() != xs.size() || fabs(div->second - (double)numel(xs)) > 0.5) return std::nullopt;
+    auto mul = binary(red->x, B_MUL);
+    if (!mul || !same(mul->first, mul->second)) return std::nullopt;
+    auto sub = binary(mul->first, B_SUB);
+    if (!sub) return std::nullopt;
+    const ClassId y = canon(sub->first), t = canon(sub->second);
+    if (dtype(y) != ZYXB_F32 || dtype(t) != ZYXB_F32 || dtype(cid) != ZYXB_F32 || shape(y) != xs || shape(t) != xs) return std::nullopt;
+    Match m; m.pattern = "mse_loss"; m.desc = row_desc(ZYXB_RR_MSE, ZYXB_F32, xs); m.inputs = {y, t}; m.outputs = {cid};
+    return m;
+  }
+
   bool is_broadcast_product(ClassId c) const {
     if (auto k = cast_src(c)) c = *k;
     auto mul = binary(c, B_MUL);
@@ -641,7 +660,7 @@ class Graph {
         if (auto u = match_sgd(cid)) { updates.push_back(*u); continue; }
       }
       if (!(m = match_attention(cid)) && !(m = match_linear(cid, wanted)) && !(m = match_softmax(cid)) && !(m = match_ln_softmax(cid)) && !(m = match_layernorm(cid)) &&
-          !(m = match_reduce(cid)))
+          !(m = match_mse(cid)) && !(m = match_reduce(cid)))
         continue;
       out.push_back(std::move(*m));
     }
