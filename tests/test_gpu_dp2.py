@@ -103,7 +103,9 @@ def _rank_allreduce(rank, world, tmp, mode):
     """Every rank allreduces the same sequence of ranges (several dtypes, sizes that do not divide into shards, offsets into a
     larger buffer, a view, repeated calls on one buffer) and checks the sum it can compute by itself from the seeds."""
     os.environ["NCCL_NVLS_ENABLE"] = "0"
-    os.environ["ZYXB_ALLREDUCE"] = mode
+    os.environ["ZYXB_ALLREDUCE"] = "nccl" if mode == "nccl" else "peer"
+    if mode == "peer_direct":
+        os.environ["ZYXB_PEER_DIRECT"] = "1"       # the reduce kernel reads the peers' buffers itself instead of staged copies
     os.environ["ZYXB_PEER_WAIT_MS"] = "10000"
     from oracle import oracle as zo
     from zyx_b200 import _lib as L
@@ -164,7 +166,7 @@ def _rank_allreduce(rank, world, tmp, mode):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-@pytest.mark.parametrize("mode", ["peer", "nccl"])
+@pytest.mark.parametrize("mode", ["peer", "peer_direct", "nccl"])
 def test_allreduce_over_peer_memory_and_over_nccl(tmp_path, mode):
     """zyxb_allreduce_sum on two ranks: the copy-engine path over IPC-mapped peer memory (the default) and the NCCL path
     (ZYXB_ALLREDUCE=nccl) give the sum of the ranks' data, leave everything outside the range alone, and keep working call

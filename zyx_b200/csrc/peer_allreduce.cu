@@ -344,7 +344,12 @@ int peer_allreduce_sum(PeerComm* p, Comm* c, void* base, uint64_t buffer_bytes, 
   auto lo = [&](int r) { return std::min<uint64_t>((uint64_t)r * cs, count); };
   auto hi = [&](int r) { return std::min<uint64_t>((uint64_t)(r + 1) * cs, count); };
   const uint64_t mine_n = hi(me) - lo(me);
-  const uint64_t need = (uint64_t)(W - 1) * cs * es;
+  // ZYXB_PEER_DIRECT=1: the reduce kernel reads the peers' copies of this rank's shard over NVLink itself (plain loads from
+  // the mapped peer buffers) instead of adding up copies the copy engines staged here: one phase and one pass over local
+  // memory less, at the price of reduce CTAs that wait on NVLink latency beside the matmuls.
+  static const int direct_env = getenv("ZYXB_PEER_DIRECT") ? atoi(getenv("ZYXB_PEER_DIRECT")) : 0;
+  const bool direct = direct_env == 1 || (direct_env == 2 && count * es <= (100ull << 20));
+  const uint64_t need = direct ? 0 : (uint64_t)(W - 1) * cs * es;
   if (need > p->staging_bytes) {
     cudaStreamSynchronize(stream);
     if (p->staging) cudaFree(p->staging);
@@ -375,20 +380,24 @@ int peer_allreduce_sum(PeerComm* p, Comm* c, void* base, uint64_t buffer_bytes, 
   auto join = [&]() { for (int d = 2; d < W && e == cudaSuccess; ++d) e = cudaStreamWaitEvent(stream, p->join[d - 2], 0); };
   ReduceSrc src{};
   int slot = 0;
-  fork();
-  for (int d = 1; d < W; ++d) {
-    const int r = (me + d) % W;
-    char* dst = (char*)p->staging + (uint64_t)slot++ * cs * es;
-    src.ptr[r] = dst;
-    copy_on(d, dst, at(B.peer_base[r], lo(me)), mine_n * es);
+  if (direct) {
+    for (int r = 0; r < W; ++r) if (r != me) src.ptr[r] = at(B.peer_base[r], lo(me));
+  } else {
+    fork();
+    for (int d = 1; d < W; ++d) {
+      const int r = (me + d) % W;
+      char* dst = (char*)p->staging + (uint64_t)slot++ * cs * es;
+      src.ptr[r] = dst;
+      copy_on(d, dst, at(B.peer_base[r], lo(me)), mine_n * es);
+    }
+    join();
   }
-  join();
   src.ptr[me] = at(base, lo(me));
   if (e != cudaSuccess) { err = std::string("peer allreduce pull: ") + cudaGetErrorString(e); return ZYXB_ERR_KERNEL_LAUNCH; }
   // 3. add, in rank order
   if (mine_n) {
     // short-lived CTAs without shared memory: they slot in beside the matmul's CTAs; enough of them to stream at HBM speed
-    const unsigned grid = (unsigned)std::max<uint64_t>(1, std::min<uint64_t>(296, mine_n / 8192 + 1));
+    const unsigned grid = (unsigned)std::max<uint64_t>(1, std::min<uint64_t>(direct ? 592 : 296, mine_n / 8192 + 1));
     void* out = at(base, lo(me));
     switch (dtype) {
       case ZYXB_F32: peer_reduce_kernel<0><<<grid, 256, 0, stream>>>(src, out, mine_n, W); break;
