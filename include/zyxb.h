@@ -425,6 +425,13 @@ int32_t zyxb_allreduce_sum(zyxb_ctx* ctx, int32_t dev, uint32_t buf, uint64_t of
  * place on `world` consecutive slices of count_per_rank elements starting at offset_elems: after reduce_scatter_sum
  * slice `rank` holds the sum over ranks (the other slices are unspecified); allgather sends this rank's slice and
  * leaves all `world` slices filled.  Same stream and event rules as zyxb_allreduce_sum. */
+/* Per-device communicator options.  ZYXB_COMM_OPT_LATENCY = 1: the zyxb_allreduce_sum calls that follow sit at the end of a
+ * step with nothing left to hide behind; they take the communicator's own allreduce (NCCL: few, large messages reduced by its
+ * kernels, in the switch where the fabric offers it) even where the copy-engine exchange over peer memory is available.  That
+ * exchange is the choice for calls that overlap compute, because it takes no SM, but each call is three flag rounds among
+ * all ranks around two copy phases.  0 (the default) = back to that choice.  Every rank makes the same setting for the same call. */
+enum { ZYXB_COMM_OPT_LATENCY = 1 };
+int32_t zyxb_comm_option(zyxb_ctx* ctx, int32_t dev, int32_t option, int32_t value);
 int32_t zyxb_reduce_scatter_sum(zyxb_ctx* ctx, int32_t dev, uint32_t buf, uint64_t offset_elems, uint64_t count_per_rank, int32_t dtype,
                                 const zyxb_event* wait, int32_t n_wait, zyxb_event* out_event);
 int32_t zyxb_allgather(zyxb_ctx* ctx, int32_t dev, uint32_t buf, uint64_t offset_elems, uint64_t count_per_rank, int32_t dtype,

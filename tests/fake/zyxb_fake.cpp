@@ -266,6 +266,7 @@ int32_t zyxb_comm_unique_id(zyxb_ctx*, void* out) { memset(out, 7, 128); return 
 int32_t zyxb_comm_init(zyxb_ctx* c, int32_t, int32_t rank, int32_t world, const void*) { c->rank = rank; c->world = world; c->comm = true; return ZYXB_OK; }
 int32_t zyxb_comm_rank(zyxb_ctx* c, int32_t, int32_t* r, int32_t* w) { if (!c->comm) return fail(c, ZYXB_ERR_INCORRECT_KERNEL_ARG, "no communicator"); *r = c->rank; *w = c->world; return ZYXB_OK; }
 int32_t zyxb_comm_destroy(zyxb_ctx* c, int32_t) { c->comm = false; return ZYXB_OK; }
+int32_t zyxb_comm_option(zyxb_ctx*, int32_t, int32_t, int32_t) { return ZYXB_OK; }
 static int32_t collective(zyxb_ctx* c, uint32_t buf, uint64_t off, uint64_t count, int32_t dtype, int32_t op, zyxb_event* ev, const char* what) {
   Buf* b = get(c, buf);
   if (!c->comm) return fail(c, ZYXB_ERR_INCORRECT_KERNEL_ARG, std::string(what) + ": no communicator");

@@ -123,6 +123,8 @@ def _rank_allreduce(rank, world, tmp, mode):
             time.sleep(0.05)
         sess.device.comm_init(rank, world, open(uid_path, "rb").read())
         p, d = sess.pool, sess.device
+        if mode == "peer_latency":                  # the option a plan sets around its last collective: the communicator's own allreduce
+            d.comm_option(L.COMM_OPT_LATENCY, 1)
         data = lambda r, n, seed: np.random.default_rng(1000 * seed + r).standard_normal(n).astype(np.float32)
         cases = [(L.F32, 1 << 20, 0, 1 << 20), (L.F32, 100003, 256, 99000), (L.BF16, 5_000_000, 128, 4_999_000), (L.F16, 777, 0, 777),
                  (L.BF16, 64, 0, 7), (L.I32, 4099, 3, 4000), (L.BF16, 1 << 24, 0, 1 << 24)]
@@ -166,7 +168,7 @@ def _rank_allreduce(rank, world, tmp, mode):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-@pytest.mark.parametrize("mode", ["peer", "peer_direct", "nccl"])
+@pytest.mark.parametrize("mode", ["peer", "peer_direct", "peer_latency", "nccl"])
 def test_allreduce_over_peer_memory_and_over_nccl(tmp_path, mode):
     """zyxb_allreduce_sum on two ranks: the copy-engine path over IPC-mapped peer memory (the default) and the NCCL path
     (ZYXB_ALLREDUCE=nccl) give the sum of the ranks' data, leave everything outside the range alone, and keep working call

@@ -15,6 +15,7 @@ OK = 0
 ERR_NAMES = {1: "DyLibNotFound", 2: "Initialization", 3: "Deinitialization", 4: "DeviceEnumeration", 5: "DeviceQuery",
              6: "MemoryAllocation", 7: "MemoryDeallocation", 8: "MemoryCopyH2P", 9: "MemoryCopyP2H", 10: "IncorrectKernelArg",
              11: "KernelCompilation", 12: "KernelLaunch", 13: "KernelSync"}
+COMM_OPT_LATENCY = 1
 ERR_NAMES_INV = {name: code for code, name in ERR_NAMES.items()}
 BF16, F16, F32, F64, U8, U16, U32, U64, I8, I16, I32, I64, BOOL = range(13)
 DTYPE_SIZE = {BF16: 2, F16: 2, F32: 4, F64: 8, U8: 1, U16: 2, U32: 4, U64: 8, I8: 1, I16: 2, I32: 4, I64: 8, BOOL: 1}
@@ -145,6 +146,7 @@ SIGNATURES = {
     "zyxb_reduce_scatter_sum": (C.c_int32, [_CTX, C.c_int32, C.c_uint32, C.c_uint64, C.c_uint64, C.c_int32, _EV_P, C.c_int32, _EV_P]),
     "zyxb_allgather": (C.c_int32, [_CTX, C.c_int32, C.c_uint32, C.c_uint64, C.c_uint64, C.c_int32, _EV_P, C.c_int32, _EV_P]),
     "zyxb_comm_rank": (C.c_int32, [_CTX, C.c_int32, C.POINTER(C.c_int32), C.POINTER(C.c_int32)]),
+    "zyxb_comm_option": (C.c_int32, [_CTX, C.c_int32, C.c_int32, C.c_int32]),
     "zyxb_comm_destroy": (C.c_int32, [_CTX, C.c_int32]),
 }
 

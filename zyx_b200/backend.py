@@ -299,6 +299,9 @@ class Device:
                                                   C.byref(ev) if want_event else None))
         return ev
 
+    def comm_option(self, option, value):
+        self.be._check(self.be.lib.zyxb_comm_option(self.be.ctx, self.dev, option, value))
+
     def comm_rank(self):
         r, w = C.c_int32(), C.c_int32()
         self.be._check(self.be.lib.zyxb_comm_rank(self.be.ctx, self.dev, C.byref(r), C.byref(w)))

@@ -69,6 +69,7 @@ struct Device {
   void* tma_encode_im2col = nullptr;
   Comm* comm = nullptr;
   PeerComm* peer = nullptr;               // allreduce over peer memory (peer_allreduce.cu); created with the communicator
+  int comm_latency = 0;                   // ZYXB_COMM_OPT_LATENCY: allreduces take the communicator's own path
   // captured launch sequences (the analogue of a FrozenTape): executable graph + kernels per replay
   std::vector<std::pair<cudaGraphExec_t, uint64_t>> graphs;
   bool capturing = false;
@@ -869,7 +870,7 @@ int32_t zyxb_allreduce_sum(zyxb_ctx* ctx, int32_t dev, uint32_t buf, uint64_t of
   std::string err;
   char* p = (char*)b->ptr + offset_elems * es;
   Buffer* root = b->is_view ? get_buffer(D, b->parent) : b;
-  if (peer_usable(D.peer) && root && !root->is_view && !D.capturing) {
+  if (peer_usable(D.peer) && root && !root->is_view && !D.capturing && !D.comm_latency) {
     // the whole cudaMalloc block is mapped by the peers; the range is an offset into it
     const uint64_t byte_offset = (uint64_t)(p - (char*)root->ptr);
     st = peer_allreduce_sum(D.peer, D.comm, root->ptr, root->capacity, byte_offset, count, dtype, D.comm_stream, &D.launch_count, err);
@@ -923,6 +924,13 @@ int32_t zyxb_comm_rank(zyxb_ctx* ctx, int32_t dev, int32_t* out_rank, int32_t* o
   comm_rank(D.comm, &rank, &world);
   if (out_rank) *out_rank = rank;
   if (out_world) *out_world = world;
+  return ZYXB_OK;
+}
+
+int32_t zyxb_comm_option(zyxb_ctx* ctx, int32_t dev, int32_t option, int32_t value) {
+  DEV_OR_FAIL(ZYXB_ERR_INITIALIZATION);
+  if (option != ZYXB_COMM_OPT_LATENCY) return fail(ctx, ZYXB_ERR_INCORRECT_KERNEL_ARG, "comm_option: unknown option");
+  D.comm_latency = value != 0;
   return ZYXB_OK;
 }
 

@@ -10,6 +10,7 @@
 // place through row pitches and a (batch, head) two-level batch, and write their results back the same way.
 #include <math.h>
 #include <stdio.h>
+#include <stdlib.h>
 
 #include "../../../include/zyxb_host.h"
 #include "checkpoint.hpp"
@@ -187,9 +188,10 @@ int32_t build(zyxb_block* K) {
     CHK(P.launch(gemm(dt, out_f, in_f, R, true, false), {dout, in, K->grad[w]}));
     return P.launch(row(ZYXB_RR_COLSUM, dt, R, out_f), {dout, K->grad[b]});
   };
+  const int tail_collectives = getenv("ZYXB_TAIL_COLLECTIVES") ? atoi(getenv("ZYXB_TAIL_COLLECTIVES")) : 0;   // 1: the last group's allreduce takes the low-latency path
   auto reduce_group = [&](int g) {
     if (K->sharded) P.reduce_scatter(K->grad_bucket, group_off[g], K->shard[g]);
-    else if (c.world > 1) P.allreduce(K->grad_bucket, group_off[g], group_off[g + 1] - group_off[g]);
+    else if (c.world > 1) P.allreduce(K->grad_bucket, group_off[g], group_off[g + 1] - group_off[g], g == 2 && tail_collectives >= 1);
     return (int32_t)ZYXB_OK;
   };
   CHK(layernorm_bwd(K->s2, K->dy, P_G2, P_BE2, K->ds2));       // ds2 flows to both x1 (residual) and mlp2's output

@@ -18,6 +18,7 @@ struct Instr {
   uint64_t offset = 0, count = 0;
   int wait_collectives = 0;       // LAUNCH: wait first for this many of the oldest pending gradient-collective events (-1: all)
   int group = -1;                 // ALLGATHER: the parameter group it completes; LAUNCH: the first reader of that group's parameters
+  bool tail = false;              // ALLREDUCE: the step's last collective, nothing left to hide it behind (ZYXB_COMM_OPT_LATENCY around the call)
 };
 
 inline uint64_t dsize(int32_t dtype) { return dtype == ZYXB_F32 ? 4 : 2; }
@@ -66,9 +67,9 @@ class Plan {
     ++n_launches;
     return ZYXB_OK;
   }
-  void allreduce(uint32_t buffer, uint64_t offset, uint64_t count) {
+  void allreduce(uint32_t buffer, uint64_t offset, uint64_t count, bool tail = false) {
     Instr in;
-    in.kind = Instr::ALLREDUCE; in.buffer = buffer; in.offset = offset; in.count = count;
+    in.kind = Instr::ALLREDUCE; in.buffer = buffer; in.offset = offset; in.count = count; in.tail = tail;
     instrs.push_back(in);
     ++n_collectives;
   }
@@ -104,7 +105,11 @@ class Plan {
         zyxb_event ev{};
         int32_t st;
         if (in.kind == Instr::ALLREDUCE) {
-          if ((st = zyxb_allreduce_sum(ctx, dev, in.buffer, in.offset, in.count, dtype, nullptr, 0, &ev))) return fail(st, "zyxb_allreduce_sum");
+          if (in.tail && (st = zyxb_comm_option(ctx, dev, ZYXB_COMM_OPT_LATENCY, 1))) return fail(st, "zyxb_comm_option");
+          st = zyxb_allreduce_sum(ctx, dev, in.buffer, in.offset, in.count, dtype, nullptr, 0, &ev);
+          if (st) fail(st, "zyxb_allreduce_sum");
+          if (in.tail) zyxb_comm_option(ctx, dev, ZYXB_COMM_OPT_LATENCY, 0);
+          if (st) return st;
         } else if (in.kind == Instr::REDUCE_SCATTER) {
           if ((st = zyxb_reduce_scatter_sum(ctx, dev, in.buffer, in.offset, in.count, dtype, nullptr, 0, &ev))) return fail(st, "zyxb_reduce_scatter_sum");
         } else {

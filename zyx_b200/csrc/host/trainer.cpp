@@ -17,6 +17,8 @@
 #include <string.h>
 
 #include <algorithm>
+#include <stdlib.h>
+
 #include <string>
 #include <vector>
 
@@ -42,6 +44,7 @@ struct Instr {
   uint64_t offset = 0, count = 0;          // collectives: slice of the bucket (count per rank for the sliced ones)
   int layer = -1;                          // ALLGATHER: the layer whose parameters it completes; LAUNCH: wait for that layer's gather
   int wait_collectives = 0;                // LAUNCH: wait first for this many of the oldest pending gradient-collective events (-1: all)
+  bool tail = false;                       // ALLREDUCE: nothing of the step is left to hide it behind (ZYXB_COMM_OPT_LATENCY around the call)
   int desc_kind = 0, desc_sub = 0;         // ZYXB_KIND_* and the op / layout, for profile reports
 };
 
@@ -230,6 +233,10 @@ int32_t build(zyxb_mlp* M) {
   }
   // ---- backward, last layer first ----
   std::vector<int> collectives_of_layer(n, 1);
+  // which of the first layer's collectives (the last of a step) take the communicator's low-latency path
+  // (ZYXB_COMM_OPT_LATENCY): 0 none (default - measured at 2 and 8 GPUs it shortens the last optimizer launch's wait by
+  // 0.1 - 0.25 ms and costs the matmuls as much), 1 the very last one, 2 both halves of a split first layer
+  const int tail_collectives = getenv("ZYXB_TAIL_COLLECTIVES") ? atoi(getenv("ZYXB_TAIL_COLLECTIVES")) : 0;
   for (int i = n - 1; i >= 0; --i) {
     const Linear& L = M->layers[i];
     const uint32_t dz = i == n - 1 ? M->dy : M->dact[i];
@@ -254,10 +261,12 @@ int32_t build(zyxb_mlp* M) {
       hd.u.gemm.lda = L.out_features;                       // dZ is [B, out]: a half is a column range of every row
       if ((st = push_launch(M, P, hd, {dz, in, dw_lo}))) return st;
       Instr ar; ar.kind = Instr::ALLREDUCE; ar.offset = L.bucket_offset; ar.count = half_rows * L.in_features;
+      ar.tail = tail_collectives >= 2;
       P.push_back(ar); M->n_collectives++;
       if ((st = push_launch(M, P, hd, {dz_hi, in, dw_hi}))) return st;
       if ((st = push_launch(M, P, row_desc(ZYXB_RR_COLSUM, dt, B, L.out_features), {dz, L.bias_grad}))) return st;
       ar.offset = L.bucket_offset + half_rows * L.in_features; ar.count = L.bucket_count - half_rows * L.in_features;
+      ar.tail = tail_collectives >= 1;       // the step's last collective: only optimizer launches are left beside it
       P.push_back(ar); M->n_collectives++;
       collectives_of_layer[i] = 2;
     } else {
@@ -268,6 +277,7 @@ int32_t build(zyxb_mlp* M) {
       P.push_back(rs); M->n_collectives++;
     } else if (c.world > 1 && c.bucket_per_layer) {
       Instr ar; ar.kind = Instr::ALLREDUCE; ar.offset = L.bucket_offset; ar.count = L.bucket_count;
+      ar.tail = i == 0 && n > 1 && tail_collectives >= 1;
       P.push_back(ar); M->n_collectives++;
     }
     }
@@ -355,7 +365,12 @@ int32_t run(zyxb_mlp* M, const std::vector<Instr>& plan, const zyxb_event* wait,
   for (const Instr& in : plan) {
     if (in.kind != Instr::LAUNCH) {
       zyxb_event ev{};
-      if (in.kind == Instr::ALLREDUCE) TRY(zyxb_allreduce_sum(M->ctx, M->dev, M->grad_bucket, in.offset, in.count, M->cfg.dtype, nullptr, 0, &ev));
+      if (in.kind == Instr::ALLREDUCE) {
+        if (in.tail) TRY(zyxb_comm_option(M->ctx, M->dev, ZYXB_COMM_OPT_LATENCY, 1));
+        const int32_t st_ar = zyxb_allreduce_sum(M->ctx, M->dev, M->grad_bucket, in.offset, in.count, M->cfg.dtype, nullptr, 0, &ev);
+        if (in.tail) zyxb_comm_option(M->ctx, M->dev, ZYXB_COMM_OPT_LATENCY, 0);
+        if (st_ar) { M->err = std::string("zyxb_allreduce_sum: ") + zyxb_last_error(M->ctx); return st_ar; }
+      }
       else if (in.kind == Instr::REDUCE_SCATTER) TRY(zyxb_reduce_scatter_sum(M->ctx, M->dev, M->grad_bucket, in.offset, in.count, M->cfg.dtype, nullptr, 0, &ev));
       else TRY(zyxb_allgather(M->ctx, M->dev, M->param_bucket, in.offset, in.count, M->cfg.dtype, nullptr, 0, &ev));
       if (in.kind == Instr::ALLGATHER) {
