@@ -122,6 +122,15 @@ def test_ranges_that_wrap_around_are_refused(sess):
         p.deallocate(buf)
 
 
+def test_communicator_options_are_validated(sess):
+    d = sess.device
+    d.comm_option(L.COMM_OPT_LATENCY, 1)          # a per-device setting: accepted with or without a communicator
+    d.comm_option(L.COMM_OPT_LATENCY, 0)
+    with pytest.raises(B.BackendError) as e:
+        d.comm_option(99, 1)
+    assert e.value.status_name == "IncorrectKernelArg"
+
+
 def test_one_context_drives_two_gpus():
     """`zyxb_init` without device ids opens every GPU in one context.  The shared-memory limit of the tensor-core kernels is a
     per-device attribute: the second device must get it too (a bf16 matmul, the fused attention and a convolution on device 1
