@@ -42,6 +42,7 @@ struct AttnBwdParams {
   int64_t stride_batch;         // elements between batches of the [B, T, H*D] activations
   float scale, scale_log2;
   int causal, rn, is_bf16;
+  int grid_order;               // bit 0 / bit 1: the dQ / dK-dV kernel's grid has (batch, head) in x and the tile in y
   uint32_t* status;
 };
 
@@ -115,8 +116,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t n_qt = p.T / 128;
-  const uint32_t qt = p.causal ? n_qt - 1 - blockIdx.x : blockIdx.x;       // heavy tiles first
-  const uint32_t bh = blockIdx.y, b = bh / p.heads, h = bh % p.heads;
+  const uint32_t tile_idx = p.grid_order & 1 ? blockIdx.y : blockIdx.x, bh = p.grid_order & 1 ? blockIdx.x : blockIdx.y;
+  const uint32_t qt = p.causal ? n_qt - 1 - tile_idx : tile_idx;       // heavy tiles first
+  const uint32_t b = bh / p.heads, h = bh % p.heads;
   const uint32_t n_kv = p.causal ? (qt + 1) * 2 : p.T / 64;
 
   if (threadIdx.x == 0) {
@@ -301,8 +303,8 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const uint32_t kt = blockIdx.x;                                           // key tile; early tiles are the heavy ones under a causal mask
-  const uint32_t bh = blockIdx.y, b = bh / p.heads, h = bh % p.heads;
+  const uint32_t kt = p.grid_order & 2 ? blockIdx.y : blockIdx.x;           // key tile; early tiles are the heavy ones under a causal mask
+  const uint32_t bh = p.grid_order & 2 ? blockIdx.x : blockIdx.y, b = bh / p.heads, h = bh % p.heads;
   const uint32_t i_first = p.causal ? kt * 2 : 0;                           // first 64-query tile that sees these keys
   const uint32_t n_q = p.T / 64 - i_first;
 
@@ -532,9 +534,15 @@ int launch_attention_bwd(const zyxb_attention_desc& d, void* const* args, const 
     if (e == cudaSuccess) e = ensure_dynamic_smem(attn_bwd_dkdv_kernel, dkv::SMEM_TOTAL, &configured_dkdv);
     if (e != cudaSuccess) { err = std::string("attention backward: ") + cudaGetErrorString(e); return ZYXB_ERR_KERNEL_LAUNCH; }
   }
-  const dim3 grid((unsigned)(d.seq / 128), (unsigned)(d.batch * d.heads));
-  attn_bwd_dq_kernel<<<grid, AB_THREADS, dqk::SMEM_TOTAL, lc.stream>>>(q128, do128, k64, v64, p);
-  attn_bwd_dkdv_kernel<<<grid, AB_THREADS, dkv::SMEM_TOTAL, lc.stream>>>(q64, do64, k128, v128, p);
+  // Which grid dimension carries the tile index.  CTAs start in x-major order.  With (batch, head) in x every heavy tile of
+  // the launch (under a causal mask) starts before any light one; with the tile in x the CTAs of one head run together and
+  // meet in L2.  Measured at 8 x 16 heads, seq 2048: dQ 0.794 against 0.800 ms per backward with heads in x, dK/dV 0.847
+  // against 0.800 - its CTAs re-read Q and dO of the whole head and want the locality.  (The forward kernels gain 8 % from
+  // heads in x.)  bit 0: dQ, bit 1: dK/dV; y is limited to 65535, so many heads force heads into x.
+  p.grid_order = d.batch * d.heads <= 65535 ? 1 : 3;
+  const dim3 grid_t((unsigned)(d.seq / 128), (unsigned)(d.batch * d.heads)), grid_h((unsigned)(d.batch * d.heads), (unsigned)(d.seq / 128));
+  attn_bwd_dq_kernel<<<p.grid_order & 1 ? grid_h : grid_t, AB_THREADS, dqk::SMEM_TOTAL, lc.stream>>>(q128, do128, k64, v64, p);
+  attn_bwd_dkdv_kernel<<<p.grid_order & 2 ? grid_h : grid_t, AB_THREADS, dkv::SMEM_TOTAL, lc.stream>>>(q64, do64, k128, v128, p);
   return check_launch(lc, err, "attention backward", 3);
 }
 

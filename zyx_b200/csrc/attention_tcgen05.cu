@@ -73,8 +73,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // heavy query tiles (late rows of a causal mask) are scheduled first
   const uint32_t n_qt = p.T / AT_BM;
-  const uint32_t qt = p.causal ? n_qt - 1 - blockIdx.x : blockIdx.x;
-  const uint32_t bh = blockIdx.y, b = bh / p.heads, h = bh % p.heads;
+  // x = (batch, head), y = query tile: every heavy CTA of the launch (late query rows under a causal mask) starts before any light one
+  const uint32_t qt = p.causal ? n_qt - 1 - blockIdx.y : blockIdx.y;
+  const uint32_t bh = blockIdx.x, b = bh / p.heads, h = bh % p.heads;
   const uint32_t n_kv = p.causal ? qt + 1 : p.T / AT_BN;
 
   if (threadIdx.x == 0) {
@@ -324,8 +325,9 @@ int validate_attention(const zyxb_attention_desc& d, std::string& err) {
   if (d.head_dim != AT_D) { err = "attention: head_dim must be 128"; return ZYXB_ERR_KERNEL_COMPILATION; }
   if (d.batch == 0 || d.heads == 0 || d.seq == 0) { err = "attention: batch, heads and seq must be positive"; return ZYXB_ERR_KERNEL_COMPILATION; }
   if (d.seq % AT_BM) { err = "attention: seq must be a multiple of 128"; return ZYXB_ERR_KERNEL_COMPILATION; }
-  if (d.batch * d.heads > 65535) { err = "attention: more than 65535 (batch, head) pairs"; return ZYXB_ERR_KERNEL_COMPILATION; }
-  if (d.seq > 0x7fffff00ull) { err = "attention: seq too large"; return ZYXB_ERR_KERNEL_COMPILATION; }
+  // grid: x = (batch, head) pairs, y = 128-row tiles
+  if (d.batch > 0x7fffffffull || d.heads > 0x7fffffffull || d.batch * d.heads > 0x7fffffffull) { err = "attention: too many (batch, head) pairs"; return ZYXB_ERR_KERNEL_COMPILATION; }
+  if (d.seq / AT_BM > 65535) { err = "attention: seq too large (more than 65535 tiles of 128 rows)"; return ZYXB_ERR_KERNEL_COMPILATION; }
   if (!(d.scale >= 0.0f)) { err = "attention: scale must be positive (0 = 1/sqrt(head_dim))"; return ZYXB_ERR_KERNEL_COMPILATION; }
   return ZYXB_OK;
 }
@@ -360,7 +362,7 @@ int launch_attention(const zyxb_attention_desc& d, void* const* args, const uint
     cudaError_t e = ensure_dynamic_smem(attn_fwd_kernel, AT_SMEM_TOTAL, &configured);
     if (e != cudaSuccess) { err = std::string("attention: ") + cudaGetErrorString(e); return ZYXB_ERR_KERNEL_LAUNCH; }
   }
-  const dim3 grid((unsigned)(d.seq / AT_BM), (unsigned)(d.batch * d.heads));
+  const dim3 grid((unsigned)(d.batch * d.heads), (unsigned)(d.seq / AT_BM));
   attn_fwd_kernel<<<grid, AT_THREADS, AT_SMEM_TOTAL, lc.stream>>>(mq, mk, mv, p);
   return check_launch(lc, err, "attention");
 }
