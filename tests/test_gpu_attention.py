@@ -80,6 +80,30 @@ def test_two_tile_and_one_tile_forward_agree(sess, tmp_path, causal):
     assert np.max(np.abs(lse2 - one["lse"])) <= 1e-4 * max(1.0, float(np.max(np.abs(want_lse))))
 
 
+@pytest.mark.parametrize("causal", [True, False])
+def test_persistent_forward_equals_one_cta_per_item(sess, tmp_path, causal):
+    """More work items than SMs (320 of 256 query rows each): one CTA per SM walks several items, loading the next item's
+    tiles and issuing its first products under the previous item's output stores, with every barrier phase counted across
+    items.  The arithmetic per item does not change, so the result must equal, bit for bit, the same kernel launched with one
+    CTA per item (ZYXB_ATTENTION_CTA_PER_ITEM in a child process) - the form the other tests hold against the oracle."""
+    dtype, batch, heads, seq, D = L.BF16, 10, 16, 512, 128
+    q, k, v = (rand((batch, seq, heads * D), dtype) for _ in range(3))
+    o, lse = sess.attention(dtype, q, k, v, heads, causal=causal)
+    assert sess.device.status() == 0
+    src, dst = tmp_path / "in.npz", tmp_path / "out.npz"
+    np.savez(src, q=q, k=k, v=v, dtype=dtype, heads=heads, causal=causal)
+    env = dict(os.environ, ZYXB_ATTENTION_CTA_PER_ITEM="1")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    subprocess.run([sys.executable, "-c", _CHILD, str(src), str(dst)], check=True, env=env, cwd=root, timeout=600)
+    one = np.load(dst)
+    assert np.array_equal(o, one["o"]) and np.array_equal(lse, one["lse"])
+    # and one sampled head against the oracle
+    b, h = 7, 11
+    sl = slice(h * D, (h + 1) * D)
+    want, want_lse, exact = zm.attention(dtype, q[b:b + 1, :, sl], k[b:b + 1, :, sl], v[b:b + 1, :, sl], 1, causal)
+    check(np.ascontiguousarray(o[b:b + 1, :, sl]), want, exact, dtype)
+
+
 def test_fused_attention_large_scores_and_custom_scale(sess):
     """Peaked softmax rows (scores of order 30) exercise the running-maximum rescale of the output tile."""
     dtype, batch, heads, seq, D = L.BF16, 1, 2, 512, 128
