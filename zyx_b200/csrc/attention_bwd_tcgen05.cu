@@ -76,6 +76,33 @@ __device__ __forceinline__ void store_row32(uint16_t* dst, const uint32_t (&r)[3
 #pragma unroll
   for (int q = 0; q < 4; ++q) *reinterpret_cast<uint4*>(dst + q * 8) = make_uint4(w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
 }
+// The same for a warp whose lanes hold 32 consecutive rows: a plain store would touch 32 rows per instruction, so sixteen rows
+// at a time go through a 1280-byte shared-memory stage (rows of 64 B, padded to 80) and leave as eight rows x 64 contiguous
+// bytes per store instruction - a quarter of the memory transactions.  `out_row0`: the warp's first row at this chunk's column.
+__device__ __forceinline__ void store_rows_staged(uint8_t* stage, uint16_t* out_row0, int64_t ld, const uint32_t (&r)[32], bool bf16, bool rn, int lane) {
+  uint32_t w[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const float a = __uint_as_float(r[2 * i]), c = __uint_as_float(r[2 * i + 1]);
+    const uint16_t lo = bf16 ? f32_to_bf16(a, rn) : f32_to_f16(a, rn), hi = bf16 ? f32_to_bf16(c, rn) : f32_to_f16(c, rn);
+    w[i] = (uint32_t)lo | ((uint32_t)hi << 16);
+  }
+#pragma unroll
+  for (int pass = 0; pass < 2; ++pass) {
+    if ((lane >> 4) == pass) {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) *reinterpret_cast<uint4*>(stage + (lane & 15) * 80 + q * 16) = make_uint4(w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
+    }
+    __syncwarp();
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int r16 = (lane >> 2) + 8 * i, chunk = lane & 3;
+      const uint4 val = *reinterpret_cast<const uint4*>(stage + r16 * 80 + chunk * 16);
+      *reinterpret_cast<uint4*>(out_row0 + (int64_t)(pass * 16 + r16) * ld + chunk * 8) = val;
+    }
+    __syncwarp();
+  }
+}
 // write 32 packed columns (16 words) of row `row` into a [128 x 64] K-major swizzled tile; `half` selects columns 0..31 / 32..63
 __device__ __forceinline__ void write_tile_row(uint8_t* tile, uint32_t row, int half, const uint32_t (&pk)[16]) {
   uint8_t* p_row = tile + row * 128;
@@ -256,13 +283,15 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     }
     if (ok && mbar_wait(ds_empty((n_kv - 1) & 1), ((n_kv - 1) >> 1) & 1, abort_flag, p.status, AB_ERR_EW)) {
       tc_fence_after();
-      uint16_t* out = reinterpret_cast<uint16_t*>(p.dq) + (int64_t)b * p.stride_batch + (int64_t)grow * p.ld + (int64_t)h * 128 + half * 64;
+      // every dS tile has been written and consumed: its shared memory serves as the output stage
+      uint16_t* out0 = reinterpret_cast<uint16_t*>(p.dq) + (int64_t)b * p.stride_batch + (int64_t)(qt * 128 + quarter * 32) * p.ld + (int64_t)h * 128 + half * 64;
+      uint8_t* stage = base_ptr + DS_OFF + (warp - 2) * 1280;
 #pragma unroll 1
       for (int ch = 0; ch < 2; ++ch) {
         uint32_t r[32];
         tmem_ld32(tmem_dq + lane_addr + half * 64 + ch * 32, r);
         tmem_ld_wait();
-        store_row32(out + ch * 32, r, bf16, p.rn != 0);
+        store_rows_staged(stage, out0 + ch * 32, (int64_t)p.ld, r, bf16, p.rn != 0, lane);
       }
     }
   }
@@ -472,18 +501,20 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     }
     if (ok && mbar_wait(dst_empty((n_q - 1) & 1), ((n_q - 1) >> 1) & 1, abort_flag, p.status, AB_ERR_EW)) {
       tc_fence_after();
-      const int64_t off = (int64_t)b * p.stride_batch + (int64_t)gkey * p.ld + (int64_t)h * 128 + half * 64;
+      // every dS^T tile has been written and consumed: its shared memory serves as the output stage
+      const int64_t off = (int64_t)b * p.stride_batch + (int64_t)(gkey - lane) * p.ld + (int64_t)h * 128 + half * 64;   // the warp's first row
       uint16_t* out_v = reinterpret_cast<uint16_t*>(p.dv) + off;
       uint16_t* out_k = reinterpret_cast<uint16_t*>(p.dk) + off;
+      uint8_t* stage = base_ptr + DST_OFF + (warp - 2) * 1280;
 #pragma unroll 1
       for (int ch = 0; ch < 2; ++ch) {
         uint32_t r[32];
         tmem_ld32(tmem_dv + lane_addr + half * 64 + ch * 32, r);
         tmem_ld_wait();
-        store_row32(out_v + ch * 32, r, bf16, p.rn != 0);
+        store_rows_staged(stage, out_v + ch * 32, (int64_t)p.ld, r, bf16, p.rn != 0, lane);
         tmem_ld32(tmem_dk + lane_addr + half * 64 + ch * 32, r);
         tmem_ld_wait();
-        store_row32(out_k + ch * 32, r, bf16, p.rn != 0);
+        store_rows_staged(stage, out_k + ch * 32, (int64_t)p.ld, r, bf16, p.rn != 0, lane);
       }
     }
   }
