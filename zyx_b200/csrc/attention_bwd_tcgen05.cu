@@ -64,19 +64,7 @@ __global__ void __launch_bounds__(256) attn_delta_kernel(const uint16_t* __restr
   if (lane == 0) delta[((uint64_t)b * H + h) * T + t] = acc;
 }
 
-// store 32 f32 values (one TMEM chunk of a row) as 32 16-bit values = 64 bytes
-__device__ __forceinline__ void store_row32(uint16_t* dst, const uint32_t (&r)[32], bool bf16, bool rn) {
-  uint32_t w[16];
-#pragma unroll
-  for (int i = 0; i < 16; ++i) {
-    const float a = __uint_as_float(r[2 * i]), c = __uint_as_float(r[2 * i + 1]);
-    const uint16_t lo = bf16 ? f32_to_bf16(a, rn) : f32_to_f16(a, rn), hi = bf16 ? f32_to_bf16(c, rn) : f32_to_f16(c, rn);
-    w[i] = (uint32_t)lo | ((uint32_t)hi << 16);
-  }
-#pragma unroll
-  for (int q = 0; q < 4; ++q) *reinterpret_cast<uint4*>(dst + q * 8) = make_uint4(w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
-}
-// The same for a warp whose lanes hold 32 consecutive rows: a plain store would touch 32 rows per instruction, so sixteen rows
+// 32 f32 values of a row (one TMEM chunk) leave as 32 16-bit values = 64 bytes.  The lanes of a warp hold 32 consecutive rows: a plain store would touch 32 rows per instruction, so sixteen rows
 // at a time go through a 1280-byte shared-memory stage (rows of 64 B, padded to 80) and leave as eight rows x 64 contiguous
 // bytes per store instruction - a quarter of the memory transactions.  `out_row0`: the warp's first row at this chunk's column.
 __device__ __forceinline__ void store_rows_staged(uint8_t* stage, uint16_t* out_row0, int64_t ld, const uint32_t (&r)[32], bool bf16, bool rn, int lane) {
