@@ -1,10 +1,10 @@
-// Fused self-attention forward, two query tiles per CTA (used when seq is a multiple of 256; attention_tcgen05.cu otherwise).
+// Fused self-attention forward, persistent, two query tiles per CTA (used when seq is a multiple of 256; attention_tcgen05.cu otherwise).
 //   O = softmax(scale * Q.K^T [causal mask]) . V            MultiheadAttention::forward, zyx-nn/src/multi_head_attention.rs:197-226
 //
 // What bounded the one-tile kernel was not arithmetic: with Q, two K, two V and two P tiles the shared memory was full, so the
 // K/V rings were two deep against a load latency of thousands of clocks, every K/V tile was fetched from L2 once per 128 query
 // rows, and P went through shared memory (a 32 KB write and a 32 KB operand read per tile on top of the products' own 128 KB).
-// Here one CTA owns 256 query rows (tiles a and b) of one (batch, head):
+// Here a work item is 256 query rows (tiles a and b) of one (batch, head), and one CTA per SM walks the items:
 //   - every K_j / V_j tile is loaded once and used by both query tiles: half the L2 traffic and twice the work per ring slot;
 //   - P never touches shared memory: the softmax writes it as packed 16-bit pairs over the first 64 columns of its own S tile
 //     in TMEM, and P.V takes its A operand from TMEM (tcgen05.mma with a tensor-memory A);
@@ -14,6 +14,9 @@
 // warps 4..11 softmax of tile a, warps 12..19 softmax of tile b (two threads per query row, 64 keys each, as in the one-tile
 // kernel); warps 2 and 3 only take part in the CTA-wide barriers.
 // Per tile the chain S_g(j) -> softmax_g(j) -> P_g.V(j) -> S_g(j+1) is sequential (P overwrites S); the other tile fills the gaps.
+// Items are numbered heaviest first (under a causal mask the late query rows visit the most key tiles) and dealt to the CTAs in
+// rounds walked forwards and backwards in turn; the next item's Q, K_0, V_0 and first S products are under way while the softmax
+// warps write the finished item's output (sixteen rows at a time through a shared-memory stage: coalesced stores).
 // Measured on this chain (clock stamps of one CTA): S 890 clocks from issue until the softmax warps see it (512 of them the
 // product), row maximum and its exchange 390, exponentials 1470 (the SFU alone would need 1024), store and publish 210, P.V 510.
 // Variants that lost against this one: one thread per query row (no exchange, but one warp per scheduler cannot keep the SFU
