@@ -52,7 +52,12 @@ d = np.load(sys.argv[1])
 s = ops.Session(device_ids=[0])
 o, lse = s.attention(int(d['dtype']), d['q'], d['k'], d['v'], int(d['heads']), causal=bool(d['causal']))
 assert s.device.status() == 0
-np.savez(sys.argv[2], o=o, lse=lse)
+out = dict(o=o, lse=lse)
+if 'do' in d:
+    dq, dk, dv = s.attention_bwd(int(d['dtype']), d['q'], d['k'], d['v'], o, d['do'], lse, int(d['heads']), causal=bool(d['causal']))
+    assert s.device.status() == 0
+    out.update(dq=dq, dk=dk, dv=dv)
+np.savez(sys.argv[2], **out)
 s.close()
 """
 
@@ -89,14 +94,17 @@ def test_persistent_forward_equals_one_cta_per_item(sess, tmp_path, causal):
     dtype, batch, heads, seq, D = L.BF16, 10, 16, 512, 128
     q, k, v = (rand((batch, seq, heads * D), dtype) for _ in range(3))
     o, lse = sess.attention(dtype, q, k, v, heads, causal=causal)
+    do = rand((batch, seq, heads * D), dtype)
+    dq, dk, dv = sess.attention_bwd(dtype, q, k, v, o, do, lse, heads, causal=causal)      # the dQ kernel walks 640 items the same way
     assert sess.device.status() == 0
     src, dst = tmp_path / "in.npz", tmp_path / "out.npz"
-    np.savez(src, q=q, k=k, v=v, dtype=dtype, heads=heads, causal=causal)
+    np.savez(src, q=q, k=k, v=v, do=do, dtype=dtype, heads=heads, causal=causal)
     env = dict(os.environ, ZYXB_ATTENTION_CTA_PER_ITEM="1")
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     subprocess.run([sys.executable, "-c", _CHILD, str(src), str(dst)], check=True, env=env, cwd=root, timeout=600)
     one = np.load(dst)
     assert np.array_equal(o, one["o"]) and np.array_equal(lse, one["lse"])
+    assert np.array_equal(dq, one["dq"]) and np.array_equal(dk, one["dk"]) and np.array_equal(dv, one["dv"])
     # and one sampled head against the oracle
     b, h = 7, 11
     sl = slice(h * D, (h + 1) * D)

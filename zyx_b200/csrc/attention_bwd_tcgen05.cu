@@ -42,7 +42,8 @@ struct AttnBwdParams {
   int64_t stride_batch;         // elements between batches of the [B, T, H*D] activations
   float scale, scale_log2;
   int causal, rn, is_bf16;
-  int grid_order;               // bit 0 / bit 1: the dQ / dK-dV kernel's grid has (batch, head) in x and the tile in y
+  int grid_order;               // bit 1: the dK-dV kernel's grid has (batch, head) in x and the tile in y
+  uint32_t n_bh;                // batch * heads
   uint32_t* status;
 };
 
@@ -126,18 +127,25 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   // phases of one barrier before its waiter has seen the first
   auto ds_full = [&](int b) { return bar + 8u * (5 + 2 * NS + b); };
   auto ds_empty = [&](int b) { return bar + 8u * (7 + 2 * NS + b); };
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + BAR_OFF + 8 * (9 + 2 * NS));
+  const uint32_t qdo_empty = bar + 8u * (9 + 2 * NS);                // every S / dP product of a work item has finished: Q and dO may be overwritten
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + BAR_OFF + 8 * (10 + 2 * NS));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const uint32_t n_qt = p.T / 128;
-  const uint32_t tile_idx = p.grid_order & 1 ? blockIdx.y : blockIdx.x, bh = p.grid_order & 1 ? blockIdx.x : blockIdx.y;
-  const uint32_t qt = p.causal ? n_qt - 1 - tile_idx : tile_idx;       // heavy tiles first
-  const uint32_t b = bh / p.heads, h = bh % p.heads;
-  const uint32_t n_kv = p.causal ? (qt + 1) * 2 : p.T / 64;
+  // Persistent: a work item is one (batch, head, 128-query tile); items are numbered heaviest first (late query rows visit the
+  // most key tiles under a causal mask; all (batch, head) pairs of one query tile, then the next lighter tile) and dealt to
+  // the CTAs - one per SM - in rounds walked forwards and backwards in turn.  Barriers, TMEM and tensor maps are set up once,
+  // every ring and double-buffer phase is counted in key tiles across items, and the next item's Q, dO, first K / V tiles and
+  // first S / dP products are under way while the elementwise warps write the finished item's dQ.
+  const uint32_t n_qt = p.T / 128, n_items = n_qt * p.n_bh;
+  auto nth_item = [&](uint32_t i) { return i * gridDim.x + ((i & 1) ? gridDim.x - 1 - blockIdx.x : blockIdx.x); };
+  auto item_qt = [&](uint32_t item) { const uint32_t y = item / p.n_bh; return p.causal ? n_qt - 1 - y : y; };
+  auto item_bh = [&](uint32_t item) { return item % p.n_bh; };
+  auto kv_tiles = [&](uint32_t qt) { return p.causal ? (qt + 1) * 2 : p.T / 64; };
 
   if (threadIdx.x == 0) {
     mbar_init(qdo_full, 1);
+    mbar_init(qdo_empty, 1);
     for (int s = 0; s < NS; ++s) { mbar_init(kv_full(s), 1); mbar_init(kv_empty(s), 1); }
     for (int s = 0; s < 2; ++s) { mbar_init(sdp_full(s), 1); mbar_init(sdp_empty(s), AB_EW_WARPS); }
     for (int s = 0; s < 2; ++s) { mbar_init(ds_full(s), AB_EW_WARPS); mbar_init(ds_empty(s), 1); }
@@ -154,38 +162,43 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 
   if (warp == 0) {
     if (lane == 0) {
-      mbar_expect_tx(qdo_full, 2 * AB_BIG);
-      for (int c = 0; c < 2; ++c) {
-        tma_load_4d(base + Q_OFF + c * (AB_BIG / 2), &map_q, qdo_full, c * 64, (int)(qt * 128), (int)h, (int)b);
-        tma_load_4d(base + DO_OFF + c * (AB_BIG / 2), &map_do, qdo_full, c * 64, (int)(qt * 128), (int)h, (int)b);
-      }
-      uint32_t issued = 0;
+      uint32_t t = 0, it = 0;                                 // K / V tiles and items issued so far by this CTA
       bool ok = true;
-      for (uint32_t j = 0; j < n_kv; ++j) {
-        const int s = (int)(j % NS);
-        if (!mbar_wait(kv_empty(s), ((j / NS) & 1) ^ 1, abort_flag, p.status, AB_ERR_PRODUCER)) { ok = false; break; }
-        const uint32_t k_dst = base + KV_OFF + s * STAGE, v_dst = k_dst + AB_SMALL;
-        mbar_expect_tx(kv_full(s), 2 * AB_SMALL);
+      for (uint32_t item = nth_item(0); item < n_items && ok; item = nth_item(++it)) {
+        const uint32_t qt = item_qt(item), bh = item_bh(item), b = bh / p.heads, h = bh % p.heads;
+        if (it > 0 && !mbar_wait(qdo_empty, (it - 1) & 1, abort_flag, p.status, AB_ERR_PRODUCER)) { ok = false; break; }
+        mbar_expect_tx(qdo_full, 2 * AB_BIG);
         for (int c = 0; c < 2; ++c) {
-          tma_load_4d(k_dst + c * (AB_SMALL / 2), &map_k, kv_full(s), c * 64, (int)(j * 64), (int)h, (int)b);
-          tma_load_4d(v_dst + c * (AB_SMALL / 2), &map_v, kv_full(s), c * 64, (int)(j * 64), (int)h, (int)b);
+          tma_load_4d(base + Q_OFF + c * (AB_BIG / 2), &map_q, qdo_full, c * 64, (int)(qt * 128), (int)h, (int)b);
+          tma_load_4d(base + DO_OFF + c * (AB_BIG / 2), &map_do, qdo_full, c * 64, (int)(qt * 128), (int)h, (int)b);
         }
-        ++issued;
+        const uint32_t n_kv = kv_tiles(qt);
+        for (uint32_t j = 0; j < n_kv; ++j, ++t) {
+          const int s = (int)(t % NS);
+          if (!mbar_wait(kv_empty(s), ((t / NS) & 1) ^ 1, abort_flag, p.status, AB_ERR_PRODUCER)) { ok = false; break; }
+          const uint32_t k_dst = base + KV_OFF + s * STAGE, v_dst = k_dst + AB_SMALL;
+          mbar_expect_tx(kv_full(s), 2 * AB_SMALL);
+          for (int c = 0; c < 2; ++c) {
+            tma_load_4d(k_dst + c * (AB_SMALL / 2), &map_k, kv_full(s), c * 64, (int)(j * 64), (int)h, (int)b);
+            tma_load_4d(v_dst + c * (AB_SMALL / 2), &map_v, kv_full(s), c * 64, (int)(j * 64), (int)h, (int)b);
+          }
+        }
       }
-      if (!ok) {
-        const uint64_t t0 = global_timer_ns();
-        for (uint32_t i = 0; i < NS && i < issued; ++i) {
-          const uint32_t j = issued - 1 - i;
-          while (!mbar_try_wait(kv_full(j % NS), (j / NS) & 1) && global_timer_ns() - t0 < TC_WAIT_NS) {}
+      if (!ok) {   // drain: wait (bounded) for the copies still in flight so none lands after the CTA has gone
+        const uint64_t t_start = global_timer_ns();
+        for (uint32_t i = 0; i < NS && i < t; ++i) {
+          const uint32_t j = t - 1 - i;
+          while (!mbar_try_wait(kv_full(j % NS), (j / NS) & 1) && global_timer_ns() - t_start < TC_WAIT_NS) {}
         }
-        while (!mbar_try_wait(qdo_full, 0) && global_timer_ns() - t0 < TC_WAIT_NS) {}
+        // Q / dO of the item being set up when a wait failed (item number `it`) may still be in flight
+        while (!mbar_try_wait(qdo_full, it & 1) && global_timer_ns() - t_start < 100000000ull) {}
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       const bool bf16 = p.is_bf16 != 0;
       const uint32_t idesc_s = make_idesc(bf16, false, false, 128, 64);      // [128 q x d] x [64 keys x d]^T
-      auto issue_sdp = [&](uint32_t j) {
+      auto issue_sdp = [&](uint32_t j) {      // j: key tile counted across this CTA's items
         const uint32_t k_addr = base + KV_OFF + (j % NS) * STAGE, v_addr = k_addr + AB_SMALL;
         const uint32_t t_s = tmem_base + (j & 1) * 64, t_dp = tmem_base + 128 + (j & 1) * 64;
 #pragma unroll
@@ -202,12 +215,18 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                      make_smem_desc(v_addr + c * (AB_SMALL / 2) + kk * 32, 16, 1024), idesc_s, (c | kk) != 0 ? 1u : 0u);
         umma_commit(sdp_full(j & 1));
       };
-      bool ok = mbar_wait(qdo_full, 0, abort_flag, p.status, AB_ERR_MMA);
-      for (uint32_t j = 0; j < n_kv && ok; ++j) {
-        if (!mbar_wait(kv_full(j % NS), (j / NS) & 1, abort_flag, p.status, AB_ERR_MMA)) { ok = false; break; }
-        if (!mbar_wait(sdp_empty(j & 1), ((j >> 1) & 1) ^ 1, abort_flag, p.status, AB_ERR_MMA)) { ok = false; break; }
-        tc_fence_after();
-        issue_sdp(j);
+      uint32_t t = 0, it = 0;
+      bool ok = true;
+      for (uint32_t item = nth_item(0); item < n_items && ok; item = nth_item(++it)) {
+        const uint32_t n_kv = kv_tiles(item_qt(item));
+        if (!mbar_wait(qdo_full, it & 1, abort_flag, p.status, AB_ERR_MMA)) { ok = false; break; }
+        for (uint32_t j = 0; j < n_kv && ok; ++j, ++t) {
+          if (!mbar_wait(kv_full(t % NS), (t / NS) & 1, abort_flag, p.status, AB_ERR_MMA)) { ok = false; break; }
+          if (!mbar_wait(sdp_empty(t & 1), ((t >> 1) & 1) ^ 1, abort_flag, p.status, AB_ERR_MMA)) { ok = false; break; }
+          tc_fence_after();
+          issue_sdp(t);
+        }
+        if (ok) umma_commit(qdo_empty);
       }
     }
   } else if (warp == 10) {
@@ -215,17 +234,23 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     // dQ += dS_j . K_j, while warp 1 issues the scores of the next tiles
     if (lane == 0) {
       const uint32_t idesc_dq = make_idesc(p.is_bf16 != 0, false, true, 128, 128);     // dS [128 q x 64 keys] x K_j [64 keys x d]
+      uint32_t t = 0, it = 0;
       bool ok = true;
-      for (uint32_t j = 0; j < n_kv && ok; ++j) {
-        if (!mbar_wait(ds_full(j & 1), (j >> 1) & 1, abort_flag, p.status, AB_ERR_MMA)) { ok = false; break; }
-        tc_fence_after();
-        const uint32_t k_addr = base + KV_OFF + (j % NS) * STAGE;
+      for (uint32_t item = nth_item(0); item < n_items && ok; item = nth_item(++it)) {
+        const uint32_t n_kv = kv_tiles(item_qt(item));
+        // the item's first product overwrites dQ: the elementwise warps have read the previous item's dQ before they arrive on
+        // ds_full for this item's first tile (program order in every one of them)
+        for (uint32_t j = 0; j < n_kv && ok; ++j, ++t) {
+          if (!mbar_wait(ds_full(t & 1), (t >> 1) & 1, abort_flag, p.status, AB_ERR_MMA)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t k_addr = base + KV_OFF + (t % NS) * STAGE;
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk)     // 16 keys per instruction; K_j read MN-major: rows of 128 B, the two d chunks 8 KB apart
-          umma_f16(tmem_dq, make_smem_desc(base + DS_OFF + (j & 1) * AB_PT + kk * 32, 16, 1024),
-                   make_smem_desc(k_addr + kk * (16 * 128), AB_SMALL / 2, 1024), idesc_dq, (j != 0 || kk != 0) ? 1u : 0u);
-        umma_commit(kv_empty(j % NS));
-        umma_commit(ds_empty(j & 1));
+          for (int kk = 0; kk < 4; ++kk)     // 16 keys per instruction; K_j read MN-major: rows of 128 B, the two d chunks 8 KB apart
+            umma_f16(tmem_dq, make_smem_desc(base + DS_OFF + (t & 1) * AB_PT + kk * 32, 16, 1024),
+                     make_smem_desc(k_addr + kk * (16 * 128), AB_SMALL / 2, 1024), idesc_dq, (j != 0 || kk != 0) ? 1u : 0u);
+          umma_commit(kv_empty(t % NS));
+          umma_commit(ds_empty(t & 1));
+        }
       }
     }
   } else {
@@ -234,44 +259,48 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     const uint32_t row = quarter * 32 + lane;
     const uint32_t lane_addr = (quarter * 32u) << 16;
     const bool bf16 = p.is_bf16 != 0;
-    const uint32_t grow = qt * 128 + row;
-    const float lse2 = p.lse[(uint64_t)bh * p.T + grow] * 1.4426950408889634f;
-    const float dl = p.delta[(uint64_t)bh * p.T + grow];
+    uint32_t t0 = 0;
     bool ok = true;
-    for (uint32_t j = 0; j < n_kv && ok; ++j) {
-      const uint32_t sb = j & 1;
-      if (!mbar_wait(sdp_full(sb), (j >> 1) & 1, abort_flag, p.status, AB_ERR_EW)) { ok = false; break; }
-      tc_fence_after();
-      uint32_t s[32], d[32];
-      tmem_ld32(tmem_base + lane_addr + sb * 64 + half * 32, s);
-      tmem_ld32(tmem_base + lane_addr + 128 + sb * 64 + half * 32, d);
-      tmem_ld_wait();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(sdp_empty(sb));
-      const int32_t key0 = (int32_t)(j * 64 + half * 32);
-      const bool diag = p.causal && key0 + 31 > (int32_t)grow;
-      uint32_t pk[16];
+    for (uint32_t it = 0, item = nth_item(0); item < n_items && ok; item = nth_item(++it)) {
+      const uint32_t qt = item_qt(item), bh = item_bh(item), b = bh / p.heads, h = bh % p.heads, n_kv = kv_tiles(qt);
+      const uint32_t grow = qt * 128 + row;
+      const float lse2 = p.lse[(uint64_t)bh * p.T + grow] * 1.4426950408889634f;
+      const float dl = p.delta[(uint64_t)bh * p.T + grow];
+      for (uint32_t j = 0; j < n_kv && ok; ++j) {
+        const uint32_t t = t0 + j, sb = t & 1;
+        if (!mbar_wait(sdp_full(sb), (t >> 1) & 1, abort_flag, p.status, AB_ERR_EW)) { ok = false; break; }
+        tc_fence_after();
+        uint32_t s[32], d[32];
+        tmem_ld32(tmem_base + lane_addr + sb * 64 + half * 32, s);
+        tmem_ld32(tmem_base + lane_addr + 128 + sb * 64 + half * 32, d);
+        tmem_ld_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(sdp_empty(sb));
+        const int32_t key0 = (int32_t)(j * 64 + half * 32);
+        const bool diag = p.causal && key0 + 31 > (int32_t)grow;
+        uint32_t pk[16];
 #pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        float p0 = ex2f(fmaf(__uint_as_float(s[2 * i]), p.scale_log2, -lse2));
-        float p1 = ex2f(fmaf(__uint_as_float(s[2 * i + 1]), p.scale_log2, -lse2));
-        if (diag) {
-          p0 = key0 + 2 * i > (int32_t)grow ? 0.0f : p0;
-          p1 = key0 + 2 * i + 1 > (int32_t)grow ? 0.0f : p1;
+        for (int i = 0; i < 16; ++i) {
+          float p0 = ex2f(fmaf(__uint_as_float(s[2 * i]), p.scale_log2, -lse2));
+          float p1 = ex2f(fmaf(__uint_as_float(s[2 * i + 1]), p.scale_log2, -lse2));
+          if (diag) {
+            p0 = key0 + 2 * i > (int32_t)grow ? 0.0f : p0;
+            p1 = key0 + 2 * i + 1 > (int32_t)grow ? 0.0f : p1;
+          }
+          const float g0 = p0 * (__uint_as_float(d[2 * i]) - dl) * p.scale, g1 = p1 * (__uint_as_float(d[2 * i + 1]) - dl) * p.scale;
+          pk[i] = pack2(g0, g1, bf16);
         }
-        const float g0 = p0 * (__uint_as_float(d[2 * i]) - dl) * p.scale, g1 = p1 * (__uint_as_float(d[2 * i + 1]) - dl) * p.scale;
-        pk[i] = pack2(g0, g1, bf16);
+        if (!mbar_wait(ds_empty(sb), ((t >> 1) & 1) ^ 1, abort_flag, p.status, AB_ERR_EW)) { ok = false; break; }   // read two tiles ago
+        write_tile_row(base_ptr + DS_OFF + sb * AB_PT, row, half, pk);
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(ds_full(sb));
       }
-      if (!mbar_wait(ds_empty(sb), ((j >> 1) & 1) ^ 1, abort_flag, p.status, AB_ERR_EW)) { ok = false; break; }   // read two tiles ago
-      write_tile_row(base_ptr + DS_OFF + sb * AB_PT, row, half, pk);
-      fence_proxy_async_smem();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(ds_full(sb));
-    }
-    if (ok && mbar_wait(ds_empty((n_kv - 1) & 1), ((n_kv - 1) >> 1) & 1, abort_flag, p.status, AB_ERR_EW)) {
+      const uint32_t t_last = t0 + n_kv - 1;
+      if (!ok || !mbar_wait(ds_empty(t_last & 1), (t_last >> 1) & 1, abort_flag, p.status, AB_ERR_EW)) { ok = false; break; }
       tc_fence_after();
-      // every dS tile has been written and consumed: its shared memory serves as the output stage
+      // every dS tile of the item has been written and consumed: that shared memory serves as the output stage
       uint16_t* out0 = reinterpret_cast<uint16_t*>(p.dq) + (int64_t)b * p.stride_batch + (int64_t)(qt * 128 + quarter * 32) * p.ld + (int64_t)h * 128 + half * 64;
       uint8_t* stage = base_ptr + DS_OFF + (warp - 2) * 1280;
 #pragma unroll 1
@@ -281,6 +310,10 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         tmem_ld_wait();
         store_rows_staged(stage, out0 + ch * 32, (int64_t)p.ld, r, bf16, p.rn != 0, lane);
       }
+      tc_fence_before();
+      // no warp writes the next item's dS while another still stages its output rows in that memory
+      asm volatile("bar.sync 1, %0;" ::"n"(AB_EW_WARPS * 32) : "memory");
+      t0 += n_kv;
     }
   }
   tc_fence_before();
@@ -553,14 +586,18 @@ int launch_attention_bwd(const zyxb_attention_desc& d, void* const* args, const 
     if (e == cudaSuccess) e = ensure_dynamic_smem(attn_bwd_dkdv_kernel, dkv::SMEM_TOTAL, &configured_dkdv);
     if (e != cudaSuccess) { err = std::string("attention backward: ") + cudaGetErrorString(e); return ZYXB_ERR_KERNEL_LAUNCH; }
   }
-  // Which grid dimension carries the tile index.  CTAs start in x-major order.  With (batch, head) in x every heavy tile of
-  // the launch (under a causal mask) starts before any light one; with the tile in x the CTAs of one head run together and
-  // meet in L2.  Measured at 8 x 16 heads, seq 2048: dQ 0.794 against 0.800 ms per backward with heads in x, dK/dV 0.847
-  // against 0.800 - its CTAs re-read Q and dO of the whole head and want the locality.  (The forward kernels gain 8 % from
-  // heads in x.)  bit 0: dQ, bit 1: dK/dV; y is limited to 65535, so many heads force heads into x.
-  p.grid_order = d.batch * d.heads <= 65535 ? 1 : 3;
+  // dQ: persistent, one CTA per SM over the (batch, head, query tile) items (ZYXB_ATTENTION_CTA_PER_ITEM: one CTA per item).
+  // dK/dV: one CTA per key tile with the tile in x, so that the CTAs of one head run together and meet in L2 (measured at
+  // 8 x 16 heads, seq 2048: 0.847 ms per backward with (batch, head) in x against 0.800 - its CTAs re-read Q and dO of the whole
+  // head); y is limited to 65535, so that many heads go into x.
+  p.n_bh = (uint32_t)(d.batch * d.heads);
+  p.grid_order = d.batch * d.heads <= 65535 ? 0 : 2;
+  const uint64_t n_items = (uint64_t)p.n_bh * (d.seq / 128);
+  if (n_items > 0x7fffffffull) { err = "attention backward: too many work items"; return ZYXB_ERR_INCORRECT_KERNEL_ARG; }
+  static const bool per_item = getenv("ZYXB_ATTENTION_CTA_PER_ITEM") != nullptr;
+  const unsigned grid_dq = (unsigned)(per_item ? n_items : std::min<uint64_t>(n_items, (uint64_t)lc.sm_count));
   const dim3 grid_t((unsigned)(d.seq / 128), (unsigned)(d.batch * d.heads)), grid_h((unsigned)(d.batch * d.heads), (unsigned)(d.seq / 128));
-  attn_bwd_dq_kernel<<<p.grid_order & 1 ? grid_h : grid_t, AB_THREADS, dqk::SMEM_TOTAL, lc.stream>>>(q128, do128, k64, v64, p);
+  attn_bwd_dq_kernel<<<grid_dq, AB_THREADS, dqk::SMEM_TOTAL, lc.stream>>>(q128, do128, k64, v64, p);
   attn_bwd_dkdv_kernel<<<p.grid_order & 2 ? grid_h : grid_t, AB_THREADS, dkv::SMEM_TOTAL, lc.stream>>>(q64, do64, k128, v128, p);
   return check_launch(lc, err, "attention backward", 3);
 }
