@@ -42,7 +42,6 @@ struct AttnBwdParams {
   int64_t stride_batch;         // elements between batches of the [B, T, H*D] activations
   float scale, scale_log2;
   int causal, rn, is_bf16;
-  int grid_order;               // bit 1: the dK-dV kernel's grid has (batch, head) in x and the tile in y
   uint32_t n_bh;                // batch * heads
   uint32_t* status;
 };
@@ -349,17 +348,24 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
   auto dst_full = [&](int b) { return bar + 8u * (7 + 2 * NS + b); };
   auto pt_empty = [&](int b) { return bar + 8u * (9 + 2 * NS + b); };
   auto dst_empty = [&](int b) { return bar + 8u * (11 + 2 * NS + b); };
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + BAR_OFF + 8 * (13 + 2 * NS));
+  const uint32_t kv_empty = bar + 8u * (13 + 2 * NS);                // every S^T / dP^T product of a work item has finished: K and V may be overwritten
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + BAR_OFF + 8 * (14 + 2 * NS));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const uint32_t kt = p.grid_order & 2 ? blockIdx.y : blockIdx.x;           // key tile; early tiles are the heavy ones under a causal mask
-  const uint32_t bh = p.grid_order & 2 ? blockIdx.x : blockIdx.y, b = bh / p.heads, h = bh % p.heads;
-  const uint32_t i_first = p.causal ? kt * 2 : 0;                           // first 64-query tile that sees these keys
-  const uint32_t n_q = p.T / 64 - i_first;
+  // Persistent like the dQ kernel: a work item is one (batch, head, 128-key tile), numbered head by head (item = head * tiles +
+  // key tile), so that the CTAs running at one time work on a few heads and meet in L2 on their Q and dO; one CTA per SM takes
+  // one item of every round of gridDim.x, the rounds walked forwards and backwards in turn, which also mixes heavy (early) and
+  // light (late) key tiles evenly.  Ring and double-buffer phases are counted in query tiles across items.
+  const uint32_t n_kt = p.T / 128, n_items = n_kt * p.n_bh;
+  auto nth_item = [&](uint32_t i) { return i * gridDim.x + ((i & 1) ? gridDim.x - 1 - blockIdx.x : blockIdx.x); };
+  auto item_kt = [&](uint32_t item) { return item % n_kt; };               // key tile; early tiles are the heavy ones under a causal mask
+  auto item_bh = [&](uint32_t item) { return item / n_kt; };
+  auto first_q = [&](uint32_t kt) { return p.causal ? kt * 2 : 0u; };     // first 64-query tile that sees these keys
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
+    mbar_init(kv_empty, 1);
     for (int s = 0; s < NS; ++s) { mbar_init(qdo_full(s), 1); mbar_init(qdo_empty(s), 1); }
     for (int s = 0; s < 2; ++s) { mbar_init(sdp_full(s), 1); mbar_init(sdp_empty(s), AB_EW_WARPS); }
     for (int s = 0; s < 2; ++s) {
@@ -378,38 +384,43 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
 
   if (warp == 0) {
     if (lane == 0) {
-      mbar_expect_tx(kv_full, 2 * AB_BIG);
-      for (int c = 0; c < 2; ++c) {
-        tma_load_4d(base + K_OFF + c * (AB_BIG / 2), &map_k, kv_full, c * 64, (int)(kt * 128), (int)h, (int)b);
-        tma_load_4d(base + V_OFF + c * (AB_BIG / 2), &map_v, kv_full, c * 64, (int)(kt * 128), (int)h, (int)b);
-      }
-      uint32_t issued = 0;
+      uint32_t t = 0, it = 0;                                 // Q / dO tiles and items issued so far by this CTA
       bool ok = true;
-      for (uint32_t i = 0; i < n_q; ++i) {
-        const int s = (int)(i % NS);
-        if (!mbar_wait(qdo_empty(s), ((i / NS) & 1) ^ 1, abort_flag, p.status, AB_ERR_PRODUCER)) { ok = false; break; }
-        const uint32_t q_dst = base + QDO_OFF + s * STAGE, do_dst = q_dst + AB_SMALL;
-        mbar_expect_tx(qdo_full(s), 2 * AB_SMALL);
+      for (uint32_t item = nth_item(0); item < n_items && ok; item = nth_item(++it)) {
+        const uint32_t kt = item_kt(item), bh = item_bh(item), b = bh / p.heads, h = bh % p.heads;
+        const uint32_t i_first = first_q(kt), n_q = p.T / 64 - i_first;
+        if (it > 0 && !mbar_wait(kv_empty, (it - 1) & 1, abort_flag, p.status, AB_ERR_PRODUCER)) { ok = false; break; }
+        mbar_expect_tx(kv_full, 2 * AB_BIG);
         for (int c = 0; c < 2; ++c) {
-          tma_load_4d(q_dst + c * (AB_SMALL / 2), &map_q, qdo_full(s), c * 64, (int)((i_first + i) * 64), (int)h, (int)b);
-          tma_load_4d(do_dst + c * (AB_SMALL / 2), &map_do, qdo_full(s), c * 64, (int)((i_first + i) * 64), (int)h, (int)b);
+          tma_load_4d(base + K_OFF + c * (AB_BIG / 2), &map_k, kv_full, c * 64, (int)(kt * 128), (int)h, (int)b);
+          tma_load_4d(base + V_OFF + c * (AB_BIG / 2), &map_v, kv_full, c * 64, (int)(kt * 128), (int)h, (int)b);
         }
-        ++issued;
+        for (uint32_t i = 0; i < n_q; ++i, ++t) {
+          const int s = (int)(t % NS);
+          if (!mbar_wait(qdo_empty(s), ((t / NS) & 1) ^ 1, abort_flag, p.status, AB_ERR_PRODUCER)) { ok = false; break; }
+          const uint32_t q_dst = base + QDO_OFF + s * STAGE, do_dst = q_dst + AB_SMALL;
+          mbar_expect_tx(qdo_full(s), 2 * AB_SMALL);
+          for (int c = 0; c < 2; ++c) {
+            tma_load_4d(q_dst + c * (AB_SMALL / 2), &map_q, qdo_full(s), c * 64, (int)((i_first + i) * 64), (int)h, (int)b);
+            tma_load_4d(do_dst + c * (AB_SMALL / 2), &map_do, qdo_full(s), c * 64, (int)((i_first + i) * 64), (int)h, (int)b);
+          }
+        }
       }
-      if (!ok) {
-        const uint64_t t0 = global_timer_ns();
-        for (uint32_t k = 0; k < NS && k < issued; ++k) {
-          const uint32_t i = issued - 1 - k;
-          while (!mbar_try_wait(qdo_full(i % NS), (i / NS) & 1) && global_timer_ns() - t0 < TC_WAIT_NS) {}
+      if (!ok) {   // drain: wait (bounded) for the copies still in flight so none lands after the CTA has gone
+        const uint64_t t_start = global_timer_ns();
+        for (uint32_t k = 0; k < NS && k < t; ++k) {
+          const uint32_t i = t - 1 - k;
+          while (!mbar_try_wait(qdo_full(i % NS), (i / NS) & 1) && global_timer_ns() - t_start < TC_WAIT_NS) {}
         }
-        while (!mbar_try_wait(kv_full, 0) && global_timer_ns() - t0 < TC_WAIT_NS) {}
+        // K / V of the item being set up when a wait failed (item number `it`) may still be in flight
+        while (!mbar_try_wait(kv_full, it & 1) && global_timer_ns() - t_start < 100000000ull) {}
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       const bool bf16 = p.is_bf16 != 0;
       const uint32_t idesc_st = make_idesc(bf16, false, false, 128, 64);     // [128 keys x d] x [64 q x d]^T
-      auto issue_sdp = [&](uint32_t i) {
+      auto issue_sdp = [&](uint32_t i) {      // i: query tile counted across this CTA's items
         const uint32_t q_addr = base + QDO_OFF + (i % NS) * STAGE, do_addr = q_addr + AB_SMALL;
         const uint32_t t_s = tmem_base + (i & 1) * 64, t_dp = tmem_base + 128 + (i & 1) * 64;
 #pragma unroll
@@ -426,36 +437,48 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                      make_smem_desc(do_addr + c * (AB_SMALL / 2) + kk * 32, 16, 1024), idesc_st, (c | kk) != 0 ? 1u : 0u);
         umma_commit(sdp_full(i & 1));
       };
-      bool ok = mbar_wait(kv_full, 0, abort_flag, p.status, AB_ERR_MMA);
-      for (uint32_t i = 0; i < n_q && ok; ++i) {
-        if (!mbar_wait(qdo_full(i % NS), (i / NS) & 1, abort_flag, p.status, AB_ERR_MMA)) { ok = false; break; }
-        if (!mbar_wait(sdp_empty(i & 1), ((i >> 1) & 1) ^ 1, abort_flag, p.status, AB_ERR_MMA)) { ok = false; break; }
-        tc_fence_after();
-        issue_sdp(i);
+      uint32_t t = 0, it = 0;
+      bool ok = true;
+      for (uint32_t item = nth_item(0); item < n_items && ok; item = nth_item(++it)) {
+        const uint32_t n_q = p.T / 64 - first_q(item_kt(item));
+        if (!mbar_wait(kv_full, it & 1, abort_flag, p.status, AB_ERR_MMA)) { ok = false; break; }
+        for (uint32_t i = 0; i < n_q && ok; ++i, ++t) {
+          if (!mbar_wait(qdo_full(t % NS), (t / NS) & 1, abort_flag, p.status, AB_ERR_MMA)) { ok = false; break; }
+          if (!mbar_wait(sdp_empty(t & 1), ((t >> 1) & 1) ^ 1, abort_flag, p.status, AB_ERR_MMA)) { ok = false; break; }
+          tc_fence_after();
+          issue_sdp(t);
+        }
+        if (ok) umma_commit(kv_empty);
       }
     }
   } else if (warp == 10) {
     // second MMA issuer: dV += P^T . dO_i and dK += dS^T . Q_i, while warp 1 issues the scores of the next tiles
     if (lane == 0) {
       const uint32_t idesc_acc = make_idesc(p.is_bf16 != 0, false, true, 128, 128);    // [128 keys x 64 q] x [64 q x d]
+      uint32_t t = 0, it = 0;
       bool ok = true;
-      for (uint32_t i = 0; i < n_q && ok; ++i) {
-        const uint32_t q_addr = base + QDO_OFF + (i % NS) * STAGE, do_addr = q_addr + AB_SMALL;
-        if (!mbar_wait(pt_full(i & 1), (i >> 1) & 1, abort_flag, p.status, AB_ERR_MMA)) { ok = false; break; }
-        tc_fence_after();
+      for (uint32_t item = nth_item(0); item < n_items && ok; item = nth_item(++it)) {
+        const uint32_t n_q = p.T / 64 - first_q(item_kt(item));
+        // the item's first products overwrite dV and dK: the elementwise warps have read the previous item's before they arrive
+        // on pt_full / dst_full for this item's first tile (program order in every one of them)
+        for (uint32_t i = 0; i < n_q && ok; ++i, ++t) {
+          const uint32_t q_addr = base + QDO_OFF + (t % NS) * STAGE, do_addr = q_addr + AB_SMALL;
+          if (!mbar_wait(pt_full(t & 1), (t >> 1) & 1, abort_flag, p.status, AB_ERR_MMA)) { ok = false; break; }
+          tc_fence_after();
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk)     // dV += P^T . dO_i, 16 queries per instruction, dO_i read MN-major
-          umma_f16(tmem_dv, make_smem_desc(base + PT_OFF + (i & 1) * AB_PT + kk * 32, 16, 1024),
-                   make_smem_desc(do_addr + kk * (16 * 128), AB_SMALL / 2, 1024), idesc_acc, (i != 0 || kk != 0) ? 1u : 0u);
-        umma_commit(pt_empty(i & 1));
-        if (!mbar_wait(dst_full(i & 1), (i >> 1) & 1, abort_flag, p.status, AB_ERR_MMA)) { ok = false; break; }
-        tc_fence_after();
+          for (int kk = 0; kk < 4; ++kk)     // dV += P^T . dO_i, 16 queries per instruction, dO_i read MN-major
+            umma_f16(tmem_dv, make_smem_desc(base + PT_OFF + (t & 1) * AB_PT + kk * 32, 16, 1024),
+                     make_smem_desc(do_addr + kk * (16 * 128), AB_SMALL / 2, 1024), idesc_acc, (i != 0 || kk != 0) ? 1u : 0u);
+          umma_commit(pt_empty(t & 1));
+          if (!mbar_wait(dst_full(t & 1), (t >> 1) & 1, abort_flag, p.status, AB_ERR_MMA)) { ok = false; break; }
+          tc_fence_after();
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk)     // dK += dS^T . Q_i
-          umma_f16(tmem_dk, make_smem_desc(base + DST_OFF + (i & 1) * AB_PT + kk * 32, 16, 1024),
-                   make_smem_desc(q_addr + kk * (16 * 128), AB_SMALL / 2, 1024), idesc_acc, (i != 0 || kk != 0) ? 1u : 0u);
-        umma_commit(qdo_empty(i % NS));
-        umma_commit(dst_empty(i & 1));
+          for (int kk = 0; kk < 4; ++kk)     // dK += dS^T . Q_i
+            umma_f16(tmem_dk, make_smem_desc(base + DST_OFF + (t & 1) * AB_PT + kk * 32, 16, 1024),
+                     make_smem_desc(q_addr + kk * (16 * 128), AB_SMALL / 2, 1024), idesc_acc, (i != 0 || kk != 0) ? 1u : 0u);
+          umma_commit(qdo_empty(t % NS));
+          umma_commit(dst_empty(t & 1));
+        }
       }
     }
   } else {
@@ -464,66 +487,72 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     const uint32_t row = quarter * 32 + lane;                               // key row of the tile
     const uint32_t lane_addr = (quarter * 32u) << 16;
     const bool bf16 = p.is_bf16 != 0;
-    const int32_t gkey = (int32_t)(kt * 128 + row);
-    const float* lse_bh = p.lse + (uint64_t)bh * p.T;
-    const float* delta_bh = p.delta + (uint64_t)bh * p.T;
+    uint32_t t0 = 0;
     bool ok = true;
-    for (uint32_t i = 0; i < n_q && ok; ++i) {
-      const uint32_t sb = i & 1;
-      if (!mbar_wait(sdp_full(sb), (i >> 1) & 1, abort_flag, p.status, AB_ERR_EW)) { ok = false; break; }
-      tc_fence_after();
-      uint32_t s[32], d[32];
-      tmem_ld32(tmem_base + lane_addr + sb * 64 + half * 32, s);
-      tmem_ld32(tmem_base + lane_addr + 128 + sb * 64 + half * 32, d);
-      tmem_ld_wait();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(sdp_empty(sb));
-      const int32_t q0 = (int32_t)((i_first + i) * 64 + half * 32);         // first query of this thread's 32 columns
-      const bool diag = p.causal && q0 < gkey;                              // some of them precede the key
-      uint32_t pk[16];
-      float pr[32];
+    for (uint32_t it = 0, item = nth_item(0); item < n_items && ok; item = nth_item(++it)) {
+      const uint32_t kt = item_kt(item), bh = item_bh(item), b = bh / p.heads, h = bh % p.heads;
+      const uint32_t i_first = first_q(kt), n_q = p.T / 64 - i_first;
+      const int32_t gkey = (int32_t)(kt * 128 + row);
+      const float* lse_bh = p.lse + (uint64_t)bh * p.T;
+      const float* delta_bh = p.delta + (uint64_t)bh * p.T;
+      for (uint32_t i = 0; i < n_q && ok; ++i) {
+        const uint32_t t = t0 + i, sb = t & 1;
+        if (!mbar_wait(sdp_full(sb), (t >> 1) & 1, abort_flag, p.status, AB_ERR_EW)) { ok = false; break; }
+        tc_fence_after();
+        uint32_t s[32], d[32];
+        tmem_ld32(tmem_base + lane_addr + sb * 64 + half * 32, s);
+        tmem_ld32(tmem_base + lane_addr + 128 + sb * 64 + half * 32, d);
+        tmem_ld_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(sdp_empty(sb));
+        const int32_t q0 = (int32_t)((i_first + i) * 64 + half * 32);         // first query of this thread's 32 columns
+        const bool diag = p.causal && q0 < gkey;                              // some of them precede the key
+        uint32_t pk[16];
+        float pr[32];
 #pragma unroll
-      for (int c4 = 0; c4 < 8; ++c4) {
-        const float4 l4 = __ldg(reinterpret_cast<const float4*>(lse_bh + q0) + c4);
-        const float lv[4] = {l4.x, l4.y, l4.z, l4.w};
+        for (int c4 = 0; c4 < 8; ++c4) {
+          const float4 l4 = __ldg(reinterpret_cast<const float4*>(lse_bh + q0) + c4);
+          const float lv[4] = {l4.x, l4.y, l4.z, l4.w};
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int c = c4 * 4 + e;
-          float v = ex2f(fmaf(__uint_as_float(s[c]), p.scale_log2, -lv[e] * 1.4426950408889634f));
-          if (diag) v = q0 + c < gkey ? 0.0f : v;
-          pr[c] = v;
+          for (int e = 0; e < 4; ++e) {
+            const int c = c4 * 4 + e;
+            float v = ex2f(fmaf(__uint_as_float(s[c]), p.scale_log2, -lv[e] * 1.4426950408889634f));
+            if (diag) v = q0 + c < gkey ? 0.0f : v;
+            pr[c] = v;
+          }
         }
-      }
 #pragma unroll
-      for (int i2 = 0; i2 < 16; ++i2) pk[i2] = pack2(pr[2 * i2], pr[2 * i2 + 1], bf16);
-      if (!mbar_wait(pt_empty(sb), ((i >> 1) & 1) ^ 1, abort_flag, p.status, AB_ERR_EW)) { ok = false; break; }   // read two tiles ago
-      write_tile_row(base_ptr + PT_OFF + sb * AB_PT, row, half, pk);
-      fence_proxy_async_smem();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(pt_full(sb));
+        for (int i2 = 0; i2 < 16; ++i2) pk[i2] = pack2(pr[2 * i2], pr[2 * i2 + 1], bf16);
+        if (!mbar_wait(pt_empty(sb), ((t >> 1) & 1) ^ 1, abort_flag, p.status, AB_ERR_EW)) { ok = false; break; }   // read two tiles ago
+        write_tile_row(base_ptr + PT_OFF + sb * AB_PT, row, half, pk);
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(pt_full(sb));
 #pragma unroll
-      for (int c4 = 0; c4 < 8; ++c4) {
-        const float4 d4 = __ldg(reinterpret_cast<const float4*>(delta_bh + q0) + c4);
-        const float dv4[4] = {d4.x, d4.y, d4.z, d4.w};
+        for (int c4 = 0; c4 < 8; ++c4) {
+          const float4 d4 = __ldg(reinterpret_cast<const float4*>(delta_bh + q0) + c4);
+          const float dv4[4] = {d4.x, d4.y, d4.z, d4.w};
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int c = c4 * 4 + e;
-          pr[c] = pr[c] * (__uint_as_float(d[c]) - dv4[e]) * p.scale;
+          for (int e = 0; e < 4; ++e) {
+            const int c = c4 * 4 + e;
+            pr[c] = pr[c] * (__uint_as_float(d[c]) - dv4[e]) * p.scale;
+          }
         }
-      }
 #pragma unroll
-      for (int i2 = 0; i2 < 16; ++i2) pk[i2] = pack2(pr[2 * i2], pr[2 * i2 + 1], bf16);
-      if (!mbar_wait(dst_empty(sb), ((i >> 1) & 1) ^ 1, abort_flag, p.status, AB_ERR_EW)) { ok = false; break; }
-      write_tile_row(base_ptr + DST_OFF + sb * AB_PT, row, half, pk);
-      fence_proxy_async_smem();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(dst_full(sb));
-    }
-    if (ok && mbar_wait(dst_empty((n_q - 1) & 1), ((n_q - 1) >> 1) & 1, abort_flag, p.status, AB_ERR_EW)) {
+        for (int i2 = 0; i2 < 16; ++i2) pk[i2] = pack2(pr[2 * i2], pr[2 * i2 + 1], bf16);
+        if (!mbar_wait(dst_empty(sb), ((t >> 1) & 1) ^ 1, abort_flag, p.status, AB_ERR_EW)) { ok = false; break; }
+        write_tile_row(base_ptr + DST_OFF + sb * AB_PT, row, half, pk);
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(dst_full(sb));
+      }
+      const uint32_t t_last = t0 + n_q - 1;
+      if (!ok || !mbar_wait(dst_empty(t_last & 1), (t_last >> 1) & 1, abort_flag, p.status, AB_ERR_EW)) { ok = false; break; }
       tc_fence_after();
-      // every dS^T tile has been written and consumed: its shared memory serves as the output stage
-      const int64_t off = (int64_t)b * p.stride_batch + (int64_t)(gkey - lane) * p.ld + (int64_t)h * 128 + half * 64;   // the warp's first row
+      // every dS^T tile of the item has been written and consumed (and dV's last product was issued before dK's): that
+      // shared memory serves as the output stage
+      const int64_t off = (int64_t)b * p.stride_batch + (int64_t)(gkey - (int32_t)lane) * p.ld + (int64_t)h * 128 + half * 64;   // the warp's first row
       uint16_t* out_v = reinterpret_cast<uint16_t*>(p.dv) + off;
       uint16_t* out_k = reinterpret_cast<uint16_t*>(p.dk) + off;
       uint8_t* stage = base_ptr + DST_OFF + (warp - 2) * 1280;
@@ -537,6 +566,10 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         tmem_ld_wait();
         store_rows_staged(stage, out_k + ch * 32, (int64_t)p.ld, r, bf16, p.rn != 0, lane);
       }
+      tc_fence_before();
+      // no warp writes the next item's dS^T while another still stages its output rows in that memory
+      asm volatile("bar.sync 1, %0;" ::"n"(AB_EW_WARPS * 32) : "memory");
+      t0 += n_q;
     }
   }
   tc_fence_before();
@@ -586,19 +619,17 @@ int launch_attention_bwd(const zyxb_attention_desc& d, void* const* args, const 
     if (e == cudaSuccess) e = ensure_dynamic_smem(attn_bwd_dkdv_kernel, dkv::SMEM_TOTAL, &configured_dkdv);
     if (e != cudaSuccess) { err = std::string("attention backward: ") + cudaGetErrorString(e); return ZYXB_ERR_KERNEL_LAUNCH; }
   }
-  // dQ: persistent, one CTA per SM over the (batch, head, query tile) items (ZYXB_ATTENTION_CTA_PER_ITEM: one CTA per item).
-  // dK/dV: one CTA per key tile with the tile in x, so that the CTAs of one head run together and meet in L2 (measured at
-  // 8 x 16 heads, seq 2048: 0.847 ms per backward with (batch, head) in x against 0.800 - its CTAs re-read Q and dO of the whole
-  // head); y is limited to 65535, so that many heads go into x.
+  // Both kernels are persistent: one CTA per SM walks the (batch, head, tile) items (ZYXB_ATTENTION_CTA_PER_ITEM: one CTA per
+  // item).  dQ numbers its items heaviest query tile first; dK/dV head by head, so that the CTAs running at one time meet in
+  // L2 on the Q and dO of a few heads (with one CTA per key tile, heads in the slow grid dimension measured 0.800 ms per
+  // backward against 0.847 with heads in the fast one).
   p.n_bh = (uint32_t)(d.batch * d.heads);
-  p.grid_order = d.batch * d.heads <= 65535 ? 0 : 2;
   const uint64_t n_items = (uint64_t)p.n_bh * (d.seq / 128);
   if (n_items > 0x7fffffffull) { err = "attention backward: too many work items"; return ZYXB_ERR_INCORRECT_KERNEL_ARG; }
   static const bool per_item = getenv("ZYXB_ATTENTION_CTA_PER_ITEM") != nullptr;
   const unsigned grid_dq = (unsigned)(per_item ? n_items : std::min<uint64_t>(n_items, (uint64_t)lc.sm_count));
-  const dim3 grid_t((unsigned)(d.seq / 128), (unsigned)(d.batch * d.heads)), grid_h((unsigned)(d.batch * d.heads), (unsigned)(d.seq / 128));
   attn_bwd_dq_kernel<<<grid_dq, AB_THREADS, dqk::SMEM_TOTAL, lc.stream>>>(q128, do128, k64, v64, p);
-  attn_bwd_dkdv_kernel<<<p.grid_order & 2 ? grid_h : grid_t, AB_THREADS, dkv::SMEM_TOTAL, lc.stream>>>(q64, do64, k128, v128, p);
+  attn_bwd_dkdv_kernel<<<grid_dq, AB_THREADS, dkv::SMEM_TOTAL, lc.stream>>>(q64, do64, k128, v128, p);
   return check_launch(lc, err, "attention backward", 3);
 }
 
