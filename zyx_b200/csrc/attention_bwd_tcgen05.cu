@@ -7,10 +7,11 @@
 //
 // Three launches:
 //   attn_delta_kernel      delta [B*H, T] f32
-//   attn_bwd_dq_kernel     one CTA per 128-query tile: loops over key tiles of 64; S and dP in TMEM (lane = query),
+//   attn_bwd_dq_kernel     work item = one 128-query tile: loops over key tiles of 64; S and dP in TMEM (lane = query),
 //                          dS to shared memory as the A operand of dQ += dS.K_j
-//   attn_bwd_dkdv_kernel   one CTA per 128-key tile: loops over query tiles of 64; S^T = K.Q^T and dP^T = V.dO^T in TMEM
+//   attn_bwd_dkdv_kernel   work item = one 128-key tile: loops over query tiles of 64; S^T = K.Q^T and dP^T = V.dO^T in TMEM
 //                          (lane = key), P^T and dS^T to shared memory as the A operands of dV += P^T.dO_i, dK += dS^T.Q_i
+// Both tensor-core kernels are persistent: one CTA per SM walks the work items (see the comments at their heads).
 // Each kernel recomputes S and dP (7 tensor-core products per tile pair instead of 5) so that no accumulator is shared
 // between CTAs: no atomics, no reduction pass, bit-reproducible results.
 // One shared-memory image of a [rows, 128] tile (two 128-byte-swizzled boxes of 64 columns) serves both as a K-major
