@@ -184,14 +184,19 @@ int32_t  zyxb_mgraph_class_info(zyxb_mgraph* g, uint32_t cls, int32_t* out_dtype
 
 /* One recognised subgraph: what to hand to zyxb_program_create, and the classes whose buffers are the launch arguments
  * (inputs then outputs, the order Device::launch receives, backend/mod.rs:974).  Patterns: matmul_nn / matmul_nt
- * [_batched][_bias[_relu|_gelu]], softmax, ln_softmax, layernorm, sum, max, mean, sgd, adamw, adamw_first_step.  An optimizer
- * match covers every parameter of the update (inputs p.., g.. [, m.., v..]; outputs p', m', v' per tensor - the kernel updates
- * in place, so the shim binds each output to its input's buffer); its desc.u.optim.numel points into the graph mirror. */
+ * [_batched][_bias[_relu|_gelu]], attention, softmax, ln_softmax, layernorm, mse_loss, sum, max, mean, sgd, sgd_momentum,
+ * sgd_nesterov, adamw, adamw_first_step.  An optimizer match covers every parameter of the update (inputs p.., g.. [, m.., v.. |
+ * , buf..]; outputs p' [, m', v' | , buf'] per tensor - the kernel updates in place, so the shim binds each output to its
+ * input's buffer); its desc.u.optim.numel points into the graph mirror.  optim_step is the step t the matched update belongs to
+ * (1 = the first: no state is read; for AdamW read back from the bias-correction constants, 2 for an SGD update that reads its
+ * momentum buffer): the caller sets the program's counter to t - 1 (zyxb_program_set_step) before the launch.  0 for the
+ * other patterns.  The attention program takes one more buffer behind its output, the log-sum-exp [batch*heads, seq] f32. */
 typedef struct {
   char     pattern[32];
   int32_t  n_inputs, n_outputs;
   uint32_t inputs[128], outputs[96];
   zyxb_kernel_desc desc;
+  uint64_t optim_step;
 } zyxb_match;
 /* match_graph over every class the `outputs` depend on.  Classes in `outputs` are the ones other consumers read: a new
  * parameter value is only matched as an optimizer update when it is one of them, and a GELU layer's pre-activation listed

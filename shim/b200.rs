@@ -114,6 +114,7 @@ pub(super) struct Api {
     program_create: unsafe extern "C" fn(Ctx, i32, *const ZyxbKernelDesc, *mut u32) -> i32,
     launch: unsafe extern "C" fn(Ctx, i32, u32, *const u32, i32, *const ZyxbEvent, i32, *mut ZyxbEvent) -> i32,
     program_release: unsafe extern "C" fn(Ctx, i32, u32) -> i32,
+    program_set_step: unsafe extern "C" fn(Ctx, i32, u32, u64) -> i32,
 }
 
 impl Api {
@@ -127,7 +128,7 @@ impl Api {
             d2h: sym!(b"zyxb_d2h\0"), d2d: sym!(b"zyxb_d2d\0"), buffer_bytes: sym!(b"zyxb_buffer_bytes\0"), sync: sym!(b"zyxb_sync\0"),
             release_events: sym!(b"zyxb_release_events\0"), store_variable: sym!(b"zyxb_store_variable\0"),
             get_variable: sym!(b"zyxb_get_variable\0"), program_create: sym!(b"zyxb_program_create\0"), launch: sym!(b"zyxb_launch\0"),
-            program_release: sym!(b"zyxb_program_release\0"),
+            program_release: sym!(b"zyxb_program_release\0"), program_set_step: sym!(b"zyxb_program_set_step\0"),
             _lib: lib,
         })
     }
@@ -439,6 +440,10 @@ impl B200Device {
             let st = unsafe { (self.sh.api.program_create)(self.sh.ctx, self.dev, &desc, &mut handle) };
             if st != 0 {
                 continue;       // a shape the library refuses stays with whatever else can produce the class
+            }
+            if m.optim_step > 0 {
+                // an optimizer program's own counter says whether state is read and which bias correction applies
+                unsafe { (self.sh.api.program_set_step)(self.sh.ctx, self.dev, handle, m.optim_step - 1) };
             }
             let program = self.programs.push(handle);
             let nid = graph.nodes.push(NodeData {

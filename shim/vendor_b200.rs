@@ -26,6 +26,8 @@ pub(crate) struct B200Match {
     pub(crate) desc: ZyxbKernelDesc,
     /// optimizer programs: element counts per tensor (desc.u.optim.numel is pointed here by the caller)
     pub(crate) numel: Vec<u64>,
+    /// optimizer programs: the step t the matched update belongs to (1 = the first); the program's counter must be t - 1 before the launch
+    pub(crate) optim_step: u64,
 }
 
 #[derive(Clone, Copy)]
@@ -33,7 +35,8 @@ struct MatMulX { a: ClassId, b: ClassId, m: Dim, n: Dim, k: Dim, batch: Dim, tra
 
 #[derive(Clone, Copy)]
 struct Update { algo: i32, p: ClassId, g: ClassId, m: Option<ClassId>, v: Option<ClassId>, p_new: ClassId, m_new: Option<ClassId>,
-                v_new: Option<ClassId>, lr: f64, wd: f64, b1: f64, b2: f64, eps: f64, bc1: f64, bc2: f64, first: bool }
+                v_new: Option<ClassId>, lr: f64, wd: f64, b1: f64, b2: f64, eps: f64, bc1: f64, bc2: f64, first: bool,
+                mom: f64, damp: f64, nesterov: bool }      // SGD with momentum: m / m_new are the buffer
 
 const RR_SUM: i32 = 0; const RR_MAX: i32 = 1; const RR_MEAN: i32 = 3; const RR_SOFTMAX: i32 = 6; const RR_LN_SOFTMAX: i32 = 7; const RR_LAYERNORM: i32 = 8; const RR_MSE: i32 = 14;
 const EPI_NONE: i32 = 0; const EPI_BIAS: i32 = 1; const EPI_BIAS_RELU: i32 = 2; const EPI_BIAS_GELU: i32 = 3;
@@ -223,7 +226,7 @@ impl Graph {
         inputs.extend(bias);
         let mut outputs = vec![cid];
         if preact { outputs.push(e); }
-        Some(B200Match { pattern: "matmul", inputs, outputs, desc: ZyxbKernelDesc { kind: ZYXB_KIND_GEMM, u: ZyxbDescUnion { gemm } }, numel: Vec::new() })
+        Some(B200Match { pattern: "matmul", inputs, outputs, desc: ZyxbKernelDesc { kind: ZYXB_KIND_GEMM, u: ZyxbDescUnion { gemm } }, numel: Vec::new(), optim_step: 0 })
     }
 
     // ---- row kernels ---------------------------------------------------------------------------------------------------------
@@ -234,7 +237,7 @@ impl Graph {
             .then(|| ZyxbRowreduceDesc { op, dtype: self.dtype(x) as i32, rows: s.iter().product::<Dim>() / cols, cols, correction: 1, ..Default::default() })
     }
     fn row_match(&self, pattern: &'static str, rowreduce: ZyxbRowreduceDesc, inputs: Vec<ClassId>, out: ClassId) -> B200Match {
-        B200Match { pattern, inputs, outputs: vec![out], desc: ZyxbKernelDesc { kind: ZYXB_KIND_ROWREDUCE, u: ZyxbDescUnion { rowreduce } }, numel: Vec::new() }
+        B200Match { pattern, inputs, outputs: vec![out], desc: ZyxbKernelDesc { kind: ZYXB_KIND_ROWREDUCE, u: ZyxbDescUnion { rowreduce } }, numel: Vec::new(), optim_step: 0 }
     }
     fn keepdim_src(&self, c: ClassId) -> ClassId { self.expand_of(c).unwrap_or(c) }
     /// c = uop(x - Expand{max_keepdim(x)}) -> x
@@ -279,7 +282,7 @@ impl Graph {
         let attention = ZyxbAttentionDesc { dtype: dt as i32, batch: b as u64, heads: h as u64, seq: t as u64, head_dim: d as u64, ld: 0, scale, causal: 0 };
         // the launch takes one more buffer behind the output: the log-sum-exp [b*h, t] f32 the backward program reads
         Some(B200Match { pattern: "attention", inputs: vec![xq, xk, xv], outputs: vec![cid],
-                         desc: ZyxbKernelDesc { kind: ZYXB_KIND_ATTENTION, u: ZyxbDescUnion { attention } }, numel: Vec::new() })
+                         desc: ZyxbKernelDesc { kind: ZYXB_KIND_ATTENTION, u: ZyxbDescUnion { attention } }, numel: Vec::new(), optim_step: 0 })
     }
 
     /// softmax (tensor/mod.rs:1457-1461)
@@ -361,11 +364,53 @@ impl Graph {
 
     // ---- optimizer updates -------------------------------------------------------------------------------------------------
     /// p' = (p - g * lr).cast(p.dtype) (zyx-optim/src/sgd.rs:79-82)
+    /// x + y * const with y the class `of` (or, of == None, any tensor of the shape of `like`) -> (x, y, const)
+    fn plus_scaled(&self, e: ClassId, of: Option<ClassId>, like: ClassId) -> Option<(ClassId, ClassId, f64)> {
+        let (a, b) = self.binary_of(e, BOp::Add)?;
+        for (lhs, rhs) in [(a, b), (b, a)] {
+            if let Some((y, k)) = self.binary_const(rhs, BOp::Mul) {
+                let hit = match of { Some(o) => self.same(y, o), None => self.const_shape(y) == self.const_shape(like) };
+                if hit { return Some((lhs, y, k)); }
+            }
+        }
+        None
+    }
+    /// G = g [+ p * weight_decay] -> (g, weight_decay)
+    fn strip_decay(&self, big_g: ClassId, p: ClassId) -> (ClassId, f64) {
+        match self.plus_scaled(big_g, Some(p), p) { Some((g, _, wd)) => (g, wd), None => (big_g, 0.0) }
+    }
+    /// buf' = buf * momentum + G * (1 - dampening), buf a stored tensor -> (buf, momentum, dampening, G)
+    fn buffer_update(&self, b: ClassId, p: ClassId) -> Option<(ClassId, f64, f64, ClassId)> {
+        let (old, fresh) = self.binary_of(b, BOp::Add)?;
+        let (buf, mom) = self.binary_const(old, BOp::Mul)?;
+        let (big_g, one_minus) = self.binary_const(fresh, BOp::Mul)?;
+        (self.is_leaf(buf) && !self.same(buf, p) && self.const_shape(buf) == self.const_shape(p)).then_some((buf, mom, 1.0 - one_minus, big_g))
+    }
+    /// SGD::update (zyx-optim/src/sgd.rs:58-82, without maximize): plain, with weight decay, with momentum after the first step
+    /// (p' = p - buf' * lr) and with Nesterov (p' = p - (G + buf' * momentum) * lr).  On the first step the reference stores G
+    /// itself as the buffer, so that update is the plain form.
     fn match_sgd(&self, cid: ClassId) -> Option<Update> {
         let (p, step) = self.binary_of(self.canon(cid), BOp::Sub)?;
-        let (g, lr) = self.binary_const(step, BOp::Mul)?;
-        (self.is_leaf(p) && self.const_shape(g) == self.const_shape(p)).then_some(Update {
-            algo: OPT_SGD, p, g, m: None, v: None, p_new: cid, m_new: None, v_new: None, lr, wd: 0.0, b1: 0.0, b2: 0.0, eps: 0.0, bc1: 0.0, bc2: 0.0, first: false })
+        let (x, lr) = self.binary_const(step, BOp::Mul)?;
+        if !self.is_leaf(p) || self.const_shape(x) != self.const_shape(p) { return None; }
+        let base = Update { algo: OPT_SGD, p, g: x, m: None, v: None, p_new: cid, m_new: None, v_new: None, lr, wd: 0.0, b1: 0.0, b2: 0.0, eps: 0.0,
+                            bc1: 0.0, bc2: 0.0, first: false, mom: 0.0, damp: 0.0, nesterov: false };
+        if let Some((big_g, bnew, k)) = self.plus_scaled(x, None, p) {
+            if !self.is_leaf(bnew) {
+                if let Some((buf, mom, damp, g_in)) = self.buffer_update(bnew, p) {
+                    let ((g, wd), (g2, wd2)) = (self.strip_decay(g_in, p), self.strip_decay(big_g, p));
+                    if (k - mom).abs() <= 1e-12 * mom.abs() && self.same(g, g2) && wd == wd2 {
+                        return Some(Update { g, wd, m: Some(buf), m_new: Some(bnew), mom, damp, nesterov: true, ..base });
+                    }
+                }
+            }
+        }
+        if let Some((buf, mom, damp, g_in)) = self.buffer_update(x, p) {
+            let (g, wd) = self.strip_decay(g_in, p);
+            return Some(Update { g, wd, m: Some(buf), m_new: Some(x), mom, damp, ..base });
+        }
+        let (g, wd) = self.strip_decay(x, p);
+        Some(Update { g, wd, ..base })
     }
     /// AdamW::update for one parameter (zyx-optim/src/adamw.rs:58-95)
     fn match_adamw(&self, cid: ClassId) -> Option<Update> {
@@ -416,7 +461,8 @@ impl Graph {
             if used[i] { continue; }
             let h = updates[i];
             let same_group = |u: &Update| u.algo == h.algo && self.dtype(u.p) == self.dtype(h.p) && u.first == h.first
-                && (u.lr, u.wd, u.b1, u.b2, u.eps, u.bc1, u.bc2) == (h.lr, h.wd, h.b1, h.b2, h.eps, h.bc1, h.bc2);
+                && (u.lr, u.wd, u.b1, u.b2, u.eps, u.bc1, u.bc2) == (h.lr, h.wd, h.b1, h.b2, h.eps, h.bc1, h.bc2)
+                && (u.mom, u.damp, u.nesterov, u.m.is_some()) == (h.mom, h.damp, h.nesterov, h.m.is_some());
             let (mut p, mut g, mut ms, mut vs, mut outs, mut numel) = (vec![], vec![], vec![], vec![], vec![], vec![]);
             for j in i..updates.len() {
                 let u = updates[j];
@@ -425,14 +471,21 @@ impl Graph {
                 p.push(u.p); g.push(u.g); numel.push(self.numel_of(u.p).unwrap_or(0));
                 outs.push(u.p_new);
                 if u.algo != OPT_SGD { ms.extend(u.m); vs.extend(u.v); outs.extend(u.m_new); outs.extend(u.v_new); }
+                else if u.m.is_some() { ms.extend(u.m); outs.extend(u.m_new); }          // SGD: the momentum buffer
             }
             let optim = ZyxbOptimDesc { algo: h.algo, dtype: self.dtype(h.p) as i32, n_tensors: p.len() as i32, numel: std::ptr::null(), lr: h.lr as f32,
-                                        weight_decay: h.wd as f32, momentum: 0.0, dampening: 0.0, nesterov: 0, maximize: 0, beta1: h.b1 as f32,
+                                        weight_decay: h.wd as f32, momentum: h.mom as f32, dampening: h.damp as f32, nesterov: h.nesterov as i32, maximize: 0, beta1: h.b1 as f32,
                                         beta2: h.b2 as f32, eps: h.eps as f32, grad_scale: 0.0, standard: 0 };
             let mut inputs = p;
             inputs.extend(g); inputs.extend(ms); inputs.extend(vs);
-            out.push(B200Match { pattern: if h.algo == OPT_SGD { "sgd" } else { "adamw" }, inputs, outputs: outs,
-                                 desc: ZyxbKernelDesc { kind: ZYXB_KIND_OPTIM, u: ZyxbDescUnion { optim } }, numel });
+            let sgd_buf = h.algo == OPT_SGD && h.m.is_some();
+            let pattern = if h.algo != OPT_SGD { if h.first { "adamw_first_step" } else { "adamw" } }
+                          else if !sgd_buf { "sgd" } else if h.nesterov { "sgd_nesterov" } else { "sgd_momentum" };
+            // the step the update belongs to: AdamW's bias correction divides by 1 - beta1^t
+            let optim_step = if h.algo == OPT_SGD { if sgd_buf { 2 } else { 1 } }
+                             else if h.first { 1 } else { ((1.0 - h.bc1).ln() / h.b1.ln()).round().max(2.0) as u64 };
+            out.push(B200Match { pattern, inputs, outputs: outs,
+                                 desc: ZyxbKernelDesc { kind: ZYXB_KIND_OPTIM, u: ZyxbDescUnion { optim } }, numel, optim_step });
         }
         out
     }

@@ -266,3 +266,50 @@ def test_mse_loss_is_the_two_stage_loss_program(g):
     # 16-bit tensors: the reference's loss is a scalar of the tensor's dtype, the program's an f32 one - left to the generic path
     yb, tb = T.leaf(g, L.BF16, (96, 40)), T.leaf(g, L.BF16, (96, 40))
     assert "mse_loss" not in by_pattern(g.match([yb.mse_loss(tb).cls]))
+
+
+@pytest.mark.parametrize("nesterov", [False, True])
+@pytest.mark.parametrize("weight_decay", [0.0, 0.01])
+def test_sgd_with_momentum_is_one_program_that_reads_and_writes_the_buffers(g, nesterov, weight_decay):
+    """SGD::update with weight decay, momentum, dampening and Nesterov (sgd.rs:58-80) after the first step: one multi-tensor
+    program over (p, g, buf) that writes p' and buf'; the match says which step it is, so that the program reads the buffers."""
+    shapes = [(64, 32), (64,)]
+    params = [T.leaf(g, L.F32, s) for s in shapes]
+    grads = [T.leaf(g, L.F32, s) for s in shapes]
+    bufs = [T.leaf(g, L.F32, s) for s in shapes]
+    new_p, new_b = sgd_update(params, grads, 0.05, weight_decay=weight_decay, momentum=0.9, dampening=0.1, nesterov=nesterov, bufs=bufs)
+    ms = g.match([t.cls for t in new_p] + [t.cls for t in new_b])
+    assert [m.pattern for m in ms] == [b"sgd_nesterov" if nesterov else b"sgd_momentum"]
+    m = ms[0]
+    o = m.desc.u.optim
+    assert (o.algo, o.dtype, o.n_tensors, o.nesterov) == (L.OPT_SGD, L.F32, 2, int(nesterov))
+    for got, want in ((o.lr, 0.05), (o.momentum, 0.9), (o.dampening, 0.1), (o.weight_decay, weight_decay)):
+        assert abs(got - want) < 1e-6
+    assert [o.numel[i] for i in range(2)] == [64 * 32, 64]
+    assert m.optim_step == 2
+    assert list(m.inputs[:m.n_inputs]) == [t.cls for t in params] + [t.cls for t in grads] + [t.cls for t in bufs]
+    assert list(m.outputs[:m.n_outputs]) == [new_p[0].cls, new_b[0].cls, new_p[1].cls, new_b[1].cls]
+
+
+def test_first_sgd_step_with_momentum_is_the_plain_update(g):
+    """On the first step the reference keeps the gradient itself as the momentum buffer: no node is added, the update is the
+    plain one (with its weight decay) and the buffer's class is the decayed gradient's."""
+    p, gr = T.leaf(g, L.F32, (30, 20)), T.leaf(g, L.F32, (30, 20))
+    new_p, new_b = sgd_update([p], [gr], 0.1, weight_decay=0.02, momentum=0.9, bufs=None)
+    ms = [m for m in g.match([new_p[0].cls]) if m.pattern.startswith(b"sgd")]
+    assert [m.pattern for m in ms] == [b"sgd"]
+    o = ms[0].desc.u.optim
+    assert abs(o.weight_decay - 0.02) < 1e-7 and o.momentum == 0.0 and ms[0].optim_step == 1
+    assert list(ms[0].inputs[:2]) == [p.cls, gr.cls]
+
+
+def test_adamw_match_names_its_step(g):
+    shapes = [(16, 8)]
+    for step in (1, 2, 7, 40):
+        params = [T.leaf(g, L.F32, s) for s in shapes]
+        grads = [T.leaf(g, L.F32, s) for s in shapes]
+        m = [T.leaf(g, L.F32, s) for s in shapes] if step > 1 else None
+        v = [T.leaf(g, L.F32, s) for s in shapes] if step > 1 else None
+        new_p, new_m, new_v = adamw_update(params, grads, m, v, step)
+        ms = g.match([t.cls for t in new_p + new_m + new_v])
+        assert [x.optim_step for x in ms if x.pattern.startswith(b"adamw")] == [step]

@@ -206,8 +206,20 @@ class LayerNorm:
         return out
 
 
-def sgd_update(params, grads, lr):
-    return [(p - g * lr).cast(p.dtype) for p, g in zip(params, grads)]
+def sgd_update(params, grads, lr, weight_decay=0.0, momentum=0.0, dampening=0.0, nesterov=False, bufs=None):
+    """SGD::update (zyx-optim/src/sgd.rs:45-84) without `maximize`.  bufs: the momentum buffers of the earlier steps, or None on
+    the first step, when the reference stores the (decayed) gradient itself as the buffer.  -> new params, or (new params, new bufs)
+    when momentum != 0."""
+    new_p, new_b = [], []
+    for i, (p, g) in enumerate(zip(params, grads)):
+        if weight_decay != 0.0:
+            g = g + p * weight_decay
+        if momentum != 0.0:
+            b = bufs[i] * momentum + g * (1.0 - dampening) if bufs is not None else g
+            new_b.append(b)
+            g = g + b * momentum if nesterov else b
+        new_p.append((p - g * lr).cast(p.dtype))
+    return (new_p, new_b) if momentum != 0.0 else new_p
 
 
 def adamw_update(params, grads, m, v, t, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01):

@@ -117,6 +117,7 @@ int32_t zyxb_mgraph_match(zyxb_mgraph* G, const uint32_t* outputs, int32_t n_out
     for (size_t j = 0; j < m.outputs.size(); ++j) o.outputs[j] = m.outputs[j];
     o.desc = m.desc;
     if (o.desc.kind == ZYXB_KIND_OPTIM) o.desc.u.optim.numel = m.numel.data();   // owned by the graph mirror until it is destroyed
+    o.optim_step = m.optim_step;
   }
   return ZYXB_OK;
 }

@@ -23,6 +23,8 @@
 
 #include <algorithm>
 #include <map>
+#include <cmath>
+#include <tuple>
 #include <optional>
 #include <set>
 #include <string>
@@ -67,6 +69,7 @@ struct Match {
   std::vector<ClassId> inputs, outputs;   // launch arguments: loads, then stores (Device::launch, backend/mod.rs:974)
   zyxb_kernel_desc desc{};
   std::vector<uint64_t> numel;            // optimizer: desc.u.optim.numel points here
+  uint64_t optim_step = 0;                // optimizer: the step t of the matched update (the program's counter must be t - 1 before the launch)
 };
 
 inline bool is_float(int dt) { return dt == ZYXB_F32 || dt == ZYXB_BF16 || dt == ZYXB_F16 || dt == ZYXB_F64; }
@@ -580,9 +583,17 @@ class Graph {
   }
 
   // ---- optimizer updates -------------------------------------------------------------------------------------------------
-  struct Update { int algo; ClassId p, g, m = NONE, v = NONE, p_new, m_new = NONE, v_new = NONE; double lr, wd = 0, b1 = 0, b2 = 0, eps = 0, bc1 = 0, bc2 = 0; bool first = false; };
+  struct Update {
+    int algo; ClassId p, g, m = NONE, v = NONE, p_new, m_new = NONE, v_new = NONE;     // SGD with momentum: m is the buffer
+    double lr, wd = 0, b1 = 0, b2 = 0, eps = 0, bc1 = 0, bc2 = 0, mom = 0, damp = 0;
+    bool first = false, nesterov = false;
+  };
 
   // p' = (p - g * lr).cast(p.dtype)   (sgd.rs:79-82, no weight decay, no momentum)
+  //   G = g [+ p * weight_decay]
+  //   momentum, after the first step:  buf' = buf * momentum + G * (1 - dampening);  p' = (p - buf' * lr)            (sgd.rs:63-75)
+  //   nesterov:                                                                       p' = (p - (G + buf' * momentum) * lr)
+  // On the first step the reference stores G itself as the buffer (no node is added), so that update is the plain form.
   std::optional<Update> match_sgd(ClassId cid) const {
     const ClassId c = canon(cid);
     auto sub = binary(c, B_SUB);
@@ -590,6 +601,41 @@ class Graph {
     auto step = binary_const(sub->second, B_MUL);
     if (!step || !is_leaf(sub->first) || shape(step->first) != shape(sub->first)) return std::nullopt;
     Update u{}; u.algo = ZYXB_OPT_SGD; u.p = sub->first; u.g = step->first; u.p_new = cid; u.lr = step->second;
+    // x + y * const with y the class `of` (or, of == NONE, any stored tensor of the parameter's shape)
+    auto plus_scaled = [&](ClassId e, ClassId of) -> std::optional<std::tuple<ClassId, ClassId, double>> {
+      auto add = binary(e, B_ADD);
+      if (!add) return std::nullopt;
+      for (int swap = 0; swap < 2; ++swap) {
+        const ClassId lhs = swap ? add->second : add->first, rhs = swap ? add->first : add->second;
+        auto k = binary_const(rhs, B_MUL);
+        if (k && (of == NONE ? shape(k->first) == shape(u.p) : same(k->first, of))) return std::make_tuple(lhs, k->first, k->second);
+      }
+      return std::nullopt;
+    };
+    auto strip_decay = [&](ClassId G) { if (auto d = plus_scaled(G, u.p)) { u.wd = std::get<2>(*d); return std::get<0>(*d); } return G; };
+    // buf' = buf * momentum + G * (1 - dampening), buf a stored tensor
+    auto buffer_update = [&](ClassId b) -> bool {
+      auto add = binary(b, B_ADD);
+      if (!add) return false;
+      auto old = binary_const(add->first, B_MUL), fresh = binary_const(add->second, B_MUL);
+      if (!old || !fresh || !is_leaf(old->first) || same(old->first, u.p) || shape(old->first) != shape(u.p)) return false;
+      u.m = old->first; u.mom = old->second; u.damp = 1.0 - fresh->second; u.m_new = b; u.g = strip_decay(fresh->first);
+      return true;
+    };
+    const ClassId x = step->first;
+    if (auto nes = plus_scaled(x, NONE)) {                     // G + buf' * momentum ?
+      const Update keep = u;
+      if (!is_leaf(std::get<1>(*nes)) && buffer_update(std::get<1>(*nes)) && fabs(std::get<2>(*nes) - u.mom) <= 1e-12 * fabs(u.mom)) {
+        double wd2 = 0;
+        const ClassId G = std::get<0>(*nes);
+        ClassId g_plain = G;
+        if (auto d = plus_scaled(G, u.p)) { g_plain = std::get<0>(*d); wd2 = std::get<2>(*d); }
+        if (same(g_plain, u.g) && wd2 == u.wd) { u.nesterov = true; return u; }
+      }
+      u = keep;
+    }
+    if (buffer_update(x)) return u;
+    u.g = strip_decay(x);
     return u;
   }
   bool is_leaf(ClassId c) const { return find(c, [](const Node& n) { return n.kind == K_LEAF; }) != nullptr; }
@@ -669,22 +715,30 @@ class Graph {
     for (size_t i = 0; i < updates.size(); ++i) {
       if (used[i]) continue;
       const Update& h = updates[i];
-      Match mt; mt.pattern = h.algo == ZYXB_OPT_SGD ? "sgd" : (h.first ? "adamw_first_step" : "adamw");
+      const bool sgd_buf = h.algo == ZYXB_OPT_SGD && h.m != NONE;
+      Match mt; mt.pattern = h.algo == ZYXB_OPT_SGD ? (sgd_buf ? (h.nesterov ? "sgd_nesterov" : "sgd_momentum") : "sgd") : (h.first ? "adamw_first_step" : "adamw");
+      // the step the update belongs to: AdamW's bias correction divides by 1 - beta1^t
+      mt.optim_step = h.algo == ZYXB_OPT_SGD ? (sgd_buf ? 2 : 1)
+                                             : (h.first ? 1 : (uint64_t)std::max(2.0, std::round(std::log(1.0 - h.bc1) / std::log(h.b1))));
       std::vector<ClassId> p, g, mm, vv, outs;
       for (size_t j = i; j < updates.size(); ++j) {
         const Update& u = updates[j];
         if (used[j] || u.algo != h.algo || dtype(u.p) != dtype(h.p) || u.first != h.first || u.lr != h.lr || u.wd != h.wd || u.b1 != h.b1 ||
-            u.b2 != h.b2 || u.eps != h.eps || u.bc1 != h.bc1 || u.bc2 != h.bc2) continue;
+            u.b2 != h.b2 || u.eps != h.eps || u.bc1 != h.bc1 || u.bc2 != h.bc2 || u.mom != h.mom || u.damp != h.damp || u.nesterov != h.nesterov ||
+            (u.m == NONE) != (h.m == NONE)) continue;
         used[j] = 1;
         p.push_back(u.p); g.push_back(u.g); mt.numel.push_back(numel(shape(u.p)));
         outs.push_back(u.p_new);
         if (u.algo != ZYXB_OPT_SGD) { mm.push_back(u.m); vv.push_back(u.v); outs.push_back(u.m_new); outs.push_back(u.v_new); }
+        else if (u.m != NONE) { mm.push_back(u.m); outs.push_back(u.m_new); }
       }
       mt.desc.kind = ZYXB_KIND_OPTIM;
       auto& o = mt.desc.u.optim;
       o.algo = h.algo; o.dtype = dtype(h.p); o.n_tensors = (int32_t)p.size(); o.lr = (float)h.lr; o.weight_decay = (float)h.wd;
       o.beta1 = (float)h.b1; o.beta2 = (float)h.b2; o.eps = (float)h.eps;
+      o.momentum = (float)h.mom; o.dampening = (float)h.damp; o.nesterov = h.nesterov ? 1 : 0;
       mt.inputs = p; mt.inputs.insert(mt.inputs.end(), g.begin(), g.end());
+      if (sgd_buf) mt.inputs.insert(mt.inputs.end(), mm.begin(), mm.end());
       if (h.algo != ZYXB_OPT_SGD && !h.first) { mt.inputs.insert(mt.inputs.end(), mm.begin(), mm.end()); mt.inputs.insert(mt.inputs.end(), vv.begin(), vv.end()); }
       mt.outputs = outs;
       out.push_back(std::move(mt));
