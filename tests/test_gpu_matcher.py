@@ -122,3 +122,33 @@ def test_attention_core_from_graph_to_launch(sess):
                       what="matched attention")
     finally:
         g.close()
+
+
+@pytest.mark.parametrize("nesterov", [False, True])
+def test_sgd_with_momentum_from_graph_to_launch(sess, nesterov):
+    """A later step of SGD with weight decay, momentum, dampening (and Nesterov), traced and matched as one program over
+    (p, g, buf): the match's step goes into the program's counter so that the kernel reads the buffer; p' and buf' are the oracle's."""
+    rng = np.random.default_rng(34)
+    g = MGraph()
+    try:
+        p, gr, buf = (T.leaf(g, L.F32, (70, 33)) for _ in range(3))
+        new_p, new_b = sgd_update([p], [gr], 0.05, weight_decay=0.01, momentum=0.9, dampening=0.1, nesterov=nesterov, bufs=[buf])
+        m = pick(g.match([new_p[0].cls, new_b[0].cls]), b"sgd_nesterov" if nesterov else b"sgd_momentum", new_p[0].cls)
+        assert m.optim_step == 2
+        pv, gv, bv = (rng.standard_normal((70, 33)).astype(np.float32) for _ in range(3))
+        prog = sess.device.create_program(m.desc)
+        sess.device.set_step(prog, m.optim_step - 1)
+        bufs = [sess.pool.upload(a) for a in (pv, gv, bv)]
+        try:
+            sess.device.launch(prog, bufs)
+            got_p = sess.pool.download(bufs[0], pv.shape, np.float32)
+            got_b = sess.pool.download(bufs[2], bv.shape, np.float32)
+        finally:
+            for b_ in bufs:
+                sess.pool.deallocate(b_)
+            sess.device.release(prog)
+        want_p, want_b = pv.copy(), bv.copy()
+        zo.sgd(zo.F32, want_p, gv, want_b, lr=0.05, wd=0.01, momentum=0.9, dampening=0.1, nesterov=nesterov, first=False)
+        assert max_rel_err(got_p, want_p) <= TOL_F32 and max_rel_err(got_b, want_b) <= TOL_F32
+    finally:
+        g.close()
