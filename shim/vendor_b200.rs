@@ -40,7 +40,7 @@ struct Update { algo: i32, p: ClassId, g: ClassId, m: Option<ClassId>, v: Option
 
 const RR_SUM: i32 = 0; const RR_MAX: i32 = 1; const RR_MEAN: i32 = 3; const RR_SOFTMAX: i32 = 6; const RR_LN_SOFTMAX: i32 = 7; const RR_LAYERNORM: i32 = 8; const RR_MSE: i32 = 14;
 const EPI_NONE: i32 = 0; const EPI_BIAS: i32 = 1; const EPI_BIAS_RELU: i32 = 2; const EPI_BIAS_GELU: i32 = 3;
-const OPT_SGD: i32 = 0; const OPT_ADAMW: i32 = 2;
+const OPT_SGD: i32 = 0; const OPT_ADAM: i32 = 1; const OPT_ADAMW: i32 = 2;
 
 fn near(a: f64, b: f64) -> bool { (a - b).abs() <= 1e-2 * b.abs() }       // constants arrive rounded to the tensor dtype
 
@@ -423,23 +423,40 @@ impl Graph {
         let (root, eps) = self.binary_const(root_eps, BOp::Add)?;
         let vh = self.unary_of(root, UOp::Sqrt)?;
         let ((m_new, bc1), (v_new, bc2)) = (self.binary_const(mh, BOp::Div)?, self.binary_const(vh, BOp::Div)?);
-        // m' = m*b1 + g*(1-b1), or g*(1-b1) alone on the first step (adamw.rs:60-71); v' alike with g*g
-        let moment = |mc: ClassId, squared: bool| -> Option<(Option<ClassId>, f64, ClassId)> {
-            let grad_term = |t: ClassId| -> Option<(ClassId, f64)> {
-                let (x, om) = self.binary_const(t, BOp::Mul)?;
-                if !squared { return Some((x, om)); }
-                let (a, b) = self.binary_of(x, BOp::Mul)?;
-                self.same(a, b).then_some((a, om))
-            };
-            if let Some((l, r)) = self.binary_of(mc, BOp::Add) {
-                if let (Some((state, _)), Some((g, om))) = (self.binary_const(l, BOp::Mul), grad_term(r)) { if self.is_leaf(state) { return Some((Some(state), 1.0 - om, g)); } }
-            }
-            grad_term(mc).map(|(g, om)| (None, 1.0 - om, g))
-        };
-        let ((m, b1, g1), (v, b2, g2)) = (moment(m_new, false)?, moment(v_new, true)?);
+        let ((m, b1, g1), (v, b2, g2)) = (self.moment(m_new, false)?, self.moment(v_new, true)?);
         if !self.same(g1, g2) || m.is_some() != v.is_some() { return None; }
         Some(Update { algo: OPT_ADAMW, p, g: g1, m, v, p_new: cid, m_new: Some(m_new), v_new: Some(v_new), lr, wd: if wd != 0.0 { wd / lr } else { 0.0 },
-                      b1, b2, eps, bc1, bc2, first: m.is_none() })
+                      b1, b2, eps, bc1, bc2, first: m.is_none(), mom: 0.0, damp: 0.0, nesterov: false })
+    }
+    /// m' = m*b1 + g*(1-b1), or g*(1-b1) alone on the first step (adamw.rs:60-71, adam.rs:72-81); v' alike with g*g
+    /// -> (state, beta, g)
+    fn moment(&self, mc: ClassId, squared: bool) -> Option<(Option<ClassId>, f64, ClassId)> {
+        let grad_term = |t: ClassId| -> Option<(ClassId, f64)> {
+            let (x, om) = self.binary_const(t, BOp::Mul)?;
+            if !squared { return Some((x, om)); }
+            let (a, b) = self.binary_of(x, BOp::Mul)?;
+            self.same(a, b).then_some((a, om))
+        };
+        if let Some((l, r)) = self.binary_of(mc, BOp::Add) {
+            if let (Some((state, _)), Some((g, om))) = (self.binary_const(l, BOp::Mul), grad_term(r)) { if self.is_leaf(state) { return Some((Some(state), 1.0 - om, g)); } }
+        }
+        grad_term(mc).map(|(g, om)| (None, 1.0 - om, g))
+    }
+    /// Adam::update for one parameter without amsgrad (zyx-optim/src/adam.rs:66-101):
+    /// G = g [+ p * weight_decay]; p' = (p - lr * mh / (sqrt(vh) + eps)).cast(p.dtype)
+    fn match_adam(&self, cid: ClassId) -> Option<Update> {
+        let (p, step) = self.binary_of(self.canon(cid), BOp::Sub)?;
+        if !self.is_leaf(p) { return None; }
+        let (num, den) = self.binary_of(step, BOp::Div)?;                    // (lr * mh) / (sqrt(vh) + eps)
+        let (mh, lr) = self.binary_const(num, BOp::Mul)?;
+        let (root, eps) = self.binary_const(den, BOp::Add)?;
+        let vh = self.unary_of(root, UOp::Sqrt)?;
+        let ((m_new, bc1), (v_new, bc2)) = (self.binary_const(mh, BOp::Div)?, self.binary_const(vh, BOp::Div)?);
+        let ((m, b1, g1), (v, b2, g2)) = (self.moment(m_new, false)?, self.moment(v_new, true)?);
+        if !self.same(g1, g2) || m.is_some() != v.is_some() { return None; }
+        let (g, wd) = self.strip_decay(g1, p);
+        Some(Update { algo: OPT_ADAM, p, g, m, v, p_new: cid, m_new: Some(m_new), v_new: Some(v_new), lr, wd, b1, b2, eps, bc1, bc2,
+                      first: m.is_none(), mom: 0.0, damp: 0.0, nesterov: false })
     }
 
     /// Everything the device's match_graph needs: `order` is topo_sort_classes_without_kernels of the outputs, `wanted` the
@@ -450,7 +467,7 @@ impl Graph {
         let mut updates: Vec<Update> = Vec::new();
         for &cid in order {
             if wanted.contains(&cid) {
-                if let Some(u) = self.match_adamw(cid).or_else(|| self.match_sgd(cid)) { updates.push(u); continue; }
+                if let Some(u) = self.match_adamw(cid).or_else(|| self.match_adam(cid)).or_else(|| self.match_sgd(cid)) { updates.push(u); continue; }
             }
             let m = self.match_attention(cid).or_else(|| self.match_linear(cid, wanted)).or_else(|| self.match_softmax(cid)).or_else(|| self.match_ln_softmax(cid))
                 .or_else(|| self.match_layernorm(cid)).or_else(|| self.match_mse(cid)).or_else(|| self.match_reduce(cid));
@@ -479,7 +496,8 @@ impl Graph {
             let mut inputs = p;
             inputs.extend(g); inputs.extend(ms); inputs.extend(vs);
             let sgd_buf = h.algo == OPT_SGD && h.m.is_some();
-            let pattern = if h.algo != OPT_SGD { if h.first { "adamw_first_step" } else { "adamw" } }
+            let pattern = if h.algo == OPT_ADAM { if h.first { "adam_first_step" } else { "adam" } }
+                          else if h.algo != OPT_SGD { if h.first { "adamw_first_step" } else { "adamw" } }
                           else if !sgd_buf { "sgd" } else if h.nesterov { "sgd_nesterov" } else { "sgd_momentum" };
             // the step the update belongs to: AdamW's bias correction divides by 1 - beta1^t
             let optim_step = if h.algo == OPT_SGD { if sgd_buf { 2 } else { 1 } }

@@ -7,7 +7,7 @@ import math
 
 import pytest
 
-from tests.zyx_trace import LayerNorm, Linear, T, adamw_update, sgd_update
+from tests.zyx_trace import LayerNorm, Linear, T, adam_update, adamw_update, sgd_update
 from zyx_b200 import _lib as L
 from zyx_b200 import backend as B
 from zyx_b200.matcher import MGraph
@@ -313,3 +313,24 @@ def test_adamw_match_names_its_step(g):
         new_p, new_m, new_v = adamw_update(params, grads, m, v, step)
         ms = g.match([t.cls for t in new_p + new_m + new_v])
         assert [x.optim_step for x in ms if x.pattern.startswith(b"adamw")] == [step]
+
+
+@pytest.mark.parametrize("step,weight_decay", [(1, 0.0), (5, 0.0), (5, 0.02)])
+def test_adam_update_is_one_multi_tensor_program(g, step, weight_decay):
+    """Adam::update (adam.rs:66-101, no amsgrad): L2 weight decay inside the gradient, p' = p - lr * mh / (sqrt(vh) + eps)."""
+    shapes = [(24, 16), (24,)]
+    params = [T.leaf(g, L.F32, s) for s in shapes]
+    grads = [T.leaf(g, L.F32, s) for s in shapes]
+    m = [T.leaf(g, L.F32, s) for s in shapes] if step > 1 else None
+    v = [T.leaf(g, L.F32, s) for s in shapes] if step > 1 else None
+    new_p, new_m, new_v = adam_update(params, grads, m, v, step, lr=2e-3, betas=(0.9, 0.99), eps=1e-7, weight_decay=weight_decay)
+    ms = g.match([t.cls for t in new_p + new_m + new_v])
+    assert [x.pattern for x in ms] == [b"adam" if step > 1 else b"adam_first_step"]
+    mt = ms[0]
+    o = mt.desc.u.optim
+    assert (o.algo, o.n_tensors, mt.optim_step) == (L.OPT_ADAM, 2, step)
+    for got, want in ((o.lr, 2e-3), (o.beta1, 0.9), (o.beta2, 0.99), (o.eps, 1e-7), (o.weight_decay, weight_decay)):
+        assert abs(got - want) <= 1e-6 * max(1.0, abs(want)), (got, want)
+    want_in = [t.cls for t in params] + [t.cls for t in grads] + ([t.cls for t in m] + [t.cls for t in v] if step > 1 else [])
+    assert list(mt.inputs[:mt.n_inputs]) == want_in
+    assert list(mt.outputs[:mt.n_outputs]) == [c for trio in zip(new_p, new_m, new_v) for c in (trio[0].cls, trio[1].cls, trio[2].cls)]

@@ -237,6 +237,22 @@ def adamw_update(params, grads, m, v, t, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, 
     return new_p, new_m, new_v
 
 
+def adam_update(params, grads, m, v, t, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0):
+    """Adam::update without amsgrad (zyx-optim/src/adam.rs:66-101).  -> (new params, new m, new v); m / v are None on the first step.
+    `self.learning_rate * mh` is scalar * tensor: the constant is the left operand of the Mul."""
+    new_p, new_m, new_v = [], [], []
+    for i, (p, g) in enumerate(zip(params, grads)):
+        if weight_decay != 0.0:
+            g = g + p * weight_decay
+        mi = m[i] * betas[0] + g * (1.0 - betas[0]) if m is not None else g * (1.0 - betas[0])
+        vi = v[i] * betas[1] + g * g * (1.0 - betas[1]) if v is not None else g * g * (1.0 - betas[1])
+        mh = mi / (1.0 - betas[0] ** t)
+        vh = vi / (1.0 - betas[1] ** t)
+        q = (p - (T.scalar(p.g, lr) * mh) / (vh.sqrt() + eps)).cast(p.dtype)
+        new_p.append(q); new_m.append(mi); new_v.append(vi)
+    return new_p, new_m, new_v
+
+
 def attention_core(q, k, v, heads):
     """The mask-free core of MultiheadAttention::forward between the projections (zyx-nn/src/multi_head_attention.rs:160-172,
     197-199, 219-226): q, k, v [b, t, e] -> head split, scores * 1/sqrt(d), softmax, .matmul(v), heads merged -> [b, t, e].

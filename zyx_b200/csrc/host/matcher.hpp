@@ -640,6 +640,60 @@ class Graph {
   }
   bool is_leaf(ClassId c) const { return find(c, [](const Node& n) { return n.kind == K_LEAF; }) != nullptr; }
 
+  // m' = m*b1 + g*(1-b1)  |  g*(1-b1) on the first step
+  bool moment(ClassId mc, bool squared, ClassId& state, double& beta, ClassId& g) const {
+    auto grad_term = [&](ClassId t, double& one_minus) -> std::optional<ClassId> {
+      auto k = binary_const(t, B_MUL);
+      if (!k) return std::nullopt;
+      one_minus = k->second;
+      if (!squared) return k->first;
+      auto gg = binary(k->first, B_MUL);
+      if (!gg || !same(gg->first, gg->second)) return std::nullopt;
+      return gg->first;
+    };
+    double om = 0;
+    if (auto add = binary(mc, B_ADD)) {
+      auto decay = binary_const(add->first, B_MUL);
+      auto gt = grad_term(add->second, om);
+      if (decay && gt && is_leaf(decay->first)) { state = decay->first; beta = 1.0 - om; g = *gt; return true; }
+    }
+    if (auto gt = grad_term(mc, om)) { state = NONE; beta = 1.0 - om; g = *gt; return true; }
+    return false;
+  }
+
+  // Adam::update for one parameter without amsgrad (adam.rs:66-101), ending at the new parameter's class:
+  //   G = g [+ p * weight_decay];  m' and v' as in AdamW;  p' = (p - lr * mh / (sqrt(vh) + eps)).cast(p.dtype)
+  std::optional<Update> match_adam(ClassId cid) const {
+    Update u{}; u.algo = ZYXB_OPT_ADAM; u.p_new = cid;
+    auto sub = binary(canon(cid), B_SUB);
+    if (!sub || !is_leaf(sub->first)) return std::nullopt;
+    u.p = sub->first;
+    auto step = binary(sub->second, B_DIV);                    // (lr * mh) / (sqrt(vh) + eps)
+    if (!step) return std::nullopt;
+    auto num = binary_const(step->first, B_MUL);
+    auto root_eps = binary_const(step->second, B_ADD);
+    if (!num || !root_eps) return std::nullopt;
+    u.lr = num->second; u.eps = root_eps->second;
+    auto vh = unary(root_eps->first, U_SQRT);
+    if (!vh) return std::nullopt;
+    auto mh = binary_const(num->first, B_DIV), vhd = binary_const(*vh, B_DIV);
+    if (!mh || !vhd) return std::nullopt;
+    u.bc1 = mh->second; u.bc2 = vhd->second; u.m_new = mh->first; u.v_new = vhd->first;
+    ClassId g1 = NONE, g2 = NONE;
+    if (!moment(u.m_new, false, u.m, u.b1, g1) || !moment(u.v_new, true, u.v, u.b2, g2) || !same(g1, g2)) return std::nullopt;
+    if ((u.m == NONE) != (u.v == NONE)) return std::nullopt;
+    u.first = u.m == NONE;
+    u.g = g1;
+    // weight decay enters the gradient: G = g + p * wd
+    if (auto add = binary(g1, B_ADD))
+      for (int swap = 0; swap < 2; ++swap) {
+        const ClassId lhs = swap ? add->second : add->first, rhs = swap ? add->first : add->second;
+        auto k = binary_const(rhs, B_MUL);
+        if (k && same(k->first, u.p)) { u.g = lhs; u.wd = k->second; break; }
+      }
+    return u;
+  }
+
   // AdamW::update for one parameter (adamw.rs:58-95), ending at the new parameter's class
   std::optional<Update> match_adamw(ClassId cid) const {
     Update u{}; u.algo = ZYXB_OPT_ADAMW; u.p_new = cid;
@@ -662,26 +716,6 @@ class Graph {
     auto mh = binary_const(step->first, B_DIV), vhd = binary_const(*vh, B_DIV);
     if (!mh || !vhd) return std::nullopt;
     u.bc1 = mh->second; u.bc2 = vhd->second; u.m_new = mh->first; u.v_new = vhd->first;
-    // m' = m*b1 + g*(1-b1)  |  g*(1-b1) on the first step
-    auto moment = [&](ClassId mc, bool squared, ClassId& state, double& beta, ClassId& g) -> bool {
-      auto grad_term = [&](ClassId t, double& one_minus) -> std::optional<ClassId> {
-        auto k = binary_const(t, B_MUL);
-        if (!k) return std::nullopt;
-        one_minus = k->second;
-        if (!squared) return k->first;
-        auto gg = binary(k->first, B_MUL);
-        if (!gg || !same(gg->first, gg->second)) return std::nullopt;
-        return gg->first;
-      };
-      double om = 0;
-      if (auto add = binary(mc, B_ADD)) {
-        auto decay = binary_const(add->first, B_MUL);
-        auto gt = grad_term(add->second, om);
-        if (decay && gt && is_leaf(decay->first)) { state = decay->first; beta = 1.0 - om; g = *gt; return true; }
-      }
-      if (auto gt = grad_term(mc, om)) { state = NONE; beta = 1.0 - om; g = *gt; return true; }
-      return false;
-    };
     ClassId g1 = NONE, g2 = NONE;
     if (!moment(u.m_new, false, u.m, u.b1, g1) || !moment(u.v_new, true, u.v, u.b2, g2) || !same(g1, g2)) return std::nullopt;
     u.g = g1;
@@ -703,6 +737,7 @@ class Graph {
       std::optional<Match> m;
       if (wanted.count(cid)) {      // new parameter values are outputs of the graph; their sub-expressions are not matched as updates
         if (auto u = match_adamw(cid)) { updates.push_back(*u); continue; }
+        if (auto u = match_adam(cid)) { updates.push_back(*u); continue; }
         if (auto u = match_sgd(cid)) { updates.push_back(*u); continue; }
       }
       if (!(m = match_attention(cid)) && !(m = match_linear(cid, wanted)) && !(m = match_softmax(cid)) && !(m = match_ln_softmax(cid)) && !(m = match_layernorm(cid)) &&
@@ -716,7 +751,8 @@ class Graph {
       if (used[i]) continue;
       const Update& h = updates[i];
       const bool sgd_buf = h.algo == ZYXB_OPT_SGD && h.m != NONE;
-      Match mt; mt.pattern = h.algo == ZYXB_OPT_SGD ? (sgd_buf ? (h.nesterov ? "sgd_nesterov" : "sgd_momentum") : "sgd") : (h.first ? "adamw_first_step" : "adamw");
+      const std::string adam_name = h.algo == ZYXB_OPT_ADAM ? "adam" : "adamw";
+      Match mt; mt.pattern = h.algo == ZYXB_OPT_SGD ? (sgd_buf ? (h.nesterov ? "sgd_nesterov" : "sgd_momentum") : "sgd") : (h.first ? adam_name + "_first_step" : adam_name);
       // the step the update belongs to: AdamW's bias correction divides by 1 - beta1^t
       mt.optim_step = h.algo == ZYXB_OPT_SGD ? (sgd_buf ? 2 : 1)
                                              : (h.first ? 1 : (uint64_t)std::max(2.0, std::round(std::log(1.0 - h.bc1) / std::log(h.b1))));
