@@ -110,7 +110,8 @@ typedef struct zyxb_block zyxb_block;
 int32_t zyxb_block_create(zyxb_ctx* ctx, int32_t dev, const zyxb_block_config* config, zyxb_block** out);
 int32_t zyxb_block_destroy(zyxb_block* blk);
 const char* zyxb_block_last_error(zyxb_block* blk);
-/* which: 0 parameter, 1 gradient, 2 / 3 optimizer state; i in Module::iter() order */
+/* which: 0 parameter, 1 gradient, 2 / 3 optimizer state; i in Module::iter() order.  With shard_optimizer the state has no
+ * per-tensor buffers (IncorrectKernelArg for which >= 2), and the call first waits for parameter all-gathers still in flight. */
 int32_t zyxb_block_tensor(zyxb_block* blk, int32_t which, int32_t i, uint32_t* out_buf, uint64_t* out_numel);
 int32_t zyxb_block_io(zyxb_block* blk, uint32_t* out_x, uint32_t* out_target, uint32_t* out_loss, uint32_t* out_y);
 int32_t zyxb_block_forward_backward(zyxb_block* blk);
