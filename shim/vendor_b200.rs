@@ -39,6 +39,7 @@ struct Update { algo: i32, p: ClassId, g: ClassId, m: Option<ClassId>, v: Option
                 mom: f64, damp: f64, nesterov: bool }      // SGD with momentum: m / m_new are the buffer
 
 const RR_SUM: i32 = 0; const RR_MAX: i32 = 1; const RR_MEAN: i32 = 3; const RR_SOFTMAX: i32 = 6; const RR_LN_SOFTMAX: i32 = 7; const RR_LAYERNORM: i32 = 8; const RR_MSE: i32 = 14;
+const RR_VAR: i32 = 4; const RR_STD: i32 = 5; const RR_COLSUM: i32 = 13;
 const EPI_NONE: i32 = 0; const EPI_BIAS: i32 = 1; const EPI_BIAS_RELU: i32 = 2; const EPI_BIAS_GELU: i32 = 3;
 const OPT_SGD: i32 = 0; const OPT_ADAM: i32 = 1; const OPT_ADAMW: i32 = 2;
 
@@ -351,7 +352,39 @@ impl Graph {
         if !f32s || self.const_shape(y)? != xs || self.const_shape(t)? != xs { return None; }
         Some(self.row_match("mse_loss", self.row_desc(RR_MSE, y)?, vec![y, t], cid))
     }
+    /// var(x, [-1]) = sum((x - mean_keepdim(x))^2) / (n - correction) (tensor/reduce_ops.rs:111-123) -> (x, correction)
+    fn var_last(&self, cid: ClassId) -> Option<(ClassId, i32)> {
+        let (sq, d) = self.mean_last(cid)?;
+        let (a, b) = self.binary_of(sq, BOp::Mul)?;
+        if !self.same(a, b) { return None; }
+        let (x, mean) = self.binary_of(a, BOp::Sub)?;
+        let x = self.canon(x);
+        let (mx, _) = self.mean_last(self.keepdim_src(mean))?;
+        if !self.same(mx, x) { return None; }
+        let n = *self.const_shape(x)?.last()? as f64;
+        let corr = (n - d).round();
+        (corr >= 0.0 && corr < n && ((n - d) - corr).abs() <= 1e-6).then_some((x, corr as i32))
+    }
+    /// x [rows, cols] .sum([0]) -> x (the bias gradient of a Linear layer)
+    fn column_sum_src(&self, cid: ClassId) -> Option<ClassId> {
+        let red = |c: ClassId| self.find_in(c, |n| match n { Node::Reduce { x, rop: BOp::Add, axes } if axes.as_ref() == [0] => Some(*x), _ => None });
+        let mut x = red(cid).or_else(|| red(self.cast_src(cid)?))?;
+        if let Some(k) = self.cast_src(x) { if self.dtype(k) == self.dtype(cid) { x = k; } }     // the accumulator cast
+        let x = self.canon(x);
+        (self.const_shape(x)?.len() == 2 && self.dtype(x) == self.dtype(cid)).then_some(x)
+    }
+    /// var / std / sum / max / mean over the last axis, sum over the rows of a matrix
     fn match_reduce(&self, cid: ClassId) -> Option<B200Match> {
+        for (name, op, v) in [("var", RR_VAR, Some(cid)), ("std", RR_STD, self.unary_of(cid, UOp::Sqrt))] {
+            if let Some((x, corr)) = v.and_then(|v| self.var_last(v)) {
+                if self.dtype(cid) == self.dtype(x) {
+                    if let Some(mut d) = self.row_desc(op, x) { d.correction = corr; return Some(self.row_match(name, d, vec![x], cid)); }
+                }
+            }
+        }
+        if let Some(x) = self.column_sum_src(cid) {
+            if !self.is_broadcast_product(x) { if let Some(d) = self.row_desc(RR_COLSUM, x) { return Some(self.row_match("colsum", d, vec![x], cid)); } }
+        }
         if let Some((x, _)) = self.mean_last(cid) { if let Some(d) = self.row_desc(RR_MEAN, x) { return Some(self.row_match("mean", d, vec![x], cid)); } }
         for (rop, rr, name) in [(BOp::Add, RR_SUM, "sum"), (BOp::Max, RR_MAX, "max")] {
             if let Some(x) = self.reduce_last(cid, rop) {

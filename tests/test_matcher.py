@@ -334,3 +334,20 @@ def test_adam_update_is_one_multi_tensor_program(g, step, weight_decay):
     want_in = [t.cls for t in params] + [t.cls for t in grads] + ([t.cls for t in m] + [t.cls for t in v] if step > 1 else [])
     assert list(mt.inputs[:mt.n_inputs]) == want_in
     assert list(mt.outputs[:mt.n_outputs]) == [c for trio in zip(new_p, new_m, new_v) for c in (trio[0].cls, trio[1].cls, trio[2].cls)]
+
+
+@pytest.mark.parametrize("dtype", [L.F32, L.BF16])
+def test_var_std_and_column_sums(g, dtype):
+    """var / std over the last axis (reduce_ops.rs:111-130) with their correction, and x.sum([0]) of a matrix - the bias
+    gradient of a Linear layer - as the column-sum program."""
+    x = T.leaf(g, dtype, (48, 320))
+    v0, v1, sd, cs = x.var([-1], correction=0), x.var([-1]), x.std([-1]), x.sum([0])
+    ms = g.match([v0.cls, v1.cls, sd.cls, cs.cls])
+    at = {m.outputs[0]: m for m in ms}
+    for out, pattern, op, corr in ((v0, b"var", L.RR_VAR, 0), (v1, b"var", L.RR_VAR, 1), (sd, b"std", L.RR_STD, 1)):
+        m = at[out.cls]
+        assert m.pattern == pattern and list(m.inputs[:m.n_inputs]) == [x.cls]
+        assert_same_row(m.desc, B.rowreduce_desc(op, dtype, 48, 320, correction=corr))
+    m = at[cs.cls]
+    assert m.pattern == b"colsum" and list(m.inputs[:m.n_inputs]) == [x.cls]
+    assert_same_row(m.desc, B.rowreduce_desc(L.RR_COLSUM, dtype, 48, 320))

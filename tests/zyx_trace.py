@@ -161,6 +161,9 @@ class T:
             t = t.reshape(shape)
         return t
 
+    def std(self, axes, keepdim=False, correction=1):
+        return self.var(axes, keepdim=keepdim, correction=correction).sqrt()     # reduce_ops.rs:124-130
+
     def softmax(self, axes=(-1,)):
         e = (self - self.max(list(axes), keepdim=True)).exp()
         return e / e.sum(list(axes), keepdim=True)

@@ -540,9 +540,50 @@ class Graph {
     m.outputs = {cid};
     return m;
   }
-  // sum / max / mean over the last axis of a tensor nobody computes as a matmul product
+  // var(x, [-1]) = sum((x - mean_keepdim(x))^2) / (n - correction)   (reduce_ops.rs:111-123) -> (x, correction)
+  std::optional<std::pair<ClassId, int>> var_last(ClassId cid) const {
+    double d = 0;
+    auto sq = mean_last(cid, &d);
+    if (!sq) return std::nullopt;
+    auto xx = binary(*sq, B_MUL);
+    if (!xx || !same(xx->first, xx->second)) return std::nullopt;
+    auto centred = binary(xx->first, B_SUB);
+    if (!centred) return std::nullopt;
+    const ClassId x = canon(centred->first);
+    auto mx = mean_last(unbroadcast_keepdim(centred->second));
+    if (!mx || !same(*mx, x) || shape(x).empty()) return std::nullopt;
+    const double n = (double)shape(x).back();
+    const long corr = llround(n - d);
+    if (corr < 0 || corr >= (long)n || fabs((n - d) - (double)corr) > 1e-6) return std::nullopt;
+    return std::make_pair(x, (int)corr);
+  }
+  // sum over the rows of a matrix: x [rows, cols] .sum([0]) -> [cols] (the bias gradient of a Linear layer)
+  std::optional<ClassId> column_sum_src(ClassId cid) const {
+    auto red_of = [&](ClassId c) { return find(c, [](const Node& n) { return n.kind == K_REDUCE && n.op == B_ADD && n.axes.size() == 1 && n.axes[0] == 0; }); };
+    const Node* red = red_of(cid);
+    if (!red) { auto k = cast_src(cid); if (!k || !(red = red_of(*k))) return std::nullopt; }      // sum() casts the accumulator back for 16-bit inputs
+    ClassId x = red->x;
+    if (auto k = cast_src(x)) if (dtype(*k) == dtype(cid)) x = *k;                                  // the accumulator cast
+    x = canon(x);
+    if (shape(x).size() != 2 || dtype(x) != dtype(cid)) return std::nullopt;
+    return x;
+  }
+  // var / std / sum / max / mean over the last axis, sum over the rows of a matrix, of a tensor nobody computes as a matmul product
   std::optional<Match> match_reduce(ClassId cid) const {
     const std::pair<int, int> ops[] = {{B_ADD, ZYXB_RR_SUM}, {B_MAX, ZYXB_RR_MAX}};
+    for (int is_std = 0; is_std < 2; ++is_std) {
+      ClassId v = cid;
+      if (is_std) { auto r = unary(cid, U_SQRT); if (!r) break; v = *r; }
+      if (auto vx = var_last(v)) if (row_dtype(dtype(vx->first)) && dtype(cid) == dtype(vx->first)) {
+        Match m; m.pattern = is_std ? "std" : "var"; m.desc = row_desc(is_std ? ZYXB_RR_STD : ZYXB_RR_VAR, dtype(vx->first), shape(vx->first));
+        m.desc.u.rowreduce.correction = vx->second; m.inputs = {vx->first}; m.outputs = {cid};
+        return m;
+      }
+    }
+    if (auto x = column_sum_src(cid)) if (row_dtype(dtype(*x)) && !is_broadcast_product(*x)) {
+      Match m; m.pattern = "colsum"; m.desc = row_desc(ZYXB_RR_COLSUM, dtype(*x), shape(*x)); m.inputs = {*x}; m.outputs = {cid};
+      return m;
+    }
     if (auto x = mean_last(cid)) if (row_dtype(dtype(*x)) && shape(*x).size() >= 1) {
       Match m; m.pattern = "mean"; m.desc = row_desc(ZYXB_RR_MEAN, dtype(*x), shape(*x)); m.inputs = {*x}; m.outputs = {cid};
       return m;
