@@ -184,7 +184,7 @@ uint32_t zyxb_mgraph_binary(zyxb_mgraph* g, uint32_t x, uint32_t y, int32_t bop)
 int32_t  zyxb_mgraph_class_info(zyxb_mgraph* g, uint32_t cls, int32_t* out_dtype, int32_t* out_rank, uint64_t* out_shape8, int32_t* out_kernel_nodes);
 
 /* One recognised subgraph: what to hand to zyxb_program_create, and the classes whose buffers are the launch arguments
- * (inputs then outputs, the order Device::launch receives, backend/mod.rs:974).  Patterns: matmul_nn / matmul_nt
+ * (inputs then outputs, the order Device::launch receives, backend/mod.rs:974).  Patterns: matmul_nn / matmul_nt / matmul_tn / matmul_tt
  * [_batched][_bias[_relu|_gelu]], attention, softmax, ln_softmax, layernorm, mse_loss, sum, max, mean, var, std, colsum, sgd, sgd_momentum,
  * sgd_nesterov, adam, adam_first_step, adamw, adamw_first_step.  An optimizer match covers every parameter of the update (inputs p.., g.. [, m.., v.. |
  * , buf..]; outputs p' [, m', v' | , buf'] per tensor - the kernel updates in place, so the shim binds each output to its

@@ -31,7 +31,7 @@ pub(crate) struct B200Match {
 }
 
 #[derive(Clone, Copy)]
-struct MatMulX { a: ClassId, b: ClassId, m: Dim, n: Dim, k: Dim, batch: Dim, trans_b: bool, b_shared: bool, dtype: DType }
+struct MatMulX { a: ClassId, b: ClassId, m: Dim, n: Dim, k: Dim, batch: Dim, trans_a: bool, trans_b: bool, b_shared: bool, dtype: DType }
 
 #[derive(Clone, Copy)]
 struct Update { algo: i32, p: ClassId, g: ClassId, m: Option<ClassId>, v: Option<ClassId>, p_new: ClassId, m_new: Option<ClassId>,
@@ -116,7 +116,7 @@ impl Graph {
         Some(self.canon(src))
     }
 
-    // ---- matmul: Graph::match_matmul extended to NT on a stored tensor, rank > 2 and the accumulator casts of 16-bit inputs -------
+    // ---- matmul: Graph::match_matmul extended to NT / TN / TT on stored tensors, rank > 2 and the accumulator casts of 16-bit inputs -------
     fn match_matmul_x(&self, cid: ClassId) -> Option<MatMulX> {
         let out_shape = self.const_shape(cid)?;
         if out_shape.len() < 2 { return None; }
@@ -161,9 +161,14 @@ impl Graph {
             Some(w) => (w, true),
             None => (b, false),
         };
+        // TN on a stored tensor: a is `x.t()` of a [.., k, m] tensor (a weight gradient written as `x.t().dot(dz)`)
+        let (a, trans_a) = match self.find_in(a, |nd| match nd { Node::Permute { x, axes } if swaps_last_two(axes) => Some(*x), _ => None }) {
+            Some(x) if self.const_shape(x).is_some_and(|s| s.len() >= 2 && s[s.len() - 2] == k && s[s.len() - 1] == m) => (x, true),
+            _ => (a, false),
+        };
         let dt = self.dtype(b);
         if self.dtype(a) != dt || self.dtype(cid) != dt || !matches!(dt, DType::F32 | DType::BF16 | DType::F16 | DType::I32) { return None; }
-        Some(MatMulX { a, b, m, n, k, batch: batch_dims.iter().product(), trans_b, b_shared, dtype: dt })
+        Some(MatMulX { a, b, m, n, k, batch: batch_dims.iter().product(), trans_a, trans_b, b_shared, dtype: dt })
     }
     fn match_matmul_scaled(&self, cid: ClassId) -> Option<(MatMulX, f32)> {
         if let Some(mm) = self.match_matmul_x(cid) { return Some((mm, 1.0)); }
@@ -219,7 +224,7 @@ impl Graph {
         let epi = match (bias.is_some(), act) { (false, _) => EPI_NONE, (true, 2) => EPI_BIAS_GELU, (true, 1) => EPI_BIAS_RELU, _ => EPI_BIAS };
         let preact = act == 2 && wanted.contains(&e);
         let gemm = ZyxbGemmDesc {
-            dtype: mm.dtype as i32, m: mm.m, n: mm.n, k: mm.k, batch: mm.batch, trans_a: 0, trans_b: mm.trans_b as i32,
+            dtype: mm.dtype as i32, m: mm.m, n: mm.n, k: mm.k, batch: mm.batch, trans_a: mm.trans_a as i32, trans_b: mm.trans_b as i32,
             stride_a: (mm.m * mm.k) as i64, stride_b: if mm.b_shared { 0 } else { (mm.k * mm.n) as i64 }, stride_c: (mm.m * mm.n) as i64,
             epilogue: epi, store_preact: preact as i32, alpha, ..Default::default()
         };
@@ -269,10 +274,10 @@ impl Graph {
         if s3.len() != 3 { return None; }
         let pv_cls = self.permute_of(self.reshape_of(cid)?, &[0, 2, 1, 3])?;
         let pv = self.match_matmul_x(pv_cls)?;
-        if pv.trans_b || pv.b_shared { return None; }
+        if pv.trans_a || pv.trans_b || pv.b_shared { return None; }
         let sm = self.match_softmax(pv.a)?;
         let (qk, scale) = self.match_matmul_scaled(sm.inputs[0])?;
-        if !qk.trans_b || qk.b_shared { return None; }
+        if qk.trans_a || !qk.trans_b || qk.b_shared { return None; }
         let (xq, xk, xv) = (self.head_split_src(qk.a)?, self.head_split_src(qk.b)?, self.head_split_src(pv.b)?);
         let hs = self.const_shape(pv_cls)?;
         let (b, h, t, d) = (hs[0], hs[1], hs[2], hs[3]);

@@ -127,6 +127,36 @@ def test_batched_matmul_shared_and_per_batch_operands_and_scale(g):
 
 
 @pytest.mark.parametrize("dtype", [L.F32, L.BF16])
+def test_transposed_left_operand_is_read_where_it_lies(g, dtype):
+    """`dz.t().dot(x)`, a Linear's weight gradient written by hand: the left operand of the program is the stored dz with
+    trans_a, the descriptor the Linear-stack plan creates for its weight-gradient launch (host/trainer.cpp); with `w.t()` on
+    the right as well both flags are set; a rank-3 left operand against a shared matrix keeps its batch."""
+    dz, x = T.leaf(g, dtype, (8192, 512)), T.leaf(g, dtype, (8192, 384))
+    dw = dz.t().dot(x)
+    m = g.match([dw.cls])[-1]
+    assert m.pattern == b"matmul_tn" and m.outputs[0] == dw.cls
+    assert_same_gemm(m.desc, B.gemm_desc(dtype, 512, 384, 8192, trans_a=True))
+    assert list(m.inputs[:m.n_inputs]) == [dz.cls, x.cls]
+    w = T.leaf(g, dtype, (640, 8192))
+    tt = dz.t().dot(w.t())
+    m = g.match([tt.cls])[-1]
+    assert m.pattern == b"matmul_tt"
+    assert_same_gemm(m.desc, B.gemm_desc(dtype, 512, 640, 8192, trans_a=True, trans_b=True))
+    assert list(m.inputs[:m.n_inputs]) == [dz.cls, w.cls]
+    a3, w3 = T.leaf(g, dtype, (6, 24, 40)), T.leaf(g, dtype, (24, 56))
+    o3 = a3.t().dot(w3)
+    m = g.match([o3.cls])[-1]
+    assert m.pattern == b"matmul_tn_batched"
+    assert_same_gemm(m.desc, B.gemm_desc(dtype, 40, 56, 24, batch=6, trans_a=True, stride_b=0))
+    assert list(m.inputs[:m.n_inputs]) == [a3.cls, w3.cls]
+    # a permute that is not the exchange of the last two axes stays an operand of its own (the kernel has no such view)
+    a4 = T.leaf(g, dtype, (24, 6, 40))
+    o4 = a4.permute([1, 0, 2]).dot(T.leaf(g, dtype, (40, 56)))
+    m = g.match([o4.cls])[-1]
+    assert m.pattern == b"matmul_nn_batched" and m.inputs[0] != a4.cls
+
+
+@pytest.mark.parametrize("dtype", [L.F32, L.BF16])
 def test_softmax_and_ln_softmax(g, dtype):
     x = T.leaf(g, dtype, (8192, 32768))
     y, z = x.softmax(), x.ln_softmax()

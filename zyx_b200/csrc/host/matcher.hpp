@@ -6,13 +6,17 @@
 // vendor/mod.rs:28-95), and its consumer pushes a Node::Kernel into the matched class (backend/cblas.rs:213-238).  This file
 // is the same machinery over a mirror of that graph, extended to what an aot_only device must cover:
 //   matmul          NN as the reference; NT on a stored weight (`x.dot(W.t())` of Linear::forward, zyx-nn/src/linear.rs:39-45,
-//                   where the reference would hand the kernel the *class* W.t()); rank > 2 with batch strides; the accumulator
-//                   Casts that `sum` puts around the Reduce for 16-bit inputs (tensor/reduce_ops.rs:52-60,143-145); a
-//                   trailing `* const` (attention's 1/sqrt(d)) as alpha; `+ bias`, relu and gelu as epilogues
+//                   where the reference would hand the kernel the *class* W.t()); TN / TT when the left operand is `x.t()` of
+//                   a stored tensor (a weight gradient written as `dz.t().dot(x)`); rank > 2 with batch strides; the
+//                   accumulator Casts that `sum` puts around the Reduce for 16-bit inputs (tensor/reduce_ops.rs:52-60,143-145);
+//                   a trailing `* const` (attention's 1/sqrt(d)) as alpha; `+ bias`, relu and gelu as epilogues
+//   attention       the mask-free core of MultiheadAttention::forward (zyx-nn/src/multi_head_attention.rs:197-226)
 //   row kernels     softmax, ln_softmax (tensor/mod.rs:1427-1461), LayerNorm::forward (zyx-nn/src/layer_norm.rs:95-135),
-//                   sum / max / mean over the last axis (tensor/reduce_ops.rs:45-157)
-//   optimizer       SGD::update (zyx-optim/src/sgd.rs:45-84, without momentum), AdamW::update (zyx-optim/src/adamw.rs:51-97,
-//                   first and later steps), all matched tensors of one update grouped into one multi-tensor program
+//                   sum / max / mean / var / std over the last axis (tensor/reduce_ops.rs:45-157), `sum([0])` of a matrix
+//                   (column sums), mse_loss of f32 tensors
+//   optimizer       SGD::update (zyx-optim/src/sgd.rs:45-84: plain, weight decay, momentum with dampening, Nesterov),
+//                   Adam::update (zyx-optim/src/adam.rs, without amsgrad), AdamW::update (zyx-optim/src/adamw.rs:51-97), first
+//                   and later steps, all matched tensors of one update grouped into one multi-tensor program
 // A Rust port of this file is what `backend/b200.rs` carries; the mirror exists because the image has no Rust toolchain
 // and the matcher has to be testable on the CPU.  Symbolic (non-constant) shapes never match, as in the reference
 // (Graph::const_shape returns None).
@@ -211,7 +215,14 @@ class Graph {
   }
 
   // ---- matmul ------------------------------------------------------------------------------------------------------------
-  struct MatMul { ClassId a, b, out; uint64_t m, n, k, batch; bool trans_b, b_shared; int dtype; };
+  // a Permute that exchanges the last two axes and leaves the others where they are (`t()`, `transpose(-2, -1)`)
+  static bool swaps_last_two(const std::vector<int>& axes) {
+    const size_t r = axes.size();
+    if (r < 2) return false;
+    for (size_t i = 0; i + 2 < r; ++i) if (axes[i] != (int)i) return false;
+    return axes[r - 2] == (int)r - 1 && axes[r - 1] == (int)r - 2;
+  }
+  struct MatMul { ClassId a, b, out; uint64_t m, n, k, batch; bool trans_b, b_shared; int dtype; bool trans_a = false; };
 
   // The canonical broadcast-reduce form of Tensor::dot (tensor/mod.rs:1469-1490), ending at class `cid`:
   //   a [.., m, k] -Reshape [.., m, 1, k]-> Expand -+
@@ -256,12 +267,7 @@ class Graph {
     ClassId bt = *eb;
     const Node* perm = nullptr;
     for (;;) {
-      perm = find(bt, [](const Node& n) {
-        if (n.kind != K_PERMUTE || n.axes.size() < 2) return false;
-        const size_t r = n.axes.size();
-        for (size_t i = 0; i + 2 < r; ++i) if (n.axes[i] != (int)i) return false;
-        return n.axes[r - 2] == (int)r - 1 && n.axes[r - 1] == (int)r - 2;
-      });
+      perm = find(bt, [](const Node& n) { return n.kind == K_PERMUTE && swaps_last_two(n.axes); });
       if (perm) break;
       auto s = reshape_src(bt);
       if (!s) return std::nullopt;
@@ -273,10 +279,19 @@ class Graph {
     bool trans_b = false;
     // NT on a stored tensor: b is itself `w.t()` of a [.., n, k] tensor (Linear passes W.t() to dot, which transposes again)
     if (const Node* p2 = find(b, [&](const Node& n) { return n.kind == K_PERMUTE && n.axes == perm->axes; })) { b = p2->x; trans_b = true; }
+    // TN on a stored tensor: a is `x.t()` of a [.., k, m] tensor (a weight gradient written as `x.t().dot(dz)`); the kernel
+    // reads x where it lies
+    bool trans_a = false;
+    if (const Node* pa = find(a, [](const Node& n) { return n.kind == K_PERMUTE && swaps_last_two(n.axes); })) {
+      const auto as = shape(pa->x);
+      if (as.size() >= 2 && as[as.size() - 2] == k && as.back() == m) { a = pa->x; trans_a = true; }
+    }
     const int dt = dtype(b);
     if (dtype(a) != dt || dtype(cid) != dt) return std::nullopt;      // C is stored in the operands' dtype; accumulation is f32 / i32
     if (!(dt == ZYXB_F32 || dt == ZYXB_BF16 || dt == ZYXB_F16 || dt == ZYXB_I32)) return std::nullopt;
-    return MatMul{a, b, cid, m, n, k, numel(batch_dims), trans_b, b_shared, dt};
+    MatMul mm{a, b, cid, m, n, k, numel(batch_dims), trans_b, b_shared, dt};
+    mm.trans_a = trans_a;
+    return mm;
   }
 
   static zyxb_kernel_desc gemm_desc(const MatMul& mm, int epi, bool preact, float alpha) {
@@ -284,7 +299,7 @@ class Graph {
     d.kind = ZYXB_KIND_GEMM;
     auto& g = d.u.gemm;
     g.dtype = mm.dtype; g.m = mm.m; g.n = mm.n; g.k = mm.k; g.batch = mm.batch;
-    g.trans_a = 0; g.trans_b = mm.trans_b;
+    g.trans_a = mm.trans_a; g.trans_b = mm.trans_b;
     g.stride_a = (int64_t)(mm.m * mm.k); g.stride_b = mm.b_shared ? 0 : (int64_t)(mm.k * mm.n); g.stride_c = (int64_t)(mm.m * mm.n);
     g.epilogue = epi; g.store_preact = preact; g.alpha = alpha;
     return d;
@@ -366,7 +381,7 @@ class Graph {
     const int epi = bias == NONE ? ZYXB_EPI_NONE : act == 2 ? ZYXB_EPI_BIAS_GELU : act == 1 ? ZYXB_EPI_BIAS_RELU : ZYXB_EPI_BIAS;
     const bool preact = act == 2 && wanted.count(e) != 0;
     Match mt;
-    mt.pattern = std::string(mm.trans_b ? "matmul_nt" : "matmul_nn") + (mm.batch > 1 ? "_batched" : "") + (bias != NONE ? "_bias" : "") +
+    mt.pattern = std::string("matmul_") + (mm.trans_a ? "t" : "n") + (mm.trans_b ? "t" : "n") + (mm.batch > 1 ? "_batched" : "") + (bias != NONE ? "_bias" : "") +
                  (act == 2 ? "_gelu" : act == 1 ? "_relu" : "");
     mt.desc = gemm_desc(mm, epi, preact, sc->second);
     mt.inputs = {mm.a, mm.b};
@@ -414,11 +429,11 @@ class Graph {
     auto pv_cls = permute_src(*r, {0, 2, 1, 3});
     if (!pv_cls) return std::nullopt;
     auto pv = match_matmul(*pv_cls);
-    if (!pv || pv->trans_b || pv->b_shared) return std::nullopt;
+    if (!pv || pv->trans_a || pv->trans_b || pv->b_shared) return std::nullopt;
     auto sm = match_softmax(pv->a);
     if (!sm) return std::nullopt;
     auto sc = match_matmul_scaled(sm->inputs[0]);
-    if (!sc || !sc->first.trans_b || sc->first.b_shared) return std::nullopt;
+    if (!sc || sc->first.trans_a || !sc->first.trans_b || sc->first.b_shared) return std::nullopt;
     const MatMul& qk = sc->first;
     auto xq = head_split_src(qk.a), xk = head_split_src(qk.b), xv = head_split_src(pv->b);
     if (!xq || !xk || !xv) return std::nullopt;
