@@ -177,15 +177,24 @@ uint32_t zyxb_mgraph_expand(zyxb_mgraph* g, uint32_t x, const uint64_t* shape, i
 uint32_t zyxb_mgraph_reshape(zyxb_mgraph* g, uint32_t x, const uint64_t* shape, int32_t rank);            /* Node::Reshape */
 uint32_t zyxb_mgraph_permute(zyxb_mgraph* g, uint32_t x, const int32_t* axes, int32_t rank);              /* Node::Permute */
 uint32_t zyxb_mgraph_reduce(zyxb_mgraph* g, uint32_t x, int32_t rop, const int32_t* axes, int32_t n_axes); /* Node::Reduce */
+/* Node::Pad: `lp` zeros in front of `axis` (negative: that many elements cut off), `len` = the axis' extent afterwards */
+uint32_t zyxb_mgraph_pad(zyxb_mgraph* g, uint32_t x, int32_t axis, int64_t lp, uint64_t len);
 uint32_t zyxb_mgraph_cast(zyxb_mgraph* g, uint32_t x, int32_t dtype);                                     /* Node::Cast */
 uint32_t zyxb_mgraph_unary(zyxb_mgraph* g, uint32_t x, int32_t uop);                                      /* Node::Unary */
 uint32_t zyxb_mgraph_binary(zyxb_mgraph* g, uint32_t x, uint32_t y, int32_t bop);                         /* Node::Binary */
 /* dtype, rank, shape (up to 8 extents) of a class and how many Node::Kernel alternatives match_graph has pushed into it */
 int32_t  zyxb_mgraph_class_info(zyxb_mgraph* g, uint32_t cls, int32_t* out_dtype, int32_t* out_rank, uint64_t* out_shape8, int32_t* out_kernel_nodes);
 
+/* The value of a class that depends on no stored tensor (constants under movement ops, paddings, reductions, casts and
+ * arithmetic - how Tensor::arange and one-hot masks are built, tensor/mod.rs:773-781, 1920-1946), row-major as doubles: the
+ * constant folding the cross-entropy pattern uses to recognise its arange.  IncorrectKernelArg when the class reads a Leaf,
+ * uses an op outside that set or has an intermediate of more than 2^22 elements.  *out_n = element count; at most `capacity`
+ * values are written. */
+int32_t  zyxb_mgraph_const_value(zyxb_mgraph* g, uint32_t cls, double* out, uint64_t capacity, uint64_t* out_n);
+
 /* One recognised subgraph: what to hand to zyxb_program_create, and the classes whose buffers are the launch arguments
  * (inputs then outputs, the order Device::launch receives, backend/mod.rs:974).  Patterns: matmul_nn / matmul_nt / matmul_tn / matmul_tt
- * [_batched][_bias[_relu|_gelu]], attention, softmax, ln_softmax, layernorm, mse_loss, sum, max, mean, var, std, colsum, sgd, sgd_momentum,
+ * [_batched][_bias[_relu|_gelu]], attention, softmax, ln_softmax, layernorm, cross_entropy, mse_loss, sum, max, mean, var, std, colsum, sgd, sgd_momentum,
  * sgd_nesterov, adam, adam_first_step, adamw, adamw_first_step.  An optimizer match covers every parameter of the update (inputs p.., g.. [, m.., v.. |
  * , buf..]; outputs p' [, m', v' | , buf'] per tensor - the kernel updates in place, so the shim binds each output to its
  * input's buffer); its desc.u.optim.numel points into the graph mirror.  optim_step is the step t the matched update belongs to

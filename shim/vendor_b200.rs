@@ -2,16 +2,17 @@
 //
 // NOT COMPILED (no Rust toolchain in the build image).  It is a line-by-line port of zyx_b200/csrc/host/matcher.hpp, the C++
 // matcher that tests/test_matcher.py exercises through the C ABI on node lists transcribed from Tensor::dot, Linear::forward,
-// softmax, ln_softmax, LayerNorm::forward, SGD::update and AdamW::update; function names and order are kept the same so the two
+// softmax, ln_softmax, LayerNorm::forward, cross_entropy, SGD::update, Adam::update and AdamW::update; function names and order are kept the same so the two
 // can be read side by side.  It extends Graph::match_matmul (vendor/matmul.rs:43-71) and reuses the helpers of
 // vendor/mod.rs:28-95 (`const_shape`).
 
 #![allow(unused)]
 
-use std::collections::BTreeSet;
+use std::collections::{BTreeMap, BTreeSet};
 
 use crate::{
     DType,
+    dtype::Constant,
     backend::b200::{ZyxbDescUnion, ZyxbGemmDesc, ZyxbKernelDesc, ZyxbOptimDesc, ZyxbRowreduceDesc, ZYXB_KIND_GEMM, ZYXB_KIND_OPTIM, ZYXB_KIND_ROWREDUCE},
     graph::{ClassId, Graph, Node},
     kernel::{BOp, UOp},
@@ -30,6 +31,15 @@ pub(crate) struct B200Match {
     pub(crate) optim_step: u64,
 }
 
+/// A constant's value as f64 (Constant::cast, dtype.rs:502-518, widens every variant).
+fn const_f64(k: Constant) -> f64 {
+    match k.cast(DType::F64) { Constant::F64(b) => f64::from_le_bytes(b), _ => unreachable!() }
+}
+/// What a Cast node does to a folded value: Bool is `!= 0`, f32 rounds, the integer types truncate.
+fn cast_value(v: f64, dt: DType) -> f64 {
+    match dt { DType::Bool => (v != 0.0) as u8 as f64, DType::F32 => v as f32 as f64, DType::F64 | DType::BF16 | DType::F16 => v, _ => v.trunc() }
+}
+
 #[derive(Clone, Copy)]
 struct MatMulX { a: ClassId, b: ClassId, m: Dim, n: Dim, k: Dim, batch: Dim, trans_a: bool, trans_b: bool, b_shared: bool, dtype: DType }
 
@@ -39,7 +49,7 @@ struct Update { algo: i32, p: ClassId, g: ClassId, m: Option<ClassId>, v: Option
                 mom: f64, damp: f64, nesterov: bool }      // SGD with momentum: m / m_new are the buffer
 
 const RR_SUM: i32 = 0; const RR_MAX: i32 = 1; const RR_MEAN: i32 = 3; const RR_SOFTMAX: i32 = 6; const RR_LN_SOFTMAX: i32 = 7; const RR_LAYERNORM: i32 = 8; const RR_MSE: i32 = 14;
-const RR_VAR: i32 = 4; const RR_STD: i32 = 5; const RR_COLSUM: i32 = 13;
+const RR_VAR: i32 = 4; const RR_STD: i32 = 5; const RR_COLSUM: i32 = 13; const RR_CROSS_ENTROPY: i32 = 9;
 const EPI_NONE: i32 = 0; const EPI_BIAS: i32 = 1; const EPI_BIAS_RELU: i32 = 2; const EPI_BIAS_GELU: i32 = 3;
 const OPT_SGD: i32 = 0; const OPT_ADAM: i32 = 1; const OPT_ADAMW: i32 = 2;
 
@@ -86,7 +96,7 @@ impl Graph {
     /// a scalar constant under Expand / Reshape / Cast wrappers (tensor/mod.rs:3033-3113: rank-0 operands are cast and expanded)
     fn const_value(&self, mut c: ClassId) -> Option<f64> {
         loop {
-            if let Some(v) = self.find_in(c, |n| match n { Node::Const(k) => Some(k.as_f64()), _ => None }) { return Some(v); }
+            if let Some(v) = self.find_in(c, |n| match n { Node::Const(k) => Some(const_f64(*k)), _ => None }) { return Some(v); }
             if let Some(x) = self.expand_of(c) { c = x; continue; }
             if let Some(x) = self.reshape_of(c) { c = x; continue; }
             if let Some(x) = self.cast_src(c) { c = x; continue; }
@@ -357,6 +367,135 @@ impl Graph {
         if !f32s || self.const_shape(y)? != xs || self.const_shape(t)? != xs { return None; }
         Some(self.row_match("mse_loss", self.row_desc(RR_MSE, y)?, vec![y, t], cid))
     }
+    // ---- constant folding ---------------------------------------------------------------------------------------------------
+    /// The value of a class that depends on no stored tensor: constants under movement ops, paddings, reductions, casts and
+    /// arithmetic, the way the index helpers build them (Tensor::arange is `full(step).cumsum(0) + start - step`,
+    /// tensor/mod.rs:773-781; a cumsum is a padded, pooled sum, reduce_ops.rs:1076-1091).  Row-major, as f64 (exact for index
+    /// arithmetic).  None when a Leaf is reached, an op is not covered, a dim is symbolic or an intermediate has more than 2^22
+    /// elements.
+    fn const_eval(&self, c: ClassId) -> Option<Vec<f64>> {
+        self.eval_class(c, 1 << 22, &mut BTreeMap::new(), 0)
+    }
+    fn eval_class(&self, c: ClassId, limit: u64, memo: &mut BTreeMap<ClassId, Option<Vec<f64>>>, depth: u32) -> Option<Vec<f64>> {
+        if let Some(v) = memo.get(&c) { return v.clone(); }
+        let v = self.eval_node(c, limit, memo, depth);
+        memo.insert(c, v.clone());
+        v
+    }
+    fn eval_node(&self, c: ClassId, limit: u64, memo: &mut BTreeMap<ClassId, Option<Vec<f64>>>, depth: u32) -> Option<Vec<f64>> {
+        fn unravel(mut i: u64, shape: &[Dim], idx: &mut [u64]) { for a in (0..shape.len()).rev() { idx[a] = i % shape[a]; i /= shape[a]; } }
+        fn strides(shape: &[Dim]) -> Vec<u64> { let mut st = vec![1; shape.len()]; for a in (1..shape.len()).rev() { st[a - 1] = st[a] * shape[a]; } st }
+        if depth > 256 { return None; }
+        let os = self.const_shape(c)?;
+        let on: u64 = os.iter().product();
+        if on > limit { return None; }
+        let mut idx = vec![0u64; 16];
+        match &self.nodes[self.classes[c].nodes[0]].node {
+            Node::Const(k) => Some(vec![const_f64(*k)]),
+            Node::Reshape { x, .. } => self.eval_class(*x, limit, memo, depth + 1),
+            Node::Expand { x, .. } => {
+                let (xv, xs) = (self.eval_class(*x, limit, memo, depth + 1)?, self.const_shape(*x)?);
+                let (st, lead) = (strides(&xs), os.len() - xs.len());
+                Some((0..on).map(|o| {
+                    unravel(o, &os, &mut idx);
+                    xv[(0..xs.len()).filter(|&a| xs[a] != 1).map(|a| idx[lead + a] * st[a]).sum::<u64>() as usize]
+                }).collect())
+            }
+            Node::Permute { x, axes } => {
+                let (xv, st) = (self.eval_class(*x, limit, memo, depth + 1)?, strides(&self.const_shape(*x)?));
+                Some((0..on).map(|o| {
+                    unravel(o, &os, &mut idx);
+                    xv[axes.iter().enumerate().map(|(j, &a)| idx[j] * st[a as usize]).sum::<u64>() as usize]
+                }).collect())
+            }
+            Node::Pad { x, axis, lp, .. } => {
+                let (xv, xs) = (self.eval_class(*x, limit, memo, depth + 1)?, self.const_shape(*x)?);
+                let lp = self.find_in(*lp, |n| match n { Node::Const(k) => Some(const_f64(*k) as i64), _ => None })?;
+                let (st, ax) = (strides(&xs), *axis as usize);
+                Some((0..on).map(|o| {
+                    unravel(o, &os, &mut idx);
+                    let at = idx[ax] as i64 - lp;
+                    if at < 0 || at >= xs[ax] as i64 { return 0.0; }                  // a zero of the padding
+                    xv[(0..xs.len()).map(|a| (if a == ax { at as u64 } else { idx[a] }) * st[a]).sum::<u64>() as usize]
+                }).collect())
+            }
+            Node::Reduce { x, rop, axes } => {
+                let (xv, xs) = (self.eval_class(*x, limit, memo, depth + 1)?, self.const_shape(*x)?);
+                let init = match rop { BOp::Add => 0.0, BOp::Mul => 1.0, BOp::Max => f64::NEG_INFINITY, _ => return None };
+                let mut out = vec![init; on as usize];
+                for (i, &v) in xv.iter().enumerate() {
+                    unravel(i as u64, &xs, &mut idx);
+                    let o = (0..xs.len()).filter(|a| !axes.contains(&(*a as _))).fold(0, |o, a| o * xs[a] + idx[a]) as usize;
+                    out[o] = match rop { BOp::Add => out[o] + v, BOp::Mul => out[o] * v, _ => out[o].max(v) };
+                }
+                Some(out)
+            }
+            Node::Cast { x, dtype } => Some(self.eval_class(*x, limit, memo, depth + 1)?.into_iter().map(|v| cast_value(v, *dtype)).collect()),
+            Node::Unary { x, uop } => self.eval_class(*x, limit, memo, depth + 1)?.into_iter().map(|v| Some(match uop {
+                UOp::Neg => -v, UOp::Abs => v.abs(), UOp::Floor => v.floor(), UOp::Trunc => v.trunc(), UOp::Exp => v.exp(), UOp::Ln => v.ln(),
+                UOp::Sqrt => v.sqrt(), UOp::Reciprocal => 1.0 / v, _ => return None,
+            })).collect(),
+            Node::Binary { x, y, bop } => {
+                let (xv, yv) = (self.eval_class(*x, limit, memo, depth + 1)?, self.eval_class(*y, limit, memo, depth + 1)?);
+                if xv.len() != yv.len() || xv.len() as u64 != on { return None; }
+                let whole = !self.dtype(*x).is_float();
+                xv.into_iter().zip(yv).map(|(a, b)| Some(match bop {
+                    BOp::Add => a + b, BOp::Sub => a - b, BOp::Mul => a * b, BOp::Max => a.max(b),
+                    BOp::Div => { if whole && b == 0.0 { return None; } if whole { (a / b).trunc() } else { a / b } }
+                    BOp::Mod => { if b == 0.0 { return None; } a % b }
+                    BOp::Cmplt => (a < b) as u8 as f64, BOp::Cmpgt => (a > b) as u8 as f64, BOp::Cmpge => (a >= b) as u8 as f64,
+                    BOp::NotEq => (a != b) as u8 as f64, BOp::Eq => (a == b) as u8 as f64,
+                    _ => return None,
+                })).collect()
+            }
+            _ => None,
+        }
+    }
+
+    // ---- cross-entropy with class-index targets -----------------------------------------------------------------------------
+    /// c = [Cast]{Eq{Expand{labels.reshape([n, 1])}, Expand{arange(classes)}}}, either operand order -> labels [n]
+    /// (Tensor::one_hot_along_dim of the unsqueezed labels, tensor/mod.rs:1920-1946).  The arange is recognised by its value;
+    /// i32 labels only (what the program reads).
+    fn one_hot_labels(&self, c: ClassId, n: Dim, classes: Dim) -> Option<ClassId> {
+        let c = self.cast_src(c).unwrap_or(c);
+        let (x, y) = self.binary_of(c, BOp::Eq)?;
+        for (a, b) in [(x, y), (y, x)] {
+            let (Some(ea), Some(eb)) = (self.expand_of(a), self.expand_of(b)) else { continue };
+            if self.const_shape(ea).as_deref() != Some(&[n, 1][..]) { continue; }
+            let bs = self.const_shape(eb)?;
+            if bs != [classes] && bs != [1, classes] { continue; }
+            let Some(labels) = self.reshape_of(ea) else { continue };
+            if self.const_shape(labels).as_deref() != Some(&[n][..]) || self.dtype(labels) != DType::I32 { continue; }
+            let Some(v) = self.const_eval(eb) else { continue };
+            if v.len() as u64 == classes && v.iter().enumerate().all(|(i, &k)| k == i as f64) { return Some(self.canon(labels)); }
+        }
+        None
+    }
+    /// Tensor::cross_entropy(labels, ReduceOp::Mean) on f32 logits [n, classes] (tensor/mod.rs:1639-1656):
+    ///   per_sample = (-logits.ln_softmax([1]) * one_hot(labels)).sum([1]);  loss = per_sample.mean_all()
+    /// -> one program, args logits, labels -> per_sample, loss.
+    fn match_cross_entropy(&self, cid: ClassId) -> Option<B200Match> {
+        if self.dtype(cid) != DType::F32 { return None; }
+        let (sum, n) = self.binary_const(cid, BOp::Div)?;
+        let (ps, axes) = self.find_in(sum, |nd| match nd { Node::Reduce { x, rop: BOp::Add, axes } => Some((*x, axes.clone())), _ => None })?;
+        let per_sample = self.canon(ps);
+        let pshape = self.const_shape(per_sample)?;
+        if pshape.len() != 1 || axes.len() != 1 || (n - pshape[0] as f64).abs() > 0.5 || self.dtype(per_sample) != DType::F32 { return None; }
+        let prod = self.reduce_last(per_sample, BOp::Add)?;
+        let nc = self.const_shape(prod)?;
+        if nc.len() != 2 || nc[0] != pshape[0] { return None; }
+        let (a, b) = self.binary_of(prod, BOp::Mul)?;
+        for (neg, target) in [(a, b), (b, a)] {
+            let Some(ls) = self.unary_of(neg, UOp::Neg).and_then(|l| self.match_ln_softmax(l)) else { continue };
+            let logits = ls.inputs[0];
+            if self.dtype(logits) != DType::F32 || self.const_shape(logits)? != nc { continue; }
+            let Some(labels) = self.one_hot_labels(target, nc[0], nc[1]) else { continue };
+            let mut m = self.row_match("cross_entropy", self.row_desc(RR_CROSS_ENTROPY, logits)?, vec![logits, labels], per_sample);
+            m.outputs.push(cid);
+            return Some(m);
+        }
+        None
+    }
     /// var(x, [-1]) = sum((x - mean_keepdim(x))^2) / (n - correction) (tensor/reduce_ops.rs:111-123) -> (x, correction)
     fn var_last(&self, cid: ClassId) -> Option<(ClassId, i32)> {
         let (sq, d) = self.mean_last(cid)?;
@@ -508,7 +647,7 @@ impl Graph {
                 if let Some(u) = self.match_adamw(cid).or_else(|| self.match_adam(cid)).or_else(|| self.match_sgd(cid)) { updates.push(u); continue; }
             }
             let m = self.match_attention(cid).or_else(|| self.match_linear(cid, wanted)).or_else(|| self.match_softmax(cid)).or_else(|| self.match_ln_softmax(cid))
-                .or_else(|| self.match_layernorm(cid)).or_else(|| self.match_mse(cid)).or_else(|| self.match_reduce(cid));
+                .or_else(|| self.match_layernorm(cid)).or_else(|| self.match_cross_entropy(cid)).or_else(|| self.match_mse(cid)).or_else(|| self.match_reduce(cid));
             out.extend(m);
         }
         let mut used = vec![false; updates.len()];

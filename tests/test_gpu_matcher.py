@@ -152,3 +152,25 @@ def test_sgd_with_momentum_from_graph_to_launch(sess, nesterov):
         assert max_rel_err(got_p, want_p) <= TOL_F32 and max_rel_err(got_b, want_b) <= TOL_F32
     finally:
         g.close()
+
+
+def test_cross_entropy_from_graph_to_launch(sess):
+    """logits.cross_entropy(labels, Mean) traced with class-index labels (the one-hot compares against a folded arange),
+    matched as one program: logits, labels -> per-sample losses, mean."""
+    rng = np.random.default_rng(35)
+    g = MGraph()
+    try:
+        logits, labels = T.leaf(g, L.F32, (64, 10)), T.leaf(g, L.I32, (64,))
+        loss, per_sample = logits.cross_entropy(labels)
+        m = next(x for x in g.match([loss.cls]) if x.pattern == b"cross_entropy")
+        assert list(m.outputs[:m.n_outputs]) == [per_sample.cls, loss.cls]
+        xv = (3.0 * rng.standard_normal((64, 10))).astype(np.float32)
+        yv = rng.integers(0, 10, 64).astype(np.int32)
+        got = run_match(sess, g, m, {logits.cls: xv, labels.cls: yv})
+        want_per, want_mean = zo.cross_entropy(xv, yv)
+        x64 = xv.astype(np.float64)
+        exact = np.log(np.exp(x64 - x64.max(1, keepdims=True)).sum(1)) + x64.max(1) - x64[np.arange(64), yv]
+        assert_parity(got[per_sample.cls], want_per, exact, TOL_F32, row_axis=0, what="matched ce per-sample")
+        assert_parity(got[loss.cls].reshape(1), want_mean, np.array([exact.mean()]), TOL_F32, row_axis=0, what="matched ce mean")
+    finally:
+        g.close()

@@ -381,3 +381,107 @@ def test_var_std_and_column_sums(g, dtype):
     m = at[cs.cls]
     assert m.pattern == b"colsum" and list(m.inputs[:m.n_inputs]) == [x.cls]
     assert_same_row(m.desc, B.rowreduce_desc(L.RR_COLSUM, dtype, 48, 320))
+
+
+def test_constant_index_tensors_are_folded(g):
+    """Tensor::arange is `full(step).cumsum(0) + start - step` and a cumsum is a padded, pooled sum (tensor/mod.rs:773-781,
+    reduce_ops.rs:1076-1091): the mirror carries Pad nodes and folds such constant subgraphs to their values; anything that
+    reads a stored tensor has no constant value."""
+    assert g.const_value(T.arange(g, 0, 10, 1).cls) == [float(i) for i in range(10)]
+    assert g.const_value(T.arange(g, 3, 23, 4).cls) == [3.0, 7.0, 11.0, 15.0, 19.0]
+    ones = T.full(g, [2, 3], 1, L.I32)
+    assert g.const_value(ones.pad_zeros([(1, 0), (0, 2)]).cls) == [0, 0, 0, 0, 0] + [1, 1, 1, 0, 0] * 2
+    assert g.const_value(T.arange(g, 0, 6, 1).reshape([2, 3]).t().slice([(1, 3), (0, 2)]).cls) == [1.0, 4.0, 2.0, 5.0]
+    assert g.const_value(T.arange(g, 0, 4, 1).repeat([2]).cls) == [0.0, 1.0, 2.0, 3.0] * 2
+    assert g.const_value(T.arange(g, 1, 5, 1).cumsum(0).cls) == [1.0, 3.0, 6.0, 10.0]
+    assert g.const_value((T.arange(g, 0, 4, 1).cast(L.F32) * 0.5).cast(L.I32).cls) == [0.0, 0.0, 1.0, 1.0]
+    labels = T.leaf(g, L.I32, (4,))
+    assert g.const_value(labels.unsqueeze(1).one_hot_along_dim(3, 1).cls) is None
+    assert g.const_value(T.arange(g, 0, 3000, 1).cls) is None          # the pooled intermediate is past the folding limit
+    with pytest.raises(ValueError):
+        g.pad(labels.cls, 0, -2, 0)                                    # nothing of the axis would be left
+
+
+def test_cross_entropy_with_class_indices_is_the_loss_program(g):
+    """logits.cross_entropy(labels, Mean) as SimpleNet's training loop calls it (zyx-examples/examples/mnist.rs:66-67;
+    tensor/mod.rs:1639-1656): one program reading the logits and the i32 labels, writing the per-sample losses and their mean
+    - the descriptor of the Linear-stack plan's loss launch (host/trainer.cpp).  The one-hot matrix is recognised by folding
+    its arange; the log-probabilities and the per-sample sum stay matched on their own as alternatives."""
+    logits, labels = T.leaf(g, L.F32, (64, 10)), T.leaf(g, L.I32, (64,))
+    loss, per_sample = logits.cross_entropy(labels)
+    ms = g.match([loss.cls])
+    m = by_pattern(ms)["cross_entropy"]
+    assert_same_row(m.desc, B.rowreduce_desc(L.RR_CROSS_ENTROPY, L.F32, 64, 10))
+    assert list(m.inputs[:m.n_inputs]) == [logits.cls, labels.cls]
+    assert list(m.outputs[:m.n_outputs]) == [per_sample.cls, loss.cls]
+    assert g.info(loss.cls)[2] == 1 and g.info(per_sample.cls)[2] >= 1      # Node::Kernel alternatives in both output classes
+    assert {"ln_softmax", "sum"} <= set(by_pattern(ms))
+
+
+def test_what_only_looks_like_a_one_hot_is_not_the_loss_program(g):
+    """The comparison must be against 0 .. classes-1 along the class axis with i32 labels along the rows: an arange that starts
+    at 1, labels of another integer type (the program reads i32), labels laid along the class axis of a square problem, and a
+    stored one-hot matrix of floats all fall back to the separate row programs."""
+    def patterns(build):
+        g2 = MGraph()
+        try:
+            return set(by_pattern(g2.match([build(g2).cls])))
+        finally:
+            g2.close()
+
+    def shifted_arange(g2):
+        x, y = T.leaf(g2, L.F32, (32, 8)), T.leaf(g2, L.I32, (32,))
+        target = y.unsqueeze(1).equal(T.arange(g2, 1, 9, 1).cast(L.I32))
+        return (x.ln_softmax([1]).neg() * target).sum([1]).mean_all()
+
+    def wide_labels(g2):
+        x, y = T.leaf(g2, L.F32, (32, 8)), T.leaf(g2, L.I64, (32,))
+        return x.cross_entropy(y)[0]
+
+    def labels_along_the_classes(g2):
+        x, y = T.leaf(g2, L.F32, (8, 8)), T.leaf(g2, L.I32, (8,))
+        target = y.unsqueeze(0).equal(T.arange(g2, 0, 8, 1).cast(L.I32).reshape([8, 1]))
+        return (x.ln_softmax([1]).neg() * target).sum([1]).mean_all()
+
+    def stored_one_hot(g2):
+        x, t = T.leaf(g2, L.F32, (32, 8)), T.leaf(g2, L.F32, (32, 8))
+        return x.cross_entropy(t)[0]
+
+    for build in (shifted_arange, wide_labels, labels_along_the_classes, stored_one_hot):
+        got = patterns(build)
+        assert "cross_entropy" not in got and "ln_softmax" in got, (build.__name__, got)
+
+
+def test_matched_cross_entropy_launches_through_the_abi(g):
+    """From the match to a launch without a GPU: the descriptor goes to zyxb_program_create and the matched classes name the
+    launch arguments (loads, then stores) - here against the host-memory stand-in of the ABI (tests/fake), whose loss is
+    computed in float64; the same path on the device is tests/test_gpu_matcher.py."""
+    import ctypes as C
+
+    import numpy as np
+
+    from tests.fake.harness import Fake
+
+    logits, labels = T.leaf(g, L.F32, (48, 10)), T.leaf(g, L.I32, (48,))
+    loss, per_sample = logits.cross_entropy(labels)
+    m = by_pattern(g.match([loss.cls]))["cross_entropy"]
+    rng = np.random.default_rng(5)
+    values = {logits.cls: rng.standard_normal((48, 10)).astype(np.float32), labels.cls: rng.integers(0, 10, 48).astype(np.int32)}
+    fake = Fake()
+    prog = C.c_uint32()
+    assert fake.lib.zyxb_program_create(fake.ctx, 0, C.byref(m.desc), C.byref(prog)) == L.OK, fake.last_error()
+    bufs = []
+    for cls in list(m.inputs[:m.n_inputs]) + list(m.outputs[:m.n_outputs]):
+        nbytes = 4 * int(np.prod(g.info(cls)[1]) or 1)
+        b = C.c_uint32()
+        assert fake.lib.zyxb_alloc(fake.ctx, 0, nbytes, C.byref(b), None) == L.OK
+        if cls in values:
+            fake.upload(b.value, values[cls])
+        bufs.append(b.value)
+    args = (C.c_uint32 * len(bufs))(*bufs)
+    assert fake.lib.zyxb_launch(fake.ctx, 0, prog.value, args, len(bufs), None, 0, None) == L.OK, fake.last_error()
+    x = values[logits.cls].astype(np.float64)
+    lse = np.log(np.exp(x - x.max(1, keepdims=True)).sum(1)) + x.max(1)
+    want = lse - x[np.arange(48), values[labels.cls]]
+    np.testing.assert_allclose(fake.download(bufs[2], (48,)), want, rtol=1e-6)
+    np.testing.assert_allclose(fake.download(bufs[3], (1,)), [want.mean()], rtol=1e-6)

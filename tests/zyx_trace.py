@@ -8,11 +8,24 @@ TEST INFRASTRUCTURE: each method restates the decomposition of the reference met
     dot            tensor/mod.rs:1469-1490;  softmax / ln_softmax 1427-1461;  relu / gelu / tanh / exp / sqrt elementwise.rs
     Linear         zyx-nn/src/linear.rs:39-45;  LayerNorm zyx-nn/src/layer_norm.rs:95-135
     SGD / AdamW    zyx-optim/src/sgd.rs:45-84, adamw.rs:51-97
+    index helpers  pad_zeros / rpad_zeros (tensor/mod.rs:1120-1226: one Pad node per padded axis, negative amounts cut),
+                   slice (index_ops.rs:84-160: negative paddings, then squeeze's reshape), repeat (2766-2783), pool (2442-2543),
+                   cumsum (reduce_ops.rs:1076-1091), full (745-754), arange (773-781), one_hot_along_dim (1920-1946),
+                   cross_entropy with class-index targets (1639-1656)
 Every `.cast(dtype)` pushes a Cast node, also when the dtype does not change (zyx/src/runtime.rs:696-700)."""
 import math
 
 from zyx_b200 import _lib as L
 from zyx_b200 import matcher as M
+
+
+# DType::least_upper_dtype (zyx/src/dtype.rs:121-129): the later of the two in this order
+_ORDER = [L.BOOL, L.U8, L.U16, L.U32, L.U64, L.I8, L.I16, L.I32, L.I64, L.BF16, L.F16, L.F32, L.F64]
+_UINTS, _INTS = (L.U8, L.U16, L.U32, L.U64), (L.I8, L.I16, L.I32, L.I64)
+
+
+def _least_upper(a, b):
+    return _ORDER[max(_ORDER.index(a), _ORDER.index(b))]
 
 
 class T:
@@ -58,6 +71,106 @@ class T:
         axes[-1], axes[-2] = axes[-2], axes[-1]
         return self.permute(axes)
 
+    def transpose(self, d0, d1):
+        axes = list(range(len(self.shape)))
+        d0, d1 = d0 % len(axes), d1 % len(axes)
+        axes[d0], axes[d1] = axes[d1], axes[d0]
+        return self.permute(axes)
+
+    def unsqueeze(self, dim):
+        shape = list(self.shape)
+        dim = dim if dim >= 0 else len(shape) + dim + 1
+        return self.reshape(shape[:dim] + [1] + shape[dim:])
+
+    def squeeze(self, axes):
+        shape = list(self.shape)
+        axes = [a % len(shape) for a in axes]
+        return self.reshape([d for a, d in enumerate(shape) if d != 1 or a not in axes] or [1])
+
+    def _pad_axis(self, axis, left, right):
+        orig = self.shape[axis]
+        return T(self.g, self.g.pad(self.cls, axis, left, orig + left + right))
+
+    def pad_zeros(self, padding):
+        """(left, right) per axis from the first axis on; axes with (0, 0) push no node"""
+        cur = self
+        for axis, (left, right) in enumerate(padding):
+            if left != 0 or right != 0:
+                cur = cur._pad_axis(axis, left, right)
+        return cur
+
+    def rpad_zeros(self, padding):
+        """the same from the last axis backwards"""
+        rank = len(self.shape)
+        padding = list(padding) + [(0, 0)] * (rank - len(padding))
+        padding.reverse()
+        return self.pad_zeros(padding)
+
+    def slice(self, ranges):
+        """ranges: (start, end) per leading axis, 0 <= start <= end <= extent"""
+        shape = self.shape
+        return self.pad_zeros([(-s, -(d - e)) for (s, e), d in zip(ranges, shape)]).squeeze([])
+
+    def repeat(self, repeats):
+        shape = list(self.shape)
+        lead = len(repeats) - len(shape)
+        base = [1] * lead + shape
+        new_shape = [d for b in base for d in (1, b)]
+        expand_shape = [d for r, b in zip(repeats, base) for d in (r, b)]
+        return self.reshape(new_shape).expand(expand_shape).reshape([r * b for r, b in zip(repeats, base)])
+
+    def pool(self, kernel_size, stride=1, dilation=1):
+        """the last len(kernel_size) axes become (output positions.., kernel offsets..)"""
+        k_ = list(kernel_size)
+        s_ = [stride] * len(k_) if isinstance(stride, int) else list(stride)
+        d_ = [dilation] * len(k_) if isinstance(dilation, int) else list(dilation)
+        shape = list(self.shape)
+        rank = len(shape)
+        nb = rank - len(k_)
+        i_ = shape[nb:]
+        o_ = [-(-(i - d * (k - 1)) // s) for i, d, k, s in zip(i_, d_, k_, s_)]
+        full = [(0, d) for d in shape[:nb]]
+        sh_b = shape[:nb]
+        xup = self.repeat([1] * nb + [-(-(k * (i + d)) // i) for k, i, d in zip(k_, i_, d_)])
+        xup = xup.slice(full + [(0, k * (i + d)) for k, i, d in zip(k_, i_, d_)])
+        xup = xup.reshape(sh_b + [e for k, i, d in zip(k_, i_, d_) for e in (k, i + d)])
+        xup = xup.slice(full + [r for k, o, s in zip(k_, o_, s_) for r in ((0, k), (0, o * s))])
+        xup = xup.reshape(sh_b + [e for k, o, s in zip(k_, o_, s_) for e in (k, o, s)])
+        xup = xup.slice(full + [r for k, o in zip(k_, o_) for r in ((0, k), (0, o), (0, 1))])
+        xup = xup.reshape(sh_b + [e for k, o in zip(k_, o_) for e in (k, o)])
+        return xup.permute(list(range(nb)) + [nb + 2 * i + 1 for i in range(len(i_))] + [nb + 2 * i for i in range(len(i_))])
+
+    def cumsum(self, axis):
+        n = self.shape[axis % len(self.shape)]
+        x = self.transpose(axis, -1).rpad_zeros([(n - 1, 0)]).pool([n], 1, 1).sum([-1])
+        return x.transpose(axis, -1)
+
+    @staticmethod
+    def full(g, shape, value, dtype):
+        return T.scalar(g, value, dtype).expand(list(shape))            # Runtime::new_full: the constant, expanded
+
+    @staticmethod
+    def arange(g, start, stop, step, dtype=L.I64):
+        n = (stop - start) // step
+        return T.full(g, [n], step, dtype).cumsum(0) + T.scalar(g, start, dtype) - T.scalar(g, step, dtype)
+
+    def equal(self, rhs): return self._binary(rhs, M.B_EQ)
+
+    def one_hot_along_dim(self, num_classes, dim):
+        rank = len(self.shape)
+        dim = dim % rank
+        offset = rank - dim - 1
+        arange = T.arange(self.g, 0, num_classes, 1).cast(L.I32).reshape([num_classes] + [1] * offset)
+        return self.equal(arange)
+
+    def cross_entropy(self, target):
+        """ReduceOp::Mean; -> (loss, per-sample losses)"""
+        classes_dim = 0 if len(self.shape) <= 1 else 1
+        if tuple(self.shape) != tuple(target.shape):
+            target = target.unsqueeze(classes_dim).one_hot_along_dim(self.shape[classes_dim], classes_dim)
+        per_sample = (self.ln_softmax([classes_dim]).neg() * target).sum([classes_dim])
+        return per_sample.mean_all(), per_sample
+
     # ---- binary with broadcasting
     def _lift(self, other):
         return other if isinstance(other, T) else T.scalar(self.g, other)
@@ -71,11 +184,7 @@ class T:
             elif len(ys) == 0 and len(xs) != 0:
                 y = y.cast(xd)
             else:
-                common = L.F32 if L.F32 in (xd, yd) else xd          # least_upper_dtype for the cases the tests use
-                if xd == L.BOOL:
-                    common = yd
-                if yd == L.BOOL:
-                    common = xd
+                common = _least_upper(xd, yd)
                 x = x.cast(common) if xd != common else x
                 y = y.cast(common) if yd != common else y
         rx, ry = len(xs), len(ys)
@@ -97,6 +206,7 @@ class T:
     def _unary(self, uop):
         return T(self.g, self.g.unary(self.cls, uop))
 
+    def neg(self): return self._unary(M.U_NEG)
     def exp(self): return self._unary(M.U_EXP)
     def ln(self): return self._unary(M.U_LN)
     def sqrt(self): return self._unary(M.U_SQRT)
@@ -116,7 +226,7 @@ class T:
         shape = list(self.shape)
         axes = [a % len(shape) for a in axes]
         xd = self.dtype
-        acc = L.F32 if xd in (L.F32, L.BF16, L.F16) else L.I32
+        acc = _least_upper(xd, L.U32 if xd in _UINTS else L.I32 if xd in _INTS or xd == L.BOOL else L.F32)   # reduce_acc_dtype
         t = T(self.g, self.g.reduce(self.cast(acc).cls, rop, axes))
         if t.dtype != xd:
             t = t.cast(xd)

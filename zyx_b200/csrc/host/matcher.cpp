@@ -67,6 +67,14 @@ uint32_t zyxb_mgraph_reduce(zyxb_mgraph* G, uint32_t x, int32_t rop, const int32
   for (int i = 0; i < n_axes; ++i) { if (axes[i] < 0 || axes[i] >= (int32_t)G->g.shape(x).size()) return zyxb_matcher::NONE; n.axes.push_back(axes[i]); }
   return push(G, n);
 }
+uint32_t zyxb_mgraph_pad(zyxb_mgraph* G, uint32_t x, int32_t axis, int64_t lp, uint64_t len) {
+  if (!ok_class(G, x) || axis < 0 || axis >= (int32_t)G->g.shape(x).size()) return zyxb_matcher::NONE;
+  // what is cut off on either side has to leave something of the axis (Tensor::pad_axis, tensor/mod.rs:1126-1138)
+  const int64_t orig = (int64_t)G->g.shape(x)[axis], rp = (int64_t)len - lp - orig;
+  if ((int64_t)len < 0 || (lp < 0 ? -lp : 0) + (rp < 0 ? -rp : 0) >= orig) return zyxb_matcher::NONE;
+  Node n; n.kind = zyxb_matcher::K_PAD; n.x = x; n.axes = {axis}; n.lp = lp; n.len = len;
+  return push(G, n);
+}
 uint32_t zyxb_mgraph_cast(zyxb_mgraph* G, uint32_t x, int32_t dtype) {
   if (!ok_class(G, x)) return zyxb_matcher::NONE;
   Node n; n.kind = zyxb_matcher::K_CAST; n.x = x; n.dtype = dtype;
@@ -94,6 +102,15 @@ int32_t zyxb_mgraph_class_info(zyxb_mgraph* G, uint32_t c, int32_t* out_dtype, i
     for (uint32_t nid : cl.nodes) k += G->g.nodes[nid].kind == zyxb_matcher::K_KERNEL;
     *out_kernel_nodes = k;
   }
+  return ZYXB_OK;
+}
+
+int32_t zyxb_mgraph_const_value(zyxb_mgraph* G, uint32_t c, double* out, uint64_t capacity, uint64_t* out_n) {
+  if (!ok_class(G, c) || !out_n) return ZYXB_ERR_INCORRECT_KERNEL_ARG;
+  auto v = G->g.const_eval(c);
+  if (!v) { *out_n = 0; return ZYXB_ERR_INCORRECT_KERNEL_ARG; }
+  *out_n = v->size();
+  for (uint64_t i = 0; i < v->size() && i < capacity && out; ++i) out[i] = (*v)[i];
   return ZYXB_OK;
 }
 

@@ -13,7 +13,8 @@
 //   attention       the mask-free core of MultiheadAttention::forward (zyx-nn/src/multi_head_attention.rs:197-226)
 //   row kernels     softmax, ln_softmax (tensor/mod.rs:1427-1461), LayerNorm::forward (zyx-nn/src/layer_norm.rs:95-135),
 //                   sum / max / mean / var / std over the last axis (tensor/reduce_ops.rs:45-157), `sum([0])` of a matrix
-//                   (column sums), mse_loss of f32 tensors
+//                   (column sums), mse_loss of f32 tensors, cross_entropy of f32 logits with i32 class indices
+//                   (tensor/mod.rs:1639-1656; its one-hot compares against an arange recognised by constant folding)
 //   optimizer       SGD::update (zyx-optim/src/sgd.rs:45-84: plain, weight decay, momentum with dampening, Nesterov),
 //                   Adam::update (zyx-optim/src/adam.rs, without amsgrad), AdamW::update (zyx-optim/src/adamw.rs:51-97), first
 //                   and later steps, all matched tensors of one update grouped into one multi-tensor program
@@ -42,7 +43,7 @@ namespace zyxb_matcher {
 using ClassId = uint32_t;
 constexpr ClassId NONE = 0xffffffffu;
 
-enum Kind : int { K_CONST = 0, K_LEAF, K_EXPAND, K_PERMUTE, K_RESHAPE, K_REDUCE, K_CAST, K_UNARY, K_BINARY, K_KERNEL };
+enum Kind : int { K_CONST = 0, K_LEAF, K_EXPAND, K_PERMUTE, K_RESHAPE, K_REDUCE, K_CAST, K_UNARY, K_BINARY, K_KERNEL, K_PAD };
 // the order of zyx's enums (zyx/src/kernel/ops.rs:187-214 and 222-262)
 enum UOp : int { U_NEG = 0, U_BITNOT, U_EXP, U_EXP2, U_LN, U_LOG2, U_RECIPROCAL, U_SQRT, U_SIN, U_COS, U_FLOOR, U_TRUNC, U_ABS };
 enum BOp : int { B_ADD = 0, B_SUB, B_MUL, B_DIV, B_POW, B_MOD, B_CMPLT, B_CMPGT, B_CMPGE, B_MAX, B_OR, B_AND, B_BITXOR, B_BITOR, B_BITAND,
@@ -56,7 +57,9 @@ struct Node {
   double value = 0.0;            // Const
   uint32_t leaf_id = 0;
   std::vector<uint64_t> shape;   // Leaf, Expand, Reshape
-  std::vector<int> axes;         // Permute, Reduce
+  std::vector<int> axes;         // Permute, Reduce; Pad: the one padded axis
+  int64_t lp = 0;                // Pad: zeros in front of the axis (negative: that many elements cut off)
+  uint64_t len = 0;              // Pad: extent of the axis afterwards (zyx/src/graph/mod.rs:121-129)
   std::vector<ClassId> inputs, outputs;   // Kernel
   uint32_t program = 0;          // Kernel: index of the match (ProgramId once a device created the program)
   uint64_t time = 0;
@@ -101,6 +104,7 @@ class Graph {
         break;
       }
       case K_CAST: c.dtype = n.dtype; c.shape = classes[n.x].shape; break;
+      case K_PAD: c.dtype = classes[n.x].dtype; c.shape = classes[n.x].shape; c.shape[n.axes[0]] = n.len; break;
       case K_UNARY: c.dtype = classes[n.x].dtype; c.shape = classes[n.x].shape; break;
       case K_BINARY:
         c.dtype = (n.op == B_CMPLT || n.op == B_CMPGT || n.op == B_CMPGE || n.op == B_NOTEQ || n.op == B_EQ) ? ZYXB_BOOL : classes[n.x].dtype;
@@ -638,6 +642,193 @@ class Graph {
     return mul && expand_src(mul->first) && expand_src(mul->second);
   }
 
+  // ---- constant folding --------------------------------------------------------------------------------------------------
+  // The value of a class that depends on no stored tensor: constants under movement ops, paddings, reductions, casts and
+  // arithmetic, the way the reference's index helpers build them (Tensor::arange is `full(step).cumsum(0) + start - step`,
+  // tensor/mod.rs:773-781, and a cumsum is a padded, pooled sum, reduce_ops.rs:1076-1091).  Row-major values as doubles, exact
+  // for the index arithmetic this is for.  nullopt when a Leaf is reached, an op is not covered, or some intermediate has more
+  // than `limit` elements.
+  using Values = std::vector<double>;
+  std::optional<Values> const_eval(ClassId c, uint64_t limit = (1ull << 22)) const {
+    std::map<ClassId, std::optional<Values>> memo;
+    const Values* v = eval_class(c, limit, memo, 0);
+    return v ? std::optional<Values>(*v) : std::nullopt;
+  }
+  const Values* eval_class(ClassId c, uint64_t limit, std::map<ClassId, std::optional<Values>>& memo, int depth) const {
+    auto it = memo.find(c);
+    if (it == memo.end()) it = memo.emplace(c, eval_node(c, limit, memo, depth)).first;
+    return it->second ? &*it->second : nullptr;
+  }
+  static void unravel(uint64_t i, const std::vector<uint64_t>& shape, std::vector<uint64_t>& idx) {
+    for (size_t a = shape.size(); a-- > 0;) { idx[a] = i % shape[a]; i /= shape[a]; }
+  }
+  static double cast_value(double v, int dt) {
+    if (dt == ZYXB_BOOL) return v != 0.0 ? 1.0 : 0.0;
+    if (dt == ZYXB_F32) return (double)(float)v;
+    if (is_float(dt)) return v;
+    return std::trunc(v);
+  }
+  std::optional<Values> eval_node(ClassId c, uint64_t limit, std::map<ClassId, std::optional<Values>>& memo, int depth) const {
+    if (!valid(c) || depth > 256) return std::nullopt;
+    const Node& n = nodes[classes[c].nodes[0]];
+    const auto& os = shape(c);
+    const uint64_t on = numel(os);
+    if (on > limit) return std::nullopt;
+    auto arg = [&](ClassId x) { return valid(x) ? eval_class(x, limit, memo, depth + 1) : nullptr; };
+    if (n.kind == K_CONST) return Values{n.value};
+    if (n.kind == K_LEAF || n.kind == K_KERNEL) return std::nullopt;
+    const Values* x = arg(n.x);
+    if (!x) return std::nullopt;
+    const auto& xs = shape(n.x);
+    std::vector<uint64_t> xstride(xs.size(), 1);
+    for (size_t a = xs.size(); a-- > 1;) xstride[a - 1] = xstride[a] * xs[a];
+    Values out(on, 0.0);
+    std::vector<uint64_t> idx(std::max(os.size(), xs.size()), 0);
+    switch (n.kind) {
+      case K_RESHAPE: return *x;
+      case K_EXPAND: {
+        const size_t lead = os.size() - xs.size();
+        for (uint64_t o = 0; o < on; ++o) {
+          unravel(o, os, idx);
+          uint64_t src = 0;
+          for (size_t a = 0; a < xs.size(); ++a) if (xs[a] != 1) src += idx[lead + a] * xstride[a];
+          out[o] = (*x)[src];
+        }
+        return out;
+      }
+      case K_PERMUTE:
+        for (uint64_t o = 0; o < on; ++o) {
+          unravel(o, os, idx);
+          uint64_t src = 0;
+          for (size_t j = 0; j < n.axes.size(); ++j) src += idx[j] * xstride[n.axes[j]];
+          out[o] = (*x)[src];
+        }
+        return out;
+      case K_PAD: {
+        const size_t ax = (size_t)n.axes[0];
+        for (uint64_t o = 0; o < on; ++o) {
+          unravel(o, os, idx);
+          const int64_t at = (int64_t)idx[ax] - n.lp;
+          if (at < 0 || at >= (int64_t)xs[ax]) continue;                 // a zero of the padding
+          uint64_t src = 0;
+          for (size_t a = 0; a < xs.size(); ++a) src += (a == ax ? (uint64_t)at : idx[a]) * xstride[a];
+          out[o] = (*x)[src];
+        }
+        return out;
+      }
+      case K_REDUCE: {
+        if (n.op != B_ADD && n.op != B_MAX && n.op != B_MUL) return std::nullopt;
+        std::fill(out.begin(), out.end(), n.op == B_ADD ? 0.0 : n.op == B_MUL ? 1.0 : -INFINITY);
+        std::vector<char> reduced(xs.size(), 0);
+        for (int a : n.axes) reduced[a] = 1;
+        for (uint64_t i = 0; i < x->size(); ++i) {
+          unravel(i, xs, idx);
+          uint64_t o = 0;
+          for (size_t a = 0; a < xs.size(); ++a) if (!reduced[a]) o = o * xs[a] + idx[a];
+          const double v = (*x)[i];
+          out[o] = n.op == B_ADD ? out[o] + v : n.op == B_MUL ? out[o] * v : std::max(out[o], v);
+        }
+        return out;
+      }
+      case K_CAST:
+        for (uint64_t o = 0; o < on; ++o) out[o] = cast_value((*x)[o], n.dtype);
+        return out;
+      case K_UNARY:
+        for (uint64_t o = 0; o < on; ++o) {
+          const double v = (*x)[o];
+          switch (n.op) {
+            case U_NEG: out[o] = -v; break;
+            case U_ABS: out[o] = fabs(v); break;
+            case U_FLOOR: out[o] = floor(v); break;
+            case U_TRUNC: out[o] = std::trunc(v); break;
+            case U_EXP: out[o] = exp(v); break;
+            case U_LN: out[o] = log(v); break;
+            case U_SQRT: out[o] = sqrt(v); break;
+            case U_RECIPROCAL: out[o] = 1.0 / v; break;
+            default: return std::nullopt;
+          }
+        }
+        return out;
+      case K_BINARY: {
+        const Values* y = arg(n.y);
+        if (!y || y->size() != x->size() || x->size() != on) return std::nullopt;
+        const bool whole = !is_float(dtype(n.x));
+        for (uint64_t o = 0; o < on; ++o) {
+          const double a = (*x)[o], b = (*y)[o];
+          switch (n.op) {
+            case B_ADD: out[o] = a + b; break;
+            case B_SUB: out[o] = a - b; break;
+            case B_MUL: out[o] = a * b; break;
+            case B_DIV: if (whole && b == 0.0) return std::nullopt; out[o] = whole ? std::trunc(a / b) : a / b; break;
+            case B_MOD: if (b == 0.0) return std::nullopt; out[o] = fmod(a, b); break;
+            case B_MAX: out[o] = std::max(a, b); break;
+            case B_CMPLT: out[o] = a < b; break;
+            case B_CMPGT: out[o] = a > b; break;
+            case B_CMPGE: out[o] = a >= b; break;
+            case B_NOTEQ: out[o] = a != b; break;
+            case B_EQ: out[o] = a == b; break;
+            default: return std::nullopt;
+          }
+        }
+        return out;
+      }
+      default: return std::nullopt;
+    }
+  }
+
+  // ---- cross-entropy with class-index targets ----------------------------------------------------------------------------
+  // c = [Cast]{Eq{Expand{labels.reshape([n, 1])}, Expand{arange(classes)}}}, in either operand order -> labels [n]
+  // (Tensor::one_hot_along_dim of the unsqueezed labels, tensor/mod.rs:1920-1946).  The arange is recognised by its value: any
+  // subgraph of constants that evaluates to 0, 1, .., classes - 1.  i32 labels only (what the program reads).
+  std::optional<ClassId> one_hot_labels(ClassId c, uint64_t n, uint64_t classes) const {
+    if (auto k = cast_src(c)) c = *k;
+    auto eq = binary(c, B_EQ);
+    if (!eq) return std::nullopt;
+    for (int swap = 0; swap < 2; ++swap) {
+      auto ea = expand_src(swap ? eq->second : eq->first), eb = expand_src(swap ? eq->first : eq->second);
+      if (!ea || !eb || shape(*ea) != std::vector<uint64_t>{n, 1}) continue;
+      if (shape(*eb) != std::vector<uint64_t>{classes} && shape(*eb) != std::vector<uint64_t>{1, classes}) continue;
+      auto labels = reshape_src(*ea);
+      if (!labels || shape(*labels) != std::vector<uint64_t>{n} || dtype(*labels) != ZYXB_I32) continue;
+      auto v = const_eval(*eb);
+      if (!v || v->size() != classes) continue;
+      bool iota = true;
+      for (uint64_t i = 0; i < classes && iota; ++i) iota = (*v)[i] == (double)i;
+      if (iota) return canon(*labels);
+    }
+    return std::nullopt;
+  }
+  // Tensor::cross_entropy(labels, ReduceOp::Mean) on f32 logits [n, classes] (tensor/mod.rs:1639-1656):
+  //   per_sample = (-logits.ln_softmax([1]) * one_hot(labels)).sum([1]);   loss = per_sample.mean_all()
+  // -> one program, args logits, labels -> per_sample, loss; the one-hot matrix and the log-probabilities never exist.
+  std::optional<Match> match_cross_entropy(ClassId cid) const {
+    if (dtype(cid) != ZYXB_F32) return std::nullopt;
+    auto div = binary_const(cid, B_DIV);
+    if (!div) return std::nullopt;
+    const Node* red = find(div->first, [](const Node& n) { return n.kind == K_REDUCE && n.op == B_ADD; });
+    if (!red) return std::nullopt;
+    const ClassId per_sample = canon(red->x);        // under the no-op accumulator cast of `sum`: the class the caller holds
+    const auto ps = shape(per_sample);
+    if (ps.size() != 1 || red->axes.size() != 1 || fabs(div->second - (double)ps[0]) > 0.5 || dtype(per_sample) != ZYXB_F32) return std::nullopt;
+    auto prod = reduce_last(per_sample, B_ADD);
+    if (!prod || shape(*prod).size() != 2 || shape(*prod)[0] != ps[0]) return std::nullopt;
+    const std::vector<uint64_t> nc = shape(*prod);
+    auto mul = binary(*prod, B_MUL);
+    if (!mul) return std::nullopt;
+    for (int swap = 0; swap < 2; ++swap) {
+      auto lsm = unary(swap ? mul->second : mul->first, U_NEG);
+      if (!lsm) continue;
+      auto ls = match_ln_softmax(*lsm);
+      if (!ls || dtype(ls->inputs[0]) != ZYXB_F32 || shape(ls->inputs[0]) != nc) continue;
+      auto labels = one_hot_labels(swap ? mul->first : mul->second, nc[0], nc[1]);
+      if (!labels) continue;
+      Match m; m.pattern = "cross_entropy"; m.desc = row_desc(ZYXB_RR_CROSS_ENTROPY, ZYXB_F32, nc);
+      m.inputs = {ls->inputs[0], *labels}; m.outputs = {per_sample, cid};
+      return m;
+    }
+    return std::nullopt;
+  }
+
   // ---- optimizer updates -------------------------------------------------------------------------------------------------
   struct Update {
     int algo; ClassId p, g, m = NONE, v = NONE, p_new, m_new = NONE, v_new = NONE;     // SGD with momentum: m is the buffer
@@ -797,7 +988,7 @@ class Graph {
         if (auto u = match_sgd(cid)) { updates.push_back(*u); continue; }
       }
       if (!(m = match_attention(cid)) && !(m = match_linear(cid, wanted)) && !(m = match_softmax(cid)) && !(m = match_ln_softmax(cid)) && !(m = match_layernorm(cid)) &&
-          !(m = match_mse(cid)) && !(m = match_reduce(cid)))
+          !(m = match_cross_entropy(cid)) && !(m = match_mse(cid)) && !(m = match_reduce(cid)))
         continue;
       out.push_back(std::move(*m));
     }
@@ -876,6 +1067,7 @@ class Graph {
     for (uint64_t d : n.shape) k += "," + std::to_string(d);
     k += "|";
     for (int a : n.axes) k += "," + std::to_string(a);
+    if (n.kind == K_PAD) k += "|" + std::to_string(n.lp) + "," + std::to_string(n.len);
     return k;
   }
 };

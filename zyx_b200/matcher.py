@@ -30,10 +30,12 @@ MATCHER_SIGNATURES = {
     "zyxb_mgraph_reshape": (C.c_uint32, [_P, C.c_uint32, _U64_P, C.c_int32]),
     "zyxb_mgraph_permute": (C.c_uint32, [_P, C.c_uint32, _I32_P, C.c_int32]),
     "zyxb_mgraph_reduce": (C.c_uint32, [_P, C.c_uint32, C.c_int32, _I32_P, C.c_int32]),
+    "zyxb_mgraph_pad": (C.c_uint32, [_P, C.c_uint32, C.c_int32, C.c_int64, C.c_uint64]),
     "zyxb_mgraph_cast": (C.c_uint32, [_P, C.c_uint32, C.c_int32]),
     "zyxb_mgraph_unary": (C.c_uint32, [_P, C.c_uint32, C.c_int32]),
     "zyxb_mgraph_binary": (C.c_uint32, [_P, C.c_uint32, C.c_uint32, C.c_int32]),
     "zyxb_mgraph_class_info": (C.c_int32, [_P, C.c_uint32, _I32_P, _I32_P, _U64_P, _I32_P]),
+    "zyxb_mgraph_const_value": (C.c_int32, [_P, C.c_uint32, C.POINTER(C.c_double), C.c_uint64, _U64_P]),
     "zyxb_mgraph_match": (C.c_int32, [_P, C.POINTER(C.c_uint32), C.c_int32, C.POINTER(Match), C.c_int32, _I32_P]),
 }
 H.HOST_SIGNATURES.update(MATCHER_SIGNATURES)
@@ -86,6 +88,9 @@ class MGraph:
         arr = (C.c_int32 * len(axes))(*axes)
         return self._ok(self.lib.zyxb_mgraph_reduce(self.h, x, rop, arr, len(axes)), "reduce")
 
+    def pad(self, x, axis, lp, length):
+        return self._ok(self.lib.zyxb_mgraph_pad(self.h, x, axis, lp, length), "pad")
+
     def cast(self, x, dtype):
         return self._ok(self.lib.zyxb_mgraph_cast(self.h, x, dtype), "cast")
 
@@ -101,6 +106,15 @@ class MGraph:
         shape = (C.c_uint64 * 8)()
         assert self.lib.zyxb_mgraph_class_info(self.h, cls, C.byref(dt), C.byref(rank), shape, C.byref(k)) == L.OK
         return dt.value, tuple(shape[:rank.value]), k.value
+
+    def const_value(self, cls):
+        """The values of a class built from constants only (row-major list), or None when it is not one."""
+        n = C.c_uint64()
+        if self.lib.zyxb_mgraph_const_value(self.h, cls, None, 0, C.byref(n)) != L.OK:
+            return None
+        buf = (C.c_double * max(n.value, 1))()
+        assert self.lib.zyxb_mgraph_const_value(self.h, cls, buf, n.value, C.byref(n)) == L.OK
+        return list(buf[:n.value])
 
     def match(self, outputs):
         outs = (C.c_uint32 * len(outputs))(*outputs)
