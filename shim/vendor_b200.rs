@@ -277,8 +277,9 @@ impl Graph {
     }
     /// The mask-free core of MultiheadAttention::forward (multi_head_attention.rs:197-226) ending at the class of
     /// `attn_weights.matmul(v).transpose(1, 2).reshape([b, t, h*d])`: one fused program on the three stored [b, t, h*d] tensors.
-    /// The kernel's shapes only (16-bit dtype, head dimension 128, equal lengths that are a multiple of 128).  A causal mask is
-    /// built from pad nodes (Tensor::tri), which fall back to the separate matmul and softmax programs.
+    /// The kernel's shapes only (16-bit dtype, head dimension 128, equal lengths that are a multiple of 128).  A causal mask
+    /// (`masked_fill(ones.tril(0).equal(0), -inf)`) is not matched: `where_` computes in the dtype of the rank-0 fill value, so 16-bit
+    /// scores come out as f32 (NaN where the mask keeps them, 0 * -inf); such graphs fall back to the separate programs.
     fn match_attention(&self, cid: ClassId) -> Option<B200Match> {
         let s3 = self.const_shape(cid)?;
         if s3.len() != 3 { return None; }

@@ -422,9 +422,10 @@ class Graph {
   //   attn_weights.matmul(v).transpose(1, 2).reshape([b, t, h*d]),  attn_weights = (q.matmul(k.transpose(-2, -1)) * scale).softmax([-1]),
   // with q, k, v the head-split views of three stored [b, t, h*d] tensors: one fused program that reads those three where they
   // lie and writes the [b, t, h*d] result; scores and probabilities never exist.  The kernel's shapes only: 16-bit dtype, head
-  // dimension 128, equal query and key lengths that are a multiple of 128.  A causal mask is built from pad nodes
-  // (Tensor::tri, tensor/mod.rs:2396-2418), which this mirror does not carry: such graphs fall back to the separate
-  // matmul and softmax programs.
+  // dimension 128, equal query and key lengths that are a multiple of 128.  A causal mask
+  // (`masked_fill(ones.tril(0).equal(0), -inf)`, multi_head_attention.rs:203-207) is not matched: `where_` (tensor/mod.rs:1617-1624)
+  // computes in the dtype of the rank-0 fill value, so 16-bit scores come out as f32 - and as NaN wherever the mask keeps them
+  // (0 * -inf) - which is not what the 16-bit program computes; such graphs fall back to the separate programs.
   std::optional<Match> match_attention(ClassId cid) const {
     const auto s3 = shape(cid);
     if (s3.size() != 3) return std::nullopt;
