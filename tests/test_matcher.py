@@ -395,6 +395,9 @@ def test_constant_index_tensors_are_folded(g):
     assert g.const_value(T.arange(g, 0, 4, 1).repeat([2]).cls) == [0.0, 1.0, 2.0, 3.0] * 2
     assert g.const_value(T.arange(g, 1, 5, 1).cumsum(0).cls) == [1.0, 3.0, 6.0, 10.0]
     assert g.const_value((T.arange(g, 0, 4, 1).cast(L.F32) * 0.5).cast(L.I32).cls) == [0.0, 0.0, 1.0, 1.0]
+    for r, c, diagonal in ((4, 4, 1), (3, 5, 0), (5, 3, 2), (4, 4, -1)):      # Tensor::tri, what tril / triu and a causal mask select with
+        want = [float(col >= row + diagonal) for row in range(r) for col in range(c)]
+        assert g.const_value(T.tri(g, r, c, diagonal, L.BOOL).cls) == want, (r, c, diagonal)
     labels = T.leaf(g, L.I32, (4,))
     assert g.const_value(labels.unsqueeze(1).one_hot_along_dim(3, 1).cls) is None
     assert g.const_value(T.arange(g, 0, 3000, 1).cls) is None          # the pooled intermediate is past the folding limit

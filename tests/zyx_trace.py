@@ -154,6 +154,20 @@ class T:
         n = (stop - start) // step
         return T.full(g, [n], step, dtype).cumsum(0) + T.scalar(g, start, dtype) - T.scalar(g, step, dtype)
 
+    @staticmethod
+    def tri(g, r, c, diagonal, dtype):
+        """ones where column >= row + diagonal (tensor/mod.rs:2396-2414): a padded square of ones re-read with a longer pitch"""
+        if diagonal >= c:
+            return T.full(g, [r, c], 0, dtype)
+        if r + diagonal <= 0:
+            return T.full(g, [r, c], 1, dtype)
+        s = r + c - 1
+        t = T.full(g, [s, s], 1, dtype).rpad_zeros([(0, s)]).reshape([2 * s * s]).rpad_zeros([(0, -s)])
+        t = t.reshape([s, 2 * s - 1]).rpad_zeros([(0, -(s - 1))])
+        if diagonal <= 0:
+            return t.slice([(0, r), (-diagonal, c - diagonal)])
+        return t.slice([(diagonal, r + diagonal), (0, c)])
+
     def equal(self, rhs): return self._binary(rhs, M.B_EQ)
 
     def one_hot_along_dim(self, num_classes, dim):
