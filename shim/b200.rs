@@ -87,6 +87,10 @@ pub const ZYXB_KIND_GEMM: i32 = 2;
 pub const ZYXB_KIND_ELTWISE: i32 = 3;
 pub const ZYXB_KIND_OPTIM: i32 = 4;
 pub const ZYXB_KIND_ATTENTION: i32 = 5;
+pub const ZYXB_KIND_ATTENTION_BWD: i32 = 6;
+pub const ZYXB_KIND_CONV: i32 = 7;
+pub const ZYXB_KIND_CONV_WGRAD: i32 = 8;
+pub const ZYXB_KIND_CONV_DGRAD: i32 = 9;
 
 // ------------------------------------------------------------------------------------------------------------------
 // The entry points, resolved once (as CUDAMemoryPool / CblasDevice resolve theirs with libloading)

@@ -13,7 +13,8 @@ use std::collections::{BTreeMap, BTreeSet};
 use crate::{
     DType,
     dtype::Constant,
-    backend::b200::{ZyxbDescUnion, ZyxbGemmDesc, ZyxbKernelDesc, ZyxbOptimDesc, ZyxbRowreduceDesc, ZYXB_KIND_GEMM, ZYXB_KIND_OPTIM, ZYXB_KIND_ROWREDUCE},
+    backend::b200::{ZyxbAttentionDesc, ZyxbConvDesc, ZyxbDescUnion, ZyxbGemmDesc, ZyxbKernelDesc, ZyxbOptimDesc, ZyxbRowreduceDesc, ZYXB_KIND_ATTENTION,
+                    ZYXB_KIND_CONV, ZYXB_KIND_GEMM, ZYXB_KIND_OPTIM, ZYXB_KIND_ROWREDUCE},
     graph::{ClassId, Graph, Node},
     kernel::{BOp, UOp},
     shape::Dim,
@@ -38,6 +39,12 @@ fn const_f64(k: Constant) -> f64 {
 /// What a Cast node does to a folded value: Bool is `!= 0`, f32 rounds, the integer types truncate.
 fn cast_value(v: f64, dt: DType) -> f64 {
     match dt { DType::Bool => (v != 0.0) as u8 as f64, DType::F32 => v as f32 as f64, DType::F64 | DType::BF16 | DType::F16 => v, _ => v.trunc() }
+}
+
+/// every index of a short axis; both ends and a spread of a long one
+fn sample_axis(n: u64) -> Vec<u64> {
+    if n <= 48 { return (0..n).collect(); }
+    (0..16).chain((1..=16).map(|i| 16 + i * (n - 32) / 17)).chain(n - 16..n).collect()
 }
 
 #[derive(Clone, Copy)]
@@ -453,6 +460,180 @@ impl Graph {
         }
     }
 
+    // ---- views: where an element comes from ---------------------------------------------------------------------------------
+    /// One element of class c followed back through the movement ops that define it (Expand, Reshape, Permute, Pad, no-op Cast)
+    /// to the first class that is something else: (that class, the coordinates there), or None when the element is a zero of some
+    /// padding.  A view is recognised by what it reads, not by how it was written down: Tensor::pool (tensor/mod.rs:2442-2543) is a
+    /// dozen reshapes, expands and crops that differ with every stride and dilation, but what they read is `oy*stride + r*dilation`.
+    fn trace_element(&self, mut c: ClassId, mut idx: Vec<u64>) -> Option<Option<(ClassId, Vec<u64>)>> {
+        for _ in 0..256 {
+            let cs = self.const_shape(c)?;
+            match &self.nodes[self.classes[c].nodes[0]].node {
+                Node::Reshape { x, .. } => {
+                    let xs = self.const_shape(*x)?;
+                    let mut lin = cs.iter().zip(&idx).fold(0, |l, (&d, &i)| l * d + i);
+                    idx = vec![0; xs.len()];
+                    for a in (0..xs.len()).rev() { idx[a] = lin % xs[a]; lin /= xs[a]; }
+                    c = *x;
+                }
+                Node::Expand { x, .. } => {
+                    let xs = self.const_shape(*x)?;
+                    let lead = cs.len() - xs.len();
+                    idx = (0..xs.len()).map(|a| if xs[a] == 1 { 0 } else { idx[lead + a] }).collect();
+                    c = *x;
+                }
+                Node::Permute { x, axes } => {
+                    let mut src = vec![0; idx.len()];
+                    for (j, &a) in axes.iter().enumerate() { src[a as usize] = idx[j]; }
+                    idx = src;
+                    c = *x;
+                }
+                Node::Pad { x, axis, lp, .. } => {
+                    let lp = self.find_in(*lp, |n| match n { Node::Const(k) => Some(const_f64(*k) as i64), _ => None })?;
+                    let at = idx[*axis as usize] as i64 - lp;
+                    if at < 0 || at >= self.const_shape(*x)?[*axis as usize] as i64 { return Some(None); }
+                    idx[*axis as usize] = at as u64;
+                    c = *x;
+                }
+                Node::Cast { x, dtype } if self.dtype(*x) == *dtype => c = *x,
+                _ => break,
+            }
+        }
+        Some(Some((c, idx)))
+    }
+    /// the class a view reads (c under every movement op) and the classes passed on the way, outermost first
+    fn view_source(&self, mut c: ClassId) -> (ClassId, Vec<ClassId>) {
+        let mut chain = Vec::new();
+        for _ in 0..256 {
+            let x = match &self.nodes[self.classes[c].nodes[0]].node {
+                Node::Reshape { x, .. } | Node::Expand { x, .. } | Node::Permute { x, .. } | Node::Pad { x, .. } => *x,
+                Node::Cast { x, dtype } if self.dtype(*x) == *dtype => *x,
+                _ => break,
+            };
+            chain.push(c);
+            c = x;
+        }
+        (c, chain)
+    }
+
+    // ---- convolution ----------------------------------------------------------------------------------------------------------
+    /// Tensor::conv with groups = 1 on [n, c, h, w] (tensor/mod.rs:2583-2680), ending at cid [n, o, oh, ow]:
+    ///   x.rpad_zeros(padding).pool(kernel, stride, dilation) -Reshape, Expand over o, Permute-> [n, 1, o, oh, ow, c, kh, kw]
+    ///   * weight.reshape([1, 1, o, 1, 1, c, kh, kw]) -> sum_keepdim over (c, kh, kw) -> reshape [n, o, oh, ow]  [+ bias.reshape([1, o, 1, 1])]
+    /// Padding from the Pad nodes on the stored input, stride and dilation measured on the view, then the view held against
+    /// `x[b, ci, oy*stride_h + r*dil_h - pad_top, ox*stride_w + s*dil_w - pad_left]` (zero outside the image).
+    fn match_conv(&self, cid: ClassId) -> Option<B200Match> {
+        let out = self.const_shape(cid)?;
+        if out.len() != 4 { return None; }
+        let (mut e, mut bias) = (cid, None);
+        if let Some((p, q)) = self.binary_of(cid, BOp::Add) {
+            for (lhs, rhs) in [(p, q), (q, p)] {
+                if bias.is_some() { break; }
+                let Some(src) = self.expand_of(rhs) else { continue };
+                if self.const_shape(src).as_deref() != Some(&[1, out[1], 1, 1][..]) { continue; }
+                let b = self.canon(self.unbroadcast(rhs));
+                if self.numel_of(b) == Some(out[1]) { bias = Some(b); e = lhs; }
+            }
+        }
+        // through the closing reshape and sum_keepdim's reshape to the Reduce
+        let red_of = |cls: ClassId| self.find_in(cls, |nd| match nd { Node::Reduce { x, rop: BOp::Add, axes } => Some((*x, axes.clone())), _ => None });
+        let (mut r, mut red) = (e, None);
+        for _ in 0..4 {
+            red = red_of(r).or_else(|| red_of(self.cast_src(r)?));
+            if red.is_some() { break; }
+            let src = self.reshape_of(r)?;
+            if self.numel_of(src) != Some(out.iter().product()) { return None; }
+            r = src;
+        }
+        let (prod, axes) = red?;
+        let ps = self.const_shape(prod)?;                                    // [n, 1, o, oh, ow, c, kh, kw]
+        let mut axes: Vec<usize> = axes.iter().map(|&a| a as usize).collect();
+        axes.sort_unstable();
+        if ps.len() != 8 || axes != [5, 6, 7] || ps[1] != 1 { return None; }
+        let (n, o, oh, ow, c, kh, kw) = (ps[0], ps[2], ps[3], ps[4], ps[5], ps[6], ps[7]);
+        if out != [n, o, oh, ow] { return None; }
+        let (f0, f1) = self.binary_of(prod, BOp::Mul).or_else(|| self.binary_of(self.cast_src(prod)?, BOp::Mul))?;
+        for (xe, we) in [(f0, f1), (f1, f0)] {
+            let Some(wr) = self.expand_of(we) else { continue };
+            if self.const_shape(wr).as_deref() != Some(&[1, 1, o, 1, 1, c, kh, kw][..]) { continue; }
+            let Some(wsrc) = self.reshape_of(wr) else { continue };
+            if self.const_shape(wsrc).as_deref() != Some(&[o, c, kh, kw][..]) { continue; }
+            let w = self.canon(wsrc);
+            let (x, chain) = self.view_source(xe);
+            let Some(xs) = self.const_shape(x) else { continue };
+            if self.const_shape(xe)? != ps || xs.len() != 4 || xs[0] != n || xs[1] != c { continue; }
+            let dt = self.dtype(x);
+            if self.dtype(w) != dt || self.dtype(cid) != dt || bias.is_some_and(|b| self.dtype(b) != dt) { continue; }
+            if !matches!(dt, DType::F32 | DType::BF16 | DType::F16 | DType::I32) { continue; }
+            let (h, wd) = (xs[2], xs[3]);
+            // the declared padding: the Pad nodes directly on x (rpad_zeros pads the last axis first)
+            let mut pad = [0u64; 4];                                          // top, bottom, left, right
+            let mut ext = [n, c, h, wd];
+            for &cls in chain.iter().rev() {
+                let Node::Pad { axis, lp, len, .. } = &self.nodes[self.classes[cls].nodes[0]].node else { break };
+                let ax = *axis as usize;
+                let (Some(lp), Some(len)) = (self.find_in(*lp, |k| match k { Node::Const(k) => Some(const_f64(*k) as i64), _ => None }),
+                                             self.find_in(*len, |k| match k { Node::Const(k) => k.as_dim(), _ => None })) else { break };
+                if lp < 0 || (ax != 2 && ax != 3) || (len as i64) < lp + ext[ax] as i64 { break; }
+                pad[if ax == 2 { 0 } else { 2 }] += lp as u64;
+                pad[if ax == 2 { 1 } else { 3 }] += len - lp as u64 - ext[ax];
+                ext[ax] = len;
+            }
+            let probe = |b: u64, co: u64, oy: u64, ox: u64, ci: u64, kr: u64, ks: u64| self.trace_element(xe, vec![b, 0, co, oy, ox, ci, kr, ks]);
+            // stride and dilation: the distance between what neighbouring windows / taps read, measured where nothing is padding
+            let step = |rows: bool, window: bool| -> Option<u64> {
+                let (n_out, n_tap, n_other) = if rows { (oh, kh, ow) } else { (ow, kw, oh) };
+                if (if window { n_out } else { n_tap }) < 2 { return Some(1); }       // a single window or tap: the step is never taken
+                for o1 in sample_axis(n_out) {
+                    for t1 in 0..n_tap {
+                        let (o2, t2) = (o1 + window as u64, t1 + !window as u64);
+                        if o2 >= n_out || t2 >= n_tap { continue; }
+                        for other in sample_axis(n_other) {
+                            let (a, b) = if rows { (probe(0, 0, o1, other, 0, t1, 0)?, probe(0, 0, o2, other, 0, t2, 0)?) }
+                                         else { (probe(0, 0, other, o1, 0, 0, t1)?, probe(0, 0, other, o2, 0, 0, t2)?) };
+                            let (Some((ca, ia)), Some((cb, ib))) = (a, b) else { continue };
+                            if ca != x || cb != x { continue; }
+                            let ax = if rows { 2 } else { 3 };
+                            return (ib[ax] > ia[ax]).then(|| ib[ax] - ia[ax]);
+                        }
+                    }
+                }
+                None
+            };
+            let (Some(sh), Some(dh), Some(sw), Some(dw)) = (step(true, true), step(true, false), step(false, true), step(false, false)) else { continue };
+            // the output extent the declared padding gives must be the view's
+            let out_extent = |i: u64, before: u64, after: u64, k: u64, s: u64, d: u64| {
+                let (span, padded) = (d * (k - 1) + 1, i + before + after);
+                if padded < span { 0 } else { (padded - span) / s + 1 }
+            };
+            if out_extent(h, pad[0], pad[1], kh, sh, dh) != oh || out_extent(wd, pad[2], pad[3], kw, sw, dw) != ow { continue; }
+            let reads = |b: u64, co: u64, oy: u64, ox: u64, ci: u64, kr: u64, ks: u64| -> bool {
+                let Some(origin) = probe(b, co, oy, ox, ci, kr, ks) else { return false };
+                let (row, col) = ((oy * sh + kr * dh) as i64 - pad[0] as i64, (ox * sw + ks * dw) as i64 - pad[2] as i64);
+                if row < 0 || row >= h as i64 || col < 0 || col >= wd as i64 { return origin.is_none(); }
+                origin == Some((x, vec![b, ci, row as u64, col as u64]))
+            };
+            let (oys, oxs) = (sample_axis(oh), sample_axis(ow));
+            let mut ok = true;
+            'corners: for b in [0, n - 1] { for ci in [0, c - 1] { for co in [0, o - 1] { for &oy in &oys { for &ox in &oxs { for kr in 0..kh { for ks in 0..kw {
+                if !reads(b, co, oy, ox, ci, kr, ks) { ok = false; break 'corners; }
+            } } } } } } }
+            ok = ok && sample_axis(n).into_iter().all(|b| sample_axis(c).into_iter().all(|ci|
+                reads(b, 0, 0, 0, ci, 0, 0) && reads(b, o - 1, oh - 1, ow - 1, ci, kh - 1, kw - 1) && reads(b, 0, oh / 2, ow / 2, ci, kh / 2, kw / 2)));
+            if !ok { continue; }
+            let conv = ZyxbConvDesc {
+                dtype: dt as i32, n, c, h, w: wd, o, kh, kw, stride_h: sh as u32, stride_w: sw as u32, dil_h: dh as u32, dil_w: dw as u32,
+                pad_top: pad[0] as u32, pad_bottom: pad[1] as u32, pad_left: pad[2] as u32, pad_right: pad[3] as u32,
+                has_bias: bias.is_some() as i32, ..Default::default()
+            };
+            let mut inputs = vec![x, w];
+            inputs.extend(bias);
+            return Some(B200Match { pattern: if bias.is_some() { "conv_bias" } else { "conv" }, inputs, outputs: vec![cid],
+                                    desc: ZyxbKernelDesc { kind: ZYXB_KIND_CONV, u: ZyxbDescUnion { conv } }, numel: Vec::new(), optim_step: 0 });
+        }
+        None
+    }
+
     // ---- cross-entropy with class-index targets -----------------------------------------------------------------------------
     /// c = [Cast]{Eq{Expand{labels.reshape([n, 1])}, Expand{arange(classes)}}}, either operand order -> labels [n]
     /// (Tensor::one_hot_along_dim of the unsqueezed labels, tensor/mod.rs:1920-1946).  The arange is recognised by its value;
@@ -647,7 +828,7 @@ impl Graph {
             if wanted.contains(&cid) {
                 if let Some(u) = self.match_adamw(cid).or_else(|| self.match_adam(cid)).or_else(|| self.match_sgd(cid)) { updates.push(u); continue; }
             }
-            let m = self.match_attention(cid).or_else(|| self.match_linear(cid, wanted)).or_else(|| self.match_softmax(cid)).or_else(|| self.match_ln_softmax(cid))
+            let m = self.match_attention(cid).or_else(|| self.match_linear(cid, wanted)).or_else(|| self.match_conv(cid)).or_else(|| self.match_softmax(cid)).or_else(|| self.match_ln_softmax(cid))
                 .or_else(|| self.match_layernorm(cid)).or_else(|| self.match_cross_entropy(cid)).or_else(|| self.match_mse(cid)).or_else(|| self.match_reduce(cid));
             out.extend(m);
         }

@@ -174,3 +174,27 @@ def test_cross_entropy_from_graph_to_launch(sess):
         assert_parity(got[loss.cls].reshape(1), want_mean, np.array([exact.mean()]), TOL_F32, row_axis=0, what="matched ce mean")
     finally:
         g.close()
+
+
+def test_convolution_from_graph_to_launch(sess):
+    """Tensor::conv traced (padding, pooling view, broadcast product, sum over channel and taps, bias), recognised by what the
+    view reads, launched as the convolution program: x, w, bias -> y."""
+    rng = np.random.default_rng(36)
+    g = MGraph()
+    try:
+        x, w, b = T.leaf(g, L.F32, (2, 5, 19, 23)), T.leaf(g, L.F32, (7, 5, 3, 2)), T.leaf(g, L.F32, (7,))
+        y = x.conv(w, b, stride=(2, 1), dilation=(1, 2), padding=(1, 2, 0, 3))         # (left, right, top, bottom)
+        m = pick(g.match([y.cls]), b"conv_bias", y.cls)
+        xv = rng.standard_normal((2, 5, 19, 23)).astype(np.float32)
+        wv = rng.standard_normal((7, 5, 3, 2)).astype(np.float32)
+        bv = rng.standard_normal(7).astype(np.float32)
+        got = run_match(sess, g, m, {x.cls: xv, w.cls: wv, b.cls: bv})[y.cls]
+        want = zo.conv(zo.F32, xv, wv, bv, (2, 1), (1, 2), (0, 3, 1, 2))                # (top, bottom, left, right)
+        assert got.shape == want.shape == tuple(y.shape)
+        import torch
+        xt = torch.nn.functional.pad(torch.from_numpy(xv.astype(np.float64)), (1, 2, 0, 3))
+        exact = torch.nn.functional.conv2d(xt, torch.from_numpy(wv.astype(np.float64)), torch.from_numpy(bv.astype(np.float64)),
+                                           stride=(2, 1), dilation=(1, 2)).numpy()
+        assert_parity(got, want, exact, TOL_F32, floor=0.1, what="matched conv")
+    finally:
+        g.close()

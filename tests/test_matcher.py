@@ -488,3 +488,57 @@ def test_matched_cross_entropy_launches_through_the_abi(g):
     want = lse - x[np.arange(48), values[labels.cls]]
     np.testing.assert_allclose(fake.download(bufs[2], (48,)), want, rtol=1e-6)
     np.testing.assert_allclose(fake.download(bufs[3], (1,)), [want.mean()], rtol=1e-6)
+
+
+CONV_CASES = [
+    # dtype, x [n,c,h,w], w [o,c,kh,kw], stride (h,w), dilation (h,w), padding as Tensor::conv takes it, (top,bottom,left,right), bias
+    (L.BF16, (32, 256, 56, 56), (256, 256, 3, 3), (1, 1), (1, 1), (1,), (1, 1, 1, 1), True),
+    (L.F32, (2, 3, 32, 32), (16, 3, 7, 7), (2, 2), (1, 1), (3,), (3, 3, 3, 3), False),
+    (L.F16, (4, 8, 20, 24), (8, 8, 3, 3), (1, 1), (2, 2), (2,), (2, 2, 2, 2), True),
+    (L.F32, (3, 5, 17, 19), (6, 5, 3, 2), (2, 1), (1, 2), (1, 2, 0, 3), (0, 3, 1, 2), True),      # (left, right, top, bottom)
+    (L.BF16, (8, 64, 14, 14), (128, 64, 1, 1), (1, 1), (1, 1), (0,), (0, 0, 0, 0), False),
+    (L.F32, (2, 3, 32, 32), (24, 3, 4, 4), (4, 4), (1, 1), (0,), (0, 0, 0, 0), True),              # stride = filter size
+    (L.I32, (1, 2, 5, 9), (3, 2, 5, 3), (1, 2), (1, 1), (0,), (0, 0, 0, 0), False),               # one output row
+    (L.F32, (2, 4, 9, 9), (4, 4, 3, 3), (2, 2), (1, 1), (0,), (0, 0, 0, 0), False),
+]
+
+
+@pytest.mark.parametrize("case", CONV_CASES, ids=lambda c: "x".join(map(str, c[1])) + "_k" + "x".join(map(str, c[2][2:])))
+def test_conv_is_recognised_by_what_its_view_reads(g, case):
+    """Tensor::conv (tensor/mod.rs:2583-2680): the padded input goes through Tensor::pool's dozen movement ops, whose shapes
+    change with every stride and dilation.  The matcher reads the padding off the Pad nodes, measures stride and dilation on the
+    view and holds the whole view against `x[b, c, oy*stride + r*dil - pad, ..]`; the descriptor is the one a caller of the
+    convolution program writes by hand (zyx_b200.backend.conv_desc)."""
+    dtype, xs, ws, stride, dilation, padding, pads, has_bias = case
+    x, w = T.leaf(g, dtype, xs), T.leaf(g, dtype, ws)
+    b = T.leaf(g, dtype, (ws[0],)) if has_bias else None
+    y = x.conv(w, b, stride=stride, dilation=dilation, padding=padding)
+    assert tuple(y.shape) == tuple(B.conv_out_shape(xs, ws, stride, dilation, pads))
+    ms = [m for m in g.match([y.cls]) if m.outputs[0] == y.cls]
+    assert [m.pattern for m in ms] == [b"conv_bias" if has_bias else b"conv"]
+    m = ms[0]
+    got, want = fields(m.desc.u.conv), fields(B.conv_desc(dtype, xs, ws, stride, dilation, pads, has_bias=has_bias).u.conv)
+    assert m.desc.kind == L.KIND_CONV and got == want, (got, want)
+    assert list(m.inputs[:m.n_inputs]) == [x.cls, w.cls] + ([b.cls] if has_bias else [])
+
+
+def test_views_that_are_not_the_convolution_window_are_left_alone(g):
+    """Same shapes, same node kinds, different elements read: a filter applied to the transposed window, an image read
+    transposed, two groups."""
+    def conv_patterns(y):
+        return [m.pattern for m in g.match([y.cls]) if m.pattern.startswith(b"conv")]
+
+    x, w = T.leaf(g, L.F32, (2, 4, 12, 12)), T.leaf(g, L.F32, (6, 4, 3, 3))
+    assert conv_patterns(x.conv(w, padding=(1,))) == [b"conv"]
+    wt = w.t()
+    m = next(m for m in g.match([x.conv(wt, padding=(1,)).cls]) if m.pattern == b"conv")
+    assert list(m.inputs[:m.n_inputs]) == [x.cls, wt.cls]                            # a transposed filter is another filter class
+    assert conv_patterns(x.t().conv(w, padding=(1,))) == []                          # the view reads x[.., col, row]: no program does
+    # the window's taps exchanged under the filter: reads x[.., ox + r, oy + s] where the convolution reads x[.., oy + r, ox + s]
+    pooled = x.rpad_zeros([(1, 1), (1, 1)]).pool([3, 3], 1, 1)                       # [2, 4, 12, 12, 3, 3]
+    swapped = pooled.permute([0, 1, 3, 2, 5, 4])
+    view = swapped.reshape([2, 1, 4, 1, 12, 12, 3, 3]).expand([2, 1, 4, 6, 12, 12, 3, 3]).permute([0, 1, 3, 4, 5, 2, 6, 7])
+    y = (view * w.reshape([1, 1, 6, 1, 1, 4, 3, 3])).sum([-1, -2, -3], keepdim=True).reshape([2, 6, 12, 12])
+    assert conv_patterns(y) == []
+    xg, wg = T.leaf(g, L.F32, (2, 4, 12, 12)), T.leaf(g, L.F32, (6, 2, 3, 3))
+    assert conv_patterns(xg.conv(wg, groups=2, padding=(1,))) == []

@@ -11,7 +11,7 @@ TEST INFRASTRUCTURE: each method restates the decomposition of the reference met
     index helpers  pad_zeros / rpad_zeros (tensor/mod.rs:1120-1226: one Pad node per padded axis, negative amounts cut),
                    slice (index_ops.rs:84-160: negative paddings, then squeeze's reshape), repeat (2766-2783), pool (2442-2543),
                    cumsum (reduce_ops.rs:1076-1091), full (745-754), arange (773-781), one_hot_along_dim (1920-1946),
-                   cross_entropy with class-index targets (1639-1656)
+                   cross_entropy with class-index targets (1639-1656), tri (2396-2414), conv (2583-2680)
 Every `.cast(dtype)` pushes a Cast node, also when the dtype does not change (zyx/src/runtime.rs:696-700)."""
 import math
 
@@ -139,6 +139,35 @@ class T:
         xup = xup.slice(full + [r for k, o in zip(k_, o_) for r in ((0, k), (0, o), (0, 1))])
         xup = xup.reshape(sh_b + [e for k, o in zip(k_, o_) for e in (k, o)])
         return xup.permute(list(range(nb)) + [nb + 2 * i + 1 for i in range(len(i_))] + [nb + 2 * i for i in range(len(i_))])
+
+    def conv(self, weight, bias=None, groups=1, stride=(1,), dilation=(1,), padding=(0,)):
+        """padding: one value, one per spatial axis, or (before, after) per axis starting from the LAST axis"""
+        bs, cin_ = self.shape[:2]
+        cout, cin = weight.shape[:2]
+        hw = list(weight.shape[2:])
+        padding = list(padding)
+        if len(padding) == 1:
+            pads = padding * (2 * len(hw))
+        elif len(padding) == 2 * len(hw):
+            pads = padding
+        else:
+            pads = (padding + padding)[::-1]                                    # resolve_pool_pads, as written
+        assert groups * cin == cin_ and len(self.shape) == len(weight.shape)
+        stride, dilation = list(stride), list(dilation)
+        x = self.rpad_zeros([(pads[2 * i], pads[2 * i + 1]) for i in range(len(hw))])
+        x = x.pool(hw, stride[0] if len(stride) == 1 else stride, dilation[0] if len(dilation) == 1 else dilation)
+        rcout = cout // groups
+        oyx = list(x.shape[2:len(x.shape) - len(hw)])
+        x = x.reshape([bs, groups, cin, 1] + oyx + hw).expand([bs, groups, cin, rcout] + oyx + hw)
+        x = x.permute([0, 1, 3] + [4 + i for i in range(len(oyx))] + [2] + [4 + len(oyx) + i for i in range(len(hw))])
+        w = weight.reshape([1, groups, rcout] + [1] * len(oyx) + [cin] + hw)
+        ret = (x * w).sum([-1 - i for i in range(len(oyx) + 1)], keepdim=True).reshape([bs, cout] + oyx)
+        if bias is not None:
+            n = 1
+            for d in bias.shape:
+                n *= d
+            ret = ret + bias.reshape([1, n] + [1] * len(hw))
+        return ret
 
     def cumsum(self, axis):
         n = self.shape[axis % len(self.shape)]

@@ -10,6 +10,7 @@
 //                   a stored tensor (a weight gradient written as `dz.t().dot(x)`); rank > 2 with batch strides; the
 //                   accumulator Casts that `sum` puts around the Reduce for 16-bit inputs (tensor/reduce_ops.rs:52-60,143-145);
 //                   a trailing `* const` (attention's 1/sqrt(d)) as alpha; `+ bias`, relu and gelu as epilogues
+//   convolution     Tensor::conv with groups = 1 (tensor/mod.rs:2583-2680), recognised by what its pooling view reads
 //   attention       the mask-free core of MultiheadAttention::forward (zyx-nn/src/multi_head_attention.rs:197-226)
 //   row kernels     softmax, ln_softmax (tensor/mod.rs:1427-1461), LayerNorm::forward (zyx-nn/src/layer_norm.rs:95-135),
 //                   sum / max / mean / var / std over the last axis (tensor/reduce_ops.rs:45-157), `sum([0])` of a matrix
@@ -777,6 +778,202 @@ class Graph {
     }
   }
 
+  // ---- views: where an element comes from -------------------------------------------------------------------------------
+  // One element of class c followed back through the movement ops that define it (Expand, Reshape, Permute, Pad, no-op Cast)
+  // to the first class that is something else: that class and the element's coordinates there, or `zero` when the element is
+  // a zero of some padding.  This is how a view is recognised by what it reads instead of by how it was written down: the
+  // reference's pooling (Tensor::pool, tensor/mod.rs:2442-2543) is a dozen reshapes, expands and crops that differ with every
+  // stride and dilation, but what they read is `row = oy*stride + r*dilation`.
+  struct Origin { ClassId cls = NONE; std::vector<uint64_t> idx; bool zero = false; };
+  static uint64_t ravel(const std::vector<uint64_t>& idx, const std::vector<uint64_t>& shape) {
+    uint64_t lin = 0;
+    for (size_t a = 0; a < shape.size(); ++a) lin = lin * shape[a] + idx[a];
+    return lin;
+  }
+  Origin trace_element(ClassId c, std::vector<uint64_t> idx) const {
+    Origin o;
+    for (int hops = 0; hops < 256; ++hops) {
+      const Node& n = nodes[classes[c].nodes[0]];
+      const auto& cs = shape(c);
+      if (n.kind == K_RESHAPE) {
+        const uint64_t lin = ravel(idx, cs);
+        idx.assign(shape(n.x).size(), 0);
+        unravel(lin, shape(n.x), idx);
+      } else if (n.kind == K_EXPAND) {
+        const auto& xs = shape(n.x);
+        const size_t lead = cs.size() - xs.size();
+        std::vector<uint64_t> in(xs.size());
+        for (size_t a = 0; a < xs.size(); ++a) in[a] = xs[a] == 1 ? 0 : idx[lead + a];
+        idx = std::move(in);
+      } else if (n.kind == K_PERMUTE) {
+        std::vector<uint64_t> in(idx.size());
+        for (size_t j = 0; j < n.axes.size(); ++j) in[n.axes[j]] = idx[j];
+        idx = std::move(in);
+      } else if (n.kind == K_PAD) {
+        const size_t ax = (size_t)n.axes[0];
+        const int64_t at = (int64_t)idx[ax] - n.lp;
+        if (at < 0 || at >= (int64_t)shape(n.x)[ax]) { o.zero = true; return o; }
+        idx[ax] = (uint64_t)at;
+      } else if (!(n.kind == K_CAST && dtype(n.x) == dtype(c))) {
+        break;
+      }
+      c = n.x;
+    }
+    o.cls = c; o.idx = std::move(idx);
+    return o;
+  }
+  // the class a view reads: c under every movement op
+  ClassId view_source(ClassId c) const {
+    for (int hops = 0; hops < 256; ++hops) {
+      const Node& n = nodes[classes[c].nodes[0]];
+      const bool movement = n.kind == K_RESHAPE || n.kind == K_EXPAND || n.kind == K_PERMUTE || n.kind == K_PAD ||
+                            (n.kind == K_CAST && dtype(n.x) == dtype(c));
+      if (!movement) return c;
+      c = n.x;
+    }
+    return c;
+  }
+  // every index of a short axis; the first, last and a spread of a long one
+  static std::vector<uint64_t> sample_axis(uint64_t n) {
+    std::vector<uint64_t> v;
+    if (n <= 48) { for (uint64_t i = 0; i < n; ++i) v.push_back(i); return v; }
+    for (uint64_t i = 0; i < 16; ++i) v.push_back(i);
+    for (uint64_t i = 1; i <= 16; ++i) v.push_back(16 + i * (n - 32) / 17);
+    for (uint64_t i = n - 16; i < n; ++i) v.push_back(i);
+    return v;
+  }
+
+  // ---- convolution -------------------------------------------------------------------------------------------------------
+  // Tensor::conv with groups = 1 on [n, c, h, w] (tensor/mod.rs:2583-2680), ending at cid [n, o, oh, ow]:
+  //   x.rpad_zeros(padding).pool(kernel, stride, dilation) -Reshape, Expand over o, Permute-> [n, 1, o, oh, ow, c, kh, kw]
+  //   * weight.reshape([1, 1, o, 1, 1, c, kh, kw]) -> sum_keepdim over (c, kh, kw) -> reshape [n, o, oh, ow]  [+ bias.reshape([1, o, 1, 1])]
+  // The padding is read off the Pad nodes that sit on the stored input; stride and dilation are measured on the view (two
+  // neighbouring output rows, two neighbouring filter rows), and then the whole view is held against
+  //   x[b, ci, oy*stride_h + r*dil_h - pad_top, ox*stride_w + s*dil_w - pad_left]   (zero outside the image)
+  // for every window position and tap at the corner (image, channel) pairs, every (image, channel) pair at two windows, and
+  // both ends of the filter axis the view is expanded over (long axes: both ends and a spread).
+  std::optional<Match> match_conv(ClassId cid) const {
+    const auto out = shape(cid);
+    if (out.size() != 4) return std::nullopt;
+    ClassId e = cid, bias = NONE;
+    if (auto add = binary(cid, B_ADD))
+      for (int swap = 0; swap < 2 && bias == NONE; ++swap) {
+        const ClassId lhs = swap ? add->second : add->first, rhs = swap ? add->first : add->second;
+        auto src = expand_src(rhs);
+        if (!src || shape(*src) != std::vector<uint64_t>{1, out[1], 1, 1}) continue;
+        const ClassId b = canon(unbroadcast(rhs));
+        if (numel(shape(b)) == out[1]) { bias = b; e = lhs; }
+      }
+    // through the closing reshape and sum_keepdim's reshape to the Reduce
+    auto is_red = [](const Node& n) { return n.kind == K_REDUCE && n.op == B_ADD; };
+    const Node* red = nullptr;
+    ClassId r = e;
+    for (int i = 0; i < 4 && !red; ++i) {
+      if ((red = find(r, is_red))) break;
+      if (auto k = cast_src(r)) if ((red = find(*k, is_red))) break;
+      auto src = reshape_src(r);
+      if (!src || numel(shape(*src)) != numel(out)) return std::nullopt;
+      r = *src;
+    }
+    if (!red) return std::nullopt;
+    const auto ps = shape(red->x);                                   // [n, 1, o, oh, ow, c, kh, kw]
+    std::vector<int> axes = red->axes;
+    std::sort(axes.begin(), axes.end());
+    if (ps.size() != 8 || axes != std::vector<int>{5, 6, 7} || ps[1] != 1) return std::nullopt;
+    const uint64_t N = ps[0], O = ps[2], OH = ps[3], OW = ps[4], C = ps[5], KH = ps[6], KW = ps[7];
+    if (out != std::vector<uint64_t>{N, O, OH, OW}) return std::nullopt;
+    ClassId prod = red->x;
+    auto mul = binary(prod, B_MUL);
+    if (!mul) { auto k = cast_src(prod); if (!k || !(mul = binary(*k, B_MUL))) return std::nullopt; }   // the accumulator cast
+    for (int swap = 0; swap < 2; ++swap) {
+      const ClassId xe = swap ? mul->second : mul->first, we = swap ? mul->first : mul->second;
+      auto wr = expand_src(we);
+      if (!wr || shape(*wr) != std::vector<uint64_t>{1, 1, O, 1, 1, C, KH, KW}) continue;
+      auto wsrc = reshape_src(*wr);
+      if (!wsrc || shape(*wsrc) != std::vector<uint64_t>{O, C, KH, KW}) continue;
+      const ClassId w = canon(*wsrc), x = view_source(xe);
+      const auto xs = shape(x);
+      if (shape(xe) != ps || xs.size() != 4 || xs[0] != N || xs[1] != C) continue;
+      const int dt = dtype(x);
+      if (dtype(w) != dt || dtype(cid) != dt || (bias != NONE && dtype(bias) != dt)) continue;
+      if (!(dt == ZYXB_F32 || dt == ZYXB_BF16 || dt == ZYXB_F16 || dt == ZYXB_I32)) continue;
+      const uint64_t H = xs[2], W = xs[3];
+      // the declared padding: the Pad nodes directly on x (rpad_zeros pads the last axis first)
+      uint64_t pad[4] = {0, 0, 0, 0};                                // top, bottom, left, right
+      {
+        std::vector<ClassId> chain;
+        for (ClassId c = xe; c != x; c = nodes[classes[c].nodes[0]].x) chain.push_back(c);
+        uint64_t ext[4] = {N, C, H, W};
+        for (auto it = chain.rbegin(); it != chain.rend(); ++it) {
+          const Node& n = nodes[classes[*it].nodes[0]];
+          if (n.kind != K_PAD || n.lp < 0 || (n.axes[0] != 2 && n.axes[0] != 3)) break;
+          const int64_t after = (int64_t)n.len - n.lp - (int64_t)ext[n.axes[0]];
+          if (after < 0) break;
+          pad[n.axes[0] == 2 ? 0 : 2] += (uint64_t)n.lp; pad[n.axes[0] == 2 ? 1 : 3] += (uint64_t)after;
+          ext[n.axes[0]] = n.len;
+        }
+      }
+      auto probe = [&](uint64_t b, uint64_t co, uint64_t oy, uint64_t ox, uint64_t ci, uint64_t kr, uint64_t ks) {
+        return trace_element(xe, {b, 0, co, oy, ox, ci, kr, ks});
+      };
+      // stride and dilation: the distance between what neighbouring windows / taps read, measured where nothing is padding
+      auto step = [&](bool rows, bool window) -> std::optional<uint64_t> {
+        const uint64_t n_out = rows ? OH : OW, n_tap = rows ? KH : KW;
+        if ((window ? n_out : n_tap) < 2) return 1;                 // a single window or tap: the step is never taken
+        for (uint64_t o : sample_axis(n_out)) for (uint64_t t = 0; t < n_tap; ++t) {
+          const uint64_t o2 = o + (window ? 1 : 0), t2 = t + (window ? 0 : 1);
+          if (o2 >= n_out || t2 >= n_tap) continue;
+          for (uint64_t other : sample_axis(rows ? OW : OH)) {
+            const Origin a = rows ? probe(0, 0, o, other, 0, t, 0) : probe(0, 0, other, o, 0, 0, t);
+            const Origin b = rows ? probe(0, 0, o2, other, 0, t2, 0) : probe(0, 0, other, o2, 0, 0, t2);
+            if (a.zero || b.zero || a.cls != x || b.cls != x) continue;
+            const size_t ax = rows ? 2 : 3;
+            if (b.idx[ax] <= a.idx[ax]) return std::nullopt;
+            return b.idx[ax] - a.idx[ax];
+          }
+        }
+        return std::nullopt;
+      };
+      auto sh = step(true, true), dh = step(true, false), sw = step(false, true), dw = step(false, false);
+      if (!sh || !dh || !sw || !dw) continue;
+      // the output extent the declared padding gives must be the view's
+      auto out_extent = [](uint64_t in, uint64_t before, uint64_t after, uint64_t k, uint64_t s, uint64_t d) -> uint64_t {
+        const uint64_t span = d * (k - 1) + 1, padded = in + before + after;
+        return padded < span ? 0 : (padded - span) / s + 1;
+      };
+      if (out_extent(H, pad[0], pad[1], KH, *sh, *dh) != OH || out_extent(W, pad[2], pad[3], KW, *sw, *dw) != OW) continue;
+      auto reads = [&](uint64_t b, uint64_t co, uint64_t oy, uint64_t ox, uint64_t ci, uint64_t kr, uint64_t ks) {
+        const Origin o = probe(b, co, oy, ox, ci, kr, ks);
+        const int64_t row = (int64_t)(oy * *sh + kr * *dh) - (int64_t)pad[0], col = (int64_t)(ox * *sw + ks * *dw) - (int64_t)pad[2];
+        if (row < 0 || row >= (int64_t)H || col < 0 || col >= (int64_t)W) return o.zero;
+        return !o.zero && o.cls == x && o.idx == std::vector<uint64_t>{b, ci, (uint64_t)row, (uint64_t)col};
+      };
+      bool ok = true;
+      const auto oys = sample_axis(OH), oxs = sample_axis(OW), bs = sample_axis(N), cs = sample_axis(C);
+      for (uint64_t b : {(uint64_t)0, N - 1}) for (uint64_t ci : {(uint64_t)0, C - 1}) for (uint64_t co : {(uint64_t)0, O - 1})
+        for (uint64_t oy : oys) for (uint64_t ox : oxs) for (uint64_t kr = 0; kr < KH && ok; ++kr) for (uint64_t ks = 0; ks < KW && ok; ++ks)
+          ok = reads(b, co, oy, ox, ci, kr, ks);
+      for (uint64_t b : bs) for (uint64_t ci : cs) {
+        if (!ok) break;
+        ok = reads(b, 0, 0, 0, ci, 0, 0) && reads(b, O - 1, OH - 1, OW - 1, ci, KH - 1, KW - 1) && reads(b, 0, OH / 2, OW / 2, ci, KH / 2, KW / 2);
+      }
+      if (!ok) continue;
+      Match m;
+      m.pattern = bias != NONE ? "conv_bias" : "conv";
+      m.desc.kind = ZYXB_KIND_CONV;
+      auto& c = m.desc.u.conv;
+      c.dtype = dt; c.n = N; c.c = C; c.h = H; c.w = W; c.o = O; c.kh = KH; c.kw = KW;
+      c.stride_h = (uint32_t)*sh; c.stride_w = (uint32_t)*sw; c.dil_h = (uint32_t)*dh; c.dil_w = (uint32_t)*dw;
+      c.pad_top = (uint32_t)pad[0]; c.pad_bottom = (uint32_t)pad[1]; c.pad_left = (uint32_t)pad[2]; c.pad_right = (uint32_t)pad[3];
+      c.has_bias = bias != NONE;
+      m.inputs = {x, w};
+      if (bias != NONE) m.inputs.push_back(bias);
+      m.outputs = {cid};
+      return m;
+    }
+    return std::nullopt;
+  }
+
   // ---- cross-entropy with class-index targets ----------------------------------------------------------------------------
   // c = [Cast]{Eq{Expand{labels.reshape([n, 1])}, Expand{arange(classes)}}}, in either operand order -> labels [n]
   // (Tensor::one_hot_along_dim of the unsqueezed labels, tensor/mod.rs:1920-1946).  The arange is recognised by its value: any
@@ -988,7 +1185,7 @@ class Graph {
         if (auto u = match_adam(cid)) { updates.push_back(*u); continue; }
         if (auto u = match_sgd(cid)) { updates.push_back(*u); continue; }
       }
-      if (!(m = match_attention(cid)) && !(m = match_linear(cid, wanted)) && !(m = match_softmax(cid)) && !(m = match_ln_softmax(cid)) && !(m = match_layernorm(cid)) &&
+      if (!(m = match_attention(cid)) && !(m = match_linear(cid, wanted)) && !(m = match_conv(cid)) && !(m = match_softmax(cid)) && !(m = match_ln_softmax(cid)) && !(m = match_layernorm(cid)) &&
           !(m = match_cross_entropy(cid)) && !(m = match_mse(cid)) && !(m = match_reduce(cid)))
         continue;
       out.push_back(std::move(*m));
