@@ -48,7 +48,12 @@ fn sample_axis(n: u64) -> Vec<u64> {
 }
 
 #[derive(Clone, Copy)]
-struct MatMulX { a: ClassId, b: ClassId, m: Dim, n: Dim, k: Dim, batch: Dim, trans_a: bool, trans_b: bool, b_shared: bool, dtype: DType }
+struct MatMulX {
+    a: ClassId, b: ClassId, m: Dim, n: Dim, k: Dim, batch: Dim, trans_a: bool, trans_b: bool, b_shared: bool, dtype: DType,
+    /// rank-4 products over [b, h, .., ..]: operands (and, at the merged class, the result) that are per-head views of stored
+    /// [b, t, h*d] tensors are read where they lie through a row pitch and a two-level batch
+    outer: Dim, heads: Dim, a_heads: bool, b_heads: bool, c_heads: bool,
+}
 
 #[derive(Clone, Copy)]
 struct Update { algo: i32, p: ClassId, g: ClassId, m: Option<ClassId>, v: Option<ClassId>, p_new: ClassId, m_new: Option<ClassId>,
@@ -185,7 +190,14 @@ impl Graph {
         };
         let dt = self.dtype(b);
         if self.dtype(a) != dt || self.dtype(cid) != dt || !matches!(dt, DType::F32 | DType::BF16 | DType::F16 | DType::I32) { return None; }
-        Some(MatMulX { a, b, m, n, k, batch: batch_dims.iter().product(), trans_a, trans_b, b_shared, dtype: dt })
+        let mut mm = MatMulX { a, b, m, n, k, batch: batch_dims.iter().product(), trans_a, trans_b, b_shared, dtype: dt,
+                               outer: 0, heads: 0, a_heads: false, b_heads: false, c_heads: false };
+        if batch_dims.len() == 2 && !b_shared {                   // q / k / v of attention: x.reshape([b, t, h, d]).transpose(1, 2)
+            if let Some(x) = self.head_split_src(a).filter(|&x| self.dtype(x) == dt) { mm.a = x; mm.a_heads = true; }
+            if let Some(x) = self.head_split_src(b).filter(|&x| self.dtype(x) == dt) { mm.b = x; mm.b_heads = true; }
+            if mm.a_heads || mm.b_heads { mm.outer = batch_dims[0]; mm.heads = batch_dims[1]; }
+        }
+        Some(mm)
     }
     fn match_matmul_scaled(&self, cid: ClassId) -> Option<(MatMulX, f32)> {
         if let Some(mm) = self.match_matmul_x(cid) { return Some((mm, 1.0)); }
@@ -224,7 +236,40 @@ impl Graph {
         let (za, zb) = self.binary_of(zz, BOp::Mul)?;
         (near(c1, 0.044_715) && [z1, z3, za, zb].iter().all(|&q| self.same(q, z))).then_some(z)
     }
+    fn gemm_desc(mm: &MatMulX, epi: i32, preact: bool, alpha: f32) -> ZyxbGemmDesc {
+        let mut g = ZyxbGemmDesc {
+            dtype: mm.dtype as i32, m: mm.m, n: mm.n, k: mm.k, batch: mm.batch, trans_a: mm.trans_a as i32, trans_b: mm.trans_b as i32,
+            stride_a: (mm.m * mm.k) as i64, stride_b: if mm.b_shared { 0 } else { (mm.k * mm.n) as i64 }, stride_c: (mm.m * mm.n) as i64,
+            epilogue: epi, store_preact: preact as i32, alpha, ..Default::default()
+        };
+        if mm.heads != 0 {                                        // two-level batch: images outside, heads inside
+            let h = mm.heads;
+            // a stored [rows, cols] matrix per (image, head): inside a [b, t, h*d] tensor (pitch h*cols, heads `cols` apart) or packed
+            let view = |heads: bool, rows: Dim, cols: Dim| -> (u64, i64, i64) {
+                if heads { (h * cols, (rows * h * cols) as i64, cols as i64) } else { (0, (h * rows * cols) as i64, (rows * cols) as i64) }
+            };
+            (g.batch, g.batch_inner) = (mm.outer, h);
+            (g.lda, g.stride_a, g.stride_a_inner) = if mm.trans_a { view(mm.a_heads, mm.k, mm.m) } else { view(mm.a_heads, mm.m, mm.k) };
+            (g.ldb, g.stride_b, g.stride_b_inner) = if mm.trans_b { view(mm.b_heads, mm.n, mm.k) } else { view(mm.b_heads, mm.k, mm.n) };
+            (g.ldc, g.stride_c, g.stride_c_inner) = view(mm.c_heads, mm.m, mm.n);
+        }
+        g
+    }
     fn match_linear(&self, cid: ClassId, wanted: &BTreeSet<ClassId>) -> Option<B200Match> {
+        // the heads merged back, `product.transpose(1, 2).reshape([b, t, h*d])` (multi_head_attention.rs:218-219): the product is
+        // written where the merged tensor lies
+        if let Some(p4) = self.reshape_of(cid).and_then(|r4| self.permute_of(r4, &[0, 2, 1, 3])) {
+            if let (Some(s3), Some(s4)) = (self.const_shape(cid), self.const_shape(p4)) {
+                if s3.len() == 3 && s4.len() == 4 && s3[0] == s4[0] && s3[1] == s4[2] && s3[2] == s4[1] * s4[3] {
+                    if let Some((mut mm, alpha)) = self.match_matmul_scaled(p4).filter(|(mm, _)| !mm.b_shared && mm.dtype == self.dtype(cid)) {
+                        (mm.c_heads, mm.outer, mm.heads) = (true, s4[0], s4[1]);
+                        let gemm = Self::gemm_desc(&mm, EPI_NONE, false, alpha);
+                        return Some(B200Match { pattern: "matmul", inputs: vec![mm.a, mm.b], outputs: vec![cid],
+                                                desc: ZyxbKernelDesc { kind: ZYXB_KIND_GEMM, u: ZyxbDescUnion { gemm } }, numel: Vec::new(), optim_step: 0 });
+                    }
+                }
+            }
+        }
         let (e, act) = if let Some(z) = self.gelu_of(cid) { (z, 2) } else if let Some(z) = self.relu_of(cid) { (z, 1) } else { (cid, 0) };
         let (mut core, mut bias) = (e, None);
         if let Some((x, y)) = self.binary_of(e, BOp::Add) {
@@ -240,11 +285,7 @@ impl Graph {
         if let Some(b) = bias { if self.dtype(b) != mm.dtype { return None; } }
         let epi = match (bias.is_some(), act) { (false, _) => EPI_NONE, (true, 2) => EPI_BIAS_GELU, (true, 1) => EPI_BIAS_RELU, _ => EPI_BIAS };
         let preact = act == 2 && wanted.contains(&e);
-        let gemm = ZyxbGemmDesc {
-            dtype: mm.dtype as i32, m: mm.m, n: mm.n, k: mm.k, batch: mm.batch, trans_a: mm.trans_a as i32, trans_b: mm.trans_b as i32,
-            stride_a: (mm.m * mm.k) as i64, stride_b: if mm.b_shared { 0 } else { (mm.k * mm.n) as i64 }, stride_c: (mm.m * mm.n) as i64,
-            epilogue: epi, store_preact: preact as i32, alpha, ..Default::default()
-        };
+        let gemm = Self::gemm_desc(&mm, epi, preact, alpha);
         let mut inputs = vec![mm.a, mm.b];
         inputs.extend(bias);
         let mut outputs = vec![cid];
@@ -296,7 +337,8 @@ impl Graph {
         let sm = self.match_softmax(pv.a)?;
         let (qk, scale) = self.match_matmul_scaled(sm.inputs[0])?;
         if qk.trans_a || !qk.trans_b || qk.b_shared { return None; }
-        let (xq, xk, xv) = (self.head_split_src(qk.a)?, self.head_split_src(qk.b)?, self.head_split_src(pv.b)?);
+        if !qk.a_heads || !qk.b_heads || !pv.b_heads || pv.a_heads { return None; }          // q, k, v: per-head views of stored tensors
+        let (xq, xk, xv) = (qk.a, qk.b, pv.b);
         let hs = self.const_shape(pv_cls)?;
         let (b, h, t, d) = (hs[0], hs[1], hs[2], hs[3]);
         let shapes_ok = qk.m == t && qk.n == t && qk.k == d && pv.m == t && pv.k == t && pv.n == d && qk.batch == b * h && pv.batch == b * h

@@ -542,3 +542,33 @@ def test_views_that_are_not_the_convolution_window_are_left_alone(g):
     assert conv_patterns(y) == []
     xg, wg = T.leaf(g, L.F32, (2, 4, 12, 12)), T.leaf(g, L.F32, (6, 2, 3, 3))
     assert conv_patterns(xg.conv(wg, groups=2, padding=(1,))) == []
+
+
+@pytest.mark.parametrize("dtype", [L.BF16, L.F32])
+def test_unfused_attention_reads_and_writes_the_per_head_views_in_place(g, dtype):
+    """Outside the fused kernel's shapes (head dimension 64, f32) attention stays three programs, and none of them needs a
+    [b, h, t, d] copy: q, k, v are read as per-head views of the stored [b, t, h*d] tensors (row pitch h*d, heads d apart, a
+    two-level batch), and the product with v is written straight into the merged [b, t, h*d] tensor - the descriptors of the
+    transformer-block plan's unfused path (host/block.cpp: head_view_a / _b / _c, score_view_a / _c)."""
+    nb, t, h, d = 2, 256, 4, 64
+    e = h * d
+    q, k, v = (T.leaf(g, dtype, (nb, t, e)) for _ in range(3))
+    split = lambda x: x.reshape([nb, t, h, d]).permute([0, 2, 1, 3])
+    scale = 1.0 / math.sqrt(d)
+    scores = split(q).dot(split(k).t()) * scale
+    probs = scores.softmax()
+    merged = probs.dot(split(v)).permute([0, 2, 1, 3]).reshape([nb, t, e])
+    at = {m.outputs[0]: m for m in g.match([merged.cls])}
+    ms = at[scores.cls]
+    assert ms.pattern == b"matmul_nt_batched_heads" and list(ms.inputs[:ms.n_inputs]) == [q.cls, k.cls]
+    want = B.gemm_desc(dtype, t, t, d, batch=nb, batch_inner=h, trans_b=True, lda=e, stride_a=t * e, stride_a_inner=d,
+                       ldb=e, stride_b=t * e, stride_b_inner=d, stride_c=h * t * t, stride_c_inner=t * t)
+    got_f, want_f = fields(ms.desc.u.gemm), fields(want.u.gemm)
+    assert abs(got_f.pop("alpha") - scale) <= 1e-2 * scale and want_f.pop("alpha") == 0.0 and got_f == want_f, (got_f, want_f)
+    mp = at[probs.cls]
+    assert mp.pattern == b"softmax" and list(mp.inputs[:mp.n_inputs]) == [scores.cls]
+    assert_same_row(mp.desc, B.rowreduce_desc(L.RR_SOFTMAX, dtype, nb * h * t, t))
+    mv = at[merged.cls]
+    assert mv.pattern == b"matmul_nn_batched_heads" and list(mv.inputs[:mv.n_inputs]) == [probs.cls, v.cls]
+    assert_same_gemm(mv.desc, B.gemm_desc(dtype, t, d, t, batch=nb, batch_inner=h, stride_a=h * t * t, stride_a_inner=t * t,
+                                          ldb=e, stride_b=t * e, stride_b_inner=d, ldc=e, stride_c=t * e, stride_c_inner=d))

@@ -7,7 +7,8 @@
 // is the same machinery over a mirror of that graph, extended to what an aot_only device must cover:
 //   matmul          NN as the reference; NT on a stored weight (`x.dot(W.t())` of Linear::forward, zyx-nn/src/linear.rs:39-45,
 //                   where the reference would hand the kernel the *class* W.t()); TN / TT when the left operand is `x.t()` of
-//                   a stored tensor (a weight gradient written as `dz.t().dot(x)`); rank > 2 with batch strides; the
+//                   a stored tensor (a weight gradient written as `dz.t().dot(x)`); rank > 2 with batch strides; per-head
+//                   views of stored [b, t, h*d] tensors as operands and as the merged result (no [b, h, t, d] copies); the
 //                   accumulator Casts that `sum` puts around the Reduce for 16-bit inputs (tensor/reduce_ops.rs:52-60,143-145);
 //                   a trailing `* const` (attention's 1/sqrt(d)) as alpha; `+ bias`, relu and gelu as epilogues
 //   convolution     Tensor::conv with groups = 1 (tensor/mod.rs:2583-2680), recognised by what its pooling view reads
@@ -227,7 +228,12 @@ class Graph {
     for (size_t i = 0; i + 2 < r; ++i) if (axes[i] != (int)i) return false;
     return axes[r - 2] == (int)r - 1 && axes[r - 1] == (int)r - 2;
   }
-  struct MatMul { ClassId a, b, out; uint64_t m, n, k, batch; bool trans_b, b_shared; int dtype; bool trans_a = false; };
+  struct MatMul {
+    ClassId a, b, out; uint64_t m, n, k, batch; bool trans_b, b_shared; int dtype; bool trans_a = false;
+    // rank-4 products over [b, h, .., ..]: operands (and, at the merged class, the result) that are per-head views of stored
+    // [b, t, h*d] tensors are read where they lie through a row pitch and a two-level batch
+    uint64_t outer = 0, heads = 0; bool a_heads = false, b_heads = false, c_heads = false;
+  };
 
   // The canonical broadcast-reduce form of Tensor::dot (tensor/mod.rs:1469-1490), ending at class `cid`:
   //   a [.., m, k] -Reshape [.., m, 1, k]-> Expand -+
@@ -296,6 +302,12 @@ class Graph {
     if (!(dt == ZYXB_F32 || dt == ZYXB_BF16 || dt == ZYXB_F16 || dt == ZYXB_I32)) return std::nullopt;
     MatMul mm{a, b, cid, m, n, k, numel(batch_dims), trans_b, b_shared, dt};
     mm.trans_a = trans_a;
+    if (batch_dims.size() == 2 && !b_shared) {                // q / k / v of attention: x.reshape([b, t, h, d]).transpose(1, 2)
+      auto xa = head_split_src(a), xb = head_split_src(b);
+      if (xa && dtype(*xa) == dt) { mm.a = *xa; mm.a_heads = true; }
+      if (xb && dtype(*xb) == dt) { mm.b = *xb; mm.b_heads = true; }
+      if (mm.a_heads || mm.b_heads) { mm.outer = batch_dims[0]; mm.heads = batch_dims[1]; }
+    }
     return mm;
   }
 
@@ -307,6 +319,18 @@ class Graph {
     g.trans_a = mm.trans_a; g.trans_b = mm.trans_b;
     g.stride_a = (int64_t)(mm.m * mm.k); g.stride_b = mm.b_shared ? 0 : (int64_t)(mm.k * mm.n); g.stride_c = (int64_t)(mm.m * mm.n);
     g.epilogue = epi; g.store_preact = preact; g.alpha = alpha;
+    if (mm.heads) {                                          // two-level batch: images outside, heads inside
+      const uint64_t H = mm.heads;
+      g.batch = mm.outer; g.batch_inner = H;
+      // a stored [rows, cols] matrix per (image, head): inside a [b, t, h*d] tensor (pitch h*cols, heads `cols` apart) or packed
+      auto view = [H](bool heads, uint64_t rows, uint64_t cols, uint64_t& ld, int64_t& outer, int64_t& inner) {
+        if (heads) { ld = H * cols; outer = (int64_t)(rows * H * cols); inner = (int64_t)cols; }
+        else { ld = 0; outer = (int64_t)(H * rows * cols); inner = (int64_t)(rows * cols); }
+      };
+      view(mm.a_heads, mm.trans_a ? mm.k : mm.m, mm.trans_a ? mm.m : mm.k, g.lda, g.stride_a, g.stride_a_inner);
+      view(mm.b_heads, mm.trans_b ? mm.n : mm.k, mm.trans_b ? mm.k : mm.n, g.ldb, g.stride_b, g.stride_b_inner);
+      view(mm.c_heads, mm.m, mm.n, g.ldc, g.stride_c, g.stride_c_inner);
+    }
     return d;
   }
 
@@ -362,7 +386,25 @@ class Graph {
 
   // matmul [* const] [+ bias [relu | gelu]] ending at cid.  `wanted` are classes somebody else reads (the outputs of the
   // graph being matched): a pre-activation among them becomes the program's second output.
+  static std::string gemm_name(const MatMul& mm) {
+    return std::string("matmul_") + (mm.trans_a ? "t" : "n") + (mm.trans_b ? "t" : "n") + (mm.batch > 1 ? "_batched" : "") + (mm.heads ? "_heads" : "");
+  }
   std::optional<Match> match_linear(ClassId cid, const std::set<ClassId>& wanted) const {
+    // the heads merged back, `product.transpose(1, 2).reshape([b, t, h*d])` (multi_head_attention.rs:218-219): the product is
+    // written where the merged tensor lies
+    if (shape(cid).size() == 3)
+      if (auto r4 = reshape_src(cid)) if (auto p4 = permute_src(*r4, {0, 2, 1, 3})) {
+        const auto s4 = shape(*p4), s3 = shape(cid);
+        if (s4.size() == 4 && s3[0] == s4[0] && s3[1] == s4[2] && s3[2] == s4[1] * s4[3])
+          if (auto sc = match_matmul_scaled(*p4)) if (!sc->first.b_shared && dtype(cid) == sc->first.dtype) {
+            MatMul mm = sc->first;
+            mm.c_heads = true; mm.outer = s4[0]; mm.heads = s4[1];
+            Match mt;
+            mt.pattern = gemm_name(mm); mt.desc = gemm_desc(mm, ZYXB_EPI_NONE, false, sc->second);
+            mt.inputs = {mm.a, mm.b}; mt.outputs = {cid};
+            return mt;
+          }
+      }
     ClassId e = cid;
     int act = 0;
     if (auto z = gelu_of(cid)) { e = *z; act = 2; }
@@ -386,8 +428,7 @@ class Graph {
     const int epi = bias == NONE ? ZYXB_EPI_NONE : act == 2 ? ZYXB_EPI_BIAS_GELU : act == 1 ? ZYXB_EPI_BIAS_RELU : ZYXB_EPI_BIAS;
     const bool preact = act == 2 && wanted.count(e) != 0;
     Match mt;
-    mt.pattern = std::string("matmul_") + (mm.trans_a ? "t" : "n") + (mm.trans_b ? "t" : "n") + (mm.batch > 1 ? "_batched" : "") + (bias != NONE ? "_bias" : "") +
-                 (act == 2 ? "_gelu" : act == 1 ? "_relu" : "");
+    mt.pattern = gemm_name(mm) + (bias != NONE ? "_bias" : "") + (act == 2 ? "_gelu" : act == 1 ? "_relu" : "");
     mt.desc = gemm_desc(mm, epi, preact, sc->second);
     mt.inputs = {mm.a, mm.b};
     if (bias != NONE) mt.inputs.push_back(bias);
@@ -441,8 +482,8 @@ class Graph {
     auto sc = match_matmul_scaled(sm->inputs[0]);
     if (!sc || sc->first.trans_a || !sc->first.trans_b || sc->first.b_shared) return std::nullopt;
     const MatMul& qk = sc->first;
-    auto xq = head_split_src(qk.a), xk = head_split_src(qk.b), xv = head_split_src(pv->b);
-    if (!xq || !xk || !xv) return std::nullopt;
+    if (!qk.a_heads || !qk.b_heads || !pv->b_heads || pv->a_heads) return std::nullopt;      // q, k, v: per-head views of stored tensors
+    const std::optional<ClassId> xq = qk.a, xk = qk.b, xv = pv->b;
     const auto hs = shape(*pv_cls);                          // [b, h, t, d]
     const uint64_t B = hs[0], H = hs[1], T = hs[2], D = hs[3];
     if (qk.m != T || qk.n != T || qk.k != D || pv->m != T || pv->k != T || pv->n != D || qk.batch != B * H || pv->batch != B * H) return std::nullopt;
