@@ -13,8 +13,8 @@ use std::collections::{BTreeMap, BTreeSet};
 use crate::{
     DType,
     dtype::Constant,
-    backend::b200::{ZyxbAttentionDesc, ZyxbConvDesc, ZyxbDescUnion, ZyxbGemmDesc, ZyxbKernelDesc, ZyxbOptimDesc, ZyxbRowreduceDesc, ZYXB_KIND_ATTENTION,
-                    ZYXB_KIND_CONV, ZYXB_KIND_GEMM, ZYXB_KIND_OPTIM, ZYXB_KIND_ROWREDUCE},
+    backend::b200::{ZyxbAttentionDesc, ZyxbConvDesc, ZyxbDescUnion, ZyxbEltwiseDesc, ZyxbGemmDesc, ZyxbKernelDesc, ZyxbOptimDesc, ZyxbRowreduceDesc, ZYXB_KIND_ATTENTION,
+                    ZYXB_KIND_CONV, ZYXB_KIND_ELTWISE, ZYXB_KIND_GEMM, ZYXB_KIND_OPTIM, ZYXB_KIND_ROWREDUCE},
     graph::{ClassId, Graph, Node},
     kernel::{BOp, UOp},
     shape::Dim,
@@ -62,6 +62,8 @@ struct Update { algo: i32, p: ClassId, g: ClassId, m: Option<ClassId>, v: Option
 
 const RR_SUM: i32 = 0; const RR_MAX: i32 = 1; const RR_MEAN: i32 = 3; const RR_SOFTMAX: i32 = 6; const RR_LN_SOFTMAX: i32 = 7; const RR_LAYERNORM: i32 = 8; const RR_MSE: i32 = 14;
 const RR_VAR: i32 = 4; const RR_STD: i32 = 5; const RR_COLSUM: i32 = 13; const RR_CROSS_ENTROPY: i32 = 9;
+const EW_RELU: i32 = 0; const EW_GELU: i32 = 1; const EW_ADD: i32 = 2; const EW_SUB: i32 = 3; const EW_MUL: i32 = 4; const EW_SCALE: i32 = 5;
+const EW_CAST: i32 = 9; const EW_TANH: i32 = 10; const EW_SIGMOID: i32 = 11; const EW_EXP: i32 = 12; const EW_BIAS_ADD: i32 = 13;
 const EPI_NONE: i32 = 0; const EPI_BIAS: i32 = 1; const EPI_BIAS_RELU: i32 = 2; const EPI_BIAS_GELU: i32 = 3;
 const OPT_SGD: i32 = 0; const OPT_ADAM: i32 = 1; const OPT_ADAMW: i32 = 2;
 
@@ -417,6 +419,60 @@ impl Graph {
         if !f32s || self.const_shape(y)? != xs || self.const_shape(t)? != xs { return None; }
         Some(self.row_match("mse_loss", self.row_desc(RR_MSE, y)?, vec![y, t], cid))
     }
+    // ---- elementwise programs ------------------------------------------------------------------------------------------------
+    /// What is left when no larger pattern ends at a class: one elementwise program over stored operands
+    /// (tensor/elementwise.rs).  Operands are whole tensors of the result's shape - a broadcast operand is either a scalar
+    /// constant (scale) or a vector along the last axis (bias).  16-bit and f32 floats only (what the kernels take).
+    fn match_eltwise(&self, cid: ClassId) -> Option<B200Match> {
+        let is_row = |d: DType| matches!(d, DType::F32 | DType::BF16 | DType::F16);
+        let (dt, cs) = (self.dtype(cid), self.const_shape(cid)?);
+        let n: Dim = cs.iter().product();
+        if !is_row(dt) || cs.is_empty() || n == 0 { return None; }
+        let plain = |x: ClassId| self.expand_of(x).is_none() && self.const_value(x).is_none() && self.const_shape(x).as_ref() == Some(&cs);
+        let whole = |x: ClassId| plain(x) && self.dtype(x) == dt;
+        let program = |pattern: &'static str, op: i32, inputs: Vec<ClassId>, p0: f32, cols: Dim, dt_in: DType| {
+            let eltwise = ZyxbEltwiseDesc { op, dtype: dt_in as i32, dtype_out: dt as i32, numel: n, cols, p0 };
+            Some(B200Match { pattern, inputs: inputs.into_iter().map(|c| self.canon(c)).collect(), outputs: vec![cid],
+                             desc: ZyxbKernelDesc { kind: ZYXB_KIND_ELTWISE, u: ZyxbDescUnion { eltwise } }, numel: Vec::new(), optim_step: 0 })
+        };
+        if let Some(z) = self.gelu_of(cid).filter(|&z| whole(z)) { return program("gelu", EW_GELU, vec![z], 0.0, 0, dt); }
+        if let Some(z) = self.relu_of(cid).filter(|&z| whole(z)) { return program("relu", EW_RELU, vec![z], 0.0, 0, dt); }
+        if let Some(u) = self.tanh_of(cid).filter(|&u| whole(u)) { return program("tanh", EW_TANH, vec![u], 0.0, 0, dt); }
+        // sigmoid(x) = e / (e + 1), e = exp(x)   (elementwise.rs:457-460)
+        if let Some((e, den)) = self.binary_of(cid, BOp::Div) {
+            if let Some((e2, one)) = self.binary_const(den, BOp::Add) {
+                if self.same(e, e2) && (one - 1.0).abs() <= 1e-6 {
+                    if let Some(x) = self.unary_of(e, UOp::Exp).filter(|&x| whole(x)) { return program("sigmoid", EW_SIGMOID, vec![x], 0.0, 0, dt); }
+                }
+            }
+        }
+        if let Some(x) = self.unary_of(cid, UOp::Exp).filter(|&x| whole(x)) { return program("exp", EW_EXP, vec![x], 0.0, 0, dt); }
+        if let Some(x) = self.cast_src(cid).filter(|&x| is_row(self.dtype(x)) && plain(x)) { return program("cast", EW_CAST, vec![x], 0.0, 0, self.dtype(x)); }
+        if let Some((x, k)) = self.binary_const(cid, BOp::Mul).filter(|&(x, _)| whole(x)) { return program("scale", EW_SCALE, vec![x], k as f32, 0, dt); }
+        for (bop, ew, name) in [(BOp::Add, EW_ADD, "add"), (BOp::Sub, EW_SUB, "sub"), (BOp::Mul, EW_MUL, "mul")] {
+            if let Some((x, y)) = self.binary_of(cid, bop).filter(|&(x, y)| whole(x) && whole(y)) { return program(name, ew, vec![x, y], 0.0, 0, dt); }
+        }
+        let (p, q) = self.binary_of(cid, BOp::Add)?;                          // x + bias along the last axis
+        for (x, be) in [(p, q), (q, p)] {
+            if !whole(x) || self.expand_of(be).is_none() || self.const_value(be).is_some() { continue; }
+            let b = self.canon(self.unbroadcast(be));
+            let cols = *cs.last()?;
+            if self.const_shape(b).as_deref() == Some(&[cols][..]) && self.dtype(b) == dt && self.trailing_vector(be) {
+                return program("bias_add", EW_BIAS_ADD, vec![x, b], 0.0, cols, dt);
+            }
+        }
+        None
+    }
+    /// c = Expand{[Reshape]{v [n]}} with v laid along the LAST axis of c (every wrapper keeps all but the last extent at 1)
+    fn trailing_vector(&self, c: ClassId) -> bool {
+        let Some(mut s) = self.expand_of(c) else { return false };
+        loop {
+            let Some(sh) = self.const_shape(s) else { return false };
+            if sh.is_empty() || sh[..sh.len() - 1].iter().any(|&d| d != 1) { return false; }
+            match self.reshape_of(s) { Some(r) => s = r, None => return true }
+        }
+    }
+
     // ---- constant folding ---------------------------------------------------------------------------------------------------
     /// The value of a class that depends on no stored tensor: constants under movement ops, paddings, reductions, casts and
     /// arithmetic, the way the index helpers build them (Tensor::arange is `full(step).cumsum(0) + start - step`,
@@ -905,6 +961,23 @@ impl Graph {
                              else if h.first { 1 } else { ((1.0 - h.bc1).ln() / h.b1.ln()).round().max(2.0) as u64 };
             out.push(B200Match { pattern, inputs, outputs: outs,
                                  desc: ZyxbKernelDesc { kind: ZYXB_KIND_OPTIM, u: ZyxbDescUnion { optim } }, numel, optim_step });
+        }
+        // Elementwise programs, on demand: whatever somebody has to produce - an output of the graph or an input of a program found
+        // above - that is neither stored nor the result of one of those programs gets an elementwise program if one fits, and that
+        // program's inputs are looked at in turn.  (Offering every Mul and Add of the graph as a program of its own would bury the
+        // patterns above under their own sub-expressions.)
+        let has_kernel = |c: ClassId| self.classes[c].nodes.iter().any(|&nid| matches!(self.nodes[nid].node, Node::Kernel { .. }));
+        let mut produced: BTreeSet<ClassId> = out.iter().flat_map(|m| m.outputs.iter().map(|&o| self.canon(o))).collect();
+        let mut tried = BTreeSet::new();
+        let mut demand: Vec<ClassId> = wanted.iter().rev().copied().collect();
+        for m in &out { demand.extend(m.inputs.iter().rev()); }
+        while let Some(c) = demand.pop() {
+            let k = self.canon(c);
+            if !tried.insert(k) || produced.contains(&k) || self.is_leaf(c) || has_kernel(c) || has_kernel(k) { continue; }
+            let Some(m) = self.match_eltwise(c) else { continue };
+            produced.insert(k);
+            demand.extend(m.inputs.iter().rev());
+            out.push(m);
         }
         out
     }

@@ -235,17 +235,19 @@ def test_adamw_update_is_one_multi_tensor_program(g, dtype, step):
 
 
 def test_what_is_not_a_pattern_is_left_alone(g):
-    a, b = T.leaf(g, L.F32, (32, 16)), T.leaf(g, L.F32, (32, 16))
-    c = (a * b + a).exp()                       # an elementwise chain: no descriptor covers it
     wrong_k = T.leaf(g, L.F32, (8, 5)).reshape((8, 1, 5)).expand((8, 3, 5)) * T.leaf(g, L.F32, (3, 5)).reshape((1, 3, 5)).expand((8, 3, 5))
     d = wrong_k.sum([-1])                       # product and sum, but the right operand is not a transposed [k, n] tensor
-    assert g.match([c.cls, d.cls]) == []
-    # a bf16 tensor cast to f32 by the user and summed: the f32 row sum reads the *cast* class (somebody else has to produce
-    # it), never the bf16 leaf - the 16-bit kernel would round the result
+    i = T.leaf(g, L.I32, (32, 16))
+    assert g.match([d.cls, (i * i + i).cls]) == []         # nor is there an elementwise program for integers
+    # a bf16 tensor cast to f32 by the user and summed: the f32 row sum reads the *cast* class, never the bf16 leaf (the 16-bit
+    # kernel would round the result), and the cast it now depends on becomes a program of its own
     leaf = T.leaf(g, L.BF16, (8, 4))
     wide = leaf.cast(L.F32)
     ms = g.match([wide.sum([-1]).cls])
-    assert [m.pattern for m in ms] == [b"sum"] and ms[0].desc.u.rowreduce.dtype == L.F32 and ms[0].inputs[0] == wide.cls != leaf.cls
+    assert [m.pattern for m in ms] == [b"sum", b"cast"]
+    assert ms[0].desc.u.rowreduce.dtype == L.F32 and ms[0].inputs[0] == wide.cls != leaf.cls
+    e = ms[1].desc.u.eltwise
+    assert (e.op, e.dtype, e.dtype_out, e.numel) == (L.EW_CAST, L.BF16, L.F32, 32) and ms[1].inputs[0] == leaf.cls and ms[1].outputs[0] == wide.cls
 
 
 def test_constructor_arguments_are_validated(g):
@@ -572,3 +574,41 @@ def test_unfused_attention_reads_and_writes_the_per_head_views_in_place(g, dtype
     assert mv.pattern == b"matmul_nn_batched_heads" and list(mv.inputs[:mv.n_inputs]) == [probs.cls, v.cls]
     assert_same_gemm(mv.desc, B.gemm_desc(dtype, t, d, t, batch=nb, batch_inner=h, stride_a=h * t * t, stride_a_inner=t * t,
                                           ldb=e, stride_b=t * e, stride_b_inner=d, ldc=e, stride_c=t * e, stride_c_inner=d))
+
+
+def test_elementwise_programs_are_matched_on_demand(g):
+    """No larger pattern ends at these classes, and somebody needs them - they are outputs of the graph or inputs of a matched
+    program - so each becomes one elementwise program (the descriptors of zyx_b200.backend.eltwise_desc) and its operands are
+    looked at in turn.  Sub-expressions nobody asks for (the inside of a gelu, the terms of an optimizer update) are not offered."""
+    a, b = T.leaf(g, L.F32, (32, 16)), T.leaf(g, L.F32, (32, 16))
+    ab = a * b
+    s1 = ab + a
+    c = s1.exp()
+    ms = g.match([c.cls])
+    assert [(m.pattern, list(m.inputs[:m.n_inputs]), m.outputs[0]) for m in ms] == [
+        (b"exp", [s1.cls], c.cls), (b"add", [ab.cls, a.cls], s1.cls), (b"mul", [a.cls, b.cls], ab.cls)]
+    for m, op in zip(ms, (L.EW_EXP, L.EW_ADD, L.EW_MUL)):
+        assert m.desc.kind == L.KIND_ELTWISE and fields(m.desc.u.eltwise) == fields(B.eltwise_desc(op, L.F32, 512).u.eltwise)
+    assert g.match([c.cls]) == []                                   # every class on the way now holds its program
+    x = T.leaf(g, L.BF16, (64, 48))
+    bias = T.leaf(g, L.BF16, (48,))
+    outs = {"gelu": x.gelu(), "relu": x.relu(), "tanh": x.tanh(), "sigmoid": x.exp() / (x.exp() + 1), "scale": x * 0.25,
+            "sub": x - x.relu(), "bias_add": x + bias, "cast": x.cast(L.F32)}
+    at = {m.outputs[0]: m for m in g.match([t.cls for t in outs.values()])}
+    ops = {"gelu": L.EW_GELU, "relu": L.EW_RELU, "tanh": L.EW_TANH, "sigmoid": L.EW_SIGMOID, "scale": L.EW_SCALE, "sub": L.EW_SUB,
+           "bias_add": L.EW_BIAS_ADD, "cast": L.EW_CAST}
+    for name, t in outs.items():
+        m = at[t.cls]
+        assert m.pattern == name.encode(), (name, m.pattern)
+        want = B.eltwise_desc(ops[name], L.BF16, 64 * 48, p0=0.25 if name == "scale" else 0.0, cols=48 if name == "bias_add" else 0,
+                              dtype_out=L.F32 if name == "cast" else None)
+        assert fields(m.desc.u.eltwise) == fields(want.u.eltwise), name
+        want_in = {"sub": [x.cls, outs["relu"].cls], "bias_add": [x.cls, bias.cls]}.get(name, [x.cls])
+        assert list(m.inputs[:m.n_inputs]) == want_in, name
+    assert len(at) == len(outs)                                     # x.relu() under the subtraction is the relu already matched
+    # a bias laid along the rows is not the bias form; an optimizer update offers none of its terms
+    col = T.leaf(g, L.BF16, (64,))
+    assert g.match([(x + col.reshape([64, 1])).cls]) == []
+    from tests.zyx_trace import sgd_update as sgd
+    p, gr = T.leaf(g, L.F32, (50, 30)), T.leaf(g, L.F32, (50, 30))
+    assert [m.pattern for m in g.match([sgd([p], [gr], 0.01, weight_decay=0.1)[0].cls])] == [b"sgd"]

@@ -17,6 +17,8 @@
 //                   sum / max / mean / var / std over the last axis (tensor/reduce_ops.rs:45-157), `sum([0])` of a matrix
 //                   (column sums), mse_loss of f32 tensors, cross_entropy of f32 logits with i32 class indices
 //                   (tensor/mod.rs:1639-1656; its one-hot compares against an arange recognised by constant folding)
+//   elementwise     relu, gelu, tanh, sigmoid, exp, float casts, * const, + - * of whole tensors, + bias (tensor/elementwise.rs),
+//                   on demand: for outputs of the graph and inputs of matched programs that nothing produces yet
 //   optimizer       SGD::update (zyx-optim/src/sgd.rs:45-84: plain, weight decay, momentum with dampening, Nesterov),
 //                   Adam::update (zyx-optim/src/adam.rs, without amsgrad), AdamW::update (zyx-optim/src/adamw.rs:51-97), first
 //                   and later steps, all matched tensors of one update grouped into one multi-tensor program
@@ -685,6 +687,62 @@ class Graph {
     return mul && expand_src(mul->first) && expand_src(mul->second);
   }
 
+  // ---- elementwise programs ---------------------------------------------------------------------------------------------
+  // What is left when no larger pattern ends at a class: one elementwise program over stored operands (tensor/elementwise.rs).
+  // Operands are whole tensors of the result's shape - a broadcast operand is either a scalar constant (scale) or a vector
+  // along the last axis (bias) - so the broadcast product inside a dot or the shifted row inside a softmax are not offered as
+  // programs of their own.  16-bit and f32 floats only (what the kernels take).
+  std::optional<Match> match_eltwise(ClassId cid) const {
+    const int dt = dtype(cid);
+    const auto& cs = shape(cid);
+    const uint64_t n = numel(cs);
+    if (!row_dtype(dt) || cs.empty() || n == 0) return std::nullopt;
+    auto whole = [&](ClassId x) { return shape(x) == cs && dtype(x) == dt && !expand_src(x) && !const_value(x); };
+    auto program = [&](const char* name, int op, std::vector<ClassId> in, float p0 = 0.0f, uint64_t cols = 0, int dt_in = -1) {
+      Match m; m.pattern = name; m.desc.kind = ZYXB_KIND_ELTWISE;
+      auto& e = m.desc.u.eltwise;
+      e.op = op; e.dtype = dt_in < 0 ? dt : dt_in; e.dtype_out = dt; e.numel = n; e.cols = cols; e.p0 = p0;
+      for (ClassId& c : in) c = canon(c);
+      m.inputs = std::move(in); m.outputs = {cid};
+      return m;
+    };
+    if (auto z = gelu_of(cid)) if (whole(*z)) return program("gelu", ZYXB_EW_GELU, {*z});
+    if (auto z = relu_of(cid)) if (whole(*z)) return program("relu", ZYXB_EW_RELU, {*z});
+    if (auto u = tanh_of(cid)) if (whole(*u)) return program("tanh", ZYXB_EW_TANH, {*u});
+    if (auto div = binary(cid, B_DIV))                               // sigmoid(x) = e / (e + 1), e = exp(x)   (elementwise.rs:457-460)
+      if (auto den = binary_const(div->second, B_ADD)) if (same(den->first, div->first) && fabs(den->second - 1.0) <= 1e-6)
+        if (auto x = unary(div->first, U_EXP)) if (whole(*x)) return program("sigmoid", ZYXB_EW_SIGMOID, {*x});
+    if (auto x = unary(cid, U_EXP)) if (whole(*x)) return program("exp", ZYXB_EW_EXP, {*x});
+    if (auto x = cast_src(cid)) if (row_dtype(dtype(*x)) && shape(*x) == cs && !expand_src(*x) && !const_value(*x))
+      return program("cast", ZYXB_EW_CAST, {*x}, 0.0f, 0, dtype(*x));
+    if (auto sc = binary_const(cid, B_MUL)) if (whole(sc->first)) return program("scale", ZYXB_EW_SCALE, {sc->first}, (float)sc->second);
+    const std::tuple<int, int, const char*> ops[] = {{B_ADD, ZYXB_EW_ADD, "add"}, {B_SUB, ZYXB_EW_SUB, "sub"}, {B_MUL, ZYXB_EW_MUL, "mul"}};
+    for (auto [bop, ew, name] : ops)
+      if (auto b = binary(cid, bop)) if (whole(b->first) && whole(b->second)) return program(name, ew, {b->first, b->second});
+    if (auto add = binary(cid, B_ADD))                               // x + bias along the last axis
+      for (int swap = 0; swap < 2; ++swap) {
+        const ClassId x = swap ? add->second : add->first, be = swap ? add->first : add->second;
+        if (!whole(x) || !expand_src(be) || const_value(be)) continue;
+        const ClassId b = canon(unbroadcast(be));
+        if (shape(b) == std::vector<uint64_t>{cs.back()} && dtype(b) == dt && trailing_vector(be))
+          return program("bias_add", ZYXB_EW_BIAS_ADD, {x, b}, 0.0f, cs.back());
+      }
+    return std::nullopt;
+  }
+  // c = Expand{[Reshape]{v [n]}} with v laid along the LAST axis of c (every wrapper keeps all but the last extent at 1)
+  bool trailing_vector(ClassId c) const {
+    auto e = expand_src(c);
+    if (!e) return false;
+    for (ClassId s = *e;;) {
+      const auto& sh = shape(s);
+      if (sh.empty()) return false;
+      for (size_t i = 0; i + 1 < sh.size(); ++i) if (sh[i] != 1) return false;
+      auto r = reshape_src(s);
+      if (!r) return true;
+      s = *r;
+    }
+  }
+
   // ---- constant folding --------------------------------------------------------------------------------------------------
   // The value of a class that depends on no stored tensor: constants under movement ops, paddings, reductions, casts and
   // arithmetic, the way the reference's index helpers build them (Tensor::arange is `full(step).cumsum(0) + start - step`,
@@ -1264,6 +1322,27 @@ class Graph {
       if (h.algo != ZYXB_OPT_SGD && !h.first) { mt.inputs.insert(mt.inputs.end(), mm.begin(), mm.end()); mt.inputs.insert(mt.inputs.end(), vv.begin(), vv.end()); }
       mt.outputs = outs;
       out.push_back(std::move(mt));
+    }
+    // Elementwise programs, on demand: whatever somebody has to produce - an output of the graph or an input of a program found
+    // above - that is neither stored nor the result of one of those programs gets an elementwise program if one fits, and that
+    // program's inputs are looked at in turn.  (Offering every Mul and Add of the graph as a program of its own would bury the
+    // patterns above under their own sub-expressions.)
+    {
+      auto has_kernel = [&](ClassId c) { for (uint32_t nid : classes[c].nodes) if (nodes[nid].kind == K_KERNEL) return true; return false; };
+      std::set<ClassId> produced, tried;
+      for (const Match& m : out) for (ClassId o : m.outputs) produced.insert(canon(o));
+      std::vector<ClassId> demand(wanted.rbegin(), wanted.rend());
+      for (const Match& m : out) demand.insert(demand.end(), m.inputs.rbegin(), m.inputs.rend());
+      while (!demand.empty()) {
+        const ClassId c = demand.back();
+        demand.pop_back();
+        if (!valid(c) || !tried.insert(canon(c)).second || produced.count(canon(c)) || is_leaf(c) || has_kernel(c) || has_kernel(canon(c))) continue;
+        auto m = match_eltwise(c);
+        if (!m) continue;
+        produced.insert(canon(c));
+        demand.insert(demand.end(), m->inputs.rbegin(), m->inputs.rend());
+        out.push_back(std::move(*m));
+      }
     }
     for (size_t i = 0; i < out.size(); ++i) {
       if (out[i].desc.kind == ZYXB_KIND_OPTIM) out[i].desc.u.optim.numel = out[i].numel.data();
