@@ -60,7 +60,7 @@ struct Update { algo: i32, p: ClassId, g: ClassId, m: Option<ClassId>, v: Option
                 v_new: Option<ClassId>, lr: f64, wd: f64, b1: f64, b2: f64, eps: f64, bc1: f64, bc2: f64, first: bool,
                 mom: f64, damp: f64, nesterov: bool }      // SGD with momentum: m / m_new are the buffer
 
-const RR_SUM: i32 = 0; const RR_MAX: i32 = 1; const RR_MEAN: i32 = 3; const RR_SOFTMAX: i32 = 6; const RR_LN_SOFTMAX: i32 = 7; const RR_LAYERNORM: i32 = 8; const RR_MSE: i32 = 14;
+const RR_SUM: i32 = 0; const RR_MAX: i32 = 1; const RR_MIN: i32 = 2; const RR_MEAN: i32 = 3; const RR_SOFTMAX: i32 = 6; const RR_LN_SOFTMAX: i32 = 7; const RR_LAYERNORM: i32 = 8; const RR_MSE: i32 = 14;
 const RR_VAR: i32 = 4; const RR_STD: i32 = 5; const RR_COLSUM: i32 = 13; const RR_CROSS_ENTROPY: i32 = 9;
 const EW_RELU: i32 = 0; const EW_GELU: i32 = 1; const EW_ADD: i32 = 2; const EW_SUB: i32 = 3; const EW_MUL: i32 = 4; const EW_SCALE: i32 = 5;
 const EW_CAST: i32 = 9; const EW_TANH: i32 = 10; const EW_SIGMOID: i32 = 11; const EW_EXP: i32 = 12; const EW_BIAS_ADD: i32 = 13;
@@ -299,7 +299,8 @@ impl Graph {
     fn row_desc(&self, op: i32, x: ClassId) -> Option<ZyxbRowreduceDesc> {
         let s = self.const_shape(x)?;
         let cols = *s.last()?;
-        matches!(self.dtype(x), DType::F32 | DType::BF16 | DType::F16)
+        let exact_int = self.dtype(x) == DType::I32 && matches!(op, RR_SUM | RR_MAX | RR_MIN);       // i32 sum / max / min are exact programs
+        (matches!(self.dtype(x), DType::F32 | DType::BF16 | DType::F16) || exact_int)
             .then(|| ZyxbRowreduceDesc { op, dtype: self.dtype(x) as i32, rows: s.iter().product::<Dim>() / cols, cols, correction: 1, ..Default::default() })
     }
     fn row_match(&self, pattern: &'static str, rowreduce: ZyxbRowreduceDesc, inputs: Vec<ClassId>, out: ClassId) -> B200Match {
@@ -810,6 +811,14 @@ impl Graph {
             if !self.is_broadcast_product(x) { if let Some(d) = self.row_desc(RR_COLSUM, x) { return Some(self.row_match("colsum", d, vec![x], cid)); } }
         }
         if let Some((x, _)) = self.mean_last(cid) { if let Some(d) = self.row_desc(RR_MEAN, x) { return Some(self.row_match("mean", d, vec![x], cid)); } }
+        // min = -max(-x) for floats, !max(!x) bitwise for integers (Tensor::inverse, reduce_ops.rs:33-42, 93-99); keepdim reshapes outside
+        let c = match self.reshape_of(cid) { Some(r) if self.numel_of(r) == self.numel_of(cid) => r, _ => cid };
+        for uop in [UOp::Neg, UOp::BitNot] {
+            let x = self.unary_of(c, uop).and_then(|inner| self.reduce_last(inner, BOp::Max)).and_then(|nx| self.unary_of(nx, uop)).map(|x| self.canon(x));
+            if let Some(x) = x.filter(|&x| self.dtype(x) == self.dtype(cid) && (uop == UOp::Neg) == self.dtype(x).is_float()) {
+                if let Some(d) = self.row_desc(RR_MIN, x) { return Some(self.row_match("min", d, vec![x], cid)); }
+            }
+        }
         for (rop, rr, name) in [(BOp::Add, RR_SUM, "sum"), (BOp::Max, RR_MAX, "max")] {
             if let Some(x) = self.reduce_last(cid, rop) {
                 if self.dtype(cid) != self.dtype(x) || self.is_broadcast_product(x) { continue; }

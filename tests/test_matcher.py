@@ -195,6 +195,19 @@ def test_plain_reductions(g):
     assert_same_row(m["mean"].desc, B.rowreduce_desc(L.RR_MEAN, L.F32, 100, 333))
 
 
+def test_min_is_the_inverted_max(g):
+    """ReduceOp::Min is `inverse().max().inverse()` (reduce_ops.rs:33-42, 93-99): a negation around the max of the negated
+    tensor for floats, a bitwise not for integers; the row program takes the tensor itself."""
+    for dtype in (L.F32, L.BF16, L.I32):
+        x = T.leaf(g, dtype, (40, 96))
+        lo, lo_keep = x.min([-1]), x.min([-1], keepdim=True)
+        at = {m.outputs[0]: m for m in g.match([lo.cls, lo_keep.cls])}
+        for out in (lo, lo_keep):
+            m = at[out.cls]
+            assert m.pattern == b"min" and list(m.inputs[:m.n_inputs]) == [x.cls]
+            assert_same_row(m.desc, B.rowreduce_desc(L.RR_MIN, dtype, 40, 96))
+
+
 def test_sgd_update_of_simplenet_is_one_multi_tensor_program(g):
     shapes = [(128, 784), (128,), (10, 128), (10,)]
     params = [T.leaf(g, L.F32, s) for s in shapes]

@@ -282,6 +282,17 @@ class T:
     def sum(self, axes, keepdim=False): return self._reduce(M.B_ADD, axes, keepdim)
     def max(self, axes, keepdim=False): return self._reduce(M.B_MAX, axes, keepdim)
 
+    def min(self, axes, keepdim=False):
+        """ReduceOp::Min = inverse().max().inverse() (reduce_ops.rs:33-42, 93-99); the keepdim reshape comes last"""
+        inv = (lambda t: t._unary(M.U_NEG)) if self.dtype in (L.F32, L.BF16, L.F16, L.F64) else (lambda t: t._unary(M.U_BITNOT))
+        t = inv(inv(self).max(axes))
+        if keepdim:
+            shape = list(self.shape)
+            for a in axes:
+                shape[a % len(shape)] = 1
+            t = t.reshape(shape)
+        return t
+
     def mean(self, axes, keepdim=False):
         shape = list(self.shape)
         n = 1

@@ -14,7 +14,7 @@
 //   convolution     Tensor::conv with groups = 1 (tensor/mod.rs:2583-2680), recognised by what its pooling view reads
 //   attention       the mask-free core of MultiheadAttention::forward (zyx-nn/src/multi_head_attention.rs:197-226)
 //   row kernels     softmax, ln_softmax (tensor/mod.rs:1427-1461), LayerNorm::forward (zyx-nn/src/layer_norm.rs:95-135),
-//                   sum / max / mean / var / std over the last axis (tensor/reduce_ops.rs:45-157), `sum([0])` of a matrix
+//                   sum / max / min / mean / var / std over the last axis (tensor/reduce_ops.rs:45-157), `sum([0])` of a matrix
 //                   (column sums), mse_loss of f32 tensors, cross_entropy of f32 logits with i32 class indices
 //                   (tensor/mod.rs:1639-1656; its one-hot compares against an arange recognised by constant folding)
 //   elementwise     relu, gelu, tanh, sigmoid, exp, float casts, * const, + - * of whole tensors, + bias (tensor/elementwise.rs),
@@ -651,6 +651,20 @@ class Graph {
     if (auto x = mean_last(cid)) if (row_dtype(dtype(*x)) && shape(*x).size() >= 1) {
       Match m; m.pattern = "mean"; m.desc = row_desc(ZYXB_RR_MEAN, dtype(*x), shape(*x)); m.inputs = {*x}; m.outputs = {cid};
       return m;
+    }
+    // min = -max(-x) for floats, !max(!x) bitwise for integers (Tensor::inverse, reduce_ops.rs:33-42, 93-99); keepdim reshapes outside
+    {
+      ClassId c = cid;
+      if (auto r = reshape_src(cid)) if (numel(shape(*r)) == numel(shape(cid))) c = *r;
+      for (int uop : {(int)U_NEG, (int)U_BITNOT})
+        if (auto inner = unary(c, uop)) if (auto nx = reduce_last(*inner, B_MAX)) if (auto x0 = unary(*nx, uop)) {
+          const ClassId x = canon(*x0);
+          const bool ok = uop == U_NEG ? row_dtype(dtype(x)) : dtype(x) == ZYXB_I32;
+          if (ok && dtype(cid) == dtype(x) && !shape(x).empty()) {
+            Match m; m.pattern = "min"; m.desc = row_desc(ZYXB_RR_MIN, dtype(x), shape(x)); m.inputs = {x}; m.outputs = {cid};
+            return m;
+          }
+        }
     }
     for (auto [rop, rr] : ops)
       if (auto x = reduce_last(cid, rop)) {
