@@ -333,7 +333,9 @@ pub struct B200Device {
     device_id: DeviceId,
     memory_pool_id: PoolId,
     /// DeviceProgramId -> the library's program handle
-    programs: Slab<DeviceProgramId, u32>,
+    /// program handle and the buffers the device itself appends to every launch of it (the fused attention program writes its
+    /// log-sum-exp [batch*heads, seq] f32 behind the output; the graph has no class for it)
+    programs: Slab<DeviceProgramId, (u32, Vec<u32>)>,
 }
 
 impl std::fmt::Debug for B200Device {
@@ -426,8 +428,11 @@ impl B200Device {
     }
 
     pub fn release(&mut self, program_id: DeviceProgramId) {
-        let handle = self.programs[program_id];
+        let (handle, extra) = self.programs[program_id].clone();
         unsafe { (self.sh.api.program_release)(self.sh.ctx, self.dev, handle) };
+        for buffer in extra {
+            unsafe { (self.sh.api.free)(self.sh.ctx, self.dev, buffer, std::ptr::null(), 0) };
+        }
         self.programs.remove(program_id);
     }
 
@@ -449,7 +454,17 @@ impl B200Device {
                 // an optimizer program's own counter says whether state is read and which bias correction applies
                 unsafe { (self.sh.api.program_set_step)(self.sh.ctx, self.dev, handle, m.optim_step - 1) };
             }
-            let program = self.programs.push(handle);
+            let mut extra = Vec::new();
+            if desc.kind == ZYXB_KIND_ATTENTION {
+                let a = unsafe { desc.u.attention };
+                let (mut lse, mut ev) = (0u32, ZyxbEvent::default());
+                if unsafe { (self.sh.api.alloc)(self.sh.ctx, self.dev, a.batch * a.heads * a.seq * 4, &mut lse, &mut ev) } != 0 {
+                    unsafe { (self.sh.api.program_release)(self.sh.ctx, self.dev, handle) };
+                    continue;
+                }
+                extra.push(lse);
+            }
+            let program = self.programs.push((handle, extra));
             let nid = graph.nodes.push(NodeData {
                 node: Node::Kernel {
                     inputs: m.inputs.clone().into_boxed_slice(),
@@ -471,10 +486,11 @@ impl B200Device {
         let _ = memory_pool;        // buffer ids are the library's own handles
         let evs = raw_events(event_wait_list);
         let (p, n) = ptr_len(&evs);
-        let ids: Vec<u32> = args.iter().map(|&a| usize::from(a) as u32).collect();
+        let (handle, extra) = &self.programs[program_id];
+        let ids: Vec<u32> = args.iter().map(|&a| usize::from(a) as u32).chain(extra.iter().copied()).collect();
         let mut out = ZyxbEvent::default();
         check(&self.sh, unsafe {
-            (self.sh.api.launch)(self.sh.ctx, self.dev, self.programs[program_id], ids.as_ptr(), ids.len() as i32, p, n, &mut out)
+            (self.sh.api.launch)(self.sh.ctx, self.dev, *handle, ids.as_ptr(), ids.len() as i32, p, n, &mut out)
         })?;
         Ok(Event::B200(B200Event(out)))
     }
