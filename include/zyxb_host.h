@@ -197,8 +197,9 @@ int32_t  zyxb_mgraph_const_value(zyxb_mgraph* g, uint32_t cls, double* out, uint
  * [_batched][_heads][_bias[_relu|_gelu]], conv[_bias], attention, softmax, ln_softmax, layernorm, cross_entropy, mse_loss, sum, max, min, mean, var, std, colsum, sgd, sgd_momentum,
  * sgd_nesterov, adam, adam_first_step, adamw, adamw_first_step; and, for outputs of the graph and inputs of those programs that nothing
  * produces yet, the elementwise programs relu, gelu, tanh, sigmoid, exp, cast, scale, add, sub, mul, bias_add.  An optimizer match covers every parameter of the update (inputs p.., g.. [, m.., v.. |
- * , buf..]; outputs p' [, m', v' | , buf'] per tensor - the kernel updates in place, so the shim binds each output to its
- * input's buffer); its desc.u.optim.numel points into the graph mirror.  optim_step is the step t the matched update belongs to
+ * , buf..]; outputs p' [, m', v' | , buf'] per tensor - the program updates where its arguments lie, so the shim's launch copies
+ * p, m, v into the output buffers first and runs the program on p'.., g.., m'.., v'..); its desc.u.optim.numel points into the
+ * graph mirror.  optim_step is the step t the matched update belongs to
  * (1 = the first: no state is read; for AdamW read back from the bias-correction constants, 2 for an SGD update that reads its
  * momentum buffer): the caller sets the program's counter to t - 1 (zyxb_program_set_step) before the launch.  0 for the
  * other patterns.  The attention program takes one more buffer behind its output, the log-sum-exp [batch*heads, seq] f32. */

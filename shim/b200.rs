@@ -332,10 +332,28 @@ pub struct B200Device {
     device_info: DeviceInfo,
     device_id: DeviceId,
     memory_pool_id: PoolId,
-    /// DeviceProgramId -> the library's program handle
-    /// program handle and the buffers the device itself appends to every launch of it (the fused attention program writes its
-    /// log-sum-exp [batch*heads, seq] f32 behind the output; the graph has no class for it)
-    programs: Slab<DeviceProgramId, (u32, Vec<u32>)>,
+    programs: Slab<DeviceProgramId, ProgramEntry>,
+}
+
+/// What the device keeps per program beside the library's handle.
+#[derive(Clone, Default)]
+struct ProgramEntry {
+    handle: u32,
+    /// buffers the device itself appends to every launch: the fused attention program writes its log-sum-exp
+    /// [batch*heads, seq] f32 behind the output, and the graph has no class for it
+    scratch: Vec<u32>,
+    /// an optimizer program updates its tensors where they lie, while the graph hands the launch fresh buffers for p', m', v'
+    /// (args = loads ++ stores) and still owns the old values: the launch copies p, m, v into the stores first and runs the
+    /// program on the copies
+    in_place: Option<InPlace>,
+}
+#[derive(Clone, Copy)]
+struct InPlace {
+    tensors: usize,
+    /// state tensors per parameter: 0 plain SGD, 1 SGD with momentum (the buffer), 2 Adam / AdamW (m, v)
+    states: usize,
+    /// false on a first step: the loads are p.., g.. only and the program writes the state without reading it
+    reads_state: bool,
 }
 
 impl std::fmt::Debug for B200Device {
@@ -428,9 +446,9 @@ impl B200Device {
     }
 
     pub fn release(&mut self, program_id: DeviceProgramId) {
-        let (handle, extra) = self.programs[program_id].clone();
+        let ProgramEntry { handle, scratch, .. } = self.programs[program_id].clone();
         unsafe { (self.sh.api.program_release)(self.sh.ctx, self.dev, handle) };
-        for buffer in extra {
+        for buffer in scratch {
             unsafe { (self.sh.api.free)(self.sh.ctx, self.dev, buffer, std::ptr::null(), 0) };
         }
         self.programs.remove(program_id);
@@ -454,7 +472,12 @@ impl B200Device {
                 // an optimizer program's own counter says whether state is read and which bias correction applies
                 unsafe { (self.sh.api.program_set_step)(self.sh.ctx, self.dev, handle, m.optim_step - 1) };
             }
-            let mut extra = Vec::new();
+            let mut entry = ProgramEntry { handle, ..Default::default() };
+            if desc.kind == ZYXB_KIND_OPTIM {
+                let tensors = unsafe { desc.u.optim.n_tensors } as usize;
+                let states = m.outputs.len() / tensors - 1;
+                entry.in_place = Some(InPlace { tensors, states, reads_state: m.inputs.len() > 2 * tensors });
+            }
             if desc.kind == ZYXB_KIND_ATTENTION {
                 let a = unsafe { desc.u.attention };
                 let (mut lse, mut ev) = (0u32, ZyxbEvent::default());
@@ -462,9 +485,9 @@ impl B200Device {
                     unsafe { (self.sh.api.program_release)(self.sh.ctx, self.dev, handle) };
                     continue;
                 }
-                extra.push(lse);
+                entry.scratch.push(lse);
             }
-            let program = self.programs.push((handle, extra));
+            let program = self.programs.push(entry);
             let nid = graph.nodes.push(NodeData {
                 node: Node::Kernel {
                     inputs: m.inputs.clone().into_boxed_slice(),
@@ -486,11 +509,33 @@ impl B200Device {
         let _ = memory_pool;        // buffer ids are the library's own handles
         let evs = raw_events(event_wait_list);
         let (p, n) = ptr_len(&evs);
-        let (handle, extra) = &self.programs[program_id];
-        let ids: Vec<u32> = args.iter().map(|&a| usize::from(a) as u32).chain(extra.iter().copied()).collect();
+        let entry = self.programs[program_id].clone();
+        let mut ids: Vec<u32> = args.iter().map(|&a| usize::from(a) as u32).chain(entry.scratch.iter().copied()).collect();
+        let (mut p, mut n) = (p, n);
+        if let Some(InPlace { tensors: t, states, reads_state }) = entry.in_place {
+            // loads p.., g.. [, state0.., state1..]; stores (p', state0', state1') per tensor.  The copies and the launch run in
+            // order on the device's compute stream; the first copy takes the wait list.
+            let loads = t * (2 + if reads_state { states } else { 0 });
+            let store = |i: usize, s: usize| ids[loads + i * (1 + states) + s];
+            let mut copies = Vec::new();
+            for i in 0..t {
+                copies.push((ids[i], store(i, 0)));
+                if reads_state { for s in 0..states { copies.push((ids[(2 + s) * t + i], store(i, 1 + s))); } }
+            }
+            for (src, dst) in copies {
+                let (mut bytes, mut ev) = (0u64, ZyxbEvent::default());
+                check(&self.sh, unsafe { (self.sh.api.buffer_bytes)(self.sh.ctx, self.dev, src, &mut bytes) })?;
+                check(&self.sh, unsafe { (self.sh.api.d2d)(self.sh.ctx, self.dev, src, 0, self.dev, dst, 0, bytes, p, n, &mut ev) })?;
+                unsafe { (self.sh.api.release_events)(self.sh.ctx, self.dev, &ev, 1) };
+                (p, n) = (std::ptr::null(), 0);
+            }
+            // what the program takes: p'.., g.., state0'.., state1'..
+            ids = (0..t).map(|i| store(i, 0)).chain(ids[t..2 * t].iter().copied())
+                .chain((0..states).flat_map(|s| (0..t).map(move |i| (i, s))).map(|(i, s)| store(i, 1 + s))).collect();
+        }
         let mut out = ZyxbEvent::default();
         check(&self.sh, unsafe {
-            (self.sh.api.launch)(self.sh.ctx, self.dev, *handle, ids.as_ptr(), ids.len() as i32, p, n, &mut out)
+            (self.sh.api.launch)(self.sh.ctx, self.dev, entry.handle, ids.as_ptr(), ids.len() as i32, p, n, &mut out)
         })?;
         Ok(Event::B200(B200Event(out)))
     }

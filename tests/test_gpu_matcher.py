@@ -75,7 +75,7 @@ def test_softmax_layernorm_and_sgd_from_graph_to_launch(sess):
         got = run_match(sess, g, pick(ms, b"layernorm", y_ln.cls), {x.cls: xv, ln.weight.cls: wv, ln.bias.cls: bv})[y_ln.cls]
         # 4096-term f32 sums in another order than the oracle's: the shared parity rule (oracle, or float64 attribution)
         assert_parity(got, zo.layernorm(zo.F32, xv, wv, bv, 1e-5), exact_layernorm(xv, wv, bv, 1e-5), TOL_F32, what="matched layernorm")
-        # the optimizer kernel updates in place: the shim binds the output class to the parameter's buffer
+        # the optimizer program updates where its arguments lie (the shim's launch copies p into the output buffer first)
         m = pick(ms, b"sgd", new_p.cls)
         pv, gv = rng.standard_normal((50, 30)).astype(np.float32), rng.standard_normal((50, 30)).astype(np.float32)
         prog = sess.device.create_program(m.desc)
