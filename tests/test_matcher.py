@@ -1,8 +1,9 @@
 """The e-graph matcher (zyx_b200/csrc/host/matcher.hpp through the C ABI of include/zyxb_host.h) on node lists transcribed from
-the reference's Tensor::dot, Linear::forward, softmax, ln_softmax, LayerNorm::forward, SGD::update and AdamW::update
-(tests/zyx_trace.py): the emitted descriptor must equal the hand-written one the training plans create for the same layer, and
-the launch arguments must be the stored tensors (loads first, then stores).  CPU only; the GPU run of a matched descriptor is in
-tests/test_gpu_matcher.py."""
+the reference's Tensor::dot, Linear::forward, MultiheadAttention::forward, Tensor::conv, softmax, ln_softmax, LayerNorm::forward,
+the reductions, cross_entropy, mse_loss, the elementwise functions, SGD::update, Adam::update and AdamW::update
+(tests/zyx_trace.py): the emitted descriptor must equal the hand-written one the training plans (or a caller of
+zyx_b200.backend's descriptor builders) create for the same operation, and the launch arguments must be the stored tensors
+(loads first, then stores).  CPU only; the GPU run of a matched descriptor is in tests/test_gpu_matcher.py."""
 import math
 
 import pytest
