@@ -191,10 +191,12 @@ def test_convolution_from_graph_to_launch(sess):
         got = run_match(sess, g, m, {x.cls: xv, w.cls: wv, b.cls: bv})[y.cls]
         want = zo.conv(zo.F32, xv, wv, bv, (2, 1), (1, 2), (0, 3, 1, 2))                # (top, bottom, left, right)
         assert got.shape == want.shape == tuple(y.shape)
-        import torch
-        xt = torch.nn.functional.pad(torch.from_numpy(xv.astype(np.float64)), (1, 2, 0, 3))
-        exact = torch.nn.functional.conv2d(xt, torch.from_numpy(wv.astype(np.float64)), torch.from_numpy(bv.astype(np.float64)),
-                                           stride=(2, 1), dilation=(1, 2)).numpy()
+        xp = np.pad(xv.astype(np.float64), ((0, 0), (0, 0), (0, 3), (1, 2)))           # the float64 convolution of the same values
+        exact = np.zeros(want.shape) + bv.astype(np.float64)[None, :, None, None]
+        for r in range(3):
+            for s in range(2):
+                win = xp[:, :, r:r + 2 * 10:2, 2 * s:2 * s + 24]                        # rows oy*2 + r, columns ox + 2*s
+                exact += np.einsum("nchw,oc->nohw", win, wv[:, :, r, s].astype(np.float64))
         assert_parity(got, want, exact, TOL_F32, floor=0.1, what="matched conv")
     finally:
         g.close()
