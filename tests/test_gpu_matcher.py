@@ -200,3 +200,41 @@ def test_convolution_from_graph_to_launch(sess):
         assert_parity(got, want, exact, TOL_F32, floor=0.1, what="matched conv")
     finally:
         g.close()
+
+
+def test_unfused_attention_from_graph_to_launch(sess):
+    """Head dimension 32 in f32 is outside the fused kernel's shapes: the traced attention core is three programs - scores,
+    softmax, product with v - whose matmuls read q, k, v as per-head views of the stored [b, t, h*d] tensors and write the
+    merged [b, t, h*d] result in place (row pitches and a two-level batch; no [b, h, t, d] copy anywhere)."""
+    import math
+    rng = np.random.default_rng(37)
+    nb, t, h, d = 2, 64, 4, 32
+    e = h * d
+    g = MGraph()
+    try:
+        q, k, v = (T.leaf(g, L.F32, (nb, t, e)) for _ in range(3))
+        split = lambda x: x.reshape([nb, t, h, d]).permute([0, 2, 1, 3])
+        scale = 1.0 / math.sqrt(d)
+        scores = split(q).dot(split(k).t()) * scale
+        probs = scores.softmax()
+        merged = probs.dot(split(v)).permute([0, 2, 1, 3]).reshape([nb, t, e])
+        ms = g.match([merged.cls])
+        m_s, m_p, m_o = pick(ms, b"matmul_nt_batched_heads", scores.cls), pick(ms, b"softmax", probs.cls), pick(ms, b"matmul_nn_batched_heads", merged.cls)
+        assert list(m_s.inputs[:2]) == [q.cls, k.cls] and list(m_o.inputs[:2]) == [probs.cls, v.cls]
+        qv, kv, vv = (rng.uniform(-1, 1, (nb, t, e)).astype(np.float32) for _ in range(3))
+        s_got = run_match(sess, g, m_s, {q.cls: qv, k.cls: kv})[scores.cls]
+        p_got = run_match(sess, g, m_p, {scores.cls: s_got})[probs.cls]
+        o_got = run_match(sess, g, m_o, {probs.cls: p_got, v.cls: vv})[merged.cls]
+        heads = lambda x: np.ascontiguousarray(x.reshape(nb, t, h, d).transpose(0, 2, 1, 3)).reshape(nb * h, t, d)
+        s_want = zo.gemm(zo.F32, heads(qv), heads(kv), tb=True, alpha=scale)
+        p_want = zo.softmax(zo.F32, s_want.reshape(-1, t)).reshape(nb * h, t, t)
+        o_want = zo.gemm(zo.F32, p_want, heads(vv)).reshape(nb, h, t, d).transpose(0, 2, 1, 3).reshape(nb, t, e)
+        s64 = np.einsum("bqd,bkd->bqk", heads(qv).astype(np.float64), heads(kv).astype(np.float64)) * scale
+        p64 = np.exp(s64 - s64.max(-1, keepdims=True))
+        p64 /= p64.sum(-1, keepdims=True)
+        exact = np.einsum("bqk,bkd->bqd", p64, heads(vv).astype(np.float64)).reshape(nb, h, t, d).transpose(0, 2, 1, 3).reshape(nb, t, e)
+        assert s_got.shape == (nb, h, t, t) and o_got.shape == (nb, t, e)
+        assert max_rel_err(s_got.reshape(nb * h, t, t), s_want, floor=0.1) <= TOL_F32
+        assert_parity(o_got, o_want, exact, TOL_F32, floor=0.1, what="matched unfused attention")
+    finally:
+        g.close()
