@@ -209,6 +209,9 @@ typedef struct {
   uint32_t inputs[128], outputs[96];
   zyxb_kernel_desc desc;
   uint64_t optim_step;
+  uint64_t input_offsets[128];  /* per input: the element of that class's buffer the program's argument starts at (a matmul operand
+                                   that is a slice of a stored tensor, e.g. q of a fused q/k/v projection); the caller passes
+                                   zyxb_buffer_view(buffer, offset * element size, the rest) for a non-zero entry */
 } zyxb_match;
 /* match_graph over every class the `outputs` depend on.  Classes in `outputs` are the ones other consumers read: a new
  * parameter value is only matched as an optimizer update when it is one of them, and a GELU layer's pre-activation listed

@@ -111,6 +111,7 @@ pub(super) struct Api {
     d2h: unsafe extern "C" fn(Ctx, i32, u32, u64, *mut c_void, u64, *const ZyxbEvent, i32) -> i32,
     d2d: unsafe extern "C" fn(Ctx, i32, u32, u64, i32, u32, u64, u64, *const ZyxbEvent, i32, *mut ZyxbEvent) -> i32,
     buffer_bytes: unsafe extern "C" fn(Ctx, i32, u32, *mut u64) -> i32,
+    buffer_view: unsafe extern "C" fn(Ctx, i32, u32, u64, u64, *mut u32) -> i32,
     sync: unsafe extern "C" fn(Ctx, i32, *const ZyxbEvent, i32) -> i32,
     release_events: unsafe extern "C" fn(Ctx, i32, *const ZyxbEvent, i32) -> i32,
     store_variable: unsafe extern "C" fn(Ctx, i32, i32, *const c_void, *mut u32) -> i32,
@@ -129,7 +130,7 @@ impl Api {
             init: sym!(b"zyxb_init\0"), shutdown: sym!(b"zyxb_shutdown\0"), last_error: sym!(b"zyxb_last_error\0"),
             device_count: sym!(b"zyxb_device_count\0"), device_info: sym!(b"zyxb_device_info\0"), free_compute: sym!(b"zyxb_free_compute\0"),
             free_bytes: sym!(b"zyxb_free_bytes\0"), alloc: sym!(b"zyxb_alloc\0"), free: sym!(b"zyxb_free\0"), h2d: sym!(b"zyxb_h2d\0"),
-            d2h: sym!(b"zyxb_d2h\0"), d2d: sym!(b"zyxb_d2d\0"), buffer_bytes: sym!(b"zyxb_buffer_bytes\0"), sync: sym!(b"zyxb_sync\0"),
+            d2h: sym!(b"zyxb_d2h\0"), d2d: sym!(b"zyxb_d2d\0"), buffer_bytes: sym!(b"zyxb_buffer_bytes\0"), buffer_view: sym!(b"zyxb_buffer_view\0"), sync: sym!(b"zyxb_sync\0"),
             release_events: sym!(b"zyxb_release_events\0"), store_variable: sym!(b"zyxb_store_variable\0"),
             get_variable: sym!(b"zyxb_get_variable\0"), program_create: sym!(b"zyxb_program_create\0"), launch: sym!(b"zyxb_launch\0"),
             program_release: sym!(b"zyxb_program_release\0"), program_set_step: sym!(b"zyxb_program_set_step\0"),
@@ -346,6 +347,9 @@ struct ProgramEntry {
     /// (args = loads ++ stores) and still owns the old values: the launch copies p, m, v into the stores first and runs the
     /// program on the copies
     in_place: Option<InPlace>,
+    /// (argument index, byte offset): arguments that are slices of their buffer (q of a fused q/k/v projection); the launch
+    /// passes a view of the buffer from that byte on
+    slices: Vec<(usize, u64)>,
 }
 #[derive(Clone, Copy)]
 struct InPlace {
@@ -478,6 +482,10 @@ impl B200Device {
                 let states = m.outputs.len() / tensors - 1;
                 entry.in_place = Some(InPlace { tensors, states, reads_state: m.inputs.len() > 2 * tensors });
             }
+            if desc.kind == ZYXB_KIND_GEMM {
+                let es: u64 = if unsafe { desc.u.gemm.dtype } == DType::F32 as i32 || unsafe { desc.u.gemm.dtype } == DType::I32 as i32 { 4 } else { 2 };
+                entry.slices = m.input_offsets.iter().enumerate().filter(|&(_, &o)| o != 0).map(|(i, &o)| (i, o * es)).collect();
+            }
             if desc.kind == ZYXB_KIND_ATTENTION {
                 let a = unsafe { desc.u.attention };
                 let (mut lse, mut ev) = (0u32, ZyxbEvent::default());
@@ -512,6 +520,14 @@ impl B200Device {
         let entry = self.programs[program_id].clone();
         let mut ids: Vec<u32> = args.iter().map(|&a| usize::from(a) as u32).chain(entry.scratch.iter().copied()).collect();
         let (mut p, mut n) = (p, n);
+        let mut views = Vec::new();
+        for &(arg, byte_offset) in &entry.slices {
+            let (mut bytes, mut view) = (0u64, 0u32);
+            check(&self.sh, unsafe { (self.sh.api.buffer_bytes)(self.sh.ctx, self.dev, ids[arg], &mut bytes) })?;
+            check(&self.sh, unsafe { (self.sh.api.buffer_view)(self.sh.ctx, self.dev, ids[arg], byte_offset, bytes - byte_offset, &mut view) })?;
+            ids[arg] = view;
+            views.push(view);
+        }
         if let Some(InPlace { tensors: t, states, reads_state }) = entry.in_place {
             // loads p.., g.. [, state0.., state1..]; stores (p', state0', state1') per tensor.  The copies and the launch run in
             // order on the device's compute stream; the first copy takes the wait list.
@@ -534,9 +550,13 @@ impl B200Device {
                 .chain((0..states).flat_map(|s| (0..t).map(move |i| (i, s))).map(|(i, s)| store(i, 1 + s))).collect();
         }
         let mut out = ZyxbEvent::default();
-        check(&self.sh, unsafe {
+        let launched = check(&self.sh, unsafe {
             (self.sh.api.launch)(self.sh.ctx, self.dev, entry.handle, ids.as_ptr(), ids.len() as i32, p, n, &mut out)
-        })?;
+        });
+        for view in views {             // a view is a name for a range of its parent: releasing it frees nothing
+            unsafe { (self.sh.api.free)(self.sh.ctx, self.dev, view, std::ptr::null(), 0) };
+        }
+        launched?;
         Ok(Event::B200(B200Event(out)))
     }
 }

@@ -30,6 +30,9 @@ pub(crate) struct B200Match {
     pub(crate) numel: Vec<u64>,
     /// optimizer programs: the step t the matched update belongs to (1 = the first); the program's counter must be t - 1 before the launch
     pub(crate) optim_step: u64,
+    /// per input: the element of that class's buffer the program's argument starts at (empty: all 0) - a matmul operand that is a
+    /// slice of a stored tensor, e.g. q of a fused q/k/v projection; the device passes a view of the buffer
+    pub(crate) input_offsets: Vec<u64>,
 }
 
 /// A constant's value as f64 (Constant::cast, dtype.rs:502-518, widens every variant).
@@ -53,7 +56,11 @@ struct MatMulX {
     /// rank-4 products over [b, h, .., ..]: operands (and, at the merged class, the result) that are per-head views of stored
     /// [b, t, h*d] tensors are read where they lie through a row pitch and a two-level batch
     outer: Dim, heads: Dim, a_heads: bool, b_heads: bool, c_heads: bool,
+    /// a_heads / b_heads: where the view starts in the stored tensor and how it steps (elements)
+    a_view: Pitch, b_view: Pitch,
 }
+#[derive(Clone, Copy, Default, PartialEq)]
+struct Pitch { offset: u64, ld: u64, inner: u64, outer: u64 }
 
 #[derive(Clone, Copy)]
 struct Update { algo: i32, p: ClassId, g: ClassId, m: Option<ClassId>, v: Option<ClassId>, p_new: ClassId, m_new: Option<ClassId>,
@@ -72,9 +79,22 @@ fn near(a: f64, b: f64) -> bool { (a - b).abs() <= 1e-2 * b.abs() }       // con
 impl Graph {
     // ---- node finders; a class may be a no-op Cast of the class holding the node (runtime.rs:696-700 pushes a Cast for every
     // `.cast`, also when the dtype does not change), so those are looked through ------------------------------------------------
+    /// a node that leaves its operand as it is: a Cast to the dtype the operand has, `x * 1`, `x / 1` (what dropout leaves behind
+    /// outside training with p = 0: x / (1 - p), tensor/mod.rs:822-828)
     fn noop_cast(&self, c: ClassId) -> Option<ClassId> {
         self.classes[c].nodes.iter().find_map(|&nid| match &self.nodes[nid].node {
             Node::Cast { x, dtype } if self.dtype(*x) == *dtype => Some(*x),
+            Node::Binary { x, y, bop: BOp::Mul | BOp::Div } if self.dtype(c).is_float() && self.const_shape(*x) == self.const_shape(c) => {
+                let mut k = *y;                                // a rank-0 constant 1 under its Cast / Reshape / Expand wrappers
+                for _ in 0..8 {
+                    match &self.nodes[self.classes[k].nodes[0]].node {
+                        Node::Const(v) => return (const_f64(*v) == 1.0).then_some(*x),
+                        Node::Cast { x, .. } | Node::Expand { x, .. } | Node::Reshape { x, .. } => k = *x,
+                        _ => return None,
+                    }
+                }
+                None
+            }
             _ => None,
         })
     }
@@ -192,11 +212,19 @@ impl Graph {
         };
         let dt = self.dtype(b);
         if self.dtype(a) != dt || self.dtype(cid) != dt || !matches!(dt, DType::F32 | DType::BF16 | DType::F16 | DType::I32) { return None; }
-        let mut mm = MatMulX { a, b, m, n, k, batch: batch_dims.iter().product(), trans_a, trans_b, b_shared, dtype: dt,
-                               outer: 0, heads: 0, a_heads: false, b_heads: false, c_heads: false };
-        if batch_dims.len() == 2 && !b_shared {                   // q / k / v of attention: x.reshape([b, t, h, d]).transpose(1, 2)
-            if let Some(x) = self.head_split_src(a).filter(|&x| self.dtype(x) == dt) { mm.a = x; mm.a_heads = true; }
-            if let Some(x) = self.head_split_src(b).filter(|&x| self.dtype(x) == dt) { mm.b = x; mm.b_heads = true; }
+        let mut mm = MatMulX { a: self.canon(a), b: self.canon(b), m, n, k, batch: batch_dims.iter().product(), trans_a, trans_b, b_shared, dtype: dt,
+                               outer: 0, heads: 0, a_heads: false, b_heads: false, c_heads: false, a_view: Pitch::default(), b_view: Pitch::default() };
+        if batch_dims.len() == 2 && !b_shared {
+            // q / k / v of attention, `x.reshape([b, t, h, d]).transpose(1, 2)` (multi_head_attention.rs:160-172) or the same of a
+            // slice of a fused projection (`c_attn.forward(x).split([c, c, c], 2)`, causal_self_attention.rs:39-52): any operand that
+            // is a view with unit step along its rows is read where it lies
+            for (which, op) in [(0, a), (1, b)] {
+                let Some((src, offset, st)) = self.affine_view(op) else { continue };
+                if src == self.canon(op) || self.dtype(src) != dt || st[3] != 1 || st[2] <= 0 || st[0] < 0 || st[1] < 0 { continue; }
+                if offset * (if matches!(dt, DType::F32 | DType::I32) { 4 } else { 2 }) % 256 != 0 { continue; }      // zyxb_buffer_view starts on 256-byte boundaries
+                let pitch = Pitch { offset, ld: st[2] as u64, inner: st[1] as u64, outer: st[0] as u64 };
+                if which == 0 { (mm.a, mm.a_heads, mm.a_view) = (src, true, pitch); } else { (mm.b, mm.b_heads, mm.b_view) = (src, true, pitch); }
+            }
             if mm.a_heads || mm.b_heads { mm.outer = batch_dims[0]; mm.heads = batch_dims[1]; }
         }
         Some(mm)
@@ -247,13 +275,13 @@ impl Graph {
         if mm.heads != 0 {                                        // two-level batch: images outside, heads inside
             let h = mm.heads;
             // a stored [rows, cols] matrix per (image, head): inside a [b, t, h*d] tensor (pitch h*cols, heads `cols` apart) or packed
-            let view = |heads: bool, rows: Dim, cols: Dim| -> (u64, i64, i64) {
-                if heads { (h * cols, (rows * h * cols) as i64, cols as i64) } else { (0, (h * rows * cols) as i64, (rows * cols) as i64) }
-            };
+            let packed = |rows: Dim, cols: Dim| -> (u64, i64, i64) { (0, (h * rows * cols) as i64, (rows * cols) as i64) };
+            let pitched = |p: Pitch| -> (u64, i64, i64) { (p.ld, p.outer as i64, p.inner as i64) };
             (g.batch, g.batch_inner) = (mm.outer, h);
-            (g.lda, g.stride_a, g.stride_a_inner) = if mm.trans_a { view(mm.a_heads, mm.k, mm.m) } else { view(mm.a_heads, mm.m, mm.k) };
-            (g.ldb, g.stride_b, g.stride_b_inner) = if mm.trans_b { view(mm.b_heads, mm.n, mm.k) } else { view(mm.b_heads, mm.k, mm.n) };
-            (g.ldc, g.stride_c, g.stride_c_inner) = view(mm.c_heads, mm.m, mm.n);
+            (g.lda, g.stride_a, g.stride_a_inner) = if mm.a_heads { pitched(mm.a_view) } else if mm.trans_a { packed(mm.k, mm.m) } else { packed(mm.m, mm.k) };
+            (g.ldb, g.stride_b, g.stride_b_inner) = if mm.b_heads { pitched(mm.b_view) } else if mm.trans_b { packed(mm.n, mm.k) } else { packed(mm.k, mm.n) };
+            // heads merged: the result lies in [b, t, h*d]
+            (g.ldc, g.stride_c, g.stride_c_inner) = if mm.c_heads { (h * mm.n, (mm.m * h * mm.n) as i64, mm.n as i64) } else { packed(mm.m, mm.n) };
         }
         g
     }
@@ -267,7 +295,8 @@ impl Graph {
                         (mm.c_heads, mm.outer, mm.heads) = (true, s4[0], s4[1]);
                         let gemm = Self::gemm_desc(&mm, EPI_NONE, false, alpha);
                         return Some(B200Match { pattern: "matmul", inputs: vec![mm.a, mm.b], outputs: vec![cid],
-                                                desc: ZyxbKernelDesc { kind: ZYXB_KIND_GEMM, u: ZyxbDescUnion { gemm } }, numel: Vec::new(), optim_step: 0 });
+                                                desc: ZyxbKernelDesc { kind: ZYXB_KIND_GEMM, u: ZyxbDescUnion { gemm } }, numel: Vec::new(), optim_step: 0,
+                                                input_offsets: vec![mm.a_view.offset, mm.b_view.offset] });
                     }
                 }
             }
@@ -292,7 +321,8 @@ impl Graph {
         inputs.extend(bias);
         let mut outputs = vec![cid];
         if preact { outputs.push(e); }
-        Some(B200Match { pattern: "matmul", inputs, outputs, desc: ZyxbKernelDesc { kind: ZYXB_KIND_GEMM, u: ZyxbDescUnion { gemm } }, numel: Vec::new(), optim_step: 0 })
+        Some(B200Match { pattern: "matmul", inputs, outputs, desc: ZyxbKernelDesc { kind: ZYXB_KIND_GEMM, u: ZyxbDescUnion { gemm } }, numel: Vec::new(), optim_step: 0,
+                         input_offsets: vec![mm.a_view.offset, mm.b_view.offset] })
     }
 
     // ---- row kernels ---------------------------------------------------------------------------------------------------------
@@ -304,7 +334,7 @@ impl Graph {
             .then(|| ZyxbRowreduceDesc { op, dtype: self.dtype(x) as i32, rows: s.iter().product::<Dim>() / cols, cols, correction: 1, ..Default::default() })
     }
     fn row_match(&self, pattern: &'static str, rowreduce: ZyxbRowreduceDesc, inputs: Vec<ClassId>, out: ClassId) -> B200Match {
-        B200Match { pattern, inputs, outputs: vec![out], desc: ZyxbKernelDesc { kind: ZYXB_KIND_ROWREDUCE, u: ZyxbDescUnion { rowreduce } }, numel: Vec::new(), optim_step: 0 }
+        B200Match { pattern, inputs, outputs: vec![out], desc: ZyxbKernelDesc { kind: ZYXB_KIND_ROWREDUCE, u: ZyxbDescUnion { rowreduce } }, numel: Vec::new(), optim_step: 0, input_offsets: Vec::new() }
     }
     fn keepdim_src(&self, c: ClassId) -> ClassId { self.expand_of(c).unwrap_or(c) }
     /// c = uop(x - Expand{max_keepdim(x)}) -> x
@@ -317,14 +347,6 @@ impl Graph {
     // ---- fused attention ----------------------------------------------------------------------------------------------------
     fn permute_of(&self, c: ClassId, want: &[usize]) -> Option<ClassId> {
         self.find_in(c, |n| match n { Node::Permute { x, axes } if axes.as_ref() == want => Some(*x), _ => None })
-    }
-    /// c [b, h, t, d] = x.reshape([b, t, h, d]).transpose(1, 2) of a stored x [b, t, h*d] (multi_head_attention.rs:160-172) -> x
-    fn head_split_src(&self, c: ClassId) -> Option<ClassId> {
-        let s4 = self.const_shape(c)?;
-        if s4.len() != 4 { return None; }
-        let x = self.reshape_of(self.permute_of(c, &[0, 2, 1, 3])?)?;
-        let s3 = self.const_shape(x)?;
-        (s3.len() == 3 && s3[0] == s4[0] && s3[1] == s4[2] && s3[2] == s4[1] * s4[3]).then(|| self.canon(x))
     }
     /// The mask-free core of MultiheadAttention::forward (multi_head_attention.rs:197-226) ending at the class of
     /// `attn_weights.matmul(v).transpose(1, 2).reshape([b, t, h*d])`: one fused program on the three stored [b, t, h*d] tensors.
@@ -342,16 +364,19 @@ impl Graph {
         if qk.trans_a || !qk.trans_b || qk.b_shared { return None; }
         if !qk.a_heads || !qk.b_heads || !pv.b_heads || pv.a_heads { return None; }          // q, k, v: per-head views of stored tensors
         let (xq, xk, xv) = (qk.a, qk.b, pv.b);
+        // the program reads q, k, v and writes the result with one row pitch: whole [b, t, h*d] tensors, not slices of a wider one
+        let whole = |p: Pitch, t: Dim, h: Dim, d: Dim| p == Pitch { offset: 0, ld: h * d, inner: d, outer: t * h * d };
         let hs = self.const_shape(pv_cls)?;
         let (b, h, t, d) = (hs[0], hs[1], hs[2], hs[3]);
         let shapes_ok = qk.m == t && qk.n == t && qk.k == d && pv.m == t && pv.k == t && pv.n == d && qk.batch == b * h && pv.batch == b * h
             && s3[0] == b && s3[1] == t && s3[2] == h * d;
         let dt = qk.dtype;
         if !shapes_ok || !matches!(dt, DType::BF16 | DType::F16) || pv.dtype != dt || d != 128 || t % 128 != 0 { return None; }
+        if ![qk.a_view, qk.b_view, pv.b_view].into_iter().all(|p| whole(p, t, h, d)) { return None; }
         let attention = ZyxbAttentionDesc { dtype: dt as i32, batch: b as u64, heads: h as u64, seq: t as u64, head_dim: d as u64, ld: 0, scale, causal: 0 };
         // the launch takes one more buffer behind the output: the log-sum-exp [b*h, t] f32 the backward program reads
         Some(B200Match { pattern: "attention", inputs: vec![xq, xk, xv], outputs: vec![cid],
-                         desc: ZyxbKernelDesc { kind: ZYXB_KIND_ATTENTION, u: ZyxbDescUnion { attention } }, numel: Vec::new(), optim_step: 0 })
+                         desc: ZyxbKernelDesc { kind: ZYXB_KIND_ATTENTION, u: ZyxbDescUnion { attention } }, numel: Vec::new(), optim_step: 0, input_offsets: Vec::new() })
     }
 
     /// softmax (tensor/mod.rs:1457-1461)
@@ -434,7 +459,7 @@ impl Graph {
         let program = |pattern: &'static str, op: i32, inputs: Vec<ClassId>, p0: f32, cols: Dim, dt_in: DType| {
             let eltwise = ZyxbEltwiseDesc { op, dtype: dt_in as i32, dtype_out: dt as i32, numel: n, cols, p0 };
             Some(B200Match { pattern, inputs: inputs.into_iter().map(|c| self.canon(c)).collect(), outputs: vec![cid],
-                             desc: ZyxbKernelDesc { kind: ZYXB_KIND_ELTWISE, u: ZyxbDescUnion { eltwise } }, numel: Vec::new(), optim_step: 0 })
+                             desc: ZyxbKernelDesc { kind: ZYXB_KIND_ELTWISE, u: ZyxbDescUnion { eltwise } }, numel: Vec::new(), optim_step: 0, input_offsets: Vec::new() })
         };
         if let Some(z) = self.gelu_of(cid).filter(|&z| whole(z)) { return program("gelu", EW_GELU, vec![z], 0.0, 0, dt); }
         if let Some(z) = self.relu_of(cid).filter(|&z| whole(z)) { return program("relu", EW_RELU, vec![z], 0.0, 0, dt); }
@@ -600,6 +625,42 @@ impl Graph {
         }
         Some(Some((c, idx)))
     }
+    /// c as a strided window of a stored tensor: element idx of c is element `offset + sum(idx[a] * strides[a])` of `src`, row-major
+    /// -> (src, offset, strides).  Measured, not derived: the origin and one step along every axis give offset and strides, then
+    /// every corner and a spread of other elements must agree (a reshape of a permuted tensor is no such window and fails at its
+    /// far corner).  None when some element is padding or the elements come from more than one class.
+    fn affine_view(&self, c: ClassId) -> Option<(ClassId, u64, Vec<i64>)> {
+        let cs = self.const_shape(c)?;
+        let rank = cs.len();
+        if rank == 0 || rank > 6 || cs.iter().product::<Dim>() == 0 { return None; }
+        let lin_of = |cls: ClassId, idx: &[u64]| -> Option<i64> { Some(self.const_shape(cls)?.iter().zip(idx).fold(0i64, |l, (&d, &i)| l * d as i64 + i as i64)) };
+        let (c0, i0) = self.trace_element(c, vec![0; rank])??;
+        let (src, offset) = (self.canon(c0), lin_of(c0, &i0)?);
+        let at = |idx: &[u64]| -> Option<i64> {
+            let (cls, i) = self.trace_element(c, idx.to_vec())??;
+            if self.canon(cls) != src { return None; }
+            lin_of(cls, &i)
+        };
+        let mut strides = vec![0i64; rank];
+        let mut idx = vec![0u64; rank];
+        for a in 0..rank {
+            if cs[a] < 2 { continue; }
+            idx[a] = 1;
+            strides[a] = at(&idx)? - offset;
+            idx[a] = 0;
+        }
+        let agrees = |idx: &[u64]| at(idx) == Some(offset + idx.iter().zip(&strides).map(|(&i, &s)| i as i64 * s).sum::<i64>());
+        for corner in 0..1u64 << rank {
+            for a in 0..rank { idx[a] = if corner >> a & 1 == 1 { cs[a] - 1 } else { 0 }; }
+            if !agrees(&idx) { return None; }
+        }
+        let mut seed = 0x9e37_79b9_7f4a_7c15u64;                              // a fixed spread of interior elements
+        for _ in 0..256 {
+            for a in 0..rank { seed = seed.wrapping_mul(6364136223846793005).wrapping_add(1442695040888963407); idx[a] = (seed >> 33) % cs[a]; }
+            if !agrees(&idx) { return None; }
+        }
+        Some((src, offset as u64, strides))
+    }
     /// the class a view reads (c under every movement op) and the classes passed on the way, outermost first
     fn view_source(&self, mut c: ClassId) -> (ClassId, Vec<ClassId>) {
         let mut chain = Vec::new();
@@ -728,7 +789,7 @@ impl Graph {
             let mut inputs = vec![x, w];
             inputs.extend(bias);
             return Some(B200Match { pattern: if bias.is_some() { "conv_bias" } else { "conv" }, inputs, outputs: vec![cid],
-                                    desc: ZyxbKernelDesc { kind: ZYXB_KIND_CONV, u: ZyxbDescUnion { conv } }, numel: Vec::new(), optim_step: 0 });
+                                    desc: ZyxbKernelDesc { kind: ZYXB_KIND_CONV, u: ZyxbDescUnion { conv } }, numel: Vec::new(), optim_step: 0, input_offsets: Vec::new() });
         }
         None
     }
@@ -969,24 +1030,32 @@ impl Graph {
             let optim_step = if h.algo == OPT_SGD { if sgd_buf { 2 } else { 1 } }
                              else if h.first { 1 } else { ((1.0 - h.bc1).ln() / h.b1.ln()).round().max(2.0) as u64 };
             out.push(B200Match { pattern, inputs, outputs: outs,
-                                 desc: ZyxbKernelDesc { kind: ZYXB_KIND_OPTIM, u: ZyxbDescUnion { optim } }, numel, optim_step });
+                                 desc: ZyxbKernelDesc { kind: ZYXB_KIND_OPTIM, u: ZyxbDescUnion { optim } }, numel, optim_step, input_offsets: Vec::new() });
         }
-        // Elementwise programs, on demand: whatever somebody has to produce - an output of the graph or an input of a program found
-        // above - that is neither stored nor the result of one of those programs gets an elementwise program if one fits, and that
-        // program's inputs are looked at in turn.  (Offering every Mul and Add of the graph as a program of its own would bury the
-        // patterns above under their own sub-expressions.)
+        // Elementwise programs, on demand.  Walk down from the outputs of the graph through the programs found above (for a class
+        // several of them end at, the one found last: the largest pattern): whatever that walk needs and nothing stored or matched
+        // produces gets an elementwise program if one fits, and the walk continues through its operands.  Offering every Mul and
+        // Add of the graph as a program of its own would bury the patterns above under their own sub-expressions; following the
+        // inputs of every alternative would do the same with the inside of a softmax.
         let has_kernel = |c: ClassId| self.classes[c].nodes.iter().any(|&nid| matches!(self.nodes[nid].node, Node::Kernel { .. }));
-        let mut produced: BTreeSet<ClassId> = out.iter().flat_map(|m| m.outputs.iter().map(|&o| self.canon(o))).collect();
-        let mut tried = BTreeSet::new();
-        let mut demand: Vec<ClassId> = wanted.iter().rev().copied().collect();
-        for m in &out { demand.extend(m.inputs.iter().rev()); }
-        while let Some(c) = demand.pop() {
+        let mut producer: BTreeMap<ClassId, usize> = BTreeMap::new();
+        for (i, m) in out.iter().enumerate() { for &o in &m.outputs { producer.insert(self.canon(o), i); } }
+        let mut seen = BTreeSet::new();
+        let mut need: Vec<ClassId> = wanted.iter().rev().copied().collect();
+        while let Some(c) = need.pop() {
             let k = self.canon(c);
-            if !tried.insert(k) || produced.contains(&k) || self.is_leaf(c) || has_kernel(c) || has_kernel(k) { continue; }
-            let Some(m) = self.match_eltwise(c) else { continue };
-            produced.insert(k);
-            demand.extend(m.inputs.iter().rev());
-            out.push(m);
+            if !seen.insert(k) || self.is_leaf(c) { continue; }
+            let via = match producer.get(&k) {
+                Some(&i) => i,
+                None => {
+                    if has_kernel(c) || has_kernel(k) { continue; }
+                    let Some(m) = self.match_eltwise(c) else { continue };
+                    out.push(m);
+                    producer.insert(k, out.len() - 1);
+                    out.len() - 1
+                }
+            };
+            need.extend(out[via].inputs.iter().rev());
         }
         out
     }

@@ -626,3 +626,44 @@ def test_elementwise_programs_are_matched_on_demand(g):
     from tests.zyx_trace import sgd_update as sgd
     p, gr = T.leaf(g, L.F32, (50, 30)), T.leaf(g, L.F32, (50, 30))
     assert [m.pattern for m in g.match([sgd([p], [gr], 0.01, weight_decay=0.1)[0].cls])] == [b"sgd"]
+
+
+def test_causal_self_attention_reads_its_fused_projection_in_place(g):
+    """CausalSelfAttention::forward (zyx-nn/src/causal_self_attention.rs:36-71): q, k, v are slices of ONE [b, t, 3c] projection.
+    The per-head products read them there - row pitch 3c, heads d apart, the slice's start as the argument's offset into the
+    projection's buffer - and the dropout that is a division by one outside training is looked through."""
+    from tests.zyx_trace import causal_self_attention
+    nb, t, c, h = 2, 128, 256, 4
+    d = c // h
+    x = T.leaf(g, L.BF16, (nb, t, c))
+    c_attn, c_proj = Linear(g, L.BF16, c, 3 * c), Linear(g, L.BF16, c, c)
+    y, scores, att, merged, qkv = causal_self_attention(x, c_attn, c_proj, h)
+    at = {m.outputs[0]: m for m in g.match([y.cls])}
+    m = at[qkv.cls]                                       # the fused projection: one matmul over [b*t] rows... as a batch of b
+    assert m.pattern == b"matmul_nt_batched_bias" and list(m.inputs[:3]) == [x.cls, c_attn.weight.cls, c_attn.bias.cls]
+    ms = at[scores.cls]
+    assert ms.pattern == b"matmul_nt_batched_heads" and list(ms.inputs[:2]) == [qkv.cls, qkv.cls]
+    assert list(ms.input_offsets[:2]) == [0, c]           # q starts at feature 0, k at feature c of every row
+    want = B.gemm_desc(L.BF16, t, t, d, batch=nb, batch_inner=h, trans_b=True, lda=3 * c, stride_a=t * 3 * c, stride_a_inner=d,
+                       ldb=3 * c, stride_b=t * 3 * c, stride_b_inner=d, stride_c=h * t * t, stride_c_inner=t * t)
+    got_f, want_f = fields(ms.desc.u.gemm), fields(want.u.gemm)
+    assert abs(got_f.pop("alpha") - 1.0 / math.sqrt(d)) <= 1e-2 / math.sqrt(d) and want_f.pop("alpha") == 0.0 and got_f == want_f, (got_f, want_f)
+    soft = next(m for m in at.values() if m.pattern == b"softmax")
+    mv = at[merged.cls]
+    assert mv.pattern == b"matmul_nn_batched_heads"
+    assert list(mv.inputs[:2]) == [soft.outputs[0], qkv.cls] and list(mv.input_offsets[:2]) == [0, 2 * c]
+    assert g.info(att.cls)[1] == (nb, h, t, t) and att.cls != soft.outputs[0]          # the division by 1 - p sits between them
+    assert_same_gemm(mv.desc, B.gemm_desc(L.BF16, t, d, t, batch=nb, batch_inner=h, stride_a=h * t * t, stride_a_inner=t * t,
+                                          ldb=3 * c, stride_b=t * 3 * c, stride_b_inner=d, ldc=c, stride_c=t * c, stride_c_inner=d))
+    mo = at[y.cls]
+    assert mo.pattern == b"matmul_nt_batched_bias" and list(mo.inputs[:3]) == [merged.cls, c_proj.weight.cls, c_proj.bias.cls]
+    # a slice that does not start on a 256-byte boundary of its buffer cannot be handed over as a view (zyxb_buffer_view): left alone
+    x3 = T.leaf(g, L.BF16, (2, 32, 96))
+    odd = causal_self_attention(x3, Linear(g, L.BF16, 96, 288), Linear(g, L.BF16, 96, 96), 4)
+    at3 = {m.outputs[0]: m for m in g.match([odd[0].cls])}
+    assert odd[1].cls not in at3 or list(at3[odd[1].cls].input_offsets[:2]) == [0, 0]
+    # head dimension 128 would fit the fused program's tiles, but its q, k, v share one row pitch with its output: slices of a
+    # wider tensor stay three programs
+    x2 = T.leaf(g, L.BF16, (2, 256, 512))
+    y2 = causal_self_attention(x2, Linear(g, L.BF16, 512, 1536), Linear(g, L.BF16, 512, 512), 4)[0]
+    assert b"attention" not in {m.pattern for m in g.match([y2.cls])}

@@ -111,6 +111,21 @@ class T:
         shape = self.shape
         return self.pad_zeros([(-s, -(d - e)) for (s, e), d in zip(ranges, shape)]).squeeze([])
 
+    def split(self, sizes, axis):
+        """consecutive slices along one axis (tensor/mod.rs:2340-2381)"""
+        shape = self.shape
+        axis = axis % len(shape)
+        out, acc = [], 0
+        for size in sizes:
+            out.append(self.slice([(0, d) for d in shape[:axis]] + [(acc, acc + size)]))
+            acc += size
+        return out
+
+    def dropout(self, p, training=False):
+        """outside training: x / (1 - p) (tensor/mod.rs:822-828); the training branch draws a random mask and is not transcribed"""
+        assert not training
+        return self / (1.0 - p)
+
     def repeat(self, repeats):
         shape = list(self.shape)
         lead = len(repeats) - len(shape)
@@ -431,3 +446,19 @@ def attention_core(q, k, v, heads):
     scores = qh.dot(kh.t()) * (1.0 / math.sqrt(d))
     out = scores.softmax().dot(vh)
     return out.permute([0, 2, 1, 3]).reshape([b, t, e])
+
+
+def causal_self_attention(x, c_attn, c_proj, n_head, dropout_p=0.0):
+    """CausalSelfAttention::forward (zyx-nn/src/causal_self_attention.rs:36-71) outside training: one fused q/k/v projection,
+    split along the features, head split, scores * scale, softmax, dropout, .dot(v), heads merged, output projection.  (The
+    reference's own mask is commented out there.)  -> (y, scores, probabilities after dropout, merged heads, qkv)"""
+    b, t, c = x.shape
+    qkv = c_attn.forward(x)
+    q, k, v = qkv.split([c, c, c], 2)
+    heads = lambda z: z.reshape([b, t, n_head, c // n_head]).transpose(1, 2)
+    k, q, v = heads(k), heads(q), heads(v)
+    scale = 1.0 / math.sqrt(c // n_head)
+    scores = q.dot(k.t()) * scale
+    att = scores.softmax([-1]).dropout(dropout_p)
+    merged = att.dot(v).transpose(1, 2).reshape([b, t, c])
+    return c_proj.forward(merged), scores, att, merged, qkv

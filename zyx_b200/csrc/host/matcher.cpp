@@ -135,6 +135,7 @@ int32_t zyxb_mgraph_match(zyxb_mgraph* G, const uint32_t* outputs, int32_t n_out
     o.desc = m.desc;
     if (o.desc.kind == ZYXB_KIND_OPTIM) o.desc.u.optim.numel = m.numel.data();   // owned by the graph mirror until it is destroyed
     o.optim_step = m.optim_step;
+    for (size_t j = 0; j < m.input_offsets.size() && j < 128; ++j) o.input_offsets[j] = m.input_offsets[j];
   }
   return ZYXB_OK;
 }

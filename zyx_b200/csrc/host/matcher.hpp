@@ -81,6 +81,7 @@ struct Match {
   zyxb_kernel_desc desc{};
   std::vector<uint64_t> numel;            // optimizer: desc.u.optim.numel points here
   uint64_t optim_step = 0;                // optimizer: the step t of the matched update (the program's counter must be t - 1 before the launch)
+  std::vector<uint64_t> input_offsets;    // per input: the element the program's argument starts at inside that class's buffer (empty: all 0)
 };
 
 inline bool is_float(int dt) { return dt == ZYXB_F32 || dt == ZYXB_BF16 || dt == ZYXB_F16 || dt == ZYXB_F64; }
@@ -142,8 +143,22 @@ class Graph {
     }
     return nullptr;
   }
+  // a node that leaves its operand as it is: a Cast to the dtype the operand has, `x * 1`, `x / 1` (what dropout leaves
+  // behind outside training with p = 0: x / (1 - p), tensor/mod.rs:822-828)
   const Node* noop_cast(ClassId c) const {
-    for (uint32_t nid : classes[c].nodes) if (nodes[nid].kind == K_CAST && classes[nodes[nid].x].dtype == classes[c].dtype) return &nodes[nid];
+    for (uint32_t nid : classes[c].nodes) {
+      const Node& n = nodes[nid];
+      if (n.kind == K_CAST && classes[n.x].dtype == classes[c].dtype) return &n;
+      if (n.kind == K_BINARY && (n.op == B_MUL || n.op == B_DIV) && classes[n.x].shape == classes[c].shape && is_float(classes[c].dtype)) {
+        ClassId k = n.y;                               // a rank-0 constant 1 under its Cast / Reshape / Expand wrappers
+        for (int hops = 0; hops < 8; ++hops) {
+          const Node& kn = nodes[classes[k].nodes[0]];
+          if (kn.kind == K_CONST) { if (kn.value == 1.0) return &n; break; }
+          if (kn.kind != K_CAST && kn.kind != K_EXPAND && kn.kind != K_RESHAPE) break;
+          k = kn.x;
+        }
+      }
+    }
     return nullptr;
   }
   ClassId canon(ClassId c) const { while (const Node* k = noop_cast(c)) c = k->x; return c; }
@@ -235,6 +250,8 @@ class Graph {
     // rank-4 products over [b, h, .., ..]: operands (and, at the merged class, the result) that are per-head views of stored
     // [b, t, h*d] tensors are read where they lie through a row pitch and a two-level batch
     uint64_t outer = 0, heads = 0; bool a_heads = false, b_heads = false, c_heads = false;
+    // a_heads / b_heads: where the view starts in the stored tensor and how it steps (elements): row pitch, head to head, image to image
+    struct Pitch { uint64_t offset = 0, ld = 0, inner = 0, outer = 0; } a_view, b_view;
   };
 
   // The canonical broadcast-reduce form of Tensor::dot (tensor/mod.rs:1469-1490), ending at class `cid`:
@@ -302,12 +319,20 @@ class Graph {
     const int dt = dtype(b);
     if (dtype(a) != dt || dtype(cid) != dt) return std::nullopt;      // C is stored in the operands' dtype; accumulation is f32 / i32
     if (!(dt == ZYXB_F32 || dt == ZYXB_BF16 || dt == ZYXB_F16 || dt == ZYXB_I32)) return std::nullopt;
-    MatMul mm{a, b, cid, m, n, k, numel(batch_dims), trans_b, b_shared, dt};
+    MatMul mm{canon(a), canon(b), cid, m, n, k, numel(batch_dims), trans_b, b_shared, dt};
     mm.trans_a = trans_a;
-    if (batch_dims.size() == 2 && !b_shared) {                // q / k / v of attention: x.reshape([b, t, h, d]).transpose(1, 2)
-      auto xa = head_split_src(a), xb = head_split_src(b);
-      if (xa && dtype(*xa) == dt) { mm.a = *xa; mm.a_heads = true; }
-      if (xb && dtype(*xb) == dt) { mm.b = *xb; mm.b_heads = true; }
+    if (batch_dims.size() == 2 && !b_shared) {
+      // q / k / v of attention, `x.reshape([b, t, h, d]).transpose(1, 2)` (multi_head_attention.rs:160-172) or the same of a slice
+      // of a fused projection (`c_attn.forward(x).split([c, c, c], 2)`, causal_self_attention.rs:39-52): any operand that is a
+      // view with unit step along its rows is read where it lies
+      for (int which = 0; which < 2; ++which) {
+        const ClassId op = which ? b : a;
+        auto v = affine_view(op);
+        if (!v || v->src == canon(op) || dtype(v->src) != dt || v->strides[3] != 1 || v->strides[2] <= 0 || v->strides[0] < 0 || v->strides[1] < 0) continue;
+        if (v->offset * (dt == ZYXB_F32 || dt == ZYXB_I32 ? 4 : 2) % 256 != 0) continue;      // zyxb_buffer_view starts on 256-byte boundaries
+        MatMul::Pitch pv{v->offset, (uint64_t)v->strides[2], (uint64_t)v->strides[1], (uint64_t)v->strides[0]};
+        if (which) { mm.b = v->src; mm.b_heads = true; mm.b_view = pv; } else { mm.a = v->src; mm.a_heads = true; mm.a_view = pv; }
+      }
       if (mm.a_heads || mm.b_heads) { mm.outer = batch_dims[0]; mm.heads = batch_dims[1]; }
     }
     return mm;
@@ -325,13 +350,16 @@ class Graph {
       const uint64_t H = mm.heads;
       g.batch = mm.outer; g.batch_inner = H;
       // a stored [rows, cols] matrix per (image, head): inside a [b, t, h*d] tensor (pitch h*cols, heads `cols` apart) or packed
-      auto view = [H](bool heads, uint64_t rows, uint64_t cols, uint64_t& ld, int64_t& outer, int64_t& inner) {
-        if (heads) { ld = H * cols; outer = (int64_t)(rows * H * cols); inner = (int64_t)cols; }
-        else { ld = 0; outer = (int64_t)(H * rows * cols); inner = (int64_t)(rows * cols); }
+      auto packed = [H](uint64_t rows, uint64_t cols, uint64_t& ld, int64_t& outer, int64_t& inner) {
+        ld = 0; outer = (int64_t)(H * rows * cols); inner = (int64_t)(rows * cols);
       };
-      view(mm.a_heads, mm.trans_a ? mm.k : mm.m, mm.trans_a ? mm.m : mm.k, g.lda, g.stride_a, g.stride_a_inner);
-      view(mm.b_heads, mm.trans_b ? mm.n : mm.k, mm.trans_b ? mm.k : mm.n, g.ldb, g.stride_b, g.stride_b_inner);
-      view(mm.c_heads, mm.m, mm.n, g.ldc, g.stride_c, g.stride_c_inner);
+      auto pitched = [](const MatMul::Pitch& p, uint64_t& ld, int64_t& outer, int64_t& inner) { ld = p.ld; outer = (int64_t)p.outer; inner = (int64_t)p.inner; };
+      if (mm.a_heads) pitched(mm.a_view, g.lda, g.stride_a, g.stride_a_inner);
+      else packed(mm.trans_a ? mm.k : mm.m, mm.trans_a ? mm.m : mm.k, g.lda, g.stride_a, g.stride_a_inner);
+      if (mm.b_heads) pitched(mm.b_view, g.ldb, g.stride_b, g.stride_b_inner);
+      else packed(mm.trans_b ? mm.n : mm.k, mm.trans_b ? mm.k : mm.n, g.ldb, g.stride_b, g.stride_b_inner);
+      if (mm.c_heads) { g.ldc = H * mm.n; g.stride_c = (int64_t)(mm.m * H * mm.n); g.stride_c_inner = (int64_t)mm.n; }   // heads merged: [b, t, h*d]
+      else packed(mm.m, mm.n, g.ldc, g.stride_c, g.stride_c_inner);
     }
     return d;
   }
@@ -404,6 +432,7 @@ class Graph {
             Match mt;
             mt.pattern = gemm_name(mm); mt.desc = gemm_desc(mm, ZYXB_EPI_NONE, false, sc->second);
             mt.inputs = {mm.a, mm.b}; mt.outputs = {cid};
+            mt.input_offsets = {mm.a_view.offset, mm.b_view.offset};
             return mt;
           }
       }
@@ -433,7 +462,8 @@ class Graph {
     mt.pattern = gemm_name(mm) + (bias != NONE ? "_bias" : "") + (act == 2 ? "_gelu" : act == 1 ? "_relu" : "");
     mt.desc = gemm_desc(mm, epi, preact, sc->second);
     mt.inputs = {mm.a, mm.b};
-    if (bias != NONE) mt.inputs.push_back(bias);
+    mt.input_offsets = {mm.a_view.offset, mm.b_view.offset};
+    if (bias != NONE) { mt.inputs.push_back(bias); mt.input_offsets.push_back(0); }
     mt.outputs = {cid};
     if (preact) mt.outputs.push_back(e);
     return mt;
@@ -449,18 +479,6 @@ class Graph {
   std::optional<ClassId> permute_src(ClassId c, const std::vector<int>& axes) const {
     const Node* n = find(c, [&](const Node& n) { return n.kind == K_PERMUTE && n.axes == axes; });
     return n ? std::optional<ClassId>(n->x) : std::nullopt;
-  }
-  // c [b, h, t, d] = x.reshape([b, t, h, d]).transpose(1, 2) of a stored x [b, t, h*d] (multi_head_attention.rs:160-172) -> x
-  std::optional<ClassId> head_split_src(ClassId c) const {
-    const auto s4 = shape(c);
-    if (s4.size() != 4) return std::nullopt;
-    auto r = permute_src(c, {0, 2, 1, 3});
-    if (!r) return std::nullopt;
-    auto x = reshape_src(*r);
-    if (!x) return std::nullopt;
-    const auto s3 = shape(*x);
-    if (s3.size() != 3 || s3[0] != s4[0] || s3[1] != s4[2] || s3[2] != s4[1] * s4[3]) return std::nullopt;
-    return canon(*x);
   }
   // The core of MultiheadAttention::forward without masks (multi_head_attention.rs:197-226), ending at the class of
   //   attn_weights.matmul(v).transpose(1, 2).reshape([b, t, h*d]),  attn_weights = (q.matmul(k.transpose(-2, -1)) * scale).softmax([-1]),
@@ -492,6 +510,10 @@ class Graph {
     const int dt = qk.dtype;
     if ((dt != ZYXB_BF16 && dt != ZYXB_F16) || pv->dtype != dt || D != 128 || T % 128 != 0) return std::nullopt;
     if (s3[0] != B || s3[1] != T || s3[2] != H * D) return std::nullopt;
+    // the program reads q, k, v and writes the result with one row pitch: whole [b, t, h*d] tensors, not slices of a wider one
+    const MatMul::Pitch* const views[] = {&qk.a_view, &qk.b_view, &pv->b_view};
+    for (const MatMul::Pitch* p : views)
+      if (p->offset != 0 || p->ld != H * D || p->inner != D || p->outer != T * H * D) return std::nullopt;
     Match m;
     m.pattern = "attention";
     m.desc.kind = ZYXB_KIND_ATTENTION;
@@ -935,6 +957,49 @@ class Graph {
     o.cls = c; o.idx = std::move(idx);
     return o;
   }
+  // c as a strided window of a stored tensor: element idx of c is element offset + sum(idx[a] * strides[a]) of `src`, row-major.
+  // Measured, not derived: the origin and one step along every axis give offset and strides, then every corner and a spread of
+  // other elements must agree (a reshape of a permuted tensor, say, is no such window and fails at its far corner).  nullopt
+  // when some element is padding or the elements come from more than one class.
+  struct View { ClassId src = NONE; uint64_t offset = 0; std::vector<int64_t> strides; };
+  std::optional<View> affine_view(ClassId c) const {
+    const auto& cs = shape(c);
+    const size_t rank = cs.size();
+    if (rank == 0 || rank > 6 || numel(cs) == 0) return std::nullopt;
+    std::vector<uint64_t> idx(rank, 0);
+    const Origin o0 = trace_element(c, idx);
+    if (o0.zero) return std::nullopt;
+    View v; v.src = canon(o0.cls); v.offset = ravel(o0.idx, shape(o0.cls)); v.strides.assign(rank, 0);
+    auto at = [&](const std::vector<uint64_t>& i) -> std::optional<int64_t> {
+      const Origin o = trace_element(c, i);
+      if (o.zero || canon(o.cls) != v.src) return std::nullopt;
+      return (int64_t)ravel(o.idx, shape(o.cls));
+    };
+    for (size_t a = 0; a < rank; ++a) {
+      if (cs[a] < 2) continue;
+      idx[a] = 1;
+      auto lin = at(idx);
+      idx[a] = 0;
+      if (!lin) return std::nullopt;
+      v.strides[a] = *lin - (int64_t)v.offset;
+    }
+    auto agrees = [&](const std::vector<uint64_t>& i) {
+      int64_t want = (int64_t)v.offset;
+      for (size_t a = 0; a < rank; ++a) want += (int64_t)i[a] * v.strides[a];
+      auto lin = at(i);
+      return lin && *lin == want;
+    };
+    for (uint64_t corner = 0; corner < (1ull << rank); ++corner) {
+      for (size_t a = 0; a < rank; ++a) idx[a] = (corner >> a & 1) ? cs[a] - 1 : 0;
+      if (!agrees(idx)) return std::nullopt;
+    }
+    uint64_t seed = 0x9e3779b97f4a7c15ull;                            // a fixed spread of interior elements
+    for (int probe = 0; probe < 256; ++probe) {
+      for (size_t a = 0; a < rank; ++a) { seed = seed * 6364136223846793005ull + 1442695040888963407ull; idx[a] = (seed >> 33) % cs[a]; }
+      if (!agrees(idx)) return std::nullopt;
+    }
+    return v;
+  }
   // the class a view reads: c under every movement op
   ClassId view_source(ClassId c) const {
     for (int hops = 0; hops < 256; ++hops) {
@@ -1337,25 +1402,31 @@ class Graph {
       mt.outputs = outs;
       out.push_back(std::move(mt));
     }
-    // Elementwise programs, on demand: whatever somebody has to produce - an output of the graph or an input of a program found
-    // above - that is neither stored nor the result of one of those programs gets an elementwise program if one fits, and that
-    // program's inputs are looked at in turn.  (Offering every Mul and Add of the graph as a program of its own would bury the
-    // patterns above under their own sub-expressions.)
+    // Elementwise programs, on demand.  Walk down from the outputs of the graph through the programs found above (for a class
+    // several of them end at, the one found last: the largest pattern): whatever that walk needs and nothing stored or matched
+    // produces gets an elementwise program if one fits, and the walk continues through its operands.  Offering every Mul and Add
+    // of the graph as a program of its own would bury the patterns above under their own sub-expressions; following the inputs of
+    // every alternative would do the same with the inside of a softmax.
     {
       auto has_kernel = [&](ClassId c) { for (uint32_t nid : classes[c].nodes) if (nodes[nid].kind == K_KERNEL) return true; return false; };
-      std::set<ClassId> produced, tried;
-      for (const Match& m : out) for (ClassId o : m.outputs) produced.insert(canon(o));
-      std::vector<ClassId> demand(wanted.rbegin(), wanted.rend());
-      for (const Match& m : out) demand.insert(demand.end(), m.inputs.rbegin(), m.inputs.rend());
-      while (!demand.empty()) {
-        const ClassId c = demand.back();
-        demand.pop_back();
-        if (!valid(c) || !tried.insert(canon(c)).second || produced.count(canon(c)) || is_leaf(c) || has_kernel(c) || has_kernel(canon(c))) continue;
-        auto m = match_eltwise(c);
-        if (!m) continue;
-        produced.insert(canon(c));
-        demand.insert(demand.end(), m->inputs.rbegin(), m->inputs.rend());
-        out.push_back(std::move(*m));
+      std::map<ClassId, size_t> producer;
+      for (size_t i = 0; i < out.size(); ++i) for (ClassId o : out[i].outputs) producer[canon(o)] = i;
+      std::set<ClassId> seen;
+      std::vector<ClassId> need(wanted.rbegin(), wanted.rend());
+      while (!need.empty()) {
+        const ClassId c = need.back();
+        need.pop_back();
+        if (!valid(c) || !seen.insert(canon(c)).second || is_leaf(c)) continue;
+        auto it = producer.find(canon(c));
+        if (it == producer.end()) {
+          if (has_kernel(c) || has_kernel(canon(c))) continue;
+          auto m = match_eltwise(c);
+          if (!m) continue;
+          out.push_back(std::move(*m));
+          it = producer.emplace(canon(c), out.size() - 1).first;
+        }
+        const Match& via = out[it->second];
+        need.insert(need.end(), via.inputs.rbegin(), via.inputs.rend());
       }
     }
     for (size_t i = 0; i < out.size(); ++i) {

@@ -15,7 +15,7 @@ NONE = 0xFFFFFFFF
 
 class Match(C.Structure):
     _fields_ = [("pattern", C.c_char * 32), ("n_inputs", C.c_int32), ("n_outputs", C.c_int32), ("inputs", C.c_uint32 * 128),
-                ("outputs", C.c_uint32 * 96), ("desc", L.KernelDesc), ("optim_step", C.c_uint64)]
+                ("outputs", C.c_uint32 * 96), ("desc", L.KernelDesc), ("optim_step", C.c_uint64), ("input_offsets", C.c_uint64 * 128)]
 
 
 _P = C.c_void_p
