@@ -218,6 +218,10 @@ typedef struct {
  * there becomes the matmul program's second output.  Each match is also pushed into its output classes as a Node::Kernel
  * alternative (graph/mod.rs:177-182).  Returns the number of matches in *out_n (may exceed capacity). */
 int32_t  zyxb_mgraph_match(zyxb_mgraph* g, const uint32_t* outputs, int32_t n_outputs, zyxb_match* out, int32_t capacity, int32_t* out_n);
+/* What the programs matched so far do not cover: walking down from `outputs` through the Node::Kernel alternatives (the one
+ * pushed last in each class), the classes that are needed but are neither stored tensors nor produced by a program.  *out_n = 0
+ * means the device can execute the graph on its own. */
+int32_t  zyxb_mgraph_uncovered(zyxb_mgraph* g, const uint32_t* outputs, int32_t n_outputs, uint32_t* out_classes, int32_t capacity, int32_t* out_n);
 
 #ifdef __cplusplus
 }

@@ -475,6 +475,9 @@ impl Graph {
         if let Some(x) = self.unary_of(cid, UOp::Exp).filter(|&x| whole(x)) { return program("exp", EW_EXP, vec![x], 0.0, 0, dt); }
         if let Some(x) = self.cast_src(cid).filter(|&x| is_row(self.dtype(x)) && plain(x)) { return program("cast", EW_CAST, vec![x], 0.0, 0, self.dtype(x)); }
         if let Some((x, k)) = self.binary_const(cid, BOp::Mul).filter(|&(x, _)| whole(x)) { return program("scale", EW_SCALE, vec![x], k as f32, 0, dt); }
+        // x / const as x * (1 / const): what the reference's own C backend computes under -ffast-math (reciprocal math); dropout
+        // outside training is such a division (x / (1 - p), tensor/mod.rs:822-828)
+        if let Some((x, k)) = self.binary_const(cid, BOp::Div).filter(|&(x, k)| whole(x) && k != 0.0) { return program("scale", EW_SCALE, vec![x], (1.0 / k) as f32, 0, dt); }
         for (bop, ew, name) in [(BOp::Add, EW_ADD, "add"), (BOp::Sub, EW_SUB, "sub"), (BOp::Mul, EW_MUL, "mul")] {
             if let Some((x, y)) = self.binary_of(cid, bop).filter(|&(x, y)| whole(x) && whole(y)) { return program(name, ew, vec![x, y], 0.0, 0, dt); }
         }
@@ -984,6 +987,24 @@ impl Graph {
         let (g, wd) = self.strip_decay(g1, p);
         Some(Update { algo: OPT_ADAM, p, g, m, v, p_new: cid, m_new: Some(m_new), v_new: Some(v_new), lr, wd, b1, b2, eps, bc1, bc2,
                       first: m.is_none(), mom: 0.0, damp: 0.0, nesterov: false })
+    }
+
+    /// What the programs pushed so far do NOT cover: walking down from `outputs` through the Node::Kernel alternatives (at each class
+    /// the one pushed last, the largest pattern), the classes that are needed but are neither stored nor produced by a program.
+    /// Empty: the device can execute the graph on its own.
+    pub(crate) fn uncovered_b200(&self, outputs: &BTreeSet<ClassId>) -> Vec<ClassId> {
+        let (mut missing, mut seen) = (Vec::new(), BTreeSet::new());
+        let mut need: Vec<ClassId> = outputs.iter().rev().copied().collect();
+        while let Some(c) = need.pop() {
+            if !seen.insert(self.canon(c)) || self.is_leaf(c) { continue; }
+            let (mut k, mut kernel) = (c, None);
+            loop {                                                 // the class and what it is a no-op of
+                kernel = self.classes[k].nodes.iter().rev().find_map(|&nid| match &self.nodes[nid].node { Node::Kernel { inputs, .. } => Some(inputs.clone()), _ => None });
+                match (kernel.is_some(), self.noop_cast(k)) { (false, Some(x)) => k = x, _ => break }
+            }
+            match kernel { Some(inputs) => need.extend(inputs.iter().rev()), None => missing.push(c) }
+        }
+        missing
     }
 
     /// Everything the device's match_graph needs: `order` is topo_sort_classes_without_kernels of the outputs, `wanted` the

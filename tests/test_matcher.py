@@ -667,3 +667,64 @@ def test_causal_self_attention_reads_its_fused_projection_in_place(g):
     x2 = T.leaf(g, L.BF16, (2, 256, 512))
     y2 = causal_self_attention(x2, Linear(g, L.BF16, 512, 1536), Linear(g, L.BF16, 512, 512), 4)[0]
     assert b"attention" not in {m.pattern for m in g.match([y2.cls])}
+
+
+def cover(matches, outputs, leaves):
+    """The programs a walk down from `outputs` uses (at each class the match found last, the largest pattern), in the order the
+    walk meets them; every class on the way must be stored or produced."""
+    producer = {}
+    for m in matches:
+        for o in m.outputs[:m.n_outputs]:
+            producer[o] = m
+    used, seen, need = [], set(), list(reversed(outputs))
+    while need:
+        c = need.pop()
+        if c in seen or c in leaves:
+            continue
+        seen.add(c)
+        assert c in producer, "class %d is needed and nothing produces it" % c
+        m = producer[c]
+        if not any(m is u for u in used):
+            used.append(m)
+        need.extend(reversed(m.inputs[:m.n_inputs]))
+    return used
+
+
+@pytest.mark.parametrize("norm_first", [True, False])
+def test_a_whole_transformer_encoder_layer_is_covered(g, norm_first):
+    """TransformerEncoderLayer::forward (zyx-nn/src/transformer_encoder_layer.rs:84-172; MultiheadAttention, two LayerNorms, the
+    feed-forward pair with GELU, two residual additions, dropouts that are divisions by one outside training) traced as the
+    reference builds it: the matched programs cover the graph - nothing is left for another device - and the cover is the eleven
+    launches a hand-written plan would make."""
+    from tests.zyx_trace import TransformerEncoderLayer
+    layer = TransformerEncoderLayer(g, L.BF16, 512, 4, 2048, norm_first=norm_first)
+    x = T.leaf(g, L.BF16, (2, 256, 512))
+    y = layer.forward(x)
+    ms = g.match([y.cls])
+    assert g.uncovered([y.cls]) == []
+    leaves = {x.cls}
+    for lin in (layer.self_attn.q_proj, layer.self_attn.k_proj, layer.self_attn.v_proj, layer.self_attn.out_proj, layer.linear1, layer.linear2):
+        leaves |= {lin.weight.cls, lin.bias.cls}
+    for ln in (layer.norm1, layer.norm2):
+        leaves |= {ln.weight.cls, ln.bias.cls}
+    used = sorted(m.pattern.decode() for m in cover(ms, [y.cls], leaves))
+    assert used == sorted(["layernorm"] * 2 + ["matmul_nt_batched_bias"] * 5 + ["attention", "matmul_nt_batched_bias_gelu"] + ["add"] * 2)
+    # without the programs (a fresh mirror of the same graph, nothing matched yet) the output itself is what is missing
+    g2 = MGraph()
+    try:
+        y2 = TransformerEncoderLayer(g2, L.BF16, 512, 4, 2048, norm_first=norm_first).forward(T.leaf(g2, L.BF16, (2, 256, 512)))
+        assert g2.uncovered([y2.cls]) == [y2.cls]
+    finally:
+        g2.close()
+    # a dropout probability other than zero leaves real divisions by 1 - p: scale programs (x * 1/(1 - p), the reciprocal the
+    # reference's C backend forms under -ffast-math), and the attention stays three programs around the scaled probabilities
+    g3 = MGraph()
+    try:
+        y3 = TransformerEncoderLayer(g3, L.BF16, 512, 4, 2048, dropout=0.125, norm_first=norm_first).forward(T.leaf(g3, L.BF16, (2, 256, 512)))
+        ms3 = g3.match([y3.cls])
+        assert g3.uncovered([y3.cls]) == []
+        scales = [m for m in ms3 if m.pattern == b"scale"]
+        assert len(scales) == 4 and all(abs(m.desc.u.eltwise.p0 - 1.0 / 0.875) < 1e-6 for m in scales)
+        assert b"attention" not in {m.pattern for m in ms3}
+    finally:
+        g3.close()

@@ -462,3 +462,47 @@ def causal_self_attention(x, c_attn, c_proj, n_head, dropout_p=0.0):
     att = scores.softmax([-1]).dropout(dropout_p)
     merged = att.dot(v).transpose(1, 2).reshape([b, t, c])
     return c_proj.forward(merged), scores, att, merged, qkv
+
+
+class MultiheadAttention:
+    """zyx-nn/src/multi_head_attention.rs: batch_first, no bias_kv / zero_attn, no masks, need_weights = false, outside training."""
+
+    def __init__(self, g, dtype, embed_dim, num_heads, dropout=0.0, bias=True):
+        self.h, self.d, self.dropout = num_heads, embed_dim // num_heads, dropout
+        self.q_proj, self.k_proj, self.v_proj, self.out_proj = (Linear(g, dtype, embed_dim, embed_dim, bias) for _ in range(4))
+
+    def forward(self, query, key, value):
+        b, t_q, _ = query.shape
+        t_kv = key.shape[1]
+        h, d = self.h, self.d
+        q = self.q_proj.forward(query).reshape([b, t_q, h, d]).transpose(1, 2)
+        k = self.k_proj.forward(key).reshape([b, t_kv, h, d]).transpose(1, 2)
+        v = self.v_proj.forward(value).reshape([b, t_kv, h, d]).transpose(1, 2)
+        weights = (q.dot(k.transpose(-2, -1)) * (1.0 / math.sqrt(d))).softmax([-1])
+        if self.dropout > 0.0:
+            weights = weights.dropout(self.dropout)
+        out = weights.dot(v).transpose(1, 2).reshape([b, t_q, h * d])
+        return self.out_proj.forward(out)
+
+
+class TransformerEncoderLayer:
+    """zyx-nn/src/transformer_encoder_layer.rs:84-172 without masks, outside training (every dropout is `/ (1 - p)`)."""
+
+    def __init__(self, g, dtype, d_model, nhead, dim_feedforward, dropout=0.0, activation=T.gelu, eps=1e-5, norm_first=True):
+        self.self_attn = MultiheadAttention(g, dtype, d_model, nhead, dropout)
+        self.linear1, self.linear2 = Linear(g, dtype, d_model, dim_feedforward), Linear(g, dtype, dim_feedforward, d_model)
+        self.norm1, self.norm2 = LayerNorm(g, dtype, d_model, eps), LayerNorm(g, dtype, d_model, eps)
+        self.dropout, self.activation, self.norm_first = dropout, activation, norm_first
+
+    def _sa(self, x):
+        return self.self_attn.forward(x, x, x).dropout(self.dropout)
+
+    def _ff(self, x):
+        return self.linear2.forward(self.activation(self.linear1.forward(x)).dropout(self.dropout)).dropout(self.dropout)
+
+    def forward(self, x):
+        if self.norm_first:
+            x = x + self._sa(self.norm1.forward(x))
+            return x + self._ff(self.norm2.forward(x))
+        x = self.norm1.forward(x + self._sa(x))
+        return self.norm2.forward(x + self._ff(x))

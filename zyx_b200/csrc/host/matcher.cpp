@@ -105,6 +105,16 @@ int32_t zyxb_mgraph_class_info(zyxb_mgraph* G, uint32_t c, int32_t* out_dtype, i
   return ZYXB_OK;
 }
 
+int32_t zyxb_mgraph_uncovered(zyxb_mgraph* G, const uint32_t* outputs, int32_t n_outputs, uint32_t* out, int32_t capacity, int32_t* out_n) {
+  if (!G || !outputs || n_outputs < 1 || !out_n) return ZYXB_ERR_INCORRECT_KERNEL_ARG;
+  std::vector<uint32_t> outs(outputs, outputs + n_outputs);
+  for (uint32_t o : outs) if (!G->g.valid(o)) return ZYXB_ERR_INCORRECT_KERNEL_ARG;
+  const auto missing = G->g.uncovered(outs);
+  *out_n = (int32_t)missing.size();
+  for (size_t i = 0; i < missing.size() && (int32_t)i < capacity && out; ++i) out[i] = missing[i];
+  return ZYXB_OK;
+}
+
 int32_t zyxb_mgraph_const_value(zyxb_mgraph* G, uint32_t c, double* out, uint64_t capacity, uint64_t* out_n) {
   if (!ok_class(G, c) || !out_n) return ZYXB_ERR_INCORRECT_KERNEL_ARG;
   auto v = G->g.const_eval(c);

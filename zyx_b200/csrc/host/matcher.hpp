@@ -752,6 +752,9 @@ class Graph {
     if (auto x = cast_src(cid)) if (row_dtype(dtype(*x)) && shape(*x) == cs && !expand_src(*x) && !const_value(*x))
       return program("cast", ZYXB_EW_CAST, {*x}, 0.0f, 0, dtype(*x));
     if (auto sc = binary_const(cid, B_MUL)) if (whole(sc->first)) return program("scale", ZYXB_EW_SCALE, {sc->first}, (float)sc->second);
+    // x / const as x * (1 / const): what the reference's own C backend computes under -ffast-math (reciprocal math); dropout
+    // outside training is such a division (x / (1 - p), tensor/mod.rs:822-828)
+    if (auto sc = binary_const(cid, B_DIV)) if (whole(sc->first) && sc->second != 0.0) return program("scale", ZYXB_EW_SCALE, {sc->first}, (float)(1.0 / sc->second));
     const std::tuple<int, int, const char*> ops[] = {{B_ADD, ZYXB_EW_ADD, "add"}, {B_SUB, ZYXB_EW_SUB, "sub"}, {B_MUL, ZYXB_EW_MUL, "mul"}};
     for (auto [bop, ew, name] : ops)
       if (auto b = binary(cid, bop)) if (whole(b->first) && whole(b->second)) return program(name, ew, {b->first, b->second});
@@ -1436,6 +1439,29 @@ class Graph {
       for (ClassId o : out[i].outputs) classes[o].nodes.push_back((uint32_t)nodes.size() - 1);
     }
     return out;
+  }
+
+  // What the programs pushed so far do NOT cover: walking down from `outputs` through the Node::Kernel alternatives (at each
+  // class the one pushed last, the largest pattern), the classes that are needed but are neither stored nor produced by a
+  // program.  Empty: the device can execute the graph on its own.
+  std::vector<ClassId> uncovered(const std::vector<ClassId>& outputs) const {
+    std::vector<ClassId> missing, need(outputs.rbegin(), outputs.rend());
+    std::set<ClassId> seen;
+    while (!need.empty()) {
+      ClassId c = need.back();
+      need.pop_back();
+      if (!valid(c) || !seen.insert(canon(c)).second || is_leaf(c)) continue;
+      const Node* kernel = nullptr;
+      for (ClassId k = c;;) {                               // the class and what it is a no-op of
+        for (uint32_t nid : classes[k].nodes) if (nodes[nid].kind == K_KERNEL) kernel = &nodes[nid];
+        const Node* noop = kernel ? nullptr : noop_cast(k);
+        if (!noop) break;
+        k = noop->x;
+      }
+      if (!kernel) { missing.push_back(c); continue; }
+      need.insert(need.end(), kernel->inputs.rbegin(), kernel->inputs.rend());
+    }
+    return missing;
   }
 
   // every class reachable from `outputs`, operands before users (the order match_graph walks)

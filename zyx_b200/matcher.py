@@ -36,6 +36,7 @@ MATCHER_SIGNATURES = {
     "zyxb_mgraph_binary": (C.c_uint32, [_P, C.c_uint32, C.c_uint32, C.c_int32]),
     "zyxb_mgraph_class_info": (C.c_int32, [_P, C.c_uint32, _I32_P, _I32_P, _U64_P, _I32_P]),
     "zyxb_mgraph_const_value": (C.c_int32, [_P, C.c_uint32, C.POINTER(C.c_double), C.c_uint64, _U64_P]),
+    "zyxb_mgraph_uncovered": (C.c_int32, [_P, C.POINTER(C.c_uint32), C.c_int32, C.POINTER(C.c_uint32), C.c_int32, _I32_P]),
     "zyxb_mgraph_match": (C.c_int32, [_P, C.POINTER(C.c_uint32), C.c_int32, C.POINTER(Match), C.c_int32, _I32_P]),
 }
 H.HOST_SIGNATURES.update(MATCHER_SIGNATURES)
@@ -125,3 +126,11 @@ class MGraph:
         if st != L.OK:
             raise ValueError("zyxb_mgraph_match failed: %d" % st)
         return [buf[i] for i in range(min(n.value, cap))]
+
+    def uncovered(self, outputs):
+        """Classes the matched programs need but nothing produces (not stored, no program): empty when the graph is covered."""
+        outs = (C.c_uint32 * len(outputs))(*outputs)
+        n = C.c_int32()
+        buf = (C.c_uint32 * 256)()
+        assert self.lib.zyxb_mgraph_uncovered(self.h, outs, len(outputs), buf, 256, C.byref(n)) == L.OK
+        return list(buf[:min(n.value, 256)])
