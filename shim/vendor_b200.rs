@@ -100,6 +100,15 @@ impl Graph {
     }
     fn canon(&self, mut c: ClassId) -> ClassId { while let Some(x) = self.noop_cast(c) { c = x; } c }
     fn same(&self, a: ClassId, b: ClassId) -> bool { self.canon(a) == self.canon(b) }
+    /// The class whose buffer holds c's elements: c under no-op nodes and Reshapes (dense row-major storage does not know its
+    /// shape).  Program inputs are named by it, so that `x.reshape([0, 784])` of a stored batch is the batch's own buffer.
+    fn storage(&self, mut c: ClassId) -> ClassId {
+        for _ in 0..64 {
+            c = self.canon(c);
+            match self.reshape_of(c) { Some(x) => c = x, None => break }
+        }
+        self.canon(c)
+    }
     fn find_in<T>(&self, mut c: ClassId, f: impl Fn(&Node) -> Option<T>) -> Option<T> {
         for _ in 0..8 {
             if let Some(t) = self.classes[c].nodes.iter().find_map(|&nid| f(&self.nodes[nid].node)) { return Some(t); }
@@ -998,11 +1007,12 @@ impl Graph {
         while let Some(c) = need.pop() {
             if !seen.insert(self.canon(c)) || self.is_leaf(c) { continue; }
             let (mut k, mut kernel) = (c, None);
-            loop {                                                 // the class and what it is a no-op of
+            loop {                                                 // the class, what it is a no-op of, what it is a reshape of
                 kernel = self.classes[k].nodes.iter().rev().find_map(|&nid| match &self.nodes[nid].node { Node::Kernel { inputs, .. } => Some(inputs.clone()), _ => None });
-                match (kernel.is_some(), self.noop_cast(k)) { (false, Some(x)) => k = x, _ => break }
+                if kernel.is_some() { break; }
+                match self.noop_cast(k).or_else(|| self.reshape_of(k)) { Some(x) if !self.is_leaf(x) => k = x, _ => break }
             }
-            match kernel { Some(inputs) => need.extend(inputs.iter().rev()), None => missing.push(c) }
+            match kernel { Some(inputs) => need.extend(inputs.iter().rev()), None => if !self.is_leaf(self.storage(c)) { missing.push(c) } }
         }
         missing
     }
@@ -1064,6 +1074,8 @@ impl Graph {
         let mut seen = BTreeSet::new();
         let mut need: Vec<ClassId> = wanted.iter().rev().copied().collect();
         while let Some(c) = need.pop() {
+            // nothing ends at a reshaped class: its elements are the source's
+            let c = if producer.contains_key(&self.canon(c)) { c } else { self.storage(c) };
             let k = self.canon(c);
             if !seen.insert(k) || self.is_leaf(c) { continue; }
             let via = match producer.get(&k) {
@@ -1077,6 +1089,13 @@ impl Graph {
                 }
             };
             need.extend(out[via].inputs.iter().rev());
+        }
+        // inputs are named by the class whose buffer holds them (a reshape of a stored tensor is that tensor), unless a program ends
+        // at the reshape itself
+        for m in &mut out {
+            for input in &mut m.inputs {
+                if !producer.contains_key(&self.canon(*input)) && !has_kernel(*input) && !has_kernel(self.canon(*input)) { *input = self.storage(*input); }
+            }
         }
         out
     }

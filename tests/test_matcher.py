@@ -728,3 +728,27 @@ def test_a_whole_transformer_encoder_layer_is_covered(g, norm_first):
         assert b"attention" not in {m.pattern for m in ms3}
     finally:
         g3.close()
+
+
+def test_the_mnist_example_forward_loss_and_update_are_covered(g):
+    """zyx-examples/examples/mnist.rs: `x.reshape([0, 784])`, Linear + relu, Linear, cross_entropy with class indices, and the
+    SGD update with momentum of a later step.  Four programs cover it (the two layers, the loss, the update); the reshape of
+    the stored batch is the batch's own buffer, so the first matmul reads the batch itself."""
+    batch = T.leaf(g, L.F32, (128, 784))
+    labels = T.leaf(g, L.I32, (128,))
+    l1, l2 = Linear(g, L.F32, 784, 128), Linear(g, L.F32, 128, 10)
+    logits = l2.forward(l1.forward(batch.reshape([128, 784])).relu())
+    loss, _ = logits.cross_entropy(labels)
+    params = [l1.weight, l1.bias, l2.weight, l2.bias]
+    grads = [T.leaf(g, L.F32, p.shape) for p in params]          # what Tape::gradient hands to the optimizer
+    bufs = [T.leaf(g, L.F32, p.shape) for p in params]
+    new_p, new_b = sgd_update(params, grads, 0.01, momentum=0.9, bufs=bufs)
+    outs = [loss.cls] + [t.cls for t in new_p + new_b]
+    ms = g.match(outs)
+    assert g.uncovered(outs) == []
+    leaves = {t.cls for t in [batch, labels] + params + grads + bufs}
+    used = cover(ms, outs, leaves)
+    assert [m.pattern for m in used] == [b"cross_entropy", b"matmul_nt_bias", b"matmul_nt_bias_relu", b"sgd_momentum"]
+    first = used[2]
+    assert list(first.inputs[:3]) == [batch.cls, l1.weight.cls, l1.bias.cls]
+    assert_same_gemm(first.desc, B.gemm_desc(L.F32, 128, 128, 784, trans_b=True, epilogue=L.EPI_BIAS_RELU))

@@ -163,6 +163,17 @@ class Graph {
   }
   ClassId canon(ClassId c) const { while (const Node* k = noop_cast(c)) c = k->x; return c; }
   bool same(ClassId a, ClassId b) const { return canon(a) == canon(b); }
+  // The class whose buffer holds c's elements: c under no-op nodes and Reshapes (dense row-major storage does not know its shape).
+  // Program inputs are named by it, so that `x.reshape([0, 784])` of a stored batch is the batch's own buffer.
+  ClassId storage(ClassId c) const {
+    for (int hops = 0; hops < 64; ++hops) {
+      c = canon(c);
+      const Node* r = find(c, [](const Node& n) { return n.kind == K_RESHAPE; });
+      if (!r) break;
+      c = r->x;
+    }
+    return canon(c);
+  }
   std::optional<std::pair<ClassId, ClassId>> binary(ClassId c, int bop) const {
     const Node* n = find(c, [&](const Node& n) { return n.kind == K_BINARY && n.op == bop; });
     if (!n) return std::nullopt;
@@ -1410,16 +1421,18 @@ class Graph {
     // produces gets an elementwise program if one fits, and the walk continues through its operands.  Offering every Mul and Add
     // of the graph as a program of its own would bury the patterns above under their own sub-expressions; following the inputs of
     // every alternative would do the same with the inside of a softmax.
+    auto has_kernel = [&](ClassId c) { for (uint32_t nid : classes[c].nodes) if (nodes[nid].kind == K_KERNEL) return true; return false; };
+    std::map<ClassId, size_t> producer;
     {
-      auto has_kernel = [&](ClassId c) { for (uint32_t nid : classes[c].nodes) if (nodes[nid].kind == K_KERNEL) return true; return false; };
-      std::map<ClassId, size_t> producer;
       for (size_t i = 0; i < out.size(); ++i) for (ClassId o : out[i].outputs) producer[canon(o)] = i;
       std::set<ClassId> seen;
       std::vector<ClassId> need(wanted.rbegin(), wanted.rend());
       while (!need.empty()) {
-        const ClassId c = need.back();
+        ClassId c = need.back();
         need.pop_back();
-        if (!valid(c) || !seen.insert(canon(c)).second || is_leaf(c)) continue;
+        if (!valid(c)) continue;
+        if (!producer.count(canon(c))) c = storage(c);                // nothing ends at the reshaped class: its elements are the source's
+        if (!seen.insert(canon(c)).second || is_leaf(c)) continue;
         auto it = producer.find(canon(c));
         if (it == producer.end()) {
           if (has_kernel(c) || has_kernel(canon(c))) continue;
@@ -1432,6 +1445,8 @@ class Graph {
         need.insert(need.end(), via.inputs.rbegin(), via.inputs.rend());
       }
     }
+    // inputs are named by the class whose buffer holds them (a reshape of a stored tensor is that tensor), unless a program ends at the reshape itself
+    for (Match& m : out) for (ClassId& in : m.inputs) if (!producer.count(canon(in)) && !has_kernel(in) && !has_kernel(canon(in))) in = storage(in);
     for (size_t i = 0; i < out.size(); ++i) {
       if (out[i].desc.kind == ZYXB_KIND_OPTIM) out[i].desc.u.optim.numel = out[i].numel.data();
       Node k; k.kind = K_KERNEL; k.inputs = out[i].inputs; k.outputs = out[i].outputs; k.program = (uint32_t)i; k.time = 1;
@@ -1452,13 +1467,16 @@ class Graph {
       need.pop_back();
       if (!valid(c) || !seen.insert(canon(c)).second || is_leaf(c)) continue;
       const Node* kernel = nullptr;
-      for (ClassId k = c;;) {                               // the class and what it is a no-op of
+      for (ClassId k = c;;) {                               // the class, what it is a no-op of, what it is a reshape of
         for (uint32_t nid : classes[k].nodes) if (nodes[nid].kind == K_KERNEL) kernel = &nodes[nid];
-        const Node* noop = kernel ? nullptr : noop_cast(k);
-        if (!noop) break;
-        k = noop->x;
+        if (kernel) break;
+        const Node* through = noop_cast(k);
+        if (!through) through = find(k, [](const Node& n) { return n.kind == K_RESHAPE; });
+        if (!through) break;
+        k = through->x;
+        if (is_leaf(k)) break;
       }
-      if (!kernel) { missing.push_back(c); continue; }
+      if (!kernel) { if (!is_leaf(storage(c))) missing.push_back(c); continue; }
       need.insert(need.end(), kernel->inputs.rbegin(), kernel->inputs.rend());
     }
     return missing;
