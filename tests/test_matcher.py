@@ -752,3 +752,17 @@ def test_the_mnist_example_forward_loss_and_update_are_covered(g):
     first = used[2]
     assert list(first.inputs[:3]) == [batch.cls, l1.weight.cls, l1.bias.cls]
     assert_same_gemm(first.desc, B.gemm_desc(L.F32, 128, 128, 784, trans_b=True, epilogue=L.EPI_BIAS_RELU))
+
+
+def test_the_encoder_layer_at_the_transformer_configuration_size(g):
+    """Batch 8, sequence 2048, d_model 2048, 16 heads of 128, feed-forward 8192 (the transformer-block configuration): covered,
+    with the fused attention program at exactly that shape and the feed-forward matmuls at theirs."""
+    from tests.zyx_trace import TransformerEncoderLayer
+    layer = TransformerEncoderLayer(g, L.BF16, 2048, 16, 8192, norm_first=True)
+    y = layer.forward(T.leaf(g, L.BF16, (8, 2048, 2048)))
+    ms = g.match([y.cls])
+    assert g.uncovered([y.cls]) == []
+    a = next(m for m in ms if m.pattern == b"attention").desc.u.attention
+    assert (a.dtype, a.batch, a.heads, a.seq, a.head_dim, a.causal) == (L.BF16, 8, 16, 2048, 128, 0) and abs(a.scale - 128 ** -0.5) < 1e-3
+    up = next(m for m in ms if m.pattern == b"matmul_nt_batched_bias_gelu").desc.u.gemm
+    assert (up.m, up.n, up.k, up.batch, up.trans_b, up.epilogue, up.stride_b) == (2048, 8192, 2048, 8, 1, L.EPI_BIAS_GELU, 0)
