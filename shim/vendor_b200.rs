@@ -223,6 +223,8 @@ impl Graph {
         if self.dtype(a) != dt || self.dtype(cid) != dt || !matches!(dt, DType::F32 | DType::BF16 | DType::F16 | DType::I32) { return None; }
         let mut mm = MatMulX { a: self.canon(a), b: self.canon(b), m, n, k, batch: batch_dims.iter().product(), trans_a, trans_b, b_shared, dtype: dt,
                                outer: 0, heads: 0, a_heads: false, b_heads: false, c_heads: false, a_view: Pitch::default(), b_view: Pitch::default() };
+        // one right operand for every matrix of a dense batch (a Linear applied to [b, t, features]): the batch is just more rows
+        if b_shared && !trans_a { (mm.m, mm.batch, mm.b_shared) = (mm.m * mm.batch, 1, false); }
         if batch_dims.len() == 2 && !b_shared {
             // q / k / v of attention, `x.reshape([b, t, h, d]).transpose(1, 2)` (multi_head_attention.rs:160-172) or the same of a
             // slice of a fused projection (`c_attn.forward(x).split([c, c, c], 2)`, causal_self_attention.rs:39-52): any operand that

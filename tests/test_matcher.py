@@ -121,8 +121,8 @@ def test_batched_matmul_shared_and_per_batch_operands_and_scale(g):
         a3, w3 = T.leaf(g3, L.F32, (6, 40, 24)), T.leaf(g3, L.F32, (24, 56))
         o3 = a3.dot(w3)
         m3 = g3.match([o3.cls])[-1]
-        assert m3.pattern == b"matmul_nn_batched" and m3.outputs[0] == o3.cls
-        assert_same_gemm(m3.desc, B.gemm_desc(L.F32, 40, 56, 24, batch=6, stride_b=0))
+        assert m3.pattern == b"matmul_nn" and m3.outputs[0] == o3.cls          # one matrix for the whole batch: 6 * 40 rows
+        assert_same_gemm(m3.desc, B.gemm_desc(L.F32, 240, 56, 24))
     finally:
         g3.close()
 
@@ -131,7 +131,8 @@ def test_batched_matmul_shared_and_per_batch_operands_and_scale(g):
 def test_transposed_left_operand_is_read_where_it_lies(g, dtype):
     """`dz.t().dot(x)`, a Linear's weight gradient written by hand: the left operand of the program is the stored dz with
     trans_a, the descriptor the Linear-stack plan creates for its weight-gradient launch (host/trainer.cpp); with `w.t()` on
-    the right as well both flags are set; a rank-3 left operand against a shared matrix keeps its batch."""
+    the right as well both flags are set; a transposed rank-3 left operand against a shared matrix keeps its batch (stride 0 on
+    the right), where an untransposed one folds its batch into the rows."""
     dz, x = T.leaf(g, dtype, (8192, 512)), T.leaf(g, dtype, (8192, 384))
     dw = dz.t().dot(x)
     m = g.match([dw.cls])[-1]
@@ -154,7 +155,7 @@ def test_transposed_left_operand_is_read_where_it_lies(g, dtype):
     a4 = T.leaf(g, dtype, (24, 6, 40))
     o4 = a4.permute([1, 0, 2]).dot(T.leaf(g, dtype, (40, 56)))
     m = g.match([o4.cls])[-1]
-    assert m.pattern == b"matmul_nn_batched" and m.inputs[0] != a4.cls
+    assert m.pattern == b"matmul_nn" and m.inputs[0] != a4.cls              # (its 6 x 24 rows folded against the shared right operand)
 
 
 @pytest.mark.parametrize("dtype", [L.F32, L.BF16])
@@ -639,8 +640,9 @@ def test_causal_self_attention_reads_its_fused_projection_in_place(g):
     c_attn, c_proj = Linear(g, L.BF16, c, 3 * c), Linear(g, L.BF16, c, c)
     y, scores, att, merged, qkv = causal_self_attention(x, c_attn, c_proj, h)
     at = {m.outputs[0]: m for m in g.match([y.cls])}
-    m = at[qkv.cls]                                       # the fused projection: one matmul over [b*t] rows... as a batch of b
-    assert m.pattern == b"matmul_nt_batched_bias" and list(m.inputs[:3]) == [x.cls, c_attn.weight.cls, c_attn.bias.cls]
+    m = at[qkv.cls]                                       # the fused projection: one matmul over all b * t rows
+    assert m.pattern == b"matmul_nt_bias" and list(m.inputs[:3]) == [x.cls, c_attn.weight.cls, c_attn.bias.cls]
+    assert_same_gemm(m.desc, B.gemm_desc(L.BF16, nb * t, 3 * c, c, trans_b=True, epilogue=L.EPI_BIAS))
     ms = at[scores.cls]
     assert ms.pattern == b"matmul_nt_batched_heads" and list(ms.inputs[:2]) == [qkv.cls, qkv.cls]
     assert list(ms.input_offsets[:2]) == [0, c]           # q starts at feature 0, k at feature c of every row
@@ -656,7 +658,7 @@ def test_causal_self_attention_reads_its_fused_projection_in_place(g):
     assert_same_gemm(mv.desc, B.gemm_desc(L.BF16, t, d, t, batch=nb, batch_inner=h, stride_a=h * t * t, stride_a_inner=t * t,
                                           ldb=3 * c, stride_b=t * 3 * c, stride_b_inner=d, ldc=c, stride_c=t * c, stride_c_inner=d))
     mo = at[y.cls]
-    assert mo.pattern == b"matmul_nt_batched_bias" and list(mo.inputs[:3]) == [merged.cls, c_proj.weight.cls, c_proj.bias.cls]
+    assert mo.pattern == b"matmul_nt_bias" and list(mo.inputs[:3]) == [merged.cls, c_proj.weight.cls, c_proj.bias.cls]
     # a slice that does not start on a 256-byte boundary of its buffer cannot be handed over as a view (zyxb_buffer_view): left alone
     x3 = T.leaf(g, L.BF16, (2, 32, 96))
     odd = causal_self_attention(x3, Linear(g, L.BF16, 96, 288), Linear(g, L.BF16, 96, 96), 4)
@@ -708,7 +710,7 @@ def test_a_whole_transformer_encoder_layer_is_covered(g, norm_first):
     for ln in (layer.norm1, layer.norm2):
         leaves |= {ln.weight.cls, ln.bias.cls}
     used = sorted(m.pattern.decode() for m in cover(ms, [y.cls], leaves))
-    assert used == sorted(["layernorm"] * 2 + ["matmul_nt_batched_bias"] * 5 + ["attention", "matmul_nt_batched_bias_gelu"] + ["add"] * 2)
+    assert used == sorted(["layernorm"] * 2 + ["matmul_nt_bias"] * 5 + ["attention", "matmul_nt_bias_gelu"] + ["add"] * 2)
     # without the programs (a fresh mirror of the same graph, nothing matched yet) the output itself is what is missing
     g2 = MGraph()
     try:
@@ -764,5 +766,5 @@ def test_the_encoder_layer_at_the_transformer_configuration_size(g):
     assert g.uncovered([y.cls]) == []
     a = next(m for m in ms if m.pattern == b"attention").desc.u.attention
     assert (a.dtype, a.batch, a.heads, a.seq, a.head_dim, a.causal) == (L.BF16, 8, 16, 2048, 128, 0) and abs(a.scale - 128 ** -0.5) < 1e-3
-    up = next(m for m in ms if m.pattern == b"matmul_nt_batched_bias_gelu").desc.u.gemm
-    assert (up.m, up.n, up.k, up.batch, up.trans_b, up.epilogue, up.stride_b) == (2048, 8192, 2048, 8, 1, L.EPI_BIAS_GELU, 0)
+    up = next(m for m in ms if m.pattern == b"matmul_nt_bias_gelu")         # the batch folded into the rows: the plan's own launch
+    assert_same_gemm(up.desc, B.gemm_desc(L.BF16, 8 * 2048, 8192, 2048, trans_b=True, epilogue=L.EPI_BIAS_GELU))

@@ -7,7 +7,8 @@
 // is the same machinery over a mirror of that graph, extended to what an aot_only device must cover:
 //   matmul          NN as the reference; NT on a stored weight (`x.dot(W.t())` of Linear::forward, zyx-nn/src/linear.rs:39-45,
 //                   where the reference would hand the kernel the *class* W.t()); TN / TT when the left operand is `x.t()` of
-//                   a stored tensor (a weight gradient written as `dz.t().dot(x)`); rank > 2 with batch strides; per-head
+//                   a stored tensor (a weight gradient written as `dz.t().dot(x)`); rank > 2 with batch strides, a right
+//                   operand shared by the whole batch folding the batch into the rows; per-head
 //                   views of stored [b, t, h*d] tensors as operands and as the merged result (no [b, h, t, d] copies); the
 //                   accumulator Casts that `sum` puts around the Reduce for 16-bit inputs (tensor/reduce_ops.rs:52-60,143-145);
 //                   a trailing `* const` (attention's 1/sqrt(d)) as alpha; `+ bias`, relu and gelu as epilogues
@@ -332,7 +333,9 @@ class Graph {
     if (!(dt == ZYXB_F32 || dt == ZYXB_BF16 || dt == ZYXB_F16 || dt == ZYXB_I32)) return std::nullopt;
     MatMul mm{canon(a), canon(b), cid, m, n, k, numel(batch_dims), trans_b, b_shared, dt};
     mm.trans_a = trans_a;
-    if (batch_dims.size() == 2 && !b_shared) {
+    // one right operand for every matrix of a dense batch (a Linear applied to [b, t, features]): the batch is just more rows
+    if (b_shared && !trans_a) { mm.m *= mm.batch; mm.batch = 1; mm.b_shared = false; }
+    if (batch_dims.size() == 2 && !b_shared) {      // (b_shared: as the batch was given, folded or not)
       // q / k / v of attention, `x.reshape([b, t, h, d]).transpose(1, 2)` (multi_head_attention.rs:160-172) or the same of a slice
       // of a fused projection (`c_attn.forward(x).split([c, c, c], 2)`, causal_self_attention.rs:39-52): any operand that is a
       // view with unit step along its rows is read where it lies
