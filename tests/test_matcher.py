@@ -768,3 +768,21 @@ def test_the_encoder_layer_at_the_transformer_configuration_size(g):
     assert (a.dtype, a.batch, a.heads, a.seq, a.head_dim, a.causal) == (L.BF16, 8, 16, 2048, 128, 0) and abs(a.scale - 128 ** -0.5) < 1e-3
     up = next(m for m in ms if m.pattern == b"matmul_nt_bias_gelu")         # the batch folded into the rows: the plan's own launch
     assert_same_gemm(up.desc, B.gemm_desc(L.BF16, 8 * 2048, 8192, 2048, trans_b=True, epilogue=L.EPI_BIAS_GELU))
+
+
+def test_a_small_convolutional_classifier_is_covered(g):
+    """Conv2d::forward is Tensor::conv (zyx-nn/src/conv2d.rs:58-68): two strided convolutions with relu, the features flattened
+    (a reshape: the same buffer) into a Linear, cross-entropy on top - six programs, nothing left over."""
+    x, labels = T.leaf(g, L.F32, (16, 3, 32, 32)), T.leaf(g, L.I32, (16,))
+    w1, b1 = T.leaf(g, L.F32, (8, 3, 3, 3)), T.leaf(g, L.F32, (8,))
+    w2, b2 = T.leaf(g, L.F32, (16, 8, 3, 3)), T.leaf(g, L.F32, (16,))
+    fc = Linear(g, L.F32, 16 * 8 * 8, 10)
+    h1 = x.conv(w1, b1, stride=(2,), padding=(1,)).relu()                   # [16, 8, 16, 16]
+    h2 = h1.conv(w2, b2, stride=(2,), padding=(1,)).relu()                  # [16, 16, 8, 8]
+    loss, _ = fc.forward(h2.reshape([16, 16 * 8 * 8])).cross_entropy(labels)
+    ms = g.match([loss.cls])
+    assert g.uncovered([loss.cls]) == []
+    leaves = {t.cls for t in (x, labels, w1, b1, w2, b2, fc.weight, fc.bias)}
+    used = cover(ms, [loss.cls], leaves)
+    assert [m.pattern for m in used] == [b"cross_entropy", b"matmul_nt_bias", b"relu", b"conv_bias", b"relu", b"conv_bias"]
+    assert list(used[1].inputs[:1]) == [h2.cls]                              # the Linear reads the second relu's buffer through the reshape
