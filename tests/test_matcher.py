@@ -786,3 +786,84 @@ def test_a_small_convolutional_classifier_is_covered(g):
     used = cover(ms, [loss.cls], leaves)
     assert [m.pattern for m in used] == [b"cross_entropy", b"matmul_nt_bias", b"relu", b"conv_bias", b"relu", b"conv_bias"]
     assert list(used[1].inputs[:1]) == [h2.cls]                              # the Linear reads the second relu's buffer through the reshape
+
+
+def test_the_mnist_example_runs_from_its_graph_through_the_abi(g):
+    """What B200Device::match_graph and ::launch do (shim/b200.rs), in Python against the host-memory stand-in of the ABI: match
+    the traced graph, create one program per match of the cover, give every class a buffer, launch in dependency order with
+    args = the matched inputs' buffers followed by the outputs' - an optimizer program on copies of the parameters, as the shim's
+    launch does - and read the loss and the new parameters back.  They are the float64 values of the same step."""
+    import ctypes as C
+
+    import numpy as np
+
+    from tests.fake.harness import Fake
+
+    rng = np.random.default_rng(9)
+    n = 32
+    batch, labels = T.leaf(g, L.F32, (n, 784)), T.leaf(g, L.I32, (n,))
+    l1, l2 = Linear(g, L.F32, 784, 128), Linear(g, L.F32, 128, 10)
+    loss, _ = l2.forward(l1.forward(batch.reshape([n, 784])).relu()).cross_entropy(labels)
+    params = [l1.weight, l1.bias, l2.weight, l2.bias]
+    grads = [T.leaf(g, L.F32, p.shape) for p in params]
+    new_p = sgd_update(params, grads, 0.05)
+    outs = [loss.cls] + [t.cls for t in new_p]
+    ms = g.match(outs)
+    assert g.uncovered(outs) == []
+    values = {batch.cls: rng.standard_normal((n, 784)).astype(np.float32), labels.cls: rng.integers(0, 10, n).astype(np.int32)}
+    for p, gr in zip(params, grads):
+        values[p.cls] = (0.05 * rng.standard_normal(p.shape)).astype(np.float32)
+        values[gr.cls] = rng.standard_normal(gr.shape).astype(np.float32)
+    fake = Fake()
+    buffers = {}
+
+    def buffer_of(cls):
+        if cls not in buffers:
+            nbytes = 4 * int(np.prod(g.info(cls)[1]) or 1)
+            b = C.c_uint32()
+            assert fake.lib.zyxb_alloc(fake.ctx, 0, nbytes, C.byref(b), None) == L.OK
+            buffers[cls] = b.value
+            if cls in values:
+                fake.upload(b.value, values[cls])
+        return buffers[cls]
+
+    order, done = [], set()
+
+    def schedule(m):                                    # operands before users
+        if id(m) in done:
+            return
+        done.add(id(m))
+        for c in m.inputs[:m.n_inputs]:
+            if c not in values:
+                schedule(producer[c])
+        order.append(m)
+
+    producer = {o: m for m in ms for o in m.outputs[:m.n_outputs]}
+    for o in outs:
+        schedule(producer[o])
+    assert [m.pattern for m in order] == [b"matmul_nt_bias_relu", b"matmul_nt_bias", b"cross_entropy", b"sgd"]
+    for m in order:
+        prog = C.c_uint32()
+        assert fake.lib.zyxb_program_create(fake.ctx, 0, C.byref(m.desc), C.byref(prog)) == L.OK, fake.last_error()
+        ins = [buffer_of(c) for c in m.inputs[:m.n_inputs]]
+        stores = [buffer_of(c) for c in m.outputs[:m.n_outputs]]
+        if m.desc.kind == L.KIND_OPTIM:
+            assert fake.lib.zyxb_program_set_step(fake.ctx, 0, prog.value, m.optim_step - 1) == L.OK
+            t = m.desc.u.optim.n_tensors
+            for i in range(t):                          # p -> p', then the program updates p' where it lies
+                nbytes = 4 * int(np.prod(g.info(m.inputs[i])[1]))
+                assert fake.lib.zyxb_d2d(fake.ctx, 0, ins[i], 0, 0, stores[i], 0, nbytes, None, 0, None) == L.OK
+            ids = stores + ins[t:2 * t]
+        else:
+            ids = ins + stores
+        args = (C.c_uint32 * len(ids))(*ids)
+        assert fake.lib.zyxb_launch(fake.ctx, 0, prog.value, args, len(ids), None, 0, None) == L.OK, (m.pattern, fake.last_error())
+    x = values[batch.cls].astype(np.float64)
+    w1, b1, w2, b2 = (values[p.cls].astype(np.float64) for p in params)
+    logits = np.maximum(x @ w1.T + b1, 0.0) @ w2.T + b2
+    lse = np.log(np.exp(logits - logits.max(1, keepdims=True)).sum(1)) + logits.max(1)
+    want_loss = (lse - logits[np.arange(n), values[labels.cls]]).mean()
+    np.testing.assert_allclose(fake.download(buffers[loss.cls], (1,))[0], want_loss, rtol=1e-5)
+    for p, gr, q in zip(params, grads, new_p):
+        np.testing.assert_allclose(fake.download(buffers[q.cls], p.shape), values[p.cls] - 0.05 * values[gr.cls], rtol=1e-6, atol=1e-7)
+        np.testing.assert_array_equal(fake.download(buffers[p.cls], p.shape), values[p.cls])      # the old parameters are untouched
