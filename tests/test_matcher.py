@@ -867,3 +867,31 @@ def test_the_mnist_example_runs_from_its_graph_through_the_abi(g):
     for p, gr, q in zip(params, grads, new_p):
         np.testing.assert_allclose(fake.download(buffers[q.cls], p.shape), values[p.cls] - 0.05 * values[gr.cls], rtol=1e-6, atol=1e-7)
         np.testing.assert_array_equal(fake.download(buffers[p.cls], p.shape), values[p.cls])      # the old parameters are untouched
+
+
+def test_the_mlp_configuration_forward_loss_and_update_are_covered(g):
+    """The Linear stack of the headline configuration (4096 -> 16384 -> 4096 -> 16384 -> 4096, GELU between, bf16, batch 8192, MSE
+    in f32 on the cast output, AdamW at a later step): the forward is the plan's four matmuls with their epilogues, the update one
+    multi-tensor program over the eight parameter tensors and their moments."""
+    dims = [4096, 16384, 4096, 16384, 4096]
+    x, target = T.leaf(g, L.BF16, (8192, dims[0])), T.leaf(g, L.F32, (8192, dims[-1]))
+    layers = [Linear(g, L.BF16, a, b) for a, b in zip(dims, dims[1:])]
+    h = x
+    for i, lin in enumerate(layers):
+        h = lin.forward(h)
+        if i + 1 < len(layers):
+            h = h.gelu()
+    loss = h.cast(L.F32).mse_loss(target)
+    params = [t for lin in layers for t in (lin.weight, lin.bias)]
+    grads, m, v = ([T.leaf(g, L.BF16, p.shape) for p in params] for _ in range(3))
+    new_p, new_m, new_v = adamw_update(params, grads, m, v, 7)
+    outs = [loss.cls] + [t.cls for t in new_p + new_m + new_v]
+    ms = g.match(outs)
+    assert g.uncovered(outs) == []
+    leaves = {t.cls for t in [x, target] + params + grads + m + v}
+    used = cover(ms, outs, leaves)
+    assert sorted(u.pattern.decode() for u in used) == sorted(["matmul_nt_bias_gelu"] * 3 + ["matmul_nt_bias", "cast", "mse_loss", "adamw"])
+    upd = next(u for u in used if u.pattern == b"adamw")
+    assert upd.desc.u.optim.n_tensors == 8 and upd.optim_step == 7 and upd.n_inputs == 32 and upd.n_outputs == 24
+    first = next(u for u in used if u.inputs[0] == x.cls)
+    assert_same_gemm(first.desc, B.gemm_desc(L.BF16, 8192, 16384, 4096, trans_b=True, epilogue=L.EPI_BIAS_GELU))
