@@ -375,10 +375,10 @@ impl Graph {
         if qk.trans_a || !qk.trans_b || qk.b_shared { return None; }
         if !qk.a_heads || !qk.b_heads || !pv.b_heads || pv.a_heads { return None; }          // q, k, v: per-head views of stored tensors
         let (xq, xk, xv) = (qk.a, qk.b, pv.b);
-        // the program reads q, k, v and writes the result with one row pitch: whole [b, t, h*d] tensors, not slices of a wider one
-        let whole = |p: Pitch, t: Dim, h: Dim, d: Dim| p == Pitch { offset: 0, ld: h * d, inner: d, outer: t * h * d };
         let hs = self.const_shape(pv_cls)?;
         let (b, h, t, d) = (hs[0], hs[1], hs[2], hs[3]);
+        // the program reads q, k, v and writes the result with one row pitch: whole [b, t, h*d] tensors, not slices of a wider one
+        let whole = |p: Pitch, t: Dim, h: Dim, d: Dim| p.offset == 0 && p.ld == h * d && (h == 1 || p.inner == d) && (b == 1 || p.outer == t * h * d);   // (a single image or head is never stepped over)
         let shapes_ok = qk.m == t && qk.n == t && qk.k == d && pv.m == t && pv.k == t && pv.n == d && qk.batch == b * h && pv.batch == b * h
             && s3[0] == b && s3[1] == t && s3[2] == h * d;
         let dt = qk.dtype;

@@ -1,0 +1,123 @@
+"""Soundness of the matcher: every matched program computes what the subgraph it replaces computes.
+
+The mirror graph carries a float64 value per class (tests/desc_interp.py: ValGraph evaluates zyx's graph semantics node by node),
+and every match - the covers and the alternatives at inner classes alike - is executed the way its descriptor reads, on the flat
+values of its input classes, and held against the values of its output classes.  A wrong operand, row pitch, batch stride,
+argument offset, transposition flag, epilogue, convolution geometry, hyper-parameter or step number shows up here, on the CPU,
+whatever the shapes are."""
+import numpy as np
+import pytest
+
+from tests.desc_interp import ValGraph, run_match
+from tests.zyx_trace import (LayerNorm, Linear, T, TransformerEncoderLayer, adam_update, adamw_update, attention_core,
+                             causal_self_attention, sgd_update)
+from zyx_b200 import _lib as L
+
+
+def check_every_match(g, outputs, expect_patterns=()):
+    ms = g.match(outputs)
+    assert ms, "nothing matched"
+    for m in ms:
+        got = run_match(g, m)
+        assert len(got) == m.n_outputs, m.pattern
+        for cls, flat in zip(m.outputs[:m.n_outputs], got):
+            want = np.asarray(g.vals[cls], np.float64).reshape(-1)
+            scale = max(float(np.abs(want).max()), 1e-30)
+            err = float(np.abs(flat - want).max()) / scale
+            assert flat.shape == want.shape and err <= 2e-6, (m.pattern, cls, err)      # constants pass through f32 descriptor fields
+    seen = {m.pattern.decode() for m in ms}
+    assert set(expect_patterns) <= seen, sorted(seen)
+    return ms
+
+
+@pytest.fixture()
+def g():
+    graph = ValGraph(seed=11)
+    yield graph
+    graph.close()
+
+
+def test_matmuls_in_every_layout_and_with_every_epilogue(g):
+    a, b = T.leaf(g, L.F32, (24, 40)), T.leaf(g, L.F32, (40, 56))
+    w, dz = T.leaf(g, L.F32, (56, 40)), T.leaf(g, L.F32, (24, 56))
+    lin = Linear(g, L.BF16, 40, 56)
+    x16 = T.leaf(g, L.BF16, (24, 40))
+    z = lin.forward(x16)
+    a3, b3 = T.leaf(g, L.F32, (3, 24, 40)), T.leaf(g, L.F32, (3, 40, 8))
+    outs = [a.dot(b), a.dot(w.t()), dz.t().dot(a), dz.t().dot(T.leaf(g, L.F32, (8, 24)).t()), z.gelu(), z, lin.forward(x16).relu(), a3.dot(b3),
+            a3.dot(b), a3.t().dot(T.leaf(g, L.F32, (24, 8))), a3.dot(b3) * 0.125]
+    check_every_match(g, [t.cls for t in outs], ["matmul_nn", "matmul_nt", "matmul_tn", "matmul_tt", "matmul_nt_bias_gelu", "matmul_nt_bias_relu",
+                                                 "matmul_nn_batched", "matmul_tn_batched"])
+
+
+def test_row_programs_losses_and_elementwise_programs(g):
+    x = T.leaf(g, L.F32, (12, 48))
+    ln = LayerNorm(g, L.F32, 48, eps=1e-5)
+    labels = T.leaf(g, L.I32, (12,))
+    t = T.leaf(g, L.F32, (12, 48))
+    loss, _ = T.leaf(g, L.F32, (12, 10)).cross_entropy(labels)
+    bias = T.leaf(g, L.F32, (48,))
+    outs = [x.softmax(), x.ln_softmax(), ln.forward(x), LayerNorm(g, L.F32, 48, weight=False, bias=False).forward(x), x.sum([-1]),
+            x.max([-1]), x.min([-1]), x.mean([-1]), x.var([-1]), x.var([-1], correction=0), x.std([-1]), x.sum([0]), x.mse_loss(t), loss,
+            x.gelu(), x.relu(), x.tanh(), x.exp() / (x.exp() + 1), (x * t + x).exp(), x * 0.25, x / 0.8, x - t, x + bias, x.cast(L.BF16)]
+    check_every_match(g, [o.cls for o in outs], ["softmax", "ln_softmax", "layernorm", "sum", "max", "min", "mean", "var", "std", "colsum",
+                                                 "mse_loss", "cross_entropy", "gelu", "relu", "tanh", "sigmoid", "exp", "add", "mul",
+                                                 "scale", "sub", "bias_add", "cast"])
+
+
+@pytest.mark.parametrize("stride,dilation,padding", [((1,), (1,), (1,)), ((2,), (1,), (3,)), ((2, 1), (1, 2), (1, 2, 0, 3)), ((3,), (2,), (0,))])
+def test_convolutions(g, stride, dilation, padding):
+    x, w, b = T.leaf(g, L.F32, (2, 3, 13, 11)), T.leaf(g, L.F32, (4, 3, 3, 2)), T.leaf(g, L.F32, (4,))
+    check_every_match(g, [x.conv(w, b, stride=stride, dilation=dilation, padding=padding).cls, x.conv(w, stride=stride, padding=padding).cls],
+                      ["conv", "conv_bias"])
+
+
+def test_attention_fused_and_in_three_programs(g):
+    q, k, v = (T.leaf(g, L.BF16, (2, 128, 256)) for _ in range(3))
+    check_every_match(g, [attention_core(q, k, v, heads=2).cls], ["attention", "matmul_nt_batched_heads", "softmax"])
+    q, k, v = (T.leaf(g, L.F32, (2, 24, 64)) for _ in range(3))
+    check_every_match(g, [attention_core(q, k, v, heads=4).cls], ["matmul_nt_batched_heads", "matmul_nn_batched_heads", "softmax"])
+    # the adjoint's products written by hand: p^T . dO and dS^T . q read the packed scores transposed and the per-head views in place
+    nb, t, h, d = 2, 24, 4, 16
+    p4, do, qq = T.leaf(g, L.F32, (nb, h, t, t)), T.leaf(g, L.F32, (nb, t, h * d)), T.leaf(g, L.F32, (nb, t, h * d))
+    split = lambda z: z.reshape([nb, t, h, d]).permute([0, 2, 1, 3])
+    dv = p4.t().dot(split(do)).permute([0, 2, 1, 3]).reshape([nb, t, h * d])
+    dp = split(do).dot(split(qq).t())
+    ms = check_every_match(g, [dv.cls, dp.cls], ["matmul_tn_batched_heads", "matmul_nt_batched_heads"])
+    assert next(m for m in ms if m.pattern == b"matmul_tn_batched_heads" and m.outputs[0] == dv.cls).desc.u.gemm.ldc == h * d
+    # q, k, v as slices of one fused projection: row pitch 3c and argument offsets (256-byte aligned slices: c = 128 in f32)
+    x = T.leaf(g, L.F32, (2, 16, 128))
+    y = causal_self_attention(x, Linear(g, L.F32, 128, 384), Linear(g, L.F32, 128, 128), 4, dropout_p=0.0)[0]
+    ms = check_every_match(g, [y.cls], ["matmul_nt_batched_heads", "matmul_nn_batched_heads", "matmul_nt_bias"])
+    assert any(list(m.input_offsets[:2]) == [0, 128] for m in ms) and any(list(m.input_offsets[:2]) == [0, 256] for m in ms)
+
+
+@pytest.mark.parametrize("norm_first,dropout", [(True, 0.0), (False, 0.0), (True, 0.25)])
+def test_a_transformer_encoder_layer(g, norm_first, dropout):
+    g.scale = 0.05                                   # weights small enough for the tanh-by-exp GELU (it overflows near |x| = 10)
+    layer = TransformerEncoderLayer(g, L.BF16, 256, 2, 256, dropout=dropout, norm_first=norm_first)
+    y = layer.forward(T.leaf(g, L.BF16, (1, 128, 256)))
+    check_every_match(g, [y.cls], ["layernorm", "matmul_nt_bias", "matmul_nt_bias_gelu", "add"] + (["attention"] if dropout == 0.0 else ["scale"]))
+    assert g.uncovered([y.cls]) == []
+
+
+def test_optimizer_updates(g):
+    shapes = [(6, 5), (7,)]
+
+    def mk(positive=False):
+        g.positive = positive
+        return [T.leaf(g, L.F32, s) for s in shapes]
+
+    outs = []
+    outs += sgd_update(mk(), mk(), 0.05)
+    outs += sgd_update(mk(), mk(), 0.03, weight_decay=0.1)
+    for nesterov in (False, True):
+        new_p, new_b = sgd_update(mk(), mk(), 0.02, weight_decay=0.01, momentum=0.9, dampening=0.1, nesterov=nesterov, bufs=mk())
+        outs += new_p + new_b
+    for update, kw in ((adamw_update, dict(lr=2e-3, weight_decay=0.02)), (adam_update, dict(lr=3e-3, weight_decay=0.01))):
+        for step in (1, 6):
+            m, v = (mk(), mk(positive=True)) if step > 1 else (None, None)          # second moments are not negative
+            for group in update(mk(), mk(), m, v, step, betas=(0.8, 0.95), eps=1e-6, **kw):
+                outs += group
+    ms = check_every_match(g, [t.cls for t in outs], ["sgd", "sgd_momentum", "sgd_nesterov", "adamw", "adamw_first_step", "adam", "adam_first_step"])
+    assert sorted(m.optim_step for m in ms if m.pattern in (b"adamw", b"adam")) == [6, 6]

@@ -527,7 +527,7 @@ class Graph {
     // the program reads q, k, v and writes the result with one row pitch: whole [b, t, h*d] tensors, not slices of a wider one
     const MatMul::Pitch* const views[] = {&qk.a_view, &qk.b_view, &pv->b_view};
     for (const MatMul::Pitch* p : views)
-      if (p->offset != 0 || p->ld != H * D || p->inner != D || p->outer != T * H * D) return std::nullopt;
+      if (p->offset != 0 || p->ld != H * D || (H > 1 && p->inner != D) || (B > 1 && p->outer != T * H * D)) return std::nullopt;   // (a single image or head is never stepped over)
     Match m;
     m.pattern = "attention";
     m.desc.kind = ZYXB_KIND_ATTENTION;
