@@ -754,27 +754,46 @@ impl Graph {
                 ext[ax] = len;
             }
             let probe = |b: u64, co: u64, oy: u64, ox: u64, ci: u64, kr: u64, ks: u64| self.trace_element(xe, vec![b, 0, co, oy, ox, ci, kr, ks]);
-            // stride and dilation: the distance between what neighbouring windows / taps read, measured where nothing is padding
-            let step = |rows: bool, window: bool| -> Option<u64> {
-                let (n_out, n_tap, n_other) = if rows { (oh, kh, ow) } else { (ow, kw, oh) };
-                if (if window { n_out } else { n_tap }) < 2 { return Some(1); }       // a single window or tap: the step is never taken
-                for o1 in sample_axis(n_out) {
-                    for t1 in 0..n_tap {
-                        let (o2, t2) = (o1 + window as u64, t1 + !window as u64);
-                        if o2 >= n_out || t2 >= n_tap { continue; }
-                        for other in sample_axis(n_other) {
-                            let (a, b) = if rows { (probe(0, 0, o1, other, 0, t1, 0)?, probe(0, 0, o2, other, 0, t2, 0)?) }
-                                         else { (probe(0, 0, other, o1, 0, 0, t1)?, probe(0, 0, other, o2, 0, 0, t2)?) };
-                            let (Some((ca, ia)), Some((cb, ib))) = (a, b) else { continue };
-                            if ca != x || cb != x { continue; }
-                            let ax = if rows { 2 } else { 3 };
-                            return (ib[ax] > ia[ax]).then(|| ib[ax] - ia[ax]);
+            // Stride and dilation, measured: along an axis a window o and tap t read coordinate o*stride + t*dilation - pad when that
+            // is inside the image and padding otherwise.  Every (window, tap) pair of the axis is probed (at a window and tap of the
+            // OTHER axis that are themselves inside the image); two windows under one tap give the stride, two taps under one window
+            // the dilation.  Where padding leaves too few probes inside the image for that (an image smaller than its padding), any
+            // pair that explains all probes - inside and outside - and the output extent describes the same convolution: the first one
+            // found is taken.
+            let solve_axis = |rows: bool| -> Option<(u64, u64)> {
+                let (n_out, n_tap, extent, n_other, n_other_tap) = if rows { (oh as i64, kh as i64, h as i64, ow, kw) } else { (ow as i64, kw as i64, wd as i64, oh, kh) };
+                let (before, total) = if rows { (pad[0] as i64, (h + pad[0] + pad[1]) as i64) } else { (pad[2] as i64, (wd + pad[2] + pad[3]) as i64) };
+                let mut probes: Vec<(i64, i64, i64)> = Vec::new();                    // (window, tap, coordinate read; -1: padding)
+                'off_axis: for other in sample_axis(n_other) {
+                    for tap in 0..n_other_tap {
+                        probes.clear();
+                        for o in sample_axis(n_out as u64) {
+                            for t in 0..n_tap as u64 {
+                                let a = if rows { probe(0, 0, o, other, 0, t, tap)? } else { probe(0, 0, other, o, 0, tap, t)? };
+                                probes.push((o as i64, t as i64, match a { Some((cls, idx)) if cls == x => idx[if rows { 2 } else { 3 }] as i64, _ => -1 }));
+                            }
                         }
+                        if probes.iter().any(|p| p.2 >= 0) { break 'off_axis; }
                     }
                 }
-                None
+                if !probes.iter().any(|p| p.2 >= 0) { return None; }                  // nothing of the image is ever read
+                let explains = |s: i64, d: i64| {
+                    s > 0 && d > 0 && total >= d * (n_tap - 1) + 1 && (total - (d * (n_tap - 1) + 1)) / s + 1 == n_out
+                        && probes.iter().all(|&(o, t, r)| { let at = o * s + t * d - before; if r >= 0 { at == r } else { at < 0 || at >= extent } })
+                };
+                let (mut s, mut d) = (0i64, if n_tap == 1 { 1 } else { 0 });         // 0: not known yet; a single tap never takes its dilation
+                for &(ao, at, ar) in &probes {
+                    for &(bo, bt, br) in &probes {
+                        if ar < 0 || br < 0 { continue; }
+                        if s == 0 && at == bt && bo > ao && (br - ar) % (bo - ao) == 0 { s = (br - ar) / (bo - ao); }
+                        if d == 0 && ao == bo && bt > at && (br - ar) % (bt - at) == 0 { d = (br - ar) / (bt - at); }
+                    }
+                }
+                if s != 0 && d != 0 && explains(s, d) { return Some((s as u64, d as u64)); }
+                let range = |known: i64| if known != 0 { known..=known } else { 1..=total + 1 };      // what is measured stays; the rest is searched
+                range(s).flat_map(|sc| range(d).map(move |dc| (sc, dc))).find(|&(sc, dc)| explains(sc, dc)).map(|(sc, dc)| (sc as u64, dc as u64))
             };
-            let (Some(sh), Some(dh), Some(sw), Some(dw)) = (step(true, true), step(true, false), step(false, true), step(false, false)) else { continue };
+            let (Some((sh, dh)), Some((sw, dw))) = (solve_axis(true), solve_axis(false)) else { continue };
             // the output extent the declared padding gives must be the view's
             let out_extent = |i: u64, before: u64, after: u64, k: u64, s: u64, d: u64| {
                 let (span, padded) = (d * (k - 1) + 1, i + before + after);

@@ -121,3 +121,31 @@ def test_optimizer_updates(g):
                 outs += group
     ms = check_every_match(g, [t.cls for t in outs], ["sgd", "sgd_momentum", "sgd_nesterov", "adamw", "adamw_first_step", "adam", "adam_first_step"])
     assert sorted(m.optim_step for m in ms if m.pattern in (b"adamw", b"adam")) == [6, 6]
+
+
+def test_convolutions_over_random_geometries(g):
+    """A hundred and fifty seeded geometries (sizes, filter shapes, strides, dilations, four-sided paddings): each is recognised, with the
+    geometry it was built with, and computes the graph's value."""
+    rng = np.random.default_rng(5)
+    done = 0
+    while done < 150:
+        n, c, o = (int(v) for v in rng.integers(1, 4, 3))
+        h, w = (int(v) for v in rng.integers(5, 15, 2))
+        kh, kw = (int(v) for v in rng.integers(1, 5, 2))
+        stride, dil = tuple(int(v) for v in rng.integers(1, 4, 2)), tuple(int(v) for v in rng.integers(1, 3, 2))
+        left, right, top, bottom = (int(v) for v in rng.integers(0, 4, 4))
+        oh = (h + top + bottom - dil[0] * (kh - 1) - 1) // stride[0] + 1
+        ow = (w + left + right - dil[1] * (kw - 1) - 1) // stride[1] + 1
+        if h + top + bottom < dil[0] * (kh - 1) + 1 or w + left + right < dil[1] * (kw - 1) + 1:
+            continue
+        x, wt = T.leaf(g, L.F32, (n, c, h, w)), T.leaf(g, L.F32, (o, c, kh, kw))
+        y = x.conv(wt, stride=stride, dilation=dil, padding=(left, right, top, bottom))
+        assert tuple(y.shape) == (n, o, oh, ow)
+        m = next(m for m in check_every_match(g, [y.cls], ["conv"]) if m.outputs[0] == y.cls)
+        d = m.desc.u.conv
+        assert (d.pad_top, d.pad_bottom, d.pad_left, d.pad_right) == (top, bottom, left, right)
+        slack = (h + top + bottom - dil[0] * (kh - 1), w + left + right - dil[1] * (kw - 1))
+        # a single window never takes its stride: the descriptor names the first stride that gives one window
+        assert (d.stride_h, d.stride_w) == tuple(s if e > 1 else max(1, k) for s, e, k in zip(stride, (oh, ow), slack))
+        assert (d.dil_h, d.dil_w) == tuple(s if k > 1 else 1 for s, k in zip(dil, (kh, kw)))
+        done += 1

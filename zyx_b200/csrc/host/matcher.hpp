@@ -1111,26 +1111,54 @@ class Graph {
       auto probe = [&](uint64_t b, uint64_t co, uint64_t oy, uint64_t ox, uint64_t ci, uint64_t kr, uint64_t ks) {
         return trace_element(xe, {b, 0, co, oy, ox, ci, kr, ks});
       };
-      // stride and dilation: the distance between what neighbouring windows / taps read, measured where nothing is padding
-      auto step = [&](bool rows, bool window) -> std::optional<uint64_t> {
-        const uint64_t n_out = rows ? OH : OW, n_tap = rows ? KH : KW;
-        if ((window ? n_out : n_tap) < 2) return 1;                 // a single window or tap: the step is never taken
-        for (uint64_t o : sample_axis(n_out)) for (uint64_t t = 0; t < n_tap; ++t) {
-          const uint64_t o2 = o + (window ? 1 : 0), t2 = t + (window ? 0 : 1);
-          if (o2 >= n_out || t2 >= n_tap) continue;
-          for (uint64_t other : sample_axis(rows ? OW : OH)) {
-            const Origin a = rows ? probe(0, 0, o, other, 0, t, 0) : probe(0, 0, other, o, 0, 0, t);
-            const Origin b = rows ? probe(0, 0, o2, other, 0, t2, 0) : probe(0, 0, other, o2, 0, 0, t2);
-            if (a.zero || b.zero || a.cls != x || b.cls != x) continue;
-            const size_t ax = rows ? 2 : 3;
-            if (b.idx[ax] <= a.idx[ax]) return std::nullopt;
-            return b.idx[ax] - a.idx[ax];
+      // Stride and dilation, measured: along an axis a window o and tap t read coordinate o*stride + t*dilation - pad when that
+      // is inside the image and padding otherwise.  Every (window, tap) pair of the axis is probed (at a window and tap of the OTHER
+      // axis that are themselves inside the image); two windows under one tap give the stride, two taps under one window the
+      // dilation.  Where padding leaves too few probes inside the image for that (an image smaller than its padding), any pair
+      // that explains all probes - inside and outside - and the output extent describes the same convolution: the first one found
+      // is taken.
+      auto solve_axis = [&](bool rows) -> std::optional<std::pair<uint64_t, uint64_t>> {
+        const int64_t n_out = (int64_t)(rows ? OH : OW), n_tap = (int64_t)(rows ? KH : KW), extent = (int64_t)(rows ? H : W);
+        const int64_t before = (int64_t)(rows ? pad[0] : pad[2]), total = extent + (int64_t)(rows ? pad[0] + pad[1] : pad[2] + pad[3]);
+        struct P { int64_t o, t, r; };                               // r < 0: padding
+        std::vector<P> probes;
+        bool any = false;
+        for (uint64_t other : sample_axis(rows ? OW : OH)) {
+          for (uint64_t tap = 0; tap < (rows ? KW : KH) && !any; ++tap) {
+            probes.clear();
+            for (uint64_t o : sample_axis((uint64_t)n_out)) for (int64_t t = 0; t < n_tap; ++t) {
+              const Origin a = rows ? probe(0, 0, o, other, 0, (uint64_t)t, tap) : probe(0, 0, other, o, 0, tap, (uint64_t)t);
+              const bool inside = !a.zero && a.cls == x;
+              probes.push_back({(int64_t)o, t, inside ? (int64_t)a.idx[rows ? 2 : 3] : -1});
+              any = any || inside;
+            }
           }
+          if (any) break;
         }
+        if (!any) return std::nullopt;                               // nothing of the image is ever read
+        auto explains = [&](int64_t s, int64_t d) {
+          if (s <= 0 || d <= 0 || total < d * (n_tap - 1) + 1 || (total - (d * (n_tap - 1) + 1)) / s + 1 != n_out) return false;
+          for (const P& a : probes) {
+            const int64_t at = a.o * s + a.t * d - before;
+            if (a.r >= 0 ? at != a.r : (at >= 0 && at < extent)) return false;
+          }
+          return true;
+        };
+        int64_t s = 0, d = n_tap == 1 ? 1 : 0;                       // 0: not known yet; a single tap never takes its dilation
+        for (const P& a : probes) for (const P& b : probes) {
+          if (a.r < 0 || b.r < 0) continue;
+          if (!s && a.t == b.t && b.o > a.o && (b.r - a.r) % (b.o - a.o) == 0) s = (b.r - a.r) / (b.o - a.o);
+          if (!d && a.o == b.o && b.t > a.t && (b.r - a.r) % (b.t - a.t) == 0) d = (b.r - a.r) / (b.t - a.t);
+        }
+        if (s && d && explains(s, d)) return std::make_pair((uint64_t)s, (uint64_t)d);
+        for (int64_t sc = s ? s : 1; sc <= (s ? s : total + 1); ++sc)      // what is measured stays; the rest is searched
+          for (int64_t dc = d ? d : 1; dc <= (d ? d : total + 1); ++dc)
+            if (explains(sc, dc)) return std::make_pair((uint64_t)sc, (uint64_t)dc);
         return std::nullopt;
       };
-      auto sh = step(true, true), dh = step(true, false), sw = step(false, true), dw = step(false, false);
-      if (!sh || !dh || !sw || !dw) continue;
+      auto rows_sd = solve_axis(true), cols_sd = solve_axis(false);
+      if (!rows_sd || !cols_sd) continue;
+      const std::optional<uint64_t> sh = rows_sd->first, dh = rows_sd->second, sw = cols_sd->first, dw = cols_sd->second;
       // the output extent the declared padding gives must be the view's
       auto out_extent = [](uint64_t in, uint64_t before, uint64_t after, uint64_t k, uint64_t s, uint64_t d) -> uint64_t {
         const uint64_t span = d * (k - 1) + 1, padded = in + before + after;
