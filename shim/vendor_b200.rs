@@ -184,7 +184,8 @@ impl Graph {
         if pr != out_shape.len() + 1 || axes.len() != 1 || axes[0] != pr - 1 { return None; }
         let k = prod_shape[pr - 1];
         let (ea, eb) = self.binary_of(prod, BOp::Mul).or_else(|| self.binary_of(self.cast_src(prod)?, BOp::Mul))?;
-        let (ea, eb) = (self.expand_of(ea)?, self.expand_of(eb)?);
+        // an operand that already has the product's shape (n = 1 on the left, m = 1 on the right) is not expanded (tensor/mod.rs:3099-3107)
+        let (ea, eb) = (self.expand_of(ea).unwrap_or(ea), self.expand_of(eb).unwrap_or(eb));
         let (a3, b3) = (self.const_shape(ea)?, self.const_shape(eb)?);
         let batch_dims = &out_shape[..out_shape.len() - 2];
         let want_a: Vec<Dim> = batch_dims.iter().copied().chain([m, 1, k]).collect();

@@ -149,3 +149,44 @@ def test_convolutions_over_random_geometries(g):
         assert (d.stride_h, d.stride_w) == tuple(s if e > 1 else max(1, k) for s, e, k in zip(stride, (oh, ow), slack))
         assert (d.dil_h, d.dil_w) == tuple(s if k > 1 else 1 for s, k in zip(dil, (kh, kw)))
         done += 1
+
+
+def test_matmuls_over_random_shapes_and_layouts(g):
+    """Eighty seeded products: rank 2 to 4, either operand stored transposed, the right one shared by the batch or not, with and
+    without a scale, a bias and an activation - whatever is matched must compute the graph's value, and a matmul ends at each."""
+    rng = np.random.default_rng(17)
+    for _ in range(80):
+        m, n, k = (int(v) for v in rng.integers(1, 9, 3))
+        batch = [int(v) for v in rng.integers(1, 4, int(rng.integers(0, 3)))]
+        ta, tb, shared = (bool(rng.integers(0, 2)) for _ in range(3))
+        a = T.leaf(g, L.F32, batch + ([k, m] if ta else [m, k]))
+        b = T.leaf(g, L.F32, ([] if shared else batch) + ([n, k] if tb else [k, n]))
+        out = (a.t() if ta else a).dot(b.t() if tb else b)
+        kind = int(rng.integers(0, 4))
+        if kind == 1:
+            out = out * 0.375
+        elif kind >= 2:
+            out = out + T.leaf(g, L.F32, (n,))
+            out = out.relu() if kind == 3 else out
+        ms = check_every_match(g, [out.cls])
+        assert any(x.pattern.startswith(b"matmul") and x.outputs[0] == out.cls for x in ms), (batch, m, n, k, ta, tb, shared, kind)
+
+
+def test_per_head_views_over_random_shapes(g):
+    """Thirty seeded attention cores outside the fused kernel's shapes (images, heads, lengths, head widths; q, k, v whole tensors
+    or slices of one fused projection): three programs each, every one computing the graph's value."""
+    rng = np.random.default_rng(23)
+    for _ in range(30):
+        nb, h, t = (int(v) for v in rng.integers(1, 4, 3))
+        t *= 3
+        d = int(rng.integers(1, 5)) * 64                          # slices of a fused projection must start on 256-byte boundaries
+        e = h * d
+        if rng.integers(0, 2):
+            q, k, v = (T.leaf(g, L.F32, (nb, t, e)) for _ in range(3))
+        else:
+            q, k, v = T.leaf(g, L.F32, (nb, t, 3 * e)).split([e, e, e], 2)
+        split = lambda z: z.reshape([nb, t, h, d]).permute([0, 2, 1, 3])
+        out = (split(q).dot(split(k).t()) * (d ** -0.5)).softmax().dot(split(v)).permute([0, 2, 1, 3]).reshape([nb, t, e])
+        ms = check_every_match(g, [out.cls], ["softmax"])
+        assert any(x.pattern.startswith(b"matmul_nn") and x.outputs[0] == out.cls and x.desc.u.gemm.ldc == (e if h > 1 or nb > 1 else x.desc.u.gemm.ldc)
+                   for x in ms), (nb, h, t, d)

@@ -288,8 +288,10 @@ class Graph {
     ClassId prod = red->x;
     auto mul = binary(prod, B_MUL);
     if (!mul) { auto c = cast_src(prod); if (!c || !(mul = binary(*c, B_MUL))) return std::nullopt; }   // the accumulator cast
-    auto ea = expand_src(mul->first), eb = expand_src(mul->second);
-    if (!ea || !eb) return std::nullopt;
+    // an operand that already has the product's shape (n = 1 on the left, m = 1 on the right) is not expanded (tensor/mod.rs:3099-3107)
+    std::optional<ClassId> ea = expand_src(mul->first), eb = expand_src(mul->second);
+    if (!ea) ea = mul->first;
+    if (!eb) eb = mul->second;
     const auto a3 = shape(*ea), b3 = shape(*eb);
     std::vector<uint64_t> batch_dims(out_shape.begin(), out_shape.end() - 2);
     std::vector<uint64_t> want_a = batch_dims; want_a.insert(want_a.end(), {m, 1, k});
