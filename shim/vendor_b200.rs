@@ -420,8 +420,10 @@ impl Graph {
         let (mut c, mut weight, mut bias) = (cid, None, None);
         for (op, slot) in [(BOp::Add, &mut bias), (BOp::Mul, &mut weight)] {
             if let Some((x, p)) = self.binary_of(c, op) {
-                let src = self.unbroadcast(p);
-                if self.expand_of(p).is_some() && self.const_shape(src).as_deref() == Some(&[cols][..]) && self.const_value(src).is_none() { *slot = Some(src); c = x; }
+                // (a rank-1 input meets its parameters unexpanded)
+                let rank1 = self.const_shape(cid)?.len() == 1;
+                let src = if self.expand_of(p).is_some() { self.unbroadcast(p) } else { self.canon(p) };
+                if (self.expand_of(p).is_some() || rank1) && self.const_shape(src).as_deref() == Some(&[cols][..]) && self.const_value(src).is_none() { *slot = Some(src); c = x; }
             }
         }
         let (centred, denom) = self.binary_of(c, BOp::Div)?;
@@ -453,6 +455,7 @@ impl Graph {
         if !self.same(d0, d1) { return None; }
         let (y, t) = self.binary_of(d0, BOp::Sub)?;
         let (y, t) = (self.canon(y), self.canon(t));
+        if self.expand_of(y).is_some() || self.expand_of(t).is_some() { return None; }      // whole tensors: x - mean(x) over a rank-1 x is the variance's business
         let f32s = [y, t, cid].iter().all(|&c| self.dtype(c) == DType::F32);
         if !f32s || self.const_shape(y)? != xs || self.const_shape(t)? != xs { return None; }
         Some(self.row_match("mse_loss", self.row_desc(RR_MSE, y)?, vec![y, t], cid))

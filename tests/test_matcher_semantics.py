@@ -14,7 +14,7 @@ from tests.zyx_trace import (LayerNorm, Linear, T, TransformerEncoderLayer, adam
 from zyx_b200 import _lib as L
 
 
-def check_every_match(g, outputs, expect_patterns=()):
+def check_every_match(g, outputs, expect_patterns=(), tol=2e-6):
     ms = g.match(outputs)
     assert ms, "nothing matched"
     for m in ms:
@@ -24,7 +24,7 @@ def check_every_match(g, outputs, expect_patterns=()):
             want = np.asarray(g.vals[cls], np.float64).reshape(-1)
             scale = max(float(np.abs(want).max()), 1e-30)
             err = float(np.abs(flat - want).max()) / scale
-            assert flat.shape == want.shape and err <= 2e-6, (m.pattern, cls, err)      # constants pass through f32 descriptor fields
+            assert flat.shape == want.shape and err <= tol, (m.pattern, cls, err)       # constants pass through f32 descriptor fields
     seen = {m.pattern.decode() for m in ms}
     assert set(expect_patterns) <= seen, sorted(seen)
     return ms
@@ -190,3 +190,47 @@ def test_per_head_views_over_random_shapes(g):
         ms = check_every_match(g, [out.cls], ["softmax"])
         assert any(x.pattern.startswith(b"matmul_nn") and x.outputs[0] == out.cls and x.desc.u.gemm.ldc == (e if h > 1 or nb > 1 else x.desc.u.gemm.ldc)
                    for x in ms), (nb, h, t, d)
+
+
+def test_row_programs_over_random_shapes(g):
+    """Sixty seeded tensors of rank 1 to 4: every reduction (with and without keepdim), softmax, ln_softmax and both layer norms
+    end in a row program that computes the graph's value."""
+    rng = np.random.default_rng(29)
+    for _ in range(60):
+        shape = [int(v) for v in rng.integers(1, 6, int(rng.integers(1, 5)))]
+        shape[-1] = int(rng.integers(2, 12))
+        x = T.leaf(g, L.F32, shape)
+        keep = bool(rng.integers(0, 2))
+        outs = {"sum": x.sum([-1], keepdim=keep), "max": x.max([-1], keepdim=keep), "min": x.min([-1], keepdim=keep),
+                "mean": x.mean([-1], keepdim=keep), "var": x.var([-1], keepdim=keep, correction=int(rng.integers(0, 2))),
+                "std": x.std([-1], keepdim=keep), "softmax": x.softmax(), "ln_softmax": x.ln_softmax(),
+                "layernorm": LayerNorm(g, L.F32, shape[-1], eps=1e-5, weight=bool(rng.integers(0, 2)), bias=bool(rng.integers(0, 2))).forward(x)}
+        ms = check_every_match(g, [t.cls for t in outs.values()])
+        at = {m.outputs[0]: m.pattern.decode() for m in ms}
+        assert {name: at.get(t.cls) for name, t in outs.items()} == {name: name for name in outs}, shape
+
+
+def test_optimizer_updates_over_random_hyper_parameters(g):
+    """Forty seeded updates: SGD in all its forms, Adam and AdamW at random steps, random learning rates, decays and momenta."""
+    rng = np.random.default_rng(31)
+    for _ in range(40):
+        g.positive = False
+        p, gr = T.leaf(g, L.F32, (5, 3)), T.leaf(g, L.F32, (5, 3))
+        lr, wd = float(rng.uniform(1e-3, 0.1)), float(rng.choice([0.0, rng.uniform(0.001, 0.1)]))
+        form = int(rng.integers(0, 3))
+        if form == 0:
+            mom = float(rng.choice([0.0, rng.uniform(0.5, 0.99)]))
+            bufs = [T.leaf(g, L.F32, (5, 3))] if mom != 0.0 else None
+            res = sgd_update([p], [gr], lr, weight_decay=wd, momentum=mom, dampening=float(rng.choice([0.0, 0.2])), nesterov=bool(rng.integers(0, 2)), bufs=bufs)
+            outs = res[0] + res[1] if mom != 0.0 else res
+        else:
+            step = int(rng.integers(1, 40))
+            m = [T.leaf(g, L.F32, (5, 3))] if step > 1 else None
+            g.positive = True
+            v = [T.leaf(g, L.F32, (5, 3))] if step > 1 else None
+            update = adamw_update if form == 1 else adam_update
+            outs = [t for group in update([p], [gr], m, v, step, lr=lr, betas=(float(rng.uniform(0.7, 0.95)), float(rng.uniform(0.9, 0.999))),
+                                          eps=1e-7, weight_decay=wd) for t in group]
+        # beta2 as an f32 descriptor field: 1 - beta2^t carries its rounding several times over
+        ms = check_every_match(g, [t.cls for t in outs], tol=1e-4)
+        assert any(x.desc.kind == L.KIND_OPTIM for x in ms), (form, lr, wd)

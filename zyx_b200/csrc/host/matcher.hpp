@@ -607,8 +607,8 @@ class Graph {
     ClassId c = cid, weight = NONE, bias = NONE;
     auto affine = [&](int bop, ClassId& param) {
       auto b = binary(c, bop);
-      if (!b || !expand_src(b->second)) return;
-      const ClassId src = unbroadcast(b->second);
+      if (!b || (!expand_src(b->second) && shape(cid).size() != 1)) return;     // (a rank-1 input meets its parameters unexpanded)
+      const ClassId src = expand_src(b->second) ? unbroadcast(b->second) : canon(b->second);
       if (shape(src).size() == 1 && shape(src)[0] == shape(cid).back() && !const_value(src)) { param = src; c = b->first; }
     };
     affine(B_ADD, bias);
@@ -728,6 +728,7 @@ class Graph {
     auto sub = binary(mul->first, B_SUB);
     if (!sub) return std::nullopt;
     const ClassId y = canon(sub->first), t = canon(sub->second);
+    if (expand_src(y) || expand_src(t)) return std::nullopt;          // whole tensors: x - mean(x) over a rank-1 x is the variance's business
     if (dtype(y) != ZYXB_F32 || dtype(t) != ZYXB_F32 || dtype(cid) != ZYXB_F32 || shape(y) != xs || shape(t) != xs) return std::nullopt;
     Match m; m.pattern = "mse_loss"; m.desc = row_desc(ZYXB_RR_MSE, ZYXB_F32, xs); m.inputs = {y, t}; m.outputs = {cid};
     return m;
