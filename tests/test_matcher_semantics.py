@@ -234,3 +234,16 @@ def test_optimizer_updates_over_random_hyper_parameters(g):
         # beta2 as an f32 descriptor field: 1 - beta2^t carries its rounding several times over
         ms = check_every_match(g, [t.cls for t in outs], tol=1e-4)
         assert any(x.desc.kind == L.KIND_OPTIM for x in ms), (form, lr, wd)
+
+
+def test_cross_entropy_over_random_shapes(g):
+    """Twenty seeded (samples, classes) pairs, square ones among them: the loss program reads the labels along the samples."""
+    rng = np.random.default_rng(37)
+    for i in range(20):
+        n = int(rng.integers(1, 12))
+        c = n if i % 4 == 0 else int(rng.integers(2, 12))
+        g.int_high = c
+        loss, per = T.leaf(g, L.F32, (n, c)).cross_entropy(T.leaf(g, L.I32, (n,)))
+        ms = check_every_match(g, [loss.cls], ["cross_entropy"])
+        m = next(x for x in ms if x.pattern == b"cross_entropy")
+        assert list(m.outputs[:2]) == [per.cls, loss.cls] and (m.desc.u.rowreduce.rows, m.desc.u.rowreduce.cols) == (n, c)
