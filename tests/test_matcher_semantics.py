@@ -247,3 +247,23 @@ def test_cross_entropy_over_random_shapes(g):
         ms = check_every_match(g, [loss.cls], ["cross_entropy"])
         m = next(x for x in ms if x.pattern == b"cross_entropy")
         assert list(m.outputs[:2]) == [per.cls, loss.cls] and (m.desc.u.rowreduce.rows, m.desc.u.rowreduce.cols) == (n, c)
+
+
+def test_random_elementwise_expressions_are_covered_and_sound(g):
+    """Fifty seeded expression trees over three tensors and a bias vector (additions, products, activations, scales, casts): the
+    on-demand elementwise programs cover each of them completely, and every program computes its class."""
+    rng = np.random.default_rng(41)
+    g.scale = 0.3
+    for _ in range(50):
+        shape = (int(rng.integers(1, 5)), int(rng.integers(2, 7)))
+        pool = [T.leaf(g, L.F32, shape) for _ in range(3)]
+        bias = T.leaf(g, L.F32, (shape[1],))
+        for _ in range(int(rng.integers(1, 7))):
+            a, b = pool[int(rng.integers(0, len(pool)))], pool[int(rng.integers(0, len(pool)))]
+            op = int(rng.integers(0, 12))
+            new = [lambda: a + b, lambda: a - b, lambda: a * b, lambda: a.relu(), lambda: a.gelu(), lambda: a.tanh(), lambda: a.exp(),
+                   lambda: a * 0.75, lambda: a / 1.25, lambda: a + bias, lambda: a.exp() / (a.exp() + 1), lambda: a.cast(L.BF16).cast(L.F32)][op]()
+            pool.append(new)
+        out = pool[-1]
+        check_every_match(g, [out.cls])
+        assert g.uncovered([out.cls]) == [], shape
