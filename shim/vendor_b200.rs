@@ -394,7 +394,7 @@ impl Graph {
     /// softmax (tensor/mod.rs:1457-1461)
     fn match_softmax(&self, cid: ClassId) -> Option<B200Match> {
         let (e, s) = self.binary_of(cid, BOp::Div)?;
-        self.expand_of(s)?;
+        if self.expand_of(s).is_none() && self.const_shape(cid)?.last() != Some(&1) { return None; }      // (one column: nothing to expand)
         if !self.same(self.reduce_last(self.keepdim_src(s), BOp::Add)?, e) { return None; }
         let x = self.shifted(e, Some(UOp::Exp))?;
         Some(self.row_match("softmax", self.row_desc(RR_SOFTMAX, x)?, vec![x], cid))
@@ -402,7 +402,7 @@ impl Graph {
     /// ln_softmax (tensor/mod.rs:1427-1431)
     fn match_ln_softmax(&self, cid: ClassId) -> Option<B200Match> {
         let (m, l) = self.binary_of(cid, BOp::Sub)?;
-        self.expand_of(l)?;
+        if self.expand_of(l).is_none() && self.const_shape(cid)?.last() != Some(&1) { return None; }
         let e = self.reduce_last(self.unary_of(self.keepdim_src(l), UOp::Ln)?, BOp::Add)?;
         if !self.same(self.unary_of(e, UOp::Exp)?, m) { return None; }
         let x = self.shifted(m, None)?;

@@ -553,7 +553,7 @@ class Graph {
   // softmax(x, [-1]) = e / e.sum_keepdim, e = (x - x.max_keepdim).exp()   (tensor/mod.rs:1457-1461)
   std::optional<Match> match_softmax(ClassId cid) const {
     auto div = binary(cid, B_DIV);
-    if (!div || !expand_src(div->second)) return std::nullopt;
+    if (!div || shape(cid).empty() || (!expand_src(div->second) && shape(cid).back() != 1)) return std::nullopt;   // (one column: nothing to expand)
     const ClassId e = div->first;
     auto sum_of = reduce_last(unbroadcast_keepdim(div->second), B_ADD);
     if (!sum_of || !same(*sum_of, e)) return std::nullopt;
@@ -565,7 +565,7 @@ class Graph {
   // ln_softmax(x, [-1]) = m - m.exp().sum_keepdim().ln(), m = x - x.max_keepdim   (tensor/mod.rs:1427-1431)
   std::optional<Match> match_ln_softmax(ClassId cid) const {
     auto sub = binary(cid, B_SUB);
-    if (!sub || !expand_src(sub->second)) return std::nullopt;
+    if (!sub || shape(cid).empty() || (!expand_src(sub->second) && shape(cid).back() != 1)) return std::nullopt;
     const ClassId m = sub->first;
     auto lnarg = unary(unbroadcast_keepdim(sub->second), U_LN);
     if (!lnarg) return std::nullopt;
