@@ -151,7 +151,8 @@ def test_convolutions_over_random_geometries(g):
         done += 1
 
 
-def test_matmuls_over_random_shapes_and_layouts(g):
+@pytest.mark.parametrize("dtype", [L.F32, L.BF16], ids=["f32", "bf16"])
+def test_matmuls_over_random_shapes_and_layouts(g, dtype):
     """Eighty seeded products: rank 2 to 4, either operand stored transposed, the right one shared by the batch or not, with and
     without a scale, a bias and an activation - whatever is matched must compute the graph's value, and a matmul ends at each."""
     rng = np.random.default_rng(17)
@@ -159,32 +160,33 @@ def test_matmuls_over_random_shapes_and_layouts(g):
         m, n, k = (int(v) for v in rng.integers(1, 9, 3))
         batch = [int(v) for v in rng.integers(1, 4, int(rng.integers(0, 3)))]
         ta, tb, shared = (bool(rng.integers(0, 2)) for _ in range(3))
-        a = T.leaf(g, L.F32, batch + ([k, m] if ta else [m, k]))
-        b = T.leaf(g, L.F32, ([] if shared else batch) + ([n, k] if tb else [k, n]))
+        a = T.leaf(g, dtype, batch + ([k, m] if ta else [m, k]))
+        b = T.leaf(g, dtype, ([] if shared else batch) + ([n, k] if tb else [k, n]))
         out = (a.t() if ta else a).dot(b.t() if tb else b)
         kind = int(rng.integers(0, 4))
         if kind == 1:
             out = out * 0.375
         elif kind >= 2:
-            out = out + T.leaf(g, L.F32, (n,))
+            out = out + T.leaf(g, dtype, (n,))
             out = out.relu() if kind == 3 else out
         ms = check_every_match(g, [out.cls])
         assert any(x.pattern.startswith(b"matmul") and x.outputs[0] == out.cls for x in ms), (batch, m, n, k, ta, tb, shared, kind)
 
 
-def test_per_head_views_over_random_shapes(g):
+@pytest.mark.parametrize("dtype", [L.F32, L.BF16], ids=["f32", "bf16"])
+def test_per_head_views_over_random_shapes(g, dtype):
     """Thirty seeded attention cores outside the fused kernel's shapes (images, heads, lengths, head widths; q, k, v whole tensors
     or slices of one fused projection): three programs each, every one computing the graph's value."""
     rng = np.random.default_rng(23)
     for _ in range(30):
         nb, h, t = (int(v) for v in rng.integers(1, 4, 3))
         t *= 3
-        d = int(rng.integers(1, 5)) * 64                          # slices of a fused projection must start on 256-byte boundaries
+        d = int(rng.integers(1, 5)) * (64 if dtype == L.F32 else 128)    # slices of a fused projection must start on 256-byte boundaries
         e = h * d
         if rng.integers(0, 2):
-            q, k, v = (T.leaf(g, L.F32, (nb, t, e)) for _ in range(3))
+            q, k, v = (T.leaf(g, dtype, (nb, t, e)) for _ in range(3))
         else:
-            q, k, v = T.leaf(g, L.F32, (nb, t, 3 * e)).split([e, e, e], 2)
+            q, k, v = T.leaf(g, dtype, (nb, t, 3 * e)).split([e, e, e], 2)
         split = lambda z: z.reshape([nb, t, h, d]).permute([0, 2, 1, 3])
         out = (split(q).dot(split(k).t()) * (d ** -0.5)).softmax().dot(split(v)).permute([0, 2, 1, 3]).reshape([nb, t, e])
         ms = check_every_match(g, [out.cls], ["softmax"])
@@ -192,19 +194,20 @@ def test_per_head_views_over_random_shapes(g):
                    for x in ms), (nb, h, t, d)
 
 
-def test_row_programs_over_random_shapes(g):
+@pytest.mark.parametrize("dtype", [L.F32, L.BF16], ids=["f32", "bf16"])
+def test_row_programs_over_random_shapes(g, dtype):
     """Sixty seeded tensors of rank 1 to 4: every reduction (with and without keepdim), softmax, ln_softmax and both layer norms
     end in a row program that computes the graph's value."""
     rng = np.random.default_rng(29)
     for _ in range(60):
         shape = [int(v) for v in rng.integers(1, 6, int(rng.integers(1, 5)))]
         shape[-1] = int(rng.integers(2, 12))
-        x = T.leaf(g, L.F32, shape)
+        x = T.leaf(g, dtype, shape)
         keep = bool(rng.integers(0, 2))
         outs = {"sum": x.sum([-1], keepdim=keep), "max": x.max([-1], keepdim=keep), "min": x.min([-1], keepdim=keep),
                 "mean": x.mean([-1], keepdim=keep), "var": x.var([-1], keepdim=keep, correction=int(rng.integers(0, 2))),
                 "std": x.std([-1], keepdim=keep), "softmax": x.softmax(), "ln_softmax": x.ln_softmax(),
-                "layernorm": LayerNorm(g, L.F32, shape[-1], eps=1e-5, weight=bool(rng.integers(0, 2)), bias=bool(rng.integers(0, 2))).forward(x)}
+                "layernorm": LayerNorm(g, dtype, shape[-1], eps=1e-5, weight=bool(rng.integers(0, 2)), bias=bool(rng.integers(0, 2))).forward(x)}
         ms = check_every_match(g, [t.cls for t in outs.values()])
         at = {m.outputs[0]: m.pattern.decode() for m in ms}
         assert {name: at.get(t.cls) for name, t in outs.items()} == {name: name for name in outs}, shape
@@ -249,27 +252,29 @@ def test_cross_entropy_over_random_shapes(g):
         assert list(m.outputs[:2]) == [per.cls, loss.cls] and (m.desc.u.rowreduce.rows, m.desc.u.rowreduce.cols) == (n, c)
 
 
-def test_random_elementwise_expressions_are_covered_and_sound(g):
+@pytest.mark.parametrize("dtype", [L.F32, L.BF16], ids=["f32", "bf16"])
+def test_random_elementwise_expressions_are_covered_and_sound(g, dtype):
     """Fifty seeded expression trees over three tensors and a bias vector (additions, products, activations, scales, casts): the
     on-demand elementwise programs cover each of them completely, and every program computes its class."""
     rng = np.random.default_rng(41)
     g.scale = 0.3
     for _ in range(50):
         shape = (int(rng.integers(1, 5)), int(rng.integers(2, 7)))
-        pool = [T.leaf(g, L.F32, shape) for _ in range(3)]
-        bias = T.leaf(g, L.F32, (shape[1],))
+        pool = [T.leaf(g, dtype, shape) for _ in range(3)]
+        bias = T.leaf(g, dtype, (shape[1],))
         for _ in range(int(rng.integers(1, 7))):
             a, b = pool[int(rng.integers(0, len(pool)))], pool[int(rng.integers(0, len(pool)))]
             op = int(rng.integers(0, 12))
             new = [lambda: a + b, lambda: a - b, lambda: a * b, lambda: a.relu(), lambda: a.gelu(), lambda: a.tanh(), lambda: a.exp(),
-                   lambda: a * 0.75, lambda: a / 1.25, lambda: a + bias, lambda: a.exp() / (a.exp() + 1), lambda: a.cast(L.BF16).cast(L.F32)][op]()
+                   lambda: a * 0.75, lambda: a / 1.25, lambda: a + bias, lambda: a.exp() / (a.exp() + 1), lambda: a.cast(L.F32 if dtype == L.BF16 else L.BF16).cast(dtype)][op]()
             pool.append(new)
         out = pool[-1]
         check_every_match(g, [out.cls])
         assert g.uncovered([out.cls]) == [], shape
 
 
-def test_random_networks_are_covered_and_sound(g):
+@pytest.mark.parametrize("dtype", [L.F32, L.BF16], ids=["f32", "bf16"])
+def test_random_networks_are_covered_and_sound(g, dtype):
     """Forty seeded stacks of Linear layers (with and without bias and activation), layer norms, residual additions, softmaxes and
     scales on [batch, features] or [batch, tokens, features] inputs, closed by a loss: covered without a leftover, every program
     computing its class."""
@@ -278,22 +283,23 @@ def test_random_networks_are_covered_and_sound(g):
     for _ in range(40):
         lead = [int(rng.integers(1, 5))] + ([int(rng.integers(1, 4))] if rng.integers(0, 2) else [])
         f = int(rng.integers(2, 9))
-        h = T.leaf(g, L.F32, lead + [f])
+        h = T.leaf(g, dtype, lead + [f])
         for _ in range(int(rng.integers(2, 6))):
             op = int(rng.integers(0, 6))
             if op <= 1:
                 f2 = int(rng.integers(1, 9))
-                z = Linear(g, L.F32, f, f2, bias=bool(rng.integers(0, 4))).forward(h)
+                z = Linear(g, dtype, f, f2, bias=bool(rng.integers(0, 4))).forward(h)
                 act = int(rng.integers(0, 3))
                 h, f = (z.relu() if act == 1 else z.gelu() if act == 2 else z), f2
             elif op == 2 and f > 1:
-                h = LayerNorm(g, L.F32, f, weight=bool(rng.integers(0, 2)), bias=bool(rng.integers(0, 2))).forward(h)
+                h = LayerNorm(g, dtype, f, weight=bool(rng.integers(0, 2)), bias=bool(rng.integers(0, 2))).forward(h)
             elif op == 3:
-                h = h + Linear(g, L.F32, f, f).forward(h)
+                h = h + Linear(g, dtype, f, f).forward(h)
             elif op == 4:
                 h = h.softmax()
             else:
                 h = h * 0.5
-        loss = h.mse_loss(T.leaf(g, L.F32, h.shape)) if rng.integers(0, 2) else h.sum([-1])
+        # the loss program is f32: a 16-bit output is cast first, as the training plans do
+        loss = h.cast(L.F32).mse_loss(T.leaf(g, L.F32, h.shape)) if rng.integers(0, 2) else h.sum([-1])
         check_every_match(g, [loss.cls])
         assert g.uncovered([loss.cls]) == [], (lead, f)
