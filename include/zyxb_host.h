@@ -194,7 +194,7 @@ int32_t  zyxb_mgraph_const_value(zyxb_mgraph* g, uint32_t cls, double* out, uint
 
 /* One recognised subgraph: what to hand to zyxb_program_create, and the classes whose buffers are the launch arguments
  * (inputs then outputs, the order Device::launch receives, backend/mod.rs:974).  Patterns: matmul_nn / matmul_nt / matmul_tn / matmul_tt
- * [_batched][_heads][_bias[_relu|_gelu]], conv[_bias], attention, softmax, ln_softmax, layernorm, cross_entropy, mse_loss, sum, max, min, mean, var, std, colsum, sgd, sgd_momentum,
+ * [_batched][_heads][_bias[_relu|_gelu] | _add], conv[_bias], attention, softmax, ln_softmax, layernorm, cross_entropy, mse_loss, sum, max, min, mean, var, std, colsum, sgd, sgd_momentum,
  * sgd_nesterov, adam, adam_first_step, adamw, adamw_first_step; and, for outputs of the graph and inputs of those programs that nothing
  * produces yet, the elementwise programs relu, gelu, tanh, sigmoid, exp, cast, scale, add, sub, mul, bias_add.  An optimizer match covers every parameter of the update (inputs p.., g.. [, m.., v.. |
  * , buf..]; outputs p' [, m', v' | , buf'] per tensor - the program updates where its arguments lie, so the shim's launch copies

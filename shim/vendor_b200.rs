@@ -71,7 +71,7 @@ const RR_SUM: i32 = 0; const RR_MAX: i32 = 1; const RR_MIN: i32 = 2; const RR_ME
 const RR_VAR: i32 = 4; const RR_STD: i32 = 5; const RR_COLSUM: i32 = 13; const RR_CROSS_ENTROPY: i32 = 9;
 const EW_RELU: i32 = 0; const EW_GELU: i32 = 1; const EW_ADD: i32 = 2; const EW_SUB: i32 = 3; const EW_MUL: i32 = 4; const EW_SCALE: i32 = 5;
 const EW_CAST: i32 = 9; const EW_TANH: i32 = 10; const EW_SIGMOID: i32 = 11; const EW_EXP: i32 = 12; const EW_BIAS_ADD: i32 = 13;
-const EPI_NONE: i32 = 0; const EPI_BIAS: i32 = 1; const EPI_BIAS_RELU: i32 = 2; const EPI_BIAS_GELU: i32 = 3;
+const EPI_NONE: i32 = 0; const EPI_BIAS: i32 = 1; const EPI_BIAS_RELU: i32 = 2; const EPI_BIAS_GELU: i32 = 3; const EPI_ADD: i32 = 6;
 const OPT_SGD: i32 = 0; const OPT_ADAM: i32 = 1; const OPT_ADAMW: i32 = 2;
 
 fn near(a: f64, b: f64) -> bool { (a - b).abs() <= 1e-2 * b.abs() }       // constants arrive rounded to the tensor dtype
@@ -324,17 +324,29 @@ impl Graph {
             }
         }
         if act != 0 && bias.is_none() { return None; }
+        // + a whole tensor of the product's shape (a residual): Add{mm, r}, for a single packed matrix without bias
+        let mut residual = None;
+        if bias.is_none() {
+            if let Some((x, y)) = self.binary_of(e, BOp::Add) {
+                for (lhs, rhs) in [(x, y), (y, x)] {
+                    if residual.is_some() || self.const_shape(rhs) != self.const_shape(e) || self.dtype(rhs) != self.dtype(e) { continue; }
+                    if self.expand_of(rhs).is_some() || self.const_value(rhs).is_some() { continue; }
+                    if self.match_matmul_scaled(lhs).is_some_and(|(mm, _)| mm.batch == 1 && mm.heads == 0) { core = lhs; residual = Some(self.canon(rhs)); }
+                }
+            }
+        }
         let (mm, alpha) = self.match_matmul_scaled(core)?;
         if let Some(b) = bias { if self.dtype(b) != mm.dtype { return None; } }
-        let epi = match (bias.is_some(), act) { (false, _) => EPI_NONE, (true, 2) => EPI_BIAS_GELU, (true, 1) => EPI_BIAS_RELU, _ => EPI_BIAS };
+        let epi = match (residual.is_some(), bias.is_some(), act) { (true, ..) => EPI_ADD, (_, false, _) => EPI_NONE, (_, true, 2) => EPI_BIAS_GELU, (_, true, 1) => EPI_BIAS_RELU, _ => EPI_BIAS };
         let preact = act == 2 && wanted.contains(&e);
         let gemm = Self::gemm_desc(&mm, epi, preact, alpha);
         let mut inputs = vec![mm.a, mm.b];
         inputs.extend(bias);
+        inputs.extend(residual);
         let mut outputs = vec![cid];
         if preact { outputs.push(e); }
         Some(B200Match { pattern: "matmul", inputs, outputs, desc: ZyxbKernelDesc { kind: ZYXB_KIND_GEMM, u: ZyxbDescUnion { gemm } }, numel: Vec::new(), optim_step: 0,
-                         input_offsets: vec![mm.a_view.offset, mm.b_view.offset] })
+                         input_offsets: vec![mm.a_view.offset, mm.b_view.offset] })      // (bias and residual start at 0: missing entries read as 0)
     }
 
     // ---- row kernels ---------------------------------------------------------------------------------------------------------

@@ -129,6 +129,8 @@ def _gemm(d, ins, offsets, out_numel):
         if d.epilogue in (L.EPI_BIAS, L.EPI_BIAS_RELU, L.EPI_BIAS_GELU):
             acc = acc + extra[None, :d.n]
         where = window(d.m, d.n, d.ldc, zo * d.stride_c + zi * d.stride_c_inner)
+        if d.epilogue == L.EPI_ADD:
+            acc = acc + extra[where]
         if pre is not None:
             pre[where] = acc
         c[where] = np.maximum(acc, 0.0) if d.epilogue == L.EPI_BIAS_RELU else _gelu(acc) if d.epilogue == L.EPI_BIAS_GELU else acc

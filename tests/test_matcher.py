@@ -895,3 +895,18 @@ def test_the_mlp_configuration_forward_loss_and_update_are_covered(g):
     assert upd.desc.u.optim.n_tensors == 8 and upd.optim_step == 7 and upd.n_inputs == 32 and upd.n_outputs == 24
     first = next(u for u in used if u.inputs[0] == x.cls)
     assert_same_gemm(first.desc, B.gemm_desc(L.BF16, 8192, 16384, 4096, trans_b=True, epilogue=L.EPI_BIAS_GELU))
+
+
+def test_a_residual_added_to_a_product_without_bias_is_the_add_epilogue(g):
+    """`r + x.dot(w.t())` with no bias in between: the matmul adds the residual as it stores (the epilogue the block plan's
+    backward uses for `dx1 + dz1.W1`); with a bias the addition stays an elementwise program after the biased matmul."""
+    x, r = T.leaf(g, L.BF16, (256, 512)), T.leaf(g, L.BF16, (256, 384))
+    lin = Linear(g, L.BF16, 512, 384, bias=False)
+    y = r + lin.forward(x)
+    m = next(m for m in g.match([y.cls]) if m.outputs[0] == y.cls)
+    assert m.pattern == b"matmul_nt_add" and list(m.inputs[:m.n_inputs]) == [x.cls, lin.weight.cls, r.cls]
+    assert_same_gemm(m.desc, B.gemm_desc(L.BF16, 256, 384, 512, trans_b=True, epilogue=L.EPI_ADD))
+    biased = Linear(g, L.BF16, 512, 384)
+    y2 = r + biased.forward(x)
+    at = {m.outputs[0]: m.pattern for m in g.match([y2.cls])}
+    assert at[y2.cls] == b"add"

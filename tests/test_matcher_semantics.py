@@ -163,14 +163,19 @@ def test_matmuls_over_random_shapes_and_layouts(g, dtype):
         a = T.leaf(g, dtype, batch + ([k, m] if ta else [m, k]))
         b = T.leaf(g, dtype, ([] if shared else batch) + ([n, k] if tb else [k, n]))
         out = (a.t() if ta else a).dot(b.t() if tb else b)
-        kind = int(rng.integers(0, 4))
+        kind = int(rng.integers(0, 5))
         if kind == 1:
             out = out * 0.375
+        elif kind == 4:
+            out = T.leaf(g, dtype, out.shape) + out                 # a residual
         elif kind >= 2:
             out = out + T.leaf(g, dtype, (n,))
             out = out.relu() if kind == 3 else out
         ms = check_every_match(g, [out.cls])
-        assert any(x.pattern.startswith(b"matmul") and x.outputs[0] == out.cls for x in ms), (batch, m, n, k, ta, tb, shared, kind)
+        # (a residual on a batch of products stays an elementwise addition after them)
+        assert any((x.pattern.startswith(b"matmul") or (kind == 4 and x.pattern == b"add")) and x.outputs[0] == out.cls for x in ms), \
+            (batch, m, n, k, ta, tb, shared, kind)
+        assert g.uncovered([out.cls]) == []
 
 
 @pytest.mark.parametrize("dtype", [L.F32, L.BF16], ids=["f32", "bf16"])

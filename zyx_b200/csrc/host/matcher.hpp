@@ -11,7 +11,8 @@
 //                   operand shared by the whole batch folding the batch into the rows; per-head
 //                   views of stored [b, t, h*d] tensors as operands and as the merged result (no [b, h, t, d] copies); the
 //                   accumulator Casts that `sum` puts around the Reduce for 16-bit inputs (tensor/reduce_ops.rs:52-60,143-145);
-//                   a trailing `* const` (attention's 1/sqrt(d)) as alpha; `+ bias`, relu and gelu as epilogues
+//                   a trailing `* const` (attention's 1/sqrt(d)) as alpha; `+ bias`, relu and gelu as epilogues; `+ residual`
+//                   (a whole tensor of the product's shape) on a product without bias
 //   convolution     Tensor::conv with groups = 1 (tensor/mod.rs:2583-2680), recognised by what its pooling view reads
 //   attention       the mask-free core of MultiheadAttention::forward (zyx-nn/src/multi_head_attention.rs:197-226)
 //   row kernels     softmax, ln_softmax (tensor/mod.rs:1427-1461), LayerNorm::forward (zyx-nn/src/layer_norm.rs:95-135),
@@ -468,18 +469,29 @@ class Graph {
       }
     }
     if (act && bias == NONE) return std::nullopt;            // the fused activations exist as bias epilogues only
+    // + a whole tensor of the product's shape (a residual): Add{mm, r}, for a single packed matrix without bias
+    ClassId residual = NONE;
+    if (bias == NONE)
+      if (auto add = binary(e, B_ADD))
+        for (int swap = 0; swap < 2 && residual == NONE; ++swap) {
+          const ClassId lhs = swap ? add->second : add->first, rhs = swap ? add->first : add->second;
+          if (shape(rhs) != shape(e) || dtype(rhs) != dtype(e) || expand_src(rhs) || const_value(rhs)) continue;
+          auto inner = match_matmul_scaled(lhs);
+          if (inner && inner->first.batch == 1 && !inner->first.heads) { core = lhs; residual = canon(rhs); }
+        }
     auto sc = match_matmul_scaled(core);
     if (!sc) return std::nullopt;
     const MatMul& mm = sc->first;
     if (bias != NONE && dtype(bias) != mm.dtype) return std::nullopt;
-    const int epi = bias == NONE ? ZYXB_EPI_NONE : act == 2 ? ZYXB_EPI_BIAS_GELU : act == 1 ? ZYXB_EPI_BIAS_RELU : ZYXB_EPI_BIAS;
+    const int epi = residual != NONE ? ZYXB_EPI_ADD : bias == NONE ? ZYXB_EPI_NONE : act == 2 ? ZYXB_EPI_BIAS_GELU : act == 1 ? ZYXB_EPI_BIAS_RELU : ZYXB_EPI_BIAS;
     const bool preact = act == 2 && wanted.count(e) != 0;
     Match mt;
-    mt.pattern = gemm_name(mm) + (bias != NONE ? "_bias" : "") + (act == 2 ? "_gelu" : act == 1 ? "_relu" : "");
+    mt.pattern = gemm_name(mm) + (bias != NONE ? "_bias" : residual != NONE ? "_add" : "") + (act == 2 ? "_gelu" : act == 1 ? "_relu" : "");
     mt.desc = gemm_desc(mm, epi, preact, sc->second);
     mt.inputs = {mm.a, mm.b};
     mt.input_offsets = {mm.a_view.offset, mm.b_view.offset};
     if (bias != NONE) { mt.inputs.push_back(bias); mt.input_offsets.push_back(0); }
+    if (residual != NONE) { mt.inputs.push_back(residual); mt.input_offsets.push_back(0); }
     mt.outputs = {cid};
     if (preact) mt.outputs.push_back(e);
     return mt;
