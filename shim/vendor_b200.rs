@@ -500,6 +500,7 @@ impl Graph {
             }
         }
         if let Some(x) = self.unary_of(cid, UOp::Exp).filter(|&x| whole(x)) { return program("exp", EW_EXP, vec![x], 0.0, 0, dt); }
+        if let Some(x) = self.unary_of(cid, UOp::Neg).filter(|&x| whole(x)) { return program("scale", EW_SCALE, vec![x], -1.0, 0, dt); }      // -x = x * -1, exactly
         if let Some(x) = self.cast_src(cid).filter(|&x| is_row(self.dtype(x)) && plain(x)) { return program("cast", EW_CAST, vec![x], 0.0, 0, self.dtype(x)); }
         if let Some((x, k)) = self.binary_const(cid, BOp::Mul).filter(|&(x, _)| whole(x)) { return program("scale", EW_SCALE, vec![x], k as f32, 0, dt); }
         // x / const as x * (1 / const): what the reference's own C backend computes under -ffast-math (reciprocal math); dropout

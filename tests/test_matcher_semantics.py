@@ -308,3 +308,12 @@ def test_random_networks_are_covered_and_sound(g, dtype):
         loss = h.cast(L.F32).mse_loss(T.leaf(g, L.F32, h.shape)) if rng.integers(0, 2) else h.sum([-1])
         check_every_match(g, [loss.cls])
         assert g.uncovered([loss.cls]) == [], (lead, f)
+
+
+def test_cross_entropy_against_a_stored_one_hot_matrix_is_covered_by_five_programs(g):
+    """`logits.cross_entropy(one_hot, Mean)` with a float target of the logits' shape has no program of its own: log-softmax, a
+    negation (a scale by -1), the product with the target, the row sums and their mean cover it."""
+    logits, target = T.leaf(g, L.F32, (12, 7)), T.leaf(g, L.F32, (12, 7))
+    loss, _ = logits.cross_entropy(target)
+    ms = check_every_match(g, [loss.cls], ["ln_softmax", "scale", "mul", "sum", "mean"])
+    assert g.uncovered([loss.cls]) == [] and b"cross_entropy" not in {m.pattern for m in ms}

@@ -778,6 +778,7 @@ class Graph {
       if (auto den = binary_const(div->second, B_ADD)) if (same(den->first, div->first) && fabs(den->second - 1.0) <= 1e-6)
         if (auto x = unary(div->first, U_EXP)) if (whole(*x)) return program("sigmoid", ZYXB_EW_SIGMOID, {*x});
     if (auto x = unary(cid, U_EXP)) if (whole(*x)) return program("exp", ZYXB_EW_EXP, {*x});
+    if (auto x = unary(cid, U_NEG)) if (whole(*x)) return program("scale", ZYXB_EW_SCALE, {*x}, -1.0f);      // -x = x * -1, exactly
     if (auto x = cast_src(cid)) if (row_dtype(dtype(*x)) && shape(*x) == cs && !expand_src(*x) && !const_value(*x))
       return program("cast", ZYXB_EW_CAST, {*x}, 0.0f, 0, dtype(*x));
     if (auto sc = binary_const(cid, B_MUL)) if (whole(sc->first)) return program("scale", ZYXB_EW_SCALE, {sc->first}, (float)sc->second);
